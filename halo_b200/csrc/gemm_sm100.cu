@@ -1,0 +1,614 @@
+// bf16 GEMM for sm_100a on the 5th-generation tensor cores.
+//
+//   D[m, n] (+)= alpha * sum_k A(m, k) * B(n, k)
+//
+// One persistent CTA per SM walks a list of 128 x 256 output tiles. Operand tiles are brought
+// into 128-byte-swizzled shared memory by TMA (each CTA fetches its own tiles), a single thread
+// issues tcgen05.mma into one of two 256-column TMEM accumulators, and four epilogue warps drain
+// the other accumulator with tcgen05.ld while the next tile is being multiplied.
+//
+// Either operand may be "K-major" (the reduction index is the contiguous one, the layout of
+// y = x W^T) or "MN-major" (the reduction index walks rows, the layout of dx = dy W and of
+// dW = dy^T x), so forward, data-gradient and weight-gradient products all read the tensors in
+// place. The tile list is either derived from (M, N, K) or read from device memory, which is how
+// the grouped (per-expert) products of an MoE layer run without a host round trip.
+//
+// Replaces what the reference obtains from cuBLAS (F.linear) and from torch's grouped_mm
+// (halo/kernels/grouped_mm.py:30-51, halo/kernels/expert_gemm.py:14-35).
+#include "sm100_common.cuh"
+
+#include <stdio.h>
+
+namespace halo {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 256;
+constexpr int kBlockK = 64;
+constexpr int kStages = 4;
+constexpr int kATileBytes = kBlockM * kBlockK * 2;  // 16 KiB
+constexpr int kBTileBytes = kBlockN * kBlockK * 2;  // 32 KiB
+constexpr int kStageBytes = kATileBytes + kBTileBytes;
+constexpr int kGemmThreads = 192;
+constexpr int kTmemCols = 512;
+
+enum : int {
+    kEpiStoreBf16 = 0,
+    kEpiStoreF32 = 1,
+    kEpiAccumBf16 = 2,
+    kEpiAccumF32 = 3,
+    kEpiSwiglu = 4,  // columns [0,128) are gate, [128,256) are up: C = silu(gate) * up
+};
+
+struct GemmWork {
+    int a_mn;     // A coordinate along M of the tile's first row
+    int a_k;      // A coordinate along the reduction index of the tile's first k-block
+    int b_mn;     // B coordinate along N of columns [0,128) of the tile
+    int b_mn2;    // B coordinate along N of columns [128,256) of the tile
+    int b_k;      // B coordinate along the reduction index
+    int k_iters;  // number of 64-wide k-blocks; 0 writes zeros
+    int c_row;    // first row of C
+    int c_col;    // first column of C (for the SwiGLU epilogue: of the activation output)
+    int m_valid;  // rows of this tile that exist in C
+    int n_valid;  // columns of this tile that exist in C
+    int pad0, pad1;
+};
+
+struct GemmParams {
+    void* C;
+    void* aux;  // SwiGLU epilogue: optional [rows, 2F] copy of the pre-activation (gate | up)
+    long long ldc;
+    long long ld_aux;
+    int epi;
+    float alpha;
+    int M, N, K;  // dense mode
+    int tiles_m, tiles_n;
+    int swiglu_f;            // SwiGLU: F (width of gate and of up); 0 otherwise
+    const GemmWork* list;    // list mode when non-null
+    const int* list_count;   // device count of list entries
+    int* status;
+};
+
+__device__ __forceinline__ bool fetch_work(const GemmParams& p, int idx, int total, GemmWork& w) {
+    if (idx >= total) return false;
+    if (p.list) {
+        w = p.list[idx];
+        return true;
+    }
+    // dense: walk groups of 8 tile-rows, column-first inside a group, so CTAs running together
+    // share A row-blocks and B column-blocks through L2
+    const int group_m = 8;
+    int per_group = group_m * p.tiles_n;
+    int g = idx / per_group;
+    int first_m = g * group_m;
+    int gsz = min(p.tiles_m - first_m, group_m);
+    int in_g = idx - g * per_group;
+    int tm = first_m + in_g % gsz;
+    int tn = in_g / gsz;
+    w.a_mn = tm * kBlockM;
+    w.a_k = 0;
+    w.b_k = 0;
+    w.k_iters = (p.K + kBlockK - 1) / kBlockK;
+    w.c_row = tm * kBlockM;
+    w.m_valid = min(kBlockM, p.M - tm * kBlockM);
+    if (p.epi == kEpiSwiglu) {
+        w.b_mn = tn * 128;
+        w.b_mn2 = p.swiglu_f + tn * 128;
+        w.c_col = tn * 128;
+        w.n_valid = min(128, p.swiglu_f - tn * 128);
+    } else {
+        w.b_mn = tn * kBlockN;
+        w.b_mn2 = tn * kBlockN + 128;
+        w.c_col = tn * kBlockN;
+        w.n_valid = min(kBlockN, p.N - tn * kBlockN);
+    }
+    return true;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bar_full[kStages], bar_empty[kStages], bar_tfull[2], bar_tempty[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&bar_tfull[a]), 1);
+            mbar_init(smem_u32(&bar_tempty[a]), 4);
+        }
+        mbar_fence_init();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    const int total = p.list ? *p.list_count : p.tiles_m * p.tiles_n;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            GemmWork w;
+            for (int idx = blockIdx.x; fetch_work(p, idx, total, w) && !abort_flag;
+                 idx += gridDim.x) {
+                for (int kb = 0; kb < w.k_iters; ++kb) {
+                    if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &abort_flag, p.status))
+                        break;
+                    const uint32_t full = smem_u32(&bar_full[stage]);
+                    const uint32_t sa = tiles_base + stage * kStageBytes;
+                    const uint32_t sb = sa + kATileBytes;
+                    mbar_expect_tx(full, kStageBytes);
+                    if (A_MN) {
+                        tma_load_2d(sa, &tmA, full, w.a_mn, w.a_k + kb * kBlockK);
+                        tma_load_2d(sa + 8192, &tmA, full, w.a_mn + 64, w.a_k + kb * kBlockK);
+                    } else {
+                        tma_load_2d(sa, &tmA, full, w.a_k + kb * kBlockK, w.a_mn);
+                    }
+                    if (B_MN) {
+                        tma_load_2d(sb, &tmB, full, w.b_mn, w.b_k + kb * kBlockK);
+                        tma_load_2d(sb + 8192, &tmB, full, w.b_mn + 64, w.b_k + kb * kBlockK);
+                        tma_load_2d(sb + 16384, &tmB, full, w.b_mn2, w.b_k + kb * kBlockK);
+                        tma_load_2d(sb + 24576, &tmB, full, w.b_mn2 + 64, w.b_k + kb * kBlockK);
+                    } else {
+                        tma_load_2d(sb, &tmB, full, w.b_k + kb * kBlockK, w.b_mn);
+                        tma_load_2d(sb + 16384, &tmB, full, w.b_k + kb * kBlockK, w.b_mn2);
+                    }
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_bf16(kBlockM, kBlockN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            GemmWork w;
+            for (int idx = blockIdx.x; fetch_work(p, idx, total, w) && !abort_flag;
+                 idx += gridDim.x) {
+                if (!mbar_wait(smem_u32(&bar_tempty[acc]), acc_phase ^ 1u, &abort_flag, p.status))
+                    break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * kBlockN;
+                bool ok = true;
+                for (int kb = 0; kb < w.k_iters; ++kb) {
+                    if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag, p.status)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = tiles_base + stage * kStageBytes;
+                    const uint32_t sb = sa + kATileBytes;
+#pragma unroll
+                    for (int k = 0; k < kBlockK / 16; ++k) {
+                        const uint64_t da = A_MN ? make_smem_desc(sa + k * 2048, 8192, 1024)
+                                                 : make_smem_desc(sa + k * 32, 16, 1024);
+                        const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024)
+                                                 : make_smem_desc(sb + k * 32, 16, 1024);
+                        tc_mma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(smem_u32(&bar_empty[stage]));  // stage reusable once these MMAs retire
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                tc_commit(smem_u32(&bar_tfull[acc]));  // accumulator complete
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue: TMEM -> registers -> global ----------------
+        const int quarter = warp & 3;  // TMEM lanes this warp may read: [32*quarter, 32*quarter+32)
+        const int row_in_tile = quarter * 32 + lane;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        GemmWork w;
+        for (int idx = blockIdx.x; fetch_work(p, idx, total, w) && !abort_flag; idx += gridDim.x) {
+            if (!mbar_wait(smem_u32(&bar_tfull[acc]), acc_phase, &abort_flag, p.status)) break;
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + acc * kBlockN + (uint32_t(quarter * 32) << 16);
+            const bool row_ok = row_in_tile < w.m_valid;
+            const long long grow = (long long)w.c_row + row_in_tile;
+            const bool zero = (w.k_iters == 0);
+            if (p.epi == kEpiSwiglu) {
+#pragma unroll 1
+                for (int c = 0; c < 128; c += 32) {
+                    uint32_t g[32], u[32];
+                    tmem_ld_32x32(t_row + c, g);
+                    tmem_ld_32x32(t_row + 128 + c, u);
+                    tmem_ld_wait();
+                    if (row_ok) {
+                        __nv_bfloat16* out =
+                            reinterpret_cast<__nv_bfloat16*>(p.C) + grow * p.ldc + w.c_col + c;
+                        __nv_bfloat16* aux =
+                            p.aux ? reinterpret_cast<__nv_bfloat16*>(p.aux) + grow * p.ld_aux +
+                                        w.c_col + c
+                                  : nullptr;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            if (c + j + 8 <= w.n_valid) {
+                                uint32_t o[4], pg[4], pu[4];
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    // round the pre-activations to bf16 first so a later
+                                    // recomputation from the saved copy sees the same values
+                                    float g0 = zero ? 0.f : __uint_as_float(g[j + 2 * q]) * p.alpha;
+                                    float g1 = zero ? 0.f : __uint_as_float(g[j + 2 * q + 1]) * p.alpha;
+                                    float u0 = zero ? 0.f : __uint_as_float(u[j + 2 * q]) * p.alpha;
+                                    float u1 = zero ? 0.f : __uint_as_float(u[j + 2 * q + 1]) * p.alpha;
+                                    pg[q] = pack_bf16(g0, g1);
+                                    pu[q] = pack_bf16(u0, u1);
+                                    __nv_bfloat162 gb = *reinterpret_cast<__nv_bfloat162*>(&pg[q]);
+                                    __nv_bfloat162 ub = *reinterpret_cast<__nv_bfloat162*>(&pu[q]);
+                                    float2 gf = __bfloat1622float2(gb), uf = __bfloat1622float2(ub);
+                                    float a0 = gf.x / (1.f + __expf(-gf.x)) * uf.x;
+                                    float a1 = gf.y / (1.f + __expf(-gf.y)) * uf.y;
+                                    o[q] = pack_bf16(a0, a1);
+                                }
+                                *reinterpret_cast<uint4*>(out + j) = make_uint4(o[0], o[1], o[2], o[3]);
+                                if (aux) {
+                                    *reinterpret_cast<uint4*>(aux + j) =
+                                        make_uint4(pg[0], pg[1], pg[2], pg[3]);
+                                    *reinterpret_cast<uint4*>(aux + p.swiglu_f + j) =
+                                        make_uint4(pu[0], pu[1], pu[2], pu[3]);
+                                }
+                            }
+                        }
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < kBlockN; c += 32) {
+                    if (c >= w.n_valid) break;  // uniform across the warp
+                    uint32_t r[32];
+                    tmem_ld_32x32(t_row + c, r);
+                    tmem_ld_wait();
+                    if (!row_ok) continue;
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = zero ? 0.f : __uint_as_float(r[j]) * p.alpha;
+                    if (p.epi == kEpiStoreBf16 || p.epi == kEpiAccumBf16) {
+                        __nv_bfloat16* out =
+                            reinterpret_cast<__nv_bfloat16*>(p.C) + grow * p.ldc + w.c_col + c;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            if (c + j + 8 <= w.n_valid) {
+                                if (p.epi == kEpiAccumBf16) {
+                                    uint4 old = *reinterpret_cast<const uint4*>(out + j);
+                                    const __nv_bfloat162* ob =
+                                        reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+                                    for (int q = 0; q < 4; ++q) {
+                                        float2 f = __bfloat1622float2(ob[q]);
+                                        v[j + 2 * q] += f.x;
+                                        v[j + 2 * q + 1] += f.y;
+                                    }
+                                }
+                                *reinterpret_cast<uint4*>(out + j) =
+                                    make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
+                                               pack_bf16(v[j + 4], v[j + 5]),
+                                               pack_bf16(v[j + 6], v[j + 7]));
+                            }
+                        }
+                    } else {
+                        float* out = reinterpret_cast<float*>(p.C) + grow * p.ldc + w.c_col + c;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            if (c + j + 4 <= w.n_valid) {
+                                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                                if (p.epi == kEpiAccumF32) {
+                                    float4 old = *reinterpret_cast<const float4*>(out + j);
+                                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                                }
+                                *reinterpret_cast<float4*>(out + j) = o;
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[acc]));
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1u;
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        // give copies that may still be in flight time to land before the CTA's memory is reused
+        uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) { }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Tile lists for grouped (per-expert) products, built on the device from the expert segments.
+// Segment e occupies rows [seg_start[e], seg_start[e] + seg_rows[e]) of the grouped operand;
+// seg_start is a multiple of 128 and the rows between segments are zero.
+// ---------------------------------------------------------------------------------------------
+
+// Rows grouped along M:  C[rows of e] = A[rows of e] * op(B_e).
+//   b_mn_stride / b_k_stride: how far expert e's weights sit along B's N / reduction coordinate.
+__global__ void plan_grouped_m_kernel(const int* __restrict__ seg_start,
+                                      const int* __restrict__ seg_rows, int num_experts, int n_cols,
+                                      int k_dim, int b_mn_stride, int b_k_stride, int swiglu_f,
+                                      GemmWork* __restrict__ list, int* __restrict__ count,
+                                      int max_items) {
+    __shared__ int base[1025];
+    const int tile_n = swiglu_f ? 128 : kBlockN;
+    const int width = swiglu_f ? swiglu_f : n_cols;
+    const int tiles_n = (width + tile_n - 1) / tile_n;
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int e = 0; e < num_experts; ++e) {
+            base[e] = acc;
+            acc += ((seg_rows[e] + kBlockM - 1) / kBlockM) * tiles_n;
+        }
+        base[num_experts] = acc;
+        *count = min(acc, max_items);
+    }
+    __syncthreads();
+    for (int e = 0; e < num_experts; ++e) {
+        const int rows = seg_rows[e];
+        const int n_items = base[e + 1] - base[e];
+        for (int i = threadIdx.x; i < n_items; i += blockDim.x) {
+            if (base[e] + i >= max_items) continue;
+            const int tm = i / tiles_n, tn = i % tiles_n;
+            GemmWork w;
+            w.a_mn = seg_start[e] + tm * kBlockM;
+            w.a_k = 0;
+            w.b_k = e * b_k_stride;
+            w.k_iters = (k_dim + kBlockK - 1) / kBlockK;
+            w.c_row = w.a_mn;
+            w.m_valid = min(kBlockM, rows - tm * kBlockM);
+            if (swiglu_f) {
+                w.b_mn = e * b_mn_stride + tn * 128;
+                w.b_mn2 = e * b_mn_stride + swiglu_f + tn * 128;
+                w.c_col = tn * 128;
+                w.n_valid = min(128, swiglu_f - tn * 128);
+            } else {
+                w.b_mn = e * b_mn_stride + tn * kBlockN;
+                w.b_mn2 = w.b_mn + 128;
+                w.c_col = tn * kBlockN;
+                w.n_valid = min(kBlockN, n_cols - tn * kBlockN);
+            }
+            w.pad0 = w.pad1 = 0;
+            list[base[e] + i] = w;
+        }
+    }
+}
+
+// Rows grouped along the reduction:  C_e[m, n] = sum_{r in rows of e} A[r, m] * B[r, n]
+// (the per-expert weight gradient dW_e = dY_e^T X_e). C is viewed as [E * m_dim, n_dim].
+__global__ void plan_grouped_k_kernel(const int* __restrict__ seg_start,
+                                      const int* __restrict__ seg_rows, int num_experts, int m_dim,
+                                      int n_dim, GemmWork* __restrict__ list,
+                                      int* __restrict__ count, int max_items) {
+    const int tiles_m = (m_dim + kBlockM - 1) / kBlockM;
+    const int tiles_n = (n_dim + kBlockN - 1) / kBlockN;
+    const int per_e = tiles_m * tiles_n;
+    const int total = min(per_e * num_experts, max_items);
+    if (blockIdx.x == 0 && threadIdx.x == 0) *count = total;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int e = i / per_e, r = i % per_e;
+        const int tm = r / tiles_n, tn = r % tiles_n;
+        GemmWork w;
+        w.a_mn = tm * kBlockM;
+        w.b_mn = tn * kBlockN;
+        w.b_mn2 = w.b_mn + 128;
+        w.a_k = seg_start[e];
+        w.b_k = seg_start[e];
+        w.k_iters = (seg_rows[e] + kBlockK - 1) / kBlockK;
+        w.c_row = e * m_dim + tm * kBlockM;
+        w.c_col = tn * kBlockN;
+        w.m_valid = min(kBlockM, m_dim - tm * kBlockM);
+        w.n_valid = min(kBlockN, n_dim - tn * kBlockN);
+        w.pad0 = w.pad1 = 0;
+        list[i] = w;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+                cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// 2-D bf16 tensor [rows, cols] with `ld` elements between rows; box = 64 columns x box_rows.
+int make_tmap_bf16(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld,
+                   int box_rows) {
+    // The encoder is a driver call: make sure this thread has the device's context current
+    // (a fresh autograd worker thread may not have made any runtime call yet).
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return -4;
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return -1;
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) || (ld % 8) != 0) return -2;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        fprintf(stderr, "halo: cuTensorMapEncodeTiled failed (%d): base=%p rows=%lld cols=%lld ld=%lld box_rows=%d\n",
+                (int)r, base, rows, cols, ld, box_rows);
+        return -3;
+    }
+    return 0;
+}
+
+static int g_num_sms = 0;
+static int num_sms() {
+    if (!g_num_sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (g_num_sms <= 0) g_num_sms = 148;
+    }
+    return g_num_sms;
+}
+
+constexpr int kGemmSmemBytes = kStages * kStageBytes + 1024;
+
+template <bool A_MN, bool B_MN>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
+                       cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_bf16_kernel<A_MN, B_MN>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kGemmSmemBytes) != cudaSuccess)
+            return -10;
+        configured = true;
+    }
+    gemm_bf16_kernel<A_MN, B_MN><<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(ta, tb, p);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+static int dispatch_gemm(int a_mn, int b_mn, const CUtensorMap& ta, const CUtensorMap& tb,
+                         const GemmParams& p, int grid, cudaStream_t s) {
+    if (!a_mn && !b_mn) return launch_gemm<false, false>(ta, tb, p, grid, s);
+    if (!a_mn && b_mn) return launch_gemm<false, true>(ta, tb, p, grid, s);
+    if (a_mn && b_mn) return launch_gemm<true, true>(ta, tb, p, grid, s);
+    return launch_gemm<true, false>(ta, tb, p, grid, s);
+}
+
+}  // namespace halo
+
+using namespace halo;
+
+extern "C" {
+
+// Dense product. A is [a_rows, a_cols] with leading dimension lda, likewise B.
+//   a_mn_major = 0: A is [M, K] (K contiguous);  1: A is [K, M] (M contiguous)
+//   b_mn_major = 0: B is [N, K] (K contiguous);  1: B is [K, N] (N contiguous)
+// epi selects the epilogue (store / accumulate, bf16 / fp32, SwiGLU). For SwiGLU, B is the
+// stacked [2F, K] weight (gate rows then up rows), N must be 2F and C is [M, F].
+int halo_gemm_bf16(const void* A, const void* B, void* C, void* aux, int M, int N, int K,
+                   long long lda, long long ldb, long long ldc, long long ld_aux, int a_mn_major,
+                   int b_mn_major, int epi, float alpha, int* status, void* stream) {
+    if (M <= 0 || N <= 0 || K < 0) return 0;
+    CUtensorMap ta, tb;
+    int rc;
+    if (a_mn_major) rc = make_tmap_bf16(&ta, A, K, M, lda, 64);
+    else rc = make_tmap_bf16(&ta, A, M, K, lda, 128);
+    if (rc) return rc;
+    if (b_mn_major) rc = make_tmap_bf16(&tb, B, K, N, ldb, 64);
+    else rc = make_tmap_bf16(&tb, B, N, K, ldb, 128);
+    if (rc) return rc * 10;
+    GemmParams p{};
+    p.C = C; p.aux = aux; p.ldc = ldc; p.ld_aux = ld_aux; p.epi = epi; p.alpha = alpha;
+    p.M = M; p.N = N; p.K = K;
+    p.tiles_m = (M + kBlockM - 1) / kBlockM;
+    if (epi == kEpiSwiglu) {
+        if (N % 2) return -20;
+        p.swiglu_f = N / 2;
+        p.tiles_n = (p.swiglu_f + 127) / 128;
+    } else {
+        p.swiglu_f = 0;
+        p.tiles_n = (N + kBlockN - 1) / kBlockN;
+    }
+    p.list = nullptr; p.list_count = nullptr; p.status = status;
+    long long tiles = (long long)p.tiles_m * p.tiles_n;
+    int grid = (int)(tiles < num_sms() ? tiles : num_sms());
+    return dispatch_gemm(a_mn_major, b_mn_major, ta, tb, p, grid, (cudaStream_t)stream);
+}
+
+// Product over a device-resident tile list (see plan_grouped_*). The operands are described as
+// plain 2-D tensors; the list carries every coordinate.
+int halo_gemm_bf16_list(const void* A, long long a_rows, long long a_cols, long long lda,
+                        const void* B, long long b_rows, long long b_cols, long long ldb, void* C,
+                        void* aux, long long ldc, long long ld_aux, int a_mn_major, int b_mn_major,
+                        int epi, float alpha, int swiglu_f, const void* list, const int* list_count,
+                        int* status, void* stream) {
+    CUtensorMap ta, tb;
+    int rc = make_tmap_bf16(&ta, A, a_rows, a_cols, lda, a_mn_major ? 64 : 128);
+    if (rc) return rc;
+    rc = make_tmap_bf16(&tb, B, b_rows, b_cols, ldb, b_mn_major ? 64 : 128);
+    if (rc) return rc * 10;
+    GemmParams p{};
+    p.C = C; p.aux = aux; p.ldc = ldc; p.ld_aux = ld_aux; p.epi = epi; p.alpha = alpha;
+    p.swiglu_f = swiglu_f;
+    p.list = reinterpret_cast<const GemmWork*>(list);
+    p.list_count = list_count;
+    p.status = status;
+    return dispatch_gemm(a_mn_major, b_mn_major, ta, tb, p, num_sms(), (cudaStream_t)stream);
+}
+
+int halo_plan_grouped_m(const int* seg_start, const int* seg_rows, int num_experts, int n_cols,
+                        int k_dim, int b_mn_stride, int b_k_stride, int swiglu_f, void* list,
+                        int* count, int max_items, void* stream) {
+    if (num_experts > 1024) return -1;
+    plan_grouped_m_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(
+        seg_start, seg_rows, num_experts, n_cols, k_dim, b_mn_stride, b_k_stride, swiglu_f,
+        reinterpret_cast<GemmWork*>(list), count, max_items);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+int halo_plan_grouped_k(const int* seg_start, const int* seg_rows, int num_experts, int m_dim,
+                        int n_dim, void* list, int* count, int max_items, void* stream) {
+    plan_grouped_k_kernel<<<32, 256, 0, (cudaStream_t)stream>>>(
+        seg_start, seg_rows, num_experts, m_dim, n_dim, reinterpret_cast<GemmWork*>(list), count,
+        max_items);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+int halo_gemm_work_bytes() { return (int)sizeof(GemmWork); }
+
+}  // extern "C"
