@@ -33,6 +33,11 @@ NVCC_FLAGS = [
 ]
 
 
+# Per-file additions: the optimizer's arithmetic is specified without fused multiply-adds so its CPU
+# twin can reproduce it bit for bit.
+EXTRA_FLAGS = {"optim.cu": ["-fmad=false"]}
+
+
 def find_nvcc() -> str:
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(nvcc):
@@ -45,7 +50,7 @@ def _newest_header_mtime() -> float:
 
 
 def _compile_one(nvcc: str, src: Path, obj: Path, verbose: bool) -> str:
-    cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+    cmd = [nvcc, *NVCC_FLAGS, *EXTRA_FLAGS.get(src.name, []), "-c", str(src), "-o", str(obj)]
     if verbose:
         cmd[1:1] = ["-Xptxas", "-v"]
     proc = subprocess.run(cmd, capture_output=True, text=True)

@@ -1,0 +1,789 @@
+// Causal flash attention for packed (variable-length) rows on sm_100a, head_dim 128, grouped-query
+// heads. Forward and backward run on tcgen05 tensor cores with the score tiles in tensor memory:
+//
+//   forward   one CTA per (128-query tile, head): S = Q K^T lands in TMEM, four softmax warps
+//             read it with tcgen05.ld, write P (bf16) into swizzled shared memory, a second MMA
+//             forms P V in TMEM, and the running output is rescaled in registers.
+//   backward  two deterministic kernels (no atomics): one owns a 128-key tile of one kv head and
+//             accumulates dK, dV in TMEM over every query tile / head that sees it; the other owns
+//             a 128-query tile and accumulates dQ in TMEM over its key tiles.
+//
+// Documents are delimited by the tile work list (built from cu_seqlens): a query tile only visits
+// key tiles of its own document, so packed rows never attend across documents.
+// K/V tiles are fetched per CTA with TMA (no cluster broadcast).
+//
+// Stands where the reference calls FlashAttention-4 / FlashAttention-2 varlen kernels
+// (halo/models/attention/selection.py:94-100, 383-462).
+#include "sm100_common.cuh"
+
+#include <stdio.h>
+
+namespace halo {
+
+constexpr int kHd = 128;
+constexpr float kLog2e = 1.4426950408889634f;
+
+int make_tmap_bf16(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld,
+                   int box_rows);  // gemm_sm100.cu
+
+// byte offset of the 16-byte chunk holding column `col` (multiple of 8) of row `row` inside a
+// [rows x 64] bf16 half-tile stored with the 128-byte swizzle
+__device__ __forceinline__ uint32_t swz_off(int row, int col) {
+    return (uint32_t)(row * 128 + ((((col >> 3) ^ row) & 7) << 4));
+}
+
+struct FwdWork {
+    int q0;        // first query row of the tile
+    int kv0;       // first key row the tile may see (its document's first row)
+    int n_kv;      // number of 128-key tiles to visit; the last one is the diagonal tile
+    int q_end;     // one past the document's last row
+};
+
+struct AttnParams {
+    const FwdWork* work;
+    void* O;              // [T, Hq*128] bf16
+    float* lse;           // [Hq, T]
+    long long ldo;
+    long long T;
+    int Hq, Hkv;
+    float scale;          // 1/sqrt(head_dim)
+    int* status;
+};
+
+constexpr int kFwdThreads = 192;
+constexpr int kTileBytes = 128 * 128 * 2;                              // 32 KiB: a 128x128 bf16 tile
+constexpr int kFwdSmem = kTileBytes * (1 + 1 + 2 * 2) + 1024;          // Q, P, 2 x (K, V)
+
+__global__ void __launch_bounds__(kFwdThreads, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bar_q, bar_kv_full[2], bar_kv_empty[2], bar_s_full, bar_p_ready, bar_o_full;
+    __shared__ uint32_t tmem_slot;
+    __shared__ volatile int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sQ = base, sP = base + kTileBytes, sKV = base + 2 * kTileBytes;
+    const int head = blockIdx.x;
+    const int kv_head = head / (p.Hq / p.Hkv);
+    const FwdWork w = p.work[blockIdx.y];
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar_q), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&bar_kv_full[s]), 1);
+            mbar_init(smem_u32(&bar_kv_empty[s]), 1);
+        }
+        mbar_init(smem_u32(&bar_s_full), 1);
+        mbar_init(smem_u32(&bar_p_ready), 128);
+        mbar_init(smem_u32(&bar_o_full), 1);
+        mbar_fence_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(smem_u32(&tmem_slot), 256);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tS = tmem_slot, tO = tmem_slot + 128;
+
+    if (warp == 4) {
+        if (lane == 0) {
+            // ---------------- TMA producer ----------------
+            mbar_expect_tx(smem_u32(&bar_q), kTileBytes);
+            tma_load_2d(sQ, &tmQ, smem_u32(&bar_q), head * kHd, w.q0);
+            tma_load_2d(sQ + 16384, &tmQ, smem_u32(&bar_q), head * kHd + 64, w.q0);
+            for (int j = 0; j < w.n_kv; ++j) {
+                const int st = j & 1;
+                if (!mbar_wait(smem_u32(&bar_kv_empty[st]), ((j >> 1) & 1) ^ 1u, &abort_flag, p.status)) break;
+                const uint32_t full = smem_u32(&bar_kv_full[st]);
+                const uint32_t sK = sKV + st * 2 * kTileBytes, sV = sK + kTileBytes;
+                const int kr = w.kv0 + j * 128;
+                mbar_expect_tx(full, 2 * kTileBytes);
+                tma_load_2d(sK, &tmK, full, kv_head * kHd, kr);
+                tma_load_2d(sK + 16384, &tmK, full, kv_head * kHd + 64, kr);
+                tma_load_2d(sV, &tmV, full, kv_head * kHd, kr);
+                tma_load_2d(sV + 16384, &tmV, full, kv_head * kHd + 64, kr);
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {
+            // ---------------- MMA issuer ----------------
+            constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);   // S = Q K^T
+            constexpr uint32_t idesc_o = make_idesc_bf16(128, 128, 0, 1);   // O = P V  (V is N-major)
+            bool ok = mbar_wait(smem_u32(&bar_q), 0, &abort_flag, p.status);
+            for (int j = 0; ok && j < w.n_kv; ++j) {
+                const int st = j & 1;
+                const uint32_t sK = sKV + st * 2 * kTileBytes, sV = sK + kTileBytes;
+                if (!mbar_wait(smem_u32(&bar_kv_full[st]), (j >> 1) & 1, &abort_flag, p.status)) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
+                    tc_mma_f16(tS, make_smem_desc(sQ + off, 16, 1024), make_smem_desc(sK + off, 16, 1024),
+                               idesc_s, ks != 0);
+                }
+                tc_commit(smem_u32(&bar_s_full));
+                if (!mbar_wait(smem_u32(&bar_p_ready), j & 1, &abort_flag, p.status)) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    // P: K-major A, 16 keys per step; V: N-major B, 16 key rows (2048 bytes) per step
+                    const uint32_t offp = (ks >> 2) * 16384 + (ks & 3) * 32;
+                    tc_mma_f16(tO, make_smem_desc(sP + offp, 16, 1024),
+                               make_smem_desc(sV + ks * 2048, 16384, 1024), idesc_o, ks != 0);
+                }
+                tc_commit(smem_u32(&bar_o_full));
+                tc_commit(smem_u32(&bar_kv_empty[st]));
+            }
+        }
+    } else {
+        // ---------------- softmax / output warps: thread = query row ----------------
+        const int row = warp * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const float c = p.scale * kLog2e;
+        float m = -INFINITY, l = 0.f;
+        float acc[128];
+#pragma unroll
+        for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+        bool ok = true;
+        for (int j = 0; j < w.n_kv; ++j) {
+            if (!mbar_wait(smem_u32(&bar_s_full), j & 1, &abort_flag, p.status)) { ok = false; break; }
+            tc_fence_after();
+            const bool diag = (j == w.n_kv - 1);
+            float mx = m;
+#pragma unroll 1
+            for (int cc = 0; cc < 128; cc += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tS + lane_base + cc, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float s = __uint_as_float(r[i]);
+                    if (!diag || cc + i <= row) mx = fmaxf(mx, s);
+                }
+            }
+            const float alpha = exp2f((m - mx) * c);
+            const float mc = mx * c;
+            float rs = 0.f;
+#pragma unroll 1
+            for (int cc = 0; cc < 128; cc += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tS + lane_base + cc, r);
+                tmem_ld_wait();
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0 = exp2f(__uint_as_float(r[i]) * c - mc);
+                    float p1 = exp2f(__uint_as_float(r[i + 1]) * c - mc);
+                    if (diag) {
+                        if (cc + i > row) p0 = 0.f;
+                        if (cc + i + 1 > row) p1 = 0.f;
+                    }
+                    pk[i >> 1] = pack_bf16(p0, p1);
+                    // sum what the second MMA will actually see
+                    const __nv_bfloat162 pb = *reinterpret_cast<__nv_bfloat162*>(&pk[i >> 1]);
+                    const float2 pf = __bfloat1622float2(pb);
+                    rs += pf.x + pf.y;
+                }
+                const uint32_t half = sP + (cc >> 6) * 16384;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const uint32_t a = half + swz_off(row, (cc & 63) + q * 8);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(pk[4 * q]),
+                                 "r"(pk[4 * q + 1]), "r"(pk[4 * q + 2]), "r"(pk[4 * q + 3])
+                                 : "memory");
+                }
+            }
+            l = l * alpha + rs;
+            m = mx;
+            fence_proxy_async_smem();
+            tc_fence_before();
+            mbar_arrive(smem_u32(&bar_p_ready));
+            if (!mbar_wait(smem_u32(&bar_o_full), j & 1, &abort_flag, p.status)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int cc = 0; cc < 128; cc += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tO + lane_base + cc, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[cc + i] = acc[cc + i] * alpha + __uint_as_float(r[i]);
+            }
+        }
+        const long long grow = (long long)w.q0 + row;
+        if (ok && grow < w.q_end) {
+            const float inv = 1.f / l;
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.O) + grow * p.ldo + head * kHd;
+#pragma unroll
+            for (int i = 0; i < 128; i += 8) {
+                *reinterpret_cast<uint4*>(out + i) =
+                    make_uint4(pack_bf16(acc[i] * inv, acc[i + 1] * inv), pack_bf16(acc[i + 2] * inv, acc[i + 3] * inv),
+                               pack_bf16(acc[i + 4] * inv, acc[i + 5] * inv), pack_bf16(acc[i + 6] * inv, acc[i + 7] * inv));
+            }
+            p.lse[(long long)head * p.T + grow] = m * p.scale + logf(l);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) { }
+        __syncthreads();
+    }
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem_slot, 256);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// backward
+// ---------------------------------------------------------------------------------------------
+// delta[h, t] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (t, h)
+__global__ void __launch_bounds__(256)
+attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
+                  float* __restrict__ delta, long long T, int Hq, long long ld_do, long long ld_o) {
+    const int lane = threadIdx.x & 31;
+    const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (wid >= T * Hq) return;
+    const long long t = wid / Hq;
+    const int h = (int)(wid % Hq);
+    const uint2 a = *reinterpret_cast<const uint2*>(dO + t * ld_do + h * kHd + lane * 4);
+    const uint2 b = *reinterpret_cast<const uint2*>(O + t * ld_o + h * kHd + lane * 4);
+    const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&b);
+    float s = 0.f;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+        const float2 x = __bfloat1622float2(ah[q]), y = __bfloat1622float2(bh[q]);
+        s += x.x * y.x + x.y * y.y;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) delta[(long long)h * T + t] = s;
+}
+
+struct BwdKvWork {
+    int kv0;      // first key row of the 128-key tile
+    int q_begin;  // first query row that can see it (== kv0)
+    int n_q;      // number of 64-query sub-tiles to visit, starting at q_begin
+    int q_end;    // one past the document's last row
+};
+
+struct BwdParams {
+    const void* work;
+    const float* lse;    // [Hq, T]
+    const float* delta;  // [Hq, T]
+    void* dQ;            // [T, ld_dq]
+    void* dK;
+    void* dV;
+    long long ld_dq, ld_dk, ld_dv;
+    long long T;
+    int Hq, Hkv;
+    float scale;
+    int* status;
+};
+
+constexpr int kBwdThreads = 192;
+constexpr int kHalfTile = 64 * 128 * 2;  // 16 KiB: a 64 x 128 bf16 tile
+// K, V (32 KiB each), P^T and dS^T (128 x 64, 16 KiB each), 2 stages of (Q, dO) 64 x 128
+constexpr int kBwdKvSmem = 2 * kTileBytes + 2 * kHalfTile + 2 * 2 * kHalfTile + 1024;
+
+// One CTA per (128-key tile, kv head). For every q head of the group and every 64-query sub-tile:
+//   S^T = K Q^T, dP^T = V dO^T  (TMEM, 64 columns each)
+//   P^T = exp(S^T * scale - lse),  dS^T = P^T * (dP^T - delta) * scale
+//   dV += P^T dO,  dK += dS^T Q   (TMEM accumulators, 128 columns each)
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                     const BwdParams p) {
+    if (status_poisoned(p.status)) return;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bar_kv, bar_q_full[2], bar_q_empty[2], bar_s_full, bar_p_ready, bar_ds_ready,
+        bar_dv_done, bar_acc_done, bar_stats;
+    __shared__ uint32_t tmem_slot;
+    __shared__ volatile int abort_flag;
+    __shared__ float s_lse[2][64], s_delta[2][64];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sK = base, sV = base + kTileBytes, sPT = base + 2 * kTileBytes,
+                   sDS = sPT + kHalfTile, sQdO = sDS + kHalfTile;
+    const int kv_head = blockIdx.x;
+    const int group = p.Hq / p.Hkv;
+    const BwdKvWork w = reinterpret_cast<const BwdKvWork*>(p.work)[blockIdx.y];
+    const int n_iter = w.n_q * group;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar_kv), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&bar_q_full[s]), 1);
+            mbar_init(smem_u32(&bar_q_empty[s]), 1);
+        }
+        mbar_init(smem_u32(&bar_s_full), 1);
+        mbar_init(smem_u32(&bar_p_ready), 128);
+        mbar_init(smem_u32(&bar_ds_ready), 128);
+        mbar_init(smem_u32(&bar_dv_done), 1);
+        mbar_init(smem_u32(&bar_acc_done), 1);
+        mbar_init(smem_u32(&bar_stats), 64);
+        mbar_fence_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(smem_u32(&tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tS = tmem_slot, tDP = tmem_slot + 64, tDV = tmem_slot + 128, tDK = tmem_slot + 256;
+
+    if (warp == 4) {
+        if (lane == 0) {
+            mbar_expect_tx(smem_u32(&bar_kv), 2 * kTileBytes);
+            tma_load_2d(sK, &tmK, smem_u32(&bar_kv), kv_head * kHd, w.kv0);
+            tma_load_2d(sK + 16384, &tmK, smem_u32(&bar_kv), kv_head * kHd + 64, w.kv0);
+            tma_load_2d(sV, &tmV, smem_u32(&bar_kv), kv_head * kHd, w.kv0);
+            tma_load_2d(sV + 16384, &tmV, smem_u32(&bar_kv), kv_head * kHd + 64, w.kv0);
+            for (int it = 0; it < n_iter; ++it) {
+                const int st = it & 1;
+                if (!mbar_wait(smem_u32(&bar_q_empty[st]), ((it >> 1) & 1) ^ 1u, &abort_flag, p.status)) break;
+                const int h = kv_head * group + it % group;
+                const int qr = w.q_begin + (it / group) * 64;
+                const uint32_t full = smem_u32(&bar_q_full[st]);
+                const uint32_t sQ = sQdO + st * 2 * kHalfTile, sdO = sQ + kHalfTile;
+                mbar_expect_tx(full, 2 * kHalfTile);
+                // 64 rows x 128 columns as two 64 x 64 boxes, 8 KiB each
+                tma_load_2d(sQ, &tmQ, full, h * kHd, qr);
+                tma_load_2d(sQ + 8192, &tmQ, full, h * kHd + 64, qr);
+                tma_load_2d(sdO, &tmdO, full, h * kHd, qr);
+                tma_load_2d(sdO + 8192, &tmdO, full, h * kHd + 64, qr);
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_st = make_idesc_bf16(128, 64, 0, 0);   // [keys x q] = K Q^T, V dO^T
+            constexpr uint32_t idesc_acc = make_idesc_bf16(128, 128, 0, 1); // [keys x hd] = P^T dO, dS^T Q
+            bool ok = mbar_wait(smem_u32(&bar_kv), 0, &abort_flag, p.status);
+            for (int it = 0; ok && it < n_iter; ++it) {
+                const int st = it & 1;
+                const uint32_t sQ = sQdO + st * 2 * kHalfTile, sdO = sQ + kHalfTile;
+                if (!mbar_wait(smem_u32(&bar_q_full[st]), (it >> 1) & 1, &abort_flag, p.status)) break;
+                // the previous iteration's dK product must have drained dS^T / S before they are reused
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t offa = (ks >> 2) * 16384 + (ks & 3) * 32;  // K / V: 128-row halves
+                    const uint32_t offb = (ks >> 2) * 8192 + (ks & 3) * 32;   // Q / dO: 64-row halves
+                    tc_mma_f16(tS, make_smem_desc(sK + offa, 16, 1024), make_smem_desc(sQ + offb, 16, 1024),
+                               idesc_st, ks != 0);
+                }
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t offa = (ks >> 2) * 16384 + (ks & 3) * 32;
+                    const uint32_t offb = (ks >> 2) * 8192 + (ks & 3) * 32;
+                    tc_mma_f16(tDP, make_smem_desc(sV + offa, 16, 1024), make_smem_desc(sdO + offb, 16, 1024),
+                               idesc_st, ks != 0);
+                }
+                tc_commit(smem_u32(&bar_s_full));
+                if (!mbar_wait(smem_u32(&bar_p_ready), it & 1, &abort_flag, p.status)) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    // A = P^T [128 keys x 64 q] K-major; B = dO [64 q x 128 hd] N-major (two 64-wide halves)
+                    tc_mma_f16(tDV, make_smem_desc(sPT + ks * 32, 16, 1024),
+                               make_smem_desc(sdO + ks * 2048, 8192, 1024), idesc_acc, (it | ks) != 0);
+                }
+                tc_commit(smem_u32(&bar_dv_done));
+                if (!mbar_wait(smem_u32(&bar_ds_ready), it & 1, &abort_flag, p.status)) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    tc_mma_f16(tDK, make_smem_desc(sDS + ks * 32, 16, 1024),
+                               make_smem_desc(sQ + ks * 2048, 8192, 1024), idesc_acc, (it | ks) != 0);
+                }
+                tc_commit(smem_u32(&bar_q_empty[st]));
+                if (it == n_iter - 1) tc_commit(smem_u32(&bar_acc_done));
+            }
+        }
+    } else {
+        // thread = key row of the tile
+        const int key = warp * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const float c = p.scale * kLog2e;
+        const long long key_abs = (long long)w.kv0 + key;
+        bool ok = true;
+        for (int it = 0; it < n_iter; ++it) {
+            const int h = kv_head * group + it % group;
+            const int qr = w.q_begin + (it / group) * 64;
+            // stage the row statistics of this query sub-tile
+            if (threadIdx.x < 64) {
+                const long long qa = (long long)qr + threadIdx.x;
+                const bool in = qa < w.q_end;
+                s_lse[it & 1][threadIdx.x] = in ? p.lse[(long long)h * p.T + qa] * kLog2e : INFINITY;
+                s_delta[it & 1][threadIdx.x] = in ? p.delta[(long long)h * p.T + qa] : 0.f;
+                mbar_arrive(smem_u32(&bar_stats));
+            }
+            if (!mbar_wait(smem_u32(&bar_stats), it & 1, &abort_flag, p.status)) { ok = false; break; }
+            if (!mbar_wait(smem_u32(&bar_s_full), it & 1, &abort_flag, p.status)) { ok = false; break; }
+            tc_fence_after();
+            const bool need_mask = (qr < w.kv0 + 128);
+            float pv[64];
+#pragma unroll
+            for (int cc = 0; cc < 64; cc += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tS + lane_base + cc, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float pe = exp2f(__uint_as_float(r[i]) * c - s_lse[it & 1][cc + i]);
+                    if (need_mask && (long long)qr + cc + i < key_abs) pe = 0.f;
+                    pv[cc + i] = pe;
+                }
+            }
+            // P^T was released by the wait on bar_dv_done that ended the previous iteration; dS^T by
+            // bar_s_full, whose commit follows (and therefore covers) the previous dK product.
+            // P^T -> shared (bf16, K-major A operand: [128 keys x 64 q], one 128-byte row per key)
+#pragma unroll
+            for (int q8 = 0; q8 < 8; ++q8) {
+                const uint32_t a = sPT + swz_off(key, q8 * 8);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a),
+                             "r"(pack_bf16(pv[q8 * 8], pv[q8 * 8 + 1])), "r"(pack_bf16(pv[q8 * 8 + 2], pv[q8 * 8 + 3])),
+                             "r"(pack_bf16(pv[q8 * 8 + 4], pv[q8 * 8 + 5])), "r"(pack_bf16(pv[q8 * 8 + 6], pv[q8 * 8 + 7]))
+                             : "memory");
+            }
+            fence_proxy_async_smem();
+            tc_fence_before();
+            mbar_arrive(smem_u32(&bar_p_ready));
+            // dS^T = P^T * (dP^T - delta) * scale
+#pragma unroll
+            for (int cc = 0; cc < 64; cc += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tDP + lane_base + cc, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    pv[cc + i] = pv[cc + i] * (__uint_as_float(r[i]) - s_delta[it & 1][cc + i]) * p.scale;
+            }
+#pragma unroll
+            for (int q8 = 0; q8 < 8; ++q8) {
+                const uint32_t a = sDS + swz_off(key, q8 * 8);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a),
+                             "r"(pack_bf16(pv[q8 * 8], pv[q8 * 8 + 1])), "r"(pack_bf16(pv[q8 * 8 + 2], pv[q8 * 8 + 3])),
+                             "r"(pack_bf16(pv[q8 * 8 + 4], pv[q8 * 8 + 5])), "r"(pack_bf16(pv[q8 * 8 + 6], pv[q8 * 8 + 7]))
+                             : "memory");
+            }
+            fence_proxy_async_smem();
+            tc_fence_before();
+            mbar_arrive(smem_u32(&bar_ds_ready));
+            // P^T may be overwritten next iteration only after the dV product has read it
+            if (!mbar_wait(smem_u32(&bar_dv_done), it & 1, &abort_flag, p.status)) { ok = false; break; }
+        }
+        if (ok && mbar_wait(smem_u32(&bar_acc_done), 0, &abort_flag, p.status)) {
+            tc_fence_after();
+            // tcgen05.ld is warp-collective: every lane issues the loads, only the stores are guarded
+            const bool live = key_abs < w.q_end;
+            __nv_bfloat16* dk = reinterpret_cast<__nv_bfloat16*>(p.dK) + key_abs * p.ld_dk + kv_head * kHd;
+            __nv_bfloat16* dv = reinterpret_cast<__nv_bfloat16*>(p.dV) + key_abs * p.ld_dv + kv_head * kHd;
+#pragma unroll 1
+            for (int cc = 0; cc < 128; cc += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tDK + lane_base + cc, r);
+                tmem_ld_wait();
+                if (live) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8)
+                        *reinterpret_cast<uint4*>(dk + cc + i) = make_uint4(
+                            pack_bf16(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
+                            pack_bf16(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])),
+                            pack_bf16(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5])),
+                            pack_bf16(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7])));
+                }
+                tmem_ld_32x32(tDV + lane_base + cc, r);
+                tmem_ld_wait();
+                if (live) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8)
+                        *reinterpret_cast<uint4*>(dv + cc + i) = make_uint4(
+                            pack_bf16(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
+                            pack_bf16(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])),
+                            pack_bf16(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5])),
+                            pack_bf16(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7])));
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) { }
+        __syncthreads();
+    }
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem_slot, 512);
+    }
+}
+
+struct BwdQWork {
+    int q0;     // first query row of the 128-query tile
+    int kv0;    // first key row of its document
+    int n_kv;   // number of 64-key sub-tiles to visit
+    int q_end;  // one past the document's last row
+};
+
+// Q, dO (32 KiB each), dS (128 x 64, 16 KiB), 2 stages of (K, V) 64 x 128
+constexpr int kBwdQSmem = 2 * kTileBytes + kHalfTile + 2 * 2 * kHalfTile + 1024;
+
+// One CTA per (128-query tile, head):  S = Q K^T, dP = dO V^T (64 key columns each),
+//   dS = P * (dP - delta) * scale,  dQ += dS K  (TMEM accumulator)
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                   const BwdParams p) {
+    if (status_poisoned(p.status)) return;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bar_q, bar_kv_full[2], bar_kv_empty[2], bar_s_full, bar_ds_ready, bar_dq_done,
+        bar_acc_done;
+    __shared__ uint32_t tmem_slot;
+    __shared__ volatile int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sQ = base, sdO = base + kTileBytes, sDS = base + 2 * kTileBytes, sKV = sDS + kHalfTile;
+    const int head = blockIdx.x;
+    const int kv_head = head / (p.Hq / p.Hkv);
+    const BwdQWork w = reinterpret_cast<const BwdQWork*>(p.work)[blockIdx.y];
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar_q), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&bar_kv_full[s]), 1);
+            mbar_init(smem_u32(&bar_kv_empty[s]), 1);
+        }
+        mbar_init(smem_u32(&bar_s_full), 1);
+        mbar_init(smem_u32(&bar_ds_ready), 128);
+        mbar_init(smem_u32(&bar_dq_done), 1);
+        mbar_init(smem_u32(&bar_acc_done), 1);
+        mbar_fence_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(smem_u32(&tmem_slot), 256);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tS = tmem_slot, tDP = tmem_slot + 64, tDQ = tmem_slot + 128;
+
+    if (warp == 4) {
+        if (lane == 0) {
+            mbar_expect_tx(smem_u32(&bar_q), 2 * kTileBytes);
+            tma_load_2d(sQ, &tmQ, smem_u32(&bar_q), head * kHd, w.q0);
+            tma_load_2d(sQ + 16384, &tmQ, smem_u32(&bar_q), head * kHd + 64, w.q0);
+            tma_load_2d(sdO, &tmdO, smem_u32(&bar_q), head * kHd, w.q0);
+            tma_load_2d(sdO + 16384, &tmdO, smem_u32(&bar_q), head * kHd + 64, w.q0);
+            for (int j = 0; j < w.n_kv; ++j) {
+                const int st = j & 1;
+                if (!mbar_wait(smem_u32(&bar_kv_empty[st]), ((j >> 1) & 1) ^ 1u, &abort_flag, p.status)) break;
+                const uint32_t full = smem_u32(&bar_kv_full[st]);
+                const uint32_t sK = sKV + st * 2 * kHalfTile, sV = sK + kHalfTile;
+                const int kr = w.kv0 + j * 64;
+                mbar_expect_tx(full, 2 * kHalfTile);
+                tma_load_2d(sK, &tmK, full, kv_head * kHd, kr);
+                tma_load_2d(sK + 8192, &tmK, full, kv_head * kHd + 64, kr);
+                tma_load_2d(sV, &tmV, full, kv_head * kHd, kr);
+                tma_load_2d(sV + 8192, &tmV, full, kv_head * kHd + 64, kr);
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);     // [q x keys]
+            constexpr uint32_t idesc_dq = make_idesc_bf16(128, 128, 0, 1);   // [q x hd] = dS K
+            bool ok = mbar_wait(smem_u32(&bar_q), 0, &abort_flag, p.status);
+            for (int j = 0; ok && j < w.n_kv; ++j) {
+                const int st = j & 1;
+                const uint32_t sK = sKV + st * 2 * kHalfTile, sV = sK + kHalfTile;
+                if (!mbar_wait(smem_u32(&bar_kv_full[st]), (j >> 1) & 1, &abort_flag, p.status)) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t offa = (ks >> 2) * 16384 + (ks & 3) * 32;
+                    const uint32_t offb = (ks >> 2) * 8192 + (ks & 3) * 32;
+                    tc_mma_f16(tS, make_smem_desc(sQ + offa, 16, 1024), make_smem_desc(sK + offb, 16, 1024),
+                               idesc_s, ks != 0);
+                }
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t offa = (ks >> 2) * 16384 + (ks & 3) * 32;
+                    const uint32_t offb = (ks >> 2) * 8192 + (ks & 3) * 32;
+                    tc_mma_f16(tDP, make_smem_desc(sdO + offa, 16, 1024), make_smem_desc(sV + offb, 16, 1024),
+                               idesc_s, ks != 0);
+                }
+                tc_commit(smem_u32(&bar_s_full));
+                if (!mbar_wait(smem_u32(&bar_ds_ready), j & 1, &abort_flag, p.status)) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    // A = dS [128 q x 64 keys] K-major; B = K [64 keys x 128 hd] N-major
+                    tc_mma_f16(tDQ, make_smem_desc(sDS + ks * 32, 16, 1024),
+                               make_smem_desc(sK + ks * 2048, 8192, 1024), idesc_dq, (j | ks) != 0);
+                }
+                tc_commit(smem_u32(&bar_dq_done));
+                tc_commit(smem_u32(&bar_kv_empty[st]));
+                if (j == w.n_kv - 1) tc_commit(smem_u32(&bar_acc_done));
+            }
+        }
+    } else {
+        const int row = warp * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const float c = p.scale * kLog2e;
+        const long long q_abs = (long long)w.q0 + row;
+        const bool in = q_abs < w.q_end;
+        const float lse2 = in ? p.lse[(long long)head * p.T + q_abs] * kLog2e : INFINITY;
+        const float dl = in ? p.delta[(long long)head * p.T + q_abs] : 0.f;
+        bool ok = true;
+        for (int j = 0; j < w.n_kv; ++j) {
+            if (!mbar_wait(smem_u32(&bar_s_full), j & 1, &abort_flag, p.status)) { ok = false; break; }
+            tc_fence_after();
+            const int k0 = w.kv0 + j * 64;
+            const bool need_mask = (k0 + 64 > w.q0);
+            float pv[64];
+#pragma unroll
+            for (int cc = 0; cc < 64; cc += 32) {
+                uint32_t r[32], d[32];
+                tmem_ld_32x32(tS + lane_base + cc, r);
+                tmem_ld_32x32(tDP + lane_base + cc, d);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float pe = exp2f(__uint_as_float(r[i]) * c - lse2);
+                    if (need_mask && (long long)k0 + cc + i > q_abs) pe = 0.f;
+                    pv[cc + i] = pe * (__uint_as_float(d[i]) - dl) * p.scale;
+                }
+            }
+            // the previous dQ product must have finished reading dS before it is overwritten
+            if (j > 0 && !mbar_wait(smem_u32(&bar_dq_done), (j - 1) & 1, &abort_flag, p.status)) { ok = false; break; }
+#pragma unroll
+            for (int q8 = 0; q8 < 8; ++q8) {
+                const uint32_t a = sDS + swz_off(row, q8 * 8);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a),
+                             "r"(pack_bf16(pv[q8 * 8], pv[q8 * 8 + 1])), "r"(pack_bf16(pv[q8 * 8 + 2], pv[q8 * 8 + 3])),
+                             "r"(pack_bf16(pv[q8 * 8 + 4], pv[q8 * 8 + 5])), "r"(pack_bf16(pv[q8 * 8 + 6], pv[q8 * 8 + 7]))
+                             : "memory");
+            }
+            fence_proxy_async_smem();
+            tc_fence_before();
+            mbar_arrive(smem_u32(&bar_ds_ready));
+        }
+        if (ok && mbar_wait(smem_u32(&bar_acc_done), 0, &abort_flag, p.status)) {
+            tc_fence_after();
+            __nv_bfloat16* dq = reinterpret_cast<__nv_bfloat16*>(p.dQ) + q_abs * p.ld_dq + head * kHd;
+#pragma unroll 1
+            for (int cc = 0; cc < 128; cc += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tDQ + lane_base + cc, r);
+                tmem_ld_wait();
+                if (in) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8)
+                        *reinterpret_cast<uint4*>(dq + cc + i) = make_uint4(
+                            pack_bf16(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
+                            pack_bf16(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])),
+                            pack_bf16(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5])),
+                            pack_bf16(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7])));
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) { }
+        __syncthreads();
+    }
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem_slot, 256);
+    }
+}
+
+static int set_smem(const void* fn, int bytes) {
+    return cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess ? 0 : -10;
+}
+
+}  // namespace halo
+
+using namespace halo;
+
+extern "C" {
+
+// q: [T, Hq*128] (row stride ldq), k / v: [T, Hkv*128] (ldk / ldv), o: [T, Hq*128] (ldo)
+// work: device array of n_tiles {q0, kv0, n_kv, q_end}; lse: [Hq, T] fp32
+int halo_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const void* work,
+                  int n_tiles, long long T, int Hq, int Hkv, int head_dim, long long ldq,
+                  long long ldk, long long ldv, long long ldo, float scale, int* status, void* stream) {
+    if (head_dim != kHd || Hq % Hkv) return -1;
+    if (n_tiles == 0) return 0;
+    CUtensorMap tq, tk, tv;
+    if (make_tmap_bf16(&tq, q, T, (long long)Hq * kHd, ldq, 128)) return -2;
+    if (make_tmap_bf16(&tk, k, T, (long long)Hkv * kHd, ldk, 128)) return -3;
+    if (make_tmap_bf16(&tv, v, T, (long long)Hkv * kHd, ldv, 128)) return -4;
+    static bool cfg = false;
+    if (!cfg) {
+        if (set_smem((const void*)attn_fwd_kernel, kFwdSmem)) return -10;
+        cfg = true;
+    }
+    AttnParams p{reinterpret_cast<const FwdWork*>(work), o, lse, ldo, T, Hq, Hkv, scale, status};
+    attn_fwd_kernel<<<dim3(Hq, n_tiles), kFwdThreads, kFwdSmem, (cudaStream_t)stream>>>(tq, tk, tv, p);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// delta: [Hq, T] fp32 scratch. kv_work: n_kv_tiles {kv0, q_begin, n_q(64-row sub-tiles), q_end};
+// q_work: n_q_tiles {q0, kv0, n_kv(64-key sub-tiles), q_end}.
+int halo_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                  const float* lse, float* delta, void* dq, void* dk, void* dv, const void* kv_work,
+                  int n_kv_tiles, const void* q_work, int n_q_tiles, long long T, int Hq, int Hkv,
+                  int head_dim, long long ldq, long long ldk, long long ldv, long long ldo,
+                  long long ld_do, long long ld_dq, long long ld_dk, long long ld_dv, float scale,
+                  int* status, void* stream) {
+    if (head_dim != kHd || Hq % Hkv) return -1;
+    if (T == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    attn_delta_kernel<<<(unsigned)((T * Hq + 7) / 8), 256, 0, s>>>(
+        (const __nv_bfloat16*)d_o, (const __nv_bfloat16*)o, delta, T, Hq, ld_do, ldo);
+    CUtensorMap tq, tk, tv, tdo, tq64, tk64, tv64, tdo64;
+    if (make_tmap_bf16(&tq, q, T, (long long)Hq * kHd, ldq, 128)) return -2;
+    if (make_tmap_bf16(&tk, k, T, (long long)Hkv * kHd, ldk, 128)) return -3;
+    if (make_tmap_bf16(&tv, v, T, (long long)Hkv * kHd, ldv, 128)) return -4;
+    if (make_tmap_bf16(&tdo, d_o, T, (long long)Hq * kHd, ld_do, 128)) return -5;
+    if (make_tmap_bf16(&tq64, q, T, (long long)Hq * kHd, ldq, 64)) return -6;
+    if (make_tmap_bf16(&tk64, k, T, (long long)Hkv * kHd, ldk, 64)) return -7;
+    if (make_tmap_bf16(&tv64, v, T, (long long)Hkv * kHd, ldv, 64)) return -8;
+    if (make_tmap_bf16(&tdo64, d_o, T, (long long)Hq * kHd, ld_do, 64)) return -9;
+    static bool cfg = false;
+    if (!cfg) {
+        if (set_smem((const void*)attn_bwd_dkdv_kernel, kBwdKvSmem)) return -10;
+        if (set_smem((const void*)attn_bwd_dq_kernel, kBwdQSmem)) return -10;
+        cfg = true;
+    }
+    BwdParams p{kv_work, lse, delta, dq, dk, dv, ld_dq, ld_dk, ld_dv, T, Hq, Hkv, scale, status};
+    if (n_kv_tiles > 0)
+        attn_bwd_dkdv_kernel<<<dim3(Hkv, n_kv_tiles), kBwdThreads, kBwdKvSmem, s>>>(tq64, tk, tv, tdo64, p);
+    p.work = q_work;
+    if (n_q_tiles > 0)
+        attn_bwd_dq_kernel<<<dim3(Hq, n_q_tiles), kBwdThreads, kBwdQSmem, s>>>(tq, tk64, tv64, tdo, p);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+}  // extern "C"

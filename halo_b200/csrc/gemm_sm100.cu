@@ -108,6 +108,7 @@ template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmParams p) {
+    if (status_poisoned(p.status)) return;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bar_full[kStages], bar_empty[kStages], bar_tfull[2], bar_tempty[2];
     __shared__ uint32_t tmem_base_slot;
@@ -399,7 +400,10 @@ __global__ void plan_grouped_m_kernel(const int* __restrict__ seg_start,
             w.b_k = e * b_k_stride;
             w.k_iters = (k_dim + kBlockK - 1) / kBlockK;
             w.c_row = w.a_mn;
-            w.m_valid = min(kBlockM, rows - tm * kBlockM);
+            // whole tiles are written: the pad rows of a segment are zero on input, so they come
+            // out as zeros and later reductions over padded row ranges stay finite
+            w.m_valid = kBlockM;
+            (void)rows;
             if (swiglu_f) {
                 w.b_mn = e * b_mn_stride + tn * 128;
                 w.b_mn2 = e * b_mn_stride + swiglu_f + tn * 128;

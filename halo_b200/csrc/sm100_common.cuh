@@ -27,8 +27,15 @@ enum : int {
 
 // Time budget of one wait inside a single-GPU kernel, in nanoseconds of %globaltimer.
 #ifndef HALO_WAIT_BUDGET_NS
-#define HALO_WAIT_BUDGET_NS 2000000000ull
+#define HALO_WAIT_BUDGET_NS 250000000ull
 #endif
+
+// A kernel that finds the status word already set returns at once: after one CTA has given up,
+// the rest of the grid (and later launches, until the host clears the word) drain immediately
+// instead of each waiting out its own budget.
+__device__ __forceinline__ bool status_poisoned(const int* status) {
+    return status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

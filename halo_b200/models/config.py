@@ -1,0 +1,178 @@
+"""Architecture description of the decoder families built here (Qwen3 dense and Qwen3-MoE shapes,
+plus the shared-expert variant), convertible to and from a Hugging Face ``config.json``.
+
+The named presets are the shapes of the benchmark configurations: a tiny MoE for CPU plumbing
+tests, the dense 9B class, the 30B-A3B MoE and the ~120B-total shared-expert MoE.
+"""
+
+from __future__ import annotations
+
+import json
+from dataclasses import asdict, dataclass, field
+from pathlib import Path
+
+
+@dataclass
+class ModelConfig:
+    vocab_size: int = 151936
+    hidden_size: int = 2048
+    num_hidden_layers: int = 48
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 4
+    head_dim: int = 128
+    intermediate_size: int = 6144          # dense FFN width (dense layers / dense models)
+    moe_intermediate_size: int = 768       # width of one routed expert
+    num_experts: int = 0                   # 0 = dense model
+    num_experts_per_tok: int = 8
+    norm_topk_prob: bool = True
+    shared_expert_intermediate_size: int = 0
+    shared_expert_gate: bool = False
+    mlp_only_layers: list[int] = field(default_factory=list)
+    decoder_sparse_step: int = 1
+    rope_theta: float = 1e6
+    rms_norm_eps: float = 1e-6
+    use_qk_norm: bool = True
+    tie_word_embeddings: bool = False
+    router_aux_loss_coef: float = 0.0
+    initializer_range: float = 0.02
+    max_position_embeddings: int = 262144
+    model_type: str = "qwen3_moe"
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    def layer_is_moe(self, i: int) -> bool:
+        return self.is_moe and i not in self.mlp_only_layers and (i + 1) % self.decoder_sparse_step == 0
+
+    @property
+    def qkv_dim(self) -> int:
+        return (self.num_attention_heads + 2 * self.num_key_value_heads) * self.head_dim
+
+    # ---- parameter counts (for MFU and memory planning) ---------------------------------
+    def param_counts(self) -> dict[str, int]:
+        H, D = self.hidden_size, self.head_dim
+        attn = H * self.qkv_dim + self.num_attention_heads * D * H + (2 * D if self.use_qk_norm else 0) + 2 * H
+        dense_mlp = 3 * H * self.intermediate_size
+        expert = 3 * H * self.moe_intermediate_size
+        shared = 3 * H * self.shared_expert_intermediate_size + (H if self.shared_expert_gate else 0)
+        total = active = 0
+        for i in range(self.num_hidden_layers):
+            if self.layer_is_moe(i):
+                total += attn + self.num_experts * expert + self.num_experts * H + shared
+                active += attn + self.num_experts_per_tok * expert + self.num_experts * H + shared
+            else:
+                total += attn + dense_mlp
+                active += attn + dense_mlp
+        emb = self.vocab_size * H
+        head = 0 if self.tie_word_embeddings else emb
+        return {"total": total + emb + head + H, "active": active + head + H, "embedding": emb,
+                "expert_total": sum(self.num_experts * expert for i in range(self.num_hidden_layers) if self.layer_is_moe(i))}
+
+    # ---- Hugging Face interchange -------------------------------------------------------
+    def to_hf_dict(self) -> dict:
+        d = {
+            "architectures": ["Qwen3MoeForCausalLM" if self.is_moe else "Qwen3ForCausalLM"],
+            "model_type": "qwen3_moe" if self.is_moe else "qwen3",
+            "vocab_size": self.vocab_size,
+            "hidden_size": self.hidden_size,
+            "num_hidden_layers": self.num_hidden_layers,
+            "num_attention_heads": self.num_attention_heads,
+            "num_key_value_heads": self.num_key_value_heads,
+            "head_dim": self.head_dim,
+            "intermediate_size": self.intermediate_size,
+            "hidden_act": "silu",
+            "rope_theta": self.rope_theta,
+            "rope_parameters": {"rope_type": "default", "rope_theta": self.rope_theta},
+            "rms_norm_eps": self.rms_norm_eps,
+            "tie_word_embeddings": self.tie_word_embeddings,
+            "attention_bias": False,
+            "attention_dropout": 0.0,
+            "initializer_range": self.initializer_range,
+            "max_position_embeddings": self.max_position_embeddings,
+            "torch_dtype": "bfloat16",
+            "use_cache": False,
+        }
+        if self.is_moe:
+            d.update({
+                "moe_intermediate_size": self.moe_intermediate_size,
+                "num_experts": self.num_experts,
+                "num_experts_per_tok": self.num_experts_per_tok,
+                "norm_topk_prob": self.norm_topk_prob,
+                "decoder_sparse_step": self.decoder_sparse_step,
+                "mlp_only_layers": list(self.mlp_only_layers),
+                "router_aux_loss_coef": self.router_aux_loss_coef,
+                "output_router_logits": False,
+            })
+            if self.shared_expert_intermediate_size:
+                d["shared_expert_intermediate_size"] = self.shared_expert_intermediate_size
+        return d
+
+    @classmethod
+    def from_hf_dict(cls, d: dict) -> "ModelConfig":
+        mt = d.get("model_type", "qwen3")
+        if mt not in ("qwen3", "qwen3_moe", "qwen2_moe"):
+            raise ValueError(f"model_type {mt!r} has no family registered here")
+        rope_theta = d.get("rope_theta") or (d.get("rope_parameters") or {}).get("rope_theta", 1e6)
+        hd = d.get("head_dim") or d["hidden_size"] // d["num_attention_heads"]
+        return cls(
+            vocab_size=d["vocab_size"], hidden_size=d["hidden_size"], num_hidden_layers=d["num_hidden_layers"],
+            num_attention_heads=d["num_attention_heads"],
+            num_key_value_heads=d.get("num_key_value_heads", d["num_attention_heads"]), head_dim=hd,
+            intermediate_size=d.get("intermediate_size", 0), moe_intermediate_size=d.get("moe_intermediate_size", 0),
+            num_experts=d.get("num_experts", 0) if mt != "qwen3" else 0,
+            num_experts_per_tok=d.get("num_experts_per_tok", 8), norm_topk_prob=d.get("norm_topk_prob", True),
+            shared_expert_intermediate_size=d.get("shared_expert_intermediate_size", 0) or 0,
+            shared_expert_gate=(mt == "qwen2_moe"),
+            mlp_only_layers=list(d.get("mlp_only_layers", []) or []), decoder_sparse_step=d.get("decoder_sparse_step", 1),
+            rope_theta=float(rope_theta), rms_norm_eps=d.get("rms_norm_eps", 1e-6), use_qk_norm=(mt != "qwen2_moe"),
+            tie_word_embeddings=d.get("tie_word_embeddings", False),
+            router_aux_loss_coef=d.get("router_aux_loss_coef", 0.0), initializer_range=d.get("initializer_range", 0.02),
+            max_position_embeddings=d.get("max_position_embeddings", 262144), model_type=mt,
+        )
+
+    def save(self, directory: str | Path) -> None:
+        Path(directory).mkdir(parents=True, exist_ok=True)
+        (Path(directory) / "config.json").write_text(json.dumps(self.to_hf_dict(), indent=2))
+
+    @classmethod
+    def load(cls, directory: str | Path) -> "ModelConfig":
+        return cls.from_hf_dict(json.loads((Path(directory) / "config.json").read_text()))
+
+    def asdict(self) -> dict:
+        return asdict(self)
+
+
+def tiny_moe_config() -> ModelConfig:
+    """4 layers, hidden 256, 4 query / 2 kv heads of 64, 8 experts of width 128, top-2, vocab 4096."""
+    return ModelConfig(vocab_size=4096, hidden_size=256, num_hidden_layers=4, num_attention_heads=4,
+                       num_key_value_heads=2, head_dim=64, intermediate_size=512, moe_intermediate_size=128,
+                       num_experts=8, num_experts_per_tok=2, rope_theta=1e6, rms_norm_eps=1e-6)
+
+
+def dense_9b_config() -> ModelConfig:
+    """36 layers, hidden 4096, 32 query / 8 kv heads of 128, SwiGLU FFN 12288."""
+    return ModelConfig(hidden_size=4096, num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8,
+                       head_dim=128, intermediate_size=12288, num_experts=0, model_type="qwen3")
+
+
+def moe_30b_a3b_config() -> ModelConfig:
+    """48 layers, hidden 2048, 32 query / 4 kv heads of 128, 128 experts of width 768, top-8."""
+    return ModelConfig(hidden_size=2048, num_hidden_layers=48, num_attention_heads=32, num_key_value_heads=4,
+                       head_dim=128, intermediate_size=6144, moe_intermediate_size=768, num_experts=128,
+                       num_experts_per_tok=8)
+
+
+def moe_120b_config() -> ModelConfig:
+    """48 layers, hidden 3072, 24 query / 4 kv heads of 128, 256 experts of width 1024 + one shared expert, top-8."""
+    return ModelConfig(hidden_size=3072, num_hidden_layers=48, num_attention_heads=24, num_key_value_heads=4,
+                       head_dim=128, intermediate_size=8192, moe_intermediate_size=1024, num_experts=256,
+                       num_experts_per_tok=8, shared_expert_intermediate_size=1024)
+
+
+PRESETS = {
+    "tiny-moe": tiny_moe_config,
+    "dense-9b": dense_9b_config,
+    "moe-30b-a3b": moe_30b_a3b_config,
+    "moe-120b": moe_120b_config,
+}

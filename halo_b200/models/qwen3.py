@@ -1,0 +1,296 @@
+"""Qwen3 / Qwen3-MoE decoder over packed rows, with every hot op on the sm_100a kernels.
+
+The model consumes one flattened token stream ``[T]`` per rank (documents delimited by
+``cu_seqlens``), as the packing collator produces it. Parameter names follow the Hugging Face
+modules so checkpoints convert by renaming only; the three projections of attention are stored
+fused (``qkv_proj``), as are ``gate`` / ``up`` (``gate_up_proj``), and routed experts are stacked
+``[E_local, 2F, H]`` / ``[E_local, H, F]`` exactly like the Hugging Face runtime layout.
+
+Per layer:  x -> RMSNorm -> qkv GEMM -> q/k-norm + RoPE + flash attention -> o GEMM -> +residual
+            -> RMSNorm -> (router GEMM -> top-k -> dispatch -> grouped SwiGLU FFN -> combine |
+            dense SwiGLU FFN) -> +residual.
+The output head is fused with the loss (no logits plane).
+
+Behavioural counterpart of the reference's patched Hugging Face models
+(halo/distributed/expert_parallel/moe_layer/layer.py:67-80, 301-342;
+halo/distributed/expert_parallel/moe_layer/routing.py:105-150).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+from torch.utils.checkpoint import checkpoint
+
+from halo_b200.ops import attention as attn_ops
+from halo_b200.ops import gemm
+from halo_b200.ops import moe as moe_ops
+from halo_b200.ops import _lib
+from halo_b200.ops.cross_entropy import fused_linear_cross_entropy, linear_logprobs
+from halo_b200.ops.norm import add_rms_norm, rms_norm
+from halo_b200.ops.rope import rope_table
+
+from .config import ModelConfig
+
+
+class _SwiGLULinear(torch.autograd.Function):
+    """act = silu(x Wg^T) * (x Wu^T) with the activation in the GEMM epilogue; recompute-free backward."""
+
+    @staticmethod
+    def forward(ctx, x, w_gate_up):
+        act, pre = gemm.swiglu_matmul(x, w_gate_up, save_pre=torch.is_grad_enabled() or True)
+        ctx.save_for_backward(x, w_gate_up, pre)
+        return act
+
+    @staticmethod
+    def backward(ctx, dact):
+        x, w, pre = ctx.saved_tensors
+        F = w.shape[0] // 2
+        dact = dact.contiguous()
+        if x.is_cuda:
+            dpre = torch.empty_like(pre)
+            rc = _lib.lib().halo_swiglu_bwd(_lib.ptr(pre), _lib.ptr(dact), _lib.ptr(dpre), _lib.c_ll(pre.shape[0]),
+                                            _lib.c_int(F), _lib.stream_ptr(x.device))
+            _lib.check(rc, "halo_swiglu_bwd")
+        else:
+            g, u = pre[:, :F].float(), pre[:, F:].float()
+            s = torch.sigmoid(g)
+            d = dact.float()
+            dpre = torch.cat([d * u * s * (1 + g * (1 - s)), d * g * s], dim=-1).to(pre.dtype)
+        dx = gemm.matmul(dpre, w, b_t=False) if ctx.needs_input_grad[0] else None
+        dw = gemm.matmul(dpre, x, a_t=True, b_t=False) if ctx.needs_input_grad[1] else None
+        return dx, dw
+
+
+class _RouterLinear(torch.autograd.Function):
+    """fp32 router logits from bf16 operands (fp32 accumulate, fp32 result)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        return gemm.matmul(x, w, out_dtype=torch.float32)
+
+    @staticmethod
+    def backward(ctx, g):
+        x, w = ctx.saved_tensors
+        gb = g.to(x.dtype)
+        # pad the expert dimension of the gradient to a multiple of 8 rows only when needed
+        dx = gemm.matmul(gb, w, b_t=False) if ctx.needs_input_grad[0] else None
+        dw = gemm.matmul(gb, x, a_t=True, b_t=False) if ctx.needs_input_grad[1] else None
+        return dx, dw
+
+
+class Attention(nn.Module):
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        self.cfg = cfg
+        H, D = cfg.hidden_size, cfg.head_dim
+        self.qkv_proj = nn.Parameter(torch.empty(cfg.qkv_dim, H, dtype=dtype, device=device))
+        self.o_proj = nn.Parameter(torch.empty(H, cfg.num_attention_heads * D, dtype=dtype, device=device))
+        if cfg.use_qk_norm:
+            self.q_norm = nn.Parameter(torch.ones(D, dtype=dtype, device=device))
+            self.k_norm = nn.Parameter(torch.ones(D, dtype=dtype, device=device))
+        else:
+            self.register_parameter("q_norm", None)
+            self.register_parameter("k_norm", None)
+
+    def forward(self, h, ctx):
+        cfg = self.cfg
+        qkv = gemm.linear(h, self.qkv_proj)
+        o = attn_ops.rope_attention(qkv, self.q_norm, self.k_norm, ctx.rope, ctx.plan, cfg.num_attention_heads,
+                                    cfg.num_key_value_heads, cfg.rms_norm_eps, cfg.use_qk_norm)
+        return gemm.linear(o, self.o_proj)
+
+
+class DenseMLP(nn.Module):
+    def __init__(self, hidden: int, width: int, dtype, device):
+        super().__init__()
+        self.gate_up_proj = nn.Parameter(torch.empty(2 * width, hidden, dtype=dtype, device=device))
+        self.down_proj = nn.Parameter(torch.empty(hidden, width, dtype=dtype, device=device))
+
+    def forward(self, h, ctx=None):
+        return gemm.linear(_SwiGLULinear.apply(h, self.gate_up_proj), self.down_proj)
+
+
+class SparseMoE(nn.Module):
+    """Router + routed experts (+ optional shared expert). Expert tensors hold only this rank's
+    experts ``[E_local, ...]`` when expert parallelism is on."""
+
+    def __init__(self, cfg: ModelConfig, dtype, device, n_local_experts: int, router_dtype=None):
+        super().__init__()
+        self.cfg = cfg
+        H, F = cfg.hidden_size, cfg.moe_intermediate_size
+        self.gate = nn.Parameter(torch.empty(cfg.num_experts, H, dtype=router_dtype or dtype, device=device))
+        self.experts_gate_up = nn.Parameter(torch.empty(n_local_experts, 2 * F, H, dtype=dtype, device=device))
+        self.experts_down = nn.Parameter(torch.empty(n_local_experts, H, F, dtype=dtype, device=device))
+        self.experts_gate_up.is_expert = True
+        self.experts_down.is_expert = True
+        if cfg.shared_expert_intermediate_size:
+            self.shared_expert = DenseMLP(H, cfg.shared_expert_intermediate_size, dtype, device)
+            self.shared_gate = (nn.Parameter(torch.empty(1, H, dtype=dtype, device=device))
+                                if cfg.shared_expert_gate else None)
+        else:
+            self.shared_expert = None
+            self.shared_gate = None
+        self.last_routing = None
+
+    def forward(self, h, ctx):
+        cfg = self.cfg
+        gate_w = self.gate if self.gate.dtype == h.dtype else self.gate.to(h.dtype)
+        logits = _RouterLinear.apply(h, gate_w) if h.is_cuda else (h.float() @ self.gate.float().t())
+        if ctx.replay_topk is not None:
+            idx = ctx.replay_topk.pop(0)
+            probs = torch.softmax(logits.float(), dim=-1)
+            w = probs.gather(-1, idx.long())
+            if cfg.norm_topk_prob:
+                w = w / w.sum(-1, keepdim=True)
+        else:
+            idx, w = moe_ops.router_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
+        if ctx.record_routing is not None:
+            ctx.record_routing.append((logits, idx))
+        out = moe_ops.moe_experts(h, idx, w, self.experts_gate_up, self.experts_down, ctx.transport)
+        if self.shared_expert is not None:
+            sh = self.shared_expert(h)
+            if self.shared_gate is not None:
+                sh = sh * torch.sigmoid(h.float() @ self.shared_gate.float().t()).to(h.dtype)
+            out = out + sh
+        return out
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, idx: int, dtype, device, n_local_experts: int, router_dtype=None):
+        super().__init__()
+        H = cfg.hidden_size
+        self.input_layernorm = nn.Parameter(torch.ones(H, dtype=dtype, device=device))
+        self.post_attention_layernorm = nn.Parameter(torch.ones(H, dtype=dtype, device=device))
+        self.self_attn = Attention(cfg, dtype, device)
+        if cfg.layer_is_moe(idx):
+            self.mlp = SparseMoE(cfg, dtype, device, n_local_experts, router_dtype)
+        else:
+            self.mlp = DenseMLP(H, cfg.intermediate_size, dtype, device)
+        self.eps = cfg.rms_norm_eps
+
+    def forward(self, x, ctx):
+        h = rms_norm(x, self.input_layernorm, self.eps)
+        a = self.self_attn(h, ctx)
+        h2, x2 = add_rms_norm(a, x, self.post_attention_layernorm, self.eps)
+        m = self.mlp(h2, ctx)
+        return x2 + m
+
+
+class ForwardContext:
+    """Per-batch state shared by all layers: attention plan, rotary table, expert transport."""
+
+    def __init__(self, plan, rope, transport, record_routing=None, replay_topk=None):
+        self.plan = plan
+        self.rope = rope
+        self.transport = transport
+        self.record_routing = record_routing
+        self.replay_topk = replay_topk
+
+
+class Qwen3Model(nn.Module):
+    """Causal LM. ``forward`` returns the loss when ``labels`` are given, else final hidden states."""
+
+    def __init__(self, cfg: ModelConfig, dtype=torch.bfloat16, device=None, transport=None,
+                 gradient_checkpointing: bool = True, router_dtype=None, layer_range: tuple[int, int] | None = None,
+                 has_embed: bool = True, has_head: bool = True):
+        super().__init__()
+        self.cfg = cfg
+        self.transport = transport or moe_ops.LocalTransport()
+        if cfg.is_moe and cfg.num_experts % self.transport.n_ranks:
+            raise ValueError(
+                f"num_experts ({cfg.num_experts}) is not divisible by expert_parallel_size ({self.transport.n_ranks})")
+        n_local = cfg.num_experts // self.transport.n_ranks if cfg.is_moe else 0
+        self.gradient_checkpointing = gradient_checkpointing
+        lo, hi = layer_range or (0, cfg.num_hidden_layers)
+        self.layer_range = (lo, hi)
+        H = cfg.hidden_size
+        self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, H, dtype=dtype, device=device)) if has_embed else None
+        self.layers = nn.ModuleList(
+            [DecoderLayer(cfg, i, dtype, device, n_local, router_dtype) for i in range(lo, hi)])
+        self.norm = nn.Parameter(torch.ones(H, dtype=dtype, device=device)) if has_head else None
+        if has_head and not (cfg.tie_word_embeddings and has_embed):
+            self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, H, dtype=dtype, device=device))
+        else:
+            self.register_parameter("lm_head", None)
+        self.has_head = has_head
+
+    # ---- initialisation ----------------------------------------------------------------------
+    @torch.no_grad()
+    def init_weights(self, seed: int = 0) -> None:
+        """N(0, initializer_range) for matrices, ones for norms; per-tensor generators keyed by the
+        global parameter name so any sharding of the experts draws the same values."""
+        std = self.cfg.initializer_range
+        from halo_b200.optim.adamw_bf16 import param_name_hash
+
+        n_local = self.layers[0].mlp.experts_gate_up.shape[0] if self.cfg.is_moe and len(self.layers) and hasattr(self.layers[0].mlp, "experts_gate_up") else 0
+        for name, p in self.named_parameters():
+            if p.dim() == 1:
+                p.fill_(1.0)
+                continue
+            dev = p.device
+            if getattr(p, "is_expert", False) and self.transport.n_ranks > 1:
+                # draw the full expert bank deterministically, keep this rank's slice
+                g = torch.Generator(device=dev).manual_seed((seed * 1000003 + param_name_hash(name)) % (2**63))
+                e0 = self.transport.rank * n_local
+                full_e = self.cfg.num_experts
+                for e in range(full_e):
+                    if e0 <= e < e0 + n_local:
+                        p[e - e0].normal_(0.0, std, generator=g)
+                    else:
+                        # advance the generator identically without keeping the values
+                        torch.empty(p.shape[1:], dtype=p.dtype, device=dev).normal_(0.0, std, generator=g)
+            else:
+                g = torch.Generator(device=dev).manual_seed((seed * 1000003 + param_name_hash(name)) % (2**63))
+                p.normal_(0.0, std, generator=g)
+
+    # ---- forward -----------------------------------------------------------------------------
+    def make_context(self, position_ids, cu_seqlens, record_routing=None, replay_topk=None) -> ForwardContext:
+        dev = position_ids.device
+        plan = attn_ops.build_plan(cu_seqlens, device=dev)
+        rope = rope_table(position_ids, self.cfg.head_dim, self.cfg.rope_theta)
+        return ForwardContext(plan, rope, self.transport, record_routing, replay_topk)
+
+    def embed(self, input_ids):
+        return torch.nn.functional.embedding(input_ids.reshape(-1), self.embed_tokens)
+
+    def run_layers(self, x, ctx):
+        for layer in self.layers:
+            if self.gradient_checkpointing and torch.is_grad_enabled():
+                x = checkpoint(layer, x, ctx, use_reentrant=False, preserve_rng_state=False)
+            else:
+                x = layer(x, ctx)
+        return x
+
+    def head_weight(self):
+        return self.lm_head if self.lm_head is not None else self.embed_tokens
+
+    def hidden_states(self, input_ids, position_ids, cu_seqlens, ctx=None):
+        ctx = ctx or self.make_context(position_ids.reshape(-1), cu_seqlens)
+        x = self.embed(input_ids)
+        x = self.run_layers(x, ctx)
+        return rms_norm(x, self.norm, self.cfg.rms_norm_eps)
+
+    def forward(self, input_ids, position_ids, cu_seqlens, labels=None, normalizer=None, ctx=None):
+        """``labels`` are next-token targets already aligned with ``input_ids`` positions
+        (-100 = not scored). Returns the summed CE divided by ``normalizer`` (default: scored tokens)."""
+        h = self.hidden_states(input_ids, position_ids, cu_seqlens, ctx)
+        if labels is None:
+            return h
+        return fused_linear_cross_entropy(h, self.head_weight(), labels.reshape(-1), normalizer)
+
+    def token_logprobs(self, input_ids, position_ids, cu_seqlens, labels, want_entropy=False, ctx=None):
+        h = self.hidden_states(input_ids, position_ids, cu_seqlens, ctx)
+        return linear_logprobs(h, self.head_weight(), labels.reshape(-1), want_entropy=want_entropy)
+
+
+def build_model(cfg: ModelConfig, device="cpu", dtype=None, transport=None, seed: int = 0,
+                gradient_checkpointing: bool = True, init: bool = True, **kw) -> Qwen3Model:
+    device = torch.device(device)
+    dtype = dtype or (torch.bfloat16 if device.type == "cuda" else torch.float32)
+    model = Qwen3Model(cfg, dtype=dtype, device=device, transport=transport,
+                       gradient_checkpointing=gradient_checkpointing, **kw)
+    if init:
+        model.init_weights(seed)
+    return model

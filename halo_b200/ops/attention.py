@@ -1,0 +1,252 @@
+"""Causal attention over packed rows (documents delimited by ``cu_seqlens``), grouped-query heads.
+
+On a GPU the tcgen05 flash kernels run (forward + the two deterministic backward kernels); the
+tile work lists are built once per batch on the host from ``cu_seqlens`` and ordered heaviest
+first. On CPU tensors a plain fp32 per-document softmax attention runs, which is also the oracle
+of the GPU tests.
+
+Stands where the reference resolves an attention backend (FA4 / FA2 varlen) for packed rows
+(halo/models/attention/selection.py:383-462, halo/models/attention/packed_position_ids.py).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import _lib
+
+HEAD_DIM = 128
+
+
+@dataclass
+class AttentionPlan:
+    """Tile work lists for one packed batch (device int32 tensors of shape [n, 4])."""
+
+    cu_seqlens: np.ndarray  # host int64 [n_docs + 1]
+    total: int
+    fwd: torch.Tensor | None = None
+    bwd_kv: torch.Tensor | None = None
+    bwd_q: torch.Tensor | None = None
+    max_seqlen: int = 0
+
+    @property
+    def n_docs(self) -> int:
+        return len(self.cu_seqlens) - 1
+
+
+def build_plan(cu_seqlens, device: torch.device | str | None = None) -> AttentionPlan:
+    """``cu_seqlens``: increasing offsets ``[0, len0, len0+len1, ...]`` of the packed documents."""
+    cu = np.asarray(cu_seqlens.cpu() if isinstance(cu_seqlens, torch.Tensor) else cu_seqlens, dtype=np.int64)
+    if cu.ndim != 1 or len(cu) < 1 or cu[0] != 0 or np.any(np.diff(cu) < 0):
+        raise ValueError("cu_seqlens must start at 0 and be non-decreasing")
+    total = int(cu[-1])
+    plan = AttentionPlan(cu_seqlens=cu, total=total)
+    lens = np.diff(cu)
+    plan.max_seqlen = int(lens.max()) if len(lens) else 0
+    device = torch.device(device) if device is not None else None
+    if device is None or device.type != "cuda":
+        return plan
+    fwd, bkv, bq = [], [], []
+    for start, end in zip(cu[:-1], cu[1:]):
+        n = int(end - start)
+        if n == 0:
+            continue
+        for i in range((n + 127) // 128):
+            q0 = int(start) + 128 * i
+            fwd.append((q0, int(start), i + 1, int(end)))
+            # dQ: 64-key sub-tiles up to the tile's last visible key
+            last = min(q0 + 128, int(end))
+            bq.append((q0, int(start), (last - int(start) + 63) // 64, int(end)))
+            # dK/dV: 64-query sub-tiles from the key tile's first row to the document end
+            bkv.append((q0, q0, (int(end) - q0 + 63) // 64, int(end)))
+
+    def to_dev(rows, key):
+        if not rows:
+            return torch.zeros((0, 4), dtype=torch.int32, device=device)
+        arr = np.asarray(rows, dtype=np.int32)
+        arr = arr[np.argsort(-arr[:, key], kind="stable")]
+        return torch.from_numpy(arr).to(device, non_blocking=True)
+
+    plan.fwd = to_dev(fwd, 2)
+    plan.bwd_q = to_dev(bq, 2)
+    plan.bwd_kv = to_dev(bkv, 2)
+    return plan
+
+
+def attention_reference(q, k, v, cu_seqlens, n_heads, n_kv_heads, scale=None):
+    """fp32 oracle. q: [T, Hq*D]; k, v: [T, Hkv*D]; returns [T, Hq*D] in q's dtype."""
+    T = q.shape[0]
+    D = q.shape[1] // n_heads
+    scale = scale if scale is not None else D**-0.5
+    qf = q.float().reshape(T, n_heads, D)
+    kf = k.float().reshape(T, n_kv_heads, D)
+    vf = v.float().reshape(T, n_kv_heads, D)
+    rep = n_heads // n_kv_heads
+    out = torch.zeros_like(qf)
+    cu = [int(x) for x in cu_seqlens]
+    for s, e in zip(cu[:-1], cu[1:]):
+        if e == s:
+            continue
+        qq = qf[s:e].transpose(0, 1)  # [H, n, D]
+        kk = kf[s:e].transpose(0, 1).repeat_interleave(rep, dim=0)
+        vv = vf[s:e].transpose(0, 1).repeat_interleave(rep, dim=0)
+        sc = (qq @ kk.transpose(1, 2)) * scale
+        n = e - s
+        mask = torch.ones(n, n, dtype=torch.bool, device=q.device).tril()
+        sc = sc.masked_fill(~mask, float("-inf"))
+        out[s:e] = (torch.softmax(sc, dim=-1) @ vv).transpose(0, 1)
+    return out.reshape(T, n_heads * D).to(q.dtype)
+
+
+def _ld(t: torch.Tensor) -> int:
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError("attention operands must be 2-D with contiguous rows")
+    return t.stride(0)
+
+
+class _FlashAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, plan: AttentionPlan, n_heads: int, n_kv_heads: int, scale: float):
+        T = q.shape[0]
+        o = torch.empty((T, n_heads * HEAD_DIM), dtype=torch.bfloat16, device=q.device)
+        lse = torch.empty((n_heads, T), dtype=torch.float32, device=q.device)
+        L = _lib.lib()
+        rc = L.halo_attn_fwd(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse), _lib.ptr(plan.fwd),
+            _lib.c_int(plan.fwd.shape[0]), _lib.c_ll(T), _lib.c_int(n_heads), _lib.c_int(n_kv_heads),
+            _lib.c_int(HEAD_DIM), _lib.c_ll(_ld(q)), _lib.c_ll(_ld(k)), _lib.c_ll(_ld(v)), _lib.c_ll(_ld(o)),
+            _lib.c_float(scale), _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr(q.device),
+        )
+        _lib.check(rc, "halo_attn_fwd")
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.plan, ctx.n_heads, ctx.n_kv_heads, ctx.scale = plan, n_heads, n_kv_heads, scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        plan = ctx.plan
+        T = q.shape[0]
+        do = do.contiguous()
+        dq = torch.empty((T, ctx.n_heads * HEAD_DIM), dtype=torch.bfloat16, device=q.device)
+        dkv = torch.empty((T, 2 * ctx.n_kv_heads * HEAD_DIM), dtype=torch.bfloat16, device=q.device)
+        dk = dkv[:, : ctx.n_kv_heads * HEAD_DIM]
+        dv = dkv[:, ctx.n_kv_heads * HEAD_DIM :]
+        delta = torch.empty((ctx.n_heads, T), dtype=torch.float32, device=q.device)
+        L = _lib.lib()
+        rc = L.halo_attn_bwd(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(do), _lib.ptr(lse), _lib.ptr(delta),
+            _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv),
+            _lib.ptr(plan.bwd_kv), _lib.c_int(plan.bwd_kv.shape[0]),
+            _lib.ptr(plan.bwd_q), _lib.c_int(plan.bwd_q.shape[0]),
+            _lib.c_ll(T), _lib.c_int(ctx.n_heads), _lib.c_int(ctx.n_kv_heads), _lib.c_int(HEAD_DIM),
+            _lib.c_ll(_ld(q)), _lib.c_ll(_ld(k)), _lib.c_ll(_ld(v)), _lib.c_ll(_ld(o)), _lib.c_ll(_ld(do)),
+            _lib.c_ll(_ld(dq)), _lib.c_ll(_ld(dk)), _lib.c_ll(_ld(dv)),
+            _lib.c_float(ctx.scale), _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr(q.device),
+        )
+        _lib.check(rc, "halo_attn_bwd")
+        return dq, dk, dv, None, None, None, None
+
+
+def flash_attention(q, k, v, plan: AttentionPlan, n_heads: int, n_kv_heads: int, scale: float | None = None):
+    """q: [T, Hq*128]; k, v: [T, Hkv*128] (row-strided views are fine); returns [T, Hq*128]."""
+    D = q.shape[1] // n_heads
+    scale = float(scale if scale is not None else D**-0.5)
+    if not q.is_cuda:
+        return attention_reference(q, k, v, plan.cu_seqlens, n_heads, n_kv_heads, scale)
+    if D != HEAD_DIM:
+        raise NotImplementedError("the sm_100a flash kernel is built for head_dim 128")
+    if plan.fwd is None:
+        raise ValueError("the attention plan was built without a CUDA device")
+    return _FlashAttention.apply(q, k, v, plan, n_heads, n_kv_heads, scale)
+
+
+class _RopeAttention(torch.autograd.Function):
+    """q/k norm + RoPE + flash attention on the fused ``qkv`` projection, as one autograd node.
+
+    The backward writes dq / dk (through the rotation and norm) and dv straight into the columns
+    of one ``dqkv`` buffer, so no gradient is sliced, zero-filled or re-added by autograd.
+    """
+
+    @staticmethod
+    def forward(ctx, qkv, wq, wk, table, plan, n_heads, n_kv_heads, eps, use_norm, scale):
+        T = qkv.shape[0]
+        dev = qkv.device
+        L = _lib.lib()
+        q = torch.empty((T, n_heads * HEAD_DIM), dtype=torch.bfloat16, device=dev)
+        k = torch.empty((T, n_kv_heads * HEAD_DIM), dtype=torch.bfloat16, device=dev)
+        rstd = torch.empty(T * (n_heads + n_kv_heads), dtype=torch.float32, device=dev)
+        rc = L.halo_qknorm_rope_fwd(
+            _lib.ptr(qkv), _lib.ptr(wq), _lib.ptr(wk), _lib.ptr(table), _lib.ptr(q), _lib.ptr(k), _lib.ptr(rstd),
+            _lib.c_ll(T), _lib.c_int(n_heads), _lib.c_int(n_kv_heads), _lib.c_int(HEAD_DIM), _lib.c_float(eps),
+            _lib.c_int(1 if use_norm else 0), _lib.stream_ptr(dev),
+        )
+        _lib.check(rc, "halo_qknorm_rope_fwd")
+        v = qkv[:, (n_heads + n_kv_heads) * HEAD_DIM :]
+        o = torch.empty((T, n_heads * HEAD_DIM), dtype=torch.bfloat16, device=dev)
+        lse = torch.empty((n_heads, T), dtype=torch.float32, device=dev)
+        rc = L.halo_attn_fwd(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse), _lib.ptr(plan.fwd),
+            _lib.c_int(plan.fwd.shape[0]), _lib.c_ll(T), _lib.c_int(n_heads), _lib.c_int(n_kv_heads),
+            _lib.c_int(HEAD_DIM), _lib.c_ll(_ld(q)), _lib.c_ll(_ld(k)), _lib.c_ll(_ld(v)), _lib.c_ll(_ld(o)),
+            _lib.c_float(scale), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev),
+        )
+        _lib.check(rc, "halo_attn_fwd")
+        ctx.save_for_backward(qkv, wq, wk, table, q, k, o, lse, rstd)
+        ctx.meta = (plan, n_heads, n_kv_heads, use_norm, scale)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        qkv, wq, wk, table, q, k, o, lse, rstd = ctx.saved_tensors
+        plan, n_heads, n_kv_heads, use_norm, scale = ctx.meta
+        T = qkv.shape[0]
+        dev = qkv.device
+        L = _lib.lib()
+        do = do.contiguous()
+        v = qkv[:, (n_heads + n_kv_heads) * HEAD_DIM :]
+        dqkv = torch.empty_like(qkv)
+        dv = dqkv[:, (n_heads + n_kv_heads) * HEAD_DIM :]
+        dq = torch.empty_like(q)
+        dk = torch.empty_like(k)
+        delta = torch.empty((n_heads, T), dtype=torch.float32, device=dev)
+        rc = L.halo_attn_bwd(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(do), _lib.ptr(lse), _lib.ptr(delta),
+            _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv),
+            _lib.ptr(plan.bwd_kv), _lib.c_int(plan.bwd_kv.shape[0]),
+            _lib.ptr(plan.bwd_q), _lib.c_int(plan.bwd_q.shape[0]),
+            _lib.c_ll(T), _lib.c_int(n_heads), _lib.c_int(n_kv_heads), _lib.c_int(HEAD_DIM),
+            _lib.c_ll(_ld(q)), _lib.c_ll(_ld(k)), _lib.c_ll(_ld(v)), _lib.c_ll(_ld(o)), _lib.c_ll(_ld(do)),
+            _lib.c_ll(_ld(dq)), _lib.c_ll(_ld(dk)), _lib.c_ll(_ld(dv)),
+            _lib.c_float(scale), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev),
+        )
+        _lib.check(rc, "halo_attn_bwd")
+        blocks = L.halo_qknorm_rope_bwd_blocks(_lib.c_ll(T), _lib.c_int(n_heads + n_kv_heads))
+        partial = torch.empty((max(blocks, 1), 256), dtype=torch.float32, device=dev)
+        dw = torch.zeros(256, dtype=torch.float32, device=dev)
+        rc = L.halo_qknorm_rope_bwd(
+            _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(qkv), _lib.ptr(wq), _lib.ptr(wk), _lib.ptr(table), _lib.ptr(rstd),
+            _lib.ptr(dqkv), _lib.ptr(partial), _lib.ptr(dw), _lib.c_void_p(0), _lib.c_int(0), _lib.c_ll(T),
+            _lib.c_int(n_heads), _lib.c_int(n_kv_heads), _lib.c_int(HEAD_DIM), _lib.c_int(1 if use_norm else 0),
+            _lib.stream_ptr(dev),
+        )
+        _lib.check(rc, "halo_qknorm_rope_bwd")
+        dwq = dw[:128].to(wq.dtype) if use_norm else None
+        dwk = dw[128:].to(wk.dtype) if use_norm else None
+        return dqkv, dwq, dwk, None, None, None, None, None, None, None
+
+
+def rope_attention(qkv, wq, wk, table, plan, n_heads, n_kv_heads, eps=1e-6, use_norm=True, scale=None):
+    """``attention(rope(norm(q)), rope(norm(k)), v)`` from the fused projection ``qkv``."""
+    D = qkv.shape[1] // (n_heads + 2 * n_kv_heads)
+    scale = float(scale if scale is not None else D**-0.5)
+    if qkv.is_cuda and D == HEAD_DIM and qkv.dtype == torch.bfloat16:
+        return _RopeAttention.apply(qkv.contiguous(), wq, wk, table, plan, n_heads, n_kv_heads, eps, use_norm, scale)
+    from .rope import qk_norm_rope_reference
+
+    q, k = qk_norm_rope_reference(qkv, wq, wk, table, n_heads, n_kv_heads, eps, use_norm)
+    v = qkv[:, (n_heads + n_kv_heads) * D :]
+    return attention_reference(q, k, v, plan.cu_seqlens, n_heads, n_kv_heads, scale)

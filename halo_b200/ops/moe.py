@@ -1,0 +1,378 @@
+"""Routed-expert FFN: router top-k, dispatch to the expert-owning rank, grouped SwiGLU FFN on
+the tcgen05 grouped GEMM, weighted combine; forward and backward, as one autograd node.
+
+Data flow for one layer on a rank that owns ``E_local`` of ``E`` experts (``N`` ranks):
+
+  counts    histogram of this rank's [T, k] routing over all E experts        (route_count)
+  exchange  all ranks' histograms -> every rank derives every rank's receive layout (transport)
+  place     each (token, k) slot gets its row in the owner's receive buffer   (route_place)
+  dispatch  token rows are pushed into the owners' buffers (peer stores)      (dispatch_rows)
+  FFN       gate_up GEMM with SwiGLU epilogue, down GEMM, per-expert tile lists built on device
+  combine   each token pulls its k expert rows back (peer loads), weights and sums them in fp32
+
+Backward runs the same movement in reverse: dout rows are pushed to the experts together with the
+routing weights, the expert side forms dy and the routing-weight gradient, the grouped GEMMs
+produce the weight and input gradients, and the input-gradient rows are pulled back and summed.
+No host synchronisation happens anywhere: segment sizes stay on the device and size the GEMM tile
+lists there; buffers are provisioned from a capacity bound that is checked on the device.
+
+Replaces DeepEP dispatch/combine, the Triton route sort / permute kernels and ``F.grouped_mm``
+(halo/distributed/expert_parallel/moe_layer/layer.py:301-342,
+halo/distributed/expert_parallel/moe_layer/compute.py:222-242, 357-361).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from . import _lib
+from .gemm import EPI_STORE_BF16, EPI_SWIGLU
+
+
+# ---------------------------------------------------------------------------------------------
+# router
+# ---------------------------------------------------------------------------------------------
+def router_topk_reference(logits: torch.Tensor, k: int, renorm: bool):
+    probs = torch.softmax(logits.float(), dim=-1)
+    w, idx = torch.topk(probs, k, dim=-1)
+    if renorm:
+        w = w / w.sum(-1, keepdim=True)
+    return idx.to(torch.int32), w
+
+
+class _RouterTopK(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, k, renorm):
+        T, E = logits.shape
+        idx = torch.empty((T, k), dtype=torch.int32, device=logits.device)
+        w = torch.empty((T, k), dtype=torch.float32, device=logits.device)
+        rc = _lib.lib().halo_router_topk_fwd(
+            _lib.ptr(logits), _lib.ptr(idx), _lib.ptr(w), _lib.c_void_p(0), _lib.c_ll(T), _lib.c_int(E),
+            _lib.c_int(k), _lib.c_int(1 if renorm else 0), _lib.stream_ptr(logits.device),
+        )
+        _lib.check(rc, "halo_router_topk_fwd")
+        ctx.save_for_backward(logits, idx)
+        ctx.meta = (k, renorm)
+        ctx.mark_non_differentiable(idx)
+        return idx, w
+
+    @staticmethod
+    def backward(ctx, _gidx, gw):
+        logits, idx = ctx.saved_tensors
+        k, renorm = ctx.meta
+        T, E = logits.shape
+        dl = torch.empty_like(logits)
+        rc = _lib.lib().halo_router_topk_bwd(
+            _lib.ptr(logits), _lib.ptr(idx), _lib.ptr(gw.contiguous().float()), _lib.ptr(dl), _lib.c_ll(T),
+            _lib.c_int(E), _lib.c_int(k), _lib.c_int(1 if renorm else 0), _lib.stream_ptr(logits.device),
+        )
+        _lib.check(rc, "halo_router_topk_bwd")
+        return dl, None, None
+
+
+def router_topk(logits: torch.Tensor, k: int, renorm: bool = True):
+    """softmax over experts, top-k, optional renormalisation. logits: fp32 [T, E].
+    Returns ``(idx int32 [T, k], weights fp32 [T, k])``."""
+    E = logits.shape[-1]
+    if not logits.is_cuda or E % 32 or E > 256 or k > 16:
+        return router_topk_reference(logits, k, renorm)
+    return _RouterTopK.apply(logits.float().contiguous(), k, renorm)
+
+
+# ---------------------------------------------------------------------------------------------
+# transport: who owns which buffer and how ranks agree on counts
+# ---------------------------------------------------------------------------------------------
+class LocalTransport:
+    """Single-rank transport: every expert is local, buffers are ordinary device tensors."""
+
+    n_ranks = 1
+    rank = 0
+
+    def __init__(self, capacity_factor: float = 1.0):
+        self.capacity_factor = capacity_factor
+        self._ptr_cache: dict[int, torch.Tensor] = {}
+
+    def capacity(self, n_slots: int, n_local_experts: int) -> int:
+        # every slot lands here; each expert segment is padded to a multiple of 128 rows
+        return n_slots + 128 * n_local_experts
+
+    def exchange_counts(self, counts: torch.Tensor) -> torch.Tensor:
+        return counts.reshape(1, -1)
+
+    def buffer(self, name: str, rows: int, cols: int, dtype: torch.dtype, device) -> torch.Tensor:
+        return torch.empty((rows, cols), dtype=dtype, device=device)
+
+    def peer_table(self, buf: torch.Tensor):
+        """Host array of every rank's base pointer for this buffer (here: just ours); it travels to
+        the kernels by value."""
+        return (_lib.c_void_p * 1)(buf.data_ptr())
+
+    def barrier(self) -> None:
+        """All ranks' writes issued before this point are visible to reads issued after it."""
+
+    @property
+    def transient_buffers(self) -> bool:
+        return False
+
+
+@dataclass
+class RoutingState:
+    """Everything derived from one layer's routing; kept for the backward."""
+
+    n_tokens: int
+    top_k: int
+    n_experts: int
+    n_local: int
+    capacity: int
+    topk_idx: torch.Tensor          # int32 [T, k]
+    slot_row: torch.Tensor          # int32 [T*k]
+    seg_start: torch.Tensor         # int32 [E_local]
+    seg_rows: torch.Tensor          # int32 [E_local]
+    total_rows: torch.Tensor        # int32 [1]
+    counts: torch.Tensor            # int32 [E] this rank's slots per expert
+    lists: dict = field(default_factory=dict)
+
+
+def _work_bytes() -> int:
+    return int(_lib.lib().halo_gemm_work_bytes())
+
+
+def plan_routing(topk_idx: torch.Tensor, n_experts: int, transport) -> RoutingState:
+    T, k = topk_idx.shape
+    dev = topk_idx.device
+    L = _lib.lib()
+    n_slots = T * k
+    idx = topk_idx.contiguous()
+    n_blocks = L.halo_route_blocks(_lib.c_ll(n_slots))
+    block_hist = torch.empty((max(n_blocks, 1), n_experts), dtype=torch.int32, device=dev)
+    counts = torch.empty(n_experts, dtype=torch.int32, device=dev)
+    s = _lib.stream_ptr(dev)
+    _lib.check(L.halo_route_count(_lib.ptr(idx), _lib.c_ll(n_slots), _lib.c_int(n_experts), _lib.ptr(block_hist),
+                                  _lib.ptr(counts), s), "halo_route_count")
+    counts_all = transport.exchange_counts(counts).contiguous()
+    n_local = n_experts // transport.n_ranks
+    seg_start = torch.empty(n_local, dtype=torch.int32, device=dev)
+    seg_rows = torch.empty(n_local, dtype=torch.int32, device=dev)
+    dst_base = torch.empty(n_experts, dtype=torch.int32, device=dev)
+    total_rows = torch.empty(1, dtype=torch.int32, device=dev)
+    _lib.check(L.halo_route_layout(_lib.ptr(counts_all), _lib.c_int(transport.n_ranks), _lib.c_int(n_experts),
+                                   _lib.c_int(transport.rank), _lib.ptr(seg_start), _lib.ptr(seg_rows),
+                                   _lib.ptr(dst_base), _lib.ptr(total_rows), s), "halo_route_layout")
+    slot_row = torch.empty(n_slots, dtype=torch.int32, device=dev)
+    _lib.check(L.halo_route_place(_lib.ptr(idx), _lib.c_ll(n_slots), _lib.c_int(n_experts), _lib.ptr(block_hist),
+                                  _lib.ptr(dst_base), _lib.ptr(slot_row), s), "halo_route_place")
+    return RoutingState(
+        n_tokens=T, top_k=k, n_experts=n_experts, n_local=n_local,
+        capacity=transport.capacity(n_slots, n_local), topk_idx=idx, slot_row=slot_row,
+        seg_start=seg_start, seg_rows=seg_rows, total_rows=total_rows, counts=counts,
+    )
+
+
+def _tile_list(state: RoutingState, kind: str, **kw):
+    """Device tile list for one grouped product shape, cached per routing state."""
+    key = (kind, tuple(sorted(kw.items())))
+    hit = state.lists.get(key)
+    if hit is not None:
+        return hit
+    L = _lib.lib()
+    dev = state.slot_row.device
+    wb = _work_bytes()
+    s = _lib.stream_ptr(dev)
+    count = torch.empty(1, dtype=torch.int32, device=dev)
+    if kind == "m":
+        tile_n = 128 if kw["swiglu_f"] else 256
+        width = kw["swiglu_f"] if kw["swiglu_f"] else kw["n_cols"]
+        tiles_n = (width + tile_n - 1) // tile_n
+        max_items = (state.capacity // 128 + state.n_local) * tiles_n
+        lst = torch.empty(max_items * wb, dtype=torch.uint8, device=dev)
+        _lib.check(L.halo_plan_grouped_m(
+            _lib.ptr(state.seg_start), _lib.ptr(state.seg_rows), _lib.c_int(state.n_local), _lib.c_int(kw["n_cols"]),
+            _lib.c_int(kw["k_dim"]), _lib.c_int(kw["b_mn_stride"]), _lib.c_int(kw["b_k_stride"]),
+            _lib.c_int(kw["swiglu_f"]), _lib.ptr(lst), _lib.ptr(count), _lib.c_int(max_items), s), "halo_plan_grouped_m")
+    else:
+        tiles = ((kw["m_dim"] + 127) // 128) * ((kw["n_dim"] + 255) // 256)
+        max_items = tiles * state.n_local
+        lst = torch.empty(max_items * wb, dtype=torch.uint8, device=dev)
+        _lib.check(L.halo_plan_grouped_k(
+            _lib.ptr(state.seg_start), _lib.ptr(state.seg_rows), _lib.c_int(state.n_local), _lib.c_int(kw["m_dim"]),
+            _lib.c_int(kw["n_dim"]), _lib.ptr(lst), _lib.ptr(count), _lib.c_int(max_items), s), "halo_plan_grouped_k")
+    state.lists[key] = (lst, count)
+    return lst, count
+
+
+def _gemm_list(a, b2d, c, lst_cnt, a_mn, b_mn, epi, aux=None, swiglu_f=0, alpha=1.0):
+    lst, cnt = lst_cnt
+    L = _lib.lib()
+    rc = L.halo_gemm_bf16_list(
+        _lib.ptr(a), _lib.c_ll(a.shape[0]), _lib.c_ll(a.shape[1]), _lib.c_ll(a.stride(0)),
+        _lib.ptr(b2d), _lib.c_ll(b2d.shape[0]), _lib.c_ll(b2d.shape[1]), _lib.c_ll(b2d.stride(0)),
+        _lib.ptr(c), _lib.ptr(aux), _lib.c_ll(c.stride(0)), _lib.c_ll(aux.stride(0) if aux is not None else 0),
+        _lib.c_int(a_mn), _lib.c_int(b_mn), _lib.c_int(epi), _lib.c_float(alpha), _lib.c_int(swiglu_f),
+        _lib.ptr(lst), _lib.ptr(cnt), _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr(a.device),
+    )
+    _lib.check(rc, "halo_gemm_bf16_list")
+
+
+def grouped_swiglu_ffn_fwd(state: RoutingState, x_rows, w_gate_up, w_down, save_pre: bool):
+    """x_rows: [cap, H] grouped by expert. Returns (y_rows [cap, H], act [cap, F], pre [cap, 2F] | None)."""
+    E, F2, H = w_gate_up.shape
+    F = F2 // 2
+    cap = x_rows.shape[0]
+    dev = x_rows.device
+    act = torch.empty((cap, F), dtype=torch.bfloat16, device=dev)
+    pre = torch.empty((cap, F2), dtype=torch.bfloat16, device=dev) if save_pre else None
+    lst1 = _tile_list(state, "m", n_cols=F2, k_dim=H, b_mn_stride=F2, b_k_stride=0, swiglu_f=F)
+    _gemm_list(x_rows, w_gate_up.reshape(E * F2, H), act, lst1, 0, 0, EPI_SWIGLU, aux=pre, swiglu_f=F)
+    return act, pre
+
+
+def grouped_down_fwd(state: RoutingState, act, w_down, out_rows):
+    E, H, F = w_down.shape
+    lst2 = _tile_list(state, "m", n_cols=H, k_dim=F, b_mn_stride=H, b_k_stride=0, swiglu_f=0)
+    _gemm_list(act, w_down.reshape(E * H, F), out_rows, lst2, 0, 0, EPI_STORE_BF16)
+    return out_rows
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU / oracle implementation of the whole routed FFN (also the gloo-rank path)
+# ---------------------------------------------------------------------------------------------
+def moe_ffn_reference(x, topk_idx, topk_w, w_gate_up, w_down, expert_offset: int = 0):
+    """Loop over experts in fp32-accumulate PyTorch. Only experts in
+    [expert_offset, expert_offset + E_local) are applied (the rest contribute zero)."""
+    T, H = x.shape
+    E_local, F2, _ = w_gate_up.shape
+    F = F2 // 2
+    out = torch.zeros((T, H), dtype=torch.float32, device=x.device)
+    for le in range(E_local):
+        e = le + expert_offset
+        tok, slot = torch.where(topk_idx == e)
+        if tok.numel() == 0:
+            continue
+        xe = x[tok]
+        pre = (xe.float() @ w_gate_up[le].float().t()).to(x.dtype)
+        act = (torch.nn.functional.silu(pre[:, :F].float()) * pre[:, F:].float()).to(x.dtype)
+        ye = (act.float() @ w_down[le].float().t()).to(x.dtype)
+        out.index_add_(0, tok, ye.float() * topk_w[tok, slot].float()[:, None])
+    return out.to(x.dtype)
+
+
+# ---------------------------------------------------------------------------------------------
+# the fused autograd node
+# ---------------------------------------------------------------------------------------------
+class _MoEExperts(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, topk_idx, topk_w, w_gate_up, w_down, transport, state_out):
+        T, H = x.shape
+        E_local, F2, _ = w_gate_up.shape
+        F = F2 // 2
+        n_experts = E_local * transport.n_ranks
+        k = topk_idx.shape[1]
+        dev = x.device
+        L = _lib.lib()
+        s = _lib.stream_ptr(dev)
+        state = plan_routing(topk_idx, n_experts, transport)
+        cap = state.capacity
+        recv_x = transport.buffer("recv_x", cap, H, torch.bfloat16, dev)
+        y_rows = transport.buffer("y_rows", cap, H, torch.bfloat16, dev)
+        px = transport.peer_table(recv_x)
+        py = transport.peer_table(y_rows)
+        _lib.check(L.halo_zero_pad_rows(_lib.ptr(recv_x), _lib.ptr(state.seg_start), _lib.ptr(state.seg_rows),
+                                        _lib.c_int(state.n_local), _lib.c_int(H), s), "halo_zero_pad_rows")
+        _lib.check(L.halo_dispatch_rows(_lib.ptr(x), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
+                                        _lib.c_void_p(0), px, _lib.c_void_p(0), _lib.c_int(transport.n_ranks), _lib.c_ll(T), _lib.c_int(k),
+                                        _lib.c_int(H), _lib.c_int(E_local), s), "halo_dispatch_rows")
+        transport.barrier()
+        need_grad = torch.is_grad_enabled() and any(ctx.needs_input_grad)
+        act, pre = grouped_swiglu_ffn_fwd(state, recv_x, w_gate_up, w_down, save_pre=need_grad)
+        grouped_down_fwd(state, act, w_down, y_rows)
+        transport.barrier()
+        out = torch.empty_like(x)
+        w32 = topk_w.float().contiguous()
+        _lib.check(L.halo_combine_rows(py, _lib.c_int(transport.n_ranks), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
+                                       _lib.ptr(w32), _lib.c_void_p(0), _lib.ptr(out), _lib.c_ll(T), _lib.c_int(k),
+                                       _lib.c_int(H), _lib.c_int(E_local), s), "halo_combine_rows")
+        if need_grad:
+            if transport.transient_buffers:
+                recv_x, y_rows = recv_x.clone(), y_rows.clone()
+            ctx.save_for_backward(recv_x, y_rows, act, pre, w32, w_gate_up, w_down)
+            ctx.state = state
+            ctx.transport = transport
+        if state_out is not None:
+            state_out.append(state)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        recv_x, y_rows, act, pre, w32, w_gate_up, w_down = ctx.saved_tensors
+        state, transport = ctx.state, ctx.transport
+        T, k = state.n_tokens, state.top_k
+        E_local, F2, H = w_gate_up.shape
+        F = F2 // 2
+        cap = state.capacity
+        dev = dout.device
+        L = _lib.lib()
+        s = _lib.stream_ptr(dev)
+        dout = dout.contiguous()
+        # 1. push dout rows and routing weights to the experts
+        dy = transport.buffer("recv_dy", cap, H, torch.bfloat16, dev)
+        row_w = transport.buffer("row_w", cap, 1, torch.float32, dev)
+        row_w.zero_()  # pad rows must scale to a finite value
+        pdy, pw = transport.peer_table(dy), transport.peer_table(row_w)
+        _lib.check(L.halo_zero_pad_rows(_lib.ptr(dy), _lib.ptr(state.seg_start), _lib.ptr(state.seg_rows),
+                                        _lib.c_int(state.n_local), _lib.c_int(H), s), "halo_zero_pad_rows")
+        _lib.check(L.halo_dispatch_rows(_lib.ptr(dout), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
+                                        _lib.ptr(w32), pdy, pw, _lib.c_int(transport.n_ranks), _lib.c_ll(T), _lib.c_int(k),
+                                        _lib.c_int(H), _lib.c_int(E_local), s), "halo_dispatch_rows")
+        transport.barrier()
+        # 2. expert side: routing-weight gradient per row, then dy = w * dout in place
+        dwrow = transport.buffer("dwrow", cap, 1, torch.float32, dev)
+        _lib.check(L.halo_scale_rows_dot(_lib.ptr(dy), _lib.ptr(y_rows), _lib.ptr(row_w), _lib.ptr(dwrow),
+                                         _lib.ptr(state.total_rows), _lib.c_int(H), s), "halo_scale_rows_dot")
+        # 3. down projection: dact = dy W_down ; dW_down[e] = dy_e^T act_e
+        dact = torch.empty((cap, F), dtype=torch.bfloat16, device=dev)
+        lst = _tile_list(state, "m", n_cols=F, k_dim=H, b_mn_stride=0, b_k_stride=H, swiglu_f=0)
+        _gemm_list(dy, w_down.reshape(E_local * H, F), dact, lst, 0, 1, EPI_STORE_BF16)
+        dw_down = torch.empty_like(w_down)
+        lst = _tile_list(state, "k", m_dim=H, n_dim=F)
+        _gemm_list(dy, act, dw_down.reshape(E_local * H, F), lst, 1, 1, EPI_STORE_BF16)
+        # 4. SwiGLU backward
+        dpre = torch.empty((cap, F2), dtype=torch.bfloat16, device=dev)
+        _lib.check(L.halo_swiglu_bwd(_lib.ptr(pre), _lib.ptr(dact), _lib.ptr(dpre), _lib.c_ll(cap), _lib.c_int(F), s),
+                   "halo_swiglu_bwd")
+        # 5. gate/up projection: dx_rows = dpre W_gate_up ; dW_gate_up[e] = dpre_e^T x_e
+        dx_rows = transport.buffer("dx_rows", cap, H, torch.bfloat16, dev)
+        lst = _tile_list(state, "m", n_cols=H, k_dim=F2, b_mn_stride=0, b_k_stride=F2, swiglu_f=0)
+        _gemm_list(dpre, w_gate_up.reshape(E_local * F2, H), dx_rows, lst, 0, 1, EPI_STORE_BF16)
+        dw_gate_up = torch.empty_like(w_gate_up)
+        lst = _tile_list(state, "k", m_dim=F2, n_dim=H)
+        _gemm_list(dpre, recv_x, dw_gate_up.reshape(E_local * F2, H), lst, 1, 1, EPI_STORE_BF16)
+        transport.barrier()
+        # 6. pull the input-gradient rows and the routing-weight gradients back to the tokens
+        dx = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+        pdx, pdw = transport.peer_table(dx_rows), transport.peer_table(dwrow)
+        _lib.check(L.halo_combine_rows(pdx, _lib.c_int(transport.n_ranks), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
+                                       _lib.c_void_p(0), _lib.c_void_p(0), _lib.ptr(dx), _lib.c_ll(T), _lib.c_int(k),
+                                       _lib.c_int(H), _lib.c_int(E_local), s), "halo_combine_rows")
+        dw = torch.empty((T, k), dtype=torch.float32, device=dev)
+        _lib.check(L.halo_gather_slot_values(pdw, _lib.c_int(transport.n_ranks), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
+                                             _lib.ptr(dw), _lib.c_ll(T * k), _lib.c_int(E_local), s),
+                   "halo_gather_slot_values")
+        return dx, None, dw, dw_gate_up, dw_down, None, None
+
+
+def moe_experts(x, topk_idx, topk_w, w_gate_up, w_down, transport=None, state_out: list | None = None):
+    """Apply the routed experts.
+
+    x: [T, H] bf16; topk_idx: int32 [T, k] global expert ids; topk_w: [T, k] routing weights;
+    w_gate_up: [E_local, 2F, H] (gate rows then up rows per expert); w_down: [E_local, H, F].
+    """
+    if transport is None:
+        transport = LocalTransport()
+    if not x.is_cuda:
+        offset = transport.rank * w_gate_up.shape[0]
+        if transport.n_ranks > 1:
+            return transport.reference_ffn(x, topk_idx, topk_w, w_gate_up, w_down)
+        return moe_ffn_reference(x, topk_idx, topk_w, w_gate_up, w_down, offset)
+    return _MoEExperts.apply(x.contiguous(), topk_idx, topk_w, w_gate_up, w_down, transport, state_out)

@@ -1,0 +1,95 @@
+"""The training step: host batch -> device, forward + fused loss, backward, gradient
+synchronisation, device-side global-norm clip / non-finite guard, optimizer step.
+
+``TrainEngine`` is the seam every trainer (SFT, preference, distillation, GRPO ...) drives; it owns
+nothing method-specific. A step never reads the device: the clip coefficient and the skip flag stay
+in device memory and are consumed by the optimizer kernel; the caller decides when to read the loss.
+
+Counterpart of the reference's trainer spine around ``training_step`` / ``clip_grad_norm_`` /
+``optimizer.step`` (halo/trainers/distributed_trainer.py:591-618,
+halo/trainers/parallelism/grad_clipping.py:125-147, halo/trainers/loop/step_guard.py:104-131).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable
+
+import torch
+
+from halo_b200.data.packing import PackedBatch
+from halo_b200.optim.adamw_bf16 import GradNorm
+
+
+@dataclass
+class StepOutput:
+    loss: torch.Tensor                 # device scalar (mean CE over the globally scored tokens)
+    grad_norm: torch.Tensor            # device scalar
+    skipped: torch.Tensor              # device int32 flag: the update was skipped (non-finite norm)
+    n_tokens: int = 0
+    extras: dict = field(default_factory=dict)
+
+
+class TrainEngine:
+    def __init__(self, model, optimizer, device, max_grad_norm: float = 1.0, parallel=None, lr_scheduler=None,
+                 loss_fn: Callable | None = None):
+        self.model = model
+        self.optimizer = optimizer
+        self.device = torch.device(device)
+        self.max_grad_norm = max_grad_norm
+        self.parallel = parallel          # halo_b200.parallel.runtime.ParallelRuntime or None
+        self.lr_scheduler = lr_scheduler
+        self.loss_fn = loss_fn
+        self.grad_norm = GradNorm(self.device)
+        self.step_count = 0
+        self.consecutive_skips = 0
+
+    # ---- pieces ---------------------------------------------------------------------------
+    def to_device(self, batch: PackedBatch) -> PackedBatch:
+        return batch.to(self.device, non_blocking=True) if self.device.type == "cuda" else batch
+
+    def global_scored_tokens(self, batch: PackedBatch):
+        """Normaliser shared by every data-parallel rank so that summed gradients average correctly."""
+        if self.parallel is not None and self.parallel.dp_world > 1:
+            return self.parallel.sum_scalar_over_dp(float(batch.n_scored))
+        return float(max(batch.n_scored, 1))
+
+    def compute_loss(self, dbatch: PackedBatch, normalizer):
+        if self.loss_fn is not None:
+            return self.loss_fn(self.model, dbatch, normalizer)
+        return self.model(dbatch.input_ids, dbatch.position_ids, dbatch.cu_seqlens, dbatch.labels, normalizer)
+
+    def clip_and_step(self) -> None:
+        params = [p for p in self.model.parameters() if p.grad is not None]
+        if self.parallel is not None:
+            self.parallel.sync_gradients(self.model)
+            self.parallel.global_grad_sq_norm(self.model, self.grad_norm)
+        else:
+            self.grad_norm.accumulate([p.grad for p in params], first=True)
+        self.grad_norm.finish(self.max_grad_norm)
+        if hasattr(self.optimizer, "defer_grad_scale"):
+            self.optimizer.defer_grad_scale(self.grad_norm.coef)
+            self.optimizer.arm_skip(self.grad_norm.skip)
+        else:
+            torch.nn.utils.clip_grad_norm_(params, self.max_grad_norm)
+        self.optimizer.step()
+        if self.lr_scheduler is not None:
+            self.lr_scheduler.step()
+        self.optimizer.zero_grad(set_to_none=True)
+
+    # ---- the step -------------------------------------------------------------------------
+    def train_step(self, batch: PackedBatch, accumulate: bool = False) -> StepOutput:
+        """One micro-batch forward/backward; unless ``accumulate``, also clip + optimizer step."""
+        dbatch = self.to_device(batch)
+        normalizer = self.global_scored_tokens(batch)
+        loss = self.compute_loss(dbatch, normalizer)
+        loss.backward()
+        if not accumulate:
+            self.clip_and_step()
+            self.step_count += 1
+        return StepOutput(loss.detach(), self.grad_norm.norm, self.grad_norm.skip, batch.n_tokens)
+
+    @torch.no_grad()
+    def eval_step(self, batch: PackedBatch) -> torch.Tensor:
+        dbatch = self.to_device(batch)
+        return self.compute_loss(dbatch, float(max(batch.n_scored, 1))).detach()
