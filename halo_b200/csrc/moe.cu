@@ -210,7 +210,8 @@ __global__ void route_scan_kernel(int* __restrict__ block_hist, int n_blocks, in
 //   total_rows[0]                padded rows this rank receives
 __global__ void route_layout_kernel(const int* __restrict__ counts_all, int n_ranks, int E, int me,
                                     int* __restrict__ seg_start, int* __restrict__ seg_rows,
-                                    int* __restrict__ dst_base, int* __restrict__ total_rows) {
+                                    int* __restrict__ dst_base, int* __restrict__ total_rows,
+                                    int cap_rows, int* __restrict__ status) {
     const int e_loc = E / n_ranks;
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     for (int r = 0; r < n_ranks; ++r) {
@@ -225,12 +226,17 @@ __global__ void route_layout_kernel(const int* __restrict__ counts_all, int n_ra
             }
             dst_base[e] = row + before_me;
             if (r == me) {
-                seg_start[le] = row;
-                seg_rows[le] = rows;
+                // a segment that would run past the provisioned buffer is truncated (and flagged):
+                // its excess slots are dropped by the dispatch kernel's own bound check
+                const int s0 = min(row, cap_rows / 128 * 128);
+                const int fit = max(0, min(rows, cap_rows / 128 * 128 - s0));
+                seg_start[le] = s0;
+                seg_rows[le] = fit;
+                if (fit != rows && status) atomicCAS(status, kStatusOk, kStatusBounds);
             }
             row += (rows + 127) / 128 * 128;
         }
-        if (r == me) total_rows[0] = row;
+        if (r == me) total_rows[0] = min(row, cap_rows);
     }
 }
 
@@ -290,7 +296,7 @@ __global__ void __launch_bounds__(256)
 dispatch_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ topk_idx,
                      const int* __restrict__ slot_row, const float* __restrict__ slot_w,
                      const PeerPtrs bufs, const PeerPtrs wbufs, int has_w,
-                     long long T, int k, int H, int experts_per_rank) {
+                     long long T, int k, int H, int experts_per_rank, int cap_rows, int* status) {
     const long long t = blockIdx.x;
     const int nvec = H / 8;
     const uint4* src = reinterpret_cast<const uint4*>(x + t * H);
@@ -299,6 +305,11 @@ dispatch_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict_
         for (int j = 0; j < k; ++j) {
             const int row = slot_row[t * k + j];
             if (row < 0) continue;
+            if (row >= cap_rows) {
+                // the receive buffer was provisioned too small for this routing: never write past it
+                if (v == 0 && status) atomicCAS(status, kStatusOk, kStatusBounds);
+                continue;
+            }
             const int r = topk_idx[t * k + j] / experts_per_rank;
             reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(bufs.p[r]) + (long long)row * H)[v] = val;
         }
@@ -306,7 +317,7 @@ dispatch_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict_
     if (has_w && threadIdx.x < k) {
         const int j = threadIdx.x;
         const int row = slot_row[t * k + j];
-        if (row >= 0)
+        if (row >= 0 && row < cap_rows)
             reinterpret_cast<float*>(wbufs.p[topk_idx[t * k + j] / experts_per_rank])[row] = slot_w[t * k + j];
     }
 }
@@ -314,10 +325,10 @@ dispatch_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict_
 // Zero the pad rows [seg_start+seg_rows, next multiple of 128) of the local buffer.
 __global__ void __launch_bounds__(256)
 zero_pad_rows_kernel(__nv_bfloat16* __restrict__ buf, const int* __restrict__ seg_start,
-                     const int* __restrict__ seg_rows, int H) {
+                     const int* __restrict__ seg_rows, int H, int cap_rows) {
     const int le = blockIdx.x;
-    const int first = seg_start[le] + seg_rows[le];
-    const int last = (first + 127) / 128 * 128;
+    const int first = min(seg_start[le] + seg_rows[le], cap_rows);
+    const int last = min((first + 127) / 128 * 128, cap_rows);
     const int nvec = H / 8;
     for (int r = first + blockIdx.y; r < last; r += gridDim.y) {
         uint4* dst = reinterpret_cast<uint4*>(buf + (long long)r * H);
@@ -330,14 +341,14 @@ __global__ void __launch_bounds__(256)
 combine_rows_kernel(const PeerPtrs bufs, const int* __restrict__ topk_idx,
                     const int* __restrict__ slot_row, const float* __restrict__ w,
                     const __nv_bfloat16* __restrict__ addend, __nv_bfloat16* __restrict__ out,
-                    long long T, int k, int H, int experts_per_rank) {
+                    long long T, int k, int H, int experts_per_rank, int cap_rows) {
     const long long t = blockIdx.x;
     const int nvec = H / 8;
     for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         for (int j = 0; j < k; ++j) {
             const int row = slot_row[t * k + j];
-            if (row < 0) continue;
+            if (row < 0 || row >= cap_rows) continue;
             const int r = topk_idx[t * k + j] / experts_per_rank;
             const uint4 u = reinterpret_cast<const uint4*>(
                 reinterpret_cast<const __nv_bfloat16*>(bufs.p[r]) + (long long)row * H)[v];
@@ -371,9 +382,9 @@ combine_rows_kernel(const PeerPtrs bufs, const int* __restrict__ topk_idx,
 __global__ void __launch_bounds__(256)
 scale_rows_dot_kernel(__nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ y,
                       const float* __restrict__ scale, float* __restrict__ dwrow,
-                      const int* __restrict__ total_rows, int H) {
+                      const int* __restrict__ total_rows, int H, int cap_rows) {
     const int lane = threadIdx.x & 31;
-    const int rows = *total_rows;
+    const int rows = min(*total_rows, cap_rows);
     const int nvec = H / 8;
     for (long long r = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); r < rows; r += (long long)gridDim.x * 8) {
         uint4* gr = reinterpret_cast<uint4*>(g + r * H);
@@ -402,11 +413,11 @@ scale_rows_dot_kernel(__nv_bfloat16* __restrict__ g, const __nv_bfloat16* __rest
 __global__ void gather_slot_values_kernel(const PeerPtrs vbufs,
                                           const int* __restrict__ topk_idx,
                                           const int* __restrict__ slot_row, float* __restrict__ out,
-                                          long long n_slots, int experts_per_rank) {
+                                          long long n_slots, int experts_per_rank, int cap_rows) {
     const long long s = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (s >= n_slots) return;
     const int row = slot_row[s];
-    out[s] = row < 0 ? 0.f : reinterpret_cast<const float*>(vbufs.p[topk_idx[s] / experts_per_rank])[row];
+    out[s] = (row < 0 || row >= cap_rows) ? 0.f : reinterpret_cast<const float*>(vbufs.p[topk_idx[s] / experts_per_rank])[row];
 }
 
 // per-expert token counts for load metrics / balancing (no host sync)
@@ -464,10 +475,12 @@ int halo_route_count(const int* idx, long long n_slots, int E, int* block_hist, 
 }
 
 int halo_route_layout(const int* counts_all, int n_ranks, int E, int me, int* seg_start,
-                      int* seg_rows, int* dst_base, int* total_rows, void* stream) {
+                      int* seg_rows, int* dst_base, int* total_rows, int cap_rows, int* status,
+                      void* stream) {
     if (E % n_ranks) return -1;
     route_layout_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(counts_all, n_ranks, E, me, seg_start,
-                                                           seg_rows, dst_base, total_rows);
+                                                           seg_rows, dst_base, total_rows, cap_rows,
+                                                           status);
     return HALO_LAUNCH_CHECK();
 }
 
@@ -497,7 +510,7 @@ static int fill_peers(PeerPtrs* out, void* const* host_ptrs, int n) {
 // bufs / wbufs: HOST arrays of n_ranks device pointers (rank r's row buffer / per-row float buffer)
 int halo_dispatch_rows(const void* x, const int* idx, const int* slot_row, const float* slot_w,
                        void* const* bufs, void* const* wbufs, int n_ranks, long long T, int k, int H,
-                       int experts_per_rank, void* stream) {
+                       int experts_per_rank, int cap_rows, int* status, void* stream) {
     if (H % 8) return -1;
     if (T == 0) return 0;
     PeerPtrs pb, pw;
@@ -505,45 +518,45 @@ int halo_dispatch_rows(const void* x, const int* idx, const int* slot_row, const
     if (wbufs) { if (fill_peers(&pw, wbufs, n_ranks)) return -2; } else { for (int i = 0; i < kMaxPeers; ++i) pw.p[i] = nullptr; }
     dispatch_rows_kernel<<<(unsigned)T, 256, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)x, idx, slot_row, slot_w, pb, pw, wbufs ? 1 : 0, T, k, H,
-        experts_per_rank);
+        experts_per_rank, cap_rows, status);
     return HALO_LAUNCH_CHECK();
 }
 
 int halo_zero_pad_rows(void* buf, const int* seg_start, const int* seg_rows, int n_local, int H,
-                       void* stream) {
+                       int cap_rows, void* stream) {
     if (n_local == 0) return 0;
     zero_pad_rows_kernel<<<dim3(n_local, 16), 256, 0, (cudaStream_t)stream>>>(
-        (__nv_bfloat16*)buf, seg_start, seg_rows, H);
+        (__nv_bfloat16*)buf, seg_start, seg_rows, H, cap_rows);
     return HALO_LAUNCH_CHECK();
 }
 
 int halo_combine_rows(void* const* bufs, int n_ranks, const int* idx, const int* slot_row, const float* w,
                       const void* addend, void* out, long long T, int k, int H, int experts_per_rank,
-                      void* stream) {
+                      int cap_rows, void* stream) {
     if (H % 8) return -1;
     if (T == 0) return 0;
     PeerPtrs pb;
     if (fill_peers(&pb, bufs, n_ranks)) return -2;
     combine_rows_kernel<<<(unsigned)T, 256, 0, (cudaStream_t)stream>>>(
         pb, idx, slot_row, w, (const __nv_bfloat16*)addend,
-        (__nv_bfloat16*)out, T, k, H, experts_per_rank);
+        (__nv_bfloat16*)out, T, k, H, experts_per_rank, cap_rows);
     return HALO_LAUNCH_CHECK();
 }
 
 int halo_scale_rows_dot(void* g, const void* y, const float* scale, float* dwrow,
-                        const int* total_rows, int H, void* stream) {
+                        const int* total_rows, int H, int cap_rows, void* stream) {
     scale_rows_dot_kernel<<<1184, 256, 0, (cudaStream_t)stream>>>(
-        (__nv_bfloat16*)g, (const __nv_bfloat16*)y, scale, dwrow, total_rows, H);
+        (__nv_bfloat16*)g, (const __nv_bfloat16*)y, scale, dwrow, total_rows, H, cap_rows);
     return HALO_LAUNCH_CHECK();
 }
 
 int halo_gather_slot_values(void* const* vbufs, int n_ranks, const int* idx, const int* slot_row, float* out,
-                            long long n_slots, int experts_per_rank, void* stream) {
+                            long long n_slots, int experts_per_rank, int cap_rows, void* stream) {
     if (n_slots == 0) return 0;
     PeerPtrs pv;
     if (fill_peers(&pv, vbufs, n_ranks)) return -2;
     gather_slot_values_kernel<<<(unsigned)((n_slots + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-        pv, idx, slot_row, out, n_slots, experts_per_rank);
+        pv, idx, slot_row, out, n_slots, experts_per_rank, cap_rows);
     return HALO_LAUNCH_CHECK();
 }
 

@@ -37,8 +37,8 @@ class _SwiGLULinear(torch.autograd.Function):
     """act = silu(x Wg^T) * (x Wu^T) with the activation in the GEMM epilogue; recompute-free backward."""
 
     @staticmethod
-    def forward(ctx, x, w_gate_up):
-        act, pre = gemm.swiglu_matmul(x, w_gate_up, save_pre=torch.is_grad_enabled() or True)
+    def forward(ctx, x, w_gate_up, grad_mode=True):
+        act, pre = gemm.swiglu_matmul(x, w_gate_up, save_pre=grad_mode and any(ctx.needs_input_grad))
         ctx.save_for_backward(x, w_gate_up, pre)
         return act
 
@@ -59,7 +59,7 @@ class _SwiGLULinear(torch.autograd.Function):
             dpre = torch.cat([d * u * s * (1 + g * (1 - s)), d * g * s], dim=-1).to(pre.dtype)
         dx = gemm.matmul(dpre, w, b_t=False) if ctx.needs_input_grad[0] else None
         dw = gemm.matmul(dpre, x, a_t=True, b_t=False) if ctx.needs_input_grad[1] else None
-        return dx, dw
+        return dx, dw, None
 
 
 class _RouterLinear(torch.autograd.Function):
@@ -109,7 +109,7 @@ class DenseMLP(nn.Module):
         self.down_proj = nn.Parameter(torch.empty(hidden, width, dtype=dtype, device=device))
 
     def forward(self, h, ctx=None):
-        return gemm.linear(_SwiGLULinear.apply(h, self.gate_up_proj), self.down_proj)
+        return gemm.linear(_SwiGLULinear.apply(h, self.gate_up_proj, torch.is_grad_enabled()), self.down_proj)
 
 
 class SparseMoE(nn.Module):

@@ -28,7 +28,42 @@ class KernelError(RuntimeError):
     """A kernel entry point refused its arguments or a launch failed."""
 
 
-def lib() -> ctypes.CDLL:
+# kernels launched per entry point (entries that only compute sizes on the host launch none)
+_KERNELS_PER_CALL = {
+    "halo_rmsnorm_bwd": 2, "halo_qknorm_rope_bwd": 2, "halo_attn_bwd": 3, "halo_route_count": 2, "halo_sq_norm": 2,
+    "halo_rmsnorm_bwd_blocks": 0, "halo_qknorm_rope_bwd_blocks": 0, "halo_gemm_work_bytes": 0,
+    "halo_rmsnorm_supported": 0, "halo_route_blocks": 0, "halo_adam_elems_per_block": 0,
+}
+LAUNCHES = {"total": 0}
+
+
+class _CountingLib:
+    """Thin proxy over the CDLL that counts kernel launches, so a benchmark can report how many of
+    this library's kernels ran inside its timed region."""
+
+    def __init__(self, cdll):
+        self._cdll = cdll
+        self._cache = {}
+
+    def __getattr__(self, name):
+        fn = self._cache.get(name)
+        if fn is None:
+            raw = getattr(self._cdll, name)
+            n = _KERNELS_PER_CALL.get(name, 1)
+
+            def fn(*args, _raw=raw, _n=n):
+                LAUNCHES["total"] += _n
+                return _raw(*args)
+
+            self._cache[name] = fn
+        return fn
+
+
+def launch_count() -> int:
+    return LAUNCHES["total"]
+
+
+def lib():
     global _LIB
     if _LIB is not None:
         return _LIB
@@ -43,7 +78,7 @@ def lib() -> ctypes.CDLL:
                     raise KernelError(
                         f"the sm_100a kernel library {LIB_PATH} is missing and could not be built: {exc}"
                     ) from exc
-            _LIB = ctypes.CDLL(str(LIB_PATH))
+            _LIB = _CountingLib(ctypes.CDLL(str(LIB_PATH)))
     return _LIB
 
 

@@ -141,6 +141,7 @@ def _work_bytes() -> int:
 
 def plan_routing(topk_idx: torch.Tensor, n_experts: int, transport) -> RoutingState:
     T, k = topk_idx.shape
+    capacity = transport.capacity(T * k, n_experts // transport.n_ranks)
     dev = topk_idx.device
     L = _lib.lib()
     n_slots = T * k
@@ -159,13 +160,14 @@ def plan_routing(topk_idx: torch.Tensor, n_experts: int, transport) -> RoutingSt
     total_rows = torch.empty(1, dtype=torch.int32, device=dev)
     _lib.check(L.halo_route_layout(_lib.ptr(counts_all), _lib.c_int(transport.n_ranks), _lib.c_int(n_experts),
                                    _lib.c_int(transport.rank), _lib.ptr(seg_start), _lib.ptr(seg_rows),
-                                   _lib.ptr(dst_base), _lib.ptr(total_rows), s), "halo_route_layout")
+                                   _lib.ptr(dst_base), _lib.ptr(total_rows), _lib.c_int(capacity),
+                                   _lib.ptr(_lib.status_word(dev)), s), "halo_route_layout")
     slot_row = torch.empty(n_slots, dtype=torch.int32, device=dev)
     _lib.check(L.halo_route_place(_lib.ptr(idx), _lib.c_ll(n_slots), _lib.c_int(n_experts), _lib.ptr(block_hist),
                                   _lib.ptr(dst_base), _lib.ptr(slot_row), s), "halo_route_place")
     return RoutingState(
         n_tokens=T, top_k=k, n_experts=n_experts, n_local=n_local,
-        capacity=transport.capacity(n_slots, n_local), topk_idx=idx, slot_row=slot_row,
+        capacity=capacity, topk_idx=idx, slot_row=slot_row,
         seg_start=seg_start, seg_rows=seg_rows, total_rows=total_rows, counts=counts,
     )
 
@@ -263,7 +265,7 @@ def moe_ffn_reference(x, topk_idx, topk_w, w_gate_up, w_down, expert_offset: int
 # ---------------------------------------------------------------------------------------------
 class _MoEExperts(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, topk_idx, topk_w, w_gate_up, w_down, transport, state_out):
+    def forward(ctx, x, topk_idx, topk_w, w_gate_up, w_down, transport, state_out, grad_mode):
         T, H = x.shape
         E_local, F2, _ = w_gate_up.shape
         F = F2 // 2
@@ -279,12 +281,13 @@ class _MoEExperts(torch.autograd.Function):
         px = transport.peer_table(recv_x)
         py = transport.peer_table(y_rows)
         _lib.check(L.halo_zero_pad_rows(_lib.ptr(recv_x), _lib.ptr(state.seg_start), _lib.ptr(state.seg_rows),
-                                        _lib.c_int(state.n_local), _lib.c_int(H), s), "halo_zero_pad_rows")
+                                        _lib.c_int(state.n_local), _lib.c_int(H), _lib.c_int(cap), s), "halo_zero_pad_rows")
         _lib.check(L.halo_dispatch_rows(_lib.ptr(x), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
                                         _lib.c_void_p(0), px, _lib.c_void_p(0), _lib.c_int(transport.n_ranks), _lib.c_ll(T), _lib.c_int(k),
-                                        _lib.c_int(H), _lib.c_int(E_local), s), "halo_dispatch_rows")
+                                        _lib.c_int(H), _lib.c_int(E_local), _lib.c_int(cap),
+                                        _lib.ptr(_lib.status_word(dev)), s), "halo_dispatch_rows")
         transport.barrier()
-        need_grad = torch.is_grad_enabled() and any(ctx.needs_input_grad)
+        need_grad = grad_mode and any(ctx.needs_input_grad)
         act, pre = grouped_swiglu_ffn_fwd(state, recv_x, w_gate_up, w_down, save_pre=need_grad)
         grouped_down_fwd(state, act, w_down, y_rows)
         transport.barrier()
@@ -292,7 +295,7 @@ class _MoEExperts(torch.autograd.Function):
         w32 = topk_w.float().contiguous()
         _lib.check(L.halo_combine_rows(py, _lib.c_int(transport.n_ranks), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
                                        _lib.ptr(w32), _lib.c_void_p(0), _lib.ptr(out), _lib.c_ll(T), _lib.c_int(k),
-                                       _lib.c_int(H), _lib.c_int(E_local), s), "halo_combine_rows")
+                                       _lib.c_int(H), _lib.c_int(E_local), _lib.c_int(cap), s), "halo_combine_rows")
         if need_grad:
             if transport.transient_buffers:
                 recv_x, y_rows = recv_x.clone(), y_rows.clone()
@@ -321,15 +324,16 @@ class _MoEExperts(torch.autograd.Function):
         row_w.zero_()  # pad rows must scale to a finite value
         pdy, pw = transport.peer_table(dy), transport.peer_table(row_w)
         _lib.check(L.halo_zero_pad_rows(_lib.ptr(dy), _lib.ptr(state.seg_start), _lib.ptr(state.seg_rows),
-                                        _lib.c_int(state.n_local), _lib.c_int(H), s), "halo_zero_pad_rows")
+                                        _lib.c_int(state.n_local), _lib.c_int(H), _lib.c_int(cap), s), "halo_zero_pad_rows")
         _lib.check(L.halo_dispatch_rows(_lib.ptr(dout), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
                                         _lib.ptr(w32), pdy, pw, _lib.c_int(transport.n_ranks), _lib.c_ll(T), _lib.c_int(k),
-                                        _lib.c_int(H), _lib.c_int(E_local), s), "halo_dispatch_rows")
+                                        _lib.c_int(H), _lib.c_int(E_local), _lib.c_int(cap),
+                                        _lib.ptr(_lib.status_word(dev)), s), "halo_dispatch_rows")
         transport.barrier()
         # 2. expert side: routing-weight gradient per row, then dy = w * dout in place
         dwrow = transport.buffer("dwrow", cap, 1, torch.float32, dev)
         _lib.check(L.halo_scale_rows_dot(_lib.ptr(dy), _lib.ptr(y_rows), _lib.ptr(row_w), _lib.ptr(dwrow),
-                                         _lib.ptr(state.total_rows), _lib.c_int(H), s), "halo_scale_rows_dot")
+                                         _lib.ptr(state.total_rows), _lib.c_int(H), _lib.c_int(cap), s), "halo_scale_rows_dot")
         # 3. down projection: dact = dy W_down ; dW_down[e] = dy_e^T act_e
         dact = torch.empty((cap, F), dtype=torch.bfloat16, device=dev)
         lst = _tile_list(state, "m", n_cols=F, k_dim=H, b_mn_stride=0, b_k_stride=H, swiglu_f=0)
@@ -354,12 +358,12 @@ class _MoEExperts(torch.autograd.Function):
         pdx, pdw = transport.peer_table(dx_rows), transport.peer_table(dwrow)
         _lib.check(L.halo_combine_rows(pdx, _lib.c_int(transport.n_ranks), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
                                        _lib.c_void_p(0), _lib.c_void_p(0), _lib.ptr(dx), _lib.c_ll(T), _lib.c_int(k),
-                                       _lib.c_int(H), _lib.c_int(E_local), s), "halo_combine_rows")
+                                       _lib.c_int(H), _lib.c_int(E_local), _lib.c_int(cap), s), "halo_combine_rows")
         dw = torch.empty((T, k), dtype=torch.float32, device=dev)
         _lib.check(L.halo_gather_slot_values(pdw, _lib.c_int(transport.n_ranks), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
-                                             _lib.ptr(dw), _lib.c_ll(T * k), _lib.c_int(E_local), s),
+                                             _lib.ptr(dw), _lib.c_ll(T * k), _lib.c_int(E_local), _lib.c_int(cap), s),
                    "halo_gather_slot_values")
-        return dx, None, dw, dw_gate_up, dw_down, None, None
+        return dx, None, dw, dw_gate_up, dw_down, None, None, None
 
 
 def moe_experts(x, topk_idx, topk_w, w_gate_up, w_down, transport=None, state_out: list | None = None):
@@ -375,4 +379,5 @@ def moe_experts(x, topk_idx, topk_w, w_gate_up, w_down, transport=None, state_ou
         if transport.n_ranks > 1:
             return transport.reference_ffn(x, topk_idx, topk_w, w_gate_up, w_down)
         return moe_ffn_reference(x, topk_idx, topk_w, w_gate_up, w_down, offset)
-    return _MoEExperts.apply(x.contiguous(), topk_idx, topk_w, w_gate_up, w_down, transport, state_out)
+    return _MoEExperts.apply(x.contiguous(), topk_idx, topk_w, w_gate_up, w_down, transport, state_out,
+                             torch.is_grad_enabled())
