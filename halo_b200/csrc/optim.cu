@@ -60,29 +60,42 @@ struct AdamTable {
     int n_tensors;
 };
 
+// One tensor described by value in the kernel parameters (no device-side table to upload).
+struct AdamSingle {
+    void* p;
+    const void* g;
+    void* m;
+    void* v;
+    long long numel;
+    unsigned long long name_hash;
+};
+
 constexpr int kAdamThreads = 256;
 constexpr int kAdamElemsPerBlock = kAdamThreads * 4 * 16;
 
 template <bool GRAD_F32>
 __global__ void __launch_bounds__(kAdamThreads)
-adamw_bf16_kernel(AdamTable tab, float beta1, float beta2, float one_minus_beta1,
+adamw_bf16_kernel(AdamTable tab, AdamSingle one, float beta1, float beta2, float one_minus_beta1,
                   float one_minus_beta2, float step_size, float bc2_sqrt, float eps, float wd_factor,
                   unsigned long long key_step, const float* __restrict__ grad_scale,
                   const int* __restrict__ skip) {
     if (skip && *skip) return;
     // which tensor does this block belong to
+    const bool single = tab.n_tensors == 0;
     int lo = 0, hi = tab.n_tensors;
     while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
         if (tab.block_start[mid] <= (int)blockIdx.x) lo = mid; else hi = mid;
     }
     const int ti = lo;
-    const long long n = tab.numel[ti];
-    const long long chunk0 = (long long)(blockIdx.x - tab.block_start[ti]) * kAdamElemsPerBlock;
-    __nv_bfloat16* p = (__nv_bfloat16*)tab.p[ti];
-    __nv_bfloat16* m = (__nv_bfloat16*)tab.m[ti];
-    __nv_bfloat16* v = (__nv_bfloat16*)tab.v[ti];
-    const uint64_t mixed = splitmix64(splitmix64(key_step) ^ tab.name_hash[ti]);
+    const long long n = single ? one.numel : tab.numel[ti];
+    const long long chunk0 =
+        (long long)(blockIdx.x - (single ? 0 : tab.block_start[ti])) * kAdamElemsPerBlock;
+    __nv_bfloat16* p = (__nv_bfloat16*)(single ? one.p : tab.p[ti]);
+    __nv_bfloat16* m = (__nv_bfloat16*)(single ? one.m : tab.m[ti]);
+    __nv_bfloat16* v = (__nv_bfloat16*)(single ? one.v : tab.v[ti]);
+    const void* gptr = single ? one.g : tab.g[ti];
+    const uint64_t mixed = splitmix64(splitmix64(key_step) ^ (single ? one.name_hash : tab.name_hash[ti]));
     const uint32_t k0 = (uint32_t)mixed, k1 = (uint32_t)(mixed >> 32);
     float scale = 1.f;
     const bool has_scale = grad_scale != nullptr;
@@ -122,10 +135,10 @@ adamw_bf16_kernel(AdamTable tab, float beta1, float beta2, float one_minus_beta1
             }
         }
         if (GRAD_F32) {
-            const float* g = (const float*)tab.g[ti];
+            const float* g = (const float*)gptr;
             for (int j = 0; j < 4; ++j) gf[j] = j < cnt ? g[e0 + j] : 0.f;
         } else {
-            const __nv_bfloat16* g = (const __nv_bfloat16*)tab.g[ti];
+            const __nv_bfloat16* g = (const __nv_bfloat16*)gptr;
             for (int j = 0; j < 4; ++j) gf[j] = j < cnt ? __bfloat162float(g[e0 + j]) : 0.f;
         }
         __nv_bfloat16 po[4], mo[4], vo[4];
@@ -242,14 +255,36 @@ int halo_adamw_bf16_step(void* const* p, const void* const* g, void* const* m, v
                          const float* grad_scale, const int* skip, void* stream) {
     if (n_tensors <= 0 || total_blocks <= 0) return 0;
     AdamTable t{p, g, m, v, numel, name_hash, block_start, n_tensors};
+    AdamSingle one{};
     const float omb1 = (float)(1.0 - (double)beta1), omb2 = (float)(1.0 - (double)beta2);
     cudaStream_t s = (cudaStream_t)stream;
     if (grad_is_f32)
         adamw_bf16_kernel<true><<<total_blocks, kAdamThreads, 0, s>>>(
-            t, beta1, beta2, omb1, omb2, step_size, bc2_sqrt, eps, wd_factor, key ^ step, grad_scale, skip);
+            t, one, beta1, beta2, omb1, omb2, step_size, bc2_sqrt, eps, wd_factor, key ^ step, grad_scale, skip);
     else
         adamw_bf16_kernel<false><<<total_blocks, kAdamThreads, 0, s>>>(
-            t, beta1, beta2, omb1, omb2, step_size, bc2_sqrt, eps, wd_factor, key ^ step, grad_scale, skip);
+            t, one, beta1, beta2, omb1, omb2, step_size, bc2_sqrt, eps, wd_factor, key ^ step, grad_scale, skip);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// One tensor, every pointer passed by value: the form the host-state optimizer streams buckets with.
+int halo_adamw_bf16_step_single(void* p, const void* g, void* m, void* v, long long numel,
+                                unsigned long long name_hash, int grad_is_f32, float beta1, float beta2,
+                                float step_size, float bc2_sqrt, float eps, float wd_factor,
+                                unsigned long long key, unsigned long long step, const float* grad_scale,
+                                const int* skip, void* stream) {
+    if (numel <= 0) return 0;
+    AdamTable t{};
+    AdamSingle one{p, g, m, v, numel, name_hash};
+    const float omb1 = (float)(1.0 - (double)beta1), omb2 = (float)(1.0 - (double)beta2);
+    const long long blocks = (numel + kAdamElemsPerBlock - 1) / kAdamElemsPerBlock;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (grad_is_f32)
+        adamw_bf16_kernel<true><<<(unsigned)blocks, kAdamThreads, 0, s>>>(
+            t, one, beta1, beta2, omb1, omb2, step_size, bc2_sqrt, eps, wd_factor, key ^ step, grad_scale, skip);
+    else
+        adamw_bf16_kernel<false><<<(unsigned)blocks, kAdamThreads, 0, s>>>(
+            t, one, beta1, beta2, omb1, omb2, step_size, bc2_sqrt, eps, wd_factor, key ^ step, grad_scale, skip);
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

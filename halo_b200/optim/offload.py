@@ -1,0 +1,131 @@
+"""AdamWBF16 with the moments of the large tensors kept in page-locked host memory.
+
+A model whose weights, gradients and both moments do not fit one GPU (the 30B-A3B shape on a single
+B200: 8 bytes per parameter = 244 GB) can still take exact AdamWBF16 steps: the two bf16 moments
+of every large tensor live in host memory and stream through a double-buffered device staging area
+while the step kernel runs - host->device copy of bucket i+1, update of bucket i and device->host
+copy of bucket i-1 overlap on three streams. The arithmetic, the rounding noise and the clip / skip
+contract are those of :class:`AdamWBF16`; only the placement of the state differs.
+
+The reference has no counterpart: it shards optimizer state over ranks instead
+(halo/checkpoint/parallel/optimizer.py) and does not run its large MoE shapes on one GPU.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from halo_b200.ops import _lib
+
+from .adamw_bf16 import AdamWBF16, param_name_hash
+
+HOST_STATE_MIN_NUMEL = 8 * 1024 * 1024  # smaller tensors keep their moments on the device
+
+
+def _pinned_zeros(numel: int, dtype: torch.dtype) -> torch.Tensor:
+    """Zero-filled host tensor registered with CUDA as page-locked, without the size rounding of
+    torch's pinned-memory cache (which would waste up to 2x on multi-hundred-MB tensors)."""
+    t = torch.zeros(numel, dtype=dtype)
+    if torch.cuda.is_available():
+        rc = torch.cuda.cudart().cudaHostRegister(t.data_ptr(), t.numel() * t.element_size(), 0)
+        if int(rc) != 0:
+            raise RuntimeError(f"cudaHostRegister failed with {rc} for {t.numel() * t.element_size()} bytes")
+    return t
+
+
+class HostStateAdamWBF16(AdamWBF16):
+    def __init__(self, params, *args, host_min_numel: int = HOST_STATE_MIN_NUMEL, **kwargs):
+        super().__init__(params, *args, **kwargs)
+        self.host_min_numel = host_min_numel
+        self._staging = None
+        self._streams = None
+        self._slot_free = None
+
+    def _on_host(self, p) -> bool:
+        return p.is_cuda and p.dtype == torch.bfloat16 and p.numel() >= self.host_min_numel
+
+    def _state_for(self, p, group):
+        st = self.state[p]
+        if not st and self._on_host(p):
+            st["step"] = 0
+            st["exp_avg"] = _pinned_zeros(p.numel(), torch.bfloat16)
+            st["exp_avg_sq"] = _pinned_zeros(p.numel(), torch.bfloat16)
+            st["host_state"] = True
+            return st
+        return super()._state_for(p, group)
+
+    def _ensure_staging(self, device, max_numel: int):
+        if self._staging is None or self._staging[0][0].numel() < max_numel:
+            self._staging = [
+                (torch.empty(max_numel, dtype=torch.bfloat16, device=device),
+                 torch.empty(max_numel, dtype=torch.bfloat16, device=device))
+                for _ in range(2)
+            ]
+            self._streams = (torch.cuda.Stream(device), torch.cuda.Stream(device))
+            self._slot_free = [torch.cuda.Event(), torch.cuda.Event()]
+            for ev in self._slot_free:
+                ev.record(torch.cuda.current_stream(device))
+
+    def _cuda_step(self, gi, items, device, gdtype, b1, b2, step_size, bc2_sqrt, eps, wd_factor, step):
+        on_dev = [it for it in items if not it[2].get("host_state")]
+        on_host = [it for it in items if it[2].get("host_state")]
+        if on_dev:
+            super()._cuda_step(gi, on_dev, device, gdtype, b1, b2, step_size, bc2_sqrt, eps, wd_factor, step)
+        if not on_host:
+            return
+        L = _lib.lib()
+        self._ensure_staging(device, max(p.numel() for _, p, _ in on_host))
+        h2d, d2h = self._streams
+        compute = torch.cuda.current_stream(device)
+        # the copies read the gradient scale / skip words only through the kernel, nothing to order there
+        for i, (name, p, st) in enumerate(on_host):
+            slot = i & 1
+            n = p.numel()
+            m_dev, v_dev = self._staging[slot][0][:n], self._staging[slot][1][:n]
+            h2d.wait_event(self._slot_free[slot])
+            with torch.cuda.stream(h2d):
+                m_dev.copy_(st["exp_avg"], non_blocking=True)
+                v_dev.copy_(st["exp_avg_sq"], non_blocking=True)
+                ev_in = torch.cuda.Event()
+                ev_in.record(h2d)
+            compute.wait_event(ev_in)
+            g = p.grad.contiguous()
+            rc = L.halo_adamw_bf16_step_single(
+                _lib.ptr(p), _lib.ptr(g), _lib.ptr(m_dev), _lib.ptr(v_dev), _lib.c_ll(n),
+                ctypes.c_ulonglong(param_name_hash(name)), _lib.c_int(1 if gdtype == torch.float32 else 0),
+                _lib.c_float(b1), _lib.c_float(b2), _lib.c_float(step_size), _lib.c_float(bc2_sqrt),
+                _lib.c_float(eps), _lib.c_float(wd_factor), ctypes.c_ulonglong(self.key), ctypes.c_ulonglong(step),
+                _lib.ptr(self._grad_scale), _lib.ptr(self._skip), _lib.stream_ptr(device),
+            )
+            _lib.check(rc, "halo_adamw_bf16_step_single")
+            ev_done = torch.cuda.Event()
+            ev_done.record(compute)
+            d2h.wait_event(ev_done)
+            with torch.cuda.stream(d2h):
+                st["exp_avg"].copy_(m_dev, non_blocking=True)
+                st["exp_avg_sq"].copy_(v_dev, non_blocking=True)
+                self._slot_free[slot].record(d2h)
+
+    def synchronize_state(self) -> None:
+        """Wait until every moment written by the last step has landed in host memory (call before
+        reading the state, e.g. to save a checkpoint)."""
+        if self._streams is not None:
+            for s in self._streams:
+                s.synchronize()
+
+    def state_bytes_on_host(self) -> int:
+        total = 0
+        for st in self.state.values():
+            if st.get("host_state"):
+                total += 2 * st["exp_avg"].numel() * 2
+        return total
+
+    @staticmethod
+    def expected_step_seconds(host_bytes: int, pcie_gbs: float = 50.0) -> float:
+        """Lower bound of the streamed part of a step: every moment crosses PCIe once each way,
+        both directions concurrently."""
+        return host_bytes / (pcie_gbs * 1e9) if host_bytes else 0.0
+
+

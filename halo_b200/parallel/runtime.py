@@ -1,0 +1,162 @@
+"""Run-time side of the parallel layout on one NVLink/NVSwitch box: the expert-parallel transport
+over peer-mapped (symmetric) memory and the gradient synchronisation of the replicated parameters.
+
+``SymmetricTransport`` gives the MoE kernels what they need to move tokens themselves: one set of
+row buffers per rank, allocated once through ``torch.distributed._symmetric_memory`` so that every
+rank holds a device pointer to every peer's buffer, plus a device-side barrier between the push,
+compute and pull phases. The kernels then store to / load from peer memory directly; no collective
+library call carries token data.
+
+``ParallelRuntime`` owns the groups of a run and the per-step reductions: replicated (non-expert)
+gradients are summed over the data-parallel group, expert gradients over the expert-replica group
+when experts are replicated, and the global gradient norm is assembled from the pieces each group
+tiles exactly once.
+
+Counterpart of the reference's EP config / dispatcher plumbing and gradient sweeps
+(halo/distributed/expert_parallel/config.py:149-280, halo/trainers/parallelism/grad_sync.py:159-210,
+halo/trainers/parallelism/grad_clipping.py:161-228).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from halo_b200.ops import _lib
+
+
+class SymmetricTransport:
+    """Expert-parallel transport over peer-mapped buffers of one process group."""
+
+    def __init__(self, group, device, capacity_factor: float = 1.5):
+        self.group = group
+        self.device = torch.device(device)
+        self.n_ranks = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.capacity_factor = capacity_factor
+        self._bufs: dict[str, tuple[torch.Tensor, object]] = {}
+        self._cap = None
+        self._hidden = None
+        self._barrier_handle = None
+        self.stable_until_backward = True
+
+    # ---- provisioning ---------------------------------------------------------------------
+    def configure(self, max_tokens: int, top_k: int, hidden: int, n_local_experts: int) -> None:
+        """Allocate the row buffers for the largest batch this run will route (collective call)."""
+        import torch.distributed._symmetric_memory as symm
+
+        mean_rows = max_tokens * top_k  # every rank sends max_tokens * top_k slots; on average it receives as many
+        cap = int(self.capacity_factor * mean_rows) + 128 * n_local_experts
+        cap = (cap + 127) // 128 * 128
+        self._cap, self._hidden = cap, hidden
+        for name, cols, dtype in (("recv_x", hidden, torch.bfloat16), ("y_rows", hidden, torch.bfloat16),
+                                  ("recv_dy", hidden, torch.bfloat16), ("dx_rows", hidden, torch.bfloat16),
+                                  ("row_w", 1, torch.float32), ("dwrow", 1, torch.float32)):
+            t = symm.empty((cap, cols), dtype=dtype, device=self.device)
+            hdl = symm.rendezvous(t, self.group)
+            self._bufs[name] = (t, hdl)
+        self._barrier_handle = self._bufs["recv_x"][1]
+
+    def capacity(self, n_slots: int, n_local_experts: int) -> int:
+        if self._cap is None:
+            raise RuntimeError("SymmetricTransport.configure() must run before the first MoE layer")
+        return self._cap
+
+    def buffer(self, name: str, rows: int, cols: int, dtype: torch.dtype, device) -> torch.Tensor:
+        t, _ = self._bufs[name]
+        if t.shape[0] < rows or t.shape[1] != cols or t.dtype != dtype:
+            raise RuntimeError(f"symmetric buffer {name!r} {tuple(t.shape)} cannot serve [{rows}, {cols}] {dtype}")
+        return t
+
+    def peer_table(self, buf: torch.Tensor):
+        for t, hdl in self._bufs.values():
+            if t.data_ptr() == buf.data_ptr():
+                ptrs = list(hdl.buffer_ptrs)
+                return (_lib.c_void_p * self.n_ranks)(*ptrs)
+        raise RuntimeError("peer_table() needs a buffer handed out by this transport")
+
+    # ---- control plane -----------------------------------------------------------------------
+    def exchange_counts(self, counts: torch.Tensor) -> torch.Tensor:
+        """All ranks' per-expert slot counts, ``[n_ranks, E]`` (tiny; NCCL all-gather)."""
+        out = torch.empty((self.n_ranks, counts.numel()), dtype=counts.dtype, device=counts.device)
+        dist.all_gather_into_tensor(out, counts.contiguous(), group=self.group)
+        return out
+
+    def barrier(self) -> None:
+        """Device-side barrier on the current stream: peer stores issued before it are visible to
+        peer loads issued after it. Bounded by the symmetric-memory barrier's own timeout."""
+        self._barrier_handle.barrier(channel=0)
+
+    @property
+    def transient_buffers(self) -> bool:
+        # the buffers are reused by the next MoE layer; with per-layer recomputation the backward of a
+        # layer runs right after its own forward, so they are still intact then
+        return not self.stable_until_backward
+
+    def reference_ffn(self, x, topk_idx, topk_w, w_gate_up, w_down):
+        raise RuntimeError("the CPU expert-parallel path uses GlooTransport (halo_b200.parallel.expert_parallel)")
+
+
+class ParallelRuntime:
+    """Groups and per-step reductions of one run."""
+
+    def __init__(self, device, dp_group=None, ep_group=None, expert_replica_group=None, transport=None):
+        self.device = torch.device(device)
+        self.dp_group = dp_group
+        self.ep_group = ep_group
+        self.expert_replica_group = expert_replica_group
+        self.transport = transport
+        self.dp_world = dist.get_world_size(dp_group) if dp_group is not None else 1
+        self.ep_world = dist.get_world_size(ep_group) if ep_group is not None else 1
+        self._flat = None
+
+    @classmethod
+    def for_expert_parallel(cls, world: int, device) -> "ParallelRuntime":
+        """EP over every rank of the job; the non-expert parameters are replicated over the same ranks."""
+        group = dist.group.WORLD
+        transport = SymmetricTransport(group, device)
+        return cls(device, dp_group=group, ep_group=group, expert_replica_group=None, transport=transport)
+
+    # ---- scalars -----------------------------------------------------------------------------
+    def sum_scalar_over_dp(self, value: float) -> torch.Tensor:
+        t = torch.tensor([value], dtype=torch.float32, device=self.device)
+        dist.all_reduce(t, group=self.dp_group)
+        return t.clamp_min(1.0)
+
+    # ---- gradients ---------------------------------------------------------------------------
+    @staticmethod
+    def split_params(model):
+        experts, shared = [], []
+        for p in model.parameters():
+            if p.grad is None:
+                continue
+            (experts if getattr(p, "is_expert", False) else shared).append(p)
+        return experts, shared
+
+    def sync_gradients(self, model) -> None:
+        """Sum the replicated parameters' gradients over the data-parallel group (the loss is already
+        normalised by the global token count, so a sum is the average the optimizer wants)."""
+        experts, shared = self.split_params(model)
+        if self.dp_world > 1 and shared:
+            by_dtype: dict[torch.dtype, list] = {}
+            for p in shared:
+                by_dtype.setdefault(p.grad.dtype, []).append(p.grad)
+            for grads in by_dtype.values():
+                flat = torch.cat([g.reshape(-1) for g in grads])
+                dist.all_reduce(flat, group=self.dp_group)
+                off = 0
+                for g in grads:
+                    n = g.numel()
+                    g.copy_(flat[off:off + n].view_as(g))
+                    off += n
+        if self.expert_replica_group is not None and experts:
+            for p in experts:
+                dist.all_reduce(p.grad, group=self.expert_replica_group)
+
+    def global_grad_sq_norm(self, model, grad_norm) -> None:
+        """total_sq = ||replicated grads||^2 (counted once) + sum over EP ranks of ||expert grads||^2."""
+        experts, shared = self.split_params(model)
+        grad_norm.accumulate([p.grad for p in experts], first=True)
+        if self.ep_world > 1:
+            dist.all_reduce(grad_norm.total_sq, group=self.ep_group)
+        grad_norm.accumulate([p.grad for p in shared], first=False)

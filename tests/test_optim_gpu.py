@@ -26,6 +26,9 @@ def test_adamw_bf16_bit_exact(grad_dtype):
     for step in range(3):
         for (_, pc), (_, pg), g in zip(cpu, gpu, gs):
             gg = (g * (step + 1)).to(grad_dtype)
+            if grad_dtype != pc.dtype:
+                pc.grad_dtype = grad_dtype
+                pg.grad_dtype = grad_dtype
             pc.grad = gg.clone()
             pg.grad = gg.clone().cuda()
         scale = torch.tensor([0.37])
