@@ -1,0 +1,156 @@
+"""Environment knobs of the framework, read through one small set of typed readers.
+
+Names keep the reference's prefixes (``HALO_``, ``DIST_``, ``NVLINK_``) so an existing launch
+environment carries over (halo/env.py:33-158). A blank value counts as unset; a malformed value
+warns once and falls back to the default rather than silently flipping a knob.
+"""
+
+from __future__ import annotations
+
+import logging
+import os
+from datetime import timedelta
+
+log = logging.getLogger(__name__)
+
+_TRUE = frozenset({"1", "true", "yes", "on"})
+_FALSE = frozenset({"0", "false", "no", "off"})
+_warned: set[str] = set()
+
+DEFAULT_NCCL_TIMEOUT_MINUTES = 30
+DEFAULT_STORE_TIMEOUT_HOURS = 4
+DEFAULT_FS_PROBE_TIMEOUT_SECONDS = 60
+WATCHDOG_WARN_FRACTION = 0.8
+
+# every knob this package reads, with its meaning (kept complete by tests/test_foundations.py)
+CATALOGUE = {
+    "HALO_DATA_ROOT": "scratch directory for profiles, caches and run logs",
+    "HALO_LOG_LEVEL": "root log level of the framework's handler",
+    "HALO_WEIGHT_SYNC_CHUNK_MB": "size of one packed trainer->rollout weight chunk",
+    "HALO_WEIGHT_SYNC_GATHER_AHEAD": "expert layers gathered ahead of the one being sent",
+    "HALO_EP_CAPACITY_FACTOR": "receive-buffer rows per rank as a multiple of the mean load",
+    "HALO_KERNEL_WAIT_MS": "host-side bound on waits for a device event",
+    "HALO_BOUNDED_WAIT_SECONDS": "deadline of a bounded stream wait in weight sync",
+    "DIST_NCCL_TIMEOUT_MINUTES": "collective watchdog of every process group",
+    "DIST_STORE_TIMEOUT_HOURS": "timeout of store-based joins that outlast the watchdog",
+    "DIST_FS_PROBE_TIMEOUT_SECONDS": "how long to poll for the shared-filesystem sentinel",
+    "DIST_INPUT_SHARED_FILESYSTEM": "inputs are on a filesystem every node sees",
+    "DIST_OUTPUT_SHARED_FILESYSTEM": "outputs go to a filesystem every node sees",
+    "NVLINK_DOMAIN_SIZE": "ranks per NVLink domain (overrides detection)",
+}
+
+
+def _raw(name: str) -> str | None:
+    v = os.environ.get(name)
+    return v if v is not None and v.strip() else None
+
+
+def _warn_once(name: str, msg: str) -> None:
+    if name not in _warned:
+        _warned.add(name)
+        log.warning(msg)
+
+
+def env_flag(name: str, default: bool = False) -> bool:
+    v = _raw(name)
+    if v is None:
+        return default
+    low = v.strip().lower()
+    if low in _TRUE:
+        return True
+    if low in _FALSE:
+        return False
+    _warn_once(name, f"ignoring {name}={v!r}: expected one of 1/true/yes/on/0/false/no/off; using {default}")
+    return default
+
+
+def env_int(name: str, default: int | None) -> int | None:
+    v = _raw(name)
+    if v is None:
+        return default
+    try:
+        return int(v)
+    except ValueError:
+        _warn_once(name, f"ignoring {name}={v!r}: expected an integer; using {default}")
+        return default
+
+
+def env_float(name: str, default: float | None) -> float | None:
+    v = _raw(name)
+    if v is None:
+        return default
+    try:
+        return float(v)
+    except ValueError:
+        _warn_once(name, f"ignoring {name}={v!r}: expected a number; using {default}")
+        return default
+
+
+def env_positive_int(name: str, default: int) -> int:
+    v = env_int(name, default)
+    if v is None or v < 1:
+        _warn_once(name, f"ignoring {name}={v!r}: expected a positive integer; using {default}")
+        return default
+    return v
+
+
+def env_non_negative_int(name: str, default: int) -> int:
+    v = env_int(name, default)
+    if v is None or v < 0:
+        _warn_once(name, f"ignoring {name}={v!r}: expected a non-negative integer; using {default}")
+        return default
+    return v
+
+
+def env_positive_float(name: str, default: float) -> float:
+    v = env_float(name, default)
+    if v is None or v <= 0:
+        _warn_once(name, f"ignoring {name}={v!r}: expected a positive number; using {default}")
+        return default
+    return v
+
+
+def env_str(name: str, default: str | None = None) -> str | None:
+    v = os.environ.get(name)
+    return default if v is None else v
+
+
+def nccl_timeout() -> timedelta:
+    return timedelta(minutes=env_positive_int("DIST_NCCL_TIMEOUT_MINUTES", DEFAULT_NCCL_TIMEOUT_MINUTES))
+
+
+def store_timeout() -> timedelta:
+    return timedelta(hours=env_positive_int("DIST_STORE_TIMEOUT_HOURS", DEFAULT_STORE_TIMEOUT_HOURS))
+
+
+def fs_probe_timeout() -> timedelta:
+    return timedelta(seconds=env_positive_int("DIST_FS_PROBE_TIMEOUT_SECONDS", DEFAULT_FS_PROBE_TIMEOUT_SECONDS))
+
+
+def watchdog_bounded_seconds() -> float:
+    """Longest one rank may block outside a collective before its peers' watchdog is at risk."""
+    return nccl_timeout().total_seconds() * WATCHDOG_WARN_FRACTION
+
+
+def data_root() -> str:
+    return env_str("HALO_DATA_ROOT") or os.path.join(os.path.expanduser("~"), ".cache", "halo_b200")
+
+
+def data_path(*parts: str) -> str:
+    return os.path.join(data_root(), *parts)
+
+
+def torch_trace_dir() -> str:
+    return data_path("profiling", "torch")
+
+
+def weight_sync_chunk_bytes() -> int:
+    return env_positive_int("HALO_WEIGHT_SYNC_CHUNK_MB", 1024) * 1024 * 1024
+
+
+def weight_sync_gather_ahead() -> int:
+    return env_non_negative_int("HALO_WEIGHT_SYNC_GATHER_AHEAD", 1)
+
+
+def ep_capacity_factor() -> float:
+    return env_positive_float("HALO_EP_CAPACITY_FACTOR", 1.5)

@@ -224,25 +224,20 @@ class Qwen3Model(nn.Module):
         std = self.cfg.initializer_range
         from halo_b200.optim.adamw_bf16 import param_name_hash
 
-        n_local = self.layers[0].mlp.experts_gate_up.shape[0] if self.cfg.is_moe and len(self.layers) and hasattr(self.layers[0].mlp, "experts_gate_up") else 0
         for name, p in self.named_parameters():
             if p.dim() == 1:
                 p.fill_(1.0)
                 continue
             dev = p.device
-            if getattr(p, "is_expert", False) and self.transport.n_ranks > 1:
-                # draw the full expert bank deterministically, keep this rank's slice
-                g = torch.Generator(device=dev).manual_seed((seed * 1000003 + param_name_hash(name)) % (2**63))
-                e0 = self.transport.rank * n_local
-                full_e = self.cfg.num_experts
-                for e in range(full_e):
-                    if e0 <= e < e0 + n_local:
-                        p[e - e0].normal_(0.0, std, generator=g)
-                    else:
-                        # advance the generator identically without keeping the values
-                        torch.empty(p.shape[1:], dtype=p.dtype, device=dev).normal_(0.0, std, generator=g)
+            base = (seed * 1000003 + param_name_hash(name)) % (2**62)
+            if getattr(p, "is_expert", False):
+                # one generator per (parameter, global expert): any sharding draws the same values
+                e0 = self.transport.rank * p.shape[0]
+                for le in range(p.shape[0]):
+                    g = torch.Generator(device=dev).manual_seed(base + e0 + le)
+                    p[le].normal_(0.0, std, generator=g)
             else:
-                g = torch.Generator(device=dev).manual_seed((seed * 1000003 + param_name_hash(name)) % (2**63))
+                g = torch.Generator(device=dev).manual_seed(base)
                 p.normal_(0.0, std, generator=g)
 
     # ---- forward -----------------------------------------------------------------------------

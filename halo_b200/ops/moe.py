@@ -374,7 +374,7 @@ def moe_experts(x, topk_idx, topk_w, w_gate_up, w_down, transport=None, state_ou
     """
     if transport is None:
         transport = LocalTransport()
-    if not x.is_cuda:
+    if not x.is_cuda or hasattr(transport, "reference_ffn") and not hasattr(transport, "peer_table"):
         offset = transport.rank * w_gate_up.shape[0]
         if transport.n_ranks > 1:
             return transport.reference_ffn(x, topk_idx, topk_w, w_gate_up, w_down)

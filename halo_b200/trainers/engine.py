@@ -71,7 +71,12 @@ class TrainEngine:
             self.optimizer.defer_grad_scale(self.grad_norm.coef)
             self.optimizer.arm_skip(self.grad_norm.skip)
         else:
-            torch.nn.utils.clip_grad_norm_(params, self.max_grad_norm)
+            # a stock optimizer: apply the (device-resident) clip coefficient in place; a non-finite
+            # norm zeroes the update by zeroing the gradients
+            keep = (self.grad_norm.skip == 0).to(torch.float32)
+            coef = torch.nan_to_num(self.grad_norm.coef * keep, nan=0.0)
+            for p in params:
+                p.grad.nan_to_num_(nan=0.0, posinf=0.0, neginf=0.0).mul_(coef.to(p.grad.dtype))
         self.optimizer.step()
         if self.lr_scheduler is not None:
             self.lr_scheduler.step()
