@@ -1,0 +1,95 @@
+"""Runtime parameter names <-> Hugging Face hub tensor names.
+
+At run time attention holds one fused ``qkv_proj``, the dense FFN one ``gate_up_proj`` and the
+routed experts two stacked banks; on disk a checkpoint uses the hub names of Qwen3 / Qwen3-MoE
+(``q_proj`` / ``k_proj`` / ``v_proj``, ``gate_proj`` / ``up_proj``, ``experts.{e}.gate_proj`` ...)
+so ``transformers`` loads it without custom code. The expert bank layouts are the kinds of the
+reference's ``ExpertLayout`` (halo/models/moe/expert_layout.py:63-163): this family is
+``SEPARATE_GLU`` on the hub and ``FUSED`` at run time.
+"""
+
+from __future__ import annotations
+
+import re
+
+import torch
+
+EXPERT_LAYOUT_KINDS = ("FUSED", "FUSED_SPLIT_PER_EXPERT", "SEPARATE_GLU", "SEPARATE_MLP", "INTERLEAVED_GLU")
+_LAYER = re.compile(r"^layers\.(\d+)\.(.+)$")
+
+
+def runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, expert_offset: int = 0) -> dict:
+    """One runtime tensor -> {hub name: tensor}. ``first_layer``: global index of ``layers.0`` (pipeline
+    stages); ``expert_offset``: global index of local expert 0 (expert-parallel shards)."""
+    if name == "embed_tokens":
+        return {"model.embed_tokens.weight": tensor}
+    if name == "norm":
+        return {"model.norm.weight": tensor}
+    if name == "lm_head":
+        return {"lm_head.weight": tensor}
+    m = _LAYER.match(name)
+    if not m:
+        raise KeyError(f"no hub name for runtime parameter {name!r}")
+    li, rest = int(m.group(1)) + first_layer, m.group(2)
+    pre = f"model.layers.{li}."
+    D, Hq, Hkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+    if rest in ("input_layernorm", "post_attention_layernorm"):
+        return {pre + rest + ".weight": tensor}
+    if rest == "self_attn.qkv_proj":
+        q, k, v = tensor.split([Hq * D, Hkv * D, Hkv * D], dim=0)
+        return {pre + "self_attn.q_proj.weight": q, pre + "self_attn.k_proj.weight": k,
+                pre + "self_attn.v_proj.weight": v}
+    if rest == "self_attn.o_proj":
+        return {pre + "self_attn.o_proj.weight": tensor}
+    if rest in ("self_attn.q_norm", "self_attn.k_norm"):
+        return {pre + rest + ".weight": tensor}
+    if rest == "mlp.gate_up_proj":
+        g, u = tensor.chunk(2, dim=0)
+        return {pre + "mlp.gate_proj.weight": g, pre + "mlp.up_proj.weight": u}
+    if rest == "mlp.down_proj":
+        return {pre + "mlp.down_proj.weight": tensor}
+    if rest == "mlp.gate":
+        return {pre + "mlp.gate.weight": tensor}
+    if rest == "mlp.experts_gate_up":
+        out = {}
+        for le in range(tensor.shape[0]):
+            g, u = tensor[le].chunk(2, dim=0)
+            out[pre + f"mlp.experts.{le + expert_offset}.gate_proj.weight"] = g
+            out[pre + f"mlp.experts.{le + expert_offset}.up_proj.weight"] = u
+        return out
+    if rest == "mlp.experts_down":
+        return {pre + f"mlp.experts.{le + expert_offset}.down_proj.weight": tensor[le] for le in range(tensor.shape[0])}
+    if rest == "mlp.shared_expert.gate_up_proj":
+        g, u = tensor.chunk(2, dim=0)
+        return {pre + "mlp.shared_expert.gate_proj.weight": g, pre + "mlp.shared_expert.up_proj.weight": u}
+    if rest == "mlp.shared_expert.down_proj":
+        return {pre + "mlp.shared_expert.down_proj.weight": tensor}
+    if rest == "mlp.shared_gate":
+        return {pre + "mlp.shared_expert_gate.weight": tensor}
+    raise KeyError(f"no hub name for runtime parameter {name!r}")
+
+
+def hub_sources(name: str, shape, cfg, first_layer: int = 0, expert_offset: int = 0) -> list[tuple[str, tuple]]:
+    """Inverse view used by the loader: the hub tensors a runtime parameter is assembled from, each
+    with the index of the destination slice ``(dim0 start, dim0 stop[, expert])``."""
+    probe = torch.empty(shape, device="meta")
+    pieces = runtime_to_hub(name, probe, cfg, first_layer, expert_offset)
+    out, row = [], 0
+    m = _LAYER.match(name)
+    rest = m.group(2) if m else name
+    if rest in ("mlp.experts_gate_up", "mlp.experts_down"):
+        F = cfg.moe_intermediate_size
+        for hub in pieces:
+            e = int(re.search(r"experts\.(\d+)\.", hub).group(1)) - expert_offset
+            if hub.endswith("gate_proj.weight"):
+                out.append((hub, (e, 0, F)))
+            elif hub.endswith("up_proj.weight"):
+                out.append((hub, (e, F, 2 * F)))
+            else:
+                out.append((hub, (e, 0, shape[1])))
+        return out
+    for hub, t in pieces.items():
+        n = t.shape[0]
+        out.append((hub, (None, row, row + n)))
+        row += n
+    return out

@@ -1,0 +1,104 @@
+"""Model saves. The ladder picks the saver from the parallel layout (pipeline stages -> expert
+parallel (gathered | sharded) -> data parallel / single process), and every saver ends in the same
+standard layout: ``config.json`` + SafeTensors shards under hub names, loadable by
+``transformers.AutoModelForCausalLM.from_pretrained`` (halo/checkpoint/parallel/save.py:63-104,
+halo/checkpoint/parallel/ep.py:134-325).
+
+Gathered expert-parallel save: the non-expert tensors come from the writer rank's replica; then,
+layer by layer, each expert bank is all-gathered over the expert group and converted to per-expert
+hub tensors on the writer, so peak extra memory is one layer's experts.
+"""
+
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.distributed as dist
+
+from halo_b200.runtime.consensus import DeferredRankFailure
+
+from .atomic import atomic_write_json, remove_stale_staged
+from .hub_layout import runtime_to_hub
+from .writing import StreamingShardWriter
+
+COMPLETE_MARKER = "trainer_state.json"
+
+
+def _ep_info(model):
+    tr = getattr(model, "transport", None)
+    n = getattr(tr, "n_ranks", 1) if tr is not None else 1
+    r = getattr(tr, "rank", 0) if tr is not None else 0
+    g = getattr(tr, "group", None)
+    return n, r, g
+
+
+def _gather_expert_bank(t: torch.Tensor, n_ranks: int, group) -> torch.Tensor:
+    if n_ranks == 1:
+        return t
+    out = torch.empty((n_ranks,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+    dist.all_gather_into_tensor(out, t.contiguous(), group=group)
+    return out.reshape((n_ranks * t.shape[0],) + tuple(t.shape[1:]))
+
+
+def save_model(model, directory: str, is_writer: bool | None = None, save_dtype: torch.dtype | None = torch.bfloat16,
+               max_shard_bytes: int = 5 * 1024**3, sharded_experts: bool = False, extra_state: dict | None = None) -> None:
+    """COLLECTIVE over the expert group when experts are sharded. ``is_writer``: this rank writes the
+    files (default: global rank 0). ``sharded_experts``: every rank writes only its own experts to
+    ``ep_shard_<rank>/`` (merge offline with halo_b200.checkpoint.tools.merge_ep_shards)."""
+    cfg = model.cfg
+    n_ep, ep_rank, ep_group = _ep_info(model)
+    live = dist.is_available() and dist.is_initialized()
+    rank = dist.get_rank() if live else 0
+    if is_writer is None:
+        is_writer = rank == 0
+    guard = DeferredRankFailure()
+    first_layer = model.layer_range[0]
+    writer = None
+    with guard.catch():
+        if sharded_experts and n_ep > 1:
+            directory_w = os.path.join(directory, f"ep_shard_{ep_rank:05d}")
+            writer = StreamingShardWriter(directory_w, max_shard_bytes, save_dtype)
+        elif is_writer:
+            remove_stale_staged(directory)
+            writer = StreamingShardWriter(directory, max_shard_bytes, save_dtype)
+    # 1. non-expert tensors (replicated: taken from the writer's copy)
+    with guard.catch():
+        for name, p in model.named_parameters():
+            if getattr(p, "is_expert", False):
+                continue
+            if writer is not None and is_writer:
+                for hub, t in runtime_to_hub(name, p.detach(), cfg, first_layer).items():
+                    writer.add(hub, t)
+    # 2. expert banks, one layer at a time
+    for name, p in model.named_parameters():
+        if not getattr(p, "is_expert", False):
+            continue
+        if sharded_experts and n_ep > 1:
+            with guard.catch():
+                for hub, t in runtime_to_hub(name, p.detach(), cfg, first_layer, ep_rank * p.shape[0]).items():
+                    writer.add(hub, t)
+            continue
+        full = _gather_expert_bank(p.detach(), n_ep, ep_group)   # collective: every rank takes part
+        with guard.catch():
+            if is_writer and writer is not None:
+                for hub, t in runtime_to_hub(name, full, cfg, first_layer, 0).items():
+                    writer.add(hub, t)
+        del full
+    with guard.catch():
+        if writer is not None:
+            writer.finish()
+        if is_writer:
+            cfg.save(directory)
+            if extra_state is not None:
+                atomic_write_json(os.path.join(directory, "halo_state.json"), extra_state)
+    guard.raise_if_any(None if not live else dist.group.WORLD, "saving the model failed")
+
+
+def mark_complete(directory: str, trainer_state: dict) -> None:
+    """Written last: a checkpoint without it is incomplete and never resumed from."""
+    atomic_write_json(os.path.join(directory, COMPLETE_MARKER), trainer_state)
+
+
+def is_complete(directory: str) -> bool:
+    return os.path.isfile(os.path.join(directory, COMPLETE_MARKER))
