@@ -43,6 +43,8 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=65536)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run reduced)")
     ap.add_argument("--optimizer-state", default="auto", choices=["auto", "device", "host"])
+    ap.add_argument("--activation-reserve-gb", type=float, default=42.0,
+                    help="device memory kept free of optimizer state for activations, workspaces and staging")
     ap.add_argument("--doc-dist", default="loguniform")
     ap.add_argument("--lr", type=float, default=1e-5)
     return ap.parse_args()
@@ -190,7 +192,11 @@ def main() -> int:
     if opt_state == "host":
         from halo_b200.optim.offload import HostStateAdamWBF16
 
-        opt = HostStateAdamWBF16(named, lr=args.lr, weight_decay=0.01)
+        # moments stay on the device for as many tensors as fit beside gradients, activations and staging
+        free_bytes, _ = torch.cuda.mem_get_info(dev)
+        reserve = int(args.activation_reserve_gb * 1e9)
+        budget = max(0, free_bytes - 2 * local_params - reserve)
+        opt = HostStateAdamWBF16(named, lr=args.lr, weight_decay=0.01, device_state_budget_bytes=budget)
     else:
         opt = AdamWBF16(named, lr=args.lr, weight_decay=0.01)
     engine = TrainEngine(model, opt, dev, max_grad_norm=1.0, parallel=parallel)
@@ -270,6 +276,7 @@ def main() -> int:
                 "doc_lengths": f"{args.doc_dist} in [256, 16384]",
                 "l2": "activations and weights per step are far larger than the 126 MB L2 (no flush needed)",
                 "params_total": counts["total"], "peak_gib": round(peak_gib, 1),
+                "optimizer_state_on_host_gb": round(getattr(opt, "state_bytes_on_host", lambda: 0)() / 1e9, 1),
             },
             "clocks": clocks,
             "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e / args.steps, 2),

@@ -26,6 +26,13 @@ constexpr float kLog2e = 1.4426950408889634f;
 int make_tmap_bf16(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld,
                    int box_rows);  // gemm_sm100.cu
 
+// 2^x on the special-function unit (one MUFU op; inputs here are <= 8 after max subtraction)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // byte offset of the 16-byte chunk holding column `col` (multiple of 8) of row `row` inside a
 // [rows x 64] bf16 half-tile stored with the 128-byte swizzle
 __device__ __forceinline__ uint32_t swz_off(int row, int col) {
@@ -166,7 +173,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     if (!diag || cc + i <= row) mx = fmaxf(mx, s);
                 }
             }
-            const float alpha = exp2f((m - mx) * c);
+            const float alpha = fast_exp2((m - mx) * c);
             const float mc = mx * c;
             float rs = 0.f;
 #pragma unroll 1
@@ -177,8 +184,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float p0 = exp2f(__uint_as_float(r[i]) * c - mc);
-                    float p1 = exp2f(__uint_as_float(r[i + 1]) * c - mc);
+                    float p0 = fast_exp2(__uint_as_float(r[i]) * c - mc);
+                    float p1 = fast_exp2(__uint_as_float(r[i + 1]) * c - mc);
                     if (diag) {
                         if (cc + i > row) p0 = 0.f;
                         if (cc + i + 1 > row) p1 = 0.f;
@@ -441,7 +448,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    float pe = exp2f(__uint_as_float(r[i]) * c - s_lse[it & 1][cc + i]);
+                    float pe = fast_exp2(__uint_as_float(r[i]) * c - s_lse[it & 1][cc + i]);
                     if (need_mask && (long long)qr + cc + i < key_abs) pe = 0.f;
                     pv[cc + i] = pe;
                 }
@@ -665,7 +672,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    float pe = exp2f(__uint_as_float(r[i]) * c - lse2);
+                    float pe = fast_exp2(__uint_as_float(r[i]) * c - lse2);
                     if (need_mask && (long long)k0 + cc + i > q_abs) pe = 0.f;
                     pv[cc + i] = pe * (__uint_as_float(d[i]) - dl) * p.scale;
                 }
@@ -718,6 +725,240 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Forward, second form: 64-key tiles, the running output accumulates in TMEM and is rescaled
+// only when a row maximum grows by more than 2^8 (so the exponentials stay bounded without a
+// rescale on every tile), and the CTA is small enough (112 KiB of shared memory, 256 TMEM
+// columns, <= 168 registers) for two CTAs to share an SM: while one CTA's softmax warps work on
+// a score tile, the other CTA's MMAs run, which is what keeps the tensor cores busy.
+// Work items are the {q0, kv0, n_kv (64-key tiles), q_end} records also used by the dQ kernel.
+// ---------------------------------------------------------------------------------------------
+// Q + 2 x (K, V) = 96 KiB. P has no buffer of its own: once S = Q K^T has completed, the K tile
+// of the stage is dead, so P (same 16 KiB) is written over it and the stage is released after P V.
+constexpr int kFwd2Tiles = kTileBytes + 2 * 2 * kHalfTile;
+constexpr int kFwd2Smem = kFwd2Tiles + 256;                              // + barriers and scalars
+
+// 160 registers: six warps of 160 x 32 registers fit twice into the 64K-register file (the
+// allocation granularity makes 168 miss it)
+// 128 registers: warps are allotted to the four register-file partitions in whole groups of four,
+// so a 6-warp CTA is charged for 8; two CTAs per SM then need <= 65536 / (2 * 8 * 32) registers.
+__global__ void __maxnreg__(128)
+attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+    if (status_poisoned(p.status)) return;
+    extern __shared__ __align__(1024) uint8_t smem2[];
+    const uint32_t base = smem_u32(smem2);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem2 + kFwd2Tiles);
+    // bars[0]=q, [1..2]=kv_full, [3..4]=kv_empty, [5]=s_full[0], [6]=p_ready, [7]=o_full, [8]=s_full[1]
+    uint32_t* tmem_slot_p = reinterpret_cast<uint32_t*>(smem2 + kFwd2Tiles + 80);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem2 + kFwd2Tiles + 88);
+    if (base & 1023u) {
+        if (threadIdx.x == 0 && p.status) atomicCAS(p.status, kStatusOk, kStatusBadArgument);
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t sQ = base, sKV = base + kTileBytes;
+    const uint32_t bar_q = smem_u32(&bars[0]), bar_p_ready = smem_u32(&bars[6]), bar_o_full = smem_u32(&bars[7]);
+    const uint32_t bar_s_full[2] = {smem_u32(&bars[5]), smem_u32(&bars[8])};
+    const int head = blockIdx.x;
+    const int kv_head = head / (p.Hq / p.Hkv);
+    const FwdWork w = p.work[blockIdx.y];
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        mbar_init(bar_q, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&bars[1 + s]), 1);
+            mbar_init(smem_u32(&bars[3 + s]), 1);
+        }
+        mbar_init(bar_s_full[0], 1);
+        mbar_init(bar_s_full[1], 1);
+        mbar_init(bar_p_ready, 128);
+        mbar_init(bar_o_full, 1);
+        mbar_fence_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(smem_u32(tmem_slot_p), 256);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem0 = *tmem_slot_p;
+    // two 64-column score buffers so the next tile's Q K^T runs while this tile's softmax does
+    const uint32_t tS = tmem0, tO = tmem0 + 128;
+
+    if (warp == 4) {
+        if (lane == 0) {
+            mbar_expect_tx(bar_q, kTileBytes);
+            tma_load_2d(sQ, &tmQ, bar_q, head * kHd, w.q0);
+            tma_load_2d(sQ + 16384, &tmQ, bar_q, head * kHd + 64, w.q0);
+            for (int j = 0; j < w.n_kv; ++j) {
+                const int st = j & 1;
+                if (!mbar_wait(smem_u32(&bars[3 + st]), ((j >> 1) & 1) ^ 1u, abort_flag, p.status)) break;
+                const uint32_t full = smem_u32(&bars[1 + st]);
+                const uint32_t sK = sKV + st * 2 * kHalfTile, sV = sK + kHalfTile;
+                const int kr = w.kv0 + j * 64;
+                mbar_expect_tx(full, 2 * kHalfTile);
+                tma_load_2d(sK, &tmK, full, kv_head * kHd, kr);
+                tma_load_2d(sK + 8192, &tmK, full, kv_head * kHd + 64, kr);
+                tma_load_2d(sV, &tmV, full, kv_head * kHd, kr);
+                tma_load_2d(sV + 8192, &tmV, full, kv_head * kHd + 64, kr);
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);
+            constexpr uint32_t idesc_o = make_idesc_bf16(128, 128, 0, 1);
+            bool ok = mbar_wait(bar_q, 0, abort_flag, p.status);
+            auto issue_s = [&](int j) -> bool {
+                const int st = j & 1;
+                const uint32_t sK = sKV + st * 2 * kHalfTile;
+                if (!mbar_wait(smem_u32(&bars[1 + st]), (j >> 1) & 1, abort_flag, p.status)) return false;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t offa = (ks >> 2) * 16384 + (ks & 3) * 32;
+                    const uint32_t offb = (ks >> 2) * 8192 + (ks & 3) * 32;
+                    tc_mma_f16(tS + st * 64, make_smem_desc(sQ + offa, 16, 1024),
+                               make_smem_desc(sK + offb, 16, 1024), idesc_s, ks != 0);
+                }
+                tc_commit(bar_s_full[st]);
+                return true;
+            };
+            if (ok && w.n_kv > 0) ok = issue_s(0);
+            for (int j = 0; ok && j < w.n_kv; ++j) {
+                const int st = j & 1;
+                const uint32_t sK = sKV + st * 2 * kHalfTile, sV = sK + kHalfTile;
+                if (j + 1 < w.n_kv && !issue_s(j + 1)) break;
+                if (!mbar_wait(bar_p_ready, j & 1, abort_flag, p.status)) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    // P sits where this stage's K tile was
+                    tc_mma_f16(tO, make_smem_desc(sK + ks * 32, 16, 1024),
+                               make_smem_desc(sV + ks * 2048, 8192, 1024), idesc_o, (j | ks) != 0);
+                }
+                tc_commit(bar_o_full);
+                tc_commit(smem_u32(&bars[3 + st]));
+            }
+        }
+    } else {
+        const int row = warp * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const float c = p.scale * kLog2e;
+        const long long q_abs = (long long)w.q0 + row;
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < w.n_kv; ++j) {
+            if (!mbar_wait(bar_s_full[j & 1], (j >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t tSj = tS + (j & 1) * 64;
+            const int k0 = w.kv0 + j * 64;
+            const bool need_mask = (k0 + 63 > w.q0);
+            const uint32_t sP = sKV + (j & 1) * 2 * kHalfTile;
+            float mx = m_ref;
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+                uint32_t r[32];
+                tmem_ld_32x32(tSj + lane_base + half * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (!need_mask || (long long)k0 + half * 32 + i <= q_abs) mx = fmaxf(mx, __uint_as_float(r[i]));
+            }
+            // the previous P V product must be done before P is overwritten or O is rescaled
+            if (j > 0 && !mbar_wait(bar_o_full, (j - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+            const bool grow = (mx - m_ref) * c > 8.f;   // also true on the first tile (m_ref = -inf)
+            if (__any_sync(0xffffffffu, grow)) {
+                const float alpha = fast_exp2((m_ref - mx) * c);
+                if (j > 0) {
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int cc = 0; cc < 128; cc += 32) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(tO + lane_base + cc, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                        tmem_st_32x32(tO + lane_base + cc, r);
+                    }
+                    tmem_st_wait();
+                }
+                l *= alpha;
+                m_ref = mx;
+            }
+            const float mc = m_ref * c;
+            float rs = 0.f;
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+                uint32_t r[32];
+                tmem_ld_32x32(tSj + lane_base + half * 32, r);   // second read of the tile: cheaper than 64 live registers
+                tmem_ld_wait();
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0 = fast_exp2(__uint_as_float(r[i]) * c - mc);
+                    float p1 = fast_exp2(__uint_as_float(r[i + 1]) * c - mc);
+                    if (need_mask) {
+                        if ((long long)k0 + half * 32 + i > q_abs) p0 = 0.f;
+                        if ((long long)k0 + half * 32 + i + 1 > q_abs) p1 = 0.f;
+                    }
+                    pk[i >> 1] = pack_bf16(p0, p1);
+                    const float2 pf = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&pk[i >> 1]));
+                    rs += pf.x + pf.y;
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const uint32_t a = sP + swz_off(row, half * 32 + q * 8);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(pk[4 * q]),
+                                 "r"(pk[4 * q + 1]), "r"(pk[4 * q + 2]), "r"(pk[4 * q + 3])
+                                 : "memory");
+                }
+            }
+            l += rs;
+            fence_proxy_async_smem();
+            tc_fence_before();
+            mbar_arrive(bar_p_ready);
+        }
+        if (ok && mbar_wait(bar_o_full, (w.n_kv - 1) & 1, abort_flag, p.status)) {
+            tc_fence_after();
+            const bool live = q_abs < w.q_end;
+            const float inv = 1.f / l;
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.O) + q_abs * p.ldo + head * kHd;
+#pragma unroll 1
+            for (int cc = 0; cc < 128; cc += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tO + lane_base + cc, r);
+                tmem_ld_wait();
+                if (live) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8)
+                        *reinterpret_cast<uint4*>(out + cc + i) = make_uint4(
+                            pack_bf16(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv),
+                            pack_bf16(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv),
+                            pack_bf16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv),
+                            pack_bf16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv));
+                }
+            }
+            if (live) p.lse[(long long)head * p.T + q_abs] = m_ref * p.scale + logf(l);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) { }
+        __syncthreads();
+    }
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem0, 256);
+    }
+}
+
+
 static int set_smem(const void* fn, int bytes) {
     return cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess ? 0 : -10;
 }
@@ -747,6 +988,65 @@ int halo_attn_fwd(const void* q, const void* k, const void* v, void* o, float* l
     AttnParams p{reinterpret_cast<const FwdWork*>(work), o, lse, ldo, T, Hq, Hkv, scale, status};
     attn_fwd_kernel<<<dim3(Hq, n_tiles), kFwdThreads, kFwdSmem, (cudaStream_t)stream>>>(tq, tk, tv, p);
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Second form of the forward (64-key tiles, two CTAs per SM). work: n_tiles {q0, kv0, n_kv64, q_end}.
+int halo_attn_fwd2(const void* q, const void* k, const void* v, void* o, float* lse, const void* work,
+                   int n_tiles, long long T, int Hq, int Hkv, int head_dim, long long ldq,
+                   long long ldk, long long ldv, long long ldo, float scale, int* status, void* stream) {
+    if (head_dim != kHd || Hq % Hkv) return -1;
+    if (n_tiles == 0) return 0;
+    CUtensorMap tq, tk, tv;
+    if (make_tmap_bf16(&tq, q, T, (long long)Hq * kHd, ldq, 128)) return -2;
+    if (make_tmap_bf16(&tk, k, T, (long long)Hkv * kHd, ldk, 64)) return -3;
+    if (make_tmap_bf16(&tv, v, T, (long long)Hkv * kHd, ldv, 64)) return -4;
+    static bool cfg = false;
+    if (!cfg) {
+        if (set_smem((const void*)attn_fwd2_kernel, kFwd2Smem)) return -10;
+        // two CTAs per SM need the largest shared-memory carve-out
+        cudaFuncSetAttribute((const void*)attn_fwd2_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+        cfg = true;
+    }
+    AttnParams p{reinterpret_cast<const FwdWork*>(work), o, lse, ldo, T, Hq, Hkv, scale, status};
+    attn_fwd2_kernel<<<dim3(Hq, n_tiles), kFwdThreads, kFwd2Smem, (cudaStream_t)stream>>>(tq, tk, tv, p);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Resident CTAs per SM the second forward form achieves on the current device (diagnostic).
+int halo_attn_fwd2_occupancy() {
+    set_smem((const void*)attn_fwd2_kernel, kFwd2Smem);
+    cudaFuncSetAttribute((const void*)attn_fwd2_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
+    int n = -1;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_fwd2_kernel, kFwdThreads, kFwd2Smem);
+    cudaFuncAttributes a;
+    cudaFuncGetAttributes(&a, (const void*)attn_fwd2_kernel);
+    int n0 = -1, n64 = -1;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n0, attn_fwd2_kernel, kFwdThreads, 0);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n64, attn_fwd2_kernel, kFwdThreads, 65536);
+    for (int bs = 64; bs <= 512; bs *= 2) {
+        int o = -1;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&o, attn_fwd2_kernel, bs, 0);
+        fprintf(stderr, "fwd2 occ(block=%d, dyn=0)=%d\n", bs, o);
+    }
+    {
+        int o = -1;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&o, attn_delta_kernel, 256, 0);
+        fprintf(stderr, "delta kernel occ(256)=%d\n", o);
+        int dev = 0, v = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&v, cudaDevAttrMaxBlocksPerMultiprocessor, dev);
+        fprintf(stderr, "max blocks/SM=%d\n", v);
+        cudaDeviceGetAttribute(&v, cudaDevAttrMaxRegistersPerMultiprocessor, dev);
+        fprintf(stderr, "regs/SM=%d\n", v);
+        cudaDeviceGetAttribute(&v, cudaDevAttrMaxRegistersPerBlock, dev);
+        fprintf(stderr, "regs/block=%d\n", v);
+    }
+    fprintf(stderr, "fwd2: regs=%d static_smem=%zu local=%zu maxthreads=%d maxdyn=%d carveout=%d occ(dyn=0)=%d occ(64K)=%d occ(%d)=%d\n",
+            a.numRegs, a.sharedSizeBytes, a.localSizeBytes, a.maxThreadsPerBlock, a.maxDynamicSharedSizeBytes,
+            a.preferredShmemCarveout, n0, n64, kFwd2Smem, n);
+    return n;
 }
 
 // delta: [Hq, T] fp32 scratch. kv_work: n_kv_tiles {kv0, q_begin, n_q(64-row sub-tiles), q_end};

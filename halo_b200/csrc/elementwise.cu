@@ -412,14 +412,14 @@ cross_entropy_inplace_kernel(__nv_bfloat16* __restrict__ logits, const long long
         m = nm;
     }
     const float wm = warp_max(m);
-    s = warp_sum(s * __expf(m - wm));
+    s = warp_sum(m == -INFINITY ? 0.f : s * __expf(m - wm));  // a thread (or a whole warp) may own no column
     if (lane == 0) { sm[warp] = wm; ss[warp] = s; }
     __syncthreads();
     if (warp == 0) {
         float mm = lane < (int)(blockDim.x >> 5) ? sm[lane] : -INFINITY;
         float sv = lane < (int)(blockDim.x >> 5) ? ss[lane] : 0.f;
         const float gm = warp_max(mm);
-        sv = warp_sum(sv * __expf(mm - gm));
+        sv = warp_sum(mm == -INFINITY ? 0.f : sv * __expf(mm - gm));
         if (lane == 0) row_lse = gm + logf(sv);
     }
     __syncthreads();
@@ -468,7 +468,7 @@ logprob_entropy_kernel(const __nv_bfloat16* __restrict__ logits, const long long
         m = nm;
     }
     const float wm = warp_max(m);
-    const float sc = __expf(m - wm);
+    const float sc = (m == -INFINITY) ? 0.f : __expf(m - wm);  // a thread may own no column
     s = warp_sum(s * sc);
     tsum = warp_sum(tsum * sc);
     if (lane == 0) { sm[warp] = wm; ss[warp] = s; st[warp] = tsum; }
@@ -479,7 +479,7 @@ logprob_entropy_kernel(const __nv_bfloat16* __restrict__ logits, const long long
         float sv = lane < nw ? ss[lane] : 0.f;
         float tv = lane < nw ? st[lane] : 0.f;
         const float gm = warp_max(mm);
-        const float c2 = __expf(mm - gm);
+        const float c2 = (mm == -INFINITY) ? 0.f : __expf(mm - gm);
         sv = warp_sum(sv * c2);
         tv = warp_sum(tv * c2);
         if (lane == 0) {

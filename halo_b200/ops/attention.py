@@ -11,6 +11,7 @@ Stands where the reference resolves an attention backend (FA4 / FA2 varlen) for 
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import numpy as np
@@ -19,6 +20,23 @@ import torch
 from . import _lib
 
 HEAD_DIM = 128
+# 1: 128-key tiles, output rescaled in registers, one CTA per SM
+# 2: 64-key tiles, output accumulated in TMEM with lazy rescale, two CTAs per SM
+FWD_VARIANT = int(os.environ.get("HALO_ATTN_FWD_VARIANT", "2"))
+
+
+def _launch_fwd(L, q, k, v, o, lse, plan, T, n_heads, n_kv_heads, scale, dev):
+    if FWD_VARIANT == 2:
+        work, fn, what = plan.bwd_q, L.halo_attn_fwd2, "halo_attn_fwd2"
+    else:
+        work, fn, what = plan.fwd, L.halo_attn_fwd, "halo_attn_fwd"
+    rc = fn(
+        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse), _lib.ptr(work),
+        _lib.c_int(work.shape[0]), _lib.c_ll(T), _lib.c_int(n_heads), _lib.c_int(n_kv_heads),
+        _lib.c_int(HEAD_DIM), _lib.c_ll(_ld(q)), _lib.c_ll(_ld(k)), _lib.c_ll(_ld(v)), _lib.c_ll(_ld(o)),
+        _lib.c_float(scale), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev),
+    )
+    _lib.check(rc, what)
 
 
 @dataclass
@@ -113,14 +131,7 @@ class _FlashAttention(torch.autograd.Function):
         T = q.shape[0]
         o = torch.empty((T, n_heads * HEAD_DIM), dtype=torch.bfloat16, device=q.device)
         lse = torch.empty((n_heads, T), dtype=torch.float32, device=q.device)
-        L = _lib.lib()
-        rc = L.halo_attn_fwd(
-            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse), _lib.ptr(plan.fwd),
-            _lib.c_int(plan.fwd.shape[0]), _lib.c_ll(T), _lib.c_int(n_heads), _lib.c_int(n_kv_heads),
-            _lib.c_int(HEAD_DIM), _lib.c_ll(_ld(q)), _lib.c_ll(_ld(k)), _lib.c_ll(_ld(v)), _lib.c_ll(_ld(o)),
-            _lib.c_float(scale), _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr(q.device),
-        )
-        _lib.check(rc, "halo_attn_fwd")
+        _launch_fwd(_lib.lib(), q, k, v, o, lse, plan, T, n_heads, n_kv_heads, scale, q.device)
         ctx.save_for_backward(q, k, v, o, lse)
         ctx.plan, ctx.n_heads, ctx.n_kv_heads, ctx.scale = plan, n_heads, n_kv_heads, scale
         return o
@@ -188,13 +199,7 @@ class _RopeAttention(torch.autograd.Function):
         v = qkv[:, (n_heads + n_kv_heads) * HEAD_DIM :]
         o = torch.empty((T, n_heads * HEAD_DIM), dtype=torch.bfloat16, device=dev)
         lse = torch.empty((n_heads, T), dtype=torch.float32, device=dev)
-        rc = L.halo_attn_fwd(
-            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse), _lib.ptr(plan.fwd),
-            _lib.c_int(plan.fwd.shape[0]), _lib.c_ll(T), _lib.c_int(n_heads), _lib.c_int(n_kv_heads),
-            _lib.c_int(HEAD_DIM), _lib.c_ll(_ld(q)), _lib.c_ll(_ld(k)), _lib.c_ll(_ld(v)), _lib.c_ll(_ld(o)),
-            _lib.c_float(scale), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev),
-        )
-        _lib.check(rc, "halo_attn_fwd")
+        _launch_fwd(L, q, k, v, o, lse, plan, T, n_heads, n_kv_heads, scale, dev)
         ctx.save_for_backward(qkv, wq, wk, table, q, k, o, lse, rstd)
         ctx.meta = (plan, n_heads, n_kv_heads, use_norm, scale)
         return o

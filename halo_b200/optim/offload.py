@@ -3,8 +3,9 @@
 A model whose weights, gradients and both moments do not fit one GPU (the 30B-A3B shape on a single
 B200: 8 bytes per parameter = 244 GB) can still take exact AdamWBF16 steps: the two bf16 moments
 of every large tensor live in host memory and stream through a double-buffered device staging area
-while the step kernel runs - host->device copy of bucket i+1, update of bucket i and device->host
-copy of bucket i-1 overlap on three streams. The arithmetic, the rounding noise and the clip / skip
+while the step kernel runs - host->device copies of the next buckets, the update of bucket i and
+device->host copies of the previous ones overlap on three streams (four staging slots, so both
+DMA directions stay busy). The arithmetic, the rounding noise and the clip / skip
 contract are those of :class:`AdamWBF16`; only the placement of the state differs.
 
 The reference has no counterpart: it shards optimizer state over ranks instead
@@ -22,6 +23,7 @@ from halo_b200.ops import _lib
 from .adamw_bf16 import AdamWBF16, param_name_hash
 
 HOST_STATE_MIN_NUMEL = 8 * 1024 * 1024  # smaller tensors keep their moments on the device
+STAGING_SLOTS = 4  # >= 3 so that the host->device and device->host copies of neighbouring buckets overlap
 
 
 def _pinned_zeros(numel: int, dtype: torch.dtype) -> torch.Tensor:
@@ -36,9 +38,12 @@ def _pinned_zeros(numel: int, dtype: torch.dtype) -> torch.Tensor:
 
 
 class HostStateAdamWBF16(AdamWBF16):
-    def __init__(self, params, *args, host_min_numel: int = HOST_STATE_MIN_NUMEL, **kwargs):
+    def __init__(self, params, *args, host_min_numel: int = HOST_STATE_MIN_NUMEL,
+                 device_state_budget_bytes: int = 0, **kwargs):
         super().__init__(params, *args, **kwargs)
         self.host_min_numel = host_min_numel
+        # moments of large tensors stay on the device while this budget lasts (4 bytes per element)
+        self.device_budget = int(device_state_budget_bytes)
         self._staging = None
         self._streams = None
         self._slot_free = None
@@ -48,6 +53,9 @@ class HostStateAdamWBF16(AdamWBF16):
 
     def _state_for(self, p, group):
         st = self.state[p]
+        if not st and self._on_host(p) and self.device_budget >= 4 * p.numel():
+            self.device_budget -= 4 * p.numel()
+            return super()._state_for(p, group)
         if not st and self._on_host(p):
             st["step"] = 0
             st["exp_avg"] = _pinned_zeros(p.numel(), torch.bfloat16)
@@ -61,10 +69,10 @@ class HostStateAdamWBF16(AdamWBF16):
             self._staging = [
                 (torch.empty(max_numel, dtype=torch.bfloat16, device=device),
                  torch.empty(max_numel, dtype=torch.bfloat16, device=device))
-                for _ in range(2)
+                for _ in range(STAGING_SLOTS)
             ]
             self._streams = (torch.cuda.Stream(device), torch.cuda.Stream(device))
-            self._slot_free = [torch.cuda.Event(), torch.cuda.Event()]
+            self._slot_free = [torch.cuda.Event() for _ in range(STAGING_SLOTS)]
             for ev in self._slot_free:
                 ev.record(torch.cuda.current_stream(device))
 
@@ -81,7 +89,7 @@ class HostStateAdamWBF16(AdamWBF16):
         compute = torch.cuda.current_stream(device)
         # the copies read the gradient scale / skip words only through the kernel, nothing to order there
         for i, (name, p, st) in enumerate(on_host):
-            slot = i & 1
+            slot = i % STAGING_SLOTS
             n = p.numel()
             m_dev, v_dev = self._staging[slot][0][:n], self._staging[slot][1][:n]
             h2d.wait_event(self._slot_free[slot])
