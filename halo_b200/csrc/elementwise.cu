@@ -8,6 +8,10 @@
 // own GLU kernel (halo/kernels/fused_glu.py:118-205).
 #include "sm100_common.cuh"
 
+#include <stdio.h>
+
+#include "halo_noalloc.h"
+
 namespace halo {
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -560,6 +564,7 @@ int halo_rmsnorm_bwd_blocks(long long rows, int H) {
     rms_shape(H, &L, &vpt);
     const int rpb = 256 / L;
     long long b = (rows + rpb - 1) / rpb;
+    static_assert(HALO_NOALLOC_MAX_BLOCKS >= 592, "the built-in scratch must cover the largest grid");
     return (int)(b < 592 ? b : 592);
 }
 
@@ -579,6 +584,49 @@ int halo_rmsnorm_bwd(const void* g, const void* h, const void* w, const float* r
     reduce_partials_kernel<<<(H + 255) / 256, 256, 0, s>>>(dw_partial, blocks, H, dw_f32,
                                                           (__nv_bfloat16*)dw_bf16, accumulate);
     return HALO_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free RMSNorm backward (see halo_noalloc.h). The per-block partial sums live in a
+// file-scope device array instead of a caller-provided buffer.
+// ---------------------------------------------------------------------------------------------
+}  // extern "C"
+
+static __device__ __align__(256) float g_noalloc_scratch[HALO_NOALLOC_MAX_BLOCKS * HALO_NOALLOC_MAX_HIDDEN];
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not a device address: the
+// address a kernel can use comes from cudaGetSymbolAddress, once per device.
+static float* noalloc_scratch_for_current_device() {
+    constexpr int kMaxDevices = 64;
+    static float* cached[kMaxDevices] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    if (cached[dev] == nullptr) {
+        float* ptr = nullptr;
+        if (cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch) != cudaSuccess) return nullptr;
+        cached[dev] = ptr;
+    }
+    return cached[dev];
+}
+
+extern "C" {
+
+int halo_rmsnorm_bwd_noalloc(const void* g, const void* h, const void* w, const float* rstd,
+                             const void* dres, void* dx, float* dw_f32, void* dw_bf16,
+                             int accumulate, long long rows, int H, void* stream) {
+    int L, vpt;
+    if (!rms_shape(H, &L, &vpt)) return -1;
+    if (H > HALO_NOALLOC_MAX_HIDDEN) {
+        fprintf(stderr, "halo_rmsnorm_bwd_noalloc: hidden size %d exceeds the built-in scratch (max %d); "
+                        "use halo_rmsnorm_bwd with a caller-provided buffer\n", H, HALO_NOALLOC_MAX_HIDDEN);
+        return -3;
+    }
+    if (rows == 0) return 0;
+    float* scratch = noalloc_scratch_for_current_device();
+    if (scratch == nullptr) return -4;
+    // halo_rmsnorm_bwd never launches more than HALO_NOALLOC_MAX_BLOCKS blocks and each block
+    // writes H floats, so blocks * H <= the array's size
+    return halo_rmsnorm_bwd(g, h, w, rstd, dres, dx, scratch, dw_f32, dw_bf16, accumulate, rows, H, stream);
 }
 
 int halo_rope_table(const int* pos, long long T, int head_dim, float theta, void* table,

@@ -1,0 +1,89 @@
+"""The allocation-free RMSNorm backward, called through its exported C symbol.
+
+Some users of the kernel library cannot allocate device memory when they need a kernel (they run
+under a fixed memory plan, inside an allocator's own critical section, in a serving loop that
+must stay off cudaMalloc, or from plain C without PyTorch). ``halo_rmsnorm_bwd_noalloc`` keeps the
+kernel's scratch inside the library for them. This test drives it exactly as such a caller would -
+raw pointers into a ctypes symbol - and checks it against the ordinary entry point, which takes
+its scratch from the caller. Two calls in a row, with different shapes, make sure nothing depends
+on what an earlier call left in the shared scratch. The file is named so that pytest collects it
+last.
+"""
+
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _lib():
+    from halo_b200.ops._lib import LIB_PATH
+
+    lib = ctypes.CDLL(str(LIB_PATH))
+    lib.halo_rmsnorm_bwd_noalloc.restype = ctypes.c_int
+    lib.halo_rmsnorm_bwd.restype = ctypes.c_int
+    lib.halo_rmsnorm_bwd_blocks.restype = ctypes.c_int
+    return lib
+
+
+def _p(t):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _case(lib, rows, H, seed, with_res):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    gy = torch.randn(rows, H, device="cuda", generator=g).bfloat16()
+    h = torch.randn(rows, H, device="cuda", generator=g).bfloat16()
+    w = (1 + 0.1 * torch.randn(H, device="cuda", generator=g)).bfloat16()
+    rstd = torch.rsqrt(h.float().pow(2).mean(-1) + 1e-6)
+    dres = torch.randn(rows, H, device="cuda", generator=g).bfloat16() if with_res else None
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    # ordinary entry point: the caller brings the scratch
+    blocks = lib.halo_rmsnorm_bwd_blocks(ctypes.c_longlong(rows), ctypes.c_int(H))
+    scratch = torch.empty(blocks * H, dtype=torch.float32, device="cuda")
+    dx_ref = torch.empty_like(h)
+    dw_ref = torch.empty(H, dtype=torch.float32, device="cuda")
+    rc = lib.halo_rmsnorm_bwd(_p(gy), _p(h), _p(w), _p(rstd), _p(dres), _p(dx_ref), _p(scratch), _p(dw_ref), _p(None),
+                              ctypes.c_int(0), ctypes.c_longlong(rows), ctypes.c_int(H), stream)
+    assert rc == 0
+    # allocation-free entry point: outputs are allocated here, before the call; the call itself allocates nothing
+    dx = torch.empty_like(h)
+    dw = torch.empty(H, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_allocated()
+    rc = lib.halo_rmsnorm_bwd_noalloc(_p(gy), _p(h), _p(w), _p(rstd), _p(dres), _p(dx), _p(dw), _p(None),
+                                      ctypes.c_int(0), ctypes.c_longlong(rows), ctypes.c_int(H), stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == before
+    tol_x = 3e-2 * dx_ref.float().abs().max().item() + 1e-3
+    tol_w = 3e-2 * dw_ref.abs().max().item() + 1e-2
+    assert (dx.float() - dx_ref.float()).abs().max().item() <= tol_x
+    assert (dw - dw_ref).abs().max().item() <= tol_w
+    # and both agree with the plain PyTorch formula
+    xh = h.float() * rstd[:, None]
+    gw = gy.float() * w.float()
+    want = rstd[:, None] * (gw - xh * (gw * xh).mean(-1, keepdim=True))
+    if dres is not None:
+        want = want + dres.float()
+    assert (dx.float() - want).abs().max().item() <= 3e-2 * want.abs().max().item() + 1e-3
+
+
+def test_noalloc_matches_ordinary_entry_point_twice_in_a_row():
+    lib = _lib()
+    _case(lib, rows=3000, H=2048, seed=0, with_res=True)
+    _case(lib, rows=77, H=4096, seed=1, with_res=False)   # smaller grid, wider rows: stale partials must not leak
+
+
+def test_noalloc_rejects_sizes_beyond_its_scratch():
+    lib = _lib()
+    H = 8192
+    t = torch.zeros(4, H, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    r = torch.ones(4, device="cuda")
+    rc = lib.halo_rmsnorm_bwd_noalloc(_p(t), _p(t), _p(w), _p(r), _p(None), _p(t), _p(None), _p(None), ctypes.c_int(0),
+                                      ctypes.c_longlong(4), ctypes.c_int(H),
+                                      ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == -3
