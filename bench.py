@@ -27,6 +27,7 @@ import sys
 import threading
 import time
 
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
 REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)
 
@@ -43,7 +44,7 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=65536)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run reduced)")
     ap.add_argument("--optimizer-state", default="auto", choices=["auto", "device", "host"])
-    ap.add_argument("--activation-reserve-gb", type=float, default=42.0,
+    ap.add_argument("--activation-reserve-gb", type=float, default=64.0,
                     help="device memory kept free of optimizer state for activations, workspaces and staging")
     ap.add_argument("--doc-dist", default="loguniform")
     ap.add_argument("--lr", type=float, default=1e-5)
@@ -116,7 +117,8 @@ def reference_arm(args) -> int:
     ref_dir = os.path.join(REPO, "baseline", "_ref")
     why = None
     if not os.path.isdir(ref_dir):
-        why = "baseline/_ref is absent: the reference was not installable offline (see DESIGN.md)"
+        why = ("the reference could not be installed offline: its build backend (hatchling) and its runtime "
+               "dependencies trl, accelerate, peft and deep_ep are absent from the offline wheelhouse")
     else:
         sys.path.insert(0, ref_dir)
         missing = []

@@ -1,0 +1,189 @@
+"""Argument dataclasses shared by every training script: model, data, optimisation, run and
+parallelism (field names follow halo/configs/parallelism_arguments.py:22-288 and the Hugging Face
+``TrainingArguments`` names the reference's recipes use)."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Literal
+
+from halo_b200.config_validation import ConfigError
+from halo_b200.parallel.config import ParallelismConfig
+
+
+@dataclass
+class ModelArguments:
+    model_name_or_path: str = ""
+    model_preset: str = ""                  # one of halo_b200.models.config.PRESETS when training from scratch
+    init_from_scratch: bool = False
+    torch_dtype: Literal["bfloat16", "float32"] = "bfloat16"
+    trust_remote_code: bool = False
+    max_length: int = 0                     # 0 = the model's context window
+
+    def __post_init__(self):
+        if not self.model_name_or_path and not self.model_preset:
+            raise ConfigError("set model_name_or_path (a checkpoint directory) or model_preset (train from scratch)")
+        if self.model_preset and not self.init_from_scratch and not self.model_name_or_path:
+            self.init_from_scratch = True
+
+
+@dataclass
+class DataArguments:
+    dataset_path: str = ""                  # directory or file of jsonl / parquet / preprocessed shards
+    dataset_format: Literal["auto", "text", "messages", "prompt_completion", "preference", "tokens", "synthetic"] = "auto"
+    eval_dataset_path: str = ""
+    text_field: str = "text"
+    packing: bool = True
+    packed_row_length: int = 8192
+    completion_only_loss: bool = False
+    shuffle_seed: int = 0
+    synthetic_vocab: int = 0
+    doc_length_min: int = 256
+    doc_length_max: int = 16384
+    num_proc: int = 4
+
+
+@dataclass
+class TrainingArguments:
+    output_dir: str = "runs/%Y%m%d-%H%M%S"
+    overwrite_output_dir: bool = False
+    max_steps: int = -1
+    num_train_epochs: float = 1.0
+    per_device_train_batch_size: int = 1     # packed rows per rank per micro-step
+    gradient_accumulation_steps: int = 1
+    learning_rate: float = 1e-5
+    weight_decay: float = 0.01
+    adam_beta1: float = 0.9
+    adam_beta2: float = 0.999
+    adam_epsilon: float = 1e-8
+    max_grad_norm: float = 1.0
+    lr_scheduler_type: Literal["linear", "cosine", "constant", "constant_with_warmup"] = "cosine"
+    warmup_ratio: float = 0.0
+    warmup_steps: int = 0
+    optim: Literal["adamw_bf16", "adamw_torch", "adamw_bf16_host_state", "muon"] = "adamw_bf16"
+    bf16: bool = True
+    gradient_checkpointing: bool = True
+    use_fused_kernels: bool = True
+    logging_steps: int = 1
+    logging_nan_inf_filter: bool = False
+    save_steps: int = 0
+    save_total_limit: int = 0
+    save_sharded_ep: bool = False
+    eval_steps: int = 0
+    seed: int = 42
+    resume_from_checkpoint: str = ""         # "" = none, "auto" = newest complete checkpoint in output_dir
+    allow_optimizer_warm_restart: bool = False
+    max_consecutive_nonfinite_steps: int = 5
+    report_to: str = "none"
+    enable_torch_profiler: bool = False
+    router_aux_loss_coef: float = 0.0
+    moe_balancing: Literal["auto", "aux_loss", "bias_update", "none"] = "auto"
+
+    def __post_init__(self):
+        if self.gradient_accumulation_steps < 1 or self.per_device_train_batch_size < 1:
+            raise ConfigError("per_device_train_batch_size and gradient_accumulation_steps must be >= 1")
+        if self.learning_rate < 0 or self.max_grad_norm < 0:
+            raise ConfigError("learning_rate and max_grad_norm must be >= 0")
+        if not 0.0 <= self.warmup_ratio < 1.0:
+            raise ConfigError("warmup_ratio must lie in [0, 1)")
+
+
+@dataclass
+class ParallelismArguments:
+    expert_parallel_size: int = 1
+    expert_tensor_parallel_size: int = 1
+    tensor_parallel_size: int = 1
+    context_parallel_size: int = 1
+    pipeline_parallel_size: int = 1
+    pipeline_microbatches: int = 0
+    pipeline_schedule: Literal["1f1b", "gpipe"] = "1f1b"
+    pipeline_split: list[int] | None = None
+    ep_scope: Literal["auto", "node", "global"] = "auto"
+    ep_buffer_backend: Literal["auto", "symmetric", "nccl", "elastic", "legacy"] = "auto"
+    nvlink_domain_size: int = 0
+    fsdp_reshard_after_forward: bool = False
+    fsdp_reshard_after_backward: bool = True
+    fsdp_defer_grad_sync: bool = False
+    fsdp_shard_ep1_experts: bool = True
+    use_hsdp: bool = False
+    fp32_router: bool = False
+    fp32_experts: bool = False
+    fp32_non_ep_params: bool = False
+    fp32_grad_reduce: bool = False
+    bf16_optimizer: bool | None = None
+    use_grouped_gemm: bool = True
+    max_concurrent_loading: int | None = None
+    ep_lazy_loading: bool = True
+
+    def to_config(self, world_size: int = 0, global_rank: int = -1, init_from_scratch: bool = False) -> ParallelismConfig:
+        return ParallelismConfig(
+            world_size=world_size, global_rank=global_rank, nvlink_domain_size=self.nvlink_domain_size,
+            ep_size=self.expert_parallel_size, expert_tp_size=self.expert_tensor_parallel_size,
+            tp_size=self.tensor_parallel_size, cp_size=self.context_parallel_size, pp_size=self.pipeline_parallel_size,
+            pp_schedule=self.pipeline_schedule, pp_microbatches=self.pipeline_microbatches, pp_split=self.pipeline_split,
+            ep_scope=self.ep_scope, ep_buffer_backend=self.ep_buffer_backend, fp32_router=self.fp32_router,
+            fp32_experts=self.fp32_experts, fp32_non_ep_params=self.fp32_non_ep_params,
+            fp32_grad_reduce=self.fp32_grad_reduce, bf16_optimizer=self.bf16_optimizer,
+            use_grouped_gemm=self.use_grouped_gemm, fsdp_reshard_after_forward=self.fsdp_reshard_after_forward,
+            fsdp_reshard_after_backward=self.fsdp_reshard_after_backward, fsdp_defer_grad_sync=self.fsdp_defer_grad_sync,
+            fsdp_shard_ep1_experts=self.fsdp_shard_ep1_experts, use_hsdp=self.use_hsdp,
+            max_concurrent_loading=self.max_concurrent_loading, ep_lazy_loading=self.ep_lazy_loading,
+            init_from_scratch=init_from_scratch)
+
+
+# ---- per-method arguments ---------------------------------------------------------------------------
+@dataclass
+class SFTArguments:
+    assistant_only_loss: bool = False
+    dataset_text_field: str = "text"
+
+
+@dataclass
+class PreferenceArguments:
+    preference_loss: Literal["dpo", "ipo", "kto", "smpo"] = "dpo"
+    beta: float = 0.1
+    label_smoothing: float = 0.0
+    reference_free: bool = False
+    kto_desirable_weight: float = 1.0
+    kto_undesirable_weight: float = 1.0
+    smpo_margin: float = 1.0
+    sft_loss_weight: float = 0.0
+
+
+@dataclass
+class RewardArguments:
+    center_rewards_coefficient: float = 0.0
+    num_labels: int = 1
+
+
+@dataclass
+class DistillationArguments:
+    teacher_model_name_or_path: str = ""
+    distill_mode: Literal["teacher", "self", "sdpg"] = "teacher"
+    temperature: float = 1.0
+    kd_loss: Literal["forward_kl", "reverse_kl", "jsd"] = "forward_kl"
+    kd_weight: float = 1.0
+    ce_weight: float = 0.0
+    top_k_logits: int = 0
+
+
+@dataclass
+class GRPOArguments:
+    num_generations: int = 8
+    max_prompt_length: int = 1024
+    max_completion_length: int = 4096
+    grpo_beta: float = 0.0                      # KL weight against the reference policy
+    epsilon: float = 0.2
+    epsilon_high: float = 0.28
+    loss_type: Literal["grpo", "dapo", "dr_grpo", "bnpo"] = "dapo"
+    scale_rewards: Literal["group", "batch", "none", "maxrl"] = "group"
+    std_floor: float = 0.0
+    importance_clip_max: float = 2.0
+    token_budget: int = 65536
+    num_iterations: int = 1
+    sync_weights_every: int = 1
+    trust_region_mask_fraction: float = 1.0
+    zero_gradient_round_limit: int = 0
+    rollout_backend: Literal["in_process", "vllm", "sglang", "resident_copy"] = "resident_copy"
+    rollout_gpus: int = 0
+    weight_sync_chunk_mb: int = 1024

@@ -1,0 +1,93 @@
+"""Config parser, argument dataclasses, parallelism rules and rank layouts (CPU)."""
+
+import pytest
+
+from halo_b200.config_validation import ConfigError
+from halo_b200.configs.arguments import (DataArguments, ModelArguments, ParallelismArguments, SFTArguments,
+                                         TrainingArguments)
+from halo_b200.configs.parser import ArgumentParser, expand_output_dir
+from halo_b200.parallel import layout as L
+from halo_b200.parallel.config import ParallelismConfig
+from halo_b200.parallel.rules import SUPPORTED_AXIS_SETS, reject_model_layout
+
+
+def _parser():
+    return ArgumentParser(ModelArguments, DataArguments, TrainingArguments, ParallelismArguments, SFTArguments)
+
+
+def test_yaml_then_cli_override(tmp_path):
+    y = tmp_path / "c.yaml"
+    y.write_text("model_preset: tiny-moe\nlearning_rate: 2.0e-4\nexpert_parallel_size: 2\npipeline_split: [2, 2]\n")
+    m, d, t, p, s = _parser().parse([str(y), "--learning_rate=1e-3", "--max_steps=5"])
+    assert t.learning_rate == 1e-3 and t.max_steps == 5 and p.expert_parallel_size == 2
+    assert p.pipeline_split == [2, 2] and m.init_from_scratch and t.bf16 is True
+
+
+def test_unknown_retired_and_container_keys(tmp_path):
+    with pytest.raises(ConfigError, match="Did you mean"):
+        _parser().parse(["--model_preset=tiny-moe", "--learning_rat=1"])
+    with pytest.raises(ConfigError, match="retired"):
+        _parser().parse(["--model_preset=tiny-moe", "--use_liger_kernel=true"])
+    with pytest.raises(ConfigError, match="YAML"):
+        _parser().parse(["--model_preset=tiny-moe", "--pipeline_split=[1,3]"])
+    with pytest.raises(ConfigError, match="one of"):
+        _parser().parse(["--model_preset=tiny-moe", "--pipeline_schedule=zigzag"])
+
+
+def test_output_dir_pattern():
+    assert expand_output_dir("runs/%Y", now=0).startswith("runs/19")
+    assert expand_output_dir("runs/fixed") == "runs/fixed"
+
+
+def test_allowlist_has_eleven_sets_and_refusals_explain():
+    assert len(SUPPORTED_AXIS_SETS) == 11
+    for kw, needle in ((dict(tp_size=2, cp_size=2), "TP partners"), (dict(expert_tp_size=2, cp_size=2), "same tokens"),
+                       (dict(pp_size=2, cp_size=2), "too small")):
+        with pytest.raises(ConfigError, match=needle):
+            ParallelismConfig(world_size=8, global_rank=0, **kw)
+
+
+@pytest.mark.parametrize("world,kw,dp", [
+    (8, dict(), 8), (8, dict(ep_size=8), 8), (8, dict(ep_size=4, expert_tp_size=2), 4), (8, dict(tp_size=2), 4),
+    (8, dict(cp_size=2), 4), (8, dict(ep_size=8, cp_size=2), 4), (8, dict(ep_size=8, tp_size=2), 4),
+    (8, dict(pp_size=2, ep_size=4, nvlink_domain_size=4), 4), (16, dict(ep_size=16, gpus_per_node=8), 16),
+])
+def test_supported_layouts_and_data_parallel_width(world, kw, dp):
+    for rank in range(world):
+        pc = ParallelismConfig(world_size=world, global_rank=rank, **kw)
+        assert pc.data_parallel_size == dp
+        assert rank in pc.ep_group_ranks() and rank in pc.dp_group_ranks() and rank in pc.pp_chain_ranks()
+
+
+def test_groups_partition_the_world():
+    pc = ParallelismConfig(world_size=16, global_rank=0, ep_size=4, expert_tp_size=2, gpus_per_node=8)
+    for kind in ("ep_group", "dispatch_group", "expert_tp_group", "expert_replica", "dp_group"):
+        groups = pc.all_groups(kind)
+        flat = sorted(r for g in groups for r in g)
+        assert flat == list(range(16)), kind
+    assert pc.all_groups("expert_tp_group")[0] == [0, 4]
+    assert pc.all_groups("dispatch_group")[0] == [0, 1, 2, 3]
+
+
+def test_layouts_at_scale():
+    lay = L.StridedLayout(4096, 1024, 72 * 0 + 8)
+    seen = set()
+    for g in range(lay.num_groups):
+        ranks = lay.group_ranks(g)
+        assert len(ranks) == 1024 and not (seen & set(ranks))
+        seen |= set(ranks)
+        for pos, r in enumerate(ranks):
+            assert lay.locate(r) == (pos, g)
+    assert len(seen) == 4096
+    blk = L.BlockLayout(1024, 8, 8)
+    assert blk.locate(731) == (3, 91) and blk.replica_ranks(3)[91] == 731
+
+
+def test_model_dependent_refusals():
+    from halo_b200.models.config import moe_30b_a3b_config, dense_9b_config
+
+    with pytest.raises(ConfigError, match="not divisible"):
+        reject_model_layout(ParallelismConfig(world_size=6, global_rank=0, ep_size=6, gpus_per_node=6), moe_30b_a3b_config())
+    with pytest.raises(ConfigError, match="without routed experts"):
+        reject_model_layout(ParallelismConfig(world_size=8, global_rank=0, ep_size=8), dense_9b_config())
+    reject_model_layout(ParallelismConfig(world_size=8, global_rank=0, tp_size=2), dense_9b_config())
