@@ -44,7 +44,7 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=65536)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run reduced)")
     ap.add_argument("--optimizer-state", default="auto", choices=["auto", "device", "host"])
-    ap.add_argument("--activation-reserve-gb", type=float, default=64.0,
+    ap.add_argument("--activation-reserve-gb", type=float, default=36.0,
                     help="device memory kept free of optimizer state for activations, workspaces and staging")
     ap.add_argument("--doc-dist", default="loguniform")
     ap.add_argument("--lr", type=float, default=1e-5)

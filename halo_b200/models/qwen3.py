@@ -20,7 +20,6 @@ from __future__ import annotations
 
 import torch
 import torch.nn as nn
-from torch.utils.checkpoint import checkpoint
 
 from halo_b200.ops import attention as attn_ops
 from halo_b200.ops import gemm
@@ -31,6 +30,7 @@ from halo_b200.ops.norm import add_rms_norm, rms_norm
 from halo_b200.ops.rope import rope_table
 
 from .config import ModelConfig
+from .recompute import recompute
 
 
 class _SwiGLULinear(torch.autograd.Function):
@@ -215,6 +215,9 @@ class Qwen3Model(nn.Module):
         else:
             self.register_parameter("lm_head", None)
         self.has_head = has_head
+        # optional hook ``gate(params)`` called before a group of parameters is first read in a step;
+        # an optimizer that updates parameters asynchronously uses it to order the reads
+        self.param_gate = None
 
     # ---- initialisation ----------------------------------------------------------------------
     @torch.no_grad()
@@ -247,19 +250,27 @@ class Qwen3Model(nn.Module):
         rope = rope_table(position_ids, self.cfg.head_dim, self.cfg.rope_theta)
         return ForwardContext(plan, rope, self.transport, record_routing, replay_topk)
 
+    def _gate(self, params):
+        if self.param_gate is not None:
+            self.param_gate(params)
+
     def embed(self, input_ids):
+        self._gate([self.embed_tokens])
         return torch.nn.functional.embedding(input_ids.reshape(-1), self.embed_tokens)
 
     def run_layers(self, x, ctx):
         for layer in self.layers:
+            self._gate(layer.parameters())
             if self.gradient_checkpointing and torch.is_grad_enabled():
-                x = checkpoint(layer, x, ctx, use_reentrant=False, preserve_rng_state=False)
+                x = recompute(layer, x, ctx)
             else:
                 x = layer(x, ctx)
         return x
 
     def head_weight(self):
-        return self.lm_head if self.lm_head is not None else self.embed_tokens
+        w = self.lm_head if self.lm_head is not None else self.embed_tokens
+        self._gate([w, self.norm])
+        return w
 
     def hidden_states(self, input_ids, position_ids, cu_seqlens, ctx=None):
         ctx = ctx or self.make_context(position_ids.reshape(-1), cu_seqlens)

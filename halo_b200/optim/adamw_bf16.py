@@ -264,7 +264,8 @@ class AdamWBF16(torch.optim.Optimizer):
                 _lib.ptr(self._grad_scale), _lib.ptr(self._skip), _lib.stream_ptr(device),
             )
         _lib.check(rc, "halo_adamw_bf16_step")
-        self._keepalive = (tab, bstart, grads)
+        # the tables are device tensors: freeing them after the launch is stream-ordered and safe. Gradients
+        # must NOT be kept alive here, or a whole extra set would survive zero_grad until the next step.
 
 
 class GradNorm:
@@ -307,7 +308,6 @@ class GradNorm:
                 _lib.ptr(self.total_sq), _lib.c_int(0 if (first and i == 0) else 1), _lib.stream_ptr(self.device),
             )
             _lib.check(rc, "halo_sq_norm")
-            self._keep = (tab, bstart, gs)
 
     def finish(self, max_norm: float) -> None:
         """coef = min(1, max_norm / (norm + 1e-6)); skip = norm is not finite."""

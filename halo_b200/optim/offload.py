@@ -47,6 +47,8 @@ class HostStateAdamWBF16(AdamWBF16):
         self._staging = None
         self._streams = None
         self._slot_free = None
+        self._opt_stream = None
+        self.ready_events: dict = {}   # parameter -> event recorded after its streamed update
 
     def _on_host(self, p) -> bool:
         return p.is_cuda and p.dtype == torch.bfloat16 and p.numel() >= self.host_min_numel
@@ -72,6 +74,7 @@ class HostStateAdamWBF16(AdamWBF16):
                 for _ in range(STAGING_SLOTS)
             ]
             self._streams = (torch.cuda.Stream(device), torch.cuda.Stream(device))
+            self._opt_stream = torch.cuda.Stream(device)
             self._slot_free = [torch.cuda.Event() for _ in range(STAGING_SLOTS)]
             for ev in self._slot_free:
                 ev.record(torch.cuda.current_stream(device))
@@ -86,8 +89,12 @@ class HostStateAdamWBF16(AdamWBF16):
         L = _lib.lib()
         self._ensure_staging(device, max(p.numel() for _, p, _ in on_host))
         h2d, d2h = self._streams
-        compute = torch.cuda.current_stream(device)
-        # the copies read the gradient scale / skip words only through the kernel, nothing to order there
+        main = torch.cuda.current_stream(device)
+        # The streamed updates run on their own stream, so the next step's forward can start on the
+        # layers that are already updated while later layers are still crossing PCIe. Consumers call
+        # wait_ready() before they read a parameter.
+        compute = self._opt_stream
+        compute.wait_stream(main)   # gradients, clip coefficient and skip flag are final
         for i, (name, p, st) in enumerate(on_host):
             slot = i % STAGING_SLOTS
             n = p.numel()
@@ -100,26 +107,44 @@ class HostStateAdamWBF16(AdamWBF16):
                 ev_in.record(h2d)
             compute.wait_event(ev_in)
             g = p.grad.contiguous()
+            g.record_stream(compute)   # zero_grad may release it while the side stream still reads it
             rc = L.halo_adamw_bf16_step_single(
                 _lib.ptr(p), _lib.ptr(g), _lib.ptr(m_dev), _lib.ptr(v_dev), _lib.c_ll(n),
                 ctypes.c_ulonglong(param_name_hash(name)), _lib.c_int(1 if gdtype == torch.float32 else 0),
                 _lib.c_float(b1), _lib.c_float(b2), _lib.c_float(step_size), _lib.c_float(bc2_sqrt),
                 _lib.c_float(eps), _lib.c_float(wd_factor), ctypes.c_ulonglong(self.key), ctypes.c_ulonglong(step),
-                _lib.ptr(self._grad_scale), _lib.ptr(self._skip), _lib.stream_ptr(device),
+                _lib.ptr(self._grad_scale), _lib.ptr(self._skip), ctypes.c_void_p(compute.cuda_stream),
             )
             _lib.check(rc, "halo_adamw_bf16_step_single")
             ev_done = torch.cuda.Event()
             ev_done.record(compute)
+            self.ready_events[p] = ev_done
             d2h.wait_event(ev_done)
             with torch.cuda.stream(d2h):
                 st["exp_avg"].copy_(m_dev, non_blocking=True)
                 st["exp_avg_sq"].copy_(v_dev, non_blocking=True)
                 self._slot_free[slot].record(d2h)
+        if self._grad_scale is not None:
+            self._grad_scale.record_stream(compute)
+
+    def wait_ready(self, params, stream=None) -> None:
+        """Make ``stream`` (default: the current one) wait for the streamed updates of ``params``."""
+        if not self.ready_events:
+            return
+        stream = stream or torch.cuda.current_stream()
+        for p in params:
+            ev = self.ready_events.pop(p, None)
+            if ev is not None:
+                stream.wait_event(ev)
+
+    def wait_all_ready(self) -> None:
+        self.wait_ready(list(self.ready_events))
 
     def synchronize_state(self) -> None:
         """Wait until every moment written by the last step has landed in host memory (call before
         reading the state, e.g. to save a checkpoint)."""
         if self._streams is not None:
+            self._opt_stream.synchronize()
             for s in self._streams:
                 s.synchronize()
 

@@ -1,0 +1,241 @@
+"""The trainer spine shared by every method: optimizer / scheduler construction, the accumulation
+loop over packed batches, logging through callbacks, the non-finite step guard, periodic saves
+(weights -> optimizer shards -> scheduler / RNG sidecars -> ``trainer_state.json`` last) and exact
+resume from the newest complete checkpoint.
+
+Method trainers (SFT, preference, reward, distillation, GRPO) subclass :class:`Trainer` and
+override ``compute_loss`` (and, for RL, ``next_batches``); the parallel layout never leaks into
+them. Counterpart of the reference's ``DistributedTrainerMixin`` and its loop helpers
+(halo/trainers/distributed_trainer.py:175-684, halo/trainers/loop/checkpointing.py,
+halo/trainers/loop/step_guard.py, halo/checkpoint/parallel/resume_source.py).
+"""
+
+from __future__ import annotations
+
+import logging
+import os
+import re
+import shutil
+import time
+from typing import Callable, Iterable, Iterator
+
+import torch
+
+from halo_b200.checkpoint import optimizer_state as opt_io
+from halo_b200.checkpoint.atomic import atomic_torch_save, atomic_write_json
+from halo_b200.checkpoint.save import is_complete, mark_complete, save_model
+from halo_b200.configs.arguments import TrainingArguments
+from halo_b200.data.packing import PackedBatch
+from halo_b200.optim.factory import build_optimizer
+from halo_b200.optim.schedule import LRScheduler
+from halo_b200.trainers.engine import TrainEngine
+
+log = logging.getLogger(__name__)
+CHECKPOINT_RE = re.compile(r"^checkpoint-(\d+)$")
+
+
+class NonFiniteRun(RuntimeError):
+    """Too many consecutive steps had a non-finite gradient norm."""
+
+
+class Callback:
+    def on_train_begin(self, trainer): ...
+    def on_step_end(self, trainer, logs: dict): ...
+    def on_log(self, trainer, logs: dict): ...
+    def on_save(self, trainer, directory: str): ...
+    def on_train_end(self, trainer): ...
+
+
+def list_checkpoints(output_dir: str) -> list[tuple[int, str]]:
+    out = []
+    if os.path.isdir(output_dir):
+        for name in os.listdir(output_dir):
+            m = CHECKPOINT_RE.match(name)
+            if m:
+                out.append((int(m.group(1)), os.path.join(output_dir, name)))
+    return sorted(out)
+
+
+def newest_complete_checkpoint(output_dir: str) -> str | None:
+    """The newest checkpoint whose completeness marker exists (an interrupted save is skipped)."""
+    for _, path in reversed(list_checkpoints(output_dir)):
+        if is_complete(path):
+            return path
+    return None
+
+
+class Trainer:
+    def __init__(self, model, args: TrainingArguments, train_batches: Iterable[PackedBatch] | Callable[[], Iterator],
+                 eval_batches: Iterable[PackedBatch] | None = None, device=None, parallel=None,
+                 callbacks: list[Callback] | None = None, optimizer=None, parallelism_fingerprint: dict | None = None):
+        self.model, self.args, self.parallel = model, args, parallel
+        self.device = torch.device(device or next(model.parameters()).device)
+        self.train_batches, self.eval_batches = train_batches, eval_batches
+        self.callbacks = list(callbacks or [])
+        self.optimizer = optimizer or build_optimizer(
+            model, args.optim if self.device.type == "cuda" or args.optim == "adamw_torch" else
+            ("adamw_bf16" if next(model.parameters()).dtype == torch.bfloat16 else "adamw_torch"),
+            lr=args.learning_rate, weight_decay=args.weight_decay, betas=(args.adam_beta1, args.adam_beta2),
+            eps=args.adam_epsilon)
+        total = args.max_steps if args.max_steps > 0 else 0
+        warmup = args.warmup_steps or int(args.warmup_ratio * total)
+        self.lr_scheduler = LRScheduler(self.optimizer, args.lr_scheduler_type, total, warmup)
+        self.engine = TrainEngine(model, self.optimizer, self.device, args.max_grad_norm, parallel, self.lr_scheduler,
+                                  loss_fn=self._loss_adapter)
+        self.global_step = 0
+        self.tokens_seen = 0
+        self.fingerprint = parallelism_fingerprint or {"world_size": self.world_size}
+        self.log_history: list[dict] = []
+        self._pending_skip = None
+        self._consecutive_skips = 0
+        self.rank = int(os.environ.get("RANK", "0"))
+
+    # ---- hooks for subclasses --------------------------------------------------------------
+    def compute_loss(self, model, batch: PackedBatch, normalizer):
+        return model(batch.input_ids, batch.position_ids, batch.cu_seqlens, batch.labels, normalizer)
+
+    def _loss_adapter(self, model, batch, normalizer):
+        return self.compute_loss(model, batch, normalizer)
+
+    def next_batches(self) -> Iterator[PackedBatch]:
+        src = self.train_batches() if callable(self.train_batches) else self.train_batches
+        return iter(src)
+
+    @property
+    def world_size(self) -> int:
+        return int(os.environ.get("WORLD_SIZE", "1"))
+
+    @property
+    def is_main(self) -> bool:
+        return self.rank == 0
+
+    # ---- the loop --------------------------------------------------------------------------
+    def train(self, resume_from_checkpoint: str | None = None) -> dict:
+        args = self.args
+        resume = resume_from_checkpoint if resume_from_checkpoint is not None else args.resume_from_checkpoint
+        if resume == "auto":
+            resume = newest_complete_checkpoint(args.output_dir)
+        if resume:
+            self.load_checkpoint(resume)
+        for cb in self.callbacks:
+            cb.on_train_begin(self)
+        it = self.next_batches()
+        # a resumed run skips the batches the interrupted run consumed
+        for _ in range(self.global_step * args.gradient_accumulation_steps):
+            next(it, None)
+        t_last = time.perf_counter()
+        done = False
+        while not done:
+            micro = []
+            for _ in range(args.gradient_accumulation_steps):
+                b = next(it, None)
+                if b is None:
+                    done = True
+                    break
+                micro.append(b)
+            if not micro:
+                break
+            out = None
+            for i, b in enumerate(micro):
+                out = self.engine.train_step(b, accumulate=i < len(micro) - 1)
+                self.tokens_seen += b.n_tokens
+            self.global_step += 1
+            self._guard_non_finite(out)
+            if args.logging_steps and self.global_step % args.logging_steps == 0:
+                now = time.perf_counter()
+                logs = {"step": self.global_step, "loss": float(out.loss.reshape(-1)[0].item()),
+                        "grad_norm": float(out.grad_norm.item()), "lr": self.lr_scheduler.get_last_lr()[0],
+                        "tokens": self.tokens_seen, "step_seconds": (now - t_last) / args.logging_steps}
+                t_last = now
+                self.log_history.append(logs)
+                for cb in self.callbacks:
+                    cb.on_log(self, logs)
+                if self.is_main:
+                    log.info("step %d loss %.4f grad_norm %.3f lr %.3g", logs["step"], logs["loss"], logs["grad_norm"], logs["lr"])
+            for cb in self.callbacks:
+                cb.on_step_end(self, {"step": self.global_step})
+            if args.save_steps and self.global_step % args.save_steps == 0:
+                self.save_checkpoint()
+            if args.eval_steps and self.eval_batches is not None and self.global_step % args.eval_steps == 0:
+                self.evaluate()
+            if 0 < args.max_steps <= self.global_step:
+                break
+        for cb in self.callbacks:
+            cb.on_train_end(self)
+        return {"global_step": self.global_step, "log_history": self.log_history}
+
+    def _guard_non_finite(self, out) -> None:
+        """The skip flag of a step is read one step late, so the read never stalls the step it guards."""
+        prev = self._pending_skip
+        self._pending_skip = out.skipped.clone() if out is not None else None
+        if prev is not None and int(prev.item()):
+            self._consecutive_skips += 1
+            log.warning("step %d was skipped: non-finite gradient norm", self.global_step - 1)
+            if self._consecutive_skips >= self.args.max_consecutive_nonfinite_steps:
+                raise NonFiniteRun(f"{self._consecutive_skips} consecutive steps had a non-finite gradient norm")
+        elif prev is not None:
+            self._consecutive_skips = 0
+
+    @torch.no_grad()
+    def evaluate(self) -> dict:
+        losses = [float(self.engine.eval_step(b).reshape(-1)[0].item()) for b in self.eval_batches]
+        logs = {"step": self.global_step, "eval_loss": sum(losses) / max(1, len(losses))}
+        self.log_history.append(logs)
+        for cb in self.callbacks:
+            cb.on_log(self, logs)
+        return logs
+
+    # ---- save / resume ---------------------------------------------------------------------
+    def checkpoint_dir(self, step: int | None = None) -> str:
+        return os.path.join(self.args.output_dir, f"checkpoint-{self.global_step if step is None else step}")
+
+    def save_checkpoint(self) -> str:
+        d = self.checkpoint_dir()
+        os.makedirs(d, exist_ok=True)
+        save_model(self.model, d, sharded_experts=self.args.save_sharded_ep, save_dtype=None)  # exact resume: keep the dtype
+        opt_io.save_optimizer_shard(self.optimizer, d, self.rank, self.fingerprint, write_meta=self.is_main)
+        atomic_torch_save({"cpu": torch.get_rng_state(),
+                           "cuda": torch.cuda.get_rng_state(self.device) if self.device.type == "cuda" else None},
+                          os.path.join(d, f"rng_state_{self.rank}.pth"))
+        if self.parallel is not None:
+            import torch.distributed as dist
+
+            dist.barrier()
+        if self.is_main:
+            atomic_torch_save(self.lr_scheduler.state_dict(), os.path.join(d, "scheduler.pt"))
+            mark_complete(d, {"global_step": self.global_step, "tokens_seen": self.tokens_seen,
+                              "log_history": self.log_history[-50:], "world_size": self.world_size})
+            self._rotate()
+        for cb in self.callbacks:
+            cb.on_save(self, d)
+        return d
+
+    def _rotate(self) -> None:
+        limit = self.args.save_total_limit
+        if limit and limit > 0:
+            done = [p for _, p in list_checkpoints(self.args.output_dir) if is_complete(p)]
+            for p in done[:-limit]:
+                shutil.rmtree(p, ignore_errors=True)
+
+    def load_checkpoint(self, directory: str) -> None:
+        import json
+
+        from halo_b200.checkpoint.load import load_model_weights
+
+        if not is_complete(directory):
+            raise FileNotFoundError(f"{directory!r} has no completeness marker: the save was interrupted")
+        load_model_weights(self.model, directory)
+        opt_io.load_optimizer_shard(self.optimizer, directory, self.rank, self.fingerprint,
+                                    self.args.allow_optimizer_warm_restart)
+        state = json.load(open(os.path.join(directory, "trainer_state.json")))
+        self.global_step, self.tokens_seen = state["global_step"], state.get("tokens_seen", 0)
+        sched = os.path.join(directory, "scheduler.pt")
+        if os.path.isfile(sched):
+            self.lr_scheduler.load_state_dict(torch.load(sched, weights_only=False))
+        rng = os.path.join(directory, f"rng_state_{self.rank}.pth")
+        if os.path.isfile(rng):
+            blob = torch.load(rng, weights_only=False)
+            torch.set_rng_state(blob["cpu"])
+            if blob.get("cuda") is not None and self.device.type == "cuda":
+                torch.cuda.set_rng_state(blob["cuda"], self.device)
+        self.engine.step_count = self.global_step

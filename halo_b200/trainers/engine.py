@@ -43,6 +43,8 @@ class TrainEngine:
         self.grad_norm = GradNorm(self.device)
         self.step_count = 0
         self.consecutive_skips = 0
+        if hasattr(optimizer, "wait_ready") and hasattr(model, "param_gate"):
+            model.param_gate = optimizer.wait_ready
 
     # ---- pieces ---------------------------------------------------------------------------
     def to_device(self, batch: PackedBatch) -> PackedBatch:

@@ -1,0 +1,164 @@
+"""GRPO trainers.
+
+``GRPOTrainer`` consumes *rounds*: a round is a set of rollouts (prompt + sampled completion token
+ids, the sampler's per-token log-probs, one reward per completion, grouped ``num_generations`` per
+prompt). It computes group-relative advantages, packs the rows into token-budget micro-batches,
+takes the importance ratios from the loss forward itself when nothing needs the old log-probs
+earlier (on-policy, one iteration), and applies the clipped token objective. After the update the
+weights are pushed to the rollout copy through the weight-sync group.
+
+Rollouts come from a ``rollout_source`` callable: an offline dataset of stored rollouts, a live
+engine client, or the synthetic generator used by the benchmark configuration (the trainers of
+halo/trainers/grpo/offline/*, online.py and environmental/*)."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from halo_b200.configs.arguments import GRPOArguments
+from halo_b200.data.packing import PackedBatch, pack_documents
+from halo_b200.trainers.base import Trainer
+from halo_b200.trainers.grpo import advantages as adv_mod
+from halo_b200.trainers.grpo import microbatch, objective
+
+
+@dataclass
+class Rollout:
+    prompt_ids: np.ndarray
+    completion_ids: np.ndarray
+    sampler_logprobs: np.ndarray | None   # per completion token; None = treat as on-policy
+    reward: float
+
+
+@dataclass
+class GRPOBatch(PackedBatch):
+    advantages: torch.Tensor = None       # [T] advantage of the row each token belongs to
+    old_logprobs: torch.Tensor = None     # [T] sampler log-probs aligned with labels (0 where unknown)
+    has_old: bool = False
+    degenerate: torch.Tensor = None       # [T] bool: token belongs to a zero-spread group
+    seq_lengths: torch.Tensor = None      # [n_rows] completion lengths
+
+    def to(self, device, non_blocking: bool = True):
+        b = PackedBatch.to(self, device, non_blocking)
+        mv = lambda t: None if t is None else t.to(device, non_blocking=non_blocking)  # noqa: E731
+        return GRPOBatch(b.input_ids, b.position_ids, b.labels, b.cu_seqlens, b.n_scored, mv(self.advantages),
+                         mv(self.old_logprobs), self.has_old, mv(self.degenerate), mv(self.seq_lengths))
+
+
+def build_grpo_batch(rollouts: list[Rollout], adv: torch.Tensor, degenerate: torch.Tensor) -> GRPOBatch:
+    docs, masks = [], []
+    for r in rollouts:
+        docs.append(np.concatenate([r.prompt_ids, r.completion_ids]))
+        masks.append(np.concatenate([np.zeros(len(r.prompt_ids), bool), np.ones(len(r.completion_ids), bool)]))
+    base = pack_documents(docs, label_masks=masks)
+    T = base.n_tokens
+    a = torch.zeros(T)
+    old = torch.zeros(T)
+    deg = torch.zeros(T, dtype=torch.bool)
+    has_old = all(r.sampler_logprobs is not None for r in rollouts)
+    for i, r in enumerate(rollouts):
+        s, e = int(base.cu_seqlens[i]), int(base.cu_seqlens[i + 1])
+        a[s:e] = float(adv[i])
+        deg[s:e] = bool(degenerate[i])
+        if has_old:
+            # label at position t scores token t+1: completion token j sits at label index len(prompt) + j - 1
+            p = len(r.prompt_ids)
+            old[s + p - 1:s + p - 1 + len(r.completion_ids)] = torch.from_numpy(np.asarray(r.sampler_logprobs, np.float32))
+    return GRPOBatch(base.input_ids, base.position_ids, base.labels, base.cu_seqlens, base.n_scored, a, old, has_old,
+                     deg, torch.tensor([len(r.completion_ids) for r in rollouts], dtype=torch.float32))
+
+
+class GRPOTrainer(Trainer):
+    def __init__(self, model, args, rollout_source, grpo_args: GRPOArguments | None = None, ref_model=None,
+                 weight_sync=None, **kw):
+        self.grpo = grpo_args or GRPOArguments()
+        self.rollout_source = rollout_source
+        self.ref_model = ref_model
+        self.weight_sync = weight_sync
+        self.rounds_done = 0
+        self.zero_gradient_rounds = 0
+        super().__init__(model, args, train_batches=self._rounds, **kw)
+
+    # ---- rounds -> micro-batches ---------------------------------------------------------------
+    def _world_max(self, n: int) -> int:
+        if self.parallel is None:
+            return n
+        import torch.distributed as dist
+
+        t = torch.tensor([n], dtype=torch.int64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return int(t.item())
+
+    def plan_round(self, rollouts: list[Rollout]) -> list[GRPOBatch]:
+        g = self.grpo
+        rewards = torch.tensor([r.reward for r in rollouts], dtype=torch.float32)
+        adv, degenerate = adv_mod.group_advantages(rewards, g.num_generations, g.scale_rewards, g.std_floor)
+        if bool(degenerate.all()):
+            self.zero_gradient_rounds += 1
+            if g.zero_gradient_round_limit and self.zero_gradient_rounds >= g.zero_gradient_round_limit:
+                raise RuntimeError(f"{self.zero_gradient_rounds} rounds in a row carried no learning signal")
+        else:
+            self.zero_gradient_rounds = 0
+        lengths = [len(r.prompt_ids) + len(r.completion_ids) for r in rollouts]
+        bins = microbatch.plan_microbatches(lengths, g.token_budget, self._world_max if self.parallel else None)
+        self._round_tokens = float(sum(len(r.completion_ids) for r in rollouts))
+        out = []
+        for b in bins:
+            if not b:
+                continue
+            out.append(build_grpo_batch([rollouts[i] for i in b], adv[b], degenerate[b]))
+        return out
+
+    def _rounds(self):
+        while True:
+            rollouts = self.rollout_source(self.rounds_done)
+            if rollouts is None:
+                return
+            batches = self.plan_round(rollouts)
+            self.args.gradient_accumulation_steps = max(1, len(batches))
+            for b in batches:
+                yield b.pin() if torch.cuda.is_available() else b
+            self.rounds_done += 1
+
+    # ---- objective -----------------------------------------------------------------------------
+    def compute_loss(self, model, batch: GRPOBatch, normalizer):
+        g = self.grpo
+        logp, _ = model.token_logprobs(batch.input_ids, batch.position_ids, batch.cu_seqlens, batch.labels)
+        mask = batch.labels.reshape(-1) != -100
+        # on-policy single iteration: the old log-probs are this forward's own (detached) values
+        old = batch.old_logprobs if (batch.has_old and g.num_iterations > 1) else logp.detach()
+        is_w = None
+        if batch.has_old:
+            is_w = objective.importance_weights(logp, batch.old_logprobs, mask, g.importance_clip_max)
+        ref = None
+        if g.grpo_beta and self.ref_model is not None:
+            with torch.no_grad():
+                ref, _ = self.ref_model.token_logprobs(batch.input_ids, batch.position_ids, batch.cu_seqlens, batch.labels)
+        num, _ = objective.grpo_token_loss(logp, old, batch.advantages, mask, g.epsilon, g.epsilon_high, g.grpo_beta,
+                                           ref, is_w)
+        denom = objective.normalizer(g.loss_type if g.loss_type != "grpo" else "dapo", mask, batch.seq_lengths,
+                                     g.max_completion_length, batch.degenerate)
+        if self.args.gradient_accumulation_steps > 1:
+            denom = torch.as_tensor(max(self._round_tokens, 1.0), device=num.device)
+        return num / denom
+
+    # ---- weight push ---------------------------------------------------------------------------
+    def after_optimizer_step(self):
+        if self.weight_sync is not None and self.global_step % max(1, self.grpo.sync_weights_every) == 0:
+            self.weight_sync.push(self.model)
+
+
+def synthetic_rollouts(round_index: int, n_prompts: int = 64, n_generations: int = 8, vocab: int = 151936,
+                       prompt_len=(128, 1024), response_len=(256, 4096), seed: int = 0) -> list[Rollout]:
+    """Random token ids, N(0,1) rewards (the synthetic rollouts of the asynchronous-GRPO benchmark)."""
+    rng = np.random.default_rng(seed * 100003 + round_index)
+    out = []
+    for _ in range(n_prompts):
+        prompt = rng.integers(0, vocab, size=int(rng.integers(prompt_len[0], prompt_len[1] + 1)))
+        for _ in range(n_generations):
+            comp = rng.integers(0, vocab, size=int(rng.integers(response_len[0], response_len[1] + 1)))
+            out.append(Rollout(prompt, comp, None, float(rng.normal())))
+    return out

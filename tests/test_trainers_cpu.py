@@ -1,0 +1,126 @@
+"""Objectives and trainer spine on CPU: closed-form checks of the losses, GRPO pieces, micro-batch
+planning, and save / resume of a short SFT run."""
+
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from halo_b200.configs.arguments import GRPOArguments, PreferenceArguments, TrainingArguments
+from halo_b200.data.packing import pack_documents, synthetic_packed_batch
+from halo_b200.models.config import ModelConfig
+from halo_b200.models.qwen3 import build_model
+from halo_b200.trainers import losses
+from halo_b200.trainers.base import Trainer, newest_complete_checkpoint
+from halo_b200.trainers.grpo import advantages, microbatch, objective
+from halo_b200.trainers.grpo.trainer import GRPOTrainer, synthetic_rollouts
+from halo_b200.trainers.preference import PreferenceBatch, PreferenceTrainer
+
+
+def _tiny(seed=0, moe=False):
+    cfg = ModelConfig(vocab_size=512, hidden_size=64, num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=1,
+                      head_dim=32, intermediate_size=128, moe_intermediate_size=32, num_experts=4 if moe else 0,
+                      num_experts_per_tok=2, model_type="qwen3_moe" if moe else "qwen3")
+    return cfg, build_model(cfg, device="cpu", seed=seed)
+
+
+def test_dpo_matches_closed_form_and_kto_sign():
+    pc, pr, rc, rr = (torch.tensor([x]) for x in (-10.0, -12.0, -11.0, -11.5))
+    loss, cw, rw = losses.dpo_loss(pc, pr, rc, rr, beta=0.5)
+    assert abs(loss.item() - (-math.log(1 / (1 + math.exp(-0.5 * 1.5))))) < 1e-6
+    assert cw.item() == pytest.approx(0.5) and rw.item() == pytest.approx(-0.25)
+    good = losses.kto_loss(torch.tensor([0.0]), torch.tensor([-1.0]), torch.tensor([True]), torch.tensor(0.0))
+    bad = losses.kto_loss(torch.tensor([0.0]), torch.tensor([-1.0]), torch.tensor([False]), torch.tensor(0.0))
+    assert good.item() < 0.5 < bad.item()
+
+
+def test_segment_sums_and_divergences():
+    v = torch.arange(6.0)
+    assert losses.segment_sums(v, [0, 2, 6]).tolist() == [1.0, 14.0]
+    a = torch.randn(5, 11)
+    assert losses.distillation_divergence(a, a).abs().item() < 1e-6
+    assert losses.distillation_divergence(a, torch.randn(5, 11), "jsd").item() > 0
+
+
+def test_group_advantages_and_degenerate_groups():
+    r = torch.tensor([1.0, 2.0, 3.0, 4.0, 5.0, 5.0, 5.0, 5.0])
+    adv, deg = advantages.group_advantages(r, 4, "group")
+    assert adv[:4].sum().abs().item() < 1e-5 and adv[4:].abs().max().item() == 0
+    assert deg.tolist() == [False] * 4 + [True] * 4
+    adv_none, _ = advantages.group_advantages(r, 4, "none")
+    assert adv_none[:4].tolist() == [-1.5, -0.5, 0.5, 1.5]
+    with pytest.raises(ValueError):
+        advantages.group_advantages(torch.tensor([float("nan"), 1.0]), 2)
+    assert advantages.offline_group_advantages(r, 4, "minmax")[:4].tolist() == pytest.approx([-1, -1 / 3, 1 / 3, 1], abs=1e-3)
+
+
+def test_clipped_objective_and_importance_weights():
+    logp = torch.tensor([0.0, 0.0, 0.0], requires_grad=True)
+    old = torch.tensor([0.0, -1.0, 1.0])
+    adv = torch.tensor([1.0, 1.0, -1.0])
+    num, per = objective.grpo_token_loss(logp, old, adv, torch.ones(3, dtype=torch.bool), 0.2, 0.28)
+    assert per[0].item() == pytest.approx(-1.0)
+    assert per[1].item() == pytest.approx(-1.28)            # ratio e > 1.28: clipped for a positive advantage
+    assert per[2].item() == pytest.approx(0.8)              # ratio 1/e < 0.8: clipped for a negative one
+    num.backward()
+    assert logp.grad[1].item() == 0 and logp.grad[2].item() == 0 and logp.grad[0].item() == pytest.approx(-1.0)
+    w = objective.importance_weights(torch.tensor([0.0, 2.0]), torch.tensor([0.0, 0.0]), torch.tensor([True, True]), 2.0)
+    assert w.tolist() == [1.0, 2.0]
+    assert objective.k3_kl(torch.tensor([0.0]), torch.tensor([100.0])).item() == pytest.approx(math.exp(5) - 6)
+
+
+def test_microbatch_plan_is_world_uniform():
+    lens = [900, 800, 300, 200, 100, 50]
+    bins = microbatch.first_fit_decreasing(lens, 1000)
+    assert all(sum(lens[i] for i in b) <= 1000 for b in bins) and sorted(i for b in bins for i in b) == list(range(6))
+    padded = microbatch.plan_microbatches([100], 1000, world_max_bins=lambda n: 3)
+    assert [len(b) for b in padded] == [0, 0, 1]            # idle slots lead, the real backward is last
+    dealt = microbatch.deal_rows_across_ranks(lens, 2)
+    assert sorted(len(d) for d in dealt) == [3, 3]
+    with pytest.raises(ValueError):
+        microbatch.first_fit_decreasing([2000], 1000)
+
+
+def test_sft_save_resume_is_exact(tmp_path):
+    cfg, _ = _tiny()
+    batches = [synthetic_packed_batch(128, cfg.vocab_size, seed=i, lo=16, hi=64) for i in range(8)]
+
+    def run(steps, out, resume=""):
+        _, model = _tiny()
+        args = TrainingArguments(output_dir=str(out), max_steps=6, learning_rate=1e-2, save_steps=3,
+                                 optim="adamw_torch", lr_scheduler_type="linear", logging_steps=1)
+        t = Trainer(model, args, batches[:steps], device="cpu")   # an interrupted run: the data ends early
+        t.train(resume_from_checkpoint=resume)
+        return model, t
+
+    m_full, t_full = run(6, tmp_path / "a")
+    assert newest_complete_checkpoint(str(tmp_path / "a")).endswith("checkpoint-6")
+    m_part, _ = run(3, tmp_path / "b")
+    m_res, t_res = run(6, tmp_path / "b", resume="auto")
+    assert t_res.global_step == 6
+    for (n, a), (_, b) in zip(m_full.named_parameters(), m_res.named_parameters()):
+        assert torch.allclose(a, b, atol=1e-6), n
+    os.remove(os.path.join(tmp_path, "b", "checkpoint-6", "trainer_state.json"))
+    assert newest_complete_checkpoint(str(tmp_path / "b")).endswith("checkpoint-3")
+
+
+def test_preference_and_grpo_trainers_step():
+    cfg, model = _tiny(moe=True)
+    rng = np.random.default_rng(0)
+    docs = [rng.integers(0, 512, size=n) for n in (20, 24, 18, 30)]
+    base = pack_documents(docs)
+    pb = PreferenceBatch(base.input_ids, base.position_ids, base.labels, base.cu_seqlens, base.n_scored,
+                         ref_logps=torch.full((4,), -100.0))
+    args = TrainingArguments(output_dir="unused", max_steps=2, learning_rate=1e-3, optim="adamw_torch")
+    t = PreferenceTrainer(model, args, [pb, pb], pref_args=PreferenceArguments(beta=0.1), device="cpu")
+    assert t.train()["global_step"] == 2
+
+    def source(i):
+        return synthetic_rollouts(i, n_prompts=2, n_generations=4, vocab=512, prompt_len=(4, 8), response_len=(6, 12)) if i < 2 else None
+
+    g = GRPOTrainer(model, TrainingArguments(output_dir="unused", max_steps=2, learning_rate=1e-3, optim="adamw_torch"),
+                    source, grpo_args=GRPOArguments(num_generations=4, token_budget=64), device="cpu")
+    out = g.train()
+    assert out["global_step"] == 2 and all(math.isfinite(l["loss"]) for l in out["log_history"])
