@@ -46,6 +46,9 @@ def parse_args():
     ap.add_argument("--optimizer-state", default="auto", choices=["auto", "device", "host"])
     ap.add_argument("--activation-reserve-gb", type=float, default=36.0,
                     help="device memory kept free of optimizer state for activations, workspaces and staging")
+    ap.add_argument("--fused-optimizer", type=int, default=1,
+                    help="N > 1: 1 = fused reduce-scatter/AdamW/all-gather kernels for the replicated parameters, "
+                         "0 = NCCL all-reduce + local optimizer (the baseline path)")
     ap.add_argument("--doc-dist", default="loguniform")
     ap.add_argument("--lr", type=float, default=1e-5)
     return ap.parse_args()
@@ -184,13 +187,20 @@ def main() -> int:
     state_bytes = local_params * 8  # bf16 weights + bf16 grads + two bf16 moments
     opt_state = args.optimizer_state
     if opt_state == "auto":
-        opt_state = "host" if state_bytes > 150e9 else "device"
+        total_mem = torch.cuda.get_device_properties(dev).total_memory
+        rows_cap = int(1.5 * args.seq_len * cfg.num_experts_per_tok) if world > 1 else 0
+        transport_bytes = 4 * rows_cap * cfg.hidden_size * 2
+        need = state_bytes + transport_bytes + int(args.activation_reserve_gb * 1e9)
+        opt_state = "host" if need > 0.90 * total_mem else "device"
 
     if transport is not None:
         transport.configure(max_tokens=args.seq_len, top_k=cfg.num_experts_per_tok, hidden=cfg.hidden_size,
                             n_local_experts=cfg.num_experts // world)
     model = build_model(cfg, device=dev, seed=0, transport=transport, gradient_checkpointing=True)
     named = list(model.named_parameters())
+    if parallel is not None and args.fused_optimizer:
+        # replicated parameters: sharded AdamWBF16 fused with reduce-scatter / all-gather over peer memory
+        named = parallel.enable_fused_optimizer(model, lr=args.lr, weight_decay=0.01)
     if opt_state == "host":
         from halo_b200.optim.offload import HostStateAdamWBF16
 
@@ -252,7 +262,7 @@ def main() -> int:
     e2e = tokens / (ms_e2e / 1e3)
     peak_gib = torch.cuda.max_memory_allocated(dev) / 2**30
     if rank == 0:
-        par = f"ep{world}" + (f"+dp{world}" if world > 1 else "") + ("+host_optimizer_state" if opt_state == "host" else "")
+        par = f"ep{world}" + (f"+dp{world}" if world > 1 else "") + ("+fused_zero" if parallel is not None and parallel.fused_optimizer is not None else "") + ("+host_optimizer_state" if opt_state == "host" else "")
         line = {
             "metric": "train tokens/s, 30B-A3B MoE, packed 64k rows (whole job)",
             "value": round(value, 1),
@@ -295,4 +305,15 @@ def main() -> int:
 
 
 if __name__ == "__main__":
-    sys.exit(main())
+    try:
+        code = main()
+    except BaseException:
+        import traceback
+
+        traceback.print_exc()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        # leave at once: a rank that lingers in teardown while its peers wait in a collective would
+        # hold the whole job until a watchdog fires
+        os._exit(1)
+    sys.exit(code)

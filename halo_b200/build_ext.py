@@ -35,7 +35,7 @@ NVCC_FLAGS = [
 
 # Per-file additions: the optimizer's arithmetic is specified without fused multiply-adds so its CPU
 # twin can reproduce it bit for bit.
-EXTRA_FLAGS = {"optim.cu": ["-fmad=false"]}
+EXTRA_FLAGS = {"optim.cu": ["-fmad=false"], "collectives_sm100.cu": ["-fmad=false"]}
 
 
 def find_nvcc() -> str:

@@ -109,6 +109,18 @@ class ParallelRuntime:
         self.dp_world = dist.get_world_size(dp_group) if dp_group is not None else 1
         self.ep_world = dist.get_world_size(ep_group) if ep_group is not None else 1
         self._flat = None
+        self.fused_optimizer = None   # halo_b200.parallel.zero.FusedShardedAdamW for the replicated parameters
+
+    def enable_fused_optimizer(self, model, lr, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01):
+        """Shard the optimizer of the replicated parameters over the data-parallel group and fuse it
+        with its reduce-scatter / all-gather. Returns the (name, parameter) pairs the caller still has to
+        give an ordinary optimizer: the experts."""
+        from halo_b200.parallel.zero import FusedShardedAdamW
+
+        shared = [(n, p) for n, p in model.named_parameters() if not getattr(p, "is_expert", False)]
+        experts = [(n, p) for n, p in model.named_parameters() if getattr(p, "is_expert", False)]
+        self.fused_optimizer = FusedShardedAdamW(shared, self.dp_group, self.device, lr, betas, eps, weight_decay)
+        return experts
 
     @classmethod
     def for_expert_parallel(cls, world: int, device) -> "ParallelRuntime":

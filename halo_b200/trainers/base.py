@@ -97,6 +97,9 @@ class Trainer:
     def _loss_adapter(self, model, batch, normalizer):
         return self.compute_loss(model, batch, normalizer)
 
+    def after_optimizer_step(self) -> None:
+        """Hook for trainers that act on fresh weights (pushing them to a rollout copy, say)."""
+
     def next_batches(self) -> Iterator[PackedBatch]:
         src = self.train_batches() if callable(self.train_batches) else self.train_batches
         return iter(src)
@@ -140,6 +143,7 @@ class Trainer:
                 out = self.engine.train_step(b, accumulate=i < len(micro) - 1)
                 self.tokens_seen += b.n_tokens
             self.global_step += 1
+            self.after_optimizer_step()
             self._guard_non_finite(out)
             if args.logging_steps and self.global_step % args.logging_steps == 0:
                 now = time.perf_counter()

@@ -61,7 +61,31 @@ class TrainEngine:
             return self.loss_fn(self.model, dbatch, normalizer)
         return self.model(dbatch.input_ids, dbatch.position_ids, dbatch.cu_seqlens, dbatch.labels, normalizer)
 
+    def _fused_clip_and_step(self, fused) -> None:
+        """Replicated parameters go through the fused reduce-scatter / AdamW / all-gather kernels, the
+        experts through the ordinary optimizer; one scalar all-reduce assembles the global norm."""
+        import torch.distributed as dist
+
+        shard_sq = fused.pack_and_reduce()
+        experts = [p for p in self.model.parameters() if p.grad is not None and getattr(p, "is_expert", False)]
+        self.grad_norm.accumulate([p.grad for p in experts], first=True)
+        self.grad_norm.total_sq.add_(shard_sq)
+        dist.all_reduce(self.grad_norm.total_sq, group=self.parallel.dp_group)
+        self.grad_norm.finish(self.max_grad_norm)
+        self.optimizer.defer_grad_scale(self.grad_norm.coef)
+        self.optimizer.arm_skip(self.grad_norm.skip)
+        self.optimizer.step()
+        fused.step(self.grad_norm.coef, self.grad_norm.skip)
+        if self.lr_scheduler is not None:
+            self.lr_scheduler.step()
+            fused.lr = self.optimizer.param_groups[0]["lr"]
+        self.optimizer.zero_grad(set_to_none=True)
+        fused.zero_grad()
+
     def clip_and_step(self) -> None:
+        fused = getattr(self.parallel, "fused_optimizer", None) if self.parallel is not None else None
+        if fused is not None:
+            return self._fused_clip_and_step(fused)
         params = [p for p in self.model.parameters() if p.grad is not None]
         if self.parallel is not None:
             self.parallel.sync_gradients(self.model)

@@ -1,0 +1,150 @@
+"""Run under torchrun on 2+ GPUs: the expert transport over peer memory, the fused sharded optimizer
+and the peer-store broadcast against single-device references. Prints ``CHECKS PASSED`` on rank 0."""
+
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+
+def close(a, b, tol, what):
+    err = (a.float() - b.float()).abs().max().item()
+    ref = b.float().abs().max().item()
+    assert err <= tol * ref + 1e-3, f"{what}: max err {err} (ref max {ref})"
+
+
+def check_expert_transport(parallel, dev, rank, world):
+    """Each rank owns E/world experts; every rank's tokens must come back as if all experts were local."""
+    from halo_b200.ops.moe import moe_experts, moe_ffn_reference
+
+    T, H, F, E, k = 1536, 512, 256, 16, 4
+    tr = parallel.transport
+    tr.configure(max_tokens=T, top_k=k, hidden=H, n_local_experts=E // world)
+    g = torch.Generator(device=dev).manual_seed(7)
+    wgu_full = (torch.randn(E, 2 * F, H, device=dev, generator=g) * 0.05).bfloat16()
+    wd_full = (torch.randn(E, H, F, device=dev, generator=g) * 0.05).bfloat16()
+    g2 = torch.Generator(device=dev).manual_seed(100 + rank)
+    x = torch.randn(T, H, device=dev, generator=g2).bfloat16()
+    scores = torch.rand(T, E, device=dev, generator=g2)
+    w, idx = torch.topk(scores, k, dim=-1)
+    w = (w / w.sum(-1, keepdim=True)).float()
+    idx = idx.to(torch.int32)
+    e0, e1 = rank * (E // world), (rank + 1) * (E // world)
+    xa, wa = x.clone().requires_grad_(), w.clone().requires_grad_()
+    wgu = wgu_full[e0:e1].clone().requires_grad_()
+    wd = wd_full[e0:e1].clone().requires_grad_()
+    out = moe_experts(xa, idx, wa, wgu, wd, tr)
+    gout = torch.randn(T, H, device=dev, generator=g2).bfloat16()
+    out.backward(gout)
+    torch.cuda.synchronize()
+    # reference: all experts local, this rank's tokens
+    xb, wb = x.float().requires_grad_(), w.clone().requires_grad_()
+    wgub, wdb = wgu_full.float().requires_grad_(), wd_full.float().requires_grad_()
+    ref = moe_ffn_reference(xb, idx, wb, wgub, wdb)
+    ref.backward(gout.float())
+    close(out, ref, 3e-2, "ep out")
+    close(xa.grad, xb.grad, 4e-2, "ep dx")
+    close(wa.grad, wb.grad, 4e-2, "ep dw_route")
+    # expert weight gradients: sum over ranks of the reference's per-rank contributions
+    gw = wgub.grad.clone()
+    gd = wdb.grad.clone()
+    dist.all_reduce(gw)
+    dist.all_reduce(gd)
+    close(wgu.grad, gw[e0:e1], 5e-2, "ep dw_gate_up")
+    close(wd.grad, gd[e0:e1], 5e-2, "ep dw_down")
+
+
+def check_fused_optimizer(dev, rank, world):
+    from halo_b200.optim.adamw_bf16 import adamw_bf16_step_reference, param_name_hash, SR_KEY
+    from halo_b200.parallel.zero import FusedShardedAdamW
+
+    shapes = {"a.weight": (300, 64), "b.norm": (64,), "c.weight": (1000, 33), "d.weight": (7,)}
+    g = torch.Generator().manual_seed(3)
+    init = {n: torch.randn(s, generator=g).bfloat16() for n, s in shapes.items()}
+    params = [(n, torch.nn.Parameter(t.clone().to(dev))) for n, t in init.items()]
+    opt = FusedShardedAdamW(params, dist.group.WORLD, dev, lr=1e-2, weight_decay=0.1)
+    ref_p = {n: t.clone() for n, t in init.items()}
+    ref_m = {n: torch.zeros_like(t) for n, t in init.items()}
+    ref_v = {n: torch.zeros_like(t) for n, t in init.items()}
+    for step in range(1, 4):
+        grads_all = []
+        for r in range(world):
+            gr = torch.Generator().manual_seed(1000 * step + r)
+            grads_all.append({n: (torch.randn(s, generator=gr) * 0.1).bfloat16() for n, s in shapes.items()})
+        for n, p in params:
+            p.grad = grads_all[rank][n].to(dev)
+        sq = opt.pack_and_reduce()
+        dist.all_reduce(sq)
+        total = {n: sum(ga[n].float() for ga in grads_all) for n in shapes}
+        want_sq = sum(t.pow(2).sum() for t in total.values())
+        assert abs(sq.item() - want_sq.item()) <= 1e-3 * want_sq.item(), (sq.item(), want_sq.item())
+        scale = torch.tensor([0.5], device=dev)
+        opt.step(scale, None)
+        torch.cuda.synchronize()
+        b1, b2 = 0.9, 0.999
+        for n in shapes:
+            wd = 0.1 if len(shapes[n]) > 1 else 0.0
+            adamw_bf16_step_reference(ref_p[n], total[n], ref_m[n], ref_v[n], beta1=b1, beta2=b2,
+                                      step_size=1e-2 / (1 - b1**step), bc2_sqrt=(1 - b2**step) ** 0.5, eps=1e-8,
+                                      wd_factor=1.0 - 1e-2 * wd, key=SR_KEY, step=step, name_hash=param_name_hash(n),
+                                      grad_scale=0.5)
+        for n, p in params:
+            assert torch.equal(p.detach().cpu(), ref_p[n]), f"fused optimizer: {n} differs at step {step} on rank {rank}"
+
+
+def check_broadcast_and_allreduce(dev, rank, world):
+    import torch.distributed._symmetric_memory as symm
+
+    from halo_b200.ops import _lib
+
+    n = 1 << 20
+    buf = symm.empty((n,), dtype=torch.bfloat16, device=dev)
+    buf.zero_()
+    h = symm.rendezvous(buf, dist.group.WORLD)
+    h.barrier(channel=0)
+    src = torch.arange(n, device=dev, dtype=torch.float32).bfloat16()
+    L = _lib.lib()
+    if rank == 0:
+        ptrs = (_lib.c_void_p * world)(*list(h.buffer_ptrs))
+        _lib.check(L.halo_broadcast_bytes(_lib.ptr(src), ptrs, _lib.c_int(world), _lib.c_ll(0), _lib.c_ll(n * 2),
+                                          _lib.stream_ptr(dev)), "halo_broadcast_bytes")
+    h.barrier(channel=0)
+    torch.cuda.synchronize()
+    assert torch.equal(buf, src), "broadcast payload differs"
+    small = symm.empty((64,), dtype=torch.float32, device=dev)
+    small.fill_(float(rank + 1))
+    hs = symm.rendezvous(small, dist.group.WORLD)
+    hs.barrier(channel=0)
+    out = torch.empty(64, device=dev)
+    ptrs = (_lib.c_void_p * world)(*list(hs.buffer_ptrs))
+    _lib.check(L.halo_allreduce_small(ptrs, _lib.c_int(world), _lib.ptr(out), _lib.c_int(64), _lib.stream_ptr(dev)),
+               "halo_allreduce_small")
+    torch.cuda.synchronize()
+    assert torch.all(out == world * (world + 1) / 2)
+    hs.barrier(channel=0)
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    from halo_b200.ops import _lib
+    from halo_b200.parallel.runtime import ParallelRuntime
+
+    parallel = ParallelRuntime.for_expert_parallel(world, dev)
+    check_expert_transport(parallel, dev, rank, world)
+    check_fused_optimizer(dev, rank, world)
+    check_broadcast_and_allreduce(dev, rank, world)
+    _lib.raise_on_status(dev)
+    dist.barrier()
+    if rank == 0:
+        print("CHECKS PASSED")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
