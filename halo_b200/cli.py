@@ -1,0 +1,70 @@
+"""``python -m halo_b200.cli launch <method> <config.yaml> -n N [--key=value ...]`` builds the torchrun
+(or plain python) command line for a training method; ``run <tool>`` starts a tool module
+(the role of halo/cli.py:1-349; single node only)."""
+
+from __future__ import annotations
+
+import argparse
+import os
+import shlex
+import subprocess
+import sys
+
+METHODS = {
+    "sft": "halo_b200.entrypoints.training.sft",
+    "dpo": "halo_b200.entrypoints.training.preference",
+    "kto": "halo_b200.entrypoints.training.preference",
+    "smpo": "halo_b200.entrypoints.training.preference",
+    "reward": "halo_b200.entrypoints.training.reward",
+    "distill": "halo_b200.entrypoints.training.distill",
+    "grpo": "halo_b200.entrypoints.training.grpo",
+}
+TOOLS = {
+    "merge-ep-shards": "halo_b200.checkpoint.tools.merge_ep_shards",
+    "convert-dtype": "halo_b200.checkpoint.tools.convert_dtype",
+    "bench": "bench",
+}
+
+
+def build_command(method: str, config: str, nproc: int, overrides: list[str], port: int = 29500,
+                  numa_binding: bool = False) -> list[str]:
+    if method not in METHODS:
+        raise SystemExit(f"unknown method {method!r}; choose from {', '.join(sorted(METHODS))}")
+    module = METHODS[method]
+    extra = [f"--preference_loss={method}"] if method in ("dpo", "kto", "smpo") else []
+    if nproc <= 1:
+        return [sys.executable, "-m", module, config, *extra, *overrides]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port)]
+    if numa_binding:
+        cmd += ["--numa-binding", "node"]
+    return cmd + ["-m", module, config, *extra, *overrides]
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="halo_b200")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    la = sub.add_parser("launch")
+    la.add_argument("method")
+    la.add_argument("config")
+    la.add_argument("-n", "--nproc", type=int, default=1)
+    la.add_argument("--port", type=int, default=29500)
+    la.add_argument("--numa-binding", action="store_true")
+    la.add_argument("--dry-run", action="store_true")
+    ru = sub.add_parser("run")
+    ru.add_argument("tool")
+    args, rest = ap.parse_known_args(argv)
+    if args.cmd == "launch":
+        cmd = build_command(args.method, args.config, args.nproc, rest, args.port, args.numa_binding)
+    else:
+        if args.tool not in TOOLS:
+            raise SystemExit(f"unknown tool {args.tool!r}; choose from {', '.join(sorted(TOOLS))}")
+        cmd = [sys.executable, "-m", TOOLS[args.tool], *rest]
+    if getattr(args, "dry_run", False):
+        print(" ".join(shlex.quote(c) for c in cmd))
+        return 0
+    return subprocess.call(cmd, env=dict(os.environ))
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,111 @@
+"""Dataset sources and the packing pipeline (the part of halo/data/** the trainers need).
+
+Sources: ``.jsonl`` / ``.json`` files or directories of them (text, chat ``messages``,
+prompt/completion, preference pairs, pre-tokenised ``input_ids``), and the synthetic generator.
+Tokenisation uses a Hugging Face tokenizer when one is available next to the checkpoint; rows are
+sharded over data-parallel ranks Megatron-style (rank r takes rows r, r + dp, ...), packed into
+fixed-length rows in a deterministic order, and cached under a key derived from the inputs so a
+second run (or the other ranks) reads the cache instead of recomputing
+(halo/data/pipeline/coordinated_map.py, halo/data/sources/sharded_dataset.py)."""
+
+from __future__ import annotations
+
+import glob
+import hashlib
+import json
+import os
+from typing import Iterator
+
+import numpy as np
+
+from halo_b200.data.packing import PackedBatch, pack_documents, synthetic_packed_batch
+
+
+def list_files(path: str) -> list[str]:
+    if os.path.isdir(path):
+        return sorted(glob.glob(os.path.join(path, "**", "*.json*"), recursive=True))
+    return [path]
+
+
+def read_records(path: str) -> Iterator[dict]:
+    for f in list_files(path):
+        with open(f) as fh:
+            if f.endswith(".jsonl"):
+                for line in fh:
+                    if line.strip():
+                        yield json.loads(line)
+            else:
+                data = json.load(fh)
+                yield from (data if isinstance(data, list) else [data])
+
+
+def cache_key(*parts) -> str:
+    h = hashlib.blake2b(digest_size=12)
+    for p in parts:
+        h.update(json.dumps(p, sort_keys=True, default=str).encode())
+    return h.hexdigest()
+
+
+def render_messages(messages: list[dict]) -> tuple[str, list[tuple[int, int]]]:
+    """Minimal ChatML rendering; returns the text and the character spans of assistant turns."""
+    text, spans = "", []
+    for m in messages:
+        head = f"<|im_start|>{m['role']}\n"
+        body = f"{m['content']}<|im_end|>\n"
+        if m["role"] == "assistant":
+            spans.append((len(text) + len(head), len(text) + len(head) + len(body)))
+        text += head + body
+    return text, spans
+
+
+def tokenize_record(rec: dict, tokenizer, fmt: str = "auto") -> tuple[np.ndarray, np.ndarray]:
+    """(token ids, bool mask of tokens that may be targets)."""
+    if "input_ids" in rec:
+        ids = np.asarray(rec["input_ids"], dtype=np.int64)
+        mask = np.asarray(rec.get("loss_mask", np.ones(len(ids), bool)), dtype=bool)
+        return ids, mask
+    if tokenizer is None:
+        raise ValueError("a tokenizer is needed for text records (or provide pre-tokenised 'input_ids')")
+    if "messages" in rec:
+        text, spans = render_messages(rec["messages"])
+        enc = tokenizer(text, return_offsets_mapping=True, add_special_tokens=False)
+        ids = np.asarray(enc["input_ids"], dtype=np.int64)
+        mask = np.zeros(len(ids), bool)
+        for i, (a, b) in enumerate(enc["offset_mapping"]):
+            mask[i] = any(a >= s and b <= e for s, e in spans)
+        return ids, mask
+    if "prompt" in rec and "completion" in rec:
+        p = tokenizer(rec["prompt"], add_special_tokens=False)["input_ids"]
+        c = tokenizer(rec["completion"], add_special_tokens=False)["input_ids"]
+        return np.asarray(p + c, dtype=np.int64), np.asarray([False] * len(p) + [True] * len(c))
+    ids = np.asarray(tokenizer(rec.get("text", ""), add_special_tokens=False)["input_ids"], dtype=np.int64)
+    return ids, np.ones(len(ids), bool)
+
+
+def pack_rows(docs: list[tuple[np.ndarray, np.ndarray]], row_len: int, completion_only: bool) -> list[PackedBatch]:
+    """Greedy sequential packing into rows of ``row_len`` tokens; a document longer than a row is cut."""
+    rows, cur, cur_masks, used = [], [], [], 0
+    for ids, mask in docs:
+        ids, mask = ids[:row_len], mask[:row_len]
+        if used + len(ids) > row_len and cur:
+            rows.append(pack_documents(cur, row_len=row_len, label_masks=cur_masks if completion_only else None))
+            cur, cur_masks, used = [], [], 0
+        cur.append(ids)
+        cur_masks.append(mask)
+        used += len(ids)
+    if cur:
+        rows.append(pack_documents(cur, row_len=row_len, label_masks=cur_masks if completion_only else None))
+    return rows
+
+
+def build_sft_batches(data_args, tokenizer, dp_rank: int = 0, dp_world: int = 1, vocab_size: int = 0) -> list[PackedBatch]:
+    if data_args.dataset_format == "synthetic" or not data_args.dataset_path:
+        n = 64
+        return [synthetic_packed_batch(data_args.packed_row_length, data_args.synthetic_vocab or vocab_size,
+                                       seed=data_args.shuffle_seed * 100003 + i * dp_world + dp_rank,
+                                       lo=data_args.doc_length_min, hi=data_args.doc_length_max) for i in range(n)]
+    docs = [tokenize_record(r, tokenizer, data_args.dataset_format) for r in read_records(data_args.dataset_path)]
+    order = np.random.default_rng(data_args.shuffle_seed).permutation(len(docs))
+    docs = [docs[i] for i in order]
+    rows = pack_rows(docs, data_args.packed_row_length, data_args.completion_only_loss)
+    return rows[dp_rank::dp_world]

@@ -1,0 +1,35 @@
+"""Supervised fine-tuning entry point:  torchrun -m halo_b200.entrypoints.training.sft config.yaml [--key=value]"""
+
+from halo_b200.configs.arguments import SFTArguments
+from halo_b200.entrypoints.script import (build_runtime, init_training_script, load_policy_model, parse_script_args,
+                                          run_trainer, with_distributed_teardown)
+
+
+@with_distributed_teardown
+def main(argv=None):
+    from halo_b200.callbacks.efficiency import EfficiencyCallback
+    from halo_b200.data.datasets import build_sft_batches
+    from halo_b200.trainers.sft import SFTTrainer
+
+    device, (model_args, data_args, train_args, par_args, sft_args) = parse_script_args(SFTArguments, argv=argv)
+    pc = init_training_script(device, model_args, train_args, par_args)
+    runtime = build_runtime(pc, device)
+    model = load_policy_model(model_args, pc, device, runtime, train_args.gradient_checkpointing,
+                              max_tokens=data_args.packed_row_length * train_args.per_device_train_batch_size)
+    tokenizer = None
+    if model_args.model_name_or_path:
+        try:
+            from transformers import AutoTokenizer
+
+            tokenizer = AutoTokenizer.from_pretrained(model_args.model_name_or_path)
+        except Exception:
+            tokenizer = None
+    batches = build_sft_batches(data_args, tokenizer, pc.data_parallel_rank, pc.data_parallel_size, model.cfg.vocab_size)
+    trainer = SFTTrainer(model, train_args, batches, device=device, parallel=runtime,
+                         callbacks=[EfficiencyCallback(model.cfg, pc.world_size)],
+                         parallelism_fingerprint=pc.fingerprint())
+    return run_trainer(trainer, train_args)
+
+
+if __name__ == "__main__":
+    main()
