@@ -1,0 +1,175 @@
+"""Kernel microbenchmarks at the shapes of the 30B-A3B MoE layer (64k-token packed rows).
+
+    python benchmarks/kernels.py                    # every case, full shapes
+    python benchmarks/kernels.py --only gemm attn   # a subset
+    python benchmarks/kernels.py --small --iters 1 --warmup 1 --only gemm_qkv   # a case sized for a profiler capture
+
+Timing: CUDA events on the launching stream around each call, after warm-up, with a write of a buffer
+larger than L2 between iterations; the median is reported. Rates are set against the measured copy
+bandwidth and bf16 GEMM rate of the machine when a ``MEASURED_PEAKS.json`` is found at the repository
+root (else against 6.65 TB/s and 1.59 PFLOP/s).
+
+Covers what the reference's kernel benchmarks cover (tests/gpu/profiling/benchmark_roofline.py,
+benchmark_grouped_mm.py, benchmark_moe_block.py, benchmark_attention_implementations.py).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from halo_b200.data.packing import sample_doc_lengths  # noqa: E402
+from halo_b200.ops import attention as attn_ops  # noqa: E402
+from halo_b200.ops import gemm, moe as moe_ops  # noqa: E402
+from halo_b200.ops.norm import add_rms_norm, rms_norm  # noqa: E402
+
+import numpy as np  # noqa: E402
+
+
+def peaks():
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        p = json.load(open(path))
+        return p["hbm_gbs"], p["bf16_tflops"], "of measured"
+    return 6650.0, 1590.0, "of fallback"
+
+
+class Timer:
+    def __init__(self, iters, warmup):
+        self.iters, self.warmup = iters, warmup
+        self.flush = torch.empty(192 << 20, dtype=torch.uint8, device="cuda")
+
+    def __call__(self, fn):
+        for _ in range(self.warmup):
+            fn()
+        times = []
+        for _ in range(self.iters):
+            self.flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+        return statistics.median(times)
+
+
+def bf16(*shape):
+    return torch.randn(*shape, device="cuda", dtype=torch.bfloat16) * 0.05
+
+
+def cases(small: bool):
+    T = 8192 if small else 65536
+    H, F, E, K = 2048, 768, 128, 8
+    NQ, NKV, HD = 32, 4, 128
+    V = 16384 if small else 151936
+    out = {}
+
+    # ---- dense GEMMs --------------------------------------------------------------------------
+    def dense(name, M, N, Kd, a_t=False, b_t=True):
+        a = bf16(Kd, M) if a_t else bf16(M, Kd)
+        b = bf16(N, Kd) if b_t else bf16(Kd, N)
+        c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        out[name] = (lambda: gemm.matmul(a, b, a_t=a_t, b_t=b_t, out=c), 2.0 * M * N * Kd, 2.0 * (M * Kd + N * Kd + M * N))
+
+    dense("gemm_qkv", T, (NQ + 2 * NKV) * HD, H)
+    dense("gemm_o", T, H, NQ * HD)
+    dense("gemm_qkv_dgrad", T, H, (NQ + 2 * NKV) * HD, b_t=False)
+    dense("gemm_qkv_wgrad", (NQ + 2 * NKV) * HD, H, T, a_t=True, b_t=False)
+    dense("gemm_head", T, V, H)
+    dense("gemm_square_8192", 8192, 8192, 8192)
+
+    def cublas(name, M, N, Kd):
+        a, b = bf16(M, Kd), bf16(N, Kd)
+        out[name] = (lambda: torch.matmul(a, b.t()), 2.0 * M * N * Kd, 2.0 * (M * Kd + N * Kd + M * N))
+
+    cublas("cublas_qkv", T, (NQ + 2 * NKV) * HD, H)
+    cublas("cublas_square_8192", 8192, 8192, 8192)
+
+    # ---- routed experts (single rank holds all experts) ----------------------------------------
+    x = bf16(T, H)
+    logits = torch.randn(T, E, device="cuda", dtype=torch.bfloat16)
+    idx, w = moe_ops.router_topk(logits, K, True)
+    w_gu, w_dn = bf16(E, 2 * F, H), bf16(E, H, F)
+    expert_flops = 2.0 * T * K * 3 * H * F
+    out["moe_experts_fwd"] = (lambda: moe_ops.moe_experts(x, idx, w, w_gu, w_dn), expert_flops,
+                              2.0 * (2 * T * H + 2 * T * K * (2 * H + F) + 3 * E * H * F))
+
+    xg = x.clone().requires_grad_(True)
+    wg, wd = w_gu.clone().requires_grad_(True), w_dn.clone().requires_grad_(True)
+    dy = bf16(T, H)
+
+    def moe_fb():
+        y = moe_ops.moe_experts(xg, idx, w, wg, wd)
+        y.backward(dy)
+        xg.grad = wg.grad = wd.grad = None
+
+    out["moe_experts_fwd_bwd"] = (moe_fb, 3 * expert_flops, 0.0)
+
+    # ---- attention ----------------------------------------------------------------------------
+    for dist_name in ("chat", "loguniform"):
+        lens = sample_doc_lengths(T, np.random.default_rng(0), dist_name)
+        cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+        plan = attn_ops.build_plan(cu, "cuda")
+        q, k, v = bf16(T, NQ * HD), bf16(T, NKV * HD), bf16(T, NKV * HD)
+        flops = sum(4.0 * NQ * HD * (n * (n + 1) / 2) for n in lens)
+        out[f"attn_fwd_{dist_name}"] = (lambda q=q, k=k, v=v, plan=plan: attn_ops.flash_attention(q, k, v, plan, NQ, NKV),
+                                       flops, 2.0 * T * HD * (2 * NQ + 2 * NKV))
+        qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+        do = bf16(T, NQ * HD)
+
+        def attn_fb(qg=qg, kg=kg, vg=vg, plan=plan, do=do):
+            o = attn_ops.flash_attention(qg, kg, vg, plan, NQ, NKV)
+            o.backward(do)
+            qg.grad = kg.grad = vg.grad = None
+
+        out[f"attn_fwd_bwd_{dist_name}"] = (attn_fb, 3.5 * flops, 0.0)
+
+    # ---- bandwidth-bound pieces ---------------------------------------------------------------
+    wn = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    res = bf16(T, H)
+    out["rmsnorm_fwd"] = (lambda: rms_norm(x, wn, 1e-6), 0.0, 2.0 * 2 * T * H)
+    out["add_rmsnorm_fwd"] = (lambda: add_rms_norm(x, res, wn, 1e-6), 0.0, 2.0 * 4 * T * H)
+    big = torch.empty(1 << 30, dtype=torch.bfloat16, device="cuda") if not small else torch.empty(1 << 27, dtype=torch.bfloat16, device="cuda")
+    big2 = torch.empty_like(big)
+    out["copy_reference"] = (lambda: big2.copy_(big), 0.0, 2.0 * 2 * big.numel())
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", nargs="*", default=None, help="substrings of case names to run")
+    ap.add_argument("--small", action="store_true", help="8k tokens, 16k vocabulary: sized for a profiler capture")
+    ap.add_argument("--iters", type=int, default=7)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--json", default="")
+    args = ap.parse_args()
+    hbm, tf, tag = peaks()
+    timer = Timer(args.iters, args.warmup)
+    rows = []
+    for name, (fn, flops, nbytes) in cases(args.small).items():
+        if args.only and not any(s in name for s in args.only):
+            continue
+        ms = timer(fn)
+        tfs = flops / ms / 1e9 if flops else 0.0
+        gbs = nbytes / ms / 1e6 if nbytes else 0.0
+        frac = max(tfs / tf, gbs / hbm)
+        rows.append({"case": name, "ms": round(ms, 4), "tflops": round(tfs, 1), "gb_s": round(gbs, 1),
+                     "fraction_of_peak": round(frac, 3)})
+        print(f"{name:28s} {ms:9.3f} ms  {tfs:8.1f} TF/s  {gbs:8.1f} GB/s  {frac:5.2f} {tag}", flush=True)
+    if args.json:
+        os.makedirs(os.path.dirname(args.json) or ".", exist_ok=True)
+        json.dump({"peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "basis": tag}, "rows": rows}, open(args.json, "w"), indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -36,20 +36,22 @@ def _ep_info(model):
 def _gather_expert_bank(t: torch.Tensor, n_ranks: int, group) -> torch.Tensor:
     if n_ranks == 1:
         return t
-    out = torch.empty((n_ranks,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+    out = torch.empty((n_ranks * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
     dist.all_gather_into_tensor(out, t.contiguous(), group=group)
-    return out.reshape((n_ranks * t.shape[0],) + tuple(t.shape[1:]))
+    return out
 
 
 def save_model(model, directory: str, is_writer: bool | None = None, save_dtype: torch.dtype | None = torch.bfloat16,
-               max_shard_bytes: int = 5 * 1024**3, sharded_experts: bool = False, extra_state: dict | None = None) -> None:
+               max_shard_bytes: int = 5 * 1024**3, sharded_experts: bool = False, extra_state: dict | None = None,
+               group=None) -> None:
     """COLLECTIVE over the expert group when experts are sharded. ``is_writer``: this rank writes the
     files (default: global rank 0). ``sharded_experts``: every rank writes only its own experts to
-    ``ep_shard_<rank>/`` (merge offline with halo_b200.checkpoint.tools.merge_ep_shards)."""
+    ``ep_shard_<rank>/`` (merge offline with halo_b200.checkpoint.tools.merge_ep_shards). ``group``: the
+    ranks that take part in the save (default: the whole job); failures are agreed over it."""
     cfg = model.cfg
     n_ep, ep_rank, ep_group = _ep_info(model)
     live = dist.is_available() and dist.is_initialized()
-    rank = dist.get_rank() if live else 0
+    rank = dist.get_rank(group) if live else 0
     if is_writer is None:
         is_writer = rank == 0
     guard = DeferredRankFailure()
@@ -92,7 +94,7 @@ def save_model(model, directory: str, is_writer: bool | None = None, save_dtype:
             cfg.save(directory)
             if extra_state is not None:
                 atomic_write_json(os.path.join(directory, "halo_state.json"), extra_state)
-    guard.raise_if_any(None if not live else dist.group.WORLD, "saving the model failed")
+    guard.raise_if_any(None if not live else (group or dist.group.WORLD), "saving the model failed")
 
 
 def mark_complete(directory: str, trainer_state: dict) -> None:

@@ -59,7 +59,7 @@ __device__ __forceinline__ __nv_bfloat16 sr_bf16_c(float x, uint32_t noise16) {
 // phase 1: sum[i] = sum_r grads_r[lo + i]  (fp32, rank order);  partial[b] = sum of squares
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-rs_sum_norm_kernel(const Peers grads, int n_ranks, long long lo, long long count, float* __restrict__ sum_out,
+rs_sum_norm_kernel(const __grid_constant__ Peers grads, int n_ranks, long long lo, long long count, float* __restrict__ sum_out,
                    float* __restrict__ partial) {
     __shared__ float red[8];
     float acc = 0.f;
@@ -113,7 +113,7 @@ struct SliceTable {
 constexpr int kSliceElemsPerBlock = 256 * 8 * 8;
 
 __global__ void __launch_bounds__(256)
-adam_allgather_kernel(const Peers params, int n_ranks, int my_rank, long long lo, const float* __restrict__ gsum,
+adam_allgather_kernel(const __grid_constant__ Peers params, int n_ranks, int my_rank, long long lo, const float* __restrict__ gsum,
                       __nv_bfloat16* __restrict__ m, __nv_bfloat16* __restrict__ v, SliceTable tab, float beta1,
                       float beta2, float omb1, float omb2, float step_size, float bc2_sqrt, float eps,
                       unsigned long long key_step, const float* __restrict__ grad_scale, const int* __restrict__ skip) {
@@ -183,7 +183,7 @@ adam_allgather_kernel(const Peers params, int n_ranks, int my_rank, long long lo
 
 // dst_r[i] = src[i] for every destination rank (16-byte vectors; n_bytes multiple of 16)
 __global__ void __launch_bounds__(256)
-broadcast_bytes_kernel(const uint4* __restrict__ src, const Peers dst, int n_dst, long long dst_offset_vec,
+broadcast_bytes_kernel(const uint4* __restrict__ src, const __grid_constant__ Peers dst, int n_dst, long long dst_offset_vec,
                        long long nvec) {
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
         const uint4 u = src[i];
@@ -192,7 +192,7 @@ broadcast_bytes_kernel(const uint4* __restrict__ src, const Peers dst, int n_dst
 }
 
 // out[i] = sum_r bufs_r[i]   (fp32, n small)
-__global__ void allreduce_small_kernel(const Peers bufs, int n_ranks, float* __restrict__ out, int n) {
+__global__ void allreduce_small_kernel(const __grid_constant__ Peers bufs, int n_ranks, float* __restrict__ out, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     float s = 0.f;

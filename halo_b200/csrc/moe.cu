@@ -285,7 +285,9 @@ route_place_kernel(const int* __restrict__ topk_idx, long long n_slots, int E,
 // ---------------------------------------------------------------------------------------------
 // Token movement. `bufs.p[r]` is the base of rank r's buffer ([rows, H] bf16); for the local rank
 // it is an ordinary device pointer, for a peer it is that GPU's memory mapped into this process.
-// The table travels by value in the kernel parameters, so no device-side table is needed.
+// The table travels by value in the kernel parameters, so no device-side table is needed; it is
+// declared __grid_constant__ so that indexing it by a run-time rank reads the parameter bank instead
+// of first copying the whole table to each thread's stack.
 // ---------------------------------------------------------------------------------------------
 constexpr int kMaxPeers = 16;
 struct PeerPtrs {
@@ -295,7 +297,7 @@ struct PeerPtrs {
 __global__ void __launch_bounds__(256)
 dispatch_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ topk_idx,
                      const int* __restrict__ slot_row, const float* __restrict__ slot_w,
-                     const PeerPtrs bufs, const PeerPtrs wbufs, int has_w,
+                     const __grid_constant__ PeerPtrs bufs, const __grid_constant__ PeerPtrs wbufs, int has_w,
                      long long T, int k, int H, int experts_per_rank, int cap_rows, int* status) {
     const long long t = blockIdx.x;
     const int nvec = H / 8;
@@ -338,7 +340,7 @@ zero_pad_rows_kernel(__nv_bfloat16* __restrict__ buf, const int* __restrict__ se
 
 // out[t] = sum_j w[t,j] * bufs[rank(t,j)][row(t,j)]   (+ addend[t]);  w == nullptr means 1.
 __global__ void __launch_bounds__(256)
-combine_rows_kernel(const PeerPtrs bufs, const int* __restrict__ topk_idx,
+combine_rows_kernel(const __grid_constant__ PeerPtrs bufs, const int* __restrict__ topk_idx,
                     const int* __restrict__ slot_row, const float* __restrict__ w,
                     const __nv_bfloat16* __restrict__ addend, __nv_bfloat16* __restrict__ out,
                     long long T, int k, int H, int experts_per_rank, int cap_rows) {
@@ -409,8 +411,60 @@ scale_rows_dot_kernel(__nv_bfloat16* __restrict__ g, const __nv_bfloat16* __rest
     }
 }
 
+// SwiGLU backward on the expert side with the routing weight folded in. Per row r (one warp each):
+//   act      = silu(gate) * up                      (from the saved pre-activations)
+//   dwrow[r] = <dact_u[r], act>                      = d loss / d routing weight of the row
+//   dpre[r]  = w[r] * swiglu'(pre[r]) (.) dact_u[r]
+//   act_w[r] = w[r] * act                            (left operand of the down-projection weight gradient)
+// where dact_u = dout_rows W_down is the unscaled activation gradient. <dout, y> = <dout W_down, act>, so
+// neither the expert output rows nor a pre-scaled copy of the incoming gradient is needed.
+__global__ void __launch_bounds__(256)
+swiglu_bwd_weighted_kernel(const __nv_bfloat16* __restrict__ pre, const __nv_bfloat16* __restrict__ dact,
+                           const float* __restrict__ w, __nv_bfloat16* __restrict__ dpre,
+                           __nv_bfloat16* __restrict__ act_w, float* __restrict__ dwrow,
+                           const int* __restrict__ total_rows, int F, int cap_rows) {
+    const int lane = threadIdx.x & 31;
+    const int rows = min(*total_rows, cap_rows);
+    const int nvec = F / 8;
+    for (long long r = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); r < rows; r += (long long)gridDim.x * 8) {
+        const float sc = w[r];
+        const __nv_bfloat16* pg = pre + r * 2 * F;
+        float dot = 0.f;
+        for (int v = lane; v < nvec; v += 32) {
+            const uint4 gu = *reinterpret_cast<const uint4*>(pg + v * 8);
+            const uint4 uu = *reinterpret_cast<const uint4*>(pg + F + v * 8);
+            const uint4 du = *reinterpret_cast<const uint4*>(dact + r * F + v * 8);
+            const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gu);
+            const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uu);
+            const __nv_bfloat162* dh = reinterpret_cast<const __nv_bfloat162*>(&du);
+            uint4 og, ou, oa;
+            __nv_bfloat162* ogh = reinterpret_cast<__nv_bfloat162*>(&og);
+            __nv_bfloat162* ouh = reinterpret_cast<__nv_bfloat162*>(&ou);
+            __nv_bfloat162* oah = reinterpret_cast<__nv_bfloat162*>(&oa);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float2 g = __bfloat1622float2(gh[q]), u = __bfloat1622float2(uh[q]), d = __bfloat1622float2(dh[q]);
+                const float sx = 1.f / (1.f + __expf(-g.x)), sy = 1.f / (1.f + __expf(-g.y));
+                // the forward rounded act to bf16 before the down projection; use the same value here
+                const float2 a = __bfloat1622float2(__floats2bfloat162_rn(g.x * sx * u.x, g.y * sy * u.y));
+                dot += d.x * a.x + d.y * a.y;
+                const float dx = d.x * sc, dy = d.y * sc;
+                ouh[q] = __floats2bfloat162_rn(dx * g.x * sx, dy * g.y * sy);
+                ogh[q] = __floats2bfloat162_rn(dx * u.x * sx * (1.f + g.x * (1.f - sx)),
+                                               dy * u.y * sy * (1.f + g.y * (1.f - sy)));
+                oah[q] = __floats2bfloat162_rn(a.x * sc, a.y * sc);
+            }
+            *reinterpret_cast<uint4*>(dpre + r * 2 * F + v * 8) = og;
+            *reinterpret_cast<uint4*>(dpre + r * 2 * F + F + v * 8) = ou;
+            *reinterpret_cast<uint4*>(act_w + r * F + v * 8) = oa;
+        }
+        dot = wsum(dot);
+        if (lane == 0) dwrow[r] = dot;
+    }
+}
+
 // dw[t,j] = dwrow_bufs[rank(t,j)][row(t,j)]
-__global__ void gather_slot_values_kernel(const PeerPtrs vbufs,
+__global__ void gather_slot_values_kernel(const __grid_constant__ PeerPtrs vbufs,
                                           const int* __restrict__ topk_idx,
                                           const int* __restrict__ slot_row, float* __restrict__ out,
                                           long long n_slots, int experts_per_rank, int cap_rows) {
@@ -547,6 +601,15 @@ int halo_scale_rows_dot(void* g, const void* y, const float* scale, float* dwrow
                         const int* total_rows, int H, int cap_rows, void* stream) {
     scale_rows_dot_kernel<<<1184, 256, 0, (cudaStream_t)stream>>>(
         (__nv_bfloat16*)g, (const __nv_bfloat16*)y, scale, dwrow, total_rows, H, cap_rows);
+    return HALO_LAUNCH_CHECK();
+}
+
+int halo_swiglu_bwd_weighted(const void* pre, const void* dact, const float* w, void* dpre, void* act_w, float* dwrow,
+                             const int* total_rows, int F, int cap_rows, void* stream) {
+    if (F % 8) return -1;
+    swiglu_bwd_weighted_kernel<<<2368, 256, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)pre, (const __nv_bfloat16*)dact, w, (__nv_bfloat16*)dpre, (__nv_bfloat16*)act_w, dwrow,
+        total_rows, F, cap_rows);
     return HALO_LAUNCH_CHECK();
 }
 

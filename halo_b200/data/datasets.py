@@ -109,3 +109,51 @@ def build_sft_batches(data_args, tokenizer, dp_rank: int = 0, dp_world: int = 1,
     docs = [docs[i] for i in order]
     rows = pack_rows(docs, data_args.packed_row_length, data_args.completion_only_loss)
     return rows[dp_rank::dp_world]
+
+
+def build_preference_batches(data_args, tokenizer, dp_rank: int = 0, dp_world: int = 1, vocab_size: int = 0,
+                             kto: bool = False):
+    """Rows of (chosen, rejected) document pairs laid out chosen-first: document 2i is chosen, 2i+1 rejected
+    (the preference row processor of halo/data/pipeline/preferences.py). Prompt tokens are never scored."""
+    import torch
+
+    from halo_b200.trainers.preference import PreferenceBatch
+
+    row_len = data_args.packed_row_length
+    pairs = []
+    if data_args.dataset_format == "synthetic" or not data_args.dataset_path:
+        rng = np.random.default_rng(data_args.shuffle_seed + 7919 * dp_rank)
+        v = data_args.synthetic_vocab or vocab_size
+        for _ in range(256):
+            p = rng.integers(0, v, size=int(rng.integers(8, 64)))
+            c = rng.integers(0, v, size=int(rng.integers(8, 128)))
+            r = rng.integers(0, v, size=int(rng.integers(8, 128)))
+            pairs.append((p, c, r))
+    else:
+        for rec in read_records(data_args.dataset_path):
+            tok = lambda s: np.asarray(tokenizer(s, add_special_tokens=False)["input_ids"], dtype=np.int64)  # noqa: E731
+            pairs.append((tok(rec["prompt"]), tok(rec["chosen"]), tok(rec["rejected"])))
+        pairs = pairs[dp_rank::dp_world]
+    rows, docs, masks, used = [], [], [], 0
+
+    def flush():
+        nonlocal docs, masks, used
+        if docs:
+            b = pack_documents(docs, row_len=row_len, label_masks=masks)
+            n_docs = len(b.cu_seqlens) - 1
+            desirable = torch.tensor([(i % 2 == 0) for i in range(n_docs)]) if kto else None
+            rows.append(PreferenceBatch(b.input_ids, b.position_ids, b.labels, b.cu_seqlens, b.n_scored, None, desirable))
+        docs, masks, used = [], [], 0
+
+    for p, c, r in pairs:
+        need = 2 * len(p) + len(c) + len(r)
+        if need > row_len:
+            continue
+        if used + need > row_len:
+            flush()
+        for tail in (c, r):
+            docs.append(np.concatenate([p, tail]))
+            masks.append(np.concatenate([np.zeros(len(p), bool), np.ones(len(tail), bool)]))
+        used += need
+    flush()
+    return rows

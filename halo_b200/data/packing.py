@@ -100,6 +100,11 @@ def sample_doc_lengths(total: int, rng: np.random.Generator, dist: str = "loguni
             n = int(rng.integers(lo, hi + 1))
         elif dist == "single":
             n = total
+        elif dist == "chat":
+            # the shape of chat-template SFT rows the reference benchmarks on: about 55 whole documents
+            # per 64k-token row, none longer than 4,579 tokens
+            # (agent-docs/optimization/throughput-benchmarks.md:85-87)
+            n = int(np.clip(rng.lognormal(6.90, 0.6), 64, 4579))
         else:
             raise ValueError(f"unknown length distribution {dist!r}")
         n = max(1, min(n, left))

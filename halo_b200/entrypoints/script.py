@@ -39,12 +39,12 @@ def parse_script_args(*extra_dataclasses, argv=None):
     return device, parsed
 
 
-def init_training_script(device, model_args, train_args, par_args):
+def init_training_script(device, model_args, train_args, par_args, world_size: int = 0, global_rank: int = -1):
     torch.manual_seed(train_args.seed)
     reason = None
     pc = None
     try:
-        pc = par_args.to_config(init_from_scratch=model_args.init_from_scratch)
+        pc = par_args.to_config(world_size=world_size, global_rank=global_rank, init_from_scratch=model_args.init_from_scratch)
     except ValueError as exc:
         reason = str(exc)
     reject_across_ranks(reason, what="parallelism configuration")
@@ -53,20 +53,21 @@ def init_training_script(device, model_args, train_args, par_args):
     return pc
 
 
-def build_runtime(pc, device):
-    """Process groups + transports for the layout (expert parallel over the whole job is the wired path)."""
+def build_runtime(pc, device, group=None):
+    """Process groups + transports for the layout (expert parallel over all trainer ranks is the wired
+    path). ``group``: the trainer subgroup when some ranks of the job serve rollouts instead."""
     if pc.world_size == 1 or not dist.is_initialized():
         return None
     from halo_b200.parallel.runtime import ParallelRuntime
 
+    group = group if group is not None else dist.group.WORLD
     if pc.ep_size == pc.world_size and device.type == "cuda":
-        return ParallelRuntime.for_expert_parallel(pc.world_size, device)
+        return ParallelRuntime.for_expert_parallel(pc.world_size, device, group=group)
     if pc.ep_size > 1:
         from halo_b200.parallel.expert_parallel import CollectiveTransport
 
-        return ParallelRuntime(device, dp_group=dist.group.WORLD, ep_group=dist.group.WORLD,
-                               transport=CollectiveTransport(dist.group.WORLD))
-    return ParallelRuntime(device, dp_group=dist.group.WORLD)
+        return ParallelRuntime(device, dp_group=group, ep_group=group, transport=CollectiveTransport(group))
+    return ParallelRuntime(device, dp_group=group)
 
 
 def load_policy_model(model_args, pc, device, runtime, gradient_checkpointing=True, max_tokens=0):
@@ -88,12 +89,24 @@ def load_policy_model(model_args, pc, device, runtime, gradient_checkpointing=Tr
                            gradient_checkpointing=gradient_checkpointing)
 
 
+def load_tokenizer(model_args):
+    if not model_args.model_name_or_path:
+        return None
+    try:
+        from transformers import AutoTokenizer
+
+        return AutoTokenizer.from_pretrained(model_args.model_name_or_path)
+    except Exception as exc:   # a checkpoint directory without tokenizer files: pre-tokenised data still works
+        log.warning("no tokenizer at %s (%s)", model_args.model_name_or_path, exc)
+        return None
+
+
 def run_trainer(trainer, train_args):
     result = trainer.train()
     final = os.path.join(train_args.output_dir, "final")
     from halo_b200.checkpoint.save import save_model
 
-    save_model(trainer.model, final)
+    save_model(trainer.model, final, group=trainer.parallel.dp_group if trainer.parallel is not None else None)
     return result
 
 

@@ -1,0 +1,95 @@
+"""GRPO entry point. Rollouts come from a JSONL file of scored generations (offline GRPO) or from the
+synthetic generator; the trained weights are pushed to a resident rollout copy after each step when
+``rollout_backend: resident_copy`` names rollout GPUs."""
+
+import json
+
+import numpy as np
+
+from halo_b200.configs.arguments import GRPOArguments
+from halo_b200.entrypoints.script import (build_runtime, init_training_script, load_policy_model, parse_script_args,
+                                          run_trainer, with_distributed_teardown)
+
+
+def rollouts_from_jsonl(path: str, group: int):
+    """Each line: {"prompt_ids": [...], "completion_ids": [...], "reward": x, "sampler_logps": [...]?}; lines of
+    one prompt are consecutive. Yields one round per ``group``-aligned block of 64 prompts."""
+    from halo_b200.trainers.grpo.trainer import Rollout
+
+    rows = [json.loads(l) for l in open(path) if l.strip()]
+    per_round = 64 * group
+
+    def source(round_index: int):
+        block = rows[round_index * per_round:(round_index + 1) * per_round]
+        if not block:
+            return None
+        return [Rollout(np.asarray(r["prompt_ids"]), np.asarray(r["completion_ids"]),
+                        None if r.get("sampler_logps") is None else np.asarray(r["sampler_logps"], dtype=np.float32),
+                        float(r["reward"])) for r in block]
+
+    return source
+
+
+def serve_rollout_copy(model_args, pc, device, roles, grpo_args):
+    """A rollout rank: hold a full (unsharded) serving copy and take every pushed update."""
+    import torch
+
+    from halo_b200.models.config import PRESETS, ModelConfig
+    from halo_b200.models.qwen3 import build_model
+    from halo_b200.weight_sync.group import build_manifest
+    from halo_b200.weight_sync.roles import make_sync, rollout_loop
+
+    cfg = PRESETS[model_args.model_preset]() if model_args.init_from_scratch else ModelConfig.load(model_args.model_name_or_path)
+    dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
+    serving = build_model(cfg, device=device, dtype=dtype, transport=None, gradient_checkpointing=False)
+    sync = make_sync(roles, device, build_manifest(serving), grpo_args.weight_sync_chunk_mb << 20)
+    n = rollout_loop(sync, roles, device, dict(serving.named_parameters()))
+    return {"updates": n}
+
+
+@with_distributed_teardown
+def main(argv=None):
+    from halo_b200.trainers.grpo.trainer import GRPOTrainer, synthetic_rollouts
+
+    device, (model_args, data_args, train_args, par_args, grpo_args) = parse_script_args(GRPOArguments, argv=argv)
+    roles = None
+    if grpo_args.rollout_gpus > 0:
+        from halo_b200.weight_sync.roles import split_roles
+
+        roles = split_roles(grpo_args.rollout_gpus)
+    pc = init_training_script(device, model_args, train_args, par_args,
+                              world_size=len(roles.trainer_ranks) if roles else 0,
+                              global_rank=(roles.rank if roles.is_trainer else 0) if roles else -1)
+    if roles is not None and not roles.is_trainer:
+        return serve_rollout_copy(model_args, pc, device, roles, grpo_args)
+    runtime = build_runtime(pc, device, group=roles.trainer_group if roles else None)
+    model = load_policy_model(model_args, pc, device, runtime, train_args.gradient_checkpointing,
+                              max_tokens=grpo_args.token_budget)
+    if data_args.dataset_path:
+        source = rollouts_from_jsonl(data_args.dataset_path, grpo_args.num_generations)
+    else:
+        vocab = data_args.synthetic_vocab or model.cfg.vocab_size
+
+        def source(i):
+            return synthetic_rollouts(i, n_prompts=8, n_generations=grpo_args.num_generations, vocab=vocab,
+                                      prompt_len=(8, min(64, grpo_args.max_prompt_length)),
+                                      response_len=(8, min(256, grpo_args.max_completion_length)),
+                                      seed=train_args.seed + pc.data_parallel_rank)
+    weight_sync = None
+    if roles is not None:
+        from halo_b200.weight_sync.group import full_manifest
+        from halo_b200.weight_sync.roles import ModelWeightPusher, make_sync
+
+        sync = make_sync(roles, device, full_manifest(model), grpo_args.weight_sync_chunk_mb << 20)
+        weight_sync = ModelWeightPusher(sync, roles, device, runtime.ep_group if runtime else None)
+    trainer = GRPOTrainer(model, train_args, source, grpo_args=grpo_args, weight_sync=weight_sync, device=device,
+                          parallel=runtime, parallelism_fingerprint=pc.fingerprint())
+    try:
+        return run_trainer(trainer, train_args)
+    finally:
+        if weight_sync is not None:
+            weight_sync.close()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,7 +1,7 @@
 """Supervised fine-tuning entry point:  torchrun -m halo_b200.entrypoints.training.sft config.yaml [--key=value]"""
 
 from halo_b200.configs.arguments import SFTArguments
-from halo_b200.entrypoints.script import (build_runtime, init_training_script, load_policy_model, parse_script_args,
+from halo_b200.entrypoints.script import (build_runtime, init_training_script, load_policy_model, load_tokenizer, parse_script_args,
                                           run_trainer, with_distributed_teardown)
 
 
@@ -16,14 +16,7 @@ def main(argv=None):
     runtime = build_runtime(pc, device)
     model = load_policy_model(model_args, pc, device, runtime, train_args.gradient_checkpointing,
                               max_tokens=data_args.packed_row_length * train_args.per_device_train_batch_size)
-    tokenizer = None
-    if model_args.model_name_or_path:
-        try:
-            from transformers import AutoTokenizer
-
-            tokenizer = AutoTokenizer.from_pretrained(model_args.model_name_or_path)
-        except Exception:
-            tokenizer = None
+    tokenizer = load_tokenizer(model_args)
     batches = build_sft_batches(data_args, tokenizer, pc.data_parallel_rank, pc.data_parallel_size, model.cfg.vocab_size)
     trainer = SFTTrainer(model, train_args, batches, device=device, parallel=runtime,
                          callbacks=[EfficiencyCallback(model.cfg, pc.world_size)],

@@ -148,7 +148,8 @@ class SparseMoE(nn.Module):
             idx, w = moe_ops.router_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
         if ctx.record_routing is not None:
             ctx.record_routing.append((logits, idx))
-        out = moe_ops.moe_experts(h, idx, w, self.experts_gate_up, self.experts_down, ctx.transport)
+        out = moe_ops.moe_experts(h, idx, w, self.experts_gate_up, self.experts_down, ctx.transport,
+                                  skip_output=getattr(ctx, "output_unused", False))
         if self.shared_expert is not None:
             sh = self.shared_expert(h)
             if self.shared_gate is not None:
@@ -187,6 +188,7 @@ class ForwardContext:
         self.transport = transport
         self.record_routing = record_routing
         self.replay_topk = replay_topk
+        self.output_unused = False   # set while a layer is re-run only to rebuild its graph
 
 
 class Qwen3Model(nn.Module):

@@ -28,8 +28,14 @@ class _Recompute(torch.autograd.Function):
     def backward(ctx, grad_out):
         (x,) = ctx.saved_tensors
         xin = x.detach().requires_grad_(True)
-        with torch.enable_grad():
-            out = ctx.layer(xin, ctx.fwd_ctx)
+        # the value of this second pass is never read (only its graph is): the layer's last op may skip
+        # producing it
+        ctx.fwd_ctx.output_unused = True
+        try:
+            with torch.enable_grad():
+                out = ctx.layer(xin, ctx.fwd_ctx)
+        finally:
+            ctx.fwd_ctx.output_unused = False
         torch.autograd.backward(out, grad_out)
         return None, None, xin.grad
 

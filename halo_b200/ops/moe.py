@@ -265,7 +265,7 @@ def moe_ffn_reference(x, topk_idx, topk_w, w_gate_up, w_down, expert_offset: int
 # ---------------------------------------------------------------------------------------------
 class _MoEExperts(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, topk_idx, topk_w, w_gate_up, w_down, transport, state_out, grad_mode):
+    def forward(ctx, x, topk_idx, topk_w, w_gate_up, w_down, transport, state_out, grad_mode, skip_output=False):
         T, H = x.shape
         E_local, F2, _ = w_gate_up.shape
         F = F2 // 2
@@ -289,17 +289,22 @@ class _MoEExperts(torch.autograd.Function):
         transport.barrier()
         need_grad = grad_mode and any(ctx.needs_input_grad)
         act, pre = grouped_swiglu_ffn_fwd(state, recv_x, w_gate_up, w_down, save_pre=need_grad)
-        grouped_down_fwd(state, act, w_down, y_rows)
-        transport.barrier()
-        out = torch.empty_like(x)
         w32 = topk_w.float().contiguous()
-        _lib.check(L.halo_combine_rows(py, _lib.c_int(transport.n_ranks), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
-                                       _lib.ptr(w32), _lib.c_void_p(0), _lib.ptr(out), _lib.c_ll(T), _lib.c_int(k),
-                                       _lib.c_int(H), _lib.c_int(E_local), _lib.c_int(cap), s), "halo_combine_rows")
+        if skip_output and need_grad:
+            # a recomputation whose value nobody reads: the backward needs only the dispatched rows and the
+            # pre-activations, so the down projection and the pull back to the tokens are left out
+            out = torch.empty_like(x)
+        else:
+            grouped_down_fwd(state, act, w_down, y_rows)
+            transport.barrier()
+            out = torch.empty_like(x)
+            _lib.check(L.halo_combine_rows(py, _lib.c_int(transport.n_ranks), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
+                                           _lib.ptr(w32), _lib.c_void_p(0), _lib.ptr(out), _lib.c_ll(T), _lib.c_int(k),
+                                           _lib.c_int(H), _lib.c_int(E_local), _lib.c_int(cap), s), "halo_combine_rows")
         if need_grad:
             if transport.transient_buffers:
-                recv_x, y_rows = recv_x.clone(), y_rows.clone()
-            ctx.save_for_backward(recv_x, y_rows, act, pre, w32, w_gate_up, w_down)
+                recv_x = recv_x.clone()
+            ctx.save_for_backward(recv_x, pre, w32, w_gate_up, w_down)
             ctx.state = state
             ctx.transport = transport
         if state_out is not None:
@@ -308,7 +313,7 @@ class _MoEExperts(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout):
-        recv_x, y_rows, act, pre, w32, w_gate_up, w_down = ctx.saved_tensors
+        recv_x, pre, w32, w_gate_up, w_down = ctx.saved_tensors
         state, transport = ctx.state, ctx.transport
         T, k = state.n_tokens, state.top_k
         E_local, F2, H = w_gate_up.shape
@@ -318,10 +323,10 @@ class _MoEExperts(torch.autograd.Function):
         L = _lib.lib()
         s = _lib.stream_ptr(dev)
         dout = dout.contiguous()
-        # 1. push dout rows and routing weights to the experts
+        # 1. push dout rows (unscaled) and routing weights to the experts
         dy = transport.buffer("recv_dy", cap, H, torch.bfloat16, dev)
         row_w = transport.buffer("row_w", cap, 1, torch.float32, dev)
-        row_w.zero_()  # pad rows must scale to a finite value
+        row_w.zero_()  # pad rows scale to zero
         pdy, pw = transport.peer_table(dy), transport.peer_table(row_w)
         _lib.check(L.halo_zero_pad_rows(_lib.ptr(dy), _lib.ptr(state.seg_start), _lib.ptr(state.seg_rows),
                                         _lib.c_int(state.n_local), _lib.c_int(H), _lib.c_int(cap), s), "halo_zero_pad_rows")
@@ -330,21 +335,22 @@ class _MoEExperts(torch.autograd.Function):
                                         _lib.c_int(H), _lib.c_int(E_local), _lib.c_int(cap),
                                         _lib.ptr(_lib.status_word(dev)), s), "halo_dispatch_rows")
         transport.barrier()
-        # 2. expert side: routing-weight gradient per row, then dy = w * dout in place
-        dwrow = transport.buffer("dwrow", cap, 1, torch.float32, dev)
-        _lib.check(L.halo_scale_rows_dot(_lib.ptr(dy), _lib.ptr(y_rows), _lib.ptr(row_w), _lib.ptr(dwrow),
-                                         _lib.ptr(state.total_rows), _lib.c_int(H), _lib.c_int(cap), s), "halo_scale_rows_dot")
-        # 3. down projection: dact = dy W_down ; dW_down[e] = dy_e^T act_e
+        # 2. unscaled activation gradient: dact_u = dout_rows W_down
         dact = torch.empty((cap, F), dtype=torch.bfloat16, device=dev)
         lst = _tile_list(state, "m", n_cols=F, k_dim=H, b_mn_stride=0, b_k_stride=H, swiglu_f=0)
         _gemm_list(dy, w_down.reshape(E_local * H, F), dact, lst, 0, 1, EPI_STORE_BF16)
+        # 3. SwiGLU backward with the routing weight folded in: dpre = w * swiglu'(pre) dact_u, act_w = w * act,
+        #    dwrow = <dact_u, act> (= <dout, expert output>, without ever forming the expert output)
+        dwrow = transport.buffer("dwrow", cap, 1, torch.float32, dev)
+        dpre = torch.empty((cap, F2), dtype=torch.bfloat16, device=dev)
+        act_w = torch.empty((cap, F), dtype=torch.bfloat16, device=dev)
+        _lib.check(L.halo_swiglu_bwd_weighted(_lib.ptr(pre), _lib.ptr(dact), _lib.ptr(row_w), _lib.ptr(dpre),
+                                              _lib.ptr(act_w), _lib.ptr(dwrow), _lib.ptr(state.total_rows),
+                                              _lib.c_int(F), _lib.c_int(cap), s), "halo_swiglu_bwd_weighted")
+        # 4. dW_down[e] = dout_e^T (w * act)_e
         dw_down = torch.empty_like(w_down)
         lst = _tile_list(state, "k", m_dim=H, n_dim=F)
-        _gemm_list(dy, act, dw_down.reshape(E_local * H, F), lst, 1, 1, EPI_STORE_BF16)
-        # 4. SwiGLU backward
-        dpre = torch.empty((cap, F2), dtype=torch.bfloat16, device=dev)
-        _lib.check(L.halo_swiglu_bwd(_lib.ptr(pre), _lib.ptr(dact), _lib.ptr(dpre), _lib.c_ll(cap), _lib.c_int(F), s),
-                   "halo_swiglu_bwd")
+        _gemm_list(dy, act_w, dw_down.reshape(E_local * H, F), lst, 1, 1, EPI_STORE_BF16)
         # 5. gate/up projection: dx_rows = dpre W_gate_up ; dW_gate_up[e] = dpre_e^T x_e
         dx_rows = transport.buffer("dx_rows", cap, H, torch.bfloat16, dev)
         lst = _tile_list(state, "m", n_cols=H, k_dim=F2, b_mn_stride=0, b_k_stride=F2, swiglu_f=0)
@@ -363,14 +369,17 @@ class _MoEExperts(torch.autograd.Function):
         _lib.check(L.halo_gather_slot_values(pdw, _lib.c_int(transport.n_ranks), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
                                              _lib.ptr(dw), _lib.c_ll(T * k), _lib.c_int(E_local), _lib.c_int(cap), s),
                    "halo_gather_slot_values")
-        return dx, None, dw, dw_gate_up, dw_down, None, None, None
+        return dx, None, dw, dw_gate_up, dw_down, None, None, None, None
 
 
-def moe_experts(x, topk_idx, topk_w, w_gate_up, w_down, transport=None, state_out: list | None = None):
+def moe_experts(x, topk_idx, topk_w, w_gate_up, w_down, transport=None, state_out: list | None = None,
+                skip_output: bool = False):
     """Apply the routed experts.
 
     x: [T, H] bf16; topk_idx: int32 [T, k] global expert ids; topk_w: [T, k] routing weights;
     w_gate_up: [E_local, 2F, H] (gate rows then up rows per expert); w_down: [E_local, H, F].
+    ``skip_output``: the caller will not read the result (a recomputation that only rebuilds what the
+    backward needs); the returned tensor is then uninitialised.
     """
     if transport is None:
         transport = LocalTransport()
@@ -380,4 +389,4 @@ def moe_experts(x, topk_idx, topk_w, w_gate_up, w_down, transport=None, state_ou
             return transport.reference_ffn(x, topk_idx, topk_w, w_gate_up, w_down)
         return moe_ffn_reference(x, topk_idx, topk_w, w_gate_up, w_down, offset)
     return _MoEExperts.apply(x.contiguous(), topk_idx, topk_w, w_gate_up, w_down, transport, state_out,
-                             torch.is_grad_enabled())
+                             torch.is_grad_enabled(), skip_output)

@@ -79,12 +79,15 @@ class ParallelismConfig:
 
     # ---- resolution ------------------------------------------------------------------------
     def _resolve_world(self) -> None:
+        explicit_world = self.world_size > 0     # a subset of the job (the trainer ranks of a split job)
         if self.world_size <= 0:
             self.world_size = int(os.environ.get("WORLD_SIZE", "1"))
         if self.global_rank < 0:
             self.global_rank = int(os.environ.get("RANK", "0"))
         if self.gpus_per_node <= 0:
             self.gpus_per_node = int(os.environ.get("LOCAL_WORLD_SIZE", "0")) or self.world_size
+            if explicit_world and self.world_size < self.gpus_per_node:
+                self.gpus_per_node = self.world_size
         if self.nvlink_domain_size <= 0:
             self.nvlink_domain_size = int(os.environ.get("NVLINK_DOMAIN_SIZE", "0") or 0) or self.gpus_per_node
         if not 0 <= self.global_rank < self.world_size:

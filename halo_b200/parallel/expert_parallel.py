@@ -19,44 +19,59 @@ import torch.distributed as dist
 from halo_b200.ops.moe import moe_ffn_reference
 
 
+def _row_counts(n: int, group) -> list[int]:
+    world = dist.get_world_size(group)
+    t = torch.tensor([n], dtype=torch.int64)
+    out = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+    dist.all_gather(out, t, group=group)
+    return [int(o.item()) for o in out]
+
+
+def _pad_rows(x, rows: int):
+    if x.shape[0] == rows:
+        return x.contiguous()
+    pad = torch.zeros((rows - x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    return torch.cat([x, pad], dim=0)
+
+
 class _GatherRows(torch.autograd.Function):
-    """cat over ranks of equally-shaped tensors; backward: sum over ranks of the matching slice."""
+    """cat over ranks (row counts may differ per rank); backward: sum over ranks of the matching slice."""
 
     @staticmethod
-    def forward(ctx, x, group):
-        world = dist.get_world_size(group)
-        parts = [torch.empty_like(x) for _ in range(world)]
-        dist.all_gather(parts, x.contiguous(), group=group)
-        ctx.group, ctx.rows = group, x.shape[0]
-        return torch.cat(parts, dim=0)
+    def forward(ctx, x, group, counts):
+        world, widest = dist.get_world_size(group), max(counts)
+        parts = [torch.empty((widest,) + tuple(x.shape[1:]), dtype=x.dtype) for _ in range(world)]
+        dist.all_gather(parts, _pad_rows(x, widest), group=group)
+        ctx.group, ctx.counts = group, counts
+        return torch.cat([p[:c] for p, c in zip(parts, counts)], dim=0)
 
     @staticmethod
     def backward(ctx, g):
         g = g.contiguous().clone()
         dist.all_reduce(g, group=ctx.group)
         r = dist.get_rank(ctx.group)
-        return g[r * ctx.rows:(r + 1) * ctx.rows], None
+        lo = sum(ctx.counts[:r])
+        return g[lo:lo + ctx.counts[r]], None, None
 
 
 class _ScatterSumRows(torch.autograd.Function):
-    """out_r = sum over ranks of partial[r*rows:(r+1)*rows]; backward: gather of the gradient."""
+    """out_r = sum over ranks of this rank's row block of ``partial``; backward: gather of the gradient."""
 
     @staticmethod
-    def forward(ctx, partial, group):
-        world = dist.get_world_size(group)
-        ctx.group = group
+    def forward(ctx, partial, group, counts):
+        ctx.group, ctx.counts = group, counts
         total = partial.contiguous().clone()
         dist.all_reduce(total, group=group)
-        rows = partial.shape[0] // world
         r = dist.get_rank(group)
-        return total[r * rows:(r + 1) * rows].clone()
+        lo = sum(counts[:r])
+        return total[lo:lo + counts[r]].clone()
 
     @staticmethod
     def backward(ctx, g):
-        world = dist.get_world_size(ctx.group)
-        parts = [torch.empty_like(g) for _ in range(world)]
-        dist.all_gather(parts, g.contiguous(), group=ctx.group)
-        return torch.cat(parts, dim=0), None
+        world, widest = dist.get_world_size(ctx.group), max(ctx.counts)
+        parts = [torch.empty((widest,) + tuple(g.shape[1:]), dtype=g.dtype) for _ in range(world)]
+        dist.all_gather(parts, _pad_rows(g, widest), group=ctx.group)
+        return torch.cat([p[:c] for p, c in zip(parts, ctx.counts)], dim=0), None, None
 
 
 class CollectiveTransport:
@@ -70,13 +85,12 @@ class CollectiveTransport:
 
     def reference_ffn(self, x, topk_idx, topk_w, w_gate_up, w_down):
         e_local = w_gate_up.shape[0]
-        xs = _GatherRows.apply(x, self.group)
-        ws = _GatherRows.apply(topk_w.to(torch.float32), self.group)
-        idx_parts = [torch.empty_like(topk_idx) for _ in range(self.n_ranks)]
-        dist.all_gather(idx_parts, topk_idx.contiguous(), group=self.group)
-        idx = torch.cat(idx_parts, dim=0)
+        counts = _row_counts(x.shape[0], self.group)
+        xs = _GatherRows.apply(x, self.group, counts)
+        ws = _GatherRows.apply(topk_w.to(torch.float32), self.group, counts)
+        idx = _GatherRows.apply(topk_idx, self.group, counts)
         partial = moe_ffn_reference(xs, idx, ws, w_gate_up, w_down, expert_offset=self.rank * e_local)
-        return _ScatterSumRows.apply(partial, self.group)
+        return _ScatterSumRows.apply(partial, self.group, counts)
 
     # the CUDA kernels never see this transport
     def capacity(self, n_slots, n_local):  # pragma: no cover

@@ -123,9 +123,10 @@ class ParallelRuntime:
         return experts
 
     @classmethod
-    def for_expert_parallel(cls, world: int, device) -> "ParallelRuntime":
-        """EP over every rank of the job; the non-expert parameters are replicated over the same ranks."""
-        group = dist.group.WORLD
+    def for_expert_parallel(cls, world: int, device, group=None) -> "ParallelRuntime":
+        """EP over every rank of ``group`` (default: the job); the non-expert parameters are replicated
+        over the same ranks."""
+        group = group if group is not None else dist.group.WORLD
         transport = SymmetricTransport(group, device)
         return cls(device, dp_group=group, ep_group=group, expert_replica_group=None, transport=transport)
 

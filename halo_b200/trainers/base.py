@@ -89,6 +89,10 @@ class Trainer:
         self._pending_skip = None
         self._consecutive_skips = 0
         self.rank = int(os.environ.get("RANK", "0"))
+        if parallel is not None and parallel.dp_group is not None:
+            import torch.distributed as dist
+
+            self.rank = dist.get_rank(parallel.dp_group)   # rank among the trainers of the job
 
     # ---- hooks for subclasses --------------------------------------------------------------
     def compute_loss(self, model, batch: PackedBatch, normalizer):
@@ -106,6 +110,10 @@ class Trainer:
 
     @property
     def world_size(self) -> int:
+        if self.parallel is not None and self.parallel.dp_group is not None:
+            import torch.distributed as dist
+
+            return dist.get_world_size(self.parallel.dp_group)
         return int(os.environ.get("WORLD_SIZE", "1"))
 
     @property
@@ -196,7 +204,8 @@ class Trainer:
     def save_checkpoint(self) -> str:
         d = self.checkpoint_dir()
         os.makedirs(d, exist_ok=True)
-        save_model(self.model, d, sharded_experts=self.args.save_sharded_ep, save_dtype=None)  # exact resume: keep the dtype
+        save_model(self.model, d, sharded_experts=self.args.save_sharded_ep, save_dtype=None,
+                   group=self.parallel.dp_group if self.parallel is not None else None)  # exact resume: keep the dtype
         opt_io.save_optimizer_shard(self.optimizer, d, self.rank, self.fingerprint, write_meta=self.is_main)
         atomic_torch_save({"cpu": torch.get_rng_state(),
                            "cuda": torch.cuda.get_rng_state(self.device) if self.device.type == "cuda" else None},
@@ -204,7 +213,7 @@ class Trainer:
         if self.parallel is not None:
             import torch.distributed as dist
 
-            dist.barrier()
+            dist.barrier(group=self.parallel.dp_group)
         if self.is_main:
             atomic_torch_save(self.lr_scheduler.state_dict(), os.path.join(d, "scheduler.pt"))
             mark_complete(d, {"global_step": self.global_step, "tokens_seen": self.tokens_seen,

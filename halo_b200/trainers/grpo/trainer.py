@@ -89,7 +89,7 @@ class GRPOTrainer(Trainer):
         import torch.distributed as dist
 
         t = torch.tensor([n], dtype=torch.int64, device=self.device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.parallel.dp_group)
         return int(t.item())
 
     def plan_round(self, rollouts: list[Rollout]) -> list[GRPOBatch]:

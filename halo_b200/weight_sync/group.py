@@ -32,9 +32,9 @@ def full_named_tensors(model, ep_group=None):
     for name, p in model.named_parameters():
         t = p.detach()
         if getattr(p, "is_expert", False) and n_ep > 1:
-            out = torch.empty((n_ep,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+            out = torch.empty((n_ep * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
             dist.all_gather_into_tensor(out, t.contiguous(), group=ep_group)
-            t = out.reshape((n_ep * t.shape[0],) + tuple(t.shape[1:]))
+            t = out
         yield name, t
 
 
@@ -107,3 +107,27 @@ class BroadcastSync:
 
 def build_manifest(model) -> list:
     return manifest_of((n, p) for n, p in model.named_parameters())
+
+
+def full_manifest(model, n_ep: int | None = None) -> list:
+    """Manifest of the gathered (unsharded) tensors of an expert-parallel model, without gathering them."""
+    tr = getattr(model, "transport", None)
+    n_ep = n_ep if n_ep is not None else (getattr(tr, "n_ranks", 1) if tr is not None else 1)
+
+    class _Shape:
+        def __init__(self, shape, dtype):
+            self.shape, self.dtype = torch.Size(shape), dtype
+
+        def numel(self):
+            return self.shape.numel()
+
+        def element_size(self):
+            return torch.empty((), dtype=self.dtype).element_size()
+
+    out = []
+    for n, p in model.named_parameters():
+        shape = tuple(p.shape)
+        if getattr(p, "is_expert", False) and n_ep > 1:
+            shape = (n_ep * shape[0],) + shape[1:]
+        out.append((n, _Shape(shape, p.dtype)))
+    return manifest_of(out)

@@ -38,3 +38,45 @@ def _worker(rank, world):
 
 def test_broadcast_sync_over_gloo():
     run_gloo_ranks(_worker, 2)
+
+
+def _split_worker(rank, world):
+    """Two expert-parallel trainer ranks and one rollout rank: after a push the rollout rank's unsharded
+    serving copy equals the trainers' gathered weights, tensor for tensor."""
+    import torch.distributed as dist
+
+    from halo_b200.models.config import PRESETS
+    from halo_b200.models.qwen3 import build_model
+    from halo_b200.parallel.expert_parallel import CollectiveTransport
+    from halo_b200.weight_sync.group import build_manifest, full_manifest, full_named_tensors
+    from halo_b200.weight_sync.roles import ModelWeightPusher, make_sync, rollout_loop, split_roles
+
+    roles = split_roles(1)
+    cfg = PRESETS["tiny-moe"]()
+    if roles.is_trainer:
+        torch.manual_seed(1)
+        model = build_model(cfg, device="cpu", dtype=torch.float32, transport=CollectiveTransport(roles.trainer_group))
+        with torch.no_grad():
+            for p in model.parameters():
+                p.add_(0.25)                      # the trainers moved away from the initial weights
+        sync = make_sync(roles, "cpu", full_manifest(model), chunk_bytes=1 << 16)
+        pusher = ModelWeightPusher(sync, roles, "cpu", roles.trainer_group)
+        pusher.push(model)
+        want = dict(full_named_tensors(model, roles.trainer_group))
+        pusher.close()
+        if rank == roles.src_rank:
+            dist.send(torch.stack([t.double().sum() for t in want.values()]), dst=roles.rollout_ranks[0])
+    else:
+        torch.manual_seed(1)
+        serving = build_model(cfg, device="cpu", dtype=torch.float32, transport=None)
+        params = dict(serving.named_parameters())
+        sync = make_sync(roles, "cpu", build_manifest(serving), chunk_bytes=1 << 16)
+        assert rollout_loop(sync, roles, "cpu", params) == 1
+        sums = torch.zeros(len(params), dtype=torch.float64)
+        dist.recv(sums, src=roles.src_rank)
+        got = torch.stack([p.detach().double().sum() for p in params.values()])
+        assert torch.allclose(got, sums, rtol=0, atol=1e-9)
+
+
+def test_split_roles_push_reaches_the_rollout_copy():
+    run_gloo_ranks(_split_worker, 3)
