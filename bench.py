@@ -271,7 +271,7 @@ def main() -> int:
     e2e = tokens / (ms_e2e / 1e3)
     peak_gib = torch.cuda.max_memory_allocated(dev) / 2**30
     if rank == 0:
-        par = f"ep{world}" + (f"+dp{world}" if world > 1 else "") + ("+fused_zero" if parallel is not None and parallel.fused_optimizer is not None else "") + ("+host_optimizer_state" if opt_state == "host" else "")
+        par = f"ep{world}" + (f"+dp{world}" if world > 1 else "") + ("+fused_zero" if parallel is not None and parallel.fused_optimizer is not None else "") + ("+host_optimizer_state" if getattr(opt, "state_bytes_on_host", lambda: 0)() > 0 else "")
         line = {
             "metric": "train tokens/s, 30B-A3B MoE, packed 64k rows (whole job)",
             "value": round(value, 1),

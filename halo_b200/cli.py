@@ -22,6 +22,10 @@ METHODS = {
 TOOLS = {
     "merge-ep-shards": "halo_b200.checkpoint.tools.merge_ep_shards",
     "convert-dtype": "halo_b200.checkpoint.tools.convert_dtype",
+    "merge-models": "halo_b200.checkpoint.tools.merge_models",
+    "relayout-experts": "halo_b200.checkpoint.tools.relayout_experts",
+    "patch-vocab": "halo_b200.checkpoint.tools.patch_vocab",
+    "kernel-bench": "benchmarks.kernels",
     "bench": "bench",
 }
 

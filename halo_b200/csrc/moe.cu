@@ -38,13 +38,15 @@ __device__ __forceinline__ float wmax(float v) {
 template <int EPL>  // experts per lane
 __global__ void __launch_bounds__(256)
 router_topk_fwd_kernel(const float* __restrict__ logits, int* __restrict__ topk_idx,
-                       float* __restrict__ topk_w, float* __restrict__ probs_out, long long T, int k,
-                       int renorm) {
+                       float* __restrict__ topk_w, float* __restrict__ probs_out,
+                       const float* __restrict__ sel_bias, long long T, int k, int renorm) {
     const int lane = threadIdx.x & 31;
     const long long t = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (t >= T) return;
     constexpr int E = EPL * 32;
-    float p[EPL];
+    float p[EPL], b[EPL];   // b: per-expert selection bias (balancing); it ranks experts, it never weighs them
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) b[i] = sel_bias ? sel_bias[i * 32 + lane] : 0.f;
     float m = -INFINITY;
 #pragma unroll
     for (int i = 0; i < EPL; ++i) {
@@ -70,12 +72,13 @@ router_topk_fwd_kernel(const float* __restrict__ logits, int* __restrict__ topk_
     int my_idx = 0;
     unsigned taken = 0;
     for (int r = 0; r < k; ++r) {
-        float best = -1.f;
+        float best = -INFINITY, best_p = 0.f;
         int best_e = E;
 #pragma unroll
         for (int i = 0; i < EPL; ++i) {
-            if (!((taken >> i) & 1u) && p[i] > best) {
-                best = p[i];
+            if (!((taken >> i) & 1u) && p[i] + b[i] > best) {
+                best = p[i] + b[i];
+                best_p = p[i];
                 best_e = i * 32 + lane;
             }
         }
@@ -83,18 +86,20 @@ router_topk_fwd_kernel(const float* __restrict__ logits, int* __restrict__ topk_
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const float op = __shfl_xor_sync(0xffffffffu, best_p, o);
             const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
             if (ob > best || (ob == best && oe < best_e)) {
                 best = ob;
+                best_p = op;
                 best_e = oe;
             }
         }
         if ((best_e & 31) == lane) taken |= 1u << (best_e >> 5);
         if (lane == r) {
-            my_w = best;
+            my_w = best_p;
             my_idx = best_e;
         }
-        sel_sum += best;
+        sel_sum += best_p;
     }
     if (lane < k) {
         topk_idx[t * k + lane] = my_idx;
@@ -488,13 +493,13 @@ extern "C" {
 
 #define HALO_LAUNCH_CHECK() (cudaGetLastError() == cudaSuccess ? 0 : -11)
 
-int halo_router_topk_fwd(const float* logits, int* idx, float* w, float* probs, long long T, int E,
-                         int k, int renorm, void* stream) {
+int halo_router_topk_fwd(const float* logits, int* idx, float* w, float* probs, const float* sel_bias,
+                         long long T, int E, int k, int renorm, void* stream) {
     if (E % 32 || E > 256 || k > 16 || k > E) return -1;
     dim3 grid((unsigned)((T + 7) / 8));
     cudaStream_t s = (cudaStream_t)stream;
     switch (E / 32) {
-#define RT(V) case V: router_topk_fwd_kernel<V><<<grid, 256, 0, s>>>(logits, idx, w, probs, T, k, renorm); break;
+#define RT(V) case V: router_topk_fwd_kernel<V><<<grid, 256, 0, s>>>(logits, idx, w, probs, sel_bias, T, k, renorm); break;
         RT(1) RT(2) RT(3) RT(4) RT(5) RT(6) RT(7) RT(8)
 #undef RT
         default: return -2;

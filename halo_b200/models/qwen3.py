@@ -132,6 +132,10 @@ class SparseMoE(nn.Module):
         else:
             self.shared_expert = None
             self.shared_gate = None
+        # auxiliary-loss-free balancing: a per-expert bias that only ranks experts (never a parameter,
+        # saved as a sidecar by the balancing callback)
+        self.register_buffer("selection_bias", None, persistent=False)
+        self.load_counter = None      # (ExpertLoadCounter, layer index) when load metrics are on
         self.last_routing = None
 
     def forward(self, h, ctx):
@@ -145,7 +149,10 @@ class SparseMoE(nn.Module):
             if cfg.norm_topk_prob:
                 w = w / w.sum(-1, keepdim=True)
         else:
-            idx, w = moe_ops.router_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
+            idx, w = moe_ops.router_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob, self.selection_bias)
+        if self.load_counter is not None and not getattr(ctx, "output_unused", False):
+            counter, layer_index = self.load_counter
+            counter.add(layer_index, idx)     # first pass only: a recomputation replays the same routing
         if ctx.record_routing is not None:
             ctx.record_routing.append((logits, idx))
         out = moe_ops.moe_experts(h, idx, w, self.experts_gate_up, self.experts_down, ctx.transport,

@@ -34,9 +34,14 @@ from .gemm import EPI_STORE_BF16, EPI_SWIGLU
 # ---------------------------------------------------------------------------------------------
 # router
 # ---------------------------------------------------------------------------------------------
-def router_topk_reference(logits: torch.Tensor, k: int, renorm: bool):
+def router_topk_reference(logits: torch.Tensor, k: int, renorm: bool, sel_bias: torch.Tensor | None = None):
     probs = torch.softmax(logits.float(), dim=-1)
-    w, idx = torch.topk(probs, k, dim=-1)
+    if sel_bias is None:
+        w, idx = torch.topk(probs, k, dim=-1)
+    else:
+        # the balancing bias ranks experts; the weights stay the unbiased probabilities
+        _, idx = torch.topk(probs + sel_bias.float(), k, dim=-1)
+        w = probs.gather(-1, idx)
     if renorm:
         w = w / w.sum(-1, keepdim=True)
     return idx.to(torch.int32), w
@@ -44,13 +49,13 @@ def router_topk_reference(logits: torch.Tensor, k: int, renorm: bool):
 
 class _RouterTopK(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, logits, k, renorm):
+    def forward(ctx, logits, k, renorm, sel_bias=None):
         T, E = logits.shape
         idx = torch.empty((T, k), dtype=torch.int32, device=logits.device)
         w = torch.empty((T, k), dtype=torch.float32, device=logits.device)
         rc = _lib.lib().halo_router_topk_fwd(
-            _lib.ptr(logits), _lib.ptr(idx), _lib.ptr(w), _lib.c_void_p(0), _lib.c_ll(T), _lib.c_int(E),
-            _lib.c_int(k), _lib.c_int(1 if renorm else 0), _lib.stream_ptr(logits.device),
+            _lib.ptr(logits), _lib.ptr(idx), _lib.ptr(w), _lib.c_void_p(0), _lib.ptr(sel_bias), _lib.c_ll(T),
+            _lib.c_int(E), _lib.c_int(k), _lib.c_int(1 if renorm else 0), _lib.stream_ptr(logits.device),
         )
         _lib.check(rc, "halo_router_topk_fwd")
         ctx.save_for_backward(logits, idx)
@@ -69,16 +74,19 @@ class _RouterTopK(torch.autograd.Function):
             _lib.c_int(E), _lib.c_int(k), _lib.c_int(1 if renorm else 0), _lib.stream_ptr(logits.device),
         )
         _lib.check(rc, "halo_router_topk_bwd")
-        return dl, None, None
+        return dl, None, None, None
 
 
-def router_topk(logits: torch.Tensor, k: int, renorm: bool = True):
-    """softmax over experts, top-k, optional renormalisation. logits: fp32 [T, E].
+def router_topk(logits: torch.Tensor, k: int, renorm: bool = True, sel_bias: torch.Tensor | None = None):
+    """softmax over experts, top-k, optional renormalisation. logits: fp32 [T, E]. ``sel_bias`` ([E],
+    no gradient) is added to the probabilities for the ranking only (auxiliary-loss-free balancing).
     Returns ``(idx int32 [T, k], weights fp32 [T, k])``."""
     E = logits.shape[-1]
     if not logits.is_cuda or E % 32 or E > 256 or k > 16:
-        return router_topk_reference(logits, k, renorm)
-    return _RouterTopK.apply(logits.float().contiguous(), k, renorm)
+        return router_topk_reference(logits, k, renorm, sel_bias)
+    if sel_bias is not None:
+        sel_bias = sel_bias.detach().float().contiguous()
+    return _RouterTopK.apply(logits.float().contiguous(), k, renorm, sel_bias)
 
 
 # ---------------------------------------------------------------------------------------------

@@ -83,3 +83,17 @@ def test_moe_empty_experts():
     out.float().sum().backward()
     assert torch.all(wgu.grad[4:] == 0) and torch.all(wd.grad[4:] == 0)
     assert torch.isfinite(wgu.grad).all() and torch.isfinite(wd.grad).all()
+
+
+@pytest.mark.gpu
+def test_router_topk_selection_bias_matches_reference():
+    torch.manual_seed(3)
+    logits = torch.randn(1000, 128, device="cuda")
+    bias = torch.randn(128, device="cuda") * 0.05
+    from halo_b200.ops.moe import router_topk, router_topk_reference
+
+    idx, w = router_topk(logits, 8, True, bias)
+    ridx, rw = router_topk_reference(logits, 8, True, bias)
+    assert torch.equal(idx.sort(-1).values, ridx.sort(-1).values)
+    assert torch.allclose(w.sum(-1), torch.ones_like(w.sum(-1)), atol=1e-5)
+    assert torch.allclose(w.sort(-1).values, rw.sort(-1).values, atol=1e-5)

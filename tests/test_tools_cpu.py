@@ -1,0 +1,102 @@
+"""Offline checkpoint tools, expert layout conversions, head transform, selection bias (CPU)."""
+
+import json
+import os
+
+import pytest
+import torch
+
+from halo_b200.checkpoint.load import CheckpointIndex, from_pretrained
+from halo_b200.checkpoint.save import save_model
+from halo_b200.checkpoint.tools import convert_dtype, merge_models, patch_vocab, relayout_experts
+from halo_b200.models import moe_families as mf
+from halo_b200.models.config import PRESETS
+from halo_b200.models.head_transform import HeadTransform, chunked_cross_entropy
+from halo_b200.models.qwen3 import build_model
+from halo_b200.ops.moe import router_topk_reference
+
+
+def _tiny(tmp_path, seed, name):
+    model = build_model(PRESETS["tiny-moe"](), device="cpu", dtype=torch.float32, seed=seed)
+    d = str(tmp_path / name)
+    save_model(model, d, save_dtype=None)
+    return model, d
+
+
+def test_layout_round_trips_every_kind():
+    E, F, H = 4, 6, 8
+    gu, dn = torch.randn(E, 2 * F, H), torch.randn(E, H, F)
+    for kind in mf.LAYOUT_KINDS:
+        back = mf.to_runtime_banks(kind, mf.from_runtime_banks(kind, gu, dn), E)
+        assert torch.equal(back[0], gu) and torch.equal(back[1], dn), kind
+
+
+def test_family_registry_refuses_unbuilt_decoders():
+    assert mf.require_runnable("qwen3_moe").layout == mf.SEPARATE_GLU
+    with pytest.raises(NotImplementedError, match="attention sinks"):
+        mf.require_runnable("gpt_oss")
+    with pytest.raises(KeyError):
+        mf.family_spec("no_such_family")
+    assert len(mf.families()) >= 18
+
+
+def test_convert_and_merge_tools(tmp_path):
+    a_model, a = _tiny(tmp_path, 0, "a")
+    b_model, b = _tiny(tmp_path, 1, "b")
+    out = str(tmp_path / "bf16")
+    assert convert_dtype.main([a, out, "--dtype", "bfloat16"]) == 0
+    idx = CheckpointIndex(out)
+    assert idx.get("model.norm.weight").dtype == torch.bfloat16
+    lin = str(tmp_path / "lin")
+    merge_models.main([a, b, "--out", lin, "--method", "linear", "--weights", "1", "3"])
+    name = "model.layers.0.self_attn.o_proj.weight"
+    want = 0.25 * CheckpointIndex(a).get(name) + 0.75 * CheckpointIndex(b).get(name)
+    assert torch.allclose(CheckpointIndex(lin).get(name), want, atol=1e-6)
+    sl = str(tmp_path / "slerp")
+    merge_models.main([a, b, "--out", sl, "--method", "slerp", "--t", "0.0"])
+    assert torch.allclose(CheckpointIndex(sl).get(name), CheckpointIndex(a).get(name), atol=1e-5)
+    ti = str(tmp_path / "ties")
+    merge_models.main([a, a, "--out", ti, "--method", "ties", "--base", b, "--density", "1.0"])
+    assert torch.allclose(CheckpointIndex(ti).get(name), CheckpointIndex(a).get(name), atol=1e-5)
+    merged = from_pretrained(lin, device="cpu", dtype=torch.float32)     # the merge is a loadable checkpoint
+    assert merged.cfg.num_experts == a_model.cfg.num_experts
+
+
+def test_relayout_and_vocab_patch(tmp_path):
+    model, a = _tiny(tmp_path, 0, "a")
+    fused = str(tmp_path / "fused")
+    relayout_experts.main([a, fused, "--from", "SEPARATE_GLU", "--to", "FUSED"])
+    assert "model.layers.0.mlp.experts.gate_up_proj" in CheckpointIndex(fused).weight_map
+    back = str(tmp_path / "back")
+    relayout_experts.main([fused, back, "--from", "FUSED", "--to", "SEPARATE_GLU"])
+    ia, ib = CheckpointIndex(a), CheckpointIndex(back)
+    assert sorted(ia.weight_map) == sorted(ib.weight_map)
+    for k in ia.weight_map:
+        assert torch.equal(ia.get(k), ib.get(k)), k
+    grown = str(tmp_path / "grown")
+    v = model.cfg.vocab_size
+    patch_vocab.main([a, grown, "--vocab-size", str(v + 16)])
+    e = CheckpointIndex(grown).get("model.embed_tokens.weight")
+    assert e.shape[0] == v + 16 and torch.allclose(e[-1], e[:v].mean(0), atol=1e-6)
+    assert json.load(open(os.path.join(grown, "config.json")))["vocab_size"] == v + 16
+
+
+def test_head_transform_matches_plain_cross_entropy_and_softcap_bounds_logits():
+    torch.manual_seed(0)
+    h, w, y = torch.randn(33, 16), torch.randn(50, 16), torch.randint(0, 50, (33,))
+    plain = torch.nn.functional.cross_entropy(h @ w.t(), y)
+    assert torch.allclose(chunked_cross_entropy(h, w, y, HeadTransform(), chunk_rows=8), plain, atol=1e-5)
+    t = HeadTransform(logit_scale=2.0, softcap=5.0, vocab_cut=40)
+    assert t.apply(h @ t.weight_view(w).t()).abs().max() <= 5.0 and not t.fusable
+
+
+def test_selection_bias_changes_ranking_not_weights():
+    torch.manual_seed(0)
+    logits = torch.randn(64, 32)
+    idx0, w0 = router_topk_reference(logits, 4, False)
+    bias = torch.zeros(32)
+    bias[7] = 10.0                                      # expert 7 is always selected now
+    idx1, w1 = router_topk_reference(logits, 4, False, bias)
+    assert bool((idx1 == 7).any(-1).all())
+    probs = torch.softmax(logits, -1)
+    assert torch.allclose(w1, probs.gather(-1, idx1.long()))      # weights are the unbiased probabilities
