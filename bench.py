@@ -50,6 +50,8 @@ def parse_args():
                     help="N > 1: 1 = fused reduce-scatter/AdamW/all-gather kernels for the replicated parameters, "
                          "0 = NCCL all-reduce + local optimizer (the baseline path)")
     ap.add_argument("--doc-dist", default="chat")
+    ap.add_argument("--recompute", default="auto", choices=["auto", "full"],
+                    help="auto: layers keep their attention-half activations where memory allows")
     ap.add_argument("--lr", type=float, default=1e-5)
     return ap.parse_args()
 
@@ -232,6 +234,18 @@ def main() -> int:
             dist.barrier()
         torch.cuda.synchronize()
 
+    light_layers = 0
+    if args.recompute == "auto":
+        # one untimed probe step under full recomputation measures the real peak; the memory that is left then
+        # buys the lighter policy (keep the attention half's activations) for as many layers as fit
+        from halo_b200.models.qwen3 import plan_recompute
+
+        out = engine.train_step(host_batches[0])
+        float(out.loss.item())
+        torch.cuda.synchronize()
+        total_mem = torch.cuda.get_device_properties(dev).total_memory
+        free = int(0.92 * total_mem) - torch.cuda.max_memory_allocated(dev)
+        light_layers = plan_recompute(model, args.seq_len, free, reserve_bytes=8 << 30)
     for i in range(args.warmup):
         out = engine.train_step(host_batches[i % n_batches])
         float(out.loss.item())
@@ -293,7 +307,9 @@ def main() -> int:
                 "top_k": cfg.num_experts_per_tok, "vocab": cfg.vocab_size,
                 "global_batch": world, "seq_len": args.seq_len, "parallelism": par,
                 "optimizer": "AdamWBF16 (bf16 weights and moments, stochastic rounding), max_grad_norm 1.0",
-                "gradient_checkpointing": "per decoder layer",
+                "gradient_checkpointing": (f"per decoder layer; {light_layers} of {len(model.layers)} layers re-run only their "
+                                           "feed-forward half (memory left after a probe step)") if light_layers
+                else "per decoder layer",
                 "doc_lengths": DOC_DIST_NOTE.get(args.doc_dist, args.doc_dist),
                 "l2": "activations and weights per step are far larger than the 126 MB L2 (no flush needed)",
                 "params_total": counts["total"], "peak_gib": round(peak_gib, 1),

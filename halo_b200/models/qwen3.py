@@ -177,6 +177,9 @@ class DecoderLayer(nn.Module):
         else:
             self.mlp = DenseMLP(H, cfg.intermediate_size, dtype, device)
         self.eps = cfg.rms_norm_eps
+        # "full": the whole layer is re-run in the backward pass; "mlp": the attention half keeps its
+        # activations (about 30 KB per token) and only the feed-forward half is re-run; "none": nothing is re-run
+        self.recompute_policy = "full"
 
     def forward(self, x, ctx):
         h = rms_norm(x, self.input_layernorm, self.eps)
@@ -184,6 +187,12 @@ class DecoderLayer(nn.Module):
         h2, x2 = add_rms_norm(a, x, self.post_attention_layernorm, self.eps)
         m = self.mlp(h2, ctx)
         return x2 + m
+
+    def attention_half(self, x, ctx):
+        return x + self.self_attn(rms_norm(x, self.input_layernorm, self.eps), ctx)
+
+    def mlp_half(self, x2, ctx):
+        return x2 + self.mlp(rms_norm(x2, self.post_attention_layernorm, self.eps), ctx)
 
 
 class ForwardContext:
@@ -236,11 +245,16 @@ class Qwen3Model(nn.Module):
         std = self.cfg.initializer_range
         from halo_b200.optim.adamw_bf16 import param_name_hash
 
+        first = self.layer_range[0]
         for name, p in self.named_parameters():
             if p.dim() == 1:
                 p.fill_(1.0)
                 continue
             dev = p.device
+            if first and name.startswith("layers."):
+                # a pipeline stage numbers its layers from 0: key the draw by the layer's global index
+                _, li, rest = name.split(".", 2)
+                name = f"layers.{int(li) + first}.{rest}"
             base = (seed * 1000003 + param_name_hash(name)) % (2**62)
             if getattr(p, "is_expert", False):
                 # one generator per (parameter, global expert): any sharding draws the same values
@@ -270,8 +284,11 @@ class Qwen3Model(nn.Module):
     def run_layers(self, x, ctx):
         for layer in self.layers:
             self._gate(layer.parameters())
-            if self.gradient_checkpointing and torch.is_grad_enabled():
+            policy = layer.recompute_policy if (self.gradient_checkpointing and torch.is_grad_enabled()) else "none"
+            if policy == "full":
                 x = recompute(layer, x, ctx)
+            elif policy == "mlp":
+                x = recompute(layer.mlp_half, layer.attention_half(x, ctx), ctx)
             else:
                 x = layer(x, ctx)
         return x
@@ -298,6 +315,31 @@ class Qwen3Model(nn.Module):
     def token_logprobs(self, input_ids, position_ids, cu_seqlens, labels, want_entropy=False, ctx=None):
         h = self.hidden_states(input_ids, position_ids, cu_seqlens, ctx)
         return linear_logprobs(h, self.head_weight(), labels.reshape(-1), want_entropy=want_entropy)
+
+
+def attention_half_bytes_per_token(cfg: ModelConfig, itemsize: int = 2) -> int:
+    """Activation bytes per token that a layer keeps under the "mlp" recompute policy: normed input, fused
+    QKV (before and after rotary + QK-norm), attention output, projected output, residual sum, softmax statistics."""
+    q = cfg.num_attention_heads * cfg.head_dim
+    return itemsize * (3 * cfg.hidden_size + 2 * cfg.qkv_dim + q) + 4 * cfg.num_attention_heads
+
+
+def plan_recompute(model, tokens_per_step: int, free_bytes: int, reserve_bytes: int = 8 << 30, group=None) -> int:
+    """Give as many layers as fit in ``free_bytes - reserve_bytes`` the lighter "mlp" policy (from the last layer
+    backwards: those activations live shortest). Every rank of ``group`` adopts the smallest count any rank can
+    afford, so all ranks run the same collectives. Returns the number of layers that were lightened.
+
+    The role of the reference's measured ``gradient_checkpointing_plan: auto``
+    (halo/models/gradient_checkpointing_plan.py)."""
+    per_layer = attention_half_bytes_per_token(model.cfg, next(model.parameters()).element_size()) * tokens_per_step
+    n = max(0, min(len(model.layers), int((free_bytes - reserve_bytes) // max(per_layer, 1))))
+    if group is not None or (torch.distributed.is_available() and torch.distributed.is_initialized()):
+        t = torch.tensor([n], dtype=torch.int64, device=next(model.parameters()).device)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MIN, group=group)
+        n = int(t.item())
+    for i, layer in enumerate(model.layers):
+        layer.recompute_policy = "mlp" if i >= len(model.layers) - n else "full"
+    return n
 
 
 def build_model(cfg: ModelConfig, device="cpu", dtype=None, transport=None, seed: int = 0,

@@ -113,3 +113,31 @@ def test_documents_do_not_attend_across_boundaries():
     other = (ha[:40] - hb[:40]).abs().max().item()
     assert same < 2e-2, same          # fp32 reduction-order noise only
     assert other > 20 * same, (same, other)  # negative control: different documents do differ
+
+
+def test_recompute_policies_give_the_same_gradients():
+    """full / mlp-half / no recomputation differ only in what is kept alive, never in the result."""
+    import dataclasses
+
+    from halo_b200.data.packing import synthetic_packed_batch
+    from halo_b200.models.config import PRESETS
+    from halo_b200.models.qwen3 import build_model, plan_recompute
+
+    cfg = dataclasses.replace(PRESETS["tiny-moe"](), num_hidden_layers=3)
+    b = synthetic_packed_batch(128, cfg.vocab_size, seed=0, lo=8, hi=64)
+    grads = {}
+    for policy in ("full", "mlp", "none"):
+        m = build_model(cfg, device="cpu", dtype=torch.float32, seed=2)
+        for layer in m.layers:
+            layer.recompute_policy = policy
+        loss = m(b.input_ids, b.position_ids, b.cu_seqlens, b.labels)
+        loss.backward()
+        grads[policy] = (loss.detach(), {n: p.grad.clone() for n, p in m.named_parameters()})
+    for policy in ("mlp", "none"):
+        assert torch.allclose(grads[policy][0], grads["full"][0], atol=1e-6)
+        for n, g in grads["full"][1].items():
+            assert torch.allclose(grads[policy][1][n], g, rtol=1e-5, atol=1e-7), (policy, n)
+    m = build_model(cfg, device="cpu", dtype=torch.float32, seed=2)
+    per_layer = 128 * 4 * (3 * cfg.hidden_size + 2 * cfg.qkv_dim + cfg.num_attention_heads * cfg.head_dim) + 128 * 4 * cfg.num_attention_heads
+    assert plan_recompute(m, 128, free_bytes=2 * per_layer + 10, reserve_bytes=0) == 2
+    assert [l.recompute_policy for l in m.layers] == ["full", "mlp", "mlp"]

@@ -1,0 +1,62 @@
+"""Pipeline parallelism on two gloo ranks: the 1F1B and GPipe schedules give the loss and the gradients of the
+unsplit model, micro-batch for micro-batch."""
+
+import pytest
+import torch
+
+from halo_b200.parallel.pipeline import partition_layers
+from tests.common.gloo import run_gloo_ranks
+
+
+def test_partition_balances_head_cost():
+    assert partition_layers(8, 2, head_weight=2.0) == [(0, 5), (5, 8)]
+    assert partition_layers(48, 4, head_weight=0.0) == [(0, 12), (12, 24), (24, 36), (36, 48)]
+    assert partition_layers(6, 3, split=[1, 3]) == [(0, 1), (1, 3), (3, 6)]
+    with pytest.raises(ValueError):
+        partition_layers(2, 3)
+    with pytest.raises(ValueError):
+        partition_layers(6, 3, split=[3, 3])
+    ranges = partition_layers(48, 8, head_weight=3.0)
+    assert ranges[0][0] == 0 and ranges[-1][1] == 48 and all(b > a for a, b in ranges)
+    assert ranges[-1][1] - ranges[-1][0] < ranges[0][1] - ranges[0][0]
+
+
+def _worker(rank, world, schedule):
+    import dataclasses
+
+    import torch.distributed as dist
+
+    from halo_b200.data.packing import synthetic_packed_batch
+    from halo_b200.models.config import PRESETS
+    from halo_b200.models.qwen3 import build_model
+    from halo_b200.parallel.pipeline import PipelineStage, broadcast_loss, build_stage_model, run_schedule
+
+    cfg = dataclasses.replace(PRESETS["tiny-moe"](), num_hidden_layers=4)
+    row = 96
+    micro = [synthetic_packed_batch(row, cfg.vocab_size, seed=i, lo=8, hi=48) for i in range(3)]
+    norm = float(sum(b.n_scored for b in micro))
+    stage_model = build_stage_model(cfg, rank, world, "cpu", dtype=torch.float32, seed=5, split=[2])
+    stage = PipelineStage(stage_model, dist.group.WORLD, row)
+    loss = broadcast_loss(stage, run_schedule(stage, micro, norm, schedule))
+
+    full = build_model(cfg, device="cpu", dtype=torch.float32, seed=5)
+    ref = sum(full(b.input_ids, b.position_ids, b.cu_seqlens, b.labels, norm) for b in micro)
+    ref.backward()
+    assert torch.allclose(loss, ref.detach(), rtol=1e-5, atol=1e-6), (float(loss), float(ref))
+    lo = stage_model.layer_range[0]
+    full_params = dict(full.named_parameters())
+    checked = 0
+    for name, p in stage_model.named_parameters():
+        if name.startswith("layers."):
+            _, li, rest = name.split(".", 2)
+            name = f"layers.{int(li) + lo}.{rest}"
+        q = full_params[name]
+        assert torch.equal(p.detach(), q.detach()), name              # same initial weights as the unsplit model
+        assert torch.allclose(p.grad, q.grad, rtol=1e-4, atol=1e-6), name
+        checked += 1
+    assert checked > 5
+
+
+@pytest.mark.parametrize("schedule", ["1f1b", "gpipe"])
+def test_pipeline_matches_unsplit_model(schedule):
+    run_gloo_ranks(_worker, 2, args=(schedule,), timeout=90.0)
