@@ -45,7 +45,7 @@ def matmul(
     a_t: bool = False,
     b_t: bool = True,
     out: torch.Tensor | None = None,
-    out_dtype: torch.dtype = torch.bfloat16,
+    out_dtype: torch.dtype | None = None,
     accumulate: bool = False,
     alpha: float = 1.0,
 ) -> torch.Tensor:
@@ -60,6 +60,10 @@ def matmul(
         raise ValueError(f"reduction sizes differ: {K} vs {Kb}")
     if out is not None:
         out_dtype = out.dtype
+    if out_dtype is None:
+        # the kernel rounds its fp32 accumulators to bf16; the PyTorch path keeps the operands' precision, so an
+        # fp32 model on the CPU really computes in fp32
+        out_dtype = torch.bfloat16 if a.is_cuda else a.dtype
     if not a.is_cuda:
         af = a.float().t() if a_t else a.float()
         bf = b.float().t() if b_t else b.float()

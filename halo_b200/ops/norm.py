@@ -20,7 +20,7 @@ def rms_norm_reference(x, weight, eps, residual=None):
     h = x if residual is None else (x + residual)
     hf = h.float()
     rstd = torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + eps)
-    y = weight * (hf * rstd).to(x.dtype)
+    y = weight * (hf * rstd).to(h.dtype)
     return (y, h) if residual is not None else y
 
 
