@@ -191,6 +191,37 @@ broadcast_bytes_kernel(const uint4* __restrict__ src, const __grid_constant__ Pe
     }
 }
 
+// dst[i] = src[i] where src may be another GPU's memory mapped into this process (16-byte vectors, four
+// loads in flight per thread to cover the NVLink round trip).
+__global__ void __launch_bounds__(256)
+peer_pull_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, long long nvec) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+        const uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], d = src[i + 3 * stride];
+        dst[i] = a; dst[i + stride] = b; dst[i + 2 * stride] = c; dst[i + 3 * stride] = d;
+    }
+    for (; i < nvec; i += stride) dst[i] = src[i];
+}
+
+// dst[i] += src[i] on bf16 pairs (fp32 add, one rounding); src may be a peer's memory.
+__global__ void __launch_bounds__(256)
+peer_pull_add_bf16_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, long long nvec) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        const uint4 s = src[i];
+        uint4 d = dst[i];
+        const __nv_bfloat162* sh = reinterpret_cast<const __nv_bfloat162*>(&s);
+        __nv_bfloat162* dh = reinterpret_cast<__nv_bfloat162*>(&d);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float2 a = __bfloat1622float2(sh[q]), b = __bfloat1622float2(dh[q]);
+            dh[q] = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+        }
+        dst[i] = d;
+    }
+}
+
 // out[i] = sum_r bufs_r[i]   (fp32, n small)
 __global__ void allreduce_small_kernel(const __grid_constant__ Peers bufs, int n_ranks, float* __restrict__ out, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -261,6 +292,21 @@ int halo_broadcast_bytes(const void* src, void* const* dsts, int n_dst, long lon
     if (blocks > 148 * 8) blocks = 148 * 8;
     broadcast_bytes_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const uint4*)src, d, n_dst,
                                                                              dst_offset / 16, nvec);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Copy (accumulate == 0) or bf16-add (accumulate != 0) n_bytes from src, which may be a peer's mapped memory.
+int halo_peer_pull(void* dst, const void* src, long long n_bytes, int accumulate, void* stream) {
+    if ((n_bytes % 16) || (reinterpret_cast<uintptr_t>(src) % 16) || (reinterpret_cast<uintptr_t>(dst) % 16)) return -1;
+    if (n_bytes == 0) return 0;
+    const long long nvec = n_bytes / 16;
+    long long blocks = (nvec + 1023) / 1024;
+    if (blocks > 148 * 4) blocks = 148 * 4;
+    if (blocks < 1) blocks = 1;
+    if (accumulate)
+        peer_pull_add_bf16_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((uint4*)dst, (const uint4*)src, nvec);
+    else
+        peer_pull_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((uint4*)dst, (const uint4*)src, nvec);
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -97,8 +97,21 @@ class Attention(nn.Module):
     def forward(self, h, ctx):
         cfg = self.cfg
         qkv = gemm.linear(h, self.qkv_proj)
-        o = attn_ops.rope_attention(qkv, self.q_norm, self.k_norm, ctx.rope, ctx.plan, cfg.num_attention_heads,
-                                    cfg.num_key_value_heads, cfg.rms_norm_eps, cfg.use_qk_norm)
+        if ctx.cp is not None:
+            # context parallel: this rank holds one chunk of the row; keys and values of straddling documents
+            # come from the lower ranks
+            from halo_b200.ops.rope import qk_norm_rope
+            from halo_b200.parallel.context_parallel import cp_attention
+
+            cp, layout = ctx.cp
+            q, k = qk_norm_rope(qkv, self.q_norm, self.k_norm, ctx.rope, cfg.num_attention_heads,
+                                cfg.num_key_value_heads, cfg.rms_norm_eps, cfg.use_qk_norm)
+            v = qkv[:, (cfg.num_attention_heads + cfg.num_key_value_heads) * cfg.head_dim:]
+            o = cp_attention(q, k, v, layout, ctx.plan, cp.group, cp.exchange, cfg.num_attention_heads,
+                             cfg.num_key_value_heads)
+        else:
+            o = attn_ops.rope_attention(qkv, self.q_norm, self.k_norm, ctx.rope, ctx.plan, cfg.num_attention_heads,
+                                        cfg.num_key_value_heads, cfg.rms_norm_eps, cfg.use_qk_norm)
         return gemm.linear(o, self.o_proj)
 
 
@@ -198,8 +211,9 @@ class DecoderLayer(nn.Module):
 class ForwardContext:
     """Per-batch state shared by all layers: attention plan, rotary table, expert transport."""
 
-    def __init__(self, plan, rope, transport, record_routing=None, replay_topk=None):
+    def __init__(self, plan, rope, transport, record_routing=None, replay_topk=None, cp=None):
         self.plan = plan
+        self.cp = cp                 # (ContextParallel, CPLayout) when the row is cut over a context-parallel group
         self.rope = rope
         self.transport = transport
         self.record_routing = record_routing
@@ -221,6 +235,7 @@ class Qwen3Model(nn.Module):
                 f"num_experts ({cfg.num_experts}) is not divisible by expert_parallel_size ({self.transport.n_ranks})")
         n_local = cfg.num_experts // self.transport.n_ranks if cfg.is_moe else 0
         self.gradient_checkpointing = gradient_checkpointing
+        self.context_parallel = None      # halo_b200.parallel.context_parallel.ContextParallel when cp > 1
         lo, hi = layer_range or (0, cfg.num_hidden_layers)
         self.layer_range = (lo, hi)
         H = cfg.hidden_size
@@ -268,9 +283,14 @@ class Qwen3Model(nn.Module):
 
     # ---- forward -----------------------------------------------------------------------------
     def make_context(self, position_ids, cu_seqlens, record_routing=None, replay_topk=None) -> ForwardContext:
+        """``cu_seqlens`` always describes the whole packed row; under context parallelism ``position_ids``
+        (like the token ids) are this rank's chunk of it."""
         dev = position_ids.device
-        plan = attn_ops.build_plan(cu_seqlens, device=dev)
         rope = rope_table(position_ids, self.cfg.head_dim, self.cfg.rope_theta)
+        if self.context_parallel is not None:
+            layout, plan = self.context_parallel.layout_and_plan(cu_seqlens)
+            return ForwardContext(plan, rope, self.transport, record_routing, replay_topk, (self.context_parallel, layout))
+        plan = attn_ops.build_plan(cu_seqlens, device=dev)
         return ForwardContext(plan, rope, self.transport, record_routing, replay_topk)
 
     def _gate(self, params):

@@ -55,8 +55,12 @@ class AttentionPlan:
         return len(self.cu_seqlens) - 1
 
 
-def build_plan(cu_seqlens, device: torch.device | str | None = None) -> AttentionPlan:
-    """``cu_seqlens``: increasing offsets ``[0, len0, len0+len1, ...]`` of the packed documents."""
+def build_plan(cu_seqlens, device: torch.device | str | None = None, q_lo: int = 0) -> AttentionPlan:
+    """``cu_seqlens``: increasing offsets ``[0, len0, len0+len1, ...]`` of the packed documents.
+
+    ``q_lo``: rows below it are keys only (the foreign prefix of a context-parallel chunk): no query tile is
+    listed for them, and the dK/dV lists start their query range at ``q_lo``. The caller keeps the query and
+    output-gradient rows below ``q_lo`` at zero, so the rows of a tile that straddles ``q_lo`` add nothing."""
     cu = np.asarray(cu_seqlens.cpu() if isinstance(cu_seqlens, torch.Tensor) else cu_seqlens, dtype=np.int64)
     if cu.ndim != 1 or len(cu) < 1 or cu[0] != 0 or np.any(np.diff(cu) < 0):
         raise ValueError("cu_seqlens must start at 0 and be non-decreasing")
@@ -72,14 +76,18 @@ def build_plan(cu_seqlens, device: torch.device | str | None = None) -> Attentio
         n = int(end - start)
         if n == 0:
             continue
+        if int(end) <= q_lo:
+            continue                      # a document that lies wholly in the prefix has no local queries
         for i in range((n + 127) // 128):
             q0 = int(start) + 128 * i
-            fwd.append((q0, int(start), i + 1, int(end)))
-            # dQ: 64-key sub-tiles up to the tile's last visible key
             last = min(q0 + 128, int(end))
-            bq.append((q0, int(start), (last - int(start) + 63) // 64, int(end)))
-            # dK/dV: 64-query sub-tiles from the key tile's first row to the document end
-            bkv.append((q0, q0, (int(end) - q0 + 63) // 64, int(end)))
+            if last > q_lo:
+                fwd.append((q0, int(start), i + 1, int(end)))
+                # dQ: 64-key sub-tiles up to the tile's last visible key
+                bq.append((q0, int(start), (last - int(start) + 63) // 64, int(end)))
+            # dK/dV: 64-query sub-tiles from the key tile's first row (or the first local query) to the document end
+            qb = max(q0, (q_lo - int(start)) // 64 * 64 + int(start)) if q_lo > q0 else q0
+            bkv.append((q0, qb, (int(end) - qb + 63) // 64, int(end)))
 
     def to_dev(rows, key):
         if not rows:

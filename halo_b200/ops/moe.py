@@ -117,8 +117,14 @@ class LocalTransport:
         the kernels by value."""
         return (_lib.c_void_p * 1)(buf.data_ptr())
 
-    def barrier(self) -> None:
+    def barrier(self, channel: int = 0) -> None:
         """All ranks' writes issued before this point are visible to reads issued after it."""
+
+    def barrier_before_push(self) -> None:
+        """Peers are done reading the buffers this rank is about to fill (nothing to do on one rank)."""
+
+    def side_stream(self, device):
+        return None
 
     @property
     def transient_buffers(self) -> bool:
@@ -290,6 +296,7 @@ class _MoEExperts(torch.autograd.Function):
         py = transport.peer_table(y_rows)
         _lib.check(L.halo_zero_pad_rows(_lib.ptr(recv_x), _lib.ptr(state.seg_start), _lib.ptr(state.seg_rows),
                                         _lib.c_int(state.n_local), _lib.c_int(H), _lib.c_int(cap), s), "halo_zero_pad_rows")
+        transport.barrier_before_push()     # after the local zeroing, before anyone's rows arrive
         _lib.check(L.halo_dispatch_rows(_lib.ptr(x), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
                                         _lib.c_void_p(0), px, _lib.c_void_p(0), _lib.c_int(transport.n_ranks), _lib.c_ll(T), _lib.c_int(k),
                                         _lib.c_int(H), _lib.c_int(E_local), _lib.c_int(cap),
@@ -338,6 +345,7 @@ class _MoEExperts(torch.autograd.Function):
         pdy, pw = transport.peer_table(dy), transport.peer_table(row_w)
         _lib.check(L.halo_zero_pad_rows(_lib.ptr(dy), _lib.ptr(state.seg_start), _lib.ptr(state.seg_rows),
                                         _lib.c_int(state.n_local), _lib.c_int(H), _lib.c_int(cap), s), "halo_zero_pad_rows")
+        transport.barrier_before_push()     # row_w is zeroed everywhere before any rank's weights land in it
         _lib.check(L.halo_dispatch_rows(_lib.ptr(dout), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
                                         _lib.ptr(w32), pdy, pw, _lib.c_int(transport.n_ranks), _lib.c_ll(T), _lib.c_int(k),
                                         _lib.c_int(H), _lib.c_int(E_local), _lib.c_int(cap),
@@ -355,28 +363,51 @@ class _MoEExperts(torch.autograd.Function):
         _lib.check(L.halo_swiglu_bwd_weighted(_lib.ptr(pre), _lib.ptr(dact), _lib.ptr(row_w), _lib.ptr(dpre),
                                               _lib.ptr(act_w), _lib.ptr(dwrow), _lib.ptr(state.total_rows),
                                               _lib.c_int(F), _lib.c_int(cap), s), "halo_swiglu_bwd_weighted")
-        # 4. dW_down[e] = dout_e^T (w * act)_e
-        dw_down = torch.empty_like(w_down)
-        lst = _tile_list(state, "k", m_dim=H, n_dim=F)
-        _gemm_list(dy, act_w, dw_down.reshape(E_local * H, F), lst, 1, 1, EPI_STORE_BF16)
-        # 5. gate/up projection: dx_rows = dpre W_gate_up ; dW_gate_up[e] = dpre_e^T x_e
+        # 4. input gradient rows first: dx_rows = dpre W_gate_up
         dx_rows = transport.buffer("dx_rows", cap, H, torch.bfloat16, dev)
         lst = _tile_list(state, "m", n_cols=H, k_dim=F2, b_mn_stride=0, b_k_stride=F2, swiglu_f=0)
         _gemm_list(dpre, w_gate_up.reshape(E_local * F2, H), dx_rows, lst, 0, 1, EPI_STORE_BF16)
-        dw_gate_up = torch.empty_like(w_gate_up)
-        lst = _tile_list(state, "k", m_dim=F2, n_dim=H)
-        _gemm_list(dpre, recv_x, dw_gate_up.reshape(E_local * F2, H), lst, 1, 1, EPI_STORE_BF16)
-        transport.barrier()
-        # 6. pull the input-gradient rows and the routing-weight gradients back to the tokens
         dx = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
-        pdx, pdw = transport.peer_table(dx_rows), transport.peer_table(dwrow)
-        _lib.check(L.halo_combine_rows(pdx, _lib.c_int(transport.n_ranks), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
-                                       _lib.c_void_p(0), _lib.c_void_p(0), _lib.ptr(dx), _lib.c_ll(T), _lib.c_int(k),
-                                       _lib.c_int(H), _lib.c_int(E_local), _lib.c_int(cap), s), "halo_combine_rows")
         dw = torch.empty((T, k), dtype=torch.float32, device=dev)
-        _lib.check(L.halo_gather_slot_values(pdw, _lib.c_int(transport.n_ranks), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
-                                             _lib.ptr(dw), _lib.c_ll(T * k), _lib.c_int(E_local), _lib.c_int(cap), s),
-                   "halo_gather_slot_values")
+        pdx, pdw = transport.peer_table(dx_rows), transport.peer_table(dwrow)
+
+        def pull_back():
+            # 6. pull the input-gradient rows and the routing-weight gradients back to the tokens
+            st = _lib.stream_ptr(dev)
+            _lib.check(L.halo_combine_rows(pdx, _lib.c_int(transport.n_ranks), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
+                                           _lib.c_void_p(0), _lib.c_void_p(0), _lib.ptr(dx), _lib.c_ll(T), _lib.c_int(k),
+                                           _lib.c_int(H), _lib.c_int(E_local), _lib.c_int(cap), st), "halo_combine_rows")
+            _lib.check(L.halo_gather_slot_values(pdw, _lib.c_int(transport.n_ranks), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
+                                                 _lib.ptr(dw), _lib.c_ll(T * k), _lib.c_int(E_local), _lib.c_int(cap), st),
+                       "halo_gather_slot_values")
+
+        def weight_grads():
+            # 5. dW_down[e] = dout_e^T (w * act)_e ; dW_gate_up[e] = dpre_e^T x_e
+            dw_down = torch.empty_like(w_down)
+            _gemm_list(dy, act_w, dw_down.reshape(E_local * H, F), _tile_list(state, "k", m_dim=H, n_dim=F), 1, 1, EPI_STORE_BF16)
+            dw_gate_up = torch.empty_like(w_gate_up)
+            _gemm_list(dpre, recv_x, dw_gate_up.reshape(E_local * F2, H), _tile_list(state, "k", m_dim=F2, n_dim=H), 1, 1,
+                       EPI_STORE_BF16)
+            return dw_gate_up, dw_down
+
+        side = transport.side_stream(dev) if transport.n_ranks > 1 else None
+        if side is None:
+            dw_gate_up, dw_down = weight_grads()
+            transport.barrier()
+            pull_back()
+        else:
+            # the pull over NVLink runs beside the two weight-gradient products, which need nothing from it
+            main = torch.cuda.current_stream(dev)
+            fork = torch.cuda.Event()
+            fork.record(main)
+            side.wait_event(fork)
+            with torch.cuda.stream(side):
+                transport.barrier(channel=1)
+                pull_back()
+                joined = torch.cuda.Event()
+                joined.record(side)
+            dw_gate_up, dw_down = weight_grads()
+            main.wait_event(joined)
         return dx, None, dw, dw_gate_up, dw_down, None, None, None, None
 
 

@@ -38,6 +38,7 @@ class SymmetricTransport:
         self._cap = None
         self._hidden = None
         self._barrier_handle = None
+        self._side = None
         self.stable_until_backward = True
 
     # ---- provisioning ---------------------------------------------------------------------
@@ -82,10 +83,21 @@ class SymmetricTransport:
         dist.all_gather_into_tensor(out, counts.contiguous(), group=self.group)
         return out
 
-    def barrier(self) -> None:
+    def barrier(self, channel: int = 0) -> None:
         """Device-side barrier on the current stream: peer stores issued before it are visible to
-        peer loads issued after it. Bounded by the symmetric-memory barrier's own timeout."""
-        self._barrier_handle.barrier(channel=0)
+        peer loads issued after it. Bounded by the symmetric-memory barrier's own timeout. Barriers issued
+        from different streams use different channels, so that their arrivals cannot pair up crosswise."""
+        self._barrier_handle.barrier(channel=channel)
+
+    def barrier_before_push(self) -> None:
+        """Run before an expert op fills peers' receive buffers: every rank has finished the products of its
+        previous expert op that still read those buffers (they may run beside that op's pull on another stream)."""
+        self._barrier_handle.barrier(channel=2)
+
+    def side_stream(self, device):
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=device)
+        return self._side
 
     @property
     def transient_buffers(self) -> bool:

@@ -1,5 +1,5 @@
-"""Run under torchrun on 2+ GPUs: the expert transport over peer memory, the fused sharded optimizer
-and the peer-store broadcast against single-device references. Prints ``CHECKS PASSED`` on rank 0."""
+"""Run under torchrun on 2+ GPUs: the expert transport over peer memory, the fused sharded optimizer,
+the peer-store broadcast and context-parallel attention against single-device references. Prints ``CHECKS PASSED`` on rank 0."""
 
 import os
 import sys
@@ -127,6 +127,44 @@ def check_broadcast_and_allreduce(dev, rank, world):
     hs.barrier(channel=0)
 
 
+def check_context_parallel(dev, rank, world):
+    """Attention of this rank's chunk of a packed row (K/V of straddling documents pulled from peers) against
+    the flash kernel run on the whole row by one GPU, forward and backward."""
+    import numpy as np
+
+    from halo_b200.ops import attention as attn_ops
+    from halo_b200.parallel.context_parallel import CPExchange, build_cp_plan, chunk_bounds, cp_attention, make_layout
+
+    Hq, Hkv, D = 8, 2, 128
+    total = 2048 * world
+    rng = np.random.default_rng(5)
+    lens, left = [], total
+    while left > 0:
+        n = int(min(left, rng.integers(100, 3000)))
+        lens.append(n)
+        left -= n
+    cu = np.concatenate([[0], np.cumsum(lens)])
+    g = torch.Generator(device=dev).manual_seed(11)              # same data on every rank
+    q = (torch.randn(total, Hq * D, device=dev, generator=g) * 0.5).bfloat16()
+    k = (torch.randn(total, Hkv * D, device=dev, generator=g) * 0.5).bfloat16()
+    v = (torch.randn(total, Hkv * D, device=dev, generator=g) * 0.5).bfloat16()
+    do = (torch.randn(total, Hq * D, device=dev, generator=g) * 0.5).bfloat16()
+    qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
+    ref = attn_ops.flash_attention(qf, kf, vf, attn_ops.build_plan(cu, dev), Hq, Hkv)
+    ref.backward(do)
+    lo, hi = chunk_bounds(total, world, rank)
+    lay = make_layout(cu, rank, world)
+    ex = CPExchange(dist.group.WORLD, dev, hi - lo, total - (hi - lo), 2 * Hkv * D)
+    ql, kl, vl = (t[lo:hi].clone().requires_grad_() for t in (q, k, v))
+    out = cp_attention(ql, kl, vl, lay, build_cp_plan(lay, dev), dist.group.WORLD, ex, Hq, Hkv)
+    out.backward(do[lo:hi])
+    torch.cuda.synchronize()
+    close(out, ref[lo:hi], 2e-2, "cp out")
+    close(ql.grad, qf.grad[lo:hi], 3e-2, "cp dq")
+    close(kl.grad, kf.grad[lo:hi], 3e-2, "cp dk")
+    close(vl.grad, vf.grad[lo:hi], 3e-2, "cp dv")
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
@@ -139,6 +177,7 @@ def main():
     check_expert_transport(parallel, dev, rank, world)
     check_fused_optimizer(dev, rank, world)
     check_broadcast_and_allreduce(dev, rank, world)
+    check_context_parallel(dev, rank, world)
     _lib.raise_on_status(dev)
     dist.barrier()
     if rank == 0:
