@@ -50,6 +50,8 @@ def parse_args():
                     help="N > 1: 1 = fused reduce-scatter/AdamW/all-gather kernels for the replicated parameters, "
                          "0 = NCCL all-reduce + local optimizer (the baseline path)")
     ap.add_argument("--doc-dist", default="chat")
+    ap.add_argument("--ep-lanes", type=int, default=2,
+                    help="parts an expert-parallel MoE call is cut into so that one part's NVLink transfers overlap another's GEMMs")
     ap.add_argument("--recompute", default="auto", choices=["auto", "full"],
                     help="auto: layers keep their attention-half activations where memory allows")
     ap.add_argument("--lr", type=float, default=1e-5)
@@ -185,7 +187,7 @@ def main() -> int:
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
-        parallel = ParallelRuntime.for_expert_parallel(world, dev)
+        parallel = ParallelRuntime.for_expert_parallel(world, dev, n_lanes=args.ep_lanes)
         transport = parallel.transport
 
     cfg = PRESETS[args.model]()
@@ -285,7 +287,7 @@ def main() -> int:
     e2e = tokens / (ms_e2e / 1e3)
     peak_gib = torch.cuda.max_memory_allocated(dev) / 2**30
     if rank == 0:
-        par = f"ep{world}" + (f"+dp{world}" if world > 1 else "") + ("+fused_zero" if parallel is not None and parallel.fused_optimizer is not None else "") + ("+host_optimizer_state" if getattr(opt, "state_bytes_on_host", lambda: 0)() > 0 else "")
+        par = f"ep{world}" + (f"+dp{world}" if world > 1 else "") + (f"+ep_lanes{args.ep_lanes}" if world > 1 and args.ep_lanes > 1 else "") + ("+fused_zero" if parallel is not None and parallel.fused_optimizer is not None else "") + ("+host_optimizer_state" if getattr(opt, "state_bytes_on_host", lambda: 0)() > 0 else "")
         line = {
             "metric": "train tokens/s, 30B-A3B MoE, packed 64k rows (whole job)",
             "value": round(value, 1),

@@ -81,12 +81,16 @@ class _RouterLinear(torch.autograd.Function):
 
 
 class Attention(nn.Module):
-    def __init__(self, cfg: ModelConfig, dtype, device):
+    def __init__(self, cfg: ModelConfig, dtype, device, tp_size: int = 1):
         super().__init__()
         self.cfg = cfg
         H, D = cfg.hidden_size, cfg.head_dim
-        self.qkv_proj = nn.Parameter(torch.empty(cfg.qkv_dim, H, dtype=dtype, device=device))
-        self.o_proj = nn.Parameter(torch.empty(H, cfg.num_attention_heads * D, dtype=dtype, device=device))
+        # under tensor parallelism a rank holds 1/tp of the query and of the key/value heads
+        self.n_heads, self.n_kv_heads = cfg.num_attention_heads // tp_size, cfg.num_key_value_heads // tp_size
+        self.qkv_proj = nn.Parameter(torch.empty((self.n_heads + 2 * self.n_kv_heads) * D, H, dtype=dtype, device=device))
+        self.o_proj = nn.Parameter(torch.empty(H, self.n_heads * D, dtype=dtype, device=device))
+        if tp_size > 1:
+            self.qkv_proj.tp_kind, self.o_proj.tp_kind = "qkv", "o"
         if cfg.use_qk_norm:
             self.q_norm = nn.Parameter(torch.ones(D, dtype=dtype, device=device))
             self.k_norm = nn.Parameter(torch.ones(D, dtype=dtype, device=device))
@@ -96,6 +100,14 @@ class Attention(nn.Module):
 
     def forward(self, h, ctx):
         cfg = self.cfg
+        if ctx.tp is not None:
+            # token shards -> whole row, a slice of the heads, partial output summed back into token shards
+            from halo_b200.parallel.tensor_parallel import gather_seq, reduce_scatter_seq
+
+            qkv = gemm.linear(gather_seq(h, ctx.tp), self.qkv_proj)
+            o = attn_ops.rope_attention(qkv, self.q_norm, self.k_norm, ctx.rope, ctx.plan, self.n_heads, self.n_kv_heads,
+                                        cfg.rms_norm_eps, cfg.use_qk_norm)
+            return reduce_scatter_seq(gemm.linear(o, self.o_proj), ctx.tp)
         qkv = gemm.linear(h, self.qkv_proj)
         if ctx.cp is not None:
             # context parallel: this rank holds one chunk of the row; keys and values of straddling documents
@@ -116,12 +128,21 @@ class Attention(nn.Module):
 
 
 class DenseMLP(nn.Module):
-    def __init__(self, hidden: int, width: int, dtype, device):
+    def __init__(self, hidden: int, width: int, dtype, device, tp_size: int = 1):
         super().__init__()
+        width //= tp_size
+        self.tp_size = tp_size
         self.gate_up_proj = nn.Parameter(torch.empty(2 * width, hidden, dtype=dtype, device=device))
         self.down_proj = nn.Parameter(torch.empty(hidden, width, dtype=dtype, device=device))
+        if tp_size > 1:
+            self.gate_up_proj.tp_kind, self.down_proj.tp_kind = "gate_up", "down"
 
     def forward(self, h, ctx=None):
+        if self.tp_size > 1:
+            from halo_b200.parallel.tensor_parallel import gather_seq, reduce_scatter_seq
+
+            act = _SwiGLULinear.apply(gather_seq(h, ctx.tp), self.gate_up_proj, torch.is_grad_enabled())
+            return reduce_scatter_seq(gemm.linear(act, self.down_proj), ctx.tp)
         return gemm.linear(_SwiGLULinear.apply(h, self.gate_up_proj, torch.is_grad_enabled()), self.down_proj)
 
 
@@ -179,16 +200,17 @@ class SparseMoE(nn.Module):
 
 
 class DecoderLayer(nn.Module):
-    def __init__(self, cfg: ModelConfig, idx: int, dtype, device, n_local_experts: int, router_dtype=None):
+    def __init__(self, cfg: ModelConfig, idx: int, dtype, device, n_local_experts: int, router_dtype=None, tp_size: int = 1):
         super().__init__()
         H = cfg.hidden_size
         self.input_layernorm = nn.Parameter(torch.ones(H, dtype=dtype, device=device))
         self.post_attention_layernorm = nn.Parameter(torch.ones(H, dtype=dtype, device=device))
-        self.self_attn = Attention(cfg, dtype, device)
+        self.self_attn = Attention(cfg, dtype, device, tp_size)
         if cfg.layer_is_moe(idx):
+            # attention-only tensor parallelism for MoE layers: router and experts see this rank's token shard
             self.mlp = SparseMoE(cfg, dtype, device, n_local_experts, router_dtype)
         else:
-            self.mlp = DenseMLP(H, cfg.intermediate_size, dtype, device)
+            self.mlp = DenseMLP(H, cfg.intermediate_size, dtype, device, tp_size)
         self.eps = cfg.rms_norm_eps
         # "full": the whole layer is re-run in the backward pass; "mlp": the attention half keeps its
         # activations (about 30 KB per token) and only the feed-forward half is re-run; "none": nothing is re-run
@@ -211,8 +233,9 @@ class DecoderLayer(nn.Module):
 class ForwardContext:
     """Per-batch state shared by all layers: attention plan, rotary table, expert transport."""
 
-    def __init__(self, plan, rope, transport, record_routing=None, replay_topk=None, cp=None):
+    def __init__(self, plan, rope, transport, record_routing=None, replay_topk=None, cp=None, tp=None):
         self.plan = plan
+        self.tp = tp                 # TensorParallel when activations are token-sharded over a tensor-parallel group
         self.cp = cp                 # (ContextParallel, CPLayout) when the row is cut over a context-parallel group
         self.rope = rope
         self.transport = transport
@@ -226,7 +249,7 @@ class Qwen3Model(nn.Module):
 
     def __init__(self, cfg: ModelConfig, dtype=torch.bfloat16, device=None, transport=None,
                  gradient_checkpointing: bool = True, router_dtype=None, layer_range: tuple[int, int] | None = None,
-                 has_embed: bool = True, has_head: bool = True):
+                 has_embed: bool = True, has_head: bool = True, tensor_parallel=None):
         super().__init__()
         self.cfg = cfg
         self.transport = transport or moe_ops.LocalTransport()
@@ -236,12 +259,18 @@ class Qwen3Model(nn.Module):
         n_local = cfg.num_experts // self.transport.n_ranks if cfg.is_moe else 0
         self.gradient_checkpointing = gradient_checkpointing
         self.context_parallel = None      # halo_b200.parallel.context_parallel.ContextParallel when cp > 1
+        self.tensor_parallel = tensor_parallel    # halo_b200.parallel.tensor_parallel.TensorParallel when tp > 1
+        tp_size = tensor_parallel.size if tensor_parallel is not None else 1
+        if tp_size > 1:
+            from halo_b200.parallel.tensor_parallel import check_divisibility
+
+            check_divisibility(cfg, tp_size)
         lo, hi = layer_range or (0, cfg.num_hidden_layers)
         self.layer_range = (lo, hi)
         H = cfg.hidden_size
         self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, H, dtype=dtype, device=device)) if has_embed else None
         self.layers = nn.ModuleList(
-            [DecoderLayer(cfg, i, dtype, device, n_local, router_dtype) for i in range(lo, hi)])
+            [DecoderLayer(cfg, i, dtype, device, n_local, router_dtype, tp_size) for i in range(lo, hi)])
         self.norm = nn.Parameter(torch.ones(H, dtype=dtype, device=device)) if has_head else None
         if has_head and not (cfg.tie_word_embeddings and has_embed):
             self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, H, dtype=dtype, device=device))
@@ -277,6 +306,16 @@ class Qwen3Model(nn.Module):
                 for le in range(p.shape[0]):
                     g = torch.Generator(device=dev).manual_seed(base + e0 + le)
                     p[le].normal_(0.0, std, generator=g)
+            elif getattr(p, "tp_kind", None) is not None:
+                # draw the unsliced tensor (same values under any tensor-parallel width) and keep this rank's slice
+                from halo_b200.parallel.tensor_parallel import slice_for_rank
+
+                tp = self.tensor_parallel
+                full_shape = {"qkv": (self.cfg.qkv_dim, p.shape[1]), "o": (p.shape[0], p.shape[1] * tp.size),
+                              "gate_up": (p.shape[0] * tp.size, p.shape[1]), "down": (p.shape[0], p.shape[1] * tp.size)}[p.tp_kind]
+                g = torch.Generator(device=dev).manual_seed(base)
+                full = torch.empty(full_shape, dtype=p.dtype, device=dev).normal_(0.0, std, generator=g)
+                p.copy_(slice_for_rank(p.tp_kind, full, self.cfg, tp.rank, tp.size))
             else:
                 g = torch.Generator(device=dev).manual_seed(base)
                 p.normal_(0.0, std, generator=g)
@@ -291,7 +330,7 @@ class Qwen3Model(nn.Module):
             layout, plan = self.context_parallel.layout_and_plan(cu_seqlens)
             return ForwardContext(plan, rope, self.transport, record_routing, replay_topk, (self.context_parallel, layout))
         plan = attn_ops.build_plan(cu_seqlens, device=dev)
-        return ForwardContext(plan, rope, self.transport, record_routing, replay_topk)
+        return ForwardContext(plan, rope, self.transport, record_routing, replay_topk, tp=self.tensor_parallel)
 
     def _gate(self, params):
         if self.param_gate is not None:

@@ -186,6 +186,24 @@ def plan_routing(topk_idx: torch.Tensor, n_experts: int, transport) -> RoutingSt
     )
 
 
+def _alloc(transport, shape, dtype, dev):
+    """A temporary for an expert op. A lane of a multi-lane transport runs on its own stream; PyTorch's caching
+    allocator keeps one pool per stream, and with several GB of temporaries per lane those pools cannot lend to
+    each other, so an almost full device would spend its time releasing and re-mapping segments. Lanes therefore
+    take their temporaries from the pool of the stream that issued the op and mark them as used by the lane's
+    stream (the block is not handed out again before the lane's work on it has finished)."""
+    home = getattr(transport, "alloc_stream", None)
+    if home is None:
+        return torch.empty(shape, dtype=dtype, device=dev)
+    with torch.cuda.stream(home):
+        t = torch.empty(shape, dtype=dtype, device=dev)
+    t.record_stream(transport.stream)
+    side = getattr(transport, "_side", None)
+    if side is not None:
+        t.record_stream(side)
+    return t
+
+
 def _tile_list(state: RoutingState, kind: str, **kw):
     """Device tile list for one grouped product shape, cached per routing state."""
     key = (kind, tuple(sorted(kw.items())))
@@ -231,14 +249,14 @@ def _gemm_list(a, b2d, c, lst_cnt, a_mn, b_mn, epi, aux=None, swiglu_f=0, alpha=
     _lib.check(rc, "halo_gemm_bf16_list")
 
 
-def grouped_swiglu_ffn_fwd(state: RoutingState, x_rows, w_gate_up, w_down, save_pre: bool):
+def grouped_swiglu_ffn_fwd(state: RoutingState, x_rows, w_gate_up, w_down, save_pre: bool, transport=None):
     """x_rows: [cap, H] grouped by expert. Returns (y_rows [cap, H], act [cap, F], pre [cap, 2F] | None)."""
     E, F2, H = w_gate_up.shape
     F = F2 // 2
     cap = x_rows.shape[0]
     dev = x_rows.device
-    act = torch.empty((cap, F), dtype=torch.bfloat16, device=dev)
-    pre = torch.empty((cap, F2), dtype=torch.bfloat16, device=dev) if save_pre else None
+    act = _alloc(transport, (cap, F), torch.bfloat16, dev)
+    pre = _alloc(transport, (cap, F2), torch.bfloat16, dev) if save_pre else None
     lst1 = _tile_list(state, "m", n_cols=F2, k_dim=H, b_mn_stride=F2, b_k_stride=0, swiglu_f=F)
     _gemm_list(x_rows, w_gate_up.reshape(E * F2, H), act, lst1, 0, 0, EPI_SWIGLU, aux=pre, swiglu_f=F)
     return act, pre
@@ -303,16 +321,16 @@ class _MoEExperts(torch.autograd.Function):
                                         _lib.ptr(_lib.status_word(dev)), s), "halo_dispatch_rows")
         transport.barrier()
         need_grad = grad_mode and any(ctx.needs_input_grad)
-        act, pre = grouped_swiglu_ffn_fwd(state, recv_x, w_gate_up, w_down, save_pre=need_grad)
+        act, pre = grouped_swiglu_ffn_fwd(state, recv_x, w_gate_up, w_down, save_pre=need_grad, transport=transport)
         w32 = topk_w.float().contiguous()
         if skip_output and need_grad:
             # a recomputation whose value nobody reads: the backward needs only the dispatched rows and the
             # pre-activations, so the down projection and the pull back to the tokens are left out
-            out = torch.empty_like(x)
+            out = _alloc(transport, tuple(x.shape), x.dtype, dev)
         else:
             grouped_down_fwd(state, act, w_down, y_rows)
             transport.barrier()
-            out = torch.empty_like(x)
+            out = _alloc(transport, tuple(x.shape), x.dtype, dev)
             _lib.check(L.halo_combine_rows(py, _lib.c_int(transport.n_ranks), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
                                            _lib.ptr(w32), _lib.c_void_p(0), _lib.ptr(out), _lib.c_ll(T), _lib.c_int(k),
                                            _lib.c_int(H), _lib.c_int(E_local), _lib.c_int(cap), s), "halo_combine_rows")
@@ -352,14 +370,14 @@ class _MoEExperts(torch.autograd.Function):
                                         _lib.ptr(_lib.status_word(dev)), s), "halo_dispatch_rows")
         transport.barrier()
         # 2. unscaled activation gradient: dact_u = dout_rows W_down
-        dact = torch.empty((cap, F), dtype=torch.bfloat16, device=dev)
+        dact = _alloc(transport, (cap, F), torch.bfloat16, dev)
         lst = _tile_list(state, "m", n_cols=F, k_dim=H, b_mn_stride=0, b_k_stride=H, swiglu_f=0)
         _gemm_list(dy, w_down.reshape(E_local * H, F), dact, lst, 0, 1, EPI_STORE_BF16)
         # 3. SwiGLU backward with the routing weight folded in: dpre = w * swiglu'(pre) dact_u, act_w = w * act,
         #    dwrow = <dact_u, act> (= <dout, expert output>, without ever forming the expert output)
         dwrow = transport.buffer("dwrow", cap, 1, torch.float32, dev)
-        dpre = torch.empty((cap, F2), dtype=torch.bfloat16, device=dev)
-        act_w = torch.empty((cap, F), dtype=torch.bfloat16, device=dev)
+        dpre = _alloc(transport, (cap, F2), torch.bfloat16, dev)
+        act_w = _alloc(transport, (cap, F), torch.bfloat16, dev)
         _lib.check(L.halo_swiglu_bwd_weighted(_lib.ptr(pre), _lib.ptr(dact), _lib.ptr(row_w), _lib.ptr(dpre),
                                               _lib.ptr(act_w), _lib.ptr(dwrow), _lib.ptr(state.total_rows),
                                               _lib.c_int(F), _lib.c_int(cap), s), "halo_swiglu_bwd_weighted")
@@ -367,8 +385,8 @@ class _MoEExperts(torch.autograd.Function):
         dx_rows = transport.buffer("dx_rows", cap, H, torch.bfloat16, dev)
         lst = _tile_list(state, "m", n_cols=H, k_dim=F2, b_mn_stride=0, b_k_stride=F2, swiglu_f=0)
         _gemm_list(dpre, w_gate_up.reshape(E_local * F2, H), dx_rows, lst, 0, 1, EPI_STORE_BF16)
-        dx = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
-        dw = torch.empty((T, k), dtype=torch.float32, device=dev)
+        dx = _alloc(transport, (T, H), torch.bfloat16, dev)
+        dw = _alloc(transport, (T, k), torch.float32, dev)
         pdx, pdw = transport.peer_table(dx_rows), transport.peer_table(dwrow)
 
         def pull_back():
@@ -383,9 +401,9 @@ class _MoEExperts(torch.autograd.Function):
 
         def weight_grads():
             # 5. dW_down[e] = dout_e^T (w * act)_e ; dW_gate_up[e] = dpre_e^T x_e
-            dw_down = torch.empty_like(w_down)
+            dw_down = _alloc(transport, tuple(w_down.shape), w_down.dtype, dev)
             _gemm_list(dy, act_w, dw_down.reshape(E_local * H, F), _tile_list(state, "k", m_dim=H, n_dim=F), 1, 1, EPI_STORE_BF16)
-            dw_gate_up = torch.empty_like(w_gate_up)
+            dw_gate_up = _alloc(transport, tuple(w_gate_up.shape), w_gate_up.dtype, dev)
             _gemm_list(dpre, recv_x, dw_gate_up.reshape(E_local * F2, H), _tile_list(state, "k", m_dim=F2, n_dim=H), 1, 1,
                        EPI_STORE_BF16)
             return dw_gate_up, dw_down
@@ -411,6 +429,40 @@ class _MoEExperts(torch.autograd.Function):
         return dx, None, dw, dw_gate_up, dw_down, None, None, None, None
 
 
+def _moe_experts_lanes(x, topk_idx, topk_w, w_gate_up, w_down, lanes, state_out, skip_output):
+    """Cut the tokens into one part per lane and run each part's whole expert op (push, products, pull) on the
+    lane's own stream and buffers: while one part moves rows over NVLink, another part's products keep the
+    tensor cores busy. Every rank cuts at the same places, so the lanes' barriers pair up across ranks."""
+    T = x.shape[0]
+    n = len(lanes) if T >= 256 * len(lanes) else 1
+    step = ((T + n - 1) // n + 127) // 128 * 128
+    dev = x.device
+    main = torch.cuda.current_stream(dev)
+    fork = torch.cuda.Event()
+    fork.record(main)
+    grad_mode = torch.is_grad_enabled()
+    outs, done = [], []
+    for i in range(n):
+        lo, hi = i * step, min(T, (i + 1) * step)
+        if lo >= hi:
+            break
+        lane = lanes[i]
+        lane.alloc_stream = main
+        xs, ids, ws = x[lo:hi], topk_idx[lo:hi], topk_w[lo:hi]
+        lane.stream.wait_event(fork)
+        with torch.cuda.stream(lane.stream):
+            o = _MoEExperts.apply(xs, ids, ws, w_gate_up, w_down, lane, state_out, grad_mode, skip_output)
+            ev = torch.cuda.Event()
+            ev.record(lane.stream)
+        outs.append(o)
+        done.append(ev)
+    for ev in done:
+        main.wait_event(ev)
+    for o in outs:
+        o.record_stream(main)
+    return outs[0] if len(outs) == 1 else torch.cat(outs, dim=0)
+
+
 def moe_experts(x, topk_idx, topk_w, w_gate_up, w_down, transport=None, state_out: list | None = None,
                 skip_output: bool = False):
     """Apply the routed experts.
@@ -427,5 +479,8 @@ def moe_experts(x, topk_idx, topk_w, w_gate_up, w_down, transport=None, state_ou
         if transport.n_ranks > 1:
             return transport.reference_ffn(x, topk_idx, topk_w, w_gate_up, w_down)
         return moe_ffn_reference(x, topk_idx, topk_w, w_gate_up, w_down, offset)
+    lanes = getattr(transport, "lanes", None)
+    if lanes:
+        return _moe_experts_lanes(x.contiguous(), topk_idx, topk_w, w_gate_up, w_down, lanes, state_out, skip_output)
     return _MoEExperts.apply(x.contiguous(), topk_idx, topk_w, w_gate_up, w_down, transport, state_out,
                              torch.is_grad_enabled(), skip_output)

@@ -28,8 +28,15 @@ from halo_b200.ops import _lib
 class SymmetricTransport:
     """Expert-parallel transport over peer-mapped buffers of one process group."""
 
-    def __init__(self, group, device, capacity_factor: float = 1.5):
+    def __init__(self, group, device, capacity_factor: float = 1.5, n_lanes: int = 1, channel_base: int = 0):
+        """``n_lanes`` > 1: the tokens of one MoE call are cut into that many parts, each routed through its own
+        half-size buffers on its own stream, so one part's transfers over NVLink run beside another part's expert
+        products. ``channel_base``: first barrier channel of this transport (three are used)."""
         self.group = group
+        self.channel_base = channel_base
+        self.lanes = ([SymmetricTransport(group, device, capacity_factor, 1, 4 * (i + 1)) for i in range(n_lanes)]
+                      if n_lanes > 1 else None)
+        self.stream = None
         self.device = torch.device(device)
         self.n_ranks = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -46,6 +53,12 @@ class SymmetricTransport:
         """Allocate the row buffers for the largest batch this run will route (collective call)."""
         import torch.distributed._symmetric_memory as symm
 
+        if self.lanes:
+            per_lane = ((max_tokens + len(self.lanes) - 1) // len(self.lanes) + 127) // 128 * 128
+            for lane in self.lanes:
+                lane.configure(per_lane, top_k, hidden, n_local_experts)
+                lane.stream = torch.cuda.Stream(device=self.device)
+            return
         mean_rows = max_tokens * top_k  # every rank sends max_tokens * top_k slots; on average it receives as many
         cap = int(self.capacity_factor * mean_rows) + 128 * n_local_experts
         cap = (cap + 127) // 128 * 128
@@ -87,12 +100,12 @@ class SymmetricTransport:
         """Device-side barrier on the current stream: peer stores issued before it are visible to
         peer loads issued after it. Bounded by the symmetric-memory barrier's own timeout. Barriers issued
         from different streams use different channels, so that their arrivals cannot pair up crosswise."""
-        self._barrier_handle.barrier(channel=channel)
+        self._barrier_handle.barrier(channel=self.channel_base + channel)
 
     def barrier_before_push(self) -> None:
         """Run before an expert op fills peers' receive buffers: every rank has finished the products of its
         previous expert op that still read those buffers (they may run beside that op's pull on another stream)."""
-        self._barrier_handle.barrier(channel=2)
+        self._barrier_handle.barrier(channel=self.channel_base + 2)
 
     def side_stream(self, device):
         if self._side is None:
@@ -135,11 +148,11 @@ class ParallelRuntime:
         return experts
 
     @classmethod
-    def for_expert_parallel(cls, world: int, device, group=None) -> "ParallelRuntime":
+    def for_expert_parallel(cls, world: int, device, group=None, n_lanes: int = 2) -> "ParallelRuntime":
         """EP over every rank of ``group`` (default: the job); the non-expert parameters are replicated
         over the same ranks."""
         group = group if group is not None else dist.group.WORLD
-        transport = SymmetricTransport(group, device)
+        transport = SymmetricTransport(group, device, n_lanes=n_lanes)
         return cls(device, dp_group=group, ep_group=group, expert_replica_group=None, transport=transport)
 
     # ---- scalars -----------------------------------------------------------------------------

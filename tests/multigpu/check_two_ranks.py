@@ -165,6 +165,34 @@ def check_context_parallel(dev, rank, world):
     close(vl.grad, vf.grad[lo:hi], 3e-2, "cp dv")
 
 
+def check_tensor_parallel_collectives(dev, rank, world):
+    """Sequence gather and reduce-scatter over peer memory against NCCL, forward and backward."""
+    from halo_b200.parallel.tensor_parallel import TensorParallel, gather_seq, reduce_scatter_seq
+
+    T, H = 1024 * world, 256
+    tp = TensorParallel(dist.group.WORLD, dev, hidden=H, max_tokens=T)
+    g = torch.Generator(device=dev).manual_seed(50 + rank)
+    shard = torch.randn(T // world, H, device=dev, generator=g).bfloat16().requires_grad_()
+    full = gather_seq(shard, tp)
+    want = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
+    dist.all_gather_into_tensor(want, shard.detach())
+    assert torch.equal(full, want), "tp gather"
+    partial = torch.randn(T, H, device=dev, generator=g).bfloat16().requires_grad_()
+    mine = reduce_scatter_seq(partial, tp)
+    ref = partial.detach().float().clone()
+    dist.all_reduce(ref)
+    lo, hi = tp.shard_rows(T)
+    close(mine, ref[lo:hi], 1e-2, "tp reduce-scatter")
+    gy = torch.randn(T // world, H, device=dev, generator=g).bfloat16()
+    mine.backward(gy)                                   # backward of a reduce-scatter is a gather
+    want_g = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
+    dist.all_gather_into_tensor(want_g, gy)
+    assert torch.equal(partial.grad, want_g), "tp reduce-scatter backward"
+    full.backward(want_g)                               # backward of a gather is a reduce-scatter
+    ref_g = want_g.float() * world
+    close(shard.grad, ref_g[lo:hi], 1e-2, "tp gather backward")
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
@@ -178,6 +206,7 @@ def main():
     check_fused_optimizer(dev, rank, world)
     check_broadcast_and_allreduce(dev, rank, world)
     check_context_parallel(dev, rank, world)
+    check_tensor_parallel_collectives(dev, rank, world)
     _lib.raise_on_status(dev)
     dist.barrier()
     if rank == 0:

@@ -1,0 +1,71 @@
+"""Tensor parallelism with token-sharded activations on two gloo ranks: a dense and a MoE model give the loss
+and the gradients of the unsliced model; weight slices reassemble to the full tensors."""
+
+import pytest
+import torch
+
+from halo_b200.models.config import PRESETS, ModelConfig
+from halo_b200.parallel.tensor_parallel import slice_for_rank, unslice
+from tests.common.gloo import run_gloo_ranks
+
+
+def test_slices_reassemble():
+    cfg = ModelConfig(hidden_size=64, num_attention_heads=8, num_key_value_heads=4, head_dim=16, intermediate_size=96)
+    shapes = {"qkv": (cfg.qkv_dim, 64), "o": (64, 8 * 16), "gate_up": (2 * 96, 64), "down": (64, 96)}
+    for kind, shape in shapes.items():
+        full = torch.randn(shape)
+        for size in (2, 4):
+            parts = [slice_for_rank(kind, full, cfg, r, size) for r in range(size)]
+            assert torch.equal(unslice(kind, parts, cfg), full), (kind, size)
+
+
+def _worker(rank, world, preset):
+    import dataclasses
+
+    import numpy as np
+    import torch.distributed as dist
+
+    from halo_b200.data.packing import PackedBatch, pack_documents
+    from halo_b200.models.qwen3 import build_model
+    from halo_b200.parallel.tensor_parallel import TensorParallel, gather_full_weight
+
+    if preset == "dense":
+        cfg = ModelConfig(vocab_size=512, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                          head_dim=16, intermediate_size=96, num_experts=0, model_type="qwen3")
+    else:
+        cfg = dataclasses.replace(PRESETS["tiny-moe"](), num_hidden_layers=2)
+    rng = np.random.default_rng(1)
+    full = pack_documents([rng.integers(0, cfg.vocab_size, size=n) for n in (50, 31, 47)])     # 128 tokens
+    norm = float(full.n_scored)
+    tp = TensorParallel(dist.group.WORLD, "cpu")
+    model = build_model(cfg, device="cpu", dtype=torch.float32, seed=4, tensor_parallel=tp)
+    lo, hi = tp.shard_rows(full.n_tokens)
+    # token ids and labels are this rank's shard; positions and document boundaries describe the whole row
+    ctx = model.make_context(full.position_ids, full.cu_seqlens)
+    local = PackedBatch(full.input_ids[lo:hi], full.position_ids, full.labels[lo:hi], full.cu_seqlens, 0)
+    loss = model(local.input_ids, local.position_ids, local.cu_seqlens, local.labels, norm, ctx=ctx)
+    loss.backward()
+    total = loss.detach().clone()
+    dist.all_reduce(total)
+
+    ref = build_model(cfg, device="cpu", dtype=torch.float32, seed=4)
+    ref_loss = ref(full.input_ids, full.position_ids, full.cu_seqlens, full.labels, norm)
+    ref_loss.backward()
+    assert torch.allclose(total, ref_loss.detach(), rtol=1e-5, atol=1e-6), (float(total), float(ref_loss))
+    ref_params = dict(ref.named_parameters())
+    for name, p in model.named_parameters():
+        kind = getattr(p, "tp_kind", None)
+        if kind is None:
+            g = p.grad.clone()
+            dist.all_reduce(g)                       # replicated weights saw only this rank's tokens
+            want_w, want_g = ref_params[name].detach(), ref_params[name].grad
+        else:
+            g = gather_full_weight(kind, p.grad, cfg, tp)          # sliced weights saw every token
+            want_w, want_g = ref_params[name].detach(), ref_params[name].grad
+            assert torch.equal(gather_full_weight(kind, p.detach(), cfg, tp), want_w), name
+        assert torch.allclose(g, want_g, rtol=2e-4, atol=2e-6), name
+
+
+@pytest.mark.parametrize("preset", ["dense", "moe"])
+def test_tensor_parallel_matches_unsliced_model(preset):
+    run_gloo_ranks(_worker, 2, args=(preset,), timeout=120.0)
