@@ -66,6 +66,13 @@ struct GemmParams {
     const GemmWork* list;    // list mode when non-null
     const int* list_count;   // device count of list entries
     int* status;
+    // Reduce-scatter epilogue (dense bf16 store only): rows [d * rs_rows, (d + 1) * rs_rows) of the product belong
+    // to rank d, and a tile of those rows is stored straight into rank d's staging buffer c_peers[d] (that GPU's
+    // memory mapped into this process) at row rs_rank * rs_rows + (row - d * rs_rows): slot rs_rank of the owner's
+    // [rs_ranks][rs_rows][N] staging area. Tiles of other owners are visited first, the rank's own last, so the
+    // NVLink stores of the early tiles drain while the later tiles are still being multiplied.
+    void* c_peers[8];
+    int rs_ranks, rs_rank, rs_rows;
 };
 
 __device__ __forceinline__ bool fetch_work(const GemmParams& p, int idx, int total, GemmWork& w) {
@@ -77,18 +84,32 @@ __device__ __forceinline__ bool fetch_work(const GemmParams& p, int idx, int tot
     // dense: walk groups of 8 tile-rows, column-first inside a group, so CTAs running together
     // share A row-blocks and B column-blocks through L2
     const int group_m = 8;
+    int tiles_m = p.tiles_m, tm_base = 0;
+    w.pad0 = 0;
+    if (p.rs_ranks > 1) {
+        // owner-major order starting after this rank: every owner's row block is a dense sub-problem
+        const int tm_per_owner = p.rs_rows / kBlockM;
+        const int per_owner = tm_per_owner * p.tiles_n;
+        const int o_seq = idx / per_owner;
+        const int owner = (p.rs_rank + 1 + o_seq) % p.rs_ranks;
+        idx -= o_seq * per_owner;
+        tiles_m = tm_per_owner;
+        tm_base = owner * tm_per_owner;
+        w.pad0 = owner;
+    }
     int per_group = group_m * p.tiles_n;
     int g = idx / per_group;
     int first_m = g * group_m;
-    int gsz = min(p.tiles_m - first_m, group_m);
+    int gsz = min(tiles_m - first_m, group_m);
     int in_g = idx - g * per_group;
-    int tm = first_m + in_g % gsz;
+    int tm = tm_base + first_m + in_g % gsz;
     int tn = in_g / gsz;
     w.a_mn = tm * kBlockM;
     w.a_k = 0;
     w.b_k = 0;
     w.k_iters = (p.K + kBlockK - 1) / kBlockK;
     w.c_row = tm * kBlockM;
+    if (p.rs_ranks > 1) w.c_row = p.rs_rank * p.rs_rows + (tm * kBlockM - w.pad0 * p.rs_rows);
     w.m_valid = min(kBlockM, p.M - tm * kBlockM);
     if (p.epi == kEpiSwiglu) {
         w.b_mn = tn * 128;
@@ -107,7 +128,7 @@ __device__ __forceinline__ bool fetch_work(const GemmParams& p, int idx, int tot
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const GemmParams p) {
+                 const __grid_constant__ GemmParams p) {
     if (status_poisoned(p.status)) return;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bar_full[kStages], bar_empty[kStages], bar_tfull[2], bar_tempty[2];
@@ -298,8 +319,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = zero ? 0.f : __uint_as_float(r[j]) * p.alpha;
                     if (p.epi == kEpiStoreBf16 || p.epi == kEpiAccumBf16) {
+                        void* cbase = p.rs_ranks > 1 ? p.c_peers[w.pad0] : p.C;   // owner's staging area or C
                         __nv_bfloat16* out =
-                            reinterpret_cast<__nv_bfloat16*>(p.C) + grow * p.ldc + w.c_col + c;
+                            reinterpret_cast<__nv_bfloat16*>(cbase) + grow * p.ldc + w.c_col + c;
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) {
                             if (c + j + 8 <= w.n_valid) {
@@ -572,6 +594,36 @@ int halo_gemm_bf16(const void* A, const void* B, void* C, void* aux, int M, int 
     long long tiles = (long long)p.tiles_m * p.tiles_n;
     int grid = (int)(tiles < num_sms() ? tiles : num_sms());
     return dispatch_gemm(a_mn_major, b_mn_major, ta, tb, p, grid, (cudaStream_t)stream);
+}
+
+// Row-parallel product fused with the reduce-scatter's transfer: C_partial = A B^T is never stored locally; every
+// tile goes into slot `rank` of its owner's staging area (see GemmParams). `stage_ptrs`: HOST array of n_ranks
+// device pointers (rank d's [n_ranks][rows_per_rank][N] bf16 staging area as mapped into this process). After the
+// kernel and a barrier over the ranks, each rank sums its n_ranks slots.
+int halo_gemm_bf16_reduce_scatter(const void* A, const void* B, void* const* stage_ptrs, int n_ranks, int rank,
+                                  int M, int N, int K, long long lda, long long ldb, int b_mn_major, int* status,
+                                  void* stream) {
+    if (n_ranks < 2 || n_ranks > 8 || M % n_ranks) return -21;
+    const int rows = M / n_ranks;
+    if (rows % kBlockM || N % 8) return -22;
+    CUtensorMap ta, tb;
+    int rc = make_tmap_bf16(&ta, A, M, K, lda, 128);
+    if (rc) return rc;
+    if (b_mn_major) rc = make_tmap_bf16(&tb, B, K, N, ldb, 64);
+    else rc = make_tmap_bf16(&tb, B, N, K, ldb, 128);
+    if (rc) return rc * 10;
+    GemmParams p{};
+    p.C = nullptr; p.aux = nullptr; p.ldc = N; p.ld_aux = 0; p.epi = kEpiStoreBf16; p.alpha = 1.f;
+    p.M = M; p.N = N; p.K = K;
+    p.tiles_m = M / kBlockM;
+    p.tiles_n = (N + kBlockN - 1) / kBlockN;
+    p.swiglu_f = 0;
+    p.list = nullptr; p.list_count = nullptr; p.status = status;
+    for (int i = 0; i < n_ranks; ++i) p.c_peers[i] = stage_ptrs[i];
+    p.rs_ranks = n_ranks; p.rs_rank = rank; p.rs_rows = rows;
+    long long tiles = (long long)p.tiles_m * p.tiles_n;
+    int grid = (int)(tiles < num_sms() ? tiles : num_sms());
+    return dispatch_gemm(0, b_mn_major, ta, tb, p, grid, (cudaStream_t)stream);
 }
 
 // Product over a device-resident tile list (see plan_grouped_*). The operands are described as

@@ -102,12 +102,12 @@ class Attention(nn.Module):
         cfg = self.cfg
         if ctx.tp is not None:
             # token shards -> whole row, a slice of the heads, partial output summed back into token shards
-            from halo_b200.parallel.tensor_parallel import gather_seq, reduce_scatter_seq
+            from halo_b200.parallel.tensor_parallel import gather_seq, row_parallel_linear
 
             qkv = gemm.linear(gather_seq(h, ctx.tp), self.qkv_proj)
             o = attn_ops.rope_attention(qkv, self.q_norm, self.k_norm, ctx.rope, ctx.plan, self.n_heads, self.n_kv_heads,
                                         cfg.rms_norm_eps, cfg.use_qk_norm)
-            return reduce_scatter_seq(gemm.linear(o, self.o_proj), ctx.tp)
+            return row_parallel_linear(o, self.o_proj, ctx.tp)
         qkv = gemm.linear(h, self.qkv_proj)
         if ctx.cp is not None:
             # context parallel: this rank holds one chunk of the row; keys and values of straddling documents
@@ -139,10 +139,10 @@ class DenseMLP(nn.Module):
 
     def forward(self, h, ctx=None):
         if self.tp_size > 1:
-            from halo_b200.parallel.tensor_parallel import gather_seq, reduce_scatter_seq
+            from halo_b200.parallel.tensor_parallel import gather_seq, row_parallel_linear
 
             act = _SwiGLULinear.apply(gather_seq(h, ctx.tp), self.gate_up_proj, torch.is_grad_enabled())
-            return reduce_scatter_seq(gemm.linear(act, self.down_proj), ctx.tp)
+            return row_parallel_linear(act, self.down_proj, ctx.tp)
         return gemm.linear(_SwiGLULinear.apply(h, self.gate_up_proj, torch.is_grad_enabled()), self.down_proj)
 
 

@@ -12,11 +12,14 @@ The reference keeps activations replicated and all-reduces them (halo/distribute
 local_linears.py:94-111, parallelize_attention.py:40-193); gather + reduce-scatter moves the same bytes and leaves
 every token-local op with ``1 / tp`` of the work.
 
-On GPUs both collectives run on this framework's own kernels over peer-mapped memory: the gather publishes the
-shard in a symmetric buffer and pulls the peers' shards with the peer-copy kernel; the reduce-scatter publishes
-the partial product and every rank sums its own row block out of all peers' buffers in fp32
-(``rs_sum_norm_kernel``, the kernel of the sharded optimizer's gradient reduction). CPU tensors take
-``torch.distributed`` collectives so that gloo tests cover slicing, layouts and gradients.
+On GPUs both collectives run on this framework's own kernels over peer-mapped memory. The gather publishes the
+shard in a symmetric buffer and pulls the peers' shards with the peer-copy kernel. The second projection is ONE
+kernel with its reduce-scatter's transfer (``halo_gemm_bf16_reduce_scatter``): the tcgen05 GEMM's epilogue stores
+every output tile straight into the staging slot of the rank that owns those rows, other owners' tiles first, so
+the NVLink stores drain under the remaining tiles' math; each rank then sums its slots in fp32
+(``rs_sum_norm_kernel``, the kernel of the sharded optimizer's gradient reduction). A stand-alone reduce-scatter of
+an existing tensor (the backward of the gather) publishes the tensor and sums over the peers' buffers with the same
+kernel. CPU tensors take ``torch.distributed`` collectives so that gloo tests cover slicing, layouts and gradients.
 """
 
 from __future__ import annotations
@@ -115,6 +118,62 @@ class _ReduceScatterSeq(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         return _all_gather_rows(g.contiguous(), ctx.tp), None
+
+
+def _fused_gemm_reduce_scatter(x: torch.Tensor, w: torch.Tensor, tp: TensorParallel) -> torch.Tensor:
+    """y_shard = rows of (x w^T summed over ranks) owned by this rank, with the transfer inside the GEMM: every
+    output tile is stored by the epilogue straight into its owner's staging slot over NVLink (tiles of other owners
+    first), then each rank sums its slots in fp32."""
+    T, N = x.shape[0], w.shape[0]
+    rows = T // tp.size
+    if tp.sym.shape[0] * tp.sym.shape[1] < T * N:
+        raise RuntimeError("the tensor-parallel staging buffer is smaller than the product")
+    L = _lib.lib()
+    dev = x.device
+    tp.barrier()        # every rank has finished reading its staging slots of the previous product
+    rc = L.halo_gemm_bf16_reduce_scatter(_lib.ptr(x), _lib.ptr(w), tp._ptr_table, _lib.c_int(tp.size), _lib.c_int(tp.rank),
+                                         _lib.c_int(T), _lib.c_int(N), _lib.c_int(x.shape[1]), _lib.c_ll(x.stride(0)),
+                                         _lib.c_ll(w.stride(0)), _lib.c_int(0), _lib.ptr(_lib.status_word(dev)),
+                                         _lib.stream_ptr(dev))
+    _lib.check(rc, "halo_gemm_bf16_reduce_scatter")
+    tp.barrier()        # all partial tiles have landed
+    n = rows * N
+    slots = (_lib.c_void_p * tp.size)(*[tp.sym.data_ptr() + s * n * 2 for s in range(tp.size)])
+    gsum = torch.empty(n, dtype=torch.float32, device=dev)
+    partial = torch.empty(int(L.halo_rs_blocks(_lib.c_ll(n))), dtype=torch.float32, device=dev)
+    _lib.check(L.halo_rs_sum_norm(slots, _lib.c_int(tp.size), _lib.c_ll(0), _lib.c_ll(n), _lib.ptr(gsum), _lib.ptr(partial),
+                                  _lib.stream_ptr(dev)), "halo_rs_sum_norm")
+    return gsum.view(rows, N).to(x.dtype)
+
+
+class _RowParallelLinear(torch.autograd.Function):
+    """y_shard = reduce_scatter(x w^T) for a row-sliced ``w`` ([N, K / tp]) and the matching slice of ``x``."""
+
+    @staticmethod
+    def forward(ctx, x, w, tp):
+        from halo_b200.ops import gemm
+
+        ctx.tp = tp
+        ctx.save_for_backward(x, w)
+        rows_ok = x.shape[0] % (128 * tp.size) == 0
+        if x.is_cuda and x.dtype == torch.bfloat16 and rows_ok and x.stride(1) == 1 and w.is_contiguous():
+            return _fused_gemm_reduce_scatter(x, w, tp)
+        return _reduce_scatter_rows(gemm.matmul(x, w).contiguous(), tp)
+
+    @staticmethod
+    def backward(ctx, g):
+        from halo_b200.ops import gemm
+
+        x, w = ctx.saved_tensors
+        dy = _all_gather_rows(g.contiguous(), ctx.tp)
+        dx = gemm.matmul(dy, w, b_t=False) if ctx.needs_input_grad[0] else None
+        dw = gemm.matmul(dy, x, a_t=True, b_t=False) if ctx.needs_input_grad[1] else None
+        return dx, dw, None
+
+
+def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, tp: TensorParallel) -> torch.Tensor:
+    """Second projection of a tensor-parallel block: [T, K / tp] x [N, K / tp]^T summed over ranks -> [T / tp, N]."""
+    return _RowParallelLinear.apply(x, w, tp)
 
 
 def gather_seq(x_shard: torch.Tensor, tp: TensorParallel) -> torch.Tensor:

@@ -191,6 +191,19 @@ def check_tensor_parallel_collectives(dev, rank, world):
     full.backward(want_g)                               # backward of a gather is a reduce-scatter
     ref_g = want_g.float() * world
     close(shard.grad, ref_g[lo:hi], 1e-2, "tp gather backward")
+    # the row-parallel product with the reduce-scatter's transfer in the GEMM epilogue
+    from halo_b200.parallel.tensor_parallel import row_parallel_linear
+
+    K = 384
+    x = (torch.randn(T, K, device=dev, generator=g) * 0.1).bfloat16().requires_grad_()
+    w = (torch.randn(H, K, device=dev, generator=g) * 0.1).bfloat16().requires_grad_()
+    y = row_parallel_linear(x, w, tp)
+    ref_y = x.detach().float() @ w.detach().float().t()
+    dist.all_reduce(ref_y)
+    close(y, ref_y[lo:hi], 2e-2, "tp fused gemm + reduce-scatter")
+    y.backward(gy)
+    close(x.grad, want_g.float() @ w.detach().float(), 2e-2, "tp row-parallel dx")
+    close(w.grad, want_g.float().t() @ x.detach().float(), 2e-2, "tp row-parallel dw")
 
 
 def main():
