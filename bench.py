@@ -50,8 +50,9 @@ def parse_args():
                     help="N > 1: 1 = fused reduce-scatter/AdamW/all-gather kernels for the replicated parameters, "
                          "0 = NCCL all-reduce + local optimizer (the baseline path)")
     ap.add_argument("--doc-dist", default="chat")
-    ap.add_argument("--ep-lanes", type=int, default=2,
-                    help="parts an expert-parallel MoE call is cut into so that one part's NVLink transfers overlap another's GEMMs")
+    ap.add_argument("--ep-lanes", type=int, default=0,
+                    help="parts an expert-parallel MoE call is cut into so that one part's NVLink transfers overlap another's GEMMs "
+                         "(0 = automatic: 2 from four GPUs up, where most rows cross NVLink)")
     ap.add_argument("--recompute", default="auto", choices=["auto", "full"],
                     help="auto: layers keep their attention-half activations where memory allows")
     ap.add_argument("--lr", type=float, default=1e-5)
@@ -187,6 +188,8 @@ def main() -> int:
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
+        if args.ep_lanes <= 0:
+            args.ep_lanes = 2 if world >= 4 else 1
         parallel = ParallelRuntime.for_expert_parallel(world, dev, n_lanes=args.ep_lanes)
         transport = parallel.transport
 
@@ -246,7 +249,7 @@ def main() -> int:
         float(out.loss.item())
         torch.cuda.synchronize()
         total_mem = torch.cuda.get_device_properties(dev).total_memory
-        free = int(0.92 * total_mem) - torch.cuda.max_memory_allocated(dev)
+        free = int(0.92 * total_mem) - torch.cuda.max_memory_reserved(dev)   # reserved: what the allocator really holds
         light_layers = plan_recompute(model, args.seq_len, free, reserve_bytes=8 << 30)
     for i in range(args.warmup):
         out = engine.train_step(host_batches[i % n_batches])

@@ -304,28 +304,30 @@ dispatch_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict_
                      const int* __restrict__ slot_row, const float* __restrict__ slot_w,
                      const __grid_constant__ PeerPtrs bufs, const __grid_constant__ PeerPtrs wbufs, int has_w,
                      long long T, int k, int H, int experts_per_rank, int cap_rows, int* status) {
-    const long long t = blockIdx.x;
     const int nvec = H / 8;
-    const uint4* src = reinterpret_cast<const uint4*>(x + t * H);
-    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
-        const uint4 val = src[v];
-        for (int j = 0; j < k; ++j) {
-            const int row = slot_row[t * k + j];
-            if (row < 0) continue;
-            if (row >= cap_rows) {
-                // the receive buffer was provisioned too small for this routing: never write past it
-                if (v == 0 && status) atomicCAS(status, kStatusOk, kStatusBounds);
-                continue;
+    // the grid may be smaller than T (a bounded footprint leaves room on every SM for a GEMM running beside it)
+    for (long long t = blockIdx.x; t < T; t += gridDim.x) {
+        const uint4* src = reinterpret_cast<const uint4*>(x + t * H);
+        for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+            const uint4 val = src[v];
+            for (int j = 0; j < k; ++j) {
+                const int row = slot_row[t * k + j];
+                if (row < 0) continue;
+                if (row >= cap_rows) {
+                    // the receive buffer was provisioned too small for this routing: never write past it
+                    if (v == 0 && status) atomicCAS(status, kStatusOk, kStatusBounds);
+                    continue;
+                }
+                const int r = topk_idx[t * k + j] / experts_per_rank;
+                reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(bufs.p[r]) + (long long)row * H)[v] = val;
             }
-            const int r = topk_idx[t * k + j] / experts_per_rank;
-            reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(bufs.p[r]) + (long long)row * H)[v] = val;
         }
-    }
-    if (has_w && threadIdx.x < k) {
-        const int j = threadIdx.x;
-        const int row = slot_row[t * k + j];
-        if (row >= 0 && row < cap_rows)
-            reinterpret_cast<float*>(wbufs.p[topk_idx[t * k + j] / experts_per_rank])[row] = slot_w[t * k + j];
+        if (has_w && threadIdx.x < k) {
+            const int j = threadIdx.x;
+            const int row = slot_row[t * k + j];
+            if (row >= 0 && row < cap_rows)
+                reinterpret_cast<float*>(wbufs.p[topk_idx[t * k + j] / experts_per_rank])[row] = slot_w[t * k + j];
+        }
     }
 }
 
@@ -349,38 +351,54 @@ combine_rows_kernel(const __grid_constant__ PeerPtrs bufs, const int* __restrict
                     const int* __restrict__ slot_row, const float* __restrict__ w,
                     const __nv_bfloat16* __restrict__ addend, __nv_bfloat16* __restrict__ out,
                     long long T, int k, int H, int experts_per_rank, int cap_rows) {
-    const long long t = blockIdx.x;
     const int nvec = H / 8;
-    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int j = 0; j < k; ++j) {
-            const int row = slot_row[t * k + j];
-            if (row < 0 || row >= cap_rows) continue;
-            const int r = topk_idx[t * k + j] / experts_per_rank;
-            const uint4 u = reinterpret_cast<const uint4*>(
-                reinterpret_cast<const __nv_bfloat16*>(bufs.p[r]) + (long long)row * H)[v];
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-            const float wj = w ? w[t * k + j] : 1.f;
+    constexpr int kChunk = 8;   // rows fetched together: all loads of a chunk are in flight before any is used
+    for (long long t = blockIdx.x; t < T; t += gridDim.x) {
+        for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int j0 = 0; j0 < k; j0 += kChunk) {
+                uint4 u[kChunk];
+                float wj[kChunk];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const float2 f = __bfloat1622float2(h[q]);
-                acc[2 * q] += wj * f.x;
-                acc[2 * q + 1] += wj * f.y;
-            }
-        }
-        if (addend) {
-            const uint4 u = reinterpret_cast<const uint4*>(addend + t * H)[v];
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+                for (int jj = 0; jj < kChunk; ++jj) {
+                    const int j = j0 + jj;
+                    u[jj] = make_uint4(0, 0, 0, 0);
+                    wj[jj] = 0.f;
+                    if (j < k) {
+                        const int row = slot_row[t * k + j];
+                        if (row >= 0 && row < cap_rows) {
+                            const int r = topk_idx[t * k + j] / experts_per_rank;
+                            u[jj] = reinterpret_cast<const uint4*>(
+                                reinterpret_cast<const __nv_bfloat16*>(bufs.p[r]) + (long long)row * H)[v];
+                            wj[jj] = w ? w[t * k + j] : 1.f;
+                        }
+                    }
+                }
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const float2 f = __bfloat1622float2(h[q]);
-                acc[2 * q] += f.x;
-                acc[2 * q + 1] += f.y;
+                for (int jj = 0; jj < kChunk; ++jj) {
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u[jj]);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float2 f = __bfloat1622float2(h[q]);
+                        acc[2 * q] += wj[jj] * f.x;
+                        acc[2 * q + 1] += wj[jj] * f.y;
+                    }
+                }
             }
+            if (addend) {
+                const uint4 ua = reinterpret_cast<const uint4*>(addend + t * H)[v];
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&ua);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 f = __bfloat1622float2(h[q]);
+                    acc[2 * q] += f.x;
+                    acc[2 * q + 1] += f.y;
+                }
+            }
+            reinterpret_cast<uint4*>(out + t * H)[v] =
+                make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]),
+                           pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
         }
-        reinterpret_cast<uint4*>(out + t * H)[v] =
-            make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]),
-                       pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
     }
 }
 
@@ -493,6 +511,22 @@ extern "C" {
 
 #define HALO_LAUNCH_CHECK() (cudaGetLastError() == cudaSuccess ? 0 : -11)
 
+// Blocks of the row-moving kernels: four per SM (half of an SM's thread slots, no shared memory), so that a GEMM
+// CTA launched on another stream can become resident beside them. HALO_ROW_BLOCKS_PER_SM overrides (0 = one block per row).
+static int g_row_blocks_per_sm = -1;
+static unsigned row_grid(long long T) {
+    if (g_row_blocks_per_sm < 0) {
+        const char* e = getenv("HALO_ROW_BLOCKS_PER_SM");
+        g_row_blocks_per_sm = e ? atoi(e) : 4;
+    }
+    if (g_row_blocks_per_sm == 0) return (unsigned)T;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long cap = (long long)sms * g_row_blocks_per_sm;
+    return (unsigned)(T < cap ? T : cap);
+}
+
 int halo_router_topk_fwd(const float* logits, int* idx, float* w, float* probs, const float* sel_bias,
                          long long T, int E, int k, int renorm, void* stream) {
     if (E % 32 || E > 256 || k > 16 || k > E) return -1;
@@ -575,7 +609,7 @@ int halo_dispatch_rows(const void* x, const int* idx, const int* slot_row, const
     PeerPtrs pb, pw;
     if (fill_peers(&pb, bufs, n_ranks)) return -2;
     if (wbufs) { if (fill_peers(&pw, wbufs, n_ranks)) return -2; } else { for (int i = 0; i < kMaxPeers; ++i) pw.p[i] = nullptr; }
-    dispatch_rows_kernel<<<(unsigned)T, 256, 0, (cudaStream_t)stream>>>(
+    dispatch_rows_kernel<<<row_grid(T), 256, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)x, idx, slot_row, slot_w, pb, pw, wbufs ? 1 : 0, T, k, H,
         experts_per_rank, cap_rows, status);
     return HALO_LAUNCH_CHECK();
@@ -596,7 +630,7 @@ int halo_combine_rows(void* const* bufs, int n_ranks, const int* idx, const int*
     if (T == 0) return 0;
     PeerPtrs pb;
     if (fill_peers(&pb, bufs, n_ranks)) return -2;
-    combine_rows_kernel<<<(unsigned)T, 256, 0, (cudaStream_t)stream>>>(
+    combine_rows_kernel<<<row_grid(T), 256, 0, (cudaStream_t)stream>>>(
         pb, idx, slot_row, w, (const __nv_bfloat16*)addend,
         (__nv_bfloat16*)out, T, k, H, experts_per_rank, cap_rows);
     return HALO_LAUNCH_CHECK();
