@@ -52,7 +52,7 @@ def parse_args():
     ap.add_argument("--doc-dist", default="chat")
     ap.add_argument("--ep-lanes", type=int, default=0,
                     help="parts an expert-parallel MoE call is cut into so that one part's NVLink transfers overlap another's GEMMs "
-                         "(0 = automatic: 2 from four GPUs up, where most rows cross NVLink)")
+                         "(0 or 1 = one part; two parts measured slower on 2 and 4 GPUs and are off by default)")
     ap.add_argument("--recompute", default="auto", choices=["auto", "full"],
                     help="auto: layers keep their attention-half activations where memory allows")
     ap.add_argument("--lr", type=float, default=1e-5)
@@ -189,7 +189,7 @@ def main() -> int:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
         if args.ep_lanes <= 0:
-            args.ep_lanes = 2 if world >= 4 else 1
+            args.ep_lanes = 1
         parallel = ParallelRuntime.for_expert_parallel(world, dev, n_lanes=args.ep_lanes)
         transport = parallel.transport
 

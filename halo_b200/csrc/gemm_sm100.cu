@@ -125,6 +125,111 @@ __device__ __forceinline__ bool fetch_work(const GemmParams& p, int idx, int tot
     return true;
 }
 
+// One epilogue warp's share of a finished tile: its 32 TMEM lanes (rows row_in_tile of the tile) x the tile's
+// columns, read with tcgen05.ld and stored according to p.epi. Warp-collective: every lane must call it.
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, const GemmWork& w, uint32_t t_row, int row_in_tile) {
+    const bool row_ok = row_in_tile < w.m_valid;
+    const long long grow = (long long)w.c_row + row_in_tile;
+    const bool zero = (w.k_iters == 0);
+    if (p.epi == kEpiSwiglu) {
+#pragma unroll 1
+        for (int c = 0; c < 128; c += 32) {
+            uint32_t g[32], u[32];
+            tmem_ld_32x32(t_row + c, g);
+            tmem_ld_32x32(t_row + 128 + c, u);
+            tmem_ld_wait();
+            if (row_ok) {
+                __nv_bfloat16* out =
+                    reinterpret_cast<__nv_bfloat16*>(p.C) + grow * p.ldc + w.c_col + c;
+                __nv_bfloat16* aux =
+                    p.aux ? reinterpret_cast<__nv_bfloat16*>(p.aux) + grow * p.ld_aux +
+                                w.c_col + c
+                          : nullptr;
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    if (c + j + 8 <= w.n_valid) {
+                        uint32_t o[4], pg[4], pu[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            // round the pre-activations to bf16 first so a later
+                            // recomputation from the saved copy sees the same values
+                            float g0 = zero ? 0.f : __uint_as_float(g[j + 2 * q]) * p.alpha;
+                            float g1 = zero ? 0.f : __uint_as_float(g[j + 2 * q + 1]) * p.alpha;
+                            float u0 = zero ? 0.f : __uint_as_float(u[j + 2 * q]) * p.alpha;
+                            float u1 = zero ? 0.f : __uint_as_float(u[j + 2 * q + 1]) * p.alpha;
+                            pg[q] = pack_bf16(g0, g1);
+                            pu[q] = pack_bf16(u0, u1);
+                            __nv_bfloat162 gb = *reinterpret_cast<__nv_bfloat162*>(&pg[q]);
+                            __nv_bfloat162 ub = *reinterpret_cast<__nv_bfloat162*>(&pu[q]);
+                            float2 gf = __bfloat1622float2(gb), uf = __bfloat1622float2(ub);
+                            float a0 = gf.x / (1.f + __expf(-gf.x)) * uf.x;
+                            float a1 = gf.y / (1.f + __expf(-gf.y)) * uf.y;
+                            o[q] = pack_bf16(a0, a1);
+                        }
+                        *reinterpret_cast<uint4*>(out + j) = make_uint4(o[0], o[1], o[2], o[3]);
+                        if (aux) {
+                            *reinterpret_cast<uint4*>(aux + j) =
+                                make_uint4(pg[0], pg[1], pg[2], pg[3]);
+                            *reinterpret_cast<uint4*>(aux + p.swiglu_f + j) =
+                                make_uint4(pu[0], pu[1], pu[2], pu[3]);
+                        }
+                    }
+                }
+            }
+        }
+    } else {
+#pragma unroll 1
+        for (int c = 0; c < kBlockN; c += 32) {
+            if (c >= w.n_valid) break;  // uniform across the warp
+            uint32_t r[32];
+            tmem_ld_32x32(t_row + c, r);
+            tmem_ld_wait();
+            if (!row_ok) continue;
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = zero ? 0.f : __uint_as_float(r[j]) * p.alpha;
+            if (p.epi == kEpiStoreBf16 || p.epi == kEpiAccumBf16) {
+                void* cbase = p.rs_ranks > 1 ? p.c_peers[w.pad0] : p.C;   // owner's staging area or C
+                __nv_bfloat16* out =
+                    reinterpret_cast<__nv_bfloat16*>(cbase) + grow * p.ldc + w.c_col + c;
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    if (c + j + 8 <= w.n_valid) {
+                        if (p.epi == kEpiAccumBf16) {
+                            uint4 old = *reinterpret_cast<const uint4*>(out + j);
+                            const __nv_bfloat162* ob =
+                                reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                float2 f = __bfloat1622float2(ob[q]);
+                                v[j + 2 * q] += f.x;
+                                v[j + 2 * q + 1] += f.y;
+                            }
+                        }
+                        *reinterpret_cast<uint4*>(out + j) =
+                            make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
+                                       pack_bf16(v[j + 4], v[j + 5]),
+                                       pack_bf16(v[j + 6], v[j + 7]));
+                    }
+                }
+            } else {
+                float* out = reinterpret_cast<float*>(p.C) + grow * p.ldc + w.c_col + c;
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    if (c + j + 4 <= w.n_valid) {
+                        float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        if (p.epi == kEpiAccumF32) {
+                            float4 old = *reinterpret_cast<const float4*>(out + j);
+                            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                        }
+                        *reinterpret_cast<float4*>(out + j) = o;
+                    }
+                }
+            }
+        }
+    }
+}
+
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -258,106 +363,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (!mbar_wait(smem_u32(&bar_tfull[acc]), acc_phase, &abort_flag, p.status)) break;
             tc_fence_after();
             const uint32_t t_row = tmem_base + acc * kBlockN + (uint32_t(quarter * 32) << 16);
-            const bool row_ok = row_in_tile < w.m_valid;
-            const long long grow = (long long)w.c_row + row_in_tile;
-            const bool zero = (w.k_iters == 0);
-            if (p.epi == kEpiSwiglu) {
-#pragma unroll 1
-                for (int c = 0; c < 128; c += 32) {
-                    uint32_t g[32], u[32];
-                    tmem_ld_32x32(t_row + c, g);
-                    tmem_ld_32x32(t_row + 128 + c, u);
-                    tmem_ld_wait();
-                    if (row_ok) {
-                        __nv_bfloat16* out =
-                            reinterpret_cast<__nv_bfloat16*>(p.C) + grow * p.ldc + w.c_col + c;
-                        __nv_bfloat16* aux =
-                            p.aux ? reinterpret_cast<__nv_bfloat16*>(p.aux) + grow * p.ld_aux +
-                                        w.c_col + c
-                                  : nullptr;
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            if (c + j + 8 <= w.n_valid) {
-                                uint32_t o[4], pg[4], pu[4];
-#pragma unroll
-                                for (int q = 0; q < 4; ++q) {
-                                    // round the pre-activations to bf16 first so a later
-                                    // recomputation from the saved copy sees the same values
-                                    float g0 = zero ? 0.f : __uint_as_float(g[j + 2 * q]) * p.alpha;
-                                    float g1 = zero ? 0.f : __uint_as_float(g[j + 2 * q + 1]) * p.alpha;
-                                    float u0 = zero ? 0.f : __uint_as_float(u[j + 2 * q]) * p.alpha;
-                                    float u1 = zero ? 0.f : __uint_as_float(u[j + 2 * q + 1]) * p.alpha;
-                                    pg[q] = pack_bf16(g0, g1);
-                                    pu[q] = pack_bf16(u0, u1);
-                                    __nv_bfloat162 gb = *reinterpret_cast<__nv_bfloat162*>(&pg[q]);
-                                    __nv_bfloat162 ub = *reinterpret_cast<__nv_bfloat162*>(&pu[q]);
-                                    float2 gf = __bfloat1622float2(gb), uf = __bfloat1622float2(ub);
-                                    float a0 = gf.x / (1.f + __expf(-gf.x)) * uf.x;
-                                    float a1 = gf.y / (1.f + __expf(-gf.y)) * uf.y;
-                                    o[q] = pack_bf16(a0, a1);
-                                }
-                                *reinterpret_cast<uint4*>(out + j) = make_uint4(o[0], o[1], o[2], o[3]);
-                                if (aux) {
-                                    *reinterpret_cast<uint4*>(aux + j) =
-                                        make_uint4(pg[0], pg[1], pg[2], pg[3]);
-                                    *reinterpret_cast<uint4*>(aux + p.swiglu_f + j) =
-                                        make_uint4(pu[0], pu[1], pu[2], pu[3]);
-                                }
-                            }
-                        }
-                    }
-                }
-            } else {
-#pragma unroll 1
-                for (int c = 0; c < kBlockN; c += 32) {
-                    if (c >= w.n_valid) break;  // uniform across the warp
-                    uint32_t r[32];
-                    tmem_ld_32x32(t_row + c, r);
-                    tmem_ld_wait();
-                    if (!row_ok) continue;
-                    float v[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = zero ? 0.f : __uint_as_float(r[j]) * p.alpha;
-                    if (p.epi == kEpiStoreBf16 || p.epi == kEpiAccumBf16) {
-                        void* cbase = p.rs_ranks > 1 ? p.c_peers[w.pad0] : p.C;   // owner's staging area or C
-                        __nv_bfloat16* out =
-                            reinterpret_cast<__nv_bfloat16*>(cbase) + grow * p.ldc + w.c_col + c;
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            if (c + j + 8 <= w.n_valid) {
-                                if (p.epi == kEpiAccumBf16) {
-                                    uint4 old = *reinterpret_cast<const uint4*>(out + j);
-                                    const __nv_bfloat162* ob =
-                                        reinterpret_cast<const __nv_bfloat162*>(&old);
-#pragma unroll
-                                    for (int q = 0; q < 4; ++q) {
-                                        float2 f = __bfloat1622float2(ob[q]);
-                                        v[j + 2 * q] += f.x;
-                                        v[j + 2 * q + 1] += f.y;
-                                    }
-                                }
-                                *reinterpret_cast<uint4*>(out + j) =
-                                    make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
-                                               pack_bf16(v[j + 4], v[j + 5]),
-                                               pack_bf16(v[j + 6], v[j + 7]));
-                            }
-                        }
-                    } else {
-                        float* out = reinterpret_cast<float*>(p.C) + grow * p.ldc + w.c_col + c;
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            if (c + j + 4 <= w.n_valid) {
-                                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                                if (p.epi == kEpiAccumF32) {
-                                    float4 old = *reinterpret_cast<const float4*>(out + j);
-                                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                                }
-                                *reinterpret_cast<float4*>(out + j) = o;
-                            }
-                        }
-                    }
-                }
-            }
+            epilogue_tile(p, w, t_row, row_in_tile);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[acc]));

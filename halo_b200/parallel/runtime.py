@@ -148,7 +148,7 @@ class ParallelRuntime:
         return experts
 
     @classmethod
-    def for_expert_parallel(cls, world: int, device, group=None, n_lanes: int = 2) -> "ParallelRuntime":
+    def for_expert_parallel(cls, world: int, device, group=None, n_lanes: int = 1) -> "ParallelRuntime":
         """EP over every rank of ``group`` (default: the job); the non-expert parameters are replicated
         over the same ranks."""
         group = group if group is not None else dist.group.WORLD
