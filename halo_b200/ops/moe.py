@@ -204,9 +204,22 @@ def _alloc(transport, shape, dtype, dev):
     return t
 
 
-def _tile_list(state: RoutingState, kind: str, **kw):
+_PAIR_ENABLED = None
+
+
+def _pair_ok(k_dim: int, swiglu: bool) -> int:
+    """Which GEMM kernel runs a grouped product. On the 30B-A3B expert shapes the CTA-pair form (256-row tiles)
+    shortens the kernels themselves by only 1-5 % and the step as a whole measured no faster, so grouped products
+    stay on the single-CTA kernel unless HALO_GEMM_PAIR=2 forces the pair form everywhere."""
+    global _PAIR_ENABLED
+    if _PAIR_ENABLED is None:
+        _PAIR_ENABLED = int(_lib.lib().halo_gemm_pair_enabled())
+    return int(_PAIR_ENABLED == 2 and not swiglu)
+
+
+def _tile_list(state: RoutingState, kind: str, pair: int = 0, **kw):
     """Device tile list for one grouped product shape, cached per routing state."""
-    key = (kind, tuple(sorted(kw.items())))
+    key = (kind, pair, tuple(sorted(kw.items())))
     hit = state.lists.get(key)
     if hit is not None:
         return hit
@@ -224,19 +237,21 @@ def _tile_list(state: RoutingState, kind: str, **kw):
         _lib.check(L.halo_plan_grouped_m(
             _lib.ptr(state.seg_start), _lib.ptr(state.seg_rows), _lib.c_int(state.n_local), _lib.c_int(kw["n_cols"]),
             _lib.c_int(kw["k_dim"]), _lib.c_int(kw["b_mn_stride"]), _lib.c_int(kw["b_k_stride"]),
-            _lib.c_int(kw["swiglu_f"]), _lib.ptr(lst), _lib.ptr(count), _lib.c_int(max_items), s), "halo_plan_grouped_m")
+            _lib.c_int(kw["swiglu_f"]), _lib.ptr(lst), _lib.ptr(count), _lib.c_int(max_items), s, _lib.c_int(pair)),
+            "halo_plan_grouped_m")
     else:
         tiles = ((kw["m_dim"] + 127) // 128) * ((kw["n_dim"] + 255) // 256)
         max_items = tiles * state.n_local
         lst = torch.empty(max_items * wb, dtype=torch.uint8, device=dev)
         _lib.check(L.halo_plan_grouped_k(
             _lib.ptr(state.seg_start), _lib.ptr(state.seg_rows), _lib.c_int(state.n_local), _lib.c_int(kw["m_dim"]),
-            _lib.c_int(kw["n_dim"]), _lib.ptr(lst), _lib.ptr(count), _lib.c_int(max_items), s), "halo_plan_grouped_k")
+            _lib.c_int(kw["n_dim"]), _lib.ptr(lst), _lib.ptr(count), _lib.c_int(max_items), s, _lib.c_int(pair)),
+            "halo_plan_grouped_k")
     state.lists[key] = (lst, count)
     return lst, count
 
 
-def _gemm_list(a, b2d, c, lst_cnt, a_mn, b_mn, epi, aux=None, swiglu_f=0, alpha=1.0):
+def _gemm_list(a, b2d, c, lst_cnt, a_mn, b_mn, epi, aux=None, swiglu_f=0, alpha=1.0, pair=0):
     lst, cnt = lst_cnt
     L = _lib.lib()
     rc = L.halo_gemm_bf16_list(
@@ -244,7 +259,7 @@ def _gemm_list(a, b2d, c, lst_cnt, a_mn, b_mn, epi, aux=None, swiglu_f=0, alpha=
         _lib.ptr(b2d), _lib.c_ll(b2d.shape[0]), _lib.c_ll(b2d.shape[1]), _lib.c_ll(b2d.stride(0)),
         _lib.ptr(c), _lib.ptr(aux), _lib.c_ll(c.stride(0)), _lib.c_ll(aux.stride(0) if aux is not None else 0),
         _lib.c_int(a_mn), _lib.c_int(b_mn), _lib.c_int(epi), _lib.c_float(alpha), _lib.c_int(swiglu_f),
-        _lib.ptr(lst), _lib.ptr(cnt), _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr(a.device),
+        _lib.ptr(lst), _lib.ptr(cnt), _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr(a.device), _lib.c_int(pair),
     )
     _lib.check(rc, "halo_gemm_bf16_list")
 
@@ -264,8 +279,9 @@ def grouped_swiglu_ffn_fwd(state: RoutingState, x_rows, w_gate_up, w_down, save_
 
 def grouped_down_fwd(state: RoutingState, act, w_down, out_rows):
     E, H, F = w_down.shape
-    lst2 = _tile_list(state, "m", n_cols=H, k_dim=F, b_mn_stride=H, b_k_stride=0, swiglu_f=0)
-    _gemm_list(act, w_down.reshape(E * H, F), out_rows, lst2, 0, 0, EPI_STORE_BF16)
+    pair = _pair_ok(F, False)
+    lst2 = _tile_list(state, "m", pair, n_cols=H, k_dim=F, b_mn_stride=H, b_k_stride=0, swiglu_f=0)
+    _gemm_list(act, w_down.reshape(E * H, F), out_rows, lst2, 0, 0, EPI_STORE_BF16, pair=pair)
     return out_rows
 
 
@@ -371,8 +387,9 @@ class _MoEExperts(torch.autograd.Function):
         transport.barrier()
         # 2. unscaled activation gradient: dact_u = dout_rows W_down
         dact = _alloc(transport, (cap, F), torch.bfloat16, dev)
-        lst = _tile_list(state, "m", n_cols=F, k_dim=H, b_mn_stride=0, b_k_stride=H, swiglu_f=0)
-        _gemm_list(dy, w_down.reshape(E_local * H, F), dact, lst, 0, 1, EPI_STORE_BF16)
+        pair = _pair_ok(H, False)
+        lst = _tile_list(state, "m", pair, n_cols=F, k_dim=H, b_mn_stride=0, b_k_stride=H, swiglu_f=0)
+        _gemm_list(dy, w_down.reshape(E_local * H, F), dact, lst, 0, 1, EPI_STORE_BF16, pair=pair)
         # 3. SwiGLU backward with the routing weight folded in: dpre = w * swiglu'(pre) dact_u, act_w = w * act,
         #    dwrow = <dact_u, act> (= <dout, expert output>, without ever forming the expert output)
         dwrow = transport.buffer("dwrow", cap, 1, torch.float32, dev)
@@ -383,8 +400,9 @@ class _MoEExperts(torch.autograd.Function):
                                               _lib.c_int(F), _lib.c_int(cap), s), "halo_swiglu_bwd_weighted")
         # 4. input gradient rows first: dx_rows = dpre W_gate_up
         dx_rows = transport.buffer("dx_rows", cap, H, torch.bfloat16, dev)
-        lst = _tile_list(state, "m", n_cols=H, k_dim=F2, b_mn_stride=0, b_k_stride=F2, swiglu_f=0)
-        _gemm_list(dpre, w_gate_up.reshape(E_local * F2, H), dx_rows, lst, 0, 1, EPI_STORE_BF16)
+        pair = _pair_ok(F2, False)
+        lst = _tile_list(state, "m", pair, n_cols=H, k_dim=F2, b_mn_stride=0, b_k_stride=F2, swiglu_f=0)
+        _gemm_list(dpre, w_gate_up.reshape(E_local * F2, H), dx_rows, lst, 0, 1, EPI_STORE_BF16, pair=pair)
         dx = _alloc(transport, (T, H), torch.bfloat16, dev)
         dw = _alloc(transport, (T, k), torch.float32, dev)
         pdx, pdw = transport.peer_table(dx_rows), transport.peer_table(dwrow)
@@ -402,10 +420,12 @@ class _MoEExperts(torch.autograd.Function):
         def weight_grads():
             # 5. dW_down[e] = dout_e^T (w * act)_e ; dW_gate_up[e] = dpre_e^T x_e
             dw_down = _alloc(transport, tuple(w_down.shape), w_down.dtype, dev)
-            _gemm_list(dy, act_w, dw_down.reshape(E_local * H, F), _tile_list(state, "k", m_dim=H, n_dim=F), 1, 1, EPI_STORE_BF16)
+            pk = _pair_ok(4096, False)      # the reduction runs over an expert's rows: long
+            _gemm_list(dy, act_w, dw_down.reshape(E_local * H, F), _tile_list(state, "k", pk, m_dim=H, n_dim=F), 1, 1,
+                       EPI_STORE_BF16, pair=pk)
             dw_gate_up = _alloc(transport, tuple(w_gate_up.shape), w_gate_up.dtype, dev)
-            _gemm_list(dpre, recv_x, dw_gate_up.reshape(E_local * F2, H), _tile_list(state, "k", m_dim=F2, n_dim=H), 1, 1,
-                       EPI_STORE_BF16)
+            _gemm_list(dpre, recv_x, dw_gate_up.reshape(E_local * F2, H), _tile_list(state, "k", pk, m_dim=F2, n_dim=H), 1, 1,
+                       EPI_STORE_BF16, pair=pk)
             return dw_gate_up, dw_down
 
         side = transport.side_stream(dev) if transport.n_ranks > 1 else None
