@@ -32,6 +32,8 @@ REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)
 
 BASELINE_TOK_S_PER_GPU = 19326.0  # reference, Qwen3.6-35B-A3B EP8 64k packed, 8x B300 (published)
+# published tokens/s/GPU of the reference for the other model presets (8x B300): Qwen3.5-9B 64k packed DP8
+BASELINES = {"moe-30b-a3b": BASELINE_TOK_S_PER_GPU, "dense-9b": 17206.0}
 
 
 def parse_args():
@@ -204,11 +206,13 @@ def main() -> int:
     opt_state = args.optimizer_state
     if opt_state == "auto":
         total_mem = torch.cuda.get_device_properties(dev).total_memory
-        rows_cap = int(1.5 * args.seq_len * cfg.num_experts_per_tok) if world > 1 else 0
+        rows_cap = int(1.5 * args.seq_len * cfg.num_experts_per_tok) if world > 1 and cfg.is_moe else 0
         transport_bytes = 4 * rows_cap * cfg.hidden_size * 2
         need = state_bytes + transport_bytes + int(args.activation_reserve_gb * 1e9)
         opt_state = "host" if need > 0.90 * total_mem else "device"
 
+    if transport is not None and not cfg.is_moe:
+        transport = None          # a dense model: data parallel only, nothing to route
     if transport is not None:
         transport.configure(max_tokens=args.seq_len, top_k=cfg.num_experts_per_tok, hidden=cfg.hidden_size,
                             n_local_experts=cfg.num_experts // world)
@@ -290,9 +294,10 @@ def main() -> int:
     e2e = tokens / (ms_e2e / 1e3)
     peak_gib = torch.cuda.max_memory_allocated(dev) / 2**30
     if rank == 0:
-        par = f"ep{world}" + (f"+dp{world}" if world > 1 else "") + (f"+ep_lanes{args.ep_lanes}" if world > 1 and args.ep_lanes > 1 else "") + ("+fused_zero" if parallel is not None and parallel.fused_optimizer is not None else "") + ("+host_optimizer_state" if getattr(opt, "state_bytes_on_host", lambda: 0)() > 0 else "")
+        par = (f"ep{world}" if cfg.is_moe else "") + (f"+dp{world}" if world > 1 else "") + (f"+ep_lanes{args.ep_lanes}" if world > 1 and args.ep_lanes > 1 else "") + ("+fused_zero" if parallel is not None and parallel.fused_optimizer is not None else "") + ("+host_optimizer_state" if getattr(opt, "state_bytes_on_host", lambda: 0)() > 0 else "")
         line = {
-            "metric": "train tokens/s, 30B-A3B MoE, packed 64k rows (whole job)",
+            "metric": ("train tokens/s, 30B-A3B MoE, packed 64k rows (whole job)" if args.model == "moe-30b-a3b"
+                       else f"train tokens/s, {args.model}, packed rows (whole job)"),
             "value": round(value, 1),
             "unit": "tokens/s",
             "n_gpus": world,
@@ -301,7 +306,7 @@ def main() -> int:
             "ms_per_step": round(ms_dev / args.steps, 2),
             "higher_is_better": True,
             "scaling": "weak",
-            "vs_baseline": round(value / world / BASELINE_TOK_S_PER_GPU, 4),
+            "vs_baseline": round(value / world / BASELINES.get(args.model, BASELINE_TOK_S_PER_GPU), 4),
             "dtype": "bf16",
             "data": "synthetic: uniform-random token ids, packed documents, random-init weights",
             "impl": "halo_b200",
