@@ -65,12 +65,18 @@ def save_model(model, directory: str, is_writer: bool | None = None, save_dtype:
             remove_stale_staged(directory)
             writer = StreamingShardWriter(directory, max_shard_bytes, save_dtype)
     # 1. non-expert tensors (replicated: taken from the writer's copy)
-    with guard.catch():
-        for name, p in model.named_parameters():
-            if getattr(p, "is_expert", False):
-                continue
+    tp = getattr(model, "tensor_parallel", None)
+    for name, p in model.named_parameters():
+        if getattr(p, "is_expert", False):
+            continue
+        t_full = p.detach()
+        if tp is not None and getattr(p, "tp_kind", None) is not None:
+            from halo_b200.parallel.tensor_parallel import gather_full_weight
+
+            t_full = gather_full_weight(p.tp_kind, t_full, cfg, tp)     # collective: every rank takes part
+        with guard.catch():
             if writer is not None and is_writer:
-                for hub, t in runtime_to_hub(name, p.detach(), cfg, first_layer).items():
+                for hub, t in runtime_to_hub(name, t_full, cfg, first_layer).items():
                     writer.add(hub, t)
     # 2. expert banks, one layer at a time
     for name, p in model.named_parameters():

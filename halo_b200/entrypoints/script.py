@@ -61,6 +61,8 @@ def build_runtime(pc, device, group=None):
     from halo_b200.parallel.runtime import ParallelRuntime
 
     group = group if group is not None else dist.group.WORLD
+    if pc.tp_size > 1 or pc.cp_size > 1:
+        return _token_cutting_runtime(pc, device, group)
     if pc.ep_size == pc.world_size and device.type == "cuda":
         return ParallelRuntime.for_expert_parallel(pc.world_size, device, group=group)
     if pc.ep_size > 1:
@@ -70,15 +72,66 @@ def build_runtime(pc, device, group=None):
     return ParallelRuntime(device, dp_group=group)
 
 
+def _token_cutting_runtime(pc, device, group):
+    """Tensor or context parallelism (both cut a row's tokens over consecutive ranks), optionally times data
+    parallelism. Every rank creates every subgroup, in the same order."""
+    from halo_b200.parallel.runtime import ParallelRuntime
+
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    width = pc.tp_size if pc.tp_size > 1 else pc.cp_size
+    if pc.tp_size > 1 and pc.cp_size > 1:
+        raise ValueError("tensor and context parallelism together are not wired into the entry points")
+    if pc.ep_size > 1:
+        raise ValueError("expert parallelism together with tensor / context parallelism is not wired into the entry points")
+    ranks = [dist.get_global_rank(group, r) for r in range(world)] if group is not dist.group.WORLD else list(range(world))
+    mine = replica = None
+    for b in range(world // width):                       # blocks of consecutive ranks share a row
+        g = dist.new_group(ranks[b * width:(b + 1) * width])
+        if b == rank // width:
+            mine = g
+    for j in range(width):                                # ranks with the same position hold the same weight slices
+        g = dist.new_group(ranks[j::width])
+        if j == rank % width:
+            replica = g
+    return {"group": group, "axis_group": mine, "replica_group": replica if world > width else None,
+            "kind": "tp" if pc.tp_size > 1 else "cp", "device": device, "runtime_cls": ParallelRuntime}
+
+
+def finish_token_cutting_runtime(spec: dict, cfg, max_tokens: int):
+    """Second half of :func:`_token_cutting_runtime`, once the model config and the row length are known."""
+    from halo_b200.parallel.context_parallel import ContextParallel
+    from halo_b200.parallel.tensor_parallel import TensorParallel
+
+    tp = cp = None
+    if spec["kind"] == "tp":
+        tp = TensorParallel(spec["axis_group"], spec["device"], hidden=cfg.hidden_size, max_tokens=max_tokens)
+    else:
+        cp = ContextParallel(spec["axis_group"], spec["device"], cfg, max_tokens)
+    return spec["runtime_cls"](spec["device"], dp_group=spec["group"], tensor_parallel=tp, context_parallel=cp,
+                               tp_replica_group=spec["replica_group"] if tp is not None else None)
+
+
 def load_policy_model(model_args, pc, device, runtime, gradient_checkpointing=True, max_tokens=0):
     from halo_b200.checkpoint.load import from_pretrained
     from halo_b200.models.config import PRESETS, ModelConfig
     from halo_b200.models.qwen3 import build_model
 
     dtype = torch.bfloat16 if model_args.torch_dtype == "bfloat16" and device.type == "cuda" else torch.float32
-    transport = runtime.transport if runtime is not None else None
     cfg = PRESETS[model_args.model_preset]() if model_args.init_from_scratch else ModelConfig.load(model_args.model_name_or_path)
     reject_model_layout(pc, cfg)
+    if isinstance(runtime, dict):          # tensor / context parallelism: needs the model's sizes to finish
+        runtime = finish_token_cutting_runtime(runtime, cfg, max_tokens)
+        if not model_args.init_from_scratch and runtime.tensor_parallel is not None:
+            raise NotImplementedError("loading a checkpoint into tensor-parallel slices is not built: train from a preset "
+                                      "or load without tensor parallelism")
+        model = build_model(cfg, device=device, dtype=dtype, gradient_checkpointing=gradient_checkpointing,
+                            tensor_parallel=runtime.tensor_parallel) if model_args.init_from_scratch else \
+            from_pretrained(model_args.model_name_or_path, device=device, dtype=dtype,
+                            gradient_checkpointing=gradient_checkpointing)
+        model.context_parallel = runtime.context_parallel
+        model.parallel_runtime = runtime
+        return model
+    transport = runtime.transport if runtime is not None else None
     if transport is not None and hasattr(transport, "configure") and cfg.is_moe:
         transport.configure(max_tokens=max_tokens, top_k=cfg.num_experts_per_tok, hidden=cfg.hidden_size,
                             n_local_experts=cfg.num_experts // transport.n_ranks)

@@ -17,6 +17,7 @@ def main(argv=None):
     runtime = build_runtime(pc, device)
     model = load_policy_model(model_args, pc, device, runtime, train_args.gradient_checkpointing,
                               max_tokens=data_args.packed_row_length)
+    runtime = getattr(model, "parallel_runtime", runtime)      # tensor / context parallelism finish their runtime there
     if kd_args.distill_mode == "teacher" and kd_args.teacher_model_name_or_path:
         t_args = ModelArguments(model_name_or_path=kd_args.teacher_model_name_or_path, torch_dtype=model_args.torch_dtype)
         teacher = load_policy_model(t_args, pc, device, runtime, False, max_tokens=data_args.packed_row_length)

@@ -65,6 +65,7 @@ def main(argv=None):
     runtime = build_runtime(pc, device, group=roles.trainer_group if roles else None)
     model = load_policy_model(model_args, pc, device, runtime, train_args.gradient_checkpointing,
                               max_tokens=grpo_args.token_budget)
+    runtime = getattr(model, "parallel_runtime", runtime)      # tensor / context parallelism finish their runtime there
     if data_args.dataset_path:
         source = rollouts_from_jsonl(data_args.dataset_path, grpo_args.num_generations)
     else:

@@ -17,6 +17,7 @@ def main(argv=None):
     runtime = build_runtime(pc, device)
     model = load_policy_model(model_args, pc, device, runtime, train_args.gradient_checkpointing,
                               max_tokens=data_args.packed_row_length)
+    runtime = getattr(model, "parallel_runtime", runtime)      # tensor / context parallelism finish their runtime there
     needs_ref = pref_args.preference_loss in ("dpo", "ipo", "kto") and not pref_args.reference_free
     ref_model = copy.deepcopy(model).eval() if needs_ref else None   # the frozen reference starts as the policy
     batches = build_preference_batches(data_args, load_tokenizer(model_args), pc.data_parallel_rank,

@@ -17,6 +17,7 @@ def main(argv=None):
     runtime = build_runtime(pc, device)
     model = load_policy_model(model_args, pc, device, runtime, train_args.gradient_checkpointing,
                               max_tokens=data_args.packed_row_length)
+    runtime = getattr(model, "parallel_runtime", runtime)      # tensor / context parallelism finish their runtime there
     head = SequenceHead(model.cfg.hidden_size, rw_args.num_labels, dtype=torch.float32, device=device)
     batches = build_preference_batches(data_args, load_tokenizer(model_args), pc.data_parallel_rank,
                                        pc.data_parallel_size, model.cfg.vocab_size)

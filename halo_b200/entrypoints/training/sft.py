@@ -16,6 +16,7 @@ def main(argv=None):
     runtime = build_runtime(pc, device)
     model = load_policy_model(model_args, pc, device, runtime, train_args.gradient_checkpointing,
                               max_tokens=data_args.packed_row_length * train_args.per_device_train_batch_size)
+    runtime = getattr(model, "parallel_runtime", runtime)      # tensor / context parallelism finish their runtime there
     tokenizer = load_tokenizer(model_args)
     batches = build_sft_batches(data_args, tokenizer, pc.data_parallel_rank, pc.data_parallel_size, model.cfg.vocab_size)
     trainer = SFTTrainer(model, train_args, batches, device=device, parallel=runtime,

@@ -125,8 +125,16 @@ class SymmetricTransport:
 class ParallelRuntime:
     """Groups and per-step reductions of one run."""
 
-    def __init__(self, device, dp_group=None, ep_group=None, expert_replica_group=None, transport=None):
+    def __init__(self, device, dp_group=None, ep_group=None, expert_replica_group=None, transport=None,
+                 tensor_parallel=None, context_parallel=None, tp_replica_group=None):
+        """``dp_group``: every rank that holds a copy of the replicated parameters and sees its own tokens (data,
+        context and tensor-parallel ranks alike: all three cut the tokens). ``tensor_parallel`` /
+        ``context_parallel``: the objects the model carries when those axes are on. ``tp_replica_group``: ranks
+        with the same tensor-parallel rank (they hold the same weight slices); None when tp spans the job."""
         self.device = torch.device(device)
+        self.tensor_parallel = tensor_parallel
+        self.context_parallel = context_parallel
+        self.tp_replica_group = tp_replica_group
         self.dp_group = dp_group
         self.ep_group = ep_group
         self.expert_replica_group = expert_replica_group
@@ -162,14 +170,38 @@ class ParallelRuntime:
         return t.clamp_min(1.0)
 
     # ---- gradients ---------------------------------------------------------------------------
-    @staticmethod
-    def split_params(model):
+    def split_params(self, model):
+        """(expert-sharded, replicated) parameters that have a gradient; tensor-parallel slices are a third
+        kind, returned by :meth:`sliced_params`. Without expert parallelism the expert banks are replicated like
+        everything else."""
         experts, shared = [], []
         for p in model.parameters():
-            if p.grad is None:
+            if p.grad is None or getattr(p, "tp_kind", None) is not None:
                 continue
-            (experts if getattr(p, "is_expert", False) else shared).append(p)
+            (experts if getattr(p, "is_expert", False) and self.ep_world > 1 else shared).append(p)
         return experts, shared
+
+    @staticmethod
+    def sliced_params(model):
+        return [p for p in model.parameters() if p.grad is not None and getattr(p, "tp_kind", None) is not None]
+
+    def slice_batch(self, batch):
+        """This rank's part of a packed row under context or tensor parallelism (both cut the tokens; positions and
+        document boundaries of the whole row stay available to attention)."""
+        from halo_b200.data.packing import PackedBatch
+        from halo_b200.parallel.context_parallel import chunk_bounds
+
+        if self.context_parallel is not None:
+            from halo_b200.parallel.context_parallel import slice_batch
+
+            return slice_batch(batch, self.context_parallel.rank, self.context_parallel.size)
+        if self.tensor_parallel is not None:
+            tp = self.tensor_parallel
+            lo, hi = chunk_bounds(batch.n_tokens, tp.size, tp.rank)
+            labels = batch.labels[lo:hi]
+            return PackedBatch(batch.input_ids[lo:hi], batch.position_ids, labels, batch.cu_seqlens,
+                               int((labels != -100).sum()))
+        return batch
 
     def sync_gradients(self, model) -> None:
         """Sum the replicated parameters' gradients over the data-parallel group (the loss is already
@@ -190,6 +222,9 @@ class ParallelRuntime:
         if self.expert_replica_group is not None and experts:
             for p in experts:
                 dist.all_reduce(p.grad, group=self.expert_replica_group)
+        if self.tp_replica_group is not None:
+            for p in self.sliced_params(model):       # a slice saw every token of its replica's rows already
+                dist.all_reduce(p.grad, group=self.tp_replica_group)
 
     def global_grad_sq_norm(self, model, grad_norm) -> None:
         """total_sq = ||replicated grads||^2 (counted once) + sum over EP ranks of ||expert grads||^2."""
@@ -197,4 +232,11 @@ class ParallelRuntime:
         grad_norm.accumulate([p.grad for p in experts], first=True)
         if self.ep_world > 1:
             dist.all_reduce(grad_norm.total_sq, group=self.ep_group)
+        sliced = self.sliced_params(model)
+        if sliced:
+            # every tensor-parallel rank holds a different slice: sum their squares over the tensor-parallel group
+            tmp = grad_norm.total_sq.clone()
+            grad_norm.accumulate([p.grad for p in sliced], first=True)
+            dist.all_reduce(grad_norm.total_sq, group=self.tensor_parallel.group)
+            grad_norm.total_sq.add_(tmp)
         grad_norm.accumulate([p.grad for p in shared], first=False)

@@ -111,6 +111,8 @@ class TrainEngine:
     # ---- the step -------------------------------------------------------------------------
     def train_step(self, batch: PackedBatch, accumulate: bool = False) -> StepOutput:
         """One micro-batch forward/backward; unless ``accumulate``, also clip + optimizer step."""
+        if self.parallel is not None and (self.parallel.context_parallel is not None or self.parallel.tensor_parallel is not None):
+            batch = self.parallel.slice_batch(batch)      # this rank's tokens of the row, cut before the copy
         dbatch = self.to_device(batch)
         normalizer = self.global_scored_tokens(batch)
         loss = self.compute_loss(dbatch, normalizer)
