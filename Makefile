@@ -1,0 +1,32 @@
+# Common entry points. GPU targets expect a B200 (sm_100a).
+PY ?= python
+NPROC ?= 8
+
+.PHONY: build test-cpu test-gpu test-multigpu bench bench-multi kernel-bench train clean
+
+build:            ## compile halo_b200/lib/libhalo_b200.so for sm_100a
+	$(PY) -c "import __graft_entry__ as g; g.build()"
+
+test-cpu:         ## everything that runs without a GPU (gloo ranks for the multi-process paths)
+	$(PY) -m pytest tests -q -m "not gpu"
+
+test-gpu: build   ## kernel numerics and model tests on one GPU
+	$(PY) -m pytest tests -q -m gpu
+
+test-multigpu: build   ## peer-memory paths on two GPUs
+	$(PY) -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 tests/multigpu/check_two_ranks.py
+
+bench: build      ## flagship benchmark on one GPU
+	$(PY) bench.py
+
+bench-multi: build
+	$(PY) -m torch.distributed.run --nnodes=1 --nproc-per-node $(NPROC) --master-addr 127.0.0.1 bench.py --gpus $(NPROC)
+
+kernel-bench: build
+	$(PY) benchmarks/kernels.py
+
+train:            ## make train METHOD=sft CONFIG=examples/sft_tiny_moe.yaml NPROC=1
+	$(PY) -m halo_b200.cli launch $(METHOD) $(CONFIG) -n $(NPROC)
+
+clean:
+	rm -f halo_b200/lib/libhalo_b200.so halo_b200/lib/*.o

@@ -63,6 +63,7 @@ class TrainingArguments:
     optim: Literal["adamw_bf16", "adamw_torch", "adamw_bf16_host_state", "muon"] = "adamw_bf16"
     bf16: bool = True
     gradient_checkpointing: bool = True
+    gradient_checkpointing_plan: Literal["full", "auto"] = "full"   # auto: lighter policy where memory allows, planned after step 1
     use_fused_kernels: bool = True
     logging_steps: int = 1
     logging_nan_inf_filter: bool = False

@@ -91,3 +91,41 @@ def test_model_dependent_refusals():
     with pytest.raises(ConfigError, match="without routed experts"):
         reject_model_layout(ParallelismConfig(world_size=8, global_rank=0, ep_size=8), dense_9b_config())
     reject_model_layout(ParallelismConfig(world_size=8, global_rank=0, tp_size=2), dense_9b_config())
+
+
+def test_prepared_dataset_round_trip_and_coordinated_cache(tmp_path):
+    import json
+
+    import numpy as np
+
+    from halo_b200.data import preprocessed as pp
+
+    src = tmp_path / "docs.jsonl"
+    rng = np.random.default_rng(0)
+    with open(src, "w") as f:
+        for _ in range(40):
+            f.write(json.dumps({"input_ids": rng.integers(0, 100, size=int(rng.integers(5, 60))).tolist()}) + "\n")
+    out = str(tmp_path / "prepared")
+    assert pp.main([str(src), out, "--row-len", "128"]) == 0
+    meta = pp.read_metadata(out)
+    rows0, rows1 = pp.load_rows(out, 0, 2, expect_row_len=128), pp.load_rows(out, 1, 2)
+    assert len(rows0) + len(rows1) == meta["n_rows"] and all(r.n_tokens == 128 for r in rows0 + rows1)
+    assert rows0[0].cu_seqlens[0] == 0 and rows0[0].cu_seqlens[-1] == 128
+    import pytest
+
+    with pytest.raises(ValueError, match="packed to 128"):
+        pp.load_rows(out, expect_row_len=256)
+    with pytest.raises(FileNotFoundError):
+        pp.read_metadata(str(tmp_path))
+    calls = []
+
+    def build(d):
+        calls.append(d)
+        open(d + "/artifact", "w").write("x")
+
+    d1 = pp.coordinated_cache(str(tmp_path / "cache"), ["a", 1], build)
+    d2 = pp.coordinated_cache(str(tmp_path / "cache"), ["a", 1], build)
+    d3 = pp.coordinated_cache(str(tmp_path / "cache"), ["a", 1], build, rank=1, wait_seconds=1)     # found: no wait
+    assert d1 == d2 == d3 and len(calls) == 1
+    with pytest.raises(TimeoutError):
+        pp.coordinated_cache(str(tmp_path / "cache"), ["b"], build, rank=1, wait_seconds=0.3, poll_seconds=0.05)

@@ -124,3 +124,32 @@ def test_preference_and_grpo_trainers_step():
                     source, grpo_args=GRPOArguments(num_generations=4, token_budget=64), device="cpu")
     out = g.train()
     assert out["global_step"] == 2 and all(math.isfinite(l["loss"]) for l in out["log_history"])
+
+
+def test_world_metrics_and_small_callbacks():
+    from halo_b200.callbacks.extras import EarlyStopCallback, VariableSchedulerCallback
+    from halo_b200.trainers.metrics import WorldMetrics
+
+    m = WorldMetrics()
+    m.add_sum("tokens", 10)
+    m.add_sum("tokens", torch.tensor(5.0))
+    m.add_mean("loss", 6.0, 3)
+    m.add_mean("loss", 2.0, 1)
+    m.add_fraction("clipped", 1, 4)
+    m.add_max("grad_norm", 2.0)
+    m.add_max("grad_norm", torch.tensor(7.0))
+    out = m.reduce()
+    assert out == {"tokens": 15.0, "loss": 2.0, "clipped": 0.25, "grad_norm": 7.0}
+    assert m.reduce() == {}
+    pts = [(0, 0.1), (100, 0.5)]
+    assert abs(VariableSchedulerCallback.value_at(pts, 50) - 0.3) < 1e-9 and VariableSchedulerCallback.value_at(pts, 500) == 0.5
+
+    class T:
+        class args:
+            max_steps = 100
+        global_step = 7
+
+    es = EarlyStopCallback("eval_loss", patience=2)
+    for v in (1.0, 0.9, 0.95, 0.97):
+        es.on_log(T, {"eval_loss": v})
+    assert T.args.max_steps == 7
