@@ -46,7 +46,7 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=65536)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run reduced)")
     ap.add_argument("--optimizer-state", default="auto", choices=["auto", "device", "host"])
-    ap.add_argument("--activation-reserve-gb", type=float, default=36.0,
+    ap.add_argument("--activation-reserve-gb", type=float, default=30.0,
                     help="device memory kept free of optimizer state for activations, workspaces and staging")
     ap.add_argument("--fused-optimizer", type=int, default=1,
                     help="N > 1: 1 = fused reduce-scatter/AdamW/all-gather kernels for the replicated parameters, "
@@ -208,7 +208,7 @@ def main() -> int:
         total_mem = torch.cuda.get_device_properties(dev).total_memory
         rows_cap = int(1.5 * args.seq_len * cfg.num_experts_per_tok) if world > 1 and cfg.is_moe else 0
         transport_bytes = 4 * rows_cap * cfg.hidden_size * 2
-        need = state_bytes + transport_bytes + int(args.activation_reserve_gb * 1e9)
+        need = state_bytes + transport_bytes + int(max(args.activation_reserve_gb, 36.0) * 1e9)
         opt_state = "host" if need > 0.90 * total_mem else "device"
 
     if transport is not None and not cfg.is_moe:

@@ -7,7 +7,7 @@ from halo_b200.entrypoints.script import (build_runtime, init_training_script, l
 
 @with_distributed_teardown
 def main(argv=None):
-    from halo_b200.callbacks.efficiency import EfficiencyCallback
+    from halo_b200.callbacks.extras import build_callbacks
     from halo_b200.data.datasets import build_sft_batches
     from halo_b200.trainers.sft import SFTTrainer
 
@@ -20,7 +20,8 @@ def main(argv=None):
     tokenizer = load_tokenizer(model_args)
     batches = build_sft_batches(data_args, tokenizer, pc.data_parallel_rank, pc.data_parallel_size, model.cfg.vocab_size)
     trainer = SFTTrainer(model, train_args, batches, device=device, parallel=runtime,
-                         callbacks=[EfficiencyCallback(model.cfg, pc.world_size)],
+                         callbacks=build_callbacks(train_args, model, pc.world_size, pc.global_rank,
+                                                   tokens_per_step=data_args.packed_row_length),
                          parallelism_fingerprint=pc.fingerprint())
     return run_trainer(trainer, train_args)
 
