@@ -79,3 +79,37 @@ def test_linear_autograd():
     yr.backward(gy.float())
     for got, ref in ((y, yr), (x.grad, xr.grad), (w.grad, wr.grad)):
         assert (got.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-3
+
+
+@pytest.mark.parametrize("a_t,b_t", [(False, True), (False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("mnk", [(2048, 1024, 2048), (1000, 520, 1600), (300, 2048, 4096)])
+def test_pair_kernel_shapes(a_t, b_t, mnk):
+    """Long reductions with narrow outputs take the CTA-pair (cta_group::2) kernel; odd sizes exercise the half
+    tiles of the second CTA and the clipped edges."""
+    from halo_b200.ops import _lib
+    from halo_b200.ops.gemm import matmul
+
+    M, N, K = mnk
+    torch.manual_seed(1)
+    a = _rand((K, M) if a_t else (M, K), 0.3)
+    b = _rand((N, K) if b_t else (K, N), 0.3)
+    out = matmul(a, b, a_t=a_t, b_t=b_t)
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+    ref = _ref(a, b, a_t, b_t)
+    err = (out.float() - ref).abs().max().item()
+    assert err <= 2e-2 * ref.abs().max().item() + 1e-3, err
+
+
+def test_every_product_on_the_pair_kernel_in_a_fresh_process():
+    """HALO_GEMM_PAIR=2 routes every dense and grouped product through the pair kernel; the kernel choice is read
+    once per process, so the GEMM and MoE numerics run again in a child process with the switch set."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, HALO_GEMM_PAIR="2")
+    r = subprocess.run([sys.executable, "-m", "pytest", "tests/test_gemm_gpu.py", "tests/test_moe_gpu.py", "-q", "-m", "gpu", "-x",
+                        "-k", "not fresh_process"], cwd=root, env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
