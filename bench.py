@@ -52,6 +52,8 @@ def parse_args():
                     help="N > 1: 1 = fused reduce-scatter/AdamW/all-gather kernels for the replicated parameters, "
                          "0 = NCCL all-reduce + local optimizer (the baseline path)")
     ap.add_argument("--doc-dist", default="chat")
+    ap.add_argument("--host-compute", default="auto", choices=["auto", "0", "1"],
+                    help="update host-resident optimizer state on the host CPU (auto: when a short probe says the CPU keeps up)")
     ap.add_argument("--ep-lanes", type=int, default=0,
                     help="parts an expert-parallel MoE call is cut into so that one part's NVLink transfers overlap another's GEMMs "
                          "(0 or 1 = one part; two parts measured slower on 2 and 4 GPUs and are off by default)")
@@ -228,7 +230,9 @@ def main() -> int:
         free_bytes, _ = torch.cuda.mem_get_info(dev)
         reserve = int(args.activation_reserve_gb * 1e9)
         budget = max(0, free_bytes - 2 * local_params - reserve)
-        opt = HostStateAdamWBF16(named, lr=args.lr, weight_decay=0.01, device_state_budget_bytes=budget)
+        host_compute = {"auto": "auto", "1": True, "0": False}[args.host_compute]
+        opt = HostStateAdamWBF16(named, lr=args.lr, weight_decay=0.01, device_state_budget_bytes=budget,
+                                 host_compute=host_compute)
     else:
         opt = AdamWBF16(named, lr=args.lr, weight_decay=0.01)
     engine = TrainEngine(model, opt, dev, max_grad_norm=1.0, parallel=parallel)
@@ -324,6 +328,8 @@ def main() -> int:
                 "l2": "activations and weights per step are far larger than the 126 MB L2 (no flush needed)",
                 "params_total": counts["total"], "peak_gib": round(peak_gib, 1),
                 "optimizer_state_on_host_gb": round(getattr(opt, "state_bytes_on_host", lambda: 0)() / 1e9, 1),
+                "host_side_update": bool(getattr(opt, "host_compute", False)) and getattr(opt, "state_bytes_on_host", lambda: 0)() > 0,
+                "host_update_rate_gparams_s": round(getattr(opt, "host_rate", 0.0) / 1e9, 2),
             },
             "clocks": clocks,
             "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e / args.steps, 2),

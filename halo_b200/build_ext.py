@@ -59,8 +59,28 @@ def _compile_one(nvcc: str, src: Path, obj: Path, verbose: bool) -> str:
     return proc.stderr
 
 
+HOST_LIB_PATH = LIB_DIR / "libhalo_host.so"
+# no fused multiply-add (the host optimizer reproduces the device kernel bit for bit); AVX2 is the widest vector
+# set every B200 host CPU has
+HOST_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-shared", "-fopenmp", "-mavx2", "-ffp-contract=off", "-fno-math-errno"]
+
+
+def build_host(force: bool = False) -> Path:
+    """The CPU-side library (host optimizer): plain g++ with OpenMP, no CUDA."""
+    LIB_DIR.mkdir(exist_ok=True)
+    sources = sorted(CSRC_DIR.glob("*.cpp"))
+    newest = max((s.stat().st_mtime for s in sources), default=0.0)
+    if sources and (force or not HOST_LIB_PATH.exists() or HOST_LIB_PATH.stat().st_mtime < newest):
+        gxx = shutil.which("g++") or "g++"
+        proc = subprocess.run([gxx, *HOST_FLAGS, *map(str, sources), "-o", str(HOST_LIB_PATH)], capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError(f"g++ failed on the host library:\n{proc.stdout}\n{proc.stderr}")
+    return HOST_LIB_PATH
+
+
 def build(force: bool = False, verbose: bool = False) -> Path:
     """Compile what changed and link the library; returns its path."""
+    build_host(force)
     nvcc = find_nvcc()
     LIB_DIR.mkdir(exist_ok=True)
     obj_dir = LIB_DIR / "obj"

@@ -131,3 +131,20 @@ def raise_on_status(device: torch.device | None = None) -> None:
         names = {1: "a wait inside a kernel ran out of its time budget", 2: "bad argument",
                  3: "a wait on a peer GPU ran out of its time budget", 4: "index out of bounds"}
         raise KernelError(f"kernel status {v}: {names.get(v, 'unknown')}")
+
+
+_HOST_LIB = None
+
+
+def host_lib():
+    """The CPU-side library (``libhalo_host.so``: the host optimizer); built on first use if missing."""
+    global _HOST_LIB
+    if _HOST_LIB is None:
+        from halo_b200.build_ext import HOST_LIB_PATH, build_host
+
+        if not HOST_LIB_PATH.exists():
+            build_host()
+        _HOST_LIB = ctypes.CDLL(str(HOST_LIB_PATH))
+        _HOST_LIB.halo_host_adamw_bf16.restype = ctypes.c_int
+        _HOST_LIB.halo_host_threads.restype = ctypes.c_int
+    return _HOST_LIB

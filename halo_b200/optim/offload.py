@@ -15,6 +15,8 @@ The reference has no counterpart: it shards optimizer state over ranks instead
 from __future__ import annotations
 
 import ctypes
+import threading
+import time
 
 import torch
 
@@ -37,10 +39,45 @@ def _pinned_zeros(numel: int, dtype: torch.dtype) -> torch.Tensor:
     return t
 
 
+def host_update_rate(n: int = 1 << 25) -> float:
+    """Parameters per second of the host-CPU AdamWBF16 on this machine (all cores), from a short run."""
+    L = _lib.host_lib()
+    t = [torch.zeros(n, dtype=torch.bfloat16) for _ in range(4)]
+    u = [ctypes.c_void_p(x.data_ptr()) for x in t]
+    best = 0.0
+    for _ in range(2):
+        t0 = time.perf_counter()
+        L.halo_host_adamw_bf16(u[0], u[1], u[2], u[3], ctypes.c_longlong(n), ctypes.c_ulonglong(1), ctypes.c_ulonglong(2),
+                               ctypes.c_ulonglong(3), ctypes.c_float(0.9), ctypes.c_float(0.999), ctypes.c_float(1e-3),
+                               ctypes.c_float(0.05), ctypes.c_float(1e-8), ctypes.c_float(1.0), ctypes.c_float(1.0),
+                               ctypes.c_int(0), ctypes.c_int(0))
+        best = max(best, n / (time.perf_counter() - t0))
+    return best
+
+
+# The host update moves 4 bytes per parameter over PCIe (gradient out, weight in) instead of 8 (both moments in and
+# out); it pays when the CPU keeps up with the halved transfer: about 27 GB/s per direction with both directions busy.
+HOST_COMPUTE_MIN_RATE = 8.4e9
+
+
 class HostStateAdamWBF16(AdamWBF16):
     def __init__(self, params, *args, host_min_numel: int = HOST_STATE_MIN_NUMEL,
-                 device_state_budget_bytes: int = 0, **kwargs):
+                 device_state_budget_bytes: int = 0, host_compute: bool | str = "auto", **kwargs):
+        """``host_compute``: update the host-resident tensors ON the host CPU (bit-identical C++ kernel; gradient
+        goes out, weight comes back) instead of streaming their moments through the device. ``"auto"`` decides from
+        a short measurement of this machine's CPU."""
         super().__init__(params, *args, **kwargs)
+        if host_compute == "auto":
+            try:
+                self.host_rate = host_update_rate()
+            except Exception:  # noqa: BLE001 - no compiler / library on this machine: keep streaming
+                self.host_rate = 0.0
+            host_compute = self.host_rate >= HOST_COMPUTE_MIN_RATE
+        self.host_compute = bool(host_compute)
+        self._worker = None
+        self._cpu_flags: dict = {}
+        self._g_host = None
+        self._cpu_streams = None
         self.host_min_numel = host_min_numel
         # moments of large tensors stay on the device while this budget lasts (4 bytes per element)
         self.device_budget = int(device_state_budget_bytes)
@@ -86,6 +123,8 @@ class HostStateAdamWBF16(AdamWBF16):
             super()._cuda_step(gi, on_dev, device, gdtype, b1, b2, step_size, bc2_sqrt, eps, wd_factor, step)
         if not on_host:
             return
+        if self.host_compute:
+            return self._host_compute_step(on_host, device, b1, b2, step_size, bc2_sqrt, eps, wd_factor, step)
         L = _lib.lib()
         self._ensure_staging(device, max(p.numel() for _, p, _ in on_host))
         h2d, d2h = self._streams
@@ -127,22 +166,101 @@ class HostStateAdamWBF16(AdamWBF16):
         if self._grad_scale is not None:
             self._grad_scale.record_stream(compute)
 
+    # ---- update on the host CPU ------------------------------------------------------------------------
+    def _host_compute_step(self, on_host, device, b1, b2, step_size, bc2_sqrt, eps, wd_factor, step):
+        """Gradient to the host, AdamWBF16 there (all cores), new weight back; one background thread keeps the
+        copy of tensor i + 1, the update of tensor i and the return of tensor i - 1 going at the same time. The
+        caller returns at once; consumers of a parameter wait in :meth:`wait_ready`."""
+        self.join_host_worker()
+        main = torch.cuda.current_stream(device)
+        # the host needs the clip coefficient and the skip verdict: one read per step, after the norm is final
+        scale = float(self._grad_scale.item()) if self._grad_scale is not None else None
+        if self._skip is not None and int(self._skip.item()):
+            return
+        if self._cpu_streams is None:
+            self._cpu_streams = (torch.cuda.Stream(device), torch.cuda.Stream(device))
+            biggest = max(p.numel() for _, p, _ in on_host)
+            self._g_host = [_pinned_zeros(biggest, torch.bfloat16) for _ in range(2)]
+        d2h, h2d = self._cpu_streams
+        d2h.wait_stream(main)
+        work = []
+        for name, p, st in on_host:
+            if "master" not in st:
+                st["master"] = _pinned_zeros(p.numel(), torch.bfloat16)
+                st["master"].copy_(p.detach().reshape(-1))            # once: the host keeps the weights it updates
+            g = p.grad.contiguous()
+            g.record_stream(d2h)
+            flag = threading.Event()
+            self._cpu_flags[p] = flag
+            work.append((name, p, st, g, flag))
+        hyper = (b1, b2, step_size, bc2_sqrt, eps, wd_factor, step, scale)
+        self._worker = threading.Thread(target=self._host_worker, args=(work, hyper, device), daemon=True)
+        self._worker.start()
+
+    def _host_worker(self, work, hyper, device):
+        b1, b2, step_size, bc2_sqrt, eps, wd_factor, step, scale = hyper
+        torch.cuda.set_device(device)
+        L = _lib.host_lib()
+        d2h, h2d = self._cpu_streams
+        out_events = [None, None]
+
+        def fetch(i):
+            _, p, _, g, _ = work[i]
+            with torch.cuda.stream(d2h):
+                self._g_host[i % 2][:p.numel()].copy_(g.reshape(-1), non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(d2h)
+            return ev
+
+        pending = fetch(0)
+        for i, (name, p, st, g, flag) in enumerate(work):
+            nxt = fetch(i + 1) if i + 1 < len(work) else None          # its slot was released by update i - 1
+            pending.synchronize()
+            n = p.numel()
+            ptr = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+            L.halo_host_adamw_bf16(
+                ptr(st["master"]), ptr(self._g_host[i % 2]), ptr(st["exp_avg"]), ptr(st["exp_avg_sq"]), ctypes.c_longlong(n),
+                ctypes.c_ulonglong(param_name_hash(name)), ctypes.c_ulonglong(self.key), ctypes.c_ulonglong(step),
+                ctypes.c_float(b1), ctypes.c_float(b2), ctypes.c_float(step_size), ctypes.c_float(bc2_sqrt), ctypes.c_float(eps),
+                ctypes.c_float(wd_factor), ctypes.c_float(scale if scale is not None else 1.0),
+                ctypes.c_int(0 if scale is None else 1), ctypes.c_int(0))
+            with torch.cuda.stream(h2d):
+                p.data.copy_(st["master"].view(p.shape), non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(h2d)
+            self.ready_events[p] = ev
+            flag.set()
+            work[i] = (name, p, st, None, flag)                        # the gradient may be freed now
+            pending = nxt
+
+    def join_host_worker(self) -> None:
+        if self._worker is not None:
+            self._worker.join()
+            self._worker = None
+
     def wait_ready(self, params, stream=None) -> None:
         """Make ``stream`` (default: the current one) wait for the streamed updates of ``params``."""
-        if not self.ready_events:
+        if not self.ready_events and not self._cpu_flags:
             return
         stream = stream or torch.cuda.current_stream()
         for p in params:
+            flag = self._cpu_flags.pop(p, None)
+            if flag is not None:
+                flag.wait()                       # the host thread has issued this parameter's return copy
             ev = self.ready_events.pop(p, None)
             if ev is not None:
                 stream.wait_event(ev)
 
     def wait_all_ready(self) -> None:
-        self.wait_ready(list(self.ready_events))
+        self.wait_ready(list(dict.fromkeys(list(self._cpu_flags) + list(self.ready_events))))
 
     def synchronize_state(self) -> None:
         """Wait until every moment written by the last step has landed in host memory (call before
         reading the state, e.g. to save a checkpoint)."""
+        self.join_host_worker()
+        if self._cpu_streams is not None:
+            for s in self._cpu_streams:
+                s.synchronize()
         if self._streams is not None:
             self._opt_stream.synchronize()
             for s in self._streams:

@@ -67,3 +67,40 @@ def test_skip_flag_and_grad_norm():
     opt.step()
     for b, (_, p) in zip(before, gpu):
         assert torch.equal(b, p.detach())
+
+
+@pytest.mark.parametrize("host_compute", [False, True])
+def test_host_state_optimizer_matches_the_device_optimizer_bit_for_bit(host_compute):
+    """Moments in host memory - streamed through the device, or updated on the host CPU - give the very weights
+    and moments of the all-device optimizer after several clipped steps."""
+    from halo_b200.optim.adamw_bf16 import AdamWBF16, GradNorm
+    from halo_b200.optim.offload import HostStateAdamWBF16
+
+    torch.manual_seed(0)
+    shapes = {"a.big": (300, 1000), "b.small": (17, 33), "c.big": (128, 4096)}
+    base = {n: torch.randn(s, device="cuda").bfloat16() for n, s in shapes.items()}
+    ref_p = [(n, torch.nn.Parameter(t.clone())) for n, t in base.items()]
+    off_p = [(n, torch.nn.Parameter(t.clone())) for n, t in base.items()]
+    ref = AdamWBF16(ref_p, lr=1e-2, weight_decay=0.1)
+    off = HostStateAdamWBF16(off_p, lr=1e-2, weight_decay=0.1, host_min_numel=100_000, host_compute=host_compute)
+    norm_r, norm_o = GradNorm(torch.device("cuda")), GradNorm(torch.device("cuda"))
+    for step in range(4):
+        g = {n: (torch.randn(s, device="cuda") * (3.0 if step == 2 else 0.3)).bfloat16() for n, s in shapes.items()}
+        for params, opt, norm in ((ref_p, ref, norm_r), (off_p, off, norm_o)):
+            for n, p in params:
+                p.grad = g[n].clone()
+            norm.accumulate([p.grad for _, p in params], first=True)
+            norm.finish(1.0)
+            opt.defer_grad_scale(norm.coef)
+            opt.arm_skip(norm.skip)
+            opt.step()
+            opt.zero_grad(set_to_none=True)
+        off.wait_all_ready()
+        torch.cuda.synchronize()
+    off.synchronize_state()
+    assert off.state_bytes_on_host() > 0
+    for (n, a), (_, b) in zip(ref_p, off_p):
+        assert torch.equal(a.detach().view(torch.int16), b.detach().view(torch.int16)), n
+        sa, sb = ref.state[a], off.state[b]
+        assert torch.equal(sa["exp_avg"].cpu().view(torch.int16), sb["exp_avg"].cpu().view(torch.int16)), n
+        assert torch.equal(sa["exp_avg_sq"].cpu().view(torch.int16), sb["exp_avg_sq"].cpu().view(torch.int16)), n
