@@ -172,6 +172,8 @@ class HostStateAdamWBF16(AdamWBF16):
         copy of tensor i + 1, the update of tensor i and the return of tensor i - 1 going at the same time. The
         caller returns at once; consumers of a parameter wait in :meth:`wait_ready`."""
         self.join_host_worker()
+        if self._cpu_streams is not None:
+            self._cpu_streams[1].synchronize()      # last step's return copies have left the host weights
         main = torch.cuda.current_stream(device)
         # the host needs the clip coefficient and the skip verdict: one read per step, after the norm is final
         scale = float(self._grad_scale.item()) if self._grad_scale is not None else None
