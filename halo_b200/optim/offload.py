@@ -30,12 +30,18 @@ STAGING_SLOTS = 4  # >= 3 so that the host->device and device->host copies of ne
 
 def _pinned_zeros(numel: int, dtype: torch.dtype) -> torch.Tensor:
     """Zero-filled host tensor registered with CUDA as page-locked, without the size rounding of
-    torch's pinned-memory cache (which would waste up to 2x on multi-hundred-MB tensors)."""
-    t = torch.zeros(numel, dtype=dtype)
+    torch's pinned-memory cache (which would waste up to 2x on multi-hundred-MB tensors). The registered
+    range is made of whole pages that belong to this tensor alone: two registrations must never share a page."""
+    page = 4096
+    nbytes = numel * torch.empty((), dtype=dtype).element_size()
+    raw = torch.zeros(nbytes + 2 * page, dtype=torch.uint8)
+    off = (-raw.data_ptr()) % page
+    t = raw[off:off + nbytes].view(dtype)
     if torch.cuda.is_available():
-        rc = torch.cuda.cudart().cudaHostRegister(t.data_ptr(), t.numel() * t.element_size(), 0)
+        span = (nbytes + page - 1) // page * page
+        rc = torch.cuda.cudart().cudaHostRegister(raw.data_ptr() + off, max(span, page), 0)
         if int(rc) != 0:
-            raise RuntimeError(f"cudaHostRegister failed with {rc} for {t.numel() * t.element_size()} bytes")
+            raise RuntimeError(f"cudaHostRegister failed with {rc} for {span} bytes")
     return t
 
 
