@@ -28,6 +28,20 @@ HOST_STATE_MIN_NUMEL = 8 * 1024 * 1024  # smaller tensors keep their moments on 
 STAGING_SLOTS = 4  # >= 3 so that the host->device and device->host copies of neighbouring buckets overlap
 
 
+class _PinGuard:
+    """Unregisters a page-locked range when the tensor that owns it goes away (a later allocation may get the
+    same pages back from the C allocator, and registering a range twice is an error)."""
+
+    def __init__(self, ptr: int):
+        self.ptr = ptr
+
+    def __del__(self):
+        try:
+            torch.cuda.cudart().cudaHostUnregister(self.ptr)
+        except Exception:  # noqa: BLE001 - interpreter shutdown
+            pass
+
+
 def _pinned_zeros(numel: int, dtype: torch.dtype) -> torch.Tensor:
     """Zero-filled host tensor registered with CUDA as page-locked, without the size rounding of
     torch's pinned-memory cache (which would waste up to 2x on multi-hundred-MB tensors). The registered
@@ -42,6 +56,7 @@ def _pinned_zeros(numel: int, dtype: torch.dtype) -> torch.Tensor:
         rc = torch.cuda.cudart().cudaHostRegister(raw.data_ptr() + off, max(span, page), 0)
         if int(rc) != 0:
             raise RuntimeError(f"cudaHostRegister failed with {rc} for {span} bytes")
+        t._halo_pin = _PinGuard(raw.data_ptr() + off)
     return t
 
 
