@@ -440,11 +440,12 @@ scale_rows_dot_kernel(__nv_bfloat16* __restrict__ g, const __nv_bfloat16* __rest
 //   dpre[r]  = w[r] * swiglu'(pre[r]) (.) dact_u[r]
 //   act_w[r] = w[r] * act                            (left operand of the down-projection weight gradient)
 // where dact_u = dout_rows W_down is the unscaled activation gradient. <dout, y> = <dout W_down, act>, so
-// neither the expert output rows nor a pre-scaled copy of the incoming gradient is needed.
+// neither the expert output rows nor a pre-scaled copy of the incoming gradient is needed. dpre may be pre and
+// act_w may be dact_u (in place): a thread reads the vectors it overwrites before it writes them.
 __global__ void __launch_bounds__(256)
-swiglu_bwd_weighted_kernel(const __nv_bfloat16* __restrict__ pre, const __nv_bfloat16* __restrict__ dact,
-                           const float* __restrict__ w, __nv_bfloat16* __restrict__ dpre,
-                           __nv_bfloat16* __restrict__ act_w, float* __restrict__ dwrow,
+swiglu_bwd_weighted_kernel(const __nv_bfloat16* pre, const __nv_bfloat16* dact,
+                           const float* __restrict__ w, __nv_bfloat16* dpre,
+                           __nv_bfloat16* act_w, float* __restrict__ dwrow,
                            const int* __restrict__ total_rows, int F, int cap_rows) {
     const int lane = threadIdx.x & 31;
     const int rows = min(*total_rows, cap_rows);

@@ -391,15 +391,33 @@ class _MoEExperts(torch.autograd.Function):
         lst = _tile_list(state, "m", pair, n_cols=F, k_dim=H, b_mn_stride=0, b_k_stride=H, swiglu_f=0)
         _gemm_list(dy, w_down.reshape(E_local * H, F), dact, lst, 0, 1, EPI_STORE_BF16, pair=pair)
         # 3. SwiGLU backward with the routing weight folded in: dpre = w * swiglu'(pre) dact_u, act_w = w * act,
-        #    dwrow = <dact_u, act> (= <dout, expert output>, without ever forming the expert output)
+        #    dwrow = <dact_u, act> (= <dout, expert output>, without ever forming the expert output).
+        #    Both outputs overwrite their inputs (element for element, same index): dpre lands on pre, act_w on dact_u.
         dwrow = transport.buffer("dwrow", cap, 1, torch.float32, dev)
-        dpre = _alloc(transport, (cap, F2), torch.bfloat16, dev)
-        act_w = _alloc(transport, (cap, F), torch.bfloat16, dev)
+        dpre, act_w = pre, dact
         _lib.check(L.halo_swiglu_bwd_weighted(_lib.ptr(pre), _lib.ptr(dact), _lib.ptr(row_w), _lib.ptr(dpre),
                                               _lib.ptr(act_w), _lib.ptr(dwrow), _lib.ptr(state.total_rows),
                                               _lib.c_int(F), _lib.c_int(cap), s), "halo_swiglu_bwd_weighted")
-        # 4. input gradient rows first: dx_rows = dpre W_gate_up
-        dx_rows = transport.buffer("dx_rows", cap, H, torch.bfloat16, dev)
+        def weight_grads():
+            # 5. dW_down[e] = dout_e^T (w * act)_e ; dW_gate_up[e] = dpre_e^T x_e
+            dw_down = _alloc(transport, tuple(w_down.shape), w_down.dtype, dev)
+            pk = _pair_ok(4096, False)      # the reduction runs over an expert's rows: long
+            _gemm_list(dy, act_w, dw_down.reshape(E_local * H, F), _tile_list(state, "k", pk, m_dim=H, n_dim=F), 1, 1,
+                       EPI_STORE_BF16, pair=pk)
+            dw_gate_up = _alloc(transport, tuple(w_gate_up.shape), w_gate_up.dtype, dev)
+            _gemm_list(dpre, recv_x, dw_gate_up.reshape(E_local * F2, H), _tile_list(state, "k", pk, m_dim=F2, n_dim=H), 1, 1,
+                       EPI_STORE_BF16, pair=pk)
+            return dw_gate_up, dw_down
+
+        # 4. input gradient rows: dx_rows = dpre W_gate_up. On one rank the weight gradients go first, after which the
+        #    incoming-gradient rows are dead and their storage takes dx_rows; across ranks dx_rows is the peers' window
+        #    and goes first so that its pull can run beside the weight gradients.
+        early_weight_grads = transport.n_ranks == 1
+        if early_weight_grads:
+            dw_gate_up, dw_down = weight_grads()
+            dx_rows = dy
+        else:
+            dx_rows = transport.buffer("dx_rows", cap, H, torch.bfloat16, dev)
         pair = _pair_ok(F2, False)
         lst = _tile_list(state, "m", pair, n_cols=H, k_dim=F2, b_mn_stride=0, b_k_stride=F2, swiglu_f=0)
         _gemm_list(dpre, w_gate_up.reshape(E_local * F2, H), dx_rows, lst, 0, 1, EPI_STORE_BF16, pair=pair)
@@ -417,20 +435,10 @@ class _MoEExperts(torch.autograd.Function):
                                                  _lib.ptr(dw), _lib.c_ll(T * k), _lib.c_int(E_local), _lib.c_int(cap), st),
                        "halo_gather_slot_values")
 
-        def weight_grads():
-            # 5. dW_down[e] = dout_e^T (w * act)_e ; dW_gate_up[e] = dpre_e^T x_e
-            dw_down = _alloc(transport, tuple(w_down.shape), w_down.dtype, dev)
-            pk = _pair_ok(4096, False)      # the reduction runs over an expert's rows: long
-            _gemm_list(dy, act_w, dw_down.reshape(E_local * H, F), _tile_list(state, "k", pk, m_dim=H, n_dim=F), 1, 1,
-                       EPI_STORE_BF16, pair=pk)
-            dw_gate_up = _alloc(transport, tuple(w_gate_up.shape), w_gate_up.dtype, dev)
-            _gemm_list(dpre, recv_x, dw_gate_up.reshape(E_local * F2, H), _tile_list(state, "k", pk, m_dim=F2, n_dim=H), 1, 1,
-                       EPI_STORE_BF16, pair=pk)
-            return dw_gate_up, dw_down
-
         side = transport.side_stream(dev) if transport.n_ranks > 1 else None
         if side is None:
-            dw_gate_up, dw_down = weight_grads()
+            if not early_weight_grads:
+                dw_gate_up, dw_down = weight_grads()
             transport.barrier()
             pull_back()
         else:
