@@ -1,0 +1,150 @@
+"""Multi-GPU kernel benchmarks: the kernels that compute and move data over NVLink in one launch, each against its
+roofline (the slower of FLOPs / measured GEMM rate and NVLink bytes / measured peer-copy bandwidth) and against the
+library baseline (NCCL collective + separate kernel).
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 benchmarks/collectives.py
+
+Timing: CUDA events on the launching stream after warm-up, a barrier before each timed launch, the MAX over ranks
+of the median is reported by rank 0. Link bandwidth reference: 770 GB/s per direction per GPU (measured peer copy).
+"""
+
+from __future__ import annotations
+
+import json
+import os
+import statistics
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+LINK_GBS = 770.0
+
+
+def peaks():
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        p = json.load(open(path))
+        return p["hbm_gbs"], p["bf16_tflops"]
+    return 6650.0, 1590.0
+
+
+def timed(fn, iters=7, warmup=3):
+    for _ in range(warmup):
+        fn()
+    out = []
+    for _ in range(iters):
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        out.append(a.elapsed_time(b))
+    t = torch.tensor([statistics.median(out)], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    from halo_b200.ops import _lib, gemm
+    from halo_b200.ops.moe import moe_experts, router_topk
+    from halo_b200.parallel.runtime import ParallelRuntime
+    from halo_b200.parallel.tensor_parallel import TensorParallel, _all_gather_rows, row_parallel_linear
+    from halo_b200.parallel.zero import FusedShardedAdamW
+
+    hbm, tf = peaks()
+    rows = []
+
+    def report(name, ms, flops=0.0, link_bytes=0.0, note=""):
+        roof_ms = max(flops / (tf * 1e9) if flops else 0.0, link_bytes / (LINK_GBS * 1e6) if link_bytes else 0.0)
+        rec = {"case": name, "ms": round(ms, 3), "roofline_ms": round(roof_ms, 3),
+               "fraction_of_roofline": round(roof_ms / ms, 3) if ms else 0.0, "note": note}
+        rows.append(rec)
+        if rank == 0:
+            print(f"{name:44s} {ms:8.3f} ms   roofline {roof_ms:7.3f} ms   {rec['fraction_of_roofline']:5.2f}  {note}", flush=True)
+
+    # ---- row-parallel GEMM with the reduce-scatter's transfer in its epilogue (O-projection shape, TP = world) ----
+    T, H, K = 65536, 2048, 4096 // world
+    tp = TensorParallel(dist.group.WORLD, dev, hidden=H, max_tokens=T)
+    x = (torch.randn(T, K, device=dev) * 0.05).bfloat16()
+    w = (torch.randn(H, K, device=dev) * 0.05).bfloat16()
+    flops = 2.0 * T * H * K
+    link = (world - 1) / world * T * H * 2.0          # partial tiles this rank sends to the other owners
+    ms = timed(lambda: row_parallel_linear(x, w, tp))
+    report("fused GEMM + reduce-scatter (own kernels)", ms, flops, link, f"[{T}x{K}] x [{H}x{K}]^T, tp={world}")
+    y_full = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
+    y_shard = torch.empty(T // world, H, device=dev, dtype=torch.bfloat16)
+
+    def baseline_rs():
+        gemm.matmul(x, w, out=y_full)
+        dist.reduce_scatter_tensor(y_shard, y_full)
+
+    report("  baseline: own GEMM, then NCCL reduce-scatter", timed(baseline_rs), flops, link)
+
+    # ---- sequence gather by peer pulls vs NCCL all-gather --------------------------------------------------------
+    shard = (torch.randn(T // world, H, device=dev) * 0.05).bfloat16()
+    link = (world - 1) / world * T * H * 2.0
+    report("sequence gather by peer pulls", timed(lambda: _all_gather_rows(shard, tp)), 0.0, link)
+    full = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
+    report("  baseline: NCCL all-gather", timed(lambda: dist.all_gather_into_tensor(full, shard)), 0.0, link)
+
+    # ---- reduce-scatter + AdamW + all-gather of the replicated parameters (1.4 B parameters) -----------------------
+    n = 1_400_000_000 // 8 * 8
+    p = torch.nn.Parameter(torch.zeros(n, device=dev, dtype=torch.bfloat16))
+    opt = FusedShardedAdamW([("flat", p)], dist.group.WORLD, dev, lr=1e-4)
+    p.grad = torch.full((n,), 1e-3, device=dev, dtype=torch.bfloat16)
+    one = torch.ones(1, device=dev)
+    zero = torch.zeros(1, device=dev, dtype=torch.int32)
+
+    def fused_step():
+        opt.pack_and_reduce()
+        opt.step(one, zero)
+
+    link = 2.0 * (world - 1) / world * n * 2.0        # gradient slice in from every peer, weight slice out to every peer
+    ms = timed(fused_step, iters=5, warmup=2)
+    report("reduce-scatter + AdamWBF16 + all-gather (two kernels)", ms, 0.0, link, f"{n / 1e9:.1f} B bf16 parameters")
+    g = p.grad
+
+    def baseline_zero():
+        dist.all_reduce(g)
+
+    report("  baseline: NCCL all-reduce of the gradients alone", timed(baseline_zero, iters=5, warmup=2), 0.0, link)
+    del opt, p, g
+
+    # ---- expert dispatch + grouped GEMMs + combine over peer memory (one MoE layer forward, 30B-A3B shapes) -----------
+    E, F, topk = 128, 768, 8
+    parallel = ParallelRuntime.for_expert_parallel(world, dev)
+    parallel.transport.configure(max_tokens=T, top_k=topk, hidden=H, n_local_experts=E // world)
+    xm = (torch.randn(T, H, device=dev) * 0.05).bfloat16()
+    idx, wts = router_topk(torch.randn(T, E, device=dev), topk, True)
+    wgu = (torch.randn(E // world, 2 * F, H, device=dev) * 0.05).bfloat16()
+    wdn = (torch.randn(E // world, H, F, device=dev) * 0.05).bfloat16()
+    flops = 2.0 * T * topk * 3 * H * F
+    link = 2.0 * (world - 1) / world * T * topk * H * 2.0      # rows out to the experts and back
+    with torch.no_grad():
+        ms = timed(lambda: moe_experts(xm, idx, wts, wgu, wdn, parallel.transport), iters=5, warmup=2)
+    report("MoE layer forward: push, grouped GEMMs, pull", ms, flops, link, "transfer and GEMMs are serial phases: roofline is their sum")
+    rows[-1]["roofline_ms"] = round(flops / (tf * 1e9) + link / (LINK_GBS * 1e6), 3)
+    rows[-1]["fraction_of_roofline"] = round(rows[-1]["roofline_ms"] / ms, 3)
+    if rank == 0:
+        print(f"{'  (serial-phase roofline)':44s} {ms:8.3f} ms   roofline {rows[-1]['roofline_ms']:7.3f} ms   "
+              f"{rows[-1]['fraction_of_roofline']:5.2f}", flush=True)
+    _lib.raise_on_status(dev)
+    if rank == 0 and len(sys.argv) > 1:
+        os.makedirs(os.path.dirname(sys.argv[1]) or ".", exist_ok=True)
+        json.dump({"world": world, "link_gbs": LINK_GBS, "bf16_tflops": tf, "rows": rows}, open(sys.argv[1], "w"), indent=1)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
