@@ -52,8 +52,9 @@ def parse_args():
                     help="N > 1: 1 = fused reduce-scatter/AdamW/all-gather kernels for the replicated parameters, "
                          "0 = NCCL all-reduce + local optimizer (the baseline path)")
     ap.add_argument("--doc-dist", default="chat")
-    ap.add_argument("--host-compute", default="auto", choices=["auto", "0", "1"],
-                    help="update host-resident optimizer state on the host CPU (auto: when a short probe says the CPU keeps up)")
+    ap.add_argument("--host-compute", default="0", choices=["auto", "0", "1"],
+                    help="update host-resident optimizer state on the host CPU instead of streaming it through the device "
+                         "(measured 2.6x slower on the 16-core benchmark hosts: off by default)")
     ap.add_argument("--ep-lanes", type=int, default=0,
                     help="parts an expert-parallel MoE call is cut into so that one part's NVLink transfers overlap another's GEMMs "
                          "(0 or 1 = one part; two parts measured slower on 2 and 4 GPUs and are off by default)")
