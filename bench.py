@@ -46,7 +46,7 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=65536)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run reduced)")
     ap.add_argument("--optimizer-state", default="auto", choices=["auto", "device", "host"])
-    ap.add_argument("--activation-reserve-gb", type=float, default=30.0,
+    ap.add_argument("--activation-reserve-gb", type=float, default=26.0,
                     help="device memory kept free of optimizer state for activations, workspaces and staging")
     ap.add_argument("--fused-optimizer", type=int, default=1,
                     help="N > 1: 1 = fused reduce-scatter/AdamW/all-gather kernels for the replicated parameters, "
