@@ -127,10 +127,63 @@ __device__ __forceinline__ bool fetch_work(const GemmParams& p, int idx, int tot
 
 // One epilogue warp's share of a finished tile: its 32 TMEM lanes (rows row_in_tile of the tile) x the tile's
 // columns, read with tcgen05.ld and stored according to p.epi. Warp-collective: every lane must call it.
-__device__ __forceinline__ void epilogue_tile(const GemmParams& p, const GemmWork& w, uint32_t t_row, int row_in_tile) {
+// `stage`: shared-memory address of this warp's 8 KB transposition buffer.
+constexpr int kEpiStageBytesPerWarp = 32 * 256;   // 32 rows x 128 bf16 columns
+
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, const GemmWork& w, uint32_t t_row, int row_in_tile,
+                                              uint32_t stage) {
     const bool row_ok = row_in_tile < w.m_valid;
     const long long grow = (long long)w.c_row + row_in_tile;
     const bool zero = (w.k_iters == 0);
+    if (p.epi == kEpiStoreBf16 && p.rs_ranks > 1) {
+        // Reduce-scatter epilogue: the tile goes into the owner rank's staging area over NVLink. A thread owns one
+        // accumulator row, so storing straight from registers would put 16-byte pieces 2*ldc bytes apart on the link;
+        // instead the warp transposes 128 columns at a time through shared memory (16-byte units, XOR-swizzled by row)
+        // and writes two 256-byte row segments per instruction. (For local stores L2 merges the pieces and the direct
+        // path below measured faster.)
+        const int lane = threadIdx.x & 31;
+        const int warp_row0 = row_in_tile - lane;                 // first tile row of this warp
+        __nv_bfloat16* cbase = reinterpret_cast<__nv_bfloat16*>(p.rs_ranks > 1 ? p.c_peers[w.pad0] : p.C);
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBlockN; c0 += 128) {
+            if (c0 >= w.n_valid) break;                           // uniform across the warp
+#pragma unroll 1
+            for (int cc = 0; cc < 128; cc += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(t_row + c0 + cc, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    uint32_t o[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float a = zero ? 0.f : __uint_as_float(r[j + 2 * q]) * p.alpha;
+                        const float b = zero ? 0.f : __uint_as_float(r[j + 2 * q + 1]) * p.alpha;
+                        o[q] = pack_bf16(a, b);
+                    }
+                    const int unit = (cc + j) >> 3;                // 16-byte unit within the 256-byte row
+                    const uint32_t a = stage + lane * 256 + ((unit ^ (lane & 15)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                                 : "memory");
+                }
+            }
+            __syncwarp();
+            const int unit = lane & 15;
+            const int col = c0 + unit * 8;
+#pragma unroll 4
+            for (int k = 0; k < 16; ++k) {
+                const int rr = 2 * k + (lane >> 4);                // row within the warp's 32
+                uint32_t v0, v1, v2, v3;
+                const uint32_t a = stage + rr * 256 + ((unit ^ (rr & 15)) << 4);
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(a));
+                if (warp_row0 + rr < w.m_valid && col + 8 <= w.n_valid)
+                    *reinterpret_cast<uint4*>(cbase + ((long long)w.c_row + warp_row0 + rr) * p.ldc + w.c_col + col) =
+                        make_uint4(v0, v1, v2, v3);
+            }
+            __syncwarp();
+        }
+        return;
+    }
     if (p.epi == kEpiSwiglu) {
 #pragma unroll 1
         for (int c = 0; c < 128; c += 32) {
@@ -356,6 +409,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // ---------------- epilogue: TMEM -> registers -> global ----------------
         const int quarter = warp & 3;  // TMEM lanes this warp may read: [32*quarter, 32*quarter+32)
         const int row_in_tile = quarter * 32 + lane;
+        const uint32_t epi_stage = tiles_base + kStages * kStageBytes + quarter * kEpiStageBytesPerWarp;
         int acc = 0;
         uint32_t acc_phase = 0;
         GemmWork w;
@@ -363,7 +417,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (!mbar_wait(smem_u32(&bar_tfull[acc]), acc_phase, &abort_flag, p.status)) break;
             tc_fence_after();
             const uint32_t t_row = tmem_base + acc * kBlockN + (uint32_t(quarter * 32) << 16);
-            epilogue_tile(p, w, t_row, row_in_tile);
+            epilogue_tile(p, w, t_row, row_in_tile, epi_stage);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[acc]));
@@ -402,7 +456,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // ---------------------------------------------------------------------------------------------
 constexpr int kPairStages = 6;
 constexpr int kPairStageBytes = 2 * kATileBytes;  // 128 x 64 of A and 128 x 64 of B
-constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024;
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + 4 * 32 * 256;   // + the epilogue's transposition buffers
 
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
     uint32_t r;
@@ -617,6 +671,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         // ---------------- epilogue (both CTAs, each its own 128 rows) ----------------
         const int quarter = warp & 3;
         const int row_in_tile = quarter * 32 + lane;
+        const uint32_t epi_stage = tiles_base + kPairStages * kPairStageBytes + quarter * kEpiStageBytesPerWarp;
         int acc = 0;
         uint32_t acc_phase = 0;
         GemmWork w;
@@ -627,7 +682,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             GemmWork mine = w;
             mine.c_row = w.c_row + int(rank) * 128;
             mine.m_valid = max(0, min(128, w.m_valid - int(rank) * 128));
-            epilogue_tile(p, mine, t_row, row_in_tile);
+            epilogue_tile(p, mine, t_row, row_in_tile, epi_stage);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&bar_tempty[acc]), 0));
@@ -802,7 +857,7 @@ static int num_sms() {
     return g_num_sms;
 }
 
-constexpr int kGemmSmemBytes = kStages * kStageBytes + 1024;
+constexpr int kGemmSmemBytes = kStages * kStageBytes + 1024 + 4 * kEpiStageBytesPerWarp;
 
 template <bool A_MN, bool B_MN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
