@@ -224,7 +224,11 @@ def main() -> int:
     if parallel is not None and args.fused_optimizer:
         # replicated parameters: sharded AdamWBF16 fused with reduce-scatter / all-gather over peer memory
         named = parallel.enable_fused_optimizer(model, lr=args.lr, weight_decay=0.01)
-    if opt_state == "host":
+    if not named:
+        from halo_b200.parallel.zero import NoParametersLeft
+
+        opt = NoParametersLeft(args.lr)        # a dense model: the fused sharded optimizer holds every parameter
+    elif opt_state == "host":
         from halo_b200.optim.offload import HostStateAdamWBF16
 
         # moments stay on the device for as many tensors as fit beside gradients, activations and staging

@@ -159,7 +159,7 @@ def run_trainer(trainer, train_args):
     final = os.path.join(train_args.output_dir, "final")
     from halo_b200.checkpoint.save import save_model
 
-    save_model(trainer.model, final, group=trainer.parallel.dp_group if trainer.parallel is not None else None)
+    save_model(trainer.model, final, group=trainer.group, is_writer=trainer.is_main)
     return result
 
 

@@ -85,6 +85,9 @@ def main(argv=None):
         weight_sync = ModelWeightPusher(sync, roles, device, runtime.ep_group if runtime else None)
     trainer = GRPOTrainer(model, train_args, source, grpo_args=grpo_args, weight_sync=weight_sync, device=device,
                           parallel=runtime, parallelism_fingerprint=pc.fingerprint())
+    if roles is not None:
+        trainer.collective_group = roles.trainer_group       # the rollout ranks take no part in saves and barriers
+        trainer.rank = roles.rank
     try:
         return run_trainer(trainer, train_args)
     finally:

@@ -167,3 +167,23 @@ class FusedShardedAdamW:
         self.step_count = sd["step"]
         self.m.copy_(sd["m"])
         self.v.copy_(sd["v"])
+
+
+class NoParametersLeft:
+    """Stands in for the ordinary optimizer when every parameter went to the fused sharded optimizer (a dense
+    model): it accepts the engine's calls and owns the learning-rate slot the scheduler writes."""
+
+    def __init__(self, lr: float):
+        self.param_groups = [{"lr": lr, "params": []}]
+        self.state: dict = {}
+
+    def defer_grad_scale(self, scale) -> None: ...
+    def arm_skip(self, flag) -> None: ...
+    def step(self) -> None: ...
+    def zero_grad(self, set_to_none: bool = True) -> None: ...
+
+    def state_dict(self) -> dict:
+        return {"param_groups": [{"lr": self.param_groups[0]["lr"]}]}
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.param_groups[0]["lr"] = sd["param_groups"][0]["lr"]

@@ -88,6 +88,7 @@ class Trainer:
         self.log_history: list[dict] = []
         self._pending_skip = None
         self._consecutive_skips = 0
+        self.collective_group = None      # set by a job whose ranks are not all trainers (split trainer / rollout roles)
         self.rank = int(os.environ.get("RANK", "0"))
         if parallel is not None and parallel.dp_group is not None:
             import torch.distributed as dist
@@ -115,6 +116,13 @@ class Trainer:
 
             return dist.get_world_size(self.parallel.dp_group)
         return int(os.environ.get("WORLD_SIZE", "1"))
+
+    @property
+    def group(self):
+        """The ranks that take part in this trainer's collectives (None = the whole job)."""
+        if self.collective_group is not None:
+            return self.collective_group
+        return self.parallel.dp_group if self.parallel is not None else None
 
     @property
     def is_main(self) -> bool:
@@ -205,15 +213,15 @@ class Trainer:
         d = self.checkpoint_dir()
         os.makedirs(d, exist_ok=True)
         save_model(self.model, d, sharded_experts=self.args.save_sharded_ep, save_dtype=None,
-                   group=self.parallel.dp_group if self.parallel is not None else None)  # exact resume: keep the dtype
+                   group=self.group)  # exact resume: keep the dtype
         opt_io.save_optimizer_shard(self.optimizer, d, self.rank, self.fingerprint, write_meta=self.is_main)
         atomic_torch_save({"cpu": torch.get_rng_state(),
                            "cuda": torch.cuda.get_rng_state(self.device) if self.device.type == "cuda" else None},
                           os.path.join(d, f"rng_state_{self.rank}.pth"))
-        if self.parallel is not None:
+        if self.parallel is not None or self.collective_group is not None:
             import torch.distributed as dist
 
-            dist.barrier(group=self.parallel.dp_group)
+            dist.barrier(group=self.group)
         if self.is_main:
             atomic_torch_save(self.lr_scheduler.state_dict(), os.path.join(d, "scheduler.pt"))
             mark_complete(d, {"global_step": self.global_step, "tokens_seen": self.tokens_seen,

@@ -80,3 +80,21 @@ def _split_worker(rank, world):
 
 def test_split_roles_push_reaches_the_rollout_copy():
     run_gloo_ranks(_split_worker, 3)
+
+
+def test_one_trainer_one_rollout_job_finishes(tmp_path):
+    """A split job whose trainer side is a single rank: saves and barriers must involve the trainer alone (the
+    rollout rank sits in its receive loop), and closing the pusher ends the rollout rank."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = tmp_path / "grpo.yaml"
+    cfg.write_text("model_preset: tiny-moe\ninit_from_scratch: true\nmax_steps: 2\noptim: adamw_torch\n"
+                   f"output_dir: {tmp_path}/run\nnum_generations: 4\ntoken_budget: 2048\nmax_completion_length: 64\n"
+                   "rollout_gpus: 1\n")
+    r = subprocess.run([sys.executable, "-m", "halo_b200.cli", "launch", "grpo", str(cfg), "-n", "2", "--port", "29683"],
+                       cwd=root, capture_output=True, text=True, timeout=240, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert os.path.isfile(tmp_path / "run" / "final" / "config.json")
