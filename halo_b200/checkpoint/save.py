@@ -87,7 +87,15 @@ def save_model(model, directory: str, is_writer: bool | None = None, save_dtype:
                 for hub, t in runtime_to_hub(name, p.detach(), cfg, first_layer, ep_rank * p.shape[0]).items():
                     writer.add(hub, t)
             continue
-        full = _gather_expert_bank(p.detach(), n_ep, ep_group)   # collective: every rank takes part
+        local = p.detach()
+        etp = getattr(model, "expert_tensor_parallel", None)
+        if etp is not None and getattr(p, "etp_kind", None) is not None:
+            from halo_b200.parallel.expert_tensor_parallel import unslice_expert_bank
+
+            parts = [torch.empty_like(local) for _ in range(etp.size)]
+            dist.all_gather(parts, local.contiguous(), group=etp.group)       # collective over the width-cut group
+            local = unslice_expert_bank(p.etp_kind, parts)
+        full = _gather_expert_bank(local, n_ep, ep_group)   # collective: every rank takes part
         with guard.catch():
             if is_writer and writer is not None:
                 for hub, t in runtime_to_hub(name, full, cfg, first_layer, 0).items():

@@ -150,15 +150,21 @@ class SparseMoE(nn.Module):
     """Router + routed experts (+ optional shared expert). Expert tensors hold only this rank's
     experts ``[E_local, ...]`` when expert parallelism is on."""
 
-    def __init__(self, cfg: ModelConfig, dtype, device, n_local_experts: int, router_dtype=None):
+    def __init__(self, cfg: ModelConfig, dtype, device, n_local_experts: int, router_dtype=None, etp=None):
         super().__init__()
         self.cfg = cfg
+        self.etp = etp            # ExpertTensorParallel: every expert's width is cut over its group
         H, F = cfg.hidden_size, cfg.moe_intermediate_size
+        if etp is not None:
+            etp.check(cfg)
+            F //= etp.size
         self.gate = nn.Parameter(torch.empty(cfg.num_experts, H, dtype=router_dtype or dtype, device=device))
         self.experts_gate_up = nn.Parameter(torch.empty(n_local_experts, 2 * F, H, dtype=dtype, device=device))
         self.experts_down = nn.Parameter(torch.empty(n_local_experts, H, F, dtype=dtype, device=device))
         self.experts_gate_up.is_expert = True
         self.experts_down.is_expert = True
+        if etp is not None:
+            self.experts_gate_up.etp_kind, self.experts_down.etp_kind = "gate_up", "down"
         if cfg.shared_expert_intermediate_size:
             self.shared_expert = DenseMLP(H, cfg.shared_expert_intermediate_size, dtype, device)
             self.shared_gate = (nn.Parameter(torch.empty(1, H, dtype=dtype, device=device))
@@ -189,8 +195,17 @@ class SparseMoE(nn.Module):
             counter.add(layer_index, idx)     # first pass only: a recomputation replays the same routing
         if ctx.record_routing is not None:
             ctx.record_routing.append((logits, idx))
-        out = moe_ops.moe_experts(h, idx, w, self.experts_gate_up, self.experts_down, ctx.transport,
-                                  skip_output=getattr(ctx, "output_unused", False))
+        if self.etp is not None:
+            # every rank of the group routes the same tokens through its slice of each expert; the partial outputs
+            # are summed in token space (and the partial input / routing-weight gradients on the way back)
+            from halo_b200.parallel.expert_tensor_parallel import copy_to_group, sum_from_group
+
+            part = moe_ops.moe_experts(copy_to_group(h, self.etp), idx, copy_to_group(w, self.etp), self.experts_gate_up,
+                                       self.experts_down, ctx.transport)
+            out = sum_from_group(part, self.etp)
+        else:
+            out = moe_ops.moe_experts(h, idx, w, self.experts_gate_up, self.experts_down, ctx.transport,
+                                      skip_output=getattr(ctx, "output_unused", False))
         if self.shared_expert is not None:
             sh = self.shared_expert(h)
             if self.shared_gate is not None:
@@ -200,7 +215,8 @@ class SparseMoE(nn.Module):
 
 
 class DecoderLayer(nn.Module):
-    def __init__(self, cfg: ModelConfig, idx: int, dtype, device, n_local_experts: int, router_dtype=None, tp_size: int = 1):
+    def __init__(self, cfg: ModelConfig, idx: int, dtype, device, n_local_experts: int, router_dtype=None, tp_size: int = 1,
+                 etp=None):
         super().__init__()
         H = cfg.hidden_size
         self.input_layernorm = nn.Parameter(torch.ones(H, dtype=dtype, device=device))
@@ -208,7 +224,7 @@ class DecoderLayer(nn.Module):
         self.self_attn = Attention(cfg, dtype, device, tp_size)
         if cfg.layer_is_moe(idx):
             # attention-only tensor parallelism for MoE layers: router and experts see this rank's token shard
-            self.mlp = SparseMoE(cfg, dtype, device, n_local_experts, router_dtype)
+            self.mlp = SparseMoE(cfg, dtype, device, n_local_experts, router_dtype, etp)
         else:
             self.mlp = DenseMLP(H, cfg.intermediate_size, dtype, device, tp_size)
         self.eps = cfg.rms_norm_eps
@@ -249,7 +265,7 @@ class Qwen3Model(nn.Module):
 
     def __init__(self, cfg: ModelConfig, dtype=torch.bfloat16, device=None, transport=None,
                  gradient_checkpointing: bool = True, router_dtype=None, layer_range: tuple[int, int] | None = None,
-                 has_embed: bool = True, has_head: bool = True, tensor_parallel=None):
+                 has_embed: bool = True, has_head: bool = True, tensor_parallel=None, expert_tensor_parallel=None):
         super().__init__()
         self.cfg = cfg
         self.transport = transport or moe_ops.LocalTransport()
@@ -260,6 +276,7 @@ class Qwen3Model(nn.Module):
         self.gradient_checkpointing = gradient_checkpointing
         self.context_parallel = None      # halo_b200.parallel.context_parallel.ContextParallel when cp > 1
         self.tensor_parallel = tensor_parallel    # halo_b200.parallel.tensor_parallel.TensorParallel when tp > 1
+        self.expert_tensor_parallel = expert_tensor_parallel
         tp_size = tensor_parallel.size if tensor_parallel is not None else 1
         if tp_size > 1:
             from halo_b200.parallel.tensor_parallel import check_divisibility
@@ -270,7 +287,7 @@ class Qwen3Model(nn.Module):
         H = cfg.hidden_size
         self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, H, dtype=dtype, device=device)) if has_embed else None
         self.layers = nn.ModuleList(
-            [DecoderLayer(cfg, i, dtype, device, n_local, router_dtype, tp_size) for i in range(lo, hi)])
+            [DecoderLayer(cfg, i, dtype, device, n_local, router_dtype, tp_size, expert_tensor_parallel) for i in range(lo, hi)])
         self.norm = nn.Parameter(torch.ones(H, dtype=dtype, device=device)) if has_head else None
         if has_head and not (cfg.tie_word_embeddings and has_embed):
             self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, H, dtype=dtype, device=device))
@@ -303,9 +320,19 @@ class Qwen3Model(nn.Module):
             if getattr(p, "is_expert", False):
                 # one generator per (parameter, global expert): any sharding draws the same values
                 e0 = self.transport.rank * p.shape[0]
+                etp = self.expert_tensor_parallel if getattr(p, "etp_kind", None) is not None else None
                 for le in range(p.shape[0]):
                     g = torch.Generator(device=dev).manual_seed(base + e0 + le)
-                    p[le].normal_(0.0, std, generator=g)
+                    if etp is None:
+                        p[le].normal_(0.0, std, generator=g)
+                    else:
+                        # draw the unsliced expert (same values under any width cut) and keep this rank's slice
+                        from halo_b200.parallel.expert_tensor_parallel import slice_expert_bank
+
+                        full_shape = ((p.shape[1] * etp.size, p.shape[2]) if p.etp_kind == "gate_up"
+                                      else (p.shape[1], p.shape[2] * etp.size))
+                        full = torch.empty(full_shape, dtype=p.dtype, device=dev).normal_(0.0, std, generator=g)
+                        p[le].copy_(slice_expert_bank(p.etp_kind, full[None], etp.rank, etp.size)[0])
             elif getattr(p, "tp_kind", None) is not None:
                 # draw the unsliced tensor (same values under any tensor-parallel width) and keep this rank's slice
                 from halo_b200.parallel.tensor_parallel import slice_for_rank

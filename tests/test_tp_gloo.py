@@ -69,3 +69,42 @@ def _worker(rank, world, preset):
 @pytest.mark.parametrize("preset", ["dense", "moe"])
 def test_tensor_parallel_matches_unsliced_model(preset):
     run_gloo_ranks(_worker, 2, args=(preset,), timeout=120.0)
+
+
+def _etp_worker(rank, world):
+    import dataclasses
+
+    import numpy as np
+    import torch.distributed as dist
+
+    from halo_b200.data.packing import pack_documents
+    from halo_b200.models.qwen3 import build_model
+    from halo_b200.parallel.expert_tensor_parallel import ExpertTensorParallel, unslice_expert_bank
+
+    cfg = dataclasses.replace(PRESETS["tiny-moe"](), num_hidden_layers=2)
+    rng = np.random.default_rng(2)
+    batch = pack_documents([rng.integers(0, cfg.vocab_size, size=n) for n in (40, 70, 18)])
+    etp = ExpertTensorParallel(dist.group.WORLD)
+    model = build_model(cfg, device="cpu", dtype=torch.float32, seed=6, expert_tensor_parallel=etp)
+    loss = model(batch.input_ids, batch.position_ids, batch.cu_seqlens, batch.labels)     # every rank: the same tokens
+    loss.backward()
+    ref = build_model(cfg, device="cpu", dtype=torch.float32, seed=6)
+    ref_loss = ref(batch.input_ids, batch.position_ids, batch.cu_seqlens, batch.labels)
+    ref_loss.backward()
+    assert torch.allclose(loss.detach(), ref_loss.detach(), rtol=1e-5, atol=1e-6)
+    ref_params = dict(ref.named_parameters())
+    for name, p in model.named_parameters():
+        kind = getattr(p, "etp_kind", None)
+        if kind is None:
+            assert torch.allclose(p.grad, ref_params[name].grad, rtol=2e-4, atol=2e-6), name   # replicated: same on every rank
+        else:
+            parts = [torch.empty_like(p.grad) for _ in range(world)]
+            dist.all_gather(parts, p.grad.contiguous())
+            assert torch.allclose(unslice_expert_bank(kind, parts), ref_params[name].grad, rtol=2e-4, atol=2e-6), name
+            wparts = [torch.empty_like(p.detach()) for _ in range(world)]
+            dist.all_gather(wparts, p.detach().contiguous())
+            assert torch.equal(unslice_expert_bank(kind, wparts), ref_params[name].detach()), name
+
+
+def test_expert_tensor_parallel_matches_unsliced_experts():
+    run_gloo_ranks(_etp_worker, 2, timeout=120.0)
