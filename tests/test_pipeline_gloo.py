@@ -60,3 +60,55 @@ def _worker(rank, world, schedule):
 @pytest.mark.parametrize("schedule", ["1f1b", "gpipe"])
 def test_pipeline_matches_unsplit_model(schedule):
     run_gloo_ranks(_worker, 2, args=(schedule,), timeout=90.0)
+
+
+def _train_worker(rank, world, out_path):
+    import dataclasses
+
+    import numpy as np
+    import torch.distributed as dist
+
+    from halo_b200.data.packing import synthetic_packed_batch
+    from halo_b200.models.config import PRESETS
+    from halo_b200.models.qwen3 import build_model
+    from halo_b200.parallel.pipeline import PipelineStage, build_stage_model
+    from halo_b200.trainers.engine import TrainEngine
+    from halo_b200.trainers.pipeline_engine import PipelineEngine
+
+    cfg = dataclasses.replace(PRESETS["tiny-moe"](), num_hidden_layers=4)
+    row, steps, n_micro = 96, 4, 3
+    batches = [[synthetic_packed_batch(row, cfg.vocab_size, seed=10 * s + i, lo=8, hi=48) for i in range(n_micro)]
+               for s in range(steps)]
+    if world > 1:
+        model = build_stage_model(cfg, rank, world, "cpu", dtype=torch.float32, seed=9, split=[2])
+        eng = PipelineEngine(PipelineStage(model, dist.group.WORLD, row), torch.optim.AdamW(model.parameters(), lr=3e-4),
+                             max_grad_norm=0.5)
+        curve = []
+        for mb in batches:
+            o = eng.train_step(mb)
+            curve.append([float(o.loss), float(o.grad_norm)])     # read now: the norm tensor is reused every step
+    else:
+        model = build_model(cfg, device="cpu", dtype=torch.float32, seed=9)
+        eng = TrainEngine(model, torch.optim.AdamW(model.parameters(), lr=3e-4), "cpu", max_grad_norm=0.5)
+        curve = []
+        for mb in batches:
+            norm = float(sum(b.n_scored for b in mb))
+            eng.global_scored_tokens = lambda batch, norm=norm: norm      # one normaliser for the whole step
+            total = 0.0
+            for i, b in enumerate(mb):
+                o = eng.train_step(b, accumulate=i < len(mb) - 1)
+                total += float(o.loss)
+            curve.append([total, float(o.grad_norm)])
+    if rank == 0:
+        np.save(out_path, np.asarray(curve))
+
+
+def test_pipeline_training_follows_the_single_process_curve(tmp_path):
+    import numpy as np
+
+    single, pp = str(tmp_path / "single.npy"), str(tmp_path / "pp.npy")
+    _train_worker(0, 1, single)
+    run_gloo_ranks(_train_worker, 2, args=(pp,), timeout=180.0)
+    a, b = np.load(single), np.load(pp)
+    assert np.max(np.abs(a[:, 0] - b[:, 0])) < 2e-3, (a, b)
+    assert np.max(np.abs(a[:, 1] - b[:, 1]) / a[:, 1]) < 5e-3, (a, b)
