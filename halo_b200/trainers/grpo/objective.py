@@ -65,3 +65,69 @@ def trust_region_breaker(is_weights: torch.Tensor, mask: torch.Tensor, clip_max:
     m = mask.to(torch.float32)
     frac = ((is_weights >= clip_max).to(torch.float32) * m).sum() / m.sum().clamp_min(1.0)
     return bool(frac > max_fraction)
+
+
+# ---- optional mask stages (off by default; halo/trainers/grpo/objective/logratio.py:205-257) -------------------
+def trajectory_sums(values: torch.Tensor, traj_ids: torch.Tensor, n_traj: int, mask: torch.Tensor) -> torch.Tensor:
+    out = torch.zeros(n_traj, dtype=torch.float32, device=values.device)
+    return out.scatter_add_(0, traj_ids.long(), values.float() * mask.float())
+
+
+def geometric_mean_band_mask(logratio: torch.Tensor, traj_ids: torch.Tensor, n_traj: int, mask: torch.Tensor,
+                             low: float = 0.5, high: float = 2.0) -> torch.Tensor:
+    """Per trajectory: exp(mean log-ratio over its response tokens) must lie in [low, high]; trajectories outside
+    the band are dropped whole. Returns a per-token bool mask (True = keep)."""
+    s = trajectory_sums(logratio, traj_ids, n_traj, mask)
+    n = trajectory_sums(torch.ones_like(logratio), traj_ids, n_traj, mask).clamp_min(1.0)
+    g = torch.exp(s / n)
+    keep = (g >= low) & (g <= high)
+    return keep[traj_ids.long()]
+
+
+def raw_ratio_veto_mask(logratio: torch.Tensor, traj_ids: torch.Tensor, n_traj: int, mask: torch.Tensor,
+                        max_ratio: float = 100.0) -> torch.Tensor:
+    """A single token whose raw ratio explodes vetoes its whole trajectory."""
+    bad = (torch.exp(logratio.clamp(max=50.0)) > max_ratio) & mask
+    hit = torch.zeros(n_traj, dtype=torch.float32, device=logratio.device).scatter_add_(0, traj_ids.long(), bad.float())
+    return (hit == 0)[traj_ids.long()]
+
+
+def off_policy_sequence_mask(logp_train: torch.Tensor, logp_sampler: torch.Tensor, advantages_tok: torch.Tensor,
+                             traj_ids: torch.Tensor, n_traj: int, mask: torch.Tensor, delta: float = 0.1) -> torch.Tensor:
+    """Off-policy sequence masking: a trajectory with NEGATIVE advantage whose mean sampler-to-trainer divergence
+    exceeds ``delta`` is dropped (it would push the policy away from something it no longer does)."""
+    div = trajectory_sums(logp_sampler - logp_train.detach(), traj_ids, n_traj, mask)
+    n = trajectory_sums(torch.ones_like(logp_train), traj_ids, n_traj, mask).clamp_min(1.0)
+    adv = torch.zeros(n_traj, dtype=torch.float32, device=logp_train.device).scatter_reduce_(
+        0, traj_ids.long(), advantages_tok.float(), reduce="amin", include_self=False)
+    drop = (adv < 0) & (div / n > delta)
+    return (~drop)[traj_ids.long()]
+
+
+# ---- relative rank rewards (halo/trainers/grpo/objective/relative_rewards.py:18-133) ------------------------------
+def dense_rank_rewards(keys: list[tuple], group_size: int) -> torch.Tensor:
+    """Hierarchical dense ranks inside each group: completions are ordered by a tuple of criteria (first criterion
+    dominates, later ones break ties) and receive rewards evenly spaced in [0, 1] by dense rank (equal keys share a
+    reward; a group whose keys are all equal gets 0.5 everywhere)."""
+    n = len(keys)
+    if n % group_size:
+        raise ValueError(f"{n} completions do not form whole groups of {group_size}")
+    out = torch.zeros(n, dtype=torch.float32)
+    for g0 in range(0, n, group_size):
+        group = keys[g0:g0 + group_size]
+        distinct = sorted(set(group))
+        if len(distinct) == 1:
+            out[g0:g0 + group_size] = 0.5
+            continue
+        rank = {k: i for i, k in enumerate(distinct)}
+        for i, k in enumerate(group):
+            out[g0 + i] = rank[k] / (len(distinct) - 1)
+    return out
+
+
+def centered_logprobs(logp_token: torch.Tensor, candidate_logps: torch.Tensor, candidate_mask: torch.Tensor) -> torch.Tensor:
+    """Score centring: subtract from a sampled token's log-prob the mean log-prob of the engine's candidate tokens
+    at that position (a control variate computed from the sampler's own top candidates)."""
+    m = candidate_mask.float()
+    mean = (candidate_logps * m).sum(-1) / m.sum(-1).clamp_min(1.0)
+    return logp_token - mean

@@ -153,3 +153,50 @@ def test_world_metrics_and_small_callbacks():
     for v in (1.0, 0.9, 0.95, 0.97):
         es.on_log(T, {"eval_loss": v})
     assert T.args.max_steps == 7
+
+
+def test_grpo_mask_stages_rank_rewards_reference_cache_and_async_source(tmp_path):
+    import time
+
+    import numpy as np
+
+    from halo_b200.trainers.grpo import objective as ob
+    from halo_b200.trainers.grpo.async_rollouts import AsyncRolloutSource
+    from halo_b200.trainers.grpo.reference_cache import ReferenceCache
+
+    traj = torch.tensor([0, 0, 0, 1, 1, 2, 2, 2])
+    mask = torch.ones(8, dtype=torch.bool)
+    logratio = torch.tensor([0.0, 0.1, -0.1, 2.0, 2.0, 0.0, 0.0, 6.0])
+    band = ob.geometric_mean_band_mask(logratio, traj, 3, mask, 0.5, 2.0)
+    assert band.tolist() == [True] * 3 + [False] * 2 + [False] * 3          # traj 1: e^2, traj 2: e^2 > 2
+    veto = ob.raw_ratio_veto_mask(logratio, traj, 3, mask, max_ratio=100.0)
+    assert veto.tolist() == [True] * 5 + [False] * 3                         # only traj 2 holds a ratio > 100
+    adv = torch.tensor([-1.0] * 3 + [1.0] * 2 + [-1.0] * 3)
+    opsm = ob.off_policy_sequence_mask(torch.zeros(8), torch.tensor([0.5] * 3 + [0.5] * 2 + [0.0] * 3), adv, traj, 3, mask, 0.1)
+    assert opsm.tolist() == [False] * 3 + [True] * 5                         # negative advantage AND divergent: traj 0 only
+    r = ob.dense_rank_rewards([(1, 0), (1, 5), (0, 9), (1, 5), (2, 2), (2, 2), (2, 2), (2, 2)], 4)
+    assert r.tolist() == [0.5, 1.0, 0.0, 1.0, 0.5, 0.5, 0.5, 0.5]
+    c = ob.centered_logprobs(torch.tensor([-1.0]), torch.tensor([[-1.0, -3.0, -9.0]]), torch.tensor([[True, True, False]]))
+    assert torch.allclose(c, torch.tensor([1.0]))
+
+    rows = [np.arange(3, dtype=np.float32), np.zeros(0, dtype=np.float32), np.ones(5, dtype=np.float32) * -2]
+    cache = ReferenceCache.build(str(tmp_path / "ref"), "k1", rows)
+    assert len(cache) == 3 and cache[0].tolist() == [0, 1, 2] and cache[1].size == 0 and cache[2].sum() == -10
+    assert ReferenceCache.exists(str(tmp_path / "ref"), "k1") and not ReferenceCache.exists(str(tmp_path / "ref"), "k2")
+
+    made = []
+
+    def generate(i, version):
+        made.append((i, version))
+        time.sleep(0.01)
+        return None if i >= 4 else [f"round{i}@v{version}"]
+
+    src = AsyncRolloutSource(generate, prefetch=1, max_staleness=1)
+    assert src(0) == ["round0@v0"]
+    src.pause()
+    src.resume(3)                         # three optimizer steps later: anything produced at version <= 1 is stale
+    got = src(1)
+    assert got is not None and got[0].endswith("@v3") and src.discarded >= 1
+    while src(0) is not None:
+        pass
+    src.close()
