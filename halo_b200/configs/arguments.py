@@ -18,6 +18,8 @@ class ModelArguments:
     init_from_scratch: bool = False
     torch_dtype: Literal["bfloat16", "float32"] = "bfloat16"
     trust_remote_code: bool = False
+    freeze_patterns: list[str] | None = None      # regexes of parameter names to freeze
+    train_only_patterns: list[str] | None = None  # or: train only what matches
     max_length: int = 0                     # 0 = the model's context window
 
     def __post_init__(self):

@@ -136,10 +136,17 @@ def load_policy_model(model_args, pc, device, runtime, gradient_checkpointing=Tr
         transport.configure(max_tokens=max_tokens, top_k=cfg.num_experts_per_tok, hidden=cfg.hidden_size,
                             n_local_experts=cfg.num_experts // transport.n_ranks)
     if model_args.init_from_scratch:
-        return build_model(cfg, device=device, dtype=dtype, transport=transport,
-                           gradient_checkpointing=gradient_checkpointing)
-    return from_pretrained(model_args.model_name_or_path, device=device, dtype=dtype, transport=transport,
-                           gradient_checkpointing=gradient_checkpointing)
+        model = build_model(cfg, device=device, dtype=dtype, transport=transport,
+                            gradient_checkpointing=gradient_checkpointing)
+    else:
+        model = from_pretrained(model_args.model_name_or_path, device=device, dtype=dtype, transport=transport,
+                                gradient_checkpointing=gradient_checkpointing)
+    if model_args.freeze_patterns or model_args.train_only_patterns:
+        from halo_b200.models.freeze import apply_freeze_patterns
+
+        stats = apply_freeze_patterns(model, model_args.freeze_patterns, model_args.train_only_patterns)
+        log.info("frozen %d parameters, training %d", stats["frozen"], stats["trainable"])
+    return model
 
 
 def load_tokenizer(model_args):

@@ -211,6 +211,11 @@ class Trainer:
 
     def save_checkpoint(self) -> str:
         d = self.checkpoint_dir()
+        if self.is_main:
+            from halo_b200.checkpoint.preflight import checkpoint_bytes, require_free_space
+
+            ep_world = self.parallel.ep_world if self.parallel is not None else 1
+            require_free_space(self.args.output_dir, checkpoint_bytes(self.model, ep_world=ep_world))
         os.makedirs(d, exist_ok=True)
         save_model(self.model, d, sharded_experts=self.args.save_sharded_ep, save_dtype=None,
                    group=self.group)  # exact resume: keep the dtype

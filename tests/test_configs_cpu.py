@@ -129,3 +129,40 @@ def test_prepared_dataset_round_trip_and_coordinated_cache(tmp_path):
     assert d1 == d2 == d3 and len(calls) == 1
     with pytest.raises(TimeoutError):
         pp.coordinated_cache(str(tmp_path / "cache"), ["b"], build, rank=1, wait_seconds=0.3, poll_seconds=0.05)
+
+
+def test_freeze_patterns_preflight_and_collators(tmp_path):
+    import dataclasses
+
+    import numpy as np
+    import pytest
+    import torch
+
+    from halo_b200.checkpoint.preflight import checkpoint_bytes, require_free_space
+    from halo_b200.data import collators
+    from halo_b200.models.config import PRESETS
+    from halo_b200.models.freeze import apply_freeze_patterns
+    from halo_b200.models.qwen3 import build_model
+
+    model = build_model(dataclasses.replace(PRESETS["tiny-moe"](), num_hidden_layers=2), device="cpu", dtype=torch.float32)
+    stats = apply_freeze_patterns(model, freeze=["embed_tokens", r"layers\.0\."])
+    assert not model.embed_tokens.requires_grad and not model.layers[0].self_attn.o_proj.requires_grad
+    assert model.layers[1].self_attn.o_proj.requires_grad and stats["frozen"] > 0 and stats["trainable"] > 0
+    with pytest.raises(ValueError, match="matches no parameter"):
+        apply_freeze_patterns(model, freeze=["no_such_tensor"])
+    apply_freeze_patterns(model, train_only=[r"mlp\.gate$"])
+    assert sum(p.requires_grad for p in model.parameters()) == 2
+    need = checkpoint_bytes(model, with_optimizer=False)
+    assert need == sum(p.numel() * 4 for p in model.parameters())
+    assert require_free_space(str(tmp_path / "new" / "dir"), 1024) > 0
+    with pytest.raises(OSError, match="GiB are free"):
+        require_free_space(str(tmp_path), 1 << 60)
+    docs = [np.arange(5), np.arange(3)]
+    assert collators.padding_free(docs).n_tokens == 8
+    fs = collators.fixed_shape(docs, 16)
+    assert fs.n_tokens == 16 and fs.cu_seqlens.tolist() == [0, 5, 8, 16] and fs.n_scored == 6
+    with pytest.raises(ValueError):
+        collators.fixed_shape(docs, 6)
+    pb = collators.padded(docs, pad_token_id=9, pad_to_multiple_of=4)
+    assert pb["input_ids"].shape == (2, 8) and pb["attention_mask"].sum().item() == 8 and pb["input_ids"][1, 3].item() == 9
+    assert pb["labels"][0, :4].tolist() == [1, 2, 3, 4] and pb["labels"][0, 4].item() == -100
