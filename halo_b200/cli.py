@@ -26,6 +26,8 @@ TOOLS = {
     "relayout-experts": "halo_b200.checkpoint.tools.relayout_experts",
     "patch-vocab": "halo_b200.checkpoint.tools.patch_vocab",
     "kernel-bench": "benchmarks.kernels",
+    "nvlink-health": "halo_b200.diagnostics.nvlink_health",
+    "prepare-dataset": "halo_b200.data.preprocessed",
     "bench": "bench",
 }
 
