@@ -1,9 +1,9 @@
 """Runtime parameter names <-> Hugging Face hub tensor names.
 
 At run time attention holds one fused ``qkv_proj``, the dense FFN one ``gate_up_proj`` and the
-routed experts two stacked banks; on disk a checkpoint uses the hub names of Qwen3 / Qwen3-MoE
-(``q_proj`` / ``k_proj`` / ``v_proj``, ``gate_proj`` / ``up_proj``, ``experts.{e}.gate_proj`` ...)
-so ``transformers`` loads it without custom code. The expert bank layouts are the kinds of the
+routed experts two stacked banks; on disk a checkpoint uses the hub names of its family
+(``q_proj`` / ``k_proj`` / ``v_proj``, ``gate_proj`` / ``up_proj``, ``experts.{e}.gate_proj`` ..., or Mixtral's
+``block_sparse_moe.experts.{e}.w1`` / ``w3`` / ``w2``) so ``transformers`` loads it without custom code. The expert bank layouts are the kinds of the
 reference's ``ExpertLayout`` (halo/models/moe/expert_layout.py:63-163): this family is
 ``SEPARATE_GLU`` on the hub and ``FUSED`` at run time.
 """
@@ -16,6 +16,12 @@ import torch
 
 EXPERT_LAYOUT_KINDS = ("FUSED", "FUSED_SPLIT_PER_EXPERT", "SEPARATE_GLU", "SEPARATE_MLP", "INTERLEAVED_GLU")
 _LAYER = re.compile(r"^layers\.(\d+)\.(.+)$")
+# family -> (feed-forward block, gate / up / down projection names of one expert) as the hub stores them
+MOE_HUB_NAMES = {
+    "qwen3_moe": ("mlp", "gate_proj", "up_proj", "down_proj"),
+    "qwen2_moe": ("mlp", "gate_proj", "up_proj", "down_proj"),
+    "mixtral": ("block_sparse_moe", "w1", "w3", "w2"),
+}
 
 
 def runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, expert_offset: int = 0) -> dict:
@@ -39,6 +45,9 @@ def runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, e
         q, k, v = tensor.split([Hq * D, Hkv * D, Hkv * D], dim=0)
         return {pre + "self_attn.q_proj.weight": q, pre + "self_attn.k_proj.weight": k,
                 pre + "self_attn.v_proj.weight": v}
+    if rest == "self_attn.qkv_bias":
+        q, k, v = tensor.split([Hq * D, Hkv * D, Hkv * D], dim=0)
+        return {pre + "self_attn.q_proj.bias": q, pre + "self_attn.k_proj.bias": k, pre + "self_attn.v_proj.bias": v}
     if rest == "self_attn.o_proj":
         return {pre + "self_attn.o_proj.weight": tensor}
     if rest in ("self_attn.q_norm", "self_attn.k_norm"):
@@ -48,17 +57,18 @@ def runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, e
         return {pre + "mlp.gate_proj.weight": g, pre + "mlp.up_proj.weight": u}
     if rest == "mlp.down_proj":
         return {pre + "mlp.down_proj.weight": tensor}
+    block, gate_name, up_name, down_name = MOE_HUB_NAMES.get(getattr(cfg, "family", ""), MOE_HUB_NAMES["qwen3_moe"])
     if rest == "mlp.gate":
-        return {pre + "mlp.gate.weight": tensor}
+        return {pre + f"{block}.gate.weight": tensor}
     if rest == "mlp.experts_gate_up":
         out = {}
         for le in range(tensor.shape[0]):
             g, u = tensor[le].chunk(2, dim=0)
-            out[pre + f"mlp.experts.{le + expert_offset}.gate_proj.weight"] = g
-            out[pre + f"mlp.experts.{le + expert_offset}.up_proj.weight"] = u
+            out[pre + f"{block}.experts.{le + expert_offset}.{gate_name}.weight"] = g
+            out[pre + f"{block}.experts.{le + expert_offset}.{up_name}.weight"] = u
         return out
     if rest == "mlp.experts_down":
-        return {pre + f"mlp.experts.{le + expert_offset}.down_proj.weight": tensor[le] for le in range(tensor.shape[0])}
+        return {pre + f"{block}.experts.{le + expert_offset}.{down_name}.weight": tensor[le] for le in range(tensor.shape[0])}
     if rest == "mlp.shared_expert.gate_up_proj":
         g, u = tensor.chunk(2, dim=0)
         return {pre + "mlp.shared_expert.gate_proj.weight": g, pre + "mlp.shared_expert.up_proj.weight": u}
@@ -78,12 +88,13 @@ def hub_sources(name: str, shape, cfg, first_layer: int = 0, expert_offset: int 
     m = _LAYER.match(name)
     rest = m.group(2) if m else name
     if rest in ("mlp.experts_gate_up", "mlp.experts_down"):
-        F = cfg.moe_intermediate_size
+        _, gate_name, up_name, _ = MOE_HUB_NAMES.get(getattr(cfg, "family", ""), MOE_HUB_NAMES["qwen3_moe"])
+        F = shape[1] // 2          # gate rows, then up rows, of the fused bank (unused for the down bank)
         for hub in pieces:
             e = int(re.search(r"experts\.(\d+)\.", hub).group(1)) - expert_offset
-            if hub.endswith("gate_proj.weight"):
+            if hub.endswith(f"{gate_name}.weight"):
                 out.append((hub, (e, 0, F)))
-            elif hub.endswith("up_proj.weight"):
+            elif hub.endswith(f"{up_name}.weight"):
                 out.append((hub, (e, F, 2 * F)))
             else:
                 out.append((hub, (e, 0, shape[1])))

@@ -55,9 +55,19 @@ def load_model_weights(model, directory: str, strict: bool = True) -> dict:
     ep_rank = getattr(tr, "rank", 0) if tr is not None else 0
     first_layer = model.layer_range[0]
     missing, loaded = [], 0
+    tp = getattr(model, "tensor_parallel", None)
+    etp = getattr(model, "expert_tensor_parallel", None)
     for name, p in model.named_parameters():
         is_expert = getattr(p, "is_expert", False)
         offset = ep_rank * p.shape[0] if is_expert else 0
+        tp_kind = getattr(p, "tp_kind", None) if tp is not None else None
+        etp_kind = getattr(p, "etp_kind", None) if etp is not None else None
+        if tp_kind is not None or etp_kind is not None:
+            # a width-sliced parameter: assemble the unsliced tensor from its hub pieces on the host, keep this
+            # rank's slice
+            n, got = _load_sliced(index, name, p, cfg, first_layer, offset, tp_kind, tp, etp_kind, etp, missing)
+            loaded += got
+            continue
         for hub, (e, lo, hi) in hub_sources(name, tuple(p.shape), cfg, first_layer, offset):
             if hub not in index:
                 if hub == "lm_head.weight" and "model.embed_tokens.weight" in index:
@@ -76,6 +86,43 @@ def load_model_weights(model, directory: str, strict: bool = True) -> dict:
         raise KeyError(f"{len(missing)} tensors are absent from {directory!r}, e.g. {missing[:4]}: refusing to leave "
                        f"parameters at their random initialisation")
     return {"loaded": loaded, "missing": missing}
+
+
+def _full_shape(p, cfg, tp_kind, tp, etp_kind, etp):
+    if tp_kind in ("qkv", "qkv_bias"):
+        return (cfg.qkv_dim, *p.shape[1:])
+    if tp_kind == "gate_up":
+        return (p.shape[0] * tp.size, p.shape[1])
+    if tp_kind in ("o", "down"):
+        return (p.shape[0], p.shape[1] * tp.size)
+    if etp_kind == "gate_up":
+        return (p.shape[0], p.shape[1] * etp.size, p.shape[2])
+    return (p.shape[0], p.shape[1], p.shape[2] * etp.size)
+
+
+def _load_sliced(index, name, p, cfg, first_layer, offset, tp_kind, tp, etp_kind, etp, missing):
+    shape = _full_shape(p, cfg, tp_kind, tp, etp_kind, etp)
+    full = torch.empty(shape, dtype=p.dtype)
+    got = 0
+    for hub, (e, lo, hi) in hub_sources(name, shape, cfg, first_layer, offset):
+        if hub not in index:
+            missing.append(hub)
+            continue
+        t = index.get(hub)
+        dst = full[e, lo:hi] if e is not None else full[lo:hi]
+        if tuple(t.shape) != tuple(dst.shape):
+            raise ValueError(f"{hub}: checkpoint shape {tuple(t.shape)} does not fit {tuple(dst.shape)}")
+        dst.copy_(t.to(dst.dtype))
+        got += 1
+    if tp_kind is not None:
+        from halo_b200.parallel.tensor_parallel import slice_for_rank
+
+        p.copy_(slice_for_rank(tp_kind, full, cfg, tp.rank, tp.size))
+    else:
+        from halo_b200.parallel.expert_tensor_parallel import slice_expert_bank
+
+        p.copy_(slice_expert_bank(etp_kind, full, etp.rank, etp.size))
+    return 1, got
 
 
 def from_pretrained(directory: str, device="cpu", dtype=None, transport=None, **kw):

@@ -121,13 +121,10 @@ def load_policy_model(model_args, pc, device, runtime, gradient_checkpointing=Tr
     reject_model_layout(pc, cfg)
     if isinstance(runtime, dict):          # tensor / context parallelism: needs the model's sizes to finish
         runtime = finish_token_cutting_runtime(runtime, cfg, max_tokens)
-        if not model_args.init_from_scratch and runtime.tensor_parallel is not None:
-            raise NotImplementedError("loading a checkpoint into tensor-parallel slices is not built: train from a preset "
-                                      "or load without tensor parallelism")
         model = build_model(cfg, device=device, dtype=dtype, gradient_checkpointing=gradient_checkpointing,
                             tensor_parallel=runtime.tensor_parallel) if model_args.init_from_scratch else \
             from_pretrained(model_args.model_name_or_path, device=device, dtype=dtype,
-                            gradient_checkpointing=gradient_checkpointing)
+                            gradient_checkpointing=gradient_checkpointing, tensor_parallel=runtime.tensor_parallel)
         model.context_parallel = runtime.context_parallel
         model.parallel_runtime = runtime
         return model

@@ -1,5 +1,7 @@
-"""Architecture description of the decoder families built here (Qwen3 dense and Qwen3-MoE shapes,
-plus the shared-expert variant), convertible to and from a Hugging Face ``config.json``.
+"""Architecture description of the decoder families built here, convertible to and from a Hugging Face
+``config.json``: Qwen3 and Qwen3-MoE (per-head q/k norm), Qwen2 (biased q/k/v projections), Qwen2-MoE (gated
+shared expert), Llama and Mistral (plain pre-norm decoder, optional rotary scaling) and Mixtral (top-k of
+softmax, ``block_sparse_moe`` names on the hub).
 
 The named presets are the shapes of the benchmark configurations: a tiny MoE for CPU plumbing
 tests, the dense 9B class, the 30B-A3B MoE and the ~120B-total shared-expert MoE.
@@ -10,6 +12,20 @@ from __future__ import annotations
 import json
 from dataclasses import asdict, dataclass, field
 from pathlib import Path
+
+
+# Per family: the Hugging Face architecture, whether q / k carry a per-head RMSNorm, whether the q / k / v bias is a
+# config key (Llama, Qwen3) or fixed by the family (Qwen2: always on), whether the config has a sliding window, and
+# how the hub names the feed-forward block and its experts.
+FAMILIES = {
+    "qwen3": dict(architecture="Qwen3ForCausalLM", moe=False, qk_norm=True, bias_key=True, bias_default=False, has_window=False),
+    "qwen3_moe": dict(architecture="Qwen3MoeForCausalLM", moe=True, qk_norm=True, bias_key=True, bias_default=False, has_window=False),
+    "qwen2": dict(architecture="Qwen2ForCausalLM", moe=False, qk_norm=False, bias_key=False, bias_default=True, has_window=True),
+    "qwen2_moe": dict(architecture="Qwen2MoeForCausalLM", moe=True, qk_norm=False, bias_key=False, bias_default=True, has_window=True),
+    "llama": dict(architecture="LlamaForCausalLM", moe=False, qk_norm=False, bias_key=True, bias_default=False, has_window=False),
+    "mistral": dict(architecture="MistralForCausalLM", moe=False, qk_norm=False, bias_key=False, bias_default=False, has_window=True),
+    "mixtral": dict(architecture="MixtralForCausalLM", moe=True, qk_norm=False, bias_key=False, bias_default=False, has_window=True),
+}
 
 
 @dataclass
@@ -32,6 +48,8 @@ class ModelConfig:
     rope_theta: float = 1e6
     rms_norm_eps: float = 1e-6
     use_qk_norm: bool = True
+    attention_bias: bool = False           # bias on the q / k / v projections (Qwen2)
+    rope_scaling: dict | None = None       # Hugging Face ``rope_scaling`` / ``rope_parameters`` entry, None = plain
     tie_word_embeddings: bool = False
     router_aux_loss_coef: float = 0.0
     initializer_range: float = 0.02
@@ -52,7 +70,8 @@ class ModelConfig:
     # ---- parameter counts (for MFU and memory planning) ---------------------------------
     def param_counts(self) -> dict[str, int]:
         H, D = self.hidden_size, self.head_dim
-        attn = H * self.qkv_dim + self.num_attention_heads * D * H + (2 * D if self.use_qk_norm else 0) + 2 * H
+        attn = (H * self.qkv_dim + self.num_attention_heads * D * H + (2 * D if self.use_qk_norm else 0) + 2 * H
+                + (self.qkv_dim if self.attention_bias else 0))
         dense_mlp = 3 * H * self.intermediate_size
         expert = 3 * H * self.moe_intermediate_size
         shared = 3 * H * self.shared_expert_intermediate_size + (H if self.shared_expert_gate else 0)
@@ -71,9 +90,14 @@ class ModelConfig:
 
     # ---- Hugging Face interchange -------------------------------------------------------
     def to_hf_dict(self) -> dict:
+        fam = FAMILIES[self.family]
+        rope = {"rope_type": "default", "rope_theta": self.rope_theta}
+        if self.rope_scaling:
+            rope = {**self.rope_scaling, "rope_theta": self.rope_theta}
+            rope.setdefault("rope_type", rope.pop("type", "default"))
         d = {
-            "architectures": ["Qwen3MoeForCausalLM" if self.is_moe else "Qwen3ForCausalLM"],
-            "model_type": "qwen3_moe" if self.is_moe else "qwen3",
+            "architectures": [fam["architecture"]],
+            "model_type": self.family,
             "vocab_size": self.vocab_size,
             "hidden_size": self.hidden_size,
             "num_hidden_layers": self.num_hidden_layers,
@@ -83,17 +107,28 @@ class ModelConfig:
             "intermediate_size": self.intermediate_size,
             "hidden_act": "silu",
             "rope_theta": self.rope_theta,
-            "rope_parameters": {"rope_type": "default", "rope_theta": self.rope_theta},
+            "rope_parameters": rope,
             "rms_norm_eps": self.rms_norm_eps,
             "tie_word_embeddings": self.tie_word_embeddings,
-            "attention_bias": False,
             "attention_dropout": 0.0,
             "initializer_range": self.initializer_range,
             "max_position_embeddings": self.max_position_embeddings,
             "torch_dtype": "bfloat16",
             "use_cache": False,
         }
-        if self.is_moe:
+        if self.rope_scaling:
+            d["rope_scaling"] = {k: v for k, v in rope.items() if k != "rope_theta"}
+        if fam["bias_key"]:
+            d["attention_bias"] = self.attention_bias
+        elif self.family == "qwen2_moe":
+            d["qkv_bias"] = self.attention_bias
+        if fam["has_window"]:
+            d["sliding_window"] = None
+        if self.family == "mixtral":
+            d.update({"num_local_experts": self.num_experts, "num_experts_per_tok": self.num_experts_per_tok,
+                      "router_aux_loss_coef": self.router_aux_loss_coef, "output_router_logits": False,
+                      "intermediate_size": self.moe_intermediate_size})
+        elif self.is_moe:
             d.update({
                 "moe_intermediate_size": self.moe_intermediate_size,
                 "num_experts": self.num_experts,
@@ -108,24 +143,52 @@ class ModelConfig:
                 d["shared_expert_intermediate_size"] = self.shared_expert_intermediate_size
         return d
 
+    @property
+    def family(self) -> str:
+        """The Hugging Face ``model_type`` this configuration is written as."""
+        if self.model_type in FAMILIES and FAMILIES[self.model_type]["moe"] == self.is_moe:
+            return self.model_type
+        return "qwen3_moe" if self.is_moe else "qwen3"
+
     @classmethod
     def from_hf_dict(cls, d: dict) -> "ModelConfig":
         mt = d.get("model_type", "qwen3")
-        if mt not in ("qwen3", "qwen3_moe", "qwen2_moe"):
-            raise ValueError(f"model_type {mt!r} has no family registered here")
-        rope_theta = d.get("rope_theta") or (d.get("rope_parameters") or {}).get("rope_theta", 1e6)
+        if mt not in FAMILIES:
+            raise ValueError(f"model_type {mt!r} has no family registered here (known: {sorted(FAMILIES)})")
+        fam = FAMILIES[mt]
+        window = d.get("sliding_window")
+        if fam["has_window"] and window and d.get("use_sliding_window", True) and window < d.get("max_position_embeddings", 0):
+            raise ValueError(f"{mt} checkpoint with sliding_window={window}: windowed attention is not built; "
+                             f"only full causal attention over each document")
+        rp = d.get("rope_parameters") or {}
+        rope_theta = d.get("rope_theta") or rp.get("rope_theta", 1e6 if mt.startswith("qwen") else 1e4)
+        scaling = d.get("rope_scaling") or ({k: v for k, v in rp.items() if k != "rope_theta"} if rp else None)
+        if scaling:
+            scaling = dict(scaling)
+            scaling.setdefault("rope_type", scaling.pop("type", "default"))
+            if scaling["rope_type"] == "default":
+                scaling = None
         hd = d.get("head_dim") or d["hidden_size"] // d["num_attention_heads"]
+        if mt == "mixtral":
+            n_exp, width, dense_width = d.get("num_local_experts", 8), d["intermediate_size"], d["intermediate_size"]
+            topk, renorm = d.get("num_experts_per_tok", 2), True
+        else:
+            n_exp = d.get("num_experts", 0) if fam["moe"] else 0
+            width, dense_width = d.get("moe_intermediate_size", 0), d.get("intermediate_size", 0)
+            topk, renorm = d.get("num_experts_per_tok", 8), d.get("norm_topk_prob", mt != "qwen2_moe")
         return cls(
             vocab_size=d["vocab_size"], hidden_size=d["hidden_size"], num_hidden_layers=d["num_hidden_layers"],
             num_attention_heads=d["num_attention_heads"],
             num_key_value_heads=d.get("num_key_value_heads", d["num_attention_heads"]), head_dim=hd,
-            intermediate_size=d.get("intermediate_size", 0), moe_intermediate_size=d.get("moe_intermediate_size", 0),
-            num_experts=d.get("num_experts", 0) if mt != "qwen3" else 0,
-            num_experts_per_tok=d.get("num_experts_per_tok", 8), norm_topk_prob=d.get("norm_topk_prob", True),
+            intermediate_size=dense_width, moe_intermediate_size=width,
+            num_experts=n_exp, num_experts_per_tok=topk, norm_topk_prob=renorm,
             shared_expert_intermediate_size=d.get("shared_expert_intermediate_size", 0) or 0,
             shared_expert_gate=(mt == "qwen2_moe"),
             mlp_only_layers=list(d.get("mlp_only_layers", []) or []), decoder_sparse_step=d.get("decoder_sparse_step", 1),
-            rope_theta=float(rope_theta), rms_norm_eps=d.get("rms_norm_eps", 1e-6), use_qk_norm=(mt != "qwen2_moe"),
+            rope_theta=float(rope_theta), rms_norm_eps=d.get("rms_norm_eps", 1e-6), use_qk_norm=fam["qk_norm"],
+            attention_bias=(bool(d.get("attention_bias", False)) if fam["bias_key"]
+                            else bool(d.get("qkv_bias", fam["bias_default"]))),
+            rope_scaling=scaling,
             tie_word_embeddings=d.get("tie_word_embeddings", False),
             router_aux_loss_coef=d.get("router_aux_loss_coef", 0.0), initializer_range=d.get("initializer_range", 0.02),
             max_position_embeddings=d.get("max_position_embeddings", 262144), model_type=mt,

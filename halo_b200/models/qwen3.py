@@ -1,4 +1,5 @@
-"""Qwen3 / Qwen3-MoE decoder over packed rows, with every hot op on the sm_100a kernels.
+"""Pre-norm decoder (Qwen3 / Qwen3-MoE, and the Qwen2, Llama, Mistral and Mixtral variants of it that the
+configuration's family switches select) over packed rows, with every hot op on the sm_100a kernels.
 
 The model consumes one flattened token stream ``[T]`` per rank (documents delimited by
 ``cu_seqlens``), as the packing collator produces it. Parameter names follow the Hugging Face
@@ -91,6 +92,13 @@ class Attention(nn.Module):
         self.o_proj = nn.Parameter(torch.empty(H, self.n_heads * D, dtype=dtype, device=device))
         if tp_size > 1:
             self.qkv_proj.tp_kind, self.o_proj.tp_kind = "qkv", "o"
+        # Qwen2 puts a bias on q / k / v (not on o); under tensor parallelism it is cut like the rows it belongs to
+        if cfg.attention_bias:
+            self.qkv_bias = nn.Parameter(torch.zeros((self.n_heads + 2 * self.n_kv_heads) * D, dtype=dtype, device=device))
+            if tp_size > 1:
+                self.qkv_bias.tp_kind = "qkv_bias"
+        else:
+            self.register_parameter("qkv_bias", None)
         if cfg.use_qk_norm:
             self.q_norm = nn.Parameter(torch.ones(D, dtype=dtype, device=device))
             self.k_norm = nn.Parameter(torch.ones(D, dtype=dtype, device=device))
@@ -98,17 +106,20 @@ class Attention(nn.Module):
             self.register_parameter("q_norm", None)
             self.register_parameter("k_norm", None)
 
+    def _biased(self, qkv):
+        return qkv if self.qkv_bias is None else qkv + self.qkv_bias
+
     def forward(self, h, ctx):
         cfg = self.cfg
         if ctx.tp is not None:
             # token shards -> whole row, a slice of the heads, partial output summed back into token shards
             from halo_b200.parallel.tensor_parallel import gather_seq, row_parallel_linear
 
-            qkv = gemm.linear(gather_seq(h, ctx.tp), self.qkv_proj)
+            qkv = self._biased(gemm.linear(gather_seq(h, ctx.tp), self.qkv_proj))
             o = attn_ops.rope_attention(qkv, self.q_norm, self.k_norm, ctx.rope, ctx.plan, self.n_heads, self.n_kv_heads,
                                         cfg.rms_norm_eps, cfg.use_qk_norm)
             return row_parallel_linear(o, self.o_proj, ctx.tp)
-        qkv = gemm.linear(h, self.qkv_proj)
+        qkv = self._biased(gemm.linear(h, self.qkv_proj))
         if ctx.cp is not None:
             # context parallel: this rank holds one chunk of the row; keys and values of straddling documents
             # come from the lower ranks
@@ -309,7 +320,7 @@ class Qwen3Model(nn.Module):
         first = self.layer_range[0]
         for name, p in self.named_parameters():
             if p.dim() == 1:
-                p.fill_(1.0)
+                p.fill_(0.0 if name.endswith("bias") else 1.0)
                 continue
             dev = p.device
             if first and name.startswith("layers."):
@@ -338,7 +349,7 @@ class Qwen3Model(nn.Module):
                 from halo_b200.parallel.tensor_parallel import slice_for_rank
 
                 tp = self.tensor_parallel
-                full_shape = {"qkv": (self.cfg.qkv_dim, p.shape[1]), "o": (p.shape[0], p.shape[1] * tp.size),
+                full_shape = {"qkv": (self.cfg.qkv_dim, *p.shape[1:]), "qkv_bias": (self.cfg.qkv_dim,), "o": (p.shape[0], p.shape[1] * tp.size),
                               "gate_up": (p.shape[0] * tp.size, p.shape[1]), "down": (p.shape[0], p.shape[1] * tp.size)}[p.tp_kind]
                 g = torch.Generator(device=dev).manual_seed(base)
                 full = torch.empty(full_shape, dtype=p.dtype, device=dev).normal_(0.0, std, generator=g)
@@ -352,7 +363,8 @@ class Qwen3Model(nn.Module):
         """``cu_seqlens`` always describes the whole packed row; under context parallelism ``position_ids``
         (like the token ids) are this rank's chunk of it."""
         dev = position_ids.device
-        rope = rope_table(position_ids, self.cfg.head_dim, self.cfg.rope_theta)
+        rope = rope_table(position_ids, self.cfg.head_dim, self.cfg.rope_theta, self.cfg.rope_scaling,
+                          self.cfg.max_position_embeddings)
         if self.context_parallel is not None:
             layout, plan = self.context_parallel.layout_and_plan(cu_seqlens)
             return ForwardContext(plan, rope, self.transport, record_routing, replay_topk, (self.context_parallel, layout))

@@ -11,6 +11,9 @@ halo/distributed/context_parallel/ulysses_attention.py:63-76) after the HF q_nor
 
 from __future__ import annotations
 
+import json
+import math
+
 import torch
 
 from . import _lib
@@ -18,11 +21,74 @@ from . import _lib
 HEAD_DIM = 128
 
 
-def rope_table(position_ids: torch.Tensor, head_dim: int, theta: float) -> torch.Tensor:
-    """``[T, head_dim/2, 2]`` fp32 (cos, sin), each rounded to bf16 as the HF module does."""
+def scaled_inverse_frequencies(head_dim: int, theta: float, scaling: dict, max_positions: int = 0):
+    """Inverse frequencies ``[head_dim/2]`` (fp32, CPU) and the factor applied to cos / sin for a Hugging Face
+    ``rope_scaling`` entry: ``linear`` (positions divided by ``factor``), ``llama3`` (low frequencies divided by
+    ``factor``, a smooth ramp between the two wavelength bounds) and ``yarn`` (per-frequency blend of interpolation
+    and extrapolation, with the attention temperature folded into cos / sin)."""
+    kind = scaling.get("rope_type", scaling.get("type", "default"))
+    half = head_dim // 2
+    inv = theta ** (-torch.arange(0, half, dtype=torch.float32) * 2.0 / head_dim)
+    if kind == "default":
+        return inv, 1.0
+    factor = float(scaling["factor"])
+    if kind == "linear":
+        return inv / factor, 1.0
+    if kind == "llama3":
+        low, high = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
+        old = float(scaling["original_max_position_embeddings"])
+        wavelen = 2.0 * math.pi / inv
+        smooth = (old / wavelen - low) / (high - low)
+        blended = (1.0 - smooth) * inv / factor + smooth * inv
+        out = torch.where(wavelen > old / low, inv / factor, inv)
+        mid = (wavelen <= old / low) & (wavelen >= old / high)
+        return torch.where(mid, blended, out), 1.0
+    if kind == "yarn":
+        old = float(scaling.get("original_max_position_embeddings") or max_positions)
+        beta_fast, beta_slow = float(scaling.get("beta_fast") or 32.0), float(scaling.get("beta_slow") or 1.0)
+        mscale, mscale_all = scaling.get("mscale"), scaling.get("mscale_all_dim")
+
+        def temperature(scale, m=1.0):
+            return 1.0 if scale <= 1.0 else 0.1 * m * math.log(scale) + 1.0
+
+        attention_factor = scaling.get("attention_factor")
+        if attention_factor is None:
+            attention_factor = (temperature(factor, mscale) / temperature(factor, mscale_all)
+                                if mscale and mscale_all else temperature(factor))
+
+        def correction_dim(rotations):
+            return head_dim * math.log(old / (rotations * 2.0 * math.pi)) / (2.0 * math.log(theta))
+
+        lo, hi = correction_dim(beta_fast), correction_dim(beta_slow)
+        if scaling.get("truncate", True):
+            lo, hi = math.floor(lo), math.ceil(hi)
+        lo, hi = max(lo, 0), min(hi, head_dim - 1)
+        if lo == hi:
+            hi += 0.001
+        ramp = ((torch.arange(half, dtype=torch.float32) - lo) / (hi - lo)).clamp(0, 1)
+        extrapolation_share = 1.0 - ramp
+        return (inv / factor) * (1.0 - extrapolation_share) + inv * extrapolation_share, float(attention_factor)
+    raise ValueError(f"rope scaling of type {kind!r} is not built (known: default, linear, llama3, yarn)")
+
+
+_SCALED_CACHE: dict = {}
+
+
+def rope_table(position_ids: torch.Tensor, head_dim: int, theta: float, scaling: dict | None = None,
+               max_positions: int = 0) -> torch.Tensor:
+    """``[T, head_dim/2, 2]`` fp32 (cos, sin), each rounded to bf16 as the HF module does. With ``scaling`` the
+    frequencies come from :func:`scaled_inverse_frequencies` (built once per configuration, kept on the device)."""
     pos = position_ids.reshape(-1)
     T = pos.shape[0]
     half = head_dim // 2
+    if scaling:
+        key = (head_dim, theta, json.dumps(scaling, sort_keys=True), max_positions, str(pos.device))
+        if key not in _SCALED_CACHE:
+            inv, factor = scaled_inverse_frequencies(head_dim, theta, scaling, max_positions)
+            _SCALED_CACHE[key] = (inv.to(pos.device), factor)
+        inv, factor = _SCALED_CACHE[key]
+        ang = pos.float()[:, None] * inv[None, :]
+        return torch.stack([(ang.cos() * factor).bfloat16().float(), (ang.sin() * factor).bfloat16().float()], dim=-1)
     if not pos.is_cuda:
         inv = theta ** (-torch.arange(0, half, dtype=torch.float32) * 2.0 / head_dim)
         ang = pos.float()[:, None] * inv[None, :]

@@ -191,7 +191,7 @@ def slice_for_rank(kind: str, full: torch.Tensor, cfg, rank: int, size: int) -> 
     """This rank's slice of a full weight. ``kind``: ``qkv`` (rows: heads of q, k, v), ``o`` (columns: q heads),
     ``gate_up`` (rows: gate and up halves), ``down`` (columns)."""
     D = cfg.head_dim
-    if kind == "qkv":
+    if kind in ("qkv", "qkv_bias"):      # the bias of the fused projection is cut like its rows
         Hq, Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
         q, k, v = full.split([Hq * D, Hkv * D, Hkv * D], dim=0)
         nq, nk = Hq // size * D, Hkv // size * D
@@ -212,7 +212,7 @@ def slice_for_rank(kind: str, full: torch.Tensor, cfg, rank: int, size: int) -> 
 def unslice(kind: str, parts: list[torch.Tensor], cfg) -> torch.Tensor:
     """Inverse of :func:`slice_for_rank` given every rank's slice in rank order."""
     size, D = len(parts), cfg.head_dim
-    if kind == "qkv":
+    if kind in ("qkv", "qkv_bias"):
         nq, nk = cfg.num_attention_heads // size * D, cfg.num_key_value_heads // size * D
         qs, ks, vs = zip(*(p.split([nq, nk, nk], dim=0) for p in parts))
         return torch.cat(list(qs) + list(ks) + list(vs), dim=0)

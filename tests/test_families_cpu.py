@@ -1,0 +1,94 @@
+"""Decoder families beyond Qwen3: a model of each family, saved in hub layout, loads in ``transformers`` (which
+converts the hub names itself) and gives our logits; a checkpoint written by ``transformers`` loads here; rotary
+scaling follows the Hugging Face frequencies; windowed checkpoints are refused by name."""
+
+import numpy as np
+import pytest
+import torch
+
+from halo_b200.checkpoint.load import from_pretrained
+from halo_b200.checkpoint.save import save_model
+from halo_b200.data.packing import pack_documents
+from halo_b200.models.config import FAMILIES, ModelConfig
+from halo_b200.models.qwen3 import build_model
+from halo_b200.ops.rope import scaled_inverse_frequencies
+
+LLAMA3 = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+          "original_max_position_embeddings": 64}
+YARN = {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 32}
+
+
+def family_config(family: str, **kw) -> ModelConfig:
+    base = dict(vocab_size=512, hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                head_dim=32, intermediate_size=192, moe_intermediate_size=0, num_experts=0, model_type=family, rope_theta=10000.0,
+                max_position_embeddings=256, use_qk_norm=FAMILIES[family]["qk_norm"],
+                attention_bias=FAMILIES[family]["bias_default"])
+    if FAMILIES[family]["moe"]:
+        base.update(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=96, norm_topk_prob=True)
+    if family == "mixtral":
+        base.update(intermediate_size=96)
+    if family == "qwen2_moe":
+        base.update(shared_expert_intermediate_size=64, shared_expert_gate=True, norm_topk_prob=False)
+    base.update(kw)
+    return ModelConfig(**base)
+
+
+def logits_of(model, ids):
+    b = pack_documents([ids])
+    with torch.no_grad():
+        return model.hidden_states(b.input_ids, b.position_ids, b.cu_seqlens) @ model.head_weight().t(), b
+
+
+CASES = [("llama", {}), ("llama", {"rope_scaling": LLAMA3}), ("llama", {"attention_bias": True}), ("mistral", {}),
+         ("qwen2", {}), ("qwen2", {"rope_scaling": YARN}), ("mixtral", {}), ("qwen2_moe", {})]
+
+
+@pytest.mark.parametrize("family,extra", CASES, ids=[f"{f}-{'-'.join(e) or 'plain'}" for f, e in CASES])
+def test_family_round_trip_through_transformers(tmp_path, family, extra):
+    transformers = pytest.importorskip("transformers")
+    cfg = family_config(family, **extra)
+    model = build_model(cfg, device="cpu", seed=5, gradient_checkpointing=False)
+    if cfg.attention_bias:
+        with torch.no_grad():
+            for layer in model.layers:       # a zero bias would hide a wrong split
+                layer.self_attn.qkv_bias.normal_(0.0, 0.5, generator=torch.Generator().manual_seed(11))
+    d = str(tmp_path / "hf")
+    save_model(model, d, save_dtype=None)
+    assert ModelConfig.load(d) == cfg
+    hf = transformers.AutoModelForCausalLM.from_pretrained(d, torch_dtype=torch.float32, attn_implementation="eager")
+    hf.eval()
+    assert type(hf).__name__ == FAMILIES[family]["architecture"]
+    ids = np.random.default_rng(2).integers(0, cfg.vocab_size, size=96)
+    ours, b = logits_of(model, ids)
+    with torch.no_grad():
+        theirs = hf(input_ids=b.input_ids[None]).logits[0]
+    assert (ours - theirs).abs().max().item() < 5e-2 * theirs.abs().max().item()
+    # and the other way: what transformers writes loads here, tensor for tensor
+    d2 = str(tmp_path / "from_hf")
+    hf.save_pretrained(d2, safe_serialization=True)
+    back = from_pretrained(d2, device="cpu", dtype=torch.float32, gradient_checkpointing=False)
+    for (n, a), (_, c) in zip(model.named_parameters(), back.named_parameters()):
+        assert torch.equal(a, c), n
+
+
+@pytest.mark.parametrize("scaling", [LLAMA3, YARN, {"rope_type": "linear", "factor": 2.0}])
+def test_scaled_frequencies_match_transformers(scaling):
+    pytest.importorskip("transformers")
+    from transformers import LlamaConfig
+    from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
+
+    hf_cfg = LlamaConfig(hidden_size=128, num_attention_heads=4, head_dim=32, max_position_embeddings=256,
+                         rope_parameters={**scaling, "rope_theta": 10000.0})
+    want, want_factor = ROPE_INIT_FUNCTIONS[scaling["rope_type"]](hf_cfg, "cpu")
+    got, factor = scaled_inverse_frequencies(32, 10000.0, scaling, 256)
+    assert torch.allclose(got, want, rtol=1e-6, atol=0)
+    assert abs(factor - want_factor) < 1e-6
+
+
+def test_windowed_checkpoint_is_refused_by_name():
+    d = family_config("mistral").to_hf_dict()
+    d["sliding_window"] = 64
+    with pytest.raises(ValueError, match="sliding_window=64"):
+        ModelConfig.from_hf_dict(d)
+    with pytest.raises(ValueError, match="no family registered"):
+        ModelConfig.from_hf_dict({**d, "model_type": "mamba"})

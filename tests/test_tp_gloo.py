@@ -108,3 +108,38 @@ def _etp_worker(rank, world):
 
 def test_expert_tensor_parallel_matches_unsliced_experts():
     run_gloo_ranks(_etp_worker, 2, timeout=120.0)
+
+
+def _sliced_load_worker(rank, world, directory):
+    import torch.distributed as dist
+
+    from halo_b200.checkpoint.load import from_pretrained
+    from halo_b200.parallel.tensor_parallel import TensorParallel, gather_full_weight
+
+    tp = TensorParallel(dist.group.WORLD, "cpu")
+    whole = from_pretrained(directory, device="cpu", dtype=torch.float32)
+    sliced = from_pretrained(directory, device="cpu", dtype=torch.float32, tensor_parallel=tp)
+    want = dict(whole.named_parameters())
+    n_sliced = 0
+    for name, p in sliced.named_parameters():
+        kind = getattr(p, "tp_kind", None)
+        got = p.detach() if kind is None else gather_full_weight(kind, p.detach(), whole.cfg, tp)
+        n_sliced += kind is not None
+        assert torch.equal(got, want[name].detach()), name
+    assert n_sliced == 5 * whole.cfg.num_hidden_layers      # qkv, its bias, o, gate_up, down
+
+
+def test_checkpoint_loads_into_tensor_parallel_slices(tmp_path):
+    from halo_b200.checkpoint.save import save_model
+    from halo_b200.models.qwen3 import build_model
+
+    cfg = ModelConfig(vocab_size=512, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                      head_dim=16, intermediate_size=96, moe_intermediate_size=0, num_experts=0, model_type="qwen2",
+                      use_qk_norm=False, attention_bias=True)
+    model = build_model(cfg, device="cpu", seed=9)
+    with torch.no_grad():
+        for layer in model.layers:
+            layer.self_attn.qkv_bias.normal_(0.0, 0.3, generator=torch.Generator().manual_seed(2))
+    d = str(tmp_path / "ckpt")
+    save_model(model, d, save_dtype=None)
+    run_gloo_ranks(_sliced_load_worker, 2, args=(d,), timeout=120.0)
