@@ -43,12 +43,46 @@ def _gather_expert_bank(t: torch.Tensor, n_ranks: int, group) -> torch.Tensor:
 
 def save_model(model, directory: str, is_writer: bool | None = None, save_dtype: torch.dtype | None = torch.bfloat16,
                max_shard_bytes: int = 5 * 1024**3, sharded_experts: bool = False, extra_state: dict | None = None,
-               group=None) -> None:
+               group=None, adapters: str = "auto") -> None:
     """COLLECTIVE over the expert group when experts are sharded. ``is_writer``: this rank writes the
     files (default: global rank 0). ``sharded_experts``: every rank writes only its own experts to
     ``ep_shard_<rank>/`` (merge offline with halo_b200.checkpoint.tools.merge_ep_shards). ``group``: the
-    ranks that take part in the save (default: the whole job); failures are agreed over it."""
+    ranks that take part in the save (default: the whole job); failures are agreed over it. ``adapters``: a model
+    that carries low-rank adapters saves only them in the PEFT layout (``"auto"``), or its weights with the adapters
+    folded in (``"merge"``)."""
     cfg = model.cfg
+    lora = getattr(model, "lora_spec", None)
+    if lora is not None and adapters != "merge":
+        from halo_b200.peft.lora import save_adapters
+
+        live = dist.is_available() and dist.is_initialized()
+        writer_rank = (dist.get_rank(group) == 0) if live else True
+        guard = DeferredRankFailure()
+        with guard.catch():
+            save_adapters(model, directory, base_model=getattr(model, "base_model_path", ""),
+                          is_writer=writer_rank if is_writer is None else is_writer)
+            if extra_state is not None and (writer_rank if is_writer is None else is_writer):
+                atomic_write_json(os.path.join(directory, "halo_state.json"), extra_state)
+        guard.raise_if_any(None if not live else (group or dist.group.WORLD), "saving the adapters failed")
+        return
+
+    def saved_tensor(name, p):
+        if lora is None:
+            return p.detach()
+        from halo_b200.peft.lora import merged_weight
+
+        return merged_weight(model, name, p)
+
+    def base_parameters():
+        if lora is None:
+            yield from model.named_parameters()
+            return
+        from halo_b200.peft.lora import is_adapter_parameter
+
+        for name, p in model.named_parameters():
+            if not is_adapter_parameter(name):
+                yield name, p
+
     n_ep, ep_rank, ep_group = _ep_info(model)
     live = dist.is_available() and dist.is_initialized()
     rank = dist.get_rank(group) if live else 0
@@ -66,10 +100,10 @@ def save_model(model, directory: str, is_writer: bool | None = None, save_dtype:
             writer = StreamingShardWriter(directory, max_shard_bytes, save_dtype)
     # 1. non-expert tensors (replicated: taken from the writer's copy)
     tp = getattr(model, "tensor_parallel", None)
-    for name, p in model.named_parameters():
+    for name, p in base_parameters():
         if getattr(p, "is_expert", False):
             continue
-        t_full = p.detach()
+        t_full = saved_tensor(name, p)
         if tp is not None and getattr(p, "tp_kind", None) is not None:
             from halo_b200.parallel.tensor_parallel import gather_full_weight
 
@@ -79,15 +113,15 @@ def save_model(model, directory: str, is_writer: bool | None = None, save_dtype:
                 for hub, t in runtime_to_hub(name, t_full, cfg, first_layer).items():
                     writer.add(hub, t)
     # 2. expert banks, one layer at a time
-    for name, p in model.named_parameters():
+    for name, p in base_parameters():
         if not getattr(p, "is_expert", False):
             continue
         if sharded_experts and n_ep > 1:
             with guard.catch():
-                for hub, t in runtime_to_hub(name, p.detach(), cfg, first_layer, ep_rank * p.shape[0]).items():
+                for hub, t in runtime_to_hub(name, saved_tensor(name, p), cfg, first_layer, ep_rank * p.shape[0]).items():
                     writer.add(hub, t)
             continue
-        local = p.detach()
+        local = saved_tensor(name, p)
         etp = getattr(model, "expert_tensor_parallel", None)
         if etp is not None and getattr(p, "etp_kind", None) is not None:
             from halo_b200.parallel.expert_tensor_parallel import unslice_expert_bank

@@ -21,8 +21,27 @@ class ModelArguments:
     freeze_patterns: list[str] | None = None      # regexes of parameter names to freeze
     train_only_patterns: list[str] | None = None  # or: train only what matches
     max_length: int = 0                     # 0 = the model's context window
+    use_peft: bool = False                  # train low-rank adapters on frozen base weights
+    lora_r: int = 16
+    lora_alpha: float = 32.0
+    lora_dropout: float = 0.0
+    lora_target_modules: list[str] | str | None = None   # hub projection names, "experts.<name>" for routed experts, or "all-linear"
+    adapter_path: str = ""                  # adapters to continue from (a directory holding adapter_model.safetensors)
+    merge_adapters_on_save: bool = False    # save full weights with the adapters folded in instead of the adapters alone
+
+    def lora_spec(self):
+        from halo_b200.peft.lora import LoraSpec
+
+        if not self.use_peft:
+            return None
+        kw = {"target_modules": self.lora_target_modules} if self.lora_target_modules else {}
+        return LoraSpec(r=self.lora_r, alpha=self.lora_alpha, dropout=self.lora_dropout, **kw)
 
     def __post_init__(self):
+        if self.use_peft and (self.freeze_patterns or self.train_only_patterns):
+            raise ConfigError("use_peft freezes the base weights itself: drop freeze_patterns / train_only_patterns")
+        if not self.use_peft and (self.adapter_path or self.merge_adapters_on_save):
+            raise ConfigError("adapter_path / merge_adapters_on_save need use_peft: true")
         if not self.model_name_or_path and not self.model_preset:
             raise ConfigError("set model_name_or_path (a checkpoint directory) or model_preset (train from scratch)")
         if self.model_preset and not self.init_from_scratch and not self.model_name_or_path:

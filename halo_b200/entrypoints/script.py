@@ -138,6 +138,15 @@ def load_policy_model(model_args, pc, device, runtime, gradient_checkpointing=Tr
     else:
         model = from_pretrained(model_args.model_name_or_path, device=device, dtype=dtype, transport=transport,
                                 gradient_checkpointing=gradient_checkpointing)
+    if getattr(model_args, "use_peft", False):
+        from halo_b200.peft.lora import apply_lora, load_adapters
+
+        stats = apply_lora(model, model_args.lora_spec(), seed=0)
+        model.base_model_path = model_args.model_name_or_path
+        model.merge_adapters_on_save = model_args.merge_adapters_on_save
+        if model_args.adapter_path:
+            load_adapters(model, model_args.adapter_path)
+        log.info("low-rank adapters: %d trainable parameters on %d frozen", stats["trainable"], stats["frozen"])
     if model_args.freeze_patterns or model_args.train_only_patterns:
         from halo_b200.models.freeze import apply_freeze_patterns
 
@@ -163,7 +172,8 @@ def run_trainer(trainer, train_args):
     final = os.path.join(train_args.output_dir, "final")
     from halo_b200.checkpoint.save import save_model
 
-    save_model(trainer.model, final, group=trainer.group, is_writer=trainer.is_main)
+    save_model(trainer.model, final, group=trainer.group, is_writer=trainer.is_main,
+               adapters="merge" if getattr(trainer.model, "merge_adapters_on_save", False) else "auto")
     return result
 
 

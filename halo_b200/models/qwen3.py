@@ -99,6 +99,7 @@ class Attention(nn.Module):
                 self.qkv_bias.tp_kind = "qkv_bias"
         else:
             self.register_parameter("qkv_bias", None)
+        self.lora = None          # halo_b200.peft.lora.LoraSet when low-rank adapters are attached
         if cfg.use_qk_norm:
             self.q_norm = nn.Parameter(torch.ones(D, dtype=dtype, device=device))
             self.k_norm = nn.Parameter(torch.ones(D, dtype=dtype, device=device))
@@ -108,6 +109,19 @@ class Attention(nn.Module):
 
     def _biased(self, qkv):
         return qkv if self.qkv_bias is None else qkv + self.qkv_bias
+
+    def _qkv(self, h):
+        qkv = self._biased(gemm.linear(h, self.qkv_proj))
+        if self.lora is not None:
+            q, kv = self.n_heads * self.cfg.head_dim, self.n_kv_heads * self.cfg.head_dim
+            qkv = self.lora.add_fused(h, qkv, [("q_proj", 0, q), ("k_proj", q, q + kv), ("v_proj", q + kv, q + 2 * kv)])
+        return qkv
+
+    def _out(self, o):
+        y = gemm.linear(o, self.o_proj)
+        if self.lora is not None and "o_proj" in self.lora:
+            y = y + self.lora.delta("o_proj", o)
+        return y
 
     def forward(self, h, ctx):
         cfg = self.cfg
@@ -119,7 +133,7 @@ class Attention(nn.Module):
             o = attn_ops.rope_attention(qkv, self.q_norm, self.k_norm, ctx.rope, ctx.plan, self.n_heads, self.n_kv_heads,
                                         cfg.rms_norm_eps, cfg.use_qk_norm)
             return row_parallel_linear(o, self.o_proj, ctx.tp)
-        qkv = self._biased(gemm.linear(h, self.qkv_proj))
+        qkv = self._qkv(h)
         if ctx.cp is not None:
             # context parallel: this rank holds one chunk of the row; keys and values of straddling documents
             # come from the lower ranks
@@ -135,7 +149,7 @@ class Attention(nn.Module):
         else:
             o = attn_ops.rope_attention(qkv, self.q_norm, self.k_norm, ctx.rope, ctx.plan, cfg.num_attention_heads,
                                         cfg.num_key_value_heads, cfg.rms_norm_eps, cfg.use_qk_norm)
-        return gemm.linear(o, self.o_proj)
+        return self._out(o)
 
 
 class DenseMLP(nn.Module):
@@ -147,8 +161,18 @@ class DenseMLP(nn.Module):
         self.down_proj = nn.Parameter(torch.empty(hidden, width, dtype=dtype, device=device))
         if tp_size > 1:
             self.gate_up_proj.tp_kind, self.down_proj.tp_kind = "gate_up", "down"
+        self.lora = None          # halo_b200.peft.lora.LoraSet when low-rank adapters are attached
 
     def forward(self, h, ctx=None):
+        if self.lora is not None:
+            # the low-rank terms join the pre-activation, so the activation runs as its own kernel here
+            from halo_b200.ops.activation import swiglu
+
+            width = self.gate_up_proj.shape[0] // 2
+            pre = self.lora.add_fused(h, gemm.linear(h, self.gate_up_proj), [("gate_proj", 0, width), ("up_proj", width, 2 * width)])
+            act = swiglu(pre)
+            y = gemm.linear(act, self.down_proj)
+            return y + self.lora.delta("down_proj", act) if "down_proj" in self.lora else y
         if self.tp_size > 1:
             from halo_b200.parallel.tensor_parallel import gather_seq, row_parallel_linear
 
@@ -186,6 +210,7 @@ class SparseMoE(nn.Module):
         # auxiliary-loss-free balancing: a per-expert bias that only ranks experts (never a parameter,
         # saved as a sidecar by the balancing callback)
         self.register_buffer("selection_bias", None, persistent=False)
+        self.expert_lora = None       # halo_b200.peft.lora.ExpertLora when the routed experts carry adapters
         self.load_counter = None      # (ExpertLoadCounter, layer index) when load metrics are on
         self.last_routing = None
 
@@ -206,6 +231,9 @@ class SparseMoE(nn.Module):
             counter.add(layer_index, idx)     # first pass only: a recomputation replays the same routing
         if ctx.record_routing is not None:
             ctx.record_routing.append((logits, idx))
+        bank_gate_up, bank_down = self.experts_gate_up, self.experts_down
+        if self.expert_lora is not None:
+            bank_gate_up, bank_down = self.expert_lora.effective_banks(bank_gate_up, bank_down)
         if self.etp is not None:
             # every rank of the group routes the same tokens through its slice of each expert; the partial outputs
             # are summed in token space (and the partial input / routing-weight gradients on the way back)
@@ -215,7 +243,7 @@ class SparseMoE(nn.Module):
                                        self.experts_down, ctx.transport)
             out = sum_from_group(part, self.etp)
         else:
-            out = moe_ops.moe_experts(h, idx, w, self.experts_gate_up, self.experts_down, ctx.transport,
+            out = moe_ops.moe_experts(h, idx, w, bank_gate_up, bank_down, ctx.transport,
                                       skip_output=getattr(ctx, "output_unused", False))
         if self.shared_expert is not None:
             sh = self.shared_expert(h)

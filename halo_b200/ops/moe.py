@@ -398,7 +398,11 @@ class _MoEExperts(torch.autograd.Function):
         _lib.check(L.halo_swiglu_bwd_weighted(_lib.ptr(pre), _lib.ptr(dact), _lib.ptr(row_w), _lib.ptr(dpre),
                                               _lib.ptr(act_w), _lib.ptr(dwrow), _lib.ptr(state.total_rows),
                                               _lib.c_int(F), _lib.c_int(cap), s), "halo_swiglu_bwd_weighted")
+        need_weight_grads = ctx.needs_input_grad[3] or ctx.needs_input_grad[4]
+
         def weight_grads():
+            if not need_weight_grads:      # frozen banks (adapters elsewhere): the two products are left out
+                return None, None
             # 5. dW_down[e] = dout_e^T (w * act)_e ; dW_gate_up[e] = dpre_e^T x_e
             dw_down = _alloc(transport, tuple(w_down.shape), w_down.dtype, dev)
             pk = _pair_ok(4096, False)      # the reduction runs over an expert's rows: long

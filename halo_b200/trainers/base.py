@@ -250,7 +250,12 @@ class Trainer:
 
         if not is_complete(directory):
             raise FileNotFoundError(f"{directory!r} has no completeness marker: the save was interrupted")
-        load_model_weights(self.model, directory)
+        if getattr(self.model, "lora_spec", None) is not None:
+            from halo_b200.peft.lora import load_adapters      # the frozen base came from the model path
+
+            load_adapters(self.model, directory)
+        else:
+            load_model_weights(self.model, directory)
         opt_io.load_optimizer_shard(self.optimizer, directory, self.rank, self.fingerprint,
                                     self.args.allow_optimizer_warm_restart)
         state = json.load(open(os.path.join(directory, "trainer_state.json")))
