@@ -1,0 +1,121 @@
+"""Kernels of the model families beyond the flagship (residual-stream ops, per-stream norm, gated mean,
+masked-softmax backward, standalone SwiGLU, block-scaled fake quantisation) against fp32 PyTorch statements of the
+same ops. Collected last: the flagship's kernels are judged before these."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _compare(op, ref, inputs, bf16_mask, tol=3e-2):
+    """Run ``op`` on bf16 CUDA copies (where ``bf16_mask`` says so) and ``ref`` on fp32 copies; compare outputs and
+    every input gradient in relative max-norm."""
+    dev = "cuda"
+    a = [(x.to(dev).bfloat16() if m else x.to(dev)).requires_grad_(x.is_floating_point()) for x, m in zip(inputs, bf16_mask)]
+    b = [(x.to(dev).bfloat16().float() if m else x.to(dev).float()).requires_grad_(True) for x, m in zip(inputs, bf16_mask)]
+    ya, yb = op(*a), ref(*b)
+    g = torch.randn(yb.shape, device=dev, generator=torch.Generator(device=dev).manual_seed(3))
+    (ya.float() * g).sum().backward()
+    (yb.float() * g).sum().backward()
+    assert (ya.float() - yb.float()).abs().max() <= tol * yb.float().abs().max() + 1e-3
+    for i, (p, q) in enumerate(zip(a, b)):
+        assert p.grad is not None, i
+        assert (p.grad.float() - q.grad).abs().max() <= tol * q.grad.abs().max() + 2e-3, i
+
+
+@pytest.mark.parametrize("N", [1, 2, 4, 8])
+@pytest.mark.parametrize("T,H", [(5, 64), (300, 2048)])
+def test_stream_collapse_mix_inject(N, T, H):
+    from halo_b200.ops import streams as S
+
+    torch.manual_seed(N * 100 + T)
+    stream, block = torch.randn(T, N, H), torch.randn(T, H)
+    w, post, gate = torch.rand(T, N), torch.rand(T, N), torch.randn(T, N)
+    comb = torch.softmax(torch.randn(T, N, N), dim=-1)
+    _compare(S.collapse_streams, S.collapse_streams_reference, [stream, w], [True, False])
+    _compare(S.mix_streams, S.mix_streams_reference, [block, stream, post, comb], [True, True, False, False])
+    _compare(S.inject_streams, S.inject_streams_reference, [block, stream, gate], [True, True, False])
+
+
+@pytest.mark.parametrize("N,iters", [(2, 1), (4, 20), (8, 4)])
+def test_sinkhorn(N, iters):
+    from halo_b200.ops import streams as S
+
+    torch.manual_seed(N)
+    comb = torch.softmax(torch.randn(777, N, N), dim=-1) + 1e-6
+    _compare(lambda c: S.sinkhorn_knopp(c, iters, 1e-6), lambda c: S.sinkhorn_knopp_reference(c, iters, 1e-6), [comb], [False],
+             tol=1e-4)
+    with torch.no_grad():
+        out = S.sinkhorn_knopp(comb.cuda(), iters, 1e-6)
+    assert torch.allclose(out.cpu(), S.sinkhorn_knopp_reference(comb, iters, 1e-6), atol=1e-5)
+
+
+def test_stream_projection():
+    from halo_b200.ops import streams as S
+
+    torch.manual_seed(0)
+    T, N, H = 400, 4, 512
+    stream, fn = torch.randn(T, N, H), torch.randn(N * N + 2 * N, N * H) * 0.05
+    _compare(lambda s, f: S.project_streams(s, f, 1e-6), lambda s, f: S.project_streams_reference(s, f, 1e-6), [stream, fn],
+             [True, False])
+
+
+@pytest.mark.parametrize("streams", [1, 2, 4])
+@pytest.mark.parametrize("rows,H", [(3, 64), (1100, 1024)])
+def test_grouped_rms_norm_and_gate_mix(streams, rows, H):
+    from halo_b200.ops import streams as S
+
+    torch.manual_seed(streams + rows)
+    x, w = torch.randn(rows, streams * H), torch.randn(streams * H) * 0.1
+    _compare(lambda a, b: S.grouped_rms_norm(a, b, 1e-6, streams), lambda a, b: S.grouped_rms_norm_reference(a, b, 1e-6, streams),
+             [x, w], [True, False])
+    normed, down, w_up = torch.randn(rows, streams * H), torch.randn(rows, 16), torch.randn(streams * H, 16) * 0.3
+    _compare(lambda a, b, c: S.gate_mix(a, b, c, streams), lambda a, b, c: S.gate_mix_reference(a, b, c, streams),
+             [normed, down, w_up], [True, True, True], tol=5e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_masked_softmax_backward(dtype):
+    from halo_b200.ops import streams as S
+
+    torch.manual_seed(1)
+    heads, Q, K, scale = 4, 70, 333, 0.2
+    scores = torch.randn(heads, Q, K, device="cuda")
+    allowed = torch.rand(Q, K, device="cuda") > 0.4
+    allowed[:, 0] = True
+    masked = (scores * scale).masked_fill(~allowed, float("-inf"))
+    lse = torch.logsumexp(masked, dim=-1)
+    upstream = torch.randn(heads, Q, K, device="cuda")
+    probs = torch.softmax(masked, dim=-1)
+    delta = (probs * upstream).sum(-1)
+    want_d = probs * (upstream - delta.unsqueeze(-1)) * scale
+    p, d = S.masked_softmax_backward(scores, allowed, lse, scale, upstream, delta, True, dtype)
+    tol = 1e-2 if dtype == torch.bfloat16 else 1e-5
+    assert p.dtype == dtype and (p.float() - probs).abs().max() <= tol
+    assert (d.float() - want_d).abs().max() <= tol * max(1.0, want_d.abs().max().item())
+    # a strided mask view and the probabilities alone
+    wide = torch.zeros(Q, K + 5, device="cuda", dtype=torch.bool)
+    wide[:, :K] = allowed
+    p2, none = S.masked_softmax_backward(scores, wide[:, :K], lse, scale, writes_probs=True, dtype=dtype)
+    assert none is None and torch.equal(p2, p)
+
+
+def test_standalone_swiglu():
+    from halo_b200.ops.activation import swiglu, swiglu_reference
+
+    torch.manual_seed(2)
+    pre = torch.randn(513, 2 * 768)
+    _compare(swiglu, swiglu_reference, [pre], [True])
+
+
+@pytest.mark.parametrize("fmt", ["mxfp8", "mxfp4", "nvfp4"])
+def test_fake_quant_kernel_is_bit_identical_to_the_tensor_ops(fmt):
+    from halo_b200.ops import lowp
+
+    torch.manual_seed(4)
+    x = (torch.randn(257, 1024, device="cuda") * torch.logspace(-6, 3, 1024, device="cuda")).bfloat16()
+    x[3, :32] = 0
+    got = lowp.fake_quant(x, fmt)
+    want = lowp.fake_quant_reference(x, fmt)
+    assert got.dtype == x.dtype and torch.equal(got, want)
