@@ -33,6 +33,8 @@ def runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, e
         return {"model.norm.weight": tensor}
     if name == "lm_head":
         return {"lm_head.weight": tensor}
+    if name.startswith("hc_head."):
+        return {"model." + name: tensor}
     m = _LAYER.match(name)
     if not m:
         raise KeyError(f"no hub name for runtime parameter {name!r}")
@@ -41,6 +43,8 @@ def runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, e
     D, Hq, Hkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
     if rest in ("input_layernorm", "post_attention_layernorm"):
         return {pre + rest + ".weight": tensor}
+    if rest.startswith(("attn_hc.", "ffn_hc.")):       # hyper-connection parameters keep their names
+        return {pre + rest: tensor}
     if rest == "self_attn.qkv_proj":
         q, k, v = tensor.split([Hq * D, Hkv * D, Hkv * D], dim=0)
         return {pre + "self_attn.q_proj.weight": q, pre + "self_attn.k_proj.weight": k,

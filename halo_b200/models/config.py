@@ -50,6 +50,11 @@ class ModelConfig:
     use_qk_norm: bool = True
     attention_bias: bool = False           # bias on the q / k / v projections (Qwen2)
     rope_scaling: dict | None = None       # Hugging Face ``rope_scaling`` / ``rope_parameters`` entry, None = plain
+    hc_mult: int = 1                       # residual streams per token (1 = the plain residual; > 1 = hyper-connections)
+    hc_kind: str = "mhc"                   # "mhc": Sinkhorn-projected mixing matrices; "gated": per-stream norm + gated mean + inject
+    hc_sinkhorn_iters: int = 20
+    hc_eps: float = 1e-6
+    hc_mix_rank: int = 16                  # rank of the gated variant's gate projection
     tie_word_embeddings: bool = False
     router_aux_loss_coef: float = 0.0
     initializer_range: float = 0.02
@@ -83,6 +88,13 @@ class ModelConfig:
             else:
                 total += attn + dense_mlp
                 active += attn + dense_mlp
+        if self.hc_mult > 1:
+            n = self.hc_mult
+            per_layer = (2 * ((2 * n + n * n) * (n * H + 1) + 3) if self.hc_kind == "mhc"
+                         else 2 * (n * H + 2 * self.hc_mix_rank * n * H + n * n * H))
+            head_collapse = n * n * H + n + 1 if self.hc_kind == "mhc" else 0
+            total += self.num_hidden_layers * per_layer + head_collapse
+            active += self.num_hidden_layers * per_layer + head_collapse
         emb = self.vocab_size * H
         head = 0 if self.tie_word_embeddings else emb
         return {"total": total + emb + head + H, "active": active + head + H, "embedding": emb,
@@ -118,6 +130,9 @@ class ModelConfig:
         }
         if self.rope_scaling:
             d["rope_scaling"] = {k: v for k, v in rope.items() if k != "rope_theta"}
+        if self.hc_mult > 1:
+            d.update({"hc_mult": self.hc_mult, "hc_kind": self.hc_kind, "hc_sinkhorn_iters": self.hc_sinkhorn_iters,
+                      "hc_eps": self.hc_eps, "hc_mix_rank": self.hc_mix_rank})
         if fam["bias_key"]:
             d["attention_bias"] = self.attention_bias
         elif self.family == "qwen2_moe":
@@ -188,7 +203,8 @@ class ModelConfig:
             rope_theta=float(rope_theta), rms_norm_eps=d.get("rms_norm_eps", 1e-6), use_qk_norm=fam["qk_norm"],
             attention_bias=(bool(d.get("attention_bias", False)) if fam["bias_key"]
                             else bool(d.get("qkv_bias", fam["bias_default"]))),
-            rope_scaling=scaling,
+            rope_scaling=scaling, hc_mult=int(d.get("hc_mult", 1)), hc_sinkhorn_iters=int(d.get("hc_sinkhorn_iters", 20)),
+            hc_eps=float(d.get("hc_eps", 1e-6)), hc_kind=d.get("hc_kind", "mhc"), hc_mix_rank=int(d.get("hc_mix_rank", 16)),
             tie_word_embeddings=d.get("tie_word_embeddings", False),
             router_aux_loss_coef=d.get("router_aux_loss_coef", 0.0), initializer_range=d.get("initializer_range", 0.02),
             max_position_embeddings=d.get("max_position_embeddings", 262144), model_type=mt,

@@ -285,6 +285,49 @@ class DecoderLayer(nn.Module):
         return x2 + self.mlp(rms_norm(x2, self.post_attention_layernorm, self.eps), ctx)
 
 
+class HyperConnectedLayer(DecoderLayer):
+    """The same two blocks on ``N`` residual streams ``[T, N, H]``: each block reads the streams collapsed by its
+    hyper-connection and its output is mixed back into all of them."""
+
+    def __init__(self, cfg: ModelConfig, idx: int, dtype, device, n_local_experts: int, router_dtype=None, tp_size: int = 1,
+                 etp=None):
+        super().__init__(cfg, idx, dtype, device, n_local_experts, router_dtype, tp_size, etp)
+        from .hyper_connections import GatedResidual, HyperConnection
+
+        self.gated = cfg.hc_kind == "gated"
+        if self.gated:
+            args = (cfg.hidden_size, cfg.hc_mult, cfg.hc_mix_rank, cfg.rms_norm_eps, dtype, device)
+            self.attn_hc = GatedResidual(*args, seed=2 * idx)
+            self.ffn_hc = GatedResidual(*args, seed=2 * idx + 1)
+        elif cfg.hc_kind == "mhc":
+            args = (cfg.hidden_size, cfg.hc_mult, cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_norm_eps, device)
+            self.attn_hc = HyperConnection(*args)
+            self.ffn_hc = HyperConnection(*args)
+        else:
+            raise ValueError(f"hc_kind {cfg.hc_kind!r}: known kinds are 'mhc' and 'gated'")
+
+    def _around(self, hc, block, streams):
+        """``block`` on the collapsed streams, its output spread back over them."""
+        if self.gated:
+            from halo_b200.ops.streams import inject_streams
+
+            collapsed, gates = hc(streams)
+            return inject_streams(block(collapsed), streams, gates.to(streams.dtype))
+        from .hyper_connections import mixed
+
+        post, comb, collapsed = hc(streams)
+        return mixed(block(collapsed), streams, post, comb)
+
+    def attention_half(self, streams, ctx):
+        return self._around(self.attn_hc, lambda x: self.self_attn(rms_norm(x, self.input_layernorm, self.eps), ctx), streams)
+
+    def mlp_half(self, streams, ctx):
+        return self._around(self.ffn_hc, lambda x: self.mlp(rms_norm(x, self.post_attention_layernorm, self.eps), ctx), streams)
+
+    def forward(self, streams, ctx):
+        return self.mlp_half(self.attention_half(streams, ctx), ctx)
+
+
 class ForwardContext:
     """Per-batch state shared by all layers: attention plan, rotary table, expert transport."""
 
@@ -325,8 +368,18 @@ class Qwen3Model(nn.Module):
         self.layer_range = (lo, hi)
         H = cfg.hidden_size
         self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, H, dtype=dtype, device=device)) if has_embed else None
+        if cfg.hc_mult > 1 and (tp_size > 1 or (lo, hi) != (0, cfg.num_hidden_layers)):
+            raise ValueError("hyper-connected models (hc_mult > 1) are built for data / expert parallel layouts: turn tensor "
+                             "and pipeline parallelism off")
+        layer_cls = HyperConnectedLayer if cfg.hc_mult > 1 else DecoderLayer
         self.layers = nn.ModuleList(
-            [DecoderLayer(cfg, i, dtype, device, n_local, router_dtype, tp_size, expert_tensor_parallel) for i in range(lo, hi)])
+            [layer_cls(cfg, i, dtype, device, n_local, router_dtype, tp_size, expert_tensor_parallel) for i in range(lo, hi)])
+        if cfg.hc_mult > 1 and has_head and cfg.hc_kind == "mhc":
+            from .hyper_connections import HyperHead
+
+            self.hc_head = HyperHead(H, cfg.hc_mult, cfg.hc_eps, cfg.rms_norm_eps, device)
+        else:
+            self.hc_head = None
         self.norm = nn.Parameter(torch.ones(H, dtype=dtype, device=device)) if has_head else None
         if has_head and not (cfg.tie_word_embeddings and has_embed):
             self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, H, dtype=dtype, device=device))
@@ -346,7 +399,12 @@ class Qwen3Model(nn.Module):
         from halo_b200.optim.adamw_bf16 import param_name_hash
 
         first = self.layer_range[0]
+        for module in self.modules():
+            if hasattr(module, "reset_parameters") and module is not self:
+                module.reset_parameters()          # hyper-connections: the plain residual model's function
         for name, p in self.named_parameters():
+            if "_hc." in name or name.startswith("hc_head."):
+                continue
             if p.dim() == 1:
                 p.fill_(0.0 if name.endswith("bias") else 1.0)
                 continue
@@ -427,7 +485,13 @@ class Qwen3Model(nn.Module):
     def hidden_states(self, input_ids, position_ids, cu_seqlens, ctx=None):
         ctx = ctx or self.make_context(position_ids.reshape(-1), cu_seqlens)
         x = self.embed(input_ids)
+        if self.cfg.hc_mult > 1:
+            x = x.unsqueeze(1).expand(-1, self.cfg.hc_mult, -1).contiguous()      # every stream starts as the embedding
         x = self.run_layers(x, ctx)
+        if self.hc_head is not None:
+            x = self.hc_head(x)
+        elif self.cfg.hc_mult > 1:
+            x = x.float().mean(1).to(x.dtype)          # the gated variant reads the streams' mean
         return rms_norm(x, self.norm, self.cfg.rms_norm_eps)
 
     def forward(self, input_ids, position_ids, cu_seqlens, labels=None, normalizer=None, ctx=None):
