@@ -35,6 +35,14 @@ def runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, e
         return {"lm_head.weight": tensor}
     if name.startswith("hc_head."):
         return {"model." + name: tensor}
+    if name.startswith("mtp."):
+        # the head is stored as layer ``num_hidden_layers``, with the names of the DeepSeek-V3 release beside the block's
+        own = {"mtp.embedding_norm": "enorm.weight", "mtp.hidden_norm": "hnorm.weight", "mtp.projection": "eh_proj.weight",
+               "mtp.output_norm": "shared_head.norm.weight"}
+        if name in own:
+            return {f"model.layers.{cfg.num_hidden_layers}.{own[name]}": tensor}
+        return runtime_to_hub(f"layers.{cfg.num_hidden_layers - first_layer}." + name[len("mtp.layer."):], tensor, cfg, first_layer,
+                              expert_offset)
     m = _LAYER.match(name)
     if not m:
         raise KeyError(f"no hub name for runtime parameter {name!r}")
@@ -90,7 +98,7 @@ def hub_sources(name: str, shape, cfg, first_layer: int = 0, expert_offset: int 
     pieces = runtime_to_hub(name, probe, cfg, first_layer, expert_offset)
     out, row = [], 0
     m = _LAYER.match(name)
-    rest = m.group(2) if m else name
+    rest = m.group(2) if m else (name[len("mtp.layer."):] if name.startswith("mtp.layer.") else name)
     if rest in ("mlp.experts_gate_up", "mlp.experts_down"):
         _, gate_name, up_name, _ = MOE_HUB_NAMES.get(getattr(cfg, "family", ""), MOE_HUB_NAMES["qwen3_moe"])
         F = shape[1] // 2          # gate rows, then up rows, of the fused bank (unused for the down bank)

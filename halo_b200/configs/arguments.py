@@ -21,6 +21,9 @@ class ModelArguments:
     freeze_patterns: list[str] | None = None      # regexes of parameter names to freeze
     train_only_patterns: list[str] | None = None  # or: train only what matches
     max_length: int = 0                     # 0 = the model's context window
+    enable_mtp_head: bool = False           # train a multi-token-prediction head beside the next-token loss
+    mtp_loss_weight: float = 0.3
+    mtp_objective: Literal["joint", "detached"] = "joint"
     use_peft: bool = False                  # train low-rank adapters on frozen base weights
     lora_r: int = 16
     lora_alpha: float = 32.0

@@ -118,6 +118,13 @@ def load_policy_model(model_args, pc, device, runtime, gradient_checkpointing=Tr
 
     dtype = torch.bfloat16 if model_args.torch_dtype == "bfloat16" and device.type == "cuda" else torch.float32
     cfg = PRESETS[model_args.model_preset]() if model_args.init_from_scratch else ModelConfig.load(model_args.model_name_or_path)
+    new_mtp_head = False
+    if getattr(model_args, "enable_mtp_head", False):
+        import dataclasses
+
+        new_mtp_head = not cfg.num_nextn_predict_layers      # the checkpoint has none yet: the head starts from its initialisation
+        cfg = dataclasses.replace(cfg, num_nextn_predict_layers=1, mtp_loss_weight=model_args.mtp_loss_weight,
+                                  mtp_objective=model_args.mtp_objective)
     reject_model_layout(pc, cfg)
     if isinstance(runtime, dict):          # tensor / context parallelism: needs the model's sizes to finish
         runtime = finish_token_cutting_runtime(runtime, cfg, max_tokens)
@@ -135,6 +142,16 @@ def load_policy_model(model_args, pc, device, runtime, gradient_checkpointing=Tr
     if model_args.init_from_scratch:
         model = build_model(cfg, device=device, dtype=dtype, transport=transport,
                             gradient_checkpointing=gradient_checkpointing)
+    elif new_mtp_head:
+        from halo_b200.checkpoint.load import load_model_weights
+
+        model = build_model(cfg, device=device, dtype=dtype, transport=transport, gradient_checkpointing=gradient_checkpointing)
+        report = load_model_weights(model, model_args.model_name_or_path, strict=False)
+        head_prefix = f"model.layers.{cfg.num_hidden_layers}."
+        stray = [n for n in report["missing"] if not n.startswith(head_prefix)]
+        if stray:
+            raise KeyError(f"{len(stray)} tensors are absent from {model_args.model_name_or_path!r}, e.g. {stray[:4]}")
+        log.info("multi-token-prediction head: %d tensors start from their initialisation", len(report["missing"]))
     else:
         model = from_pretrained(model_args.model_name_or_path, device=device, dtype=dtype, transport=transport,
                                 gradient_checkpointing=gradient_checkpointing)

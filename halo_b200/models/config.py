@@ -50,6 +50,9 @@ class ModelConfig:
     use_qk_norm: bool = True
     attention_bias: bool = False           # bias on the q / k / v projections (Qwen2)
     rope_scaling: dict | None = None       # Hugging Face ``rope_scaling`` / ``rope_parameters`` entry, None = plain
+    num_nextn_predict_layers: int = 0      # 1 = a multi-token-prediction head trained beside the next-token loss
+    mtp_loss_weight: float = 0.3
+    mtp_objective: str = "joint"           # "joint": the head's loss also reaches the trunk; "detached": it does not
     hc_mult: int = 1                       # residual streams per token (1 = the plain residual; > 1 = hyper-connections)
     hc_kind: str = "mhc"                   # "mhc": Sinkhorn-projected mixing matrices; "gated": per-stream norm + gated mean + inject
     hc_sinkhorn_iters: int = 20
@@ -88,6 +91,13 @@ class ModelConfig:
             else:
                 total += attn + dense_mlp
                 active += attn + dense_mlp
+        if self.num_nextn_predict_layers:
+            L = self.num_hidden_layers
+            moe = self.layer_is_moe(L)
+            block = attn + (self.num_experts * expert + self.num_experts * H + shared if moe else dense_mlp)
+            block_active = attn + (self.num_experts_per_tok * expert + self.num_experts * H + shared if moe else dense_mlp)
+            total += block + 2 * H * H + 3 * H
+            active += block_active + 2 * H * H + 3 * H
         if self.hc_mult > 1:
             n = self.hc_mult
             per_layer = (2 * ((2 * n + n * n) * (n * H + 1) + 3) if self.hc_kind == "mhc"
@@ -130,6 +140,9 @@ class ModelConfig:
         }
         if self.rope_scaling:
             d["rope_scaling"] = {k: v for k, v in rope.items() if k != "rope_theta"}
+        if self.num_nextn_predict_layers:
+            d.update({"num_nextn_predict_layers": self.num_nextn_predict_layers, "mtp_loss_weight": self.mtp_loss_weight,
+                      "mtp_objective": self.mtp_objective})
         if self.hc_mult > 1:
             d.update({"hc_mult": self.hc_mult, "hc_kind": self.hc_kind, "hc_sinkhorn_iters": self.hc_sinkhorn_iters,
                       "hc_eps": self.hc_eps, "hc_mix_rank": self.hc_mix_rank})
@@ -203,6 +216,8 @@ class ModelConfig:
             rope_theta=float(rope_theta), rms_norm_eps=d.get("rms_norm_eps", 1e-6), use_qk_norm=fam["qk_norm"],
             attention_bias=(bool(d.get("attention_bias", False)) if fam["bias_key"]
                             else bool(d.get("qkv_bias", fam["bias_default"]))),
+            num_nextn_predict_layers=int(d.get("num_nextn_predict_layers", 0) or 0),
+            mtp_loss_weight=float(d.get("mtp_loss_weight", 0.3)), mtp_objective=d.get("mtp_objective", "joint"),
             rope_scaling=scaling, hc_mult=int(d.get("hc_mult", 1)), hc_sinkhorn_iters=int(d.get("hc_sinkhorn_iters", 20)),
             hc_eps=float(d.get("hc_eps", 1e-6)), hc_kind=d.get("hc_kind", "mhc"), hc_mix_rank=int(d.get("hc_mix_rank", 16)),
             tie_word_embeddings=d.get("tie_word_embeddings", False),

@@ -380,6 +380,17 @@ class Qwen3Model(nn.Module):
             self.hc_head = HyperHead(H, cfg.hc_mult, cfg.hc_eps, cfg.rms_norm_eps, device)
         else:
             self.hc_head = None
+        if cfg.num_nextn_predict_layers:
+            if cfg.num_nextn_predict_layers != 1 or cfg.hc_mult > 1 or tp_size > 1 or (lo, hi) != (0, cfg.num_hidden_layers):
+                raise ValueError("the multi-token-prediction head is built as one block on an unsliced, single-stage, "
+                                 "plain-residual model")
+            if cfg.mtp_objective not in ("joint", "detached"):
+                raise ValueError(f"mtp_objective {cfg.mtp_objective!r}: known objectives are 'joint' and 'detached'")
+            from .mtp import MTPHead
+
+            self.mtp = MTPHead(cfg, dtype, device, n_local, router_dtype)
+        else:
+            self.mtp = None
         self.norm = nn.Parameter(torch.ones(H, dtype=dtype, device=device)) if has_head else None
         if has_head and not (cfg.tie_word_embeddings and has_embed):
             self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, H, dtype=dtype, device=device))
@@ -482,8 +493,8 @@ class Qwen3Model(nn.Module):
         self._gate([w, self.norm])
         return w
 
-    def hidden_states(self, input_ids, position_ids, cu_seqlens, ctx=None):
-        ctx = ctx or self.make_context(position_ids.reshape(-1), cu_seqlens)
+    def trunk_states(self, input_ids, ctx):
+        """The last layer's output, before the final norm (``[T, H]``)."""
         x = self.embed(input_ids)
         if self.cfg.hc_mult > 1:
             x = x.unsqueeze(1).expand(-1, self.cfg.hc_mult, -1).contiguous()      # every stream starts as the embedding
@@ -492,15 +503,43 @@ class Qwen3Model(nn.Module):
             x = self.hc_head(x)
         elif self.cfg.hc_mult > 1:
             x = x.float().mean(1).to(x.dtype)          # the gated variant reads the streams' mean
-        return rms_norm(x, self.norm, self.cfg.rms_norm_eps)
+        return x
+
+    def hidden_states(self, input_ids, position_ids, cu_seqlens, ctx=None):
+        ctx = ctx or self.make_context(position_ids.reshape(-1), cu_seqlens)
+        return rms_norm(self.trunk_states(input_ids, ctx), self.norm, self.cfg.rms_norm_eps)
+
+    def mtp_states(self, trunk, input_ids, ctx):
+        """The multi-token-prediction head's normed states for the shared output head."""
+        nxt = torch.roll(input_ids.reshape(-1), -1)
+        emb = torch.nn.functional.embedding(nxt, self.embed_tokens)
+        if self.cfg.mtp_objective == "detached":
+            trunk, emb = trunk.detach(), emb.detach()
+        self._gate(self.mtp.parameters())
+        return self.mtp(trunk, emb, ctx, self.gradient_checkpointing and torch.is_grad_enabled())
 
     def forward(self, input_ids, position_ids, cu_seqlens, labels=None, normalizer=None, ctx=None):
         """``labels`` are next-token targets already aligned with ``input_ids`` positions
         (-100 = not scored). Returns the summed CE divided by ``normalizer`` (default: scored tokens)."""
-        h = self.hidden_states(input_ids, position_ids, cu_seqlens, ctx)
-        if labels is None:
-            return h
-        return fused_linear_cross_entropy(h, self.head_weight(), labels.reshape(-1), normalizer)
+        if self.mtp is None or labels is None:
+            h = self.hidden_states(input_ids, position_ids, cu_seqlens, ctx)
+            if labels is None:
+                return h
+            return fused_linear_cross_entropy(h, self.head_weight(), labels.reshape(-1), normalizer)
+        from .mtp import shifted_targets
+
+        ctx = ctx or self.make_context(position_ids.reshape(-1), cu_seqlens)
+        trunk = self.trunk_states(input_ids, ctx)
+        flat = labels.reshape(-1)
+        if normalizer is None:
+            normalizer = (flat != -100).sum().clamp(min=1)      # both terms share the next-token count
+        w = self.head_weight()
+        loss = fused_linear_cross_entropy(rms_norm(trunk, self.norm, self.cfg.rms_norm_eps), w, flat, normalizer)
+        head_w = w.detach() if self.cfg.mtp_objective == "detached" else w
+        head_loss = fused_linear_cross_entropy(self.mtp_states(trunk, input_ids, ctx), head_w, shifted_targets(flat, cu_seqlens),
+                                               normalizer)
+        self.last_mtp_loss = head_loss.detach()
+        return loss + self.cfg.mtp_loss_weight * head_loss
 
     def token_logprobs(self, input_ids, position_ids, cu_seqlens, labels, want_entropy=False, ctx=None):
         h = self.hidden_states(input_ids, position_ids, cu_seqlens, ctx)
