@@ -28,6 +28,9 @@ TOOLS = {
     "kernel-bench": "benchmarks.kernels",
     "nvlink-health": "halo_b200.diagnostics.nvlink_health",
     "prepare-dataset": "halo_b200.data.preprocessed",
+    "generate": "halo_b200.entrypoints.generation",
+    "evaluate": "halo_b200.entrypoints.evaluation",
+    "merge-adapter": "halo_b200.checkpoint.tools.merge_adapter",
     "bench": "bench",
 }
 

@@ -212,3 +212,9 @@ class GRPOArguments:
     rollout_backend: Literal["in_process", "vllm", "sglang", "resident_copy"] = "resident_copy"
     rollout_gpus: int = 0
     weight_sync_chunk_mb: int = 1024
+    prompts_per_round: int = 8                  # in_process rollouts: prompts sampled per round (x num_generations completions)
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = 0
+    reward_terms: list[dict] | None = None      # reward composer spec for in_process rollouts on text prompts
+    synthetic_reward_token: int = -1            # >= 0: tokenizer-free reward = share of completion tokens equal to it

@@ -30,6 +30,45 @@ def rollouts_from_jsonl(path: str, group: int):
     return source
 
 
+def in_process_source(model, model_args, data_args, train_args, grpo_args, pc):
+    """On-policy rollouts sampled from the trainer's own weights (``rollout_backend: in_process``). Prompts: a JSONL of
+    {"prompt_ids": [...]} or {"prompt": "..."} rows (each data-parallel rank takes its stride), else random ones."""
+    from halo_b200.inference.generate import SamplingParams
+    from halo_b200.trainers.grpo.online import OnPolicyRolloutSource, text_reward, token_match_reward
+
+    tokenizer = None
+    if data_args.dataset_path:
+        rows = [json.loads(l) for l in open(data_args.dataset_path) if l.strip()]
+        rows = rows[pc.data_parallel_rank::max(1, pc.data_parallel_size)]
+        if rows and "prompt_ids" not in rows[0]:
+            from halo_b200.entrypoints.script import load_tokenizer
+
+            tokenizer = load_tokenizer(model_args)
+            for r in rows:
+                r["prompt_ids"] = tokenizer(r["prompt"])["input_ids"]
+        prompts = rows
+    else:
+        rng = np.random.default_rng(train_args.seed + pc.data_parallel_rank)
+        vocab = data_args.synthetic_vocab or model.cfg.vocab_size
+        prompts = [rng.integers(0, vocab, size=int(rng.integers(4, min(32, grpo_args.max_prompt_length) + 1))) for _ in range(256)]
+    if grpo_args.synthetic_reward_token >= 0:
+        reward = token_match_reward(grpo_args.synthetic_reward_token)
+    elif grpo_args.reward_terms:
+        from halo_b200.entrypoints.script import load_tokenizer
+        from halo_b200.rewards.terms import RewardComposer, parse_terms
+
+        tokenizer = tokenizer or load_tokenizer(model_args)
+        reward = text_reward(tokenizer, RewardComposer(parse_terms(grpo_args.reward_terms)))
+    else:
+        raise ValueError("rollout_backend: in_process needs reward_terms (text prompts) or synthetic_reward_token")
+    eos = getattr(tokenizer, "eos_token_id", None) if tokenizer is not None else None
+    sampling = SamplingParams(max_new_tokens=grpo_args.max_completion_length, temperature=grpo_args.temperature,
+                              top_k=grpo_args.top_k, top_p=grpo_args.top_p)
+    return OnPolicyRolloutSource(model, prompts, reward, grpo_args.num_generations, sampling, grpo_args.prompts_per_round,
+                                 eos_token_id=eos, seed=train_args.seed + pc.data_parallel_rank,
+                                 max_prompt_length=grpo_args.max_prompt_length)
+
+
 def serve_rollout_copy(model_args, pc, device, roles, grpo_args):
     """A rollout rank: hold a full (unsharded) serving copy and take every pushed update."""
     import torch
@@ -66,7 +105,9 @@ def main(argv=None):
     model = load_policy_model(model_args, pc, device, runtime, train_args.gradient_checkpointing,
                               max_tokens=grpo_args.token_budget)
     runtime = getattr(model, "parallel_runtime", runtime)      # tensor / context parallelism finish their runtime there
-    if data_args.dataset_path:
+    if grpo_args.rollout_backend == "in_process":
+        source = in_process_source(model, model_args, data_args, train_args, grpo_args, pc)
+    elif data_args.dataset_path:
         source = rollouts_from_jsonl(data_args.dataset_path, grpo_args.num_generations)
     else:
         vocab = data_args.synthetic_vocab or model.cfg.vocab_size

@@ -125,6 +125,11 @@ class Attention(nn.Module):
 
     def forward(self, h, ctx):
         cfg = self.cfg
+        if ctx.kv_cache is not None:
+            # generation: keys / values go to the cache, a decode step attends the cache
+            from halo_b200.inference.generate import cached_attention
+
+            return cached_attention(self, h, ctx)
         if ctx.tp is not None:
             # token shards -> whole row, a slice of the heads, partial output summed back into token shards
             from halo_b200.parallel.tensor_parallel import gather_seq, row_parallel_linear
@@ -340,6 +345,7 @@ class ForwardContext:
         self.record_routing = record_routing
         self.replay_topk = replay_topk
         self.output_unused = False   # set while a layer is re-run only to rebuild its graph
+        self.kv_cache = None         # halo_b200.inference.generate.KVCache while sampling
 
 
 class Qwen3Model(nn.Module):
@@ -460,13 +466,18 @@ class Qwen3Model(nn.Module):
         """``cu_seqlens`` always describes the whole packed row; under context parallelism ``position_ids``
         (like the token ids) are this rank's chunk of it."""
         dev = position_ids.device
-        rope = rope_table(position_ids, self.cfg.head_dim, self.cfg.rope_theta, self.cfg.rope_scaling,
-                          self.cfg.max_position_embeddings)
+        rope = self.rope(position_ids)
         if self.context_parallel is not None:
             layout, plan = self.context_parallel.layout_and_plan(cu_seqlens)
             return ForwardContext(plan, rope, self.transport, record_routing, replay_topk, (self.context_parallel, layout))
         plan = attn_ops.build_plan(cu_seqlens, device=dev)
         return ForwardContext(plan, rope, self.transport, record_routing, replay_topk, tp=self.tensor_parallel)
+
+    def rope(self, position_ids):
+        """cos / sin table of these positions, in the rounding of the model's dtype."""
+        exact = next(self.parameters()).dtype == torch.float32 and not position_ids.is_cuda
+        return rope_table(position_ids, self.cfg.head_dim, self.cfg.rope_theta, self.cfg.rope_scaling,
+                          self.cfg.max_position_embeddings, round_bf16=not exact)
 
     def _gate(self, params):
         if self.param_gate is not None:

@@ -75,9 +75,10 @@ _SCALED_CACHE: dict = {}
 
 
 def rope_table(position_ids: torch.Tensor, head_dim: int, theta: float, scaling: dict | None = None,
-               max_positions: int = 0) -> torch.Tensor:
-    """``[T, head_dim/2, 2]`` fp32 (cos, sin), each rounded to bf16 as the HF module does. With ``scaling`` the
-    frequencies come from :func:`scaled_inverse_frequencies` (built once per configuration, kept on the device)."""
+               max_positions: int = 0, round_bf16: bool = True) -> torch.Tensor:
+    """``[T, head_dim/2, 2]`` fp32 (cos, sin), each rounded to bf16 as the HF module does for a bf16 model
+    (``round_bf16=False``: an fp32 model keeps them exact, as HF does there). With ``scaling`` the frequencies come
+    from :func:`scaled_inverse_frequencies` (built once per configuration, kept on the device)."""
     pos = position_ids.reshape(-1)
     T = pos.shape[0]
     half = head_dim // 2
@@ -88,10 +89,15 @@ def rope_table(position_ids: torch.Tensor, head_dim: int, theta: float, scaling:
             _SCALED_CACHE[key] = (inv.to(pos.device), factor)
         inv, factor = _SCALED_CACHE[key]
         ang = pos.float()[:, None] * inv[None, :]
-        return torch.stack([(ang.cos() * factor).bfloat16().float(), (ang.sin() * factor).bfloat16().float()], dim=-1)
+        cos, sin = ang.cos() * factor, ang.sin() * factor
+        if round_bf16:
+            cos, sin = cos.bfloat16().float(), sin.bfloat16().float()
+        return torch.stack([cos, sin], dim=-1)
     if not pos.is_cuda:
         inv = theta ** (-torch.arange(0, half, dtype=torch.float32) * 2.0 / head_dim)
         ang = pos.float()[:, None] * inv[None, :]
+        if not round_bf16:
+            return torch.stack([ang.cos(), ang.sin()], dim=-1)
         return torch.stack([ang.cos().bfloat16().float(), ang.sin().bfloat16().float()], dim=-1)
     table = torch.empty((T, half, 2), dtype=torch.float32, device=pos.device)
     pos32 = pos.to(torch.int32).contiguous()
