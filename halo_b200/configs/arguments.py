@@ -212,9 +212,11 @@ class GRPOArguments:
     rollout_backend: Literal["in_process", "vllm", "sglang", "resident_copy"] = "resident_copy"
     rollout_gpus: int = 0
     weight_sync_chunk_mb: int = 1024
+    rollout_prefetch: int = 0                   # rounds the rollout ranks sample ahead (0 = strictly on-policy, 1 = one update stale)
     prompts_per_round: int = 8                  # in_process rollouts: prompts sampled per round (x num_generations completions)
     temperature: float = 1.0
     top_p: float = 1.0
     top_k: int = 0
     reward_terms: list[dict] | None = None      # reward composer spec for in_process rollouts on text prompts
     synthetic_reward_token: int = -1            # >= 0: tokenizer-free reward = share of completion tokens equal to it
+    synthetic_reward_below: int = -1            # >= 0: tokenizer-free reward = share of completion tokens with an id below it

@@ -30,16 +30,25 @@ def rollouts_from_jsonl(path: str, group: int):
     return source
 
 
+def has_live_reward(grpo_args) -> bool:
+    return grpo_args.synthetic_reward_token >= 0 or grpo_args.synthetic_reward_below >= 0 or bool(grpo_args.reward_terms)
+
+
 def in_process_source(model, model_args, data_args, train_args, grpo_args, pc):
-    """On-policy rollouts sampled from the trainer's own weights (``rollout_backend: in_process``). Prompts: a JSONL of
-    {"prompt_ids": [...]} or {"prompt": "..."} rows (each data-parallel rank takes its stride), else random ones."""
+    """On-policy rollouts sampled from the trainer's own weights (``rollout_backend: in_process``)."""
+    return sampling_source(model, model_args, data_args, train_args, grpo_args, pc.data_parallel_rank, pc.data_parallel_size)
+
+
+def sampling_source(model, model_args, data_args, train_args, grpo_args, consumer_rank: int, n_consumers: int):
+    """A source that samples from ``model`` for consumer ``consumer_rank`` of ``n_consumers``. Prompts: a JSONL of
+    {"prompt_ids": [...]} or {"prompt": "..."} rows (each consumer takes its stride), else random ones."""
     from halo_b200.inference.generate import SamplingParams
-    from halo_b200.trainers.grpo.online import OnPolicyRolloutSource, text_reward, token_match_reward
+    from halo_b200.trainers.grpo.online import OnPolicyRolloutSource, text_reward, token_below_reward, token_match_reward
 
     tokenizer = None
     if data_args.dataset_path:
         rows = [json.loads(l) for l in open(data_args.dataset_path) if l.strip()]
-        rows = rows[pc.data_parallel_rank::max(1, pc.data_parallel_size)]
+        rows = rows[consumer_rank::max(1, n_consumers)]
         if rows and "prompt_ids" not in rows[0]:
             from halo_b200.entrypoints.script import load_tokenizer
 
@@ -48,11 +57,13 @@ def in_process_source(model, model_args, data_args, train_args, grpo_args, pc):
                 r["prompt_ids"] = tokenizer(r["prompt"])["input_ids"]
         prompts = rows
     else:
-        rng = np.random.default_rng(train_args.seed + pc.data_parallel_rank)
+        rng = np.random.default_rng(train_args.seed + consumer_rank)
         vocab = data_args.synthetic_vocab or model.cfg.vocab_size
         prompts = [rng.integers(0, vocab, size=int(rng.integers(4, min(32, grpo_args.max_prompt_length) + 1))) for _ in range(256)]
     if grpo_args.synthetic_reward_token >= 0:
         reward = token_match_reward(grpo_args.synthetic_reward_token)
+    elif grpo_args.synthetic_reward_below >= 0:
+        reward = token_below_reward(grpo_args.synthetic_reward_below)
     elif grpo_args.reward_terms:
         from halo_b200.entrypoints.script import load_tokenizer
         from halo_b200.rewards.terms import RewardComposer, parse_terms
@@ -60,17 +71,18 @@ def in_process_source(model, model_args, data_args, train_args, grpo_args, pc):
         tokenizer = tokenizer or load_tokenizer(model_args)
         reward = text_reward(tokenizer, RewardComposer(parse_terms(grpo_args.reward_terms)))
     else:
-        raise ValueError("rollout_backend: in_process needs reward_terms (text prompts) or synthetic_reward_token")
+        raise ValueError("sampled rollouts need reward_terms (text prompts) or synthetic_reward_token")
     eos = getattr(tokenizer, "eos_token_id", None) if tokenizer is not None else None
     sampling = SamplingParams(max_new_tokens=grpo_args.max_completion_length, temperature=grpo_args.temperature,
                               top_k=grpo_args.top_k, top_p=grpo_args.top_p)
     return OnPolicyRolloutSource(model, prompts, reward, grpo_args.num_generations, sampling, grpo_args.prompts_per_round,
-                                 eos_token_id=eos, seed=train_args.seed + pc.data_parallel_rank,
+                                 eos_token_id=eos, seed=train_args.seed + consumer_rank,
                                  max_prompt_length=grpo_args.max_prompt_length)
 
 
-def serve_rollout_copy(model_args, pc, device, roles, grpo_args):
-    """A rollout rank: hold a full (unsharded) serving copy and take every pushed update."""
+def serve_rollout_copy(model_args, pc, device, roles, grpo_args, data_args=None, train_args=None):
+    """A rollout rank: hold a full (unsharded) serving copy and take every pushed update; with a reward configured
+    it also samples the trainers' rounds from that copy and publishes them through the rendezvous store."""
     import torch
 
     from halo_b200.models.config import PRESETS, ModelConfig
@@ -82,8 +94,21 @@ def serve_rollout_copy(model_args, pc, device, roles, grpo_args):
     dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
     serving = build_model(cfg, device=device, dtype=dtype, transport=None, gradient_checkpointing=False)
     sync = make_sync(roles, device, build_manifest(serving), grpo_args.weight_sync_chunk_mb << 20)
-    n = rollout_loop(sync, roles, device, dict(serving.named_parameters()))
-    return {"updates": n}
+    publisher = None
+    if has_live_reward(grpo_args):
+        import torch.distributed as dist
+
+        from halo_b200.trainers.grpo.remote_rollouts import RolloutPublisher, served_trainers
+
+        mine = served_trainers(roles.rollout_ranks.index(roles.rank), len(roles.rollout_ranks), len(roles.trainer_ranks))
+        publisher = RolloutPublisher(
+            dist.distributed_c10d._get_default_store(), mine,
+            lambda t: sampling_source(serving, model_args, data_args, train_args, grpo_args, t, len(roles.trainer_ranks)),
+            prefetch=grpo_args.rollout_prefetch)
+        publisher.start()
+    n = rollout_loop(sync, roles, device, dict(serving.named_parameters()),
+                     on_update=publisher.on_update if publisher is not None else None)
+    return {"updates": n, "rounds": publisher.next_round if publisher is not None else 0}
 
 
 @with_distributed_teardown
@@ -100,12 +125,18 @@ def main(argv=None):
                               world_size=len(roles.trainer_ranks) if roles else 0,
                               global_rank=(roles.rank if roles.is_trainer else 0) if roles else -1)
     if roles is not None and not roles.is_trainer:
-        return serve_rollout_copy(model_args, pc, device, roles, grpo_args)
+        return serve_rollout_copy(model_args, pc, device, roles, grpo_args, data_args, train_args)
     runtime = build_runtime(pc, device, group=roles.trainer_group if roles else None)
     model = load_policy_model(model_args, pc, device, runtime, train_args.gradient_checkpointing,
                               max_tokens=grpo_args.token_budget)
     runtime = getattr(model, "parallel_runtime", runtime)      # tensor / context parallelism finish their runtime there
-    if grpo_args.rollout_backend == "in_process":
+    if roles is not None and has_live_reward(grpo_args):
+        import torch.distributed as dist
+
+        from halo_b200.trainers.grpo.remote_rollouts import StoreRolloutSource
+
+        source = StoreRolloutSource(dist.distributed_c10d._get_default_store(), roles.rank)     # sampled on the rollout ranks
+    elif grpo_args.rollout_backend == "in_process":
         source = in_process_source(model, model_args, data_args, train_args, grpo_args, pc)
     elif data_args.dataset_path:
         source = rollouts_from_jsonl(data_args.dataset_path, grpo_args.num_generations)

@@ -167,11 +167,15 @@ class Trainer:
                         "grad_norm": float(out.grad_norm.item()), "lr": self.lr_scheduler.get_last_lr()[0],
                         "tokens": self.tokens_seen, "step_seconds": (now - t_last) / args.logging_steps}
                 t_last = now
+                logs.update(self.extra_logs())
                 self.log_history.append(logs)
                 for cb in self.callbacks:
                     cb.on_log(self, logs)
                 if self.is_main:
-                    log.info("step %d loss %.4f grad_norm %.3f lr %.3g", logs["step"], logs["loss"], logs["grad_norm"], logs["lr"])
+                    extras = "".join(f" {k} {v:.4g}" for k, v in logs.items() if k not in
+                                     ("step", "loss", "grad_norm", "lr", "tokens", "step_seconds") and isinstance(v, (int, float)))
+                    log.info("step %d loss %.4f grad_norm %.3f lr %.3g%s", logs["step"], logs["loss"], logs["grad_norm"], logs["lr"],
+                             extras)
             for cb in self.callbacks:
                 cb.on_step_end(self, {"step": self.global_step})
             if args.save_steps and self.global_step % args.save_steps == 0:
@@ -183,6 +187,10 @@ class Trainer:
         for cb in self.callbacks:
             cb.on_train_end(self)
         return {"global_step": self.global_step, "log_history": self.log_history}
+
+    def extra_logs(self) -> dict:
+        """Method-specific scalars added to every log record."""
+        return {}
 
     def _guard_non_finite(self, out) -> None:
         """The skip flag of a step is read one step late, so the read never stalls the step it guards."""

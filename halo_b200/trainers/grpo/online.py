@@ -28,6 +28,15 @@ def token_match_reward(target_token: int) -> Callable:
     return reward
 
 
+def token_below_reward(threshold: int) -> Callable:
+    """Fraction of completion tokens whose id is below ``threshold`` (a dense signal on any vocabulary)."""
+
+    def reward(prompt_ids, completion_ids, task=None) -> float:
+        return float(np.mean(np.asarray(completion_ids) < threshold)) if len(completion_ids) else 0.0
+
+    return reward
+
+
 def text_reward(tokenizer, composer) -> Callable:
     """Decode and score with a reward composer; a failing scorer counts as that term's failure value there."""
 

@@ -145,6 +145,16 @@ class GRPOTrainer(Trainer):
             denom = torch.as_tensor(max(self._round_tokens, 1.0), device=num.device)
         return num / denom
 
+    def extra_logs(self) -> dict:
+        out = {}
+        src = self.rollout_source
+        if hasattr(src, "mean_reward"):
+            out["rollout_reward"] = float(src.mean_reward)
+        if hasattr(src, "last_version"):
+            out["rollout_version"] = int(src.last_version)
+            out["rollout_wait_seconds"] = float(src.waited_seconds)
+        return out
+
     # ---- weight push ---------------------------------------------------------------------------
     def after_optimizer_step(self):
         if self.weight_sync is not None and self.global_step % max(1, self.grpo.sync_weights_every) == 0:

@@ -49,3 +49,27 @@ def test_on_policy_grpo_raises_the_reward(tmp_path):
     trainer.train()
     assert np.mean(rewards[:5]) < 0.15                   # a fresh policy emits token 7 about once in 32
     assert np.mean(rewards[-5:]) > np.mean(rewards[:5]) + 0.3, (rewards[:5], rewards[-5:])
+
+
+def test_split_job_samples_on_the_rollout_rank(tmp_path):
+    """One trainer rank and one rollout rank (gloo): the rollout rank samples every round from its serving copy,
+    which follows the trainer's weights, and the reward rises."""
+    import os
+    import re
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = tmp_path / "grpo.yaml"
+    cfg.write_text("model_preset: tiny-moe\ninit_from_scratch: true\nmax_steps: 12\noptim: adamw_torch\nlearning_rate: 2.0e-2\n"
+                   "lr_scheduler_type: constant\nweight_decay: 0.0\n"
+                   f"output_dir: {tmp_path}/run\nnum_generations: 8\nprompts_per_round: 4\ntoken_budget: 4096\n"
+                   "max_completion_length: 8\nmax_prompt_length: 16\nrollout_gpus: 1\nsynthetic_reward_below: 2048\nsynthetic_vocab: 64\n"
+                   "rollout_prefetch: 1\n")
+    r = subprocess.run([sys.executable, "-m", "halo_b200.cli", "launch", "grpo", str(cfg), "-n", "2", "--port", "29697"],
+                       cwd=root, capture_output=True, text=True, timeout=420, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    out = r.stdout + r.stderr
+    assert r.returncode == 0, out[-4000:]
+    rewards = [float(x) for x in re.findall(r"rollout_reward ([0-9.]+)", out)]
+    assert len(rewards) >= 10, out[-2000:]
+    assert 0.3 < rewards[0] < 0.7 and max(rewards[-3:]) > rewards[0] + 0.1, rewards
