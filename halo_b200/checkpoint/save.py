@@ -145,6 +145,46 @@ def save_model(model, directory: str, is_writer: bool | None = None, save_dtype:
     guard.raise_if_any(None if not live else (group or dist.group.WORLD), "saving the model failed")
 
 
+def save_pipeline_stages(model, directory: str, stage_index: int, n_stages: int, group=None,
+                         save_dtype: torch.dtype | None = torch.bfloat16, max_shard_bytes: int = 5 * 1024**3) -> None:
+    """COLLECTIVE over the pipeline group (one rank per stage). Every stage writes its own layers - complete tensors
+    under hub names - into shard files of its own stem in ``directory``; the first stage then merges the stages'
+    tensor lists into the one ``model.safetensors.index.json`` and writes ``config.json``, so the result is an
+    ordinary checkpoint (halo/checkpoint/parallel/pp.py)."""
+    cfg = model.cfg
+    guard = DeferredRankFailure()
+    first_layer = model.layer_range[0]
+    weight_map, total = {}, 0
+    with guard.catch():
+        if stage_index == 0:
+            remove_stale_staged(directory)
+        writer = StreamingShardWriter(directory, max_shard_bytes, save_dtype, prefix=f"model-stage{stage_index:03d}")
+        for name, p in model.named_parameters():
+            for hub, t in runtime_to_hub(name, p.detach(), cfg, first_layer).items():
+                writer.add(hub, t)
+        writer.finish(write_index=False)
+        weight_map, total = writer.weight_map, writer.total_bytes
+    live = dist.is_available() and dist.is_initialized()
+    guard.raise_if_any(None if not live else (group or dist.group.WORLD), "a pipeline stage failed to write its tensors")
+    parts = [None] * n_stages
+    if live and n_stages > 1:
+        dist.all_gather_object(parts, (weight_map, total), group=group)
+    else:
+        parts = [(weight_map, total)]
+    with guard.catch():
+        if stage_index == 0:
+            merged: dict[str, str] = {}
+            for wm, _ in parts:
+                clash = set(merged) & set(wm)
+                if clash:
+                    raise KeyError(f"tensors written by two stages: {sorted(clash)[:3]}")
+                merged.update(wm)
+            atomic_write_json(os.path.join(directory, "model.safetensors.index.json"),
+                              {"metadata": {"total_size": sum(t for _, t in parts)}, "weight_map": merged})
+            cfg.save(directory)
+    guard.raise_if_any(None if not live else (group or dist.group.WORLD), "merging the pipeline stages' index failed")
+
+
 def mark_complete(directory: str, trainer_state: dict) -> None:
     """Written last: a checkpoint without it is incomplete and never resumed from."""
     atomic_write_json(os.path.join(directory, COMPLETE_MARKER), trainer_state)

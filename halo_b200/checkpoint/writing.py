@@ -16,8 +16,13 @@ SINGLE_NAME = "model.safetensors"
 
 
 class StreamingShardWriter:
-    def __init__(self, directory: str, max_shard_bytes: int = 5 * 1024**3, save_dtype: torch.dtype | None = None):
+    def __init__(self, directory: str, max_shard_bytes: int = 5 * 1024**3, save_dtype: torch.dtype | None = None,
+                 prefix: str = "model"):
+        """``prefix``: stem of the shard files. Writers that share a directory (pipeline stages) use distinct stems
+        and leave the merged index to their leader (``finish(write_index=False)``)."""
         self.directory = directory
+        self.prefix = prefix
+        self.weight_map: dict[str, str] = {}
         self.max_shard_bytes = max_shard_bytes
         self.save_dtype = save_dtype
         self.pending: dict[str, torch.Tensor] = {}
@@ -43,18 +48,20 @@ class StreamingShardWriter:
     def _flush(self) -> None:
         if not self.pending:
             return
-        tmp_name = f"model-part-{len(self.shards) + 1:05d}.safetensors"
+        tmp_name = f"{self.prefix}-part-{len(self.shards) + 1:05d}.safetensors"
         with staged_path(os.path.join(self.directory, tmp_name)) as tmp:
             save_file(self.pending, tmp, metadata={"format": "pt"})
         self.shards.append((tmp_name, list(self.pending)))
         self.pending, self.pending_bytes = {}, 0
 
-    def finish(self) -> list[str]:
-        """Cut the last shard, give the files their final names and write the index. Returns file names."""
+    def finish(self, write_index: bool = True) -> list[str]:
+        """Cut the last shard, give the files their final names and write the index (``self.weight_map`` holds it
+        either way). Returns file names."""
         self._flush()
         n = len(self.shards)
         names = []
-        if n == 1:
+        if n == 1 and write_index and self.prefix == "model":
+            self.weight_map = {t: SINGLE_NAME for t in self.shards[0][1]}
             os.replace(os.path.join(self.directory, self.shards[0][0]), os.path.join(self.directory, SINGLE_NAME))
             names.append(SINGLE_NAME)
             stale = os.path.join(self.directory, INDEX_NAME)
@@ -63,11 +70,13 @@ class StreamingShardWriter:
             return names
         weight_map = {}
         for i, (tmp_name, tensors) in enumerate(self.shards):
-            final = f"model-{i + 1:05d}-of-{n:05d}.safetensors"
+            final = f"{self.prefix}-{i + 1:05d}-of-{n:05d}.safetensors"
             os.replace(os.path.join(self.directory, tmp_name), os.path.join(self.directory, final))
             names.append(final)
             for t in tensors:
                 weight_map[t] = final
-        atomic_write_json(os.path.join(self.directory, INDEX_NAME),
-                          {"metadata": {"total_size": self.total_bytes}, "weight_map": weight_map})
+        self.weight_map = weight_map
+        if write_index:
+            atomic_write_json(os.path.join(self.directory, INDEX_NAME),
+                              {"metadata": {"total_size": self.total_bytes}, "weight_map": weight_map})
         return names

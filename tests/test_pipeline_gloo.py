@@ -112,3 +112,42 @@ def test_pipeline_training_follows_the_single_process_curve(tmp_path):
     a, b = np.load(single), np.load(pp)
     assert np.max(np.abs(a[:, 0] - b[:, 0])) < 2e-3, (a, b)
     assert np.max(np.abs(a[:, 1] - b[:, 1]) / a[:, 1]) < 5e-3, (a, b)
+
+
+def _save_worker(rank, world, directory):
+    import dataclasses
+
+    import torch.distributed as dist
+
+    from halo_b200.checkpoint.load import from_pretrained, load_model_weights
+    from halo_b200.checkpoint.save import save_pipeline_stages
+    from halo_b200.models.config import PRESETS
+    from halo_b200.models.qwen3 import build_model
+    from halo_b200.parallel.pipeline import build_stage_model
+
+    cfg = dataclasses.replace(PRESETS["tiny-moe"](), num_hidden_layers=4)
+    stage_model = build_stage_model(cfg, rank, world, "cpu", dtype=torch.float32, seed=5, split=[2])
+    save_pipeline_stages(stage_model, directory, rank, world, save_dtype=None, max_shard_bytes=2 << 20)
+    dist.barrier()
+    # the merged directory is an ordinary checkpoint: the whole model loads from it and equals the unsplit build ...
+    whole = from_pretrained(directory, device="cpu", dtype=torch.float32)
+    want = build_model(cfg, device="cpu", dtype=torch.float32, seed=5)
+    for (n, a), (_, b) in zip(whole.named_parameters(), want.named_parameters()):
+        assert torch.equal(a, b), n
+    # ... and a stage reads only its own layers back
+    again = build_stage_model(cfg, rank, world, "cpu", dtype=torch.float32, seed=99, split=[2])
+    load_model_weights(again, directory)
+    for (n, a), (_, b) in zip(again.named_parameters(), stage_model.named_parameters()):
+        assert torch.equal(a, b), n
+
+
+def test_stages_save_one_ordinary_checkpoint(tmp_path):
+    import json
+    import os
+
+    d = str(tmp_path / "ckpt")
+    run_gloo_ranks(_save_worker, 2, args=(d,), timeout=120.0)
+    index = json.load(open(os.path.join(d, "model.safetensors.index.json")))
+    files = set(index["weight_map"].values())
+    assert any(f.startswith("model-stage000-") for f in files) and any(f.startswith("model-stage001-") for f in files)
+    assert all(os.path.isfile(os.path.join(d, f)) for f in files) and os.path.isfile(os.path.join(d, "config.json"))
