@@ -124,3 +124,35 @@ def test_generation_and_evaluation_clis(tmp_path, capsys):
                                        b.position_ids, b.cu_seqlens, b.labels).item()
     assert report["tokens"] == 97 and abs(report["loss"] - want) < 1e-4
     assert 0.0 <= report["mtp_acceptance"] <= 1.0 and report["mtp_loss"] > 0
+
+
+def test_generation_callbacks(tmp_path):
+    from halo_b200.callbacks.generation import GenerateExamplesCallback, MtpAcceptanceGate, MtpGateFailed, PhaseTimerCallback
+    from halo_b200.configs.arguments import TrainingArguments
+    from halo_b200.diagnostics.phase_timers import PhaseTimers
+    from halo_b200.trainers.sft import SFTTrainer
+
+    cfg = dataclasses.replace(dense_cfg(), num_nextn_predict_layers=1)
+    rng = np.random.default_rng(0)
+    train = [pack_documents([rng.integers(0, 128, size=40)]) for _ in range(2)]
+
+    def run(lr, gate):
+        model = build_model(cfg, device="cpu", seed=1, gradient_checkpointing=False)
+        args = TrainingArguments(output_dir=str(tmp_path / f"run{lr}"), max_steps=30, learning_rate=lr, optim="adamw_torch",
+                                 lr_scheduler_type="constant", weight_decay=0.0, logging_steps=10)
+        timers = PhaseTimers(device="cpu")
+        examples = GenerateExamplesCallback([[1, 2, 3]], every=10, max_new_tokens=4)
+        trainer = SFTTrainer(model, args, iter(train * 100), device=torch.device("cpu"),
+                             callbacks=[examples, gate, PhaseTimerCallback(timers)])
+        with timers.span("whole"):
+            pass
+        trainer.train()
+        return trainer, examples
+
+    gate = MtpAcceptanceGate(train, min_gain=0.2)
+    trainer, examples = run(3e-3, gate)                      # the held-out rows are the training rows: acceptance rises
+    assert gate.final > gate.baseline + 0.2
+    assert [h["step"] for h in examples.history] == [10, 20, 30] and len(examples.history[0]["examples"][0]["completion_ids"]) == 4
+    assert any("phase/whole" in rec for rec in trainer.log_history)
+    with pytest.raises(MtpGateFailed, match="rejected"):
+        run(0.0 + 1e-12, MtpAcceptanceGate(train, min_gain=0.2))     # nothing learned: the gate fails the run
