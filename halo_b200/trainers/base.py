@@ -194,9 +194,12 @@ class Trainer:
 
     def _guard_non_finite(self, out) -> None:
         """The skip flag of a step is read one step late, so the read never stalls the step it guards."""
-        prev = self._pending_skip
+        prev, prev_requested = self._pending_skip, getattr(self, "_pending_requested", None)
         self._pending_skip = out.skipped.clone() if out is not None else None
-        if prev is not None and int(prev.item()):
+        self._pending_requested = out.extras.get("requested_skip") if out is not None else None
+        if prev is not None and prev_requested is not None and int(prev_requested.item()):
+            log.warning("step %d was skipped on the trainer's request (trust-region breaker)", self.global_step - 1)
+        elif prev is not None and int(prev.item()):
             self._consecutive_skips += 1
             log.warning("step %d was skipped: non-finite gradient norm", self.global_step - 1)
             if self._consecutive_skips >= self.args.max_consecutive_nonfinite_steps:

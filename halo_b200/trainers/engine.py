@@ -43,6 +43,10 @@ class TrainEngine:
         self.grad_norm = GradNorm(self.device)
         self.step_count = 0
         self.consecutive_skips = 0
+        # a device int32 flag a trainer may set before the optimizer step: non-zero on any rank skips this update on
+        # every rank (consumed and cleared by the step)
+        self.skip_request: torch.Tensor | None = None
+        self.last_skip_was_requested: torch.Tensor | None = None
         if hasattr(optimizer, "wait_ready") and hasattr(model, "param_gate"):
             model.param_gate = optimizer.wait_ready
 
@@ -72,6 +76,7 @@ class TrainEngine:
         self.grad_norm.total_sq.add_(shard_sq)
         dist.all_reduce(self.grad_norm.total_sq, group=self.parallel.dp_group)
         self.grad_norm.finish(self.max_grad_norm)
+        self._apply_skip_request()
         self.optimizer.defer_grad_scale(self.grad_norm.coef)
         self.optimizer.arm_skip(self.grad_norm.skip)
         self.optimizer.step()
@@ -81,6 +86,19 @@ class TrainEngine:
             fused.lr = self.optimizer.param_groups[0]["lr"]
         self.optimizer.zero_grad(set_to_none=True)
         fused.zero_grad()
+
+    def _apply_skip_request(self) -> None:
+        """Fold a trainer's skip request into the step's skip flag (after the gradient norm set it)."""
+        req, self.skip_request = self.skip_request, None
+        if req is None:
+            return
+        req = req.to(self.grad_norm.skip.dtype).reshape(self.grad_norm.skip.shape)
+        if self.parallel is not None and self.parallel.dp_world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(req, op=dist.ReduceOp.MAX, group=self.parallel.dp_group)
+        self.grad_norm.skip.copy_(torch.maximum(self.grad_norm.skip, req))
+        self.last_skip_was_requested = req
 
     def clip_and_step(self) -> None:
         fused = getattr(self.parallel, "fused_optimizer", None) if self.parallel is not None else None
@@ -93,6 +111,7 @@ class TrainEngine:
         else:
             self.grad_norm.accumulate([p.grad for p in params], first=True)
         self.grad_norm.finish(self.max_grad_norm)
+        self._apply_skip_request()
         if hasattr(self.optimizer, "defer_grad_scale"):
             self.optimizer.defer_grad_scale(self.grad_norm.coef)
             self.optimizer.arm_skip(self.grad_norm.skip)
@@ -120,7 +139,9 @@ class TrainEngine:
         if not accumulate:
             self.clip_and_step()
             self.step_count += 1
-        return StepOutput(loss.detach(), self.grad_norm.norm, self.grad_norm.skip, batch.n_tokens)
+        requested, self.last_skip_was_requested = self.last_skip_was_requested, None
+        return StepOutput(loss.detach(), self.grad_norm.norm, self.grad_norm.skip, batch.n_tokens,
+                          {} if requested is None else {"requested_skip": requested})
 
     @torch.no_grad()
     def eval_step(self, batch: PackedBatch) -> torch.Tensor:

@@ -60,11 +60,15 @@ def normalizer(loss_type: str, mask: torch.Tensor, seq_lengths: torch.Tensor | N
     raise ValueError(f"unknown loss_type {loss_type!r}")
 
 
+def capped_fraction(is_weights: torch.Tensor, mask: torch.Tensor, clip_max: float) -> torch.Tensor:
+    """Share of counted tokens whose importance weight sits at the cap (a device scalar)."""
+    m = mask.to(torch.float32)
+    return ((is_weights >= clip_max).to(torch.float32) * m).sum() / m.sum().clamp_min(1.0)
+
+
 def trust_region_breaker(is_weights: torch.Tensor, mask: torch.Tensor, clip_max: float, max_fraction: float) -> bool:
     """True when so many tokens sit at the importance-weight cap that the round should be skipped."""
-    m = mask.to(torch.float32)
-    frac = ((is_weights >= clip_max).to(torch.float32) * m).sum() / m.sum().clamp_min(1.0)
-    return bool(frac > max_fraction)
+    return bool(capped_fraction(is_weights, mask, clip_max) > max_fraction)
 
 
 # ---- optional mask stages (off by default; halo/trainers/grpo/objective/logratio.py:205-257) -------------------

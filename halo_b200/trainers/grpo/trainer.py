@@ -133,6 +133,12 @@ class GRPOTrainer(Trainer):
         is_w = None
         if batch.has_old:
             is_w = objective.importance_weights(logp, batch.old_logprobs, mask, g.importance_clip_max)
+            if g.trust_region_mask_fraction < 1.0:
+                # the breaker: too many tokens at the importance cap means the sampler and the trainer have drifted
+                # apart; the whole round's update is skipped on every rank (the flag stays on the device)
+                over = (objective.capped_fraction(is_w, mask, g.importance_clip_max) > g.trust_region_mask_fraction).to(torch.int32)
+                prev = self.engine.skip_request
+                self.engine.skip_request = over if prev is None else torch.maximum(prev, over)
         ref = None
         if g.grpo_beta and self.ref_model is not None:
             with torch.no_grad():

@@ -73,3 +73,36 @@ def test_split_job_samples_on_the_rollout_rank(tmp_path):
     rewards = [float(x) for x in re.findall(r"rollout_reward ([0-9.]+)", out)]
     assert len(rewards) >= 10, out[-2000:]
     assert 0.3 < rewards[0] < 0.7 and max(rewards[-3:]) > rewards[0] + 0.1, rewards
+
+
+def test_trust_region_breaker_skips_the_update(tmp_path):
+    """Rollouts whose sampler log-probabilities are far from the trainer's put every token at the importance cap:
+    with the breaker armed the weights stay put, without it they move."""
+    from halo_b200.trainers.grpo.trainer import Rollout
+
+    def run(fraction):
+        model = build_model(tiny(), device="cpu", seed=0, gradient_checkpointing=False)
+        before = {n: p.detach().clone() for n, p in model.named_parameters()}
+        rng = np.random.default_rng(1)
+
+        def source(i):
+            if i >= 2:
+                return None
+            out = []
+            for _ in range(2):
+                prompt = rng.integers(0, 32, size=4)
+                for _ in range(4):
+                    comp = rng.integers(0, 32, size=6)
+                    out.append(Rollout(prompt, comp, np.full(6, -30.0, dtype=np.float32), float(rng.normal())))
+            return out
+
+        args = TrainingArguments(output_dir=str(tmp_path / f"r{fraction}"), max_steps=2, learning_rate=1e-2, optim="adamw_torch",
+                                 weight_decay=0.0, lr_scheduler_type="constant", logging_steps=1000)
+        trainer = GRPOTrainer(model, args, source, device=torch.device("cpu"),
+                              grpo_args=GRPOArguments(num_generations=4, max_completion_length=6, token_budget=4096,
+                                                      trust_region_mask_fraction=fraction))
+        trainer.train()
+        return max(float((p.detach() - before[n]).abs().max()) for n, p in model.named_parameters())
+
+    assert run(0.5) == 0.0
+    assert run(1.0) > 0.0
