@@ -212,6 +212,7 @@ class GRPOArguments:
     rollout_backend: Literal["in_process", "vllm", "sglang", "resident_copy"] = "resident_copy"
     rollout_gpus: int = 0
     weight_sync_chunk_mb: int = 1024
+    push_parity_tolerance: float = 0.05         # nats; after the first push trainers and rollout copy score one fixed row (0 = off)
     rollout_prefetch: int = 0                   # rounds the rollout ranks sample ahead (0 = strictly on-policy, 1 = one update stale)
     prompts_per_round: int = 8                  # in_process rollouts: prompts sampled per round (x num_generations completions)
     temperature: float = 1.0

@@ -106,8 +106,19 @@ def serve_rollout_copy(model_args, pc, device, roles, grpo_args, data_args=None,
             lambda t: sampling_source(serving, model_args, data_args, train_args, grpo_args, t, len(roles.trainer_ranks)),
             prefetch=grpo_args.rollout_prefetch)
         publisher.start()
-    n = rollout_loop(sync, roles, device, dict(serving.named_parameters()),
-                     on_update=publisher.on_update if publisher is not None else None)
+    first_rollout_rank = roles.rank == roles.rollout_ranks[0]
+
+    def on_update(n_updates: int) -> None:
+        if n_updates == 1 and first_rollout_rank and grpo_args.push_parity_tolerance > 0:
+            import torch.distributed as dist
+
+            from halo_b200.weight_sync import parity
+
+            parity.publish(dist.distributed_c10d._get_default_store(), parity.score_fixed_row(serving, device))
+        if publisher is not None:
+            publisher.on_update(n_updates)
+
+    n = rollout_loop(sync, roles, device, dict(serving.named_parameters()), on_update=on_update)
     return {"updates": n, "rounds": publisher.next_round if publisher is not None else 0}
 
 
@@ -155,6 +166,8 @@ def main(argv=None):
 
         sync = make_sync(roles, device, full_manifest(model), grpo_args.weight_sync_chunk_mb << 20)
         weight_sync = ModelWeightPusher(sync, roles, device, runtime.ep_group if runtime else None)
+        if grpo_args.push_parity_tolerance > 0:
+            weight_sync.parity_tolerance = grpo_args.push_parity_tolerance
     trainer = GRPOTrainer(model, train_args, source, grpo_args=grpo_args, weight_sync=weight_sync, device=device,
                           parallel=runtime, parallelism_fingerprint=pc.fingerprint())
     if roles is not None:

@@ -65,12 +65,20 @@ class ModelWeightPusher:
     def __init__(self, sync, roles: Roles, device, ep_group=None):
         self.sync, self.roles, self.device, self.ep_group = sync, roles, torch.device(device), ep_group
         self.pushes = 0
+        self.parity_tolerance = 0.0       # > 0: after the first push, compare one fixed row's scores with the rollout copy's
+        self.parity_gap = None
 
     def push(self, model) -> None:
         gathered = dict(full_named_tensors(model, self.ep_group))    # collective over the trainers
         _control(PUSH, self.roles, self.device)
         self.sync.push(gathered if self.roles.rank == self.roles.src_rank else None)
         self.pushes += 1
+        if self.pushes == 1 and self.parity_tolerance > 0:
+            from . import parity
+
+            mine = parity.score_fixed_row(model, self.device)           # collective over the trainers under expert parallelism
+            if self.roles.rank == self.roles.src_rank:
+                self.parity_gap = parity.compare(dist.distributed_c10d._get_default_store(), mine, self.parity_tolerance)
 
     def close(self) -> None:
         _control(STOP, self.roles, self.device)

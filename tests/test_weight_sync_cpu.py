@@ -98,3 +98,36 @@ def test_one_trainer_one_rollout_job_finishes(tmp_path):
                        cwd=root, capture_output=True, text=True, timeout=240, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert os.path.isfile(tmp_path / "run" / "final" / "config.json")
+
+
+def test_push_parity_compares_fixed_row_scores():
+    import numpy as np
+    import pytest
+
+    from halo_b200.models.config import tiny_moe_config
+    from halo_b200.models.qwen3 import build_model
+    from halo_b200.weight_sync import parity
+
+    class Store(dict):
+        def set(self, k, v):
+            self[k] = v
+
+        def check(self, keys):
+            return all(k in self for k in keys)
+
+        def get(self, k):
+            return self[k]
+
+    trainer = build_model(tiny_moe_config(), device="cpu", seed=0, gradient_checkpointing=False)
+    copy = build_model(tiny_moe_config(), device="cpu", seed=0, gradient_checkpointing=False)
+    store = Store()
+    parity.publish(store, parity.score_fixed_row(copy, "cpu"))
+    mine = parity.score_fixed_row(trainer, "cpu")
+    assert mine.shape == (94,) and parity.compare(store, mine, 0.05, 1.0) < 1e-6
+    with torch.no_grad():
+        copy.layers[1].self_attn.o_proj.mul_(1.5)                 # a tensor that did not arrive intact
+    parity.publish(store, parity.score_fixed_row(copy, "cpu"))
+    with pytest.raises(RuntimeError, match="push parity failed"):
+        parity.compare(store, mine, 0.05, 1.0)
+    with pytest.raises(TimeoutError):
+        parity.compare(Store(), mine, 0.05, 0.1)
