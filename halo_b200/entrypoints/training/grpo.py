@@ -31,7 +31,8 @@ def rollouts_from_jsonl(path: str, group: int):
 
 
 def has_live_reward(grpo_args) -> bool:
-    return grpo_args.synthetic_reward_token >= 0 or grpo_args.synthetic_reward_below >= 0 or bool(grpo_args.reward_terms)
+    return (grpo_args.synthetic_reward_token >= 0 or grpo_args.synthetic_reward_below >= 0 or bool(grpo_args.reward_terms)
+            or bool(grpo_args.environment_type))
 
 
 def in_process_source(model, model_args, data_args, train_args, grpo_args, pc):
@@ -45,6 +46,23 @@ def sampling_source(model, model_args, data_args, train_args, grpo_args, consume
     from halo_b200.inference.generate import SamplingParams
     from halo_b200.trainers.grpo.online import OnPolicyRolloutSource, text_reward, token_below_reward, token_match_reward
 
+    if grpo_args.environment_type:
+        from halo_b200.entrypoints.script import load_tokenizer
+        from halo_b200.trainers.grpo.environment_rollouts import EnvironmentRolloutSource
+
+        if not data_args.dataset_path:
+            raise ValueError("environment rollouts need dataset_path: a JSONL of task rows for the environment")
+        tasks = [json.loads(l) for l in open(data_args.dataset_path) if l.strip()][consumer_rank::max(1, n_consumers)]
+        composer = None
+        if grpo_args.reward_terms:
+            from halo_b200.rewards.terms import RewardComposer, parse_terms
+
+            composer = RewardComposer(parse_terms(grpo_args.reward_terms))
+        sampling = SamplingParams(max_new_tokens=grpo_args.max_completion_length, temperature=grpo_args.temperature,
+                                  top_k=grpo_args.top_k, top_p=grpo_args.top_p)
+        return EnvironmentRolloutSource(model, load_tokenizer(model_args), tasks, grpo_args.environment_type, grpo_args.num_generations,
+                                        sampling, grpo_args.prompts_per_round, composer, grpo_args.environment_options,
+                                        seed=train_args.seed + consumer_rank)
     tokenizer = None
     if data_args.dataset_path:
         rows = [json.loads(l) for l in open(data_args.dataset_path) if l.strip()]

@@ -99,3 +99,62 @@ class CodeEnvironment(Environment):
 
     def close(self):
         self.sandbox.close()
+
+
+@register_environment("tool_qa")
+class ToolQAEnvironment(Environment):
+    """A question answered over several turns with tools (calculator, optionally a sandboxed ``python``), under the
+    native tool-call protocol or ReAct (``protocol`` option). The score is the graded final answer."""
+
+    env_type = "tool_qa"
+    max_turns = 6
+
+    def __init__(self, task, **options):
+        super().__init__(task, **options)
+        from .protocols import PROTOCOLS, default_tools
+
+        self.protocol = options.get("protocol", "native")
+        self.parse, self.render = PROTOCOLS[self.protocol]
+        self.sandbox = make_sandbox(options["sandbox"]) if options.get("sandbox") else None
+        self.registry = options.get("tools") or default_tools(self.sandbox)
+        self.answer = None
+
+    def tools(self):
+        return self.registry.definitions() if self.protocol == "native" else []
+
+    def reset(self):
+        from .protocols import REACT_INSTRUCTIONS
+
+        system = self.options.get("system_prompt", "Solve the problem; use the tools when they help.")
+        if self.protocol == "react":
+            system += "\n" + REACT_INSTRUCTIONS.format(names=", ".join(self.registry.names()))
+        self.record.messages = [{"role": "system", "content": system}, {"role": "user", "content": self.task["question"]}]
+        return list(self.record.messages)
+
+    def step(self, reply: Turn):
+        from .protocols import MalformedTurn
+
+        self.record.turns.append(reply)
+        try:
+            parsed = self.parse(reply)
+        except MalformedTurn as exc:
+            return self.recover(str(exc))
+        if parsed.final_answer is not None:
+            self.answer, self.record.done_reason = parsed.final_answer, "answered"
+            return [], True
+        if not self.charge_tool_calls(len(parsed.calls)):
+            self.record.done_reason = "tool_budget"
+            return [], True
+        return [self.render(c, self.registry.call(c)) for c in parsed.calls], False
+
+    def score(self) -> float:
+        text = self.answer or ""
+        if "\\boxed" in text:
+            self.record.score = graders.boxed_accuracy(text, self.task["answer"], strict=False)
+        else:
+            self.record.score = float(graders.normalize_answer(text) == graders.normalize_answer(str(self.task["answer"])))
+        return self.record.score
+
+    def close(self):
+        if self.sandbox is not None:
+            self.sandbox.close()

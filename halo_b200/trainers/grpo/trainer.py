@@ -31,6 +31,7 @@ class Rollout:
     completion_ids: np.ndarray
     sampler_logprobs: np.ndarray | None   # per completion token; None = treat as on-policy
     reward: float
+    completion_mask: np.ndarray | None = None   # 1 on tokens the policy produced, 0 on environment tokens in between; None = all 1
 
 
 @dataclass
@@ -52,7 +53,8 @@ def build_grpo_batch(rollouts: list[Rollout], adv: torch.Tensor, degenerate: tor
     docs, masks = [], []
     for r in rollouts:
         docs.append(np.concatenate([r.prompt_ids, r.completion_ids]))
-        masks.append(np.concatenate([np.zeros(len(r.prompt_ids), bool), np.ones(len(r.completion_ids), bool)]))
+        own = np.ones(len(r.completion_ids), bool) if r.completion_mask is None else np.asarray(r.completion_mask, bool)
+        masks.append(np.concatenate([np.zeros(len(r.prompt_ids), bool), own]))
     base = pack_documents(docs, label_masks=masks)
     T = base.n_tokens
     a = torch.zeros(T)
