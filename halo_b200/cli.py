@@ -30,6 +30,7 @@ TOOLS = {
     "prepare-dataset": "halo_b200.data.preprocessed",
     "generate": "halo_b200.entrypoints.generation",
     "evaluate": "halo_b200.entrypoints.evaluation",
+    "reward-scoring": "halo_b200.entrypoints.reward_scoring",
     "merge-adapter": "halo_b200.checkpoint.tools.merge_adapter",
     "bench": "bench",
 }

@@ -87,3 +87,24 @@ def test_resumable_batch(tmp_path):
     done = asyncio.run(run_batch(client, reqs, store))           # everything is on disk: nothing is sent again
     assert len(calls) == n and len(done) == 3
     assert all(json.loads(l)["request_id"] for l in open(store))
+
+
+def test_offline_reward_scoring_resumes(tmp_path, capsys):
+    import json
+
+    from halo_b200.entrypoints import reward_scoring
+
+    rows = tmp_path / "rows.jsonl"
+    rows.write_text("\n".join(json.dumps({"completion": f"so \\boxed{{{i}}}", "target": str(i if i % 2 else -1)}) for i in range(6)))
+    terms = tmp_path / "terms.yaml"
+    terms.write_text("reward_terms:\n  - {type: grader, grader: boxed_accuracy, weight: 2.0}\n")
+    out = tmp_path / "scored.jsonl"
+    assert reward_scoring.main(["score", str(rows), "--terms", str(terms), "--out", str(out)]) == 0
+    first = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert first["scored"] == 6 and first["mean_reward"] == 1.0            # three of six right, weight 2
+    scored = [json.loads(l) for l in open(out)]
+    assert [r["reward"] for r in scored] == [0.0, 2.0, 0.0, 2.0, 0.0, 2.0]
+    out.write_text("\n".join(json.dumps(r) for r in scored[:4]) + "\n")     # an interrupted run left four rows
+    assert reward_scoring.main(["score", str(rows), "--terms", str(terms), "--out", str(out)]) == 0
+    again = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert again["scored"] == 2 and again["skipped"] == 4 and len(open(out).read().splitlines()) == 6
