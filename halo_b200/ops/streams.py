@@ -341,24 +341,39 @@ class _Project(torch.autograd.Function):
             dx = (gs @ fn.float() - x.float() * coeff.unsqueeze(-1)).to(x.dtype).reshape(ctx.stream_shape)
         dfn = None
         if ctx.needs_input_grad[1]:
-            dfn = (gs.t().to(x.dtype) @ x).float() if x.is_cuda else gs.t() @ x.float()
+            if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0:
+                from .gemm import matmul
+
+                gs16 = _pad_rows(gs.t().contiguous()).t().contiguous().to(x.dtype)        # [T, Kp]: columns padded to 8
+                dfn = matmul(gs16, x, a_t=True, b_t=False, out_dtype=torch.float32)[:K]
+            else:
+                dfn = gs.t() @ x.float()
             dfn = dfn.to(fn.dtype)
         return dx, dfn, None
 
 
+def _pad_rows(t: torch.Tensor, multiple: int = 8) -> torch.Tensor:
+    extra = (-t.shape[0]) % multiple
+    return t if not extra else torch.cat([t, t.new_zeros(extra, *t.shape[1:])], dim=0)
+
+
 def _skinny_product(x: torch.Tensor, fn: torch.Tensor) -> torch.Tensor:
     """``x @ fn^T`` in fp32 for a handful of output columns. On CUDA the fp32 weights are split into a bf16 head
-    and a bf16 remainder so the wide bf16 ``x`` is read once by one tensor-core product; the two partial results are
-    added in fp32 (relative error ~2^-16 of the weights, far below the bf16 rounding already in ``x``)."""
-    if not x.is_cuda:
+    and a bf16 remainder so the wide bf16 ``x`` is read once by one tensor-core product with an fp32 result; the two
+    partial results are added in fp32 (relative error ~2^-16 of the weights, far below the bf16 rounding already in
+    ``x``)."""
+    if not x.is_cuda or x.dtype != torch.bfloat16 or x.shape[1] % 8:
         return x.float() @ fn.float().t()
-    f32 = fn.float()
+    from .gemm import matmul
+
+    K = fn.shape[0]
+    f32 = fn.detach().float()
     hi = f32.to(torch.bfloat16)
     lo = (f32 - hi.float()).to(torch.bfloat16)
-    both = torch.cat([hi, lo], dim=0)                       # [2K, W]
-    out = torch.matmul(x, both.t()).float()                 # plain library GEMM, fp32 accumulation
-    K = fn.shape[0]
-    return out[:, :K] + out[:, K:]
+    hi, lo = _pad_rows(hi), _pad_rows(lo)                    # the GEMM wants row counts in multiples of 8
+    Kp = hi.shape[0]
+    out = matmul(x, torch.cat([hi, lo], dim=0), out_dtype=torch.float32)        # [T, 2 Kp] fp32
+    return out[:, :K] + out[:, Kp:Kp + K]
 
 
 def project_streams(stream: torch.Tensor, fn: torch.Tensor, norm_eps: float) -> torch.Tensor:
