@@ -59,6 +59,7 @@ class DataArguments:
     text_field: str = "text"
     packing: bool = True
     packed_row_length: int = 8192
+    packing_strategy: Literal["sequential", "best_fit"] = "sequential"
     completion_only_loss: bool = False
     shuffle_seed: int = 0
     synthetic_vocab: int = 0

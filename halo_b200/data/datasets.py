@@ -66,6 +66,11 @@ def tokenize_record(rec: dict, tokenizer, fmt: str = "auto") -> tuple[np.ndarray
         return ids, mask
     if tokenizer is None:
         raise ValueError("a tokenizer is needed for text records (or provide pre-tokenised 'input_ids')")
+    if "messages" in rec and getattr(tokenizer, "chat_template", None):
+        from .chat_render import render_conversation
+
+        ids, mask, _ = render_conversation(tokenizer, rec["messages"], rec.get("tools"))
+        return ids, mask
     if "messages" in rec:
         text, spans = render_messages(rec["messages"])
         enc = tokenizer(text, return_offsets_mapping=True, add_special_tokens=False)
@@ -82,8 +87,17 @@ def tokenize_record(rec: dict, tokenizer, fmt: str = "auto") -> tuple[np.ndarray
     return ids, np.ones(len(ids), bool)
 
 
-def pack_rows(docs: list[tuple[np.ndarray, np.ndarray]], row_len: int, completion_only: bool) -> list[PackedBatch]:
-    """Greedy sequential packing into rows of ``row_len`` tokens; a document longer than a row is cut."""
+def pack_rows(docs: list[tuple[np.ndarray, np.ndarray]], row_len: int, completion_only: bool, strategy: str = "sequential") -> list[PackedBatch]:
+    """Packing into rows of ``row_len`` tokens; a document longer than a row is cut. ``sequential``: greedy in order;
+    ``best_fit``: best-fit-decreasing inside a look-ahead window (fuller rows)."""
+    if strategy == "best_fit":
+        from .sources import best_fit_rows
+
+        out = []
+        for members in best_fit_rows([len(ids) for ids, _ in docs], row_len):
+            out.append(pack_documents([docs[i][0][:row_len] for i in members], row_len=row_len,
+                                      label_masks=[docs[i][1][:row_len] for i in members] if completion_only else None))
+        return out
     rows, cur, cur_masks, used = [], [], [], 0
     for ids, mask in docs:
         ids, mask = ids[:row_len], mask[:row_len]
@@ -107,7 +121,8 @@ def build_sft_batches(data_args, tokenizer, dp_rank: int = 0, dp_world: int = 1,
     docs = [tokenize_record(r, tokenizer, data_args.dataset_format) for r in read_records(data_args.dataset_path)]
     order = np.random.default_rng(data_args.shuffle_seed).permutation(len(docs))
     docs = [docs[i] for i in order]
-    rows = pack_rows(docs, data_args.packed_row_length, data_args.completion_only_loss)
+    rows = pack_rows(docs, data_args.packed_row_length, data_args.completion_only_loss,
+                     getattr(data_args, "packing_strategy", "sequential"))
     return rows[dp_rank::dp_world]
 
 

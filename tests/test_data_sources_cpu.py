@@ -1,0 +1,119 @@
+"""Data sources on CPU: chat rendering finds the assistant spans by prefix rendering (and notices templates that rewrite
+history), corpus mixes keep their ratios on every prefix and resume, shards and the replica identity check, best-fit
+packing."""
+
+import numpy as np
+import pytest
+
+from halo_b200.data.chat_render import completion_spans, render_conversation
+from halo_b200.data.sources import CorpusMix, assert_replicas_identical, best_fit_rows, data_digest, shard_for_rank
+from tests.common.gloo import run_gloo_ranks
+
+
+class WordTokenizer:
+    """Whitespace words are tokens; the template wraps turns in role markers."""
+
+    chat_template = "yes"
+
+    def __init__(self, drop_old_reasoning=False):
+        self.vocab, self.drop = {}, drop_old_reasoning
+
+    def _ids(self, text):
+        return [self.vocab.setdefault(w, len(self.vocab)) for w in text.split()]
+
+    def apply_chat_template(self, messages, add_generation_prompt=False, tokenize=True, tools=None):
+        parts = []
+        last_user = max((i for i, m in enumerate(messages) if m["role"] == "user"), default=-1)
+        for i, m in enumerate(messages):
+            content = m["content"]
+            if self.drop and m["role"] == "assistant" and i < last_user:
+                content = content.split("</think>")[-1]              # reasoning before the last user turn is cut from history
+            parts.append(f"<{m['role']}> {content} <end>")
+        text = " ".join(parts) + (" <assistant>" if add_generation_prompt else "")
+        return self._ids(text)
+
+
+CONV = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "two plus two ?"},
+        {"role": "assistant", "content": "<think> easy </think> four"}, {"role": "user", "content": "times three ?"},
+        {"role": "assistant", "content": "twelve"}]
+
+
+def test_assistant_spans_by_prefix_rendering():
+    tok = WordTokenizer()
+    ids, mask, report = render_conversation(tok, CONV)
+    words = {v: k for k, v in tok.vocab.items()}
+    scored = [[words[i] for i in ids[a:b]] for a, b in completion_spans(mask)]
+    assert scored == [["<think>", "easy", "</think>", "four", "<end>"], ["twelve", "<end>"]] and report == {"rewritten": 0, "turns": 2}
+    _, last, _ = render_conversation(tok, CONV, last_turn_only=True)
+    assert completion_spans(last) == completion_spans(mask)[-1:]
+    _, everything, _ = render_conversation(tok, CONV, train_on="all")
+    assert everything.all()
+
+
+def test_history_rewriting_template_is_noticed():
+    tok = WordTokenizer(drop_old_reasoning=True)
+    ids, mask, report = render_conversation(tok, CONV)
+    words = {v: k for k, v in tok.vocab.items()}
+    assert report == {"rewritten": 1, "turns": 2}                       # the first turn's tokens changed once it became history
+    assert [[words[i] for i in ids[a:b]] for a, b in completion_spans(mask)] == [["twelve", "<end>"]]
+
+
+def test_corpus_mix_keeps_ratios_on_every_prefix_and_resumes():
+    a, b, c = [f"a{i}" for i in range(7)], [f"b{i}" for i in range(50)], [f"c{i}" for i in range(3)]
+    mix = CorpusMix([a, b, c], [1, 6, 3], seed=4)
+    picks = [next(mix) for _ in range(200)]
+    for n in (10, 50, 200):
+        counts = np.bincount([i for i, _ in picks[:n]], minlength=3)
+        assert np.abs(counts - np.array([0.1, 0.6, 0.3]) * n).max() <= 1.0
+    first_epoch_c = [d for i, d in picks if i == 2][:3]
+    assert sorted(first_epoch_c) == c                                       # an epoch visits every document once
+    resumed = CorpusMix([a, b, c], [1, 6, 3], seed=4)
+    for _ in range(120):
+        next(resumed)
+    state = resumed.state_dict()
+    fresh = CorpusMix([a, b, c], [1, 6, 3], seed=4)
+    fresh.load_state_dict(state)
+    assert [next(fresh) for _ in range(80)] == picks[120:200]
+    with pytest.raises(ValueError):
+        CorpusMix([a], [0.0])
+
+
+def test_shards_and_best_fit():
+    files = [f"part-{i:03d}.jsonl" for i in range(10)]
+    seen = []
+    for r in range(4):
+        mine, (off, stride) = shard_for_rank(files, r, 4)
+        assert (off, stride) == (0, 1)
+        seen += mine
+    assert sorted(seen) == files
+    assert shard_for_rank(files[:2], 3, 4) == (files[:2], (3, 4))
+    rng = np.random.default_rng(0)
+    lengths = rng.integers(50, 900, size=400).tolist()
+    rows = best_fit_rows(lengths, 1024, window=128)
+    assert sorted(i for r in rows for i in r) == list(range(400))
+    assert all(sum(lengths[i] for i in r) <= 1024 for r in rows)
+    sequential, used = 1, 0
+    for n in lengths:
+        if used + n > 1024:
+            sequential, used = sequential + 1, 0
+        used += n
+    assert len(rows) < 0.93 * sequential                                   # fuller rows than greedy in order
+
+
+def _identity_worker(rank, world, same):
+    from halo_b200.data.packing import pack_documents
+
+    rows = [pack_documents([np.arange(10) + (0 if same else rank)])]
+    if same:
+        assert_replicas_identical(rows)
+    else:
+        with pytest.raises(RuntimeError, match="different data"):
+            assert_replicas_identical(rows)
+
+
+@pytest.mark.parametrize("same", [True, False])
+def test_replica_identity_is_agreed_on_every_rank(same):
+    run_gloo_ranks(_identity_worker, 2, args=(same,), timeout=60.0)
+    from halo_b200.data.packing import pack_documents
+
+    assert data_digest([pack_documents([np.arange(5)])]) != data_digest([pack_documents([np.arange(6)])])
