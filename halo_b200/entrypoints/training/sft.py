@@ -19,6 +19,12 @@ def main(argv=None):
     runtime = getattr(model, "parallel_runtime", runtime)      # tensor / context parallelism finish their runtime there
     tokenizer = load_tokenizer(model_args)
     batches = build_sft_batches(data_args, tokenizer, pc.data_parallel_rank, pc.data_parallel_size, model.cfg.vocab_size)
+    token_cut = getattr(runtime, "tensor_parallel", None) or getattr(runtime, "context_parallel", None) if runtime is not None else None
+    if token_cut is not None:
+        from halo_b200.data.sources import assert_replicas_identical
+
+        # the ranks of a tensor- / context-parallel group each take their tokens of the SAME row
+        assert_replicas_identical(batches[:32], token_cut.group, "tensor- or context-parallel group")
     trainer = SFTTrainer(model, train_args, batches, device=device, parallel=runtime,
                          callbacks=build_callbacks(train_args, model, pc.world_size, pc.global_rank,
                                                    tokens_per_step=data_args.packed_row_length),
