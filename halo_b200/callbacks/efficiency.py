@@ -50,6 +50,9 @@ class EfficiencyCallback(Callback):
 
             self._last = time.perf_counter()
 
+    def on_batch(self, trainer, batch):
+        self.note_batch(batch)
+
     def note_batch(self, batch):
         self._tokens += batch.n_tokens
         self._flops += model_flops_per_step(self.cfg, batch.cu_seqlens, batch.n_tokens)

@@ -40,6 +40,7 @@ class NonFiniteRun(RuntimeError):
 
 class Callback:
     def on_train_begin(self, trainer): ...
+    def on_batch(self, trainer, batch): ...
     def on_step_end(self, trainer, logs: dict): ...
     def on_log(self, trainer, logs: dict): ...
     def on_save(self, trainer, directory: str): ...
@@ -158,6 +159,10 @@ class Trainer:
             for i, b in enumerate(micro):
                 out = self.engine.train_step(b, accumulate=i < len(micro) - 1)
                 self.tokens_seen += b.n_tokens
+                for cb in self.callbacks:
+                    on_batch = getattr(cb, "on_batch", None)
+                    if on_batch is not None:
+                        on_batch(self, b)
             self.global_step += 1
             self.after_optimizer_step()
             self._guard_non_finite(out)

@@ -200,3 +200,27 @@ def test_grpo_mask_stages_rank_rewards_reference_cache_and_async_source(tmp_path
     while src(0) is not None:
         pass
     src.close()
+
+
+def test_efficiency_metrics_reach_the_logs(tmp_path):
+    """Tokens per second and model-FLOPs utilisation come from the batches the trainer really ran."""
+    import torch
+
+    from halo_b200.callbacks.efficiency import EfficiencyCallback, model_flops_per_step
+    from halo_b200.configs.arguments import TrainingArguments
+    from halo_b200.data.packing import synthetic_packed_batch
+    from halo_b200.models.config import tiny_moe_config
+    from halo_b200.models.qwen3 import build_model
+    from halo_b200.trainers.sft import SFTTrainer
+
+    cfg = tiny_moe_config()
+    model = build_model(cfg, device="cpu", seed=0)
+    batches = [synthetic_packed_batch(128, cfg.vocab_size, seed=i, lo=16, hi=64) for i in range(4)]
+    eff = EfficiencyCallback(cfg, 1)
+    args = TrainingArguments(output_dir=str(tmp_path / "run"), max_steps=2, optim="adamw_torch", logging_steps=1)
+    trainer = SFTTrainer(model, args, iter(batches), device=torch.device("cpu"), callbacks=[eff])
+    trainer.train()
+    rec = trainer.log_history[-1]
+    assert rec["tokens_per_s_per_gpu"] > 0 and rec["mfu"] > 0
+    flops = model_flops_per_step(cfg, batches[1].cu_seqlens, batches[1].n_tokens)
+    assert abs(rec["mfu"] * eff.peak * (128 / rec["tokens_per_s_per_gpu"]) / flops - 1.0) < 1e-6
