@@ -155,16 +155,18 @@ def save_pipeline_stages(model, directory: str, stage_index: int, n_stages: int,
     guard = DeferredRankFailure()
     first_layer = model.layer_range[0]
     weight_map, total = {}, 0
+    live = dist.is_available() and dist.is_initialized()
     with guard.catch():
         if stage_index == 0:
-            remove_stale_staged(directory)
+            remove_stale_staged(directory)       # leftovers of an interrupted save, before any stage stages a new file
+    guard.raise_if_any(None if not live else (group or dist.group.WORLD), "preparing the checkpoint directory failed")
+    with guard.catch():
         writer = StreamingShardWriter(directory, max_shard_bytes, save_dtype, prefix=f"model-stage{stage_index:03d}")
         for name, p in model.named_parameters():
             for hub, t in runtime_to_hub(name, p.detach(), cfg, first_layer).items():
                 writer.add(hub, t)
         writer.finish(write_index=False)
         weight_map, total = writer.weight_map, writer.total_bytes
-    live = dist.is_available() and dist.is_initialized()
     guard.raise_if_any(None if not live else (group or dist.group.WORLD), "a pipeline stage failed to write its tensors")
     parts = [None] * n_stages
     if live and n_stages > 1:
