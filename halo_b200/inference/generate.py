@@ -5,7 +5,8 @@ Prefill packs all prompts into ONE varlen row and runs the training kernels unch
 packed documents, grouped expert GEMMs); each layer's rotated keys and values are scattered into a padded cache
 ``[layers, batch, max_len, kv_heads, head_dim]`` on the way. A decode step feeds one token per sequence: the
 projections, the router and the expert products are the same ops at ``T = batch``, and attention reads the cache -
-one query row against its sequence's cached keys, a memory-bound product evaluated with batched tensor ops.
+one query row against its sequence's cached keys - with the decode kernel of ``csrc/decode_attention.cu`` (all query
+heads of a key/value head in one CTA, the cache streamed once; batched tensor ops on CPU).
 Sampling (temperature, top-k, nucleus) runs on the device in fp32 with a generator seeded per call; the sampled
 token's log-probability under the *unmodified* distribution is returned for importance ratios.
 
@@ -86,6 +87,18 @@ class KVCache:
         B = q.shape[0]
         Hkv, D = self.k.shape[-2:]
         G = n_heads // Hkv
+        if q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128) and G <= 16:
+            # the decode kernel streams the cache once and reads the lengths on the device (no host synchronisation)
+            from halo_b200.ops import _lib
+
+            qc = q.contiguous()
+            out = torch.empty_like(qc)
+            rc = _lib.lib().halo_decode_attention(
+                _lib.ptr(qc), _lib.ptr(self.k[li]), _lib.ptr(self.v[li]), _lib.ptr(self._cols), _lib.ptr(out), _lib.c_int(B),
+                _lib.c_int(n_heads), _lib.c_int(Hkv), _lib.c_int(D), _lib.c_ll(self.k.shape[2]),
+                _lib.c_float(scale if scale is not None else D ** -0.5), _lib.stream_ptr(q.device))
+            _lib.check(rc, "halo_decode_attention")
+            return out
         upto = int(self._cols.max().item()) + 1
         k, v = self.k[li, :, :upto], self.v[li, :, :upto]                 # [B, S, Hkv, D]
         qh = q.reshape(B, Hkv, G, D).float()
