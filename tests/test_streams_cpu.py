@@ -84,3 +84,33 @@ def test_shape_guards():
         S.collapse_streams(torch.randn(3, 4, 8), torch.randn(3, 3))
     with pytest.raises(ValueError, match="built for 1..8"):
         S.collapse_streams(torch.randn(3, 9, 8), torch.randn(3, 9))
+
+
+def test_block_sparse_attention_matches_the_dense_mask():
+    from halo_b200.ops.block_sparse_attention import block_sparse_attention, dense_reference, key_positions
+
+    g = torch.Generator().manual_seed(0)
+    ratio, topk, Hq, Hkv, D = 4, 3, 4, 2, 16
+    docs = [23, 9, 2]
+    T = sum(docs)
+    first = torch.cat([torch.full((n,), s) for n, s in zip(docs, [0, 23, 32])])
+    visible = torch.cat([torch.arange(1, n + 1) for n in docs])
+    spans = torch.stack([first, visible], dim=1)
+    blocks = torch.zeros(T, topk, dtype=torch.int64)
+    for t in range(T):
+        complete = int(visible[t]) // ratio
+        if complete:
+            pick = torch.randperm(complete, generator=g)[:topk]
+            blocks[t, :len(pick)] = pick                     # distinct blocks; unused slots keep 0 and are masked by the count
+    pos, ok = key_positions(spans, blocks, ratio)
+    assert (pos[ok] < (first + visible)[:, None].expand_as(pos)[ok]).all()          # never a key from the future or another document
+    assert int(ok[0].sum()) == 1 and int(ok[22].sum()) == min(5, topk) * ratio + 3
+    q, k, v = (torch.randn(T, h, D, generator=g, requires_grad=True) for h in (Hq, Hkv, Hkv))
+    got = block_sparse_attention(q, k, v, spans, blocks, ratio, chunk_queries=7)
+    want = dense_reference(q, k, v, spans, blocks, ratio)
+    assert torch.allclose(got, want, atol=1e-5)
+    w = torch.randn(got.shape, generator=g)
+    ga = torch.autograd.grad((got * w).sum(), (q, k, v))
+    gb = torch.autograd.grad((want * w).sum(), (q, k, v))
+    for a, b in zip(ga, gb):
+        assert torch.allclose(a, b, atol=1e-5)
