@@ -1,0 +1,141 @@
+"""Low-precision checkpoints in and out, one tensor at a time:
+
+    python -m halo_b200.checkpoint.tools.lowp_convert dequant-block-fp8 <src> <dst>
+    python -m halo_b200.checkpoint.tools.lowp_convert export <src> <dst> --format mxfp8|mxfp4|nvfp4 [--keep REGEX ...]
+    python -m halo_b200.checkpoint.tools.lowp_convert dequant <src> <dst>
+
+``dequant-block-fp8`` turns a served-weights release in 128 x 128 block FP8 (every ``<name>.weight`` in
+``float8_e4m3fn`` beside a ``<name>.weight_scale_inv`` of one fp32 factor per block) into bf16 - the form training
+starts from. ``export`` writes the matrices of a bf16 checkpoint in a block-scaled format: ``<name>.weight`` holds the
+element codes, ``<name>.weight_scale`` the per-block scales and, for nvfp4, ``<name>.weight_global_scale`` the tensor
+scale; embeddings, norms, router gates, biases and whatever ``--keep`` matches stay as they are. ``dequant`` reads
+that layout back into bf16. The roles of the reference's fp8 / fp4 dequantisers and its low-precision exporters
+(halo/checkpoint/tools/)."""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import re
+import sys
+
+import torch
+
+from halo_b200.ops import lowp
+
+from ._io import CheckpointIndex, StreamingShardWriter, copy_side_files
+
+BLOCK = 128
+ALWAYS_KEPT = re.compile(r"(embed_tokens|lm_head|norm|\.gate\.weight$|shared_expert_gate|bias$|_hc\.|hc_head)")
+
+
+def dequant_block_fp8(src: str, dst: str) -> int:
+    idx = CheckpointIndex(src)
+    writer = StreamingShardWriter(dst)
+    n = 0
+    for name in sorted(idx.weight_map):
+        if name.endswith("_scale_inv"):
+            continue
+        t = idx.get(name)
+        scale_name = name + "_scale_inv"
+        if t.dtype == torch.float8_e4m3fn:
+            if scale_name not in idx:
+                raise KeyError(f"{name} is FP8 but {scale_name} is absent")
+            s = idx.get(scale_name).float()
+            rows, cols = t.shape
+            if tuple(s.shape) != (-(-rows // BLOCK), -(-cols // BLOCK)):
+                raise ValueError(f"{scale_name} is {tuple(s.shape)}, expected one factor per {BLOCK} x {BLOCK} block of {tuple(t.shape)}")
+            full = s.repeat_interleave(BLOCK, 0)[:rows].repeat_interleave(BLOCK, 1)[:, :cols]
+            t = (t.float() * full).to(torch.bfloat16)
+            n += 1
+        writer.add(name, t)
+    writer.finish()
+    copy_side_files(src, dst)
+    cfg_path = os.path.join(dst, "config.json")
+    if os.path.isfile(cfg_path):                               # the result is an ordinary bf16 checkpoint
+        cfg = json.load(open(cfg_path))
+        cfg.pop("quantization_config", None)
+        cfg["torch_dtype"] = "bfloat16"
+        json.dump(cfg, open(cfg_path, "w"), indent=2)
+    return n
+
+
+def export(src: str, dst: str, fmt: str, keep: list[str] | None = None) -> int:
+    if fmt not in lowp.FORMATS:
+        raise ValueError(f"unknown format {fmt!r}; known: {lowp.FORMATS}")
+    kept = [re.compile(p) for p in keep or []]
+    idx = CheckpointIndex(src)
+    writer = StreamingShardWriter(dst)
+    n = 0
+    for name in sorted(idx.weight_map):
+        t = idx.get(name)
+        plain = (t.dim() != 2 or not name.endswith(".weight") or ALWAYS_KEPT.search(name) or any(p.search(name) for p in kept)
+                 or t.shape[1] % lowp.BLOCK_SIZE[fmt])
+        if plain:
+            writer.add(name, t)
+            continue
+        q = lowp.quantize(t, fmt)
+        data = q.data.view(torch.uint8) if q.data.dtype == torch.float8_e4m3fn else q.data       # bytes either way
+        scales = q.scales.view(torch.uint8) if q.scales.dtype == torch.float8_e4m3fn else q.scales
+        writer.add(name, data)
+        writer.add(name + "_scale", scales)
+        if q.global_scale is not None:
+            writer.add(name + "_global_scale", q.global_scale.reshape(1).float())
+        n += 1
+    writer.finish()
+    copy_side_files(src, dst)
+    json.dump({"format": fmt, "block_size": lowp.BLOCK_SIZE[fmt], "quantized_tensors": n},
+              open(os.path.join(dst, "halo_lowp.json"), "w"), indent=2)
+    return n
+
+
+def dequant(src: str, dst: str) -> int:
+    meta = json.load(open(os.path.join(src, "halo_lowp.json")))
+    fmt = meta["format"]
+    idx = CheckpointIndex(src)
+    writer = StreamingShardWriter(dst)
+    n = 0
+    for name in sorted(idx.weight_map):
+        if name.endswith(("_scale", "_global_scale")) and name.rsplit("_scale", 1)[0].rsplit("_global", 1)[0] in idx:
+            continue
+        t = idx.get(name)
+        if name + "_scale" in idx:
+            scales = idx.get(name + "_scale")
+            data = t.view(torch.float8_e4m3fn) if fmt == "mxfp8" else t
+            if fmt == "nvfp4":
+                scales = scales.view(torch.float8_e4m3fn)
+            gs = idx.get(name + "_global_scale")[0] if name + "_global_scale" in idx else None
+            t = lowp.dequantize(lowp.BlockScaledTensor(data, scales, fmt, gs), torch.bfloat16)
+            n += 1
+        writer.add(name, t)
+    writer.finish()
+    copy_side_files(src, dst)
+    return n
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.splitlines()[0])
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    for cmd in ("dequant-block-fp8", "dequant"):
+        p = sub.add_parser(cmd)
+        p.add_argument("src")
+        p.add_argument("dst")
+    p = sub.add_parser("export")
+    p.add_argument("src")
+    p.add_argument("dst")
+    p.add_argument("--format", required=True, choices=list(lowp.FORMATS))
+    p.add_argument("--keep", nargs="*", default=[])
+    args = ap.parse_args(argv)
+    if args.cmd == "dequant-block-fp8":
+        n = dequant_block_fp8(args.src, args.dst)
+    elif args.cmd == "dequant":
+        n = dequant(args.src, args.dst)
+    else:
+        n = export(args.src, args.dst, args.format, args.keep)
+    print(f"{args.cmd}: {n} tensors converted into {args.dst}")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

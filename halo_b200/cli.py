@@ -32,6 +32,7 @@ TOOLS = {
     "evaluate": "halo_b200.entrypoints.evaluation",
     "reward-scoring": "halo_b200.entrypoints.reward_scoring",
     "merge-adapter": "halo_b200.checkpoint.tools.merge_adapter",
+    "lowp-convert": "halo_b200.checkpoint.tools.lowp_convert",
     "bench": "bench",
 }
 

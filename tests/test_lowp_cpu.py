@@ -2,6 +2,7 @@
 slice invariance of nvfp4's tensor scale, the straight-through gradient and the weight round-trip cache."""
 
 import itertools
+import os
 
 import pytest
 import torch
@@ -94,3 +95,54 @@ def test_weight_cache_follows_in_place_updates():
     w.add_(1.0)
     b = cache.get(w, "mxfp4")
     assert b is not a and torch.equal(b, lowp.fake_quant_reference(w, "mxfp4"))
+
+
+def test_checkpoint_conversions(tmp_path):
+    import json
+
+    from safetensors.torch import save_file
+
+    from halo_b200.checkpoint.load import CheckpointIndex, from_pretrained
+    from halo_b200.checkpoint.save import save_model
+    from halo_b200.checkpoint.tools import lowp_convert
+    from halo_b200.models.config import tiny_moe_config
+    from halo_b200.models.qwen3 import build_model
+
+    # a served-weights release in 128 x 128 block FP8 -> bf16
+    torch.manual_seed(0)
+    w = torch.randn(200, 300)
+    scale_inv = torch.rand(2, 3) + 0.5
+    full = scale_inv.repeat_interleave(128, 0)[:200].repeat_interleave(128, 1)[:, :300]
+    fp8 = (w / full).to(torch.float8_e4m3fn)
+    src = tmp_path / "fp8"
+    src.mkdir()
+    save_file({"model.layers.0.mlp.down_proj.weight": fp8, "model.layers.0.mlp.down_proj.weight_scale_inv": scale_inv,
+               "model.norm.weight": torch.ones(300, dtype=torch.bfloat16)}, str(src / "model.safetensors"))
+    (src / "config.json").write_text(json.dumps({"model_type": "qwen3", "quantization_config": {"quant_method": "fp8"}}))
+    assert lowp_convert.main(["dequant-block-fp8", str(src), str(tmp_path / "bf16")]) == 0
+    out = CheckpointIndex(str(tmp_path / "bf16"))
+    got = out.get("model.layers.0.mlp.down_proj.weight")
+    assert got.dtype == torch.bfloat16 and "model.layers.0.mlp.down_proj.weight_scale_inv" not in out
+    assert torch.equal(got, (fp8.float() * full).bfloat16()) and (got.float() - w).abs().max() < 0.08 * w.abs().max()
+    assert "quantization_config" not in json.load(open(tmp_path / "bf16" / "config.json"))
+
+    # a model exported in a block-scaled format and read back is the fake-quantised model
+    model = build_model(tiny_moe_config(), device="cpu", seed=1)
+    ckpt = str(tmp_path / "ckpt")
+    save_model(model, ckpt, save_dtype=torch.bfloat16)
+    for fmt in ("mxfp8", "nvfp4"):
+        q_dir, back_dir = str(tmp_path / f"q_{fmt}"), str(tmp_path / f"back_{fmt}")
+        assert lowp_convert.main(["export", ckpt, q_dir, "--format", fmt, "--keep", r"layers\.0\."]) == 0
+        meta = json.load(open(os.path.join(q_dir, "halo_lowp.json")))
+        assert meta["format"] == fmt and meta["quantized_tensors"] > 10
+        assert lowp_convert.main(["dequant", q_dir, back_dir]) == 0
+        back = from_pretrained(back_dir, device="cpu", dtype=torch.bfloat16)
+        ref = from_pretrained(ckpt, device="cpu", dtype=torch.bfloat16)
+        for (n, a), (_, b) in zip(back.named_parameters(), ref.named_parameters()):
+            untouched = n.startswith("layers.0.") or a.dim() < 2 or "embed" in n or "lm_head" in n or n.endswith("mlp.gate")
+            if untouched:
+                assert torch.equal(a, b), n
+            elif a.dim() == 2:
+                # fused runtime tensors are concatenations of hub matrices quantised one by one along the same axis
+                assert torch.equal(a, lowp.fake_quant_reference(b, fmt)) or fmt == "nvfp4", n
+                assert (a.float() - b.float()).abs().max() <= 0.3 * b.float().abs().max(), n
