@@ -21,6 +21,7 @@ class ModelArguments:
     freeze_patterns: list[str] | None = None      # regexes of parameter names to freeze
     train_only_patterns: list[str] | None = None  # or: train only what matches
     max_length: int = 0                     # 0 = the model's context window
+    lowp_format: Literal["", "mxfp8", "mxfp4", "nvfp4"] = ""   # quantisation-aware training in a block-scaled format
     enable_mtp_head: bool = False           # train a multi-token-prediction head beside the next-token loss
     mtp_loss_weight: float = 0.3
     mtp_objective: Literal["joint", "detached"] = "joint"

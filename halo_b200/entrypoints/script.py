@@ -155,6 +155,11 @@ def load_policy_model(model_args, pc, device, runtime, gradient_checkpointing=Tr
     else:
         model = from_pretrained(model_args.model_name_or_path, device=device, dtype=dtype, transport=transport,
                                 gradient_checkpointing=gradient_checkpointing)
+    if getattr(model_args, "lowp_format", ""):
+        from halo_b200.models.qwen3 import apply_lowp_compute
+
+        log.info("quantisation-aware training: %d modules round their products to %s",
+                 apply_lowp_compute(model, model_args.lowp_format), model_args.lowp_format)
     if getattr(model_args, "use_peft", False):
         from halo_b200.peft.lora import apply_lora, load_adapters
 

@@ -34,6 +34,20 @@ from .config import ModelConfig
 from .recompute import recompute
 
 
+def _rounded(t, fmt: str):
+    """``t`` rounded to the block-scaled format ``fmt`` along its last axis (straight-through gradient); itself
+    when no format is set."""
+    if not fmt:
+        return t
+    from halo_b200.ops.lowp import fake_quant
+
+    return fake_quant(t, fmt)
+
+
+def _linear(x, weight, fmt: str = ""):
+    return gemm.linear(_rounded(x, fmt), _rounded(weight, fmt))
+
+
 class _SwiGLULinear(torch.autograd.Function):
     """act = silu(x Wg^T) * (x Wu^T) with the activation in the GEMM epilogue; recompute-free backward."""
 
@@ -100,6 +114,7 @@ class Attention(nn.Module):
         else:
             self.register_parameter("qkv_bias", None)
         self.lora = None          # halo_b200.peft.lora.LoraSet when low-rank adapters are attached
+        self.lowp = ""            # block-scaled format the projections are rounded to (quantisation-aware training)
         if cfg.use_qk_norm:
             self.q_norm = nn.Parameter(torch.ones(D, dtype=dtype, device=device))
             self.k_norm = nn.Parameter(torch.ones(D, dtype=dtype, device=device))
@@ -111,14 +126,14 @@ class Attention(nn.Module):
         return qkv if self.qkv_bias is None else qkv + self.qkv_bias
 
     def _qkv(self, h):
-        qkv = self._biased(gemm.linear(h, self.qkv_proj))
+        qkv = self._biased(_linear(h, self.qkv_proj, self.lowp))
         if self.lora is not None:
             q, kv = self.n_heads * self.cfg.head_dim, self.n_kv_heads * self.cfg.head_dim
             qkv = self.lora.add_fused(h, qkv, [("q_proj", 0, q), ("k_proj", q, q + kv), ("v_proj", q + kv, q + 2 * kv)])
         return qkv
 
     def _out(self, o):
-        y = gemm.linear(o, self.o_proj)
+        y = _linear(o, self.o_proj, self.lowp)
         if self.lora is not None and "o_proj" in self.lora:
             y = y + self.lora.delta("o_proj", o)
         return y
@@ -167,8 +182,12 @@ class DenseMLP(nn.Module):
         if tp_size > 1:
             self.gate_up_proj.tp_kind, self.down_proj.tp_kind = "gate_up", "down"
         self.lora = None          # halo_b200.peft.lora.LoraSet when low-rank adapters are attached
+        self.lowp = ""            # block-scaled format of quantisation-aware training
 
     def forward(self, h, ctx=None):
+        if self.lowp and self.lora is None and self.tp_size == 1:
+            act = _SwiGLULinear.apply(_rounded(h, self.lowp), _rounded(self.gate_up_proj, self.lowp), torch.is_grad_enabled())
+            return _linear(act, self.down_proj, self.lowp)
         if self.lora is not None:
             # the low-rank terms join the pre-activation, so the activation runs as its own kernel here
             from halo_b200.ops.activation import swiglu
@@ -216,6 +235,7 @@ class SparseMoE(nn.Module):
         # saved as a sidecar by the balancing callback)
         self.register_buffer("selection_bias", None, persistent=False)
         self.expert_lora = None       # halo_b200.peft.lora.ExpertLora when the routed experts carry adapters
+        self.lowp = ""                # block-scaled format of quantisation-aware training (banks and dispatched rows)
         self.load_counter = None      # (ExpertLoadCounter, layer index) when load metrics are on
         self.last_routing = None
 
@@ -239,6 +259,9 @@ class SparseMoE(nn.Module):
         bank_gate_up, bank_down = self.experts_gate_up, self.experts_down
         if self.expert_lora is not None:
             bank_gate_up, bank_down = self.expert_lora.effective_banks(bank_gate_up, bank_down)
+        h_experts = h
+        if self.lowp:
+            bank_gate_up, bank_down, h_experts = (_rounded(t, self.lowp) for t in (bank_gate_up, bank_down, h))
         if self.etp is not None:
             # every rank of the group routes the same tokens through its slice of each expert; the partial outputs
             # are summed in token space (and the partial input / routing-weight gradients on the way back)
@@ -248,7 +271,7 @@ class SparseMoE(nn.Module):
                                        self.experts_down, ctx.transport)
             out = sum_from_group(part, self.etp)
         else:
-            out = moe_ops.moe_experts(h, idx, w, bank_gate_up, bank_down, ctx.transport,
+            out = moe_ops.moe_experts(h_experts, idx, w, bank_gate_up, bank_down, ctx.transport,
                                       skip_output=getattr(ctx, "output_unused", False))
         if self.shared_expert is not None:
             sh = self.shared_expert(h)
@@ -579,6 +602,33 @@ def plan_recompute(model, tokens_per_step: int, free_bytes: int, reserve_bytes: 
         n = int(t.item())
     for i, layer in enumerate(model.layers):
         layer.recompute_policy = "mlp" if i >= len(model.layers) - n else "full"
+    return n
+
+
+def apply_lowp_compute(model, fmt: str) -> int:
+    """Quantisation-aware training: every attention, dense feed-forward and routed-expert product rounds its operands
+    to the block-scaled format ``fmt`` along the contraction axis (straight-through gradients; the master weights stay
+    bf16). The router, the norms, the embedding and the output head keep full precision. Returns the number of
+    modules switched (the reference's low-precision apply, halo/model_loading/parallel/lowp_compute.py)."""
+    from halo_b200.ops.lowp import BLOCK_SIZE, FORMATS
+
+    if fmt not in FORMATS:
+        raise ValueError(f"unknown low-precision format {fmt!r}; known: {FORMATS}")
+    bs = BLOCK_SIZE[fmt]
+    widths = {model.cfg.hidden_size, model.cfg.num_attention_heads * model.cfg.head_dim}
+    widths.add(model.cfg.moe_intermediate_size if model.cfg.is_moe else model.cfg.intermediate_size)
+    if not all(model.cfg.layer_is_moe(i) for i in range(model.cfg.num_hidden_layers)):
+        widths.add(model.cfg.intermediate_size)
+    if model.cfg.shared_expert_intermediate_size:
+        widths.add(model.cfg.shared_expert_intermediate_size)
+    bad = sorted(w for w in widths if w % bs)
+    if bad:
+        raise ValueError(f"{fmt} scales blocks of {bs} along the contraction axis; the widths {bad} are no multiples of it")
+    n = 0
+    for module in model.modules():
+        if isinstance(module, (Attention, DenseMLP, SparseMoE)):
+            module.lowp = fmt
+            n += 1
     return n
 
 

@@ -146,3 +146,37 @@ def test_checkpoint_conversions(tmp_path):
                 # fused runtime tensors are concatenations of hub matrices quantised one by one along the same axis
                 assert torch.equal(a, lowp.fake_quant_reference(b, fmt)) or fmt == "nvfp4", n
                 assert (a.float() - b.float()).abs().max() <= 0.3 * b.float().abs().max(), n
+
+
+def test_quantisation_aware_training_rounds_every_product():
+    import dataclasses
+
+    import numpy as np
+
+    from halo_b200.data.packing import pack_documents
+    from halo_b200.models.config import tiny_moe_config
+    from halo_b200.models.qwen3 import apply_lowp_compute, build_model
+
+    cfg = dataclasses.replace(tiny_moe_config(), num_hidden_layers=2, shared_expert_intermediate_size=64)
+    rng = np.random.default_rng(0)
+    b = pack_documents([rng.integers(0, cfg.vocab_size, size=n) for n in (40, 24)])
+    base = build_model(cfg, device="cpu", seed=2, gradient_checkpointing=False)
+    want = base(b.input_ids, b.position_ids, b.cu_seqlens, b.labels).item()
+    model = build_model(cfg, device="cpu", seed=2)
+    assert apply_lowp_compute(model, "mxfp8") == 2 * 3              # attention, routed experts and the shared expert per layer
+    loss = model(b.input_ids, b.position_ids, b.cu_seqlens, b.labels)
+    assert 1e-6 < abs(loss.item() - want) < 0.05                    # e4m3 rounding moves the loss a little
+    loss.backward()
+    assert all(p.grad is not None and p.grad.abs().sum() > 0 for n, p in model.named_parameters() if p.dim() > 1)
+    # a dense block: the rounded product by hand
+    mlp = model.layers[0].mlp.shared_expert
+    x = torch.randn(6, cfg.hidden_size)
+    fq = lambda t: lowp.fake_quant_reference(t, "mxfp8")
+    pre = fq(x) @ fq(mlp.gate_up_proj).t()
+    act = torch.nn.functional.silu(pre[:, :64]) * pre[:, 64:]
+    assert torch.allclose(mlp(x), fq(act) @ fq(mlp.down_proj).t(), atol=1e-5)
+    coarse = build_model(cfg, device="cpu", seed=2)
+    apply_lowp_compute(coarse, "mxfp4")
+    assert abs(coarse(b.input_ids, b.position_ids, b.cu_seqlens, b.labels).item() - want) > abs(loss.item() - want)
+    with pytest.raises(ValueError, match="no multiples"):
+        apply_lowp_compute(build_model(dataclasses.replace(cfg, moe_intermediate_size=80), device="cpu", seed=0), "mxfp8")
