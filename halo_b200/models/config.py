@@ -49,6 +49,7 @@ class ModelConfig:
     rms_norm_eps: float = 1e-6
     use_qk_norm: bool = True
     attention_bias: bool = False           # bias on the q / k / v projections (Qwen2)
+    sliding_window: int = 0                # > 0: every query sees only its last ``sliding_window`` keys (Mistral-style)
     rope_scaling: dict | None = None       # Hugging Face ``rope_scaling`` / ``rope_parameters`` entry, None = plain
     num_nextn_predict_layers: int = 0      # 1 = a multi-token-prediction head trained beside the next-token loss
     mtp_loss_weight: float = 0.3
@@ -151,7 +152,10 @@ class ModelConfig:
         elif self.family == "qwen2_moe":
             d["qkv_bias"] = self.attention_bias
         if fam["has_window"]:
-            d["sliding_window"] = None
+            d["sliding_window"] = self.sliding_window or None
+            if self.family.startswith("qwen2"):
+                d["use_sliding_window"] = bool(self.sliding_window)
+                d["max_window_layers"] = 0 if self.sliding_window else self.num_hidden_layers
         if self.family == "mixtral":
             d.update({"num_local_experts": self.num_experts, "num_experts_per_tok": self.num_experts_per_tok,
                       "router_aux_loss_coef": self.router_aux_loss_coef, "output_router_logits": False,
@@ -184,10 +188,12 @@ class ModelConfig:
         if mt not in FAMILIES:
             raise ValueError(f"model_type {mt!r} has no family registered here (known: {sorted(FAMILIES)})")
         fam = FAMILIES[mt]
-        window = d.get("sliding_window")
-        if fam["has_window"] and window and d.get("use_sliding_window", True) and window < d.get("max_position_embeddings", 0):
-            raise ValueError(f"{mt} checkpoint with sliding_window={window}: windowed attention is not built; "
-                             f"only full causal attention over each document")
+        window = d.get("sliding_window") or 0
+        if not (fam["has_window"] and window and d.get("use_sliding_window", True) and window < d.get("max_position_embeddings", 0)):
+            window = 0
+        if window and d.get("max_window_layers", 0) not in (0, None):
+            raise ValueError(f"{mt} checkpoint that windows only the layers from {d['max_window_layers']} on: a per-layer mix of "
+                             f"full and windowed attention is not built")
         rp = d.get("rope_parameters") or {}
         rope_theta = d.get("rope_theta") or rp.get("rope_theta", 1e6 if mt.startswith("qwen") else 1e4)
         scaling = d.get("rope_scaling") or ({k: v for k, v in rp.items() if k != "rope_theta"} if rp else None)
@@ -214,6 +220,7 @@ class ModelConfig:
             shared_expert_gate=(mt == "qwen2_moe"),
             mlp_only_layers=list(d.get("mlp_only_layers", []) or []), decoder_sparse_step=d.get("decoder_sparse_step", 1),
             rope_theta=float(rope_theta), rms_norm_eps=d.get("rms_norm_eps", 1e-6), use_qk_norm=fam["qk_norm"],
+            sliding_window=int(window),
             attention_bias=(bool(d.get("attention_bias", False)) if fam["bias_key"]
                             else bool(d.get("qkv_bias", fam["bias_default"]))),
             num_nextn_predict_layers=int(d.get("num_nextn_predict_layers", 0) or 0),

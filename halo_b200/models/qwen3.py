@@ -125,6 +125,24 @@ class Attention(nn.Module):
     def _biased(self, qkv):
         return qkv if self.qkv_bias is None else qkv + self.qkv_bias
 
+    def _windowed(self, qkv, ctx):
+        """Windowed attention through the masked-attention op (tiles of queries under a ``[T, T]`` mask: the flash
+        kernel has no window; meant for rows of a few thousand tokens)."""
+        from halo_b200.ops.masked_attention import masked_attention, window_mask
+        from halo_b200.ops.rope import qk_norm_rope
+
+        cfg = self.cfg
+        if ctx.cp is not None or ctx.tp is not None or ctx.kv_cache is not None:
+            raise NotImplementedError("windowed attention is built for unsliced rows outside generation")
+        Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        q, k = qk_norm_rope(qkv, self.q_norm, self.k_norm, ctx.rope, Hq, Hkv, cfg.rms_norm_eps, cfg.use_qk_norm)
+        v = qkv[:, (Hq + Hkv) * D:]
+        if getattr(ctx, "window", None) is None:
+            ctx.window = window_mask(ctx.plan.cu_seqlens, cfg.sliding_window, device=qkv.device)     # shared by the layers
+        T = qkv.shape[0]
+        o = masked_attention(q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D), ctx.window)
+        return o.reshape(T, Hq * D)
+
     def _qkv(self, h):
         qkv = self._biased(_linear(h, self.qkv_proj, self.lowp))
         if self.lora is not None:
@@ -140,7 +158,7 @@ class Attention(nn.Module):
 
     def forward(self, h, ctx):
         cfg = self.cfg
-        if ctx.kv_cache is not None:
+        if ctx.kv_cache is not None and not cfg.sliding_window:
             # generation: keys / values go to the cache, a decode step attends the cache
             from halo_b200.inference.generate import cached_attention
 
@@ -154,6 +172,8 @@ class Attention(nn.Module):
                                         cfg.rms_norm_eps, cfg.use_qk_norm)
             return row_parallel_linear(o, self.o_proj, ctx.tp)
         qkv = self._qkv(h)
+        if cfg.sliding_window:
+            return self._out(self._windowed(qkv, ctx))
         if ctx.cp is not None:
             # context parallel: this rank holds one chunk of the row; keys and values of straddling documents
             # come from the lower ranks

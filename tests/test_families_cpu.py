@@ -1,6 +1,6 @@
 """Decoder families beyond Qwen3: a model of each family, saved in hub layout, loads in ``transformers`` (which
 converts the hub names itself) and gives our logits; a checkpoint written by ``transformers`` loads here; rotary
-scaling follows the Hugging Face frequencies; windowed checkpoints are refused by name."""
+scaling follows the Hugging Face frequencies; windowed attention (Mistral-style) follows the Hugging Face mask."""
 
 import numpy as np
 import pytest
@@ -39,7 +39,7 @@ def logits_of(model, ids):
         return model.hidden_states(b.input_ids, b.position_ids, b.cu_seqlens) @ model.head_weight().t(), b
 
 
-CASES = [("llama", {}), ("llama", {"rope_scaling": LLAMA3}), ("llama", {"attention_bias": True}), ("mistral", {}),
+CASES = [("mistral", {"sliding_window": 16}), ("qwen2", {"sliding_window": 24}), ("llama", {}), ("llama", {"rope_scaling": LLAMA3}), ("llama", {"attention_bias": True}), ("mistral", {}),
          ("qwen2", {}), ("qwen2", {"rope_scaling": YARN}), ("mixtral", {}), ("qwen2_moe", {})]
 
 
@@ -85,10 +85,15 @@ def test_scaled_frequencies_match_transformers(scaling):
     assert abs(factor - want_factor) < 1e-6
 
 
-def test_windowed_checkpoint_is_refused_by_name():
+def test_window_and_family_gates():
     d = family_config("mistral").to_hf_dict()
     d["sliding_window"] = 64
-    with pytest.raises(ValueError, match="sliding_window=64"):
-        ModelConfig.from_hf_dict(d)
+    assert ModelConfig.from_hf_dict(d).sliding_window == 64
+    d["sliding_window"] = 4096                      # as wide as the context: plain causal attention
+    assert ModelConfig.from_hf_dict(d).sliding_window == 0
+    q = family_config("qwen2", sliding_window=16).to_hf_dict()
+    q["max_window_layers"] = 1
+    with pytest.raises(ValueError, match="per-layer mix"):
+        ModelConfig.from_hf_dict(q)
     with pytest.raises(ValueError, match="no family registered"):
         ModelConfig.from_hf_dict({**d, "model_type": "mamba"})

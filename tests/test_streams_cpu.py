@@ -114,3 +114,30 @@ def test_block_sparse_attention_matches_the_dense_mask():
     gb = torch.autograd.grad((want * w).sum(), (q, k, v))
     for a, b in zip(ga, gb):
         assert torch.allclose(a, b, atol=1e-5)
+
+
+@pytest.mark.parametrize("kind", ["random", "tree", "window"])
+def test_masked_attention_closed_form_backward(kind):
+    from halo_b200.ops.masked_attention import masked_attention, masked_attention_reference, tree_mask, window_mask
+
+    g = torch.Generator().manual_seed(3)
+    Q, Hq, Hkv, D = 37, 4, 2, 16
+    if kind == "random":
+        allowed = torch.rand(Q, Q, generator=g) > 0.5
+        allowed[5] = False                                                  # a query that sees nothing
+    elif kind == "tree":
+        # a 10-token prompt with three completions branching off its end
+        parent = torch.tensor(list(range(-1, 9)) + [9] + list(range(10, 18)) + [9] + list(range(19, 27)) + [9] + list(range(28, 36)))
+        allowed = tree_mask(parent)
+        assert allowed[36, :10].all() and not allowed[36, 10:28].any() and allowed[36, 28:].all()
+    else:
+        allowed = window_mask([0, 20, 37], 6)
+        assert allowed[25, 20:26].all() and not allowed[25, :20].any() and int(allowed[19].sum()) == 6
+    q = torch.randn(Q, Hq, D, generator=g, requires_grad=True)
+    k, v = (torch.randn(Q, Hkv, D, generator=g, requires_grad=True) for _ in range(2))
+    got = masked_attention(q, k, v, allowed, scores_per_tile=Hq * Q * 8)     # several query tiles
+    want = masked_attention_reference(q, k, v, allowed)
+    assert torch.allclose(got, want, atol=1e-5)
+    w = torch.randn(got.shape, generator=g)
+    for a, b in zip(torch.autograd.grad((got * w).sum(), (q, k, v)), torch.autograd.grad((want * w).sum(), (q, k, v))):
+        assert torch.allclose(a, b, atol=1e-5)
