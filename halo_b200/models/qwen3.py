@@ -125,9 +125,10 @@ class Attention(nn.Module):
     def _biased(self, qkv):
         return qkv if self.qkv_bias is None else qkv + self.qkv_bias
 
-    def _windowed(self, qkv, ctx):
-        """Windowed attention through the masked-attention op (tiles of queries under a ``[T, T]`` mask: the flash
-        kernel has no window; meant for rows of a few thousand tokens)."""
+    def _masked(self, qkv, ctx):
+        """Attention under an explicit ``[T, T]`` mask through the masked-attention op: the context's own mask (tree
+        packing: completions that share a stored-once prompt) or the sliding window of the configuration. The flash
+        kernel serves neither; meant for rows of a few thousand tokens."""
         from halo_b200.ops.masked_attention import masked_attention, window_mask
         from halo_b200.ops.rope import qk_norm_rope
 
@@ -137,10 +138,17 @@ class Attention(nn.Module):
         Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         q, k = qk_norm_rope(qkv, self.q_norm, self.k_norm, ctx.rope, Hq, Hkv, cfg.rms_norm_eps, cfg.use_qk_norm)
         v = qkv[:, (Hq + Hkv) * D:]
-        if getattr(ctx, "window", None) is None:
-            ctx.window = window_mask(ctx.plan.cu_seqlens, cfg.sliding_window, device=qkv.device)     # shared by the layers
+        mask = getattr(ctx, "attention_mask", None)
+        if cfg.sliding_window:
+            if getattr(ctx, "window", None) is None:
+                ctx.window = window_mask(ctx.plan.cu_seqlens, cfg.sliding_window, device=qkv.device)     # shared by the layers
+                if mask is not None:
+                    ctx.window = ctx.window & mask.to(qkv.device)
+            mask = ctx.window
+        elif mask.device != qkv.device:
+            mask = ctx.attention_mask = mask.to(qkv.device)
         T = qkv.shape[0]
-        o = masked_attention(q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D), ctx.window)
+        o = masked_attention(q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D), mask)
         return o.reshape(T, Hq * D)
 
     def _qkv(self, h):
@@ -172,8 +180,8 @@ class Attention(nn.Module):
                                         cfg.rms_norm_eps, cfg.use_qk_norm)
             return row_parallel_linear(o, self.o_proj, ctx.tp)
         qkv = self._qkv(h)
-        if cfg.sliding_window:
-            return self._out(self._windowed(qkv, ctx))
+        if cfg.sliding_window or getattr(ctx, "attention_mask", None) is not None:
+            return self._out(self._masked(qkv, ctx))
         if ctx.cp is not None:
             # context parallel: this rank holds one chunk of the row; keys and values of straddling documents
             # come from the lower ranks
@@ -389,6 +397,7 @@ class ForwardContext:
         self.replay_topk = replay_topk
         self.output_unused = False   # set while a layer is re-run only to rebuild its graph
         self.kv_cache = None         # halo_b200.inference.generate.KVCache while sampling
+        self.attention_mask = None   # bool [T, T]: an explicit mask (tree packing) served by the masked-attention op
 
 
 class Qwen3Model(nn.Module):

@@ -41,12 +41,13 @@ class GRPOBatch(PackedBatch):
     has_old: bool = False
     degenerate: torch.Tensor = None       # [T] bool: token belongs to a zero-spread group
     seq_lengths: torch.Tensor = None      # [n_rows] completion lengths
+    attention_mask: torch.Tensor = None   # [T, T] bool under tree packing (prompts stored once per group)
 
     def to(self, device, non_blocking: bool = True):
         b = PackedBatch.to(self, device, non_blocking)
         mv = lambda t: None if t is None else t.to(device, non_blocking=non_blocking)  # noqa: E731
         return GRPOBatch(b.input_ids, b.position_ids, b.labels, b.cu_seqlens, b.n_scored, mv(self.advantages),
-                         mv(self.old_logprobs), self.has_old, mv(self.degenerate), mv(self.seq_lengths))
+                         mv(self.old_logprobs), self.has_old, mv(self.degenerate), mv(self.seq_lengths), mv(self.attention_mask))
 
 
 def build_grpo_batch(rollouts: list[Rollout], adv: torch.Tensor, degenerate: torch.Tensor) -> GRPOBatch:
@@ -71,6 +72,40 @@ def build_grpo_batch(rollouts: list[Rollout], adv: torch.Tensor, degenerate: tor
             old[s + p - 1:s + p - 1 + len(r.completion_ids)] = torch.from_numpy(np.asarray(r.sampler_logprobs, np.float32))
     return GRPOBatch(base.input_ids, base.position_ids, base.labels, base.cu_seqlens, base.n_scored, a, old, has_old,
                      deg, torch.tensor([len(r.completion_ids) for r in rollouts], dtype=torch.float32))
+
+
+def build_grpo_tree_batch(rollouts: list[Rollout], adv: torch.Tensor, degenerate: torch.Tensor, group_size: int) -> GRPOBatch:
+    """The same round with every prompt stored once: the ``group_size`` completions of a prompt are branches of one tree
+    (:mod:`halo_b200.data.tree_layout`). ``rollouts`` hold the generations of a prompt contiguously."""
+    from halo_b200.data.tree_layout import pack_trees
+
+    if len(rollouts) % group_size:
+        raise ValueError(f"{len(rollouts)} rollouts do not split into groups of {group_size}")
+    groups, masks = [], []
+    for g0 in range(0, len(rollouts), group_size):
+        members = rollouts[g0:g0 + group_size]
+        if any(not np.array_equal(m.prompt_ids, members[0].prompt_ids) for m in members):
+            raise ValueError("tree packing needs the generations of a prompt to sit together")
+        groups.append((members[0].prompt_ids, [m.completion_ids for m in members]))
+        masks.append([np.ones(len(m.completion_ids), bool) if m.completion_mask is None else np.asarray(m.completion_mask, bool)
+                      for m in members])
+    tree = pack_trees(groups, masks)
+    T = tree.input_ids.numel()
+    a, old, deg = torch.zeros(T), torch.zeros(T), torch.zeros(T, dtype=torch.bool)
+    has_old = all(r.sampler_logprobs is not None for r in rollouts)
+    i = 0
+    for own in tree.branch_slices:
+        for start, stop in own:
+            r = rollouts[i]
+            lo, hi = start - 1, stop - 1                  # the labels that score this branch's completion tokens
+            a[lo:hi] = float(adv[i])
+            deg[lo:hi] = bool(degenerate[i])
+            if has_old:
+                old[lo:hi] = torch.from_numpy(np.asarray(r.sampler_logprobs, np.float32))
+            i += 1
+    n_scored = int((tree.labels != -100).sum())
+    return GRPOBatch(tree.input_ids, tree.position_ids, tree.labels, tree.cu_seqlens, n_scored, a, old, has_old, deg,
+                     torch.tensor([len(r.completion_ids) for r in rollouts], dtype=torch.float32), tree.allowed)
 
 
 class GRPOTrainer(Trainer):
@@ -104,10 +139,20 @@ class GRPOTrainer(Trainer):
                 raise RuntimeError(f"{self.zero_gradient_rounds} rounds in a row carried no learning signal")
         else:
             self.zero_gradient_rounds = 0
-        lengths = [len(r.prompt_ids) + len(r.completion_ids) for r in rollouts]
-        bins = microbatch.plan_microbatches(lengths, g.token_budget, self._world_max if self.parallel else None)
         self._round_tokens = float(sum(len(r.completion_ids) for r in rollouts))
         out = []
+        if getattr(g, "tree_packing", False):
+            G = g.num_generations
+            group_len = [len(rollouts[i].prompt_ids) - 1 + sum(1 + len(r.completion_ids) for r in rollouts[i:i + G])
+                         for i in range(0, len(rollouts), G)]
+            for b in microbatch.plan_microbatches(group_len, g.token_budget, self._world_max if self.parallel else None):
+                if not b:
+                    continue
+                idx = [i for gi in sorted(b) for i in range(gi * G, (gi + 1) * G)]
+                out.append(build_grpo_tree_batch([rollouts[i] for i in idx], adv[idx], degenerate[idx], G))
+            return out
+        lengths = [len(r.prompt_ids) + len(r.completion_ids) for r in rollouts]
+        bins = microbatch.plan_microbatches(lengths, g.token_budget, self._world_max if self.parallel else None)
         for b in bins:
             if not b:
                 continue
@@ -128,7 +173,11 @@ class GRPOTrainer(Trainer):
     # ---- objective -----------------------------------------------------------------------------
     def compute_loss(self, model, batch: GRPOBatch, normalizer):
         g = self.grpo
-        logp, _ = model.token_logprobs(batch.input_ids, batch.position_ids, batch.cu_seqlens, batch.labels)
+        ctx = None
+        if batch.attention_mask is not None:
+            ctx = model.make_context(batch.position_ids.reshape(-1), batch.cu_seqlens)
+            ctx.attention_mask = batch.attention_mask
+        logp, _ = model.token_logprobs(batch.input_ids, batch.position_ids, batch.cu_seqlens, batch.labels, ctx=ctx)
         mask = batch.labels.reshape(-1) != -100
         # on-policy single iteration: the old log-probs are this forward's own (detached) values
         old = batch.old_logprobs if (batch.has_old and g.num_iterations > 1) else logp.detach()

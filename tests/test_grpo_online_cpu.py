@@ -2,6 +2,7 @@
 training raises the mean reward; the sampler's log-probabilities line up with the trainer's."""
 
 import numpy as np
+import pytest
 import torch
 
 from halo_b200.configs.arguments import GRPOArguments, TrainingArguments
@@ -32,7 +33,8 @@ def test_sampler_logprobs_are_the_trainers(tmp_path):
     assert torch.allclose(logp[scored], batch.old_logprobs[scored], atol=1e-4)
 
 
-def test_on_policy_grpo_raises_the_reward(tmp_path):
+@pytest.mark.parametrize("tree", [False, True])
+def test_on_policy_grpo_raises_the_reward(tmp_path, tree):
     torch.manual_seed(0)
     model = build_model(tiny(), device="cpu", seed=0, gradient_checkpointing=False)
     rng = np.random.default_rng(0)
@@ -41,8 +43,8 @@ def test_on_policy_grpo_raises_the_reward(tmp_path):
                                 sampling=SamplingParams(max_new_tokens=8), prompts_per_round=4, seed=3, rounds=40)
     args = TrainingArguments(output_dir=str(tmp_path / "run"), max_steps=40, learning_rate=2e-2, optim="adamw_torch",
                              lr_scheduler_type="constant", weight_decay=0.0, logging_steps=1000, gradient_checkpointing=False)
-    trainer = GRPOTrainer(model, args, src, grpo_args=GRPOArguments(num_generations=8, max_completion_length=8, token_budget=4096),
-                          device=torch.device("cpu"))
+    trainer = GRPOTrainer(model, args, src, device=torch.device("cpu"),
+                          grpo_args=GRPOArguments(num_generations=8, max_completion_length=8, token_budget=4096, tree_packing=tree))
     rewards = []
     trainer.callbacks.append(type("Track", (), {"on_step_end": lambda self, t, logs=None: rewards.append(src.mean_reward),
                                                 "__getattr__": lambda self, name: (lambda *a, **k: None)})())
@@ -106,3 +108,42 @@ def test_trust_region_breaker_skips_the_update(tmp_path):
 
     assert run(0.5) == 0.0
     assert run(1.0) > 0.0
+
+
+def test_tree_packing_gives_the_flat_loss_and_gradients(tmp_path):
+    """The same round, flat (every completion carries its prompt) and tree-packed (each prompt stored once): the
+    objective, its gradients and the per-token log-probabilities agree; the tree row is shorter."""
+    from halo_b200.trainers.grpo import advantages as adv_mod
+    from halo_b200.trainers.grpo.trainer import Rollout, build_grpo_tree_batch
+
+    rng = np.random.default_rng(5)
+    G, rollouts = 3, []
+    for plen in (9, 5):
+        prompt = rng.integers(0, 32, size=plen)
+        for _ in range(G):
+            n = int(rng.integers(3, 8))
+            mask = np.ones(n, dtype=np.int64)
+            mask[rng.integers(0, n)] = 0                                       # an environment token inside the completion
+            rollouts.append(Rollout(prompt, rng.integers(0, 32, size=n), -rng.random(n).astype(np.float32), float(rng.normal()), mask))
+    rewards = torch.tensor([r.reward for r in rollouts])
+    adv, deg = adv_mod.group_advantages(rewards, G, "group", 0.0)
+    flat = build_grpo_batch(rollouts, adv, deg)
+    tree = build_grpo_tree_batch(rollouts, adv, deg, G)
+    assert tree.input_ids.numel() == flat.input_ids.numel() - (G - 1) * (8 + 4)
+    assert int((tree.labels != -100).sum()) == int((flat.labels != -100).sum())
+
+    def run(batch):
+        model = build_model(tiny(), device="cpu", seed=0, gradient_checkpointing=False)
+        args = TrainingArguments(output_dir=str(tmp_path / "x"), max_steps=1, optim="adamw_torch", logging_steps=1000)
+        trainer = GRPOTrainer(model, args, lambda i: None, device=torch.device("cpu"),
+                              grpo_args=GRPOArguments(num_generations=G, max_completion_length=8, num_iterations=2))
+        trainer._round_tokens = 1.0
+        loss = trainer.compute_loss(model, batch, None)
+        loss.backward()
+        return loss.item(), {n: p.grad.clone() for n, p in model.named_parameters()}
+
+    loss_flat, g_flat = run(flat)
+    loss_tree, g_tree = run(tree)
+    assert abs(loss_flat - loss_tree) < 1e-5 and abs(loss_flat) > 1e-3
+    for n in g_flat:
+        assert torch.allclose(g_flat[n], g_tree[n], atol=1e-5, rtol=1e-3), n
