@@ -21,7 +21,10 @@ MOE_HUB_NAMES = {
     "qwen3_moe": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "qwen2_moe": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "mixtral": ("block_sparse_moe", "w1", "w3", "w2"),
+    "glm4_moe": ("mlp", "gate_proj", "up_proj", "down_proj"),
 }
+# how a family names its always-on shared feed-forward block
+SHARED_EXPERT_NAMES = {"glm4_moe": "shared_experts"}
 
 
 def runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, expert_offset: int = 0) -> dict:
@@ -81,11 +84,14 @@ def runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, e
         return out
     if rest == "mlp.experts_down":
         return {pre + f"{block}.experts.{le + expert_offset}.{down_name}.weight": tensor[le] for le in range(tensor.shape[0])}
+    shared = SHARED_EXPERT_NAMES.get(getattr(cfg, "family", ""), "shared_expert")
     if rest == "mlp.shared_expert.gate_up_proj":
         g, u = tensor.chunk(2, dim=0)
-        return {pre + "mlp.shared_expert.gate_proj.weight": g, pre + "mlp.shared_expert.up_proj.weight": u}
+        return {pre + f"mlp.{shared}.gate_proj.weight": g, pre + f"mlp.{shared}.up_proj.weight": u}
     if rest == "mlp.shared_expert.down_proj":
-        return {pre + "mlp.shared_expert.down_proj.weight": tensor}
+        return {pre + f"mlp.{shared}.down_proj.weight": tensor}
+    if rest == "mlp.e_score_correction_bias":
+        return {pre + f"{block}.gate.e_score_correction_bias": tensor}
     if rest == "mlp.shared_gate":
         return {pre + "mlp.shared_expert_gate.weight": tensor}
     raise KeyError(f"no hub name for runtime parameter {name!r}")

@@ -25,6 +25,9 @@ FAMILIES = {
     "llama": dict(architecture="LlamaForCausalLM", moe=False, qk_norm=False, bias_key=True, bias_default=False, has_window=False),
     "mistral": dict(architecture="MistralForCausalLM", moe=False, qk_norm=False, bias_key=False, bias_default=False, has_window=True),
     "mixtral": dict(architecture="MixtralForCausalLM", moe=True, qk_norm=False, bias_key=False, bias_default=False, has_window=True),
+    # sigmoid scores with a selection bias and group-limited top-k, always-on shared experts, leading dense layers,
+    # rotary embedding on the first half of every head
+    "glm4_moe": dict(architecture="Glm4MoeForCausalLM", moe=True, qk_norm=True, bias_key=True, bias_default=False, has_window=False),
 }
 
 
@@ -49,6 +52,12 @@ class ModelConfig:
     rms_norm_eps: float = 1e-6
     use_qk_norm: bool = True
     attention_bias: bool = False           # bias on the q / k / v projections (Qwen2)
+    partial_rotary_factor: float = 1.0     # share of every head's dims that the rotary embedding turns (the leading ones)
+    score_function: str = "softmax"        # "softmax" | "sigmoid" (scores of the router)
+    router_bias: bool = False              # a stored per-expert selection bias (``e_score_correction_bias``) ranks the experts
+    n_group: int = 1                       # group-limited routing: experts in ``n_group`` groups, ``topk_group`` of them eligible
+    topk_group: int = 1
+    routed_scaling_factor: float = 1.0
     sliding_window: int = 0                # > 0: every query sees only its last ``sliding_window`` keys (Mistral-style)
     rope_scaling: dict | None = None       # Hugging Face ``rope_scaling`` / ``rope_parameters`` entry, None = plain
     num_nextn_predict_layers: int = 0      # 1 = a multi-token-prediction head trained beside the next-token loss
@@ -84,6 +93,7 @@ class ModelConfig:
         dense_mlp = 3 * H * self.intermediate_size
         expert = 3 * H * self.moe_intermediate_size
         shared = 3 * H * self.shared_expert_intermediate_size + (H if self.shared_expert_gate else 0)
+        shared += self.num_experts if self.router_bias else 0
         total = active = 0
         for i in range(self.num_hidden_layers):
             if self.layer_is_moe(i):
@@ -156,7 +166,20 @@ class ModelConfig:
             if self.family.startswith("qwen2"):
                 d["use_sliding_window"] = bool(self.sliding_window)
                 d["max_window_layers"] = 0 if self.sliding_window else self.num_hidden_layers
-        if self.family == "mixtral":
+        if self.family == "glm4_moe":
+            first_dense = 0
+            while first_dense in self.mlp_only_layers:
+                first_dense += 1
+            if sorted(self.mlp_only_layers) != list(range(first_dense)):
+                raise ValueError("glm4_moe stores its dense layers as a leading run (first_k_dense_replace)")
+            d.update({"moe_intermediate_size": self.moe_intermediate_size, "n_routed_experts": self.num_experts,
+                      "num_experts_per_tok": self.num_experts_per_tok, "norm_topk_prob": self.norm_topk_prob,
+                      "n_shared_experts": self.shared_expert_intermediate_size // max(self.moe_intermediate_size, 1),
+                      "n_group": self.n_group, "topk_group": self.topk_group, "first_k_dense_replace": first_dense,
+                      "routed_scaling_factor": self.routed_scaling_factor, "use_qk_norm": self.use_qk_norm,
+                      "partial_rotary_factor": self.partial_rotary_factor})
+            d["rope_parameters"]["partial_rotary_factor"] = self.partial_rotary_factor
+        elif self.family == "mixtral":
             d.update({"num_local_experts": self.num_experts, "num_experts_per_tok": self.num_experts_per_tok,
                       "router_aux_loss_coef": self.router_aux_loss_coef, "output_router_logits": False,
                       "intermediate_size": self.moe_intermediate_size})
@@ -196,21 +219,30 @@ class ModelConfig:
                              f"full and windowed attention is not built")
         rp = d.get("rope_parameters") or {}
         rope_theta = d.get("rope_theta") or rp.get("rope_theta", 1e6 if mt.startswith("qwen") else 1e4)
-        scaling = d.get("rope_scaling") or ({k: v for k, v in rp.items() if k != "rope_theta"} if rp else None)
+        scaling = d.get("rope_scaling") or ({k: v for k, v in rp.items() if k not in ("rope_theta", "partial_rotary_factor")} if rp else None)
         if scaling:
             scaling = dict(scaling)
             scaling.setdefault("rope_type", scaling.pop("type", "default"))
             if scaling["rope_type"] == "default":
                 scaling = None
         hd = d.get("head_dim") or d["hidden_size"] // d["num_attention_heads"]
-        if mt == "mixtral":
+        extra = {}
+        if mt == "glm4_moe":
+            n_exp, width, dense_width = d["n_routed_experts"], d["moe_intermediate_size"], d["intermediate_size"]
+            topk, renorm = d.get("num_experts_per_tok", 8), d.get("norm_topk_prob", True)
+            extra = dict(partial_rotary_factor=float(d.get("partial_rotary_factor", rp.get("partial_rotary_factor", 0.5))),
+                         score_function="sigmoid", router_bias=True, n_group=int(d.get("n_group", 1)),
+                         topk_group=int(d.get("topk_group", 1)), routed_scaling_factor=float(d.get("routed_scaling_factor", 1.0)),
+                         shared_expert_intermediate_size=int(d.get("n_shared_experts", 0) or 0) * width,
+                         mlp_only_layers=list(range(int(d.get("first_k_dense_replace", 0)))), use_qk_norm=bool(d.get("use_qk_norm", False)))
+        elif mt == "mixtral":
             n_exp, width, dense_width = d.get("num_local_experts", 8), d["intermediate_size"], d["intermediate_size"]
             topk, renorm = d.get("num_experts_per_tok", 2), True
         else:
             n_exp = d.get("num_experts", 0) if fam["moe"] else 0
             width, dense_width = d.get("moe_intermediate_size", 0), d.get("intermediate_size", 0)
             topk, renorm = d.get("num_experts_per_tok", 8), d.get("norm_topk_prob", mt != "qwen2_moe")
-        return cls(
+        fields = dict(
             vocab_size=d["vocab_size"], hidden_size=d["hidden_size"], num_hidden_layers=d["num_hidden_layers"],
             num_attention_heads=d["num_attention_heads"],
             num_key_value_heads=d.get("num_key_value_heads", d["num_attention_heads"]), head_dim=hd,
@@ -231,6 +263,8 @@ class ModelConfig:
             router_aux_loss_coef=d.get("router_aux_loss_coef", 0.0), initializer_range=d.get("initializer_range", 0.02),
             max_position_embeddings=d.get("max_position_embeddings", 262144), model_type=mt,
         )
+        fields.update(extra)
+        return cls(**fields)
 
     def save(self, directory: str | Path) -> None:
         Path(directory).mkdir(parents=True, exist_ok=True)

@@ -7,7 +7,7 @@ layout kinds and the conversion of every kind to the run-time banks ``gate_up [E
 are the content of the reference's ``ExpertLayout`` (halo/models/moe/expert_layout.py:63-163) and
 ``MoEFamilySpec`` registry (halo/models/moe/family_specs.py:66-426).
 
-``runnable`` marks the families whose whole decoder this package implements (the Qwen3 line). The others are
+``runnable`` marks the families whose whole decoder this package implements (the Qwen line, Mixtral, GLM-4-MoE). The others are
 registered so that loading one fails with a sentence that names what is missing instead of a shape error.
 """
 
@@ -64,7 +64,7 @@ for _s in (
     MoEFamilySpec("deepseek_v4", SEPARATE_GLU, score_function="sigmoid", selection_bias=True, routed_scaling_factor=2.5,
                   grouped_topk=True, shared_experts=True, missing="multi-head latent attention, hyper-connections"),
     MoEFamilySpec("glm4_moe", SEPARATE_GLU, score_function="sigmoid", selection_bias=True, grouped_topk=True,
-                  shared_experts=True, missing="partial rotary embedding, grouped top-k routing"),
+                  shared_experts=True, runnable=True),
     MoEFamilySpec("glm5_next", SEPARATE_GLU, score_function="sigmoid", selection_bias=True, shared_experts=True,
                   missing="sparse (DSA) attention, hyper-connections"),
     MoEFamilySpec("gemma4", FUSED, activation="gelu_tanh", missing="sliding/global attention mix, logit soft-capping"),
@@ -76,7 +76,7 @@ for _s in (
     MoEFamilySpec("lfm2_moe", SEPARATE_MLP, score_function="sigmoid", selection_bias=True, missing="short-convolution mixer layers"),
     MoEFamilySpec("mistral4", SEPARATE_MLP, missing="family decoder"),
     MoEFamilySpec("mixtral", SEPARATE_MLP, router_name="block_sparse_moe.gate", experts_prefix="block_sparse_moe.experts",
-                  missing="sliding-window attention"),
+                  runnable=True),
     MoEFamilySpec("nemotron_h", SEPARATE_MLP, score_function="sigmoid", shared_experts=True, activation="relu2",
                   missing="Mamba-2 mixer layers, non-gated experts"),
     MoEFamilySpec("step3p7", SEPARATE_GLU, shared_experts=True, missing="family decoder"),

@@ -262,6 +262,12 @@ class SparseMoE(nn.Module):
         # auxiliary-loss-free balancing: a per-expert bias that only ranks experts (never a parameter,
         # saved as a sidecar by the balancing callback)
         self.register_buffer("selection_bias", None, persistent=False)
+        # families that ship a selection bias with the checkpoint (it ranks experts, never weights them): stored, not trained
+        if cfg.router_bias:
+            self.e_score_correction_bias = nn.Parameter(torch.zeros(cfg.num_experts, dtype=torch.float32, device=device),
+                                                        requires_grad=False)
+        else:
+            self.register_parameter("e_score_correction_bias", None)
         self.expert_lora = None       # halo_b200.peft.lora.ExpertLora when the routed experts carry adapters
         self.lowp = ""                # block-scaled format of quantisation-aware training (banks and dispatched rows)
         self.load_counter = None      # (ExpertLoadCounter, layer index) when load metrics are on
@@ -271,12 +277,19 @@ class SparseMoE(nn.Module):
         cfg = self.cfg
         gate_w = self.gate if self.gate.dtype == h.dtype else self.gate.to(h.dtype)
         logits = _RouterLinear.apply(h, gate_w) if h.is_cuda else (h.float() @ self.gate.float().t())
+        bias = self.selection_bias
+        if self.e_score_correction_bias is not None:
+            bias = self.e_score_correction_bias if bias is None else self.e_score_correction_bias + bias
         if ctx.replay_topk is not None:
             idx = ctx.replay_topk.pop(0)
-            probs = torch.softmax(logits.float(), dim=-1)
+            probs = torch.sigmoid(logits.float()) if cfg.score_function == "sigmoid" else torch.softmax(logits.float(), dim=-1)
             w = probs.gather(-1, idx.long())
             if cfg.norm_topk_prob:
-                w = w / w.sum(-1, keepdim=True)
+                w = w / (w.sum(-1, keepdim=True) + (1e-20 if cfg.score_function == "sigmoid" else 0.0))
+            w = w * cfg.routed_scaling_factor
+        elif cfg.score_function == "sigmoid":
+            idx, w = moe_ops.router_sigmoid_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob, bias, cfg.n_group,
+                                                 cfg.topk_group, cfg.routed_scaling_factor)
         else:
             idx, w = moe_ops.router_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob, self.selection_bias)
         if self.load_counter is not None and not getattr(ctx, "output_unused", False):
@@ -528,7 +541,8 @@ class Qwen3Model(nn.Module):
     def rope(self, position_ids):
         """cos / sin table of these positions, in the rounding of the model's dtype."""
         exact = next(self.parameters()).dtype == torch.float32 and not position_ids.is_cuda
-        return rope_table(position_ids, self.cfg.head_dim, self.cfg.rope_theta, self.cfg.rope_scaling,
+        rotated = int(self.cfg.head_dim * self.cfg.partial_rotary_factor)      # partial rotary: the leading dims of a head
+        return rope_table(position_ids, rotated, self.cfg.rope_theta, self.cfg.rope_scaling,
                           self.cfg.max_position_embeddings, round_bf16=not exact)
 
     def _gate(self, params):

@@ -47,6 +47,27 @@ def router_topk_reference(logits: torch.Tensor, k: int, renorm: bool, sel_bias: 
     return idx.to(torch.int32), w
 
 
+def router_sigmoid_topk(logits: torch.Tensor, k: int, renorm: bool, sel_bias: torch.Tensor | None = None, n_group: int = 1,
+                        topk_group: int = 1, scaling: float = 1.0):
+    """Routing of the sigmoid-score families (DeepSeek-V3 / GLM-4 style): scores = sigmoid(logits); the ranking adds the
+    selection bias and, with ``n_group > 1``, keeps only the ``topk_group`` groups of experts whose two best biased
+    scores sum highest; the weights are the unbiased scores of the chosen experts, renormalised and scaled. Tensor
+    ops with autograd (the score matrix is ``[T, E]``: small beside the expert products)."""
+    scores = torch.sigmoid(logits.float())
+    choice = scores if sel_bias is None else scores + sel_bias.float()
+    if n_group > 1:
+        T, E = choice.shape
+        grouped = choice.view(T, n_group, E // n_group)
+        group_scores = grouped.topk(min(2, E // n_group), dim=-1).values.sum(-1)
+        keep = torch.zeros_like(group_scores, dtype=torch.bool).scatter_(1, group_scores.topk(topk_group, dim=-1).indices, True)
+        choice = choice.masked_fill(~keep[:, :, None].expand_as(grouped).reshape(T, E), 0.0)
+    idx = choice.detach().topk(k, dim=-1).indices
+    w = scores.gather(-1, idx)
+    if renorm:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return idx.to(torch.int32), w * scaling
+
+
 class _RouterTopK(torch.autograd.Function):
     @staticmethod
     def forward(ctx, logits, k, renorm, sel_bias=None):

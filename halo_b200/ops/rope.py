@@ -112,6 +112,7 @@ def rope_table(position_ids: torch.Tensor, head_dim: int, theta: float, scaling:
 def qk_norm_rope_reference(qkv, wq, wk, table, n_heads, n_kv_heads, eps, use_norm=True):
     T = qkv.shape[0]
     D = qkv.shape[1] // (n_heads + 2 * n_kv_heads)
+    R = 2 * table.shape[1]               # rotated dims of a head: all of them, or the leading part (partial rotary)
     q = qkv[:, : n_heads * D].reshape(T, n_heads, D)
     k = qkv[:, n_heads * D : (n_heads + n_kv_heads) * D].reshape(T, n_kv_heads, D)
     cos = torch.cat([table[..., 0], table[..., 0]], dim=-1)[:, None, :].to(qkv.dtype)
@@ -125,8 +126,10 @@ def qk_norm_rope_reference(qkv, wq, wk, table, n_heads, n_kv_heads, eps, use_nor
         return w * (xf * rstd).to(x.dtype)
 
     def rot(x):
-        x1, x2 = x[..., : D // 2], x[..., D // 2 :]
-        return (x * cos) + (torch.cat([-x2, x1], dim=-1) * sin)
+        xr, rest = x[..., :R], x[..., R:]
+        x1, x2 = xr[..., : R // 2], xr[..., R // 2 :]
+        turned = (xr * cos) + (torch.cat([-x2, x1], dim=-1) * sin)
+        return turned if R == D else torch.cat([turned, rest], dim=-1)
 
     return rot(norm(q, wq)).reshape(T, n_heads * D), rot(norm(k, wk)).reshape(T, n_kv_heads * D)
 
@@ -174,6 +177,6 @@ class _QKNormRope(torch.autograd.Function):
 
 def qk_norm_rope(qkv, wq, wk, table, n_heads, n_kv_heads, eps=1e-6, use_norm=True):
     D = qkv.shape[1] // (n_heads + 2 * n_kv_heads)
-    if not qkv.is_cuda or D != HEAD_DIM or qkv.dtype != torch.bfloat16:
+    if not qkv.is_cuda or D != HEAD_DIM or qkv.dtype != torch.bfloat16 or 2 * table.shape[1] != D:
         return qk_norm_rope_reference(qkv, wq, wk, table, n_heads, n_kv_heads, eps, use_norm)
     return _QKNormRope.apply(qkv.contiguous(), wq, wk, table, n_heads, n_kv_heads, eps, use_norm)
