@@ -145,8 +145,44 @@ def cases(small: bool):
     return out
 
 
+def family_cases(small: bool):
+    """Bandwidth-bound kernels of the other families and of generation (run with ``--families``): residual-stream ops
+    at 4 streams, per-stream norm, block-scaled fake quantisation, standalone SwiGLU, decode attention over a cache."""
+    from halo_b200.inference.generate import KVCache
+    from halo_b200.ops import lowp, streams
+    from halo_b200.ops.activation import swiglu
+
+    T = 8192 if small else 32768
+    H, N = 2048, 4
+    out = {}
+    st, blk = bf16(T, N, H), bf16(T, H)
+    w = torch.rand(T, N, device="cuda")
+    comb = torch.softmax(torch.randn(T, N, N, device="cuda"), dim=-1)
+    with torch.no_grad():
+        out["stream_collapse_fwd"] = (lambda: streams.collapse_streams(st, w), 0.0, 2.0 * T * H * (N + 1))
+        out["stream_mix_fwd"] = (lambda: streams.mix_streams(blk, st, w, comb), 0.0, 2.0 * T * H * (2 * N + 1))
+        out["stream_inject_fwd"] = (lambda: streams.inject_streams(blk, st, w), 0.0, 2.0 * T * H * (2 * N + 1))
+        out["sinkhorn_20_iters"] = (lambda: streams.sinkhorn_knopp(comb, 20, 1e-6), 0.0, 4.0 * 2 * T * N * N)
+        wide, nw = bf16(T, N * H), torch.zeros(N * H, device="cuda")
+        out["grouped_rmsnorm_fwd"] = (lambda: streams.grouped_rms_norm(wide, nw, 1e-6, N), 0.0, 2.0 * 2 * T * N * H)
+        for fmt in lowp.FORMATS:
+            out[f"fake_quant_{fmt}"] = (lambda fmt=fmt: lowp.fake_quant(wide, fmt), 0.0, 2.0 * 2 * T * N * H)
+        pre = bf16(T, 2 * 6144)
+        out["swiglu_fwd"] = (lambda: swiglu(pre), 0.0, 2.0 * 3 * T * 6144)
+        B, S, NQ, NKV, HD = (16, 2048, 32, 4, 128) if small else (64, 8192, 32, 4, 128)
+        cache = KVCache(1, B, S, NKV, HD, torch.bfloat16, "cuda")
+        cache.k.normal_()
+        cache.v.normal_()
+        cache.lengths.fill_(S - 1)
+        cache.begin_decode()
+        q = bf16(B, NQ * HD)
+        out["decode_attention"] = (lambda: cache.attend(0, q, NQ), 4.0 * B * NQ * HD * S, 2.0 * 2 * B * S * NKV * HD)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--families", action="store_true", help="the other families' kernels and decode attention instead of the flagship's")
     ap.add_argument("--only", nargs="*", default=None, help="substrings of case names to run")
     ap.add_argument("--small", action="store_true", help="8k tokens, 16k vocabulary: sized for a profiler capture")
     ap.add_argument("--iters", type=int, default=7)
@@ -156,7 +192,7 @@ def main():
     hbm, tf, tag = peaks()
     timer = Timer(args.iters, args.warmup)
     rows = []
-    for name, (fn, flops, nbytes) in cases(args.small).items():
+    for name, (fn, flops, nbytes) in (family_cases(args.small) if args.families else cases(args.small)).items():
         if args.only and not any(s in name for s in args.only):
             continue
         ms = timer(fn)
