@@ -31,6 +31,7 @@ TOOLS = {
     "generate": "halo_b200.entrypoints.generation",
     "evaluate": "halo_b200.entrypoints.evaluation",
     "reward-scoring": "halo_b200.entrypoints.reward_scoring",
+    "env-eval": "halo_b200.entrypoints.env_eval",
     "merge-adapter": "halo_b200.checkpoint.tools.merge_adapter",
     "lowp-convert": "halo_b200.checkpoint.tools.lowp_convert",
     "bench": "bench",

@@ -120,3 +120,20 @@ def test_sampled_episodes_become_masked_rows():
         logp, _ = model.token_logprobs(batch.input_ids, batch.position_ids, batch.cu_seqlens, batch.labels)
     scored = batch.labels.reshape(-1) != -100
     assert torch.allclose(logp[scored], batch.old_logprobs[scored], atol=1e-4)       # sampler and trainer agree token by token
+
+
+def test_environment_evaluation_report():
+    from halo_b200.entrypoints.env_eval import evaluate_tasks
+    from halo_b200.inference.generate import SamplingParams
+    from halo_b200.models.config import ModelConfig
+    from halo_b200.models.qwen3 import build_model
+
+    cfg = ModelConfig(vocab_size=264, hidden_size=32, num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=1,
+                      head_dim=16, intermediate_size=64, moe_intermediate_size=0, num_experts=0, model_type="qwen3")
+    model = build_model(cfg, device="cpu", seed=0, gradient_checkpointing=False)
+    tasks = [{"question": "2 + 2?", "answer": "4"}, {"question": "3 * 3?", "answer": "9"}]
+    report, episodes = evaluate_tasks(model, ByteTokenizer(), tasks, "tool_qa", 2, SamplingParams(max_new_tokens=4, seed=None),
+                                      {"protocol": "native"})
+    # under the tagged-call protocol free text is a final answer: a random policy answers at once, wrongly
+    assert report["episodes"] == 4 and report["tasks"] == 2 and report["mean_score"] == 0.0 and report["pass@2"] == 0.0
+    assert report["cut_short"] == 0.0 and all(e["done_reason"] == "answered" and e["turns"] == 1 for e in episodes)
