@@ -15,15 +15,34 @@ import numpy as np
 CHATML_ROLES = ("system", "user", "assistant", "tool")
 
 
+def load_chat_template(name: str = "chatml") -> str:
+    """A bundled training-time chat template (``halo_b200/data/templates/<name>.jinja``), for tokenizers that ship none:
+    ``tokenizer.chat_template = load_chat_template()``."""
+    import os
+
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "templates", f"{name}.jinja")
+    if not os.path.isfile(path):
+        raise FileNotFoundError(f"no bundled chat template named {name!r}")
+    return open(path).read()
+
+
 def chatml(messages: list[dict], add_generation_prompt: bool = False) -> str:
     text = "".join(f"<|im_start|>{m['role']}\n{m['content']}<|im_end|>\n" for m in messages)
     return text + ("<|im_start|>assistant\n" if add_generation_prompt else "")
 
 
+def template_ids(tokenizer, messages, add_generation_prompt: bool, tools=None) -> list[int]:
+    """Token ids of the tokenizer's own chat template (whatever container its version returns them in)."""
+    kw = {"tools": tools} if tools else {}
+    out = tokenizer.apply_chat_template(messages, add_generation_prompt=add_generation_prompt, tokenize=True, **kw)
+    if hasattr(out, "keys"):
+        out = out["input_ids"]
+    return [int(t) for t in out]
+
+
 def _render_ids(tokenizer, messages, add_generation_prompt: bool, tools=None) -> list[int]:
     if getattr(tokenizer, "chat_template", None) or not hasattr(tokenizer, "__call__"):
-        kw = {"tools": tools} if tools else {}
-        return list(tokenizer.apply_chat_template(messages, add_generation_prompt=add_generation_prompt, tokenize=True, **kw))
+        return template_ids(tokenizer, messages, add_generation_prompt, tools)
     return list(tokenizer(chatml(messages, add_generation_prompt), add_special_tokens=False)["input_ids"])
 
 

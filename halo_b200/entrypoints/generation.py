@@ -39,7 +39,9 @@ def read_prompts(path: str, tokenizer):
         if tokenizer is None:
             raise ValueError("text prompts need a tokenizer beside the checkpoint")
         if "messages" in r:
-            r["prompt_ids"] = tokenizer.apply_chat_template(r["messages"], add_generation_prompt=True, tokenize=True)
+            from halo_b200.data.chat_render import template_ids
+
+            r["prompt_ids"] = template_ids(tokenizer, r["messages"], True)
         else:
             r["prompt_ids"] = tokenizer(r["prompt"])["input_ids"]
     return rows

@@ -41,8 +41,9 @@ class LocalPolicy:
         return self.episodes[key]
 
     def _render(self, messages, tools) -> list[int]:
-        kw = {"tools": tools} if tools else {}
-        return list(self.tokenizer.apply_chat_template(messages, add_generation_prompt=True, tokenize=True, **kw))
+        from halo_b200.data.chat_render import template_ids
+
+        return template_ids(self.tokenizer, messages, True, tools)
 
     def for_episode(self, key: int):
         """The ``generate`` callable bound to one episode's token record."""

@@ -117,3 +117,29 @@ def test_replica_identity_is_agreed_on_every_rank(same):
     from halo_b200.data.packing import pack_documents
 
     assert data_digest([pack_documents([np.arange(5)])]) != data_digest([pack_documents([np.arange(6)])])
+
+
+def test_bundled_chat_template_extends_history_and_marks_assistant_turns():
+    transformers = pytest.importorskip("transformers")
+    from tokenizers import Tokenizer, models, pre_tokenizers
+
+    from halo_b200.data.chat_render import load_chat_template, template_ids
+
+    vocab = {chr(i): i - 32 for i in range(32, 127)}
+    vocab["\n"], vocab["[UNK]"] = len(vocab), len(vocab) + 1
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="[UNK]"))
+    tok.pre_tokenizer = pre_tokenizers.Split("", "isolated")
+    t = transformers.PreTrainedTokenizerFast(tokenizer_object=tok)
+    t.chat_template = load_chat_template()
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"}, {"role": "assistant", "content": "hello"},
+            {"role": "tool", "content": "42"}, {"role": "assistant", "content": "ok"}]
+    ids, mask, report = render_conversation(t, msgs)
+    assert report == {"rewritten": 0, "turns": 2}
+    texts = [t.decode(ids[a:b]).replace(" ", "") for a, b in completion_spans(mask)]
+    assert texts == ["hello<|im_end|>\n", "ok<|im_end|>\n"]
+    shorter = template_ids(t, msgs[:3], False)
+    assert list(ids[:len(shorter)]) == shorter                                   # history is never rewritten
+    with_tools = t.apply_chat_template(msgs[:2], tokenize=False, tools=[{"type": "function", "function": {"name": "calc"}}])
+    assert "<tools>" in with_tools and '"name": "calc"' in with_tools and with_tools.count("<|im_start|>system") == 1
+    with pytest.raises(FileNotFoundError):
+        load_chat_template("nope")
