@@ -155,6 +155,9 @@ def load_policy_model(model_args, pc, device, runtime, gradient_checkpointing=Tr
     else:
         model = from_pretrained(model_args.model_name_or_path, device=device, dtype=dtype, transport=transport,
                                 gradient_checkpointing=gradient_checkpointing)
+    from halo_b200.models.attention_selection import describe
+
+    log.info(describe(model.cfg, device, dtype))
     if getattr(model_args, "lowp_format", ""):
         from halo_b200.models.qwen3 import apply_lowp_compute
 

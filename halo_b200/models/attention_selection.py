@@ -1,0 +1,35 @@
+"""Which attention path serves a model, decided once from its configuration and device and logged at load time
+(the role of halo/models/attention/selection.py:383-462, with one in-tree kernel family instead of five backends).
+
+* ``flash``     - the sm_100a flash kernels: bf16 on CUDA, head_dim 128, causal attention inside packed documents,
+                  grouped-query heads; deterministic forward and backward (no atomics), so a determinism request
+                  changes nothing.
+* ``masked``    - the masked-attention op (query tiles under an explicit ``[T, T]`` mask): sliding windows and tree
+                  packing; element-wise half on the masked-softmax kernel, products on library GEMMs.
+* ``reference`` - tensor ops: CPU runs, fp32 models, head dims the kernels are not built for.
+"""
+
+from __future__ import annotations
+
+import torch
+
+
+def attention_path(cfg, device, dtype, tree_packing: bool = False) -> tuple[str, str]:
+    device = torch.device(device)
+    if cfg.sliding_window:
+        return "masked", f"sliding_window={cfg.sliding_window}: the flash kernel has no window"
+    if tree_packing:
+        return "masked", "tree packing: branches attend a shared trunk"
+    if device.type != "cuda":
+        return "reference", f"device {device.type}"
+    if dtype != torch.bfloat16:
+        return "reference", f"dtype {dtype} (the kernels take bf16)"
+    if cfg.head_dim != 128:
+        return "reference", f"head_dim {cfg.head_dim} (the kernels are built for 128)"
+    return "flash", "bf16, head_dim 128, packed causal rows"
+
+
+def describe(cfg, device, dtype, tree_packing: bool = False) -> str:
+    path, why = attention_path(cfg, device, dtype, tree_packing)
+    rotary = "fused QK-norm + RoPE kernel" if path == "flash" and cfg.partial_rotary_factor == 1.0 else "rotary as tensor ops"
+    return f"attention path: {path} ({why}); {rotary}"
