@@ -1,6 +1,7 @@
 """Low-precision checkpoints in and out, one tensor at a time:
 
     python -m halo_b200.checkpoint.tools.lowp_convert dequant-block-fp8 <src> <dst>
+    python -m halo_b200.checkpoint.tools.lowp_convert export-block-fp8 <src> <dst> [--keep REGEX ...]
     python -m halo_b200.checkpoint.tools.lowp_convert export <src> <dst> --format mxfp8|mxfp4|nvfp4 [--keep REGEX ...]
     python -m halo_b200.checkpoint.tools.lowp_convert dequant <src> <dst>
 
@@ -57,6 +58,39 @@ def dequant_block_fp8(src: str, dst: str) -> int:
         cfg = json.load(open(cfg_path))
         cfg.pop("quantization_config", None)
         cfg["torch_dtype"] = "bfloat16"
+        json.dump(cfg, open(cfg_path, "w"), indent=2)
+    return n
+
+
+def export_block_fp8(src: str, dst: str, keep: list[str] | None = None) -> int:
+    """bf16 matrices -> ``float8_e4m3fn`` with one fp32 ``weight_scale_inv`` per 128 x 128 block (the served-weights layout
+    :func:`dequant_block_fp8` reads; inference engines load it directly)."""
+    kept = [re.compile(p) for p in keep or []]
+    idx = CheckpointIndex(src)
+    writer = StreamingShardWriter(dst)
+    n = 0
+    for name in sorted(idx.weight_map):
+        t = idx.get(name)
+        if t.dim() != 2 or not name.endswith(".weight") or ALWAYS_KEPT.search(name) or any(p.search(name) for p in kept):
+            writer.add(name, t)
+            continue
+        rows, cols = t.shape
+        pr, pc = -(-rows // BLOCK) * BLOCK, -(-cols // BLOCK) * BLOCK
+        padded = torch.zeros(pr, pc, dtype=torch.float32)
+        padded[:rows, :cols] = t.float()
+        blocks = padded.view(pr // BLOCK, BLOCK, pc // BLOCK, BLOCK)
+        scale = (blocks.abs().amax(dim=(1, 3)) / lowp.E4M3_MAX).clamp(min=1e-12)              # [rows/128, cols/128]
+        q = (blocks / scale[:, None, :, None]).clamp(-lowp.E4M3_MAX, lowp.E4M3_MAX).to(torch.float8_e4m3fn)
+        writer.add(name, q.view(pr, pc)[:rows, :cols].contiguous())
+        writer.add(name + "_scale_inv", scale)
+        n += 1
+    writer.finish()
+    copy_side_files(src, dst)
+    cfg_path = os.path.join(dst, "config.json")
+    if os.path.isfile(cfg_path):
+        cfg = json.load(open(cfg_path))
+        cfg["quantization_config"] = {"quant_method": "fp8", "fmt": "e4m3", "weight_block_size": [BLOCK, BLOCK],
+                                      "activation_scheme": "dynamic"}
         json.dump(cfg, open(cfg_path, "w"), indent=2)
     return n
 
@@ -121,6 +155,10 @@ def main(argv=None) -> int:
         p = sub.add_parser(cmd)
         p.add_argument("src")
         p.add_argument("dst")
+    p = sub.add_parser("export-block-fp8")
+    p.add_argument("src")
+    p.add_argument("dst")
+    p.add_argument("--keep", nargs="*", default=[])
     p = sub.add_parser("export")
     p.add_argument("src")
     p.add_argument("dst")
@@ -131,6 +169,8 @@ def main(argv=None) -> int:
         n = dequant_block_fp8(args.src, args.dst)
     elif args.cmd == "dequant":
         n = dequant(args.src, args.dst)
+    elif args.cmd == "export-block-fp8":
+        n = export_block_fp8(args.src, args.dst, args.keep)
     else:
         n = export(args.src, args.dst, args.format, args.keep)
     print(f"{args.cmd}: {n} tensors converted into {args.dst}")

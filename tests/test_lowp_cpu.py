@@ -126,6 +126,17 @@ def test_checkpoint_conversions(tmp_path):
     assert torch.equal(got, (fp8.float() * full).bfloat16()) and (got.float() - w).abs().max() < 0.08 * w.abs().max()
     assert "quantization_config" not in json.load(open(tmp_path / "bf16" / "config.json"))
 
+    # and back: exporting the bf16 result gives a release that dequantises to (nearly) the same weights
+    assert lowp_convert.main(["export-block-fp8", str(tmp_path / "bf16"), str(tmp_path / "fp8_again")]) == 0
+    again = CheckpointIndex(str(tmp_path / "fp8_again"))
+    assert again.get("model.layers.0.mlp.down_proj.weight").dtype == torch.float8_e4m3fn
+    assert again.get("model.layers.0.mlp.down_proj.weight_scale_inv").shape == (2, 3)
+    assert again.get("model.norm.weight").dtype == torch.bfloat16
+    assert lowp_convert.main(["dequant-block-fp8", str(tmp_path / "fp8_again"), str(tmp_path / "bf16_again")]) == 0
+    twice = CheckpointIndex(str(tmp_path / "bf16_again")).get("model.layers.0.mlp.down_proj.weight")
+    assert (twice.float() - got.float()).abs().max() <= 0.07 * got.float().abs().max()
+    assert json.load(open(tmp_path / "fp8_again" / "config.json"))["quantization_config"]["weight_block_size"] == [128, 128]
+
     # a model exported in a block-scaled format and read back is the fake-quantised model
     model = build_model(tiny_moe_config(), device="cpu", seed=1)
     ckpt = str(tmp_path / "ckpt")
