@@ -22,6 +22,7 @@ MOE_HUB_NAMES = {
     "qwen2_moe": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "mixtral": ("block_sparse_moe", "w1", "w3", "w2"),
     "glm4_moe": ("mlp", "gate_proj", "up_proj", "down_proj"),
+    "olmoe": ("mlp", "gate_proj", "up_proj", "down_proj"),
 }
 # how a family names its always-on shared feed-forward block
 SHARED_EXPERT_NAMES = {"glm4_moe": "shared_experts"}

@@ -27,6 +27,8 @@ FAMILIES = {
     "mixtral": dict(architecture="MixtralForCausalLM", moe=True, qk_norm=False, bias_key=False, bias_default=False, has_window=True),
     # sigmoid scores with a selection bias and group-limited top-k, always-on shared experts, leading dense layers,
     # rotary embedding on the first half of every head
+    # one RMSNorm over the whole q (and k) projection instead of one per head; top-k weights not renormalised
+    "olmoe": dict(architecture="OlmoeForCausalLM", moe=True, qk_norm=True, bias_key=True, bias_default=False, has_window=False),
     "glm4_moe": dict(architecture="Glm4MoeForCausalLM", moe=True, qk_norm=True, bias_key=True, bias_default=False, has_window=False),
 }
 
@@ -51,6 +53,7 @@ class ModelConfig:
     rope_theta: float = 1e6
     rms_norm_eps: float = 1e-6
     use_qk_norm: bool = True
+    qk_norm_whole_width: bool = False      # the q / k norm spans all heads of the projection (OLMoE) instead of one head
     attention_bias: bool = False           # bias on the q / k / v projections (Qwen2)
     partial_rotary_factor: float = 1.0     # share of every head's dims that the rotary embedding turns (the leading ones)
     score_function: str = "softmax"        # "softmax" | "sigmoid" (scores of the router)
@@ -88,7 +91,8 @@ class ModelConfig:
     # ---- parameter counts (for MFU and memory planning) ---------------------------------
     def param_counts(self) -> dict[str, int]:
         H, D = self.hidden_size, self.head_dim
-        attn = (H * self.qkv_dim + self.num_attention_heads * D * H + (2 * D if self.use_qk_norm else 0) + 2 * H
+        norm_width = (self.num_attention_heads + self.num_key_value_heads) * D if self.qk_norm_whole_width else 2 * D
+        attn = (H * self.qkv_dim + self.num_attention_heads * D * H + (norm_width if self.use_qk_norm else 0) + 2 * H
                 + (self.qkv_dim if self.attention_bias else 0))
         dense_mlp = 3 * H * self.intermediate_size
         expert = 3 * H * self.moe_intermediate_size
@@ -179,6 +183,10 @@ class ModelConfig:
                       "routed_scaling_factor": self.routed_scaling_factor, "use_qk_norm": self.use_qk_norm,
                       "partial_rotary_factor": self.partial_rotary_factor})
             d["rope_parameters"]["partial_rotary_factor"] = self.partial_rotary_factor
+        elif self.family == "olmoe":
+            d.update({"num_experts": self.num_experts, "num_experts_per_tok": self.num_experts_per_tok,
+                      "norm_topk_prob": self.norm_topk_prob, "intermediate_size": self.moe_intermediate_size, "clip_qkv": None,
+                      "router_aux_loss_coef": self.router_aux_loss_coef, "output_router_logits": False})
         elif self.family == "mixtral":
             d.update({"num_local_experts": self.num_experts, "num_experts_per_tok": self.num_experts_per_tok,
                       "router_aux_loss_coef": self.router_aux_loss_coef, "output_router_logits": False,
@@ -235,6 +243,12 @@ class ModelConfig:
                          topk_group=int(d.get("topk_group", 1)), routed_scaling_factor=float(d.get("routed_scaling_factor", 1.0)),
                          shared_expert_intermediate_size=int(d.get("n_shared_experts", 0) or 0) * width,
                          mlp_only_layers=list(range(int(d.get("first_k_dense_replace", 0)))), use_qk_norm=bool(d.get("use_qk_norm", False)))
+        elif mt == "olmoe":
+            if d.get("clip_qkv"):
+                raise ValueError("an OLMoE checkpoint with clip_qkv set: clamping the projections is not built")
+            n_exp, width, dense_width = d.get("num_experts", 64), d["intermediate_size"], d["intermediate_size"]
+            topk, renorm = d.get("num_experts_per_tok", 8), d.get("norm_topk_prob", False)
+            extra = dict(qk_norm_whole_width=True)
         elif mt == "mixtral":
             n_exp, width, dense_width = d.get("num_local_experts", 8), d["intermediate_size"], d["intermediate_size"]
             topk, renorm = d.get("num_experts_per_tok", 2), True

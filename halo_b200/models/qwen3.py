@@ -116,8 +116,11 @@ class Attention(nn.Module):
         self.lora = None          # halo_b200.peft.lora.LoraSet when low-rank adapters are attached
         self.lowp = ""            # block-scaled format the projections are rounded to (quantisation-aware training)
         if cfg.use_qk_norm:
-            self.q_norm = nn.Parameter(torch.ones(D, dtype=dtype, device=device))
-            self.k_norm = nn.Parameter(torch.ones(D, dtype=dtype, device=device))
+            if cfg.qk_norm_whole_width and tp_size > 1:
+                raise ValueError("a q / k norm over all heads cannot be cut over tensor-parallel ranks")
+            wq, wk = (self.n_heads * D, self.n_kv_heads * D) if cfg.qk_norm_whole_width else (D, D)
+            self.q_norm = nn.Parameter(torch.ones(wq, dtype=dtype, device=device))
+            self.k_norm = nn.Parameter(torch.ones(wk, dtype=dtype, device=device))
         else:
             self.register_parameter("q_norm", None)
             self.register_parameter("k_norm", None)

@@ -256,13 +256,15 @@ def rope_attention(qkv, wq, wk, table, plan, n_heads, n_kv_heads, eps=1e-6, use_
     """``attention(rope(norm(q)), rope(norm(k)), v)`` from the fused projection ``qkv``."""
     D = qkv.shape[1] // (n_heads + 2 * n_kv_heads)
     scale = float(scale if scale is not None else D**-0.5)
-    if qkv.is_cuda and D == HEAD_DIM and qkv.dtype == torch.bfloat16 and 2 * table.shape[1] == D:
+    per_head_norm = not use_norm or wq is None or wq.numel() == D
+    if qkv.is_cuda and D == HEAD_DIM and qkv.dtype == torch.bfloat16 and 2 * table.shape[1] == D and per_head_norm:
         return _RopeAttention.apply(qkv.contiguous(), wq, wk, table, plan, n_heads, n_kv_heads, eps, use_norm, scale)
     from .rope import qk_norm_rope_reference
 
     q, k = qk_norm_rope_reference(qkv, wq, wk, table, n_heads, n_kv_heads, eps, use_norm)
     v = qkv[:, (n_heads + n_kv_heads) * D :]
     if qkv.is_cuda and D == HEAD_DIM and qkv.dtype == torch.bfloat16:
-        # partial rotary: the rotation runs as tensor ops (the fused kernel turns whole heads), attention on the kernel
+        # partial rotary / whole-width q-k norm: these run as tensor ops (the fused kernel norms and turns whole heads
+        # one by one), attention itself on the kernel
         return flash_attention(q, k, v, plan, n_heads, n_kv_heads, scale)
     return attention_reference(q, k, v, plan.cu_seqlens, n_heads, n_kv_heads, scale)

@@ -122,6 +122,11 @@ def qk_norm_rope_reference(qkv, wq, wk, table, n_heads, n_kv_heads, eps, use_nor
         if not use_norm:
             return x
         xf = x.float()
+        if w.numel() == x.shape[1] * x.shape[2]:
+            # one norm over the whole projection (all heads together), as OLMoE does, instead of one per head
+            flat = xf.reshape(T, -1)
+            rstd = torch.rsqrt(flat.pow(2).mean(-1, keepdim=True) + eps)
+            return (w * (flat * rstd).to(x.dtype)).reshape(x.shape)
         rstd = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
         return w * (xf * rstd).to(x.dtype)
 
@@ -177,6 +182,7 @@ class _QKNormRope(torch.autograd.Function):
 
 def qk_norm_rope(qkv, wq, wk, table, n_heads, n_kv_heads, eps=1e-6, use_norm=True):
     D = qkv.shape[1] // (n_heads + 2 * n_kv_heads)
-    if not qkv.is_cuda or D != HEAD_DIM or qkv.dtype != torch.bfloat16 or 2 * table.shape[1] != D:
+    whole_width_norm = use_norm and wq is not None and wq.numel() != D
+    if not qkv.is_cuda or D != HEAD_DIM or qkv.dtype != torch.bfloat16 or 2 * table.shape[1] != D or whole_width_norm:
         return qk_norm_rope_reference(qkv, wq, wk, table, n_heads, n_kv_heads, eps, use_norm)
     return _QKNormRope.apply(qkv.contiguous(), wq, wk, table, n_heads, n_kv_heads, eps, use_norm)

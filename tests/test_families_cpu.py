@@ -29,6 +29,8 @@ def family_config(family: str, **kw) -> ModelConfig:
         base.update(intermediate_size=96)
     if family == "qwen2_moe":
         base.update(shared_expert_intermediate_size=64, shared_expert_gate=True, norm_topk_prob=False)
+    if family == "olmoe":
+        base.update(intermediate_size=96, norm_topk_prob=False, qk_norm_whole_width=True)
     if family == "glm4_moe":
         base.update(num_experts=8, partial_rotary_factor=0.5, score_function="sigmoid", router_bias=True, n_group=2, topk_group=1,
                     routed_scaling_factor=1.5, shared_expert_intermediate_size=96, mlp_only_layers=[0], use_qk_norm=True)
@@ -43,7 +45,7 @@ def logits_of(model, ids):
 
 
 CASES = [("mistral", {"sliding_window": 16}), ("qwen2", {"sliding_window": 24}), ("llama", {}), ("llama", {"rope_scaling": LLAMA3}), ("llama", {"attention_bias": True}), ("mistral", {}),
-         ("qwen2", {}), ("qwen2", {"rope_scaling": YARN}), ("mixtral", {}), ("qwen2_moe", {}),
+         ("qwen2", {}), ("qwen2", {"rope_scaling": YARN}), ("mixtral", {}), ("qwen2_moe", {}), ("olmoe", {}),
          ("glm4_moe", {}), ("glm4_moe", {"n_group": 4, "topk_group": 2, "use_qk_norm": False, "attention_bias": True})]
 
 
@@ -52,6 +54,11 @@ def test_family_round_trip_through_transformers(tmp_path, family, extra):
     transformers = pytest.importorskip("transformers")
     cfg = family_config(family, **extra)
     model = build_model(cfg, device="cpu", seed=5, gradient_checkpointing=False)
+    if cfg.use_qk_norm:
+        with torch.no_grad():
+            for layer in model.layers:       # all-ones norm weights would hide a wrong norm scope
+                layer.self_attn.q_norm.normal_(1.0, 0.2, generator=torch.Generator().manual_seed(17))
+                layer.self_attn.k_norm.normal_(1.0, 0.2, generator=torch.Generator().manual_seed(19))
     if cfg.router_bias:
         with torch.no_grad():
             for layer in model.layers:       # a zero selection bias would hide a wrong ranking
