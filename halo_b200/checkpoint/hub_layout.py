@@ -37,6 +37,8 @@ def runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, e
         return {"model.norm.weight": tensor}
     if name == "lm_head":
         return {"lm_head.weight": tensor}
+    if name == "score_head.score.weight":          # the sequence-level head of reward / classification models
+        return {"score.weight": tensor}
     if name.startswith("hc_head."):
         return {"model." + name: tensor}
     if name.startswith("mtp."):

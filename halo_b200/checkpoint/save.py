@@ -140,6 +140,17 @@ def save_model(model, directory: str, is_writer: bool | None = None, save_dtype:
             writer.finish()
         if is_writer:
             cfg.save(directory)
+            head = getattr(model, "head", None)
+            if head is not None and hasattr(head, "score"):
+                # a model with a sequence-level head is written as the family's sequence-classification architecture
+                import json
+
+                path = os.path.join(directory, "config.json")
+                d = json.load(open(path))
+                d["architectures"] = [a.replace("ForCausalLM", "ForSequenceClassification") for a in d["architectures"]]
+                d["num_labels"] = int(head.score.weight.shape[0])
+                d.setdefault("pad_token_id", 0)
+                atomic_write_json(path, d)
             if extra_state is not None:
                 atomic_write_json(os.path.join(directory, "halo_state.json"), extra_state)
     guard.raise_if_any(None if not live else (group or dist.group.WORLD), "saving the model failed")

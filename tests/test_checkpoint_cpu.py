@@ -71,3 +71,29 @@ def test_transformers_loads_our_checkpoint_and_agrees(tmp_path, moe):
         ours = model.hidden_states(b.input_ids, b.position_ids, b.cu_seqlens) @ model.head_weight().t()
         theirs = hf(input_ids=b.input_ids[None]).logits[0]
     assert (ours - theirs).abs().max().item() < 5e-2 * theirs.abs().max().item()
+
+
+def test_reward_model_saves_as_sequence_classification(tmp_path):
+    """A model with a sequence-level head is saved as the family's sequence-classification architecture; ``transformers``
+    loads it and scores a document as we do; the trainer can resume from it."""
+    transformers = pytest.importorskip("transformers")
+    from halo_b200.trainers.reward import SequenceHead, _WithHead
+
+    cfg = ModelConfig(vocab_size=1024, hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                      head_dim=32, intermediate_size=256, moe_intermediate_size=0, num_experts=0, model_type="qwen3")
+    model = build_model(cfg, device="cpu", seed=1, gradient_checkpointing=False)
+    head = SequenceHead(cfg.hidden_size, 3)
+    wrapped = _WithHead(model, head)
+    d = str(tmp_path / "rm")
+    save_model(wrapped, d, save_dtype=None)
+    hf = transformers.AutoModelForSequenceClassification.from_pretrained(d, dtype=torch.float32, attn_implementation="eager").eval()
+    assert type(hf).__name__ == "Qwen3ForSequenceClassification" and hf.config.num_labels == 3
+    ids = np.random.default_rng(0).integers(1, cfg.vocab_size, size=40)          # no pad token inside
+    b = pack_documents([ids])
+    with torch.no_grad():
+        ours = head(model.hidden_states(b.input_ids, b.position_ids, b.cu_seqlens), b.cu_seqlens)[0]
+        theirs = hf(input_ids=b.input_ids[None]).logits[0]
+    assert torch.allclose(ours, theirs, atol=1e-4)
+    again = _WithHead(build_model(cfg, device="cpu", seed=9, gradient_checkpointing=False), SequenceHead(cfg.hidden_size, 3))
+    load_model_weights(again, d)
+    assert torch.equal(again.head.score.weight, head.score.weight)
