@@ -16,6 +16,8 @@ METHODS = {
     "kto": "halo_b200.entrypoints.training.preference",
     "smpo": "halo_b200.entrypoints.training.preference",
     "reward": "halo_b200.entrypoints.training.reward",
+    "classification": "halo_b200.entrypoints.training.classification",
+    "embedding": "halo_b200.entrypoints.training.embedding",
     "distill": "halo_b200.entrypoints.training.distill",
     "grpo": "halo_b200.entrypoints.training.grpo",
 }

@@ -184,6 +184,12 @@ class RewardArguments:
 
 
 @dataclass
+class EmbeddingArguments:
+    temperature: float = 0.05
+    pairs_per_row: int = 16
+
+
+@dataclass
 class DistillationArguments:
     teacher_model_name_or_path: str = ""
     distill_mode: Literal["teacher", "self", "sdpg"] = "teacher"

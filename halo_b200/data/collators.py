@@ -7,6 +7,8 @@ by other tooling."""
 
 from __future__ import annotations
 
+from dataclasses import dataclass
+
 import numpy as np
 import torch
 
@@ -37,3 +39,15 @@ def padded(docs, pad_token_id: int = 0, max_len: int | None = None, pad_to_multi
         mask[i, :len(d)] = 1
         labels[i, :len(d) - 1] = d[1:]
     return {"input_ids": torch.from_numpy(ids), "attention_mask": torch.from_numpy(mask), "labels": torch.from_numpy(labels)}
+
+
+@dataclass
+class ClassificationBatch(PackedBatch):
+    """A packed row whose every document carries one class label."""
+
+    doc_labels: torch.Tensor = None      # [n_docs] int64
+
+    def to(self, device, non_blocking: bool = True):
+        b = PackedBatch.to(self, device, non_blocking)
+        return ClassificationBatch(b.input_ids, b.position_ids, b.labels, b.cu_seqlens, b.n_scored,
+                                   self.doc_labels.to(device, non_blocking=non_blocking))

@@ -172,3 +172,76 @@ def build_preference_batches(data_args, tokenizer, dp_rank: int = 0, dp_world: i
         used += need
     flush()
     return rows
+
+
+def build_classification_batches(data_args, tokenizer, num_labels: int, dp_rank: int = 0, dp_world: int = 1, vocab_size: int = 0):
+    """Packed rows of whole documents with one label each (``{"text" | "input_ids", "label"}`` records). Without a
+    dataset: synthetic documents whose label is a function of their first token (learnable)."""
+    import torch
+
+    from halo_b200.data.collators import ClassificationBatch
+
+    row_len = data_args.packed_row_length
+    docs = []
+    if data_args.dataset_format == "synthetic" or not data_args.dataset_path:
+        rng = np.random.default_rng(data_args.shuffle_seed + 7919 * dp_rank)
+        v = data_args.synthetic_vocab or vocab_size
+        for _ in range(512):
+            ids = rng.integers(0, v, size=int(rng.integers(8, 96)))
+            docs.append((ids, int(ids[0] % num_labels)))
+    else:
+        for rec in read_records(data_args.dataset_path):
+            ids, _ = tokenize_record(rec, tokenizer, data_args.dataset_format)
+            label = int(rec["label"])
+            if not 0 <= label < num_labels:
+                raise ValueError(f"label {label} outside 0..{num_labels - 1}")
+            docs.append((ids[:row_len], label))
+        docs = docs[dp_rank::dp_world]
+    rows, cur, labels, used = [], [], [], 0
+
+    def flush():
+        nonlocal cur, labels, used
+        if cur:
+            b = pack_documents(cur)              # no padding "document": every document of the row carries a label
+            rows.append(ClassificationBatch(b.input_ids, b.position_ids, b.labels, b.cu_seqlens, b.n_scored, torch.tensor(labels)))
+        cur, labels, used = [], [], 0
+
+    for ids, label in docs:
+        if used + len(ids) > row_len:
+            flush()
+        cur.append(ids)
+        labels.append(label)
+        used += len(ids)
+    flush()
+    return rows
+
+
+def build_embedding_batches(data_args, tokenizer, dp_rank: int = 0, dp_world: int = 1, vocab_size: int = 0, pairs_per_row: int = 16):
+    """Packed rows in which documents alternate query, positive (``{"query", "positive"}`` records); the other pairs of
+    a row are the in-batch negatives. Without a dataset: the positive is a noisy copy of the query."""
+    row_len = data_args.packed_row_length
+    pairs = []
+    if data_args.dataset_format == "synthetic" or not data_args.dataset_path:
+        rng = np.random.default_rng(data_args.shuffle_seed + 104729 * dp_rank)
+        v = data_args.synthetic_vocab or vocab_size
+        for _ in range(512):
+            q = rng.integers(0, v, size=int(rng.integers(8, 48)))
+            p = q.copy()
+            flip = rng.random(len(p)) < 0.2
+            p[flip] = rng.integers(0, v, size=int(flip.sum()))
+            pairs.append((q, p))
+    else:
+        tok = lambda s: np.asarray(tokenizer(s, add_special_tokens=False)["input_ids"], dtype=np.int64)  # noqa: E731
+        for rec in read_records(data_args.dataset_path):
+            pairs.append((tok(rec["query"])[:row_len // 2], tok(rec["positive"])[:row_len // 2]))
+        pairs = pairs[dp_rank::dp_world]
+    rows, cur, used = [], [], 0
+    for q, p in pairs:
+        if cur and (used + len(q) + len(p) > row_len or len(cur) >= 2 * pairs_per_row):
+            rows.append(pack_documents(cur))
+            cur, used = [], 0
+        cur += [q, p]
+        used += len(q) + len(p)
+    if len(cur) >= 4:                       # a row needs at least one negative
+        rows.append(pack_documents(cur))
+    return rows

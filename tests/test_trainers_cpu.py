@@ -224,3 +224,22 @@ def test_efficiency_metrics_reach_the_logs(tmp_path):
     assert rec["tokens_per_s_per_gpu"] > 0 and rec["mfu"] > 0
     flops = model_flops_per_step(cfg, batches[1].cu_seqlens, batches[1].n_tokens)
     assert abs(rec["mfu"] * eff.peak * (128 / rec["tokens_per_s_per_gpu"]) / flops - 1.0) < 1e-6
+
+
+@pytest.mark.parametrize("method,extra,arch", [("classification", "num_labels: 4\n", "Qwen3MoeForSequenceClassification"),
+                                               ("embedding", "temperature: 0.1\n", "Qwen3MoeForCausalLM")])
+def test_classification_and_embedding_entry_points(tmp_path, method, extra, arch):
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = tmp_path / "c.yaml"
+    cfg.write_text("model_preset: tiny-moe\ninit_from_scratch: true\ndataset_format: synthetic\npacked_row_length: 256\n"
+                   f"max_steps: 3\noptim: adamw_torch\noutput_dir: {tmp_path}/run\n" + extra)
+    r = subprocess.run([sys.executable, "-m", "halo_b200.cli", "launch", method, str(cfg), "-n", "1"], cwd=root,
+                       capture_output=True, text=True, timeout=240, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert "step 3 " in r.stdout + r.stderr
+    assert json.load(open(tmp_path / "run" / "final" / "config.json"))["architectures"] == [arch]
