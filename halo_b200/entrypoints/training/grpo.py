@@ -110,7 +110,13 @@ def serve_rollout_copy(model_args, pc, device, roles, grpo_args, data_args=None,
 
     cfg = PRESETS[model_args.model_preset]() if model_args.init_from_scratch else ModelConfig.load(model_args.model_name_or_path)
     dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
-    serving = build_model(cfg, device=device, dtype=dtype, transport=None, gradient_checkpointing=False)
+    if model_args.init_from_scratch:
+        serving = build_model(cfg, device=device, dtype=dtype, transport=None, gradient_checkpointing=False)
+    else:
+        # the first rounds are sampled before any push arrives: the copy starts from the same checkpoint as the trainers
+        from halo_b200.checkpoint.load import from_pretrained
+
+        serving = from_pretrained(model_args.model_name_or_path, device=device, dtype=dtype, gradient_checkpointing=False)
     sync = make_sync(roles, device, build_manifest(serving), grpo_args.weight_sync_chunk_mb << 20)
     publisher = None
     if has_live_reward(grpo_args):
@@ -186,8 +192,23 @@ def main(argv=None):
         weight_sync = ModelWeightPusher(sync, roles, device, runtime.ep_group if runtime else None)
         if grpo_args.push_parity_tolerance > 0:
             weight_sync.parity_tolerance = grpo_args.push_parity_tolerance
-    trainer = GRPOTrainer(model, train_args, source, grpo_args=grpo_args, weight_sync=weight_sync, device=device,
-                          parallel=runtime, parallelism_fingerprint=pc.fingerprint())
+    ref_model = None
+    if grpo_args.grpo_beta > 0:
+        # the KL anchor: a frozen copy of the policy as it starts (same weights, same sharding, never updated)
+        import copy
+
+        import torch
+
+        base_args = copy.copy(model_args)
+        if getattr(base_args, "use_peft", False):
+            base_args.use_peft, base_args.adapter_path, base_args.merge_adapters_on_save = False, "", False
+        ref_model = load_policy_model(base_args, pc, device, runtime, False, max_tokens=grpo_args.token_budget)
+        for p in ref_model.parameters():
+            p.requires_grad_(False)
+        ref_model.eval()
+        torch.manual_seed(train_args.seed)
+    trainer = GRPOTrainer(model, train_args, source, grpo_args=grpo_args, ref_model=ref_model, weight_sync=weight_sync,
+                          device=device, parallel=runtime, parallelism_fingerprint=pc.fingerprint())
     if roles is not None:
         trainer.collective_group = roles.trainer_group       # the rollout ranks take no part in saves and barriers
         trainer.rank = roles.rank
