@@ -152,6 +152,9 @@ def main(argv=None):
 
     device, (model_args, data_args, train_args, par_args, grpo_args) = parse_script_args(GRPOArguments, argv=argv)
     roles = None
+    if grpo_args.rollout_gpus > 0 and getattr(model_args, "use_peft", False):
+        raise ValueError("rollout_gpus with use_peft: pushing adapters to the rollout copy is not built; sample in process "
+                         "(rollout_backend: in_process) or train full weights")
     if grpo_args.rollout_gpus > 0:
         from halo_b200.weight_sync.roles import split_roles
 
