@@ -22,7 +22,7 @@ DEFAULT_STORE_TIMEOUT_HOURS = 4
 DEFAULT_FS_PROBE_TIMEOUT_SECONDS = 60
 WATCHDOG_WARN_FRACTION = 0.8
 
-# every knob this package reads, with its meaning (kept complete by tests/test_foundations.py)
+# every knob this package reads, with its meaning (kept complete by tests/test_conventions_cpu.py)
 CATALOGUE = {
     "HALO_DATA_ROOT": "scratch directory for profiles, caches and run logs",
     "HALO_LOG_LEVEL": "root log level of the framework's handler",
@@ -31,6 +31,10 @@ CATALOGUE = {
     "HALO_EP_CAPACITY_FACTOR": "receive-buffer rows per rank as a multiple of the mean load",
     "HALO_KERNEL_WAIT_MS": "host-side bound on waits for a device event",
     "HALO_BOUNDED_WAIT_SECONDS": "deadline of a bounded stream wait in weight sync",
+    "HALO_ROLLOUT_WAIT_SECONDS": "how long a trainer waits for a round from its rollout rank",
+    "HALO_GEMM_PAIR": "CTA-pair GEMM: 1 where it wins (default), 0 never, 2 everywhere",
+    "HALO_ATTN_FWD_VARIANT": "forward attention kernel form (2 = output kept in TMEM, the default)",
+    "HALO_ROW_BLOCKS_PER_SM": "thread blocks per SM of the expert row kernels (dispatch / combine)",
     "DIST_NCCL_TIMEOUT_MINUTES": "collective watchdog of every process group",
     "DIST_STORE_TIMEOUT_HOURS": "timeout of store-based joins that outlast the watchdog",
     "DIST_FS_PROBE_TIMEOUT_SECONDS": "how long to poll for the shared-filesystem sentinel",
