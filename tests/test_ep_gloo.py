@@ -66,3 +66,45 @@ def test_ep2_matches_ep1_loss_curve(tmp_path):
     assert a.shape == b.shape == (STEPS,)
     assert abs(a[0] - np.log(4096)) < 0.2
     assert np.max(np.abs(a - b)) < 5e-3, (a, b)
+
+
+def _trace_worker(rank, world):
+    """Two training steps under expert parallelism with the collectives recorded: every rank enters the same
+    collectives in the same order, and the second step repeats the first (nothing depends on the data)."""
+    import torch
+    import torch.distributed as dist
+
+    from halo_b200.data.packing import synthetic_packed_batch
+    from halo_b200.models.config import tiny_moe_config
+    from halo_b200.models.qwen3 import build_model
+    from halo_b200.parallel.expert_parallel import CollectiveTransport
+    from halo_b200.parallel.runtime import ParallelRuntime
+    from halo_b200.trainers.engine import TrainEngine
+    from tests.common.collective_recorder import recording
+
+    cfg = tiny_moe_config()
+    transport = CollectiveTransport(dist.group.WORLD)
+    parallel = ParallelRuntime("cpu", dp_group=dist.group.WORLD, ep_group=dist.group.WORLD, transport=transport)
+    model = build_model(cfg, device="cpu", seed=0, transport=transport)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+    engine = TrainEngine(model, opt, "cpu", parallel=parallel)
+    steps = []
+    for step in range(2):
+        # ranks see different rows with different token counts and routing: the trace must not depend on them
+        batch = synthetic_packed_batch(96 + 32 * rank, cfg.vocab_size, seed=10 * step + rank, lo=8, hi=40)
+        with recording() as trace:
+            engine.train_step(batch)
+        steps.append([(name, n) for name, n, _ in trace])
+    assert steps[0] == steps[1], "the second step entered different collectives than the first"
+    everyone = [None] * world
+    dist.all_gather_object(everyone, steps[0])
+    assert all(t == everyone[0] for t in everyone), "ranks entered different collectives"
+    names = [name for name, _ in steps[0]]
+    per_layer = 4 * 2          # forward pass, recomputation and backward of a layer each exchange counts and rows
+    assert len(names) >= cfg.num_hidden_layers * per_layer and "all_reduce" in names
+
+
+def test_collective_order_is_rank_uniform_and_static():
+    from tests.common.gloo import run_gloo_ranks
+
+    run_gloo_ranks(_trace_worker, 2, timeout=180.0)
