@@ -108,3 +108,32 @@ def test_collective_order_is_rank_uniform_and_static():
     from tests.common.gloo import run_gloo_ranks
 
     run_gloo_ranks(_trace_worker, 2, timeout=180.0)
+
+
+def _negative_control_worker(rank, world):
+    """The expert-parallel layer equals the undistributed one - and the bound that says so can fail: with this rank's
+    experts rotated by one place the same comparison is off by orders of magnitude."""
+    import torch.distributed as dist
+
+    from halo_b200.ops.moe import moe_experts, moe_ffn_reference, router_topk
+    from halo_b200.parallel.expert_parallel import CollectiveTransport
+
+    g = torch.Generator().manual_seed(7)                       # the same on every rank: the full banks
+    T, H, F, E, k = 48 + 16 * rank, 64, 32, 8, 2
+    gate_up, down = torch.randn(E, 2 * F, H, generator=g) * 0.2, torch.randn(E, H, F, generator=g) * 0.2
+    mine = torch.Generator().manual_seed(100 + rank)           # this rank's own tokens
+    x = torch.randn(T, H, generator=mine)
+    idx, w = router_topk(torch.randn(T, E, generator=mine), k, True)
+    want = moe_ffn_reference(x, idx, w, gate_up, down, 0)
+    per = E // world
+    local_gu, local_dn = gate_up[rank * per:(rank + 1) * per].clone(), down[rank * per:(rank + 1) * per].clone()
+    transport = CollectiveTransport(dist.group.WORLD)
+    got = moe_experts(x, idx, w, local_gu, local_dn, transport)
+    tol = 1e-5
+    assert (got - want).abs().max() < tol
+    wrong = moe_experts(x, idx, w, local_gu.roll(1, 0), local_dn.roll(1, 0), transport)
+    assert (wrong - want).abs().max() > 1e3 * tol
+
+
+def test_expert_parallel_layer_with_a_wrong_expert_negative_control():
+    run_gloo_ranks(_negative_control_worker, 2, timeout=120.0)
