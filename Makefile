@@ -2,7 +2,7 @@
 PY ?= python
 NPROC ?= 8
 
-.PHONY: build test-cpu test-gpu test-multigpu bench bench-multi kernel-bench train clean
+.PHONY: build test-cpu test-gpu test-multigpu bench bench-multi bench-band kernel-bench train clean
 
 build:            ## compile halo_b200/lib/libhalo_b200.so for sm_100a
 	$(PY) -c "import __graft_entry__ as g; g.build()"
@@ -21,6 +21,9 @@ bench: build      ## flagship benchmark on one GPU
 
 bench-multi: build
 	$(PY) -m torch.distributed.run --nnodes=1 --nproc-per-node $(NPROC) --master-addr 127.0.0.1 bench.py --gpus $(NPROC)
+
+bench-band: build   ## hold the one-GPU benchmark to its stored band (BAND=<name> picks another; see benchmarks/band.py --list)
+	$(PY) bench.py --steps 3 --warmup 3 | $(PY) benchmarks/band.py $(or $(BAND),moe30b_ep1_n1)
 
 kernel-bench: build
 	$(PY) benchmarks/kernels.py

@@ -153,3 +153,24 @@ def test_large_job_layouts_against_golden_memberships():
     assert (pc.data_parallel_size, pc.ep_group_size, pc.num_nodes, pc.ep_scope) == (1024, 8, 128, "node")
     assert config(64, 3, ep_size=8).fingerprint() != config(64, 3, ep_size=4).fingerprint()      # the layout is in the fingerprint
     assert config(64, 3, ep_size=8).fingerprint() == config(64, 11, ep_size=8).fingerprint()     # the rank is not
+
+
+def test_benchmark_bands():
+    import sys
+
+    sys.path.insert(0, os.path.join(ROOT, "benchmarks"))
+    import band
+
+    b = band.load_band("moe30b_ep8_n8")
+    result = {"n_gpus": 8, "value": 8 * 24000.0, "config": {"model": "moe-30b-a3b", "peak_gib": 146.0}, "clocks": {"reasons": ["sw_power_cap"]}}
+    ok, notes = band.check(b, result)
+    assert ok and "inside the band" in notes[0]
+    assert not band.check(b, {**result, "value": 8 * 20000.0})[0]                          # a regression
+    assert band.check(b, {**result, "value": 8 * 30000.0}) == (True, [n for n in band.check(b, {**result, "value": 8 * 30000.0})[1]])
+    assert "raise the band" in band.check(b, {**result, "value": 8 * 30000.0})[1][0]
+    assert not band.check(b, {**result, "config": {"model": "moe-30b-a3b", "peak_gib": 170.0}})[0]
+    assert not band.check(b, {**result, "n_gpus": 4})[0]
+    assert not band.check(b, {**result, "clocks": {"reasons": ["hw_thermal_slowdown"]}})[0]
+    for f in os.listdir(os.path.join(ROOT, "benchmarks", "baselines")):
+        stored = band.load_band(f[:-5])
+        assert stored["command"].endswith("--steps 3 --warmup 3") and stored["provenance"]["hardware"]
