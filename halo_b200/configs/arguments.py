@@ -222,6 +222,7 @@ class GRPOArguments:
     weight_sync_chunk_mb: int = 1024
     environment_type: str = ""                  # e.g. "qa", "code", "tool_qa": rollouts are episodes of this environment over the dataset's tasks
     environment_options: dict | None = None
+    routing_replay: bool = False                # MoE: train with the experts the sampler routed every token to
     tree_packing: bool = False                  # store every prompt once per group; its completions attend it as branches of a tree
     push_parity_tolerance: float = 0.05         # nats; after the first push trainers and rollout copy score one fixed row (0 = off)
     rollout_prefetch: int = 0                   # rounds the rollout ranks sample ahead (0 = strictly on-policy, 1 = one update stale)

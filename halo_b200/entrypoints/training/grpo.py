@@ -95,7 +95,7 @@ def sampling_source(model, model_args, data_args, train_args, grpo_args, consume
                               top_k=grpo_args.top_k, top_p=grpo_args.top_p)
     return OnPolicyRolloutSource(model, prompts, reward, grpo_args.num_generations, sampling, grpo_args.prompts_per_round,
                                  eos_token_id=eos, seed=train_args.seed + consumer_rank,
-                                 max_prompt_length=grpo_args.max_prompt_length)
+                                 max_prompt_length=grpo_args.max_prompt_length, record_routing=grpo_args.routing_replay)
 
 
 def serve_rollout_copy(model_args, pc, device, roles, grpo_args, data_args=None, train_args=None):

@@ -170,7 +170,10 @@ class Generator:
         return gemm.matmul(h, w, out_dtype=torch.float32) if h.is_cuda else h.float() @ w.float().t()
 
     @torch.no_grad()
-    def generate(self, prompts: list, params: SamplingParams | None = None) -> list[Generation]:
+    def generate(self, prompts: list, params: SamplingParams | None = None, record_routing: bool = False) -> list[Generation]:
+        """``record_routing``: also return, per sequence, the experts every processed token was routed to
+        (``extra["routing"]``: int16 ``[moe layers, prompt + generated - 1, top_k]``, ``extra["routing_layers"]``: their
+        layer indices) so that training can replay the sampler's routing."""
         from halo_b200.models.qwen3 import ForwardContext
 
         params = params or SamplingParams()
@@ -192,8 +195,10 @@ class Generator:
         pos = torch.from_numpy(np.concatenate([np.arange(n) for n in lens])).to(dev)
         seq = torch.from_numpy(np.repeat(np.arange(B), lens)).to(dev)
         cu = torch.from_numpy(np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)).to(dev)
+        trace: dict | None = {} if record_routing else None
         ctx = m.make_context(pos, cu)
         ctx.kv_cache = cache
+        ctx.routing_trace = trace
         cache.begin_prefill(seq, pos, torch.from_numpy(lens).to(dev))
         trunk = m.trunk_states(ids, ctx)
         cache.end_prefill()
@@ -220,9 +225,22 @@ class Generator:
             cache.begin_decode()
             dctx = ForwardContext(None, m.rope(cache.lengths), m.transport)
             dctx.kv_cache = cache
+            dctx.routing_trace = trace
             trunk = m.trunk_states(tok, dctx)
             cache.end_decode()
             logits = self._logits(trunk)
         n_cpu, tok_cpu, lp_cpu, stop_cpu = n_generated.cpu().numpy(), tokens.cpu().numpy(), logps.cpu().numpy(), stopped.cpu().numpy()
-        return [Generation(prompts[b], tok_cpu[b, :n_cpu[b]].copy(), lp_cpu[b, :n_cpu[b]].copy(), "stop" if stop_cpu[b] else "length")
+        outs = [Generation(prompts[b], tok_cpu[b, :n_cpu[b]].copy(), lp_cpu[b, :n_cpu[b]].copy(), "stop" if stop_cpu[b] else "length")
                 for b in range(B)]
+        if trace:
+            layers = sorted(trace)
+            # per layer: the prefill's [T, k] rows (packed by sequence), then one [B, k] row per decode step
+            prefill = np.stack([trace[li][0].cpu().numpy() for li in layers])                       # [L, T, k]
+            decode = np.stack([np.stack([t.cpu().numpy() for t in trace[li][1:]]) if len(trace[li]) > 1
+                               else np.zeros((0, B, prefill.shape[-1]), dtype=prefill.dtype) for li in layers])   # [L, steps, B, k]
+            offsets = np.concatenate([[0], np.cumsum(lens)])
+            for b, g in enumerate(outs):
+                fed = max(int(n_cpu[b]) - 1, 0)                      # generated tokens that were fed back (all but the last)
+                rows = np.concatenate([prefill[:, offsets[b]:offsets[b + 1]], decode[:, :fed, b]], axis=1)
+                g.extra["routing"], g.extra["routing_layers"] = rows.astype(np.int16), layers
+        return outs

@@ -275,6 +275,7 @@ class SparseMoE(nn.Module):
         self.lowp = ""                # block-scaled format of quantisation-aware training (banks and dispatched rows)
         self.load_counter = None      # (ExpertLoadCounter, layer index) when load metrics are on
         self.last_routing = None
+        self.layer_index = -1         # global index of the decoder layer this block belongs to (set by the layer)
 
     def forward(self, h, ctx):
         cfg = self.cfg
@@ -283,8 +284,24 @@ class SparseMoE(nn.Module):
         bias = self.selection_bias
         if self.e_score_correction_bias is not None:
             bias = self.e_score_correction_bias if bias is None else self.e_score_correction_bias + bias
-        if ctx.replay_topk is not None:
-            idx = ctx.replay_topk.pop(0)
+        forced, partial = None, False
+        if isinstance(ctx.replay_topk, dict):
+            partial = True
+            # routing replay keyed by layer (safe under recomputation): the sampler's expert choice per token, -1 where
+            # the sampler never routed the token - there this forward routes for itself
+            forced = ctx.replay_topk.get(self.layer_index)
+        elif ctx.replay_topk is not None:
+            forced = ctx.replay_topk.pop(0)
+        if forced is not None:
+            idx = forced.to(logits.device)
+            if partial:                   # merged on the device: no host read of "is anything missing"
+                with torch.no_grad():
+                    own, _ = (moe_ops.router_sigmoid_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob, bias, cfg.n_group,
+                                                          cfg.topk_group, cfg.routed_scaling_factor)
+                              if cfg.score_function == "sigmoid" else
+                              moe_ops.router_topk(logits.detach(), cfg.num_experts_per_tok, cfg.norm_topk_prob, bias))
+                idx = torch.where(idx < 0, own.to(idx.dtype), idx)
+            idx = idx.to(torch.int32)
             probs = torch.sigmoid(logits.float()) if cfg.score_function == "sigmoid" else torch.softmax(logits.float(), dim=-1)
             w = probs.gather(-1, idx.long())
             if cfg.norm_topk_prob:
@@ -300,6 +317,8 @@ class SparseMoE(nn.Module):
             counter.add(layer_index, idx)     # first pass only: a recomputation replays the same routing
         if ctx.record_routing is not None:
             ctx.record_routing.append((logits, idx))
+        if getattr(ctx, "routing_trace", None) is not None:
+            ctx.routing_trace.setdefault(self.layer_index, []).append(idx.detach())
         bank_gate_up, bank_down = self.experts_gate_up, self.experts_down
         if self.expert_lora is not None:
             bank_gate_up, bank_down = self.expert_lora.effective_banks(bank_gate_up, bank_down)
@@ -336,6 +355,7 @@ class DecoderLayer(nn.Module):
         if cfg.layer_is_moe(idx):
             # attention-only tensor parallelism for MoE layers: router and experts see this rank's token shard
             self.mlp = SparseMoE(cfg, dtype, device, n_local_experts, router_dtype, etp)
+            self.mlp.layer_index = idx
         else:
             self.mlp = DenseMLP(H, cfg.intermediate_size, dtype, device, tp_size)
         self.eps = cfg.rms_norm_eps

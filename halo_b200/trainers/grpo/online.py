@@ -52,7 +52,7 @@ def text_reward(tokenizer, composer) -> Callable:
 class OnPolicyRolloutSource:
     def __init__(self, model, prompts: Sequence, reward_fn: Callable, num_generations: int, sampling: SamplingParams,
                  prompts_per_round: int = 8, eos_token_id: int | None = None, seed: int = 0, max_prompt_length: int = 0,
-                 rounds: int = 0):
+                 rounds: int = 0, record_routing: bool = False):
         if not len(prompts):
             raise ValueError("on-policy rollouts need at least one prompt")
         self.generator = Generator(model, eos_token_id=eos_token_id)
@@ -60,6 +60,7 @@ class OnPolicyRolloutSource:
         self.g, self.sampling, self.per_round = num_generations, sampling, prompts_per_round
         self.seed, self.max_prompt, self.rounds = seed, max_prompt_length, rounds
         self.mean_reward = float("nan")
+        self.record_routing = record_routing and model.cfg.is_moe
 
     def _prompt(self, i: int):
         item = self.prompts[i % len(self.prompts)]
@@ -75,11 +76,12 @@ class OnPolicyRolloutSource:
         params = SamplingParams(self.sampling.max_new_tokens, self.sampling.temperature, self.sampling.top_k, self.sampling.top_p,
                                 self.sampling.stop_token_ids, self.seed * 1000003 + round_index)
         was_training = self.generator.model.training
-        outs = self.generator.generate(batch, params)
+        outs = self.generator.generate(batch, params, record_routing=self.record_routing)
         self.generator.model.train(was_training)
         rollouts = []
         for n, out in enumerate(outs):
             ids, task = picks[n // self.g]
-            rollouts.append(Rollout(ids, out.token_ids, out.logprobs, self.reward_fn(ids, out.token_ids, task)))
+            rollouts.append(Rollout(ids, out.token_ids, out.logprobs, self.reward_fn(ids, out.token_ids, task),
+                                    routing=out.extra.get("routing"), routing_layers=out.extra.get("routing_layers")))
         self.mean_reward = float(np.mean([r.reward for r in rollouts]))
         return rollouts

@@ -49,7 +49,8 @@ class RolloutPublisher:
                 self.store.set(key, END)
                 self.exhausted = True
                 continue
-            blob = [(r.prompt_ids, r.completion_ids, r.sampler_logprobs, r.reward) for r in rollouts]
+            blob = [(r.prompt_ids, r.completion_ids, r.sampler_logprobs, r.reward, r.completion_mask, r.routing, r.routing_layers)
+                    for r in rollouts]
             self.store.set(key, pickle.dumps({"version": version, "rollouts": blob, "mean_reward": self.sources[t].mean_reward}))
         self.next_round += 1
 
@@ -95,5 +96,5 @@ class StoreRolloutSource:
             return None
         msg = pickle.loads(blob)
         self.last_version, self.mean_reward = msg["version"], msg["mean_reward"]
-        return [Rollout(np.asarray(p), np.asarray(c), None if lp is None else np.asarray(lp, dtype=np.float32), float(r))
-                for p, c, lp, r in msg["rollouts"]]
+        return [Rollout(np.asarray(p), np.asarray(c), None if lp is None else np.asarray(lp, dtype=np.float32), float(r), mask, routing, layers)
+                for p, c, lp, r, mask, routing, layers in msg["rollouts"]]

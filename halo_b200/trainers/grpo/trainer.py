@@ -32,6 +32,8 @@ class Rollout:
     sampler_logprobs: np.ndarray | None   # per completion token; None = treat as on-policy
     reward: float
     completion_mask: np.ndarray | None = None   # 1 on tokens the policy produced, 0 on environment tokens in between; None = all 1
+    routing: np.ndarray | None = None           # [moe layers, prompt + completion - 1, top_k]: the sampler's experts per token
+    routing_layers: list | None = None          # the decoder-layer index of every row of ``routing``
 
 
 @dataclass
@@ -42,12 +44,14 @@ class GRPOBatch(PackedBatch):
     degenerate: torch.Tensor = None       # [T] bool: token belongs to a zero-spread group
     seq_lengths: torch.Tensor = None      # [n_rows] completion lengths
     attention_mask: torch.Tensor = None   # [T, T] bool under tree packing (prompts stored once per group)
+    replay_routing: dict = None           # {layer index: [T, top_k] int32, -1 = unknown}: the sampler's routing to replay
 
     def to(self, device, non_blocking: bool = True):
         b = PackedBatch.to(self, device, non_blocking)
         mv = lambda t: None if t is None else t.to(device, non_blocking=non_blocking)  # noqa: E731
         return GRPOBatch(b.input_ids, b.position_ids, b.labels, b.cu_seqlens, b.n_scored, mv(self.advantages),
-                         mv(self.old_logprobs), self.has_old, mv(self.degenerate), mv(self.seq_lengths), mv(self.attention_mask))
+                         mv(self.old_logprobs), self.has_old, mv(self.degenerate), mv(self.seq_lengths), mv(self.attention_mask),
+                         None if self.replay_routing is None else {k: mv(v) for k, v in self.replay_routing.items()})
 
 
 def build_grpo_batch(rollouts: list[Rollout], adv: torch.Tensor, degenerate: torch.Tensor) -> GRPOBatch:
@@ -70,8 +74,17 @@ def build_grpo_batch(rollouts: list[Rollout], adv: torch.Tensor, degenerate: tor
             # label at position t scores token t+1: completion token j sits at label index len(prompt) + j - 1
             p = len(r.prompt_ids)
             old[s + p - 1:s + p - 1 + len(r.completion_ids)] = torch.from_numpy(np.asarray(r.sampler_logprobs, np.float32))
+    replay = None
+    if all(r.routing is not None for r in rollouts):
+        layers, k = rollouts[0].routing_layers, rollouts[0].routing.shape[-1]
+        replay = {li: torch.full((T, k), -1, dtype=torch.int32) for li in layers}
+        for i, r in enumerate(rollouts):
+            s = int(base.cu_seqlens[i])
+            n = min(r.routing.shape[1], len(r.prompt_ids) + len(r.completion_ids))
+            for row, li in enumerate(layers):
+                replay[li][s:s + n] = torch.from_numpy(r.routing[row, :n].astype(np.int32))
     return GRPOBatch(base.input_ids, base.position_ids, base.labels, base.cu_seqlens, base.n_scored, a, old, has_old,
-                     deg, torch.tensor([len(r.completion_ids) for r in rollouts], dtype=torch.float32))
+                     deg, torch.tensor([len(r.completion_ids) for r in rollouts], dtype=torch.float32), None, replay)
 
 
 def build_grpo_tree_batch(rollouts: list[Rollout], adv: torch.Tensor, degenerate: torch.Tensor, group_size: int) -> GRPOBatch:
@@ -174,8 +187,9 @@ class GRPOTrainer(Trainer):
     def compute_loss(self, model, batch: GRPOBatch, normalizer):
         g = self.grpo
         ctx = None
-        if batch.attention_mask is not None:
-            ctx = model.make_context(batch.position_ids.reshape(-1), batch.cu_seqlens)
+        replay = batch.replay_routing if getattr(g, "routing_replay", False) else None
+        if batch.attention_mask is not None or replay is not None:
+            ctx = model.make_context(batch.position_ids.reshape(-1), batch.cu_seqlens, replay_topk=replay)
             ctx.attention_mask = batch.attention_mask
         logp, _ = model.token_logprobs(batch.input_ids, batch.position_ids, batch.cu_seqlens, batch.labels, ctx=ctx)
         mask = batch.labels.reshape(-1) != -100

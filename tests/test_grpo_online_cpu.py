@@ -147,3 +147,52 @@ def test_tree_packing_gives_the_flat_loss_and_gradients(tmp_path):
     assert abs(loss_flat - loss_tree) < 1e-5 and abs(loss_flat) > 1e-3
     for n in g_flat:
         assert torch.allclose(g_flat[n], g_tree[n], atol=1e-5, rtol=1e-3), n
+
+
+def test_routing_replay_trains_with_the_samplers_experts(tmp_path):
+    """The sampler records the experts of every token it processed; a trainer whose router has drifted still routes
+    those tokens as the sampler did (and routes the one unseen token of each row itself)."""
+    import dataclasses
+
+    from halo_b200.models.config import tiny_moe_config
+
+    cfg = dataclasses.replace(tiny_moe_config(), num_hidden_layers=2, vocab_size=64)
+    sampler = build_model(cfg, device="cpu", seed=0, gradient_checkpointing=False)
+    prompts = [np.array([1, 2, 3, 4, 5]), np.array([6, 7, 8])]
+    src = OnPolicyRolloutSource(sampler, prompts, token_match_reward(7), num_generations=2, sampling=SamplingParams(max_new_tokens=4),
+                                prompts_per_round=2, seed=1, record_routing=True)
+    rollouts = src(0)
+    r = rollouts[0]
+    assert r.routing.shape == (2, len(r.prompt_ids) + len(r.completion_ids) - 1, cfg.num_experts_per_tok) and r.routing_layers == [0, 1]
+    batch = build_grpo_batch(rollouts, torch.zeros(4), torch.zeros(4, dtype=torch.bool))
+    assert set(batch.replay_routing) == {0, 1} and int((batch.replay_routing[0] < 0).all(-1).sum()) == 4     # one unseen token per row
+    # the sampler's own forward over the packed rows picks the same experts as it did while sampling
+    records = []
+    ctx = sampler.make_context(batch.position_ids.reshape(-1), batch.cu_seqlens, record_routing=records)
+    with torch.no_grad():
+        sampler.hidden_states(batch.input_ids, batch.position_ids, batch.cu_seqlens, ctx)
+    for li in (0, 1):
+        known = (batch.replay_routing[li] >= 0).all(-1)
+        assert torch.equal(records[li][1][known].sort(-1).values, batch.replay_routing[li][known].sort(-1).values)
+    # a trainer with a different router: free routing differs, replayed routing is the sampler's
+    trainer_model = build_model(cfg, device="cpu", seed=0, gradient_checkpointing=True)
+    with torch.no_grad():
+        for layer in trainer_model.layers:
+            layer.mlp.gate.copy_(torch.randn(layer.mlp.gate.shape, generator=torch.Generator().manual_seed(5)))
+    free, forced = [], []
+    with torch.no_grad():
+        trainer_model.hidden_states(batch.input_ids, batch.position_ids, batch.cu_seqlens,
+                                    trainer_model.make_context(batch.position_ids.reshape(-1), batch.cu_seqlens, record_routing=free))
+        trainer_model.hidden_states(batch.input_ids, batch.position_ids, batch.cu_seqlens,
+                                    trainer_model.make_context(batch.position_ids.reshape(-1), batch.cu_seqlens, record_routing=forced,
+                                                               replay_topk=batch.replay_routing))
+    known = (batch.replay_routing[0] >= 0).all(-1)
+    assert not torch.equal(free[0][1][known], batch.replay_routing[0][known])
+    assert torch.equal(forced[0][1][known], batch.replay_routing[0][known])
+    assert torch.equal(forced[0][1][~known], free[0][1][~known])                       # unseen tokens route for themselves
+    # and a training step with replay (under recomputation, which runs every layer twice) goes through
+    args = TrainingArguments(output_dir=str(tmp_path / "run"), max_steps=1, optim="adamw_torch", logging_steps=1000)
+    t = GRPOTrainer(trainer_model, args, lambda i: rollouts if i == 0 else None, device=torch.device("cpu"),
+                    grpo_args=GRPOArguments(num_generations=2, max_completion_length=4, routing_replay=True))
+    t.train()
+    assert t.global_step == 1
