@@ -174,3 +174,31 @@ def test_benchmark_bands():
     for f in os.listdir(os.path.join(ROOT, "benchmarks", "baselines")):
         stored = band.load_band(f[:-5])
         assert stored["command"].endswith("--steps 3 --warmup 3") and stored["provenance"]["hardware"]
+
+
+def test_every_example_recipe_parses_for_its_method():
+    """Each YAML under ``examples/`` names its launch method in its first comment; its keys must be known to that
+    method's argument classes (a recipe that drifted from the code fails here, not on a GPU box)."""
+    import importlib
+
+    from halo_b200 import cli
+    from halo_b200.configs.arguments import DataArguments, ModelArguments, ParallelismArguments, TrainingArguments
+    from halo_b200.configs.parser import ArgumentParser
+
+    method_args = {"sft": "SFTArguments", "dpo": "PreferenceArguments", "kto": "PreferenceArguments", "smpo": "PreferenceArguments",
+                   "reward": "RewardArguments",
+                   "classification": "RewardArguments", "embedding": "EmbeddingArguments", "distill": "DistillationArguments",
+                   "grpo": "GRPOArguments"}
+    arguments = importlib.import_module("halo_b200.configs.arguments")
+    seen = set()
+    for name in sorted(os.listdir(os.path.join(ROOT, "examples"))):
+        if not name.endswith(".yaml"):
+            continue
+        path = os.path.join(ROOT, "examples", name)
+        method = next((m for m in sorted(method_args, key=len, reverse=True) if name.startswith(m) or f"launch {m} " in read(path)), None)
+        assert method in cli.METHODS, f"{name}: cannot tell its method"
+        parser = ArgumentParser(ModelArguments, DataArguments, TrainingArguments, ParallelismArguments, getattr(arguments, method_args[method]))
+        parsed = parser.parse([path])
+        assert parsed[0].model_preset == "tiny-moe", name
+        seen.add(method)
+    assert seen == set(method_args)
