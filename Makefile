@@ -2,7 +2,7 @@
 PY ?= python
 NPROC ?= 8
 
-.PHONY: build test-cpu test-gpu test-multigpu bench bench-multi bench-band kernel-bench train clean
+.PHONY: build test-cpu test-gpu test-multigpu bench bench-multi bench-band verify-records kernel-bench train clean
 
 build:            ## compile halo_b200/lib/libhalo_b200.so for sm_100a
 	$(PY) -c "import __graft_entry__ as g; g.build()"
@@ -24,6 +24,10 @@ bench-multi: build
 
 bench-band: build   ## hold the one-GPU benchmark to its stored band (BAND=<name> picks another; see benchmarks/band.py --list)
 	$(PY) bench.py --steps 3 --warmup 3 | $(PY) benchmarks/band.py $(or $(BAND),moe30b_ep1_n1)
+
+verify-records:   ## numerics unchanged by a change: make verify-records BASE=<records.json written at the base commit>
+	$(PY) benchmarks/records.py record /tmp/halo_b200_head_records.json
+	$(PY) benchmarks/records.py compare $(BASE) /tmp/halo_b200_head_records.json
 
 kernel-bench: build
 	$(PY) benchmarks/kernels.py

@@ -202,3 +202,21 @@ def test_every_example_recipe_parses_for_its_method():
         assert parsed[0].model_preset == "tiny-moe", name
         seen.add(method)
     assert seen == set(method_args)
+
+
+def test_tensor_records_compare():
+    import copy
+    import sys
+
+    sys.path.insert(0, os.path.join(ROOT, "benchmarks"))
+    import records
+
+    step = {"loss": 1.25, "grad_norm": 2.0, "grads": {"w": ("abc", 3.0)}, "weights": {"w": ("def", 4.0)}}
+    base = {"workloads": {"single": [[step]], "ep2": [[step], [step]]}}
+    assert records.compare(base, copy.deepcopy(base)) == []
+    moved = copy.deepcopy(base)
+    moved["workloads"]["ep2"][1][0]["grads"]["w"] = ("zzz", 3.0000001)
+    assert len(records.compare(base, moved)) == 1 and "ep2 rank 1 step 0" in records.compare(base, moved)[0]
+    assert records.compare(base, moved, tolerance=1e-6) == []                      # within tolerance on the norms
+    del moved["workloads"]["single"]
+    assert any("one record only" in d for d in records.compare(base, moved))
