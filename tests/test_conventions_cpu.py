@@ -212,7 +212,7 @@ def test_tensor_records_compare():
     import records
 
     step = {"loss": 1.25, "grad_norm": 2.0, "grads": {"w": ("abc", 3.0)}, "weights": {"w": ("def", 4.0)}}
-    base = {"workloads": {"single": [[step]], "ep2": [[step], [step]]}}
+    base = {"workloads": {"single": [[copy.deepcopy(step)]], "ep2": [[copy.deepcopy(step)], [copy.deepcopy(step)]]}}
     assert records.compare(base, copy.deepcopy(base)) == []
     moved = copy.deepcopy(base)
     moved["workloads"]["ep2"][1][0]["grads"]["w"] = ("zzz", 3.0000001)
