@@ -29,6 +29,7 @@ TOOLS = {
     "patch-vocab": "halo_b200.checkpoint.tools.patch_vocab",
     "kernel-bench": "benchmarks.kernels",
     "nvlink-health": "halo_b200.diagnostics.nvlink_health",
+    "trace-report": "halo_b200.diagnostics.trace_report",
     "prepare-dataset": "halo_b200.data.preprocessed",
     "generate": "halo_b200.entrypoints.generation",
     "evaluate": "halo_b200.entrypoints.evaluation",

@@ -100,3 +100,26 @@ def test_selection_bias_changes_ranking_not_weights():
     assert bool((idx1 == 7).any(-1).all())
     probs = torch.softmax(logits, -1)
     assert torch.allclose(w1, probs.gather(-1, idx1.long()))      # weights are the unbiased probabilities
+
+
+def test_trace_report_groups_kernels_and_measures_overlap(tmp_path):
+    import gzip
+    import json
+
+    from halo_b200.diagnostics import trace_report
+
+    def ev(name, ts, dur, tid=7, cat="kernel"):
+        return {"ph": "X", "cat": cat, "name": name, "ts": ts, "dur": dur, "pid": 0, "tid": tid}
+
+    events = [ev("gemm_bf16_kernel<0,0>", 0, 100), ev("gemm_bf16_kernel<0,0>", 100, 100), ev("attn_fwd_kernel", 200, 50),
+              ev("ncclDevKernel_AllReduce", 150, 100, tid=9), ev("rmsnorm_fwd_kernel<1,32>", 300, 10),
+              {"ph": "X", "cat": "cpu_op", "name": "aten::mm", "ts": 0, "dur": 500, "pid": 1, "tid": 1}]
+    path = tmp_path / "trace.json.gz"
+    with gzip.open(path, "wt") as f:
+        json.dump({"traceEvents": events}, f)
+    rep = trace_report.summarise(trace_report.load_events(str(path)))
+    assert rep["launches"] == 5 and rep["device_time_us"] == 360.0
+    assert rep["kernels"][0]["name"].startswith("gemm_bf16") and rep["kernels"][0]["launches"] == 2
+    assert rep["families"] == {"gemm": 200.0, "collectives": 100.0, "attention": 50.0, "element-wise": 10.0}
+    assert rep["span_us"] == 310.0 and rep["busy_us"] == 260.0 and rep["overlap_us"] == 100.0      # the all-reduce ran beside compute
+    assert trace_report.main([str(path), "--top", "3"]) == 0
