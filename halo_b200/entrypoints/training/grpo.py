@@ -1,6 +1,13 @@
-"""GRPO entry point. Rollouts come from a JSONL file of scored generations (offline GRPO) or from the
-synthetic generator; the trained weights are pushed to a resident rollout copy after each step when
-``rollout_backend: resident_copy`` names rollout GPUs."""
+"""GRPO entry point. Where a round's rollouts come from:
+
+* ``rollout_gpus: N`` with a reward configured - the last ``N`` ranks hold a serving copy of the policy, receive the
+  weights after every optimizer step, sample the trainers' rounds from it and publish them through the rendezvous
+  store (``rollout_prefetch`` rounds ahead);
+* ``rollout_backend: in_process`` - the trainer's own weights sample every round;
+* ``environment_type`` - either of the above plays environment episodes (multi-turn, tools) instead of single turns;
+* ``dataset_path`` of scored generations - offline GRPO; nothing - synthetic rollouts of the benchmark's shape.
+
+With ``grpo_beta > 0`` a frozen copy of the starting policy anchors the KL term."""
 
 import json
 
