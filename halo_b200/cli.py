@@ -30,6 +30,7 @@ TOOLS = {
     "kernel-bench": "benchmarks.kernels",
     "nvlink-health": "halo_b200.diagnostics.nvlink_health",
     "trace-report": "halo_b200.diagnostics.trace_report",
+    "convert-recipe": "halo_b200.configs.convert_recipe",
     "prepare-dataset": "halo_b200.data.preprocessed",
     "generate": "halo_b200.entrypoints.generation",
     "evaluate": "halo_b200.entrypoints.evaluation",

@@ -166,3 +166,44 @@ def test_freeze_patterns_preflight_and_collators(tmp_path):
     pb = collators.padded(docs, pad_token_id=9, pad_to_multiple_of=4)
     assert pb["input_ids"].shape == (2, 8) and pb["attention_mask"].sum().item() == 8 and pb["input_ids"][1, 3].item() == 9
     assert pb["labels"][0, :4].tolist() == [1, 2, 3, 4] and pb["labels"][0, 4].item() == -100
+
+
+def test_reference_recipe_converts_and_parses(tmp_path):
+    import dataclasses
+
+    import yaml
+
+    from halo_b200.configs import arguments as A
+    from halo_b200.configs import convert_recipe
+    from halo_b200.configs.parser import ArgumentParser
+
+    fields = set()
+    for name in dir(A):
+        c = getattr(A, name)
+        if dataclasses.is_dataclass(c) and isinstance(c, type):
+            fields |= {f.name for f in dataclasses.fields(c)}
+    assert not (convert_recipe.KEPT - fields) and not ({v[0] for v in convert_recipe.RENAMED.values()} - fields)
+
+    data = tmp_path / "train.jsonl"
+    data.write_text('{"messages": []}\n')
+    recipe = {"model_name_or_path": "/models/qwen3-30b-a3b", "dataset": [str(data)], "conversation_field": "messages",
+              "assistant_message_template": "<|im_start|>assistant\n", "use_peft": True, "lora_r": 64, "lora_alpha": 128,
+              "lora_target_modules": ["q_proj", "v_proj"], "per_device_train_batch_size": 4, "gradient_accumulation_steps": 4,
+              "gradient_checkpointing_kwargs": {"use_reentrant": False}, "learning_rate": 1e-4, "lr_scheduler_type": "cosine",
+              "warmup_steps": 32, "max_length": 4096, "packing": True, "output_dir": "checkpoints/x", "eval_strategy": "steps",
+              "eval_steps": 500, "save_total_limit": 3, "save_only_model": True, "logging_steps": 1, "logging_first_step": True,
+              "report_to": "none", "dataloader_num_workers": 4, "attn_implementation": "flash_attention_4", "expert_parallel_size": 8,
+              "moe_balancing": "bias_update", "fp32_grad_reduce": True}
+    src, dst = tmp_path / "ref.yaml", tmp_path / "ours.yaml"
+    src.write_text(yaml.safe_dump(recipe))
+    assert convert_recipe.main([str(src), str(dst)]) == 0
+    text = dst.read_text()
+    assert "launch sft" in text and "dropped attn_implementation" in text and "dataloader_num_workers -> num_proc" in text
+    parsed = ArgumentParser(A.ModelArguments, A.DataArguments, A.TrainingArguments, A.ParallelismArguments, A.SFTArguments).parse([str(dst)])
+    assert parsed[0].lora_r == 64 and parsed[1].dataset_path == str(data) and parsed[1].completion_only_loss and parsed[1].num_proc == 4
+    assert parsed[3].expert_parallel_size == 8
+    src.write_text(yaml.safe_dump({**recipe, "use_vllm": True, "load_in_4bit": True, "num_generations": 8}))
+    with pytest.raises(ValueError, match="load_in_4bit"):
+        convert_recipe.main([str(src), str(dst)])
+    assert convert_recipe.main([str(src), str(dst), "--lenient"]) == 0 and "NOT CONVERTED load_in_4bit" in dst.read_text()
+    assert "launch grpo" in dst.read_text() and "dropped use_vllm: no generation server: add rollout_gpus" in dst.read_text()
