@@ -22,13 +22,17 @@ from .streams import masked_softmax_backward
 SCORES_PER_TILE = 1 << 26
 
 
-def masked_attention_reference(q, k, v, allowed, scale=None):
+def masked_attention_reference(q, k, v, allowed, scale=None, sinks=None):
     """``q [Q, Hq, D]``, ``k`` / ``v [K, Hkv, D]``, ``allowed [Q, K]`` bool -> ``[Q, Hq, D]`` (plain autograd form)."""
     Hq, Hkv, D = q.shape[1], k.shape[1], q.shape[2]
     kk, vv = (t.repeat_interleave(Hq // Hkv, dim=1).float() for t in (k, v))
     scores = torch.einsum("qhd,khd->hqk", q.float(), kk) * (D ** -0.5 if scale is None else scale)
     scores = scores.masked_fill(~allowed[None], float("-inf"))
-    probs = torch.nan_to_num(torch.softmax(scores, dim=-1), nan=0.0)
+    if sinks is not None:
+        joined = torch.cat([scores, sinks.float()[:, None, None].expand(-1, scores.shape[1], 1)], dim=-1)
+        probs = torch.softmax(joined, dim=-1)[..., :-1]
+    else:
+        probs = torch.nan_to_num(torch.softmax(scores, dim=-1), nan=0.0)
     return torch.einsum("hqk,khd->qhd", probs, vv).to(q.dtype)
 
 
@@ -39,7 +43,7 @@ def _tiles(n_queries: int, n_keys: int, heads: int, budget: int):
 
 class _MaskedAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, allowed, scale, budget):
+    def forward(ctx, q, k, v, allowed, scale, budget, sinks=None):
         Q, Hq, D = q.shape
         K, Hkv = k.shape[0], k.shape[1]
         G = Hq // Hkv
@@ -52,19 +56,22 @@ class _MaskedAttention(torch.autograd.Function):
             scores = torch.bmm(qt.float(), kh.float().transpose(1, 2)).reshape(Hq, hi - lo, K) * scale
             scores = scores.masked_fill(~allowed[lo:hi][None], float("-inf"))
             tile_lse = torch.logsumexp(scores, dim=-1)
+            if sinks is not None:
+                # an attention sink: one learned logit per head joins every softmax (and takes its share of the mass)
+                tile_lse = torch.logaddexp(tile_lse, sinks.float()[:, None].expand_as(tile_lse))
             tile_lse = torch.where(torch.isinf(tile_lse), torch.zeros_like(tile_lse), tile_lse)     # empty rows: exp(-inf - 0) = 0
             probs = torch.exp(scores - tile_lse[..., None])
             o = torch.bmm(probs.reshape(Hkv, G * (hi - lo), K), vh.float()).reshape(Hq, hi - lo, D)
             out[lo:hi] = o.permute(1, 0, 2).to(q.dtype)
             lse[:, lo:hi] = tile_lse
-        ctx.save_for_backward(q, k, v, allowed, out, lse)
-        ctx.meta = (scale, budget)
+        ctx.save_for_backward(q, k, v, allowed, out, lse, sinks if sinks is not None else q.new_zeros(0))
+        ctx.meta = (scale, budget, sinks is not None)
         return out
 
     @staticmethod
     def backward(ctx, d_out):
-        q, k, v, allowed, out, lse = ctx.saved_tensors
-        scale, budget = ctx.meta
+        q, k, v, allowed, out, lse, sinks = ctx.saved_tensors
+        scale, budget, has_sinks = ctx.meta
         Q, Hq, D = q.shape
         K, Hkv = k.shape[0], k.shape[1]
         G = Hq // Hkv
@@ -85,18 +92,23 @@ class _MaskedAttention(torch.autograd.Function):
             dv += torch.bmm(probs.transpose(1, 2), gt)
             dk += torch.bmm(d_scores.transpose(1, 2), qt)
             dq[lo:hi] = torch.bmm(d_scores, kh).reshape(Hq, n, D).permute(1, 0, 2).to(q.dtype)
-        return dq, dk.permute(1, 0, 2).to(k.dtype), dv.permute(1, 0, 2).to(v.dtype), None, None, None
+        dsinks = None
+        if has_sinks:
+            # the sink's probability is exp(sink - lse) and its "value" is zero: d sink = -sum_q p_sink * delta
+            dsinks = -(torch.exp(sinks.float()[:, None] - lse) * delta).sum(-1).to(sinks.dtype)
+        return dq, dk.permute(1, 0, 2).to(k.dtype), dv.permute(1, 0, 2).to(v.dtype), None, None, None, dsinks
 
 
 def masked_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, allowed: torch.Tensor, scale: float | None = None,
-                     scores_per_tile: int = SCORES_PER_TILE) -> torch.Tensor:
-    """``q [Q, Hq, D]``, ``k`` / ``v [K, Hkv, D]``, ``allowed [Q, K]`` bool -> ``[Q, Hq, D]``."""
+                     scores_per_tile: int = SCORES_PER_TILE, sinks: torch.Tensor | None = None) -> torch.Tensor:
+    """``q [Q, Hq, D]``, ``k`` / ``v [K, Hkv, D]``, ``allowed [Q, K]`` bool -> ``[Q, Hq, D]``. ``sinks [Hq]``: one learned
+    logit per head that joins every row's softmax without a value (attention sinks)."""
     if q.shape[1] % k.shape[1]:
         raise ValueError(f"{q.shape[1]} query heads do not group over {k.shape[1]} key/value heads")
     if tuple(allowed.shape) != (q.shape[0], k.shape[0]):
         raise ValueError(f"mask {tuple(allowed.shape)} where queries and keys give {(q.shape[0], k.shape[0])}")
     scale = q.shape[2] ** -0.5 if scale is None else scale
-    return _MaskedAttention.apply(q, k, v, allowed.bool(), float(scale), scores_per_tile)
+    return _MaskedAttention.apply(q, k, v, allowed.bool(), float(scale), scores_per_tile, sinks)
 
 
 def tree_mask(parent: torch.Tensor) -> torch.Tensor:

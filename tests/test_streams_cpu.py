@@ -141,3 +141,10 @@ def test_masked_attention_closed_form_backward(kind):
     w = torch.randn(got.shape, generator=g)
     for a, b in zip(torch.autograd.grad((got * w).sum(), (q, k, v)), torch.autograd.grad((want * w).sum(), (q, k, v))):
         assert torch.allclose(a, b, atol=1e-5)
+    # with attention sinks: one learned logit per head joins every softmax
+    sinks = torch.randn(Hq, generator=g, requires_grad=True)
+    got = masked_attention(q, k, v, allowed, scores_per_tile=Hq * Q * 8, sinks=sinks)
+    want = masked_attention_reference(q, k, v, allowed, sinks=sinks)
+    assert torch.allclose(got, want, atol=1e-5) and not torch.allclose(got, masked_attention(q, k, v, allowed), atol=1e-3)
+    for a, b in zip(torch.autograd.grad((got * w).sum(), (q, k, v, sinks)), torch.autograd.grad((want * w).sum(), (q, k, v, sinks))):
+        assert torch.allclose(a, b, atol=1e-5)
