@@ -24,6 +24,36 @@ MOE_HUB_NAMES = {
     "glm4_moe": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "olmoe": ("mlp", "gate_proj", "up_proj", "down_proj"),
 }
+# gpt-oss stores each bank as ONE tensor, transposed, with gate and up columns interleaved (``INTERLEAVED_GLU``)
+WHOLE_BANK_FAMILIES = ("gpt_oss",)
+
+
+def _interleave(gate_then_up: torch.Tensor, dim: int) -> torch.Tensor:
+    """``[.., 2F, ..]`` gate rows then up rows -> gate and up alternating along ``dim``."""
+    g, u = gate_then_up.chunk(2, dim=dim)
+    return torch.stack([g, u], dim=dim + 1).flatten(dim, dim + 1)
+
+
+def _deinterleave(alternating: torch.Tensor, dim: int) -> torch.Tensor:
+    index = [slice(None)] * alternating.dim()
+    even, odd = list(index), list(index)
+    even[dim], odd[dim] = slice(0, None, 2), slice(1, None, 2)
+    return torch.cat([alternating[tuple(even)], alternating[tuple(odd)]], dim=dim)
+
+
+def whole_bank_source(name: str, cfg, first_layer: int = 0):
+    """For a parameter that the hub stores as one transformed tensor: ``(hub name, function hub tensor -> runtime
+    tensor)``; ``None`` for every other parameter."""
+    m = _LAYER.match(name)
+    if not m or getattr(cfg, "family", "") not in WHOLE_BANK_FAMILIES:
+        return None
+    pre = f"model.layers.{int(m.group(1)) + first_layer}.mlp.experts."
+    return {
+        "mlp.experts_gate_up": (pre + "gate_up_proj", lambda t: _deinterleave(t.transpose(1, 2), 1).contiguous()),
+        "mlp.experts_gate_up_bias": (pre + "gate_up_proj_bias", lambda t: _deinterleave(t, 1).contiguous()),
+        "mlp.experts_down": (pre + "down_proj", lambda t: t.transpose(1, 2).contiguous()),
+        "mlp.experts_down_bias": (pre + "down_proj_bias", lambda t: t),
+    }.get(m.group(2))
 # how a family names its always-on shared feed-forward block
 SHARED_EXPERT_NAMES = {"glm4_moe": "shared_experts"}
 
@@ -68,6 +98,10 @@ def runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, e
         return {pre + "self_attn.q_proj.bias": q, pre + "self_attn.k_proj.bias": k, pre + "self_attn.v_proj.bias": v}
     if rest == "self_attn.o_proj":
         return {pre + "self_attn.o_proj.weight": tensor}
+    if rest == "self_attn.o_bias":
+        return {pre + "self_attn.o_proj.bias": tensor}
+    if rest == "self_attn.sinks":
+        return {pre + "self_attn.sinks": tensor}
     if rest in ("self_attn.q_norm", "self_attn.k_norm"):
         return {pre + rest + ".weight": tensor}
     if rest == "mlp.gate_up_proj":
@@ -75,6 +109,17 @@ def runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, e
         return {pre + "mlp.gate_proj.weight": g, pre + "mlp.up_proj.weight": u}
     if rest == "mlp.down_proj":
         return {pre + "mlp.down_proj.weight": tensor}
+    if getattr(cfg, "family", "") in WHOLE_BANK_FAMILIES and rest.startswith("mlp."):
+        if expert_offset or (rest.startswith("mlp.experts_") and tensor.shape[0] != cfg.num_experts):
+            raise ValueError("this family's banks are stored whole: a shard of the experts has no hub form")
+        whole = {"mlp.gate": ("router.weight", lambda t: t), "mlp.gate_bias": ("router.bias", lambda t: t),
+                 "mlp.experts_gate_up": ("experts.gate_up_proj", lambda t: _interleave(t, 1).transpose(1, 2)),
+                 "mlp.experts_gate_up_bias": ("experts.gate_up_proj_bias", lambda t: _interleave(t, 1)),
+                 "mlp.experts_down": ("experts.down_proj", lambda t: t.transpose(1, 2)),
+                 "mlp.experts_down_bias": ("experts.down_proj_bias", lambda t: t)}
+        if rest in whole:
+            hub, to_hub = whole[rest]
+            return {pre + "mlp." + hub: to_hub(tensor)}
     block, gate_name, up_name, down_name = MOE_HUB_NAMES.get(getattr(cfg, "family", ""), MOE_HUB_NAMES["qwen3_moe"])
     if rest == "mlp.gate":
         return {pre + f"{block}.gate.weight": tensor}

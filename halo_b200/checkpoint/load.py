@@ -12,7 +12,7 @@ import os
 import torch
 from safetensors import safe_open
 
-from .hub_layout import hub_sources
+from .hub_layout import hub_sources, whole_bank_source
 from .writing import INDEX_NAME, SINGLE_NAME
 
 
@@ -67,6 +67,19 @@ def load_model_weights(model, directory: str, strict: bool = True) -> dict:
             # rank's slice
             n, got = _load_sliced(index, name, p, cfg, first_layer, offset, tp_kind, tp, etp_kind, etp, missing)
             loaded += got
+            continue
+        whole = whole_bank_source(name, cfg, first_layer)
+        if whole is not None:
+            # stored as one transformed tensor (transposed, gate / up interleaved): undone on the host
+            hub, to_runtime = whole
+            if hub not in index:
+                missing.append(hub)
+                continue
+            t = to_runtime(index.get(hub))
+            if tuple(t.shape) != tuple(p.shape):
+                raise ValueError(f"{hub}: checkpoint shape {tuple(t.shape)} does not fit {tuple(p.shape)}")
+            p.copy_(t.to(p.dtype))
+            loaded += 1
             continue
         for hub, (e, lo, hi) in hub_sources(name, tuple(p.shape), cfg, first_layer, offset):
             if hub not in index:

@@ -32,6 +32,8 @@ class ModelArguments:
     lora_target_modules: list[str] | str | None = None   # hub projection names, "experts.<name>" for routed experts, or "all-linear"
     adapter_path: str = ""                  # adapters to continue from (a directory holding adapter_model.safetensors)
     merge_adapters_on_save: bool = False    # save full weights with the adapters folded in instead of the adapters alone
+    reset_sinks: bool = True                # gpt-oss: neutralize the attention sinks for fine-tuning; false keeps them live and frozen
+    train_sinks: bool = False               # gpt-oss: train the live sinks (needs reset_sinks: false and full fine-tuning)
 
     def lora_spec(self):
         from halo_b200.peft.lora import LoraSpec
@@ -44,6 +46,10 @@ class ModelArguments:
     def __post_init__(self):
         if self.use_peft and (self.freeze_patterns or self.train_only_patterns):
             raise ConfigError("use_peft freezes the base weights itself: drop freeze_patterns / train_only_patterns")
+        if self.train_sinks and self.reset_sinks:
+            raise ConfigError("train_sinks: true contradicts reset_sinks: true - set reset_sinks: false alongside train_sinks")
+        if self.train_sinks and self.use_peft:
+            raise ConfigError("train_sinks needs full fine-tuning: with adapters keep the sinks live and frozen")
         if not self.use_peft and (self.adapter_path or self.merge_adapters_on_save):
             raise ConfigError("adapter_path / merge_adapters_on_save need use_peft: true")
         if not self.model_name_or_path and not self.model_preset:

@@ -28,6 +28,7 @@ KEPT = {
     "trust_remote_code", "optim", "seed", "routing_replay", "mtp_loss_weight", "environment_type", "max_grad_norm", "adam_beta1",
     "adam_beta2", "adam_epsilon", "router_aux_loss_coef", "resume_from_checkpoint", "gradient_checkpointing_plan", "temperature",
     "rollout_backend", "save_sharded_ep", "label_smoothing", "center_rewards_coefficient", "num_labels", "text_field",
+    "reset_sinks", "train_sinks",
 }
 # renamed: reference key -> (our key, optional value transform)
 RENAMED = {
@@ -92,7 +93,6 @@ UNSUPPORTED = {
     "load_in_4bit": "4-bit base weights (QLoRA) are not built",
     "use_bnb_nested_quant": "4-bit base weights (QLoRA) are not built",
     "images_field": "vision-language rows are not built",
-    "reset_sinks": "attention sinks (gpt-oss) are not built",
     "lora_modules_to_save": "adapters are saved alone or merged; extra full modules beside them are not built",
     "pooling_mode": "embeddings are the last token's hidden state",
 }

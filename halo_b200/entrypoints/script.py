@@ -158,6 +158,12 @@ def load_policy_model(model_args, pc, device, runtime, gradient_checkpointing=Tr
     from halo_b200.models.attention_selection import describe
 
     log.info(describe(model.cfg, device, dtype))
+    if model.cfg.attention_sinks:
+        from halo_b200.models.attention_sinks import apply_sinks_policy, policy_from_flags
+
+        policy = policy_from_flags(getattr(model_args, "reset_sinks", True), getattr(model_args, "train_sinks", False))
+        n = apply_sinks_policy(model, policy, pretrained=not model_args.init_from_scratch)
+        log.info("attention sinks: %d tensors, policy %s", n, model.sinks_policy)
     if getattr(model_args, "lowp_format", ""):
         from halo_b200.models.qwen3 import apply_lowp_compute
 

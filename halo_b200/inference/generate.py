@@ -81,13 +81,15 @@ class KVCache:
         self.v[li][self._rows, self._cols] = v.reshape(-1, Hkv, D)
         return li
 
-    def attend(self, li: int, q: torch.Tensor, n_heads: int, scale: float | None = None) -> torch.Tensor:
+    def attend(self, li: int, q: torch.Tensor, n_heads: int, scale: float | None = None, window: int = 0,
+               sinks: torch.Tensor | None = None) -> torch.Tensor:
         """One query per sequence ``[B, heads * head_dim]`` against keys ``0 .. lengths[b]`` (the token just written
-        included)."""
+        included); ``window`` limits it to the last ``window`` of them and ``sinks [heads]`` adds one value-less logit
+        per head to the softmax - both run as tensor operations."""
         B = q.shape[0]
         Hkv, D = self.k.shape[-2:]
         G = n_heads // Hkv
-        if q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128) and G <= 16:
+        if q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128) and G <= 16 and not window and sinks is None:
             # the decode kernel streams the cache once and reads the lengths on the device (no host synchronisation)
             from halo_b200.ops import _lib
 
@@ -104,8 +106,15 @@ class KVCache:
         qh = q.reshape(B, Hkv, G, D).float()
         scores = torch.einsum("bhgd,bshd->bhgs", qh, k.float()) * (scale if scale is not None else D ** -0.5)
         visible = torch.arange(upto, device=q.device)[None, :] <= self._cols[:, None]        # [B, S]
+        if window:
+            visible = visible & (torch.arange(upto, device=q.device)[None, :] > self._cols[:, None] - window)
         scores = scores.masked_fill(~visible[:, None, None, :], float("-inf"))
-        out = torch.einsum("bhgs,bshd->bhgd", torch.softmax(scores, dim=-1), v.float())
+        if sinks is not None:
+            sink = sinks.float().reshape(1, Hkv, G, 1).expand(B, -1, -1, -1)
+            probs = torch.softmax(torch.cat([scores, sink], dim=-1), dim=-1)[..., :-1]
+        else:
+            probs = torch.softmax(scores, dim=-1)
+        out = torch.einsum("bhgs,bshd->bhgd", probs, v.float())
         return out.reshape(B, n_heads * D).to(q.dtype)
 
 
@@ -121,7 +130,12 @@ def cached_attention(attn, h, ctx):
     q, k = qk_norm_rope(qkv, attn.q_norm, attn.k_norm, ctx.rope, Hq, Hkv, cfg.rms_norm_eps, cfg.use_qk_norm)
     v = qkv[:, (Hq + Hkv) * D:]
     li = cache.write(k, v)
-    if cache.mode == "prefill":
+    special = attn.window or attn.sinks is not None
+    if special and cache.mode == "prefill":
+        o = attn.masked_core(q, k, v, ctx)
+    elif special:
+        o = cache.attend(li, q, Hq, window=attn.window, sinks=attn.sinks)
+    elif cache.mode == "prefill":
         if q.is_cuda and D != 128:
             o = attn_ops.attention_reference(q, k, v, ctx.plan.cu_seqlens, Hq, Hkv)
         else:

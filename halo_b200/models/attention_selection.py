@@ -4,8 +4,8 @@
 * ``flash``     - the sm_100a flash kernels: bf16 on CUDA, head_dim 128, causal attention inside packed documents,
                   grouped-query heads; deterministic forward and backward (no atomics), so a determinism request
                   changes nothing.
-* ``masked``    - the masked-attention op (query tiles under an explicit ``[T, T]`` mask): sliding windows and tree
-                  packing; element-wise half on the masked-softmax kernel, products on library GEMMs.
+* ``masked``    - the masked-attention op (query tiles under an explicit ``[T, T]`` mask): sliding windows, attention
+                  sinks and tree packing; element-wise half on the masked-softmax kernel, products on library GEMMs.
 * ``reference`` - tensor ops: CPU runs, fp32 models, head dims the kernels are not built for.
 """
 
@@ -16,8 +16,11 @@ import torch
 
 def attention_path(cfg, device, dtype, tree_packing: bool = False) -> tuple[str, str]:
     device = torch.device(device)
+    if getattr(cfg, "attention_sinks", False):
+        return "masked", "attention sinks: the flash kernel's softmax has no extra logit"
     if cfg.sliding_window:
-        return "masked", f"sliding_window={cfg.sliding_window}: the flash kernel has no window"
+        mixed = " on the layers named sliding_attention" if getattr(cfg, "layer_types", None) else ""
+        return "masked", f"sliding_window={cfg.sliding_window}{mixed}: the flash kernel has no window"
     if tree_packing:
         return "masked", "tree packing: branches attend a shared trunk"
     if device.type != "cuda":

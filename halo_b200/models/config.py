@@ -30,6 +30,9 @@ FAMILIES = {
     # one RMSNorm over the whole q (and k) projection instead of one per head; top-k weights not renormalised
     "olmoe": dict(architecture="OlmoeForCausalLM", moe=True, qk_norm=True, bias_key=True, bias_default=False, has_window=False),
     "glm4_moe": dict(architecture="Glm4MoeForCausalLM", moe=True, qk_norm=True, bias_key=True, bias_default=False, has_window=False),
+    # a learned sink logit per head, windowed and full layers in turn, biases on every projection and on the experts,
+    # a clamped GLU in the experts, a biased router that takes the softmax of the top-k logits
+    "gpt_oss": dict(architecture="GptOssForCausalLM", moe=True, qk_norm=False, bias_key=True, bias_default=True, has_window=True),
 }
 
 
@@ -62,6 +65,13 @@ class ModelConfig:
     topk_group: int = 1
     routed_scaling_factor: float = 1.0
     sliding_window: int = 0                # > 0: every query sees only its last ``sliding_window`` keys (Mistral-style)
+    layer_types: list[str] | None = None   # per layer "sliding_attention" | "full_attention"; None = the window on every layer
+    attention_sinks: bool = False          # one learned logit per head joins every softmax (gpt-oss)
+    output_bias: bool = False              # bias on the attention output projection too (gpt-oss)
+    router_logit_bias: bool = False        # a trained bias on the router's logits (gpt-oss), unlike the selection bias
+    expert_bias: bool = False              # per-expert bias vectors on both expert projections
+    expert_activation: str = "swiglu"      # "swiglu" | "clamped_glu": gate * sigmoid(1.702 gate) * (up + 1), both clamped
+    glu_limit: float = 7.0
     rope_scaling: dict | None = None       # Hugging Face ``rope_scaling`` / ``rope_parameters`` entry, None = plain
     num_nextn_predict_layers: int = 0      # 1 = a multi-token-prediction head trained beside the next-token loss
     mtp_loss_weight: float = 0.3
@@ -93,11 +103,13 @@ class ModelConfig:
         H, D = self.hidden_size, self.head_dim
         norm_width = (self.num_attention_heads + self.num_key_value_heads) * D if self.qk_norm_whole_width else 2 * D
         attn = (H * self.qkv_dim + self.num_attention_heads * D * H + (norm_width if self.use_qk_norm else 0) + 2 * H
-                + (self.qkv_dim if self.attention_bias else 0))
+                + (self.qkv_dim if self.attention_bias else 0) + (H if self.output_bias else 0)
+                + (self.num_attention_heads if self.attention_sinks else 0))
         dense_mlp = 3 * H * self.intermediate_size
-        expert = 3 * H * self.moe_intermediate_size
+        expert = 3 * H * self.moe_intermediate_size + ((2 * self.moe_intermediate_size + H) if self.expert_bias else 0)
         shared = 3 * H * self.shared_expert_intermediate_size + (H if self.shared_expert_gate else 0)
         shared += self.num_experts if self.router_bias else 0
+        shared += self.num_experts if self.router_logit_bias else 0
         total = active = 0
         for i in range(self.num_hidden_layers):
             if self.layer_is_moe(i):
@@ -170,7 +182,13 @@ class ModelConfig:
             if self.family.startswith("qwen2"):
                 d["use_sliding_window"] = bool(self.sliding_window)
                 d["max_window_layers"] = 0 if self.sliding_window else self.num_hidden_layers
-        if self.family == "glm4_moe":
+        if self.family == "gpt_oss":
+            d.update({"num_local_experts": self.num_experts, "num_experts_per_tok": self.num_experts_per_tok,
+                      "intermediate_size": self.moe_intermediate_size, "router_aux_loss_coef": self.router_aux_loss_coef,
+                      "output_router_logits": False, "swiglu_limit": self.glu_limit,
+                      "layer_types": list(self.layer_types or ["sliding_attention" if self.sliding_window else "full_attention"]
+                                          * self.num_hidden_layers)})
+        elif self.family == "glm4_moe":
             first_dense = 0
             while first_dense in self.mlp_only_layers:
                 first_dense += 1
@@ -243,6 +261,16 @@ class ModelConfig:
                          topk_group=int(d.get("topk_group", 1)), routed_scaling_factor=float(d.get("routed_scaling_factor", 1.0)),
                          shared_expert_intermediate_size=int(d.get("n_shared_experts", 0) or 0) * width,
                          mlp_only_layers=list(range(int(d.get("first_k_dense_replace", 0)))), use_qk_norm=bool(d.get("use_qk_norm", False)))
+        elif mt == "gpt_oss":
+            n_exp, width, dense_width = d.get("num_local_experts", 128), d["intermediate_size"], d["intermediate_size"]
+            topk, renorm = d.get("num_experts_per_tok", 4), True
+            kinds = list(d.get("layer_types") or ["sliding_attention" if i % 2 == 0 else "full_attention"
+                                                   for i in range(d["num_hidden_layers"])])
+            if "sliding_attention" not in kinds:
+                window = 0
+            extra = dict(layer_types=kinds if window else None, attention_sinks=True, output_bias=bool(d.get("attention_bias", True)),
+                         router_logit_bias=True, expert_bias=True, expert_activation="clamped_glu",
+                         glu_limit=float(d.get("swiglu_limit", 7.0)))
         elif mt == "olmoe":
             if d.get("clip_qkv"):
                 raise ValueError("an OLMoE checkpoint with clip_qkv set: clamping the projections is not built")

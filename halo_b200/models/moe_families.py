@@ -7,7 +7,7 @@ layout kinds and the conversion of every kind to the run-time banks ``gate_up [E
 are the content of the reference's ``ExpertLayout`` (halo/models/moe/expert_layout.py:63-163) and
 ``MoEFamilySpec`` registry (halo/models/moe/family_specs.py:66-426).
 
-``runnable`` marks the families whose whole decoder this package implements (the Qwen line, Mixtral, GLM-4-MoE). The others are
+``runnable`` marks the families whose whole decoder this package implements (the Qwen line, Mixtral, OLMoE, GLM-4-MoE, gpt-oss). The others are
 registered so that loading one fails with a sentence that names what is missing instead of a shape error.
 """
 
@@ -59,8 +59,7 @@ for _s in (
     MoEFamilySpec("qwen3_5_moe", FUSED, shared_experts=True, missing="gated-delta-net linear-attention layers"),
     MoEFamilySpec("qwen3_next", SEPARATE_GLU, shared_experts=True, missing="gated-delta-net linear-attention layers"),
     MoEFamilySpec("qwen4_exp", FUSED, shared_experts=True, missing="block-sparse attention"),
-    MoEFamilySpec("gpt_oss", INTERLEAVED_GLU, activation="gptoss", expert_bias=True, router_name="mlp.router",
-                  missing="attention sinks, sliding-window layers, clamped GLU with expert biases"),
+    MoEFamilySpec("gpt_oss", INTERLEAVED_GLU, activation="gptoss", expert_bias=True, router_name="mlp.router", runnable=True),
     MoEFamilySpec("deepseek_v4", SEPARATE_GLU, score_function="sigmoid", selection_bias=True, routed_scaling_factor=2.5,
                   grouped_topk=True, shared_experts=True, missing="multi-head latent attention, hyper-connections"),
     MoEFamilySpec("glm4_moe", SEPARATE_GLU, score_function="sigmoid", selection_bias=True, grouped_topk=True,

@@ -96,9 +96,14 @@ class _RouterLinear(torch.autograd.Function):
 
 
 class Attention(nn.Module):
-    def __init__(self, cfg: ModelConfig, dtype, device, tp_size: int = 1):
+    def __init__(self, cfg: ModelConfig, dtype, device, tp_size: int = 1, layer_idx: int = 0):
         super().__init__()
         self.cfg = cfg
+        # the window of this layer: families that alternate windowed and full layers name each layer's kind
+        kinds = cfg.layer_types
+        self.window = cfg.sliding_window if (not kinds or layer_idx >= len(kinds) or kinds[layer_idx] == "sliding_attention") else 0
+        if (cfg.attention_sinks or cfg.output_bias) and tp_size > 1:
+            raise ValueError("attention sinks and an output-projection bias are not cut over tensor-parallel ranks")
         H, D = cfg.hidden_size, cfg.head_dim
         # under tensor parallelism a rank holds 1/tp of the query and of the key/value heads
         self.n_heads, self.n_kv_heads = cfg.num_attention_heads // tp_size, cfg.num_key_value_heads // tp_size
@@ -113,6 +118,8 @@ class Attention(nn.Module):
                 self.qkv_bias.tp_kind = "qkv_bias"
         else:
             self.register_parameter("qkv_bias", None)
+        self.o_bias = nn.Parameter(torch.zeros(H, dtype=dtype, device=device)) if cfg.output_bias else None
+        self.sinks = nn.Parameter(torch.zeros(self.n_heads, dtype=dtype, device=device)) if cfg.attention_sinks else None
         self.lora = None          # halo_b200.peft.lora.LoraSet when low-rank adapters are attached
         self.lowp = ""            # block-scaled format the projections are rounded to (quantisation-aware training)
         if cfg.use_qk_norm:
@@ -130,28 +137,40 @@ class Attention(nn.Module):
 
     def _masked(self, qkv, ctx):
         """Attention under an explicit ``[T, T]`` mask through the masked-attention op: the context's own mask (tree
-        packing: completions that share a stored-once prompt) or the sliding window of the configuration. The flash
-        kernel serves neither; meant for rows of a few thousand tokens."""
-        from halo_b200.ops.masked_attention import masked_attention, window_mask
+        packing: completions that share a stored-once prompt), the sliding window of this layer, or plain causal
+        attention with sink logits. The flash kernel serves none of them; meant for rows of a few thousand tokens."""
         from halo_b200.ops.rope import qk_norm_rope
 
         cfg = self.cfg
-        if ctx.cp is not None or ctx.tp is not None or ctx.kv_cache is not None:
-            raise NotImplementedError("windowed attention is built for unsliced rows outside generation")
         Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         q, k = qk_norm_rope(qkv, self.q_norm, self.k_norm, ctx.rope, Hq, Hkv, cfg.rms_norm_eps, cfg.use_qk_norm)
         v = qkv[:, (Hq + Hkv) * D:]
+        return self.masked_core(q, k, v, ctx)
+
+    def masked_core(self, q, k, v, ctx):
+        """``q [T, Hq*D]``, ``k`` / ``v [T, Hkv*D]`` (normed and rotated) under this layer's mask."""
+        from halo_b200.ops.masked_attention import masked_attention, window_mask
+
+        cfg = self.cfg
+        if ctx.cp is not None or ctx.tp is not None:
+            raise NotImplementedError("windowed / sink / explicitly masked attention is built for unsliced rows")
+        Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         mask = getattr(ctx, "attention_mask", None)
-        if cfg.sliding_window:
+        T = q.shape[0]
+        if self.window:
             if getattr(ctx, "window", None) is None:
-                ctx.window = window_mask(ctx.plan.cu_seqlens, cfg.sliding_window, device=qkv.device)     # shared by the layers
+                ctx.window = window_mask(ctx.plan.cu_seqlens, self.window, device=q.device)     # shared by the layers
                 if mask is not None:
-                    ctx.window = ctx.window & mask.to(qkv.device)
+                    ctx.window = ctx.window & mask.to(q.device)
             mask = ctx.window
-        elif mask.device != qkv.device:
-            mask = ctx.attention_mask = mask.to(qkv.device)
-        T = qkv.shape[0]
-        o = masked_attention(q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D), mask)
+        elif mask is None:
+            # a full layer that is here for its sinks: the causal mask of the packed documents, shared by such layers
+            if getattr(ctx, "causal", None) is None:
+                ctx.causal = window_mask(ctx.plan.cu_seqlens, T, device=q.device)
+            mask = ctx.causal
+        elif mask.device != q.device:
+            mask = ctx.attention_mask = mask.to(q.device)
+        o = masked_attention(q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D), mask, sinks=self.sinks)
         return o.reshape(T, Hq * D)
 
     def _qkv(self, h):
@@ -165,11 +184,11 @@ class Attention(nn.Module):
         y = _linear(o, self.o_proj, self.lowp)
         if self.lora is not None and "o_proj" in self.lora:
             y = y + self.lora.delta("o_proj", o)
-        return y
+        return y if self.o_bias is None else y + self.o_bias
 
     def forward(self, h, ctx):
         cfg = self.cfg
-        if ctx.kv_cache is not None and not cfg.sliding_window:
+        if ctx.kv_cache is not None:
             # generation: keys / values go to the cache, a decode step attends the cache
             from halo_b200.inference.generate import cached_attention
 
@@ -183,7 +202,7 @@ class Attention(nn.Module):
                                         cfg.rms_norm_eps, cfg.use_qk_norm)
             return row_parallel_linear(o, self.o_proj, ctx.tp)
         qkv = self._qkv(h)
-        if cfg.sliding_window or getattr(ctx, "attention_mask", None) is not None:
+        if self.window or self.sinks is not None or getattr(ctx, "attention_mask", None) is not None:
             return self._out(self._masked(qkv, ctx))
         if ctx.cp is not None:
             # context parallel: this rank holds one chunk of the row; keys and values of straddling documents
@@ -271,6 +290,18 @@ class SparseMoE(nn.Module):
                                                         requires_grad=False)
         else:
             self.register_parameter("e_score_correction_bias", None)
+        # gpt-oss: a trained bias on the router's logits, and per-expert bias vectors around a clamped GLU
+        self.gate_bias = (nn.Parameter(torch.zeros(cfg.num_experts, dtype=router_dtype or dtype, device=device))
+                          if cfg.router_logit_bias else None)
+        if cfg.expert_bias or cfg.expert_activation != "swiglu":
+            if n_local_experts != cfg.num_experts or etp is not None:
+                raise ValueError("experts with bias vectors / a clamped GLU run whole on every rank: expert parallelism and "
+                                 "expert tensor parallelism are not built for them")
+            self.experts_gate_up_bias = nn.Parameter(torch.zeros(n_local_experts, 2 * F, dtype=dtype, device=device))
+            self.experts_down_bias = nn.Parameter(torch.zeros(n_local_experts, H, dtype=dtype, device=device))
+            self.experts_gate_up_bias.is_expert = self.experts_down_bias.is_expert = True
+        else:
+            self.experts_gate_up_bias = self.experts_down_bias = None
         self.expert_lora = None       # halo_b200.peft.lora.ExpertLora when the routed experts carry adapters
         self.lowp = ""                # block-scaled format of quantisation-aware training (banks and dispatched rows)
         self.load_counter = None      # (ExpertLoadCounter, layer index) when load metrics are on
@@ -281,6 +312,8 @@ class SparseMoE(nn.Module):
         cfg = self.cfg
         gate_w = self.gate if self.gate.dtype == h.dtype else self.gate.to(h.dtype)
         logits = _RouterLinear.apply(h, gate_w) if h.is_cuda else (h.float() @ self.gate.float().t())
+        if self.gate_bias is not None:
+            logits = logits + self.gate_bias.float()
         bias = self.selection_bias
         if self.e_score_correction_bias is not None:
             bias = self.e_score_correction_bias if bias is None else self.e_score_correction_bias + bias
@@ -325,7 +358,12 @@ class SparseMoE(nn.Module):
         h_experts = h
         if self.lowp:
             bank_gate_up, bank_down, h_experts = (_rounded(t, self.lowp) for t in (bank_gate_up, bank_down, h))
-        if self.etp is not None:
+        if self.experts_gate_up_bias is not None:
+            from halo_b200.ops.biased_glu_experts import biased_glu_experts
+
+            out = biased_glu_experts(h_experts, idx, w, bank_gate_up, self.experts_gate_up_bias, bank_down,
+                                     self.experts_down_bias, cfg.glu_limit)
+        elif self.etp is not None:
             # every rank of the group routes the same tokens through its slice of each expert; the partial outputs
             # are summed in token space (and the partial input / routing-weight gradients on the way back)
             from halo_b200.parallel.expert_tensor_parallel import copy_to_group, sum_from_group
@@ -351,7 +389,7 @@ class DecoderLayer(nn.Module):
         H = cfg.hidden_size
         self.input_layernorm = nn.Parameter(torch.ones(H, dtype=dtype, device=device))
         self.post_attention_layernorm = nn.Parameter(torch.ones(H, dtype=dtype, device=device))
-        self.self_attn = Attention(cfg, dtype, device, tp_size)
+        self.self_attn = Attention(cfg, dtype, device, tp_size, idx)
         if cfg.layer_is_moe(idx):
             # attention-only tensor parallelism for MoE layers: router and experts see this rank's token shard
             self.mlp = SparseMoE(cfg, dtype, device, n_local_experts, router_dtype, etp)
@@ -510,8 +548,8 @@ class Qwen3Model(nn.Module):
         for name, p in self.named_parameters():
             if "_hc." in name or name.startswith("hc_head."):
                 continue
-            if p.dim() == 1:
-                p.fill_(0.0 if name.endswith("bias") else 1.0)
+            if p.dim() == 1 or name.endswith("bias"):
+                p.fill_(0.0 if name.endswith(("bias", "sinks")) else 1.0)
                 continue
             dev = p.device
             if first and name.startswith("layers."):

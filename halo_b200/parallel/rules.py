@@ -210,5 +210,11 @@ def reject_model_layout(pc, model_cfg, packed: bool = True) -> None:
             raise ConfigError(
                 f"tensor_parallel_size ({pc.tp_size}) must divide num_attention_heads "
                 f"({model_cfg.num_attention_heads}) and num_key_value_heads ({model_cfg.num_key_value_heads})")
+    if getattr(model_cfg, "attention_sinks", False) or getattr(model_cfg, "expert_bias", False):
+        cut = [name for name, size in (("expert_parallel_size", pc.ep_size), ("expert_tensor_parallel_size", pc.expert_tp_size),
+                                       ("tensor_parallel_size", pc.tp_size), ("context_parallel_size", pc.cp_size)) if size > 1]
+        if cut:
+            raise ConfigError(f"{model_cfg.family}: attention sinks and experts with bias vectors run whole on every rank "
+                              f"(data parallelism and pipeline stages only); drop {', '.join(cut)}")
     if pc.pp_size > 1 and model_cfg.num_hidden_layers < pc.pp_size:
         raise ConfigError(f"{model_cfg.num_hidden_layers} layers cannot fill {pc.pp_size} pipeline stages")

@@ -34,6 +34,11 @@ def family_config(family: str, **kw) -> ModelConfig:
     if family == "glm4_moe":
         base.update(num_experts=8, partial_rotary_factor=0.5, score_function="sigmoid", router_bias=True, n_group=2, topk_group=1,
                     routed_scaling_factor=1.5, shared_expert_intermediate_size=96, mlp_only_layers=[0], use_qk_norm=True)
+    if family == "gpt_oss":
+        base.update(intermediate_size=96, sliding_window=16, layer_types=["sliding_attention", "full_attention"], attention_sinks=True,
+                    output_bias=True, router_logit_bias=True, expert_bias=True, expert_activation="clamped_glu", rms_norm_eps=1e-5,
+                    rope_scaling={"rope_type": "yarn", "factor": 4.0, "beta_fast": 32.0, "beta_slow": 1.0, "truncate": False,
+                                  "original_max_position_embeddings": 64})
     base.update(kw)
     return ModelConfig(**base)
 
@@ -46,7 +51,8 @@ def logits_of(model, ids):
 
 CASES = [("mistral", {"sliding_window": 16}), ("qwen2", {"sliding_window": 24}), ("llama", {}), ("llama", {"rope_scaling": LLAMA3}), ("llama", {"attention_bias": True}), ("mistral", {}),
          ("qwen2", {}), ("qwen2", {"rope_scaling": YARN}), ("mixtral", {}), ("qwen2_moe", {}), ("olmoe", {}),
-         ("glm4_moe", {}), ("glm4_moe", {"n_group": 4, "topk_group": 2, "use_qk_norm": False, "attention_bias": True})]
+         ("glm4_moe", {}), ("glm4_moe", {"n_group": 4, "topk_group": 2, "use_qk_norm": False, "attention_bias": True}),
+         ("gpt_oss", {})]
 
 
 @pytest.mark.parametrize("family,extra", CASES, ids=[f"{f}-{'-'.join(e) or 'plain'}" for f, e in CASES])
@@ -68,6 +74,15 @@ def test_family_round_trip_through_transformers(tmp_path, family, extra):
         with torch.no_grad():
             for layer in model.layers:       # a zero bias would hide a wrong split
                 layer.self_attn.qkv_bias.normal_(0.0, 0.5, generator=torch.Generator().manual_seed(11))
+    if family == "gpt_oss":
+        with torch.no_grad():                # zero sinks and biases would hide a wrong softmax, split or interleave
+            g = torch.Generator().manual_seed(23)
+            for layer in model.layers:
+                layer.self_attn.sinks.normal_(0.0, 1.0, generator=g)
+                layer.self_attn.o_bias.normal_(0.0, 0.2, generator=g)
+                layer.mlp.gate_bias.normal_(0.0, 0.5, generator=g)
+                layer.mlp.experts_gate_up_bias.normal_(0.0, 4.0, generator=g)     # wide enough to reach the clamps
+                layer.mlp.experts_down_bias.normal_(0.0, 0.2, generator=g)
     d = str(tmp_path / "hf")
     save_model(model, d, save_dtype=None)
     assert ModelConfig.load(d) == cfg
@@ -113,3 +128,72 @@ def test_window_and_family_gates():
         ModelConfig.from_hf_dict(q)
     with pytest.raises(ValueError, match="no family registered"):
         ModelConfig.from_hf_dict({**d, "model_type": "mamba"})
+
+
+def test_biased_clamped_glu_experts_match_the_dense_form():
+    from halo_b200.ops.biased_glu_experts import biased_glu_experts, biased_glu_experts_reference
+
+    g = torch.Generator().manual_seed(3)
+    T, H, F, E, k = 40, 32, 24, 6, 2
+    x = torch.randn(T, H, generator=g, requires_grad=True)
+    banks = [torch.randn(E, 2 * F, H, generator=g) * 0.5, torch.randn(E, 2 * F, generator=g) * 4.0,       # biases reach both clamps
+             torch.randn(E, H, F, generator=g) * 0.2, torch.randn(E, H, generator=g)]
+    banks = [b.requires_grad_() for b in banks]
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32)
+    idx[:, 0] = idx[:, 0].clamp(max=E - 2)                  # the last expert is rarely hit; expert E-1 may get no token at all
+    w = torch.rand(T, k, generator=g).requires_grad_()
+    got = biased_glu_experts(x, idx, w, *banks)
+    want = biased_glu_experts_reference(x, idx, w, *banks)
+    assert torch.allclose(got, want, atol=1e-4)
+    probe = torch.randn(T, H, generator=g)
+    for a, b in zip(torch.autograd.grad((got * probe).sum(), (x, w, *banks)), torch.autograd.grad((want * probe).sum(), (x, w, *banks))):
+        assert torch.allclose(a, b, atol=1e-4)
+
+
+def test_gpt_oss_trains_and_sinks_follow_the_policy(tmp_path):
+    """A tiny gpt-oss model takes optimizer steps (loss falls; sinks, router bias and expert biases all get gradients);
+    the sinks policy neutralizes, freezes or trains the sinks; layouts that would cut the family are refused by name."""
+    from halo_b200.config_validation import ConfigError
+    from halo_b200.data.packing import synthetic_packed_batch
+    from halo_b200.models.attention_sinks import apply_sinks_policy, policy_from_flags
+    from halo_b200.parallel.config import ParallelismConfig
+    from halo_b200.parallel.rules import reject_model_layout
+    from halo_b200.trainers.engine import TrainEngine
+
+    cfg = family_config("gpt_oss")
+    model = build_model(cfg, device="cpu", seed=1, gradient_checkpointing=True)
+    assert [layer.self_attn.window for layer in model.layers] == [16, 0]
+    assert sum(p.numel() for p in model.parameters()) == cfg.param_counts()["total"]
+    assert apply_sinks_policy(model, policy_from_flags(False, True)) == 2 and model.sinks_policy == "trainable"
+    engine = TrainEngine(model, torch.optim.AdamW(model.parameters(), lr=3e-3), "cpu", max_grad_norm=1.0)
+    batch = synthetic_packed_batch(96, cfg.vocab_size, seed=0, lo=20, hi=50)
+    before = {n: p.detach().clone() for n, p in model.named_parameters()}
+    losses = [float(engine.train_step(batch).loss.reshape(-1)[0]) for _ in range(6)]
+    assert losses[-1] < losses[0] - 0.3, losses
+    moved = {n for n, p in model.named_parameters() if not torch.equal(p, before[n])}
+    for name in ("layers.0.self_attn.sinks", "layers.1.self_attn.sinks", "layers.0.self_attn.o_bias", "layers.0.mlp.gate_bias",
+                 "layers.0.mlp.experts_gate_up_bias", "layers.1.mlp.experts_down_bias"):
+        assert name in moved, name
+    # neutralized: no softmax mass, no gradient, the same function as a model without sinks
+    apply_sinks_policy(model, "neutralized")
+    assert all(not layer.self_attn.sinks.requires_grad and layer.self_attn.sinks.max() < -1e30 for layer in model.layers)
+    ids = np.random.default_rng(4).integers(0, cfg.vocab_size, size=64)
+    neutral, _ = logits_of(model, ids)
+    saved = [layer.self_attn.sinks for layer in model.layers]
+    for layer in model.layers:
+        layer.self_attn.sinks = None
+    plain, _ = logits_of(model, ids)
+    for layer, s in zip(model.layers, saved):
+        layer.self_attn.sinks = s
+    assert torch.allclose(neutral, plain, atol=1e-5)
+    fresh = build_model(cfg, device="cpu", seed=1, gradient_checkpointing=False)
+    apply_sinks_policy(fresh, "neutralized", pretrained=False)         # nothing pretrained to protect: stays live
+    assert fresh.sinks_policy == "live" and float(fresh.layers[0].self_attn.sinks.abs().max()) == 0.0
+    with pytest.raises(ValueError, match="contradicts"):
+        policy_from_flags(True, True)
+    with pytest.raises(ValueError, match="no attention sinks"):
+        apply_sinks_policy(build_model(family_config("llama"), device="cpu"), "trainable")
+    for axis in ("ep_size", "tp_size", "cp_size"):
+        with pytest.raises(ConfigError, match="run whole on every rank"):
+            reject_model_layout(ParallelismConfig(world_size=2, **{axis: 2}), cfg)
+    reject_model_layout(ParallelismConfig(world_size=4, pp_size=2), cfg)

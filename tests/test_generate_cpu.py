@@ -26,10 +26,29 @@ def full_forward_logits(model, ids):
     return (h.float() @ model.head_weight().float().t())[-1]
 
 
-@pytest.mark.parametrize("kind", ["dense", "moe"])
+def windowed_cfg():
+    """Mistral-style: every layer sees its last 6 keys (shorter than prompt + completion)."""
+    return dataclasses.replace(dense_cfg(), model_type="mistral", use_qk_norm=False, sliding_window=6, max_position_embeddings=64)
+
+
+def sink_cfg():
+    """gpt-oss style: a windowed and a full layer, sink logits, biased clamped-GLU experts."""
+    return ModelConfig(vocab_size=128, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                       intermediate_size=48, moe_intermediate_size=48, num_experts=4, num_experts_per_tok=2, model_type="gpt_oss",
+                       use_qk_norm=False, attention_bias=True, sliding_window=6, layer_types=["sliding_attention", "full_attention"],
+                       attention_sinks=True, output_bias=True, router_logit_bias=True, expert_bias=True,
+                       expert_activation="clamped_glu", max_position_embeddings=64)
+
+
+@pytest.mark.parametrize("kind", ["dense", "moe", "windowed", "sinks"])
 def test_cached_decoding_equals_the_full_forward(kind):
-    cfg = dense_cfg() if kind == "dense" else dataclasses.replace(tiny_moe_config(), num_hidden_layers=2, vocab_size=128)
+    cfg = {"dense": dense_cfg, "windowed": windowed_cfg, "sinks": sink_cfg,
+           "moe": lambda: dataclasses.replace(tiny_moe_config(), num_hidden_layers=2, vocab_size=128)}[kind]()
     model = build_model(cfg, device="cpu", seed=7, gradient_checkpointing=False)
+    if kind == "sinks":
+        with torch.no_grad():
+            for layer in model.layers:
+                layer.self_attn.sinks.normal_(0.0, 1.0, generator=torch.Generator().manual_seed(5))
     rng = np.random.default_rng(0)
     prompts = [rng.integers(0, cfg.vocab_size, size=n) for n in (5, 11, 3)]
     outs = Generator(model).generate(prompts, SamplingParams(max_new_tokens=6, temperature=0.0))

@@ -33,8 +33,9 @@ def test_layout_round_trips_every_kind():
 
 def test_family_registry_refuses_unbuilt_decoders():
     assert mf.require_runnable("qwen3_moe").layout == mf.SEPARATE_GLU
-    with pytest.raises(NotImplementedError, match="attention sinks"):
-        mf.require_runnable("gpt_oss")
+    assert mf.require_runnable("gpt_oss").layout == mf.INTERLEAVED_GLU
+    with pytest.raises(NotImplementedError, match="latent attention"):
+        mf.require_runnable("deepseek_v4")
     with pytest.raises(KeyError):
         mf.family_spec("no_such_family")
     assert len(mf.families()) >= 18
