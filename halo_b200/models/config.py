@@ -181,7 +181,12 @@ class ModelConfig:
             d["sliding_window"] = self.sliding_window or None
             if self.family.startswith("qwen2"):
                 d["use_sliding_window"] = bool(self.sliding_window)
-                d["max_window_layers"] = 0 if self.sliding_window else self.num_hidden_layers
+                first_windowed = (self.layer_types or ["sliding_attention"]).index("sliding_attention") if self.sliding_window else 0
+                if self.layer_types and "full_attention" in self.layer_types[first_windowed:]:
+                    raise ValueError("Qwen2 stores its full-attention layers as a leading run (max_window_layers)")
+                d["max_window_layers"] = first_windowed if self.sliding_window else self.num_hidden_layers
+                if self.sliding_window and self.layer_types:
+                    d["layer_types"] = list(self.layer_types)
         if self.family == "gpt_oss":
             d.update({"num_local_experts": self.num_experts, "num_experts_per_tok": self.num_experts_per_tok,
                       "intermediate_size": self.moe_intermediate_size, "router_aux_loss_coef": self.router_aux_loss_coef,
@@ -240,9 +245,14 @@ class ModelConfig:
         window = d.get("sliding_window") or 0
         if not (fam["has_window"] and window and d.get("use_sliding_window", True) and window < d.get("max_position_embeddings", 0)):
             window = 0
-        if window and d.get("max_window_layers", 0) not in (0, None):
-            raise ValueError(f"{mt} checkpoint that windows only the layers from {d['max_window_layers']} on: a per-layer mix of "
-                             f"full and windowed attention is not built")
+        kinds = None
+        if window and mt.startswith("qwen2") and d.get("max_window_layers", 0) not in (0, None):
+            # Qwen2 windows only the layers from ``max_window_layers`` on
+            first = int(d["max_window_layers"])
+            if first >= d["num_hidden_layers"]:
+                window = 0
+            else:
+                kinds = ["full_attention"] * first + ["sliding_attention"] * (d["num_hidden_layers"] - first)
         rp = d.get("rope_parameters") or {}
         rope_theta = d.get("rope_theta") or rp.get("rope_theta", 1e6 if mt.startswith("qwen") else 1e4)
         scaling = d.get("rope_scaling") or ({k: v for k, v in rp.items() if k not in ("rope_theta", "partial_rotary_factor")} if rp else None)
@@ -294,7 +304,7 @@ class ModelConfig:
             shared_expert_gate=(mt == "qwen2_moe"),
             mlp_only_layers=list(d.get("mlp_only_layers", []) or []), decoder_sparse_step=d.get("decoder_sparse_step", 1),
             rope_theta=float(rope_theta), rms_norm_eps=d.get("rms_norm_eps", 1e-6), use_qk_norm=fam["qk_norm"],
-            sliding_window=int(window),
+            sliding_window=int(window), layer_types=kinds,
             attention_bias=(bool(d.get("attention_bias", False)) if fam["bias_key"]
                             else bool(d.get("qkv_bias", fam["bias_default"]))),
             num_nextn_predict_layers=int(d.get("num_nextn_predict_layers", 0) or 0),

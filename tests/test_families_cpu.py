@@ -49,7 +49,8 @@ def logits_of(model, ids):
         return model.hidden_states(b.input_ids, b.position_ids, b.cu_seqlens) @ model.head_weight().t(), b
 
 
-CASES = [("mistral", {"sliding_window": 16}), ("qwen2", {"sliding_window": 24}), ("llama", {}), ("llama", {"rope_scaling": LLAMA3}), ("llama", {"attention_bias": True}), ("mistral", {}),
+CASES = [("mistral", {"sliding_window": 16}), ("qwen2", {"sliding_window": 24}),
+         ("qwen2", {"sliding_window": 12, "layer_types": ["full_attention", "sliding_attention"]}), ("llama", {}), ("llama", {"rope_scaling": LLAMA3}), ("llama", {"attention_bias": True}), ("mistral", {}),
          ("qwen2", {}), ("qwen2", {"rope_scaling": YARN}), ("mixtral", {}), ("qwen2_moe", {}), ("olmoe", {}),
          ("glm4_moe", {}), ("glm4_moe", {"n_group": 4, "topk_group": 2, "use_qk_norm": False, "attention_bias": True}),
          ("gpt_oss", {})]
@@ -123,9 +124,10 @@ def test_window_and_family_gates():
     d["sliding_window"] = 4096                      # as wide as the context: plain causal attention
     assert ModelConfig.from_hf_dict(d).sliding_window == 0
     q = family_config("qwen2", sliding_window=16).to_hf_dict()
-    q["max_window_layers"] = 1
-    with pytest.raises(ValueError, match="per-layer mix"):
-        ModelConfig.from_hf_dict(q)
+    q["max_window_layers"] = 1                      # Qwen2 windows the layers from this one on
+    assert ModelConfig.from_hf_dict(q).layer_types == ["full_attention", "sliding_attention"]
+    q["max_window_layers"] = 2
+    assert ModelConfig.from_hf_dict(q).sliding_window == 0
     with pytest.raises(ValueError, match="no family registered"):
         ModelConfig.from_hf_dict({**d, "model_type": "mamba"})
 
