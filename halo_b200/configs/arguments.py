@@ -32,6 +32,9 @@ class ModelArguments:
     lora_target_modules: list[str] | str | None = None   # hub projection names, "experts.<name>" for routed experts, or "all-linear"
     adapter_path: str = ""                  # adapters to continue from (a directory holding adapter_model.safetensors)
     merge_adapters_on_save: bool = False    # save full weights with the adapters folded in instead of the adapters alone
+    load_in_4bit: bool = False              # QLoRA: keep the frozen base matrices of the decoder layers as 4-bit blocks (needs use_peft)
+    bnb_4bit_quant_type: Literal["nf4", "fp4"] = "nf4"
+    use_bnb_nested_quant: bool = False      # also store the block maxima in 8 bits
     reset_sinks: bool = True                # gpt-oss: neutralize the attention sinks for fine-tuning; false keeps them live and frozen
     train_sinks: bool = False               # gpt-oss: train the live sinks (needs reset_sinks: false and full fine-tuning)
 
@@ -46,6 +49,13 @@ class ModelArguments:
     def __post_init__(self):
         if self.use_peft and (self.freeze_patterns or self.train_only_patterns):
             raise ConfigError("use_peft freezes the base weights itself: drop freeze_patterns / train_only_patterns")
+        if self.load_in_4bit and not self.use_peft:
+            raise ConfigError("load_in_4bit stores frozen base weights: it needs use_peft: true (QLoRA)")
+        if self.load_in_4bit and self.merge_adapters_on_save:
+            raise ConfigError("merge_adapters_on_save with load_in_4bit would fold the adapters into the rounded base: save the "
+                              "adapters alone and merge them into the original checkpoint with the merge-adapter tool")
+        if self.load_in_4bit and self.lowp_format:
+            raise ConfigError("load_in_4bit and lowp_format both round the base weights: choose one")
         if self.train_sinks and self.reset_sinks:
             raise ConfigError("train_sinks: true contradicts reset_sinks: true - set reset_sinks: false alongside train_sinks")
         if self.train_sinks and self.use_peft:

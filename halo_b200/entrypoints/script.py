@@ -178,6 +178,11 @@ def load_policy_model(model_args, pc, device, runtime, gradient_checkpointing=Tr
         if model_args.adapter_path:
             load_adapters(model, model_args.adapter_path)
         log.info("low-rank adapters: %d trainable parameters on %d frozen", stats["trainable"], stats["frozen"])
+        if getattr(model_args, "load_in_4bit", False):
+            from halo_b200.peft.qlora import quantize_base_weights
+
+            q = quantize_base_weights(model, model_args.bnb_4bit_quant_type, model_args.use_bnb_nested_quant)
+            log.info("4-bit base: %d matrices, %.1f M parameters in %.1f MB", q["matrices"], q["parameters"] / 1e6, q["bytes"] / 1e6)
     if model_args.freeze_patterns or model_args.train_only_patterns:
         from halo_b200.models.freeze import apply_freeze_patterns
 
