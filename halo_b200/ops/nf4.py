@@ -6,8 +6,8 @@ the fp32 block maxima are themselves stored as 8-bit codes, evenly spaced in the
 the largest maximum of each group of 256 blocks (relative error below 1.4 % even when a group spans three decades),
 which brings the overhead from 0.5 to about 0.129 bits per value.
 
-Dequantisation is a table lookup and one multiply, written as tensor operations; it runs once per layer and pass,
-just before the layer reads its weights. (The role of the bitsandbytes 4-bit storage the reference loads through
+Dequantisation is a table lookup and one multiply (``csrc/nf4.cu`` for bf16 on CUDA, tensor operations elsewhere);
+it runs once per layer and pass, just before the layer reads its weights. (The role of the bitsandbytes 4-bit storage the reference loads through
 ``load_in_4bit`` / ``use_bnb_nested_quant``, halo/model_loading/dtype.py:114-119.)"""
 
 from __future__ import annotations
@@ -92,6 +92,25 @@ def quantize_4bit(w: torch.Tensor, kind: str = "nf4", nested: bool = False, bloc
 
 
 def dequantize_4bit(p: Packed4bit, dtype: torch.dtype | None = None) -> torch.Tensor:
+    dtype = dtype or p.dtype
+    if p.codes.is_cuda and dtype == torch.bfloat16 and p.block == BLOCK:
+        # the sm_100a kernel (csrc/nf4.cu): 0.5 byte read and 2 bytes written per value, the same single rounding
+        import ctypes
+
+        from halo_b200.ops import _lib
+
+        out = torch.empty(p.shape, dtype=torch.bfloat16, device=p.codes.device)
+        maxima = p.block_maxima().float().contiguous()
+        table = (ctypes.c_float * 16)(*KINDS[p.kind])
+        rc = _lib.lib().halo_dequant_4bit_bf16(_lib.ptr(p.codes), _lib.ptr(maxima), _lib.ptr(out), _lib.c_ll(out.numel()), table,
+                                               _lib.stream_ptr(out.device))
+        _lib.check(rc, "halo_dequant_4bit_bf16")
+        return out
+    return dequantize_4bit_reference(p, dtype)
+
+
+def dequantize_4bit_reference(p: Packed4bit, dtype: torch.dtype | None = None) -> torch.Tensor:
+    """The tensor-op statement (every device): a table lookup and one multiply in fp32, one rounding."""
     table = levels(p.kind, p.codes.device)
     codes = torch.stack([p.codes >> 4, p.codes & 0xF], dim=1).reshape(-1, p.block).long()
     values = table[codes] * p.block_maxima()[:, None]
