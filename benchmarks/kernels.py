@@ -147,7 +147,7 @@ def cases(small: bool):
 
 def family_cases(small: bool):
     """Bandwidth-bound kernels of the other families and of generation (run with ``--families``): residual-stream ops
-    at 4 streams, per-stream norm, block-scaled fake quantisation, standalone SwiGLU, decode attention over a cache."""
+    at 4 streams, per-stream norm, block-scaled fake quantisation, standalone SwiGLU, decode attention over a cache, 4-bit dequantisation of an expert bank."""
     from halo_b200.inference.generate import KVCache
     from halo_b200.ops import lowp, streams
     from halo_b200.ops.activation import swiglu
@@ -177,6 +177,11 @@ def family_cases(small: bool):
         cache.begin_decode()
         q = bf16(B, NQ * HD)
         out["decode_attention"] = (lambda: cache.attend(0, q, NQ), 4.0 * B * NQ * HD * S, 2.0 * 2 * B * S * NKV * HD)
+        from halo_b200.ops import nf4
+
+        E, F = (32, 768) if small else (128, 768)              # one layer's gate/up expert bank of the 30B-A3B shape
+        packed = nf4.quantize_4bit(bf16(E, 2 * F, H), "nf4", nested=False)
+        out["dequant_nf4_expert_bank"] = (lambda: nf4.dequantize_4bit(packed), 0.0, (0.5 + 4.0 / 64 + 2.0) * E * 2 * F * H)
     return out
 
 
