@@ -23,8 +23,9 @@ def attended_keys(cu_seqlens) -> float:
 def model_flops_per_step(cfg, cu_seqlens, n_tokens: int) -> float:
     counts = cfg.param_counts()
     dense = 6.0 * (counts["active"] - 0) * n_tokens
-    attn = 12.0 * cfg.head_dim * cfg.num_attention_heads * attended_keys(cu_seqlens) * cfg.num_hidden_layers
-    return dense + attn
+    from halo_b200.models.attention_cost import attention_flops
+
+    return dense + attention_flops(cfg, cu_seqlens)        # per layer: windowed layers visit fewer keys
 
 
 class EfficiencyCallback(Callback):

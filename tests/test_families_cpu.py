@@ -199,3 +199,19 @@ def test_gpt_oss_trains_and_sinks_follow_the_policy(tmp_path):
         with pytest.raises(ConfigError, match="run whole on every rank"):
             reject_model_layout(ParallelismConfig(world_size=2, **{axis: 2}), cfg)
     reject_model_layout(ParallelismConfig(world_size=4, pp_size=2), cfg)
+
+
+def test_keys_visited_follow_each_layers_window():
+    """The attention term of the model-FLOPs count, per layer: the mask the layer really applies has that many pairs."""
+    from halo_b200.models.attention_cost import attention_flops, causal_pairs, keys_visited_per_layer, layer_windows
+    from halo_b200.ops.masked_attention import window_mask
+
+    cu = [0, 5, 45, 46, 96]
+    cfg = family_config("gpt_oss")                  # layer 0 windowed (16), layer 1 full
+    assert layer_windows(cfg) == [16, 0]
+    windowed, full = keys_visited_per_layer(cfg, cu)
+    assert windowed == float(window_mask(cu, 16).sum()) and full == float(window_mask(cu, 96).sum())
+    assert causal_pairs([40], 16) == 16 * 17 / 2 + 24 * 16 and causal_pairs([5], 16) == 15.0
+    assert attention_flops(cfg, cu) == 12.0 * cfg.head_dim * cfg.num_attention_heads * (windowed + full)
+    plain = family_config("llama")
+    assert keys_visited_per_layer(plain, cu) == [full] * 2
