@@ -22,6 +22,7 @@ MOE_HUB_NAMES = {
     "qwen2_moe": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "mixtral": ("block_sparse_moe", "w1", "w3", "w2"),
     "glm4_moe": ("mlp", "gate_proj", "up_proj", "down_proj"),
+    "deepseek_v3": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "olmoe": ("mlp", "gate_proj", "up_proj", "down_proj"),
 }
 # gpt-oss stores each bank as ONE tensor, transposed, with gate and up columns interleaved (``INTERLEAVED_GLU``)
@@ -55,7 +56,7 @@ def whole_bank_source(name: str, cfg, first_layer: int = 0):
         "mlp.experts_down_bias": (pre + "down_proj_bias", lambda t: t),
     }.get(m.group(2))
 # how a family names its always-on shared feed-forward block
-SHARED_EXPERT_NAMES = {"glm4_moe": "shared_experts"}
+SHARED_EXPERT_NAMES = {"glm4_moe": "shared_experts", "deepseek_v3": "shared_experts"}
 
 
 def runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, expert_offset: int = 0) -> dict:
@@ -98,6 +99,11 @@ def runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, e
         return {pre + "self_attn.q_proj.bias": q, pre + "self_attn.k_proj.bias": k, pre + "self_attn.v_proj.bias": v}
     if rest == "self_attn.o_proj":
         return {pre + "self_attn.o_proj.weight": tensor}
+    latent = {"self_attn.q_a_proj": "q_a_proj.weight", "self_attn.q_a_norm": "q_a_layernorm.weight", "self_attn.q_b_proj": "q_b_proj.weight",
+              "self_attn.q_proj": "q_proj.weight", "self_attn.kv_a_proj": "kv_a_proj_with_mqa.weight",
+              "self_attn.kv_a_norm": "kv_a_layernorm.weight", "self_attn.kv_b_proj": "kv_b_proj.weight"}
+    if rest in latent:          # multi-head latent attention (DeepSeek)
+        return {pre + "self_attn." + latent[rest]: tensor}
     if rest == "self_attn.o_bias":
         return {pre + "self_attn.o_proj.bias": tensor}
     if rest == "self_attn.sinks":

@@ -199,8 +199,10 @@ class Generator:
         B = len(prompts)
         lens = np.array([len(p) for p in prompts])
         stops = set(params.stop_token_ids) | ({self.eos} if self.eos is not None else set())
-        cache = KVCache(len(m.layers), B, int(lens.max()) + params.max_new_tokens, cfg.num_key_value_heads, cfg.head_dim,
-                        next(m.parameters()).dtype, dev)
+        # latent attention caches the expanded keys (one per query head, no-rotary + rotary dims) and zero-padded values
+        kv_heads, width = ((cfg.num_attention_heads, cfg.qk_nope_head_dim + cfg.qk_rope_head_dim) if cfg.kv_lora_rank
+                           else (cfg.num_key_value_heads, cfg.head_dim))
+        cache = KVCache(len(m.layers), B, int(lens.max()) + params.max_new_tokens, kv_heads, width, next(m.parameters()).dtype, dev)
         generator = None
         if params.seed is not None:
             generator = torch.Generator(device=dev).manual_seed(params.seed)

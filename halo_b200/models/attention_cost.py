@@ -37,5 +37,7 @@ def keys_visited_per_layer(cfg, cu_seqlens) -> list[float]:
 
 
 def attention_flops(cfg, cu_seqlens) -> float:
-    """Forward + backward FLOPs of the score and value products: 12 * head_dim * heads per visited pair."""
-    return 12.0 * cfg.head_dim * cfg.num_attention_heads * sum(keys_visited_per_layer(cfg, cu_seqlens))
+    """Forward + backward FLOPs of the score and value products: 12 * head_dim * heads per visited pair (latent
+    attention: 6 * (query/key width + value width), the two products have different widths there)."""
+    width = (cfg.qk_nope_head_dim + cfg.qk_rope_head_dim + cfg.v_head_dim) / 2.0 if getattr(cfg, "kv_lora_rank", 0) else cfg.head_dim
+    return 12.0 * width * cfg.num_attention_heads * sum(keys_visited_per_layer(cfg, cu_seqlens))

@@ -16,6 +16,8 @@ import torch
 
 def attention_path(cfg, device, dtype, tree_packing: bool = False) -> tuple[str, str]:
     device = torch.device(device)
+    if getattr(cfg, "kv_lora_rank", 0):
+        return "masked", "latent attention: query / key width differs from the value width"
     if getattr(cfg, "attention_sinks", False):
         return "masked", "attention sinks: the flash kernel's softmax has no extra logit"
     if cfg.sliding_window:

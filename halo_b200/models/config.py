@@ -32,6 +32,9 @@ FAMILIES = {
     "glm4_moe": dict(architecture="Glm4MoeForCausalLM", moe=True, qk_norm=True, bias_key=True, bias_default=False, has_window=False),
     # a learned sink logit per head, windowed and full layers in turn, biases on every projection and on the experts,
     # a clamped GLU in the experts, a biased router that takes the softmax of the top-k logits
+    # multi-head latent attention (queries and keys / values through low-rank bottlenecks, rotary embedding on a separate
+    # slice shared by all heads) in front of the sigmoid-routed, group-limited MoE with shared experts
+    "deepseek_v3": dict(architecture="DeepseekV3ForCausalLM", moe=True, qk_norm=False, bias_key=True, bias_default=False, has_window=False),
     "gpt_oss": dict(architecture="GptOssForCausalLM", moe=True, qk_norm=False, bias_key=True, bias_default=True, has_window=True),
 }
 
@@ -65,6 +68,12 @@ class ModelConfig:
     topk_group: int = 1
     routed_scaling_factor: float = 1.0
     sliding_window: int = 0                # > 0: every query sees only its last ``sliding_window`` keys (Mistral-style)
+    kv_lora_rank: int = 0                  # > 0: multi-head latent attention (DeepSeek); keys / values come from this many latent dims
+    q_lora_rank: int = 0                   # latent dims of the query bottleneck (0 = one plain query projection)
+    qk_nope_head_dim: int = 0              # per head: dims of q / k without rotary embedding ...
+    qk_rope_head_dim: int = 0              # ... and with it (the key's rotary slice is shared by all heads); equals ``head_dim``
+    v_head_dim: int = 0
+    rope_interleave: bool = True           # the checkpoint stores rotary pairs interleaved (even, odd) instead of in halves
     layer_types: list[str] | None = None   # per layer "sliding_attention" | "full_attention"; None = the window on every layer
     attention_sinks: bool = False          # one learned logit per head joins every softmax (gpt-oss)
     output_bias: bool = False              # bias on the attention output projection too (gpt-oss)
@@ -102,9 +111,15 @@ class ModelConfig:
     def param_counts(self) -> dict[str, int]:
         H, D = self.hidden_size, self.head_dim
         norm_width = (self.num_attention_heads + self.num_key_value_heads) * D if self.qk_norm_whole_width else 2 * D
-        attn = (H * self.qkv_dim + self.num_attention_heads * D * H + (norm_width if self.use_qk_norm else 0) + 2 * H
-                + (self.qkv_dim if self.attention_bias else 0) + (H if self.output_bias else 0)
-                + (self.num_attention_heads if self.attention_sinks else 0))
+        if self.kv_lora_rank:
+            Hq, dqk = self.num_attention_heads, self.qk_nope_head_dim + self.qk_rope_head_dim
+            q_side = (H * self.q_lora_rank + self.q_lora_rank + self.q_lora_rank * Hq * dqk) if self.q_lora_rank else H * Hq * dqk
+            attn = (q_side + H * (self.kv_lora_rank + self.qk_rope_head_dim) + self.kv_lora_rank
+                    + self.kv_lora_rank * Hq * (self.qk_nope_head_dim + self.v_head_dim) + Hq * self.v_head_dim * H + 2 * H)
+        else:
+            attn = (H * self.qkv_dim + self.num_attention_heads * D * H + (norm_width if self.use_qk_norm else 0) + 2 * H
+                    + (self.qkv_dim if self.attention_bias else 0) + (H if self.output_bias else 0)
+                    + (self.num_attention_heads if self.attention_sinks else 0))
         dense_mlp = 3 * H * self.intermediate_size
         expert = 3 * H * self.moe_intermediate_size + ((2 * self.moe_intermediate_size + H) if self.expert_bias else 0)
         shared = 3 * H * self.shared_expert_intermediate_size + (H if self.shared_expert_gate else 0)
@@ -193,7 +208,7 @@ class ModelConfig:
                       "output_router_logits": False, "swiglu_limit": self.glu_limit,
                       "layer_types": list(self.layer_types or ["sliding_attention" if self.sliding_window else "full_attention"]
                                           * self.num_hidden_layers)})
-        elif self.family == "glm4_moe":
+        elif self.family in ("glm4_moe", "deepseek_v3"):
             first_dense = 0
             while first_dense in self.mlp_only_layers:
                 first_dense += 1
@@ -205,7 +220,15 @@ class ModelConfig:
                       "n_group": self.n_group, "topk_group": self.topk_group, "first_k_dense_replace": first_dense,
                       "routed_scaling_factor": self.routed_scaling_factor, "use_qk_norm": self.use_qk_norm,
                       "partial_rotary_factor": self.partial_rotary_factor})
-            d["rope_parameters"]["partial_rotary_factor"] = self.partial_rotary_factor
+            if self.family == "glm4_moe":
+                d["rope_parameters"]["partial_rotary_factor"] = self.partial_rotary_factor
+            else:
+                for key in ("use_qk_norm", "partial_rotary_factor"):
+                    d.pop(key)
+                d.update({"kv_lora_rank": self.kv_lora_rank, "q_lora_rank": self.q_lora_rank or None,
+                          "qk_nope_head_dim": self.qk_nope_head_dim, "qk_rope_head_dim": self.qk_rope_head_dim,
+                          "v_head_dim": self.v_head_dim, "rope_interleave": self.rope_interleave,
+                          "head_dim": self.qk_rope_head_dim})
         elif self.family == "olmoe":
             d.update({"num_experts": self.num_experts, "num_experts_per_tok": self.num_experts_per_tok,
                       "norm_topk_prob": self.norm_topk_prob, "intermediate_size": self.moe_intermediate_size, "clip_qkv": None,
@@ -263,7 +286,18 @@ class ModelConfig:
                 scaling = None
         hd = d.get("head_dim") or d["hidden_size"] // d["num_attention_heads"]
         extra = {}
-        if mt == "glm4_moe":
+        if mt == "deepseek_v3":
+            n_exp, width, dense_width = d["n_routed_experts"], d["moe_intermediate_size"], d["intermediate_size"]
+            topk, renorm = d.get("num_experts_per_tok", 8), d.get("norm_topk_prob", True)
+            hd = int(d.get("qk_rope_head_dim", 64))            # the rotary table is built for the rotary slice
+            extra = dict(score_function="sigmoid", router_bias=True, n_group=int(d.get("n_group", 1)),
+                         topk_group=int(d.get("topk_group", 1)), routed_scaling_factor=float(d.get("routed_scaling_factor", 1.0)),
+                         shared_expert_intermediate_size=int(d.get("n_shared_experts", 0) or 0) * width,
+                         mlp_only_layers=list(range(int(d.get("first_k_dense_replace", 0)))), use_qk_norm=False,
+                         kv_lora_rank=int(d["kv_lora_rank"]), q_lora_rank=int(d.get("q_lora_rank") or 0),
+                         qk_nope_head_dim=int(d["qk_nope_head_dim"]), qk_rope_head_dim=hd, v_head_dim=int(d["v_head_dim"]),
+                         rope_interleave=bool(d.get("rope_interleave", True)))
+        elif mt == "glm4_moe":
             n_exp, width, dense_width = d["n_routed_experts"], d["moe_intermediate_size"], d["intermediate_size"]
             topk, renorm = d.get("num_experts_per_tok", 8), d.get("norm_topk_prob", True)
             extra = dict(partial_rotary_factor=float(d.get("partial_rotary_factor", rp.get("partial_rotary_factor", 0.5))),

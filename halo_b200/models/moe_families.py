@@ -60,8 +60,10 @@ for _s in (
     MoEFamilySpec("qwen3_next", SEPARATE_GLU, shared_experts=True, missing="gated-delta-net linear-attention layers"),
     MoEFamilySpec("qwen4_exp", FUSED, shared_experts=True, missing="block-sparse attention"),
     MoEFamilySpec("gpt_oss", INTERLEAVED_GLU, activation="gptoss", expert_bias=True, router_name="mlp.router", runnable=True),
+    MoEFamilySpec("deepseek_v3", SEPARATE_GLU, score_function="sigmoid", selection_bias=True, routed_scaling_factor=2.5,
+                  grouped_topk=True, shared_experts=True, runnable=True),
     MoEFamilySpec("deepseek_v4", SEPARATE_GLU, score_function="sigmoid", selection_bias=True, routed_scaling_factor=2.5,
-                  grouped_topk=True, shared_experts=True, missing="multi-head latent attention, hyper-connections"),
+                  grouped_topk=True, shared_experts=True, missing="its compressed sparse attention (latent attention and hyper-connections are built: see deepseek_v3)"),
     MoEFamilySpec("glm4_moe", SEPARATE_GLU, score_function="sigmoid", selection_bias=True, grouped_topk=True,
                   shared_experts=True, runnable=True),
     MoEFamilySpec("glm5_next", SEPARATE_GLU, score_function="sigmoid", selection_bias=True, shared_experts=True,

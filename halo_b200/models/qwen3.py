@@ -389,7 +389,12 @@ class DecoderLayer(nn.Module):
         H = cfg.hidden_size
         self.input_layernorm = nn.Parameter(torch.ones(H, dtype=dtype, device=device))
         self.post_attention_layernorm = nn.Parameter(torch.ones(H, dtype=dtype, device=device))
-        self.self_attn = Attention(cfg, dtype, device, tp_size, idx)
+        if cfg.kv_lora_rank:
+            from .latent_attention import LatentAttention
+
+            self.self_attn = LatentAttention(cfg, dtype, device, tp_size, idx)
+        else:
+            self.self_attn = Attention(cfg, dtype, device, tp_size, idx)
         if cfg.layer_is_moe(idx):
             # attention-only tensor parallelism for MoE layers: router and experts see this rank's token shard
             self.mlp = SparseMoE(cfg, dtype, device, n_local_experts, router_dtype, etp)

@@ -216,5 +216,8 @@ def reject_model_layout(pc, model_cfg, packed: bool = True) -> None:
         if cut:
             raise ConfigError(f"{model_cfg.family}: attention sinks and experts with bias vectors run whole on every rank "
                               f"(data parallelism and pipeline stages only); drop {', '.join(cut)}")
+    if getattr(model_cfg, "kv_lora_rank", 0) and (pc.tp_size > 1 or pc.cp_size > 1):
+        raise ConfigError(f"{model_cfg.family}: latent attention runs on whole rows with all heads on every rank; drop "
+                          f"tensor_parallel_size / context_parallel_size (expert and pipeline parallelism are fine)")
     if pc.pp_size > 1 and model_cfg.num_hidden_layers < pc.pp_size:
         raise ConfigError(f"{model_cfg.num_hidden_layers} layers cannot fill {pc.pp_size} pipeline stages")

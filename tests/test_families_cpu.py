@@ -34,6 +34,10 @@ def family_config(family: str, **kw) -> ModelConfig:
     if family == "glm4_moe":
         base.update(num_experts=8, partial_rotary_factor=0.5, score_function="sigmoid", router_bias=True, n_group=2, topk_group=1,
                     routed_scaling_factor=1.5, shared_expert_intermediate_size=96, mlp_only_layers=[0], use_qk_norm=True)
+    if family == "deepseek_v3":
+        base.update(num_experts=8, score_function="sigmoid", router_bias=True, n_group=2, topk_group=1, routed_scaling_factor=2.5,
+                    shared_expert_intermediate_size=96, mlp_only_layers=[0], use_qk_norm=False, num_key_value_heads=4, head_dim=16,
+                    kv_lora_rank=32, q_lora_rank=48, qk_nope_head_dim=24, qk_rope_head_dim=16, v_head_dim=20)
     if family == "gpt_oss":
         base.update(intermediate_size=96, sliding_window=16, layer_types=["sliding_attention", "full_attention"], attention_sinks=True,
                     output_bias=True, router_logit_bias=True, expert_bias=True, expert_activation="clamped_glu", rms_norm_eps=1e-5,
@@ -53,7 +57,9 @@ CASES = [("mistral", {"sliding_window": 16}), ("qwen2", {"sliding_window": 24}),
          ("qwen2", {"sliding_window": 12, "layer_types": ["full_attention", "sliding_attention"]}), ("llama", {}), ("llama", {"rope_scaling": LLAMA3}), ("llama", {"attention_bias": True}), ("mistral", {}),
          ("qwen2", {}), ("qwen2", {"rope_scaling": YARN}), ("mixtral", {}), ("qwen2_moe", {}), ("olmoe", {}),
          ("glm4_moe", {}), ("glm4_moe", {"n_group": 4, "topk_group": 2, "use_qk_norm": False, "attention_bias": True}),
-         ("gpt_oss", {})]
+         ("gpt_oss", {}), ("deepseek_v3", {}), ("deepseek_v3", {"q_lora_rank": 0, "rope_interleave": False}),
+         ("deepseek_v3", {"rope_scaling": {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 64, "mscale": 1.0,
+                                           "mscale_all_dim": 1.0, "beta_fast": 32.0, "beta_slow": 1.0}})]
 
 
 @pytest.mark.parametrize("family,extra", CASES, ids=[f"{f}-{'-'.join(e) or 'plain'}" for f, e in CASES])
@@ -61,6 +67,12 @@ def test_family_round_trip_through_transformers(tmp_path, family, extra):
     transformers = pytest.importorskip("transformers")
     cfg = family_config(family, **extra)
     model = build_model(cfg, device="cpu", seed=5, gradient_checkpointing=False)
+    if cfg.kv_lora_rank:
+        with torch.no_grad():
+            for layer in model.layers:       # all-ones norm weights would hide a misplaced norm
+                layer.self_attn.kv_a_norm.normal_(1.0, 0.2, generator=torch.Generator().manual_seed(29))
+                if cfg.q_lora_rank:
+                    layer.self_attn.q_a_norm.normal_(1.0, 0.2, generator=torch.Generator().manual_seed(31))
     if cfg.use_qk_norm:
         with torch.no_grad():
             for layer in model.layers:       # all-ones norm weights would hide a wrong norm scope
@@ -215,3 +227,31 @@ def test_keys_visited_follow_each_layers_window():
     assert attention_flops(cfg, cu) == 12.0 * cfg.head_dim * cfg.num_attention_heads * (windowed + full)
     plain = family_config("llama")
     assert keys_visited_per_layer(plain, cu) == [full] * 2
+
+
+@pytest.mark.parametrize("streams", [1, 2])
+def test_latent_attention_model_trains(streams):
+    """DeepSeek-V3 shape (latent attention, sigmoid group-limited routing, shared experts, a leading dense layer) takes
+    optimizer steps under per-layer recomputation - also on two hyper-connected residual streams; layouts that would cut
+    the attention block are refused by name."""
+    from halo_b200.config_validation import ConfigError
+    from halo_b200.data.packing import synthetic_packed_batch
+    from halo_b200.parallel.config import ParallelismConfig
+    from halo_b200.parallel.rules import reject_model_layout
+    from halo_b200.trainers.engine import TrainEngine
+
+    cfg = family_config("deepseek_v3", hc_mult=streams)
+    model = build_model(cfg, device="cpu", seed=2, gradient_checkpointing=True)
+    assert sum(p.numel() for p in model.parameters()) == cfg.param_counts()["total"]
+    engine = TrainEngine(model, torch.optim.AdamW(model.parameters(), lr=3e-3), "cpu", max_grad_norm=1.0)
+    batch = synthetic_packed_batch(96, cfg.vocab_size, seed=0, lo=20, hi=50)
+    before = {n: p.detach().clone() for n, p in model.named_parameters()}
+    losses = [float(engine.train_step(batch).loss.reshape(-1)[0]) for _ in range(6)]
+    assert losses[-1] < losses[0] - 0.3, losses
+    moved = {n for n, p in model.named_parameters() if not torch.equal(p, before[n])}
+    for name in ("q_a_proj", "q_a_norm", "q_b_proj", "kv_a_proj", "kv_a_norm", "kv_b_proj", "o_proj"):
+        assert f"layers.1.self_attn.{name}" in moved, name
+    for axis in ("tp_size", "cp_size"):
+        with pytest.raises(ConfigError, match="latent attention"):
+            reject_model_layout(ParallelismConfig(world_size=2, **{axis: 2}), cfg)
+    reject_model_layout(ParallelismConfig(world_size=2, ep_size=2), cfg)

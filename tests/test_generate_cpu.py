@@ -40,9 +40,18 @@ def sink_cfg():
                        expert_activation="clamped_glu", max_position_embeddings=64)
 
 
-@pytest.mark.parametrize("kind", ["dense", "moe", "windowed", "sinks"])
+def latent_cfg():
+    """DeepSeek-V3 style: latent attention (query width 24 + 16, value width 20), sigmoid routing, a shared expert."""
+    return ModelConfig(vocab_size=128, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4, head_dim=16,
+                       intermediate_size=96, moe_intermediate_size=48, num_experts=4, num_experts_per_tok=2, model_type="deepseek_v3",
+                       use_qk_norm=False, score_function="sigmoid", router_bias=True, shared_expert_intermediate_size=48,
+                       mlp_only_layers=[0], kv_lora_rank=32, q_lora_rank=24, qk_nope_head_dim=24, qk_rope_head_dim=16, v_head_dim=20,
+                       max_position_embeddings=64)
+
+
+@pytest.mark.parametrize("kind", ["dense", "moe", "windowed", "sinks", "latent"])
 def test_cached_decoding_equals_the_full_forward(kind):
-    cfg = {"dense": dense_cfg, "windowed": windowed_cfg, "sinks": sink_cfg,
+    cfg = {"dense": dense_cfg, "windowed": windowed_cfg, "sinks": sink_cfg, "latent": latent_cfg,
            "moe": lambda: dataclasses.replace(tiny_moe_config(), num_hidden_layers=2, vocab_size=128)}[kind]()
     model = build_model(cfg, device="cpu", seed=7, gradient_checkpointing=False)
     if kind == "sinks":
