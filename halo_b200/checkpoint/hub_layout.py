@@ -59,7 +59,21 @@ def whole_bank_source(name: str, cfg, first_layer: int = 0):
 SHARED_EXPERT_NAMES = {"glm4_moe": "shared_experts", "deepseek_v3": "shared_experts"}
 
 
+LAYER_NORMS = ("input_layernorm", "post_attention_layernorm", "pre_feedforward_layernorm", "post_feedforward_layernorm")
+
+
+def stored_with_unit_offset(name: str, cfg) -> bool:
+    """Gemma stores every RMSNorm weight as ``w - 1`` (the module multiplies by ``1 + weight``); at run time the norms
+    are plain, so the loader adds the one back and the writer takes it off."""
+    if not getattr(cfg, "norm_unit_offset", False):
+        return False
+    m = _LAYER.match(name)
+    return name == "norm" or bool(m and m.group(2) in LAYER_NORMS + ("self_attn.q_norm", "self_attn.k_norm"))
+
+
 def runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, expert_offset: int = 0) -> dict:
+    if stored_with_unit_offset(name, cfg):
+        tensor = tensor - 1
     """One runtime tensor -> {hub name: tensor}. ``first_layer``: global index of ``layers.0`` (pipeline
     stages); ``expert_offset``: global index of local expert 0 (expert-parallel shards)."""
     if name == "embed_tokens":
@@ -86,7 +100,7 @@ def runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, e
     li, rest = int(m.group(1)) + first_layer, m.group(2)
     pre = f"model.layers.{li}."
     D, Hq, Hkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
-    if rest in ("input_layernorm", "post_attention_layernorm"):
+    if rest in LAYER_NORMS:
         return {pre + rest + ".weight": tensor}
     if rest.startswith(("attn_hc.", "ffn_hc.")):       # hyper-connection parameters keep their names
         return {pre + rest: tensor}

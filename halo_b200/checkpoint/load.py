@@ -12,7 +12,7 @@ import os
 import torch
 from safetensors import safe_open
 
-from .hub_layout import hub_sources, whole_bank_source
+from .hub_layout import hub_sources, stored_with_unit_offset, whole_bank_source
 from .writing import INDEX_NAME, SINGLE_NAME
 
 
@@ -93,6 +93,8 @@ def load_model_weights(model, directory: str, strict: bool = True) -> dict:
             if tuple(t.shape) != tuple(dst.shape):
                 raise ValueError(f"{hub}: checkpoint shape {tuple(t.shape)} does not fit {tuple(dst.shape)}")
             dst.copy_(t.to(dst.dtype))
+            if stored_with_unit_offset(name, cfg):
+                dst.add_(1)
             loaded += 1
     index.close()
     if strict and missing:

@@ -127,14 +127,14 @@ def cached_attention(attn, h, ctx):
     cfg, cache = attn.cfg, ctx.kv_cache
     Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
     qkv = attn._qkv(h)
-    q, k = qk_norm_rope(qkv, attn.q_norm, attn.k_norm, ctx.rope, Hq, Hkv, cfg.rms_norm_eps, cfg.use_qk_norm)
+    q, k = qk_norm_rope(qkv, attn.q_norm, attn.k_norm, attn.rope_of(ctx), Hq, Hkv, cfg.rms_norm_eps, cfg.use_qk_norm)
     v = qkv[:, (Hq + Hkv) * D:]
     li = cache.write(k, v)
-    special = attn.window or attn.sinks is not None
+    special = attn.window or attn.sinks is not None or attn.scale is not None
     if special and cache.mode == "prefill":
         o = attn.masked_core(q, k, v, ctx)
     elif special:
-        o = cache.attend(li, q, Hq, window=attn.window, sinks=attn.sinks)
+        o = cache.attend(li, q, Hq, scale=attn.scale, window=attn.window, sinks=attn.sinks)
     elif cache.mode == "prefill":
         if q.is_cuda and D != 128:
             o = attn_ops.attention_reference(q, k, v, ctx.plan.cu_seqlens, Hq, Hkv)
@@ -240,6 +240,7 @@ class Generator:
                 break
             cache.begin_decode()
             dctx = ForwardContext(None, m.rope(cache.lengths), m.transport)
+            dctx.rope_local = m.rope_local(cache.lengths)
             dctx.kv_cache = cache
             dctx.routing_trace = trace
             trunk = m.trunk_states(tok, dctx)

@@ -1,7 +1,8 @@
 """Architecture description of the decoder families built here, convertible to and from a Hugging Face
 ``config.json``: Qwen3 and Qwen3-MoE (per-head q/k norm), Qwen2 (biased q/k/v projections), Qwen2-MoE (gated
-shared expert), Llama and Mistral (plain pre-norm decoder, optional rotary scaling) and Mixtral (top-k of
-softmax, ``block_sparse_moe`` names on the hub).
+shared expert), Llama and Mistral (plain pre-norm decoder, optional rotary scaling), Mixtral (top-k of
+softmax, ``block_sparse_moe`` names on the hub), OLMoE, GLM-4-MoE, gpt-oss (sinks, biased clamped-GLU experts),
+DeepSeek-V3 (latent attention) and Gemma 3 (windowed / full layer mix, four norms per layer).
 
 The named presets are the shapes of the benchmark configurations: a tiny MoE for CPU plumbing
 tests, the dense 9B class, the 30B-A3B MoE and the ~120B-total shared-expert MoE.
@@ -34,6 +35,9 @@ FAMILIES = {
     # a clamped GLU in the experts, a biased router that takes the softmax of the top-k logits
     # multi-head latent attention (queries and keys / values through low-rank bottlenecks, rotary embedding on a separate
     # slice shared by all heads) in front of the sigmoid-routed, group-limited MoE with shared experts
+    # Gemma 3 (text): five windowed layers per full one with their own rotary base, norms before AND after both blocks
+    # with weights stored as (w - 1), tanh-GELU gating, embeddings scaled by sqrt(hidden), a configured softmax scale
+    "gemma3_text": dict(architecture="Gemma3ForCausalLM", moe=False, qk_norm=True, bias_key=True, bias_default=False, has_window=True),
     "deepseek_v3": dict(architecture="DeepseekV3ForCausalLM", moe=True, qk_norm=False, bias_key=True, bias_default=False, has_window=False),
     "gpt_oss": dict(architecture="GptOssForCausalLM", moe=True, qk_norm=False, bias_key=True, bias_default=True, has_window=True),
 }
@@ -68,6 +72,12 @@ class ModelConfig:
     topk_group: int = 1
     routed_scaling_factor: float = 1.0
     sliding_window: int = 0                # > 0: every query sees only its last ``sliding_window`` keys (Mistral-style)
+    hidden_activation: str = "silu"        # gate activation of the dense feed-forward block: "silu" | "gelu_tanh"
+    sandwich_norms: bool = False           # an RMSNorm on the output of each block too (Gemma): four norms per layer
+    norm_unit_offset: bool = False         # the checkpoint stores norm weights as (w - 1); at run time they are plain weights
+    embedding_multiplier: float = 1.0      # token embeddings are scaled by this (Gemma: sqrt(hidden_size))
+    query_pre_attn_scalar: int = 0         # softmax scale = this ** -0.5 (0 = head_dim)
+    rope_local_theta: float = 0.0          # rotary base of the windowed layers when it differs from the full layers' (0 = the same)
     kv_lora_rank: int = 0                  # > 0: multi-head latent attention (DeepSeek); keys / values come from this many latent dims
     q_lora_rank: int = 0                   # latent dims of the query bottleneck (0 = one plain query projection)
     qk_nope_head_dim: int = 0              # per head: dims of q / k without rotary embedding ...
@@ -118,7 +128,7 @@ class ModelConfig:
                     + self.kv_lora_rank * Hq * (self.qk_nope_head_dim + self.v_head_dim) + Hq * self.v_head_dim * H + 2 * H)
         else:
             attn = (H * self.qkv_dim + self.num_attention_heads * D * H + (norm_width if self.use_qk_norm else 0) + 2 * H
-                    + (self.qkv_dim if self.attention_bias else 0) + (H if self.output_bias else 0)
+                    + (2 * H if self.sandwich_norms else 0) + (self.qkv_dim if self.attention_bias else 0) + (H if self.output_bias else 0)
                     + (self.num_attention_heads if self.attention_sinks else 0))
         dense_mlp = 3 * H * self.intermediate_size
         expert = 3 * H * self.moe_intermediate_size + ((2 * self.moe_intermediate_size + H) if self.expert_bias else 0)
@@ -202,7 +212,17 @@ class ModelConfig:
                 d["max_window_layers"] = first_windowed if self.sliding_window else self.num_hidden_layers
                 if self.sliding_window and self.layer_types:
                     d["layer_types"] = list(self.layer_types)
-        if self.family == "gpt_oss":
+        if self.family == "gemma3_text":
+            for key in ("hidden_act", "rope_theta", "rope_scaling"):
+                d.pop(key, None)
+            full = d.pop("rope_parameters")
+            d.update({"hidden_activation": "gelu_pytorch_tanh", "query_pre_attn_scalar": self.query_pre_attn_scalar or self.head_dim,
+                      "attn_logit_softcapping": None, "final_logit_softcapping": None,
+                      "layer_types": list(self.layer_types or ["sliding_attention" if self.sliding_window else "full_attention"]
+                                          * self.num_hidden_layers),
+                      "rope_parameters": {"full_attention": full, "sliding_attention": {
+                          "rope_type": "default", "rope_theta": self.rope_local_theta or self.rope_theta}}})
+        elif self.family == "gpt_oss":
             d.update({"num_local_experts": self.num_experts, "num_experts_per_tok": self.num_experts_per_tok,
                       "intermediate_size": self.moe_intermediate_size, "router_aux_loss_coef": self.router_aux_loss_coef,
                       "output_router_logits": False, "swiglu_limit": self.glu_limit,
@@ -277,6 +297,10 @@ class ModelConfig:
             else:
                 kinds = ["full_attention"] * first + ["sliding_attention"] * (d["num_hidden_layers"] - first)
         rp = d.get("rope_parameters") or {}
+        local_theta = 0.0
+        if "full_attention" in rp:             # one entry per layer kind (Gemma 3)
+            local_theta = float((rp.get("sliding_attention") or {}).get("rope_theta", 0.0))
+            rp = rp["full_attention"]
         rope_theta = d.get("rope_theta") or rp.get("rope_theta", 1e6 if mt.startswith("qwen") else 1e4)
         scaling = d.get("rope_scaling") or ({k: v for k, v in rp.items() if k not in ("rope_theta", "partial_rotary_factor")} if rp else None)
         if scaling:
@@ -305,6 +329,23 @@ class ModelConfig:
                          topk_group=int(d.get("topk_group", 1)), routed_scaling_factor=float(d.get("routed_scaling_factor", 1.0)),
                          shared_expert_intermediate_size=int(d.get("n_shared_experts", 0) or 0) * width,
                          mlp_only_layers=list(range(int(d.get("first_k_dense_replace", 0)))), use_qk_norm=bool(d.get("use_qk_norm", False)))
+        elif mt == "gemma3_text":
+            if d.get("attn_logit_softcapping") or d.get("final_logit_softcapping"):
+                raise ValueError("a Gemma checkpoint with logit soft-capping: tanh capping of scores / logits is not built")
+            if d.get("use_bidirectional_attention"):
+                raise ValueError("bidirectional attention is not built")
+            n_exp, width, dense_width = 0, 0, d["intermediate_size"]
+            topk, renorm = 8, True
+            kinds = list(d.get("layer_types") or ["full_attention" if (i + 1) % 6 == 0 else "sliding_attention"
+                                                   for i in range(d["num_hidden_layers"])])
+            if "sliding_attention" not in kinds:
+                window = 0
+            theta = float(rp.get("rope_theta", 1e6))
+            extra = dict(layer_types=kinds if window else None, hidden_activation="gelu_tanh", sandwich_norms=True, norm_unit_offset=True,
+                         embedding_multiplier=float(d["hidden_size"]) ** 0.5,
+                         query_pre_attn_scalar=int(d.get("query_pre_attn_scalar", 256)),
+                         rope_local_theta=local_theta if window and local_theta != theta else 0.0,
+                         tie_word_embeddings=d.get("tie_word_embeddings", True))
         elif mt == "gpt_oss":
             n_exp, width, dense_width = d.get("num_local_experts", 128), d["intermediate_size"], d["intermediate_size"]
             topk, renorm = d.get("num_experts_per_tok", 4), True

@@ -102,8 +102,9 @@ class Attention(nn.Module):
         # the window of this layer: families that alternate windowed and full layers name each layer's kind
         kinds = cfg.layer_types
         self.window = cfg.sliding_window if (not kinds or layer_idx >= len(kinds) or kinds[layer_idx] == "sliding_attention") else 0
-        if (cfg.attention_sinks or cfg.output_bias) and tp_size > 1:
-            raise ValueError("attention sinks and an output-projection bias are not cut over tensor-parallel ranks")
+        if (cfg.attention_sinks or cfg.output_bias or self.window or (cfg.query_pre_attn_scalar or cfg.head_dim) != cfg.head_dim) and tp_size > 1:
+            raise ValueError("attention sinks, an output-projection bias, a sliding window and a configured softmax scale are not "
+                             "cut over tensor-parallel ranks")
         H, D = cfg.hidden_size, cfg.head_dim
         # under tensor parallelism a rank holds 1/tp of the query and of the key/value heads
         self.n_heads, self.n_kv_heads = cfg.num_attention_heads // tp_size, cfg.num_key_value_heads // tp_size
@@ -118,6 +119,9 @@ class Attention(nn.Module):
                 self.qkv_bias.tp_kind = "qkv_bias"
         else:
             self.register_parameter("qkv_bias", None)
+        # a configured softmax scale (Gemma's query_pre_attn_scalar); None = head_dim ** -0.5, which the flash kernel uses
+        qpas = cfg.query_pre_attn_scalar
+        self.scale = float(qpas) ** -0.5 if qpas and qpas != D else None
         self.o_bias = nn.Parameter(torch.zeros(H, dtype=dtype, device=device)) if cfg.output_bias else None
         self.sinks = nn.Parameter(torch.zeros(self.n_heads, dtype=dtype, device=device)) if cfg.attention_sinks else None
         self.lora = None          # halo_b200.peft.lora.LoraSet when low-rank adapters are attached
@@ -132,6 +136,11 @@ class Attention(nn.Module):
             self.register_parameter("q_norm", None)
             self.register_parameter("k_norm", None)
 
+    def rope_of(self, ctx):
+        """The rotary table of this layer: windowed layers of a family with a local rotary base have their own."""
+        local = getattr(ctx, "rope_local", None)
+        return local if (self.window and local is not None) else ctx.rope
+
     def _biased(self, qkv):
         return qkv if self.qkv_bias is None else qkv + self.qkv_bias
 
@@ -143,7 +152,7 @@ class Attention(nn.Module):
 
         cfg = self.cfg
         Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
-        q, k = qk_norm_rope(qkv, self.q_norm, self.k_norm, ctx.rope, Hq, Hkv, cfg.rms_norm_eps, cfg.use_qk_norm)
+        q, k = qk_norm_rope(qkv, self.q_norm, self.k_norm, self.rope_of(ctx), Hq, Hkv, cfg.rms_norm_eps, cfg.use_qk_norm)
         v = qkv[:, (Hq + Hkv) * D:]
         return self.masked_core(q, k, v, ctx)
 
@@ -170,7 +179,7 @@ class Attention(nn.Module):
             mask = ctx.causal
         elif mask.device != q.device:
             mask = ctx.attention_mask = mask.to(q.device)
-        o = masked_attention(q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D), mask, sinks=self.sinks)
+        o = masked_attention(q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D), mask, scale=self.scale, sinks=self.sinks)
         return o.reshape(T, Hq * D)
 
     def _qkv(self, h):
@@ -202,7 +211,7 @@ class Attention(nn.Module):
                                         cfg.rms_norm_eps, cfg.use_qk_norm)
             return row_parallel_linear(o, self.o_proj, ctx.tp)
         qkv = self._qkv(h)
-        if self.window or self.sinks is not None or getattr(ctx, "attention_mask", None) is not None:
+        if self.window or self.sinks is not None or self.scale is not None or getattr(ctx, "attention_mask", None) is not None:
             return self._out(self._masked(qkv, ctx))
         if ctx.cp is not None:
             # context parallel: this rank holds one chunk of the row; keys and values of straddling documents
@@ -233,8 +242,19 @@ class DenseMLP(nn.Module):
             self.gate_up_proj.tp_kind, self.down_proj.tp_kind = "gate_up", "down"
         self.lora = None          # halo_b200.peft.lora.LoraSet when low-rank adapters are attached
         self.lowp = ""            # block-scaled format of quantisation-aware training
+        self.activation = "silu"  # "gelu_tanh": Gemma's gate; runs as tensor ops between the two GEMMs
 
     def forward(self, h, ctx=None):
+        if self.activation != "silu":
+            if self.tp_size > 1 or self.lowp:
+                raise NotImplementedError("the tanh-GELU gate is built for unsliced, full-precision feed-forward blocks")
+            width = self.gate_up_proj.shape[0] // 2
+            pre = gemm.linear(h, self.gate_up_proj)
+            if self.lora is not None:
+                pre = self.lora.add_fused(h, pre, [("gate_proj", 0, width), ("up_proj", width, 2 * width)])
+            act = torch.nn.functional.gelu(pre[:, :width], approximate="tanh") * pre[:, width:]
+            y = gemm.linear(act, self.down_proj)
+            return y + self.lora.delta("down_proj", act) if self.lora is not None and "down_proj" in self.lora else y
         if self.lowp and self.lora is None and self.tp_size == 1:
             act = _SwiGLULinear.apply(_rounded(h, self.lowp), _rounded(self.gate_up_proj, self.lowp), torch.is_grad_enabled())
             return _linear(act, self.down_proj, self.lowp)
@@ -401,12 +421,23 @@ class DecoderLayer(nn.Module):
             self.mlp.layer_index = idx
         else:
             self.mlp = DenseMLP(H, cfg.intermediate_size, dtype, device, tp_size)
+            self.mlp.activation = cfg.hidden_activation
+        # Gemma: each block's output is normed as well before it joins the residual (``post_attention_layernorm`` is then
+        # the norm of the attention OUTPUT, and the feed-forward block has its own pair)
+        self.sandwich = cfg.sandwich_norms
+        if self.sandwich:
+            if cfg.hc_mult > 1:
+                raise ValueError("output norms and hyper-connections are not combined")
+            self.pre_feedforward_layernorm = nn.Parameter(torch.ones(H, dtype=dtype, device=device))
+            self.post_feedforward_layernorm = nn.Parameter(torch.ones(H, dtype=dtype, device=device))
         self.eps = cfg.rms_norm_eps
         # "full": the whole layer is re-run in the backward pass; "mlp": the attention half keeps its
         # activations (about 30 KB per token) and only the feed-forward half is re-run; "none": nothing is re-run
         self.recompute_policy = "full"
 
     def forward(self, x, ctx):
+        if self.sandwich:
+            return self.mlp_half(self.attention_half(x, ctx), ctx)
         h = rms_norm(x, self.input_layernorm, self.eps)
         a = self.self_attn(h, ctx)
         h2, x2 = add_rms_norm(a, x, self.post_attention_layernorm, self.eps)
@@ -414,9 +445,13 @@ class DecoderLayer(nn.Module):
         return x2 + m
 
     def attention_half(self, x, ctx):
-        return x + self.self_attn(rms_norm(x, self.input_layernorm, self.eps), ctx)
+        a = self.self_attn(rms_norm(x, self.input_layernorm, self.eps), ctx)
+        return x + (rms_norm(a, self.post_attention_layernorm, self.eps) if self.sandwich else a)
 
     def mlp_half(self, x2, ctx):
+        if self.sandwich:
+            m = self.mlp(rms_norm(x2, self.pre_feedforward_layernorm, self.eps), ctx)
+            return x2 + rms_norm(m, self.post_feedforward_layernorm, self.eps)
         return x2 + self.mlp(rms_norm(x2, self.post_attention_layernorm, self.eps), ctx)
 
 
@@ -477,6 +512,7 @@ class ForwardContext:
         self.output_unused = False   # set while a layer is re-run only to rebuild its graph
         self.kv_cache = None         # halo_b200.inference.generate.KVCache while sampling
         self.attention_mask = None   # bool [T, T]: an explicit mask (tree packing) served by the masked-attention op
+        self.rope_local = None       # rotary table of the windowed layers when their base differs (Gemma 3)
 
 
 class Qwen3Model(nn.Module):
@@ -602,7 +638,17 @@ class Qwen3Model(nn.Module):
             layout, plan = self.context_parallel.layout_and_plan(cu_seqlens)
             return ForwardContext(plan, rope, self.transport, record_routing, replay_topk, (self.context_parallel, layout))
         plan = attn_ops.build_plan(cu_seqlens, device=dev)
-        return ForwardContext(plan, rope, self.transport, record_routing, replay_topk, tp=self.tensor_parallel)
+        ctx = ForwardContext(plan, rope, self.transport, record_routing, replay_topk, tp=self.tensor_parallel)
+        ctx.rope_local = self.rope_local(position_ids)
+        return ctx
+
+    def rope_local(self, position_ids):
+        """The windowed layers' own table (their rotary base, no scaling), or None when they share the full layers'."""
+        if not self.cfg.rope_local_theta:
+            return None
+        exact = next(self.parameters()).dtype == torch.float32 and not position_ids.is_cuda
+        return rope_table(position_ids, self.cfg.head_dim, self.cfg.rope_local_theta, None, self.cfg.max_position_embeddings,
+                          round_bf16=not exact)
 
     def rope(self, position_ids):
         """cos / sin table of these positions, in the rounding of the model's dtype."""
@@ -617,7 +663,10 @@ class Qwen3Model(nn.Module):
 
     def embed(self, input_ids):
         self._gate([self.embed_tokens])
-        return torch.nn.functional.embedding(input_ids.reshape(-1), self.embed_tokens)
+        x = torch.nn.functional.embedding(input_ids.reshape(-1), self.embed_tokens)
+        if self.cfg.embedding_multiplier != 1.0:
+            x = x * torch.tensor(self.cfg.embedding_multiplier, dtype=x.dtype, device=x.device)     # rounded to the model's dtype first
+        return x
 
     def run_layers(self, x, ctx):
         for layer in self.layers:

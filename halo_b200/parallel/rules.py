@@ -216,6 +216,12 @@ def reject_model_layout(pc, model_cfg, packed: bool = True) -> None:
         if cut:
             raise ConfigError(f"{model_cfg.family}: attention sinks and experts with bias vectors run whole on every rank "
                               f"(data parallelism and pipeline stages only); drop {', '.join(cut)}")
+    masked_only = [what for what, on in (("a sliding window", getattr(model_cfg, "sliding_window", 0)),
+                                         ("a configured softmax scale", (getattr(model_cfg, "query_pre_attn_scalar", 0) or model_cfg.head_dim) != model_cfg.head_dim),
+                                         ("a tanh-GELU gate", getattr(model_cfg, "hidden_activation", "silu") != "silu")) if on]
+    if masked_only and (pc.tp_size > 1 or pc.cp_size > 1):
+        raise ConfigError(f"{model_cfg.family}: {', '.join(masked_only)} run on whole rows with all heads on every rank; drop "
+                          f"tensor_parallel_size / context_parallel_size")
     if getattr(model_cfg, "kv_lora_rank", 0) and (pc.tp_size > 1 or pc.cp_size > 1):
         raise ConfigError(f"{model_cfg.family}: latent attention runs on whole rows with all heads on every rank; drop "
                           f"tensor_parallel_size / context_parallel_size (expert and pipeline parallelism are fine)")

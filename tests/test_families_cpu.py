@@ -34,6 +34,10 @@ def family_config(family: str, **kw) -> ModelConfig:
     if family == "glm4_moe":
         base.update(num_experts=8, partial_rotary_factor=0.5, score_function="sigmoid", router_bias=True, n_group=2, topk_group=1,
                     routed_scaling_factor=1.5, shared_expert_intermediate_size=96, mlp_only_layers=[0], use_qk_norm=True)
+    if family == "gemma3_text":
+        base.update(num_hidden_layers=3, sliding_window=16, layer_types=["sliding_attention", "sliding_attention", "full_attention"],
+                    hidden_activation="gelu_tanh", sandwich_norms=True, norm_unit_offset=True, embedding_multiplier=128 ** 0.5,
+                    query_pre_attn_scalar=24, rope_local_theta=500.0, tie_word_embeddings=True)
     if family == "deepseek_v3":
         base.update(num_experts=8, score_function="sigmoid", router_bias=True, n_group=2, topk_group=1, routed_scaling_factor=2.5,
                     shared_expert_intermediate_size=96, mlp_only_layers=[0], use_qk_norm=False, num_key_value_heads=4, head_dim=16,
@@ -57,7 +61,8 @@ CASES = [("mistral", {"sliding_window": 16}), ("qwen2", {"sliding_window": 24}),
          ("qwen2", {"sliding_window": 12, "layer_types": ["full_attention", "sliding_attention"]}), ("llama", {}), ("llama", {"rope_scaling": LLAMA3}), ("llama", {"attention_bias": True}), ("mistral", {}),
          ("qwen2", {}), ("qwen2", {"rope_scaling": YARN}), ("mixtral", {}), ("qwen2_moe", {}), ("olmoe", {}),
          ("glm4_moe", {}), ("glm4_moe", {"n_group": 4, "topk_group": 2, "use_qk_norm": False, "attention_bias": True}),
-         ("gpt_oss", {}), ("deepseek_v3", {}), ("deepseek_v3", {"q_lora_rank": 0, "rope_interleave": False}),
+         ("gpt_oss", {}), ("gemma3_text", {}), ("gemma3_text", {"rope_scaling": {"rope_type": "linear", "factor": 8.0}, "tie_word_embeddings": False}),
+         ("deepseek_v3", {}), ("deepseek_v3", {"q_lora_rank": 0, "rope_interleave": False}),
          ("deepseek_v3", {"rope_scaling": {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 64, "mscale": 1.0,
                                            "mscale_all_dim": 1.0, "beta_fast": 32.0, "beta_slow": 1.0}})]
 
@@ -67,6 +72,13 @@ def test_family_round_trip_through_transformers(tmp_path, family, extra):
     transformers = pytest.importorskip("transformers")
     cfg = family_config(family, **extra)
     model = build_model(cfg, device="cpu", seed=5, gradient_checkpointing=False)
+    if cfg.sandwich_norms:
+        with torch.no_grad():
+            g = torch.Generator().manual_seed(37)
+            for layer in model.layers:       # all-ones norm weights would hide a misplaced norm or a forgotten offset
+                for name in ("input_layernorm", "post_attention_layernorm", "pre_feedforward_layernorm", "post_feedforward_layernorm"):
+                    getattr(layer, name).normal_(1.0, 0.3, generator=g)
+            model.norm.normal_(1.0, 0.3, generator=g)
     if cfg.kv_lora_rank:
         with torch.no_grad():
             for layer in model.layers:       # all-ones norm weights would hide a misplaced norm
@@ -112,7 +124,8 @@ def test_family_round_trip_through_transformers(tmp_path, family, extra):
     hf.save_pretrained(d2, safe_serialization=True)
     back = from_pretrained(d2, device="cpu", dtype=torch.float32, gradient_checkpointing=False)
     for (n, a), (_, c) in zip(model.named_parameters(), back.named_parameters()):
-        assert torch.equal(a, c), n
+        # norms stored as (w - 1) come back through one fp32 subtraction and addition
+        assert torch.equal(a, c) or (cfg.norm_unit_offset and a.dim() == 1 and torch.allclose(a, c, atol=1e-6, rtol=0)), n
 
 
 @pytest.mark.parametrize("scaling", [LLAMA3, YARN, {"rope_type": "linear", "factor": 2.0}])
@@ -255,3 +268,36 @@ def test_latent_attention_model_trains(streams):
         with pytest.raises(ConfigError, match="latent attention"):
             reject_model_layout(ParallelismConfig(world_size=2, **{axis: 2}), cfg)
     reject_model_layout(ParallelismConfig(world_size=2, ep_size=2), cfg)
+
+
+def test_gemma3_trains_under_every_recomputation_policy():
+    """The four-norm layer gives the same loss and gradients whether it runs whole, in halves or under recomputation."""
+    from halo_b200.data.packing import synthetic_packed_batch
+
+    cfg = family_config("gemma3_text")
+    batch = synthetic_packed_batch(96, cfg.vocab_size, seed=0, lo=20, hi=50)
+    results = {}
+    for policy in ("none", "mlp", "full"):
+        model = build_model(cfg, device="cpu", seed=2, gradient_checkpointing=policy != "none")
+        for layer in model.layers:
+            layer.recompute_policy = policy
+        out = model(batch.input_ids, batch.position_ids, batch.cu_seqlens, batch.labels)
+        loss = out.loss if hasattr(out, "loss") else out
+        loss.sum().backward()
+        results[policy] = (loss.detach().sum(), {n: p.grad.clone() for n, p in model.named_parameters() if p.grad is not None})
+    base_loss, base_grads = results["none"]
+    from halo_b200.config_validation import ConfigError
+    from halo_b200.parallel.config import ParallelismConfig
+    from halo_b200.parallel.rules import reject_model_layout
+
+    for fam in ("gemma3_text", "mistral"):
+        with pytest.raises(ConfigError, match="whole rows"):
+            reject_model_layout(ParallelismConfig(world_size=2, tp_size=2), family_config(fam, sliding_window=16))
+    reject_model_layout(ParallelismConfig(world_size=2, tp_size=2), family_config("mistral"))
+    assert "layers.0.pre_feedforward_layernorm" in base_grads and "layers.2.post_feedforward_layernorm" in base_grads
+    for policy in ("mlp", "full"):
+        loss, grads = results[policy]
+        assert torch.allclose(loss, base_loss, atol=1e-6)
+        assert grads.keys() == base_grads.keys()
+        for n in grads:
+            assert torch.allclose(grads[n], base_grads[n], atol=1e-5), (policy, n)

@@ -49,9 +49,17 @@ def latent_cfg():
                        max_position_embeddings=64)
 
 
-@pytest.mark.parametrize("kind", ["dense", "moe", "windowed", "sinks", "latent"])
+def gemma_cfg():
+    """Gemma 3 style: windowed layers with their own rotary base, a full layer, output norms, tanh-GELU gate, scaled embeddings."""
+    return dataclasses.replace(dense_cfg(), model_type="gemma3_text", num_hidden_layers=3, sliding_window=6, max_position_embeddings=64,
+                               layer_types=["sliding_attention", "sliding_attention", "full_attention"], hidden_activation="gelu_tanh",
+                               sandwich_norms=True, norm_unit_offset=True, embedding_multiplier=8.0, query_pre_attn_scalar=24,
+                               rope_local_theta=500.0, tie_word_embeddings=True)
+
+
+@pytest.mark.parametrize("kind", ["dense", "moe", "windowed", "sinks", "latent", "gemma"])
 def test_cached_decoding_equals_the_full_forward(kind):
-    cfg = {"dense": dense_cfg, "windowed": windowed_cfg, "sinks": sink_cfg, "latent": latent_cfg,
+    cfg = {"dense": dense_cfg, "windowed": windowed_cfg, "sinks": sink_cfg, "latent": latent_cfg, "gemma": gemma_cfg,
            "moe": lambda: dataclasses.replace(tiny_moe_config(), num_hidden_layers=2, vocab_size=128)}[kind]()
     model = build_model(cfg, device="cpu", seed=7, gradient_checkpointing=False)
     if kind == "sinks":
