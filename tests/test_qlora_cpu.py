@@ -4,6 +4,7 @@ recomputation policy; only adapters remain as parameters; the SFT entry point tr
 
 import dataclasses
 import os
+import re
 import subprocess
 import sys
 
@@ -67,11 +68,12 @@ def test_quantized_base_equals_the_rounded_model(kind, policy):
         apply_lora(m, spec, seed=0)
         with torch.no_grad():
             for n, p in m.named_parameters():
-                if ".lora_B" in n or "lora_b" in n.lower():
+                if re.search(r"\.B[._]", n):
                     p.normal_(0.0, 0.05, generator=torch.Generator().manual_seed(len(n)))     # a zero B hides the adapters
         return m
 
     q, plain = make(), make()
+    assert sum(float(p.abs().sum()) > 0 for n, p in q.named_parameters() if re.search(r"\.B[._]", n)) >= 2 * cfg.num_hidden_layers
     before = {n for n, _ in q.named_parameters()}
     stats = quantize_base_weights(q, "nf4")
     assert is_quantized(q) and stats["matrices"] == (4 if kind == "dense" else 6) * cfg.num_hidden_layers
