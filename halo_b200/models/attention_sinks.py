@@ -1,5 +1,5 @@
 """What a run does with the attention sinks of a gpt-oss checkpoint (one learned logit per head that joins every
-softmax): ``neutralized`` sets them to the most negative finite value, so they take no softmax mass and get no
+softmax): ``neutralized`` sets them to (almost) the most negative finite bf16 value, so they take no softmax mass and get no
 gradient - fine-tuning then behaves like a model without sinks; ``live`` keeps the pretrained values and freezes
 them (the on-policy setting: the policy must predict like the sampler); ``trainable`` keeps and trains them.
 (The role of halo/models/attention/gpt_oss_sinks.py:1-344: ``SinksPolicy`` and ``apply_sinks_policy``.)"""
@@ -47,7 +47,8 @@ def apply_sinks_policy(model, policy: str, pretrained: bool = True) -> int:
         policy = "live"
     for _, p in sinks:
         if policy == "neutralized":
-            p.fill_(torch.finfo(p.dtype).min)
+            # just inside the bf16 range, so that a save in bf16 (or a reload in fp32) keeps it finite
+            p.fill_(0.99 * torch.finfo(torch.bfloat16).min)
         p.requires_grad_(policy == "trainable")
     setattr(model, POLICY_ATTR, policy)
     return len(sinks)

@@ -137,3 +137,38 @@ def _negative_control_worker(rank, world):
 
 def test_expert_parallel_layer_with_a_wrong_expert_negative_control():
     run_gloo_ranks(_negative_control_worker, 2, timeout=120.0)
+
+
+def _latent_family_worker(rank, world, directory):
+    """DeepSeek-V3 shape under expert parallelism 2: each rank loads its experts from a hub-layout checkpoint, and the loss
+    of the whole batch equals the undistributed model's."""
+    import torch.distributed as dist
+
+    from halo_b200.checkpoint.load import from_pretrained
+    from halo_b200.data.packing import synthetic_packed_batch
+    from halo_b200.parallel.expert_parallel import CollectiveTransport
+
+    whole = from_pretrained(directory, device="cpu", dtype=torch.float32, gradient_checkpointing=False)
+    sharded = from_pretrained(directory, device="cpu", dtype=torch.float32, gradient_checkpointing=False,
+                              transport=CollectiveTransport(dist.group.WORLD))
+    assert sharded.layers[1].mlp.experts_gate_up.shape[0] == whole.cfg.num_experts // world
+    batch = synthetic_packed_batch(64 + 16 * rank, whole.cfg.vocab_size, seed=rank, lo=8, hi=30)
+    outs = []
+    for m in (whole, sharded):
+        out = m(batch.input_ids, batch.position_ids, batch.cu_seqlens, batch.labels)
+        loss = (out.loss if hasattr(out, "loss") else out).sum()
+        loss.backward()
+        outs.append(loss.detach())
+    assert torch.allclose(outs[0], outs[1], atol=1e-5), outs
+    a, b = whole.layers[1].self_attn.kv_b_proj.grad, sharded.layers[1].self_attn.kv_b_proj.grad
+    assert torch.allclose(a, b, atol=1e-5)
+
+
+def test_latent_attention_family_under_expert_parallelism(tmp_path):
+    from halo_b200.checkpoint.save import save_model
+    from halo_b200.models.qwen3 import build_model
+    from tests.test_families_cpu import family_config
+
+    model = build_model(family_config("deepseek_v3"), device="cpu", seed=9, gradient_checkpointing=False)
+    save_model(model, str(tmp_path / "ckpt"), save_dtype=None)
+    run_gloo_ranks(_latent_family_worker, 2, args=(str(tmp_path / "ckpt"),), timeout=240.0)

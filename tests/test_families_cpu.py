@@ -301,3 +301,39 @@ def test_gemma3_trains_under_every_recomputation_policy():
         assert grads.keys() == base_grads.keys()
         for n in grads:
             assert torch.allclose(grads[n], base_grads[n], atol=1e-5), (policy, n)
+
+
+def test_sft_entry_point_fine_tunes_a_gpt_oss_checkpoint(tmp_path):
+    """From a hub-layout gpt-oss checkpoint: the default run neutralizes the sinks (and says so), ``reset_sinks: false`` with
+    ``train_sinks: true`` trains them; the saved model reloads with the policy's sinks."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = family_config("gpt_oss")
+    model = build_model(cfg, device="cpu", seed=4, gradient_checkpointing=False)
+    with torch.no_grad():
+        for layer in model.layers:
+            layer.self_attn.sinks.fill_(0.5)
+    base = str(tmp_path / "base")
+    save_model(model, base, save_dtype=None)
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+
+    def run(name, extra):
+        y = tmp_path / f"{name}.yaml"
+        y.write_text(f"model_name_or_path: {base}\ntorch_dtype: float32\ndataset_format: synthetic\npacked_row_length: 128\nmax_steps: 2\n"
+                     f"save_steps: 2\noptim: adamw_torch\nlearning_rate: 1.0e-2\nlogging_steps: 1\noutput_dir: {tmp_path}/{name}\n" + extra)
+        r = subprocess.run([sys.executable, "-m", "halo_b200.cli", "launch", "sft", str(y)], cwd=root, capture_output=True, text=True,
+                           timeout=300, env=env)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+        return r.stdout + r.stderr, from_pretrained(str(tmp_path / name / "final"), device="cpu", dtype=torch.float32)
+
+    log, tuned = run("neutral", "")
+    assert "policy neutralized" in log
+    assert all(float(layer.self_attn.sinks.detach().max()) < -1e30 for layer in tuned.layers)
+    assert torch.isfinite(tuned.layers[0].self_attn.sinks.detach().bfloat16()).all()
+    log, tuned = run("trained", "reset_sinks: false\ntrain_sinks: true\n")
+    assert "policy trainable" in log
+    sinks = torch.stack([layer.self_attn.sinks for layer in tuned.layers])
+    assert torch.isfinite(sinks).all() and float((sinks - 0.5).abs().max()) > 1e-4 and float((sinks - 0.5).abs().max()) < 0.5
