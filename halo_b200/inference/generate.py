@@ -82,14 +82,14 @@ class KVCache:
         return li
 
     def attend(self, li: int, q: torch.Tensor, n_heads: int, scale: float | None = None, window: int = 0,
-               sinks: torch.Tensor | None = None) -> torch.Tensor:
+               sinks: torch.Tensor | None = None, softcap: float = 0.0) -> torch.Tensor:
         """One query per sequence ``[B, heads * head_dim]`` against keys ``0 .. lengths[b]`` (the token just written
         included); ``window`` limits it to the last ``window`` of them and ``sinks [heads]`` adds one value-less logit
         per head to the softmax - both run as tensor operations."""
         B = q.shape[0]
         Hkv, D = self.k.shape[-2:]
         G = n_heads // Hkv
-        if q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128) and G <= 16 and not window and sinks is None:
+        if q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128) and G <= 16 and not window and sinks is None and not softcap:
             # the decode kernel streams the cache once and reads the lengths on the device (no host synchronisation)
             from halo_b200.ops import _lib
 
@@ -105,6 +105,8 @@ class KVCache:
         k, v = self.k[li, :, :upto], self.v[li, :, :upto]                 # [B, S, Hkv, D]
         qh = q.reshape(B, Hkv, G, D).float()
         scores = torch.einsum("bhgd,bshd->bhgs", qh, k.float()) * (scale if scale is not None else D ** -0.5)
+        if softcap:
+            scores = softcap * torch.tanh(scores / softcap)
         visible = torch.arange(upto, device=q.device)[None, :] <= self._cols[:, None]        # [B, S]
         if window:
             visible = visible & (torch.arange(upto, device=q.device)[None, :] > self._cols[:, None] - window)
@@ -130,11 +132,11 @@ def cached_attention(attn, h, ctx):
     q, k = qk_norm_rope(qkv, attn.q_norm, attn.k_norm, attn.rope_of(ctx), Hq, Hkv, cfg.rms_norm_eps, cfg.use_qk_norm)
     v = qkv[:, (Hq + Hkv) * D:]
     li = cache.write(k, v)
-    special = attn.window or attn.sinks is not None or attn.scale is not None
+    special = attn.window or attn.sinks is not None or attn.scale is not None or attn.softcap
     if special and cache.mode == "prefill":
         o = attn.masked_core(q, k, v, ctx)
     elif special:
-        o = cache.attend(li, q, Hq, scale=attn.scale, window=attn.window, sinks=attn.sinks)
+        o = cache.attend(li, q, Hq, scale=attn.scale, window=attn.window, sinks=attn.sinks, softcap=attn.softcap)
     elif cache.mode == "prefill":
         if q.is_cuda and D != 128:
             o = attn_ops.attention_reference(q, k, v, ctx.plan.cu_seqlens, Hq, Hkv)
@@ -180,6 +182,8 @@ class Generator:
     def _logits(self, trunk_rows: torch.Tensor) -> torch.Tensor:
         m = self.model
         h = rms_norm(trunk_rows, m.norm, m.cfg.rms_norm_eps)
+        if m.cfg.final_logit_softcapping:
+            return m.capped_logits(h)
         w = m.head_weight()
         return gemm.matmul(h, w, out_dtype=torch.float32) if h.is_cuda else h.float() @ w.float().t()
 

@@ -37,6 +37,9 @@ FAMILIES = {
     # slice shared by all heads) in front of the sigmoid-routed, group-limited MoE with shared experts
     # Gemma 3 (text): five windowed layers per full one with their own rotary base, norms before AND after both blocks
     # with weights stored as (w - 1), tanh-GELU gating, embeddings scaled by sqrt(hidden), a configured softmax scale
+    # Gemma 2: the same block as Gemma 3 without q / k norms and with one rotary base, plus tanh soft-capping of the
+    # attention scores and of the output logits
+    "gemma2": dict(architecture="Gemma2ForCausalLM", moe=False, qk_norm=False, bias_key=True, bias_default=False, has_window=True),
     "gemma3_text": dict(architecture="Gemma3ForCausalLM", moe=False, qk_norm=True, bias_key=True, bias_default=False, has_window=True),
     "deepseek_v3": dict(architecture="DeepseekV3ForCausalLM", moe=True, qk_norm=False, bias_key=True, bias_default=False, has_window=False),
     "gpt_oss": dict(architecture="GptOssForCausalLM", moe=True, qk_norm=False, bias_key=True, bias_default=True, has_window=True),
@@ -77,6 +80,8 @@ class ModelConfig:
     norm_unit_offset: bool = False         # the checkpoint stores norm weights as (w - 1); at run time they are plain weights
     embedding_multiplier: float = 1.0      # token embeddings are scaled by this (Gemma: sqrt(hidden_size))
     query_pre_attn_scalar: int = 0         # softmax scale = this ** -0.5 (0 = head_dim)
+    attn_logit_softcapping: float = 0.0    # > 0: attention scores pass through cap * tanh(. / cap) before the mask (Gemma 2)
+    final_logit_softcapping: float = 0.0   # > 0: the same on the output logits
     rope_local_theta: float = 0.0          # rotary base of the windowed layers when it differs from the full layers' (0 = the same)
     kv_lora_rank: int = 0                  # > 0: multi-head latent attention (DeepSeek); keys / values come from this many latent dims
     q_lora_rank: int = 0                   # latent dims of the query bottleneck (0 = one plain query projection)
@@ -212,16 +217,19 @@ class ModelConfig:
                 d["max_window_layers"] = first_windowed if self.sliding_window else self.num_hidden_layers
                 if self.sliding_window and self.layer_types:
                     d["layer_types"] = list(self.layer_types)
-        if self.family == "gemma3_text":
-            for key in ("hidden_act", "rope_theta", "rope_scaling"):
-                d.pop(key, None)
-            full = d.pop("rope_parameters")
+        if self.family in ("gemma2", "gemma3_text"):
+            d.pop("hidden_act", None)
             d.update({"hidden_activation": "gelu_pytorch_tanh", "query_pre_attn_scalar": self.query_pre_attn_scalar or self.head_dim,
-                      "attn_logit_softcapping": None, "final_logit_softcapping": None,
+                      "attn_logit_softcapping": self.attn_logit_softcapping or None,
+                      "final_logit_softcapping": self.final_logit_softcapping or None,
                       "layer_types": list(self.layer_types or ["sliding_attention" if self.sliding_window else "full_attention"]
-                                          * self.num_hidden_layers),
-                      "rope_parameters": {"full_attention": full, "sliding_attention": {
-                          "rope_type": "default", "rope_theta": self.rope_local_theta or self.rope_theta}}})
+                                          * self.num_hidden_layers)})
+            if self.family == "gemma3_text":
+                for key in ("rope_theta", "rope_scaling"):
+                    d.pop(key, None)
+                full = d.pop("rope_parameters")
+                d["rope_parameters"] = {"full_attention": full, "sliding_attention": {
+                    "rope_type": "default", "rope_theta": self.rope_local_theta or self.rope_theta}}
         elif self.family == "gpt_oss":
             d.update({"num_local_experts": self.num_experts, "num_experts_per_tok": self.num_experts_per_tok,
                       "intermediate_size": self.moe_intermediate_size, "router_aux_loss_coef": self.router_aux_loss_coef,
@@ -329,14 +337,13 @@ class ModelConfig:
                          topk_group=int(d.get("topk_group", 1)), routed_scaling_factor=float(d.get("routed_scaling_factor", 1.0)),
                          shared_expert_intermediate_size=int(d.get("n_shared_experts", 0) or 0) * width,
                          mlp_only_layers=list(range(int(d.get("first_k_dense_replace", 0)))), use_qk_norm=bool(d.get("use_qk_norm", False)))
-        elif mt == "gemma3_text":
-            if d.get("attn_logit_softcapping") or d.get("final_logit_softcapping"):
-                raise ValueError("a Gemma checkpoint with logit soft-capping: tanh capping of scores / logits is not built")
+        elif mt in ("gemma2", "gemma3_text"):
             if d.get("use_bidirectional_attention"):
                 raise ValueError("bidirectional attention is not built")
             n_exp, width, dense_width = 0, 0, d["intermediate_size"]
             topk, renorm = 8, True
-            kinds = list(d.get("layer_types") or ["full_attention" if (i + 1) % 6 == 0 else "sliding_attention"
+            every = 6 if mt == "gemma3_text" else 2          # one full layer per this many
+            kinds = list(d.get("layer_types") or ["full_attention" if (i + 1) % every == 0 else "sliding_attention"
                                                    for i in range(d["num_hidden_layers"])])
             if "sliding_attention" not in kinds:
                 window = 0
@@ -344,7 +351,9 @@ class ModelConfig:
             extra = dict(layer_types=kinds if window else None, hidden_activation="gelu_tanh", sandwich_norms=True, norm_unit_offset=True,
                          embedding_multiplier=float(d["hidden_size"]) ** 0.5,
                          query_pre_attn_scalar=int(d.get("query_pre_attn_scalar", 256)),
-                         rope_local_theta=local_theta if window and local_theta != theta else 0.0,
+                         rope_local_theta=local_theta if window and local_theta and local_theta != theta else 0.0,
+                         attn_logit_softcapping=float(d.get("attn_logit_softcapping") or 0.0),
+                         final_logit_softcapping=float(d.get("final_logit_softcapping") or 0.0),
                          tie_word_embeddings=d.get("tie_word_embeddings", True))
         elif mt == "gpt_oss":
             n_exp, width, dense_width = d.get("num_local_experts", 128), d["intermediate_size"], d["intermediate_size"]

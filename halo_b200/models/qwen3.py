@@ -102,7 +102,8 @@ class Attention(nn.Module):
         # the window of this layer: families that alternate windowed and full layers name each layer's kind
         kinds = cfg.layer_types
         self.window = cfg.sliding_window if (not kinds or layer_idx >= len(kinds) or kinds[layer_idx] == "sliding_attention") else 0
-        if (cfg.attention_sinks or cfg.output_bias or self.window or (cfg.query_pre_attn_scalar or cfg.head_dim) != cfg.head_dim) and tp_size > 1:
+        if (cfg.attention_sinks or cfg.output_bias or self.window or cfg.attn_logit_softcapping
+                or (cfg.query_pre_attn_scalar or cfg.head_dim) != cfg.head_dim) and tp_size > 1:
             raise ValueError("attention sinks, an output-projection bias, a sliding window and a configured softmax scale are not "
                              "cut over tensor-parallel ranks")
         H, D = cfg.hidden_size, cfg.head_dim
@@ -122,6 +123,7 @@ class Attention(nn.Module):
         # a configured softmax scale (Gemma's query_pre_attn_scalar); None = head_dim ** -0.5, which the flash kernel uses
         qpas = cfg.query_pre_attn_scalar
         self.scale = float(qpas) ** -0.5 if qpas and qpas != D else None
+        self.softcap = float(cfg.attn_logit_softcapping or 0.0)
         self.o_bias = nn.Parameter(torch.zeros(H, dtype=dtype, device=device)) if cfg.output_bias else None
         self.sinks = nn.Parameter(torch.zeros(self.n_heads, dtype=dtype, device=device)) if cfg.attention_sinks else None
         self.lora = None          # halo_b200.peft.lora.LoraSet when low-rank adapters are attached
@@ -179,7 +181,8 @@ class Attention(nn.Module):
             mask = ctx.causal
         elif mask.device != q.device:
             mask = ctx.attention_mask = mask.to(q.device)
-        o = masked_attention(q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D), mask, scale=self.scale, sinks=self.sinks)
+        o = masked_attention(q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D), mask, scale=self.scale, sinks=self.sinks,
+                             softcap=self.softcap)
         return o.reshape(T, Hq * D)
 
     def _qkv(self, h):
@@ -211,7 +214,8 @@ class Attention(nn.Module):
                                         cfg.rms_norm_eps, cfg.use_qk_norm)
             return row_parallel_linear(o, self.o_proj, ctx.tp)
         qkv = self._qkv(h)
-        if self.window or self.sinks is not None or self.scale is not None or getattr(ctx, "attention_mask", None) is not None:
+        if (self.window or self.sinks is not None or self.scale is not None or self.softcap
+                or getattr(ctx, "attention_mask", None) is not None):
             return self._out(self._masked(qkv, ctx))
         if ctx.cp is not None:
             # context parallel: this rank holds one chunk of the row; keys and values of straddling documents
@@ -717,9 +721,13 @@ class Qwen3Model(nn.Module):
             h = self.hidden_states(input_ids, position_ids, cu_seqlens, ctx)
             if labels is None:
                 return h
+            if self.cfg.final_logit_softcapping:
+                return self._capped_cross_entropy(h, labels.reshape(-1), normalizer)
             return fused_linear_cross_entropy(h, self.head_weight(), labels.reshape(-1), normalizer)
         from .mtp import shifted_targets
 
+        if self.cfg.final_logit_softcapping:
+            raise NotImplementedError("a multi-token-prediction head beside soft-capped logits is not built")
         ctx = ctx or self.make_context(position_ids.reshape(-1), cu_seqlens)
         trunk = self.trunk_states(input_ids, ctx)
         flat = labels.reshape(-1)
@@ -735,7 +743,34 @@ class Qwen3Model(nn.Module):
 
     def token_logprobs(self, input_ids, position_ids, cu_seqlens, labels, want_entropy=False, ctx=None):
         h = self.hidden_states(input_ids, position_ids, cu_seqlens, ctx)
+        if self.cfg.final_logit_softcapping:
+            return self._capped_logprobs(h, labels.reshape(-1), want_entropy)
         return linear_logprobs(h, self.head_weight(), labels.reshape(-1), want_entropy=want_entropy)
+
+    # ---- soft-capped output logits (Gemma 2): row chunks of logits through cap * tanh(. / cap), as tensor ops --------
+    def capped_logits(self, h):
+        cap = self.cfg.final_logit_softcapping
+        z = h.float() @ self.head_weight().float().t()
+        return cap * torch.tanh(z / cap) if cap else z
+
+    def _capped_cross_entropy(self, h, labels, normalizer, chunk_rows: int = 4096):
+        total = h.new_zeros((), dtype=torch.float32)
+        count = (labels != -100).sum().clamp_min(1) if normalizer is None else normalizer
+        for lo in range(0, h.shape[0], chunk_rows):
+            total = total + torch.nn.functional.cross_entropy(self.capped_logits(h[lo:lo + chunk_rows]), labels[lo:lo + chunk_rows],
+                                                              ignore_index=-100, reduction="sum")
+        return total / count
+
+    def _capped_logprobs(self, h, labels, want_entropy, chunk_rows: int = 4096):
+        outs, ents = [], []
+        for lo in range(0, h.shape[0], chunk_rows):
+            logp = torch.log_softmax(self.capped_logits(h[lo:lo + chunk_rows]), dim=-1)
+            lab = labels[lo:lo + chunk_rows]
+            picked = logp.gather(-1, lab.clamp_min(0)[:, None]).squeeze(-1)
+            outs.append(torch.where(lab == -100, torch.zeros_like(picked), picked))
+            if want_entropy:
+                ents.append(-(logp.exp() * logp).sum(-1).detach())
+        return torch.cat(outs), (torch.cat(ents) if want_entropy else None)
 
 
 def attention_half_bytes_per_token(cfg: ModelConfig, itemsize: int = 2) -> int:

@@ -22,11 +22,13 @@ from .streams import masked_softmax_backward
 SCORES_PER_TILE = 1 << 26
 
 
-def masked_attention_reference(q, k, v, allowed, scale=None, sinks=None):
+def masked_attention_reference(q, k, v, allowed, scale=None, sinks=None, softcap=0.0):
     """``q [Q, Hq, D]``, ``k`` / ``v [K, Hkv, D]``, ``allowed [Q, K]`` bool -> ``[Q, Hq, D]`` (plain autograd form)."""
     Hq, Hkv, D = q.shape[1], k.shape[1], q.shape[2]
     kk, vv = (t.repeat_interleave(Hq // Hkv, dim=1).float() for t in (k, v))
     scores = torch.einsum("qhd,khd->hqk", q.float(), kk) * (D ** -0.5 if scale is None else scale)
+    if softcap:
+        scores = softcap * torch.tanh(scores / softcap)
     scores = scores.masked_fill(~allowed[None], float("-inf"))
     if sinks is not None:
         joined = torch.cat([scores, sinks.float()[:, None, None].expand(-1, scores.shape[1], 1)], dim=-1)
@@ -43,7 +45,7 @@ def _tiles(n_queries: int, n_keys: int, heads: int, budget: int):
 
 class _MaskedAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, allowed, scale, budget, sinks=None):
+    def forward(ctx, q, k, v, allowed, scale, budget, sinks=None, softcap=0.0):
         Q, Hq, D = q.shape
         K, Hkv = k.shape[0], k.shape[1]
         G = Hq // Hkv
@@ -54,6 +56,8 @@ class _MaskedAttention(torch.autograd.Function):
         for lo, hi in _tiles(Q, K, Hq, budget):
             qt = q[lo:hi].permute(1, 0, 2).reshape(Hkv, G * (hi - lo), D)    # heads of a group share their keys
             scores = torch.bmm(qt.float(), kh.float().transpose(1, 2)).reshape(Hq, hi - lo, K) * scale
+            if softcap:
+                scores = softcap * torch.tanh(scores / softcap)             # tanh soft-capping of the scaled scores (Gemma 2)
             scores = scores.masked_fill(~allowed[lo:hi][None], float("-inf"))
             tile_lse = torch.logsumexp(scores, dim=-1)
             if sinks is not None:
@@ -65,13 +69,13 @@ class _MaskedAttention(torch.autograd.Function):
             out[lo:hi] = o.permute(1, 0, 2).to(q.dtype)
             lse[:, lo:hi] = tile_lse
         ctx.save_for_backward(q, k, v, allowed, out, lse, sinks if sinks is not None else q.new_zeros(0))
-        ctx.meta = (scale, budget, sinks is not None)
+        ctx.meta = (scale, budget, sinks is not None, softcap)
         return out
 
     @staticmethod
     def backward(ctx, d_out):
         q, k, v, allowed, out, lse, sinks = ctx.saved_tensors
-        scale, budget, has_sinks = ctx.meta
+        scale, budget, has_sinks, softcap = ctx.meta
         Q, Hq, D = q.shape
         K, Hkv = k.shape[0], k.shape[1]
         G = Hq // Hkv
@@ -86,8 +90,16 @@ class _MaskedAttention(torch.autograd.Function):
             gt = d_out[lo:hi].permute(1, 0, 2).reshape(Hkv, G * n, D).float()
             raw = torch.bmm(qt, kh.transpose(1, 2)).reshape(Hq, n, K).contiguous()           # unscaled scores
             upstream = torch.bmm(gt, vh.transpose(1, 2)).reshape(Hq, n, K).contiguous()      # d_out v^T
-            probs, d_scores = masked_softmax_backward(raw, allowed[lo:hi], lse[:, lo:hi].contiguous(), scale, upstream,
-                                                      delta[:, lo:hi].contiguous(), True, torch.float32)
+            if softcap:
+                # the softmax saw cap * tanh(raw * scale / cap): its backward runs on the capped scores (scale 1) and
+                # the chain rule through the cap multiplies by (1 - tanh^2) * scale
+                t = torch.tanh(raw * (scale / softcap))
+                probs, d_scores = masked_softmax_backward(t * softcap, allowed[lo:hi], lse[:, lo:hi].contiguous(), 1.0, upstream,
+                                                          delta[:, lo:hi].contiguous(), True, torch.float32)
+                d_scores = d_scores * ((1.0 - t * t) * scale)
+            else:
+                probs, d_scores = masked_softmax_backward(raw, allowed[lo:hi], lse[:, lo:hi].contiguous(), scale, upstream,
+                                                          delta[:, lo:hi].contiguous(), True, torch.float32)
             probs, d_scores = probs.reshape(Hkv, G * n, K), d_scores.reshape(Hkv, G * n, K)
             dv += torch.bmm(probs.transpose(1, 2), gt)
             dk += torch.bmm(d_scores.transpose(1, 2), qt)
@@ -96,19 +108,20 @@ class _MaskedAttention(torch.autograd.Function):
         if has_sinks:
             # the sink's probability is exp(sink - lse) and its "value" is zero: d sink = -sum_q p_sink * delta
             dsinks = -(torch.exp(sinks.float()[:, None] - lse) * delta).sum(-1).to(sinks.dtype)
-        return dq, dk.permute(1, 0, 2).to(k.dtype), dv.permute(1, 0, 2).to(v.dtype), None, None, None, dsinks
+        return dq, dk.permute(1, 0, 2).to(k.dtype), dv.permute(1, 0, 2).to(v.dtype), None, None, None, dsinks, None
 
 
 def masked_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, allowed: torch.Tensor, scale: float | None = None,
-                     scores_per_tile: int = SCORES_PER_TILE, sinks: torch.Tensor | None = None) -> torch.Tensor:
+                     scores_per_tile: int = SCORES_PER_TILE, sinks: torch.Tensor | None = None, softcap: float = 0.0) -> torch.Tensor:
     """``q [Q, Hq, D]``, ``k`` / ``v [K, Hkv, D]``, ``allowed [Q, K]`` bool -> ``[Q, Hq, D]``. ``sinks [Hq]``: one learned
-    logit per head that joins every row's softmax without a value (attention sinks)."""
+    logit per head that joins every row's softmax without a value (attention sinks). ``softcap``: the scaled scores pass
+    through ``softcap * tanh(. / softcap)`` before the mask."""
     if q.shape[1] % k.shape[1]:
         raise ValueError(f"{q.shape[1]} query heads do not group over {k.shape[1]} key/value heads")
     if tuple(allowed.shape) != (q.shape[0], k.shape[0]):
         raise ValueError(f"mask {tuple(allowed.shape)} where queries and keys give {(q.shape[0], k.shape[0])}")
     scale = q.shape[2] ** -0.5 if scale is None else scale
-    return _MaskedAttention.apply(q, k, v, allowed.bool(), float(scale), scores_per_tile, sinks)
+    return _MaskedAttention.apply(q, k, v, allowed.bool(), float(scale), scores_per_tile, sinks, float(softcap or 0.0))
 
 
 def tree_mask(parent: torch.Tensor) -> torch.Tensor:

@@ -101,7 +101,10 @@ class PipelineStage:
         x = m.run_layers(x, ctx)
         if self.is_last:
             h = rms_norm(x, m.norm, m.cfg.rms_norm_eps)
-            out = fused_linear_cross_entropy(h, m.head_weight(), batch.labels.reshape(-1), normalizer)
+            if m.cfg.final_logit_softcapping:
+                out = m._capped_cross_entropy(h, batch.labels.reshape(-1), normalizer)
+            else:
+                out = fused_linear_cross_entropy(h, m.head_weight(), batch.labels.reshape(-1), normalizer)
         else:
             out = x
             self._send(out.detach(), self.next)

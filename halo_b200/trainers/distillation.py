@@ -76,6 +76,8 @@ class DistillationTrainer(Trainer):
             p.requires_grad_(False)
 
     def compute_loss(self, model, batch, normalizer):
+        if model.cfg.final_logit_softcapping or self.teacher.cfg.final_logit_softcapping:
+            raise NotImplementedError("distillation between soft-capped output logits is not built")
         mask = batch.labels.reshape(-1) != -100
         hs = model.hidden_states(batch.input_ids, batch.position_ids, batch.cu_seqlens)
         with torch.no_grad():

@@ -34,6 +34,10 @@ def family_config(family: str, **kw) -> ModelConfig:
     if family == "glm4_moe":
         base.update(num_experts=8, partial_rotary_factor=0.5, score_function="sigmoid", router_bias=True, n_group=2, topk_group=1,
                     routed_scaling_factor=1.5, shared_expert_intermediate_size=96, mlp_only_layers=[0], use_qk_norm=True)
+    if family == "gemma2":
+        base.update(num_hidden_layers=2, sliding_window=16, layer_types=["sliding_attention", "full_attention"], use_qk_norm=False,
+                    hidden_activation="gelu_tanh", sandwich_norms=True, norm_unit_offset=True, embedding_multiplier=128 ** 0.5,
+                    query_pre_attn_scalar=24, attn_logit_softcapping=2.0, final_logit_softcapping=0.7, tie_word_embeddings=True)
     if family == "gemma3_text":
         base.update(num_hidden_layers=3, sliding_window=16, layer_types=["sliding_attention", "sliding_attention", "full_attention"],
                     hidden_activation="gelu_tanh", sandwich_norms=True, norm_unit_offset=True, embedding_multiplier=128 ** 0.5,
@@ -54,14 +58,15 @@ def family_config(family: str, **kw) -> ModelConfig:
 def logits_of(model, ids):
     b = pack_documents([ids])
     with torch.no_grad():
-        return model.hidden_states(b.input_ids, b.position_ids, b.cu_seqlens) @ model.head_weight().t(), b
+        h = model.hidden_states(b.input_ids, b.position_ids, b.cu_seqlens)
+        return (model.capped_logits(h) if model.cfg.final_logit_softcapping else h @ model.head_weight().t()), b
 
 
 CASES = [("mistral", {"sliding_window": 16}), ("qwen2", {"sliding_window": 24}),
          ("qwen2", {"sliding_window": 12, "layer_types": ["full_attention", "sliding_attention"]}), ("llama", {}), ("llama", {"rope_scaling": LLAMA3}), ("llama", {"attention_bias": True}), ("mistral", {}),
          ("qwen2", {}), ("qwen2", {"rope_scaling": YARN}), ("mixtral", {}), ("qwen2_moe", {}), ("olmoe", {}),
          ("glm4_moe", {}), ("glm4_moe", {"n_group": 4, "topk_group": 2, "use_qk_norm": False, "attention_bias": True}),
-         ("gpt_oss", {}), ("gemma3_text", {}), ("gemma3_text", {"rope_scaling": {"rope_type": "linear", "factor": 8.0}, "tie_word_embeddings": False}),
+         ("gpt_oss", {}), ("gemma2", {}), ("gemma3_text", {}), ("gemma3_text", {"rope_scaling": {"rope_type": "linear", "factor": 8.0}, "tie_word_embeddings": False}),
          ("deepseek_v3", {}), ("deepseek_v3", {"q_lora_rank": 0, "rope_interleave": False}),
          ("deepseek_v3", {"rope_scaling": {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 64, "mscale": 1.0,
                                            "mscale_all_dim": 1.0, "beta_fast": 32.0, "beta_slow": 1.0}})]
@@ -337,3 +342,33 @@ def test_sft_entry_point_fine_tunes_a_gpt_oss_checkpoint(tmp_path):
     assert "policy trainable" in log
     sinks = torch.stack([layer.self_attn.sinks for layer in tuned.layers])
     assert torch.isfinite(sinks).all() and float((sinks - 0.5).abs().max()) > 1e-4 and float((sinks - 0.5).abs().max()) < 0.5
+
+
+def test_soft_capped_logits_loss_and_logprobs_agree():
+    """Gemma 2: the training loss, the per-token log-probabilities the preference / policy-gradient trainers use and the
+    Hugging Face loss all describe the same soft-capped distribution; the model takes optimizer steps."""
+    transformers = pytest.importorskip("transformers")
+    from halo_b200.data.packing import synthetic_packed_batch
+    from halo_b200.trainers.engine import TrainEngine
+
+    cfg = family_config("gemma2")
+    model = build_model(cfg, device="cpu", seed=3, gradient_checkpointing=True)
+    batch = synthetic_packed_batch(96, cfg.vocab_size, seed=0, lo=96, hi=97)       # one document: comparable with a padded-free HF call
+    loss = model(batch.input_ids, batch.position_ids, batch.cu_seqlens, batch.labels)
+    loss = (loss.loss if hasattr(loss, "loss") else loss).sum()
+    logp, entropy = model.token_logprobs(batch.input_ids, batch.position_ids, batch.cu_seqlens, batch.labels, want_entropy=True)
+    scored = batch.labels.reshape(-1) != -100
+    assert torch.allclose(-logp[scored].mean(), loss, atol=1e-5) and float(logp[~scored].abs().sum()) == 0.0
+    assert entropy.shape == logp.shape and float(entropy.min()) > 0
+    import tempfile
+
+    d = tempfile.mkdtemp()
+    save_model(model, d, save_dtype=None)
+    hf = transformers.AutoModelForCausalLM.from_pretrained(d, dtype=torch.float32, attn_implementation="eager").eval()
+    with torch.no_grad():
+        z = hf(input_ids=batch.input_ids.reshape(1, -1)).logits[0]
+    want = torch.nn.functional.cross_entropy(z[scored], batch.labels.reshape(-1)[scored])
+    assert torch.allclose(loss.detach(), want, atol=1e-5)
+    engine = TrainEngine(model, torch.optim.AdamW(model.parameters(), lr=3e-3), "cpu", max_grad_norm=1.0)
+    losses = [float(engine.train_step(batch).loss.reshape(-1)[0]) for _ in range(5)]
+    assert losses[-1] < losses[0] - 0.05, losses

@@ -23,7 +23,7 @@ def full_forward_logits(model, ids):
     b = pack_documents([np.asarray(ids)])
     with torch.no_grad():
         h = model.hidden_states(b.input_ids, b.position_ids, b.cu_seqlens)
-    return (h.float() @ model.head_weight().float().t())[-1]
+    return model.capped_logits(h)[-1]           # plain logits unless the family caps them
 
 
 def windowed_cfg():
@@ -57,9 +57,15 @@ def gemma_cfg():
                                rope_local_theta=500.0, tie_word_embeddings=True)
 
 
-@pytest.mark.parametrize("kind", ["dense", "moe", "windowed", "sinks", "latent", "gemma"])
+def capped_cfg():
+    """Gemma 2 style: soft-capped attention scores and output logits (caps small enough to bend both)."""
+    return dataclasses.replace(gemma_cfg(), model_type="gemma2", num_hidden_layers=2, layer_types=["sliding_attention", "full_attention"],
+                               use_qk_norm=False, rope_local_theta=0.0, attn_logit_softcapping=1.0, final_logit_softcapping=0.5)
+
+
+@pytest.mark.parametrize("kind", ["dense", "moe", "windowed", "sinks", "latent", "gemma", "capped"])
 def test_cached_decoding_equals_the_full_forward(kind):
-    cfg = {"dense": dense_cfg, "windowed": windowed_cfg, "sinks": sink_cfg, "latent": latent_cfg, "gemma": gemma_cfg,
+    cfg = {"dense": dense_cfg, "windowed": windowed_cfg, "sinks": sink_cfg, "latent": latent_cfg, "gemma": gemma_cfg, "capped": capped_cfg,
            "moe": lambda: dataclasses.replace(tiny_moe_config(), num_hidden_layers=2, vocab_size=128)}[kind]()
     model = build_model(cfg, device="cpu", seed=7, gradient_checkpointing=False)
     if kind == "sinks":

@@ -148,3 +148,9 @@ def test_masked_attention_closed_form_backward(kind):
     assert torch.allclose(got, want, atol=1e-5) and not torch.allclose(got, masked_attention(q, k, v, allowed), atol=1e-3)
     for a, b in zip(torch.autograd.grad((got * w).sum(), (q, k, v, sinks)), torch.autograd.grad((want * w).sum(), (q, k, v, sinks))):
         assert torch.allclose(a, b, atol=1e-5)
+    # tanh soft-capping of the scores (a cap small enough to bend them)
+    got = masked_attention(q * 3, k, v, allowed, scores_per_tile=Hq * Q * 8, softcap=1.5)
+    want = masked_attention_reference(q * 3, k, v, allowed, softcap=1.5)
+    assert torch.allclose(got, want, atol=1e-5) and not torch.allclose(got, masked_attention(q * 3, k, v, allowed), atol=1e-3)
+    for a, b in zip(torch.autograd.grad((got * w).sum(), (q, k, v)), torch.autograd.grad((want * w).sum(), (q, k, v))):
+        assert torch.allclose(a, b, atol=1e-5)
