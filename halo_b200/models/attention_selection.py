@@ -18,6 +18,10 @@ def attention_path(cfg, device, dtype, tree_packing: bool = False) -> tuple[str,
     device = torch.device(device)
     if getattr(cfg, "kv_lora_rank", 0):
         return "masked", "latent attention: query / key width differs from the value width"
+    if getattr(cfg, "attn_logit_softcapping", 0.0):
+        return "masked", "soft-capped attention scores: the flash kernel has no tanh between scores and softmax"
+    if (getattr(cfg, "query_pre_attn_scalar", 0) or cfg.head_dim) != cfg.head_dim and not cfg.sliding_window:
+        return "masked", f"softmax scale {cfg.query_pre_attn_scalar}^-0.5: the flash kernel scales by head_dim^-0.5"
     if getattr(cfg, "attention_sinks", False):
         return "masked", "attention sinks: the flash kernel's softmax has no extra logit"
     if cfg.sliding_window:
