@@ -166,6 +166,10 @@ def apply_lora(model, spec: LoraSpec, seed: int = 0) -> dict:
     if getattr(model, "lora_spec", None) is not None:
         raise ValueError("the model already carries adapters")
     cfg = model.cfg
+    attention_targets = sorted(set(spec.dense_targets) & {"q_proj", "k_proj", "v_proj", "o_proj"})
+    if getattr(cfg, "kv_lora_rank", 0) and attention_targets:
+        raise ValueError(f"targets {attention_targets}: latent attention has no such projections (its low-rank bottlenecks are "
+                         f"already adapters of a kind); target the feed-forward blocks or the routed experts")
     for p in model.parameters():
         p.requires_grad_(False)
     ref = next(model.parameters())

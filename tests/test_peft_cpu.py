@@ -148,6 +148,29 @@ def test_peft_reads_the_dense_adapters(tmp_path):
     assert (ours - theirs).abs().max().item() < 5e-2 * theirs.abs().max().item()
 
 
+def test_adapters_on_the_other_families():
+    """Expert pairs on gpt-oss' biased clamped-GLU banks and dense pairs on Gemma's tanh-GELU block change the function and
+    get gradients; attention targets on a latent-attention model are refused by name (nothing would read them)."""
+    from tests.test_families_cpu import family_config
+
+    for family, targets in (("gpt_oss", ["q_proj", "o_proj", "experts.gate_proj", "experts.down_proj"]),
+                            ("gemma3_text", ["v_proj", "gate_proj", "down_proj"]), ("deepseek_v3", ["experts.up_proj", "down_proj"])):
+        cfg = family_config(family)
+        model = build_model(cfg, device="cpu", seed=0, gradient_checkpointing=False)
+        b = batch(cfg)
+        base = float(loss_of(model, b))
+        apply_lora(model, LoraSpec(r=4, alpha=8.0, target_modules=targets), seed=0)
+        assert abs(float(loss_of(model, b)) - base) < 1e-6          # B starts at zero
+        randomize_b(model)
+        loss = loss_of(model, b)
+        assert abs(float(loss) - base) > 1e-5, family
+        loss.backward()
+        pairs = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+        assert pairs and all(p.grad is not None and float(p.grad.abs().sum()) > 0 for _, p in pairs), family
+    with pytest.raises(ValueError, match="latent attention has no such projections"):
+        apply_lora(build_model(family_config("deepseek_v3"), device="cpu"), LoraSpec(target_modules=["q_proj", "v_proj"]))
+
+
 def test_bad_targets_are_refused():
     with pytest.raises(ValueError, match="unknown LoRA targets"):
         LoraSpec(target_modules=["qkv_proj"])
