@@ -16,8 +16,10 @@ CHATML_ROLES = ("system", "user", "assistant", "tool")
 
 
 def load_chat_template(name: str = "chatml") -> str:
-    """A bundled training-time chat template (``halo_b200/data/templates/<name>.jinja``), for tokenizers that ship none:
-    ``tokenizer.chat_template = load_chat_template()``."""
+    """A bundled training-time chat template (``halo_b200/data/templates/<name>.jinja``: ``chatml`` with tool calls,
+    ``llama3``, ``gemma``, ``mistral``, ``harmony`` for gpt-oss), for tokenizers that ship none or ship one without
+    generation markers: ``tokenizer.chat_template = load_chat_template()``. (The reference bundles training-time
+    templates per family under ``jinja-templates/``.)"""
     import os
 
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "templates", f"{name}.jinja")

@@ -143,3 +143,39 @@ def test_bundled_chat_template_extends_history_and_marks_assistant_turns():
     assert "<tools>" in with_tools and '"name": "calc"' in with_tools and with_tools.count("<|im_start|>system") == 1
     with pytest.raises(FileNotFoundError):
         load_chat_template("nope")
+
+
+@pytest.mark.parametrize("name,opening,closing", [("llama3", "<|start_header_id|>assistant<|end_header_id|>\n\n", "<|eot_id|>"),
+                                                  ("gemma", "<start_of_turn>model\n", "<end_of_turn>"),
+                                                  ("mistral", "[/INST]", "</s>"),
+                                                  ("harmony", "<|start|>assistant<|channel|>final<|message|>", "<|end|>")])
+def test_family_chat_templates_extend_history_and_mark_assistant_turns(name, opening, closing):
+    transformers = pytest.importorskip("transformers")
+    from tokenizers import Tokenizer, models, pre_tokenizers
+
+    from halo_b200.data.chat_render import load_chat_template, template_ids
+
+    vocab = {chr(i): i - 32 for i in range(32, 127)}
+    vocab["\n"], vocab["[UNK]"] = len(vocab), len(vocab) + 1
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="[UNK]"))
+    tok.pre_tokenizer = pre_tokenizers.Split("", "isolated")
+    t = transformers.PreTrainedTokenizerFast(tokenizer_object=tok)
+    t.chat_template = load_chat_template(name)
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"}, {"role": "assistant", "content": "hello"},
+            {"role": "user", "content": "more"}, {"role": "assistant", "content": "ok"}]
+    text = t.apply_chat_template(msgs, tokenize=False)
+    assert text.count(opening) == 2 and "be brief" in text and text.index("be brief") < text.index("hi")
+    ids, mask, report = render_conversation(t, msgs)
+    spans = [t.decode(ids[a:b]).replace(" ", "") for a, b in completion_spans(mask)]
+    if name != "harmony":
+        assert report == {"rewritten": 0, "turns": 2}
+        assert spans[0].startswith("hello" + closing.replace(" ", "")) and spans[1].startswith("ok")
+        shorter = template_ids(t, msgs[:3], False)
+        assert list(ids[:len(shorter)]) == shorter
+    else:
+        # harmony closes the LAST answer with <|return|> and earlier ones with <|end|>: the earlier turn is a rewrite of
+        # what the model saw when it produced it, which the renderer reports instead of hiding
+        assert text.endswith("ok<|return|>") and "hello<|end|>" in text and report["rewritten"] == 1
+        assert spans[-1].endswith("ok<|return|>")
+    prompt = t.apply_chat_template(msgs[:2], tokenize=False, add_generation_prompt=True)
+    assert prompt.endswith({"llama3": opening, "gemma": opening, "mistral": "[/INST]", "harmony": "<|start|>assistant"}[name])
