@@ -32,6 +32,7 @@ TOOLS = {
     "trace-report": "halo_b200.diagnostics.trace_report",
     "convert-recipe": "halo_b200.configs.convert_recipe",
     "prepare-dataset": "halo_b200.data.preprocessed",
+    "deduplicate": "halo_b200.data.deduplication",
     "generate": "halo_b200.entrypoints.generation",
     "evaluate": "halo_b200.entrypoints.evaluation",
     "reward-scoring": "halo_b200.entrypoints.reward_scoring",

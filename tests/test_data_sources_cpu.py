@@ -179,3 +179,51 @@ def test_family_chat_templates_extend_history_and_mark_assistant_turns(name, ope
         assert spans[-1].endswith("ok<|return|>")
     prompt = t.apply_chat_template(msgs[:2], tokenize=False, add_generation_prompt=True)
     assert prompt.endswith({"llama3": opening, "gemma": opening, "mistral": "[/INST]", "harmony": "<|start|>assistant"}[name])
+
+
+def test_near_duplicate_removal(tmp_path):
+    """Copies that differ in casing, spacing or a word go; unrelated rows stay; the blocked search equals the one-by-one
+    greedy pass whatever the block size; the tool keeps the input order."""
+    import json
+
+    from halo_b200.data import deduplication as dd
+
+    rng = np.random.default_rng(0)
+    words = ["alpha", "bravo", "charlie", "delta", "echo", "foxtrot", "golf", "hotel", "india", "juliet", "kilo", "lima"]
+    base = [" ".join(rng.choice(words, size=30)) for _ in range(40)]
+    noisy = [b.upper().replace(" ", "  ") for b in base[:10]] + [b + " mike" for b in base[10:20]]
+    texts = base + noisy
+    keep = dd.deduplicate_texts(texts, 0.9)
+    pairs = [(i, 40 + i) for i in range(20)]
+    assert all(keep[a] != keep[b] for a, b in pairs)             # exactly one of each pair survives
+    assert keep[20:40].all() and keep.sum() == 40
+    v = dd.ngram_vectors(texts)
+    for block in (1, 7, 64):
+        assert np.array_equal(dd.keep_mask(v, 0.9, block=block), keep)
+    in_order = dd.keep_mask(v, 0.9, seed=None)
+    assert in_order[:40].all() and not in_order[40:].any()       # unseeded: the first member of a group survives
+    src, dst = tmp_path / "in.jsonl", tmp_path / "out.jsonl"
+    src.write_text("".join(json.dumps({"id": i, "messages": [{"role": "user", "content": t}]}) + "\n" for i, t in enumerate(texts)))
+    assert dd.main([str(src), str(dst), "--field", "messages"]) == 0
+    ids = [json.loads(line)["id"] for line in dst.read_text().splitlines()]
+    assert ids == sorted(ids) and len(ids) == 40
+
+
+def test_semantic_vectors_come_from_the_decoder():
+    import torch
+
+    from halo_b200.data import deduplication as dd
+    from halo_b200.models.config import ModelConfig
+    from halo_b200.models.qwen3 import build_model
+
+    class Chars:
+        def __call__(self, text, add_special_tokens=False):
+            return {"input_ids": [ord(c) % 128 for c in text]}
+
+    cfg = ModelConfig(vocab_size=128, hidden_size=32, num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=2, head_dim=16,
+                      intermediate_size=64, moe_intermediate_size=0, num_experts=0, model_type="qwen3")
+    model = build_model(cfg, device="cpu", seed=0, gradient_checkpointing=False)
+    texts = ["the cat sat", "the cat sat", "zzzzqqqq", ""]
+    v = dd.model_vectors(texts, model, Chars(), rows_per_pass=3)
+    assert v.shape == (4, 32) and torch.allclose(v.norm(dim=1), torch.ones(4), atol=1e-5)
+    assert float(v[0] @ v[1]) > 0.9999 and float(v[0] @ v[2]) < 0.9999
