@@ -27,6 +27,7 @@ TOOLS = {
     "merge-models": "halo_b200.checkpoint.tools.merge_models",
     "relayout-experts": "halo_b200.checkpoint.tools.relayout_experts",
     "patch-vocab": "halo_b200.checkpoint.tools.patch_vocab",
+    "reset-sinks": "halo_b200.checkpoint.tools.reset_sinks",
     "kernel-bench": "benchmarks.kernels",
     "nvlink-health": "halo_b200.diagnostics.nvlink_health",
     "trace-report": "halo_b200.diagnostics.trace_report",

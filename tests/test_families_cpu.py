@@ -372,3 +372,27 @@ def test_soft_capped_logits_loss_and_logprobs_agree():
     engine = TrainEngine(model, torch.optim.AdamW(model.parameters(), lr=3e-3), "cpu", max_grad_norm=1.0)
     losses = [float(engine.train_step(batch).loss.reshape(-1)[0]) for _ in range(5)]
     assert losses[-1] < losses[0] - 0.05, losses
+
+
+def test_reset_sinks_tool(tmp_path):
+    from halo_b200.checkpoint.tools import reset_sinks
+
+    cfg = family_config("gpt_oss")
+    model = build_model(cfg, device="cpu", seed=4, gradient_checkpointing=False)
+    with torch.no_grad():
+        for layer in model.layers:
+            layer.self_attn.sinks.fill_(0.25)
+    src, dst, back = (str(tmp_path / n) for n in ("src", "dst", "back"))
+    save_model(model, src, save_dtype=None)
+    assert reset_sinks.main([src, dst]) == 0
+    neutral = from_pretrained(dst, device="cpu", dtype=torch.float32)
+    assert all(float(layer.self_attn.sinks.detach().max()) < -1e30 for layer in neutral.layers)
+    for (n, a), (_, c) in zip(model.named_parameters(), neutral.named_parameters()):
+        assert n.endswith(".sinks") or torch.equal(a, c), n
+    assert reset_sinks.main([dst, back, "--from-checkpoint", src]) == 0
+    restored = from_pretrained(back, device="cpu", dtype=torch.float32)
+    assert all(torch.equal(a, c) for (_, a), (_, c) in zip(model.named_parameters(), restored.named_parameters()))
+    plain = str(tmp_path / "plain")
+    save_model(build_model(family_config("llama"), device="cpu"), plain, save_dtype=None)
+    with pytest.raises(SystemExit, match="no attention sinks"):
+        reset_sinks.main([plain, str(tmp_path / "nope")])
