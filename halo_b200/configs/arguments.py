@@ -33,6 +33,7 @@ class ModelArguments:
     adapter_path: str = ""                  # adapters to continue from (a directory holding adapter_model.safetensors)
     merge_adapters_on_save: bool = False    # save full weights with the adapters folded in instead of the adapters alone
     load_in_4bit: bool = False              # QLoRA: keep the frozen base matrices of the decoder layers as 4-bit blocks (needs use_peft)
+    load_in_8bit: bool = False              # the same with one signed byte per value (int8 blocks of 64)
     bnb_4bit_quant_type: Literal["nf4", "fp4"] = "nf4"
     use_bnb_nested_quant: bool = False      # also store the block maxima in 8 bits
     reset_sinks: bool = True                # gpt-oss: neutralize the attention sinks for fine-tuning; false keeps them live and frozen
@@ -49,8 +50,14 @@ class ModelArguments:
     def __post_init__(self):
         if self.use_peft and (self.freeze_patterns or self.train_only_patterns):
             raise ConfigError("use_peft freezes the base weights itself: drop freeze_patterns / train_only_patterns")
+        if self.load_in_4bit and self.load_in_8bit:
+            raise ConfigError("load_in_4bit and load_in_8bit: choose one storage for the frozen base")
+        if self.load_in_8bit:
+            self.load_in_4bit, self.bnb_4bit_quant_type = True, "int8"        # one code path: the storage kind differs
+            if self.use_bnb_nested_quant:
+                raise ConfigError("use_bnb_nested_quant is a 4-bit option")
         if self.load_in_4bit and not self.use_peft:
-            raise ConfigError("load_in_4bit stores frozen base weights: it needs use_peft: true (QLoRA)")
+            raise ConfigError("load_in_4bit / load_in_8bit store frozen base weights: they need use_peft: true (QLoRA)")
         if self.load_in_4bit and self.merge_adapters_on_save:
             raise ConfigError("merge_adapters_on_save with load_in_4bit would fold the adapters into the rounded base: save the "
                               "adapters alone and merge them into the original checkpoint with the merge-adapter tool")

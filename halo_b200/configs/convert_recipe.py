@@ -28,7 +28,7 @@ KEPT = {
     "trust_remote_code", "optim", "seed", "routing_replay", "mtp_loss_weight", "environment_type", "max_grad_norm", "adam_beta1",
     "adam_beta2", "adam_epsilon", "router_aux_loss_coef", "resume_from_checkpoint", "gradient_checkpointing_plan", "temperature",
     "rollout_backend", "save_sharded_ep", "label_smoothing", "center_rewards_coefficient", "num_labels", "text_field",
-    "reset_sinks", "train_sinks", "load_in_4bit", "use_bnb_nested_quant", "bnb_4bit_quant_type",
+    "reset_sinks", "train_sinks", "load_in_4bit", "load_in_8bit", "use_bnb_nested_quant", "bnb_4bit_quant_type",
 }
 # renamed: reference key -> (our key, optional value transform)
 RENAMED = {
@@ -90,7 +90,6 @@ DROPPED = {
 }
 # asks for something that does not exist here
 UNSUPPORTED = {
-    "load_in_8bit": "8-bit base weights are not built (load_in_4bit is)",
     "images_field": "vision-language rows are not built",
     "lora_modules_to_save": "adapters are saved alone or merged; extra full modules beside them are not built",
     "pooling_mode": "embeddings are the last token's hidden state",

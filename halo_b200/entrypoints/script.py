@@ -182,7 +182,8 @@ def load_policy_model(model_args, pc, device, runtime, gradient_checkpointing=Tr
             from halo_b200.peft.qlora import quantize_base_weights
 
             q = quantize_base_weights(model, model_args.bnb_4bit_quant_type, model_args.use_bnb_nested_quant)
-            log.info("4-bit base: %d matrices, %.1f M parameters in %.1f MB", q["matrices"], q["parameters"] / 1e6, q["bytes"] / 1e6)
+            log.info("quantised base (%s): %d matrices, %.1f M parameters in %.1f MB", model_args.bnb_4bit_quant_type, q["matrices"],
+                     q["parameters"] / 1e6, q["bytes"] / 1e6)
     if model_args.freeze_patterns or model_args.train_only_patterns:
         from halo_b200.models.freeze import apply_freeze_patterns
 

@@ -24,6 +24,7 @@ NF4_LEVELS = (-1.0, -0.6961928009986877, -0.5250730514526367, -0.394917488098144
 _E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
 FP4_LEVELS = tuple(-v / 6.0 for v in reversed(_E2M1)) + tuple(v / 6.0 for v in _E2M1)      # both signs of zero keep their code
 KINDS = {"nf4": NF4_LEVELS, "fp4": FP4_LEVELS}
+INT8 = "int8"          # 8-bit storage (``load_in_8bit``): one signed byte per value, code / 127 of the block maximum
 
 
 def levels(kind: str, device=None) -> torch.Tensor:
@@ -34,7 +35,7 @@ def levels(kind: str, device=None) -> torch.Tensor:
 
 @dataclass
 class Packed4bit:
-    codes: torch.Tensor               # uint8 [ceil(n / 2)]
+    codes: torch.Tensor               # uint8 [n / 2] (two 4-bit codes per byte), or [n] signed bytes viewed as uint8 for int8
     absmax: torch.Tensor | None       # fp32 [n / BLOCK], or None when nested
     shape: tuple
     dtype: torch.dtype
@@ -70,10 +71,15 @@ def quantize_4bit(w: torch.Tensor, kind: str = "nf4", nested: bool = False, bloc
     n = w.numel()
     if n % block or block % 2:
         raise ValueError(f"a tensor of {n} values does not split into blocks of {block}")
-    table = levels(kind, w.device)
     x = w.detach().reshape(-1, block).float()
     absmax = x.abs().amax(dim=1)
     unit = x / absmax.clamp_min(1e-30)[:, None]
+    if kind == INT8:
+        if nested:
+            raise ValueError("nested maxima are a 4-bit option")
+        codes = torch.round(unit * 127.0).to(torch.int8).reshape(-1)
+        return Packed4bit(codes.view(torch.uint8), absmax, tuple(w.shape), w.dtype, kind, block)
+    table = levels(kind, w.device)
     # the nearest level: the table is sorted, so its index is the number of midpoints below the value
     codes = torch.bucketize(unit, (table[1:] + table[:-1]) / 2).to(torch.uint8).reshape(-1)
     packed = (codes[0::2] << 4) | codes[1::2]
@@ -93,6 +99,9 @@ def quantize_4bit(w: torch.Tensor, kind: str = "nf4", nested: bool = False, bloc
 
 def dequantize_4bit(p: Packed4bit, dtype: torch.dtype | None = None) -> torch.Tensor:
     dtype = dtype or p.dtype
+    if p.kind == INT8:
+        values = p.codes.view(torch.int8).reshape(-1, p.block).float() * (p.block_maxima() / 127.0)[:, None]
+        return values.reshape(p.shape).to(dtype)
     if p.codes.is_cuda and dtype == torch.bfloat16 and p.block == BLOCK:
         # the sm_100a kernel (csrc/nf4.cu): 0.5 byte read and 2 bytes written per value, the same single rounding
         import ctypes
@@ -119,5 +128,7 @@ def dequantize_4bit_reference(p: Packed4bit, dtype: torch.dtype | None = None) -
 
 def quantization_error_bound(kind: str) -> float:
     """Largest distance from a value in [-1, 1] to its nearest level: the per-block relative error bound."""
+    if kind == INT8:
+        return 0.5 / 127.0
     t = levels(kind)
     return float((t[1:] - t[:-1]).max()) / 2

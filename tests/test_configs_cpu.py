@@ -202,8 +202,8 @@ def test_reference_recipe_converts_and_parses(tmp_path):
     parsed = ArgumentParser(A.ModelArguments, A.DataArguments, A.TrainingArguments, A.ParallelismArguments, A.SFTArguments).parse([str(dst)])
     assert parsed[0].lora_r == 64 and parsed[1].dataset_path == str(data) and parsed[1].completion_only_loss and parsed[1].num_proc == 4
     assert parsed[3].expert_parallel_size == 8
-    src.write_text(yaml.safe_dump({**recipe, "use_vllm": True, "load_in_8bit": True, "num_generations": 8}))
-    with pytest.raises(ValueError, match="load_in_8bit"):
+    src.write_text(yaml.safe_dump({**recipe, "use_vllm": True, "images_field": "images", "num_generations": 8}))
+    with pytest.raises(ValueError, match="images_field"):
         convert_recipe.main([str(src), str(dst)])
-    assert convert_recipe.main([str(src), str(dst), "--lenient"]) == 0 and "NOT CONVERTED load_in_8bit" in dst.read_text()
+    assert convert_recipe.main([str(src), str(dst), "--lenient"]) == 0 and "NOT CONVERTED images_field" in dst.read_text()
     assert "launch grpo" in dst.read_text() and "dropped use_vllm: no generation server: add rollout_gpus" in dst.read_text()

@@ -44,6 +44,18 @@ def test_block_format_error_bound_and_size(kind, nested):
         quantize_4bit(torch.zeros(10, 10), kind)
 
 
+def test_int8_storage():
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(64, 256, generator=g) * torch.logspace(-2, 1, 64)[:, None]
+    p = quantize_4bit(w, "int8")
+    back = dequantize_4bit(p)
+    assert p.codes.numel() == w.numel() and 8.0 * p.nbytes / w.numel() == 8.5
+    err = ((back - w).reshape(-1, 64).abs() / w.reshape(-1, 64).abs().amax(1, keepdim=True)).max()
+    assert float(err) <= quantization_error_bound("int8") + 1e-6
+    with pytest.raises(ValueError, match="4-bit option"):
+        quantize_4bit(w, "int8", nested=True)
+
+
 def _moe_cfg():
     return dataclasses.replace(tiny_moe_config(), num_hidden_layers=2, shared_expert_intermediate_size=64, vocab_size=512)
 
@@ -122,13 +134,20 @@ def test_sft_entry_point_trains_a_quantized_base(tmp_path):
     r = subprocess.run([sys.executable, "-m", "halo_b200.cli", "launch", "sft", str(cfg)], cwd=root, capture_output=True, text=True,
                        timeout=300, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
-    assert "4-bit base:" in r.stdout + r.stderr
+    assert "quantised base (nf4):" in r.stdout + r.stderr
     final = tmp_path / "run" / "final"
     assert os.path.isfile(final / "adapter_config.json")
     with safe_open(str(final / "adapter_model.safetensors"), "pt") as f:
         assert any("lora_A" in k for k in f.keys())
+    eight = tmp_path / "eight.yaml"
+    eight.write_text(cfg.read_text().replace("load_in_4bit: true\n", "load_in_8bit: true\n").replace("use_bnb_nested_quant: true\n", "")
+                     .replace(f"{tmp_path}/run", f"{tmp_path}/run8"))
+    r = subprocess.run([sys.executable, "-m", "halo_b200.cli", "launch", "sft", str(eight)], cwd=root, capture_output=True, text=True,
+                       timeout=300, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert "quantised base (int8):" in r.stdout + r.stderr and os.path.isfile(tmp_path / "run8" / "final" / "adapter_config.json")
     bad = tmp_path / "bad.yaml"
     bad.write_text(cfg.read_text().replace("use_peft: true\n", ""))
     r = subprocess.run([sys.executable, "-m", "halo_b200.cli", "launch", "sft", str(bad)], cwd=root, capture_output=True, text=True,
                        timeout=300, env=env)
-    assert r.returncode != 0 and "needs use_peft" in r.stdout + r.stderr
+    assert r.returncode != 0 and "need use_peft" in r.stdout + r.stderr
