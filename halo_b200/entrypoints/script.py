@@ -192,13 +192,28 @@ def load_policy_model(model_args, pc, device, runtime, gradient_checkpointing=Tr
     return model
 
 
+def pin_tokenizer(tokenizer, max_length: int = 0):
+    """The settings every entry point relies on: a pad token (the end-of-sequence token when the tokenizer ships none -
+    packed rows never score it, padded evaluation batches need one), right-side truncation and padding, and
+    ``model_max_length`` equal to the run's ``max_length`` so that truncation warnings refer to the run's limit
+    (the role of halo/model_loading/tokenizer_setup.py)."""
+    if tokenizer.pad_token_id is None and tokenizer.eos_token is not None:
+        tokenizer.pad_token = tokenizer.eos_token
+        log.info("tokenizer has no pad token: using the end-of-sequence token %r", tokenizer.eos_token)
+    tokenizer.padding_side = "right"
+    tokenizer.truncation_side = "right"
+    if max_length:
+        tokenizer.model_max_length = int(max_length)
+    return tokenizer
+
+
 def load_tokenizer(model_args):
     if not model_args.model_name_or_path:
         return None
     try:
         from transformers import AutoTokenizer
 
-        return AutoTokenizer.from_pretrained(model_args.model_name_or_path)
+        return pin_tokenizer(AutoTokenizer.from_pretrained(model_args.model_name_or_path), getattr(model_args, "max_length", 0))
     except Exception as exc:   # a checkpoint directory without tokenizer files: pre-tokenised data still works
         log.warning("no tokenizer at %s (%s)", model_args.model_name_or_path, exc)
         return None

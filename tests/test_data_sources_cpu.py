@@ -227,3 +227,18 @@ def test_semantic_vectors_come_from_the_decoder():
     v = dd.model_vectors(texts, model, Chars(), rows_per_pass=3)
     assert v.shape == (4, 32) and torch.allclose(v.norm(dim=1), torch.ones(4), atol=1e-5)
     assert float(v[0] @ v[1]) > 0.9999 and float(v[0] @ v[2]) < 0.9999
+
+
+def test_tokenizer_pins():
+    transformers = pytest.importorskip("transformers")
+    from tokenizers import Tokenizer, models
+
+    from halo_b200.entrypoints.script import pin_tokenizer
+
+    tok = Tokenizer(models.WordLevel({"a": 0, "<eos>": 1, "[UNK]": 2}, unk_token="[UNK]"))
+    t = transformers.PreTrainedTokenizerFast(tokenizer_object=tok, eos_token="<eos>", padding_side="left")
+    assert t.pad_token is None
+    pin_tokenizer(t, 4096)
+    assert t.pad_token == "<eos>" and t.padding_side == "right" and t.truncation_side == "right" and t.model_max_length == 4096
+    t2 = transformers.PreTrainedTokenizerFast(tokenizer_object=tok, eos_token="<eos>", pad_token="a")
+    assert pin_tokenizer(t2).pad_token == "a"                  # a shipped pad token is kept
