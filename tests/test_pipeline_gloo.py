@@ -21,7 +21,7 @@ def test_partition_balances_head_cost():
     assert ranges[-1][1] - ranges[-1][0] < ranges[0][1] - ranges[0][0]
 
 
-def _worker(rank, world, schedule):
+def _worker(rank, world, schedule, family="tiny-moe"):
     import dataclasses
 
     import torch.distributed as dist
@@ -31,7 +31,14 @@ def _worker(rank, world, schedule):
     from halo_b200.models.qwen3 import build_model
     from halo_b200.parallel.pipeline import PipelineStage, broadcast_loss, build_stage_model, run_schedule
 
-    cfg = dataclasses.replace(PRESETS["tiny-moe"](), num_hidden_layers=4)
+    if family == "tiny-moe":
+        cfg = dataclasses.replace(PRESETS["tiny-moe"](), num_hidden_layers=4)
+    else:
+        # a family whose layers differ by their GLOBAL index (windowed / full mix) and whose loss is soft-capped
+        from tests.test_families_cpu import family_config
+
+        cfg = family_config(family, num_hidden_layers=4, tie_word_embeddings=False,
+                            layer_types=["sliding_attention", "sliding_attention", "full_attention", "sliding_attention"])
     row = 96
     micro = [synthetic_packed_batch(row, cfg.vocab_size, seed=i, lo=8, hi=48) for i in range(3)]
     norm = float(sum(b.n_scored for b in micro))
@@ -60,6 +67,10 @@ def _worker(rank, world, schedule):
 @pytest.mark.parametrize("schedule", ["1f1b", "gpipe"])
 def test_pipeline_matches_unsplit_model(schedule):
     run_gloo_ranks(_worker, 2, args=(schedule,), timeout=90.0)
+
+
+def test_pipeline_stages_keep_each_layers_own_attention_kind():
+    run_gloo_ranks(_worker, 2, args=("1f1b", "gemma2"), timeout=120.0)
 
 
 def _train_worker(rank, world, out_path):
