@@ -232,3 +232,57 @@ def test_quantized_base_on_gpu_equals_the_rounded_model():
         if p.requires_grad:
             assert p.grad is not None and torch.isfinite(p.grad).all(), n
             assert (p.grad.float() - grads[n].float()).abs().max() <= 2e-2 * grads[n].float().abs().max() + 1e-6, n
+
+
+def _gpu_family_config(family):
+    from halo_b200.models.config import FAMILIES, ModelConfig
+
+    base = dict(vocab_size=2048, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                intermediate_size=512, moe_intermediate_size=0, num_experts=0, model_type=family, rope_theta=10000.0,
+                max_position_embeddings=4096, use_qk_norm=FAMILIES[family]["qk_norm"], attention_bias=FAMILIES[family]["bias_default"])
+    if FAMILIES[family]["moe"]:
+        base.update(num_experts=8, num_experts_per_tok=2, moe_intermediate_size=256, intermediate_size=256)
+    extra = {
+        "llama": dict(head_dim=128, num_attention_heads=2, num_key_value_heads=1),
+        "mistral": dict(sliding_window=64),
+        "gpt_oss": dict(sliding_window=64, layer_types=["sliding_attention", "full_attention"], attention_sinks=True, output_bias=True,
+                        router_logit_bias=True, expert_bias=True, expert_activation="clamped_glu", rms_norm_eps=1e-5),
+        "deepseek_v3": dict(score_function="sigmoid", router_bias=True, n_group=2, topk_group=1, routed_scaling_factor=2.5,
+                            shared_expert_intermediate_size=256, mlp_only_layers=[0], use_qk_norm=False, num_key_value_heads=4,
+                            intermediate_size=512, kv_lora_rank=64, q_lora_rank=96, qk_nope_head_dim=64, qk_rope_head_dim=64, v_head_dim=64),
+        "gemma2": dict(sliding_window=64, layer_types=["sliding_attention", "full_attention"], use_qk_norm=False, hidden_activation="gelu_tanh",
+                       sandwich_norms=True, norm_unit_offset=True, embedding_multiplier=16.0, query_pre_attn_scalar=96,
+                       attn_logit_softcapping=20.0, final_logit_softcapping=10.0, tie_word_embeddings=True),
+        "gemma3_text": dict(sliding_window=64, layer_types=["sliding_attention", "full_attention"], hidden_activation="gelu_tanh",
+                            sandwich_norms=True, norm_unit_offset=True, embedding_multiplier=16.0, query_pre_attn_scalar=96,
+                            rope_local_theta=500.0, tie_word_embeddings=True),
+    }[family]
+    base.update(extra)
+    return ModelConfig(**base)
+
+
+@pytest.mark.parametrize("family", ["llama", "mistral", "gpt_oss", "deepseek_v3", "gemma2", "gemma3_text"])
+def test_family_on_gpu_follows_its_fp32_cpu_twin(family):
+    """The same weights in bf16 on the GPU and in fp32 on the CPU: loss within bf16 tolerance, finite gradients of matching
+    size for every parameter (the family switches reach the same ops on both devices)."""
+    from halo_b200.data.packing import synthetic_packed_batch
+    from halo_b200.models.qwen3 import build_model
+
+    cfg = _gpu_family_config(family)
+    cpu = build_model(cfg, device="cpu", dtype=torch.float32, seed=3, gradient_checkpointing=False)
+    gpu = build_model(cfg, device="cuda", seed=3)
+    with torch.no_grad():
+        for (n, a), (_, b) in zip(cpu.named_parameters(), gpu.named_parameters()):
+            a.copy_(b.float())                                   # the bf16 values, exactly
+    batch = synthetic_packed_batch(256, cfg.vocab_size, seed=0, lo=40, hi=130)
+    losses, norms = [], []
+    for model, b in ((cpu, batch), (gpu, batch.to("cuda"))):
+        out = model(b.input_ids, b.position_ids, b.cu_seqlens, b.labels)
+        loss = (out.loss if hasattr(out, "loss") else out).sum()
+        loss.backward()
+        losses.append(float(loss))
+        grads = [p.grad for p in model.parameters() if p.requires_grad]
+        assert all(g is not None and torch.isfinite(g).all() for g in grads), family
+        norms.append(float(torch.sqrt(sum(g.float().pow(2).sum() for g in grads))))
+    assert abs(losses[0] - losses[1]) <= 3e-2 * abs(losses[0]), (family, losses)
+    assert abs(norms[0] - norms[1]) <= 0.15 * norms[0], (family, norms)
