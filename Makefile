@@ -14,7 +14,7 @@ test-gpu: build   ## kernel numerics and model tests on one GPU
 	$(PY) -m pytest tests -q -m gpu
 
 test-multigpu: build   ## peer-memory paths on two GPUs
-	$(PY) -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 tests/multigpu/check_two_ranks.py
+	$(PY) -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 tests/multigpu/check_ranks.py
 
 bench: build      ## flagship benchmark on one GPU
 	$(PY) bench.py

@@ -292,6 +292,12 @@ def main() -> int:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         if not read_loss:
             last = float(last.item())
+        if world > 1:
+            # a rank's loss is its share of the global token mean: the sum over ranks is the job's loss, the same
+            # quantity at every N
+            lt = torch.tensor([last], dtype=torch.float64, device=dev)
+            dist.all_reduce(lt)
+            last = float(lt.item())
         return float(t.item()), clocks, _lib.launch_count() - launches0, last
 
     ms_dev, clocks, launches, loss_dev = timed(dev_batches, read_loss=False)
@@ -305,7 +311,8 @@ def main() -> int:
     if rank == 0:
         par = (f"ep{world}" if cfg.is_moe else "") + (f"+dp{world}" if world > 1 else "") + (f"+ep_lanes{args.ep_lanes}" if world > 1 and args.ep_lanes > 1 else "") + ("+fused_zero" if parallel is not None and parallel.fused_optimizer is not None else "") + ("+host_optimizer_state" if getattr(opt, "state_bytes_on_host", lambda: 0)() > 0 else "")
         line = {
-            "metric": ("train tokens/s, 30B-A3B MoE, packed 64k rows (whole job)" if args.model == "moe-30b-a3b"
+            "metric": ("train tokens/s, 30B-A3B MoE, EP = n_gpus, packed 64k rows (whole job; tokens_per_s_per_gpu is the "
+                       "per-GPU figure the published baseline quotes)" if args.model == "moe-30b-a3b"
                        else f"train tokens/s, {args.model}, packed rows (whole job)"),
             "value": round(value, 1),
             "unit": "tokens/s",
@@ -325,6 +332,9 @@ def main() -> int:
                 "layers": cfg.num_hidden_layers, "hidden": cfg.hidden_size, "experts": cfg.num_experts,
                 "top_k": cfg.num_experts_per_tok, "vocab": cfg.vocab_size,
                 "global_batch": world, "seq_len": args.seq_len, "parallelism": par,
+                "ep_size": world if cfg.is_moe else 1, "dp_size": world,
+                "fused_zero": bool(parallel is not None and parallel.fused_optimizer is not None),
+                "light_layers": light_layers,
                 "optimizer": "AdamWBF16 (bf16 weights and moments, stochastic rounding), max_grad_norm 1.0",
                 "gradient_checkpointing": (f"per decoder layer; {light_layers} of {len(model.layers)} layers re-run only their "
                                            "feed-forward half (memory left after a probe step)") if light_layers

@@ -239,6 +239,10 @@ class GRPOArguments:
     num_iterations: int = 1
     sync_weights_every: int = 1
     trust_region_mask_fraction: float = 1.0
+    is_geo_band_min: float | None = None        # keep a trajectory only if exp(mean log-ratio) lies in [min, max] (None = off)
+    is_geo_band_max: float = 2.0
+    is_veto_min: float | None = None            # drop a trajectory holding a token whose raw ratio falls below this (None = off)
+    opsm_delta: float | None = None             # drop negative-advantage trajectories whose |mean log-ratio| exceeds this (None = off)
     zero_gradient_round_limit: int = 0
     rollout_backend: Literal["in_process", "vllm", "sglang", "resident_copy"] = "resident_copy"
     rollout_gpus: int = 0

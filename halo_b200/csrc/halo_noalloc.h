@@ -36,6 +36,8 @@ extern "C" {
 // previous call left in it (each call overwrites every partial it later reads, so nothing needs
 // clearing), and two calls whose kernels overlap on the GPU - different streams without an
 // ordering between them - race on it. Order such calls on one stream or with events.
+// The per-device address cache is filled without a lock: two host threads that make their first
+// call on one device at the same time both resolve the same address and store the same value.
 int halo_rmsnorm_bwd_noalloc(const void* g, const void* h, const void* w, const float* rstd,
                              const void* dres, void* dx, float* dw_f32, void* dw_bf16,
                              int accumulate, long long rows, int H, void* stream);

@@ -100,15 +100,55 @@ class Trainer:
     def compute_loss(self, model, batch: PackedBatch, normalizer):
         return model(batch.input_ids, batch.position_ids, batch.cu_seqlens, batch.labels, normalizer)
 
+    # True on trainers whose compute_loss returns the MEAN over this rank's sequences (pairs, documents): gradients are
+    # summed over the data-parallel ranks, so such a loss is re-weighted to its share of the global mean
+    sequence_mean_loss = False
+
     def _loss_adapter(self, model, batch, normalizer):
-        return self.compute_loss(model, batch, normalizer)
+        loss = self.compute_loss(model, batch, normalizer)
+        if self.sequence_mean_loss and self.parallel is not None and self.parallel.dp_world > 1:
+            n_local = float(max(len(batch.cu_seqlens) - 1, 1))
+            n_global = self.parallel.sum_scalar_over_dp(n_local)          # device scalar, one tiny reduction
+            loss = loss * (n_local / n_global.to(loss.dtype).reshape(()))
+        return loss
 
     def after_optimizer_step(self) -> None:
         """Hook for trainers that act on fresh weights (pushing them to a rollout copy, say)."""
 
     def next_batches(self) -> Iterator[PackedBatch]:
+        """The training stream. An item is either one micro-batch (``gradient_accumulation_steps`` of them make an
+        optimizer step) or a LIST of micro-batches that together make exactly one optimizer step (a source whose
+        steps have a varying number of micro-batches, such as a GRPO round, yields those)."""
         src = self.train_batches() if callable(self.train_batches) else self.train_batches
         return iter(src)
+
+    def skip_consumed(self, it: Iterator) -> Iterator:
+        """A resumed run passes over what the interrupted run consumed: ``global_step`` optimizer steps' worth of
+        single micro-batches. Sources that yield whole steps override this."""
+        for _ in range(self.global_step * self.args.gradient_accumulation_steps):
+            next(it, None)
+        return it
+
+    def step_groups(self, it: Iterator) -> Iterator[tuple[list, bool]]:
+        """The micro-batches of one optimizer step at a time, with a flag: True when the source delivered the step
+        as one list (its micro-batch losses share one denominator and add up to the step's loss), False when the
+        step was assembled from ``gradient_accumulation_steps`` independent micro-batches (the step's loss is their
+        mean). The accumulation count is read per step, before the step's first micro-batch is consumed."""
+        while True:
+            first = next(it, None)
+            if first is None:
+                return
+            if isinstance(first, (list, tuple)):
+                if first:
+                    yield list(first), True
+                continue
+            micro = [first]
+            for _ in range(self.args.gradient_accumulation_steps - 1):
+                b = next(it, None)
+                if b is None:
+                    break
+                micro.append(b)
+            yield micro, False
 
     @property
     def world_size(self) -> int:
@@ -139,36 +179,31 @@ class Trainer:
             self.load_checkpoint(resume)
         for cb in self.callbacks:
             cb.on_train_begin(self)
-        it = self.next_batches()
-        # a resumed run skips the batches the interrupted run consumed
-        for _ in range(self.global_step * args.gradient_accumulation_steps):
-            next(it, None)
+        it = self.step_groups(self.skip_consumed(self.next_batches()))
         t_last = time.perf_counter()
-        done = False
-        while not done:
-            micro = []
-            for _ in range(args.gradient_accumulation_steps):
-                b = next(it, None)
-                if b is None:
-                    done = True
-                    break
-                micro.append(b)
-            if not micro:
+        while True:
+            group = next(it, None)
+            if group is None:
                 break
-            out = None
+            micro, shares = group
+            out, step_loss = None, None
             for i, b in enumerate(micro):
                 out = self.engine.train_step(b, accumulate=i < len(micro) - 1)
+                # every micro-batch's loss is its share of the step's loss (one shared denominator)
+                step_loss = out.loss if step_loss is None else step_loss + out.loss
                 self.tokens_seen += b.n_tokens
                 for cb in self.callbacks:
                     on_batch = getattr(cb, "on_batch", None)
                     if on_batch is not None:
                         on_batch(self, b)
+            if not shares:
+                step_loss = step_loss / len(micro)
             self.global_step += 1
             self.after_optimizer_step()
             self._guard_non_finite(out)
             if args.logging_steps and self.global_step % args.logging_steps == 0:
                 now = time.perf_counter()
-                logs = {"step": self.global_step, "loss": float(out.loss.reshape(-1)[0].item()),
+                logs = {"step": self.global_step, "loss": float(step_loss.reshape(-1)[0].item()),
                         "grad_norm": float(out.grad_norm.item()), "lr": self.lr_scheduler.get_last_lr()[0],
                         "tokens": self.tokens_seen, "step_seconds": (now - t_last) / args.logging_steps}
                 t_last = now
@@ -227,11 +262,23 @@ class Trainer:
 
     def save_checkpoint(self) -> str:
         d = self.checkpoint_dir()
+        # the free-space check runs on the writer rank only, but its verdict is agreed over the group BEFORE any rank
+        # enters the collective gathers of save_model: a lone raise there would leave the others waiting in them
+        reason = None
         if self.is_main:
             from halo_b200.checkpoint.preflight import checkpoint_bytes, require_free_space
 
             ep_world = self.parallel.ep_world if self.parallel is not None else 1
-            require_free_space(self.args.output_dir, checkpoint_bytes(self.model, ep_world=ep_world))
+            try:
+                require_free_space(self.args.output_dir, checkpoint_bytes(self.model, ep_world=ep_world))
+            except Exception as exc:  # noqa: BLE001 - any failure of the check must reach every rank
+                reason = f"{type(exc).__name__}: {exc}"
+        if self.parallel is not None or self.collective_group is not None:
+            from halo_b200.runtime.consensus import reject_across_ranks
+
+            reject_across_ranks(reason, group=self.group, what="checkpoint preflight")
+        elif reason is not None:
+            raise RuntimeError(f"checkpoint preflight: {reason}")
         os.makedirs(d, exist_ok=True)
         save_model(self.model, d, sharded_experts=self.args.save_sharded_ep, save_dtype=None,
                    group=self.group)  # exact resume: keep the dtype

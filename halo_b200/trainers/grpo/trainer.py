@@ -45,13 +45,17 @@ class GRPOBatch(PackedBatch):
     seq_lengths: torch.Tensor = None      # [n_rows] completion lengths
     attention_mask: torch.Tensor = None   # [T, T] bool under tree packing (prompts stored once per group)
     replay_routing: dict = None           # {layer index: [T, top_k] int32, -1 = unknown}: the sampler's routing to replay
+    traj_ids: torch.Tensor = None         # [T] index (within this batch) of the row each token belongs to
+    counted_tokens: list = None           # per row: policy-produced completion tokens (host side)
+    denominator: float = 0.0              # the whole round's loss denominator over every micro-batch and rank (0 = not set)
 
     def to(self, device, non_blocking: bool = True):
         b = PackedBatch.to(self, device, non_blocking)
         mv = lambda t: None if t is None else t.to(device, non_blocking=non_blocking)  # noqa: E731
         return GRPOBatch(b.input_ids, b.position_ids, b.labels, b.cu_seqlens, b.n_scored, mv(self.advantages),
                          mv(self.old_logprobs), self.has_old, mv(self.degenerate), mv(self.seq_lengths), mv(self.attention_mask),
-                         None if self.replay_routing is None else {k: mv(v) for k, v in self.replay_routing.items()})
+                         None if self.replay_routing is None else {k: mv(v) for k, v in self.replay_routing.items()},
+                         mv(self.traj_ids), self.counted_tokens, self.denominator)
 
 
 def build_grpo_batch(rollouts: list[Rollout], adv: torch.Tensor, degenerate: torch.Tensor) -> GRPOBatch:
@@ -65,10 +69,12 @@ def build_grpo_batch(rollouts: list[Rollout], adv: torch.Tensor, degenerate: tor
     a = torch.zeros(T)
     old = torch.zeros(T)
     deg = torch.zeros(T, dtype=torch.bool)
+    traj = torch.zeros(T, dtype=torch.int64)
     has_old = all(r.sampler_logprobs is not None for r in rollouts)
     for i, r in enumerate(rollouts):
         s, e = int(base.cu_seqlens[i]), int(base.cu_seqlens[i + 1])
         a[s:e] = float(adv[i])
+        traj[s:e] = i
         deg[s:e] = bool(degenerate[i])
         if has_old:
             # label at position t scores token t+1: completion token j sits at label index len(prompt) + j - 1
@@ -84,7 +90,21 @@ def build_grpo_batch(rollouts: list[Rollout], adv: torch.Tensor, degenerate: tor
             for row, li in enumerate(layers):
                 replay[li][s:s + n] = torch.from_numpy(r.routing[row, :n].astype(np.int32))
     return GRPOBatch(base.input_ids, base.position_ids, base.labels, base.cu_seqlens, base.n_scored, a, old, has_old,
-                     deg, torch.tensor([len(r.completion_ids) for r in rollouts], dtype=torch.float32), None, replay)
+                     deg, torch.tensor([len(r.completion_ids) for r in rollouts], dtype=torch.float32), None, replay,
+                     traj, [counted_completion_tokens(r) for r in rollouts])
+
+
+def counted_completion_tokens(r: Rollout) -> int:
+    """Completion tokens of a rollout that the policy itself produced (environment tokens in between do not count)."""
+    return int(len(r.completion_ids) if r.completion_mask is None else np.asarray(r.completion_mask, bool).sum())
+
+
+def filler_batch() -> GRPOBatch:
+    """A micro-batch that scores nothing: three tokens, every label ignored. A rank that has fewer rows than the
+    world has micro-steps runs these in the empty slots, so that it still enters every collective of the step (the
+    normaliser reduction, expert dispatch, gradient reduction) and adds exactly zero to the loss and the gradients."""
+    r = Rollout(np.zeros(2, np.int64), np.zeros(1, np.int64), None, 0.0, completion_mask=np.zeros(1, bool))
+    return build_grpo_batch([r], torch.zeros(1), torch.ones(1, dtype=torch.bool))
 
 
 def build_grpo_tree_batch(rollouts: list[Rollout], adv: torch.Tensor, degenerate: torch.Tensor, group_size: int) -> GRPOBatch:
@@ -105,6 +125,7 @@ def build_grpo_tree_batch(rollouts: list[Rollout], adv: torch.Tensor, degenerate
     tree = pack_trees(groups, masks)
     T = tree.input_ids.numel()
     a, old, deg = torch.zeros(T), torch.zeros(T), torch.zeros(T, dtype=torch.bool)
+    traj = torch.zeros(T, dtype=torch.int64)
     has_old = all(r.sampler_logprobs is not None for r in rollouts)
     i = 0
     for own in tree.branch_slices:
@@ -112,13 +133,15 @@ def build_grpo_tree_batch(rollouts: list[Rollout], adv: torch.Tensor, degenerate
             r = rollouts[i]
             lo, hi = start - 1, stop - 1                  # the labels that score this branch's completion tokens
             a[lo:hi] = float(adv[i])
+            traj[lo:hi] = i
             deg[lo:hi] = bool(degenerate[i])
             if has_old:
                 old[lo:hi] = torch.from_numpy(np.asarray(r.sampler_logprobs, np.float32))
             i += 1
     n_scored = int((tree.labels != -100).sum())
     return GRPOBatch(tree.input_ids, tree.position_ids, tree.labels, tree.cu_seqlens, n_scored, a, old, has_old, deg,
-                     torch.tensor([len(r.completion_ids) for r in rollouts], dtype=torch.float32), tree.allowed)
+                     torch.tensor([len(r.completion_ids) for r in rollouts], dtype=torch.float32), tree.allowed, None,
+                     traj, [counted_completion_tokens(r) for r in rollouts])
 
 
 class GRPOTrainer(Trainer):
@@ -142,7 +165,19 @@ class GRPOTrainer(Trainer):
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.parallel.dp_group)
         return int(t.item())
 
+    def _world_sum(self, x: float) -> float:
+        if self.parallel is None:
+            return x
+        import torch.distributed as dist
+
+        t = torch.tensor([x], dtype=torch.float64, device=self.device)
+        dist.all_reduce(t, group=self.parallel.dp_group)
+        return float(t.item())
+
     def plan_round(self, rollouts: list[Rollout]) -> list[GRPOBatch]:
+        """The micro-batches of one round = one optimizer step. Every rank returns the same number of them (slots a
+        rank cannot fill hold a filler batch that scores nothing), and each carries the ROUND's denominator: this
+        rank's share by ``loss_type``, summed over the data-parallel ranks."""
         g = self.grpo
         rewards = torch.tensor([r.reward for r in rollouts], dtype=torch.float32)
         adv, degenerate = adv_mod.group_advantages(rewards, g.num_generations, g.scale_rewards, g.std_floor)
@@ -152,36 +187,45 @@ class GRPOTrainer(Trainer):
                 raise RuntimeError(f"{self.zero_gradient_rounds} rounds in a row carried no learning signal")
         else:
             self.zero_gradient_rounds = 0
-        self._round_tokens = float(sum(len(r.completion_ids) for r in rollouts))
+        share = objective.round_denominator(g.loss_type, [counted_completion_tokens(r) for r in rollouts],
+                                            [bool(d) for d in degenerate], g.max_completion_length)
+        denominator = max(self._world_sum(share), 1.0)
         out = []
+        world_max = self._world_max if self.parallel else None
         if getattr(g, "tree_packing", False):
             G = g.num_generations
             group_len = [len(rollouts[i].prompt_ids) - 1 + sum(1 + len(r.completion_ids) for r in rollouts[i:i + G])
                          for i in range(0, len(rollouts), G)]
-            for b in microbatch.plan_microbatches(group_len, g.token_budget, self._world_max if self.parallel else None):
+            for b in microbatch.plan_microbatches(group_len, g.token_budget, world_max):
                 if not b:
+                    out.append(filler_batch())
                     continue
                 idx = [i for gi in sorted(b) for i in range(gi * G, (gi + 1) * G)]
                 out.append(build_grpo_tree_batch([rollouts[i] for i in idx], adv[idx], degenerate[idx], G))
-            return out
-        lengths = [len(r.prompt_ids) + len(r.completion_ids) for r in rollouts]
-        bins = microbatch.plan_microbatches(lengths, g.token_budget, self._world_max if self.parallel else None)
-        for b in bins:
-            if not b:
-                continue
-            out.append(build_grpo_batch([rollouts[i] for i in b], adv[b], degenerate[b]))
+        else:
+            lengths = [len(r.prompt_ids) + len(r.completion_ids) for r in rollouts]
+            for b in microbatch.plan_microbatches(lengths, g.token_budget, world_max):
+                out.append(build_grpo_batch([rollouts[i] for i in b], adv[b], degenerate[b]) if b else filler_batch())
+        for b in out:
+            b.denominator = denominator
         return out
 
     def _rounds(self):
+        """One list of micro-batches per round: the trainer loop runs a list as exactly one optimizer step, so the
+        next round's rollouts are requested only after this round's update (and weight push) has happened."""
         while True:
             rollouts = self.rollout_source(self.rounds_done)
             if rollouts is None:
                 return
             batches = self.plan_round(rollouts)
-            self.args.gradient_accumulation_steps = max(1, len(batches))
-            for b in batches:
-                yield b.pin() if torch.cuda.is_available() else b
+            yield [b.pin() if torch.cuda.is_available() else b for b in batches]
             self.rounds_done += 1
+
+    def skip_consumed(self, it):
+        """A resumed run continues with round ``global_step``: one round is one optimizer step, and rounds the
+        interrupted run already trained on are not requested again."""
+        self.rounds_done = self.global_step
+        return it
 
     # ---- objective -----------------------------------------------------------------------------
     def compute_loss(self, model, batch: GRPOBatch, normalizer):
@@ -204,17 +248,45 @@ class GRPOTrainer(Trainer):
                 over = (objective.capped_fraction(is_w, mask, g.importance_clip_max) > g.trust_region_mask_fraction).to(torch.int32)
                 prev = self.engine.skip_request
                 self.engine.skip_request = over if prev is None else torch.maximum(prev, over)
+            is_w = self._apply_mask_stages(is_w, logp, batch, mask)
         ref = None
         if g.grpo_beta and self.ref_model is not None:
             with torch.no_grad():
                 ref, _ = self.ref_model.token_logprobs(batch.input_ids, batch.position_ids, batch.cu_seqlens, batch.labels)
+        tok_w = None
+        if g.loss_type == "grpo":
+            # the per-sequence mean: every counted token weighs 1 / (counted tokens of its row)
+            per_row = torch.tensor([1.0 / max(n, 1) for n in batch.counted_tokens], dtype=torch.float32, device=logp.device)
+            tok_w = per_row[batch.traj_ids.reshape(-1)]
+        elif g.loss_type in ("dapo", "bnpo"):
+            tok_w = (~batch.degenerate.reshape(-1)).to(torch.float32)      # rows without a signal leave the numerator too
         num, _ = objective.grpo_token_loss(logp, old, batch.advantages, mask, g.epsilon, g.epsilon_high, g.grpo_beta,
-                                           ref, is_w)
-        denom = objective.normalizer(g.loss_type if g.loss_type != "grpo" else "dapo", mask, batch.seq_lengths,
-                                     g.max_completion_length, batch.degenerate)
-        if self.args.gradient_accumulation_steps > 1:
-            denom = torch.as_tensor(max(self._round_tokens, 1.0), device=num.device)
+                                           ref, is_w, tok_w)
+        # one denominator for the whole round (all micro-batches, all data-parallel ranks): gradients are SUMMED over
+        # both, so the loss scale changes neither with the token budget nor with the data-parallel width
+        if batch.denominator > 0:
+            return num / batch.denominator
+        denom = objective.normalizer(g.loss_type, mask, batch.seq_lengths, g.max_completion_length, batch.degenerate)
         return num / denom
+
+    def _apply_mask_stages(self, is_w, logp, batch: GRPOBatch, mask):
+        """The optional trajectory masks (all off by default): a masked trajectory's importance weight becomes 0, which
+        removes its surrogate term and leaves the denominator and the KL anchor in place."""
+        g = self.grpo
+        if g.is_geo_band_min is None and g.is_veto_min is None and g.opsm_delta is None:
+            return is_w
+        traj = batch.traj_ids.reshape(-1)
+        n_traj = len(batch.counted_tokens)
+        corrected = objective.corrected_tokens(batch.old_logprobs, mask)
+        logratio = (logp.detach() - batch.old_logprobs) * corrected
+        keep = torch.ones_like(mask)
+        if g.is_geo_band_min is not None:
+            keep &= objective.geometric_mean_band_mask(logratio, traj, n_traj, corrected, g.is_geo_band_min, g.is_geo_band_max)
+        if g.is_veto_min is not None:
+            keep &= objective.raw_ratio_veto_mask(logratio, traj, n_traj, corrected, g.is_veto_min)
+        if g.opsm_delta is not None:
+            keep &= objective.off_policy_sequence_mask(logratio, corrected, batch.advantages, traj, n_traj, g.opsm_delta)
+        return torch.where(keep, is_w, torch.zeros_like(is_w))
 
     def extra_logs(self) -> dict:
         out = {}

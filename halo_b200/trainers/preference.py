@@ -37,6 +37,8 @@ def sequence_logps(model, batch):
 
 
 class PreferenceTrainer(Trainer):
+    sequence_mean_loss = True
+
     def __init__(self, model, args, train_batches, pref_args: PreferenceArguments | None = None, ref_model=None, **kw):
         super().__init__(model, args, train_batches, **kw)
         self.pref = pref_args or PreferenceArguments()

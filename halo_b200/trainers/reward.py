@@ -33,6 +33,8 @@ def last_token_states(model, batch):
 class RewardTrainer(Trainer):
     """Documents alternate chosen / rejected; loss = -log sigmoid(r_chosen - r_rejected)."""
 
+    sequence_mean_loss = True
+
     def __init__(self, model, args, train_batches, head: SequenceHead, center_coef: float = 0.0, **kw):
         self.head = head
         super().__init__(_WithHead(model, head), args, train_batches, **kw)
@@ -56,6 +58,8 @@ class ClassificationTrainer(RewardTrainer):
 class EmbeddingTrainer(Trainer):
     """Contrastive (in-batch negatives) training of last-token embeddings; documents alternate
     query, positive."""
+
+    sequence_mean_loss = True
 
     def __init__(self, model, args, train_batches, temperature: float = 0.05, **kw):
         super().__init__(model, args, train_batches, **kw)

@@ -1,6 +1,6 @@
 """Kernels of the model families beyond the flagship (residual-stream ops, per-stream norm, gated mean,
 masked-softmax backward, standalone SwiGLU, block-scaled fake quantisation) against fp32 PyTorch statements of the
-same ops. Collected last: the flagship's kernels are judged before these."""
+same ops."""
 
 import pytest
 import torch

@@ -66,9 +66,25 @@ def test_clipped_objective_and_importance_weights():
     assert per[2].item() == pytest.approx(0.8)              # ratio 1/e < 0.8: clipped for a negative one
     num.backward()
     assert logp.grad[1].item() == 0 and logp.grad[2].item() == 0 and logp.grad[0].item() == pytest.approx(-1.0)
-    w = objective.importance_weights(torch.tensor([0.0, 2.0]), torch.tensor([0.0, 0.0]), torch.tensor([True, True]), 2.0)
-    assert w.tolist() == [1.0, 2.0]
+    w = objective.importance_weights(torch.tensor([-1.0, 1.0, 3.0]), torch.tensor([-1.0, -1.0, 0.0]),
+                                     torch.tensor([True, True, True]), 2.0)
+    assert w.tolist() == [1.0, 2.0, 1.0]                    # on-policy, capped, and a token the sampler was certain of
     assert objective.k3_kl(torch.tensor([0.0]), torch.tensor([100.0])).item() == pytest.approx(math.exp(5) - 6)
+    # a capped token keeps a restoring gradient: the ceiling comes from the detached policy value
+    lp = torch.tensor([-9.0, -1.0], requires_grad=True)
+    objective.k3_kl(lp, torch.tensor([0.0, -1.2])).sum().backward()
+    assert lp.grad[0].item() == pytest.approx(1.0 - math.exp(5), rel=1e-5)     # d/dlogp (exp(d) - d - 1) at d = 5
+    assert lp.grad[1].item() == pytest.approx(1.0 - math.exp(-0.2), rel=1e-5) and lp.grad[0].item() < -100
+
+
+def test_round_denominators_by_loss_type():
+    counted, deg = [10, 0, 6, 4], [False, False, True, False]
+    assert objective.round_denominator("dapo", counted, deg, 32) == 14.0
+    assert objective.round_denominator("bnpo", counted, deg, 32) == 14.0
+    assert objective.round_denominator("dr_grpo", counted, deg, 32) == 128.0
+    assert objective.round_denominator("grpo", counted, deg, 32) == 3.0
+    with pytest.raises(ValueError):
+        objective.round_denominator("other", counted, deg, 32)
 
 
 def test_microbatch_plan_is_world_uniform():
@@ -126,6 +142,50 @@ def test_preference_and_grpo_trainers_step():
     assert out["global_step"] == 2 and all(math.isfinite(l["loss"]) for l in out["log_history"])
 
 
+def test_grpo_round_is_one_optimizer_step_whatever_the_token_budget():
+    """Three rounds cut into several micro-batches each: three optimizer steps, the next round's rollouts are asked
+    for only after the previous round's update and weight push, and the loss scale does not depend on the cut."""
+    events = []
+
+    class Push:
+        def push(self, model):
+            events.append("push")
+
+    def run(budget, loss_type):
+        cfg, model = _tiny(moe=False)
+        del events[:]
+
+        def source(i):
+            events.append(f"rollouts {i}")
+            return synthetic_rollouts(i, n_prompts=2, n_generations=4, vocab=512, prompt_len=(4, 8), response_len=(6, 12)) if i < 3 else None
+
+        t = GRPOTrainer(model, TrainingArguments(output_dir="unused", learning_rate=1e-3, optim="adamw_torch", logging_steps=1),
+                        source, grpo_args=GRPOArguments(num_generations=4, token_budget=budget, loss_type=loss_type,
+                                                        max_completion_length=12), device="cpu", weight_sync=Push())
+        steps = []
+        orig = t.engine.clip_and_step
+
+        def counted_step():
+            steps.append(len(events))
+            events.append("step")
+            orig()
+
+        t.engine.clip_and_step = counted_step
+        out = t.train()
+        return out, list(events), model
+
+    out, ev, m_small = run(40, "dapo")
+    assert out["global_step"] == 3 and ev.count("step") == 3
+    assert ev == ["rollouts 0", "step", "push", "rollouts 1", "step", "push", "rollouts 2", "step", "push", "rollouts 3"]
+    for lt in ("dapo", "grpo", "dr_grpo"):
+        a, _, ma = run(40, lt)              # 3-4 micro-batches per round
+        b, _, mb = run(4096, lt)            # one micro-batch per round
+        for x, y in zip(a["log_history"], b["log_history"]):
+            assert x["loss"] == pytest.approx(y["loss"], rel=1e-4, abs=1e-6), lt
+        for (n, p), (_, q) in zip(ma.named_parameters(), mb.named_parameters()):
+            assert torch.allclose(p, q, atol=2e-5), (lt, n)
+
+
 def test_world_metrics_and_small_callbacks():
     from halo_b200.callbacks.extras import EarlyStopCallback, VariableSchedulerCallback
     from halo_b200.trainers.metrics import WorldMetrics
@@ -169,11 +229,17 @@ def test_grpo_mask_stages_rank_rewards_reference_cache_and_async_source(tmp_path
     logratio = torch.tensor([0.0, 0.1, -0.1, 2.0, 2.0, 0.0, 0.0, 6.0])
     band = ob.geometric_mean_band_mask(logratio, traj, 3, mask, 0.5, 2.0)
     assert band.tolist() == [True] * 3 + [False] * 2 + [False] * 3          # traj 1: e^2, traj 2: e^2 > 2
-    veto = ob.raw_ratio_veto_mask(logratio, traj, 3, mask, max_ratio=100.0)
-    assert veto.tolist() == [True] * 5 + [False] * 3                         # only traj 2 holds a ratio > 100
+    low = torch.tensor([0.0, 0.1, -0.1, 2.0, 2.0, 0.0, -12.0, 6.0])
+    veto = ob.raw_ratio_veto_mask(low, traj, 3, mask, veto_min=1e-4)
+    assert veto.tolist() == [True] * 5 + [False] * 3                         # only traj 2 holds a ratio below 1e-4 (e^-12)
+    certain = mask.clone()
+    certain[6] = False                                                       # ... unless that token is not a corrected one
+    assert ob.raw_ratio_veto_mask(low, traj, 3, certain, veto_min=1e-4).all()
     adv = torch.tensor([-1.0] * 3 + [1.0] * 2 + [-1.0] * 3)
-    opsm = ob.off_policy_sequence_mask(torch.zeros(8), torch.tensor([0.5] * 3 + [0.5] * 2 + [0.0] * 3), adv, traj, 3, mask, 0.1)
-    assert opsm.tolist() == [False] * 3 + [True] * 5                         # negative advantage AND divergent: traj 0 only
+    lr = torch.tensor([-0.5] * 3 + [0.5] * 2 + [0.05] * 3)                   # trainer - sampler
+    opsm = ob.off_policy_sequence_mask(lr, mask, adv, traj, 3, 0.1)
+    assert opsm.tolist() == [False] * 3 + [True] * 5                         # negative advantage AND |mean| > delta: traj 0 only
+    assert ob.off_policy_sequence_mask(-lr, mask, adv, traj, 3, 0.1).tolist() == [False] * 3 + [True] * 5   # either direction
     r = ob.dense_rank_rewards([(1, 0), (1, 5), (0, 9), (1, 5), (2, 2), (2, 2), (2, 2), (2, 2)], 4)
     assert r.tolist() == [0.5, 1.0, 0.0, 1.0, 0.5, 0.5, 0.5, 0.5]
     c = ob.centered_logprobs(torch.tensor([-1.0]), torch.tensor([[-1.0, -3.0, -9.0]]), torch.tensor([[True, True, False]]))
