@@ -57,14 +57,13 @@ def main():
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", device_id=dev)
-    from halo_b200.ops import _lib, gemm
-    from halo_b200.ops.moe import moe_experts, router_topk
-    from halo_b200.parallel.runtime import ParallelRuntime
-    from halo_b200.parallel.tensor_parallel import TensorParallel, _all_gather_rows, row_parallel_linear
-    from halo_b200.parallel.zero import FusedShardedAdamW
+    from halo_b200.ops import _lib
 
     hbm, tf = peaks()
     rows = []
+    args = [a for a in sys.argv[1:] if not a.startswith("--")]
+    only = next((a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--only=")), "")
+    out_path = args[0] if args else None
 
     def report(name, ms, flops=0.0, link_bytes=0.0, note=""):
         roof_ms = max(flops / (tf * 1e9) if flops else 0.0, link_bytes / (LINK_GBS * 1e6) if link_bytes else 0.0)
@@ -75,8 +74,28 @@ def main():
         if rank == 0:
             print(f"{name:44s} {ms:8.3f} ms   roofline {roof_ms:7.3f} ms   {rec['fraction_of_roofline']:5.2f}  {note}", flush=True)
 
+    T, H = 65536, 2048
+    if only in ("", "tp"):
+        bench_tensor_parallel(world, dev, report, timed, T, H)
+    if only in ("", "zero"):
+        bench_sharded_optimizer(world, dev, report, timed)
+    if only in ("", "moe"):
+        bench_moe_layer(world, dev, report, timed, T, H)
+    _lib.raise_on_status(dev)
+    if rank == 0 and out_path:
+        os.makedirs(os.path.dirname(out_path) or ".", exist_ok=True)
+        json.dump({"world": world, "link_gbs": LINK_GBS, "measured_copy_gbs": MEASURED_COPY_GBS, "bf16_tflops": tf, "rows": rows},
+                  open(out_path, "w"), indent=1)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def bench_tensor_parallel(world, dev, report, timed, T, H):
+    from halo_b200.ops import gemm
+    from halo_b200.parallel.tensor_parallel import TensorParallel, _all_gather_rows, row_parallel_linear
+
     # ---- row-parallel GEMM with the reduce-scatter's transfer in its epilogue (O-projection shape, TP = world) ----
-    T, H, K = 65536, 2048, 4096 // world
+    K = 4096 // world
     tp = TensorParallel(dist.group.WORLD, dev, hidden=H, max_tokens=T)
     x = (torch.randn(T, K, device=dev) * 0.05).bfloat16()
     w = (torch.randn(H, K, device=dev) * 0.05).bfloat16()
@@ -99,6 +118,11 @@ def main():
     report("sequence gather by peer pulls", timed(lambda: _all_gather_rows(shard, tp)), 0.0, link)
     full = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
     report("  baseline: NCCL all-gather", timed(lambda: dist.all_gather_into_tensor(full, shard)), 0.0, link)
+
+
+
+def bench_sharded_optimizer(world, dev, report, timed):
+    from halo_b200.parallel.zero import FusedShardedAdamW
 
     # ---- reduce-scatter + AdamW + all-gather of the replicated parameters (1.4 B parameters) -----------------------
     n = 1_400_000_000 // 8 * 8
@@ -123,25 +147,42 @@ def main():
     report("  baseline: NCCL all-reduce of the gradients alone", timed(baseline_zero, iters=5, warmup=2), 0.0, link)
     del opt, p, g
 
-    # ---- expert dispatch + grouped GEMMs + combine over peer memory (one MoE layer forward, 30B-A3B shapes) -----------
+
+
+def bench_moe_layer(world, dev, report, timed, T, H):
+    """One MoE layer at the 30B-A3B shapes (128 experts of FFN 768, top-8, EP = world), forward and forward + backward,
+    with the token movement inside the GEMM kernels and as separate push / pull kernels."""
+    from halo_b200.ops.moe import moe_experts, router_topk
+    from halo_b200.parallel.runtime import SymmetricTransport
+
     E, F, topk = 128, 768, 8
-    parallel = ParallelRuntime.for_expert_parallel(world, dev)
-    parallel.transport.configure(max_tokens=T, top_k=topk, hidden=H, n_local_experts=E // world)
     xm = (torch.randn(T, H, device=dev) * 0.05).bfloat16()
     idx, wts = router_topk(torch.randn(T, E, device=dev), topk, True)
     wgu = (torch.randn(E // world, 2 * F, H, device=dev) * 0.05).bfloat16()
     wdn = (torch.randn(E // world, H, F, device=dev) * 0.05).bfloat16()
-    flops = 2.0 * T * topk * 3 * H * F
-    link = 2.0 * (world - 1) / world * T * topk * H * 2.0      # rows out to the experts and back
-    with torch.no_grad():
-        ms = timed(lambda: moe_experts(xm, idx, wts, wgu, wdn, parallel.transport), iters=5, warmup=2)
-    report("MoE layer forward: push, grouped GEMMs, pull", ms, flops, link, "roofline: the slower of the GEMMs and the two transfers")
-    _lib.raise_on_status(dev)
-    if rank == 0 and len(sys.argv) > 1:
-        os.makedirs(os.path.dirname(sys.argv[1]) or ".", exist_ok=True)
-        json.dump({"world": world, "link_gbs": LINK_GBS, "bf16_tflops": tf, "rows": rows}, open(sys.argv[1], "w"), indent=1)
-    dist.barrier()
-    dist.destroy_process_group()
+    gout = (torch.randn(T, H, device=dev) * 0.05).bfloat16()
+    fwd_flops = 2.0 * T * topk * 3 * H * F
+    one_way = (world - 1) / world * T * topk * H * 2.0          # rows out to the experts, or back
+    for fused in (True, False):
+        tr = SymmetricTransport(dist.group.WORLD, dev)
+        tr.fused = fused
+        tr.configure(max_tokens=T, top_k=topk, hidden=H, n_local_experts=E // world)
+        name = "movement inside the GEMM kernels" if fused else "separate push / pull kernels"
+        with torch.no_grad():
+            ms = timed(lambda: moe_experts(xm, idx, wts, wgu, wdn, tr), iters=5, warmup=2)
+        # with the movement inside the kernels both directions overlap the products: the bound is the slower of the GEMMs
+        # and the two transfers
+        report(f"MoE layer forward, {name}", ms, fwd_flops, 2.0 * one_way, "roofline: the slower of the GEMMs and the two transfers")
+
+        def fwd_bwd():
+            xa = xm.detach().requires_grad_()
+            wa, wb = wgu.detach().requires_grad_(), wdn.detach().requires_grad_()
+            moe_experts(xa, idx, wts, wa, wb, tr).backward(gout)
+
+        ms = timed(fwd_bwd, iters=5, warmup=2)
+        report(f"MoE layer forward + backward, {name}", ms, 3.0 * fwd_flops, 4.0 * one_way)
+        del tr
+        torch.cuda.empty_cache()
 
 
 if __name__ == "__main__":

@@ -46,7 +46,7 @@ def find_nvcc() -> str:
 
 
 def _newest_header_mtime() -> float:
-    return max((p.stat().st_mtime for p in CSRC_DIR.glob("*.cuh")), default=0.0)
+    return max((p.stat().st_mtime for p in list(CSRC_DIR.glob("*.cuh")) + list(CSRC_DIR.glob("*.h"))), default=0.0)
 
 
 def _compile_one(nvcc: str, src: Path, obj: Path, verbose: bool) -> str:

@@ -250,7 +250,8 @@ __global__ void route_layout_kernel(const int* __restrict__ counts_all, int n_ra
 __global__ void __launch_bounds__(1024)
 route_place_kernel(const int* __restrict__ topk_idx, long long n_slots, int E,
                    const int* __restrict__ block_hist /* scanned */,
-                   const int* __restrict__ dst_base, int* __restrict__ slot_row) {
+                   const int* __restrict__ dst_base, int* __restrict__ slot_row,
+                   const int* __restrict__ my_prefix /* or null */, int* __restrict__ send_slot /* or null */) {
     extern __shared__ int sh[];
     int* base = sh;            // [E] running position of each expert inside this block
     int* warp_cnt = sh + E;    // [32][E]
@@ -281,8 +282,12 @@ route_place_kernel(const int* __restrict__ topk_idx, long long n_slots, int E,
             base[ee] = run;
         }
         __syncthreads();
-        if (e >= 0) slot_row[s] = warp_cnt[warp * E + e] + rank_in_warp;
-        else if (s < n_slots) slot_row[s] = -1;
+        if (e >= 0) {
+            const int row = warp_cnt[warp * E + e] + rank_in_warp;
+            slot_row[s] = row;
+            // the same slots listed in destination order (expert by expert, rows ascending): what a sender walks
+            if (send_slot) send_slot[my_prefix[e] + (row - dst_base[e])] = (int)s;
+        } else if (s < n_slots) slot_row[s] = -1;
         __syncthreads();
     }
 }
@@ -578,8 +583,8 @@ int halo_route_layout(const int* counts_all, int n_ranks, int E, int me, int* se
     return HALO_LAUNCH_CHECK();
 }
 
-int halo_route_place(const int* idx, long long n_slots, int E, const int* block_hist,
-                     const int* dst_base, int* slot_row, void* stream) {
+static int route_place_launch(const int* idx, long long n_slots, int E, const int* block_hist, const int* dst_base,
+                              int* slot_row, const int* my_prefix, int* send_slot, void* stream) {
     const int nb = halo_route_blocks(n_slots);
     if (nb == 0) return 0;
     const int smem = (E + 32 * E) * sizeof(int);
@@ -591,8 +596,20 @@ int halo_route_place(const int* idx, long long n_slots, int E, const int* block_
         configured = true;
     }
     route_place_kernel<<<nb, 1024, smem, (cudaStream_t)stream>>>(idx, n_slots, E, block_hist, dst_base,
-                                                                slot_row);
+                                                                slot_row, my_prefix, send_slot);
     return HALO_LAUNCH_CHECK();
+}
+
+int halo_route_place(const int* idx, long long n_slots, int E, const int* block_hist,
+                     const int* dst_base, int* slot_row, void* stream) {
+    return route_place_launch(idx, n_slots, E, block_hist, dst_base, slot_row, nullptr, nullptr, stream);
+}
+
+// As halo_route_place, and also send_slot[p] = the slot that sits at position p of this rank's destination-ordered
+// send list (my_prefix[e] = first position of expert e's slots in that list).
+int halo_route_place_send(const int* idx, long long n_slots, int E, const int* block_hist, const int* dst_base,
+                          int* slot_row, const int* my_prefix, int* send_slot, void* stream) {
+    return route_place_launch(idx, n_slots, E, block_hist, dst_base, slot_row, my_prefix, send_slot, stream);
 }
 
 static int fill_peers(PeerPtrs* out, void* const* host_ptrs, int n) {

@@ -77,8 +77,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait. `abort_flag` is a CTA-shared word every role polls; `status` is the kernel's
 // global status word. Returns false when the wait gave up (or another role already did).
+// `budget_ns`: how long to wait. Roles of a kernel whose producer itself waits on another GPU pass that wait's budget
+// on top of their own, so that they outlast it and leave through the abort flag instead of timing out first.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status) {
+                                          int* status, uint64_t budget_ns = HALO_WAIT_BUDGET_NS) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = global_timer_ns();
     uint32_t spins = 0;
@@ -86,7 +88,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 255u) == 0u) {
             if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > HALO_WAIT_BUDGET_NS) {
+            if (global_timer_ns() - t0 > budget_ns) {
                 *abort_flag = 1;
                 if (status) atomicCAS(status, kStatusOk, kStatusWaitTimeout);
                 return false;

@@ -34,6 +34,8 @@ CATALOGUE = {
     "HALO_ROLLOUT_WAIT_SECONDS": "how long a trainer waits for a round from its rollout rank",
     "HALO_GEMM_PAIR": "CTA-pair GEMM: 1 where it wins (default), 0 never, 2 everywhere",
     "HALO_ATTN_FWD_VARIANT": "forward attention kernel form (2 = output kept in TMEM, the default)",
+    "HALO_MOE_FUSED": "expert products with the token movement inside the GEMM kernels (1, default) or as separate push / pull kernels (0)",
+    "HALO_PEER_WAIT_MS": "how long a kernel waits for rows or a flag from a peer GPU before it gives up with a status (default 20000)",
     "HALO_ROW_BLOCKS_PER_SM": "thread blocks per SM of the expert row kernels (dispatch / combine)",
     "DIST_NCCL_TIMEOUT_MINUTES": "collective watchdog of every process group",
     "DIST_STORE_TIMEOUT_HOURS": "timeout of store-based joins that outlast the watchdog",
@@ -154,6 +156,10 @@ def weight_sync_chunk_bytes() -> int:
 
 def weight_sync_gather_ahead() -> int:
     return env_non_negative_int("HALO_WEIGHT_SYNC_GATHER_AHEAD", 1)
+
+
+def moe_fused() -> bool:
+    return env_flag("HALO_MOE_FUSED", True)
 
 
 def ep_capacity_factor() -> float:

@@ -120,8 +120,15 @@ class LocalTransport:
     rank = 0
 
     def __init__(self, capacity_factor: float = 1.0):
+        from halo_b200 import env
+
         self.capacity_factor = capacity_factor
-        self._ptr_cache: dict[int, torch.Tensor] = {}
+        self.fused = env.moe_fused()
+        self.seq = 0
+        self.max_tiles = 0
+        self.n_experts = 0
+        self._ctrl = None
+        self._live: dict[int, torch.Tensor] = {}
 
     def capacity(self, n_slots: int, n_local_experts: int) -> int:
         # every slot lands here; each expert segment is padded to a multiple of 128 rows
@@ -137,6 +144,25 @@ class LocalTransport:
         """Host array of every rank's base pointer for this buffer (here: just ours); it travels to
         the kernels by value."""
         return (_lib.c_void_p * 1)(buf.data_ptr())
+
+    # ---- control block of the fused path (one rank: the handshake is with itself) ----
+    def prepare_ctrl(self, n_experts: int, capacity: int, device) -> None:
+        max_tiles = capacity // 128
+        if self._ctrl is None or self.n_experts != n_experts or self.max_tiles < max_tiles or self._ctrl.device != device:
+            self.n_experts, self.max_tiles = n_experts, max_tiles
+            self._ctrl = torch.zeros(2 * n_experts + 1 + 2 * max_tiles, dtype=torch.int32, device=device)
+            self.seq = 0
+
+    def next_seq(self) -> int:
+        self.seq += 1
+        return self.seq
+
+    def ctrl_table(self):
+        return (_lib.c_void_p * 1)(self._ctrl.data_ptr())
+
+    def arrive_table(self, seq: int):
+        off = 4 * (2 * self.n_experts + 1 + (seq & 1) * self.max_tiles)
+        return (_lib.c_void_p * 1)(self._ctrl.data_ptr() + off)
 
     def barrier(self, channel: int = 0) -> None:
         """All ranks' writes issued before this point are visible to reads issued after it."""
@@ -168,6 +194,13 @@ class RoutingState:
     total_rows: torch.Tensor        # int32 [1]
     counts: torch.Tensor            # int32 [E] this rank's slots per expert
     lists: dict = field(default_factory=dict)
+    # fused path only
+    send_slot: torch.Tensor | None = None    # int32 [T*k] slot ids in destination order
+    units: torch.Tensor | None = None        # push units (bytes)
+    n_units: torch.Tensor | None = None      # int32 [1]
+    tiles: torch.Tensor | None = None        # receive-buffer tiles in arrival order (bytes)
+    n_tiles: torch.Tensor | None = None      # int32 [1]
+    seq: int = 0                             # control-block call number of the forward
 
 
 def _work_bytes() -> int:
@@ -307,6 +340,230 @@ def grouped_down_fwd(state: RoutingState, act, w_down, out_rows):
 
 
 # ---------------------------------------------------------------------------------------------
+# fused path: counts through peer memory, dispatch inside GEMM 1, combine inside the last GEMM's epilogue
+# ---------------------------------------------------------------------------------------------
+def _fused(transport) -> bool:
+    return bool(getattr(transport, "fused", False)) and hasattr(transport, "ctrl_table")
+
+
+def plan_routing_fused(topk_idx: torch.Tensor, n_experts: int, transport) -> RoutingState:
+    """Routing state of one call on the fused path: this rank's histogram, the handshake that hands it to every peer
+    and derives every receive layout, slot placement with the destination-ordered send list, the push units and the
+    receive-buffer tiles in arrival order. All on the device; nothing is read back."""
+    T, k = topk_idx.shape
+    if T * k >= 1 << 24 or n_experts > 256:
+        raise ValueError(f"the fused expert path tags rows with 24-bit slot numbers and plans up to 256 experts "
+                         f"(got {T * k} slots, {n_experts} experts); set HALO_MOE_FUSED=0 for larger calls")
+    n_ranks, me = transport.n_ranks, transport.rank
+    n_local = n_experts // n_ranks
+    capacity = transport.capacity(T * k, n_local)
+    dev = topk_idx.device
+    if hasattr(transport, "prepare_ctrl"):
+        transport.prepare_ctrl(n_experts, capacity, dev)
+    L = _lib.lib()
+    n_slots = T * k
+    idx = topk_idx.contiguous()
+    n_blocks = L.halo_route_blocks(_lib.c_ll(n_slots))
+    block_hist = torch.empty((max(n_blocks, 1), n_experts), dtype=torch.int32, device=dev)
+    counts = torch.empty(n_experts, dtype=torch.int32, device=dev)
+    s = _lib.stream_ptr(dev)
+    status = _lib.ptr(_lib.status_word(dev))
+    _lib.check(L.halo_route_count(_lib.ptr(idx), _lib.c_ll(n_slots), _lib.c_int(n_experts), _lib.ptr(block_hist),
+                                  _lib.ptr(counts), s), "halo_route_count")
+    ints = torch.empty(2 * n_local + 2 * n_experts + 3, dtype=torch.int32, device=dev)
+    seg_start, seg_rows = ints[:n_local], ints[n_local:2 * n_local]
+    dst_base = ints[2 * n_local:2 * n_local + n_experts]
+    my_prefix = ints[2 * n_local + n_experts:2 * n_local + 2 * n_experts]
+    total_rows, n_units, n_tiles = (ints[2 * n_local + 2 * n_experts + i:2 * n_local + 2 * n_experts + i + 1] for i in range(3))
+    seq = transport.next_seq()
+    ctrl = transport.ctrl_table()
+    _lib.check(L.halo_moe_handshake(ctrl, _lib.c_int(me), _lib.c_int(n_ranks), _lib.c_int(n_experts), _lib.c_int(seq),
+                                    _lib.c_int(transport.max_tiles), _lib.ptr(counts), _lib.c_int(capacity),
+                                    _lib.ptr(seg_start), _lib.ptr(seg_rows), _lib.ptr(dst_base), _lib.ptr(total_rows),
+                                    _lib.ptr(my_prefix), status, s), "halo_moe_handshake")
+    slot_row = torch.empty(n_slots, dtype=torch.int32, device=dev)
+    send_slot = torch.empty(n_slots, dtype=torch.int32, device=dev)
+    _lib.check(L.halo_route_place_send(_lib.ptr(idx), _lib.c_ll(n_slots), _lib.c_int(n_experts), _lib.ptr(block_hist),
+                                       _lib.ptr(dst_base), _lib.ptr(slot_row), _lib.ptr(my_prefix), _lib.ptr(send_slot), s),
+               "halo_route_place_send")
+    max_units = n_slots // 128 + 2 * n_experts + 2
+    units = torch.empty(max_units * int(L.halo_moe_push_unit_bytes()), dtype=torch.uint8, device=dev)
+    _lib.check(L.halo_moe_plan_push(_lib.ptr(counts), _lib.ptr(dst_base), _lib.ptr(my_prefix), _lib.c_int(me),
+                                    _lib.c_int(n_ranks), _lib.c_int(n_experts), _lib.c_int(capacity), _lib.ptr(units),
+                                    _lib.ptr(n_units), _lib.c_int(max_units), s), "halo_moe_plan_push")
+    max_tiles = capacity // 128
+    tiles = torch.empty(max(max_tiles, 1) * int(L.halo_moe_tile_bytes()), dtype=torch.uint8, device=dev)
+    _lib.check(L.halo_moe_plan_tiles(ctrl, _lib.c_int(me), _lib.c_int(n_ranks), _lib.c_int(n_experts), _lib.c_int(seq),
+                                     _lib.ptr(seg_start), _lib.ptr(seg_rows), _lib.ptr(tiles), _lib.ptr(n_tiles),
+                                     _lib.c_int(max_tiles), s), "halo_moe_plan_tiles")
+    return RoutingState(n_tokens=T, top_k=k, n_experts=n_experts, n_local=n_local, capacity=capacity, topk_idx=idx,
+                        slot_row=slot_row, seg_start=seg_start, seg_rows=seg_rows, total_rows=total_rows, counts=counts,
+                        send_slot=send_slot, units=units, n_units=n_units, tiles=tiles, n_tiles=n_tiles, seq=seq)
+
+
+def _ep_list(state: RoutingState, gated: int, n_cols: int, k_dim: int, b_mn_stride: int, b_k_stride: int, swiglu_f: int = 0):
+    """Tile list of one grouped product over the receive-buffer tiles in arrival order (cached per routing state)."""
+    key = ("ep", gated, n_cols, k_dim, b_mn_stride, b_k_stride, swiglu_f)
+    hit = state.lists.get(key)
+    if hit is not None:
+        return hit
+    L = _lib.lib()
+    dev = state.slot_row.device
+    tile_n = 128 if swiglu_f else 256
+    width = swiglu_f if swiglu_f else n_cols
+    max_items = max(state.capacity // 128, 1) * ((width + tile_n - 1) // tile_n)
+    lst = torch.empty(max_items * _work_bytes(), dtype=torch.uint8, device=dev)
+    count = torch.empty(1, dtype=torch.int32, device=dev)
+    _lib.check(L.halo_moe_plan_items(_lib.ptr(state.tiles), _lib.ptr(state.n_tiles), _lib.c_int(n_cols), _lib.c_int(k_dim),
+                                     _lib.c_int(b_mn_stride), _lib.c_int(b_k_stride), _lib.c_int(swiglu_f), _lib.c_int(gated),
+                                     _lib.ptr(lst), _lib.ptr(count), _lib.c_int(max_items), _lib.stream_ptr(dev)),
+               "halo_moe_plan_items")
+    state.lists[key] = (lst, count)
+    return lst, count
+
+
+def _dispatch_gemm(transport, state: RoutingState, seq: int, x, slot_w, recv, meta, row_w, b2d, c, aux, b_mn: int, epi: int,
+                   swiglu_f: int, lst_cnt):
+    """Kernel A: this rank's rows of ``x`` go to their owners' ``recv`` buffers while the tiles of this rank's own
+    ``recv`` are multiplied with the expert bank ``b2d`` as they fill up."""
+    lst, cnt = lst_cnt
+    dev = x.device
+    H = x.shape[1]
+    _lib.check(_lib.lib().halo_moe_dispatch_gemm(
+        _lib.ptr(x), _lib.ptr(state.send_slot), _lib.ptr(state.units), _lib.ptr(state.n_units), _lib.ptr(slot_w),
+        transport.peer_table(recv), transport.peer_table(meta), transport.peer_table(row_w) if row_w is not None else None,
+        transport.arrive_table(seq), _lib.c_int(transport.n_ranks), _lib.c_int(transport.rank), _lib.c_int(H),
+        _lib.c_int(state.top_k), _lib.ptr(recv), _lib.c_ll(recv.shape[0]), _lib.ptr(b2d), _lib.c_ll(b2d.shape[0]),
+        _lib.c_ll(b2d.shape[1]), _lib.c_ll(b2d.stride(0)), _lib.ptr(c), _lib.ptr(aux), _lib.c_ll(c.stride(0)),
+        _lib.c_ll(aux.stride(0) if aux is not None else 0), _lib.c_int(b_mn), _lib.c_int(epi), _lib.c_int(swiglu_f),
+        _lib.ptr(lst), _lib.ptr(cnt), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev)), "halo_moe_dispatch_gemm")
+
+
+def _gemm_combine(transport, a, b2d, slots, meta, b_mn: int, lst_cnt):
+    """Kernel B: grouped product of the local rows ``a`` with the expert bank, each output row stored into the slot
+    buffer of the rank that owns the token."""
+    lst, cnt = lst_cnt
+    dev = a.device
+    _lib.check(_lib.lib().halo_moe_gemm_combine(
+        _lib.ptr(a), _lib.c_ll(a.shape[0]), _lib.c_ll(a.shape[1]), _lib.c_ll(a.stride(0)), _lib.ptr(b2d),
+        _lib.c_ll(b2d.shape[0]), _lib.c_ll(b2d.shape[1]), _lib.c_ll(b2d.stride(0)), transport.peer_table(slots), _lib.ptr(meta),
+        _lib.c_int(transport.n_ranks), _lib.c_ll(slots.stride(0)), _lib.c_int(b_mn), _lib.ptr(lst), _lib.ptr(cnt),
+        _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev)), "halo_moe_gemm_combine")
+
+
+def _zero_pads(state: RoutingState, buf, meta, row_w):
+    dev = buf.device
+    _lib.check(_lib.lib().halo_moe_zero_pads(_lib.ptr(buf), _lib.ptr(meta), _lib.ptr(row_w), _lib.ptr(state.seg_start),
+                                             _lib.ptr(state.seg_rows), _lib.c_int(state.n_local), _lib.c_int(buf.shape[1]),
+                                             _lib.c_int(state.capacity), _lib.stream_ptr(dev)), "halo_moe_zero_pads")
+
+
+def _slot_sum(state: RoutingState, slots, w32, out):
+    T, k = state.n_tokens, state.top_k
+    dev = out.device
+    _lib.check(_lib.lib().halo_moe_slot_sum(_lib.ptr(slots), _lib.ptr(state.slot_row), _lib.ptr(w32), _lib.ptr(out), _lib.c_ll(T),
+                                            _lib.c_int(k), _lib.c_int(out.shape[1]), _lib.c_int(state.capacity),
+                                            _lib.stream_ptr(dev)), "halo_moe_slot_sum")
+
+
+def _fused_forward(ctx, x, topk_idx, topk_w, w_gate_up, w_down, transport, state_out, grad_mode, skip_output):
+    T, H = x.shape
+    E_local, F2, _ = w_gate_up.shape
+    F = F2 // 2
+    n_experts = E_local * transport.n_ranks
+    k = topk_idx.shape[1]
+    dev = x.device
+    state = plan_routing_fused(topk_idx, n_experts, transport)
+    cap = state.capacity
+    recv_x = transport.buffer("recv_x", cap, H, torch.bfloat16, dev)
+    meta = transport.buffer("row_meta", cap, 1, torch.int32, dev)
+    _zero_pads(state, recv_x, meta, None)
+    need_grad = grad_mode and any(ctx.needs_input_grad)
+    act = _alloc(transport, (cap, F), torch.bfloat16, dev)
+    pre = _alloc(transport, (cap, F2), torch.bfloat16, dev) if need_grad else None
+    lst1 = _ep_list(state, 1, F2, H, F2, 0, F)
+    _dispatch_gemm(transport, state, state.seq, x, None, recv_x, meta, None, w_gate_up.reshape(E_local * F2, H), act, pre, 0,
+                   EPI_SWIGLU, F, lst1)
+    w32 = topk_w.float().contiguous()
+    out = _alloc(transport, tuple(x.shape), x.dtype, dev)
+    if not (skip_output and need_grad):
+        slots = transport.buffer("slots", T * k, H, torch.bfloat16, dev)
+        lst2 = _ep_list(state, 0, H, F, H, 0)
+        _gemm_combine(transport, act, w_down.reshape(E_local * H, F), slots, meta, 0, lst2)
+        transport.barrier()
+        _slot_sum(state, slots, w32, out)
+    if need_grad:
+        if transport.transient_buffers:
+            recv_x = recv_x.clone()
+        ctx.save_for_backward(recv_x, pre, w32, w_gate_up, w_down)
+        ctx.state = state
+        ctx.transport = transport
+    if state_out is not None:
+        state_out.append(state)
+    return out
+
+
+def _fused_backward(ctx, dout):
+    recv_x, pre, w32, w_gate_up, w_down = ctx.saved_tensors
+    state, transport = ctx.state, ctx.transport
+    T, k = state.n_tokens, state.top_k
+    E_local, F2, H = w_gate_up.shape
+    F = F2 // 2
+    cap = state.capacity
+    dev = dout.device
+    L = _lib.lib()
+    s = _lib.stream_ptr(dev)
+    dout = dout.contiguous()
+    n_ranks, me = transport.n_ranks, transport.rank
+    # 1. a handshake of its own: every rank is done with the buffers of its previous call, the arrival counters restart
+    seq = transport.next_seq()
+    _lib.check(L.halo_moe_handshake(transport.ctrl_table(), _lib.c_int(me), _lib.c_int(n_ranks), _lib.c_int(state.n_experts),
+                                    _lib.c_int(seq), _lib.c_int(transport.max_tiles), _lib.c_void_p(0), _lib.c_int(cap),
+                                    _lib.c_void_p(0), _lib.c_void_p(0), _lib.c_void_p(0), _lib.c_void_p(0), _lib.c_void_p(0),
+                                    _lib.ptr(_lib.status_word(dev)), s), "halo_moe_handshake")
+    dy = transport.buffer("recv_dy", cap, H, torch.bfloat16, dev)
+    row_w = transport.buffer("row_w", cap, 1, torch.float32, dev)
+    meta = transport.buffer("row_meta", cap, 1, torch.int32, dev)
+    _zero_pads(state, dy, meta, row_w)
+    # 2. dout rows (with their routing weights) travel to the experts inside the first product:
+    #    dact_u = dout_rows W_down (unscaled activation gradient)
+    dact = _alloc(transport, (cap, F), torch.bfloat16, dev)
+    lst = _ep_list(state, 1, F, H, 0, H)
+    _dispatch_gemm(transport, state, seq, dout, w32, dy, meta, row_w, w_down.reshape(E_local * H, F), dact, None, 1,
+                   EPI_STORE_BF16, 0, lst)
+    # 3. SwiGLU backward with the routing weight folded in (dpre over pre, w * act over dact_u); every row's routing-weight
+    #    gradient goes straight to the token's owner
+    dw_slots = transport.buffer("dw_slots", T * k, 1, torch.float32, dev)
+    dpre, act_w = pre, dact
+    _lib.check(L.halo_moe_swiglu_bwd_scatter(_lib.ptr(pre), _lib.ptr(dact), _lib.ptr(row_w), _lib.ptr(dpre), _lib.ptr(act_w),
+                                             _lib.ptr(meta), transport.peer_table(dw_slots), _lib.c_int(n_ranks),
+                                             _lib.ptr(state.total_rows), _lib.c_int(F), _lib.c_int(cap), s),
+               "halo_moe_swiglu_bwd_scatter")
+    # 4. input-gradient rows dx_rows = dpre W_gate_up, stored straight into the token owners' slots
+    slots = transport.buffer("slots", T * k, H, torch.bfloat16, dev)
+    lst = _ep_list(state, 0, H, F2, 0, F2)
+    _gemm_combine(transport, dpre, w_gate_up.reshape(E_local * F2, H), slots, meta, 1, lst)
+    # 5. weight gradients (local): dW_down[e] = dout_e^T (w * act)_e ; dW_gate_up[e] = dpre_e^T x_e
+    dw_gate_up = dw_down = None
+    if ctx.needs_input_grad[3] or ctx.needs_input_grad[4]:
+        dw_down = _alloc(transport, tuple(w_down.shape), w_down.dtype, dev)
+        pk = _pair_ok(4096, False)
+        _gemm_list(dy, act_w, dw_down.reshape(E_local * H, F), _tile_list(state, "k", pk, m_dim=H, n_dim=F), 1, 1,
+                   EPI_STORE_BF16, pair=pk)
+        dw_gate_up = _alloc(transport, tuple(w_gate_up.shape), w_gate_up.dtype, dev)
+        _gemm_list(dpre, recv_x, dw_gate_up.reshape(E_local * F2, H), _tile_list(state, "k", pk, m_dim=F2, n_dim=H), 1, 1,
+                   EPI_STORE_BF16, pair=pk)
+    # 6. every rank's rows have landed: sum the k slots of each token
+    transport.barrier()
+    dx = _alloc(transport, (T, H), torch.bfloat16, dev)
+    _slot_sum(state, slots, None, dx)
+    # slots of dropped rows (a capacity overflow, reported through the status word) carry no gradient
+    valid = (state.slot_row >= 0) & (state.slot_row < cap // 128 * 128)
+    dw = torch.where(valid, dw_slots[:T * k, 0], torch.zeros((), dtype=torch.float32, device=dev)).view(T, k)
+    return dx, None, dw, dw_gate_up, dw_down, None, None, None, None
+
+
+# ---------------------------------------------------------------------------------------------
 # CPU / oracle implementation of the whole routed FFN (also the gloo-rank path)
 # ---------------------------------------------------------------------------------------------
 def moe_ffn_reference(x, topk_idx, topk_w, w_gate_up, w_down, expert_offset: int = 0):
@@ -335,6 +592,9 @@ def moe_ffn_reference(x, topk_idx, topk_w, w_gate_up, w_down, expert_offset: int
 class _MoEExperts(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, topk_idx, topk_w, w_gate_up, w_down, transport, state_out, grad_mode, skip_output=False):
+        ctx.fused = _fused(transport)
+        if ctx.fused:
+            return _fused_forward(ctx, x, topk_idx, topk_w, w_gate_up, w_down, transport, state_out, grad_mode, skip_output)
         T, H = x.shape
         E_local, F2, _ = w_gate_up.shape
         F = F2 // 2
@@ -383,6 +643,8 @@ class _MoEExperts(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout):
+        if ctx.fused:
+            return _fused_backward(ctx, dout)
         recv_x, pre, w32, w_gate_up, w_down = ctx.saved_tensors
         state, transport = ctx.state, ctx.transport
         T, k = state.n_tokens, state.top_k

@@ -47,6 +47,14 @@ class SymmetricTransport:
         self._barrier_handle = None
         self._side = None
         self.stable_until_backward = True
+        # fused path: dispatch inside the first expert GEMM, combine inside the last one's epilogue, counts exchanged
+        # through peer memory (halo_b200/csrc/moe_fused_sm100.cu)
+        from halo_b200 import env
+
+        self.fused = env.moe_fused()
+        self.seq = 0                      # calls made through the control block (every rank counts alike)
+        self.max_tiles = 0
+        self.n_experts = 0
 
     # ---- provisioning ---------------------------------------------------------------------
     def configure(self, max_tokens: int, top_k: int, hidden: int, n_local_experts: int) -> None:
@@ -63,13 +71,30 @@ class SymmetricTransport:
         cap = int(self.capacity_factor * mean_rows) + 128 * n_local_experts
         cap = (cap + 127) // 128 * 128
         self._cap, self._hidden = cap, hidden
-        for name, cols, dtype in (("recv_x", hidden, torch.bfloat16), ("y_rows", hidden, torch.bfloat16),
-                                  ("recv_dy", hidden, torch.bfloat16), ("dx_rows", hidden, torch.bfloat16),
-                                  ("row_w", 1, torch.float32), ("dwrow", 1, torch.float32)):
-            t = symm.empty((cap, cols), dtype=dtype, device=self.device)
+        slots = max_tokens * top_k
+        if self.fused:
+            self.n_experts = n_local_experts * self.n_ranks
+            self.max_tiles = cap // 128
+            ctrl_ints = 2 * self.n_ranks * self.n_experts + self.n_ranks + 2 * self.max_tiles
+            specs = (("recv_x", cap, hidden, torch.bfloat16), ("recv_dy", cap, hidden, torch.bfloat16),
+                     ("slots", slots, hidden, torch.bfloat16), ("row_w", cap, 1, torch.float32),
+                     ("row_meta", cap, 1, torch.int32), ("dw_slots", slots, 1, torch.float32),
+                     ("ctrl", ctrl_ints, 1, torch.int32))
+        else:
+            specs = (("recv_x", cap, hidden, torch.bfloat16), ("y_rows", cap, hidden, torch.bfloat16),
+                     ("recv_dy", cap, hidden, torch.bfloat16), ("dx_rows", cap, hidden, torch.bfloat16),
+                     ("row_w", cap, 1, torch.float32), ("dwrow", cap, 1, torch.float32))
+        for name, rows, cols, dtype in specs:
+            t = symm.empty((rows, cols), dtype=dtype, device=self.device)
+            if name == "ctrl":
+                t.zero_()
             hdl = symm.rendezvous(t, self.group)
             self._bufs[name] = (t, hdl)
         self._barrier_handle = self._bufs["recv_x"][1]
+        if self.fused:
+            torch.cuda.synchronize(self.device)
+            self._barrier_handle.barrier(channel=self.channel_base)      # every rank's control block is zero before the first call
+            self.seq = 0
 
     def capacity(self, n_slots: int, n_local_experts: int) -> int:
         if self._cap is None:
@@ -88,6 +113,21 @@ class SymmetricTransport:
                 ptrs = list(hdl.buffer_ptrs)
                 return (_lib.c_void_p * self.n_ranks)(*ptrs)
         raise RuntimeError("peer_table() needs a buffer handed out by this transport")
+
+    # ---- control block of the fused path ------------------------------------------------------
+    def next_seq(self) -> int:
+        """Number of the next call through the control block (1, 2, ...): flag value and buffer parity of that call."""
+        self.seq += 1
+        return self.seq
+
+    def ctrl_table(self):
+        return self.peer_table(self._bufs["ctrl"][0])
+
+    def arrive_table(self, seq: int):
+        """Every rank's arrival counters of the call ``seq`` (the control block's second half, by parity)."""
+        off = 4 * (2 * self.n_ranks * self.n_experts + self.n_ranks + (seq & 1) * self.max_tiles)
+        ptrs = [p + off for p in self._bufs["ctrl"][1].buffer_ptrs]
+        return (_lib.c_void_p * self.n_ranks)(*ptrs)
 
     # ---- control plane -----------------------------------------------------------------------
     def exchange_counts(self, counts: torch.Tensor) -> torch.Tensor:

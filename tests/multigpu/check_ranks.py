@@ -16,17 +16,21 @@ def close(a, b, tol, what):
     assert err <= tol * ref + 1e-3, f"{what}: max err {err} (ref max {ref})"
 
 
-def check_expert_transport(parallel, dev, rank, world):
-    """Each rank owns E/world experts; every rank's tokens must come back as if all experts were local."""
+def check_expert_transport(tr, dev, rank, world, what):
+    """Each rank owns E/world experts; every rank's tokens must come back as if all experts were local. Three calls in
+    a row through one transport, with a different number of tokens on every rank and call."""
+    for call in range(3):
+        _check_expert_call(tr, dev, rank, world, f"{what}, call {call}", 1536 - 128 * ((rank + call) % 3), call)
+
+
+def _check_expert_call(tr, dev, rank, world, what, T, call):
     from halo_b200.ops.moe import moe_experts, moe_ffn_reference
 
-    T, H, F, E, k = 1536, 512, 256, 16, 4
-    tr = parallel.transport
-    tr.configure(max_tokens=T, top_k=k, hidden=H, n_local_experts=E // world)
+    H, F, E, k = 512, 256, 16, 4
     g = torch.Generator(device=dev).manual_seed(7)
     wgu_full = (torch.randn(E, 2 * F, H, device=dev, generator=g) * 0.05).bfloat16()
     wd_full = (torch.randn(E, H, F, device=dev, generator=g) * 0.05).bfloat16()
-    g2 = torch.Generator(device=dev).manual_seed(100 + rank)
+    g2 = torch.Generator(device=dev).manual_seed(100 + rank + 17 * call)
     x = torch.randn(T, H, device=dev, generator=g2).bfloat16()
     scores = torch.rand(T, E, device=dev, generator=g2)
     w, idx = torch.topk(scores, k, dim=-1)
@@ -45,16 +49,16 @@ def check_expert_transport(parallel, dev, rank, world):
     wgub, wdb = wgu_full.float().requires_grad_(), wd_full.float().requires_grad_()
     ref = moe_ffn_reference(xb, idx, wb, wgub, wdb)
     ref.backward(gout.float())
-    close(out, ref, 3e-2, "ep out")
-    close(xa.grad, xb.grad, 4e-2, "ep dx")
-    close(wa.grad, wb.grad, 4e-2, "ep dw_route")
+    close(out, ref, 3e-2, f"ep out ({what})")
+    close(xa.grad, xb.grad, 4e-2, f"ep dx ({what})")
+    close(wa.grad, wb.grad, 4e-2, f"ep dw_route ({what})")
     # expert weight gradients: sum over ranks of the reference's per-rank contributions
     gw = wgub.grad.clone()
     gd = wdb.grad.clone()
     dist.all_reduce(gw)
     dist.all_reduce(gd)
-    close(wgu.grad, gw[e0:e1], 5e-2, "ep dw_gate_up")
-    close(wd.grad, gd[e0:e1], 5e-2, "ep dw_down")
+    close(wgu.grad, gw[e0:e1], 5e-2, f"ep dw_gate_up ({what})")
+    close(wd.grad, gd[e0:e1], 5e-2, f"ep dw_down ({what})")
 
 
 def check_fused_optimizer(dev, rank, world):
@@ -214,8 +218,15 @@ def main():
     from halo_b200.ops import _lib
     from halo_b200.parallel.runtime import ParallelRuntime
 
+    from halo_b200.parallel.runtime import SymmetricTransport
+
     parallel = ParallelRuntime.for_expert_parallel(world, dev)
-    check_expert_transport(parallel, dev, rank, world)
+    for fused in (True, False):
+        tr = SymmetricTransport(dist.group.WORLD, dev)
+        tr.fused = fused
+        tr.configure(max_tokens=1536, top_k=4, hidden=512, n_local_experts=16 // world)
+        check_expert_transport(tr, dev, rank, world, "movement inside the GEMM kernels" if fused else "separate push / pull kernels")
+        _lib.raise_on_status(dev)
     check_fused_optimizer(dev, rank, world)
     check_broadcast_and_allreduce(dev, rank, world)
     check_context_parallel(dev, rank, world)

@@ -33,10 +33,16 @@ def test_router_topk(T, E, k):
     _close(a.grad, b.grad, 1e-3, "dlogits")
 
 
+@pytest.mark.parametrize("fused", [True, False])
 @pytest.mark.parametrize("T,H,F,E,k", [(64, 256, 128, 8, 2), (777, 512, 256, 16, 4), (4096, 2048, 768, 32, 8)])
-def test_moe_experts_fwd_bwd(T, H, F, E, k):
+def test_moe_experts_fwd_bwd(T, H, F, E, k, fused):
+    """``fused``: token movement inside the GEMM kernels (push warps + arrival-gated tiles, scatter epilogue) against
+    the separate push / pull kernels; both against the per-expert fp32 loop."""
     from halo_b200.ops import _lib
-    from halo_b200.ops.moe import moe_experts, moe_ffn_reference
+    from halo_b200.ops.moe import LocalTransport, moe_experts, moe_ffn_reference
+
+    transport = LocalTransport()
+    transport.fused = fused
 
     torch.manual_seed(1)
     x = torch.randn(T, H, device="cuda").bfloat16()
@@ -48,7 +54,7 @@ def test_moe_experts_fwd_bwd(T, H, F, E, k):
     idx = idx.to(torch.int32)
 
     xa, wa, wgua, wda = (t.clone().requires_grad_() for t in (x, w, wgu, wd))
-    out = moe_experts(xa, idx, wa, wgua, wda)
+    out = moe_experts(xa, idx, wa, wgua, wda, transport)
     torch.cuda.synchronize()
     assert _lib.read_status() == 0
     xb, wb, wgub, wdb = (t.float().requires_grad_() for t in (x, w, wgu, wd))
@@ -63,6 +69,40 @@ def test_moe_experts_fwd_bwd(T, H, F, E, k):
     _close(wa.grad, wb.grad, 4e-2, "dw_route")
     _close(wgua.grad, wgub.grad, 4e-2, "dw_gate_up")
     _close(wda.grad, wdb.grad, 4e-2, "dw_down")
+
+
+def test_fused_moe_calls_in_a_row_share_one_control_block():
+    """Several layers' worth of calls through one transport (forward, a recomputation that skips its output, backward):
+    the control block's call numbers, buffer parities and arrival counters must carry over from call to call."""
+    from halo_b200.ops import _lib
+    from halo_b200.ops.moe import LocalTransport, moe_experts, moe_ffn_reference
+
+    torch.manual_seed(5)
+    T, H, F, E, k = 1500, 512, 256, 32, 4
+    transport = LocalTransport()
+    transport.fused = True
+    wgu = (torch.randn(E, 2 * F, H, device="cuda") * 0.05).bfloat16()
+    wd = (torch.randn(E, H, F, device="cuda") * 0.05).bfloat16()
+    for step in range(5):
+        x = torch.randn(T - 100 * step, H, device="cuda").bfloat16()
+        w, idx = torch.topk(torch.rand(x.shape[0], E, device="cuda"), k, dim=-1)
+        w = (w / w.sum(-1, keepdim=True)).float()
+        idx = idx.to(torch.int32)
+        with torch.no_grad():
+            first = moe_experts(x, idx, w, wgu, wd, transport)
+        xa, wgua = x.clone().requires_grad_(), wgu.clone().requires_grad_()
+        out = moe_experts(xa, idx, w, wgua, wd, transport, skip_output=step % 2 == 1)
+        g = torch.randn_like(first)
+        out.backward(g)
+        torch.cuda.synchronize()
+        assert _lib.read_status() == 0
+        xb, wgub = x.float().requires_grad_(), wgu.float().requires_grad_()
+        ref = moe_ffn_reference(xb, idx, w, wgub, wd.float())
+        ref.backward(g.float())
+        _close(first, ref, 3e-2, f"out, call {step}")
+        _close(xa.grad, xb.grad, 4e-2, f"dx, call {step}")
+        _close(wgua.grad, wgub.grad, 4e-2, f"dw_gate_up, call {step}")
+    assert transport.seq == 15
 
 
 def test_moe_empty_experts():
