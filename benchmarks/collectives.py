@@ -75,6 +75,8 @@ def main():
             print(f"{name:44s} {ms:8.3f} ms   roofline {roof_ms:7.3f} ms   {rec['fraction_of_roofline']:5.2f}  {note}", flush=True)
 
     T, H = 65536, 2048
+    if only in ("", "link"):
+        bench_link(world, dev, report, timed)
     if only in ("", "tp"):
         bench_tensor_parallel(world, dev, report, timed, T, H)
     if only in ("", "zero"):
@@ -88,6 +90,42 @@ def main():
                   open(out_path, "w"), indent=1)
     dist.barrier()
     dist.destroy_process_group()
+
+
+def bench_link(world, dev, report, timed):
+    """What one GPU reaches towards ONE peer over NVLink with each access form, 1 GiB each way at once on every rank
+    (rank r -> rank r+1): the copy engine, stores from a kernel, loads from a kernel. These are the practical ceilings
+    of the fused kernels' transfers; the roofline column keeps the nominal 900 GB/s."""
+    import torch.distributed._symmetric_memory as symm
+
+    from halo_b200.ops import _lib
+
+    n = 1 << 30
+    buf = symm.empty((n,), dtype=torch.uint8, device=dev)
+    hdl = symm.rendezvous(buf, dist.group.WORLD)
+    src = torch.empty(n, dtype=torch.uint8, device=dev)
+    rank = dist.get_rank()
+    peer = (rank + 1) % world
+    remote = hdl.get_buffer(peer, (n,), torch.uint8)
+    L = _lib.lib()
+    one = (_lib.c_void_p * 1)(int(hdl.buffer_ptrs[peer]))
+
+    def ce_copy():
+        remote.copy_(src)
+
+    def kernel_stores():
+        _lib.check(L.halo_broadcast_bytes(_lib.ptr(src), one, _lib.c_int(1), _lib.c_ll(0), _lib.c_ll(n), _lib.stream_ptr(dev)),
+                   "halo_broadcast_bytes")
+
+    def kernel_loads():
+        _lib.check(L.halo_peer_pull(_lib.ptr(src), _lib.c_void_p(int(hdl.buffer_ptrs[peer])), _lib.c_ll(n), _lib.c_int(0),
+                                    _lib.stream_ptr(dev)), "halo_peer_pull")
+
+    for name, fn in (("1 GiB to one peer: copy engine", ce_copy), ("1 GiB to one peer: stores from a kernel", kernel_stores),
+                     ("1 GiB from one peer: loads from a kernel", kernel_loads)):
+        ms = timed(fn, iters=5, warmup=2)
+        report(name, ms, 0.0, float(n), f"{n / ms / 1e6:.0f} GB/s per direction")
+    hdl.barrier(channel=0)
 
 
 def bench_tensor_parallel(world, dev, report, timed, T, H):
@@ -181,6 +219,19 @@ def bench_moe_layer(world, dev, report, timed, T, H):
 
         ms = timed(fwd_bwd, iters=5, warmup=2)
         report(f"MoE layer forward + backward, {name}", ms, 3.0 * fwd_flops, 4.0 * one_way)
+        if fused:
+            # one more pass with a CUDA event after every phase: where the time goes (this rank's stream)
+            from halo_b200.ops import moe as moe_ops
+
+            moe_ops.PHASE_MARKS = []
+            dist.barrier()
+            fwd_bwd()
+            torch.cuda.synchronize()
+            marks, moe_ops.PHASE_MARKS = moe_ops.PHASE_MARKS, None
+            if dist.get_rank() == 0:
+                for (_, a), (label, b) in zip(marks, marks[1:]):
+                    if label != "start":
+                        print(f"    {label:44s} {a.elapsed_time(b):7.3f} ms", flush=True)
         del tr
         torch.cuda.empty_cache()
 

@@ -201,8 +201,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const GemmWor
                             __nv_bfloat162 gb = *reinterpret_cast<__nv_bfloat162*>(&pg[q]);
                             __nv_bfloat162 ub = *reinterpret_cast<__nv_bfloat162*>(&pu[q]);
                             float2 gf = __bfloat1622float2(gb), uf = __bfloat1622float2(ub);
-                            float a0 = gf.x / (1.f + __expf(-gf.x)) * uf.x;
-                            float a1 = gf.y / (1.f + __expf(-gf.y)) * uf.y;
+                            float a0 = gf.x * sigmoid_fast(gf.x) * uf.x;
+                            float a1 = gf.y * sigmoid_fast(gf.y) * uf.y;
                             o[q] = pack_bf16(a0, a1);
                         }
                         *reinterpret_cast<uint4*>(out + j) = make_uint4(o[0], o[1], o[2], o[3]);

@@ -473,7 +473,7 @@ swiglu_bwd_weighted_kernel(const __nv_bfloat16* pre, const __nv_bfloat16* dact,
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const float2 g = __bfloat1622float2(gh[q]), u = __bfloat1622float2(uh[q]), d = __bfloat1622float2(dh[q]);
-                const float sx = 1.f / (1.f + __expf(-g.x)), sy = 1.f / (1.f + __expf(-g.y));
+                const float sx = sigmoid_fast(g.x), sy = sigmoid_fast(g.y);
                 // the forward rounded act to bf16 before the down projection; use the same value here
                 const float2 a = __bfloat1622float2(__floats2bfloat162_rn(g.x * sx * u.x, g.y * sy * u.y));
                 dot += d.x * a.x + d.y * a.y;

@@ -436,14 +436,33 @@ __device__ __forceinline__ void push_units(const EpParams& ep, volatile int* abo
     }
 }
 
-// One epilogue warp's 32 rows x n_valid columns of a finished tile, scattered to the token owners.
+// One epilogue warp's 32 rows x n_valid columns of a finished tile, sent to the token owners. Every lane owns one
+// accumulator row: it rounds 128 columns at a time to bf16 into its own 256-byte line of the warp's staging buffer and
+// hands that line to the copy engine (cp.async.bulk, shared -> global), which writes it into the owner's slot buffer -
+// local or across NVLink - as one 256-byte burst while the warp goes on with the next columns. The lines are 272
+// bytes apart so that the 32 lanes' 16-byte stores spread over all banks.
+constexpr int kScatterLine = 272;
+constexpr int kScatterStageBytesPerWarp = 32 * kScatterLine;   // 8,704
+
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes)
+                 : "memory");
+}
+
 __device__ __forceinline__ void epilogue_scatter(const GemmParams& p, const EpParams& ep, const GemmWork& w,
                                                  uint32_t t_row, int row_in_tile, uint32_t stage) {
     const int lane = threadIdx.x & 31;
-    const int warp_row0 = row_in_tile - lane;
+    const uint32_t line = stage + lane * kScatterLine;
+    int tag = -1;
+    if (row_in_tile < w.m_valid) tag = ep.meta[w.c_row + row_in_tile];
+    __nv_bfloat16* dst = nullptr;
+    if (tag >= 0)
+        dst = reinterpret_cast<__nv_bfloat16*>(ep.slot_bufs[tag >> kMetaSlotBits]) +
+              (long long)(tag & ((1 << kMetaSlotBits) - 1)) * p.ldc + w.c_col;
 #pragma unroll 1
     for (int c0 = 0; c0 < kBlockN; c0 += 128) {
-        if (c0 >= w.n_valid) break;
+        if (c0 >= w.n_valid) break;                       // uniform across the warp
+        tma_store_wait_read<0>();                         // the copy engine has read this lane's previous line
 #pragma unroll 1
         for (int cc = 0; cc < 128; cc += 32) {
             uint32_t r[32];
@@ -455,31 +474,15 @@ __device__ __forceinline__ void epilogue_scatter(const GemmParams& p, const EpPa
 #pragma unroll
                 for (int q = 0; q < 4; ++q)
                     o[q] = pack_bf16(__uint_as_float(r[j + 2 * q]) * p.alpha, __uint_as_float(r[j + 2 * q + 1]) * p.alpha);
-                const int unit = (cc + j) >> 3;
-                const uint32_t a = stage + lane * 256 + ((unit ^ (lane & 15)) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(line + (cc + j) * 2), "r"(o[0]), "r"(o[1]),
+                             "r"(o[2]), "r"(o[3])
                              : "memory");
             }
         }
-        __syncwarp();
-        const int unit = lane & 15;
-        const int col = c0 + unit * 8;
-#pragma unroll 4
-        for (int kk = 0; kk < 16; ++kk) {
-            const int rr = 2 * kk + (lane >> 4);
-            uint32_t v0, v1, v2, v3;
-            const uint32_t a = stage + rr * 256 + ((unit ^ (rr & 15)) << 4);
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(a));
-            if (warp_row0 + rr < w.m_valid && col + 8 <= w.n_valid) {
-                const int tag = ep.meta[w.c_row + warp_row0 + rr];
-                if (tag >= 0) {
-                    __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(ep.slot_bufs[tag >> kMetaSlotBits]);
-                    const long long slot = tag & ((1 << kMetaSlotBits) - 1);
-                    *reinterpret_cast<uint4*>(base + slot * p.ldc + w.c_col + col) = make_uint4(v0, v1, v2, v3);
-                }
-            }
-        }
-        __syncwarp();
+        fence_proxy_async_smem();                         // this lane's line, written by ordinary stores, is read by the copy engine
+        const int ncols = min(128, w.n_valid - c0);
+        if (dst) bulk_store(dst + c0, line, (uint32_t)ncols * 2u);
+        tma_store_commit();
     }
 }
 
@@ -488,14 +491,25 @@ __global__ void __launch_bounds__(kPush ? kEpPushThreads : kGemmThreads, 1)
 gemm_ep_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ GemmParams p, const __grid_constant__ EpParams ep) {
     if (status_poisoned(p.status)) return;
-    extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t bar_full[kStages], bar_empty[kStages], bar_tfull[2], bar_tempty[2];
-    __shared__ uint32_t tmem_base_slot;
-    __shared__ volatile int abort_flag;
+    // Dynamic shared memory only (no static variables in front of it), declared 1024-byte aligned: operand stages, the
+    // epilogue's staging lines, then the barriers and two scalars.
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    constexpr int kEpiRegion = 4 * (kScatter ? kScatterStageBytesPerWarp : kEpiStageBytesPerWarp);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + kStages * kStageBytes + kEpiRegion);
+    uint64_t* bar_full = bars;
+    uint64_t* bar_empty = bars + kStages;
+    uint64_t* bar_tfull = bars + 2 * kStages;
+    uint64_t* bar_tempty = bars + 2 * kStages + 2;
+    uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+    volatile int& abort_flag = *reinterpret_cast<volatile int*>(bars + 2 * kStages + 5);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t tiles_base = smem_u32(smem_raw);
+    if (tiles_base & 1023u) {      // uniform over the CTA: nobody has touched a barrier or TMEM yet
+        if (threadIdx.x == 0 && p.status) atomicCAS(p.status, kStatusOk, kStatusBadArgument);
+        return;
+    }
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -519,7 +533,12 @@ gemm_ep_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
-    const int total = *p.list_count;
+    // Work items come in groups of p.tiles_n (the column tiles of one 128-row tile, adjacent in the list); a CTA takes
+    // whole groups, so it asks for a row tile's arrival once and its column tiles re-read the same rows from L2.
+    const int tiles_n = max(p.tiles_n, 1);
+    const int n_groups = *p.list_count / tiles_n;
+    const int total = ((n_groups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x) * tiles_n;   // items of this CTA
+    auto item_of = [&](int it) { return ((int)blockIdx.x + (it / tiles_n) * (int)gridDim.x) * tiles_n + it % tiles_n; };
     // consumers of tiles whose producer may be waiting for another GPU's rows outlast that wait
     const uint64_t budget = kPush ? ep.wait_budget_ns + HALO_WAIT_BUDGET_NS : HALO_WAIT_BUDGET_NS;
 
@@ -529,8 +548,8 @@ gemm_ep_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int stage = 0;
             uint32_t phase = 0;
             int ready = 0;   // pad0 of the last tile found complete
-            for (int idx = blockIdx.x; idx < total && !abort_flag; idx += gridDim.x) {
-                const GemmWork w = p.list[idx];
+            for (int it = 0; it < total && !abort_flag; ++it) {
+                const GemmWork w = p.list[item_of(it)];
                 if (kPush && w.pad0 > 0 && w.pad0 != ready) {
                     if (!wait_counter_ge(ep.arrive + (w.pad0 - 1), w.pad1, &abort_flag, p.status, ep.wait_budget_ns)) break;
                     ready = w.pad0;
@@ -573,8 +592,8 @@ gemm_ep_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
-            for (int idx = blockIdx.x; idx < total && !abort_flag; idx += gridDim.x) {
-                const int k_iters = p.list[idx].k_iters;
+            for (int it = 0; it < total && !abort_flag; ++it) {
+                const int k_iters = p.list[item_of(it)].k_iters;
                 if (!mbar_wait(smem_u32(&bar_tempty[acc]), acc_phase ^ 1u, &abort_flag, p.status, budget)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * kBlockN;
@@ -612,11 +631,12 @@ gemm_ep_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // ---------------- epilogue ----------------
         const int quarter = warp & 3;
         const int row_in_tile = quarter * 32 + lane;
-        const uint32_t epi_stage = tiles_base + kStages * kStageBytes + quarter * kEpiStageBytesPerWarp;
+        const uint32_t epi_stage = tiles_base + kStages * kStageBytes +
+                                   quarter * (kScatter ? kScatterStageBytesPerWarp : kEpiStageBytesPerWarp);
         int acc = 0;
         uint32_t acc_phase = 0;
-        for (int idx = blockIdx.x; idx < total && !abort_flag; idx += gridDim.x) {
-            const GemmWork w = p.list[idx];
+        for (int it = 0; it < total && !abort_flag; ++it) {
+            const GemmWork w = p.list[item_of(it)];
             if (!mbar_wait(smem_u32(&bar_tfull[acc]), acc_phase, &abort_flag, p.status, budget)) break;
             tc_fence_after();
             const uint32_t t_row = tmem_base + acc * kBlockN + (uint32_t(quarter * 32) << 16);
@@ -630,6 +650,7 @@ gemm_ep_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 acc_phase ^= 1u;
             }
         }
+        if (kScatter) tma_store_wait<0>();     // every line this lane handed to the copy engine has been written
     } else {
         // ---------------- push warps: this rank's rows to their owners ----------------
         push_units<kPush>(ep, &abort_flag, lane, warp - 6, (int)threadIdx.x - kGemmThreads);
@@ -677,7 +698,7 @@ swiglu_bwd_weighted_scatter_kernel(const __nv_bfloat16* pre, const __nv_bfloat16
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const float2 g = __bfloat1622float2(gh[q]), u = __bfloat1622float2(uh[q]), d = __bfloat1622float2(dh[q]);
-                const float sx = 1.f / (1.f + __expf(-g.x)), sy = 1.f / (1.f + __expf(-g.y));
+                const float sx = sigmoid_fast(g.x), sy = sigmoid_fast(g.y);
                 const float2 a = __bfloat1622float2(__floats2bfloat162_rn(g.x * sx * u.x, g.y * sy * u.y));
                 dot += d.x * a.x + d.y * a.y;
                 const float dx = d.x * sc, dy = d.y * sc;
@@ -710,18 +731,22 @@ static int ep_num_sms() {
     return n;
 }
 
-constexpr int kEpSmemBytes = kStages * kStageBytes + 1024 + 4 * kEpiStageBytesPerWarp;
+// operand stages + epilogue staging (the scatter form's lines are padded: 4 x 8,704 bytes) + barriers; the kernels
+// declare their dynamic shared memory 1024-byte aligned and check that it is, so no alignment slack is provisioned
+constexpr int kEpSmemBytes = kStages * kStageBytes + 4 * kEpiStageBytesPerWarp + 128;
+constexpr int kEpScatterSmemBytes = kStages * kStageBytes + 4 * kScatterStageBytesPerWarp + 128;
 
 template <bool B_MN, bool kPush, bool kScatter>
 static int launch_ep(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, const EpParams& ep, cudaStream_t s) {
+    constexpr int smem = kScatter ? kEpScatterSmemBytes : kEpSmemBytes;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(gemm_ep_kernel<B_MN, kPush, kScatter>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kEpSmemBytes) != cudaSuccess)
+                                 smem) != cudaSuccess)
             return -10;
         configured = true;
     }
-    gemm_ep_kernel<B_MN, kPush, kScatter><<<ep_num_sms(), kPush ? kEpPushThreads : kGemmThreads, kEpSmemBytes, s>>>(ta, tb, p, ep);
+    gemm_ep_kernel<B_MN, kPush, kScatter><<<ep_num_sms(), kPush ? kEpPushThreads : kGemmThreads, smem, s>>>(ta, tb, p, ep);
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -815,7 +840,7 @@ int halo_moe_dispatch_gemm(const void* x, const int* send_slot, const void* unit
                            int n_ranks, int me, int H, int k,
                            const void* A, long long a_rows, const void* B, long long b_rows, long long b_cols, long long ldb,
                            void* C, void* aux, long long ldc, long long ld_aux, int b_mn_major, int epi, int swiglu_f,
-                           const void* list, const int* list_count, int* status, void* stream) {
+                           int tiles_n, const void* list, const int* list_count, int* status, void* stream) {
     if (n_ranks < 1 || n_ranks > kEpMaxPeers || H % 8 || me < 0 || me >= n_ranks) return -1;
     if (epi != kEpiStoreBf16 && epi != kEpiSwiglu) return -2;
     CUtensorMap ta, tb;
@@ -825,6 +850,7 @@ int halo_moe_dispatch_gemm(const void* x, const int* send_slot, const void* unit
     if (rc) return rc * 10;
     GemmParams p{};
     p.C = C; p.aux = aux; p.ldc = ldc; p.ld_aux = ld_aux; p.epi = epi; p.alpha = 1.f; p.swiglu_f = swiglu_f;
+    p.tiles_n = tiles_n;
     p.list = reinterpret_cast<const GemmWork*>(list);
     p.list_count = list_count;
     p.status = status;
@@ -849,7 +875,7 @@ int halo_moe_dispatch_gemm(const void* x, const int* send_slot, const void* unit
 // token owner's slot buffer (slot_bufs: HOST array of n_ranks device pointers to [T * k, ldc] bf16) by its tag meta[row].
 int halo_moe_gemm_combine(const void* A, long long a_rows, long long a_cols, long long lda, const void* B, long long b_rows,
                           long long b_cols, long long ldb, void* const* slot_bufs, const int* meta, int n_ranks,
-                          long long ldc, int b_mn_major, const void* list, const int* list_count, int* status,
+                          long long ldc, int b_mn_major, int tiles_n, const void* list, const int* list_count, int* status,
                           void* stream) {
     if (n_ranks < 1 || n_ranks > kEpMaxPeers || ldc % 8) return -1;
     CUtensorMap ta, tb;
@@ -859,6 +885,7 @@ int halo_moe_gemm_combine(const void* A, long long a_rows, long long a_cols, lon
     if (rc) return rc * 10;
     GemmParams p{};
     p.C = nullptr; p.aux = nullptr; p.ldc = ldc; p.ld_aux = 0; p.epi = kEpiStoreBf16; p.alpha = 1.f; p.swiglu_f = 0;
+    p.tiles_n = tiles_n;
     p.list = reinterpret_cast<const GemmWork*>(list);
     p.list_count = list_count;
     p.status = status;

@@ -246,6 +246,12 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, int a_mn_ma
            | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
 }
 
+// 1 / (1 + e^-x) on the special-function unit (one ex2, one rcp): the SiLU gate of the expert products, where an
+// IEEE division per element would cost more issue slots than the rest of the epilogue together.
+__device__ __forceinline__ float sigmoid_fast(float x) {
+    return __fdividef(1.f, 1.f + __expf(-x));
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);

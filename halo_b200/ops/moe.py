@@ -342,6 +342,18 @@ def grouped_down_fwd(state: RoutingState, act, w_down, out_rows):
 # ---------------------------------------------------------------------------------------------
 # fused path: counts through peer memory, dispatch inside GEMM 1, combine inside the last GEMM's epilogue
 # ---------------------------------------------------------------------------------------------
+# When a list, the fused path appends (phase name, CUDA event) marks to it: the microbenchmarks read phase durations
+# from consecutive marks. None (the default) records nothing.
+PHASE_MARKS: list | None = None
+
+
+def _mark(name: str, dev) -> None:
+    if PHASE_MARKS is not None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(torch.cuda.current_stream(dev))
+        PHASE_MARKS.append((name, ev))
+
+
 def _fused(transport) -> bool:
     return bool(getattr(transport, "fused", False)) and hasattr(transport, "ctrl_table")
 
@@ -418,15 +430,15 @@ def _ep_list(state: RoutingState, gated: int, n_cols: int, k_dim: int, b_mn_stri
                                      _lib.c_int(b_mn_stride), _lib.c_int(b_k_stride), _lib.c_int(swiglu_f), _lib.c_int(gated),
                                      _lib.ptr(lst), _lib.ptr(count), _lib.c_int(max_items), _lib.stream_ptr(dev)),
                "halo_moe_plan_items")
-    state.lists[key] = (lst, count)
-    return lst, count
+    state.lists[key] = (lst, count, (width + tile_n - 1) // tile_n)
+    return state.lists[key]
 
 
 def _dispatch_gemm(transport, state: RoutingState, seq: int, x, slot_w, recv, meta, row_w, b2d, c, aux, b_mn: int, epi: int,
                    swiglu_f: int, lst_cnt):
     """Kernel A: this rank's rows of ``x`` go to their owners' ``recv`` buffers while the tiles of this rank's own
     ``recv`` are multiplied with the expert bank ``b2d`` as they fill up."""
-    lst, cnt = lst_cnt
+    lst, cnt, tiles_n = lst_cnt
     dev = x.device
     H = x.shape[1]
     _lib.check(_lib.lib().halo_moe_dispatch_gemm(
@@ -436,19 +448,20 @@ def _dispatch_gemm(transport, state: RoutingState, seq: int, x, slot_w, recv, me
         _lib.c_int(state.top_k), _lib.ptr(recv), _lib.c_ll(recv.shape[0]), _lib.ptr(b2d), _lib.c_ll(b2d.shape[0]),
         _lib.c_ll(b2d.shape[1]), _lib.c_ll(b2d.stride(0)), _lib.ptr(c), _lib.ptr(aux), _lib.c_ll(c.stride(0)),
         _lib.c_ll(aux.stride(0) if aux is not None else 0), _lib.c_int(b_mn), _lib.c_int(epi), _lib.c_int(swiglu_f),
-        _lib.ptr(lst), _lib.ptr(cnt), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev)), "halo_moe_dispatch_gemm")
+        _lib.c_int(tiles_n), _lib.ptr(lst), _lib.ptr(cnt), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev)),
+        "halo_moe_dispatch_gemm")
 
 
 def _gemm_combine(transport, a, b2d, slots, meta, b_mn: int, lst_cnt):
     """Kernel B: grouped product of the local rows ``a`` with the expert bank, each output row stored into the slot
     buffer of the rank that owns the token."""
-    lst, cnt = lst_cnt
+    lst, cnt, tiles_n = lst_cnt
     dev = a.device
     _lib.check(_lib.lib().halo_moe_gemm_combine(
         _lib.ptr(a), _lib.c_ll(a.shape[0]), _lib.c_ll(a.shape[1]), _lib.c_ll(a.stride(0)), _lib.ptr(b2d),
         _lib.c_ll(b2d.shape[0]), _lib.c_ll(b2d.shape[1]), _lib.c_ll(b2d.stride(0)), transport.peer_table(slots), _lib.ptr(meta),
-        _lib.c_int(transport.n_ranks), _lib.c_ll(slots.stride(0)), _lib.c_int(b_mn), _lib.ptr(lst), _lib.ptr(cnt),
-        _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev)), "halo_moe_gemm_combine")
+        _lib.c_int(transport.n_ranks), _lib.c_ll(slots.stride(0)), _lib.c_int(b_mn), _lib.c_int(tiles_n), _lib.ptr(lst),
+        _lib.ptr(cnt), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev)), "halo_moe_gemm_combine")
 
 
 def _zero_pads(state: RoutingState, buf, meta, row_w):
@@ -473,6 +486,7 @@ def _fused_forward(ctx, x, topk_idx, topk_w, w_gate_up, w_down, transport, state
     n_experts = E_local * transport.n_ranks
     k = topk_idx.shape[1]
     dev = x.device
+    _mark("start", dev)
     state = plan_routing_fused(topk_idx, n_experts, transport)
     cap = state.capacity
     recv_x = transport.buffer("recv_x", cap, H, torch.bfloat16, dev)
@@ -482,16 +496,21 @@ def _fused_forward(ctx, x, topk_idx, topk_w, w_gate_up, w_down, transport, state
     act = _alloc(transport, (cap, F), torch.bfloat16, dev)
     pre = _alloc(transport, (cap, F2), torch.bfloat16, dev) if need_grad else None
     lst1 = _ep_list(state, 1, F2, H, F2, 0, F)
+    _mark("fwd: counts, handshake, plans", dev)
     _dispatch_gemm(transport, state, state.seq, x, None, recv_x, meta, None, w_gate_up.reshape(E_local * F2, H), act, pre, 0,
                    EPI_SWIGLU, F, lst1)
+    _mark("fwd: dispatch + gate_up GEMM + SwiGLU", dev)
     w32 = topk_w.float().contiguous()
     out = _alloc(transport, tuple(x.shape), x.dtype, dev)
     if not (skip_output and need_grad):
         slots = transport.buffer("slots", T * k, H, torch.bfloat16, dev)
         lst2 = _ep_list(state, 0, H, F, H, 0)
         _gemm_combine(transport, act, w_down.reshape(E_local * H, F), slots, meta, 0, lst2)
+        _mark("fwd: down GEMM + combine stores", dev)
         transport.barrier()
+        _mark("fwd: barrier", dev)
         _slot_sum(state, slots, w32, out)
+        _mark("fwd: slot sum", dev)
     if need_grad:
         if transport.transient_buffers:
             recv_x = recv_x.clone()
@@ -515,6 +534,7 @@ def _fused_backward(ctx, dout):
     s = _lib.stream_ptr(dev)
     dout = dout.contiguous()
     n_ranks, me = transport.n_ranks, transport.rank
+    _mark("start", dev)
     # 1. a handshake of its own: every rank is done with the buffers of its previous call, the arrival counters restart
     seq = transport.next_seq()
     _lib.check(L.halo_moe_handshake(transport.ctrl_table(), _lib.c_int(me), _lib.c_int(n_ranks), _lib.c_int(state.n_experts),
@@ -529,8 +549,10 @@ def _fused_backward(ctx, dout):
     #    dact_u = dout_rows W_down (unscaled activation gradient)
     dact = _alloc(transport, (cap, F), torch.bfloat16, dev)
     lst = _ep_list(state, 1, F, H, 0, H)
+    _mark("bwd: handshake, plans", dev)
     _dispatch_gemm(transport, state, seq, dout, w32, dy, meta, row_w, w_down.reshape(E_local * H, F), dact, None, 1,
                    EPI_STORE_BF16, 0, lst)
+    _mark("bwd: dispatch + dact GEMM", dev)
     # 3. SwiGLU backward with the routing weight folded in (dpre over pre, w * act over dact_u); every row's routing-weight
     #    gradient goes straight to the token's owner
     dw_slots = transport.buffer("dw_slots", T * k, 1, torch.float32, dev)
@@ -539,10 +561,12 @@ def _fused_backward(ctx, dout):
                                              _lib.ptr(meta), transport.peer_table(dw_slots), _lib.c_int(n_ranks),
                                              _lib.ptr(state.total_rows), _lib.c_int(F), _lib.c_int(cap), s),
                "halo_moe_swiglu_bwd_scatter")
+    _mark("bwd: SwiGLU backward", dev)
     # 4. input-gradient rows dx_rows = dpre W_gate_up, stored straight into the token owners' slots
     slots = transport.buffer("slots", T * k, H, torch.bfloat16, dev)
     lst = _ep_list(state, 0, H, F2, 0, F2)
     _gemm_combine(transport, dpre, w_gate_up.reshape(E_local * F2, H), slots, meta, 1, lst)
+    _mark("bwd: dx GEMM + combine stores", dev)
     # 5. weight gradients (local): dW_down[e] = dout_e^T (w * act)_e ; dW_gate_up[e] = dpre_e^T x_e
     dw_gate_up = dw_down = None
     if ctx.needs_input_grad[3] or ctx.needs_input_grad[4]:
@@ -553,10 +577,13 @@ def _fused_backward(ctx, dout):
         dw_gate_up = _alloc(transport, tuple(w_gate_up.shape), w_gate_up.dtype, dev)
         _gemm_list(dpre, recv_x, dw_gate_up.reshape(E_local * F2, H), _tile_list(state, "k", pk, m_dim=F2, n_dim=H), 1, 1,
                    EPI_STORE_BF16, pair=pk)
+    _mark("bwd: two weight-gradient GEMMs", dev)
     # 6. every rank's rows have landed: sum the k slots of each token
     transport.barrier()
+    _mark("bwd: barrier", dev)
     dx = _alloc(transport, (T, H), torch.bfloat16, dev)
     _slot_sum(state, slots, None, dx)
+    _mark("bwd: slot sum", dev)
     # slots of dropped rows (a capacity overflow, reported through the status word) carry no gradient
     valid = (state.slot_row >= 0) & (state.slot_row < cap // 128 * 128)
     dw = torch.where(valid, dw_slots[:T * k, 0], torch.zeros((), dtype=torch.float32, device=dev)).view(T, k)

@@ -184,15 +184,24 @@ class ParallelRuntime:
         self._flat = None
         self.fused_optimizer = None   # halo_b200.parallel.zero.FusedShardedAdamW for the replicated parameters
 
-    def enable_fused_optimizer(self, model, lr, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01):
+    def enable_fused_optimizer(self, model, lr, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, dp_replicate_size: int = 1):
         """Shard the optimizer of the replicated parameters over the data-parallel group and fuse it
         with its reduce-scatter / all-gather. Returns the (name, parameter) pairs the caller still has to
-        give an ordinary optimizer: the experts."""
+        give an ordinary optimizer: the experts. ``dp_replicate_size > 1`` is hybrid sharding: the data-parallel ranks
+        form that many replica groups (a ``(dp_replicate, dp_shard)`` mesh over the whole job); state is cut inside a
+        group, and owners of the same slice add their sums across groups."""
         from halo_b200.parallel.zero import FusedShardedAdamW
 
         shared = [(n, p) for n, p in model.named_parameters() if not getattr(p, "is_expert", False)]
         experts = [(n, p) for n, p in model.named_parameters() if getattr(p, "is_expert", False)]
-        self.fused_optimizer = FusedShardedAdamW(shared, self.dp_group, self.device, lr, betas, eps, weight_decay)
+        shard_group, replicate_group = self.dp_group, None
+        if dp_replicate_size > 1:
+            from halo_b200.parallel.mesh import build_dp_mesh, shard_and_replicate_groups
+
+            self.dp_mesh = build_dp_mesh(self.dp_world, dp_replicate_size, device_type=self.device.type)
+            shard_group, replicate_group = shard_and_replicate_groups(self.dp_mesh)
+        self.fused_optimizer = FusedShardedAdamW(shared, shard_group, self.device, lr, betas, eps, weight_decay,
+                                                 replicate_group=replicate_group)
         return experts
 
     @classmethod

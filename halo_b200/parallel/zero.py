@@ -5,7 +5,8 @@ rank, allocated as symmetric memory so every rank can address every peer's copy;
 gradient buffer. Each rank owns one contiguous slice of the flat space and the bf16 moments of
 that slice only (optimizer state is sharded N ways). One optimizer step is
 
-  pack       gradients are copied into the flat gradient buffer               (local)
+  (backward) every parameter's ``.grad`` IS its range of the flat gradient buffer, so autograd
+             accumulates straight into it; a gradient found elsewhere is copied in       (local)
   barrier
   reduce     the owner sums its slice over all peers' buffers in fp32 and     (peer loads)
              gets the slice's contribution to the global gradient norm
@@ -42,9 +43,14 @@ def _round_up(x: int, m: int) -> int:
 
 class FusedShardedAdamW:
     def __init__(self, named_params, group, device, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01,
-                 key: int = SR_KEY):
+                 key: int = SR_KEY, replicate_group=None):
+        """``group``: the ranks the flat space is cut over (the ``dp_shard`` axis). ``replicate_group``: under hybrid
+        sharding, the ranks that own the SAME slice in the other shard groups (the ``dp_replicate`` axis); every owner
+        adds its peers' slice sums before the update, so all copies of a slice take the same step."""
         import torch.distributed._symmetric_memory as symm
 
+        self.replicate_group = replicate_group
+        self.n_replicas = dist.get_world_size(replicate_group) if replicate_group is not None else 1
         self.group, self.device = group, torch.device(device)
         self.n_ranks, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.lr, self.betas, self.eps, self.weight_decay, self.key = lr, betas, eps, weight_decay, key
@@ -82,7 +88,15 @@ class FusedShardedAdamW:
         self._build_segments()
         self._p_ptrs = (_lib.c_void_p * self.n_ranks)(*list(self.hp.buffer_ptrs))
         self._g_ptrs = (_lib.c_void_p * self.n_ranks)(*list(self.hg.buffer_ptrs))
+        self._grad_views = [self.flat_g[o:o + p.numel()].view(p.shape) for (_, p), o in zip(self.named, self.offsets)]
+        self._attach_grad_views()
         self.hp.barrier(channel=0)
+
+    def _attach_grad_views(self) -> None:
+        """Point every parameter's ``.grad`` at its range of the (zeroed) flat gradient buffer. Autograd adds into an
+        existing ``.grad`` in place, so the backward writes the buffer the reduce kernel reads: no packing pass."""
+        for (_, p), view in zip(self.named, self._grad_views):
+            p.grad = view
 
     def _build_segments(self) -> None:
         L = _lib.lib()
@@ -106,6 +120,7 @@ class FusedShardedAdamW:
         self.seg_toff = torch.tensor(seg_toff, dtype=torch.int64, device=dev)
         self.seg_hash = torch.from_numpy(np.asarray(seg_hash, dtype=np.uint64).view(np.int64)).to(dev)
         self._seg_decay = seg_wd
+        self._seg_decay_dev = torch.tensor(seg_wd or [0.0], dtype=torch.float64, device=dev)
         self.seg_wd = torch.ones(max(1, len(seg_wd)), dtype=torch.float32, device=dev)
         self.block_start = torch.tensor(blocks, dtype=torch.int32, device=dev)
 
@@ -113,18 +128,25 @@ class FusedShardedAdamW:
     @torch.no_grad()
     def pack_and_reduce(self) -> torch.Tensor:
         """Phase 1. Returns the device scalar ``sum of squares`` of this rank's slice of the summed gradient."""
-        for (n, p), o in zip(self.named, self.offsets):
-            dst = self.flat_g[o:o + p.numel()]
-            if p.grad is None:
-                dst.zero_()
-            else:
-                dst.copy_(p.grad.reshape(-1))
+        for (n, p), view in zip(self.named, self._grad_views):
+            g = p.grad
+            if g is None:
+                view.zero_()                      # someone dropped the gradient: this parameter contributes nothing
+            elif g.data_ptr() != view.data_ptr():
+                view.copy_(g)                     # a gradient that was replaced instead of accumulated in place
         self.hg.barrier(channel=0)
         L = _lib.lib()
         s = _lib.stream_ptr(self.device)
         _lib.check(L.halo_rs_sum_norm(self._g_ptrs, _lib.c_int(self.n_ranks), _lib.c_ll(self.lo), _lib.c_ll(self.shard),
                                       _lib.ptr(self.gsum), _lib.ptr(self.partial), s), "halo_rs_sum_norm")
-        self.shard_sq.copy_(self.partial.sum().reshape(1))
+        if self.n_replicas > 1:
+            # hybrid sharding: the slice's sum over the other shard groups (fp32, one library all-reduce of 1/N of the
+            # gradient), and its norm from the completed sum. Every replica of a slice reports the same square, so each
+            # reports its share: the caller's sum over all ranks then counts the slice once.
+            dist.all_reduce(self.gsum, group=self.replicate_group)
+            self.shard_sq.copy_((self.gsum.double().pow(2).sum() / self.n_replicas).float().reshape(1))
+        else:
+            self.shard_sq.copy_(self.partial.sum().reshape(1))
         return self.shard_sq
 
     @torch.no_grad()
@@ -135,7 +157,9 @@ class FusedShardedAdamW:
         t = self.step_count
         step_size = self.lr / (1.0 - b1**t)
         bc2_sqrt = math.sqrt(1.0 - b2**t)
-        self.seg_wd.copy_(torch.tensor([1.0 - self.lr * w for w in self._seg_decay] or [1.0], dtype=torch.float32))
+        # 1 - lr * decay per segment, formed on the device in double and rounded once to fp32 (what the unsharded
+        # optimizer's host-side double arithmetic gives)
+        self.seg_wd.copy_(torch.mul(self._seg_decay_dev, -float(self.lr)).add_(1.0))
         L = _lib.lib()
         rc = L.halo_adam_allgather(
             self._p_ptrs, _lib.c_int(self.n_ranks), _lib.c_int(self.rank), _lib.c_ll(self.lo), _lib.ptr(self.gsum),
@@ -149,8 +173,9 @@ class FusedShardedAdamW:
         self.hp.barrier(channel=0)
 
     def zero_grad(self) -> None:
-        for _, p in self.named:
-            p.grad = None
+        """One fill of the flat gradient buffer; the parameters keep (or get back) their views into it."""
+        self.flat_g.zero_()
+        self._attach_grad_views()
 
     # ---- bookkeeping ---------------------------------------------------------------------------
     def bytes_over_nvlink_per_step(self) -> int:
@@ -159,7 +184,7 @@ class FusedShardedAdamW:
 
     def state_dict(self) -> dict:
         return {"step": self.step_count, "m": self.m.cpu(), "v": self.v.cpu(), "lo": self.lo, "shard": self.shard,
-                "n_ranks": self.n_ranks}
+                "n_ranks": self.n_ranks, "n_replicas": self.n_replicas}
 
     def load_state_dict(self, sd: dict) -> None:
         if sd["n_ranks"] != self.n_ranks or sd["shard"] != self.shard:
