@@ -17,6 +17,7 @@
 #include "sm100_common.cuh"
 
 #include <stdio.h>
+#include <stdlib.h>
 
 namespace halo {
 
@@ -726,6 +727,444 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 }
 
 // ---------------------------------------------------------------------------------------------
+// Backward, second form. Same tiling and the same deterministic split into a dK/dV kernel and a dQ kernel as above,
+// but the score / dP accumulators are double-buffered in tensor memory, the P^T / dS^T operand tiles are
+// double-buffered in shared memory, and EIGHT element-wise warps share a tile (each thread owns one row and 32 of its
+// 64 columns): the products of step i+1 are issued before the element-wise pass of step i has finished, so the tensor
+// pipe no longer idles through every exp / mask / scale pass, and a thread holds 32 instead of 64 score values.
+//   warp 0: TMA producer, warp 1: MMA issuer, warps 2..9: element-wise (TMEM lane quarter = warp & 3, column half = (warp - 2) / 4)
+// ---------------------------------------------------------------------------------------------
+constexpr int kBwd2Threads = 320;
+constexpr int kBwd2Ew = 256;                      // element-wise threads
+
+__device__ __forceinline__ void ew_bar_sync() {   // named barrier of the eight element-wise warps
+    asm volatile("bar.sync 2, %0;" ::"n"(kBwd2Ew) : "memory");
+}
+
+// K, V (32 KiB each), 2 x P^T, 2 x dS^T (128 x 64, 16 KiB each), 2 stages of (Q, dO) 64 x 128 (16 KiB each)
+constexpr int kBwdKv2Tiles = 2 * kTileBytes + 4 * kHalfTile + 2 * 2 * kHalfTile;     // 196,608
+constexpr int kBwdKv2Smem = kBwdKv2Tiles + 2048;                                      // barriers, scalars, 4 x 64 statistics
+
+__global__ void __launch_bounds__(kBwd2Threads, 1)
+attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                      const BwdParams p) {
+    if (status_poisoned(p.status)) return;
+    extern __shared__ __align__(1024) uint8_t smem_b2[];
+    const uint32_t base = smem_u32(smem_b2);
+    if (base & 1023u) {
+        if (threadIdx.x == 0 && p.status) atomicCAS(p.status, kStatusOk, kStatusBadArgument);
+        return;
+    }
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_b2 + kBwdKv2Tiles);
+    // [0] kv, [1..2] q_full, [3..4] q_empty, [5..6] s_full, [7..8] s_free, [9..10] p_ready, [11..12] ds_ready,
+    // [13..14] pt_free, [15..16] ds_free, [17] acc_done
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 19);
+    float* s_lse = reinterpret_cast<float*>(bars + 20);          // [2][64]
+    float* s_delta = s_lse + 128;                                // [2][64]
+    auto bar = [&](int i) { return smem_u32(&bars[i]); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t sK = base, sV = base + kTileBytes, sPT = base + 2 * kTileBytes, sDS = sPT + 2 * kHalfTile,
+                   sQdO = sDS + 2 * kHalfTile;
+    const int kv_head = blockIdx.x;
+    const int group = p.Hq / p.Hkv;
+    const BwdKvWork w = reinterpret_cast<const BwdKvWork*>(p.work)[blockIdx.y];
+    const int n_iter = w.n_q * group;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int i = 0; i < 18; ++i) {
+            const bool many = (i >= 7 && i <= 12);        // arrived on by every element-wise thread
+            mbar_init(bar(i), many ? kBwd2Ew : 1);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tm0 = *tmem_slot;
+    // S^T[b] at 128 b, dP^T[b] at 128 b + 64, dV at 256, dK at 384
+    const uint32_t tDV = tm0 + 256, tDK = tm0 + 384;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(bar(0), 2 * kTileBytes);
+            tma_load_2d(sK, &tmK, bar(0), kv_head * kHd, w.kv0);
+            tma_load_2d(sK + 16384, &tmK, bar(0), kv_head * kHd + 64, w.kv0);
+            tma_load_2d(sV, &tmV, bar(0), kv_head * kHd, w.kv0);
+            tma_load_2d(sV + 16384, &tmV, bar(0), kv_head * kHd + 64, w.kv0);
+            for (int it = 0; it < n_iter; ++it) {
+                const int st = it & 1;
+                if (!mbar_wait(bar(3 + st), ((it >> 1) & 1) ^ 1u, abort_flag, p.status)) break;
+                const int h = kv_head * group + it % group;
+                const int qr = w.q_begin + (it / group) * 64;
+                const uint32_t full = bar(1 + st);
+                const uint32_t sQ = sQdO + st * 2 * kHalfTile, sdO = sQ + kHalfTile;
+                mbar_expect_tx(full, 2 * kHalfTile);
+                tma_load_2d(sQ, &tmQ, full, h * kHd, qr);
+                tma_load_2d(sQ + 8192, &tmQ, full, h * kHd + 64, qr);
+                tma_load_2d(sdO, &tmdO, full, h * kHd, qr);
+                tma_load_2d(sdO + 8192, &tmdO, full, h * kHd + 64, qr);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_st = make_idesc_bf16(128, 64, 0, 0);   // [keys x q] = K Q^T, V dO^T
+            constexpr uint32_t idesc_acc = make_idesc_bf16(128, 128, 0, 1); // [keys x hd] = P^T dO, dS^T Q
+            bool ok = mbar_wait(bar(0), 0, abort_flag, p.status);
+            auto issue_s = [&](int j) -> bool {
+                const int b = j & 1;
+                const uint32_t sQ = sQdO + b * 2 * kHalfTile, sdO = sQ + kHalfTile;
+                if (!mbar_wait(bar(1 + b), (j >> 1) & 1, abort_flag, p.status)) return false;          // Q, dO of step j
+                if (!mbar_wait(bar(7 + b), ((j >> 1) & 1) ^ 1u, abort_flag, p.status)) return false;   // S^T / dP^T[b] read
+                tc_fence_after();
+                const uint32_t tS = tm0 + 128 * b, tDP = tS + 64;
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t offa = (ks >> 2) * 16384 + (ks & 3) * 32;  // K / V: 128-row halves
+                    const uint32_t offb = (ks >> 2) * 8192 + (ks & 3) * 32;   // Q / dO: 64-row halves
+                    tc_mma_f16(tS, make_smem_desc(sK + offa, 16, 1024), make_smem_desc(sQ + offb, 16, 1024), idesc_st, ks != 0);
+                }
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t offa = (ks >> 2) * 16384 + (ks & 3) * 32;
+                    const uint32_t offb = (ks >> 2) * 8192 + (ks & 3) * 32;
+                    tc_mma_f16(tDP, make_smem_desc(sV + offa, 16, 1024), make_smem_desc(sdO + offb, 16, 1024), idesc_st, ks != 0);
+                }
+                tc_commit(bar(5 + b));
+                return true;
+            };
+            if (ok && n_iter > 0) ok = issue_s(0);
+            for (int it = 0; ok && it < n_iter; ++it) {
+                const int b = it & 1;
+                const uint32_t sQ = sQdO + b * 2 * kHalfTile, sdO = sQ + kHalfTile;
+                if (it + 1 < n_iter && !issue_s(it + 1)) break;
+                if (!mbar_wait(bar(9 + b), (it >> 1) & 1, abort_flag, p.status)) break;      // P^T[b] written
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)
+                    tc_mma_f16(tDV, make_smem_desc(sPT + b * kHalfTile + ks * 32, 16, 1024),
+                               make_smem_desc(sdO + ks * 2048, 8192, 1024), idesc_acc, (it | ks) != 0);
+                tc_commit(bar(13 + b));
+                if (!mbar_wait(bar(11 + b), (it >> 1) & 1, abort_flag, p.status)) break;     // dS^T[b] written
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)
+                    tc_mma_f16(tDK, make_smem_desc(sDS + b * kHalfTile + ks * 32, 16, 1024),
+                               make_smem_desc(sQ + ks * 2048, 8192, 1024), idesc_acc, (it | ks) != 0);
+                tc_commit(bar(15 + b));
+                tc_commit(bar(3 + b));
+                if (it == n_iter - 1) tc_commit(bar(17));
+            }
+        }
+    } else {
+        const int quad = warp & 3, half = (warp - 2) >> 2;
+        const int ew_tid = threadIdx.x - 64;
+        const int key = quad * 32 + lane;                         // this thread's key row of the tile
+        const int c0 = half * 32;                                 // its first query column
+        const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+        const float c = p.scale * kLog2e;
+        const long long key_abs = (long long)w.kv0 + key;
+        bool ok = true;
+        // statistics of step 0, fetched by the first 128 element-wise threads (64 lse, 64 delta)
+        auto fetch_stat = [&](int it) -> float {
+            if (ew_tid >= 128 || it >= n_iter) return 0.f;
+            const int h = kv_head * group + it % group;
+            const long long qa = (long long)w.q_begin + (it / group) * 64 + (ew_tid & 63);
+            const bool in = qa < w.q_end;
+            if (ew_tid < 64) return in ? p.lse[(long long)h * p.T + qa] * kLog2e : INFINITY;
+            return in ? p.delta[(long long)h * p.T + qa] : 0.f;
+        };
+        float stat = fetch_stat(0);
+        for (int it = 0; it < n_iter; ++it) {
+            const int b = it & 1;
+            const int qr = w.q_begin + (it / group) * 64;
+            if (ew_tid < 64) s_lse[b * 64 + ew_tid] = stat;
+            else if (ew_tid < 128) s_delta[b * 64 + (ew_tid - 64)] = stat;
+            stat = fetch_stat(it + 1);                            // in flight during this step
+            // Every element-wise thread meets here in every step, also after a wait has given up (it then skips the
+            // step's work): nobody may leave the loop early and strand the others at this barrier.
+            ew_bar_sync();
+            if (!ok) continue;
+            if (!mbar_wait(bar(5 + b), (it >> 1) & 1, abort_flag, p.status)) { ok = false; continue; }
+            tc_fence_after();
+            uint32_t sr[32], dr[32];
+            tmem_ld_32x32(tm0 + 128 * b + lane_base + c0, sr);
+            tmem_ld_32x32(tm0 + 128 * b + 64 + lane_base + c0, dr);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(bar(7 + b));                              // S^T / dP^T[b] may be overwritten by step it + 2
+            const bool need_mask = (qr < w.kv0 + 128);
+            float pv[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                float pe = fast_exp2(__uint_as_float(sr[i]) * c - s_lse[b * 64 + c0 + i]);
+                if (need_mask && (long long)qr + c0 + i < key_abs) pe = 0.f;
+                pv[i] = pe;
+            }
+            // P^T[b] (bf16, K-major A operand: one 128-byte row of 64 queries per key) once dV of step it - 2 has read it
+            if (!mbar_wait(bar(13 + b), ((it >> 1) & 1) ^ 1u, abort_flag, p.status)) { ok = false; continue; }
+#pragma unroll
+            for (int q8 = 0; q8 < 4; ++q8) {
+                const uint32_t a = sPT + b * kHalfTile + swz_off(key, c0 + q8 * 8);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a),
+                             "r"(pack_bf16(pv[q8 * 8], pv[q8 * 8 + 1])), "r"(pack_bf16(pv[q8 * 8 + 2], pv[q8 * 8 + 3])),
+                             "r"(pack_bf16(pv[q8 * 8 + 4], pv[q8 * 8 + 5])), "r"(pack_bf16(pv[q8 * 8 + 6], pv[q8 * 8 + 7]))
+                             : "memory");
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(bar(9 + b));
+            // dS^T = P^T * (dP^T - delta) * scale
+#pragma unroll
+            for (int i = 0; i < 32; ++i) pv[i] = pv[i] * (__uint_as_float(dr[i]) - s_delta[b * 64 + c0 + i]) * p.scale;
+            if (!mbar_wait(bar(15 + b), ((it >> 1) & 1) ^ 1u, abort_flag, p.status)) { ok = false; continue; }
+#pragma unroll
+            for (int q8 = 0; q8 < 4; ++q8) {
+                const uint32_t a = sDS + b * kHalfTile + swz_off(key, c0 + q8 * 8);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a),
+                             "r"(pack_bf16(pv[q8 * 8], pv[q8 * 8 + 1])), "r"(pack_bf16(pv[q8 * 8 + 2], pv[q8 * 8 + 3])),
+                             "r"(pack_bf16(pv[q8 * 8 + 4], pv[q8 * 8 + 5])), "r"(pack_bf16(pv[q8 * 8 + 6], pv[q8 * 8 + 7]))
+                             : "memory");
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(bar(11 + b));
+        }
+        if (ok && mbar_wait(bar(17), 0, abort_flag, p.status)) {
+            tc_fence_after();
+            const bool live = key_abs < w.q_end;
+            __nv_bfloat16* dk = reinterpret_cast<__nv_bfloat16*>(p.dK) + key_abs * p.ld_dk + kv_head * kHd + half * 64;
+            __nv_bfloat16* dv = reinterpret_cast<__nv_bfloat16*>(p.dV) + key_abs * p.ld_dv + kv_head * kHd + half * 64;
+#pragma unroll 1
+            for (int cc = 0; cc < 64; cc += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tDK + lane_base + half * 64 + cc, r);
+                tmem_ld_wait();
+                if (live) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8)
+                        *reinterpret_cast<uint4*>(dk + cc + i) = make_uint4(
+                            pack_bf16(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
+                            pack_bf16(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])),
+                            pack_bf16(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5])),
+                            pack_bf16(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7])));
+                }
+                tmem_ld_32x32(tDV + lane_base + half * 64 + cc, r);
+                tmem_ld_wait();
+                if (live) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8)
+                        *reinterpret_cast<uint4*>(dv + cc + i) = make_uint4(
+                            pack_bf16(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
+                            pack_bf16(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])),
+                            pack_bf16(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5])),
+                            pack_bf16(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7])));
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) { }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tm0, 512);
+    }
+}
+
+// Q, dO (32 KiB each), 2 x dS (128 x 64, 16 KiB each), 3 stages of (K, V) 64 x 128 (16 KiB each)
+constexpr int kBwdQ2Stages = 3;
+constexpr int kBwdQ2Tiles = 2 * kTileBytes + 2 * kHalfTile + kBwdQ2Stages * 2 * kHalfTile;   // 196,608
+constexpr int kBwdQ2Smem = kBwdQ2Tiles + 512;
+
+__global__ void __launch_bounds__(kBwd2Threads, 1)
+attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                    const BwdParams p) {
+    if (status_poisoned(p.status)) return;
+    extern __shared__ __align__(1024) uint8_t smem_q2[];
+    const uint32_t base = smem_u32(smem_q2);
+    if (base & 1023u) {
+        if (threadIdx.x == 0 && p.status) atomicCAS(p.status, kStatusOk, kStatusBadArgument);
+        return;
+    }
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_q2 + kBwdQ2Tiles);
+    // [0] q, [1..3] kv_full, [4..6] kv_empty, [7..8] s_full, [9..10] s_free, [11..12] ds_ready, [13..14] ds_free, [15] acc_done
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
+    auto bar = [&](int i) { return smem_u32(&bars[i]); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t sQ = base, sdO = base + kTileBytes, sDS = base + 2 * kTileBytes, sKV = sDS + 2 * kHalfTile;
+    const int head = blockIdx.x;
+    const int kv_head = head / (p.Hq / p.Hkv);
+    const BwdQWork w = reinterpret_cast<const BwdQWork*>(p.work)[blockIdx.y];
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int i = 0; i < 16; ++i) mbar_init(bar(i), (i >= 9 && i <= 12) ? kBwd2Ew : 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tm0 = *tmem_slot;
+    const uint32_t tDQ = tm0 + 256;     // S[b] at 128 b, dP[b] at 128 b + 64
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(bar(0), 2 * kTileBytes);
+            tma_load_2d(sQ, &tmQ, bar(0), head * kHd, w.q0);
+            tma_load_2d(sQ + 16384, &tmQ, bar(0), head * kHd + 64, w.q0);
+            tma_load_2d(sdO, &tmdO, bar(0), head * kHd, w.q0);
+            tma_load_2d(sdO + 16384, &tmdO, bar(0), head * kHd + 64, w.q0);
+            for (int j = 0; j < w.n_kv; ++j) {
+                const int st = j % kBwdQ2Stages;
+                if (!mbar_wait(bar(4 + st), ((j / kBwdQ2Stages) & 1) ^ 1u, abort_flag, p.status)) break;
+                const uint32_t full = bar(1 + st);
+                const uint32_t sK = sKV + st * 2 * kHalfTile, sV = sK + kHalfTile;
+                const int kr = w.kv0 + j * 64;
+                mbar_expect_tx(full, 2 * kHalfTile);
+                tma_load_2d(sK, &tmK, full, kv_head * kHd, kr);
+                tma_load_2d(sK + 8192, &tmK, full, kv_head * kHd + 64, kr);
+                tma_load_2d(sV, &tmV, full, kv_head * kHd, kr);
+                tma_load_2d(sV + 8192, &tmV, full, kv_head * kHd + 64, kr);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);     // [q x keys]
+            constexpr uint32_t idesc_dq = make_idesc_bf16(128, 128, 0, 1);   // [q x hd] = dS K
+            bool ok = mbar_wait(bar(0), 0, abort_flag, p.status);
+            auto issue_s = [&](int j) -> bool {
+                const int b = j & 1, st = j % kBwdQ2Stages;
+                const uint32_t sK = sKV + st * 2 * kHalfTile, sV = sK + kHalfTile;
+                if (!mbar_wait(bar(1 + st), (j / kBwdQ2Stages) & 1, abort_flag, p.status)) return false;
+                if (!mbar_wait(bar(9 + b), ((j >> 1) & 1) ^ 1u, abort_flag, p.status)) return false;
+                tc_fence_after();
+                const uint32_t tS = tm0 + 128 * b, tDP = tS + 64;
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t offa = (ks >> 2) * 16384 + (ks & 3) * 32;
+                    const uint32_t offb = (ks >> 2) * 8192 + (ks & 3) * 32;
+                    tc_mma_f16(tS, make_smem_desc(sQ + offa, 16, 1024), make_smem_desc(sK + offb, 16, 1024), idesc_s, ks != 0);
+                }
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t offa = (ks >> 2) * 16384 + (ks & 3) * 32;
+                    const uint32_t offb = (ks >> 2) * 8192 + (ks & 3) * 32;
+                    tc_mma_f16(tDP, make_smem_desc(sdO + offa, 16, 1024), make_smem_desc(sV + offb, 16, 1024), idesc_s, ks != 0);
+                }
+                tc_commit(bar(7 + b));
+                return true;
+            };
+            if (ok && w.n_kv > 0) ok = issue_s(0);
+            for (int j = 0; ok && j < w.n_kv; ++j) {
+                const int b = j & 1, st = j % kBwdQ2Stages;
+                const uint32_t sK = sKV + st * 2 * kHalfTile;
+                if (j + 1 < w.n_kv && !issue_s(j + 1)) break;
+                if (!mbar_wait(bar(11 + b), (j >> 1) & 1, abort_flag, p.status)) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)
+                    tc_mma_f16(tDQ, make_smem_desc(sDS + b * kHalfTile + ks * 32, 16, 1024),
+                               make_smem_desc(sK + ks * 2048, 8192, 1024), idesc_dq, (j | ks) != 0);
+                tc_commit(bar(13 + b));
+                tc_commit(bar(4 + st));
+                if (j == w.n_kv - 1) tc_commit(bar(15));
+            }
+        }
+    } else {
+        const int quad = warp & 3, half = (warp - 2) >> 2;
+        const int row = quad * 32 + lane;
+        const int c0 = half * 32;
+        const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+        const float c = p.scale * kLog2e;
+        const long long q_abs = (long long)w.q0 + row;
+        const bool in = q_abs < w.q_end;
+        const float lse2 = in ? p.lse[(long long)head * p.T + q_abs] * kLog2e : INFINITY;
+        const float dl = in ? p.delta[(long long)head * p.T + q_abs] : 0.f;
+        bool ok = true;
+        for (int j = 0; j < w.n_kv; ++j) {
+            const int b = j & 1;
+            if (!mbar_wait(bar(7 + b), (j >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+            tc_fence_after();
+            uint32_t sr[32], dr[32];
+            tmem_ld_32x32(tm0 + 128 * b + lane_base + c0, sr);
+            tmem_ld_32x32(tm0 + 128 * b + 64 + lane_base + c0, dr);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(bar(9 + b));
+            const int k0 = w.kv0 + j * 64 + c0;
+            const bool need_mask = (k0 + 32 > w.q0);
+            float pv[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                float pe = fast_exp2(__uint_as_float(sr[i]) * c - lse2);
+                if (need_mask && (long long)k0 + i > q_abs) pe = 0.f;
+                pv[i] = pe * (__uint_as_float(dr[i]) - dl) * p.scale;
+            }
+            if (!mbar_wait(bar(13 + b), ((j >> 1) & 1) ^ 1u, abort_flag, p.status)) { ok = false; break; }
+#pragma unroll
+            for (int q8 = 0; q8 < 4; ++q8) {
+                const uint32_t a = sDS + b * kHalfTile + swz_off(row, c0 + q8 * 8);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a),
+                             "r"(pack_bf16(pv[q8 * 8], pv[q8 * 8 + 1])), "r"(pack_bf16(pv[q8 * 8 + 2], pv[q8 * 8 + 3])),
+                             "r"(pack_bf16(pv[q8 * 8 + 4], pv[q8 * 8 + 5])), "r"(pack_bf16(pv[q8 * 8 + 6], pv[q8 * 8 + 7]))
+                             : "memory");
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(bar(11 + b));
+        }
+        if (ok && mbar_wait(bar(15), 0, abort_flag, p.status)) {
+            tc_fence_after();
+            __nv_bfloat16* dq = reinterpret_cast<__nv_bfloat16*>(p.dQ) + q_abs * p.ld_dq + head * kHd + half * 64;
+#pragma unroll 1
+            for (int cc = 0; cc < 64; cc += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tDQ + lane_base + half * 64 + cc, r);
+                tmem_ld_wait();
+                if (in) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8)
+                        *reinterpret_cast<uint4*>(dq + cc + i) = make_uint4(
+                            pack_bf16(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
+                            pack_bf16(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])),
+                            pack_bf16(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5])),
+                            pack_bf16(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7])));
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) { }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tm0, 512);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Forward, second form: 64-key tiles, the running output accumulates in TMEM and is rescaled
 // only when a row maximum grows by more than 2^8 (so the exponentials stay bounded without a
 // rescale on every tile), and the CTA is small enough (112 KiB of shared memory, 256 TMEM
@@ -1072,17 +1511,26 @@ int halo_attn_bwd(const void* q, const void* k, const void* v, const void* o, co
     if (make_tmap_bf16(&tv64, v, T, (long long)Hkv * kHd, ldv, 64)) return -8;
     if (make_tmap_bf16(&tdo64, d_o, T, (long long)Hq * kHd, ld_do, 64)) return -9;
     static bool cfg = false;
+    static int variant = 2;
     if (!cfg) {
         if (set_smem((const void*)attn_bwd_dkdv_kernel, kBwdKvSmem)) return -10;
         if (set_smem((const void*)attn_bwd_dq_kernel, kBwdQSmem)) return -10;
+        if (set_smem((const void*)attn_bwd_dkdv2_kernel, kBwdKv2Smem)) return -10;
+        if (set_smem((const void*)attn_bwd_dq2_kernel, kBwdQ2Smem)) return -10;
+        const char* e = getenv("HALO_ATTN_BWD_VARIANT");      // 2 (default): double-buffered form; 1: the first form
+        if (e && atoi(e) == 1) variant = 1;
         cfg = true;
     }
     BwdParams p{kv_work, lse, delta, dq, dk, dv, ld_dq, ld_dk, ld_dv, T, Hq, Hkv, scale, status};
-    if (n_kv_tiles > 0)
-        attn_bwd_dkdv_kernel<<<dim3(Hkv, n_kv_tiles), kBwdThreads, kBwdKvSmem, s>>>(tq64, tk, tv, tdo64, p);
+    if (n_kv_tiles > 0) {
+        if (variant == 2) attn_bwd_dkdv2_kernel<<<dim3(Hkv, n_kv_tiles), kBwd2Threads, kBwdKv2Smem, s>>>(tq64, tk, tv, tdo64, p);
+        else attn_bwd_dkdv_kernel<<<dim3(Hkv, n_kv_tiles), kBwdThreads, kBwdKvSmem, s>>>(tq64, tk, tv, tdo64, p);
+    }
     p.work = q_work;
-    if (n_q_tiles > 0)
-        attn_bwd_dq_kernel<<<dim3(Hq, n_q_tiles), kBwdThreads, kBwdQSmem, s>>>(tq, tk64, tv64, tdo, p);
+    if (n_q_tiles > 0) {
+        if (variant == 2) attn_bwd_dq2_kernel<<<dim3(Hq, n_q_tiles), kBwd2Threads, kBwdQ2Smem, s>>>(tq, tk64, tv64, tdo, p);
+        else attn_bwd_dq_kernel<<<dim3(Hq, n_q_tiles), kBwdThreads, kBwdQSmem, s>>>(tq, tk64, tv64, tdo, p);
+    }
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -29,7 +29,7 @@ int make_tmap_bf16(CUtensorMap* m, const void* base, long long rows, long long c
 
 constexpr int kEpMaxPeers = 16;
 constexpr int kPushWarps = 4;
-constexpr int kEpPushThreads = kGemmThreads + kPushWarps * 32;   // 320
+constexpr int kEpPushThreads = kGemmThreads + kPushWarps * 32 + 32;   // 352: GEMM roles, push warps, one gate warp
 constexpr int kMetaSlotBits = 24;                                // row tag = (source rank << 24) | slot index at the source
 
 struct IntPeers { int* p[kEpMaxPeers]; };
@@ -513,6 +513,7 @@ gemm_ep_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
+        *reinterpret_cast<volatile int*>(bars + 2 * kStages + 6) = 0;
         for (int s = 0; s < kStages; ++s) {
             mbar_init(smem_u32(&bar_full[s]), 1);
             mbar_init(smem_u32(&bar_empty[s]), 1);
@@ -533,12 +534,13 @@ gemm_ep_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
-    // Work items come in groups of p.tiles_n (the column tiles of one 128-row tile, adjacent in the list); a CTA takes
-    // whole groups, so it asks for a row tile's arrival once and its column tiles re-read the same rows from L2.
-    const int tiles_n = max(p.tiles_n, 1);
-    const int n_groups = *p.list_count / tiles_n;
-    const int total = ((n_groups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x) * tiles_n;   // items of this CTA
-    auto item_of = [&](int it) { return ((int)blockIdx.x + (it / tiles_n) * (int)gridDim.x) * tiles_n + it % tiles_n; };
+    // Work items are dealt to the CTAs round-robin: the CTAs running together then share a handful of 128-row tiles
+    // (their column tiles) and one expert's weights through L2. (Whole column groups per CTA measured slower: 148
+    // different row tiles in flight at once spill the freshly pushed rows out of L2.)
+    const int n_items = *p.list_count;
+    const int total = (n_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;   // items of this CTA
+    auto item_of = [&](int it) { return (int)blockIdx.x + it * (int)gridDim.x; };
+    volatile int& ready_items = *reinterpret_cast<volatile int*>(bars + 2 * kStages + 6);   // items whose rows have arrived
     // consumers of tiles whose producer may be waiting for another GPU's rows outlast that wait
     const uint64_t budget = kPush ? ep.wait_budget_ns + HALO_WAIT_BUDGET_NS : HALO_WAIT_BUDGET_NS;
 
@@ -547,12 +549,25 @@ gemm_ep_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
-            int ready = 0;   // pad0 of the last tile found complete
+            int seen = 0;    // items known to have their rows (the gate warp counts them in shared memory)
             for (int it = 0; it < total && !abort_flag; ++it) {
                 const GemmWork w = p.list[item_of(it)];
-                if (kPush && w.pad0 > 0 && w.pad0 != ready) {
-                    if (!wait_counter_ge(ep.arrive + (w.pad0 - 1), w.pad1, &abort_flag, p.status, ep.wait_budget_ns)) break;
-                    ready = w.pad0;
+                if (kPush && it >= seen) {
+                    // the gate warp polls the arrival counters ahead of this thread, so that the round trip to a
+                    // counter (and to the other GPUs behind it) never sits between two tiles' loads
+                    const uint64_t t0 = global_timer_ns();
+                    uint32_t spins = 0;
+                    while ((seen = ready_items) <= it) {
+                        if ((++spins & 63u) == 0u && (abort_flag || global_timer_ns() - t0 > budget)) break;
+                    }
+                    if (seen <= it) {
+                        if (!abort_flag) {
+                            abort_flag = 1;
+                            if (p.status) atomicCAS(p.status, kStatusOk, kStatusPeerTimeout);
+                        }
+                        break;
+                    }
+                    __threadfence_block();
                     // the rows were written by ordinary stores (some by other GPUs); the loads below go through TMA
                     asm volatile("fence.proxy.async.global;" ::: "memory");
                 }
@@ -651,9 +666,21 @@ gemm_ep_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
         }
         if (kScatter) tma_store_wait<0>();     // every line this lane handed to the copy engine has been written
-    } else {
+    } else if (warp < 6 + kPushWarps) {
         // ---------------- push warps: this rank's rows to their owners ----------------
         push_units<kPush>(ep, &abort_flag, lane, warp - 6, (int)threadIdx.x - kGemmThreads);
+    } else if (kPush && lane == 0) {
+        // ---------------- gate: walk this CTA's items ahead of the producer, wait for each tile's rows ----------------
+        int ready = 0;   // pad0 of the last tile found complete
+        for (int it = 0; it < total && !abort_flag; ++it) {
+            const GemmWork w = p.list[item_of(it)];
+            if (w.pad0 > 0 && w.pad0 != ready) {
+                if (!wait_counter_ge(ep.arrive + (w.pad0 - 1), w.pad1, &abort_flag, p.status, ep.wait_budget_ns)) break;
+                ready = w.pad0;
+            }
+            __threadfence_block();          // the acquire above is ordered before the count the producer reads
+            ready_items = it + 1;
+        }
     }
 
     // ---------------- teardown ----------------

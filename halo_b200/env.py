@@ -33,6 +33,7 @@ CATALOGUE = {
     "HALO_BOUNDED_WAIT_SECONDS": "deadline of a bounded stream wait in weight sync",
     "HALO_ROLLOUT_WAIT_SECONDS": "how long a trainer waits for a round from its rollout rank",
     "HALO_GEMM_PAIR": "CTA-pair GEMM: 1 where it wins (default), 0 never, 2 everywhere",
+    "HALO_ATTN_BWD_VARIANT": "backward attention kernels (2 = double-buffered score tiles and eight element-wise warps, the default; 1 = the first form)",
     "HALO_ATTN_FWD_VARIANT": "forward attention kernel form (2 = output kept in TMEM, the default)",
     "HALO_MOE_FUSED": "expert products with the token movement inside the GEMM kernels (1, default) or as separate push / pull kernels (0)",
     "HALO_PEER_WAIT_MS": "how long a kernel waits for rows or a flag from a peer GPU before it gives up with a status (default 20000)",
