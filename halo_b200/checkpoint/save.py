@@ -157,12 +157,24 @@ def save_model(model, directory: str, is_writer: bool | None = None, save_dtype:
 
 
 def save_pipeline_stages(model, directory: str, stage_index: int, n_stages: int, group=None,
-                         save_dtype: torch.dtype | None = torch.bfloat16, max_shard_bytes: int = 5 * 1024**3) -> None:
+                         save_dtype: torch.dtype | None = torch.bfloat16, max_shard_bytes: int = 5 * 1024**3,
+                         is_writer: bool = True) -> None:
     """COLLECTIVE over the pipeline group (one rank per stage). Every stage writes its own layers - complete tensors
     under hub names - into shard files of its own stem in ``directory``; the first stage then merges the stages'
     tensor lists into the one ``model.safetensors.index.json`` and writes ``config.json``, so the result is an
-    ordinary checkpoint (halo/checkpoint/parallel/pp.py)."""
+    ordinary checkpoint (halo/checkpoint/parallel/pp.py).
+
+    With expert-sharded stages every rank of a stage calls this: the stage's expert banks are gathered over its
+    expert-parallel group (a collective of the whole stage), and only the rank with ``is_writer`` (one per stage: the
+    members of one chain) writes and takes part in the collectives over ``group``."""
     cfg = model.cfg
+    n_ep, _, ep_group = _ep_info(model)
+    if not is_writer:
+        # a stage's other replicas only hand their expert shards to the writer
+        for name, p in model.named_parameters():
+            if getattr(p, "is_expert", False) and n_ep > 1:
+                _gather_expert_bank(p.detach(), n_ep, ep_group)
+        return
     guard = DeferredRankFailure()
     first_layer = model.layer_range[0]
     weight_map, total = {}, 0
@@ -174,7 +186,10 @@ def save_pipeline_stages(model, directory: str, stage_index: int, n_stages: int,
     with guard.catch():
         writer = StreamingShardWriter(directory, max_shard_bytes, save_dtype, prefix=f"model-stage{stage_index:03d}")
         for name, p in model.named_parameters():
-            for hub, t in runtime_to_hub(name, p.detach(), cfg, first_layer).items():
+            t_full = p.detach()
+            if getattr(p, "is_expert", False) and n_ep > 1:
+                t_full = _gather_expert_bank(t_full, n_ep, ep_group)      # collective over the stage's expert group
+            for hub, t in runtime_to_hub(name, t_full, cfg, first_layer).items():
                 writer.add(hub, t)
         writer.finish(write_index=False)
         weight_map, total = writer.weight_map, writer.total_bytes

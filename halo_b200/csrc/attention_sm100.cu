@@ -34,6 +34,29 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (M = 128 rows on the 128 lanes, 16 bf16 of the reduction as 8 packed
+// 32-bit columns) is read from tensor memory.
+__device__ __forceinline__ void tc_mma_f16_tmem_a(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                  uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        :
+        : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// A warp writes its 32 TMEM lanes x 16 consecutive 32-bit columns; thread i writes lane i.
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        :
+        : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
 // byte offset of the 16-byte chunk holding column `col` (multiple of 8) of row `row` inside a
 // [rows x 64] bf16 half-tile stored with the 128-byte swizzle
 __device__ __forceinline__ uint32_t swz_off(int row, int col) {
@@ -295,6 +318,7 @@ struct BwdParams {
     int Hq, Hkv;
     float scale;
     int* status;
+    long long* phase_clocks;   // optional [32]: cycles one CTA's MMA thread and one element-wise thread spent per phase (diagnostic)
 };
 
 constexpr int kBwdThreads = 192;
@@ -728,22 +752,38 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
 // ---------------------------------------------------------------------------------------------
 // Backward, second form. Same tiling and the same deterministic split into a dK/dV kernel and a dQ kernel as above,
-// but the score / dP accumulators are double-buffered in tensor memory, the P^T / dS^T operand tiles are
-// double-buffered in shared memory, and EIGHT element-wise warps share a tile (each thread owns one row and 32 of its
-// 64 columns): the products of step i+1 are issued before the element-wise pass of step i has finished, so the tensor
-// pipe no longer idles through every exp / mask / scale pass, and a thread holds 32 instead of 64 score values.
-//   warp 0: TMA producer, warp 1: MMA issuer, warps 2..9: element-wise (TMEM lane quarter = warp & 3, column half = (warp - 2) / 4)
+// rebuilt around the fact that one step is a chain of latencies (products -> TMEM loads -> exp / mask / scale ->
+// shared-memory stores -> products), not of throughput:
+//   * the score / dP accumulators (tensor memory) and the P^T / dS^T operand tiles (shared memory) exist twice, and TWO
+//     groups of eight element-wise warps alternate steps (group g takes the steps with it % 2 == g and always works on
+//     copy g), so two steps' chains are in flight and the products of step i+1 are issued before the element-wise pass
+//     of step i has finished;
+//   * inside a group each thread owns one row and 32 of its 64 columns, so it holds 32 score values, not 64;
+//   * the streamed operand tiles (Q, dO for dK/dV; K, V for dQ) have three / four stages, so that their loads are in
+//     flight two steps ahead and the round trip to L2 never sits between two steps.
+//   warp 0: TMA producer, warp 1: MMA issuer, warps 2..17: element-wise
+//   (group = (warp - 2) / 8, TMEM lane quarter = warp & 3, column half = ((warp - 2) % 8) / 4)
 // ---------------------------------------------------------------------------------------------
-constexpr int kBwd2Threads = 320;
-constexpr int kBwd2Ew = 256;                      // element-wise threads
+constexpr int kBwd2Threads = 576;
+constexpr int kBwd2Ew = 256;                      // element-wise threads of one group
+constexpr int kBwd2EwWarps = kBwd2Ew / 32;        // a warp arrives on a barrier once, through its first lane
 
-__device__ __forceinline__ void ew_bar_sync() {   // named barrier of the eight element-wise warps
-    asm volatile("bar.sync 2, %0;" ::"n"(kBwd2Ew) : "memory");
+// All lanes of the warp have finished what the barrier publishes (their loads from tensor memory, their stores and
+// proxy fences); one lane arrives for the warp. 256 separate arrivals on one barrier word, three times a step, cost
+// more than the step's arithmetic.
+__device__ __forceinline__ void warp_arrive(uint32_t bar, int lane) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
 }
 
-// K, V (32 KiB each), 2 x P^T, 2 x dS^T (128 x 64, 16 KiB each), 2 stages of (Q, dO) 64 x 128 (16 KiB each)
-constexpr int kBwdKv2Tiles = 2 * kTileBytes + 4 * kHalfTile + 2 * 2 * kHalfTile;     // 196,608
-constexpr int kBwdKv2Smem = kBwdKv2Tiles + 2048;                                      // barriers, scalars, 4 x 64 statistics
+__device__ __forceinline__ void ew_bar_sync(int group) {   // named barrier of one group's eight warps
+    asm volatile("bar.sync %0, %1;" ::"r"(2 + group), "n"(kBwd2Ew) : "memory");
+}
+
+// K, V (32 KiB each), 2 x P^T, 2 x dS^T (128 x 64, 16 KiB each), 3 stages of (Q, dO) 64 x 128 (16 KiB each)
+constexpr int kBwdKv2Stages = 3;
+constexpr int kBwdKv2Tiles = 2 * kTileBytes + 4 * kHalfTile + kBwdKv2Stages * 2 * kHalfTile;     // 229,376
+constexpr int kBwdKv2Smem = kBwdKv2Tiles + 2048;                                                 // barriers, scalars, statistics
 
 __global__ void __launch_bounds__(kBwd2Threads, 1)
 attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -757,12 +797,12 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         return;
     }
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_b2 + kBwdKv2Tiles);
-    // [0] kv, [1..2] q_full, [3..4] q_empty, [5..6] s_full, [7..8] s_free, [9..10] p_ready, [11..12] ds_ready,
-    // [13..14] pt_free, [15..16] ds_free, [17] acc_done
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 19);
-    float* s_lse = reinterpret_cast<float*>(bars + 20);          // [2][64]
-    float* s_delta = s_lse + 128;                                // [2][64]
+    enum { kKv = 0, kQFull = 1, kQEmpty = 4, kSFull = 7, kSFree = 9, kPReady = 11, kDsReady = 13, kPtFree = 15, kDsFree = 17,
+           kAccDone = 19, kNumBars = 20 };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + kNumBars + 1);
+    float* s_lse = reinterpret_cast<float*>(bars + kNumBars + 2);          // [2 groups][64]
+    float* s_delta = s_lse + 128;                                          // [2 groups][64]
     auto bar = [&](int i) { return smem_u32(&bars[i]); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -775,9 +815,9 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
-        for (int i = 0; i < 18; ++i) {
-            const bool many = (i >= 7 && i <= 12);        // arrived on by every element-wise thread
-            mbar_init(bar(i), many ? kBwd2Ew : 1);
+        for (int i = 0; i < kNumBars; ++i) {
+            const bool many = (i >= kSFree && i < kPtFree);        // arrived on by every warp of one element-wise group
+            mbar_init(bar(i), many ? kBwd2EwWarps : 1);
         }
         mbar_fence_init();
     }
@@ -794,17 +834,17 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
     if (warp == 0) {
         if (lane == 0) {
-            mbar_expect_tx(bar(0), 2 * kTileBytes);
-            tma_load_2d(sK, &tmK, bar(0), kv_head * kHd, w.kv0);
-            tma_load_2d(sK + 16384, &tmK, bar(0), kv_head * kHd + 64, w.kv0);
-            tma_load_2d(sV, &tmV, bar(0), kv_head * kHd, w.kv0);
-            tma_load_2d(sV + 16384, &tmV, bar(0), kv_head * kHd + 64, w.kv0);
+            mbar_expect_tx(bar(kKv), 2 * kTileBytes);
+            tma_load_2d(sK, &tmK, bar(kKv), kv_head * kHd, w.kv0);
+            tma_load_2d(sK + 16384, &tmK, bar(kKv), kv_head * kHd + 64, w.kv0);
+            tma_load_2d(sV, &tmV, bar(kKv), kv_head * kHd, w.kv0);
+            tma_load_2d(sV + 16384, &tmV, bar(kKv), kv_head * kHd + 64, w.kv0);
             for (int it = 0; it < n_iter; ++it) {
-                const int st = it & 1;
-                if (!mbar_wait(bar(3 + st), ((it >> 1) & 1) ^ 1u, abort_flag, p.status)) break;
+                const int st = it % kBwdKv2Stages;
+                if (!mbar_wait(bar(kQEmpty + st), ((it / kBwdKv2Stages) & 1) ^ 1u, abort_flag, p.status)) break;
                 const int h = kv_head * group + it % group;
                 const int qr = w.q_begin + (it / group) * 64;
-                const uint32_t full = bar(1 + st);
+                const uint32_t full = bar(kQFull + st);
                 const uint32_t sQ = sQdO + st * 2 * kHalfTile, sdO = sQ + kHalfTile;
                 mbar_expect_tx(full, 2 * kHalfTile);
                 tma_load_2d(sQ, &tmQ, full, h * kHd, qr);
@@ -817,12 +857,18 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (lane == 0) {
             constexpr uint32_t idesc_st = make_idesc_bf16(128, 64, 0, 0);   // [keys x q] = K Q^T, V dO^T
             constexpr uint32_t idesc_acc = make_idesc_bf16(128, 128, 0, 1); // [keys x hd] = P^T dO, dS^T Q
-            bool ok = mbar_wait(bar(0), 0, abort_flag, p.status);
+            bool ok = mbar_wait(bar(kKv), 0, abort_flag, p.status);
+            const bool prof = p.phase_clocks != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+            long long pc[8] = {0, 0, 0, 0, 0, 0, 0, 0}, last = clock64();
+#define MMA_TICK(i) if (prof) { const long long now = clock64(); pc[i] += now - last; last = now; }
             auto issue_s = [&](int j) -> bool {
-                const int b = j & 1;
-                const uint32_t sQ = sQdO + b * 2 * kHalfTile, sdO = sQ + kHalfTile;
-                if (!mbar_wait(bar(1 + b), (j >> 1) & 1, abort_flag, p.status)) return false;          // Q, dO of step j
-                if (!mbar_wait(bar(7 + b), ((j >> 1) & 1) ^ 1u, abort_flag, p.status)) return false;   // S^T / dP^T[b] read
+                const int b = j & 1, st = j % kBwdKv2Stages;
+                const uint32_t sQ = sQdO + st * 2 * kHalfTile, sdO = sQ + kHalfTile;
+                MMA_TICK(0)
+                if (!mbar_wait(bar(kQFull + st), (j / kBwdKv2Stages) & 1, abort_flag, p.status)) return false;   // Q, dO of step j
+                MMA_TICK(1)
+                if (!mbar_wait(bar(kSFree + b), ((j >> 1) & 1) ^ 1u, abort_flag, p.status)) return false;       // S^T / dP^T[b] read
+                MMA_TICK(2)
                 tc_fence_after();
                 const uint32_t tS = tm0 + 128 * b, tDP = tS + 64;
 #pragma unroll
@@ -837,42 +883,58 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     const uint32_t offb = (ks >> 2) * 8192 + (ks & 3) * 32;
                     tc_mma_f16(tDP, make_smem_desc(sV + offa, 16, 1024), make_smem_desc(sdO + offb, 16, 1024), idesc_st, ks != 0);
                 }
-                tc_commit(bar(5 + b));
+                tc_commit(bar(kSFull + b));
+                MMA_TICK(3)
                 return true;
             };
             if (ok && n_iter > 0) ok = issue_s(0);
             for (int it = 0; ok && it < n_iter; ++it) {
-                const int b = it & 1;
-                const uint32_t sQ = sQdO + b * 2 * kHalfTile, sdO = sQ + kHalfTile;
+                const int b = it & 1, st = it % kBwdKv2Stages;
+                const uint32_t sQ = sQdO + st * 2 * kHalfTile, sdO = sQ + kHalfTile;
                 if (it + 1 < n_iter && !issue_s(it + 1)) break;
-                if (!mbar_wait(bar(9 + b), (it >> 1) & 1, abort_flag, p.status)) break;      // P^T[b] written
+                MMA_TICK(0)
+                if (!mbar_wait(bar(kPReady + b), (it >> 1) & 1, abort_flag, p.status)) break;      // P^T[b] written
+                MMA_TICK(4)
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)
                     tc_mma_f16(tDV, make_smem_desc(sPT + b * kHalfTile + ks * 32, 16, 1024),
                                make_smem_desc(sdO + ks * 2048, 8192, 1024), idesc_acc, (it | ks) != 0);
-                tc_commit(bar(13 + b));
-                if (!mbar_wait(bar(11 + b), (it >> 1) & 1, abort_flag, p.status)) break;     // dS^T[b] written
+                tc_commit(bar(kPtFree + b));
+                MMA_TICK(5)
+                if (!mbar_wait(bar(kDsReady + b), (it >> 1) & 1, abort_flag, p.status)) break;     // dS^T[b] written
+                MMA_TICK(6)
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)
                     tc_mma_f16(tDK, make_smem_desc(sDS + b * kHalfTile + ks * 32, 16, 1024),
                                make_smem_desc(sQ + ks * 2048, 8192, 1024), idesc_acc, (it | ks) != 0);
-                tc_commit(bar(15 + b));
-                tc_commit(bar(3 + b));
-                if (it == n_iter - 1) tc_commit(bar(17));
+                tc_commit(bar(kDsFree + b));
+                tc_commit(bar(kQEmpty + st));
+                if (it == n_iter - 1) tc_commit(bar(kAccDone));
+                MMA_TICK(7)
             }
+            if (prof) {
+                for (int i = 0; i < 8; ++i) p.phase_clocks[i] = pc[i];
+                p.phase_clocks[30] = n_iter;
+            }
+#undef MMA_TICK
         }
     } else {
-        const int quad = warp & 3, half = (warp - 2) >> 2;
-        const int ew_tid = threadIdx.x - 64;
+        const int g = (warp - 2) >> 3;                            // element-wise group: steps with it % 2 == g, copy g of everything
+        const int quad = warp & 3, half = ((warp - 2) & 7) >> 2;
+        const int ew_tid = (threadIdx.x - 64) & (kBwd2Ew - 1);    // index inside the group
         const int key = quad * 32 + lane;                         // this thread's key row of the tile
         const int c0 = half * 32;                                 // its first query column
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
         const float c = p.scale * kLog2e;
         const long long key_abs = (long long)w.kv0 + key;
+        const uint32_t tS = tm0 + 128 * g + lane_base + c0, tDP = tS + 64;
+        const uint32_t myPT = sPT + g * kHalfTile, myDS = sDS + g * kHalfTile;
+        float* lse_g = s_lse + g * 64;
+        float* delta_g = s_delta + g * 64;
         bool ok = true;
-        // statistics of step 0, fetched by the first 128 element-wise threads (64 lse, 64 delta)
+        // statistics of a step, fetched by the group's first 128 threads (64 lse, 64 delta) one of its steps ahead
         auto fetch_stat = [&](int it) -> float {
             if (ew_tid >= 128 || it >= n_iter) return 0.f;
             const int h = kv_head * group + it % group;
@@ -881,85 +943,99 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             if (ew_tid < 64) return in ? p.lse[(long long)h * p.T + qa] * kLog2e : INFINITY;
             return in ? p.delta[(long long)h * p.T + qa] : 0.f;
         };
-        float stat = fetch_stat(0);
-        for (int it = 0; it < n_iter; ++it) {
-            const int b = it & 1;
+        float stat = fetch_stat(g);
+        const bool prof = p.phase_clocks != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && warp == 2 && lane == 0;
+        long long pc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0}, last = clock64();
+#define EW_TICK(i) if (prof) { const long long now = clock64(); pc[i] += now - last; last = now; }
+        for (int it = g; it < n_iter; it += 2) {
+            const int k = it >> 1;                                // this group's step count: parity of its barriers
             const int qr = w.q_begin + (it / group) * 64;
-            if (ew_tid < 64) s_lse[b * 64 + ew_tid] = stat;
-            else if (ew_tid < 128) s_delta[b * 64 + (ew_tid - 64)] = stat;
-            stat = fetch_stat(it + 1);                            // in flight during this step
-            // Every element-wise thread meets here in every step, also after a wait has given up (it then skips the
-            // step's work): nobody may leave the loop early and strand the others at this barrier.
-            ew_bar_sync();
+            // Every thread of the group meets at the two barriers below in every one of its steps, also after a wait has
+            // given up (it then skips the step's work): nobody may leave the loop early and strand the others.
+            ew_bar_sync(g);                                       // the previous step's readers of the statistics are done
+            if (ew_tid < 64) lse_g[ew_tid] = stat;
+            else if (ew_tid < 128) delta_g[ew_tid - 64] = stat;
+            stat = fetch_stat(it + 2);                            // in flight during this step
+            ew_bar_sync(g);
             if (!ok) continue;
-            if (!mbar_wait(bar(5 + b), (it >> 1) & 1, abort_flag, p.status)) { ok = false; continue; }
+            EW_TICK(0)
+            if (!mbar_wait(bar(kSFull + g), k & 1, abort_flag, p.status)) { ok = false; continue; }
+            EW_TICK(1)
             tc_fence_after();
             uint32_t sr[32], dr[32];
-            tmem_ld_32x32(tm0 + 128 * b + lane_base + c0, sr);
-            tmem_ld_32x32(tm0 + 128 * b + 64 + lane_base + c0, dr);
+            tmem_ld_32x32(tS, sr);
+            tmem_ld_32x32(tDP, dr);
             tmem_ld_wait();
             tc_fence_before();
-            mbar_arrive(bar(7 + b));                              // S^T / dP^T[b] may be overwritten by step it + 2
+            EW_TICK(2)
+            warp_arrive(bar(kSFree + g), lane);                         // S^T / dP^T[g] may be overwritten by step it + 2
+            // Only the tiles on the diagonal need the causal mask; everywhere else the loop carries no compare at all.
+            // Column i of this thread is query qr + c0 + i; it sees key `key_abs` when i >= lim.
             const bool need_mask = (qr < w.kv0 + 128);
+            const int lim = (int)(key_abs - qr) - c0;
             float pv[32];
+            if (need_mask) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                float pe = fast_exp2(__uint_as_float(sr[i]) * c - s_lse[b * 64 + c0 + i]);
-                if (need_mask && (long long)qr + c0 + i < key_abs) pe = 0.f;
-                pv[i] = pe;
+                for (int i = 0; i < 32; ++i) {
+                    const float pe = fast_exp2(__uint_as_float(sr[i]) * c - lse_g[c0 + i]);
+                    pv[i] = i < lim ? 0.f : pe;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) pv[i] = fast_exp2(__uint_as_float(sr[i]) * c - lse_g[c0 + i]);
             }
-            // P^T[b] (bf16, K-major A operand: one 128-byte row of 64 queries per key) once dV of step it - 2 has read it
-            if (!mbar_wait(bar(13 + b), ((it >> 1) & 1) ^ 1u, abort_flag, p.status)) { ok = false; continue; }
+            // P^T[g] (bf16, K-major A operand: one 128-byte row of 64 queries per key) once dV of step it - 2 has read it
+            EW_TICK(3)
+            if (!mbar_wait(bar(kPtFree + g), (k & 1) ^ 1u, abort_flag, p.status)) { ok = false; continue; }
+            EW_TICK(4)
 #pragma unroll
             for (int q8 = 0; q8 < 4; ++q8) {
-                const uint32_t a = sPT + b * kHalfTile + swz_off(key, c0 + q8 * 8);
+                const uint32_t a = myPT + swz_off(key, c0 + q8 * 8);
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a),
                              "r"(pack_bf16(pv[q8 * 8], pv[q8 * 8 + 1])), "r"(pack_bf16(pv[q8 * 8 + 2], pv[q8 * 8 + 3])),
                              "r"(pack_bf16(pv[q8 * 8 + 4], pv[q8 * 8 + 5])), "r"(pack_bf16(pv[q8 * 8 + 6], pv[q8 * 8 + 7]))
                              : "memory");
             }
+            EW_TICK(5)
             fence_proxy_async_smem();
-            mbar_arrive(bar(9 + b));
+            EW_TICK(6)
+            warp_arrive(bar(kPReady + g), lane);
             // dS^T = P^T * (dP^T - delta) * scale
 #pragma unroll
-            for (int i = 0; i < 32; ++i) pv[i] = pv[i] * (__uint_as_float(dr[i]) - s_delta[b * 64 + c0 + i]) * p.scale;
-            if (!mbar_wait(bar(15 + b), ((it >> 1) & 1) ^ 1u, abort_flag, p.status)) { ok = false; continue; }
+            for (int i = 0; i < 32; ++i) pv[i] = pv[i] * (__uint_as_float(dr[i]) - delta_g[c0 + i]) * p.scale;
+            EW_TICK(7)
+            if (!mbar_wait(bar(kDsFree + g), (k & 1) ^ 1u, abort_flag, p.status)) { ok = false; continue; }
+            EW_TICK(8)
 #pragma unroll
             for (int q8 = 0; q8 < 4; ++q8) {
-                const uint32_t a = sDS + b * kHalfTile + swz_off(key, c0 + q8 * 8);
+                const uint32_t a = myDS + swz_off(key, c0 + q8 * 8);
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a),
                              "r"(pack_bf16(pv[q8 * 8], pv[q8 * 8 + 1])), "r"(pack_bf16(pv[q8 * 8 + 2], pv[q8 * 8 + 3])),
                              "r"(pack_bf16(pv[q8 * 8 + 4], pv[q8 * 8 + 5])), "r"(pack_bf16(pv[q8 * 8 + 6], pv[q8 * 8 + 7]))
                              : "memory");
             }
             fence_proxy_async_smem();
-            mbar_arrive(bar(11 + b));
+            warp_arrive(bar(kDsReady + g), lane);
+            EW_TICK(9)
         }
-        if (ok && mbar_wait(bar(17), 0, abort_flag, p.status)) {
+        if (prof) for (int i = 0; i < 10; ++i) p.phase_clocks[10 + i] = pc[i];
+#undef EW_TICK
+        // the accumulators: group 0 stores dK, group 1 stores dV (each thread one row, 64 of its 128 columns)
+        if (ok && mbar_wait(bar(kAccDone), 0, abort_flag, p.status)) {
             tc_fence_after();
             const bool live = key_abs < w.q_end;
-            __nv_bfloat16* dk = reinterpret_cast<__nv_bfloat16*>(p.dK) + key_abs * p.ld_dk + kv_head * kHd + half * 64;
-            __nv_bfloat16* dv = reinterpret_cast<__nv_bfloat16*>(p.dV) + key_abs * p.ld_dv + kv_head * kHd + half * 64;
+            const long long ld = g == 0 ? p.ld_dk : p.ld_dv;
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(g == 0 ? p.dK : p.dV) + key_abs * ld + kv_head * kHd + half * 64;
+            const uint32_t tAcc = (g == 0 ? tDK : tDV) + lane_base + half * 64;
 #pragma unroll 1
             for (int cc = 0; cc < 64; cc += 32) {
                 uint32_t r[32];
-                tmem_ld_32x32(tDK + lane_base + half * 64 + cc, r);
+                tmem_ld_32x32(tAcc + cc, r);
                 tmem_ld_wait();
                 if (live) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8)
-                        *reinterpret_cast<uint4*>(dk + cc + i) = make_uint4(
-                            pack_bf16(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
-                            pack_bf16(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])),
-                            pack_bf16(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5])),
-                            pack_bf16(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7])));
-                }
-                tmem_ld_32x32(tDV + lane_base + half * 64 + cc, r);
-                tmem_ld_wait();
-                if (live) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 8)
-                        *reinterpret_cast<uint4*>(dv + cc + i) = make_uint4(
+                        *reinterpret_cast<uint4*>(dst + cc + i) = make_uint4(
                             pack_bf16(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
                             pack_bf16(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])),
                             pack_bf16(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5])),
@@ -982,9 +1058,9 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
 }
 
-// Q, dO (32 KiB each), 2 x dS (128 x 64, 16 KiB each), 3 stages of (K, V) 64 x 128 (16 KiB each)
-constexpr int kBwdQ2Stages = 3;
-constexpr int kBwdQ2Tiles = 2 * kTileBytes + 2 * kHalfTile + kBwdQ2Stages * 2 * kHalfTile;   // 196,608
+// Q, dO (32 KiB each), 2 x dS (128 x 64, 16 KiB each), 4 stages of (K, V) 64 x 128 (16 KiB each)
+constexpr int kBwdQ2Stages = 4;
+constexpr int kBwdQ2Tiles = 2 * kTileBytes + 2 * kHalfTile + kBwdQ2Stages * 2 * kHalfTile;   // 229,376
 constexpr int kBwdQ2Smem = kBwdQ2Tiles + 512;
 
 __global__ void __launch_bounds__(kBwd2Threads, 1)
@@ -999,9 +1075,9 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         return;
     }
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_q2 + kBwdQ2Tiles);
-    // [0] q, [1..3] kv_full, [4..6] kv_empty, [7..8] s_full, [9..10] s_free, [11..12] ds_ready, [13..14] ds_free, [15] acc_done
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
+    enum { kQ = 0, kKvFull = 1, kKvEmpty = 5, kSFull = 9, kSFree = 11, kDsReady = 13, kDsFree = 15, kAccDone = 17, kNumBars = 18 };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + kNumBars + 1);
     auto bar = [&](int i) { return smem_u32(&bars[i]); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1012,7 +1088,7 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
-        for (int i = 0; i < 16; ++i) mbar_init(bar(i), (i >= 9 && i <= 12) ? kBwd2Ew : 1);
+        for (int i = 0; i < kNumBars; ++i) mbar_init(bar(i), (i >= kSFree && i < kDsFree) ? kBwd2EwWarps : 1);
         mbar_fence_init();
     }
     if (warp == 1) {
@@ -1027,15 +1103,15 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
     if (warp == 0) {
         if (lane == 0) {
-            mbar_expect_tx(bar(0), 2 * kTileBytes);
-            tma_load_2d(sQ, &tmQ, bar(0), head * kHd, w.q0);
-            tma_load_2d(sQ + 16384, &tmQ, bar(0), head * kHd + 64, w.q0);
-            tma_load_2d(sdO, &tmdO, bar(0), head * kHd, w.q0);
-            tma_load_2d(sdO + 16384, &tmdO, bar(0), head * kHd + 64, w.q0);
+            mbar_expect_tx(bar(kQ), 2 * kTileBytes);
+            tma_load_2d(sQ, &tmQ, bar(kQ), head * kHd, w.q0);
+            tma_load_2d(sQ + 16384, &tmQ, bar(kQ), head * kHd + 64, w.q0);
+            tma_load_2d(sdO, &tmdO, bar(kQ), head * kHd, w.q0);
+            tma_load_2d(sdO + 16384, &tmdO, bar(kQ), head * kHd + 64, w.q0);
             for (int j = 0; j < w.n_kv; ++j) {
                 const int st = j % kBwdQ2Stages;
-                if (!mbar_wait(bar(4 + st), ((j / kBwdQ2Stages) & 1) ^ 1u, abort_flag, p.status)) break;
-                const uint32_t full = bar(1 + st);
+                if (!mbar_wait(bar(kKvEmpty + st), ((j / kBwdQ2Stages) & 1) ^ 1u, abort_flag, p.status)) break;
+                const uint32_t full = bar(kKvFull + st);
                 const uint32_t sK = sKV + st * 2 * kHalfTile, sV = sK + kHalfTile;
                 const int kr = w.kv0 + j * 64;
                 mbar_expect_tx(full, 2 * kHalfTile);
@@ -1049,12 +1125,12 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (lane == 0) {
             constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);     // [q x keys]
             constexpr uint32_t idesc_dq = make_idesc_bf16(128, 128, 0, 1);   // [q x hd] = dS K
-            bool ok = mbar_wait(bar(0), 0, abort_flag, p.status);
+            bool ok = mbar_wait(bar(kQ), 0, abort_flag, p.status);
             auto issue_s = [&](int j) -> bool {
                 const int b = j & 1, st = j % kBwdQ2Stages;
                 const uint32_t sK = sKV + st * 2 * kHalfTile, sV = sK + kHalfTile;
-                if (!mbar_wait(bar(1 + st), (j / kBwdQ2Stages) & 1, abort_flag, p.status)) return false;
-                if (!mbar_wait(bar(9 + b), ((j >> 1) & 1) ^ 1u, abort_flag, p.status)) return false;
+                if (!mbar_wait(bar(kKvFull + st), (j / kBwdQ2Stages) & 1, abort_flag, p.status)) return false;
+                if (!mbar_wait(bar(kSFree + b), ((j >> 1) & 1) ^ 1u, abort_flag, p.status)) return false;
                 tc_fence_after();
                 const uint32_t tS = tm0 + 128 * b, tDP = tS + 64;
 #pragma unroll
@@ -1069,7 +1145,7 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     const uint32_t offb = (ks >> 2) * 8192 + (ks & 3) * 32;
                     tc_mma_f16(tDP, make_smem_desc(sdO + offa, 16, 1024), make_smem_desc(sV + offb, 16, 1024), idesc_s, ks != 0);
                 }
-                tc_commit(bar(7 + b));
+                tc_commit(bar(kSFull + b));
                 return true;
             };
             if (ok && w.n_kv > 0) ok = issue_s(0);
@@ -1077,19 +1153,20 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 const int b = j & 1, st = j % kBwdQ2Stages;
                 const uint32_t sK = sKV + st * 2 * kHalfTile;
                 if (j + 1 < w.n_kv && !issue_s(j + 1)) break;
-                if (!mbar_wait(bar(11 + b), (j >> 1) & 1, abort_flag, p.status)) break;
+                if (!mbar_wait(bar(kDsReady + b), (j >> 1) & 1, abort_flag, p.status)) break;
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)
                     tc_mma_f16(tDQ, make_smem_desc(sDS + b * kHalfTile + ks * 32, 16, 1024),
                                make_smem_desc(sK + ks * 2048, 8192, 1024), idesc_dq, (j | ks) != 0);
-                tc_commit(bar(13 + b));
-                tc_commit(bar(4 + st));
-                if (j == w.n_kv - 1) tc_commit(bar(15));
+                tc_commit(bar(kDsFree + b));
+                tc_commit(bar(kKvEmpty + st));
+                if (j == w.n_kv - 1) tc_commit(bar(kAccDone));
             }
         }
     } else {
-        const int quad = warp & 3, half = (warp - 2) >> 2;
+        const int g = (warp - 2) >> 3;
+        const int quad = warp & 3, half = ((warp - 2) & 7) >> 2;
         const int row = quad * 32 + lane;
         const int c0 = half * 32;
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
@@ -1098,55 +1175,63 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const bool in = q_abs < w.q_end;
         const float lse2 = in ? p.lse[(long long)head * p.T + q_abs] * kLog2e : INFINITY;
         const float dl = in ? p.delta[(long long)head * p.T + q_abs] : 0.f;
+        const uint32_t tS = tm0 + 128 * g + lane_base + c0, tDP = tS + 64;
+        const uint32_t myDS = sDS + g * kHalfTile;
         bool ok = true;
-        for (int j = 0; j < w.n_kv; ++j) {
-            const int b = j & 1;
-            if (!mbar_wait(bar(7 + b), (j >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+        for (int j = g; j < w.n_kv; j += 2) {
+            const int k = j >> 1;
+            if (!mbar_wait(bar(kSFull + g), k & 1, abort_flag, p.status)) { ok = false; break; }
             tc_fence_after();
             uint32_t sr[32], dr[32];
-            tmem_ld_32x32(tm0 + 128 * b + lane_base + c0, sr);
-            tmem_ld_32x32(tm0 + 128 * b + 64 + lane_base + c0, dr);
+            tmem_ld_32x32(tS, sr);
+            tmem_ld_32x32(tDP, dr);
             tmem_ld_wait();
             tc_fence_before();
-            mbar_arrive(bar(9 + b));
+            warp_arrive(bar(kSFree + g), lane);
+            // column i of this thread is key k0 + i; the row sees it when i <= lim. Off the diagonal no compare is made.
             const int k0 = w.kv0 + j * 64 + c0;
             const bool need_mask = (k0 + 32 > w.q0);
+            const int lim = (int)(q_abs - k0);
             float pv[32];
+            if (need_mask) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                float pe = fast_exp2(__uint_as_float(sr[i]) * c - lse2);
-                if (need_mask && (long long)k0 + i > q_abs) pe = 0.f;
-                pv[i] = pe * (__uint_as_float(dr[i]) - dl) * p.scale;
+                for (int i = 0; i < 32; ++i) {
+                    const float pe = fast_exp2(__uint_as_float(sr[i]) * c - lse2);
+                    pv[i] = i > lim ? 0.f : pe * (__uint_as_float(dr[i]) - dl) * p.scale;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    pv[i] = fast_exp2(__uint_as_float(sr[i]) * c - lse2) * (__uint_as_float(dr[i]) - dl) * p.scale;
             }
-            if (!mbar_wait(bar(13 + b), ((j >> 1) & 1) ^ 1u, abort_flag, p.status)) { ok = false; break; }
+            if (!mbar_wait(bar(kDsFree + g), (k & 1) ^ 1u, abort_flag, p.status)) { ok = false; break; }
 #pragma unroll
             for (int q8 = 0; q8 < 4; ++q8) {
-                const uint32_t a = sDS + b * kHalfTile + swz_off(row, c0 + q8 * 8);
+                const uint32_t a = myDS + swz_off(row, c0 + q8 * 8);
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a),
                              "r"(pack_bf16(pv[q8 * 8], pv[q8 * 8 + 1])), "r"(pack_bf16(pv[q8 * 8 + 2], pv[q8 * 8 + 3])),
                              "r"(pack_bf16(pv[q8 * 8 + 4], pv[q8 * 8 + 5])), "r"(pack_bf16(pv[q8 * 8 + 6], pv[q8 * 8 + 7]))
                              : "memory");
             }
             fence_proxy_async_smem();
-            mbar_arrive(bar(11 + b));
+            warp_arrive(bar(kDsReady + g), lane);
         }
-        if (ok && mbar_wait(bar(15), 0, abort_flag, p.status)) {
+        // the accumulator: every thread of group g stores 32 columns of its row (group, half -> which 32 of the 128)
+        if (ok && mbar_wait(bar(kAccDone), 0, abort_flag, p.status)) {
             tc_fence_after();
-            __nv_bfloat16* dq = reinterpret_cast<__nv_bfloat16*>(p.dQ) + q_abs * p.ld_dq + head * kHd + half * 64;
-#pragma unroll 1
-            for (int cc = 0; cc < 64; cc += 32) {
-                uint32_t r[32];
-                tmem_ld_32x32(tDQ + lane_base + half * 64 + cc, r);
-                tmem_ld_wait();
-                if (in) {
+            const int col = g * 64 + half * 32;
+            __nv_bfloat16* dq = reinterpret_cast<__nv_bfloat16*>(p.dQ) + q_abs * p.ld_dq + head * kHd + col;
+            uint32_t r[32];
+            tmem_ld_32x32(tDQ + lane_base + col, r);
+            tmem_ld_wait();
+            if (in) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8)
-                        *reinterpret_cast<uint4*>(dq + cc + i) = make_uint4(
-                            pack_bf16(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
-                            pack_bf16(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])),
-                            pack_bf16(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5])),
-                            pack_bf16(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7])));
-                }
+                for (int i = 0; i < 32; i += 8)
+                    *reinterpret_cast<uint4*>(dq + i) = make_uint4(
+                        pack_bf16(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
+                        pack_bf16(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])),
+                        pack_bf16(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5])),
+                        pack_bf16(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7])));
             }
         }
     }
@@ -1212,7 +1297,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         mbar_init(bar_s_full[0], 1);
         mbar_init(bar_s_full[1], 1);
-        mbar_init(bar_p_ready, 128);
+        mbar_init(bar_p_ready, 4);            // one arrival per softmax warp
         mbar_init(bar_o_full, 1);
         mbar_fence_init();
     }
@@ -1296,15 +1381,22 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const int k0 = w.kv0 + j * 64;
             const bool need_mask = (k0 + 63 > w.q0);
             const uint32_t sP = sKV + (j & 1) * 2 * kHalfTile;
+            // key column i of a half-tile is visible to this row when i <= lim - 32 * half; only diagonal tiles compare
+            const int lim = (int)(q_abs - k0);
             float mx = m_ref;
 #pragma unroll 1
             for (int half = 0; half < 2; ++half) {
                 uint32_t r[32];
                 tmem_ld_32x32(tSj + lane_base + half * 32, r);
                 tmem_ld_wait();
+                if (need_mask) {
+                    const int lh = lim - half * 32;
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (!need_mask || (long long)k0 + half * 32 + i <= q_abs) mx = fmaxf(mx, __uint_as_float(r[i]));
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, i <= lh ? __uint_as_float(r[i]) : -INFINITY);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+                }
             }
             // the previous P V product must be done before P is overwritten or O is rescaled
             if (j > 0 && !mbar_wait(bar_o_full, (j - 1) & 1, abort_flag, p.status)) { ok = false; break; }
@@ -1335,17 +1427,26 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 tmem_ld_32x32(tSj + lane_base + half * 32, r);   // second read of the tile: cheaper than 64 live registers
                 tmem_ld_wait();
                 uint32_t pk[16];
+                // the row sum is taken from the fp32 probabilities (their bf16 roundings, which the P V product reads,
+                // differ from them by unbiased noise of relative size 2^-9 that averages out over a row)
+                if (need_mask) {
+                    const int lh = lim - half * 32;
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float p0 = fast_exp2(__uint_as_float(r[i]) * c - mc);
-                    float p1 = fast_exp2(__uint_as_float(r[i + 1]) * c - mc);
-                    if (need_mask) {
-                        if ((long long)k0 + half * 32 + i > q_abs) p0 = 0.f;
-                        if ((long long)k0 + half * 32 + i + 1 > q_abs) p1 = 0.f;
+                    for (int i = 0; i < 32; i += 2) {
+                        const float e0 = fast_exp2(__uint_as_float(r[i]) * c - mc);
+                        const float e1 = fast_exp2(__uint_as_float(r[i + 1]) * c - mc);
+                        const float p0 = i <= lh ? e0 : 0.f, p1 = i + 1 <= lh ? e1 : 0.f;
+                        pk[i >> 1] = pack_bf16(p0, p1);
+                        rs += p0 + p1;
                     }
-                    pk[i >> 1] = pack_bf16(p0, p1);
-                    const float2 pf = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&pk[i >> 1]));
-                    rs += pf.x + pf.y;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float p0 = fast_exp2(__uint_as_float(r[i]) * c - mc);
+                        const float p1 = fast_exp2(__uint_as_float(r[i + 1]) * c - mc);
+                        pk[i >> 1] = pack_bf16(p0, p1);
+                        rs += p0 + p1;
+                    }
                 }
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
@@ -1358,7 +1459,8 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             l += rs;
             fence_proxy_async_smem();
             tc_fence_before();
-            mbar_arrive(bar_p_ready);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_p_ready);
         }
         if (ok && mbar_wait(bar_o_full, (w.n_kv - 1) & 1, abort_flag, p.status)) {
             tc_fence_after();
@@ -1396,6 +1498,238 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_dealloc(tmem0, 256);
     }
 }
+
+
+// Forward, third form: as the second, but the probabilities never touch shared memory. Each softmax thread writes
+// its row of P (bf16 pairs) with tcgen05.st into the tensor-memory columns its scores came from, and the P V product
+// takes its A operand from tensor memory. Shared memory then carries only Q, K and V: a third less traffic per step on
+// the resource that limits this kernel (operand fetches of the products and the K/V loads share one 128-byte-per-clock
+// port), and the proxy fence between the softmax's stores and the product disappears.
+__global__ void __maxnreg__(128)
+attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+    if (status_poisoned(p.status)) return;
+    extern __shared__ __align__(1024) uint8_t smem3[];
+    const uint32_t base = smem_u32(smem3);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem3 + kFwd2Tiles);
+    // bars[0]=q, [1..2]=kv_full, [3..4]=kv_empty, [5]=s_full[0], [6]=p_ready, [7]=o_full, [8]=s_full[1]
+    uint32_t* tmem_slot_p = reinterpret_cast<uint32_t*>(smem3 + kFwd2Tiles + 80);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem3 + kFwd2Tiles + 88);
+    if (base & 1023u) {
+        if (threadIdx.x == 0 && p.status) atomicCAS(p.status, kStatusOk, kStatusBadArgument);
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t sQ = base, sKV = base + kTileBytes;
+    const uint32_t bar_q = smem_u32(&bars[0]), bar_p_ready = smem_u32(&bars[6]), bar_o_full = smem_u32(&bars[7]);
+    const uint32_t bar_s_full[2] = {smem_u32(&bars[5]), smem_u32(&bars[8])};
+    const int head = blockIdx.x;
+    const int kv_head = head / (p.Hq / p.Hkv);
+    const FwdWork w = p.work[blockIdx.y];
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        mbar_init(bar_q, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&bars[1 + s]), 1);
+            mbar_init(smem_u32(&bars[3 + s]), 1);
+        }
+        mbar_init(bar_s_full[0], 1);
+        mbar_init(bar_s_full[1], 1);
+        mbar_init(bar_p_ready, 4);            // one arrival per softmax warp
+        mbar_init(bar_o_full, 1);
+        mbar_fence_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(smem_u32(tmem_slot_p), 256);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem0 = *tmem_slot_p;
+    // two 64-column score buffers so the next tile's Q K^T runs while this tile's softmax does
+    const uint32_t tS = tmem0, tO = tmem0 + 128;
+
+    if (warp == 4) {
+        if (lane == 0) {
+            mbar_expect_tx(bar_q, kTileBytes);
+            tma_load_2d(sQ, &tmQ, bar_q, head * kHd, w.q0);
+            tma_load_2d(sQ + 16384, &tmQ, bar_q, head * kHd + 64, w.q0);
+            for (int j = 0; j < w.n_kv; ++j) {
+                const int st = j & 1;
+                if (!mbar_wait(smem_u32(&bars[3 + st]), ((j >> 1) & 1) ^ 1u, abort_flag, p.status)) break;
+                const uint32_t full = smem_u32(&bars[1 + st]);
+                const uint32_t sK = sKV + st * 2 * kHalfTile, sV = sK + kHalfTile;
+                const int kr = w.kv0 + j * 64;
+                mbar_expect_tx(full, 2 * kHalfTile);
+                tma_load_2d(sK, &tmK, full, kv_head * kHd, kr);
+                tma_load_2d(sK + 8192, &tmK, full, kv_head * kHd + 64, kr);
+                tma_load_2d(sV, &tmV, full, kv_head * kHd, kr);
+                tma_load_2d(sV + 8192, &tmV, full, kv_head * kHd + 64, kr);
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);
+            constexpr uint32_t idesc_o = make_idesc_bf16(128, 128, 0, 1);
+            bool ok = mbar_wait(bar_q, 0, abort_flag, p.status);
+            auto issue_s = [&](int j) -> bool {
+                const int st = j & 1;
+                const uint32_t sK = sKV + st * 2 * kHalfTile;
+                if (!mbar_wait(smem_u32(&bars[1 + st]), (j >> 1) & 1, abort_flag, p.status)) return false;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t offa = (ks >> 2) * 16384 + (ks & 3) * 32;
+                    const uint32_t offb = (ks >> 2) * 8192 + (ks & 3) * 32;
+                    tc_mma_f16(tS + st * 64, make_smem_desc(sQ + offa, 16, 1024),
+                               make_smem_desc(sK + offb, 16, 1024), idesc_s, ks != 0);
+                }
+                tc_commit(bar_s_full[st]);
+                return true;
+            };
+            if (ok && w.n_kv > 0) ok = issue_s(0);
+            for (int j = 0; ok && j < w.n_kv; ++j) {
+                const int st = j & 1;
+                const uint32_t sK = sKV + st * 2 * kHalfTile, sV = sK + kHalfTile;
+                if (j + 1 < w.n_kv && !issue_s(j + 1)) break;
+                if (!mbar_wait(bar_p_ready, j & 1, abort_flag, p.status)) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    // P: 16 keys = 8 packed columns per step, in the score buffer of this step
+                    tc_mma_f16_tmem_a(tO, tS + st * 64 + ks * 8, make_smem_desc(sV + ks * 2048, 8192, 1024), idesc_o, (j | ks) != 0);
+                }
+                tc_commit(bar_o_full);
+                tc_commit(smem_u32(&bars[3 + st]));
+            }
+        }
+    } else {
+        const int row = warp * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const float c = p.scale * kLog2e;
+        const long long q_abs = (long long)w.q0 + row;
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < w.n_kv; ++j) {
+            if (!mbar_wait(bar_s_full[j & 1], (j >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t tSj = tS + (j & 1) * 64;
+            const int k0 = w.kv0 + j * 64;
+            const bool need_mask = (k0 + 63 > w.q0);
+            // key column i of a half-tile is visible to this row when i <= lim - 32 * half; only diagonal tiles compare
+            const int lim = (int)(q_abs - k0);
+            float mx = m_ref;
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+                uint32_t r[32];
+                tmem_ld_32x32(tSj + lane_base + half * 32, r);
+                tmem_ld_wait();
+                if (need_mask) {
+                    const int lh = lim - half * 32;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, i <= lh ? __uint_as_float(r[i]) : -INFINITY);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+                }
+            }
+            // the previous P V product must be done before P is overwritten or O is rescaled
+            if (j > 0 && !mbar_wait(bar_o_full, (j - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+            const bool grow = (mx - m_ref) * c > 8.f;   // also true on the first tile (m_ref = -inf)
+            if (__any_sync(0xffffffffu, grow)) {
+                const float alpha = fast_exp2((m_ref - mx) * c);
+                if (j > 0) {
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int cc = 0; cc < 128; cc += 32) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(tO + lane_base + cc, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                        tmem_st_32x32(tO + lane_base + cc, r);
+                    }
+                    tmem_st_wait();
+                }
+                l *= alpha;
+                m_ref = mx;
+            }
+            const float mc = m_ref * c;
+            float rs = 0.f;
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+                uint32_t r[32];
+                tmem_ld_32x32(tSj + lane_base + half * 32, r);   // second read of the tile: cheaper than 64 live registers
+                tmem_ld_wait();
+                uint32_t pk[16];
+                // the row sum is taken from the fp32 probabilities (their bf16 roundings, which the P V product reads,
+                // differ from them by unbiased noise of relative size 2^-9 that averages out over a row)
+                if (need_mask) {
+                    const int lh = lim - half * 32;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float e0 = fast_exp2(__uint_as_float(r[i]) * c - mc);
+                        const float e1 = fast_exp2(__uint_as_float(r[i + 1]) * c - mc);
+                        const float p0 = i <= lh ? e0 : 0.f, p1 = i + 1 <= lh ? e1 : 0.f;
+                        pk[i >> 1] = pack_bf16(p0, p1);
+                        rs += p0 + p1;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float p0 = fast_exp2(__uint_as_float(r[i]) * c - mc);
+                        const float p1 = fast_exp2(__uint_as_float(r[i + 1]) * c - mc);
+                        pk[i >> 1] = pack_bf16(p0, p1);
+                        rs += p0 + p1;
+                    }
+                }
+                tmem_st_32x16(tSj + lane_base + half * 16, pk);      // P over the first 32 columns of this score buffer
+            }
+            tmem_st_wait();
+            l += rs;
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_p_ready);
+        }
+        if (ok && mbar_wait(bar_o_full, (w.n_kv - 1) & 1, abort_flag, p.status)) {
+            tc_fence_after();
+            const bool live = q_abs < w.q_end;
+            const float inv = 1.f / l;
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.O) + q_abs * p.ldo + head * kHd;
+#pragma unroll 1
+            for (int cc = 0; cc < 128; cc += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tO + lane_base + cc, r);
+                tmem_ld_wait();
+                if (live) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8)
+                        *reinterpret_cast<uint4*>(out + cc + i) = make_uint4(
+                            pack_bf16(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv),
+                            pack_bf16(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv),
+                            pack_bf16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv),
+                            pack_bf16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv));
+                }
+            }
+            if (live) p.lse[(long long)head * p.T + q_abs] = m_ref * p.scale + logf(l);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) { }
+        __syncthreads();
+    }
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem0, 256);
+    }
+}
+
 
 
 static int set_smem(const void* fn, int bytes) {
@@ -1452,6 +1786,28 @@ int halo_attn_fwd2(const void* q, const void* k, const void* v, void* o, float* 
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
+// Third form of the forward (as the second, P kept in tensor memory). Same arguments and work list as halo_attn_fwd2.
+int halo_attn_fwd3(const void* q, const void* k, const void* v, void* o, float* lse, const void* work,
+                   int n_tiles, long long T, int Hq, int Hkv, int head_dim, long long ldq,
+                   long long ldk, long long ldv, long long ldo, float scale, int* status, void* stream) {
+    if (head_dim != kHd || Hq % Hkv) return -1;
+    if (n_tiles == 0) return 0;
+    CUtensorMap tq, tk, tv;
+    if (make_tmap_bf16(&tq, q, T, (long long)Hq * kHd, ldq, 128)) return -2;
+    if (make_tmap_bf16(&tk, k, T, (long long)Hkv * kHd, ldk, 64)) return -3;
+    if (make_tmap_bf16(&tv, v, T, (long long)Hkv * kHd, ldv, 64)) return -4;
+    static bool cfg = false;
+    if (!cfg) {
+        if (set_smem((const void*)attn_fwd3_kernel, kFwd2Smem)) return -10;
+        cudaFuncSetAttribute((const void*)attn_fwd3_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+        cfg = true;
+    }
+    AttnParams p{reinterpret_cast<const FwdWork*>(work), o, lse, ldo, T, Hq, Hkv, scale, status};
+    attn_fwd3_kernel<<<dim3(Hq, n_tiles), kFwdThreads, kFwd2Smem, (cudaStream_t)stream>>>(tq, tk, tv, p);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
 // Resident CTAs per SM the second forward form achieves on the current device (diagnostic).
 int halo_attn_fwd2_occupancy() {
     set_smem((const void*)attn_fwd2_kernel, kFwd2Smem);
@@ -1488,6 +1844,11 @@ int halo_attn_fwd2_occupancy() {
     return n;
 }
 
+// Diagnostic: a device array of 32 int64 that the dK/dV kernel's first CTA fills with the cycles its MMA thread ([0..7])
+// and one element-wise thread ([10..19]) spent in each phase of their loops, [30] = steps. Null (the default) = off.
+static long long* g_bwd_phase_clocks = nullptr;
+void halo_attn_bwd_phase_clocks(long long* dev_array) { g_bwd_phase_clocks = dev_array; }
+
 // delta: [Hq, T] fp32 scratch. kv_work: n_kv_tiles {kv0, q_begin, n_q(64-row sub-tiles), q_end};
 // q_work: n_q_tiles {q0, kv0, n_kv(64-key sub-tiles), q_end}.
 int halo_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
@@ -1521,7 +1882,7 @@ int halo_attn_bwd(const void* q, const void* k, const void* v, const void* o, co
         if (e && atoi(e) == 1) variant = 1;
         cfg = true;
     }
-    BwdParams p{kv_work, lse, delta, dq, dk, dv, ld_dq, ld_dk, ld_dv, T, Hq, Hkv, scale, status};
+    BwdParams p{kv_work, lse, delta, dq, dk, dv, ld_dq, ld_dk, ld_dv, T, Hq, Hkv, scale, status, g_bwd_phase_clocks};
     if (n_kv_tiles > 0) {
         if (variant == 2) attn_bwd_dkdv2_kernel<<<dim3(Hkv, n_kv_tiles), kBwd2Threads, kBwdKv2Smem, s>>>(tq64, tk, tv, tdo64, p);
         else attn_bwd_dkdv_kernel<<<dim3(Hkv, n_kv_tiles), kBwdThreads, kBwdKvSmem, s>>>(tq64, tk, tv, tdo64, p);

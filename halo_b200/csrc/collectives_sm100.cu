@@ -11,6 +11,11 @@
 //                   destination GPU
 //   allreduce_small one-shot all-reduce of a small fp32 vector (norm scalars, router gradients)
 //
+// Every kernel also has an NVLS form for buffers that are bound to an NVLink multicast object (their `mc` argument is
+// the multicast address of the same symmetric buffer): reductions read with multimem.ld_reduce, which sums the ranks'
+// values inside the switch, and the all-gather / broadcast stores are multimem.st, which the switch replicates to
+// every rank, so each byte crosses this GPU's links once whatever the number of peers.
+//
 // A phase boundary (all peers' gradients written / all slices summed / all weights stored) is a
 // device-side barrier issued by the host between the launches; the kernels themselves never spin
 // on another GPU.
@@ -113,7 +118,8 @@ struct SliceTable {
 constexpr int kSliceElemsPerBlock = 256 * 8 * 8;
 
 __global__ void __launch_bounds__(256)
-adam_allgather_kernel(const __grid_constant__ Peers params, int n_ranks, int my_rank, long long lo, const float* __restrict__ gsum,
+adam_allgather_kernel(const __grid_constant__ Peers params, __nv_bfloat16* mc_params, int n_ranks, int my_rank, long long lo,
+                      const float* __restrict__ gsum,
                       __nv_bfloat16* __restrict__ m, __nv_bfloat16* __restrict__ v, SliceTable tab, float beta1,
                       float beta2, float omb1, float omb2, float step_size, float bc2_sqrt, float eps,
                       unsigned long long key_step, const float* __restrict__ grad_scale, const int* __restrict__ skip) {
@@ -176,8 +182,15 @@ adam_allgather_kernel(const __grid_constant__ Peers params, int n_ranks, int my_
         *reinterpret_cast<uint4*>(m + i) = *reinterpret_cast<uint4*>(mo);
         *reinterpret_cast<uint4*>(v + i) = *reinterpret_cast<uint4*>(vo);
         const uint4 out = *reinterpret_cast<uint4*>(po);
-        for (int r = 0; r < n_ranks; ++r)   // the all-gather: one 16-byte store per peer
-            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(params.p[r]) + lo + i) = out;
+        if (mc_params) {
+            // the all-gather as ONE store: the switch writes it into every rank's parameter buffer
+            asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_params + lo + i),
+                         "r"(out.x), "r"(out.y), "r"(out.z), "r"(out.w)
+                         : "memory");
+        } else {
+            for (int r = 0; r < n_ranks; ++r)   // the all-gather: one 16-byte store per peer
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(params.p[r]) + lo + i) = out;
+        }
     }
 }
 
@@ -231,6 +244,67 @@ __global__ void allreduce_small_kernel(const __grid_constant__ Peers bufs, int n
     out[i] = s;
 }
 
+// ---------------------------------------------------------------------------------------------
+// NVLS forms (multimem.* on a multicast address)
+// ---------------------------------------------------------------------------------------------
+// sum[i] = sum over ranks of grads[lo + i], reduced inside the switch with fp32 accumulation and returned rounded to
+// bf16 (what a bf16 all-reduce delivers); partial[b] = sum of squares of the rounded sums.
+__global__ void __launch_bounds__(256)
+rs_sum_norm_mc_kernel(const __nv_bfloat16* mc_grads, long long lo, long long count, float* __restrict__ sum_out,
+                      float* __restrict__ partial) {
+    __shared__ float red[8];
+    float acc = 0.f;
+    const long long nvec = count / 8;
+    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
+        uint32_t a, b, c, d;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
+                     : "l"(mc_grads + lo + v * 8)
+                     : "memory");
+        const uint32_t u[4] = {a, b, c, d};
+        float s[8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u[q]));
+            s[2 * q] = f.x;
+            s[2 * q + 1] = f.y;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc += s[j] * s[j];
+        reinterpret_cast<float4*>(sum_out)[2 * v] = make_float4(s[0], s[1], s[2], s[3]);
+        reinterpret_cast<float4*>(sum_out)[2 * v + 1] = make_float4(s[4], s[5], s[6], s[7]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int i = 0; i < 8; ++i) t += red[i];
+        partial[blockIdx.x] = t;
+    }
+}
+
+// mc_dst[i] = src[i] on every rank of the multicast group (16-byte vectors)
+__global__ void __launch_bounds__(256)
+broadcast_bytes_mc_kernel(const uint4* __restrict__ src, uint4* mc_dst, long long nvec) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+        const uint4 u = src[i];
+        asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_dst + i), "r"(u.x), "r"(u.y),
+                     "r"(u.z), "r"(u.w)
+                     : "memory");
+    }
+}
+
+// out[i] = sum over ranks of buf[i], one multimem.ld_reduce per element
+__global__ void allreduce_small_mc_kernel(const float* mc, float* __restrict__ out, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float s;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.f32 %0, [%1];" : "=f"(s) : "l"(mc + i) : "memory");
+    out[i] = s;
+}
+
 static int fill(Peers* o, void* const* host_ptrs, int n) {
     if (n < 1 || n > kMaxPeersC) return -1;
     for (int i = 0; i < kMaxPeersC; ++i) o->p[i] = i < n ? host_ptrs[i] : nullptr;
@@ -261,21 +335,50 @@ int halo_rs_sum_norm(void* const* grads, int n_ranks, long long lo, long long co
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
+// NVLS form of halo_rs_sum_norm: mc_grads is the multicast address of the flat bf16 gradient buffer.
+int halo_rs_sum_norm_mc(const void* mc_grads, long long lo, long long count, float* sum_out, float* partial, void* stream) {
+    if ((lo % 8) || (count % 8) || !mc_grads) return -1;
+    const int blocks = halo_rs_blocks(count);
+    rs_sum_norm_mc_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)mc_grads, lo, count, sum_out, partial);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// NVLS form of halo_broadcast_bytes: one multimem.st per 16 bytes reaches every rank of the multicast group.
+int halo_broadcast_bytes_mc(const void* src, void* mc_dst, long long dst_offset, long long n_bytes, void* stream) {
+    if ((n_bytes % 16) || (dst_offset % 16) || (reinterpret_cast<uintptr_t>(src) % 16) || !mc_dst) return -1;
+    if (n_bytes == 0) return 0;
+    const long long nvec = n_bytes / 16;
+    long long blocks = (nvec + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    broadcast_bytes_mc_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+        (const uint4*)src, reinterpret_cast<uint4*>(reinterpret_cast<char*>(mc_dst) + dst_offset), nvec);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// NVLS form of halo_allreduce_small.
+int halo_allreduce_small_mc(const void* mc, float* out, int n, void* stream) {
+    if (n <= 0) return 0;
+    if (!mc) return -1;
+    allreduce_small_mc_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>((const float*)mc, out, n);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
 int halo_slice_elems_per_block() { return kSliceElemsPerBlock; }
 
+// mc_params: the multicast address of the parameter buffer (null: store to every peer in turn)
 int halo_adam_allgather(void* const* params, int n_ranks, int my_rank, long long lo, const float* gsum, void* m,
                         void* v, const long long* seg_off, const long long* seg_len, const long long* seg_toff,
                         const unsigned long long* seg_hash, const float* seg_wd, const int* block_start, int n_seg,
                         int total_blocks, float beta1, float beta2, float step_size, float bc2_sqrt, float eps,
                         unsigned long long key, unsigned long long step, const float* grad_scale, const int* skip,
-                        void* stream) {
+                        void* stream, void* mc_params) {
     if (n_seg <= 0 || total_blocks <= 0) return 0;
     Peers p;
     if (fill(&p, params, n_ranks)) return -2;
     SliceTable t{seg_off, seg_len, seg_toff, seg_hash, seg_wd, block_start, n_seg};
     const float omb1 = (float)(1.0 - (double)beta1), omb2 = (float)(1.0 - (double)beta2);
     adam_allgather_kernel<<<total_blocks, 256, 0, (cudaStream_t)stream>>>(
-        p, n_ranks, my_rank, lo, gsum, (__nv_bfloat16*)m, (__nv_bfloat16*)v, t, beta1, beta2, omb1, omb2, step_size,
+        p, (__nv_bfloat16*)mc_params, n_ranks, my_rank, lo, gsum, (__nv_bfloat16*)m, (__nv_bfloat16*)v, t, beta1, beta2, omb1, omb2, step_size,
         bc2_sqrt, eps, key ^ step, grad_scale, skip);
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

@@ -61,6 +61,8 @@ def build_runtime(pc, device, group=None):
     from halo_b200.parallel.runtime import ParallelRuntime
 
     group = group if group is not None else dist.group.WORLD
+    if pc.pp_size > 1:
+        return _pipeline_runtime(pc, device, group)
     if pc.tp_size > 1 or pc.cp_size > 1:
         return _token_cutting_runtime(pc, device, group)
     if pc.ep_size == pc.world_size and device.type == "cuda":
@@ -70,6 +72,55 @@ def build_runtime(pc, device, group=None):
 
         return ParallelRuntime(device, dp_group=group, ep_group=group, transport=CollectiveTransport(group))
     return ParallelRuntime(device, dp_group=group)
+
+
+def _pipeline_runtime(pc, device, group):
+    """Pipeline parallelism: stage s is the contiguous block of ``world / pp`` ranks starting at ``s * world / pp``; the
+    ranks at one position of every stage form a chain (the pipeline group, NCCL / gloo point-to-point), the ranks of
+    one stage are its replicas (data parallel, with the experts sharded over them when ``ep_size`` equals the stage
+    width). Every rank creates every subgroup, in the same order. Finished by :func:`load_policy_model`, which knows
+    the model's sizes."""
+    from halo_b200.parallel.runtime import ParallelRuntime
+
+    if pc.tp_size > 1 or pc.cp_size > 1:
+        raise ValueError("pipeline parallelism together with tensor / context parallelism is not wired into the entry points")
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    width = world // pc.pp_size
+    if pc.ep_size not in (1, width):
+        raise ValueError(f"with pipeline stages of {width} ranks, expert_parallel_size must be 1 or {width}, got {pc.ep_size}")
+    ranks = [dist.get_global_rank(group, r) for r in range(world)] if group is not dist.group.WORLD else list(range(world))
+    stage, pos = rank // width, rank % width
+    chain = stage_group = None
+    for j in range(width):                                # chains: one rank of every stage
+        g = dist.new_group(ranks[j::width])
+        if j == pos:
+            chain = g
+    for s in range(pc.pp_size):                           # stages: their replicas
+        g = dist.new_group(ranks[s * width:(s + 1) * width]) if width > 1 else None
+        if s == stage:
+            stage_group = g
+    parallel = None
+    if width > 1:
+        if pc.ep_size == width and device.type == "cuda":
+            parallel = ParallelRuntime.for_expert_parallel(width, device, group=stage_group)
+        elif pc.ep_size == width:
+            from halo_b200.parallel.expert_parallel import CollectiveTransport
+
+            parallel = ParallelRuntime(device, dp_group=stage_group, ep_group=stage_group, transport=CollectiveTransport(stage_group))
+        else:
+            parallel = ParallelRuntime(device, dp_group=stage_group)
+    return {"kind": "pp", "chain": chain, "stage": stage, "n_stages": pc.pp_size, "position": pos, "width": width,
+            "parallel": parallel, "device": device, "schedule": pc.pp_schedule, "split": pc.pp_split, "pc": pc}
+
+
+def finish_pipeline_runtime(spec: dict, model, optimizer, row_len: int, max_grad_norm: float, lr_scheduler=None):
+    """The stage object and the training engine of one pipeline rank, once its model slice and optimizer exist."""
+    from halo_b200.parallel.pipeline import PipelineStage
+    from halo_b200.trainers.pipeline_engine import PipelineEngine
+
+    stage = PipelineStage(model, spec["chain"], row_len)
+    return PipelineEngine(stage, optimizer, max_grad_norm, spec["schedule"], lr_scheduler, parallel=spec["parallel"],
+                          min_microbatches=spec["n_stages"] if spec["schedule"] == "1f1b" else 1)
 
 
 def _token_cutting_runtime(pc, device, group):
@@ -126,6 +177,24 @@ def load_policy_model(model_args, pc, device, runtime, gradient_checkpointing=Tr
         cfg = dataclasses.replace(cfg, num_nextn_predict_layers=1, mtp_loss_weight=model_args.mtp_loss_weight,
                                   mtp_objective=model_args.mtp_objective)
     reject_model_layout(pc, cfg)
+    if isinstance(runtime, dict) and runtime.get("kind") == "pp":
+        # this rank's stage: its layer range (head-weighted unless pipeline_split says otherwise), the embedding on the
+        # first stage, the final norm and the head on the last; from a checkpoint every stage reads only its own tensors
+        from halo_b200.parallel.pipeline import stage_layer_range
+
+        spec = runtime
+        lo, hi = stage_layer_range(cfg, spec["stage"], spec["n_stages"], spec["split"])
+        par = spec["parallel"]
+        transport = par.transport if par is not None else None
+        if transport is not None and hasattr(transport, "configure") and cfg.is_moe:
+            transport.configure(max_tokens=max_tokens, top_k=cfg.num_experts_per_tok, hidden=cfg.hidden_size,
+                                n_local_experts=cfg.num_experts // transport.n_ranks)
+        kw = dict(device=device, dtype=dtype, transport=transport, gradient_checkpointing=gradient_checkpointing,
+                  layer_range=(lo, hi), has_embed=spec["stage"] == 0, has_head=spec["stage"] == spec["n_stages"] - 1)
+        model = build_model(cfg, **kw) if model_args.init_from_scratch else from_pretrained(model_args.model_name_or_path, **kw)
+        model.parallel_runtime = spec
+        log.info("pipeline stage %d of %d: decoder layers [%d, %d)", spec["stage"], spec["n_stages"], lo, hi)
+        return model
     if isinstance(runtime, dict):          # tensor / context parallelism: needs the model's sizes to finish
         runtime = finish_token_cutting_runtime(runtime, cfg, max_tokens)
         model = build_model(cfg, device=device, dtype=dtype, gradient_checkpointing=gradient_checkpointing,
@@ -223,6 +292,17 @@ def run_trainer(trainer, train_args):
     result = trainer.train()
     final = os.path.join(train_args.output_dir, "final")
     from halo_b200.checkpoint.save import save_model
+
+    spec = getattr(trainer.model, "parallel_runtime", None)
+    if isinstance(spec, dict) and spec.get("kind") == "pp":
+        from halo_b200.checkpoint.save import save_pipeline_stages
+
+        # one chain writes (position 0 of every stage); the other replicas of a stage only hand over their expert shards
+        sharded = spec["parallel"] is not None and spec["parallel"].ep_world > 1
+        if spec["position"] == 0 or sharded:
+            save_pipeline_stages(trainer.model, final, spec["stage"], spec["n_stages"], group=spec["chain"],
+                                 is_writer=spec["position"] == 0)
+        return result
 
     save_model(trainer.model, final, group=trainer.group, is_writer=trainer.is_main,
                adapters="merge" if getattr(trainer.model, "merge_adapters_on_save", False) else "auto")

@@ -35,6 +35,8 @@ CATALOGUE = {
     "HALO_GEMM_PAIR": "CTA-pair GEMM: 1 where it wins (default), 0 never, 2 everywhere",
     "HALO_ATTN_BWD_VARIANT": "backward attention kernels (2 = double-buffered score tiles and eight element-wise warps, the default; 1 = the first form)",
     "HALO_ATTN_FWD_VARIANT": "forward attention kernel form (2 = output kept in TMEM, the default)",
+    "HALO_WEIGHT_SYNC_NVLS": "trainer -> rollout weight push through NVLink multicast stores when the arena supports it (default 1)",
+    "HALO_ZERO_NVLS": "sharded optimizer: reduce and all-gather through NVLink multicast (multimem) when the buffers support it (default 0: plain peer loads / stores, bit-identical to the unsharded optimizer)",
     "HALO_MOE_FUSED": "expert products with the token movement inside the GEMM kernels (1, default) or as separate push / pull kernels (0)",
     "HALO_PEER_WAIT_MS": "how long a kernel waits for rows or a flag from a peer GPU before it gives up with a status (default 20000)",
     "HALO_ROW_BLOCKS_PER_SM": "thread blocks per SM of the expert row kernels (dispatch / combine)",
@@ -157,6 +159,14 @@ def weight_sync_chunk_bytes() -> int:
 
 def weight_sync_gather_ahead() -> int:
     return env_non_negative_int("HALO_WEIGHT_SYNC_GATHER_AHEAD", 1)
+
+
+def weight_sync_nvls() -> bool:
+    return env_flag("HALO_WEIGHT_SYNC_NVLS", True)
+
+
+def zero_nvls() -> bool:
+    return env_flag("HALO_ZERO_NVLS", False)
 
 
 def moe_fused() -> bool:

@@ -22,11 +22,14 @@ from . import _lib
 HEAD_DIM = 128
 # 1: 128-key tiles, output rescaled in registers, one CTA per SM
 # 2: 64-key tiles, output accumulated in TMEM with lazy rescale, two CTAs per SM
+# 3: as 2, with the probabilities written to tensor memory (tcgen05.st) and read from there by the P V product
 FWD_VARIANT = int(os.environ.get("HALO_ATTN_FWD_VARIANT", "2"))
 
 
 def _launch_fwd(L, q, k, v, o, lse, plan, T, n_heads, n_kv_heads, scale, dev):
-    if FWD_VARIANT == 2:
+    if FWD_VARIANT == 3:
+        work, fn, what = plan.bwd_q, L.halo_attn_fwd3, "halo_attn_fwd3"
+    elif FWD_VARIANT == 2:
         work, fn, what = plan.bwd_q, L.halo_attn_fwd2, "halo_attn_fwd2"
     else:
         work, fn, what = plan.fwd, L.halo_attn_fwd, "halo_attn_fwd"

@@ -156,6 +156,15 @@ def run_schedule(stage: PipelineStage, micro_batches: list, normalizer, schedule
     return total.float()
 
 
+@torch.no_grad()
+def forward_only(stage: PipelineStage, batch, normalizer) -> torch.Tensor:
+    """One micro-batch through the stages without a backward (evaluation): the last stage returns the loss, the others
+    zero."""
+    fl = stage.forward_micro(batch, normalizer)
+    stage.drain()
+    return fl.out.detach().float() if stage.is_last else torch.zeros((), device=stage.device)
+
+
 def broadcast_loss(stage: PipelineStage, loss: torch.Tensor) -> torch.Tensor:
     """The last stage's loss, on every stage (for logging and the non-finite guard)."""
     t = loss.detach().clone().reshape(1).float()
@@ -164,15 +173,28 @@ def broadcast_loss(stage: PipelineStage, loss: torch.Tensor) -> torch.Tensor:
     return t[0]
 
 
+def stage_layer_range(cfg, stage: int, n_stages: int, split: list[int] | None = None) -> tuple[int, int]:
+    """Decoder layers ``[lo, hi)`` of one stage. ``split``: explicit first-layer indices of stages 1.. or, as the
+    configuration spells it, the layer COUNT of every stage."""
+    if split and len(split) == n_stages:                  # per-stage layer counts -> first-layer indices of stages 1..
+        starts, acc = [], 0
+        for n in split[:-1]:
+            acc += int(n)
+            starts.append(acc)
+        if acc + int(split[-1]) != cfg.num_hidden_layers:
+            raise ValueError(f"pipeline_split {split} does not add up to {cfg.num_hidden_layers} layers")
+        split = starts
+    head_weight = (cfg.vocab_size * cfg.hidden_size) / max(1, cfg.param_counts()["active"] / cfg.num_hidden_layers) * 0.5
+    return partition_layers(cfg.num_hidden_layers, n_stages, head_weight=min(head_weight, 4.0), split=split)[stage]
+
+
 def build_stage_model(cfg, stage: int, n_stages: int, device, dtype=None, transport=None, seed: int = 0,
                       gradient_checkpointing: bool = True, split: list[int] | None = None):
     """The stage's model slice, initialised so that the union of all stages equals the unsplit model built with
     the same seed (initialisation is keyed by parameter name and global layer index)."""
     from halo_b200.models.qwen3 import build_model
 
-    head_weight = (cfg.vocab_size * cfg.hidden_size) / max(1, cfg.param_counts()["active"] / cfg.num_hidden_layers) * 0.5
-    ranges = partition_layers(cfg.num_hidden_layers, n_stages, head_weight=min(head_weight, 4.0), split=split)
-    lo, hi = ranges[stage]
+    lo, hi = stage_layer_range(cfg, stage, n_stages, split)
     return build_model(cfg, device=device, dtype=dtype, transport=transport, seed=seed,
                        gradient_checkpointing=gradient_checkpointing, layer_range=(lo, hi), has_embed=stage == 0,
                        has_head=stage == n_stages - 1)

@@ -43,12 +43,18 @@ def _round_up(x: int, m: int) -> int:
 
 class FusedShardedAdamW:
     def __init__(self, named_params, group, device, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01,
-                 key: int = SR_KEY, replicate_group=None):
+                 key: int = SR_KEY, replicate_group=None, nvls: bool | None = None):
         """``group``: the ranks the flat space is cut over (the ``dp_shard`` axis). ``replicate_group``: under hybrid
         sharding, the ranks that own the SAME slice in the other shard groups (the ``dp_replicate`` axis); every owner
         adds its peers' slice sums before the update, so all copies of a slice take the same step."""
         import torch.distributed._symmetric_memory as symm
 
+        # NVLS: reduce through multimem.ld_reduce and all-gather through multimem.st when the buffers are bound to an
+        # NVLink multicast object. The in-switch reduction delivers bf16-rounded sums (as a bf16 all-reduce does), so
+        # this mode is not bit-identical to the unsharded optimizer; it is off unless asked for (HALO_ZERO_NVLS=1).
+        from halo_b200 import env
+
+        self._want_nvls = env.zero_nvls() if nvls is None else bool(nvls)
         self.replicate_group = replicate_group
         self.n_replicas = dist.get_world_size(replicate_group) if replicate_group is not None else 1
         self.group, self.device = group, torch.device(device)
@@ -88,6 +94,9 @@ class FusedShardedAdamW:
         self._build_segments()
         self._p_ptrs = (_lib.c_void_p * self.n_ranks)(*list(self.hp.buffer_ptrs))
         self._g_ptrs = (_lib.c_void_p * self.n_ranks)(*list(self.hg.buffer_ptrs))
+        mc_p, mc_g = int(getattr(self.hp, "multicast_ptr", 0) or 0), int(getattr(self.hg, "multicast_ptr", 0) or 0)
+        self.nvls = bool(self._want_nvls and mc_p and mc_g and self.n_ranks > 1)
+        self._mc_p, self._mc_g = (mc_p, mc_g) if self.nvls else (0, 0)
         self._grad_views = [self.flat_g[o:o + p.numel()].view(p.shape) for (_, p), o in zip(self.named, self.offsets)]
         self._attach_grad_views()
         self.hp.barrier(channel=0)
@@ -137,8 +146,12 @@ class FusedShardedAdamW:
         self.hg.barrier(channel=0)
         L = _lib.lib()
         s = _lib.stream_ptr(self.device)
-        _lib.check(L.halo_rs_sum_norm(self._g_ptrs, _lib.c_int(self.n_ranks), _lib.c_ll(self.lo), _lib.c_ll(self.shard),
-                                      _lib.ptr(self.gsum), _lib.ptr(self.partial), s), "halo_rs_sum_norm")
+        if self.nvls:
+            _lib.check(L.halo_rs_sum_norm_mc(_lib.c_void_p(self._mc_g), _lib.c_ll(self.lo), _lib.c_ll(self.shard),
+                                             _lib.ptr(self.gsum), _lib.ptr(self.partial), s), "halo_rs_sum_norm_mc")
+        else:
+            _lib.check(L.halo_rs_sum_norm(self._g_ptrs, _lib.c_int(self.n_ranks), _lib.c_ll(self.lo), _lib.c_ll(self.shard),
+                                          _lib.ptr(self.gsum), _lib.ptr(self.partial), s), "halo_rs_sum_norm")
         if self.n_replicas > 1:
             # hybrid sharding: the slice's sum over the other shard groups (fp32, one library all-reduce of 1/N of the
             # gradient), and its norm from the completed sum. Every replica of a slice reports the same square, so each
@@ -167,7 +180,7 @@ class FusedShardedAdamW:
             _lib.ptr(self.seg_hash), _lib.ptr(self.seg_wd), _lib.ptr(self.block_start), _lib.c_int(self.n_seg),
             _lib.c_int(self.total_blocks), _lib.c_float(b1), _lib.c_float(b2), _lib.c_float(step_size),
             _lib.c_float(bc2_sqrt), _lib.c_float(self.eps), ctypes.c_ulonglong(self.key), ctypes.c_ulonglong(t),
-            _lib.ptr(grad_scale), _lib.ptr(skip), _lib.stream_ptr(self.device),
+            _lib.ptr(grad_scale), _lib.ptr(skip), _lib.stream_ptr(self.device), _lib.c_void_p(self._mc_p),
         )
         _lib.check(rc, "halo_adam_allgather")
         self.hp.barrier(channel=0)

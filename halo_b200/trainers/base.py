@@ -69,6 +69,9 @@ class Trainer:
     def __init__(self, model, args: TrainingArguments, train_batches: Iterable[PackedBatch] | Callable[[], Iterator],
                  eval_batches: Iterable[PackedBatch] | None = None, device=None, parallel=None,
                  callbacks: list[Callback] | None = None, optimizer=None, parallelism_fingerprint: dict | None = None):
+        if isinstance(parallel, dict):
+            # a pipeline rank is handed its stage's description; the runtime of the stage's replicas is one field of it
+            parallel = parallel.get("parallel")
         self.model, self.args, self.parallel = model, args, parallel
         self.device = torch.device(device or next(model.parameters()).device)
         self.train_batches, self.eval_batches = train_batches, eval_batches
@@ -81,8 +84,23 @@ class Trainer:
         total = args.max_steps if args.max_steps > 0 else 0
         warmup = args.warmup_steps or int(args.warmup_ratio * total)
         self.lr_scheduler = LRScheduler(self.optimizer, args.lr_scheduler_type, total, warmup)
-        self.engine = TrainEngine(model, self.optimizer, self.device, args.max_grad_norm, parallel, self.lr_scheduler,
-                                  loss_fn=self._loss_adapter)
+        spec = getattr(model, "parallel_runtime", None)
+        if isinstance(spec, dict) and spec.get("kind") == "pp":
+            # a pipeline stage: the step is a schedule over the step's micro-batches, run by the stage's own engine (the
+            # next-token loss lives on the last stage; objectives that need more than that are refused by the rules)
+            from halo_b200.entrypoints.script import finish_pipeline_runtime
+
+            if type(self).compute_loss is not Trainer.compute_loss and not getattr(self, "pipeline_ready", False):
+                raise ValueError(f"{type(self).__name__} computes its own loss; under pipeline parallelism only the "
+                                 "next-token objective (SFT / pre-training) runs")
+            self.parallel = spec["parallel"]
+            self.engine = finish_pipeline_runtime(spec, model, self.optimizer, row_len=spec.get("row_len", 0) or self._row_len(),
+                                                  max_grad_norm=args.max_grad_norm, lr_scheduler=self.lr_scheduler)
+            pc = spec["pc"]
+            args.gradient_accumulation_steps = pc.pp_microbatch_count(args.gradient_accumulation_steps)
+        else:
+            self.engine = TrainEngine(model, self.optimizer, self.device, args.max_grad_norm, parallel, self.lr_scheduler,
+                                      loss_fn=self._loss_adapter)
         self.global_step = 0
         self.tokens_seen = 0
         self.fingerprint = parallelism_fingerprint or {"world_size": self.world_size}
@@ -95,6 +113,13 @@ class Trainer:
             import torch.distributed as dist
 
             self.rank = dist.get_rank(parallel.dp_group)   # rank among the trainers of the job
+
+    def _row_len(self) -> int:
+        """Tokens per packed row of the training stream (pipeline messages have one fixed shape)."""
+        src = self.train_batches() if callable(self.train_batches) else self.train_batches
+        first = next(iter(src))
+        first = first[0] if isinstance(first, (list, tuple)) else first
+        return int(first.n_tokens)
 
     # ---- hooks for subclasses --------------------------------------------------------------
     def compute_loss(self, model, batch: PackedBatch, normalizer):
@@ -196,7 +221,7 @@ class Trainer:
                     on_batch = getattr(cb, "on_batch", None)
                     if on_batch is not None:
                         on_batch(self, b)
-            if not shares:
+            if not shares and not getattr(self.engine, "returns_step_total", False):
                 step_loss = step_loss / len(micro)
             self.global_step += 1
             self.after_optimizer_step()

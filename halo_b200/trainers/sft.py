@@ -31,6 +31,8 @@ class SFTTrainer(Trainer):
     """``Trainer`` with the SFT objective. Batches come from the packing collator
     (:func:`halo_b200.data.packing.pack_documents`) with labels already shifted and masked."""
 
+    pipeline_ready = True      # the next-token objective: what a pipeline's last stage computes
+
     def compute_loss(self, model, batch, normalizer):
         coef = self.args.router_aux_loss_coef
         if not coef or not model.cfg.is_moe:

@@ -55,6 +55,11 @@ class ResidentCopySync:
         self.handle = symm.rendezvous(self.arena, group)
         ptrs = list(self.handle.buffer_ptrs)
         self._dst = (_lib.c_void_p * len(self.rollout_ranks))(*[ptrs[r] for r in self.rollout_ranks])
+        # NVLS: when the arena is bound to an NVLink multicast object, one multimem.st per 16 bytes reaches every rank of
+        # the group (the rollout copies and, harmlessly, the other trainers' arenas), so the sender's links carry the
+        # weights once however many rollout GPUs listen
+        mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        self._mc = mc if (mc and env.weight_sync_nvls() and len(self.rollout_ranks) > 1) else 0
         self.staging = (torch.empty(max(self.sizes or [256]), dtype=torch.uint8, device=self.device)
                         if self.rank == src_rank else None)
         self.last_seconds = 0.0
@@ -68,6 +73,11 @@ class ResidentCopySync:
             L = _lib.lib()
             for c, size in enumerate(self.sizes):
                 pack_chunk(self.slots, c, tensors, self.staging)
+                if self._mc:
+                    rc = L.halo_broadcast_bytes_mc(_lib.ptr(self.staging), _lib.c_void_p(self._mc), _lib.c_ll(self.chunk_base[c]),
+                                                   _lib.c_ll((size + 15) // 16 * 16), _lib.stream_ptr(self.device))
+                    _lib.check(rc, "halo_broadcast_bytes_mc")
+                    continue
                 rc = L.halo_broadcast_bytes(_lib.ptr(self.staging), self._dst, _lib.c_int(len(self.rollout_ranks)),
                                             _lib.c_ll(self.chunk_base[c]), _lib.c_ll((size + 15) // 16 * 16),
                                             _lib.stream_ptr(self.device))

@@ -131,6 +131,73 @@ def check_broadcast_and_allreduce(dev, rank, world):
     hs.barrier(channel=0)
 
 
+def check_nvls_forms(dev, rank, world):
+    """The multimem forms (in-switch reduction, multicast stores) against the plain peer forms, where the symmetric
+    buffers are bound to an NVLink multicast object; skipped (and said so) where they are not."""
+    import torch.distributed._symmetric_memory as symm
+
+    from halo_b200.ops import _lib
+    from halo_b200.optim.adamw_bf16 import adamw_bf16_step_reference, param_name_hash, SR_KEY
+    from halo_b200.parallel.zero import FusedShardedAdamW
+
+    n = 1 << 18
+    buf = symm.empty((n,), dtype=torch.float32, device=dev)
+    h = symm.rendezvous(buf, dist.group.WORLD)
+    mc = int(getattr(h, "multicast_ptr", 0) or 0)
+    if not mc:
+        if rank == 0:
+            print("NVLS forms skipped: the symmetric buffers have no multicast binding on this box")
+        return False
+    L = _lib.lib()
+    buf.copy_(torch.arange(n, device=dev, dtype=torch.float32) % 97 + rank)
+    h.barrier(channel=0)
+    out = torch.empty(4096, device=dev)
+    _lib.check(L.halo_allreduce_small_mc(_lib.c_void_p(mc), _lib.ptr(out), _lib.c_int(4096), _lib.stream_ptr(dev)), "allreduce mc")
+    torch.cuda.synchronize()
+    want = (torch.arange(4096, device=dev, dtype=torch.float32) % 97) * world + world * (world - 1) / 2
+    assert torch.equal(out, want), "multimem all-reduce"
+    h.barrier(channel=0)
+    src = (torch.arange(n, device=dev, dtype=torch.float32) * 3 + 1)
+    if rank == 0:
+        _lib.check(L.halo_broadcast_bytes_mc(_lib.ptr(src), _lib.c_void_p(mc), _lib.c_ll(0), _lib.c_ll(n * 4), _lib.stream_ptr(dev)),
+                   "broadcast mc")
+    torch.cuda.synchronize()
+    h.barrier(channel=0)
+    torch.cuda.synchronize()
+    assert torch.equal(buf, src), "multimem broadcast"
+    h.barrier(channel=0)
+    # the sharded optimizer through the switch: gradient sums arrive rounded to bf16, everything else as usual
+    shapes = {"a.weight": (300, 64), "b.norm": (64,), "c.weight": (1000, 33)}
+    g = torch.Generator().manual_seed(3)
+    init = {k: torch.randn(s, generator=g).bfloat16() for k, s in shapes.items()}
+    params = [(k, torch.nn.Parameter(t.clone().to(dev))) for k, t in init.items()]
+    opt = FusedShardedAdamW(params, dist.group.WORLD, dev, lr=1e-2, weight_decay=0.1, nvls=True)
+    assert opt.nvls
+    ref_p = {k: t.clone() for k, t in init.items()}
+    ref_m = {k: torch.zeros_like(t) for k, t in init.items()}
+    ref_v = {k: torch.zeros_like(t) for k, t in init.items()}
+    for step in range(1, 3):
+        grads_all = []
+        for r in range(world):
+            gr = torch.Generator().manual_seed(1000 * step + r)
+            grads_all.append({k: (torch.randn(s, generator=gr) * 0.1).bfloat16() for k, s in shapes.items()})
+        for k, p in params:
+            p.grad = grads_all[rank][k].to(dev)
+        opt.pack_and_reduce()
+        opt.step(torch.tensor([0.5], device=dev), None)
+        torch.cuda.synchronize()
+        b1, b2 = 0.9, 0.999
+        for k in shapes:
+            total = sum(ga[k].float() for ga in grads_all).bfloat16().float()      # what the switch hands back
+            adamw_bf16_step_reference(ref_p[k], total, ref_m[k], ref_v[k], beta1=b1, beta2=b2, step_size=1e-2 / (1 - b1**step),
+                                      bc2_sqrt=(1 - b2**step) ** 0.5, eps=1e-8, wd_factor=1.0 - 1e-2 * (0.1 if len(shapes[k]) > 1 else 0.0),
+                                      key=SR_KEY, step=step, name_hash=param_name_hash(k), grad_scale=0.5)
+        for k, p in params:
+            # the switch may add the ranks' values in another order than the reference: compare within a bf16 ulp or two
+            close(p.detach().cpu(), ref_p[k], 2e-2, f"sharded optimizer through the switch: {k}, step {step}")
+    return True
+
+
 def check_context_parallel(dev, rank, world):
     """Attention of this rank's chunk of a packed row (K/V of straddling documents pulled from peers) against
     the flash kernel run on the whole row by one GPU, forward and backward."""
@@ -229,12 +296,13 @@ def main():
         _lib.raise_on_status(dev)
     check_fused_optimizer(dev, rank, world)
     check_broadcast_and_allreduce(dev, rank, world)
+    nvls = check_nvls_forms(dev, rank, world)
     check_context_parallel(dev, rank, world)
     check_tensor_parallel_collectives(dev, rank, world)
     _lib.raise_on_status(dev)
     dist.barrier()
     if rank == 0:
-        print("CHECKS PASSED")
+        print(f"CHECKS PASSED (world {world}; NVLS forms {'checked' if nvls else 'not available'})")
     dist.destroy_process_group()
 
 

@@ -162,3 +162,46 @@ def test_stages_save_one_ordinary_checkpoint(tmp_path):
     files = set(index["weight_map"].values())
     assert any(f.startswith("model-stage000-") for f in files) and any(f.startswith("model-stage001-") for f in files)
     assert all(os.path.isfile(os.path.join(d, f)) for f in files) and os.path.isfile(os.path.join(d, "config.json"))
+
+
+def test_pipeline_times_expert_parallel_through_the_entry_point(tmp_path):
+    """``pipeline_parallel_size: 2`` with ``expert_parallel_size: 2`` on four CPU ranks through the launcher (the layout
+    of the 8-GPU PP2 x EP4 runs, halved): stages load only their layers, the step runs the 1F1B schedule over the
+    step's micro-batches, the two replicas of a stage shard the experts, and the loss goes down as in a single process."""
+    import os
+    import re
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def run(name, extra, n):
+        cfg = tmp_path / f"{name}.yaml"
+        cfg.write_text("model_preset: tiny-moe\ninit_from_scratch: true\ndataset_format: synthetic\npacked_row_length: 128\n"
+                       "max_steps: 6\nlearning_rate: 3.0e-3\nlr_scheduler_type: constant\noptim: adamw_torch\nweight_decay: 0.0\n"
+                       f"gradient_accumulation_steps: 2\noutput_dir: {tmp_path}/{name}\nlogging_steps: 1\n" + extra)
+        r = subprocess.run([sys.executable, "-m", "halo_b200.cli", "launch", "sft", str(cfg), "-n", str(n), "--port", "29731"],
+                           cwd=root, capture_output=True, text=True, timeout=600,
+                           env=dict(os.environ, CUDA_VISIBLE_DEVICES="", NVLINK_DOMAIN_SIZE="2"))
+        out = r.stdout + r.stderr
+        assert r.returncode == 0, out[-4000:]
+        return [float(x) for x in re.findall(r"step \d+ loss ([0-9.]+)", out)], out
+
+    pp, out = run("pp2ep2", "pipeline_parallel_size: 2\nexpert_parallel_size: 2\nmax_grad_norm: 0.0\n", 4)
+    assert len(pp) >= 6, out[-3000:]
+    assert "pipeline stage 0 of 2" in out and "pipeline stage 1 of 2" in out
+    flat, out2 = run("ep2", "expert_parallel_size: 2\nmax_grad_norm: 0.0\n", 2)
+    # the same two data-parallel replicas, the same rows and the same initialisation with and without the pipeline:
+    # the first step's loss is the same number, the curves stay together (the optimizer sees the same gradients up to
+    # one common factor, which Adam divides out)
+    assert abs(pp[0] - flat[0]) < 2e-4, (pp[:2], flat[:2])
+    assert max(abs(a - b) for a, b in zip(pp[::2][:6], flat[::2][:6])) < 2e-2, (pp, flat)
+    # the stages wrote one ordinary checkpoint: every tensor of the unsplit model, experts gathered
+    import json
+
+    idx = json.load(open(tmp_path / "pp2ep2" / "final" / "model.safetensors.index.json"))["weight_map"]
+    ref = json.load(open(tmp_path / "ep2" / "final" / "model.safetensors.index.json"))["weight_map"] \
+        if os.path.isfile(tmp_path / "ep2" / "final" / "model.safetensors.index.json") else None
+    assert any(k.startswith("model.embed_tokens") for k in idx) and any(k.startswith("lm_head") or k.startswith("model.norm") for k in idx)
+    if ref is not None:
+        assert set(idx) == set(ref)
