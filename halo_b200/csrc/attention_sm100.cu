@@ -318,7 +318,6 @@ struct BwdParams {
     int Hq, Hkv;
     float scale;
     int* status;
-    long long* phase_clocks;   // optional [32]: cycles one CTA's MMA thread and one element-wise thread spent per phase (diagnostic)
 };
 
 constexpr int kBwdThreads = 192;
@@ -780,9 +779,13 @@ __device__ __forceinline__ void ew_bar_sync(int group) {   // named barrier of o
     asm volatile("bar.sync %0, %1;" ::"r"(2 + group), "n"(kBwd2Ew) : "memory");
 }
 
-// K, V (32 KiB each), 2 x P^T, 2 x dS^T (128 x 64, 16 KiB each), 3 stages of (Q, dO) 64 x 128 (16 KiB each)
-constexpr int kBwdKv2Stages = 3;
-constexpr int kBwdKv2Tiles = 2 * kTileBytes + 4 * kHalfTile + kBwdKv2Stages * 2 * kHalfTile;     // 229,376
+// K, V (32 KiB each), 5 stages of (Q, dO) 64 x 128 (16 KiB each). P^T and dS^T never touch shared memory: every
+// element-wise thread writes its row of them (bf16 pairs) with tcgen05.st over the tensor-memory columns its scores
+// came from, and the dV / dK products take their A operand from there. (Measured per step of this kernel before:
+// the MMA thread spent 2,100 of 3,700 cycles blocked in issue, because operand fetches, the element-wise stores and the
+// TMA writes share one 128-byte-per-clock shared-memory port.)
+constexpr int kBwdKv2Stages = 5;
+constexpr int kBwdKv2Tiles = 2 * kTileBytes + kBwdKv2Stages * 2 * kHalfTile;     // 229,376
 constexpr int kBwdKv2Smem = kBwdKv2Tiles + 2048;                                                 // barriers, scalars, statistics
 
 __global__ void __launch_bounds__(kBwd2Threads, 1)
@@ -797,8 +800,7 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         return;
     }
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_b2 + kBwdKv2Tiles);
-    enum { kKv = 0, kQFull = 1, kQEmpty = 4, kSFull = 7, kSFree = 9, kPReady = 11, kDsReady = 13, kPtFree = 15, kDsFree = 17,
-           kAccDone = 19, kNumBars = 20 };
+    enum { kKv = 0, kQFull = 1, kQEmpty = 6, kSFull = 11, kPReady = 13, kDsReady = 15, kAccDone = 17, kNumBars = 18 };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + kNumBars + 1);
     float* s_lse = reinterpret_cast<float*>(bars + kNumBars + 2);          // [2 groups][64]
@@ -806,8 +808,7 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     auto bar = [&](int i) { return smem_u32(&bars[i]); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t sK = base, sV = base + kTileBytes, sPT = base + 2 * kTileBytes, sDS = sPT + 2 * kHalfTile,
-                   sQdO = sDS + 2 * kHalfTile;
+    const uint32_t sK = base, sV = base + kTileBytes, sQdO = base + 2 * kTileBytes;
     const int kv_head = blockIdx.x;
     const int group = p.Hq / p.Hkv;
     const BwdKvWork w = reinterpret_cast<const BwdKvWork*>(p.work)[blockIdx.y];
@@ -816,7 +817,7 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         for (int i = 0; i < kNumBars; ++i) {
-            const bool many = (i >= kSFree && i < kPtFree);        // arrived on by every warp of one element-wise group
+            const bool many = (i >= kPReady && i < kAccDone);      // arrived on by every warp of one element-wise group
             mbar_init(bar(i), many ? kBwd2EwWarps : 1);
         }
         mbar_fence_init();
@@ -829,7 +830,9 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tm0 = *tmem_slot;
-    // S^T[b] at 128 b, dP^T[b] at 128 b + 64, dV at 256, dK at 384
+    // S^T[b] at 128 b, dP^T[b] at 128 b + 64, dV at 256, dK at 384. P^T[b] is written over S^T[b] and dS^T[b] over
+    // dP^T[b]: the 32 queries of column half h as 16 packed columns at offset 32 h, i.e. inside the columns the writing
+    // thread has itself just read, so the two halves' warps need no order between them.
     const uint32_t tDV = tm0 + 256, tDK = tm0 + 384;
 
     if (warp == 0) {
@@ -858,17 +861,12 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             constexpr uint32_t idesc_st = make_idesc_bf16(128, 64, 0, 0);   // [keys x q] = K Q^T, V dO^T
             constexpr uint32_t idesc_acc = make_idesc_bf16(128, 128, 0, 1); // [keys x hd] = P^T dO, dS^T Q
             bool ok = mbar_wait(bar(kKv), 0, abort_flag, p.status);
-            const bool prof = p.phase_clocks != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
-            long long pc[8] = {0, 0, 0, 0, 0, 0, 0, 0}, last = clock64();
-#define MMA_TICK(i) if (prof) { const long long now = clock64(); pc[i] += now - last; last = now; }
             auto issue_s = [&](int j) -> bool {
                 const int b = j & 1, st = j % kBwdKv2Stages;
                 const uint32_t sQ = sQdO + st * 2 * kHalfTile, sdO = sQ + kHalfTile;
-                MMA_TICK(0)
                 if (!mbar_wait(bar(kQFull + st), (j / kBwdKv2Stages) & 1, abort_flag, p.status)) return false;   // Q, dO of step j
-                MMA_TICK(1)
-                if (!mbar_wait(bar(kSFree + b), ((j >> 1) & 1) ^ 1u, abort_flag, p.status)) return false;       // S^T / dP^T[b] read
-                MMA_TICK(2)
+                // S^T / dP^T[b] are free: their last readers are the dV / dK products of step j - 2, which this thread
+                // issued before this point, and the tensor pipe runs one thread's products in order
                 tc_fence_after();
                 const uint32_t tS = tm0 + 128 * b, tDP = tS + 64;
 #pragma unroll
@@ -884,7 +882,6 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     tc_mma_f16(tDP, make_smem_desc(sV + offa, 16, 1024), make_smem_desc(sdO + offb, 16, 1024), idesc_st, ks != 0);
                 }
                 tc_commit(bar(kSFull + b));
-                MMA_TICK(3)
                 return true;
             };
             if (ok && n_iter > 0) ok = issue_s(0);
@@ -892,33 +889,22 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 const int b = it & 1, st = it % kBwdKv2Stages;
                 const uint32_t sQ = sQdO + st * 2 * kHalfTile, sdO = sQ + kHalfTile;
                 if (it + 1 < n_iter && !issue_s(it + 1)) break;
-                MMA_TICK(0)
                 if (!mbar_wait(bar(kPReady + b), (it >> 1) & 1, abort_flag, p.status)) break;      // P^T[b] written
-                MMA_TICK(4)
                 tc_fence_after();
+                const uint32_t tPT = tm0 + 128 * b, tDST = tPT + 64;
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks)
-                    tc_mma_f16(tDV, make_smem_desc(sPT + b * kHalfTile + ks * 32, 16, 1024),
-                               make_smem_desc(sdO + ks * 2048, 8192, 1024), idesc_acc, (it | ks) != 0);
-                tc_commit(bar(kPtFree + b));
-                MMA_TICK(5)
+                for (int ks = 0; ks < 4; ++ks)   // 16 queries = 8 packed columns per step; queries 32.. sit at column 32
+                    tc_mma_f16_tmem_a(tDV, tPT + (ks >> 1) * 32 + (ks & 1) * 8,
+                                      make_smem_desc(sdO + ks * 2048, 8192, 1024), idesc_acc, (it | ks) != 0);
                 if (!mbar_wait(bar(kDsReady + b), (it >> 1) & 1, abort_flag, p.status)) break;     // dS^T[b] written
-                MMA_TICK(6)
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)
-                    tc_mma_f16(tDK, make_smem_desc(sDS + b * kHalfTile + ks * 32, 16, 1024),
-                               make_smem_desc(sQ + ks * 2048, 8192, 1024), idesc_acc, (it | ks) != 0);
-                tc_commit(bar(kDsFree + b));
+                    tc_mma_f16_tmem_a(tDK, tDST + (ks >> 1) * 32 + (ks & 1) * 8,
+                                      make_smem_desc(sQ + ks * 2048, 8192, 1024), idesc_acc, (it | ks) != 0);
                 tc_commit(bar(kQEmpty + st));
                 if (it == n_iter - 1) tc_commit(bar(kAccDone));
-                MMA_TICK(7)
             }
-            if (prof) {
-                for (int i = 0; i < 8; ++i) p.phase_clocks[i] = pc[i];
-                p.phase_clocks[30] = n_iter;
-            }
-#undef MMA_TICK
         }
     } else {
         const int g = (warp - 2) >> 3;                            // element-wise group: steps with it % 2 == g, copy g of everything
@@ -930,7 +916,7 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const float c = p.scale * kLog2e;
         const long long key_abs = (long long)w.kv0 + key;
         const uint32_t tS = tm0 + 128 * g + lane_base + c0, tDP = tS + 64;
-        const uint32_t myPT = sPT + g * kHalfTile, myDS = sDS + g * kHalfTile;
+        const uint32_t tPT = tm0 + 128 * g + lane_base + c0, tDST = tPT + 64;   // this thread's 16 packed columns of P^T / dS^T
         float* lse_g = s_lse + g * 64;
         float* delta_g = s_delta + g * 64;
         bool ok = true;
@@ -944,9 +930,6 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             return in ? p.delta[(long long)h * p.T + qa] : 0.f;
         };
         float stat = fetch_stat(g);
-        const bool prof = p.phase_clocks != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && warp == 2 && lane == 0;
-        long long pc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0}, last = clock64();
-#define EW_TICK(i) if (prof) { const long long now = clock64(); pc[i] += now - last; last = now; }
         for (int it = g; it < n_iter; it += 2) {
             const int k = it >> 1;                                // this group's step count: parity of its barriers
             const int qr = w.q_begin + (it / group) * 64;
@@ -958,17 +941,12 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             stat = fetch_stat(it + 2);                            // in flight during this step
             ew_bar_sync(g);
             if (!ok) continue;
-            EW_TICK(0)
             if (!mbar_wait(bar(kSFull + g), k & 1, abort_flag, p.status)) { ok = false; continue; }
-            EW_TICK(1)
             tc_fence_after();
             uint32_t sr[32], dr[32];
             tmem_ld_32x32(tS, sr);
             tmem_ld_32x32(tDP, dr);
             tmem_ld_wait();
-            tc_fence_before();
-            EW_TICK(2)
-            warp_arrive(bar(kSFree + g), lane);                         // S^T / dP^T[g] may be overwritten by step it + 2
             // Only the tiles on the diagonal need the causal mask; everywhere else the loop carries no compare at all.
             // Column i of this thread is query qr + c0 + i; it sees key `key_abs` when i >= lim.
             const bool need_mask = (qr < w.kv0 + 128);
@@ -984,42 +962,29 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
                 for (int i = 0; i < 32; ++i) pv[i] = fast_exp2(__uint_as_float(sr[i]) * c - lse_g[c0 + i]);
             }
-            // P^T[g] (bf16, K-major A operand: one 128-byte row of 64 queries per key) once dV of step it - 2 has read it
-            EW_TICK(3)
-            if (!mbar_wait(bar(kPtFree + g), (k & 1) ^ 1u, abort_flag, p.status)) { ok = false; continue; }
-            EW_TICK(4)
+            // P^T[g]: this thread's 32 probabilities as 16 packed columns, over the score columns it has just read
+            {
+                uint32_t pk[16];
 #pragma unroll
-            for (int q8 = 0; q8 < 4; ++q8) {
-                const uint32_t a = myPT + swz_off(key, c0 + q8 * 8);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a),
-                             "r"(pack_bf16(pv[q8 * 8], pv[q8 * 8 + 1])), "r"(pack_bf16(pv[q8 * 8 + 2], pv[q8 * 8 + 3])),
-                             "r"(pack_bf16(pv[q8 * 8 + 4], pv[q8 * 8 + 5])), "r"(pack_bf16(pv[q8 * 8 + 6], pv[q8 * 8 + 7]))
-                             : "memory");
+                for (int i = 0; i < 16; ++i) pk[i] = pack_bf16(pv[2 * i], pv[2 * i + 1]);
+                tmem_st_32x16(tPT, pk);
+                tmem_st_wait();
             }
-            EW_TICK(5)
-            fence_proxy_async_smem();
-            EW_TICK(6)
+            tc_fence_before();
             warp_arrive(bar(kPReady + g), lane);
             // dS^T = P^T * (dP^T - delta) * scale
 #pragma unroll
             for (int i = 0; i < 32; ++i) pv[i] = pv[i] * (__uint_as_float(dr[i]) - delta_g[c0 + i]) * p.scale;
-            EW_TICK(7)
-            if (!mbar_wait(bar(kDsFree + g), (k & 1) ^ 1u, abort_flag, p.status)) { ok = false; continue; }
-            EW_TICK(8)
+            {
+                uint32_t pk[16];
 #pragma unroll
-            for (int q8 = 0; q8 < 4; ++q8) {
-                const uint32_t a = myDS + swz_off(key, c0 + q8 * 8);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a),
-                             "r"(pack_bf16(pv[q8 * 8], pv[q8 * 8 + 1])), "r"(pack_bf16(pv[q8 * 8 + 2], pv[q8 * 8 + 3])),
-                             "r"(pack_bf16(pv[q8 * 8 + 4], pv[q8 * 8 + 5])), "r"(pack_bf16(pv[q8 * 8 + 6], pv[q8 * 8 + 7]))
-                             : "memory");
+                for (int i = 0; i < 16; ++i) pk[i] = pack_bf16(pv[2 * i], pv[2 * i + 1]);
+                tmem_st_32x16(tDST, pk);
+                tmem_st_wait();
             }
-            fence_proxy_async_smem();
+            tc_fence_before();
             warp_arrive(bar(kDsReady + g), lane);
-            EW_TICK(9)
         }
-        if (prof) for (int i = 0; i < 10; ++i) p.phase_clocks[10 + i] = pc[i];
-#undef EW_TICK
         // the accumulators: group 0 stores dK, group 1 stores dV (each thread one row, 64 of its 128 columns)
         if (ok && mbar_wait(bar(kAccDone), 0, abort_flag, p.status)) {
             tc_fence_after();
@@ -1058,9 +1023,9 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
 }
 
-// Q, dO (32 KiB each), 2 x dS (128 x 64, 16 KiB each), 4 stages of (K, V) 64 x 128 (16 KiB each)
-constexpr int kBwdQ2Stages = 4;
-constexpr int kBwdQ2Tiles = 2 * kTileBytes + 2 * kHalfTile + kBwdQ2Stages * 2 * kHalfTile;   // 229,376
+// Q, dO (32 KiB each), 5 stages of (K, V) 64 x 128 (16 KiB each); dS lives in tensor memory (see the dK/dV kernel)
+constexpr int kBwdQ2Stages = 5;
+constexpr int kBwdQ2Tiles = 2 * kTileBytes + kBwdQ2Stages * 2 * kHalfTile;   // 229,376
 constexpr int kBwdQ2Smem = kBwdQ2Tiles + 512;
 
 __global__ void __launch_bounds__(kBwd2Threads, 1)
@@ -1075,20 +1040,20 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         return;
     }
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_q2 + kBwdQ2Tiles);
-    enum { kQ = 0, kKvFull = 1, kKvEmpty = 5, kSFull = 9, kSFree = 11, kDsReady = 13, kDsFree = 15, kAccDone = 17, kNumBars = 18 };
+    enum { kQ = 0, kKvFull = 1, kKvEmpty = 6, kSFull = 11, kDsReady = 13, kAccDone = 15, kNumBars = 16 };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + kNumBars + 1);
     auto bar = [&](int i) { return smem_u32(&bars[i]); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t sQ = base, sdO = base + kTileBytes, sDS = base + 2 * kTileBytes, sKV = sDS + 2 * kHalfTile;
+    const uint32_t sQ = base, sdO = base + kTileBytes, sKV = base + 2 * kTileBytes;
     const int head = blockIdx.x;
     const int kv_head = head / (p.Hq / p.Hkv);
     const BwdQWork w = reinterpret_cast<const BwdQWork*>(p.work)[blockIdx.y];
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
-        for (int i = 0; i < kNumBars; ++i) mbar_init(bar(i), (i >= kSFree && i < kDsFree) ? kBwd2EwWarps : 1);
+        for (int i = 0; i < kNumBars; ++i) mbar_init(bar(i), (i >= kDsReady && i < kAccDone) ? kBwd2EwWarps : 1);
         mbar_fence_init();
     }
     if (warp == 1) {
@@ -1130,8 +1095,7 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 const int b = j & 1, st = j % kBwdQ2Stages;
                 const uint32_t sK = sKV + st * 2 * kHalfTile, sV = sK + kHalfTile;
                 if (!mbar_wait(bar(kKvFull + st), (j / kBwdQ2Stages) & 1, abort_flag, p.status)) return false;
-                if (!mbar_wait(bar(kSFree + b), ((j >> 1) & 1) ^ 1u, abort_flag, p.status)) return false;
-                tc_fence_after();
+                tc_fence_after();       // S / dP[b]: last read by the dQ product of step j - 2, issued before this point
                 const uint32_t tS = tm0 + 128 * b, tDP = tS + 64;
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
@@ -1155,11 +1119,11 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 if (j + 1 < w.n_kv && !issue_s(j + 1)) break;
                 if (!mbar_wait(bar(kDsReady + b), (j >> 1) & 1, abort_flag, p.status)) break;
                 tc_fence_after();
+                const uint32_t tDS = tm0 + 128 * b + 64;      // dS[b], written over dP[b]
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)
-                    tc_mma_f16(tDQ, make_smem_desc(sDS + b * kHalfTile + ks * 32, 16, 1024),
-                               make_smem_desc(sK + ks * 2048, 8192, 1024), idesc_dq, (j | ks) != 0);
-                tc_commit(bar(kDsFree + b));
+                    tc_mma_f16_tmem_a(tDQ, tDS + (ks >> 1) * 32 + (ks & 1) * 8,
+                                      make_smem_desc(sK + ks * 2048, 8192, 1024), idesc_dq, (j | ks) != 0);
                 tc_commit(bar(kKvEmpty + st));
                 if (j == w.n_kv - 1) tc_commit(bar(kAccDone));
             }
@@ -1176,7 +1140,6 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const float lse2 = in ? p.lse[(long long)head * p.T + q_abs] * kLog2e : INFINITY;
         const float dl = in ? p.delta[(long long)head * p.T + q_abs] : 0.f;
         const uint32_t tS = tm0 + 128 * g + lane_base + c0, tDP = tS + 64;
-        const uint32_t myDS = sDS + g * kHalfTile;
         bool ok = true;
         for (int j = g; j < w.n_kv; j += 2) {
             const int k = j >> 1;
@@ -1186,8 +1149,6 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             tmem_ld_32x32(tS, sr);
             tmem_ld_32x32(tDP, dr);
             tmem_ld_wait();
-            tc_fence_before();
-            warp_arrive(bar(kSFree + g), lane);
             // column i of this thread is key k0 + i; the row sees it when i <= lim. Off the diagonal no compare is made.
             const int k0 = w.kv0 + j * 64 + c0;
             const bool need_mask = (k0 + 32 > w.q0);
@@ -1204,16 +1165,14 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 for (int i = 0; i < 32; ++i)
                     pv[i] = fast_exp2(__uint_as_float(sr[i]) * c - lse2) * (__uint_as_float(dr[i]) - dl) * p.scale;
             }
-            if (!mbar_wait(bar(kDsFree + g), (k & 1) ^ 1u, abort_flag, p.status)) { ok = false; break; }
+            {
+                uint32_t pk[16];
 #pragma unroll
-            for (int q8 = 0; q8 < 4; ++q8) {
-                const uint32_t a = myDS + swz_off(row, c0 + q8 * 8);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a),
-                             "r"(pack_bf16(pv[q8 * 8], pv[q8 * 8 + 1])), "r"(pack_bf16(pv[q8 * 8 + 2], pv[q8 * 8 + 3])),
-                             "r"(pack_bf16(pv[q8 * 8 + 4], pv[q8 * 8 + 5])), "r"(pack_bf16(pv[q8 * 8 + 6], pv[q8 * 8 + 7]))
-                             : "memory");
+                for (int i = 0; i < 16; ++i) pk[i] = pack_bf16(pv[2 * i], pv[2 * i + 1]);
+                tmem_st_32x16(tDP, pk);         // this thread's 16 packed columns of dS[g], over the dP columns it has just read
+                tmem_st_wait();
             }
-            fence_proxy_async_smem();
+            tc_fence_before();
             warp_arrive(bar(kDsReady + g), lane);
         }
         // the accumulator: every thread of group g stores 32 columns of its row (group, half -> which 32 of the 128)
@@ -1844,11 +1803,6 @@ int halo_attn_fwd2_occupancy() {
     return n;
 }
 
-// Diagnostic: a device array of 32 int64 that the dK/dV kernel's first CTA fills with the cycles its MMA thread ([0..7])
-// and one element-wise thread ([10..19]) spent in each phase of their loops, [30] = steps. Null (the default) = off.
-static long long* g_bwd_phase_clocks = nullptr;
-void halo_attn_bwd_phase_clocks(long long* dev_array) { g_bwd_phase_clocks = dev_array; }
-
 // delta: [Hq, T] fp32 scratch. kv_work: n_kv_tiles {kv0, q_begin, n_q(64-row sub-tiles), q_end};
 // q_work: n_q_tiles {q0, kv0, n_kv(64-key sub-tiles), q_end}.
 int halo_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
@@ -1882,7 +1836,7 @@ int halo_attn_bwd(const void* q, const void* k, const void* v, const void* o, co
         if (e && atoi(e) == 1) variant = 1;
         cfg = true;
     }
-    BwdParams p{kv_work, lse, delta, dq, dk, dv, ld_dq, ld_dk, ld_dv, T, Hq, Hkv, scale, status, g_bwd_phase_clocks};
+    BwdParams p{kv_work, lse, delta, dq, dk, dv, ld_dq, ld_dk, ld_dv, T, Hq, Hkv, scale, status};
     if (n_kv_tiles > 0) {
         if (variant == 2) attn_bwd_dkdv2_kernel<<<dim3(Hkv, n_kv_tiles), kBwd2Threads, kBwdKv2Smem, s>>>(tq64, tk, tv, tdo64, p);
         else attn_bwd_dkdv_kernel<<<dim3(Hkv, n_kv_tiles), kBwdThreads, kBwdKvSmem, s>>>(tq64, tk, tv, tdo64, p);

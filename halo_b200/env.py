@@ -34,7 +34,7 @@ CATALOGUE = {
     "HALO_ROLLOUT_WAIT_SECONDS": "how long a trainer waits for a round from its rollout rank",
     "HALO_GEMM_PAIR": "CTA-pair GEMM: 1 where it wins (default), 0 never, 2 everywhere",
     "HALO_ATTN_BWD_VARIANT": "backward attention kernels (2 = double-buffered score tiles and eight element-wise warps, the default; 1 = the first form)",
-    "HALO_ATTN_FWD_VARIANT": "forward attention kernel form (2 = output kept in TMEM, the default)",
+    "HALO_ATTN_FWD_VARIANT": "forward attention kernel form (3 = output and probabilities kept in TMEM, the default; 2 = probabilities through shared memory; 1 = 128-key tiles)",
     "HALO_WEIGHT_SYNC_NVLS": "trainer -> rollout weight push through NVLink multicast stores when the arena supports it (default 1)",
     "HALO_ZERO_NVLS": "sharded optimizer: reduce and all-gather through NVLink multicast (multimem) when the buffers support it (default 0: plain peer loads / stores, bit-identical to the unsharded optimizer)",
     "HALO_MOE_FUSED": "expert products with the token movement inside the GEMM kernels (1, default) or as separate push / pull kernels (0)",

@@ -23,7 +23,7 @@ HEAD_DIM = 128
 # 1: 128-key tiles, output rescaled in registers, one CTA per SM
 # 2: 64-key tiles, output accumulated in TMEM with lazy rescale, two CTAs per SM
 # 3: as 2, with the probabilities written to tensor memory (tcgen05.st) and read from there by the P V product
-FWD_VARIANT = int(os.environ.get("HALO_ATTN_FWD_VARIANT", "2"))
+FWD_VARIANT = int(os.environ.get("HALO_ATTN_FWD_VARIANT", "3"))
 
 
 def _launch_fwd(L, q, k, v, o, lse, plan, T, n_heads, n_kv_heads, scale, dev):
