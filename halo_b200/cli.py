@@ -1,6 +1,8 @@
 """``python -m halo_b200.cli launch <method> <config.yaml> -n N [--key=value ...]`` builds the torchrun
 (or plain python) command line for a training method; ``run <tool>`` starts a tool module
-(the role of halo/cli.py:1-349; single node only)."""
+(the role of halo/cli.py:1-349). One node by default; ``--nnodes M --node-rank R --rdzv-endpoint host:port`` (or the
+``HALO_NNODES`` / ``HALO_NODE_RANK`` / ``HALO_RDZV_ENDPOINT`` variables a cluster launcher exports) starts one node's
+share of a multi-node job: the same line on every node, differing only in the node rank."""
 
 from __future__ import annotations
 
@@ -45,11 +47,22 @@ TOOLS = {
 
 
 def build_command(method: str, config: str, nproc: int, overrides: list[str], port: int = 29500,
-                  numa_binding: bool = False) -> list[str]:
+                  numa_binding: bool = False, nnodes: int = 1, node_rank: int = 0, rdzv_endpoint: str = "") -> list[str]:
     if method not in METHODS:
         raise SystemExit(f"unknown method {method!r}; choose from {', '.join(sorted(METHODS))}")
     module = METHODS[method]
     extra = [f"--preference_loss={method}"] if method in ("dpo", "kto", "smpo") else []
+    if nnodes > 1:
+        if not rdzv_endpoint or ":" not in rdzv_endpoint:
+            raise SystemExit("a multi-node launch needs --rdzv-endpoint host:port (the first node's address, reachable by all)")
+        if not 0 <= node_rank < nnodes:
+            raise SystemExit(f"--node-rank {node_rank} is outside 0..{nnodes - 1}")
+        host, _, rport = rdzv_endpoint.rpartition(":")
+        cmd = [sys.executable, "-m", "torch.distributed.run", f"--nnodes={nnodes}", f"--node-rank={node_rank}",
+               f"--nproc-per-node={max(nproc, 1)}", "--master-addr", host, "--master-port", rport]
+        if numa_binding:
+            cmd += ["--numa-binding", "node"]
+        return cmd + ["-m", module, config, *extra, *overrides]
     if nproc <= 1:
         return [sys.executable, "-m", module, config, *extra, *overrides]
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
@@ -69,11 +82,15 @@ def main(argv=None) -> int:
     la.add_argument("--port", type=int, default=29500)
     la.add_argument("--numa-binding", action="store_true")
     la.add_argument("--dry-run", action="store_true")
+    la.add_argument("--nnodes", type=int, default=int(os.environ.get("HALO_NNODES", "1")))
+    la.add_argument("--node-rank", type=int, default=int(os.environ.get("HALO_NODE_RANK", "0")))
+    la.add_argument("--rdzv-endpoint", default=os.environ.get("HALO_RDZV_ENDPOINT", ""))
     ru = sub.add_parser("run")
     ru.add_argument("tool")
     args, rest = ap.parse_known_args(argv)
     if args.cmd == "launch":
-        cmd = build_command(args.method, args.config, args.nproc, rest, args.port, args.numa_binding)
+        cmd = build_command(args.method, args.config, args.nproc, rest, args.port, args.numa_binding, args.nnodes,
+                            args.node_rank, args.rdzv_endpoint)
     else:
         if args.tool not in TOOLS:
             raise SystemExit(f"unknown tool {args.tool!r}; choose from {', '.join(sorted(TOOLS))}")

@@ -246,6 +246,8 @@ class GRPOArguments:
     zero_gradient_round_limit: int = 0
     rollout_backend: Literal["in_process", "vllm", "sglang", "resident_copy"] = "resident_copy"
     rollout_gpus: int = 0
+    rollout_server_url: str = ""                # vllm / sglang: http://host:port of the generation server
+    rollout_served_model: str = ""              # the model name the server answers to (default: model_name_or_path)
     weight_sync_chunk_mb: int = 1024
     environment_type: str = ""                  # e.g. "qa", "code", "tool_qa": rollouts are episodes of this environment over the dataset's tasks
     environment_options: dict | None = None

@@ -47,11 +47,45 @@ def in_process_source(model, model_args, data_args, train_args, grpo_args, pc):
     return sampling_source(model, model_args, data_args, train_args, grpo_args, pc.data_parallel_rank, pc.data_parallel_size)
 
 
+def prompts_and_reward(vocab_size: int, model_args, data_args, train_args, grpo_args, consumer_rank: int, n_consumers: int):
+    """``(prompts, reward_fn, tokenizer or None)`` of single-turn sampled rollouts for one consumer."""
+    from halo_b200.trainers.grpo.online import text_reward, token_below_reward, token_match_reward
+
+    tokenizer = None
+    if data_args.dataset_path:
+        rows = [json.loads(l) for l in open(data_args.dataset_path) if l.strip()]
+        rows = rows[consumer_rank::max(1, n_consumers)]
+        if rows and "prompt_ids" not in rows[0]:
+            from halo_b200.entrypoints.script import load_tokenizer
+
+            tokenizer = load_tokenizer(model_args)
+            for r in rows:
+                r["prompt_ids"] = tokenizer(r["prompt"])["input_ids"]
+        prompts = rows
+    else:
+        rng = np.random.default_rng(train_args.seed + consumer_rank)
+        vocab = data_args.synthetic_vocab or vocab_size
+        prompts = [rng.integers(0, vocab, size=int(rng.integers(4, min(32, grpo_args.max_prompt_length) + 1))) for _ in range(256)]
+    if grpo_args.synthetic_reward_token >= 0:
+        reward = token_match_reward(grpo_args.synthetic_reward_token)
+    elif grpo_args.synthetic_reward_below >= 0:
+        reward = token_below_reward(grpo_args.synthetic_reward_below)
+    elif grpo_args.reward_terms:
+        from halo_b200.entrypoints.script import load_tokenizer
+        from halo_b200.rewards.terms import RewardComposer, parse_terms
+
+        tokenizer = tokenizer or load_tokenizer(model_args)
+        reward = text_reward(tokenizer, RewardComposer(parse_terms(grpo_args.reward_terms)))
+    else:
+        raise ValueError("sampled rollouts need reward_terms (text prompts) or synthetic_reward_token")
+    return prompts, reward, tokenizer
+
+
 def sampling_source(model, model_args, data_args, train_args, grpo_args, consumer_rank: int, n_consumers: int):
     """A source that samples from ``model`` for consumer ``consumer_rank`` of ``n_consumers``. Prompts: a JSONL of
     {"prompt_ids": [...]} or {"prompt": "..."} rows (each consumer takes its stride), else random ones."""
     from halo_b200.inference.generate import SamplingParams
-    from halo_b200.trainers.grpo.online import OnPolicyRolloutSource, text_reward, token_below_reward, token_match_reward
+    from halo_b200.trainers.grpo.online import OnPolicyRolloutSource
 
     if grpo_args.environment_type:
         from halo_b200.entrypoints.script import load_tokenizer
@@ -70,39 +104,41 @@ def sampling_source(model, model_args, data_args, train_args, grpo_args, consume
         return EnvironmentRolloutSource(model, load_tokenizer(model_args), tasks, grpo_args.environment_type, grpo_args.num_generations,
                                         sampling, grpo_args.prompts_per_round, composer, grpo_args.environment_options,
                                         seed=train_args.seed + consumer_rank)
-    tokenizer = None
-    if data_args.dataset_path:
-        rows = [json.loads(l) for l in open(data_args.dataset_path) if l.strip()]
-        rows = rows[consumer_rank::max(1, n_consumers)]
-        if rows and "prompt_ids" not in rows[0]:
-            from halo_b200.entrypoints.script import load_tokenizer
-
-            tokenizer = load_tokenizer(model_args)
-            for r in rows:
-                r["prompt_ids"] = tokenizer(r["prompt"])["input_ids"]
-        prompts = rows
-    else:
-        rng = np.random.default_rng(train_args.seed + consumer_rank)
-        vocab = data_args.synthetic_vocab or model.cfg.vocab_size
-        prompts = [rng.integers(0, vocab, size=int(rng.integers(4, min(32, grpo_args.max_prompt_length) + 1))) for _ in range(256)]
-    if grpo_args.synthetic_reward_token >= 0:
-        reward = token_match_reward(grpo_args.synthetic_reward_token)
-    elif grpo_args.synthetic_reward_below >= 0:
-        reward = token_below_reward(grpo_args.synthetic_reward_below)
-    elif grpo_args.reward_terms:
-        from halo_b200.entrypoints.script import load_tokenizer
-        from halo_b200.rewards.terms import RewardComposer, parse_terms
-
-        tokenizer = tokenizer or load_tokenizer(model_args)
-        reward = text_reward(tokenizer, RewardComposer(parse_terms(grpo_args.reward_terms)))
-    else:
-        raise ValueError("sampled rollouts need reward_terms (text prompts) or synthetic_reward_token")
+    prompts, reward, tokenizer = prompts_and_reward(model.cfg.vocab_size, model_args, data_args, train_args, grpo_args,
+                                                    consumer_rank, n_consumers)
     eos = getattr(tokenizer, "eos_token_id", None) if tokenizer is not None else None
     sampling = SamplingParams(max_new_tokens=grpo_args.max_completion_length, temperature=grpo_args.temperature,
                               top_k=grpo_args.top_k, top_p=grpo_args.top_p)
     return OnPolicyRolloutSource(model, prompts, reward, grpo_args.num_generations, sampling, grpo_args.prompts_per_round,
                                  eos_token_id=eos, seed=train_args.seed + consumer_rank,
                                  max_prompt_length=grpo_args.max_prompt_length, record_routing=grpo_args.routing_replay)
+
+
+def server_source(model, model_args, data_args, train_args, grpo_args, pc, device):
+    """Rollouts from a generation server outside the job (``rollout_backend: vllm`` / ``sglang``): every trainer samples
+    its own prompts' completions over HTTP; global rank 0 also holds the weight-sync client. The server is checked before
+    the first round (reachable, long enough context, returns sampled token ids, takes a weight update)."""
+    from halo_b200.trainers.grpo.engine_preflight import run_preflight
+    from halo_b200.weight_sync.clients import make_client
+    from halo_b200.weight_sync.engine_push import ServerRolloutSource
+
+    if not grpo_args.rollout_server_url:
+        raise ValueError(f"rollout_backend: {grpo_args.rollout_backend} needs rollout_server_url (http://host:port of the server)")
+    if grpo_args.environment_type:
+        raise ValueError("environment episodes are played against a policy inside the job (rollout_gpus or in_process), "
+                         "not against an external server")
+    prompts, reward, _ = prompts_and_reward(model.cfg.vocab_size, model_args, data_args, train_args, grpo_args,
+                                            pc.data_parallel_rank, pc.data_parallel_size)
+    model_id = grpo_args.rollout_served_model or model_args.model_name_or_path
+    client = None
+    if pc.global_rank == 0:
+        client = make_client(grpo_args.rollout_backend, grpo_args.rollout_server_url, model_id=model_id,
+                             chunk_bytes=grpo_args.weight_sync_chunk_mb << 20)
+        run_preflight(client, model.cfg, grpo_args)
+    source = ServerRolloutSource(grpo_args.rollout_server_url, model_id, prompts, reward, grpo_args.num_generations,
+                                 grpo_args.max_completion_length, grpo_args.temperature, grpo_args.top_p, grpo_args.top_k,
+                                 grpo_args.prompts_per_round, grpo_args.max_prompt_length)
+    return source, client
 
 
 def serve_rollout_copy(model_args, pc, device, roles, grpo_args, data_args=None, train_args=None):
@@ -175,12 +211,15 @@ def main(argv=None):
     model = load_policy_model(model_args, pc, device, runtime, train_args.gradient_checkpointing,
                               max_tokens=grpo_args.token_budget)
     runtime = getattr(model, "parallel_runtime", runtime)      # tensor / context parallelism finish their runtime there
+    engine_client = None
     if roles is not None and has_live_reward(grpo_args):
         import torch.distributed as dist
 
         from halo_b200.trainers.grpo.remote_rollouts import StoreRolloutSource
 
         source = StoreRolloutSource(dist.distributed_c10d._get_default_store(), roles.rank)     # sampled on the rollout ranks
+    elif grpo_args.rollout_backend in ("vllm", "sglang"):
+        source, engine_client = server_source(model, model_args, data_args, train_args, grpo_args, pc, device)
     elif grpo_args.rollout_backend == "in_process":
         source = in_process_source(model, model_args, data_args, train_args, grpo_args, pc)
     elif data_args.dataset_path:
@@ -194,6 +233,10 @@ def main(argv=None):
                                       response_len=(8, min(256, grpo_args.max_completion_length)),
                                       seed=train_args.seed + pc.data_parallel_rank)
     weight_sync = None
+    if engine_client is not None:
+        from halo_b200.weight_sync.engine_push import EngineWeightPusher
+
+        weight_sync = EngineWeightPusher(engine_client, device, runtime.ep_group if runtime else None)
     if roles is not None:
         from halo_b200.weight_sync.group import full_manifest
         from halo_b200.weight_sync.roles import ModelWeightPusher, make_sync

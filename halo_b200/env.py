@@ -40,6 +40,9 @@ CATALOGUE = {
     "HALO_MOE_FUSED": "expert products with the token movement inside the GEMM kernels (1, default) or as separate push / pull kernels (0)",
     "HALO_PEER_WAIT_MS": "how long a kernel waits for rows or a flag from a peer GPU before it gives up with a status (default 20000)",
     "HALO_ROW_BLOCKS_PER_SM": "thread blocks per SM of the expert row kernels (dispatch / combine)",
+    "HALO_NNODES": "nodes of a multi-node launch (read by the CLI when --nnodes is not given)",
+    "HALO_NODE_RANK": "this node's index in a multi-node launch",
+    "HALO_RDZV_ENDPOINT": "host:port of the first node, the rendezvous address of a multi-node launch",
     "DIST_NCCL_TIMEOUT_MINUTES": "collective watchdog of every process group",
     "DIST_STORE_TIMEOUT_HOURS": "timeout of store-based joins that outlast the watchdog",
     "DIST_FS_PROBE_TIMEOUT_SECONDS": "how long to poll for the shared-filesystem sentinel",

@@ -95,6 +95,73 @@ class ResidentCopySync:
             unpack_chunk(self.slots, c, view, named_params)
 
 
+class ShardedCopySync:
+    """Every trainer pushes the weights it holds, nobody gathers. The rollout ranks' arena is laid out for the FULL
+    tensors (expert banks with all experts); trainer t stores its expert slice at the slice's offset inside the bank and
+    its share of the replicated tensors (dealt round-robin over the trainers) whole, each with one kernel that reads the
+    parameter memory once and stores to every rollout GPU over NVLink. With T trainers and R rollout GPUs every trainer
+    sends 1/T of the model R times and every rollout GPU receives the model once, so all links are busy for
+    (model bytes) / (link bandwidth): the floor of a full copy per rollout GPU.
+
+    All ranks of ``group`` call the constructor with the same ``full_manifest`` ((name, full shape, dtype) in one
+    order). Counterpart of the reference's sharded weight-update streams (halo/weight_sync/update_stream.py,
+    halo/trainers/grpo/rollout/weight_push.py), without their gather to one sender."""
+
+    def __init__(self, group, device, full_manifest, trainer_ranks: list[int], rollout_ranks: list[int]):
+        import torch.distributed._symmetric_memory as symm
+
+        self.group, self.device = group, torch.device(device)
+        self.rank = dist.get_rank(group)
+        self.trainer_ranks, self.rollout_ranks = list(trainer_ranks), list(rollout_ranks)
+        self.slots, sizes = plan_chunks(full_manifest, 1 << 62)           # one chunk: offsets inside one arena
+        self.offset = {s.name: s.offset for s in self.slots}
+        self.nbytes = {s.name: s.nbytes for s in self.slots}
+        self.total = sizes[0] if sizes else 256
+        self.arena = symm.empty((max(self.total, 256),), dtype=torch.uint8, device=self.device)
+        self.handle = symm.rendezvous(self.arena, group)
+        ptrs = list(self.handle.buffer_ptrs)
+        self._dst = (_lib.c_void_p * len(self.rollout_ranks))(*[ptrs[r] for r in self.rollout_ranks])
+        self.last_seconds = 0.0
+        self.bytes_sent = 0
+
+    def owner_of_replicated(self, index: int) -> int:
+        """Trainer (position in ``trainer_ranks``) that sends the ``index``-th replicated tensor."""
+        return index % len(self.trainer_ranks)
+
+    def push(self, pieces) -> None:
+        """COLLECTIVE over the group. A trainer passes ``[(name, tensor, first_row)]``: ``tensor`` holds rows
+        ``[first_row, first_row + tensor.shape[0])`` of the full tensor ``name`` (``first_row = 0`` and the whole tensor
+        for a replicated one); the rollout ranks pass an empty list."""
+        self.handle.barrier(channel=1)          # receivers are not reading the arena any more
+        L = _lib.lib()
+        self.bytes_sent = 0
+        for name, t, first_row in pieces:
+            t = t.detach()
+            if not t.is_contiguous():
+                t = t.contiguous()
+            row_bytes = t[0].numel() * t.element_size() if t.dim() > 0 and t.shape[0] > 0 else t.element_size()
+            n = t.numel() * t.element_size()
+            off = self.offset[name] + first_row * row_bytes
+            if off % 16 or n % 16:
+                raise ValueError(f"{name}: a piece of {n} bytes at offset {off} is not 16-byte aligned")
+            if off + n > self.offset[name] + (self.nbytes[name] + 255) // 256 * 256:
+                raise ValueError(f"{name}: the piece runs past its tensor in the arena")
+            rc = L.halo_broadcast_bytes(_lib.ptr(t), self._dst, _lib.c_int(len(self.rollout_ranks)), _lib.c_ll(off), _lib.c_ll(n),
+                                        _lib.stream_ptr(self.device))
+            _lib.check(rc, "halo_broadcast_bytes")
+            self.bytes_sent += n
+        if pieces:
+            ev = torch.cuda.Event()
+            ev.record()
+            bounded_event_wait(ev, what="weight push")
+        self.handle.barrier(channel=1)          # every store has landed
+
+    def view(self, name: str, shape, dtype) -> torch.Tensor:
+        """On a rollout rank: the full tensor ``name`` inside the arena (no copy)."""
+        n = self.nbytes[name]
+        return self.arena[self.offset[name]:self.offset[name] + n].view(dtype).view(shape)
+
+
 class BroadcastSync:
     """Portable path: packed chunks broadcast from ``src_rank`` over a process group."""
 

@@ -131,6 +131,38 @@ def check_broadcast_and_allreduce(dev, rank, world):
     hs.barrier(channel=0)
 
 
+def check_sharded_weight_push(dev, rank, world):
+    """First half of the ranks train (expert banks cut over them), second half receive a full copy: every trainer stores
+    its slice and its share of the replicated tensors straight into the receivers' arenas."""
+    from halo_b200.weight_sync.group import ShardedCopySync
+
+    n_train = world // 2
+    trainers, rollouts = list(range(n_train)), list(range(n_train, world))
+    E = 4 * n_train
+    manifest = [("embed", (64, 48), torch.bfloat16), ("norm", (48,), torch.float32), ("bank_a", (E, 24, 48), torch.bfloat16),
+                ("head", (64, 48), torch.bfloat16), ("bank_b", (E, 48, 8), torch.bfloat16)]
+    full = {}
+    g = torch.Generator().manual_seed(99)                      # the same full tensors on every rank
+    for name, shape, dtype in manifest:
+        full[name] = torch.randn(shape, generator=g).to(dtype).to(dev)
+    sync = ShardedCopySync(dist.group.WORLD, dev, manifest, trainers, rollouts)
+    sync.arena.zero_()
+    pieces = []
+    if rank in trainers:
+        t = trainers.index(rank)
+        e = E // n_train
+        for k, name in enumerate(("embed", "norm", "head")):
+            if sync.owner_of_replicated(k) == t:
+                pieces.append((name, full[name], 0))
+        for name in ("bank_a", "bank_b"):
+            pieces.append((name, full[name][t * e:(t + 1) * e], t * e))
+    for _ in range(2):
+        sync.push(pieces)
+    if rank in rollouts:
+        for name, shape, dtype in manifest:
+            assert torch.equal(sync.view(name, shape, dtype), full[name]), f"sharded weight push: {name} differs"
+
+
 def check_nvls_forms(dev, rank, world):
     """The multimem forms (in-switch reduction, multicast stores) against the plain peer forms, where the symmetric
     buffers are bound to an NVLink multicast object; skipped (and said so) where they are not."""
@@ -296,6 +328,7 @@ def main():
         _lib.raise_on_status(dev)
     check_fused_optimizer(dev, rank, world)
     check_broadcast_and_allreduce(dev, rank, world)
+    check_sharded_weight_push(dev, rank, world)
     nvls = check_nvls_forms(dev, rank, world)
     check_context_parallel(dev, rank, world)
     check_tensor_parallel_collectives(dev, rank, world)

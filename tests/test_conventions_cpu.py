@@ -214,3 +214,38 @@ def test_tensor_records_compare():
     assert records.compare(base, moved, tolerance=1e-6) == []                      # within tolerance on the norms
     del moved["workloads"]["single"]
     assert any("one record only" in d for d in records.compare(base, moved))
+
+
+def test_full_size_recipes_parse_and_their_layouts_pass_the_rules():
+    """Every YAML under ``examples/recipes/`` names its launch line in its first comment; the keys must be known to that
+    method's argument classes and the parallel layout must pass the composition rules at the declared world size."""
+    import importlib
+    import re
+
+    from halo_b200 import cli
+    from halo_b200.configs.arguments import DataArguments, ModelArguments, ParallelismArguments, TrainingArguments
+    from halo_b200.configs.parser import ArgumentParser
+    method_args = {"sft": "SFTArguments", "dpo": "PreferenceArguments", "reward": "RewardArguments", "distill": "DistillationArguments",
+                   "grpo": "GRPOArguments"}
+    arguments = importlib.import_module("halo_b200.configs.arguments")
+    folder = os.path.join(ROOT, "examples", "recipes")
+    names = sorted(n for n in os.listdir(folder) if n.endswith(".yaml"))
+    assert len(names) >= 12
+    for name in names:
+        path = os.path.join(folder, name)
+        first = read(path).splitlines()[0]
+        m = re.match(r"# launch (\w+) (\S+) -n (\d+)(?: --nnodes (\d+))?", first)
+        assert m, f"{name}: first line must be '# launch <method> <path> -n <N>'"
+        method, shown, n, nnodes = m.group(1), m.group(2), int(m.group(3)), int(m.group(4) or 1)
+        assert method in cli.METHODS and shown == f"examples/recipes/{name}", name
+        parser = ArgumentParser(ModelArguments, DataArguments, TrainingArguments, ParallelismArguments, getattr(arguments, method_args[method]))
+        parsed = parser.parse([path])
+        par = parsed[3]
+        world = n * nnodes - int(getattr(parsed[4], "rollout_gpus", 0) or 0)
+        pc = par.to_config(world_size=world, global_rank=0, init_from_scratch=False)
+        assert pc.world_size == world, name
+    # every recipe a launcher file names exists
+    for dirpath, _, files in os.walk(os.path.join(ROOT, "launcher-configs")):
+        for f in files:
+            for ref in re.findall(r"examples/recipes/[\w.\-]+\.yaml", read(os.path.join(dirpath, f))):
+                assert os.path.isfile(os.path.join(ROOT, ref)), f"{f} names {ref}"
