@@ -28,6 +28,11 @@ def list_files(path: str) -> list[str]:
 
 
 def read_records(path: str) -> Iterator[dict]:
+    if path.startswith("s3://"):
+        # mirrored into the node's cache by the node's first rank; the other ranks wait for its completion marker
+        from halo_b200.data.s3 import resolve_dataset_path
+
+        path = resolve_dataset_path(path, is_downloader=int(os.environ.get("LOCAL_RANK", "0")) == 0)
     for f in list_files(path):
         with open(f) as fh:
             if f.endswith(".jsonl"):

@@ -30,4 +30,5 @@ def environment_types() -> list[str]:
 
 
 def _load_builtins() -> None:
-    from . import tasks  # noqa: F401  (registers qa, code)
+    from . import tasks  # noqa: F401  (registers qa, code, tool_qa)
+    from . import mcp  # noqa: F401  (registers mcp)
