@@ -244,6 +244,14 @@ class GRPOArguments:
     is_veto_min: float | None = None            # drop a trajectory holding a token whose raw ratio falls below this (None = off)
     opsm_delta: float | None = None             # drop negative-advantage trajectories whose |mean log-ratio| exceeds this (None = off)
     zero_gradient_round_limit: int = 0
+    sdpg_beta_base: float = 0.0                 # > 0: add beta(k) x on-policy self-distillation from a hinted pass of the policy
+    sdpg_beta_warmup_steps: int = 0
+    sdpg_beta_decay_steps: int = 0
+    sdpg_loss: Literal["reverse_kl", "forward_kl", "jsd"] = "reverse_kl"
+    sdpg_temperature: float = 1.0
+    sdpg_answer_field: str = "answer"           # task-row field holding the gold answer the hint reveals
+    sdpg_hint_template: str = "\n(The reference answer is: {answer})\n"
+    opd_positive_advantage_only: bool = True    # distil only on rollouts the verifier preferred
     rollout_backend: Literal["in_process", "vllm", "sglang", "resident_copy"] = "resident_copy"
     rollout_gpus: int = 0
     rollout_server_url: str = ""                # vllm / sglang: http://host:port of the generation server

@@ -260,8 +260,25 @@ def main(argv=None):
             p.requires_grad_(False)
         ref_model.eval()
         torch.manual_seed(train_args.seed)
-    trainer = GRPOTrainer(model, train_args, source, grpo_args=grpo_args, ref_model=ref_model, weight_sync=weight_sync,
-                          device=device, parallel=runtime, parallelism_fingerprint=pc.fingerprint())
+    if grpo_args.sdpg_beta_base > 0:
+        from halo_b200.entrypoints.script import load_tokenizer
+        from halo_b200.trainers.grpo.sdpg import HintedSource, SDPGTrainer
+
+        if roles is not None and has_live_reward(grpo_args):
+            raise ValueError("sdpg_beta_base > 0 needs each rollout's task row on the trainer; rounds published by rollout "
+                             "ranks carry tokens only (use rollout_backend: in_process, vllm or sglang)")
+        if not data_args.dataset_path:
+            raise ValueError("sdpg_beta_base > 0 needs dataset_path: task rows with a prompt and the gold answer the hint reveals")
+        source = HintedSource(source, load_tokenizer(model_args), grpo_args.sdpg_answer_field, grpo_args.sdpg_hint_template)
+        trainer = SDPGTrainer(model, train_args, source, grpo_args=grpo_args, ref_model=ref_model, weight_sync=weight_sync,
+                              device=device, parallel=runtime, parallelism_fingerprint=pc.fingerprint(),
+                              sdpg_beta_base=grpo_args.sdpg_beta_base, sdpg_beta_warmup_steps=grpo_args.sdpg_beta_warmup_steps,
+                              sdpg_beta_decay_steps=grpo_args.sdpg_beta_decay_steps, sdpg_loss=grpo_args.sdpg_loss,
+                              sdpg_temperature=grpo_args.sdpg_temperature,
+                              opd_positive_advantage_only=grpo_args.opd_positive_advantage_only)
+    else:
+        trainer = GRPOTrainer(model, train_args, source, grpo_args=grpo_args, ref_model=ref_model, weight_sync=weight_sync,
+                              device=device, parallel=runtime, parallelism_fingerprint=pc.fingerprint())
     if roles is not None:
         trainer.collective_group = roles.trainer_group       # the rollout ranks take no part in saves and barriers
         trainer.rank = roles.rank

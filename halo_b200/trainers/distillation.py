@@ -58,12 +58,19 @@ def _masked_sum(s, t, m, kind, temperature):
     return (per * m).sum() * temperature**2
 
 
-def chunked_kd_loss(h_student, w_student, h_teacher, w_teacher, mask, kind="forward_kl", temperature=1.0,
-                    chunk_rows: int = 2048):
+def chunked_kd_sum(h_student, w_student, h_teacher, w_teacher, weights, kind="forward_kl", temperature=1.0,
+                   chunk_rows: int = 2048):
+    """Sum over rows of ``weights[row] * divergence(student row, teacher row)`` (times temperature squared)."""
     total = h_student.new_zeros((), dtype=torch.float32)
     for s in range(0, h_student.shape[0], chunk_rows):
         e = min(h_student.shape[0], s + chunk_rows)
-        total = total + _ChunkKD.apply(h_student[s:e], w_student, h_teacher[s:e], w_teacher, mask[s:e], kind, temperature)
+        total = total + _ChunkKD.apply(h_student[s:e], w_student, h_teacher[s:e], w_teacher, weights[s:e], kind, temperature)
+    return total
+
+
+def chunked_kd_loss(h_student, w_student, h_teacher, w_teacher, mask, kind="forward_kl", temperature=1.0,
+                    chunk_rows: int = 2048):
+    total = chunked_kd_sum(h_student, w_student, h_teacher, w_teacher, mask, kind, temperature, chunk_rows)
     return total / mask.to(torch.float32).sum().clamp_min(1)
 
 

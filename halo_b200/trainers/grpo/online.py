@@ -79,6 +79,7 @@ class OnPolicyRolloutSource:
         outs = self.generator.generate(batch, params, record_routing=self.record_routing)
         self.generator.model.train(was_training)
         rollouts = []
+        self.last_tasks = [picks[n // self.g][1] for n in range(len(outs))]      # the task row of every rollout, in order
         for n, out in enumerate(outs):
             ids, task = picks[n // self.g]
             rollouts.append(Rollout(ids, out.token_ids, out.logprobs, self.reward_fn(ids, out.token_ids, task),

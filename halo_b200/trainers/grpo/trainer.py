@@ -34,6 +34,7 @@ class Rollout:
     completion_mask: np.ndarray | None = None   # 1 on tokens the policy produced, 0 on environment tokens in between; None = all 1
     routing: np.ndarray | None = None           # [moe layers, prompt + completion - 1, top_k]: the sampler's experts per token
     routing_layers: list | None = None          # the decoder-layer index of every row of ``routing``
+    teacher_prompt_ids: np.ndarray | None = None  # prompt + privileged hint, for the self-distillation term (None = plain prompt)
 
 
 @dataclass
@@ -52,10 +53,12 @@ class GRPOBatch(PackedBatch):
     def to(self, device, non_blocking: bool = True):
         b = PackedBatch.to(self, device, non_blocking)
         mv = lambda t: None if t is None else t.to(device, non_blocking=non_blocking)  # noqa: E731
-        return GRPOBatch(b.input_ids, b.position_ids, b.labels, b.cu_seqlens, b.n_scored, mv(self.advantages),
-                         mv(self.old_logprobs), self.has_old, mv(self.degenerate), mv(self.seq_lengths), mv(self.attention_mask),
-                         None if self.replay_routing is None else {k: mv(v) for k, v in self.replay_routing.items()},
-                         mv(self.traj_ids), self.counted_tokens, self.denominator)
+        out = GRPOBatch(b.input_ids, b.position_ids, b.labels, b.cu_seqlens, b.n_scored, mv(self.advantages),
+                        mv(self.old_logprobs), self.has_old, mv(self.degenerate), mv(self.seq_lengths), mv(self.attention_mask),
+                        None if self.replay_routing is None else {k: mv(v) for k, v in self.replay_routing.items()},
+                        mv(self.traj_ids), self.counted_tokens, self.denominator)
+        out.opd = getattr(self, "opd", None)
+        return out
 
 
 def build_grpo_batch(rollouts: list[Rollout], adv: torch.Tensor, degenerate: torch.Tensor) -> GRPOBatch:
@@ -89,9 +92,11 @@ def build_grpo_batch(rollouts: list[Rollout], adv: torch.Tensor, degenerate: tor
             n = min(r.routing.shape[1], len(r.prompt_ids) + len(r.completion_ids))
             for row, li in enumerate(layers):
                 replay[li][s:s + n] = torch.from_numpy(r.routing[row, :n].astype(np.int32))
-    return GRPOBatch(base.input_ids, base.position_ids, base.labels, base.cu_seqlens, base.n_scored, a, old, has_old,
-                     deg, torch.tensor([len(r.completion_ids) for r in rollouts], dtype=torch.float32), None, replay,
-                     traj, [counted_completion_tokens(r) for r in rollouts])
+    batch = GRPOBatch(base.input_ids, base.position_ids, base.labels, base.cu_seqlens, base.n_scored, a, old, has_old,
+                      deg, torch.tensor([len(r.completion_ids) for r in rollouts], dtype=torch.float32), None, replay,
+                      traj, [counted_completion_tokens(r) for r in rollouts])
+    batch.rollouts = rollouts           # host side only: plans layered on the batch (self-distillation) read the rows
+    return batch
 
 
 def counted_completion_tokens(r: Rollout) -> int:

@@ -135,6 +135,7 @@ class ServerRolloutSource:
         with cf.ThreadPoolExecutor(max_workers=min(self.concurrency, len(picks))) as pool:
             sampled = list(pool.map(lambda p: self._sample(p[0]), picks))
         rollouts = []
+        self.last_tasks = [task for (_, task), group in zip(picks, sampled) for _ in group]
         for (ids, task), group in zip(picks, sampled):
             for toks, logps in group:
                 rollouts.append(Rollout(ids, toks, logps if len(logps) == len(toks) else None, self.reward_fn(ids, toks, task)))

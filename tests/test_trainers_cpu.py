@@ -309,3 +309,101 @@ def test_classification_and_embedding_entry_points(tmp_path, method, extra, arch
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert "step 3 " in r.stdout + r.stderr
     assert json.load(open(tmp_path / "run" / "final" / "config.json"))["architectures"] == [arch]
+
+
+# ---- SDPG: GRPO + on-policy self-distillation from a privileged (hinted) pass of the same policy ----------------------
+def test_sdpg_schedule_hint_and_pairing():
+    import numpy as np
+
+    from halo_b200.trainers.grpo.sdpg import beta_schedule, build_opd_plan, render_hint
+    from halo_b200.trainers.grpo.trainer import Rollout, build_grpo_batch
+
+    assert [round(beta_schedule(s, 10, 2.0, warmup_steps=4, decay_steps=2), 3) for s in range(10)] == \
+        [0.5, 1.0, 1.5, 2.0, 2.0, 2.0, 2.0, 2.0, 1.0, 0.0]
+    assert render_hint("answer: {answer}", "42") == "answer: 42" and render_hint("answer: {answer}", "  ") is None
+    with pytest.raises(ValueError):
+        render_hint("{solution}", "x")
+    r0 = Rollout(np.array([1, 2, 3]), np.array([10, 11]), None, 1.0, teacher_prompt_ids=np.array([1, 2, 3, 7, 8]))
+    r1 = Rollout(np.array([4, 5]), np.array([12, 13, 14]), None, 0.0, completion_mask=np.array([1, 0, 1]))
+    adv = torch.tensor([0.7, -0.7])
+    batch = build_grpo_batch([r0, r1], adv, torch.zeros(2, dtype=torch.bool))
+    plan = build_opd_plan([r0, r1], batch.cu_seqlens, adv, positive_only=True)
+    # student stream: [1 2 3 10 11 | 4 5 12 13 14]; teacher stream: [1 2 3 7 8 10 11 | 4 5 12 13 14]
+    assert plan.student_idx.tolist() == [2, 3, 6, 8] and plan.teacher_idx.tolist() == [4, 5, 8, 10]
+    assert plan.gate.tolist() == [1.0, 1.0, 0.0, 0.0]
+    # the paired positions predict the same token in both streams
+    for s, t in zip(plan.student_idx.tolist(), plan.teacher_idx.tolist()):
+        assert batch.input_ids[s + 1] == plan.input_ids[t + 1]
+
+
+def test_sdpg_adds_beta_times_gated_reverse_kl_to_the_grpo_loss():
+    import numpy as np
+
+    from halo_b200.configs.arguments import GRPOArguments, TrainingArguments
+    from halo_b200.models.config import PRESETS
+    from halo_b200.models.qwen3 import build_model
+    from halo_b200.trainers.grpo.sdpg import SDPGTrainer
+    from halo_b200.trainers.grpo.trainer import GRPOTrainer, Rollout
+
+    torch.manual_seed(0)
+    cfg = PRESETS["tiny-moe"]()
+    model = build_model(cfg, device="cpu", dtype=torch.float32)
+    rng = np.random.default_rng(0)
+    rollouts = []
+    for p in range(2):
+        prompt = rng.integers(0, cfg.vocab_size, 5)
+        for g in range(2):
+            comp = rng.integers(0, cfg.vocab_size, 4)
+            rollouts.append(Rollout(prompt, comp, None, float(g), teacher_prompt_ids=np.concatenate([prompt, rng.integers(0, cfg.vocab_size, 3)])))
+    args = TrainingArguments(max_steps=4, learning_rate=1e-3, optim="adamw_torch", output_dir="/tmp/halo_b200_runs/sdpg_unit")
+    gargs = GRPOArguments(num_generations=2, token_budget=4096, loss_type="dapo")
+    plain = GRPOTrainer(model, args, lambda i: None, grpo_args=gargs, device=torch.device("cpu"))
+    sdpg = SDPGTrainer(model, args, lambda i: None, grpo_args=gargs, device=torch.device("cpu"), sdpg_beta_base=0.5)
+    (pb,) = plain.plan_round(rollouts)
+    (sb,) = sdpg.plan_round(rollouts)
+    base = plain.compute_loss(model, pb, None)
+    total = sdpg.compute_loss(model, sb, None)
+    # the term by hand: reverse KL at the completion positions of the positive-advantage rows (generation 1 of each prompt)
+    with torch.no_grad():
+        hs = model.hidden_states(sb.input_ids, sb.position_ids, sb.cu_seqlens).reshape(-1, cfg.hidden_size)
+        ht = model.hidden_states(sb.opd.input_ids, sb.opd.position_ids, sb.opd.cu_seqlens).reshape(-1, cfg.hidden_size)
+        w = model.head_weight().float()
+        s = torch.log_softmax(hs[sb.opd.student_idx].float() @ w.t(), -1)
+        t = torch.log_softmax(ht[sb.opd.teacher_idx].float() @ w.t(), -1)
+        rkl = (s.exp() * (s - t)).sum(-1)
+        want = (rkl * sb.opd.gate).sum() / sb.opd.gate.sum()
+    assert sb.opd.gate.sum() == 8 and sb.opd.denominator == 8.0
+    assert torch.allclose(total - base, 0.5 * want, rtol=1e-4, atol=1e-6)
+    assert float(want) > 0
+    # gradients reach the student only: the loss has a gradient, and a zero beta is exactly GRPO
+    total.backward()
+    assert all(p.grad is None or torch.isfinite(p.grad).all() for p in model.parameters())
+    off = SDPGTrainer(model, args, lambda i: None, grpo_args=gargs, device=torch.device("cpu"), sdpg_beta_base=0.0)
+    (ob,) = off.plan_round(rollouts)
+    assert torch.equal(off.compute_loss(model, ob, None), base)
+
+
+def test_hinted_source_attaches_each_rows_own_answer():
+    import numpy as np
+
+    from halo_b200.trainers.grpo.sdpg import HintedSource
+    from halo_b200.trainers.grpo.trainer import Rollout
+
+    class Source:
+        mean_reward = 0.5
+
+        def __call__(self, i):
+            self.last_tasks = [{"answer": "7"}, {"answer": "7"}, {}, None]
+            return [Rollout(np.array([1, 2]), np.array([3]), None, 0.0) for _ in range(4)]
+
+    class Tok:
+        def __call__(self, text, add_special_tokens=False):
+            return {"input_ids": [100 + int(c) for c in text if c.isdigit()]}
+
+    src = HintedSource(Source(), Tok(), "answer", "the answer is {answer}")
+    rollouts = src(0)
+    assert rollouts[0].teacher_prompt_ids.tolist() == [1, 2, 107] and rollouts[1].teacher_prompt_ids.tolist() == [1, 2, 107]
+    assert rollouts[2].teacher_prompt_ids is None and rollouts[3].teacher_prompt_ids is None
+    assert src.rows_without_answer == 2 and src.mean_reward == 0.5
+    with pytest.raises(ValueError):
+        HintedSource(Source(), Tok(), "answer", "{solution}")
