@@ -95,20 +95,28 @@ def export_block_fp8(src: str, dst: str, keep: list[str] | None = None) -> int:
     return n
 
 
-def export(src: str, dst: str, fmt: str, keep: list[str] | None = None) -> int:
+def export(src: str, dst: str, fmt: str, keep: list[str] | None = None, layout: str = "block_scaled") -> int:
+    """``layout``: ``block_scaled`` writes the framework's own manifest (``halo_lowp.json``); ``compressed-tensors`` also
+    writes the ``quantization_config`` a serving engine's compressed-tensors loader reads."""
+    if layout not in ("block_scaled", "compressed-tensors"):
+        raise ValueError(f"unknown layout {layout!r}")
     if fmt not in lowp.FORMATS:
         raise ValueError(f"unknown format {fmt!r}; known: {lowp.FORMATS}")
     kept = [re.compile(p) for p in keep or []]
     idx = CheckpointIndex(src)
     writer = StreamingShardWriter(dst)
     n = 0
+    quantized_modules, kept_modules = [], []
     for name in sorted(idx.weight_map):
         t = idx.get(name)
         plain = (t.dim() != 2 or not name.endswith(".weight") or ALWAYS_KEPT.search(name) or any(p.search(name) for p in kept)
                  or t.shape[1] % lowp.BLOCK_SIZE[fmt])
         if plain:
             writer.add(name, t)
+            if t.dim() == 2 and name.endswith(".weight"):
+                kept_modules.append(name[:-len(".weight")])
             continue
+        quantized_modules.append(name[:-len(".weight")])
         q = lowp.quantize(t, fmt)
         data = q.data.view(torch.uint8) if q.data.dtype == torch.float8_e4m3fn else q.data       # bytes either way
         scales = q.scales.view(torch.uint8) if q.scales.dtype == torch.float8_e4m3fn else q.scales
@@ -121,6 +129,13 @@ def export(src: str, dst: str, fmt: str, keep: list[str] | None = None) -> int:
     copy_side_files(src, dst)
     json.dump({"format": fmt, "block_size": lowp.BLOCK_SIZE[fmt], "quantized_tensors": n},
               open(os.path.join(dst, "halo_lowp.json"), "w"), indent=2)
+    if layout == "compressed-tensors":
+        from .compressed_tensors_layout import quantization_config
+
+        cfg_path = os.path.join(dst, "config.json")
+        cfg = json.load(open(cfg_path)) if os.path.isfile(cfg_path) else {}
+        cfg["quantization_config"] = quantization_config(fmt, quantized_modules, kept_modules)
+        json.dump(cfg, open(cfg_path, "w"), indent=2)
     return n
 
 
@@ -164,6 +179,7 @@ def main(argv=None) -> int:
     p.add_argument("dst")
     p.add_argument("--format", required=True, choices=list(lowp.FORMATS))
     p.add_argument("--keep", nargs="*", default=[])
+    p.add_argument("--layout", default="block_scaled", choices=["block_scaled", "compressed-tensors"])
     args = ap.parse_args(argv)
     if args.cmd == "dequant-block-fp8":
         n = dequant_block_fp8(args.src, args.dst)
@@ -172,7 +188,7 @@ def main(argv=None) -> int:
     elif args.cmd == "export-block-fp8":
         n = export_block_fp8(args.src, args.dst, args.keep)
     else:
-        n = export(args.src, args.dst, args.format, args.keep)
+        n = export(args.src, args.dst, args.format, args.keep, args.layout)
     print(f"{args.cmd}: {n} tensors converted into {args.dst}")
     return 0
 

@@ -42,6 +42,8 @@ TOOLS = {
     "env-eval": "halo_b200.entrypoints.env_eval",
     "merge-adapter": "halo_b200.checkpoint.tools.merge_adapter",
     "lowp-convert": "halo_b200.checkpoint.tools.lowp_convert",
+    "merge-pp-stages": "halo_b200.checkpoint.tools.merge_pp_stages",
+    "weight-push-bench": "benchmarks.weight_push",
     "bench": "bench",
 }
 

@@ -124,3 +124,66 @@ def test_trace_report_groups_kernels_and_measures_overlap(tmp_path):
     assert rep["families"] == {"gemm": 200.0, "collectives": 100.0, "attention": 50.0, "element-wise": 10.0}
     assert rep["span_us"] == 310.0 and rep["busy_us"] == 260.0 and rep["overlap_us"] == 100.0      # the all-reduce ran beside compute
     assert trace_report.main([str(path), "--top", "3"]) == 0
+
+
+def test_pipeline_stage_directories_merge_into_one_loadable_checkpoint(tmp_path):
+    """Two nodes, each holding only its own stage's shard files (node 0 also the index and config): the merge tool
+    unions them, and refuses when a node's directory is missing or stages overlap."""
+    import json
+    import os
+    import shutil
+
+    from halo_b200.checkpoint.tools import merge_pp_stages
+
+    model, full = _tiny(tmp_path, 0, "whole")
+    idx = CheckpointIndex(full)
+    names = sorted(idx.weight_map)
+    half = len(names) // 2
+    node0, node1 = tmp_path / "node0", tmp_path / "node1"
+    from safetensors.torch import save_file
+
+    node0.mkdir(), node1.mkdir()
+    save_file({n: idx.get(n).contiguous() for n in names[:half]}, str(node0 / "model-stage000-00001.safetensors"))
+    save_file({n: idx.get(n).contiguous() for n in names[half:]}, str(node1 / "model-stage001-00001.safetensors"))
+    shutil.copy(os.path.join(full, "config.json"), node0 / "config.json")
+    json.dump({"metadata": {}, "weight_map": {n: "x" for n in names}}, open(node0 / "model.safetensors.index.json", "w"))
+    out = str(tmp_path / "merged")
+    assert merge_pp_stages.main([str(node0), str(node1), "--out", out]) == 0
+    merged = from_pretrained(out, device="cpu", dtype=torch.float32)
+    for (n, p), (_, q) in zip(model.named_parameters(), merged.named_parameters()):
+        assert torch.equal(p, q), n
+    with pytest.raises(ValueError, match="in none of the directories"):
+        merge_pp_stages.merge([str(node0)], str(tmp_path / "partial"))
+    shutil.copy(node0 / "model-stage000-00001.safetensors", node1 / "model-stage009-00001.safetensors")
+    with pytest.raises(ValueError, match="stages overlap"):
+        merge_pp_stages.merge([str(node0), str(node1)], str(tmp_path / "overlap"))
+
+
+def test_compressed_tensors_block_names_the_quantised_modules(tmp_path):
+    import json
+    import os
+    import re
+
+    from halo_b200.checkpoint.tools import lowp_convert
+    from halo_b200.checkpoint.tools.compressed_tensors_layout import module_targets, quantization_config
+
+    targets = module_targets(["model.layers.0.self_attn.q_proj", "model.layers.11.self_attn.q_proj",
+                              "model.layers.3.mlp.experts.17.down_proj"])
+    assert targets == [r"re:model\.layers\.\d+\.mlp\.experts\.\d+\.down_proj", r"re:model\.layers\.\d+\.self_attn\.q_proj"]
+    cfg = quantization_config("nvfp4", ["model.layers.1.self_attn.q_proj"], ["model.layers.0.self_attn.q_proj", "lm_head"])
+    assert cfg["ignore"] == ["model.layers.0.self_attn.q_proj"]          # a kept module the generalised pattern would sweep in
+    assert cfg["config_groups"]["group_0"]["weights"]["group_size"] == 16
+    _, ckpt = _tiny(tmp_path, 0, "src")
+    out = str(tmp_path / "ct")
+    assert lowp_convert.main(["export", ckpt, out, "--format", "mxfp8", "--keep", r"layers\.0\.", "--layout", "compressed-tensors"]) == 0
+    qc = json.load(open(os.path.join(out, "config.json")))["quantization_config"]
+    assert qc["quant_method"] == "compressed-tensors" and qc["format"] == "mxfp8-quantized"
+    pats = [re.compile(t[3:] + "$") for t in qc["config_groups"]["group_0"]["targets"]]
+    manifest = json.load(open(os.path.join(out, "halo_lowp.json")))
+    assert manifest["quantized_tensors"] > 0
+    idx = CheckpointIndex(out)
+    for name in idx.weight_map:
+        if name.endswith(".weight_scale"):
+            module = name[:-len(".weight_scale")]
+            assert any(p.match(module) for p in pats) and module not in qc["ignore"], module
+    assert all("layers.0." in m for m in qc["ignore"]) and qc["ignore"]
