@@ -109,7 +109,7 @@ class TrainingArguments:
     lr_scheduler_type: Literal["linear", "cosine", "constant", "constant_with_warmup"] = "cosine"
     warmup_ratio: float = 0.0
     warmup_steps: int = 0
-    optim: Literal["adamw_bf16", "adamw_torch", "adamw_bf16_host_state", "muon"] = "adamw_bf16"
+    optim: Literal["adamw_bf16", "adamw_torch", "adamw_bf16_host_state", "adamw_q8", "flash_adamw", "muon"] = "adamw_bf16"
     bf16: bool = True
     gradient_checkpointing: bool = True
     gradient_checkpointing_plan: Literal["full", "auto"] = "full"   # auto: lighter policy where memory allows, planned after step 1

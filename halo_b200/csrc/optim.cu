@@ -237,6 +237,208 @@ __global__ void clip_coef_kernel(const float* __restrict__ total_sq, float max_n
     *coef = c;
 }
 
+
+// ---- AdamW with 8-bit moments and 24-bit weights (5 bytes of state per parameter) ------------------------------------
+// The weight is the bf16 parameter plus a signed 8-bit correction in units of 1/256 of the parameter's own bf16 spacing:
+// w = p + c * ulp(p) / 256, so the update accumulates in 16 significant bits although the model computes on bf16 p.
+// The moments are stored per group of 256 elements as one fp32 scale and 8-bit codes on a square-root-spaced grid
+// (fine steps near zero): m = sign(q) (|q| / 127)^2 * m_scale, sqrt(v) = (q / 255)^2 * v_scale. Codes and the weight
+// correction are rounded stochastically (Philox noise keyed like the bf16 optimizer's) so that a slowly decaying moment is unbiased instead of
+// sticking to its grid point; a positive second moment never rounds to code 0, which keeps the denominator away from
+// eps alone. One warp owns one group (8 elements per lane), so the group maxima are warp shuffles.
+constexpr int kQ8Group = 256;
+constexpr int kQ8Threads = 256;
+constexpr int kQ8ElemsPerBlock = 2048;
+
+struct Q8Table {
+    void* const* p;                    // bf16 parameters
+    const void* const* g;              // gradients (bf16 or fp32)
+    void* const* corr;                 // int8 weight corrections
+    void* const* mq;                   // int8 first-moment codes
+    void* const* vq;                   // uint8 second-moment codes
+    void* const* m_scale;              // fp32 [groups]
+    void* const* v_scale;              // fp32 [groups]
+    const long long* numel;
+    const unsigned long long* name_hash;
+    const int* block_start;
+    int n_tensors;
+};
+
+__device__ __forceinline__ float bf16_spacing_256th(float pf) {
+    const uint32_t e = (__float_as_uint(pf) >> 23) & 0xFFu;
+    return e > 15u ? __uint_as_float((e - 15u) << 23) : 0.f;
+}
+
+template <bool GRAD_F32>
+__global__ void __launch_bounds__(kQ8Threads)
+adamw_q8_kernel(const Q8Table tab, float beta1, float beta2, float omb1, float omb2, float step_size, float bc2_sqrt,
+                float eps, float wd_factor, unsigned long long key_step, const float* __restrict__ grad_scale,
+                const int* __restrict__ skip) {
+    if (skip != nullptr && *skip != 0) return;
+    int lo = 0, hi = tab.n_tensors;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (tab.block_start[mid] <= (int)blockIdx.x) lo = mid; else hi = mid;
+    }
+    const int ti = lo;
+    const long long n = tab.numel[ti];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long group = (long long)(blockIdx.x - tab.block_start[ti]) * (kQ8ElemsPerBlock / kQ8Group) + warp;
+    const long long g0 = group * kQ8Group;
+    if (g0 >= n) return;                                        // whole warp leaves together
+    const long long e0 = g0 + lane * 8;
+    __nv_bfloat16* p = (__nv_bfloat16*)tab.p[ti];
+    signed char* corr = (signed char*)tab.corr[ti];
+    signed char* mq = (signed char*)tab.mq[ti];
+    unsigned char* vq = (unsigned char*)tab.vq[ti];
+    float* m_scale = (float*)tab.m_scale[ti];
+    float* v_scale = (float*)tab.v_scale[ti];
+    const uint64_t mixed = splitmix64(splitmix64(key_step) ^ tab.name_hash[ti]);
+    const uint32_t k0 = (uint32_t)mixed, k1 = (uint32_t)(mixed >> 32);
+    float scale = 1.f;
+    const bool has_scale = grad_scale != nullptr;
+    if (has_scale) {
+        scale = *grad_scale;
+        if (!GRAD_F32) scale = __bfloat162float(__float2bfloat16_rn(scale));
+    }
+    const float ms = m_scale[group], vs = v_scale[group];
+    float w[8], m[8], s[8];
+    float m_max = 0.f, s_max = 0.f;
+    // eight consecutive elements per lane: one 16-byte load of the parameters (and of bf16 gradients), 8-byte loads of
+    // the three code arrays when the tensor's base addresses allow it
+    const bool full = (e0 + 8 <= n) && ((((uintptr_t)(p + e0)) & 15u) == 0) && ((((uintptr_t)(corr + e0)) & 7u) == 0) &&
+                      ((((uintptr_t)(mq + e0)) & 7u) == 0) && ((((uintptr_t)(vq + e0)) & 7u) == 0) &&
+                      (GRAD_F32 || ((((uintptr_t)((const __nv_bfloat16*)tab.g[ti] + e0)) & 15u) == 0));
+    float pin[8], gin[8];
+    int cin[8], qmin[8], qvin[8];
+    if (full) {
+        const uint4 pu = *reinterpret_cast<const uint4*>(p + e0);
+        const uint2 cu = *reinterpret_cast<const uint2*>(corr + e0);
+        const uint2 mu = *reinterpret_cast<const uint2*>(mq + e0);
+        const uint2 vu = *reinterpret_cast<const uint2*>(vq + e0);
+        const __nv_bfloat16* ph = reinterpret_cast<const __nv_bfloat16*>(&pu);
+        const signed char* cb = reinterpret_cast<const signed char*>(&cu);
+        const signed char* mb = reinterpret_cast<const signed char*>(&mu);
+        const unsigned char* vb = reinterpret_cast<const unsigned char*>(&vu);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            pin[j] = __bfloat162float(ph[j]);
+            cin[j] = cb[j]; qmin[j] = mb[j]; qvin[j] = vb[j];
+        }
+        if (GRAD_F32) {
+            const float4 ga = *reinterpret_cast<const float4*>((const float*)tab.g[ti] + e0);
+            const float4 gb = *reinterpret_cast<const float4*>((const float*)tab.g[ti] + e0 + 4);
+            gin[0] = ga.x; gin[1] = ga.y; gin[2] = ga.z; gin[3] = ga.w; gin[4] = gb.x; gin[5] = gb.y; gin[6] = gb.z; gin[7] = gb.w;
+        } else {
+            const uint4 gu = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)tab.g[ti] + e0);
+            const __nv_bfloat16* gh = reinterpret_cast<const __nv_bfloat16*>(&gu);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) gin[j] = __bfloat162float(gh[j]);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const long long e = e0 + j;
+            const bool ok = e < n;
+            pin[j] = ok ? __bfloat162float(p[e]) : 0.f;
+            cin[j] = ok ? (int)corr[e] : 0;
+            qmin[j] = ok ? (int)mq[e] : 0;
+            qvin[j] = ok ? (int)vq[e] : 0;
+            if (GRAD_F32) gin[j] = ok ? ((const float*)tab.g[ti])[e] : 0.f;
+            else gin[j] = ok ? __bfloat162float(((const __nv_bfloat16*)tab.g[ti])[e]) : 0.f;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const bool ok = e0 + j < n;
+        const float pf = pin[j];
+        const int c = cin[j], qm = qmin[j], qv = qvin[j];
+        float g = gin[j];
+        if (has_scale) {
+            g = g * scale;
+            if (!GRAD_F32) g = __bfloat162float(__float2bfloat16_rn(g));
+        }
+        const float wf = pf + (float)c * bf16_spacing_256th(pf);
+        const float rm = (float)(qm < 0 ? -qm : qm) / 127.f;
+        float mf = (rm * rm) * ms;
+        if (qm < 0) mf = -mf;
+        const float rv = (float)qv / 255.f;
+        const float sf = (rv * rv) * vs;
+        const float mn = mf * beta1 + g * omb1;
+        const float vn = (sf * sf) * beta2 + (g * g) * omb2;
+        const float sn = sqrtf(vn);
+        const float denom = sn / bc2_sqrt + eps;
+        w[j] = wf * wd_factor - (step_size * mn) / denom;
+        m[j] = ok ? mn : 0.f;
+        s[j] = ok ? sn : 0.f;
+        m_max = fmaxf(m_max, fabsf(m[j]));
+        s_max = fmaxf(s_max, s[j]);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        m_max = fmaxf(m_max, __shfl_xor_sync(0xffffffffu, m_max, off));
+        s_max = fmaxf(s_max, __shfl_xor_sync(0xffffffffu, s_max, off));
+    }
+    if (lane == 0) {
+        m_scale[group] = m_max;
+        v_scale[group] = s_max;
+    }
+    const long long quad = e0 >> 2;
+    const Philox r0 = philox4x32_10(k0, k1, (uint32_t)quad, (uint32_t)((unsigned long long)quad >> 32));
+    const Philox r1 = philox4x32_10(k0, k1, (uint32_t)(quad + 1), (uint32_t)((unsigned long long)(quad + 1) >> 32));
+    __align__(16) __nv_bfloat16 pout[8];
+    __align__(8) signed char cout[8];
+    __align__(8) signed char mout[8];
+    __align__(8) unsigned char vout[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t word = j < 4 ? r0.c[j] : r1.c[j - 4];
+        // one 32-bit word per element: 11 bits of rounding noise for each moment code, 10 for the weight correction
+        const float um = (float)(word & 0x7FFu) / 2048.f;
+        const float uv = (float)((word >> 11) & 0x7FFu) / 2048.f;
+        const float uc = (float)(word >> 22) / 1024.f;
+        int qm = 0;
+        if (m_max > 0.f) {
+            const float r = sqrtf(fabsf(m[j]) / m_max) * 127.f;
+            qm = (int)floorf(r + um);
+            qm = qm > 127 ? 127 : qm;
+            if (m[j] < 0.f) qm = -qm;
+        }
+        int qv = 0;
+        if (s_max > 0.f && s[j] > 0.f) {
+            const float r = sqrtf(s[j] / s_max) * 255.f;
+            qv = (int)floorf(r + uv);
+            qv = qv > 255 ? 255 : (qv < 1 ? 1 : qv);
+        }
+        const __nv_bfloat16 pn = __float2bfloat16_rn(w[j]);
+        const float pnf = __bfloat162float(pn);
+        const float st = bf16_spacing_256th(pnf);
+        int c = 0;
+        if (st > 0.f) {
+            // stochastic: an update below 1/256 of the spacing still moves the weight in expectation
+            c = (int)floorf((w[j] - pnf) / st + uc);
+            c = c > 127 ? 127 : (c < -128 ? -128 : c);
+        }
+        pout[j] = pn;
+        cout[j] = (signed char)c;
+        mout[j] = (signed char)qm;
+        vout[j] = (unsigned char)qv;
+    }
+    if (full) {
+        *reinterpret_cast<uint4*>(p + e0) = *reinterpret_cast<const uint4*>(pout);
+        *reinterpret_cast<uint2*>(corr + e0) = *reinterpret_cast<const uint2*>(cout);
+        *reinterpret_cast<uint2*>(mq + e0) = *reinterpret_cast<const uint2*>(mout);
+        *reinterpret_cast<uint2*>(vq + e0) = *reinterpret_cast<const uint2*>(vout);
+    } else {
+        for (int j = 0; j < 8 && e0 + j < n; ++j) {
+            p[e0 + j] = pout[j];
+            corr[e0 + j] = cout[j];
+            mq[e0 + j] = mout[j];
+            vq[e0 + j] = vout[j];
+        }
+    }
+}
+
 }  // namespace halo
 
 using namespace halo;
@@ -285,6 +487,32 @@ int halo_adamw_bf16_step_single(void* p, const void* g, void* m, void* v, long l
     else
         adamw_bf16_kernel<false><<<(unsigned)blocks, kAdamThreads, 0, s>>>(
             t, one, beta1, beta2, omb1, omb2, step_size, bc2_sqrt, eps, wd_factor, key ^ step, grad_scale, skip);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+
+int halo_adam_q8_elems_per_block() { return kQ8ElemsPerBlock; }
+int halo_adam_q8_group() { return kQ8Group; }
+
+// table: device array of int64 [9, n_tensors] rows p, g, corr, mq, vq, m_scale, v_scale, numel, name_hash.
+int halo_adamw_q8_step(const long long* table, const int* block_start, int n_tensors, int total_blocks, int grad_is_f32,
+                       float beta1, float beta2, float step_size, float bc2_sqrt, float eps, float wd_factor,
+                       unsigned long long key, unsigned long long step, const float* grad_scale, const int* skip,
+                       void* stream) {
+    if (n_tensors <= 0 || total_blocks <= 0) return 0;
+    const long long* row = table;
+    Q8Table t{(void* const*)(row), (const void* const*)(row + n_tensors), (void* const*)(row + 2 * n_tensors),
+              (void* const*)(row + 3 * n_tensors), (void* const*)(row + 4 * n_tensors), (void* const*)(row + 5 * n_tensors),
+              (void* const*)(row + 6 * n_tensors), row + 7 * n_tensors, (const unsigned long long*)(row + 8 * n_tensors),
+              block_start, n_tensors};
+    const float omb1 = (float)(1.0 - (double)beta1), omb2 = (float)(1.0 - (double)beta2);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (grad_is_f32)
+        adamw_q8_kernel<true><<<total_blocks, kQ8Threads, 0, s>>>(t, beta1, beta2, omb1, omb2, step_size, bc2_sqrt, eps,
+                                                                  wd_factor, key ^ step, grad_scale, skip);
+    else
+        adamw_q8_kernel<false><<<total_blocks, kQ8Threads, 0, s>>>(t, beta1, beta2, omb1, omb2, step_size, bc2_sqrt, eps,
+                                                                   wd_factor, key ^ step, grad_scale, skip);
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

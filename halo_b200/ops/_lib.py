@@ -33,7 +33,7 @@ _KERNELS_PER_CALL = {
     "halo_rmsnorm_bwd": 2, "halo_qknorm_rope_bwd": 2, "halo_attn_bwd": 3, "halo_route_count": 2, "halo_sq_norm": 2,
     "halo_rmsnorm_bwd_blocks": 0, "halo_qknorm_rope_bwd_blocks": 0, "halo_gemm_work_bytes": 0,
     "halo_rmsnorm_supported": 0, "halo_route_blocks": 0, "halo_adam_elems_per_block": 0,
-    "halo_moe_push_unit_bytes": 0, "halo_moe_tile_bytes": 0, "halo_moe_ctrl_ints": 0,
+    "halo_adam_q8_elems_per_block": 0, "halo_adam_q8_group": 0, "halo_moe_push_unit_bytes": 0, "halo_moe_tile_bytes": 0, "halo_moe_ctrl_ints": 0,
 }
 LAUNCHES = {"total": 0}
 

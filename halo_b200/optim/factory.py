@@ -8,7 +8,7 @@ import torch
 
 from .adamw_bf16 import AdamWBF16
 
-OPTIMIZERS = ("adamw_bf16", "adamw_bf16_host_state", "adamw_torch", "muon")
+OPTIMIZERS = ("adamw_bf16", "adamw_bf16_host_state", "adamw_q8", "flash_adamw", "adamw_torch", "muon")
 
 
 def decay_groups(named_params, weight_decay: float) -> list[dict]:
@@ -40,6 +40,10 @@ def build_optimizer(model, name: str = "adamw_bf16", lr: float = 1e-5, weight_de
 
         return HostStateAdamWBF16(groups, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
                                   device_state_budget_bytes=device_state_budget_bytes)
+    if name in ("adamw_q8", "flash_adamw"):          # flash_adamw: the reference's name for its 8-bit-state optimizer
+        from .adamw_q8 import AdamWQ8
+
+        return AdamWQ8(groups, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
     if name == "muon":
         from .muon import Muon
 

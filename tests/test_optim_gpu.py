@@ -104,3 +104,48 @@ def test_host_state_optimizer_matches_the_device_optimizer_bit_for_bit(host_comp
         sa, sb = ref.state[a], off.state[b]
         for key in ("exp_avg", "exp_avg_sq"):        # host-resident moments are kept flat
             assert torch.equal(sa[key].cpu().reshape(-1).view(torch.int16), sb[key].cpu().reshape(-1).view(torch.int16)), (n, key)
+
+
+@pytest.mark.parametrize("grad_dtype", [torch.bfloat16, torch.float32])
+def test_adamw_q8_kernel_equals_its_tensor_op_statement(grad_dtype):
+    """8-bit moments and 24-bit weights: the CUDA step against the CPU twin, bit for bit, over several steps (tensors whose
+    length is not a multiple of the group, of a lane's eight elements, or of a block; one whose storage is offset so that
+    the vector path is refused)."""
+    from halo_b200.optim.adamw_q8 import AdamWQ8
+
+    sizes = [1, 7, 256, 1000, 2048, 2049, 16385, 100003]
+    ps, gs = _make(sizes, seed=5)
+    cpu = [(n, torch.nn.Parameter(p.clone())) for n, p in ps]
+    gpu = [(n, torch.nn.Parameter(p.clone().cuda())) for n, p in ps]
+    # an unaligned view: the parameter starts 2 bytes into its storage
+    base = torch.randn(4097).bfloat16()
+    cpu.append(("offset.w", torch.nn.Parameter(base.clone()[1:])))
+    gpu.append(("offset.w", torch.nn.Parameter(base.clone().cuda()[1:])))
+    gs.append(torch.randn(4096).bfloat16() * 0.01)
+    oc = AdamWQ8(cpu, lr=1e-3, weight_decay=0.01)
+    og = AdamWQ8(gpu, lr=1e-3, weight_decay=0.01)
+    for step in range(4):
+        for (_, pc), (_, pg), g in zip(cpu, gpu, gs):
+            gg = (g * (step + 1)).to(grad_dtype)
+            if grad_dtype != pc.dtype:
+                pc.grad_dtype = grad_dtype
+                pg.grad_dtype = grad_dtype
+            pc.grad = gg.clone()
+            pg.grad = gg.clone().cuda()
+        scale = torch.tensor([0.37])
+        oc.defer_grad_scale(scale)
+        og.defer_grad_scale(scale.cuda())
+        oc.step()
+        og.step()
+        for (n, pc), (_, pg) in zip(cpu, gpu):
+            sc, sg = oc.state[pc], og.state[pg]
+            assert torch.equal(pc.data, pg.data.cpu()), f"param {n} differs at step {step}"
+            for key in ("corr", "exp_avg_q", "exp_avg_sq_q", "exp_avg_scale", "exp_avg_sq_scale"):
+                assert torch.equal(sc[key], sg[key].cpu()), f"{key} of {n} differs at step {step}"
+    skip = torch.ones(1, dtype=torch.int32, device="cuda")
+    before = [pg.detach().clone() for _, pg in gpu]
+    for (_, pg), g in zip(gpu, gs):
+        pg.grad = g.to(grad_dtype).cuda()
+    og.arm_skip(skip)
+    og.step()
+    assert all(torch.equal(a, pg) for a, (_, pg) in zip(before, gpu))
