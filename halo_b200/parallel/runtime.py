@@ -243,7 +243,7 @@ class ParallelRuntime:
         if self.context_parallel is not None:
             from halo_b200.parallel.context_parallel import slice_batch
 
-            return slice_batch(batch, self.context_parallel.rank, self.context_parallel.size)
+            return slice_batch(batch, self.context_parallel.rank, self.context_parallel.size, self.context_parallel.balance)
         if self.tensor_parallel is not None:
             tp = self.tensor_parallel
             lo, hi = chunk_bounds(batch.n_tokens, tp.size, tp.rank)

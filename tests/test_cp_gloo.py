@@ -9,18 +9,57 @@ from halo_b200.parallel.context_parallel import make_layout
 from tests.common.gloo import run_gloo_ranks
 
 
-def test_layout_sources_and_returns_are_mirror_images():
-    cu = np.array([0, 10, 70, 75, 200, 256])
-    lays = [make_layout(cu, r, 4) for r in range(4)]          # chunks of 64 tokens
-    assert [(l.lo, l.hi, l.p0) for l in lays] == [(0, 64, 0), (64, 128, 10), (128, 192, 75), (192, 256, 75)]
-    assert lays[1].sources == [(0, 10, 54, 0)] and lays[1].cu_ext.tolist() == [0, 60, 65, 118]
-    assert lays[3].sources == [(1, 11, 53, 0), (2, 0, 64, 53)]
-    for r, l in enumerate(lays):                               # every pull has its matching gradient return
-        for s, src_row, n, dst_row in l.sources:
-            assert (r, src_row, n, dst_row) in lays[s].returns
-    assert sum(len(l.returns) for l in lays) == sum(len(l.sources) for l in lays)
-    with pytest.raises(ValueError):
+def test_balanced_layout_snaps_cuts_to_document_tiles_and_pairs_early_with_late_pieces():
+    cu = np.array([0, 10, 700, 750, 2000, 2560])
+    lays = [make_layout(cu, r, 2) for r in range(2)]            # four pieces; nominal cuts at 640, 1280, 1920
+    assert lays[0].bounds.tolist() == [0, 650, 1262, 1902, 2560]             # 10 + 5 * 128, 750 + 4 * 128, 750 + 9 * 128
+    assert lays[0].owner.tolist() == [0, 1, 1, 0] and lays[0].loc.tolist() == [0, 0, 612, 650]
+    assert lays[0].rows_of_rank == [650 + 658, 612 + 640]
+    assert lays[1].local_index().tolist() == list(range(650, 1902))
+    assert lays[0].to_local(1902) == (0, 650) and lays[0].to_local(700) == (1, 50)
+    # what a rank produces for foreign keys is exactly what the owners expect back
+    for r, lay in enumerate(lays):
+        for rank, my_row, n, src_row in lay.returns:
+            glo = next(lo for lo, hi, srow in lays[rank].written[rank] if srow == src_row)
+            assert lays[r].to_local(glo) == (r, my_row)
+    assert sum(len(l.returns) for l in lays) == sum(len(w) for w in lays[0].written)
+    # rank 0's late piece sees document [750, 2000) from its start: it produces dK/dV for rank 1's rows 750..1902
+    assert (750, 1262, 100) in lays[0].written[0] and (1262, 1902, 612) in lays[0].written[0]
+    with pytest.raises(ValueError, match="without tokens"):
         make_layout(np.array([0, 10]), 0, 4)
+    contiguous = make_layout(cu, 1, 2, balance=False)
+    assert contiguous.bounds.tolist() == [0, 1262, 2560] and contiguous.owner.tolist() == [0, 1]
+
+
+def test_work_lists_cover_the_causal_document_mask_exactly_once():
+    from halo_b200.parallel.context_parallel import build_cp_plan, covered_pairs
+
+    rng = np.random.default_rng(0)
+    for _ in range(6):
+        lens = np.concatenate([rng.integers(1, 700, size=int(rng.integers(1, 6))), [1100]])
+        rng.shuffle(lens)
+        cu = np.concatenate([[0], np.cumsum(lens)])
+        T = int(cu[-1])
+        want = np.zeros((T, T), bool)
+        for s, e in zip(cu[:-1], cu[1:]):
+            want[s:e, s:e] = np.tril(np.ones((e - s, e - s), bool))
+        for cp, balance in ((2, True), (4, True), (4, False)):
+            got_q, got_k = np.zeros((T, T), bool), np.zeros((T, T), bool)
+            for r in range(cp):
+                lay = make_layout(cu, r, cp, balance)
+                plan = build_cp_plan(lay, None)
+                f, k = covered_pairs(lay, plan)
+                assert not (got_q & f).any() and not (got_k & k).any()
+                got_q |= f
+                got_k |= k
+                for item in plan.cp_items[1]:                 # a key tile and each query segment lie in one piece
+                    k0, e = item[0], item[3]
+                    assert lay.piece_of(k0) == lay.piece_of(min(k0 + 127, e - 1))
+                    for qb, n in ((item[1], item[2]), (item[4], item[5])):
+                        if n:
+                            assert lay.owner[lay.piece_of(qb)] == r and (qb - k0) % 64 == 0
+                            assert lay.piece_of(min(qb + 64 * n, e) - 1) == lay.piece_of(qb)
+            assert (got_q == want).all() and (got_k == want).all()
 
 
 def _worker(rank, world):
@@ -35,7 +74,7 @@ def _worker(rank, world):
 
     cfg = dataclasses.replace(PRESETS["tiny-moe"](), num_hidden_layers=2)
     rng = np.random.default_rng(0)
-    docs = [rng.integers(0, cfg.vocab_size, size=n) for n in (37, 90, 5, 124)]     # 256 tokens; documents straddle cuts
+    docs = [rng.integers(0, cfg.vocab_size, size=n) for n in (370, 900, 50, 1240)]     # 2560 tokens; documents straddle cuts
     full_batch = pack_documents(docs)
     norm = float(full_batch.n_scored)
 
@@ -63,3 +102,23 @@ def _worker(rank, world):
 @pytest.mark.parametrize("world", [2, 4])
 def test_chunked_row_matches_whole_row(world):
     run_gloo_ranks(_worker, world, timeout=120.0)
+
+
+def test_long_document_work_is_balanced_across_ranks():
+    """One long document: with paired early / late pieces every rank visits the same number of (query tile, key tile)
+    pairs; contiguous chunks give the last rank several times the first rank's share."""
+    from halo_b200.parallel.context_parallel import build_cp_plan
+
+    cu = np.array([0, 16384])
+
+    def pairs(balance):
+        out = []
+        for r in range(4):
+            plan = build_cp_plan(make_layout(cu, r, 4, balance), None)
+            out.append(sum(n64 for _, _, n64, _ in plan.cp_items[0]))
+        return out
+
+    balanced, contiguous = pairs(True), pairs(False)
+    assert max(balanced) - min(balanced) <= 2 * 4          # at most the diagonal tiles differ
+    assert max(contiguous) > 5 * min(contiguous)
+    assert sum(balanced) == sum(contiguous)
