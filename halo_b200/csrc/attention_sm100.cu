@@ -63,6 +63,28 @@ __device__ __forceinline__ uint32_t swz_off(int row, int col) {
     return (uint32_t)(row * 128 + ((((col >> 3) ^ row) & 7) << 4));
 }
 
+// Context parallelism: the kernels work in the packed row's GLOBAL row numbers (masks, document ends, tile starts);
+// only addresses are translated. A row belongs to one piece of the row; a piece has an owner rank and a first row in that
+// rank's local order. Queries, outputs and statistics are local tensors; a key / value tile is read from its owner's
+// published buffer through that rank's tensor map (plain per-CTA TMA loads; the memory may be a peer GPU's).
+struct CpMap {
+    int n_pieces;
+    int my_rank;
+    int bound[17];   // global first row of every piece, then the row's length
+    int owner[16];
+    int loc[16];     // first row of the piece in its owner's local order
+    int stage[16];   // row of a foreign piece's first row in this rank's dK / dV staging buffer (-1: none)
+};
+struct PeerMaps {
+    CUtensorMap k[8];
+    CUtensorMap v[8];
+};
+__device__ __forceinline__ int cp_piece(const CpMap& m, int row) {
+    int pc = 0;
+    while (pc + 1 < m.n_pieces && row >= m.bound[pc + 1]) ++pc;
+    return pc;
+}
+
 struct FwdWork {
     int q0;        // first query row of the tile
     int kv0;       // first key row the tile may see (its document's first row)
@@ -318,6 +340,14 @@ struct BwdParams {
     int Hq, Hkv;
     float scale;
     int* status;
+    void* dK_stage;      // context parallelism: dK / dV of key tiles another rank owns ([rows, ld_stage])
+    void* dV_stage;
+    long long ld_stage;
+};
+
+struct BwdKvWorkCp {     // context parallelism: the local queries that see a key tile, as up to two runs (one per local piece)
+    int kv0, q_begin, n_q, q_end;
+    int q_begin2, n_q2, pad0, pad1;
 };
 
 constexpr int kBwdThreads = 192;
@@ -788,10 +818,11 @@ constexpr int kBwdKv2Stages = 5;
 constexpr int kBwdKv2Tiles = 2 * kTileBytes + kBwdKv2Stages * 2 * kHalfTile;     // 229,376
 constexpr int kBwdKv2Smem = kBwdKv2Tiles + 2048;                                                 // barriers, scalars, statistics
 
+template <bool kCP>
 __global__ void __launch_bounds__(kBwd2Threads, 1)
 attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                      const BwdParams p) {
+                      const BwdParams p, const __grid_constant__ PeerMaps peers, const __grid_constant__ CpMap cp) {
     if (status_poisoned(p.status)) return;
     extern __shared__ __align__(1024) uint8_t smem_b2[];
     const uint32_t base = smem_u32(smem_b2);
@@ -811,8 +842,27 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const uint32_t sK = base, sV = base + kTileBytes, sQdO = base + 2 * kTileBytes;
     const int kv_head = blockIdx.x;
     const int group = p.Hq / p.Hkv;
-    const BwdKvWork w = reinterpret_cast<const BwdKvWork*>(p.work)[blockIdx.y];
-    const int n_iter = w.n_q * group;
+    BwdKvWorkCp w;
+    if (kCP) {
+        w = reinterpret_cast<const BwdKvWorkCp*>(p.work)[blockIdx.y];
+    } else {
+        const BwdKvWork w4 = reinterpret_cast<const BwdKvWork*>(p.work)[blockIdx.y];
+        w.kv0 = w4.kv0; w.q_begin = w4.q_begin; w.n_q = w4.n_q; w.q_end = w4.q_end;
+        w.q_begin2 = 0; w.n_q2 = 0; w.pad0 = 0; w.pad1 = 0;
+    }
+    const int n_iter = (w.n_q + w.n_q2) * group;
+    // global first query row of 64-query sub-tile `sub`, and what to subtract from a global query row for its local row
+    int q_shift1 = 0, q_shift2 = 0;
+    if (kCP) {
+        const int p1 = cp_piece(cp, w.q_begin);
+        q_shift1 = cp.bound[p1] - cp.loc[p1];
+        if (w.n_q2 > 0) {
+            const int p2 = cp_piece(cp, w.q_begin2);
+            q_shift2 = cp.bound[p2] - cp.loc[p2];
+        }
+    }
+    auto q_row = [&](int sub) -> int { return sub < w.n_q ? w.q_begin + sub * 64 : w.q_begin2 + (sub - w.n_q) * 64; };
+    auto q_shift = [&](int sub) -> int { return sub < w.n_q ? q_shift1 : q_shift2; };
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -838,15 +888,24 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     if (warp == 0) {
         if (lane == 0) {
             mbar_expect_tx(bar(kKv), 2 * kTileBytes);
-            tma_load_2d(sK, &tmK, bar(kKv), kv_head * kHd, w.kv0);
-            tma_load_2d(sK + 16384, &tmK, bar(kKv), kv_head * kHd + 64, w.kv0);
-            tma_load_2d(sV, &tmV, bar(kKv), kv_head * kHd, w.kv0);
-            tma_load_2d(sV + 16384, &tmV, bar(kKv), kv_head * kHd + 64, w.kv0);
+            const CUtensorMap* mapK = &tmK;
+            const CUtensorMap* mapV = &tmV;
+            int k_loc = w.kv0;
+            if (kCP) {
+                const int pk = cp_piece(cp, w.kv0);
+                mapK = &peers.k[cp.owner[pk]];
+                mapV = &peers.v[cp.owner[pk]];
+                k_loc = w.kv0 - cp.bound[pk] + cp.loc[pk];
+            }
+            tma_load_2d(sK, mapK, bar(kKv), kv_head * kHd, k_loc);
+            tma_load_2d(sK + 16384, mapK, bar(kKv), kv_head * kHd + 64, k_loc);
+            tma_load_2d(sV, mapV, bar(kKv), kv_head * kHd, k_loc);
+            tma_load_2d(sV + 16384, mapV, bar(kKv), kv_head * kHd + 64, k_loc);
             for (int it = 0; it < n_iter; ++it) {
                 const int st = it % kBwdKv2Stages;
                 if (!mbar_wait(bar(kQEmpty + st), ((it / kBwdKv2Stages) & 1) ^ 1u, abort_flag, p.status)) break;
                 const int h = kv_head * group + it % group;
-                const int qr = w.q_begin + (it / group) * 64;
+                const int qr = q_row(it / group) - q_shift(it / group);     // local row of the sub-tile's first query
                 const uint32_t full = bar(kQFull + st);
                 const uint32_t sQ = sQdO + st * 2 * kHalfTile, sdO = sQ + kHalfTile;
                 mbar_expect_tx(full, 2 * kHalfTile);
@@ -924,15 +983,16 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         auto fetch_stat = [&](int it) -> float {
             if (ew_tid >= 128 || it >= n_iter) return 0.f;
             const int h = kv_head * group + it % group;
-            const long long qa = (long long)w.q_begin + (it / group) * 64 + (ew_tid & 63);
+            const long long qa = (long long)q_row(it / group) + (ew_tid & 63);
             const bool in = qa < w.q_end;
-            if (ew_tid < 64) return in ? p.lse[(long long)h * p.T + qa] * kLog2e : INFINITY;
-            return in ? p.delta[(long long)h * p.T + qa] : 0.f;
+            const long long ql = qa - q_shift(it / group);
+            if (ew_tid < 64) return in ? p.lse[(long long)h * p.T + ql] * kLog2e : INFINITY;
+            return in ? p.delta[(long long)h * p.T + ql] : 0.f;
         };
         float stat = fetch_stat(g);
         for (int it = g; it < n_iter; it += 2) {
             const int k = it >> 1;                                // this group's step count: parity of its barriers
-            const int qr = w.q_begin + (it / group) * 64;
+            const int qr = q_row(it / group);
             // Every thread of the group meets at the two barriers below in every one of its steps, also after a wait has
             // given up (it then skips the step's work): nobody may leave the loop early and strand the others.
             ew_bar_sync(g);                                       // the previous step's readers of the statistics are done
@@ -988,9 +1048,25 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         // the accumulators: group 0 stores dK, group 1 stores dV (each thread one row, 64 of its 128 columns)
         if (ok && mbar_wait(bar(kAccDone), 0, abort_flag, p.status)) {
             tc_fence_after();
-            const bool live = key_abs < w.q_end;
-            const long long ld = g == 0 ? p.ld_dk : p.ld_dv;
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(g == 0 ? p.dK : p.dV) + key_abs * ld + kv_head * kHd + half * 64;
+            bool live = key_abs < w.q_end;
+            long long ld = g == 0 ? p.ld_dk : p.ld_dv;
+            void* out_base = g == 0 ? p.dK : p.dV;
+            long long out_row = key_abs;
+            if (kCP) {
+                const int pk = cp_piece(cp, w.kv0);
+                if (cp.owner[pk] == cp.my_rank) {
+                    out_row = key_abs - cp.bound[pk] + cp.loc[pk];
+                } else {
+                    out_base = g == 0 ? p.dK_stage : p.dV_stage;
+                    ld = p.ld_stage;
+                    out_row = key_abs - cp.bound[pk] + cp.stage[pk];
+                    if (cp.stage[pk] < 0) {             // no staging was planned for this piece: record it, write nothing
+                        live = false;
+                        if (key == 0 && half == 0 && p.status) atomicCAS(p.status, kStatusOk, kStatusBounds);
+                    }
+                }
+            }
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out_base) + out_row * ld + kv_head * kHd + half * 64;
             const uint32_t tAcc = (g == 0 ? tDK : tDV) + lane_base + half * 64;
 #pragma unroll 1
             for (int cc = 0; cc < 64; cc += 32) {
@@ -1028,10 +1104,11 @@ constexpr int kBwdQ2Stages = 5;
 constexpr int kBwdQ2Tiles = 2 * kTileBytes + kBwdQ2Stages * 2 * kHalfTile;   // 229,376
 constexpr int kBwdQ2Smem = kBwdQ2Tiles + 512;
 
+template <bool kCP>
 __global__ void __launch_bounds__(kBwd2Threads, 1)
 attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                    const BwdParams p) {
+                    const BwdParams p, const __grid_constant__ PeerMaps peers, const __grid_constant__ CpMap cp) {
     if (status_poisoned(p.status)) return;
     extern __shared__ __align__(1024) uint8_t smem_q2[];
     const uint32_t base = smem_u32(smem_q2);
@@ -1050,6 +1127,11 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int head = blockIdx.x;
     const int kv_head = head / (p.Hq / p.Hkv);
     const BwdQWork w = reinterpret_cast<const BwdQWork*>(p.work)[blockIdx.y];
+    int q_shift = 0;                    // global query row - q_shift = local row (queries, dO, statistics, dQ are local)
+    if (kCP) {
+        const int pq = cp_piece(cp, w.q0);
+        q_shift = cp.bound[pq] - cp.loc[pq];
+    }
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -1069,21 +1151,30 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (warp == 0) {
         if (lane == 0) {
             mbar_expect_tx(bar(kQ), 2 * kTileBytes);
-            tma_load_2d(sQ, &tmQ, bar(kQ), head * kHd, w.q0);
-            tma_load_2d(sQ + 16384, &tmQ, bar(kQ), head * kHd + 64, w.q0);
-            tma_load_2d(sdO, &tmdO, bar(kQ), head * kHd, w.q0);
-            tma_load_2d(sdO + 16384, &tmdO, bar(kQ), head * kHd + 64, w.q0);
+            const int q_loc = w.q0 - q_shift;
+            tma_load_2d(sQ, &tmQ, bar(kQ), head * kHd, q_loc);
+            tma_load_2d(sQ + 16384, &tmQ, bar(kQ), head * kHd + 64, q_loc);
+            tma_load_2d(sdO, &tmdO, bar(kQ), head * kHd, q_loc);
+            tma_load_2d(sdO + 16384, &tmdO, bar(kQ), head * kHd + 64, q_loc);
             for (int j = 0; j < w.n_kv; ++j) {
                 const int st = j % kBwdQ2Stages;
                 if (!mbar_wait(bar(kKvEmpty + st), ((j / kBwdQ2Stages) & 1) ^ 1u, abort_flag, p.status)) break;
                 const uint32_t full = bar(kKvFull + st);
                 const uint32_t sK = sKV + st * 2 * kHalfTile, sV = sK + kHalfTile;
-                const int kr = w.kv0 + j * 64;
+                int kr = w.kv0 + j * 64;
+                const CUtensorMap* mapK = &tmK;
+                const CUtensorMap* mapV = &tmV;
+                if (kCP) {                       // the sub-tile's owner and its row in that rank's published buffer
+                    const int pk = cp_piece(cp, kr);
+                    mapK = &peers.k[cp.owner[pk]];
+                    mapV = &peers.v[cp.owner[pk]];
+                    kr = kr - cp.bound[pk] + cp.loc[pk];
+                }
                 mbar_expect_tx(full, 2 * kHalfTile);
-                tma_load_2d(sK, &tmK, full, kv_head * kHd, kr);
-                tma_load_2d(sK + 8192, &tmK, full, kv_head * kHd + 64, kr);
-                tma_load_2d(sV, &tmV, full, kv_head * kHd, kr);
-                tma_load_2d(sV + 8192, &tmV, full, kv_head * kHd + 64, kr);
+                tma_load_2d(sK, mapK, full, kv_head * kHd, kr);
+                tma_load_2d(sK + 8192, mapK, full, kv_head * kHd + 64, kr);
+                tma_load_2d(sV, mapV, full, kv_head * kHd, kr);
+                tma_load_2d(sV + 8192, mapV, full, kv_head * kHd + 64, kr);
             }
         }
     } else if (warp == 1) {
@@ -1137,8 +1228,9 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const float c = p.scale * kLog2e;
         const long long q_abs = (long long)w.q0 + row;
         const bool in = q_abs < w.q_end;
-        const float lse2 = in ? p.lse[(long long)head * p.T + q_abs] * kLog2e : INFINITY;
-        const float dl = in ? p.delta[(long long)head * p.T + q_abs] : 0.f;
+        const long long q_local = q_abs - q_shift;
+        const float lse2 = in ? p.lse[(long long)head * p.T + q_local] * kLog2e : INFINITY;
+        const float dl = in ? p.delta[(long long)head * p.T + q_local] : 0.f;
         const uint32_t tS = tm0 + 128 * g + lane_base + c0, tDP = tS + 64;
         bool ok = true;
         for (int j = g; j < w.n_kv; j += 2) {
@@ -1179,7 +1271,7 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (ok && mbar_wait(bar(kAccDone), 0, abort_flag, p.status)) {
             tc_fence_after();
             const int col = g * 64 + half * 32;
-            __nv_bfloat16* dq = reinterpret_cast<__nv_bfloat16*>(p.dQ) + q_abs * p.ld_dq + head * kHd + col;
+            __nv_bfloat16* dq = reinterpret_cast<__nv_bfloat16*>(p.dQ) + q_local * p.ld_dq + head * kHd + col;
             uint32_t r[32];
             tmem_ld_32x32(tDQ + lane_base + col, r);
             tmem_ld_wait();
@@ -1464,9 +1556,11 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 // takes its A operand from tensor memory. Shared memory then carries only Q, K and V: a third less traffic per step on
 // the resource that limits this kernel (operand fetches of the products and the K/V loads share one 128-byte-per-clock
 // port), and the proxy fence between the softmax's stores and the product disappears.
+template <bool kCP>
 __global__ void __maxnreg__(128)
 attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+                 const __grid_constant__ CUtensorMap tmV, const AttnParams p, const __grid_constant__ PeerMaps peers,
+                 const __grid_constant__ CpMap cp) {
     if (status_poisoned(p.status)) return;
     extern __shared__ __align__(1024) uint8_t smem3[];
     const uint32_t base = smem_u32(smem3);
@@ -1485,6 +1579,11 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int head = blockIdx.x;
     const int kv_head = head / (p.Hq / p.Hkv);
     const FwdWork w = p.work[blockIdx.y];
+    int q_shift = 0;                    // global query row - q_shift = local row (queries, outputs, statistics are local)
+    if (kCP) {
+        const int pq = cp_piece(cp, w.q0);
+        q_shift = cp.bound[pq] - cp.loc[pq];
+    }
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -1513,19 +1612,27 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (warp == 4) {
         if (lane == 0) {
             mbar_expect_tx(bar_q, kTileBytes);
-            tma_load_2d(sQ, &tmQ, bar_q, head * kHd, w.q0);
-            tma_load_2d(sQ + 16384, &tmQ, bar_q, head * kHd + 64, w.q0);
+            tma_load_2d(sQ, &tmQ, bar_q, head * kHd, w.q0 - q_shift);
+            tma_load_2d(sQ + 16384, &tmQ, bar_q, head * kHd + 64, w.q0 - q_shift);
             for (int j = 0; j < w.n_kv; ++j) {
                 const int st = j & 1;
                 if (!mbar_wait(smem_u32(&bars[3 + st]), ((j >> 1) & 1) ^ 1u, abort_flag, p.status)) break;
                 const uint32_t full = smem_u32(&bars[1 + st]);
                 const uint32_t sK = sKV + st * 2 * kHalfTile, sV = sK + kHalfTile;
-                const int kr = w.kv0 + j * 64;
+                int kr = w.kv0 + j * 64;
+                const CUtensorMap* mapK = &tmK;
+                const CUtensorMap* mapV = &tmV;
+                if (kCP) {                       // the tile's owner and its row in that rank's published buffer
+                    const int pk = cp_piece(cp, kr);
+                    mapK = &peers.k[cp.owner[pk]];
+                    mapV = &peers.v[cp.owner[pk]];
+                    kr = kr - cp.bound[pk] + cp.loc[pk];
+                }
                 mbar_expect_tx(full, 2 * kHalfTile);
-                tma_load_2d(sK, &tmK, full, kv_head * kHd, kr);
-                tma_load_2d(sK + 8192, &tmK, full, kv_head * kHd + 64, kr);
-                tma_load_2d(sV, &tmV, full, kv_head * kHd, kr);
-                tma_load_2d(sV + 8192, &tmV, full, kv_head * kHd + 64, kr);
+                tma_load_2d(sK, mapK, full, kv_head * kHd, kr);
+                tma_load_2d(sK + 8192, mapK, full, kv_head * kHd + 64, kr);
+                tma_load_2d(sV, mapV, full, kv_head * kHd, kr);
+                tma_load_2d(sV + 8192, mapV, full, kv_head * kHd + 64, kr);
             }
         }
     } else if (warp == 5) {
@@ -1656,7 +1763,8 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             tc_fence_after();
             const bool live = q_abs < w.q_end;
             const float inv = 1.f / l;
-            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.O) + q_abs * p.ldo + head * kHd;
+            const long long q_local = q_abs - q_shift;
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.O) + q_local * p.ldo + head * kHd;
 #pragma unroll 1
             for (int cc = 0; cc < 128; cc += 32) {
                 uint32_t r[32];
@@ -1672,7 +1780,7 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                             pack_bf16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv));
                 }
             }
-            if (live) p.lse[(long long)head * p.T + q_abs] = m_ref * p.scale + logf(l);
+            if (live) p.lse[(long long)head * p.T + q_local] = m_ref * p.scale + logf(l);
         }
     }
 
@@ -1693,6 +1801,33 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
 static int set_smem(const void* fn, int bytes) {
     return cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess ? 0 : -10;
+}
+
+// what the kernels get when context parallelism is off (never read)
+static PeerMaps g_no_peers{};
+static CpMap g_no_cp{};
+
+// Tensor maps over every rank's published key / value buffer (box of `box_rows` rows) and the piece table.
+static int fill_cp(PeerMaps* peers, CpMap* cp, void* const* kv_ptrs, int n_ranks, long long kv_rows, long long kv_ld, int v_col,
+                   int Hkv, const int* m, int box_rows) {
+    memset(peers, 0, sizeof(*peers));
+    for (int r = 0; r < 8; ++r) {
+        const int src = r < n_ranks ? r : 0;              // unused slots repeat rank 0's maps (valid, never selected)
+        const char* base = reinterpret_cast<const char*>(kv_ptrs[src]);
+        if (make_tmap_bf16(&peers->k[r], base, kv_rows, (long long)Hkv * kHd, kv_ld, box_rows)) return -1;
+        if (make_tmap_bf16(&peers->v[r], base + (long long)v_col * 2, kv_rows, (long long)Hkv * kHd, kv_ld, box_rows)) return -1;
+    }
+    cp->n_pieces = m[0];
+    cp->my_rank = m[1];
+    if (cp->n_pieces < 1 || cp->n_pieces > 16 || cp->my_rank < 0 || cp->my_rank >= n_ranks) return -2;
+    for (int i = 0; i < 17; ++i) cp->bound[i] = m[2 + i];
+    for (int i = 0; i < 16; ++i) {
+        cp->owner[i] = m[19 + i];
+        cp->loc[i] = m[35 + i];
+        cp->stage[i] = m[51 + i];
+        if (i < cp->n_pieces && (cp->owner[i] < 0 || cp->owner[i] >= n_ranks)) return -3;
+    }
+    return 0;
 }
 
 }  // namespace halo
@@ -1757,13 +1892,40 @@ int halo_attn_fwd3(const void* q, const void* k, const void* v, void* o, float* 
     if (make_tmap_bf16(&tv, v, T, (long long)Hkv * kHd, ldv, 64)) return -4;
     static bool cfg = false;
     if (!cfg) {
-        if (set_smem((const void*)attn_fwd3_kernel, kFwd2Smem)) return -10;
-        cudaFuncSetAttribute((const void*)attn_fwd3_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+        if (set_smem((const void*)attn_fwd3_kernel<false>, kFwd2Smem)) return -10;
+        cudaFuncSetAttribute((const void*)attn_fwd3_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout,
                              cudaSharedmemCarveoutMaxShared);
         cfg = true;
     }
     AttnParams p{reinterpret_cast<const FwdWork*>(work), o, lse, ldo, T, Hq, Hkv, scale, status};
-    attn_fwd3_kernel<<<dim3(Hq, n_tiles), kFwdThreads, kFwd2Smem, (cudaStream_t)stream>>>(tq, tk, tv, p);
+    attn_fwd3_kernel<false><<<dim3(Hq, n_tiles), kFwdThreads, kFwd2Smem, (cudaStream_t)stream>>>(tq, tk, tv, p, g_no_peers, g_no_cp);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Context-parallel forward: q, o, lse are this rank's local rows; kv_ptrs[r] is rank r's published [kv_rows, kv_ld] buffer
+// (keys in columns [0, v_col), values from column v_col), possibly a peer GPU's memory. work: {q0, document start,
+// 64-key sub-tiles, document end} in the row's global numbering; cp_map: n_pieces, my rank, bound[17], owner[16], loc[16],
+// stage[16] (host ints).
+int halo_attn_cp_fwd(const void* q, void* const* kv_ptrs, int n_ranks, long long kv_rows, long long kv_ld, int v_col,
+                     void* o, float* lse, const void* work, int n_tiles, long long T_local, int Hq, int Hkv,
+                     int head_dim, long long ldq, long long ldo, float scale, const int* cp_map, int* status,
+                     void* stream) {
+    if (head_dim != kHd || Hq % Hkv || n_ranks < 1 || n_ranks > 8) return -1;
+    if (n_tiles == 0) return 0;
+    CUtensorMap tq;
+    if (make_tmap_bf16(&tq, q, T_local, (long long)Hq * kHd, ldq, 128)) return -2;
+    PeerMaps peers;
+    CpMap cp;
+    if (fill_cp(&peers, &cp, kv_ptrs, n_ranks, kv_rows, kv_ld, v_col, Hkv, cp_map, 64)) return -3;
+    static bool cfg = false;
+    if (!cfg) {
+        if (set_smem((const void*)attn_fwd3_kernel<true>, kFwd2Smem)) return -10;
+        cudaFuncSetAttribute((const void*)attn_fwd3_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+        cfg = true;
+    }
+    AttnParams p{reinterpret_cast<const FwdWork*>(work), o, lse, ldo, T_local, Hq, Hkv, scale, status};
+    attn_fwd3_kernel<true><<<dim3(Hq, n_tiles), kFwdThreads, kFwd2Smem, (cudaStream_t)stream>>>(tq, peers.k[0], peers.v[0], p, peers, cp);
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -1830,22 +1992,64 @@ int halo_attn_bwd(const void* q, const void* k, const void* v, const void* o, co
     if (!cfg) {
         if (set_smem((const void*)attn_bwd_dkdv_kernel, kBwdKvSmem)) return -10;
         if (set_smem((const void*)attn_bwd_dq_kernel, kBwdQSmem)) return -10;
-        if (set_smem((const void*)attn_bwd_dkdv2_kernel, kBwdKv2Smem)) return -10;
-        if (set_smem((const void*)attn_bwd_dq2_kernel, kBwdQ2Smem)) return -10;
+        if (set_smem((const void*)attn_bwd_dkdv2_kernel<false>, kBwdKv2Smem)) return -10;
+        if (set_smem((const void*)attn_bwd_dq2_kernel<false>, kBwdQ2Smem)) return -10;
         const char* e = getenv("HALO_ATTN_BWD_VARIANT");      // 2 (default): double-buffered form; 1: the first form
         if (e && atoi(e) == 1) variant = 1;
         cfg = true;
     }
     BwdParams p{kv_work, lse, delta, dq, dk, dv, ld_dq, ld_dk, ld_dv, T, Hq, Hkv, scale, status};
     if (n_kv_tiles > 0) {
-        if (variant == 2) attn_bwd_dkdv2_kernel<<<dim3(Hkv, n_kv_tiles), kBwd2Threads, kBwdKv2Smem, s>>>(tq64, tk, tv, tdo64, p);
+        if (variant == 2)
+            attn_bwd_dkdv2_kernel<false><<<dim3(Hkv, n_kv_tiles), kBwd2Threads, kBwdKv2Smem, s>>>(tq64, tk, tv, tdo64, p, g_no_peers, g_no_cp);
         else attn_bwd_dkdv_kernel<<<dim3(Hkv, n_kv_tiles), kBwdThreads, kBwdKvSmem, s>>>(tq64, tk, tv, tdo64, p);
     }
     p.work = q_work;
     if (n_q_tiles > 0) {
-        if (variant == 2) attn_bwd_dq2_kernel<<<dim3(Hq, n_q_tiles), kBwd2Threads, kBwdQ2Smem, s>>>(tq, tk64, tv64, tdo, p);
+        if (variant == 2)
+            attn_bwd_dq2_kernel<false><<<dim3(Hq, n_q_tiles), kBwd2Threads, kBwdQ2Smem, s>>>(tq, tk64, tv64, tdo, p, g_no_peers, g_no_cp);
         else attn_bwd_dq_kernel<<<dim3(Hq, n_q_tiles), kBwdThreads, kBwdQSmem, s>>>(tq, tk64, tv64, tdo, p);
     }
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Context-parallel backward. q, o, d_o, lse, delta, dq, dk, dv: this rank's local rows; kv_ptrs as in the forward.
+// dk_stage / dv_stage ([rows, ld_stage]): where dK / dV of key tiles another rank owns are written (that rank adds them).
+// kv_work: {k0, q_begin, n_q, doc end, q_begin2, n_q2, 0, 0} (8 ints); q_work: as the forward's work list.
+int halo_attn_cp_bwd(const void* q, void* const* kv_ptrs, int n_ranks, long long kv_rows, long long kv_ld, int v_col,
+                     const void* o, const void* d_o, const float* lse, float* delta, void* dq, void* dk, void* dv,
+                     void* dk_stage, void* dv_stage, long long ld_stage, const void* kv_work, int n_kv_tiles,
+                     const void* q_work, int n_q_tiles, long long T_local, int Hq, int Hkv, int head_dim, long long ldq,
+                     long long ldo, long long ld_do, long long ld_dq, long long ld_dk, long long ld_dv, float scale,
+                     const int* cp_map, int* status, void* stream) {
+    if (head_dim != kHd || Hq % Hkv || n_ranks < 1 || n_ranks > 8) return -1;
+    if (T_local == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    attn_delta_kernel<<<(unsigned)((T_local * Hq + 7) / 8), 256, 0, s>>>(
+        (const __nv_bfloat16*)d_o, (const __nv_bfloat16*)o, delta, T_local, Hq, ld_do, ldo);
+    CUtensorMap tq, tdo, tq64, tdo64;
+    if (make_tmap_bf16(&tq, q, T_local, (long long)Hq * kHd, ldq, 128)) return -2;
+    if (make_tmap_bf16(&tdo, d_o, T_local, (long long)Hq * kHd, ld_do, 128)) return -5;
+    if (make_tmap_bf16(&tq64, q, T_local, (long long)Hq * kHd, ldq, 64)) return -6;
+    if (make_tmap_bf16(&tdo64, d_o, T_local, (long long)Hq * kHd, ld_do, 64)) return -9;
+    PeerMaps peers128, peers64;
+    CpMap cp;
+    if (fill_cp(&peers128, &cp, kv_ptrs, n_ranks, kv_rows, kv_ld, v_col, Hkv, cp_map, 128)) return -3;
+    if (fill_cp(&peers64, &cp, kv_ptrs, n_ranks, kv_rows, kv_ld, v_col, Hkv, cp_map, 64)) return -4;
+    static bool cfg = false;
+    if (!cfg) {
+        if (set_smem((const void*)attn_bwd_dkdv2_kernel<true>, kBwdKv2Smem)) return -10;
+        if (set_smem((const void*)attn_bwd_dq2_kernel<true>, kBwdQ2Smem)) return -10;
+        cfg = true;
+    }
+    BwdParams p{kv_work, lse, delta, dq, dk, dv, ld_dq, ld_dk, ld_dv, T_local, Hq, Hkv, scale, status, dk_stage, dv_stage, ld_stage};
+    if (n_kv_tiles > 0)
+        attn_bwd_dkdv2_kernel<true><<<dim3(Hkv, n_kv_tiles), kBwd2Threads, kBwdKv2Smem, s>>>(tq64, peers128.k[0], peers128.v[0], tdo64,
+                                                                                             p, peers128, cp);
+    p.work = q_work;
+    if (n_q_tiles > 0)
+        attn_bwd_dq2_kernel<true><<<dim3(Hq, n_q_tiles), kBwd2Threads, kBwdQ2Smem, s>>>(tq, peers64.k[0], peers64.v[0], tdo, p,
+                                                                                        peers64, cp);
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

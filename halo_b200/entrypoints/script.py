@@ -132,8 +132,9 @@ def _token_cutting_runtime(pc, device, group):
     width = pc.tp_size if pc.tp_size > 1 else pc.cp_size
     if pc.tp_size > 1 and pc.cp_size > 1:
         raise ValueError("tensor and context parallelism together are not wired into the entry points")
-    if pc.ep_size > 1:
-        raise ValueError("expert parallelism together with tensor / context parallelism is not wired into the entry points")
+    if pc.ep_size > 1 and (pc.tp_size > 1 or pc.ep_size != world):
+        raise ValueError("with context parallelism the experts are sharded over every rank of the job (expert_parallel_size "
+                         f"= {world}); expert parallelism together with tensor parallelism is not wired into the entry points")
     ranks = [dist.get_global_rank(group, r) for r in range(world)] if group is not dist.group.WORLD else list(range(world))
     mine = replica = None
     for b in range(world // width):                       # blocks of consecutive ranks share a row
@@ -145,7 +146,8 @@ def _token_cutting_runtime(pc, device, group):
         if j == rank % width:
             replica = g
     return {"group": group, "axis_group": mine, "replica_group": replica if world > width else None,
-            "kind": "tp" if pc.tp_size > 1 else "cp", "device": device, "runtime_cls": ParallelRuntime}
+            "kind": "tp" if pc.tp_size > 1 else "cp", "device": device, "runtime_cls": ParallelRuntime,
+            "expert_parallel": pc.ep_size > 1}
 
 
 def finish_token_cutting_runtime(spec: dict, cfg, max_tokens: int):
@@ -158,6 +160,19 @@ def finish_token_cutting_runtime(spec: dict, cfg, max_tokens: int):
         tp = TensorParallel(spec["axis_group"], spec["device"], hidden=cfg.hidden_size, max_tokens=max_tokens)
     else:
         cp = ContextParallel(spec["axis_group"], spec["device"], cfg, max_tokens)
+    if spec.get("expert_parallel"):
+        # experts sharded over every rank, rows cut over blocks of consecutive ranks: to the expert layer a rank's tokens
+        # are just tokens (it dispatches whatever it holds), and replicated parameters sum their gradients over the job
+        if spec["device"].type == "cuda":
+            from halo_b200.parallel.runtime import SymmetricTransport
+
+            transport = SymmetricTransport(spec["group"], spec["device"])
+        else:
+            from halo_b200.parallel.expert_parallel import CollectiveTransport
+
+            transport = CollectiveTransport(spec["group"])
+        return spec["runtime_cls"](spec["device"], dp_group=spec["group"], ep_group=spec["group"], transport=transport,
+                                   context_parallel=cp)
     return spec["runtime_cls"](spec["device"], dp_group=spec["group"], tensor_parallel=tp, context_parallel=cp,
                                tp_replica_group=spec["replica_group"] if tp is not None else None)
 
@@ -197,9 +212,15 @@ def load_policy_model(model_args, pc, device, runtime, gradient_checkpointing=Tr
         return model
     if isinstance(runtime, dict):          # tensor / context parallelism: needs the model's sizes to finish
         runtime = finish_token_cutting_runtime(runtime, cfg, max_tokens)
+        transport = runtime.transport
+        if transport is not None and hasattr(transport, "configure") and cfg.is_moe:
+            # a rank holds its share of a row (plus what the tile-aligned cuts add)
+            share = max_tokens // max(pc.cp_size, 1) + 512
+            transport.configure(max_tokens=share, top_k=cfg.num_experts_per_tok, hidden=cfg.hidden_size,
+                                n_local_experts=cfg.num_experts // transport.n_ranks)
         model = build_model(cfg, device=device, dtype=dtype, gradient_checkpointing=gradient_checkpointing,
-                            tensor_parallel=runtime.tensor_parallel) if model_args.init_from_scratch else \
-            from_pretrained(model_args.model_name_or_path, device=device, dtype=dtype,
+                            tensor_parallel=runtime.tensor_parallel, transport=transport) if model_args.init_from_scratch else \
+            from_pretrained(model_args.model_name_or_path, device=device, dtype=dtype, transport=transport,
                             gradient_checkpointing=gradient_checkpointing, tensor_parallel=runtime.tensor_parallel)
         model.context_parallel = runtime.context_parallel
         model.parallel_runtime = runtime

@@ -228,6 +228,13 @@ class Trainer:
             self._guard_non_finite(out)
             if args.logging_steps and self.global_step % args.logging_steps == 0:
                 now = time.perf_counter()
+                # every rank's loss is its share of the step's global loss (one shared denominator): the logged number is
+                # their sum, whatever the layout (every rank reaches this line at the same steps)
+                step_loss = step_loss.detach().reshape(-1)[:1].float().clone()
+                if self.parallel is not None and getattr(self.parallel, "dp_world", 1) > 1:
+                    import torch.distributed as dist
+
+                    dist.all_reduce(step_loss, group=self.parallel.dp_group)
                 logs = {"step": self.global_step, "loss": float(step_loss.reshape(-1)[0].item()),
                         "grad_norm": float(out.grad_norm.item()), "lr": self.lr_scheduler.get_last_lr()[0],
                         "tokens": self.tokens_seen, "step_seconds": (now - t_last) / args.logging_steps}

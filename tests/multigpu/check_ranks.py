@@ -231,12 +231,13 @@ def check_nvls_forms(dev, rank, world):
 
 
 def check_context_parallel(dev, rank, world):
-    """Attention of this rank's chunk of a packed row (K/V of straddling documents pulled from peers) against
-    the flash kernel run on the whole row by one GPU, forward and backward."""
+    """Attention of this rank's pieces of a packed row (keys and values read from their owners inside the kernels, foreign
+    dK / dV returned through the staging buffers) against the flash kernel run on the whole row by one GPU, forward and
+    backward; with paired early / late pieces and with contiguous chunks, on chat-length documents and on one long one."""
     import numpy as np
 
     from halo_b200.ops import attention as attn_ops
-    from halo_b200.parallel.context_parallel import CPExchange, build_cp_plan, chunk_bounds, cp_attention, make_layout
+    from halo_b200.parallel.context_parallel import CPExchange, TILE, build_cp_plan, cp_attention, make_layout
 
     Hq, Hkv, D = 8, 2, 128
     total = 2048 * world
@@ -246,26 +247,28 @@ def check_context_parallel(dev, rank, world):
         n = int(min(left, rng.integers(100, 3000)))
         lens.append(n)
         left -= n
-    cu = np.concatenate([[0], np.cumsum(lens)])
-    g = torch.Generator(device=dev).manual_seed(11)              # same data on every rank
-    q = (torch.randn(total, Hq * D, device=dev, generator=g) * 0.5).bfloat16()
-    k = (torch.randn(total, Hkv * D, device=dev, generator=g) * 0.5).bfloat16()
-    v = (torch.randn(total, Hkv * D, device=dev, generator=g) * 0.5).bfloat16()
-    do = (torch.randn(total, Hq * D, device=dev, generator=g) * 0.5).bfloat16()
-    qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
-    ref = attn_ops.flash_attention(qf, kf, vf, attn_ops.build_plan(cu, dev), Hq, Hkv)
-    ref.backward(do)
-    lo, hi = chunk_bounds(total, world, rank)
-    lay = make_layout(cu, rank, world)
-    ex = CPExchange(dist.group.WORLD, dev, hi - lo, total - (hi - lo), 2 * Hkv * D)
-    ql, kl, vl = (t[lo:hi].clone().requires_grad_() for t in (q, k, v))
-    out = cp_attention(ql, kl, vl, lay, build_cp_plan(lay, dev), dist.group.WORLD, ex, Hq, Hkv)
-    out.backward(do[lo:hi])
-    torch.cuda.synchronize()
-    close(out, ref[lo:hi], 2e-2, "cp out")
-    close(ql.grad, qf.grad[lo:hi], 3e-2, "cp dq")
-    close(kl.grad, kf.grad[lo:hi], 3e-2, "cp dk")
-    close(vl.grad, vf.grad[lo:hi], 3e-2, "cp dv")
+    ex = CPExchange(dist.group.WORLD, dev, total // world + 4 * TILE, total, 2 * Hkv * D)
+    for cu, balance in ((np.concatenate([[0], np.cumsum(lens)]), True), (np.array([0, total]), True),
+                        (np.concatenate([[0], np.cumsum(lens)]), False)):
+        g = torch.Generator(device=dev).manual_seed(11)              # same data on every rank
+        q = (torch.randn(total, Hq * D, device=dev, generator=g) * 0.5).bfloat16()
+        k = (torch.randn(total, Hkv * D, device=dev, generator=g) * 0.5).bfloat16()
+        v = (torch.randn(total, Hkv * D, device=dev, generator=g) * 0.5).bfloat16()
+        do = (torch.randn(total, Hq * D, device=dev, generator=g) * 0.5).bfloat16()
+        qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
+        ref = attn_ops.flash_attention(qf, kf, vf, attn_ops.build_plan(cu, dev), Hq, Hkv)
+        ref.backward(do)
+        lay = make_layout(cu, rank, world, balance)
+        idx = torch.from_numpy(lay.local_index()).to(dev)
+        ql, kl, vl = (t[idx].clone().requires_grad_() for t in (q, k, v))
+        out = cp_attention(ql, kl, vl, lay, build_cp_plan(lay, dev), dist.group.WORLD, ex, Hq, Hkv)
+        out.backward(do[idx])
+        torch.cuda.synchronize()
+        what = f"cp ({'paired' if balance else 'contiguous'} pieces, {len(cu) - 1} documents)"
+        close(out, ref[idx], 2e-2, what + " out")
+        close(ql.grad, qf.grad[idx], 3e-2, what + " dq")
+        close(kl.grad, kf.grad[idx], 3e-2, what + " dk")
+        close(vl.grad, vf.grad[idx], 3e-2, what + " dv")
 
 
 def check_tensor_parallel_collectives(dev, rank, world):

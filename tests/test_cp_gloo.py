@@ -122,3 +122,34 @@ def test_long_document_work_is_balanced_across_ranks():
     assert max(balanced) - min(balanced) <= 2 * 4          # at most the diagonal tiles differ
     assert max(contiguous) > 5 * min(contiguous)
     assert sum(balanced) == sum(contiguous)
+
+
+def test_expert_parallel_times_context_parallel_through_the_entry_point(tmp_path):
+    """``expert_parallel_size: 4`` with ``context_parallel_size: 2`` on four CPU ranks through the launcher (the layout of
+    the 8-GPU EP8 x CP2 long-row runs, halved): two pairs of ranks each cut one row, all four shard the experts; the loss
+    curve is the one of two data-parallel ranks that each hold a whole row."""
+    import os
+    import re
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def run(name, extra, n):
+        cfg = tmp_path / f"{name}.yaml"
+        cfg.write_text("model_preset: tiny-moe\ninit_from_scratch: true\ndataset_format: synthetic\npacked_row_length: 1024\n"
+                       "doc_length_min: 200\ndoc_length_max: 700\n"
+                       "max_steps: 5\nlearning_rate: 3.0e-3\nlr_scheduler_type: constant\noptim: adamw_torch\nweight_decay: 0.0\n"
+                       f"max_grad_norm: 0.0\noutput_dir: {tmp_path}/{name}\nlogging_steps: 1\n" + extra)
+        r = subprocess.run([sys.executable, "-m", "halo_b200.cli", "launch", "sft", str(cfg), "-n", str(n), "--port", "29741"],
+                           cwd=root, capture_output=True, text=True, timeout=600,
+                           env=dict(os.environ, CUDA_VISIBLE_DEVICES="", NVLINK_DOMAIN_SIZE="4"))
+        out = r.stdout + r.stderr
+        assert r.returncode == 0, out[-4000:]
+        return [float(x) for x in re.findall(r"step \d+ loss ([0-9.]+)", out)], out
+
+    both, out = run("ep4cp2", "expert_parallel_size: 4\ncontext_parallel_size: 2\n", 4)
+    assert len(both) >= 5, out[-3000:]
+    flat, _ = run("ep2", "expert_parallel_size: 2\n", 2)
+    assert abs(both[0] - flat[0]) < 4e-4, (both[:2], flat[:2])
+    assert max(abs(a - b) / b for a, b in zip(both[:5], flat[:5])) < 5e-3, (both, flat)

@@ -194,8 +194,8 @@ def test_pipeline_times_expert_parallel_through_the_entry_point(tmp_path):
     # the same two data-parallel replicas, the same rows and the same initialisation with and without the pipeline:
     # the first step's loss is the same number, the curves stay together (the optimizer sees the same gradients up to
     # one common factor, which Adam divides out)
-    assert abs(pp[0] - flat[0]) < 2e-4, (pp[:2], flat[:2])
-    assert max(abs(a - b) for a, b in zip(pp[::2][:6], flat[::2][:6])) < 2e-2, (pp, flat)
+    assert abs(pp[0] - flat[0]) < 4e-4, (pp[:2], flat[:2])
+    assert max(abs(a - b) / b for a, b in zip(pp[::2][:6], flat[::2][:6])) < 5e-3, (pp, flat)
     # the stages wrote one ordinary checkpoint: every tensor of the unsplit model, experts gathered
     import json
 
