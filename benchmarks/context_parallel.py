@@ -6,7 +6,8 @@ documents.
 
 The target is (single-GPU time) / N: keys and values are read from their owners inside the kernels, so no transfer sits
 on the critical path, and the paired early / late pieces give every rank the same causal work. `--tokens=T` sets the row
-length (default 65536), `--contiguous` times contiguous chunks instead of paired pieces.
+length (default 65536), `--contiguous` times contiguous chunks instead of paired pieces, `--direct-reads` lets the kernels
+read every foreign tile from its owner instead of from the local mirror.
 """
 
 from __future__ import annotations
@@ -60,7 +61,8 @@ def main():
         lens.append(n)
         left -= n
     cases = {"one document": np.array([0, total]), "chat-length documents": np.concatenate([[0], np.cumsum(lens)])}
-    ex = CPExchange(dist.group.WORLD, dev, total // world + 4 * TILE, total, 2 * Hkv * D)
+    direct = "--direct-reads" in sys.argv
+    ex = CPExchange(dist.group.WORLD, dev, total // world + 4 * TILE, total + TILE, 2 * Hkv * D, direct_reads=direct)
     rows = []
     for name, cu in cases.items():
         g = torch.Generator(device=dev).manual_seed(3)
@@ -97,6 +99,7 @@ def main():
         c_f, c_b = timed(cp_fwd), timed(cp_both)
         _lib.raise_on_status(dev)
         rows.append({"case": name, "tokens": total, "ranks": world, "pieces": "paired" if balance else "contiguous",
+                     "keys_and_values": "tiles read from their owners" if direct else "rows fetched once into a local mirror",
                      "single_gpu_fwd_ms": round(s_f, 3), "single_gpu_fwd_bwd_ms": round(s_b, 3),
                      "cp_fwd_ms": round(c_f, 3), "cp_fwd_bwd_ms": round(c_b, 3),
                      "fwd_vs_single_over_ranks": round(c_f / (s_f / world), 3),

@@ -67,6 +67,10 @@ __device__ __forceinline__ uint32_t swz_off(int row, int col) {
 // only addresses are translated. A row belongs to one piece of the row; a piece has an owner rank and a first row in that
 // rank's local order. Queries, outputs and statistics are local tensors; a key / value tile is read from its owner's
 // published buffer through that rank's tensor map (plain per-CTA TMA loads; the memory may be a peer GPU's).
+// Two tables are passed: one for query rows (always this rank's real pieces) and one for key rows. The key table is either
+// the same pieces with one tensor map per owner (every tile read crosses NVLink: good when few foreign rows are touched),
+// or a single piece covering the whole row, owned by nobody (`my_rank = -1`), when the needed foreign rows were first
+// fetched once into a local mirror indexed by global row; dK / dV then all go to the staging buffer at their global rows.
 struct CpMap {
     int n_pieces;
     int my_rank;
@@ -822,7 +826,8 @@ template <bool kCP>
 __global__ void __launch_bounds__(kBwd2Threads, 1)
 attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                      const BwdParams p, const __grid_constant__ PeerMaps peers, const __grid_constant__ CpMap cp) {
+                      const BwdParams p, const __grid_constant__ PeerMaps peers, const __grid_constant__ CpMap cp,
+                    const __grid_constant__ CpMap cpk) {
     if (status_poisoned(p.status)) return;
     extern __shared__ __align__(1024) uint8_t smem_b2[];
     const uint32_t base = smem_u32(smem_b2);
@@ -892,10 +897,10 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             const CUtensorMap* mapV = &tmV;
             int k_loc = w.kv0;
             if (kCP) {
-                const int pk = cp_piece(cp, w.kv0);
-                mapK = &peers.k[cp.owner[pk]];
-                mapV = &peers.v[cp.owner[pk]];
-                k_loc = w.kv0 - cp.bound[pk] + cp.loc[pk];
+                const int pk = cp_piece(cpk, w.kv0);
+                mapK = &peers.k[cpk.owner[pk]];
+                mapV = &peers.v[cpk.owner[pk]];
+                k_loc = w.kv0 - cpk.bound[pk] + cpk.loc[pk];
             }
             tma_load_2d(sK, mapK, bar(kKv), kv_head * kHd, k_loc);
             tma_load_2d(sK + 16384, mapK, bar(kKv), kv_head * kHd + 64, k_loc);
@@ -1053,14 +1058,14 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             void* out_base = g == 0 ? p.dK : p.dV;
             long long out_row = key_abs;
             if (kCP) {
-                const int pk = cp_piece(cp, w.kv0);
-                if (cp.owner[pk] == cp.my_rank) {
-                    out_row = key_abs - cp.bound[pk] + cp.loc[pk];
+                const int pk = cp_piece(cpk, w.kv0);
+                if (cpk.owner[pk] == cpk.my_rank) {
+                    out_row = key_abs - cpk.bound[pk] + cpk.loc[pk];
                 } else {
                     out_base = g == 0 ? p.dK_stage : p.dV_stage;
                     ld = p.ld_stage;
-                    out_row = key_abs - cp.bound[pk] + cp.stage[pk];
-                    if (cp.stage[pk] < 0) {             // no staging was planned for this piece: record it, write nothing
+                    out_row = key_abs - cpk.bound[pk] + cpk.stage[pk];
+                    if (cpk.stage[pk] < 0) {            // no staging was planned for this piece: record it, write nothing
                         live = false;
                         if (key == 0 && half == 0 && p.status) atomicCAS(p.status, kStatusOk, kStatusBounds);
                     }
@@ -1108,7 +1113,8 @@ template <bool kCP>
 __global__ void __launch_bounds__(kBwd2Threads, 1)
 attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                    const BwdParams p, const __grid_constant__ PeerMaps peers, const __grid_constant__ CpMap cp) {
+                    const BwdParams p, const __grid_constant__ PeerMaps peers, const __grid_constant__ CpMap cp,
+                    const __grid_constant__ CpMap cpk) {
     if (status_poisoned(p.status)) return;
     extern __shared__ __align__(1024) uint8_t smem_q2[];
     const uint32_t base = smem_u32(smem_q2);
@@ -1165,10 +1171,10 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 const CUtensorMap* mapK = &tmK;
                 const CUtensorMap* mapV = &tmV;
                 if (kCP) {                       // the sub-tile's owner and its row in that rank's published buffer
-                    const int pk = cp_piece(cp, kr);
-                    mapK = &peers.k[cp.owner[pk]];
-                    mapV = &peers.v[cp.owner[pk]];
-                    kr = kr - cp.bound[pk] + cp.loc[pk];
+                    const int pk = cp_piece(cpk, kr);
+                    mapK = &peers.k[cpk.owner[pk]];
+                    mapV = &peers.v[cpk.owner[pk]];
+                    kr = kr - cpk.bound[pk] + cpk.loc[pk];
                 }
                 mbar_expect_tx(full, 2 * kHalfTile);
                 tma_load_2d(sK, mapK, full, kv_head * kHd, kr);
@@ -1560,7 +1566,7 @@ template <bool kCP>
 __global__ void __maxnreg__(128)
 attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const AttnParams p, const __grid_constant__ PeerMaps peers,
-                 const __grid_constant__ CpMap cp) {
+                 const __grid_constant__ CpMap cp, const __grid_constant__ CpMap cpk) {
     if (status_poisoned(p.status)) return;
     extern __shared__ __align__(1024) uint8_t smem3[];
     const uint32_t base = smem_u32(smem3);
@@ -1623,10 +1629,10 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 const CUtensorMap* mapK = &tmK;
                 const CUtensorMap* mapV = &tmV;
                 if (kCP) {                       // the tile's owner and its row in that rank's published buffer
-                    const int pk = cp_piece(cp, kr);
-                    mapK = &peers.k[cp.owner[pk]];
-                    mapV = &peers.v[cp.owner[pk]];
-                    kr = kr - cp.bound[pk] + cp.loc[pk];
+                    const int pk = cp_piece(cpk, kr);
+                    mapK = &peers.k[cpk.owner[pk]];
+                    mapV = &peers.v[cpk.owner[pk]];
+                    kr = kr - cpk.bound[pk] + cpk.loc[pk];
                 }
                 mbar_expect_tx(full, 2 * kHalfTile);
                 tma_load_2d(sK, mapK, full, kv_head * kHd, kr);
@@ -1808,24 +1814,30 @@ static PeerMaps g_no_peers{};
 static CpMap g_no_cp{};
 
 // Tensor maps over every rank's published key / value buffer (box of `box_rows` rows) and the piece table.
-static int fill_cp(PeerMaps* peers, CpMap* cp, void* const* kv_ptrs, int n_ranks, long long kv_rows, long long kv_ld, int v_col,
-                   int Hkv, const int* m, int box_rows) {
+static int fill_peer_maps(PeerMaps* peers, void* const* kv_ptrs, int n_bufs, long long kv_rows, long long kv_ld, int v_col,
+                          int Hkv, int box_rows) {
     memset(peers, 0, sizeof(*peers));
+    if (n_bufs < 1 || n_bufs > 8) return -1;
     for (int r = 0; r < 8; ++r) {
-        const int src = r < n_ranks ? r : 0;              // unused slots repeat rank 0's maps (valid, never selected)
+        const int src = r < n_bufs ? r : 0;               // unused slots repeat buffer 0's maps (valid, never selected)
         const char* base = reinterpret_cast<const char*>(kv_ptrs[src]);
         if (make_tmap_bf16(&peers->k[r], base, kv_rows, (long long)Hkv * kHd, kv_ld, box_rows)) return -1;
         if (make_tmap_bf16(&peers->v[r], base + (long long)v_col * 2, kv_rows, (long long)Hkv * kHd, kv_ld, box_rows)) return -1;
     }
+    return 0;
+}
+
+// m: n_pieces, my rank (-1: owner of nothing), bound[17], owner[16], loc[16], stage[16]; owners index `n_bufs` buffers.
+static int fill_cp_map(CpMap* cp, const int* m, int n_bufs) {
     cp->n_pieces = m[0];
     cp->my_rank = m[1];
-    if (cp->n_pieces < 1 || cp->n_pieces > 16 || cp->my_rank < 0 || cp->my_rank >= n_ranks) return -2;
+    if (cp->n_pieces < 1 || cp->n_pieces > 16 || cp->my_rank < -1) return -2;
     for (int i = 0; i < 17; ++i) cp->bound[i] = m[2 + i];
     for (int i = 0; i < 16; ++i) {
         cp->owner[i] = m[19 + i];
         cp->loc[i] = m[35 + i];
         cp->stage[i] = m[51 + i];
-        if (i < cp->n_pieces && (cp->owner[i] < 0 || cp->owner[i] >= n_ranks)) return -3;
+        if (i < cp->n_pieces && (cp->owner[i] < 0 || cp->owner[i] >= n_bufs)) return -3;
     }
     return 0;
 }
@@ -1898,25 +1910,26 @@ int halo_attn_fwd3(const void* q, const void* k, const void* v, void* o, float* 
         cfg = true;
     }
     AttnParams p{reinterpret_cast<const FwdWork*>(work), o, lse, ldo, T, Hq, Hkv, scale, status};
-    attn_fwd3_kernel<false><<<dim3(Hq, n_tiles), kFwdThreads, kFwd2Smem, (cudaStream_t)stream>>>(tq, tk, tv, p, g_no_peers, g_no_cp);
+    attn_fwd3_kernel<false><<<dim3(Hq, n_tiles), kFwdThreads, kFwd2Smem, (cudaStream_t)stream>>>(tq, tk, tv, p, g_no_peers, g_no_cp, g_no_cp);
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
 // Context-parallel forward: q, o, lse are this rank's local rows; kv_ptrs[r] is rank r's published [kv_rows, kv_ld] buffer
 // (keys in columns [0, v_col), values from column v_col), possibly a peer GPU's memory. work: {q0, document start,
 // 64-key sub-tiles, document end} in the row's global numbering; cp_map: n_pieces, my rank, bound[17], owner[16], loc[16],
-// stage[16] (host ints).
+// stage[16] (host ints) for the query rows; kv_map: the same table for the key rows (owners index kv_ptrs).
 int halo_attn_cp_fwd(const void* q, void* const* kv_ptrs, int n_ranks, long long kv_rows, long long kv_ld, int v_col,
                      void* o, float* lse, const void* work, int n_tiles, long long T_local, int Hq, int Hkv,
-                     int head_dim, long long ldq, long long ldo, float scale, const int* cp_map, int* status,
-                     void* stream) {
+                     int head_dim, long long ldq, long long ldo, float scale, const int* cp_map, const int* kv_map,
+                     int* status, void* stream) {
     if (head_dim != kHd || Hq % Hkv || n_ranks < 1 || n_ranks > 8) return -1;
     if (n_tiles == 0) return 0;
     CUtensorMap tq;
     if (make_tmap_bf16(&tq, q, T_local, (long long)Hq * kHd, ldq, 128)) return -2;
     PeerMaps peers;
-    CpMap cp;
-    if (fill_cp(&peers, &cp, kv_ptrs, n_ranks, kv_rows, kv_ld, v_col, Hkv, cp_map, 64)) return -3;
+    CpMap cp, cpk;
+    if (fill_peer_maps(&peers, kv_ptrs, n_ranks, kv_rows, kv_ld, v_col, Hkv, 64)) return -3;
+    if (fill_cp_map(&cp, cp_map, 8) || fill_cp_map(&cpk, kv_map, n_ranks)) return -4;
     static bool cfg = false;
     if (!cfg) {
         if (set_smem((const void*)attn_fwd3_kernel<true>, kFwd2Smem)) return -10;
@@ -1925,7 +1938,7 @@ int halo_attn_cp_fwd(const void* q, void* const* kv_ptrs, int n_ranks, long long
         cfg = true;
     }
     AttnParams p{reinterpret_cast<const FwdWork*>(work), o, lse, ldo, T_local, Hq, Hkv, scale, status};
-    attn_fwd3_kernel<true><<<dim3(Hq, n_tiles), kFwdThreads, kFwd2Smem, (cudaStream_t)stream>>>(tq, peers.k[0], peers.v[0], p, peers, cp);
+    attn_fwd3_kernel<true><<<dim3(Hq, n_tiles), kFwdThreads, kFwd2Smem, (cudaStream_t)stream>>>(tq, peers.k[0], peers.v[0], p, peers, cp, cpk);
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -2001,13 +2014,13 @@ int halo_attn_bwd(const void* q, const void* k, const void* v, const void* o, co
     BwdParams p{kv_work, lse, delta, dq, dk, dv, ld_dq, ld_dk, ld_dv, T, Hq, Hkv, scale, status};
     if (n_kv_tiles > 0) {
         if (variant == 2)
-            attn_bwd_dkdv2_kernel<false><<<dim3(Hkv, n_kv_tiles), kBwd2Threads, kBwdKv2Smem, s>>>(tq64, tk, tv, tdo64, p, g_no_peers, g_no_cp);
+            attn_bwd_dkdv2_kernel<false><<<dim3(Hkv, n_kv_tiles), kBwd2Threads, kBwdKv2Smem, s>>>(tq64, tk, tv, tdo64, p, g_no_peers, g_no_cp, g_no_cp);
         else attn_bwd_dkdv_kernel<<<dim3(Hkv, n_kv_tiles), kBwdThreads, kBwdKvSmem, s>>>(tq64, tk, tv, tdo64, p);
     }
     p.work = q_work;
     if (n_q_tiles > 0) {
         if (variant == 2)
-            attn_bwd_dq2_kernel<false><<<dim3(Hq, n_q_tiles), kBwd2Threads, kBwdQ2Smem, s>>>(tq, tk64, tv64, tdo, p, g_no_peers, g_no_cp);
+            attn_bwd_dq2_kernel<false><<<dim3(Hq, n_q_tiles), kBwd2Threads, kBwdQ2Smem, s>>>(tq, tk64, tv64, tdo, p, g_no_peers, g_no_cp, g_no_cp);
         else attn_bwd_dq_kernel<<<dim3(Hq, n_q_tiles), kBwdThreads, kBwdQSmem, s>>>(tq, tk64, tv64, tdo, p);
     }
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
@@ -2021,7 +2034,7 @@ int halo_attn_cp_bwd(const void* q, void* const* kv_ptrs, int n_ranks, long long
                      void* dk_stage, void* dv_stage, long long ld_stage, const void* kv_work, int n_kv_tiles,
                      const void* q_work, int n_q_tiles, long long T_local, int Hq, int Hkv, int head_dim, long long ldq,
                      long long ldo, long long ld_do, long long ld_dq, long long ld_dk, long long ld_dv, float scale,
-                     const int* cp_map, int* status, void* stream) {
+                     const int* cp_map, const int* kv_map, int* status, void* stream) {
     if (head_dim != kHd || Hq % Hkv || n_ranks < 1 || n_ranks > 8) return -1;
     if (T_local == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
@@ -2033,9 +2046,10 @@ int halo_attn_cp_bwd(const void* q, void* const* kv_ptrs, int n_ranks, long long
     if (make_tmap_bf16(&tq64, q, T_local, (long long)Hq * kHd, ldq, 64)) return -6;
     if (make_tmap_bf16(&tdo64, d_o, T_local, (long long)Hq * kHd, ld_do, 64)) return -9;
     PeerMaps peers128, peers64;
-    CpMap cp;
-    if (fill_cp(&peers128, &cp, kv_ptrs, n_ranks, kv_rows, kv_ld, v_col, Hkv, cp_map, 128)) return -3;
-    if (fill_cp(&peers64, &cp, kv_ptrs, n_ranks, kv_rows, kv_ld, v_col, Hkv, cp_map, 64)) return -4;
+    CpMap cp, cpk;
+    if (fill_peer_maps(&peers128, kv_ptrs, n_ranks, kv_rows, kv_ld, v_col, Hkv, 128)) return -3;
+    if (fill_peer_maps(&peers64, kv_ptrs, n_ranks, kv_rows, kv_ld, v_col, Hkv, 64)) return -4;
+    if (fill_cp_map(&cp, cp_map, 8) || fill_cp_map(&cpk, kv_map, n_ranks)) return -12;
     static bool cfg = false;
     if (!cfg) {
         if (set_smem((const void*)attn_bwd_dkdv2_kernel<true>, kBwdKv2Smem)) return -10;
@@ -2045,11 +2059,11 @@ int halo_attn_cp_bwd(const void* q, void* const* kv_ptrs, int n_ranks, long long
     BwdParams p{kv_work, lse, delta, dq, dk, dv, ld_dq, ld_dk, ld_dv, T_local, Hq, Hkv, scale, status, dk_stage, dv_stage, ld_stage};
     if (n_kv_tiles > 0)
         attn_bwd_dkdv2_kernel<true><<<dim3(Hkv, n_kv_tiles), kBwd2Threads, kBwdKv2Smem, s>>>(tq64, peers128.k[0], peers128.v[0], tdo64,
-                                                                                             p, peers128, cp);
+                                                                                             p, peers128, cp, cpk);
     p.work = q_work;
     if (n_q_tiles > 0)
         attn_bwd_dq2_kernel<true><<<dim3(Hq, n_q_tiles), kBwd2Threads, kBwdQ2Smem, s>>>(tq, peers64.k[0], peers64.v[0], tdo, p,
-                                                                                        peers64, cp);
+                                                                                        peers64, cp, cpk);
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

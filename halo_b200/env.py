@@ -38,6 +38,7 @@ CATALOGUE = {
     "HALO_WEIGHT_SYNC_NVLS": "trainer -> rollout weight push through NVLink multicast stores when the arena supports it (default 1)",
     "HALO_ZERO_NVLS": "sharded optimizer: reduce and all-gather through NVLink multicast (multimem) when the buffers support it (default 0: plain peer loads / stores, bit-identical to the unsharded optimizer)",
     "HALO_MOE_FUSED": "expert products with the token movement inside the GEMM kernels (1, default) or as separate push / pull kernels (0)",
+    "HALO_CP_DIRECT_READS": "context parallelism: flash kernels read foreign key / value tiles from their owners on every use (1) instead of from a local mirror filled once per exchange (0, default)",
     "HALO_PEER_WAIT_MS": "how long a kernel waits for rows or a flag from a peer GPU before it gives up with a status (default 20000)",
     "HALO_ROW_BLOCKS_PER_SM": "thread blocks per SM of the expert row kernels (dispatch / combine)",
     "HALO_NNODES": "nodes of a multi-node launch (read by the CLI when --nnodes is not given)",
@@ -170,6 +171,10 @@ def weight_sync_nvls() -> bool:
 
 def zero_nvls() -> bool:
     return env_flag("HALO_ZERO_NVLS", False)
+
+
+def cp_direct_reads() -> bool:
+    return env_flag("HALO_CP_DIRECT_READS", False)
 
 
 def moe_fused() -> bool:

@@ -10,11 +10,15 @@ attention tile ever straddles two owners; ranks may therefore hold slightly diff
 normalised by the global count, expert dispatch exchanges per-rank counts anyway).
 
 **Exchange (GPU).** Each rank publishes its keys and values (after rotary) in a symmetric buffer. The flash kernels
-work in the row's global coordinates: their TMA producers read every key / value tile straight from its owner's buffer
-over NVLink (one tensor map per peer, plain per-CTA loads), while queries, outputs and statistics are addressed in the
-rank's local order. In the backward pass the dK / dV tiles of foreign keys are written to a local staging buffer that
-the owners read and add in rank order (deterministic, no atomics). Nothing is copied into a local "extended" K/V and no
-zero-padded query tensor exists.
+work in the row's global coordinates (masks, document ends, tile starts); queries, outputs and statistics are addressed
+in the rank's local order, so no zero-padded query tensor exists. Keys and values come from a local mirror indexed by
+global row that is filled once per exchange: the rank's own rows and exactly the foreign rows its queries can see, each
+pulled over NVLink once by the rank's own copy kernel. (The kernels can instead read every foreign tile from its owner
+through per-rank tensor maps; that was measured: fine for chat-length documents, five times slower than the mirror on
+one 64k-token document, where every CTA's read of a tile crosses the link again.) In the backward pass dK / dV are
+written at their global rows into a staging buffer; each owner takes its own rows and adds the peers' contributions in
+rank order (deterministic, no atomics). Under per-layer recomputation the backward pass reuses the mirror its own
+forward has just filled and exchanges nothing but the gradients.
 
 The reference's context parallelism is Ulysses all-to-all and refuses packed rows
 (halo/distributed/context_parallel/ulysses_model.py:199-312, model_rules.py); this is the packed-row replacement.
@@ -277,25 +281,38 @@ class _GatherRows(torch.autograd.Function):
 
 
 class CPExchange:
-    """Symmetric buffers and barriers of one context-parallel group (GPU path)."""
+    """Symmetric buffers and barriers of one context-parallel group (GPU path).
 
-    def __init__(self, group, device, max_local_rows: int, max_stage_rows: int, kv_cols: int):
+    ``kv``: this rank's published keys | values in local order (peers read it). ``dkv``: dK | dV this rank produced for
+    key rows, read by their owners. ``mirror`` (plain local memory, indexed by GLOBAL row): the keys | values this rank's
+    kernels read - its own rows and the foreign rows it needs, fetched once per exchange. With ``direct_reads`` the
+    kernels skip the mirror and read every foreign tile from its owner over NVLink: fine when few foreign rows are
+    touched, but every CTA's read of a tile crosses the link again (one 64k-token document on two GPUs moves 137 GB per
+    layer that way and runs five times slower than the mirror), so it is an option, not the default."""
+
+    def __init__(self, group, device, max_local_rows: int, max_row_tokens: int, kv_cols: int, direct_reads: bool | None = None):
         import torch.distributed._symmetric_memory as symm
+
+        from halo_b200 import env
 
         self.group, self.device = group, torch.device(device)
         self.n_ranks, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.direct_reads = env.cp_direct_reads() if direct_reads is None else bool(direct_reads)
         self.kv = symm.empty((max_local_rows, kv_cols), dtype=torch.bfloat16, device=self.device)
-        self.dkv = symm.empty((max(max_stage_rows, 8), kv_cols), dtype=torch.bfloat16, device=self.device)
-        # rows past a rank's own count are read by tiles at document ends (and masked): they must hold finite values
+        self.dkv = symm.empty((max(max_row_tokens, 8), kv_cols), dtype=torch.bfloat16, device=self.device)
+        # rows a tile reads past a document's end are masked, but must hold finite values
         self.kv.zero_()
         self.dkv.zero_()
+        self.mirror = torch.zeros((max(max_row_tokens, 8), kv_cols), dtype=torch.bfloat16, device=self.device)
+        self.mirror_version = 0
         self.h_kv = symm.rendezvous(self.kv, group)
         self.h_dkv = symm.rendezvous(self.dkv, group)
         self.kv_ptrs = list(self.h_kv.buffer_ptrs)
         self.dkv_ptrs = list(self.h_dkv.buffer_ptrs)
         self.kv_ptr_array = (_lib.c_void_p * self.n_ranks)(*self.kv_ptrs)
+        self.mirror_ptr_array = (_lib.c_void_p * 1)(self.mirror.data_ptr())
         self.row_bytes = kv_cols * 2
-        self.max_local_rows, self.max_stage_rows = max_local_rows, max(max_stage_rows, 8)
+        self.max_local_rows, self.max_row_tokens = max_local_rows, max(max_row_tokens, 8)
 
     def barrier(self) -> None:
         self.h_kv.barrier(channel=3)
@@ -313,9 +330,39 @@ class CPExchange:
                                        _lib.stream_ptr(self.device))
         _lib.check(rc, "halo_peer_pull")
 
+    def fetch_mirror(self, k: torch.Tensor, v: torch.Tensor, layout: CPLayout) -> int:
+        """COLLECTIVE: publish this rank's rows, then fill the mirror with them and with the foreign rows this rank's
+        queries can see (each crosses NVLink once). Returns the mirror's version."""
+        if layout.total > self.max_row_tokens:
+            raise ValueError(f"a row of {layout.total} tokens exceeds the exchange's {self.max_row_tokens}")
+        kvd = k.shape[1]
+        self.publish(k, v)
+        self.barrier()                          # every rank's rows are in place
+        for p in layout.pieces_of(layout.cp_rank):
+            lo, hi, at = int(layout.bounds[p]), int(layout.bounds[p + 1]), int(layout.loc[p])
+            if hi > lo:
+                self.mirror[lo:hi, :kvd].copy_(k[at:at + hi - lo])
+                self.mirror[lo:hi, kvd:].copy_(v[at:at + hi - lo])
+        for lo, hi, _ in layout.written[layout.cp_rank]:
+            rank, row = layout.to_local(lo)
+            self.pull(self.mirror[lo:hi], self.kv_ptrs[rank], row, hi - lo, accumulate=False)
+        self.barrier()                          # peers are done reading before anybody publishes again
+        self.mirror_version += 1
+        return self.mirror_version
+
 
 def _map_array(layout: CPLayout):
     m = layout.device_map()
+    return (_lib.c_int * len(m))(*[int(x) for x in m])
+
+
+def _mirror_map(total: int):
+    """Key table of the mirror: one piece covering the row, owned by nobody, staged at its global rows."""
+    m = np.zeros(2 + 17 + 16 * 3, dtype=np.int32)
+    m[0], m[1] = 1, -1
+    m[3:19] = total
+    m[51:67] = -1
+    m[51] = 0
     return (_lib.c_int * len(m))(*[int(x) for x in m])
 
 
@@ -326,36 +373,51 @@ class _CPFlashAttention(torch.autograd.Function):
         dev = q.device
         D = attn_ops.HEAD_DIM
         kvd = n_kv_heads * D
-        if staging_rows_needed(layout) > exchange.max_stage_rows:
-            raise ValueError("the key/value gradient staging buffer is too small for this row")
-        exchange.publish(k, v)
-        exchange.barrier()                      # every rank's keys and values are in place
+        version = 0
+        if exchange.direct_reads:
+            if staging_rows_needed(layout) > exchange.max_row_tokens:
+                raise ValueError("the key/value gradient staging buffer is too small for this row")
+            exchange.publish(k, v)
+            exchange.barrier()                      # every rank's keys and values are in place
+            ptrs, n_bufs, rows, kv_map = exchange.kv_ptr_array, exchange.n_ranks, exchange.max_local_rows, _map_array(layout)
+        else:
+            version = exchange.fetch_mirror(k, v, layout)
+            ptrs, n_bufs, rows, kv_map = exchange.mirror_ptr_array, 1, exchange.max_row_tokens, _mirror_map(layout.total)
         o = torch.empty((Tl, n_heads * D), dtype=torch.bfloat16, device=dev)
         lse = torch.empty((n_heads, Tl), dtype=torch.float32, device=dev)
         L = _lib.lib()
         rc = L.halo_attn_cp_fwd(
-            _lib.ptr(q), exchange.kv_ptr_array, _lib.c_int(exchange.n_ranks), _lib.c_ll(exchange.max_local_rows),
+            _lib.ptr(q), ptrs, _lib.c_int(n_bufs), _lib.c_ll(rows),
             _lib.c_ll(2 * kvd), _lib.c_int(kvd), _lib.ptr(o), _lib.ptr(lse), _lib.ptr(plan.fwd), _lib.c_int(plan.fwd.shape[0]),
             _lib.c_ll(Tl), _lib.c_int(n_heads), _lib.c_int(n_kv_heads), _lib.c_int(D), _lib.c_ll(attn_ops._ld(q)),
-            _lib.c_ll(attn_ops._ld(o)), _lib.c_float(scale), _map_array(layout), _lib.ptr(_lib.status_word(dev)),
+            _lib.c_ll(attn_ops._ld(o)), _lib.c_float(scale), _map_array(layout), kv_map, _lib.ptr(_lib.status_word(dev)),
             _lib.stream_ptr(dev))
         _lib.check(rc, "halo_attn_cp_fwd")
-        exchange.barrier()                      # peers are done reading before the next layer publishes
+        if exchange.direct_reads:
+            exchange.barrier()                      # peers are done reading before the next layer publishes
         ctx.save_for_backward(q, k, v, o, lse)
-        ctx.meta = (layout, plan, exchange, n_heads, n_kv_heads, scale)
+        ctx.meta = (layout, plan, exchange, n_heads, n_kv_heads, scale, version)
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, k, v, o, lse = ctx.saved_tensors
-        layout, plan, exchange, n_heads, n_kv_heads, scale = ctx.meta
+        layout, plan, exchange, n_heads, n_kv_heads, scale, version = ctx.meta
         Tl = layout.local
         dev = do.device
         D = attn_ops.HEAD_DIM
         kvd = n_kv_heads * D
         do = do.contiguous()
-        exchange.publish(k, v)
-        exchange.barrier()
+        if exchange.direct_reads:
+            exchange.publish(k, v)
+            exchange.barrier()
+            ptrs, n_bufs, rows, kv_map = exchange.kv_ptr_array, exchange.n_ranks, exchange.max_local_rows, _map_array(layout)
+        else:
+            # the mirror still holds this layer's rows when its forward was the last exchange (per-layer recomputation
+            # runs a layer's forward right before its backward); every rank sees the same sequence, so all agree
+            if exchange.mirror_version != version:
+                exchange.fetch_mirror(k, v, layout)
+            ptrs, n_bufs, rows, kv_map = exchange.mirror_ptr_array, 1, exchange.max_row_tokens, _mirror_map(layout.total)
         dq = torch.empty_like(q)
         dkv = torch.zeros((Tl, 2 * kvd), dtype=torch.bfloat16, device=dev)
         delta = torch.empty((n_heads, Tl), dtype=torch.float32, device=dev)
@@ -364,17 +426,31 @@ class _CPFlashAttention(torch.autograd.Function):
         L = _lib.lib()
         ld = attn_ops._ld
         rc = L.halo_attn_cp_bwd(
-            _lib.ptr(q), exchange.kv_ptr_array, _lib.c_int(exchange.n_ranks), _lib.c_ll(exchange.max_local_rows),
+            _lib.ptr(q), ptrs, _lib.c_int(n_bufs), _lib.c_ll(rows),
             _lib.c_ll(2 * kvd), _lib.c_int(kvd), _lib.ptr(o), _lib.ptr(do), _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(dq),
             _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(stage_k), _lib.ptr(stage_v), _lib.c_ll(2 * kvd),
             _lib.ptr(plan.bwd_kv), _lib.c_int(plan.bwd_kv.shape[0]), _lib.ptr(plan.bwd_q), _lib.c_int(plan.bwd_q.shape[0]),
             _lib.c_ll(Tl), _lib.c_int(n_heads), _lib.c_int(n_kv_heads), _lib.c_int(D), _lib.c_ll(ld(q)), _lib.c_ll(ld(o)),
             _lib.c_ll(ld(do)), _lib.c_ll(ld(dq)), _lib.c_ll(ld(dk)), _lib.c_ll(ld(dv)), _lib.c_float(scale), _map_array(layout),
-            _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev))
+            kv_map, _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev))
         _lib.check(rc, "halo_attn_cp_bwd")
-        exchange.barrier()                      # every rank's staging is complete
-        for rank, my_row, n, src_row in layout.returns:          # ascending rank: a fixed summation order
-            exchange.pull(dkv[my_row:my_row + n], exchange.dkv_ptrs[rank], src_row, n, accumulate=True)
+        exchange.barrier()                      # every rank's dK / dV are complete
+        if exchange.direct_reads:
+            for rank, my_row, n, src_row in layout.returns:          # ascending rank: a fixed summation order
+                exchange.pull(dkv[my_row:my_row + n], exchange.dkv_ptrs[rank], src_row, n, accumulate=True)
+        else:
+            # own contribution first (every local key tile was visited by a local query), then the peers' in rank order
+            for p in layout.pieces_of(layout.cp_rank):
+                lo, hi, at = int(layout.bounds[p]), int(layout.bounds[p + 1]), int(layout.loc[p])
+                if hi > lo:
+                    dkv[at:at + hi - lo].copy_(exchange.dkv[lo:hi])
+            for rank in range(layout.cp_size):
+                if rank == layout.cp_rank:
+                    continue
+                for lo, hi, _ in layout.written[rank]:
+                    owner, row = layout.to_local(lo)
+                    if owner == layout.cp_rank:
+                        exchange.pull(dkv[row:row + hi - lo], exchange.dkv_ptrs[rank], lo, hi - lo, accumulate=True)
         exchange.barrier()
         return dq, dkv[:, :kvd], dkv[:, kvd:], None, None, None, None, None, None
 
@@ -410,7 +486,7 @@ class ContextParallel:
         if self.device.type == "cuda":
             # a boundary moves by at most half a tile; a rank's pieces have four boundaries
             local = max_row_tokens // self.size + 4 * TILE
-            self.exchange = CPExchange(group, device, local, max_row_tokens, 2 * cfg.num_key_value_heads * cfg.head_dim)
+            self.exchange = CPExchange(group, device, local, max_row_tokens + TILE, 2 * cfg.num_key_value_heads * cfg.head_dim)
 
     def layout_of(self, cu_seqlens) -> CPLayout:
         return make_layout(cu_seqlens, self.rank, self.size, self.balance)

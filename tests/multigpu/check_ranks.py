@@ -247,9 +247,12 @@ def check_context_parallel(dev, rank, world):
         n = int(min(left, rng.integers(100, 3000)))
         lens.append(n)
         left -= n
-    ex = CPExchange(dist.group.WORLD, dev, total // world + 4 * TILE, total, 2 * Hkv * D)
-    for cu, balance in ((np.concatenate([[0], np.cumsum(lens)]), True), (np.array([0, total]), True),
-                        (np.concatenate([[0], np.cumsum(lens)]), False)):
+    exchanges = {False: CPExchange(dist.group.WORLD, dev, total // world + 4 * TILE, total + TILE, 2 * Hkv * D, direct_reads=False),
+                 True: CPExchange(dist.group.WORLD, dev, total // world + 4 * TILE, total + TILE, 2 * Hkv * D, direct_reads=True)}
+    chat = np.concatenate([[0], np.cumsum(lens)])
+    for cu, balance, direct in ((chat, True, False), (np.array([0, total]), True, False), (chat, False, False),
+                                (chat, True, True), (np.array([0, total]), True, True)):
+        ex = exchanges[direct]
         g = torch.Generator(device=dev).manual_seed(11)              # same data on every rank
         q = (torch.randn(total, Hq * D, device=dev, generator=g) * 0.5).bfloat16()
         k = (torch.randn(total, Hkv * D, device=dev, generator=g) * 0.5).bfloat16()
@@ -261,10 +264,17 @@ def check_context_parallel(dev, rank, world):
         lay = make_layout(cu, rank, world, balance)
         idx = torch.from_numpy(lay.local_index()).to(dev)
         ql, kl, vl = (t[idx].clone().requires_grad_() for t in (q, k, v))
-        out = cp_attention(ql, kl, vl, lay, build_cp_plan(lay, dev), dist.group.WORLD, ex, Hq, Hkv)
+        plan = build_cp_plan(lay, dev)
+        out = cp_attention(ql, kl, vl, lay, plan, dist.group.WORLD, ex, Hq, Hkv)
+        if not direct and len(cu) == 2:
+            # another exchange in between (as without recomputation): the backward must fetch its rows again; the other
+            # cases run the backward on the mirror their forward filled
+            with torch.no_grad():
+                cp_attention(ql.detach() * 0, kl.detach() * 0, vl.detach() * 0, lay, plan, dist.group.WORLD, ex, Hq, Hkv)
         out.backward(do[idx])
         torch.cuda.synchronize()
-        what = f"cp ({'paired' if balance else 'contiguous'} pieces, {len(cu) - 1} documents)"
+        what = (f"cp ({'paired' if balance else 'contiguous'} pieces, {len(cu) - 1} documents, "
+                f"{'tiles read from their owners' if direct else 'rows fetched once into the mirror'})")
         close(out, ref[idx], 2e-2, what + " out")
         close(ql.grad, qf.grad[idx], 3e-2, what + " dq")
         close(kl.grad, kf.grad[idx], 3e-2, what + " dk")
