@@ -403,29 +403,47 @@ __device__ __forceinline__ void push_units(const EpParams& ep, volatile int* abo
     for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
         const PushUnit pu = ep.units[u];
         __nv_bfloat16* dst_buf = reinterpret_cast<__nv_bfloat16*>(ep.row_bufs[pu.dst_rank]);
-        for (int i = pw; i < pu.n_rows; i += kPushWarps) {
-            const int slot = ep.send_slot[pu.pos0 + i];
-            const long long tok = slot / ep.k;
-            const int drow = pu.dst_row0 + i;
-            const uint4* src = reinterpret_cast<const uint4*>(ep.x + tok * ep.H);
-            uint4* dst = reinterpret_cast<uint4*>(dst_buf + (long long)drow * ep.H);
+        // This warp's rows are pw, pw + 4, ...: at most 32 of a unit's 128. Lane j fetches the routing slot of the warp's
+        // j-th row up front, so that no row's copy starts with a dependent index load; rows then go two at a time (sixteen
+        // 16-byte loads in flight per lane) because one row alone leaves the copy latency-bound.
+        const int n_mine = pu.n_rows > pw ? (pu.n_rows - pw + kPushWarps - 1) / kPushWarps : 0;
+        const int my_slot = lane < n_mine ? ep.send_slot[pu.pos0 + pw + lane * kPushWarps] : 0;
+        const float my_w = (ep.slot_w && lane < n_mine) ? ep.slot_w[my_slot] : 0.f;
+        for (int r = 0; r < n_mine; r += 2) {
+            const bool two = r + 1 < n_mine;
+            const int slot0 = __shfl_sync(0xffffffffu, my_slot, r);
+            const int slot1 = __shfl_sync(0xffffffffu, my_slot, two ? r + 1 : r);
+            const int drow0 = pu.dst_row0 + pw + r * kPushWarps;
+            const int drow1 = drow0 + kPushWarps;
+            const uint4* src0 = reinterpret_cast<const uint4*>(ep.x + (long long)(slot0 / ep.k) * ep.H);
+            const uint4* src1 = reinterpret_cast<const uint4*>(ep.x + (long long)(slot1 / ep.k) * ep.H);
+            uint4* dst0 = reinterpret_cast<uint4*>(dst_buf + (long long)drow0 * ep.H);
+            uint4* dst1 = reinterpret_cast<uint4*>(dst_buf + (long long)drow1 * ep.H);
             for (int v0 = 0; v0 < nvec; v0 += 32 * 8) {
-                uint4 val[8];
+                uint4 a[8], b[8];
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
                     const int v = v0 + q * 32 + lane;
-                    if (v < nvec) val[q] = src[v];
+                    if (v < nvec) {
+                        a[q] = src0[v];
+                        if (two) b[q] = src1[v];
+                    }
                 }
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
                     const int v = v0 + q * 32 + lane;
-                    if (v < nvec) dst[v] = val[q];
+                    if (v < nvec) {
+                        dst0[v] = a[q];
+                        if (two) dst1[v] = b[q];
+                    }
                 }
             }
-            if (lane == 0) {
-                ep.meta_bufs[pu.dst_rank][drow] = (ep.me << kMetaSlotBits) | slot;
-                if (ep.slot_w) ep.w_bufs[pu.dst_rank][drow] = ep.slot_w[slot];
-            }
+        }
+        // row metadata: lane j writes what belongs to the warp's j-th row
+        if (lane < n_mine) {
+            const int drow = pu.dst_row0 + pw + lane * kPushWarps;
+            ep.meta_bufs[pu.dst_rank][drow] = (ep.me << kMetaSlotBits) | my_slot;
+            if (ep.slot_w) ep.w_bufs[pu.dst_rank][drow] = my_w;
         }
         // all four push warps have issued their stores of this unit; one thread publishes the rows
         asm volatile("bar.sync 1, %0;" ::"n"(kPushWarps * 32) : "memory");
