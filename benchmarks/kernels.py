@@ -142,6 +142,19 @@ def cases(small: bool):
     big = torch.empty(1 << 30, dtype=torch.bfloat16, device="cuda") if not small else torch.empty(1 << 27, dtype=torch.bfloat16, device="cuda")
     big2 = torch.empty_like(big)
     out["copy_reference"] = (lambda: big2.copy_(big), 0.0, 2.0 * 2 * big.numel())
+
+    # ---- optimizer steps on one large tensor: bf16 moments (14 bytes moved per parameter) and 8-bit moments with 24-bit
+    # weights (12 bytes per parameter) ------------------------------------------------------------
+    from halo_b200.optim.adamw_bf16 import AdamWBF16
+    from halo_b200.optim.adamw_q8 import AdamWQ8
+
+    n_opt = (1 << 25) if small else (1 << 28)
+    for label, cls, moved in (("adamw_bf16_step", AdamWBF16, 14.0), ("adamw_q8_step", AdamWQ8, 12.0)):
+        p_opt = torch.nn.Parameter(bf16(n_opt))
+        p_opt.grad = bf16(n_opt)
+        opt = cls([("w", p_opt)], lr=1e-4)
+        opt.step()                                   # state allocation outside the timed calls
+        out[label] = (opt.step, 0.0, moved * n_opt)
     return out
 
 
