@@ -51,6 +51,9 @@ def parse_args():
     ap.add_argument("--fused-optimizer", type=int, default=1,
                     help="N > 1: 1 = fused reduce-scatter/AdamW/all-gather kernels for the replicated parameters, "
                          "0 = NCCL all-reduce + local optimizer (the baseline path)")
+    ap.add_argument("--zero3", type=int, default=0,
+                    help="N > 1: shard the decoder layers' replicated matrices over the ranks (gathered per layer pass by pull "
+                         "kernels, gradients reduce-scattered per layer); the remaining parameters take the plain path")
     ap.add_argument("--doc-dist", default="chat")
     ap.add_argument("--host-compute", default="0", choices=["auto", "0", "1"],
                     help="update host-resident optimizer state on the host CPU instead of streaming it through the device "
@@ -220,7 +223,19 @@ def main() -> int:
         transport.configure(max_tokens=args.seq_len, top_k=cfg.num_experts_per_tok, hidden=cfg.hidden_size,
                             n_local_experts=cfg.num_experts // world)
     model = build_model(cfg, device=dev, seed=0, transport=transport, gradient_checkpointing=True)
-    named = list(model.named_parameters())
+    zero3 = None
+    if parallel is not None and args.zero3:
+        from halo_b200.parallel.zero3 import shard_layers
+
+        zero3 = shard_layers(model, parallel.dp_group, dev, ep_world=world if cfg.is_moe else 1)
+        args.fused_optimizer = 0
+        args.recompute = "full"
+    named = [(n, p) for n, p in model.named_parameters() if not getattr(p, "zero3_managed", False)]
+    if zero3 is not None:
+        # one decaying group for the flat shard and the remaining matrices, one without decay for the vectors
+        from halo_b200.optim.factory import decay_groups
+
+        named = decay_groups(named, 0.01)
     if parallel is not None and args.fused_optimizer:
         # replicated parameters: sharded AdamWBF16 fused with reduce-scatter / all-gather over peer memory
         named = parallel.enable_fused_optimizer(model, lr=args.lr, weight_decay=0.01)
@@ -334,6 +349,7 @@ def main() -> int:
                 "global_batch": world, "seq_len": args.seq_len, "parallelism": par,
                 "ep_size": world if cfg.is_moe else 1, "dp_size": world,
                 "fused_zero": bool(parallel is not None and parallel.fused_optimizer is not None),
+                "zero3_layers": bool(zero3 is not None),
                 "light_layers": light_layers,
                 "optimizer": "AdamWBF16 (bf16 weights and moments, stochastic rounding), max_grad_norm 1.0",
                 "gradient_checkpointing": (f"per decoder layer; {light_layers} of {len(model.layers)} layers re-run only their "

@@ -57,7 +57,16 @@ def load_model_weights(model, directory: str, strict: bool = True) -> dict:
     missing, loaded = [], 0
     tp = getattr(model, "tensor_parallel", None)
     etp = getattr(model, "expert_tensor_parallel", None)
+    # layer matrices that live as 1 / N slices (ZeRO-3): filled into host stand-ins of their full shape, from which every
+    # rank then keeps its slices
+    zero3 = getattr(model, "zero3", None)
+    full_shapes = {n: shape for items in zero3.params for n, _, _, _, shape in items} if zero3 is not None else {}
+    stand_ins: dict = {}
     for name, p in model.named_parameters():
+        if name == "zero3_shard":
+            continue
+        if name in full_shapes:
+            p = stand_ins.setdefault(name, torch.empty(full_shapes[name], dtype=zero3.dtype))
         is_expert = getattr(p, "is_expert", False)
         offset = ep_rank * p.shape[0] if is_expert else 0
         tp_kind = getattr(p, "tp_kind", None) if tp is not None else None
@@ -97,6 +106,8 @@ def load_model_weights(model, directory: str, strict: bool = True) -> dict:
                 dst.add_(1)
             loaded += 1
     index.close()
+    if stand_ins:
+        zero3.load_full(stand_ins)              # collective: ends with a barrier
     if strict and missing:
         raise KeyError(f"{len(missing)} tensors are absent from {directory!r}, e.g. {missing[:4]}: refusing to leave "
                        f"parameters at their random initialisation")

@@ -98,12 +98,21 @@ def save_model(model, directory: str, is_writer: bool | None = None, save_dtype:
         elif is_writer:
             remove_stale_staged(directory)
             writer = StreamingShardWriter(directory, max_shard_bytes, save_dtype)
-    # 1. non-expert tensors (replicated: taken from the writer's copy)
+    # 1. non-expert tensors (replicated: taken from the writer's copy; layer matrices sharded over the data-parallel
+    #    ranks are assembled one layer at a time, a collective every rank takes part in)
     tp = getattr(model, "tensor_parallel", None)
+    zero3 = getattr(model, "zero3", None)
+    zero3_layer, zero3_full = -1, {}
     for name, p in base_parameters():
-        if getattr(p, "is_expert", False):
+        if getattr(p, "is_expert", False) or name == "zero3_shard":
             continue
-        t_full = saved_tensor(name, p)
+        if zero3 is not None and getattr(p, "zero3_managed", False):
+            li = int(name.split(".")[1])
+            if li != zero3_layer:
+                zero3_layer, zero3_full = li, zero3.full_tensors(li)
+            t_full = zero3_full[name]
+        else:
+            t_full = saved_tensor(name, p)
         if tp is not None and getattr(p, "tp_kind", None) is not None:
             from halo_b200.parallel.tensor_parallel import gather_full_weight
 

@@ -83,6 +83,19 @@ struct PeerMaps {
     CUtensorMap k[8];
     CUtensorMap v[8];
 };
+// What a context-parallel instantiation takes beyond the plain kernel's arguments; the plain instantiation carries one
+// unused byte instead, so its parameter block (and its launch cost on lists of many short CTAs) stays what it was.
+template <bool kCP>
+struct CpArgs {
+    PeerMaps peers;
+    CpMap cp;      // query rows
+    CpMap cpk;     // key rows
+};
+template <>
+struct CpArgs<false> {
+    char unused;
+};
+
 __device__ __forceinline__ int cp_piece(const CpMap& m, int row) {
     int pc = 0;
     while (pc + 1 < m.n_pieces && row >= m.bound[pc + 1]) ++pc;
@@ -826,8 +839,7 @@ template <bool kCP>
 __global__ void __launch_bounds__(kBwd2Threads, 1)
 attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                      const BwdParams p, const __grid_constant__ PeerMaps peers, const __grid_constant__ CpMap cp,
-                    const __grid_constant__ CpMap cpk) {
+                      const BwdParams p, const __grid_constant__ CpArgs<kCP> ca) {
     if (status_poisoned(p.status)) return;
     extern __shared__ __align__(1024) uint8_t smem_b2[];
     const uint32_t base = smem_u32(smem_b2);
@@ -848,7 +860,7 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const int kv_head = blockIdx.x;
     const int group = p.Hq / p.Hkv;
     BwdKvWorkCp w;
-    if (kCP) {
+    if constexpr (kCP) {
         w = reinterpret_cast<const BwdKvWorkCp*>(p.work)[blockIdx.y];
     } else {
         const BwdKvWork w4 = reinterpret_cast<const BwdKvWork*>(p.work)[blockIdx.y];
@@ -858,12 +870,12 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const int n_iter = (w.n_q + w.n_q2) * group;
     // global first query row of 64-query sub-tile `sub`, and what to subtract from a global query row for its local row
     int q_shift1 = 0, q_shift2 = 0;
-    if (kCP) {
-        const int p1 = cp_piece(cp, w.q_begin);
-        q_shift1 = cp.bound[p1] - cp.loc[p1];
+    if constexpr (kCP) {
+        const int p1 = cp_piece(ca.cp, w.q_begin);
+        q_shift1 = ca.cp.bound[p1] - ca.cp.loc[p1];
         if (w.n_q2 > 0) {
-            const int p2 = cp_piece(cp, w.q_begin2);
-            q_shift2 = cp.bound[p2] - cp.loc[p2];
+            const int p2 = cp_piece(ca.cp, w.q_begin2);
+            q_shift2 = ca.cp.bound[p2] - ca.cp.loc[p2];
         }
     }
     auto q_row = [&](int sub) -> int { return sub < w.n_q ? w.q_begin + sub * 64 : w.q_begin2 + (sub - w.n_q) * 64; };
@@ -896,11 +908,11 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             const CUtensorMap* mapK = &tmK;
             const CUtensorMap* mapV = &tmV;
             int k_loc = w.kv0;
-            if (kCP) {
-                const int pk = cp_piece(cpk, w.kv0);
-                mapK = &peers.k[cpk.owner[pk]];
-                mapV = &peers.v[cpk.owner[pk]];
-                k_loc = w.kv0 - cpk.bound[pk] + cpk.loc[pk];
+            if constexpr (kCP) {
+                const int pk = cp_piece(ca.cpk, w.kv0);
+                mapK = &ca.peers.k[ca.cpk.owner[pk]];
+                mapV = &ca.peers.v[ca.cpk.owner[pk]];
+                k_loc = w.kv0 - ca.cpk.bound[pk] + ca.cpk.loc[pk];
             }
             tma_load_2d(sK, mapK, bar(kKv), kv_head * kHd, k_loc);
             tma_load_2d(sK + 16384, mapK, bar(kKv), kv_head * kHd + 64, k_loc);
@@ -1057,15 +1069,15 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             long long ld = g == 0 ? p.ld_dk : p.ld_dv;
             void* out_base = g == 0 ? p.dK : p.dV;
             long long out_row = key_abs;
-            if (kCP) {
-                const int pk = cp_piece(cpk, w.kv0);
-                if (cpk.owner[pk] == cpk.my_rank) {
-                    out_row = key_abs - cpk.bound[pk] + cpk.loc[pk];
+            if constexpr (kCP) {
+                const int pk = cp_piece(ca.cpk, w.kv0);
+                if (ca.cpk.owner[pk] == ca.cpk.my_rank) {
+                    out_row = key_abs - ca.cpk.bound[pk] + ca.cpk.loc[pk];
                 } else {
                     out_base = g == 0 ? p.dK_stage : p.dV_stage;
                     ld = p.ld_stage;
-                    out_row = key_abs - cpk.bound[pk] + cpk.stage[pk];
-                    if (cpk.stage[pk] < 0) {            // no staging was planned for this piece: record it, write nothing
+                    out_row = key_abs - ca.cpk.bound[pk] + ca.cpk.stage[pk];
+                    if (ca.cpk.stage[pk] < 0) {            // no staging was planned for this piece: record it, write nothing
                         live = false;
                         if (key == 0 && half == 0 && p.status) atomicCAS(p.status, kStatusOk, kStatusBounds);
                     }
@@ -1113,8 +1125,7 @@ template <bool kCP>
 __global__ void __launch_bounds__(kBwd2Threads, 1)
 attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                    const BwdParams p, const __grid_constant__ PeerMaps peers, const __grid_constant__ CpMap cp,
-                    const __grid_constant__ CpMap cpk) {
+                    const BwdParams p, const __grid_constant__ CpArgs<kCP> ca) {
     if (status_poisoned(p.status)) return;
     extern __shared__ __align__(1024) uint8_t smem_q2[];
     const uint32_t base = smem_u32(smem_q2);
@@ -1134,9 +1145,9 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int kv_head = head / (p.Hq / p.Hkv);
     const BwdQWork w = reinterpret_cast<const BwdQWork*>(p.work)[blockIdx.y];
     int q_shift = 0;                    // global query row - q_shift = local row (queries, dO, statistics, dQ are local)
-    if (kCP) {
-        const int pq = cp_piece(cp, w.q0);
-        q_shift = cp.bound[pq] - cp.loc[pq];
+    if constexpr (kCP) {
+        const int pq = cp_piece(ca.cp, w.q0);
+        q_shift = ca.cp.bound[pq] - ca.cp.loc[pq];
     }
 
     if (threadIdx.x == 0) {
@@ -1170,11 +1181,11 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 int kr = w.kv0 + j * 64;
                 const CUtensorMap* mapK = &tmK;
                 const CUtensorMap* mapV = &tmV;
-                if (kCP) {                       // the sub-tile's owner and its row in that rank's published buffer
-                    const int pk = cp_piece(cpk, kr);
-                    mapK = &peers.k[cpk.owner[pk]];
-                    mapV = &peers.v[cpk.owner[pk]];
-                    kr = kr - cpk.bound[pk] + cpk.loc[pk];
+                if constexpr (kCP) {                       // the sub-tile's owner and its row in that rank's published buffer
+                    const int pk = cp_piece(ca.cpk, kr);
+                    mapK = &ca.peers.k[ca.cpk.owner[pk]];
+                    mapV = &ca.peers.v[ca.cpk.owner[pk]];
+                    kr = kr - ca.cpk.bound[pk] + ca.cpk.loc[pk];
                 }
                 mbar_expect_tx(full, 2 * kHalfTile);
                 tma_load_2d(sK, mapK, full, kv_head * kHd, kr);
@@ -1565,8 +1576,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 template <bool kCP>
 __global__ void __maxnreg__(128)
 attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, const AttnParams p, const __grid_constant__ PeerMaps peers,
-                 const __grid_constant__ CpMap cp, const __grid_constant__ CpMap cpk) {
+                 const __grid_constant__ CUtensorMap tmV, const AttnParams p, const __grid_constant__ CpArgs<kCP> ca) {
     if (status_poisoned(p.status)) return;
     extern __shared__ __align__(1024) uint8_t smem3[];
     const uint32_t base = smem_u32(smem3);
@@ -1586,9 +1596,9 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int kv_head = head / (p.Hq / p.Hkv);
     const FwdWork w = p.work[blockIdx.y];
     int q_shift = 0;                    // global query row - q_shift = local row (queries, outputs, statistics are local)
-    if (kCP) {
-        const int pq = cp_piece(cp, w.q0);
-        q_shift = cp.bound[pq] - cp.loc[pq];
+    if constexpr (kCP) {
+        const int pq = cp_piece(ca.cp, w.q0);
+        q_shift = ca.cp.bound[pq] - ca.cp.loc[pq];
     }
 
     if (threadIdx.x == 0) {
@@ -1628,11 +1638,11 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 int kr = w.kv0 + j * 64;
                 const CUtensorMap* mapK = &tmK;
                 const CUtensorMap* mapV = &tmV;
-                if (kCP) {                       // the tile's owner and its row in that rank's published buffer
-                    const int pk = cp_piece(cpk, kr);
-                    mapK = &peers.k[cpk.owner[pk]];
-                    mapV = &peers.v[cpk.owner[pk]];
-                    kr = kr - cpk.bound[pk] + cpk.loc[pk];
+                if constexpr (kCP) {                       // the tile's owner and its row in that rank's published buffer
+                    const int pk = cp_piece(ca.cpk, kr);
+                    mapK = &ca.peers.k[ca.cpk.owner[pk]];
+                    mapV = &ca.peers.v[ca.cpk.owner[pk]];
+                    kr = kr - ca.cpk.bound[pk] + ca.cpk.loc[pk];
                 }
                 mbar_expect_tx(full, 2 * kHalfTile);
                 tma_load_2d(sK, mapK, full, kv_head * kHd, kr);
@@ -1810,8 +1820,7 @@ static int set_smem(const void* fn, int bytes) {
 }
 
 // what the kernels get when context parallelism is off (never read)
-static PeerMaps g_no_peers{};
-static CpMap g_no_cp{};
+static CpArgs<false> g_no_cp_args{};
 
 // Tensor maps over every rank's published key / value buffer (box of `box_rows` rows) and the piece table.
 static int fill_peer_maps(PeerMaps* peers, void* const* kv_ptrs, int n_bufs, long long kv_rows, long long kv_ld, int v_col,
@@ -1910,7 +1919,7 @@ int halo_attn_fwd3(const void* q, const void* k, const void* v, void* o, float* 
         cfg = true;
     }
     AttnParams p{reinterpret_cast<const FwdWork*>(work), o, lse, ldo, T, Hq, Hkv, scale, status};
-    attn_fwd3_kernel<false><<<dim3(Hq, n_tiles), kFwdThreads, kFwd2Smem, (cudaStream_t)stream>>>(tq, tk, tv, p, g_no_peers, g_no_cp, g_no_cp);
+    attn_fwd3_kernel<false><<<dim3(Hq, n_tiles), kFwdThreads, kFwd2Smem, (cudaStream_t)stream>>>(tq, tk, tv, p, g_no_cp_args);
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -1926,10 +1935,9 @@ int halo_attn_cp_fwd(const void* q, void* const* kv_ptrs, int n_ranks, long long
     if (n_tiles == 0) return 0;
     CUtensorMap tq;
     if (make_tmap_bf16(&tq, q, T_local, (long long)Hq * kHd, ldq, 128)) return -2;
-    PeerMaps peers;
-    CpMap cp, cpk;
-    if (fill_peer_maps(&peers, kv_ptrs, n_ranks, kv_rows, kv_ld, v_col, Hkv, 64)) return -3;
-    if (fill_cp_map(&cp, cp_map, 8) || fill_cp_map(&cpk, kv_map, n_ranks)) return -4;
+    static CpArgs<true> ca;                  // 3 KB: kept off the stack; entry points are called from one thread per process
+    if (fill_peer_maps(&ca.peers, kv_ptrs, n_ranks, kv_rows, kv_ld, v_col, Hkv, 64)) return -3;
+    if (fill_cp_map(&ca.cp, cp_map, 8) || fill_cp_map(&ca.cpk, kv_map, n_ranks)) return -4;
     static bool cfg = false;
     if (!cfg) {
         if (set_smem((const void*)attn_fwd3_kernel<true>, kFwd2Smem)) return -10;
@@ -1938,7 +1946,7 @@ int halo_attn_cp_fwd(const void* q, void* const* kv_ptrs, int n_ranks, long long
         cfg = true;
     }
     AttnParams p{reinterpret_cast<const FwdWork*>(work), o, lse, ldo, T_local, Hq, Hkv, scale, status};
-    attn_fwd3_kernel<true><<<dim3(Hq, n_tiles), kFwdThreads, kFwd2Smem, (cudaStream_t)stream>>>(tq, peers.k[0], peers.v[0], p, peers, cp, cpk);
+    attn_fwd3_kernel<true><<<dim3(Hq, n_tiles), kFwdThreads, kFwd2Smem, (cudaStream_t)stream>>>(tq, ca.peers.k[0], ca.peers.v[0], p, ca);
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -2014,13 +2022,13 @@ int halo_attn_bwd(const void* q, const void* k, const void* v, const void* o, co
     BwdParams p{kv_work, lse, delta, dq, dk, dv, ld_dq, ld_dk, ld_dv, T, Hq, Hkv, scale, status};
     if (n_kv_tiles > 0) {
         if (variant == 2)
-            attn_bwd_dkdv2_kernel<false><<<dim3(Hkv, n_kv_tiles), kBwd2Threads, kBwdKv2Smem, s>>>(tq64, tk, tv, tdo64, p, g_no_peers, g_no_cp, g_no_cp);
+            attn_bwd_dkdv2_kernel<false><<<dim3(Hkv, n_kv_tiles), kBwd2Threads, kBwdKv2Smem, s>>>(tq64, tk, tv, tdo64, p, g_no_cp_args);
         else attn_bwd_dkdv_kernel<<<dim3(Hkv, n_kv_tiles), kBwdThreads, kBwdKvSmem, s>>>(tq64, tk, tv, tdo64, p);
     }
     p.work = q_work;
     if (n_q_tiles > 0) {
         if (variant == 2)
-            attn_bwd_dq2_kernel<false><<<dim3(Hq, n_q_tiles), kBwd2Threads, kBwdQ2Smem, s>>>(tq, tk64, tv64, tdo, p, g_no_peers, g_no_cp, g_no_cp);
+            attn_bwd_dq2_kernel<false><<<dim3(Hq, n_q_tiles), kBwd2Threads, kBwdQ2Smem, s>>>(tq, tk64, tv64, tdo, p, g_no_cp_args);
         else attn_bwd_dq_kernel<<<dim3(Hq, n_q_tiles), kBwdThreads, kBwdQSmem, s>>>(tq, tk64, tv64, tdo, p);
     }
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
@@ -2045,11 +2053,12 @@ int halo_attn_cp_bwd(const void* q, void* const* kv_ptrs, int n_ranks, long long
     if (make_tmap_bf16(&tdo, d_o, T_local, (long long)Hq * kHd, ld_do, 128)) return -5;
     if (make_tmap_bf16(&tq64, q, T_local, (long long)Hq * kHd, ldq, 64)) return -6;
     if (make_tmap_bf16(&tdo64, d_o, T_local, (long long)Hq * kHd, ld_do, 64)) return -9;
-    PeerMaps peers128, peers64;
-    CpMap cp, cpk;
-    if (fill_peer_maps(&peers128, kv_ptrs, n_ranks, kv_rows, kv_ld, v_col, Hkv, 128)) return -3;
-    if (fill_peer_maps(&peers64, kv_ptrs, n_ranks, kv_rows, kv_ld, v_col, Hkv, 64)) return -4;
-    if (fill_cp_map(&cp, cp_map, 8) || fill_cp_map(&cpk, kv_map, n_ranks)) return -12;
+    static CpArgs<true> ca128, ca64;         // key / value tensor maps with 128- and 64-row boxes
+    if (fill_peer_maps(&ca128.peers, kv_ptrs, n_ranks, kv_rows, kv_ld, v_col, Hkv, 128)) return -3;
+    if (fill_peer_maps(&ca64.peers, kv_ptrs, n_ranks, kv_rows, kv_ld, v_col, Hkv, 64)) return -4;
+    if (fill_cp_map(&ca128.cp, cp_map, 8) || fill_cp_map(&ca128.cpk, kv_map, n_ranks)) return -12;
+    ca64.cp = ca128.cp;
+    ca64.cpk = ca128.cpk;
     static bool cfg = false;
     if (!cfg) {
         if (set_smem((const void*)attn_bwd_dkdv2_kernel<true>, kBwdKv2Smem)) return -10;
@@ -2058,12 +2067,12 @@ int halo_attn_cp_bwd(const void* q, void* const* kv_ptrs, int n_ranks, long long
     }
     BwdParams p{kv_work, lse, delta, dq, dk, dv, ld_dq, ld_dk, ld_dv, T_local, Hq, Hkv, scale, status, dk_stage, dv_stage, ld_stage};
     if (n_kv_tiles > 0)
-        attn_bwd_dkdv2_kernel<true><<<dim3(Hkv, n_kv_tiles), kBwd2Threads, kBwdKv2Smem, s>>>(tq64, peers128.k[0], peers128.v[0], tdo64,
-                                                                                             p, peers128, cp, cpk);
+        attn_bwd_dkdv2_kernel<true><<<dim3(Hkv, n_kv_tiles), kBwd2Threads, kBwdKv2Smem, s>>>(tq64, ca128.peers.k[0], ca128.peers.v[0],
+                                                                                             tdo64, p, ca128);
     p.work = q_work;
     if (n_q_tiles > 0)
-        attn_bwd_dq2_kernel<true><<<dim3(Hq, n_q_tiles), kBwd2Threads, kBwdQ2Smem, s>>>(tq, peers64.k[0], peers64.v[0], tdo, p,
-                                                                                        peers64, cp, cpk);
+        attn_bwd_dq2_kernel<true><<<dim3(Hq, n_q_tiles), kBwd2Threads, kBwdQ2Smem, s>>>(tq, ca64.peers.k[0], ca64.peers.v[0], tdo, p,
+                                                                                        ca64);
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -204,6 +204,32 @@ broadcast_bytes_kernel(const uint4* __restrict__ src, const __grid_constant__ Pe
     }
 }
 
+// All-gather by pulls: dst[r * nvec + i] = shard_r[src_off + i] for every rank r (16-byte vectors; shard_r may be a peer
+// GPU's memory). Four loads in flight per thread cover the NVLink round trip. Used to assemble a layer's sharded
+// parameters in local memory right before the layer runs.
+__global__ void __launch_bounds__(256)
+allgather_pull_kernel(uint4* __restrict__ dst, const __grid_constant__ Peers shards, int n_ranks, long long src_off_vec,
+                      long long nvec) {
+    const long long total = nvec * n_ranks;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < total; i += 4 * stride) {
+        uint4 v[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const long long j = i + q * stride;
+            const int r = (int)(j / nvec);
+            v[q] = reinterpret_cast<const uint4*>(shards.p[r])[src_off_vec + (j - (long long)r * nvec)];
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) dst[i + q * stride] = v[q];
+    }
+    for (; i < total; i += stride) {
+        const int r = (int)(i / nvec);
+        dst[i] = reinterpret_cast<const uint4*>(shards.p[r])[src_off_vec + (i - (long long)r * nvec)];
+    }
+}
+
 // dst[i] = src[i] where src may be another GPU's memory mapped into this process (16-byte vectors, four
 // loads in flight per thread to cover the NVLink round trip).
 __global__ void __launch_bounds__(256)
@@ -395,6 +421,21 @@ int halo_broadcast_bytes(const void* src, void* const* dsts, int n_dst, long lon
     if (blocks > 148 * 8) blocks = 148 * 8;
     broadcast_bytes_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const uint4*)src, d, n_dst,
                                                                              dst_offset / 16, nvec);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// dst: n_ranks * n_bytes_per_rank local bytes; shards[r] + src_offset: rank r's n_bytes_per_rank bytes.
+int halo_allgather_pull(void* dst, void* const* shards, int n_ranks, long long src_offset, long long n_bytes_per_rank,
+                        void* stream) {
+    if ((n_bytes_per_rank % 16) || (src_offset % 16) || (reinterpret_cast<uintptr_t>(dst) % 16)) return -1;
+    if (n_bytes_per_rank == 0) return 0;
+    Peers p;
+    if (fill(&p, shards, n_ranks)) return -2;
+    const long long nvec = n_bytes_per_rank / 16;
+    long long blocks = (nvec * n_ranks + 1023) / 1024;
+    if (blocks > 148 * 4) blocks = 148 * 4;
+    if (blocks < 1) blocks = 1;
+    allgather_pull_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((uint4*)dst, p, n_ranks, src_offset / 16, nvec);
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -245,6 +245,19 @@ def load_policy_model(model_args, pc, device, runtime, gradient_checkpointing=Tr
     else:
         model = from_pretrained(model_args.model_name_or_path, device=device, dtype=dtype, transport=transport,
                                 gradient_checkpointing=gradient_checkpointing)
+    if getattr(pc, "fsdp_reshard_after_forward", False) and runtime is not None and runtime.dp_world > 1:
+        # ZeRO-3: the decoder layers' replicated matrices live as 1 / N slices and are gathered per layer pass
+        from halo_b200.parallel.zero3 import shard_layers
+
+        if not gradient_checkpointing:
+            raise ValueError("fsdp_reshard_after_forward gathers a layer's weights for each of its passes: it needs "
+                             "gradient_checkpointing: true")
+        if getattr(model_args, "use_peft", False):
+            raise ValueError("fsdp_reshard_after_forward with use_peft is not wired: the frozen base would be sharded, the "
+                             "adapters are tiny")
+        z = shard_layers(model, runtime.dp_group, device, ep_world=runtime.ep_world)
+        log.info("ZeRO-3: %d layer matrices sharded over %d ranks, %.1f M parameters per rank (plus two layers of staging)",
+                 sum(len(x) for x in z.params), z.world, z.shard_total / 1e6)
     from halo_b200.models.attention_selection import describe
 
     log.info(describe(model.cfg, device, dtype))

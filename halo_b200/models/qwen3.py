@@ -577,6 +577,7 @@ class Qwen3Model(nn.Module):
         # optional hook ``gate(params)`` called before a group of parameters is first read in a step;
         # an optimizer that updates parameters asynchronously uses it to order the reads
         self.param_gate = None
+        self.layer_hooks = None          # halo_b200.parallel.zero3.Zero3Layers when the layers' matrices are sharded over the ranks
 
     # ---- initialisation ----------------------------------------------------------------------
     @torch.no_grad()
@@ -673,13 +674,25 @@ class Qwen3Model(nn.Module):
         return x
 
     def run_layers(self, x, ctx):
-        for layer in self.layers:
+        hooks = self.layer_hooks          # sharded layer parameters: gathered around each layer's passes
+        for i, layer in enumerate(self.layers):
             self._gate(layer.parameters())
             policy = layer.recompute_policy if (self.gradient_checkpointing and torch.is_grad_enabled()) else "none"
+            if hooks is not None and torch.is_grad_enabled():
+                if not self.gradient_checkpointing:
+                    raise RuntimeError("sharded layer parameters are gathered per layer pass: training needs per-layer "
+                                       "recomputation (gradient_checkpointing: true)")
+                policy = "full"
             if policy == "full":
-                x = recompute(layer, x, ctx)
+                x = recompute(layer, x, ctx, hooks, i)
             elif policy == "mlp":
                 x = recompute(layer.mlp_half, layer.attention_half(x, ctx), ctx)
+            elif hooks is not None:
+                hooks.before_layer(i, backward=False)
+                try:
+                    x = layer(x, ctx)
+                finally:
+                    hooks.after_layer(i, backward=False)
             else:
                 x = layer(x, ctx)
         return x

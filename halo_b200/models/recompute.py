@@ -18,16 +18,25 @@ import torch
 
 class _Recompute(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, layer, fwd_ctx, x):
-        ctx.layer, ctx.fwd_ctx = layer, fwd_ctx
+    def forward(ctx, layer, fwd_ctx, x, hooks, index):
+        ctx.layer, ctx.fwd_ctx, ctx.hooks, ctx.index = layer, fwd_ctx, hooks, index
         ctx.save_for_backward(x)
-        with torch.no_grad():
-            return layer(x, fwd_ctx)
+        if hooks is not None:
+            hooks.before_layer(index, backward=False)
+        try:
+            with torch.no_grad():
+                return layer(x, fwd_ctx)
+        finally:
+            if hooks is not None:
+                hooks.after_layer(index, backward=False)
 
     @staticmethod
     def backward(ctx, grad_out):
         (x,) = ctx.saved_tensors
         xin = x.detach().requires_grad_(True)
+        hooks = ctx.hooks
+        if hooks is not None:
+            hooks.before_layer(ctx.index, backward=True)
         # the value of this second pass is never read (only its graph is): the layer's last op may skip
         # producing it
         ctx.fwd_ctx.output_unused = True
@@ -37,11 +46,16 @@ class _Recompute(torch.autograd.Function):
         finally:
             ctx.fwd_ctx.output_unused = False
         torch.autograd.backward(out, grad_out)
-        return None, None, xin.grad
+        if hooks is not None:
+            hooks.after_layer(ctx.index, backward=True)
+        return None, None, xin.grad, None, None
 
 
-def recompute(layer, x: torch.Tensor, fwd_ctx) -> torch.Tensor:
+def recompute(layer, x: torch.Tensor, fwd_ctx, hooks=None, index: int = -1) -> torch.Tensor:
+    """``hooks``: an object with ``before_layer(index, backward)`` / ``after_layer(index, backward)`` called around the
+    layer's first pass and around its re-run + backward: the two windows in which the layer's parameters are needed
+    (sharded parameters are gathered for exactly those windows, their gradients reduced right after the second)."""
     if not x.requires_grad:
         # nothing upstream needs a gradient, but the layer's parameters do: give autograd an edge
         x = x.detach().requires_grad_(True)
-    return _Recompute.apply(layer, fwd_ctx, x)
+    return _Recompute.apply(layer, fwd_ctx, x, hooks, index)

@@ -64,6 +64,12 @@ def dequantize_moments(mq, vq, m_scale, v_scale):
     return m, s * s
 
 
+def _sqrt32(x: torch.Tensor) -> torch.Tensor:
+    """Correctly rounded fp32 square root (what ``sqrtf`` gives on the device): the CPU's vectorised fp32 ``sqrt`` is off
+    by an ulp on a fraction of a percent of inputs; rounding the fp64 root to fp32 is exact."""
+    return x.double().sqrt().float()
+
+
 def adamw_q8_step_reference(p, g, corr, mq, vq, m_scale, v_scale, *, beta1, beta2, step_size, bc2_sqrt, eps, wd_factor, key, step,
                             name_hash, grad_scale=None, skip=False):
     """Bit-exact CPU twin of ``adamw_q8_kernel`` for one tensor (updates every state tensor in place)."""
@@ -86,7 +92,7 @@ def adamw_q8_step_reference(p, g, corr, mq, vq, m_scale, v_scale, *, beta1, beta
     omb2 = f32(1.0 - float(np.float32(beta2)))
     mn = m * f32(beta1) + gf * omb1
     vn = v_from_codes * f32(beta2) + (gf * gf) * omb2
-    sn = vn.sqrt()
+    sn = _sqrt32(vn)
     denom = sn / f32(bc2_sqrt) + f32(eps)
     wn = w * f32(wd_factor) - (f32(step_size) * mn) / denom
     # group maxima
@@ -104,11 +110,11 @@ def adamw_q8_step_reference(p, g, corr, mq, vq, m_scale, v_scale, *, beta1, beta
     uv = ((rnd_t >> 11) & 0x7FF).float() / 2048.0
     uc = (rnd_t >> 22).float() / 1024.0
     safe_mm = torch.where(mm > 0, mm, torch.ones_like(mm))
-    qm = torch.floor(torch.sqrt(mn.abs() / safe_mm) * 127.0 + um).clamp(max=127.0)
+    qm = torch.floor(_sqrt32(mn.abs() / safe_mm) * 127.0 + um).clamp(max=127.0)
     qm = torch.where(mm > 0, qm, torch.zeros_like(qm))
     qm = torch.where(mn < 0, -qm, qm)
     safe_sm = torch.where(sm > 0, sm, torch.ones_like(sm))
-    qv = torch.floor(torch.sqrt(sn / safe_sm) * 255.0 + uv).clamp(min=1.0, max=255.0)
+    qv = torch.floor(_sqrt32(sn / safe_sm) * 255.0 + uv).clamp(min=1.0, max=255.0)
     qv = torch.where((sm > 0) & (sn > 0), qv, torch.zeros_like(qv))
     pn = wn.bfloat16()
     pnf = pn.float()

@@ -15,9 +15,9 @@ def decay_groups(named_params, weight_decay: float) -> list[dict]:
     """Matrices decay; norms, biases and other 1-D tensors do not."""
     decay, no_decay = {"params": [], "param_names": []}, {"params": [], "param_names": []}
     for name, p in named_params:
-        if not p.requires_grad:
-            continue
-        g = no_decay if p.dim() <= 1 else decay
+        if not p.requires_grad or getattr(p, "zero3_managed", False):
+            continue          # frozen, or a layer matrix that lives in the rank's flat ZeRO-3 shard (stepped through that)
+        g = no_decay if (p.dim() <= 1 and not getattr(p, "flat_matrices", False)) else decay
         g["params"].append(p)
         g["param_names"].append(name)
     groups = []

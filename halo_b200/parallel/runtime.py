@@ -225,10 +225,16 @@ class ParallelRuntime:
         everything else."""
         experts, shared = [], []
         for p in model.parameters():
-            if p.grad is None or getattr(p, "tp_kind", None) is not None:
+            if p.grad is None or getattr(p, "tp_kind", None) is not None or getattr(p, "dp_sharded", False):
                 continue
             (experts if getattr(p, "is_expert", False) and self.ep_world > 1 else shared).append(p)
         return experts, shared
+
+    @staticmethod
+    def dp_sharded_params(model):
+        """Parameters of which every data-parallel rank holds a different 1 / N (a ZeRO-3 flat shard): their gradients are
+        already reduced, their squared norms add over the ranks."""
+        return [p for p in model.parameters() if p.grad is not None and getattr(p, "dp_sharded", False)]
 
     @staticmethod
     def sliced_params(model):
@@ -287,5 +293,12 @@ class ParallelRuntime:
             tmp = grad_norm.total_sq.clone()
             grad_norm.accumulate([p.grad for p in sliced], first=True)
             dist.all_reduce(grad_norm.total_sq, group=self.tensor_parallel.group)
+            grad_norm.total_sq.add_(tmp)
+        sharded = self.dp_sharded_params(model)
+        if sharded:
+            tmp = grad_norm.total_sq.clone()
+            grad_norm.accumulate([p.grad for p in sharded], first=True)
+            if self.dp_world > 1:
+                dist.all_reduce(grad_norm.total_sq, group=self.dp_group)
             grad_norm.total_sq.add_(tmp)
         grad_norm.accumulate([p.grad for p in shared], first=False)

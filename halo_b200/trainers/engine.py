@@ -105,6 +105,9 @@ class TrainEngine:
         if fused is not None:
             return self._fused_clip_and_step(fused)
         params = [p for p in self.model.parameters() if p.grad is not None]
+        zero3 = getattr(self.model, "zero3", None)
+        if zero3 is not None:
+            zero3.before_step()              # collective: nobody reads this rank's slices any more
         if self.parallel is not None:
             self.parallel.sync_gradients(self.model)
             self.parallel.global_grad_sq_norm(self.model, self.grad_norm)
@@ -126,6 +129,8 @@ class TrainEngine:
         if self.lr_scheduler is not None:
             self.lr_scheduler.step()
         self.optimizer.zero_grad(set_to_none=True)
+        if zero3 is not None:
+            zero3.after_step()               # collective: every rank's slices hold the new values
 
     # ---- the step -------------------------------------------------------------------------
     def train_step(self, batch: PackedBatch, accumulate: bool = False) -> StepOutput:

@@ -163,6 +163,67 @@ def check_sharded_weight_push(dev, rank, world):
             assert torch.equal(sync.view(name, shape, dtype), full[name]), f"sharded weight push: {name} differs"
 
 
+def check_zero3_layers(dev, rank, world):
+    """Decoder-layer matrices as 1 / N slices: the pull-gather rebuilds every layer's matrices bit for bit, the per-layer
+    reduce-scatter gives every rank the fp32 sum of its slice, and two training steps follow the replicated model."""
+    import dataclasses
+
+    from halo_b200.data.packing import synthetic_packed_batch
+    from halo_b200.models.config import PRESETS
+    from halo_b200.models.qwen3 import build_model
+    from halo_b200.optim.factory import build_optimizer
+    from halo_b200.parallel.runtime import ParallelRuntime
+    from halo_b200.parallel.zero3 import shard_layers
+    from halo_b200.trainers.engine import TrainEngine
+
+    cfg = dataclasses.replace(PRESETS["tiny-moe"](), num_hidden_layers=3, num_experts=0, intermediate_size=256)
+
+    def run(sharded):
+        model = build_model(cfg, device=dev, dtype=torch.bfloat16, seed=21, gradient_checkpointing=True)
+        originals = {n: p.detach().clone() for n, p in model.named_parameters()}
+        zero3 = shard_layers(model, dist.group.WORLD, dev) if sharded else None
+        if sharded:
+            for li in range(len(model.layers)):
+                zero3.before_layer(li, backward=False)
+                for name, p, *_ in zero3.params[li]:
+                    assert torch.equal(p.detach(), originals[name]), f"gathered {name} differs"
+                zero3.after_layer(li, backward=False)
+            # a reduce-scatter of known values: every rank writes (rank + 1) everywhere, each slice sums to N (N + 1) / 2
+            zero3.before_layer(1, backward=True)
+            for _, p, *_ in zero3.params[1]:
+                p.grad.fill_(float(rank + 1))
+            zero3.after_layer(1, backward=True)
+            torch.cuda.synchronize()
+            n = zero3.layer_len[1] // world
+            got = zero3.grad_shard[zero3.shard_off[1]:zero3.shard_off[1] + n]
+            lo = rank * n
+            used = sum(((num + 7) // 8 * 8) for _, _, _, num, _ in zero3.params[1])
+            want = torch.zeros_like(got)
+            # padding between tensors and at the layer's end stays zero
+            for _, _, at, num, _ in zero3.params[1]:
+                a, b = max(at, lo), min(at + num, lo + n)
+                if a < b:
+                    want[a - lo:b - lo] = world * (world + 1) / 2
+            assert torch.equal(got, want), "reduce-scatter of a layer's gradients differs"
+            assert used <= zero3.layer_len[1]
+            zero3.after_step()
+        opt = build_optimizer(model, "adamw_bf16", lr=1e-3, weight_decay=0.01)
+        eng = TrainEngine(model, opt, dev, max_grad_norm=1.0, parallel=ParallelRuntime(dev, dp_group=dist.group.WORLD))
+        out = []
+        for step in range(3):
+            b = synthetic_packed_batch(2048, cfg.vocab_size, seed=50 * rank + step)
+            o = eng.train_step(b)
+            t = o.loss.detach().float().clone()
+            dist.all_reduce(t)
+            out.append((float(t), float(o.grad_norm)))
+        return out
+
+    want, got = run(False), run(True)
+    assert abs(want[0][0] - got[0][0]) < 2e-3 and abs(want[0][1] - got[0][1]) < 2e-2 * want[0][1], (want, got)
+    for (lw, nw), (lg, ng) in zip(want, got):
+        assert abs(lw - lg) < 3e-2, (want, got)       # bf16 weights, differently keyed rounding noise after the first update
+
+
 def check_nvls_forms(dev, rank, world):
     """The multimem forms (in-switch reduction, multicast stores) against the plain peer forms, where the symmetric
     buffers are bound to an NVLink multicast object; skipped (and said so) where they are not."""
@@ -342,6 +403,7 @@ def main():
     check_fused_optimizer(dev, rank, world)
     check_broadcast_and_allreduce(dev, rank, world)
     check_sharded_weight_push(dev, rank, world)
+    check_zero3_layers(dev, rank, world)
     nvls = check_nvls_forms(dev, rank, world)
     check_context_parallel(dev, rank, world)
     check_tensor_parallel_collectives(dev, rank, world)
