@@ -394,7 +394,7 @@ moe_slot_sum_kernel(const __nv_bfloat16* __restrict__ slots, const int* __restri
 // bank, K-major or N-major. kPush adds four push warps and gates every A tile on its arrival counter; kScatter
 // replaces the epilogue's local store by stores into the token owners' slot buffers.
 // ---------------------------------------------------------------------------------------------
-template <bool kPush>
+template <bool kPush, bool kTwoRows>
 __device__ __forceinline__ void push_units(const EpParams& ep, volatile int* abort_flag, int lane, int pw, int ptid) {
     if (!kPush) return;
     const int n_units = *ep.n_units;
@@ -404,13 +404,16 @@ __device__ __forceinline__ void push_units(const EpParams& ep, volatile int* abo
         const PushUnit pu = ep.units[u];
         __nv_bfloat16* dst_buf = reinterpret_cast<__nv_bfloat16*>(ep.row_bufs[pu.dst_rank]);
         // This warp's rows are pw, pw + 4, ...: at most 32 of a unit's 128. Lane j fetches the routing slot of the warp's
-        // j-th row up front, so that no row's copy starts with a dependent index load; rows then go two at a time (sixteen
-        // 16-byte loads in flight per lane) because one row alone leaves the copy latency-bound.
+        // j-th row up front, so that no row's copy starts with a dependent index load. kTwoRows: rows go two at a time
+        // (sixteen 16-byte loads in flight per lane). Measured on 2 GPUs at the 30B-A3B shapes: two rows at a time shorten
+        // the backward's first kernel (2.98 -> 2.73 ms: its GEMM is short, the pushes are the long pole) and lengthen the
+        // forward's (3.48 -> 3.93 ms: the pushes then crowd the operand loads of a GEMM that is the long pole), so only
+        // the backward instantiation uses them.
         const int n_mine = pu.n_rows > pw ? (pu.n_rows - pw + kPushWarps - 1) / kPushWarps : 0;
         const int my_slot = lane < n_mine ? ep.send_slot[pu.pos0 + pw + lane * kPushWarps] : 0;
         const float my_w = (ep.slot_w && lane < n_mine) ? ep.slot_w[my_slot] : 0.f;
-        for (int r = 0; r < n_mine; r += 2) {
-            const bool two = r + 1 < n_mine;
+        for (int r = 0; r < n_mine; r += (kTwoRows ? 2 : 1)) {
+            const bool two = kTwoRows && r + 1 < n_mine;
             const int slot0 = __shfl_sync(0xffffffffu, my_slot, r);
             const int slot1 = __shfl_sync(0xffffffffu, my_slot, two ? r + 1 : r);
             const int drow0 = pu.dst_row0 + pw + r * kPushWarps;
@@ -686,7 +689,7 @@ gemm_ep_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (kScatter) tma_store_wait<0>();     // every line this lane handed to the copy engine has been written
     } else if (warp < 6 + kPushWarps) {
         // ---------------- push warps: this rank's rows to their owners ----------------
-        push_units<kPush>(ep, &abort_flag, lane, warp - 6, (int)threadIdx.x - kGemmThreads);
+        push_units<kPush, B_MN != 0>(ep, &abort_flag, lane, warp - 6, (int)threadIdx.x - kGemmThreads);
     } else if (kPush && lane == 0) {
         // ---------------- gate: walk this CTA's items ahead of the producer, wait for each tile's rows ----------------
         int ready = 0;   // pad0 of the last tile found complete

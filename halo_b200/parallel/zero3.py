@@ -115,6 +115,8 @@ class Zero3Layers:
         self.shard.flat_matrices = True        # decays like the matrices it is made of, although it is 1-D
         self.shard.dp_sharded = True           # every rank holds different values: norms add over ranks, no gradient all-reduce
         self.grad_shard = torch.zeros(self.shard_total, dtype=torch.float32, device=self.device)
+        if dtype != torch.float32:
+            self.shard.grad_dtype = torch.float32      # a bf16 parameter with an fp32 gradient (the optimizer kernel takes both)
         self.shard.grad = self.grad_shard
         self._placeholder = torch.empty(0, dtype=dtype, device=self.device)
         for items in self.params:
