@@ -90,6 +90,7 @@ class EngineWeightSyncClient:
     INFO_ROUTE = ""
     PAUSE_ROUTE = ""
     PAUSE_PAYLOAD: dict = {}
+    PAUSE_PARAMS: dict = {}
     RESUME_ROUTE = ""
     SESSION_OPEN_ROUTE = ""
     SESSION_CLOSE_ROUTE = ""

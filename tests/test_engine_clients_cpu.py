@@ -105,6 +105,8 @@ def test_push_reaches_the_fake_server_bit_for_bit(backend, tmp_path):
     proc.start()
     try:
         client = make_client(backend, f"http://127.0.0.1:{port}", model_id="tiny", chunk_bytes=4096, group_host="127.0.0.1")
+        if backend == "vllm":
+            assert client._plane("cpu") == "packed"        # vLLM's own trainer helpers need a GPU: the CPU test uses the packed plane
         client.check_server(total_timeout=30.0)
         info = client.read_server_info()
         assert info.world_size == 1 and info.max_model_len == 4096
@@ -121,8 +123,8 @@ def test_push_reaches_the_fake_server_bit_for_bit(backend, tmp_path):
         calls = [c for c in got["calls"] if c not in ("/health", "/dump")]
         if backend == "vllm":
             first = calls[:calls.index("/update_weights")]
-            assert first == ["/server_info", "/init_weight_transfer_engine", "/pause", "/start_weight_update"]
-            assert calls[-3:] == ["/finish_weight_update", "/resume", "/destroy_weight_transfer_engine"]
+            assert first == ["/server_info", "/init_weight_transfer_engine", "/pause?mode=keep", "/start_weight_update"]
+            assert calls[-2:] == ["/finish_weight_update", "/resume"]
         else:
             assert calls[:3] == ["/get_server_info", "/init_weights_update_group", "/pause_generation"]
             assert calls[-2:] == ["/continue_generation", "/destroy_weights_update_group"]
