@@ -65,9 +65,26 @@ def _fake_server(port, backend, log_path, fail_on_chunk):
             state["calls"].append(path)
             if path == routes["init"]:
                 info = body.get("init_info", body)
+                if body.get("backend") == "gloo":
+                    # a stock SGLang worker: a torch process group beside its default one, one broadcast per tensor
+                    from halo_b200.weight_sync.clients.sglang import init_custom_process_group
+
+                    state["pg"] = init_custom_process_group("gloo", f"tcp://{info['master_address']}:{info['master_port']}",
+                                                            info["world_size"], info["rank_offset"], info["group_name"], 30.0)
+                    return self._answer(200, {"success": True})
                 state["group"] = EngineGroup(info["master_address"], info["master_port"], info["rank_offset"], info["world_size"],
                                              "cpu", 30.0)
                 threading.Thread(target=lambda: state["group"].barrier(30.0), daemon=True).start()
+                return self._answer(200, {"success": True})
+            if path == routes["update"] and state.get("pg") is not None:
+                import torch.distributed as dist
+
+                for name, dt, shape in zip(body["names"], body["dtypes"], body["shapes"]):
+                    t = torch.empty(shape, dtype=getattr(torch, dt))
+                    dist.broadcast(t, src=0, group=state["pg"])
+                    state["weights"][name] = t.float()
+                state["chunks"] += 1
+                state["flushed"] = state.get("flushed", 0) + int(bool(body.get("flush_cache")))
                 return self._answer(200, {"success": True})
             if path == routes["update"]:
                 info = body.get("update_info", body)
@@ -93,6 +110,37 @@ def _fake_server(port, backend, log_path, fail_on_chunk):
     HTTPServer(("127.0.0.1", port), Handler).serve_forever()
 
 
+def test_sglang_torch_plane_meets_a_worker_that_builds_its_group_the_stock_way(tmp_path):
+    """The default SGLang data plane: a process group beside the default one on each side (rendezvous + prefixed store),
+    one broadcast per tensor, the cache flushed by the update that ends the push."""
+    import requests
+
+    from halo_b200.weight_sync.clients import make_client
+
+    port = _free_port()
+    dump = str(tmp_path / "dump.json")
+    proc = mp.get_context("spawn").Process(target=_fake_server, args=(port, "sglang", dump, -1), daemon=True)
+    proc.start()
+    try:
+        client = make_client("sglang", f"http://127.0.0.1:{port}", model_id="tiny", group_host="127.0.0.1")     # data_plane="torch"
+        client.check_server(total_timeout=30.0)
+        g = torch.Generator().manual_seed(1)
+        weights = {f"model.layers.{i}.mlp.down_proj.weight": torch.randn(12, 20, generator=g).bfloat16() for i in range(3)}
+        weights["model.norm.weight"] = torch.randn(20, generator=g)
+        client.push(weights)
+        client.close()
+        requests.get(f"http://127.0.0.1:{port}/dump", timeout=10)
+        got = json.load(open(dump))
+        for name, t in weights.items():
+            assert torch.equal(torch.tensor(got["weights"][name]), t.float()), name
+        calls = [c for c in got["calls"] if c not in ("/health", "/dump")]
+        assert calls == ["/get_server_info", "/init_weights_update_group", "/pause_generation", "/update_weights_from_distributed",
+                         "/continue_generation", "/destroy_weights_update_group"]
+    finally:
+        proc.terminate()
+        proc.join(10)
+
+
 @pytest.mark.parametrize("backend", ["vllm", "sglang"])
 def test_push_reaches_the_fake_server_bit_for_bit(backend, tmp_path):
     import requests
@@ -104,7 +152,8 @@ def test_push_reaches_the_fake_server_bit_for_bit(backend, tmp_path):
     proc = mp.get_context("spawn").Process(target=_fake_server, args=(port, backend, dump, -1), daemon=True)
     proc.start()
     try:
-        client = make_client(backend, f"http://127.0.0.1:{port}", model_id="tiny", chunk_bytes=4096, group_host="127.0.0.1")
+        extra = {"data_plane": "packed"} if backend == "sglang" else {}
+        client = make_client(backend, f"http://127.0.0.1:{port}", model_id="tiny", chunk_bytes=4096, group_host="127.0.0.1", **extra)
         if backend == "vllm":
             assert client._plane("cpu") == "packed"        # vLLM's own trainer helpers need a GPU: the CPU test uses the packed plane
         client.check_server(total_timeout=30.0)
