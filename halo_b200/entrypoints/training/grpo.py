@@ -233,10 +233,26 @@ def main(argv=None):
                                       response_len=(8, min(256, grpo_args.max_completion_length)),
                                       seed=train_args.seed + pc.data_parallel_rank)
     weight_sync = None
-    if engine_client is not None:
-        from halo_b200.weight_sync.engine_push import EngineWeightPusher
+    if engine_client is not None or (grpo_args.rollout_backend in ("vllm", "sglang") and getattr(model_args, "use_peft", False)):
+        if getattr(model_args, "use_peft", False) and not getattr(model_args, "merge_adapters_on_save", False):
+            # adapters travel as files the server loads under a versioned name; rollouts ask for that name
+            import os
 
-        weight_sync = EngineWeightPusher(engine_client, device, runtime.ep_group if runtime else None)
+            from halo_b200.weight_sync.adapter_push import AdapterPusher
+
+            weight_sync = AdapterPusher(engine_client, os.path.join(train_args.output_dir, "served_adapters"))
+            source.model_id = weight_sync.current_model_id
+            pusher, plain_push = weight_sync, weight_sync.push
+
+            def push_and_rename(m):
+                plain_push(m)
+                source.model_id = pusher.current_model_id
+
+            weight_sync.push = push_and_rename
+        else:
+            from halo_b200.weight_sync.engine_push import EngineWeightPusher
+
+            weight_sync = EngineWeightPusher(engine_client, device, runtime.ep_group if runtime else None)
     if roles is not None:
         from halo_b200.weight_sync.group import full_manifest
         from halo_b200.weight_sync.roles import ModelWeightPusher, make_sync

@@ -335,3 +335,42 @@ def test_server_rollout_source_builds_rollouts_with_sampler_logprobs():
     assert [r.reward for r in rollouts] == [0.0, 1.0, 2.0, 0.0, 1.0, 2.0]
     assert np.allclose(rollouts[4].sampler_logprobs, [-0.1, -0.4])
     assert src.mean_reward == 1.0
+
+
+def test_adapter_pusher_loads_the_new_version_before_it_unloads_the_old(tmp_path):
+    import os
+
+    from halo_b200.models.config import PRESETS
+    from halo_b200.models.qwen3 import build_model
+    from halo_b200.peft.lora import LoraSpec, apply_lora
+    from halo_b200.weight_sync.adapter_push import AdapterPusher
+
+    class Client:
+        model_id = "base"
+
+        def __init__(self):
+            self.calls = []
+
+        def load_adapter(self, name, path):
+            assert os.path.isfile(os.path.join(path, "adapter_config.json")), "the adapter must be on disk before it is announced"
+            self.calls.append(("load", name))
+
+        def unload_adapter(self, name):
+            self.calls.append(("unload", name))
+
+        def close(self):
+            self.calls.append(("close", ""))
+
+    model = build_model(PRESETS["tiny-moe"](), device="cpu", dtype=torch.float32)
+    apply_lora(model, LoraSpec(r=4, alpha=8.0, target_modules=["q_proj", "v_proj"]))
+    client = Client()
+    pusher = AdapterPusher(client, str(tmp_path), name="policy", keep_versions=2)
+    assert pusher.current_model_id == "base"
+    for _ in range(3):
+        pusher.push(model)
+    assert pusher.current_model_id == "policy-v3"
+    assert client.calls == [("load", "policy-v1"), ("load", "policy-v2"), ("unload", "policy-v1"), ("load", "policy-v3"),
+                            ("unload", "policy-v2")]
+    assert sorted(os.listdir(tmp_path)) == ["policy-v2", "policy-v3"]        # older directories are removed
+    pusher.close()
+    assert client.calls[-2:] == [("unload", "policy-v3"), ("close", "")]
