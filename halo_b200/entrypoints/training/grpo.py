@@ -241,7 +241,7 @@ def main(argv=None):
             from halo_b200.weight_sync.adapter_push import AdapterPusher
 
             weight_sync = AdapterPusher(engine_client, os.path.join(train_args.output_dir, "served_adapters"))
-            source.model_id = weight_sync.current_model_id
+            source.model_id = weight_sync.current_model_id or source.model_id
             pusher, plain_push = weight_sync, weight_sync.push
 
             def push_and_rename(m):

@@ -33,7 +33,7 @@ class AdapterPusher:
     @property
     def current_model_id(self) -> str:
         """What rollouts must ask for: the newest loaded adapter, or the base model before the first push."""
-        return self._loaded[-1] if self._loaded else (self.client.model_id or "")
+        return self._loaded[-1] if self._loaded else (getattr(self.client, "model_id", "") or "")
 
     def _versioned(self, n: int) -> str:
         return f"{self.name}-v{n}"
@@ -79,7 +79,7 @@ class AdapterPusher:
         self.pushes += 1
 
     def close(self) -> None:
-        if self.rank == self.src_rank:
+        if self.rank == self.src_rank and self.client is not None:
             for name in self._loaded:
                 try:
                     self.client.unload_adapter(name)
