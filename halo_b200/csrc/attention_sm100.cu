@@ -118,6 +118,7 @@ struct AttnParams {
     int Hq, Hkv;
     float scale;          // 1/sqrt(head_dim)
     int* status;
+    int window;           // > 0: a query sees only the last `window` keys up to itself (sliding-window layers); 0: all earlier keys
 };
 
 constexpr int kFwdThreads = 192;
@@ -360,6 +361,7 @@ struct BwdParams {
     void* dK_stage;      // context parallelism: dK / dV of key tiles another rank owns ([rows, ld_stage])
     void* dV_stage;
     long long ld_stage;
+    int window;          // as in the forward
 };
 
 struct BwdKvWorkCp {     // context parallelism: the local queries that see a key tile, as up to two runs (one per local piece)
@@ -835,7 +837,7 @@ constexpr int kBwdKv2Stages = 5;
 constexpr int kBwdKv2Tiles = 2 * kTileBytes + kBwdKv2Stages * 2 * kHalfTile;     // 229,376
 constexpr int kBwdKv2Smem = kBwdKv2Tiles + 2048;                                                 // barriers, scalars, statistics
 
-template <bool kCP>
+template <bool kCP, bool kWin = false>
 __global__ void __launch_bounds__(kBwd2Threads, 1)
 attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -1026,14 +1028,16 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tmem_ld_wait();
             // Only the tiles on the diagonal need the causal mask; everywhere else the loop carries no compare at all.
             // Column i of this thread is query qr + c0 + i; it sees key `key_abs` when i >= lim.
-            const bool need_mask = (qr < w.kv0 + 128);
+            // With a window it sees it only while i < lim + window (the query is at most window - 1 rows after the key).
+            const bool need_mask = (qr < w.kv0 + 128) || (kWin && qr + 63 - w.kv0 >= p.window);
             const int lim = (int)(key_abs - qr) - c0;
+            const int hi = kWin ? lim + p.window : 0;
             float pv[32];
             if (need_mask) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     const float pe = fast_exp2(__uint_as_float(sr[i]) * c - lse_g[c0 + i]);
-                    pv[i] = i < lim ? 0.f : pe;
+                    pv[i] = (i < lim || (kWin && i >= hi)) ? 0.f : pe;
                 }
             } else {
 #pragma unroll
@@ -1121,7 +1125,7 @@ constexpr int kBwdQ2Stages = 5;
 constexpr int kBwdQ2Tiles = 2 * kTileBytes + kBwdQ2Stages * 2 * kHalfTile;   // 229,376
 constexpr int kBwdQ2Smem = kBwdQ2Tiles + 512;
 
-template <bool kCP>
+template <bool kCP, bool kWin = false>
 __global__ void __launch_bounds__(kBwd2Threads, 1)
 attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -1260,14 +1264,15 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             tmem_ld_wait();
             // column i of this thread is key k0 + i; the row sees it when i <= lim. Off the diagonal no compare is made.
             const int k0 = w.kv0 + j * 64 + c0;
-            const bool need_mask = (k0 + 32 > w.q0);
+            const bool need_mask = (k0 + 32 > w.q0) || (kWin && k0 + p.window <= w.q0 + 127);
             const int lim = (int)(q_abs - k0);
+            const int lo = kWin ? lim - p.window + 1 : 0;                         // first visible column under a window
             float pv[32];
             if (need_mask) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     const float pe = fast_exp2(__uint_as_float(sr[i]) * c - lse2);
-                    pv[i] = i > lim ? 0.f : pe * (__uint_as_float(dr[i]) - dl) * p.scale;
+                    pv[i] = (i > lim || (kWin && i < lo)) ? 0.f : pe * (__uint_as_float(dr[i]) - dl) * p.scale;
                 }
             } else {
 #pragma unroll
@@ -1573,7 +1578,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 // takes its A operand from tensor memory. Shared memory then carries only Q, K and V: a third less traffic per step on
 // the resource that limits this kernel (operand fetches of the products and the K/V loads share one 128-byte-per-clock
 // port), and the proxy fence between the softmax's stores and the product disappears.
-template <bool kCP>
+template <bool kCP, bool kWin = false>
 __global__ void __maxnreg__(128)
 attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const AttnParams p, const __grid_constant__ CpArgs<kCP> ca) {
@@ -1699,9 +1704,11 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             tc_fence_after();
             const uint32_t tSj = tS + (j & 1) * 64;
             const int k0 = w.kv0 + j * 64;
-            const bool need_mask = (k0 + 63 > w.q0);
-            // key column i of a half-tile is visible to this row when i <= lim - 32 * half; only diagonal tiles compare
+            // key column i of a half-tile is visible to this row when lo - 32 * half <= i <= lim - 32 * half; only tiles on
+            // the diagonal, or cut by the left edge of some row's window, compare at all
+            const bool need_mask = (k0 + 63 > w.q0) || (kWin && k0 + p.window <= w.q0 + 127);
             const int lim = (int)(q_abs - k0);
+            const int lo = kWin ? lim - p.window + 1 : 0;
             float mx = m_ref;
 #pragma unroll 1
             for (int half = 0; half < 2; ++half) {
@@ -1709,9 +1716,9 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 tmem_ld_32x32(tSj + lane_base + half * 32, r);
                 tmem_ld_wait();
                 if (need_mask) {
-                    const int lh = lim - half * 32;
+                    const int lh = lim - half * 32, ll = lo - half * 32;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, i <= lh ? __uint_as_float(r[i]) : -INFINITY);
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, (i <= lh && (!kWin || i >= ll)) ? __uint_as_float(r[i]) : -INFINITY);
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
@@ -1749,12 +1756,13 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 // the row sum is taken from the fp32 probabilities (their bf16 roundings, which the P V product reads,
                 // differ from them by unbiased noise of relative size 2^-9 that averages out over a row)
                 if (need_mask) {
-                    const int lh = lim - half * 32;
+                    const int lh = lim - half * 32, ll = lo - half * 32;
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
                         const float e0 = fast_exp2(__uint_as_float(r[i]) * c - mc);
                         const float e1 = fast_exp2(__uint_as_float(r[i + 1]) * c - mc);
-                        const float p0 = i <= lh ? e0 : 0.f, p1 = i + 1 <= lh ? e1 : 0.f;
+                        const float p0 = (i <= lh && (!kWin || i >= ll)) ? e0 : 0.f;
+                        const float p1 = (i + 1 <= lh && (!kWin || i + 1 >= ll)) ? e1 : 0.f;
                         pk[i >> 1] = pack_bf16(p0, p1);
                         rs += p0 + p1;
                     }
@@ -1920,6 +1928,65 @@ int halo_attn_fwd3(const void* q, const void* k, const void* v, void* o, float* 
     }
     AttnParams p{reinterpret_cast<const FwdWork*>(work), o, lse, ldo, T, Hq, Hkv, scale, status};
     attn_fwd3_kernel<false><<<dim3(Hq, n_tiles), kFwdThreads, kFwd2Smem, (cudaStream_t)stream>>>(tq, tk, tv, p, g_no_cp_args);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Sliding-window forward (third form only): a query sees the last `window` keys up to itself. The work list's kv0 is the
+// first key tile a query tile needs (aligned to 64 rows from its document's start), not the document's start.
+int halo_attn_fwd3_window(const void* q, const void* k, const void* v, void* o, float* lse, const void* work,
+                          int n_tiles, long long T, int Hq, int Hkv, int head_dim, long long ldq, long long ldk,
+                          long long ldv, long long ldo, float scale, int window, int* status, void* stream) {
+    if (head_dim != kHd || Hq % Hkv || window <= 0) return -1;
+    if (n_tiles == 0) return 0;
+    CUtensorMap tq, tk, tv;
+    if (make_tmap_bf16(&tq, q, T, (long long)Hq * kHd, ldq, 128)) return -2;
+    if (make_tmap_bf16(&tk, k, T, (long long)Hkv * kHd, ldk, 64)) return -3;
+    if (make_tmap_bf16(&tv, v, T, (long long)Hkv * kHd, ldv, 64)) return -4;
+    static bool cfg = false;
+    if (!cfg) {
+        if (set_smem((const void*)attn_fwd3_kernel<false, true>, kFwd2Smem)) return -10;
+        cudaFuncSetAttribute((const void*)attn_fwd3_kernel<false, true>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+        cfg = true;
+    }
+    AttnParams p{reinterpret_cast<const FwdWork*>(work), o, lse, ldo, T, Hq, Hkv, scale, status, window};
+    attn_fwd3_kernel<false, true><<<dim3(Hq, n_tiles), kFwdThreads, kFwd2Smem, (cudaStream_t)stream>>>(tq, tk, tv, p, g_no_cp_args);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Sliding-window backward (double-buffered kernels only). Work lists as halo_attn_bwd's, cut to the window: a key tile's
+// query range ends window - 1 rows after its last key, a query tile's key range starts at its first row's window.
+int halo_attn_bwd_window(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
+                         float* delta, void* dq, void* dk, void* dv, const void* kv_work, int n_kv_tiles,
+                         const void* q_work, int n_q_tiles, long long T, int Hq, int Hkv, int head_dim, long long ldq,
+                         long long ldk, long long ldv, long long ldo, long long ld_do, long long ld_dq, long long ld_dk,
+                         long long ld_dv, float scale, int window, int* status, void* stream) {
+    if (head_dim != kHd || Hq % Hkv || window <= 0) return -1;
+    if (T == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    attn_delta_kernel<<<(unsigned)((T * Hq + 7) / 8), 256, 0, s>>>(
+        (const __nv_bfloat16*)d_o, (const __nv_bfloat16*)o, delta, T, Hq, ld_do, ldo);
+    CUtensorMap tq, tk, tv, tdo, tq64, tk64, tv64, tdo64;
+    if (make_tmap_bf16(&tq, q, T, (long long)Hq * kHd, ldq, 128)) return -2;
+    if (make_tmap_bf16(&tk, k, T, (long long)Hkv * kHd, ldk, 128)) return -3;
+    if (make_tmap_bf16(&tv, v, T, (long long)Hkv * kHd, ldv, 128)) return -4;
+    if (make_tmap_bf16(&tdo, d_o, T, (long long)Hq * kHd, ld_do, 128)) return -5;
+    if (make_tmap_bf16(&tq64, q, T, (long long)Hq * kHd, ldq, 64)) return -6;
+    if (make_tmap_bf16(&tk64, k, T, (long long)Hkv * kHd, ldk, 64)) return -7;
+    if (make_tmap_bf16(&tv64, v, T, (long long)Hkv * kHd, ldv, 64)) return -8;
+    if (make_tmap_bf16(&tdo64, d_o, T, (long long)Hq * kHd, ld_do, 64)) return -9;
+    static bool cfg = false;
+    if (!cfg) {
+        if (set_smem((const void*)attn_bwd_dkdv2_kernel<false, true>, kBwdKv2Smem)) return -10;
+        if (set_smem((const void*)attn_bwd_dq2_kernel<false, true>, kBwdQ2Smem)) return -10;
+        cfg = true;
+    }
+    BwdParams p{kv_work, lse, delta, dq, dk, dv, ld_dq, ld_dk, ld_dv, T, Hq, Hkv, scale, status, nullptr, nullptr, 0, window};
+    if (n_kv_tiles > 0)
+        attn_bwd_dkdv2_kernel<false, true><<<dim3(Hkv, n_kv_tiles), kBwd2Threads, kBwdKv2Smem, s>>>(tq64, tk, tv, tdo64, p, g_no_cp_args);
+    p.work = q_work;
+    if (n_q_tiles > 0)
+        attn_bwd_dq2_kernel<false, true><<<dim3(Hq, n_q_tiles), kBwd2Threads, kBwdQ2Smem, s>>>(tq, tk64, tv64, tdo, p, g_no_cp_args);
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

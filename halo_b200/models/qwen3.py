@@ -214,6 +214,12 @@ class Attention(nn.Module):
                                         cfg.rms_norm_eps, cfg.use_qk_norm)
             return row_parallel_linear(o, self.o_proj, ctx.tp)
         qkv = self._qkv(h)
+        if (self.window and self.sinks is None and self.scale is None and not self.softcap and qkv.is_cuda
+                and cfg.head_dim == attn_ops.HEAD_DIM and ctx.cp is None and getattr(ctx, "attention_mask", None) is None):
+            # a sliding-window layer on the flash kernels: work lists cut to the window, the left edge masked in the kernels
+            o = attn_ops.rope_attention(qkv, self.q_norm, self.k_norm, self.rope_of(ctx), ctx.window_plan(self.window),
+                                        cfg.num_attention_heads, cfg.num_key_value_heads, cfg.rms_norm_eps, cfg.use_qk_norm)
+            return self._out(o)
         if (self.window or self.sinks is not None or self.scale is not None or self.softcap
                 or getattr(ctx, "attention_mask", None) is not None):
             return self._out(self._masked(qkv, ctx))
@@ -517,6 +523,14 @@ class ForwardContext:
         self.kv_cache = None         # halo_b200.inference.generate.KVCache while sampling
         self.attention_mask = None   # bool [T, T]: an explicit mask (tree packing) served by the masked-attention op
         self.rope_local = None       # rotary table of the windowed layers when their base differs (Gemma 3)
+        self._window_plans = {}      # window size -> attention plan cut to that window (built on first use)
+
+    def window_plan(self, window: int):
+        plan = self._window_plans.get(window)
+        if plan is None:
+            dev = self.plan.fwd.device if self.plan.fwd is not None else None
+            plan = self._window_plans[window] = attn_ops.build_plan(self.plan.cu_seqlens, dev, window=window)
+        return plan
 
 
 class Qwen3Model(nn.Module):

@@ -27,6 +27,15 @@ FWD_VARIANT = int(os.environ.get("HALO_ATTN_FWD_VARIANT", "3"))
 
 
 def _launch_fwd(L, q, k, v, o, lse, plan, T, n_heads, n_kv_heads, scale, dev):
+    if plan.window:
+        work = plan.bwd_q
+        rc = L.halo_attn_fwd3_window(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse), _lib.ptr(work),
+            _lib.c_int(work.shape[0]), _lib.c_ll(T), _lib.c_int(n_heads), _lib.c_int(n_kv_heads),
+            _lib.c_int(HEAD_DIM), _lib.c_ll(_ld(q)), _lib.c_ll(_ld(k)), _lib.c_ll(_ld(v)), _lib.c_ll(_ld(o)),
+            _lib.c_float(scale), _lib.c_int(plan.window), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev))
+        _lib.check(rc, "halo_attn_fwd3_window")
+        return
     if FWD_VARIANT == 3:
         work, fn, what = plan.bwd_q, L.halo_attn_fwd3, "halo_attn_fwd3"
     elif FWD_VARIANT == 2:
@@ -42,6 +51,23 @@ def _launch_fwd(L, q, k, v, o, lse, plan, T, n_heads, n_kv_heads, scale, dev):
     _lib.check(rc, what)
 
 
+def _launch_bwd(L, q, k, v, o, do, lse, delta, dq, dk, dv, plan, T, n_heads, n_kv_heads, scale, dev):
+    args = [
+        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(do), _lib.ptr(lse), _lib.ptr(delta),
+        _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv),
+        _lib.ptr(plan.bwd_kv), _lib.c_int(plan.bwd_kv.shape[0]),
+        _lib.ptr(plan.bwd_q), _lib.c_int(plan.bwd_q.shape[0]),
+        _lib.c_ll(T), _lib.c_int(n_heads), _lib.c_int(n_kv_heads), _lib.c_int(HEAD_DIM),
+        _lib.c_ll(_ld(q)), _lib.c_ll(_ld(k)), _lib.c_ll(_ld(v)), _lib.c_ll(_ld(o)), _lib.c_ll(_ld(do)),
+        _lib.c_ll(_ld(dq)), _lib.c_ll(_ld(dk)), _lib.c_ll(_ld(dv)), _lib.c_float(scale)]
+    if plan.window:
+        rc = L.halo_attn_bwd_window(*args, _lib.c_int(plan.window), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev))
+        _lib.check(rc, "halo_attn_bwd_window")
+        return
+    rc = L.halo_attn_bwd(*args, _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev))
+    _lib.check(rc, "halo_attn_bwd")
+
+
 @dataclass
 class AttentionPlan:
     """Tile work lists for one packed batch (device int32 tensors of shape [n, 4])."""
@@ -52,14 +78,19 @@ class AttentionPlan:
     bwd_kv: torch.Tensor | None = None
     bwd_q: torch.Tensor | None = None
     max_seqlen: int = 0
+    window: int = 0         # > 0: sliding-window attention (a query sees the last ``window`` keys up to itself)
 
     @property
     def n_docs(self) -> int:
         return len(self.cu_seqlens) - 1
 
 
-def build_plan(cu_seqlens, device: torch.device | str | None = None, q_lo: int = 0) -> AttentionPlan:
+def build_plan(cu_seqlens, device: torch.device | str | None = None, q_lo: int = 0, window: int = 0) -> AttentionPlan:
     """``cu_seqlens``: increasing offsets ``[0, len0, len0+len1, ...]`` of the packed documents.
+
+    ``window > 0``: sliding-window attention. The lists are cut to the window - a query tile starts at the first key tile its
+    first row can see, a key tile's queries end ``window - 1`` rows after its last key - so the work (and the time) of a long
+    document grows with ``window``, not with the document's length.
 
     ``q_lo``: rows below it are keys only (the foreign prefix of a context-parallel chunk): no query tile is
     listed for them, and the dK/dV lists start their query range at ``q_lo``. The caller keeps the query and
@@ -68,12 +99,12 @@ def build_plan(cu_seqlens, device: torch.device | str | None = None, q_lo: int =
     if cu.ndim != 1 or len(cu) < 1 or cu[0] != 0 or np.any(np.diff(cu) < 0):
         raise ValueError("cu_seqlens must start at 0 and be non-decreasing")
     total = int(cu[-1])
-    plan = AttentionPlan(cu_seqlens=cu, total=total)
+    if window and q_lo:
+        raise ValueError("a sliding window together with a key-only prefix is not supported")
+    plan = AttentionPlan(cu_seqlens=cu, total=total, window=int(window))
     lens = np.diff(cu)
     plan.max_seqlen = int(lens.max()) if len(lens) else 0
     device = torch.device(device) if device is not None else None
-    if device is None or device.type != "cuda":
-        return plan
     fwd, bkv, bq = [], [], []
     for start, end in zip(cu[:-1], cu[1:]):
         n = int(end - start)
@@ -84,6 +115,15 @@ def build_plan(cu_seqlens, device: torch.device | str | None = None, q_lo: int =
         for i in range((n + 127) // 128):
             q0 = int(start) + 128 * i
             last = min(q0 + 128, int(end))
+            if window:
+                # the first key tile the tile's first row sees, aligned to 64 rows from the document's start
+                k_first = int(start) + max(0, q0 - window + 1 - int(start)) // 64 * 64
+                bq.append((q0, k_first, (last - k_first + 63) // 64, int(end)))
+                fwd.append((q0, k_first, (last - k_first + 127) // 128, int(end)))
+                # queries that see the key tile end window - 1 rows after its last key
+                q_stop = min(int(end), q0 + 127 + window)
+                bkv.append((q0, q0, (q_stop - q0 + 63) // 64, int(end)))
+                continue
             if last > q_lo:
                 fwd.append((q0, int(start), i + 1, int(end)))
                 # dQ: 64-key sub-tiles up to the tile's last visible key
@@ -91,6 +131,10 @@ def build_plan(cu_seqlens, device: torch.device | str | None = None, q_lo: int =
             # dK/dV: 64-query sub-tiles from the key tile's first row (or the first local query) to the document end
             qb = max(q0, (q_lo - int(start)) // 64 * 64 + int(start)) if q_lo > q0 else q0
             bkv.append((q0, qb, (int(end) - qb + 63) // 64, int(end)))
+
+    plan.host_lists = {"fwd": fwd, "bwd_kv": bkv, "bwd_q": bq}          # the lists as built, for inspection and tests
+    if device is None or device.type != "cuda":
+        return plan
 
     def to_dev(rows, key):
         if not rows:
@@ -105,8 +149,9 @@ def build_plan(cu_seqlens, device: torch.device | str | None = None, q_lo: int =
     return plan
 
 
-def attention_reference(q, k, v, cu_seqlens, n_heads, n_kv_heads, scale=None):
-    """fp32 oracle. q: [T, Hq*D]; k, v: [T, Hkv*D]; returns [T, Hq*D] in q's dtype."""
+def attention_reference(q, k, v, cu_seqlens, n_heads, n_kv_heads, scale=None, window: int = 0):
+    """fp32 oracle. q: [T, Hq*D]; k, v: [T, Hkv*D]; returns [T, Hq*D] in q's dtype. ``window > 0``: a query sees the last
+    ``window`` keys up to itself."""
     T = q.shape[0]
     D = q.shape[1] // n_heads
     scale = scale if scale is not None else D**-0.5
@@ -125,6 +170,8 @@ def attention_reference(q, k, v, cu_seqlens, n_heads, n_kv_heads, scale=None):
         sc = (qq @ kk.transpose(1, 2)) * scale
         n = e - s
         mask = torch.ones(n, n, dtype=torch.bool, device=q.device).tril()
+        if window:
+            mask &= ~torch.ones(n, n, dtype=torch.bool, device=q.device).tril(-int(window))
         sc = sc.masked_fill(~mask, float("-inf"))
         out[s:e] = (torch.softmax(sc, dim=-1) @ vv).transpose(0, 1)
     return out.reshape(T, n_heads * D).to(q.dtype)
@@ -159,17 +206,7 @@ class _FlashAttention(torch.autograd.Function):
         dv = dkv[:, ctx.n_kv_heads * HEAD_DIM :]
         delta = torch.empty((ctx.n_heads, T), dtype=torch.float32, device=q.device)
         L = _lib.lib()
-        rc = L.halo_attn_bwd(
-            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(do), _lib.ptr(lse), _lib.ptr(delta),
-            _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv),
-            _lib.ptr(plan.bwd_kv), _lib.c_int(plan.bwd_kv.shape[0]),
-            _lib.ptr(plan.bwd_q), _lib.c_int(plan.bwd_q.shape[0]),
-            _lib.c_ll(T), _lib.c_int(ctx.n_heads), _lib.c_int(ctx.n_kv_heads), _lib.c_int(HEAD_DIM),
-            _lib.c_ll(_ld(q)), _lib.c_ll(_ld(k)), _lib.c_ll(_ld(v)), _lib.c_ll(_ld(o)), _lib.c_ll(_ld(do)),
-            _lib.c_ll(_ld(dq)), _lib.c_ll(_ld(dk)), _lib.c_ll(_ld(dv)),
-            _lib.c_float(ctx.scale), _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr(q.device),
-        )
-        _lib.check(rc, "halo_attn_bwd")
+        _launch_bwd(L, q, k, v, o, do, lse, delta, dq, dk, dv, plan, T, ctx.n_heads, ctx.n_kv_heads, ctx.scale, q.device)
         return dq, dk, dv, None, None, None, None
 
 
@@ -178,7 +215,7 @@ def flash_attention(q, k, v, plan: AttentionPlan, n_heads: int, n_kv_heads: int,
     D = q.shape[1] // n_heads
     scale = float(scale if scale is not None else D**-0.5)
     if not q.is_cuda:
-        return attention_reference(q, k, v, plan.cu_seqlens, n_heads, n_kv_heads, scale)
+        return attention_reference(q, k, v, plan.cu_seqlens, n_heads, n_kv_heads, scale, window=plan.window)
     if D != HEAD_DIM:
         raise NotImplementedError("the sm_100a flash kernel is built for head_dim 128")
     if plan.fwd is None:
@@ -229,17 +266,7 @@ class _RopeAttention(torch.autograd.Function):
         dq = torch.empty_like(q)
         dk = torch.empty_like(k)
         delta = torch.empty((n_heads, T), dtype=torch.float32, device=dev)
-        rc = L.halo_attn_bwd(
-            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(do), _lib.ptr(lse), _lib.ptr(delta),
-            _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv),
-            _lib.ptr(plan.bwd_kv), _lib.c_int(plan.bwd_kv.shape[0]),
-            _lib.ptr(plan.bwd_q), _lib.c_int(plan.bwd_q.shape[0]),
-            _lib.c_ll(T), _lib.c_int(n_heads), _lib.c_int(n_kv_heads), _lib.c_int(HEAD_DIM),
-            _lib.c_ll(_ld(q)), _lib.c_ll(_ld(k)), _lib.c_ll(_ld(v)), _lib.c_ll(_ld(o)), _lib.c_ll(_ld(do)),
-            _lib.c_ll(_ld(dq)), _lib.c_ll(_ld(dk)), _lib.c_ll(_ld(dv)),
-            _lib.c_float(scale), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev),
-        )
-        _lib.check(rc, "halo_attn_bwd")
+        _launch_bwd(L, q, k, v, o, do, lse, delta, dq, dk, dv, plan, T, n_heads, n_kv_heads, scale, dev)
         blocks = L.halo_qknorm_rope_bwd_blocks(_lib.c_ll(T), _lib.c_int(n_heads + n_kv_heads))
         partial = torch.empty((max(blocks, 1), 256), dtype=torch.float32, device=dev)
         dw = torch.zeros(256, dtype=torch.float32, device=dev)
@@ -270,4 +297,4 @@ def rope_attention(qkv, wq, wk, table, plan, n_heads, n_kv_heads, eps=1e-6, use_
         # partial rotary / whole-width q-k norm: these run as tensor ops (the fused kernel norms and turns whole heads
         # one by one), attention itself on the kernel
         return flash_attention(q, k, v, plan, n_heads, n_kv_heads, scale)
-    return attention_reference(q, k, v, plan.cu_seqlens, n_heads, n_kv_heads, scale)
+    return attention_reference(q, k, v, plan.cu_seqlens, n_heads, n_kv_heads, scale, window=plan.window)

@@ -118,6 +118,42 @@ def _long_case(lens, scale_logits):
             assert rel < 5e-2, (name, rel)
 
 
+@pytest.mark.parametrize("lens,window", [
+    ([700, 300, 1048], 256),      # several documents, windows shorter than most of them
+    ([2048], 128),                # every key tile is cut by the diagonal or by a window edge
+    ([5000, 120], 1024),
+    ([333], 4096),                # a window longer than the document: plain causal attention
+    ([1500, 777], 100),           # a window that is no multiple of the tile sizes
+])
+def test_flash_attention_sliding_window(lens, window):
+    from halo_b200.ops import _lib
+    from halo_b200.ops.attention import attention_reference, build_plan, flash_attention
+
+    Hq, Hkv = 4, 2
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    q, k, v = _mk(cu[-1], Hq, Hkv, seed=7)
+    plan = build_plan(cu, device="cuda", window=window)
+    qg, kg, vg = (t.clone().requires_grad_() for t in (q, k, v))
+    o = flash_attention(qg, kg, vg, plan, Hq, Hkv)
+    do = torch.randn_like(o)
+    o.backward(do)
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+    qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
+    o_ref = attention_reference(qr, kr, vr, cu, Hq, Hkv, window=window)
+    o_ref.backward(do.float())
+    assert _row_rel_err(o, o_ref) < 2e-2
+    assert _row_rel_err(vg.grad, vr.grad) < 3e-2
+    assert _row_rel_err(qg.grad, qr.grad) < 4e-2
+    assert _row_rel_err(kg.grad, kr.grad) < 4e-2
+    # the window changes the result (unless it covers the whole document)
+    if window < max(lens):
+        full = flash_attention(q, k, v, build_plan(cu, device="cuda"), Hq, Hkv)
+        assert (full.float() - o.float()).abs().max().item() > 1e-2
+
+
 def test_rope_attention_fused_matches_reference():
     from halo_b200.ops.attention import build_plan, rope_attention
     from halo_b200.ops.rope import rope_table
