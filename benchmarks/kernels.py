@@ -134,6 +134,25 @@ def cases(small: bool):
 
         out[f"attn_fwd_bwd_{dist_name}"] = (attn_fb, 3.5 * flops, 0.0)
 
+    # sliding window of 4096 tokens over one document as long as the batch: the work lists drop key tiles left of the
+    # window, so the count of useful flops is the band's, not the triangle's
+    win = 4096 if not small else 1024
+    cu_w = np.array([0, T], dtype=np.int64)
+    plan_w = attn_ops.build_plan(cu_w, "cuda", window=win)
+    band = sum(min(i + 1, win) for i in range(T))
+    flops_w = 4.0 * NQ * HD * band
+    qw, kw, vw = (bf16(T, n * HD).requires_grad_(True) for n in (NQ, NKV, NKV))
+    do_w = bf16(T, NQ * HD)
+    out["attn_fwd_window"] = (lambda: attn_ops.flash_attention(qw.detach(), kw.detach(), vw.detach(), plan_w, NQ, NKV),
+                              flops_w, 2.0 * T * HD * (2 * NQ + 2 * NKV))
+
+    def attn_w_fb():
+        o = attn_ops.flash_attention(qw, kw, vw, plan_w, NQ, NKV)
+        o.backward(do_w)
+        qw.grad = kw.grad = vw.grad = None
+
+    out["attn_fwd_bwd_window"] = (attn_w_fb, 3.5 * flops_w, 0.0)
+
     # ---- bandwidth-bound pieces ---------------------------------------------------------------
     wn = torch.ones(H, device="cuda", dtype=torch.bfloat16)
     res = bf16(T, H)

@@ -61,3 +61,21 @@ def test_reference_applies_the_window():
     narrow = attention_reference(q, k, v, [0, 40], 2, 1, window=4)
     assert torch.allclose(full, wide) and not torch.allclose(full, narrow)
     assert torch.allclose(full[:4], narrow[:4])          # the first `window` rows see everything before them anyway
+
+
+def test_windowed_models_are_sent_to_the_flash_kernels_only_where_they_run():
+    import dataclasses
+
+    import torch
+
+    from halo_b200.models.attention_selection import attention_path
+    from halo_b200.models.config import PRESETS
+
+    cfg = dataclasses.replace(PRESETS["tiny-moe"](), sliding_window=64, head_dim=128)
+    assert attention_path(cfg, "cuda", torch.bfloat16)[0] == "flash"
+    assert "sliding_window=64" in attention_path(cfg, "cuda", torch.bfloat16)[1]
+    assert attention_path(cfg, "cpu", torch.float32)[0] == "masked"
+    assert attention_path(cfg, "cuda", torch.float32)[0] == "masked"
+    assert attention_path(dataclasses.replace(cfg, head_dim=64), "cuda", torch.bfloat16)[0] == "masked"
+    assert attention_path(dataclasses.replace(cfg, attention_sinks=True), "cuda", torch.bfloat16)[0] == "masked"
+    assert attention_path(cfg, "cuda", torch.bfloat16, tree_packing=True)[0] == "masked"
