@@ -119,7 +119,15 @@ struct AttnParams {
     float scale;          // 1/sqrt(head_dim)
     int* status;
     int window;           // > 0: a query sees only the last `window` keys up to itself (sliding-window layers); 0: all earlier keys
+    const float* sinks;   // [Hq] or null: one extra logit per head that joins every row's softmax and carries no value
 };
+
+// Softmax denominator with the head's sink logit: l is the sum of exp(score - m_nat) over the keys, m_nat the row's
+// reference maximum in natural-log units. The exponent is capped so that a sink far above every score gives a large
+// finite denominator (an output of zeros) rather than infinity.
+__device__ __forceinline__ float add_sink(float l, float m_nat, const float* sinks, int head) {
+    return sinks ? l + __expf(fminf(sinks[head] - m_nat, 80.f)) : l;
+}
 
 constexpr int kFwdThreads = 192;
 constexpr int kTileBytes = 128 * 128 * 2;                              // 32 KiB: a 128x128 bf16 tile
@@ -287,6 +295,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         const long long grow = (long long)w.q0 + row;
         if (ok && grow < w.q_end) {
+            l = add_sink(l, m * p.scale, p.sinks, head);
             const float inv = 1.f / l;
             __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.O) + grow * p.ldo + head * kHd;
 #pragma unroll
@@ -1538,6 +1547,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (ok && mbar_wait(bar_o_full, (w.n_kv - 1) & 1, abort_flag, p.status)) {
             tc_fence_after();
             const bool live = q_abs < w.q_end;
+            l = add_sink(l, m_ref * p.scale, p.sinks, head);
             const float inv = 1.f / l;
             __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.O) + q_abs * p.ldo + head * kHd;
 #pragma unroll 1
@@ -1728,7 +1738,9 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             if (j > 0 && !mbar_wait(bar_o_full, (j - 1) & 1, abort_flag, p.status)) { ok = false; break; }
             const bool grow = (mx - m_ref) * c > 8.f;   // also true on the first tile (m_ref = -inf)
             if (__any_sync(0xffffffffu, grow)) {
-                const float alpha = fast_exp2((m_ref - mx) * c);
+                // a row whose keys so far all lie left of its window has seen nothing yet (both maxima are -inf):
+                // it keeps its empty state instead of scaling by exp2(-inf + inf)
+                const float alpha = (kWin && mx == -INFINITY) ? 1.f : fast_exp2((m_ref - mx) * c);
                 if (j > 0) {
                     tc_fence_after();
 #pragma unroll 1
@@ -1786,6 +1798,7 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (ok && mbar_wait(bar_o_full, (w.n_kv - 1) & 1, abort_flag, p.status)) {
             tc_fence_after();
             const bool live = q_abs < w.q_end;
+            l = add_sink(l, m_ref * p.scale, p.sinks, head);
             const float inv = 1.f / l;
             const long long q_local = q_abs - q_shift;
             __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.O) + q_local * p.ldo + head * kHd;
@@ -1862,6 +1875,20 @@ static int fill_cp_map(CpMap* cp, const int* m, int n_bufs) {
 }  // namespace halo
 
 using namespace halo;
+
+template <bool kWin>
+static int launch_fwd3_sinks(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
+                             int n_tiles, cudaStream_t stream) {
+    static bool cfg = false;
+    if (!cfg) {
+        if (set_smem((const void*)attn_fwd3_kernel<false, kWin>, kFwd2Smem)) return -10;
+        cudaFuncSetAttribute((const void*)attn_fwd3_kernel<false, kWin>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+        cfg = true;
+    }
+    attn_fwd3_kernel<false, kWin><<<dim3(p.Hq, n_tiles), kFwdThreads, kFwd2Smem, stream>>>(tq, tk, tv, p, g_no_cp_args);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
 
 extern "C" {
 
@@ -1952,6 +1979,24 @@ int halo_attn_fwd3_window(const void* q, const void* k, const void* v, void* o, 
     AttnParams p{reinterpret_cast<const FwdWork*>(work), o, lse, ldo, T, Hq, Hkv, scale, status, window};
     attn_fwd3_kernel<false, true><<<dim3(Hq, n_tiles), kFwdThreads, kFwd2Smem, (cudaStream_t)stream>>>(tq, tk, tv, p, g_no_cp_args);
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Forward with attention sinks (third form), with or without a sliding window: `sinks` holds one fp32 logit per query
+// head. The logit enters the denominator in the kernel's last step, so the stored log-sum-exp and the normalised output are
+// those of the softmax over keys plus sink; the backward kernels then need no change (the sink's value vector is zero).
+int halo_attn_fwd3_sinks(const void* q, const void* k, const void* v, void* o, float* lse, const void* work,
+                         int n_tiles, long long T, int Hq, int Hkv, int head_dim, long long ldq, long long ldk,
+                         long long ldv, long long ldo, float scale, int window, const float* sinks, int* status,
+                         void* stream) {
+    if (head_dim != kHd || Hq % Hkv || window < 0 || !sinks) return -1;
+    if (n_tiles == 0) return 0;
+    CUtensorMap tq, tk, tv;
+    if (make_tmap_bf16(&tq, q, T, (long long)Hq * kHd, ldq, 128)) return -2;
+    if (make_tmap_bf16(&tk, k, T, (long long)Hkv * kHd, ldk, 64)) return -3;
+    if (make_tmap_bf16(&tv, v, T, (long long)Hkv * kHd, ldv, 64)) return -4;
+    AttnParams p{reinterpret_cast<const FwdWork*>(work), o, lse, ldo, T, Hq, Hkv, scale, status, window, sinks};
+    return window > 0 ? launch_fwd3_sinks<true>(tq, tk, tv, p, n_tiles, (cudaStream_t)stream)
+                      : launch_fwd3_sinks<false>(tq, tk, tv, p, n_tiles, (cudaStream_t)stream);
 }
 
 // Sliding-window backward (double-buffered kernels only). Work lists as halo_attn_bwd's, cut to the window: a key tile's

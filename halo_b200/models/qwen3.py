@@ -214,11 +214,16 @@ class Attention(nn.Module):
                                         cfg.rms_norm_eps, cfg.use_qk_norm)
             return row_parallel_linear(o, self.o_proj, ctx.tp)
         qkv = self._qkv(h)
-        if (self.window and self.sinks is None and self.scale is None and not self.softcap and qkv.is_cuda
-                and cfg.head_dim == attn_ops.HEAD_DIM and ctx.cp is None and getattr(ctx, "attention_mask", None) is None):
-            # a sliding-window layer on the flash kernels: work lists cut to the window, the left edge masked in the kernels
-            o = attn_ops.rope_attention(qkv, self.q_norm, self.k_norm, self.rope_of(ctx), ctx.window_plan(self.window),
-                                        cfg.num_attention_heads, cfg.num_key_value_heads, cfg.rms_norm_eps, cfg.use_qk_norm)
+        if ((self.window or self.sinks is not None or self.scale is not None) and not self.softcap and qkv.is_cuda
+                and qkv.dtype == torch.bfloat16 and ctx.cp is None and getattr(ctx, "attention_mask", None) is None
+                and (cfg.head_dim == attn_ops.HEAD_DIM or cfg.head_dim in attn_ops.PADDED_HEAD_DIMS)):
+            # windows, sinks and a configured softmax scale on the flash kernels: work lists cut to the window and its left
+            # edge masked in the kernels, the sink logit added to the denominator in the forward's last step, the scale a
+            # kernel argument
+            plan = ctx.window_plan(self.window) if self.window else ctx.plan
+            o = attn_ops.rope_attention(qkv, self.q_norm, self.k_norm, self.rope_of(ctx), plan, cfg.num_attention_heads,
+                                        cfg.num_key_value_heads, cfg.rms_norm_eps, cfg.use_qk_norm, scale=self.scale,
+                                        sinks=self.sinks)
             return self._out(o)
         if (self.window or self.sinks is not None or self.scale is not None or self.softcap
                 or getattr(ctx, "attention_mask", None) is not None):

@@ -26,7 +26,18 @@ HEAD_DIM = 128
 FWD_VARIANT = int(os.environ.get("HALO_ATTN_FWD_VARIANT", "3"))
 
 
-def _launch_fwd(L, q, k, v, o, lse, plan, T, n_heads, n_kv_heads, scale, dev):
+def _launch_fwd(L, q, k, v, o, lse, plan, T, n_heads, n_kv_heads, scale, dev, sinks=None):
+    if sinks is not None:
+        # the sink logit joins the denominator in the forward kernel's last step (with or without a window)
+        work = plan.bwd_q
+        rc = L.halo_attn_fwd3_sinks(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse), _lib.ptr(work),
+            _lib.c_int(work.shape[0]), _lib.c_ll(T), _lib.c_int(n_heads), _lib.c_int(n_kv_heads),
+            _lib.c_int(HEAD_DIM), _lib.c_ll(_ld(q)), _lib.c_ll(_ld(k)), _lib.c_ll(_ld(v)), _lib.c_ll(_ld(o)),
+            _lib.c_float(scale), _lib.c_int(plan.window), _lib.ptr(sinks), _lib.ptr(_lib.status_word(dev)),
+            _lib.stream_ptr(dev))
+        _lib.check(rc, "halo_attn_fwd3_sinks")
+        return
     if plan.window:
         work = plan.bwd_q
         rc = L.halo_attn_fwd3_window(
@@ -149,9 +160,9 @@ def build_plan(cu_seqlens, device: torch.device | str | None = None, q_lo: int =
     return plan
 
 
-def attention_reference(q, k, v, cu_seqlens, n_heads, n_kv_heads, scale=None, window: int = 0):
+def attention_reference(q, k, v, cu_seqlens, n_heads, n_kv_heads, scale=None, window: int = 0, sinks=None):
     """fp32 oracle. q: [T, Hq*D]; k, v: [T, Hkv*D]; returns [T, Hq*D] in q's dtype. ``window > 0``: a query sees the last
-    ``window`` keys up to itself."""
+    ``window`` keys up to itself. ``sinks [Hq]``: one logit per head that joins every row's softmax and carries no value."""
     T = q.shape[0]
     D = q.shape[1] // n_heads
     scale = scale if scale is not None else D**-0.5
@@ -173,8 +184,18 @@ def attention_reference(q, k, v, cu_seqlens, n_heads, n_kv_heads, scale=None, wi
         if window:
             mask &= ~torch.ones(n, n, dtype=torch.bool, device=q.device).tril(-int(window))
         sc = sc.masked_fill(~mask, float("-inf"))
-        out[s:e] = (torch.softmax(sc, dim=-1) @ vv).transpose(0, 1)
+        if sinks is not None:
+            sc = torch.cat([sc, sinks.float()[:, None, None].expand(-1, n, 1)], dim=-1)
+            out[s:e] = (torch.softmax(sc, dim=-1)[..., :n] @ vv).transpose(0, 1)
+        else:
+            out[s:e] = (torch.softmax(sc, dim=-1) @ vv).transpose(0, 1)
     return out.reshape(T, n_heads * D).to(q.dtype)
+
+
+def _sink_grad(sinks, lse, delta):
+    """Gradient of the sink logits from what the backward kernels leave behind: the sink's probability in row t of head
+    h is exp(sink_h - lse[h, t]) and its value vector is zero, so dS_sink = -P_sink * delta with delta = rowsum(dO * O)."""
+    return -(torch.exp(sinks[:, None] - lse) * delta).sum(dim=1)
 
 
 def _ld(t: torch.Tensor) -> int:
@@ -185,18 +206,18 @@ def _ld(t: torch.Tensor) -> int:
 
 class _FlashAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, plan: AttentionPlan, n_heads: int, n_kv_heads: int, scale: float):
+    def forward(ctx, q, k, v, plan: AttentionPlan, n_heads: int, n_kv_heads: int, scale: float, sinks=None):
         T = q.shape[0]
         o = torch.empty((T, n_heads * HEAD_DIM), dtype=torch.bfloat16, device=q.device)
         lse = torch.empty((n_heads, T), dtype=torch.float32, device=q.device)
-        _launch_fwd(_lib.lib(), q, k, v, o, lse, plan, T, n_heads, n_kv_heads, scale, q.device)
-        ctx.save_for_backward(q, k, v, o, lse)
+        _launch_fwd(_lib.lib(), q, k, v, o, lse, plan, T, n_heads, n_kv_heads, scale, q.device, sinks)
+        ctx.save_for_backward(q, k, v, o, lse, sinks)
         ctx.plan, ctx.n_heads, ctx.n_kv_heads, ctx.scale = plan, n_heads, n_kv_heads, scale
         return o
 
     @staticmethod
     def backward(ctx, do):
-        q, k, v, o, lse = ctx.saved_tensors
+        q, k, v, o, lse, sinks = ctx.saved_tensors
         plan = ctx.plan
         T = q.shape[0]
         do = do.contiguous()
@@ -207,20 +228,38 @@ class _FlashAttention(torch.autograd.Function):
         delta = torch.empty((ctx.n_heads, T), dtype=torch.float32, device=q.device)
         L = _lib.lib()
         _launch_bwd(L, q, k, v, o, do, lse, delta, dq, dk, dv, plan, T, ctx.n_heads, ctx.n_kv_heads, ctx.scale, q.device)
-        return dq, dk, dv, None, None, None, None
+        dsinks = _sink_grad(sinks, lse, delta) if sinks is not None and ctx.needs_input_grad[7] else None
+        return dq, dk, dv, None, None, None, None, dsinks
 
 
-def flash_attention(q, k, v, plan: AttentionPlan, n_heads: int, n_kv_heads: int, scale: float | None = None):
-    """q: [T, Hq*128]; k, v: [T, Hkv*128] (row-strided views are fine); returns [T, Hq*128]."""
+PADDED_HEAD_DIMS = (64,)
+
+
+def _pad_heads(t, n, D):
+    """[T, n*D] -> [T, n*128] with each head's columns D..127 zero."""
+    return torch.nn.functional.pad(t.reshape(t.shape[0], n, D), (0, HEAD_DIM - D)).reshape(t.shape[0], n * HEAD_DIM)
+
+
+def flash_attention(q, k, v, plan: AttentionPlan, n_heads: int, n_kv_heads: int, scale: float | None = None, sinks=None):
+    """q: [T, Hq*D]; k, v: [T, Hkv*D] (row-strided views are fine); returns [T, Hq*D]. ``sinks [Hq]``: one logit per head
+    that joins every row's softmax (and gets a gradient). D is 128; heads of 64 run on the same kernels with columns
+    64..127 of every head zero (scores and outputs are unchanged by zero columns; the tensor work is that of 128-wide
+    heads, memory stays linear in the row length)."""
     D = q.shape[1] // n_heads
     scale = float(scale if scale is not None else D**-0.5)
     if not q.is_cuda:
-        return attention_reference(q, k, v, plan.cu_seqlens, n_heads, n_kv_heads, scale, window=plan.window)
+        return attention_reference(q, k, v, plan.cu_seqlens, n_heads, n_kv_heads, scale, window=plan.window, sinks=sinks)
+    if D in PADDED_HEAD_DIMS and q.dtype == torch.bfloat16:
+        o = flash_attention(_pad_heads(q, n_heads, D), _pad_heads(k, n_kv_heads, D), _pad_heads(v, n_kv_heads, D), plan,
+                            n_heads, n_kv_heads, scale, sinks)
+        return o.reshape(-1, n_heads, HEAD_DIM)[:, :, :D].reshape(-1, n_heads * D)
     if D != HEAD_DIM:
-        raise NotImplementedError("the sm_100a flash kernel is built for head_dim 128")
+        raise NotImplementedError("the sm_100a flash kernels are built for head_dim 128 (and 64, zero-padded)")
     if plan.fwd is None:
         raise ValueError("the attention plan was built without a CUDA device")
-    return _FlashAttention.apply(q, k, v, plan, n_heads, n_kv_heads, scale)
+    if sinks is not None:
+        sinks = sinks.float().contiguous()
+    return _FlashAttention.apply(q, k, v, plan, n_heads, n_kv_heads, scale, sinks)
 
 
 class _RopeAttention(torch.autograd.Function):
@@ -231,7 +270,7 @@ class _RopeAttention(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, qkv, wq, wk, table, plan, n_heads, n_kv_heads, eps, use_norm, scale):
+    def forward(ctx, qkv, wq, wk, table, plan, n_heads, n_kv_heads, eps, use_norm, scale, sinks=None):
         T = qkv.shape[0]
         dev = qkv.device
         L = _lib.lib()
@@ -247,14 +286,14 @@ class _RopeAttention(torch.autograd.Function):
         v = qkv[:, (n_heads + n_kv_heads) * HEAD_DIM :]
         o = torch.empty((T, n_heads * HEAD_DIM), dtype=torch.bfloat16, device=dev)
         lse = torch.empty((n_heads, T), dtype=torch.float32, device=dev)
-        _launch_fwd(L, q, k, v, o, lse, plan, T, n_heads, n_kv_heads, scale, dev)
-        ctx.save_for_backward(qkv, wq, wk, table, q, k, o, lse, rstd)
+        _launch_fwd(L, q, k, v, o, lse, plan, T, n_heads, n_kv_heads, scale, dev, sinks)
+        ctx.save_for_backward(qkv, wq, wk, table, q, k, o, lse, rstd, sinks)
         ctx.meta = (plan, n_heads, n_kv_heads, use_norm, scale)
         return o
 
     @staticmethod
     def backward(ctx, do):
-        qkv, wq, wk, table, q, k, o, lse, rstd = ctx.saved_tensors
+        qkv, wq, wk, table, q, k, o, lse, rstd, sinks = ctx.saved_tensors
         plan, n_heads, n_kv_heads, use_norm, scale = ctx.meta
         T = qkv.shape[0]
         dev = qkv.device
@@ -279,22 +318,25 @@ class _RopeAttention(torch.autograd.Function):
         _lib.check(rc, "halo_qknorm_rope_bwd")
         dwq = dw[:128].to(wq.dtype) if use_norm else None
         dwk = dw[128:].to(wk.dtype) if use_norm else None
-        return dqkv, dwq, dwk, None, None, None, None, None, None, None
+        dsinks = _sink_grad(sinks, lse, delta) if sinks is not None and ctx.needs_input_grad[10] else None
+        return dqkv, dwq, dwk, None, None, None, None, None, None, None, dsinks
 
 
-def rope_attention(qkv, wq, wk, table, plan, n_heads, n_kv_heads, eps=1e-6, use_norm=True, scale=None):
-    """``attention(rope(norm(q)), rope(norm(k)), v)`` from the fused projection ``qkv``."""
+def rope_attention(qkv, wq, wk, table, plan, n_heads, n_kv_heads, eps=1e-6, use_norm=True, scale=None, sinks=None):
+    """``attention(rope(norm(q)), rope(norm(k)), v)`` from the fused projection ``qkv``; ``sinks [Hq]`` as in
+    :func:`flash_attention`."""
     D = qkv.shape[1] // (n_heads + 2 * n_kv_heads)
     scale = float(scale if scale is not None else D**-0.5)
     per_head_norm = not use_norm or wq is None or wq.numel() == D
     if qkv.is_cuda and D == HEAD_DIM and qkv.dtype == torch.bfloat16 and 2 * table.shape[1] == D and per_head_norm:
-        return _RopeAttention.apply(qkv.contiguous(), wq, wk, table, plan, n_heads, n_kv_heads, eps, use_norm, scale)
+        return _RopeAttention.apply(qkv.contiguous(), wq, wk, table, plan, n_heads, n_kv_heads, eps, use_norm, scale,
+                                    None if sinks is None else sinks.float().contiguous())
     from .rope import qk_norm_rope_reference
 
     q, k = qk_norm_rope_reference(qkv, wq, wk, table, n_heads, n_kv_heads, eps, use_norm)
     v = qkv[:, (n_heads + n_kv_heads) * D :]
-    if qkv.is_cuda and D == HEAD_DIM and qkv.dtype == torch.bfloat16:
-        # partial rotary / whole-width q-k norm: these run as tensor ops (the fused kernel norms and turns whole heads
-        # one by one), attention itself on the kernel
-        return flash_attention(q, k, v, plan, n_heads, n_kv_heads, scale)
-    return attention_reference(q, k, v, plan.cu_seqlens, n_heads, n_kv_heads, scale, window=plan.window)
+    if qkv.is_cuda and (D == HEAD_DIM or D in PADDED_HEAD_DIMS) and qkv.dtype == torch.bfloat16:
+        # partial rotary / whole-width q-k norm / 64-wide heads: these run as tensor ops (the fused kernel norms and turns
+        # whole 128-wide heads one by one), attention itself on the kernel
+        return flash_attention(q, k, v, plan, n_heads, n_kv_heads, scale, sinks)
+    return attention_reference(q, k, v, plan.cu_seqlens, n_heads, n_kv_heads, scale, window=plan.window, sinks=sinks)

@@ -154,6 +154,67 @@ def test_flash_attention_sliding_window(lens, window):
         assert (full.float() - o.float()).abs().max().item() > 1e-2
 
 
+@pytest.mark.parametrize("lens,window", [([700, 300, 1048], 0), ([1500, 777], 200), ([130], 0)])
+def test_flash_attention_sinks(lens, window):
+    """One logit per head in every row's softmax: output, dq / dk / dv and the gradient of the logits themselves."""
+    from halo_b200.ops import _lib
+    from halo_b200.ops.attention import attention_reference, build_plan, flash_attention
+
+    Hq, Hkv = 4, 2
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    q, k, v = _mk(cu[-1], Hq, Hkv, seed=11)
+    # logits that matter: scores of unit-variance inputs at scale 128^-0.5 have a standard deviation near 1
+    sinks = torch.tensor([2.0, -1.0, 0.5, 4.0], device="cuda")
+    plan = build_plan(cu, device="cuda", window=window)
+    qg, kg, vg, sg = (t.clone().requires_grad_() for t in (q, k, v, sinks))
+    o = flash_attention(qg, kg, vg, plan, Hq, Hkv, sinks=sg)
+    do = torch.randn_like(o)
+    o.backward(do)
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+    qr, kr, vr, sr = (t.float().requires_grad_() for t in (q, k, v, sinks))
+    o_ref = attention_reference(qr, kr, vr, cu, Hq, Hkv, window=window, sinks=sr)
+    o_ref.backward(do.float())
+    assert _row_rel_err(o, o_ref) < 2e-2
+    assert _row_rel_err(vg.grad, vr.grad) < 3e-2
+    assert _row_rel_err(qg.grad, qr.grad) < 4e-2
+    assert _row_rel_err(kg.grad, kr.grad) < 4e-2
+    assert ((sg.grad - sr.grad).abs() / (sr.grad.abs() + 0.02 * sr.grad.abs().mean())).max().item() < 3e-2
+    # the sinks take mass: the output differs from the sink-free one
+    plain = flash_attention(q, k, v, plan, Hq, Hkv)
+    assert (plain.float() - o.float()).abs().max().item() > 1e-2
+
+
+def test_flash_attention_heads_of_64_run_zero_padded():
+    from halo_b200.ops import _lib
+    from halo_b200.ops.attention import attention_reference, build_plan, flash_attention
+
+    Hq, Hkv, D = 8, 2, 64
+    cu = [0, 400, 1000, 1111]
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q = torch.randn(cu[-1], Hq * D, device="cuda", generator=g).bfloat16()
+    k = torch.randn(cu[-1], Hkv * D, device="cuda", generator=g).bfloat16()
+    v = torch.randn(cu[-1], Hkv * D, device="cuda", generator=g).bfloat16()
+    sinks = torch.linspace(-1, 3, Hq, device="cuda")
+    plan = build_plan(cu, device="cuda", window=128)
+    qg, kg, vg = (t.clone().requires_grad_() for t in (q, k, v))
+    o = flash_attention(qg, kg, vg, plan, Hq, Hkv, sinks=sinks)
+    assert o.shape == (cu[-1], Hq * D)
+    do = torch.randn_like(o)
+    o.backward(do)
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+    qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
+    o_ref = attention_reference(qr, kr, vr, cu, Hq, Hkv, window=128, sinks=sinks)
+    o_ref.backward(do.float())
+    assert _row_rel_err(o, o_ref) < 2e-2
+    assert _row_rel_err(vg.grad, vr.grad) < 3e-2
+    assert _row_rel_err(qg.grad, qr.grad) < 4e-2
+    assert _row_rel_err(kg.grad, kr.grad) < 4e-2
+
+
 def test_rope_attention_fused_matches_reference():
     from halo_b200.ops.attention import build_plan, rope_attention
     from halo_b200.ops.rope import rope_table
