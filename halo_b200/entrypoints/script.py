@@ -32,6 +32,12 @@ log = logging.getLogger(__name__)
 def parse_script_args(*extra_dataclasses, argv=None):
     hlog.configure_logging()
     device = init_distributed()
+    if dist.is_initialized():
+        from halo_b200.runtime import filesystem
+        from halo_b200.runtime.consensus import reject_divergent_environment
+
+        reject_divergent_environment()
+        filesystem.resolve_consensus()
     parser = ArgumentParser(ModelArguments, DataArguments, TrainingArguments, ParallelismArguments, *extra_dataclasses)
     parsed = parser.parse(argv)
     train_args = parsed[2]
@@ -48,7 +54,14 @@ def init_training_script(device, model_args, train_args, par_args, world_size: i
     except ValueError as exc:
         reason = str(exc)
     reject_across_ranks(reason, what="parallelism configuration")
-    if hlog.is_main_process():
+    from halo_b200.runtime import filesystem
+
+    if dist.is_initialized():
+        # the writer of each scope (rank 0 on shared storage, local rank 0 per node otherwise) creates the directory;
+        # a multi-node job then checks the declaration against what the mounts do
+        filesystem.makedirs_on_writer(train_args.output_dir)
+        filesystem.verify_job_directories(train_args.output_dir)
+    elif hlog.is_main_process():
         os.makedirs(train_args.output_dir, exist_ok=True)
     return pc
 

@@ -47,10 +47,20 @@ CATALOGUE = {
     "DIST_NCCL_TIMEOUT_MINUTES": "collective watchdog of every process group",
     "DIST_STORE_TIMEOUT_HOURS": "timeout of store-based joins that outlast the watchdog",
     "DIST_FS_PROBE_TIMEOUT_SECONDS": "how long to poll for the shared-filesystem sentinel",
+    "DIST_SHARED_FILESYSTEM": "inputs and outputs are on storage every node sees (default of the two flags below; single-node jobs default to 1)",
     "DIST_INPUT_SHARED_FILESYSTEM": "inputs are on a filesystem every node sees",
     "DIST_OUTPUT_SHARED_FILESYSTEM": "outputs go to a filesystem every node sees",
     "NVLINK_DOMAIN_SIZE": "ranks per NVLink domain (overrides detection)",
 }
+
+
+# knobs that legitimately differ between ranks or nodes of one job; every other catalogued knob must be the same everywhere
+PER_RANK = frozenset({"HALO_NODE_RANK", "HALO_DATA_ROOT", "HALO_LOG_LEVEL"})
+
+
+def rank_uniform_snapshot() -> dict[str, str | None]:
+    """The raw values of every catalogued knob that all ranks of a job must agree on (unset: None)."""
+    return {name: _raw(name) for name in sorted(CATALOGUE) if name not in PER_RANK}
 
 
 def _raw(name: str) -> str | None:

@@ -64,6 +64,26 @@ def reject_divergent_settings(settings: dict, group=None) -> None:
             raise RankFailure(f"setting {key!r} differs across ranks: {sorted(seen)}")
 
 
+def reject_divergent_environment(group=None) -> None:
+    """COLLECTIVE. The start-up check over the environment catalogue: a knob that picks a kernel form, a timeout or a
+    coordination scope must read the same on every rank (a per-node override would make ranks take different code
+    paths into the same collective). Names every differing knob with the ranks' values."""
+    from halo_b200 import env
+
+    mine = env.rank_uniform_snapshot()
+    every = all_gather_object(mine, group)
+    bad = []
+    for name in mine:
+        seen = [v.get(name) for v in every]
+        if len({repr(x) for x in seen}) > 1:
+            by_value: dict[str, list[int]] = {}
+            for r, x in enumerate(seen):
+                by_value.setdefault("unset" if x is None else repr(x), []).append(r)
+            bad.append(f"{name}: " + ", ".join(f"{v} on ranks {rs}" for v, rs in sorted(by_value.items())))
+    if bad:
+        raise RankFailure("environment knobs differ across ranks: " + "; ".join(bad))
+
+
 class DeferredRankFailure:
     """Collect a local exception inside a block that contains collectives, keep participating, and
     raise everywhere at the end::
