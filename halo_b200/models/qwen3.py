@@ -329,9 +329,9 @@ class SparseMoE(nn.Module):
         self.gate_bias = (nn.Parameter(torch.zeros(cfg.num_experts, dtype=router_dtype or dtype, device=device))
                           if cfg.router_logit_bias else None)
         if cfg.expert_bias or cfg.expert_activation != "swiglu":
-            if n_local_experts != cfg.num_experts or etp is not None:
-                raise ValueError("experts with bias vectors / a clamped GLU run whole on every rank: expert parallelism and "
-                                 "expert tensor parallelism are not built for them")
+            if etp is not None:
+                raise ValueError("experts with bias vectors / a clamped GLU are not cut inside an expert (expert tensor "
+                                 "parallelism); expert parallelism holds whole experts and is fine")
             self.experts_gate_up_bias = nn.Parameter(torch.zeros(n_local_experts, 2 * F, dtype=dtype, device=device))
             self.experts_down_bias = nn.Parameter(torch.zeros(n_local_experts, H, dtype=dtype, device=device))
             self.experts_gate_up_bias.is_expert = self.experts_down_bias.is_expert = True
@@ -394,10 +394,20 @@ class SparseMoE(nn.Module):
         if self.lowp:
             bank_gate_up, bank_down, h_experts = (_rounded(t, self.lowp) for t in (bank_gate_up, bank_down, h))
         if self.experts_gate_up_bias is not None:
-            from halo_b200.ops.biased_glu_experts import biased_glu_experts
+            from halo_b200.ops.biased_glu_experts import GLU_ALPHA, biased_glu_experts
 
-            out = biased_glu_experts(h_experts, idx, w, bank_gate_up, self.experts_gate_up_bias, bank_down,
-                                     self.experts_down_bias, cfg.glu_limit)
+            if h_experts.is_cuda and h_experts.dtype == torch.bfloat16:
+                # grouped products with the bias / clamped-GLU row kernels between them; dispatches over expert-parallel
+                # ranks like the plain experts
+                out = moe_ops.moe_experts(h_experts, idx, w, bank_gate_up, bank_down, ctx.transport,
+                                          skip_output=getattr(ctx, "output_unused", False),
+                                          glu=(self.experts_gate_up_bias, self.experts_down_bias, cfg.glu_limit, GLU_ALPHA))
+            else:
+                if bank_gate_up.shape[0] != cfg.num_experts:
+                    raise NotImplementedError("experts with bias vectors / a clamped GLU dispatch over expert-parallel "
+                                              "ranks on GPUs only")
+                out = biased_glu_experts(h_experts, idx, w, bank_gate_up, self.experts_gate_up_bias, bank_down,
+                                         self.experts_down_bias, cfg.glu_limit)
         elif self.etp is not None:
             # every rank of the group routes the same tokens through its slice of each expert; the partial outputs
             # are summed in token space (and the partial input / routing-weight gradients on the way back)

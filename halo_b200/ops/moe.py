@@ -331,6 +331,36 @@ def grouped_swiglu_ffn_fwd(state: RoutingState, x_rows, w_gate_up, w_down, save_
     return act, pre
 
 
+def grouped_biased_glu_fwd(state: RoutingState, x_rows, w_gate_up, gate_up_bias, limit: float, alpha: float, transport=None):
+    """Experts with bias vectors and a clamped GLU: the first product stores the raw pre-activations, one row kernel adds
+    the expert's bias (in place: the backward reads the biased values) and writes ``(up + 1) * gate * sigmoid(alpha gate)``
+    of the clamped halves. Returns (act [cap, F], pre [cap, 2F])."""
+    E, F2, H = w_gate_up.shape
+    F = F2 // 2
+    cap = x_rows.shape[0]
+    dev = x_rows.device
+    act = _alloc(transport, (cap, F), torch.bfloat16, dev)
+    pre = _alloc(transport, (cap, F2), torch.bfloat16, dev)
+    pair = _pair_ok(H, False)
+    lst1 = _tile_list(state, "m", pair, n_cols=F2, k_dim=H, b_mn_stride=F2, b_k_stride=0, swiglu_f=0)
+    _gemm_list(x_rows, w_gate_up.reshape(E * F2, H), pre, lst1, 0, 0, EPI_STORE_BF16, pair=pair)
+    _lib.check(_lib.lib().halo_expert_glu_fwd(
+        _lib.ptr(pre), _lib.ptr(gate_up_bias), _lib.ptr(act), _lib.ptr(state.seg_start), _lib.c_int(state.n_local),
+        _lib.ptr(state.total_rows), _lib.c_int(F), _lib.c_int(cap), _lib.c_float(limit), _lib.c_float(alpha),
+        _lib.stream_ptr(dev)), "halo_expert_glu_fwd")
+    return act, pre
+
+
+def _expert_colsum(state: RoutingState, src, row_w, n_cols: int):
+    """Per-expert column sums of a row buffer (weighted per row when ``row_w`` is given) -> fp32 [E_local, n_cols]."""
+    out = torch.empty((state.n_local, n_cols), dtype=torch.float32, device=src.device)
+    _lib.check(_lib.lib().halo_expert_colsum(
+        _lib.ptr(src), _lib.ptr(row_w), _lib.ptr(out), _lib.ptr(state.seg_start), _lib.ptr(state.seg_rows),
+        _lib.c_int(state.n_local), _lib.c_int(n_cols), _lib.c_int(state.capacity), _lib.stream_ptr(src.device)),
+        "halo_expert_colsum")
+    return out
+
+
 def grouped_down_fwd(state: RoutingState, act, w_down, out_rows):
     E, H, F = w_down.shape
     pair = _pair_ok(F, False)
@@ -587,7 +617,7 @@ def _fused_backward(ctx, dout):
     # slots of dropped rows (a capacity overflow, reported through the status word) carry no gradient
     valid = (state.slot_row >= 0) & (state.slot_row < cap // 128 * 128)
     dw = torch.where(valid, dw_slots[:T * k, 0], torch.zeros((), dtype=torch.float32, device=dev)).view(T, k)
-    return dx, None, dw, dw_gate_up, dw_down, None, None, None, None
+    return dx, None, dw, dw_gate_up, dw_down, None, None, None, None, None, None, None, None
 
 
 # ---------------------------------------------------------------------------------------------
@@ -618,8 +648,12 @@ def moe_ffn_reference(x, topk_idx, topk_w, w_gate_up, w_down, expert_offset: int
 # ---------------------------------------------------------------------------------------------
 class _MoEExperts(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, topk_idx, topk_w, w_gate_up, w_down, transport, state_out, grad_mode, skip_output=False):
-        ctx.fused = _fused(transport)
+    def forward(ctx, x, topk_idx, topk_w, w_gate_up, w_down, transport, state_out, grad_mode, skip_output=False,
+                gate_up_bias=None, down_bias=None, glu_limit=0.0, glu_alpha=0.0):
+        # experts with bias vectors / a clamped GLU take the separate-kernel pipeline: their element-wise half runs as
+        # row kernels between the grouped products
+        ctx.glu = (float(glu_limit), float(glu_alpha)) if gate_up_bias is not None else None
+        ctx.fused = _fused(transport) and ctx.glu is None
         if ctx.fused:
             return _fused_forward(ctx, x, topk_idx, topk_w, w_gate_up, w_down, transport, state_out, grad_mode, skip_output)
         T, H = x.shape
@@ -645,7 +679,10 @@ class _MoEExperts(torch.autograd.Function):
                                         _lib.ptr(_lib.status_word(dev)), s), "halo_dispatch_rows")
         transport.barrier()
         need_grad = grad_mode and any(ctx.needs_input_grad)
-        act, pre = grouped_swiglu_ffn_fwd(state, recv_x, w_gate_up, w_down, save_pre=need_grad, transport=transport)
+        if ctx.glu is None:
+            act, pre = grouped_swiglu_ffn_fwd(state, recv_x, w_gate_up, w_down, save_pre=need_grad, transport=transport)
+        else:
+            act, pre = grouped_biased_glu_fwd(state, recv_x, w_gate_up, gate_up_bias, *ctx.glu, transport=transport)
         w32 = topk_w.float().contiguous()
         if skip_output and need_grad:
             # a recomputation whose value nobody reads: the backward needs only the dispatched rows and the
@@ -653,6 +690,10 @@ class _MoEExperts(torch.autograd.Function):
             out = _alloc(transport, tuple(x.shape), x.dtype, dev)
         else:
             grouped_down_fwd(state, act, w_down, y_rows)
+            if ctx.glu is not None:
+                _lib.check(L.halo_expert_add_bias_rows(_lib.ptr(y_rows), _lib.ptr(down_bias), _lib.ptr(state.seg_start),
+                                                       _lib.c_int(state.n_local), _lib.ptr(state.total_rows), _lib.c_int(H),
+                                                       _lib.c_int(cap), s), "halo_expert_add_bias_rows")
             transport.barrier()
             out = _alloc(transport, tuple(x.shape), x.dtype, dev)
             _lib.check(L.halo_combine_rows(py, _lib.c_int(transport.n_ranks), _lib.ptr(state.topk_idx), _lib.ptr(state.slot_row),
@@ -661,7 +702,7 @@ class _MoEExperts(torch.autograd.Function):
         if need_grad:
             if transport.transient_buffers:
                 recv_x = recv_x.clone()
-            ctx.save_for_backward(recv_x, pre, w32, w_gate_up, w_down)
+            ctx.save_for_backward(recv_x, pre, w32, w_gate_up, w_down, down_bias)
             ctx.state = state
             ctx.transport = transport
         if state_out is not None:
@@ -672,7 +713,7 @@ class _MoEExperts(torch.autograd.Function):
     def backward(ctx, dout):
         if ctx.fused:
             return _fused_backward(ctx, dout)
-        recv_x, pre, w32, w_gate_up, w_down = ctx.saved_tensors
+        recv_x, pre, w32, w_gate_up, w_down, down_bias = ctx.saved_tensors
         state, transport = ctx.state, ctx.transport
         T, k = state.n_tokens, state.top_k
         E_local, F2, H = w_gate_up.shape
@@ -705,9 +746,26 @@ class _MoEExperts(torch.autograd.Function):
         #    Both outputs overwrite their inputs (element for element, same index): dpre lands on pre, act_w on dact_u.
         dwrow = transport.buffer("dwrow", cap, 1, torch.float32, dev)
         dpre, act_w = pre, dact
-        _lib.check(L.halo_swiglu_bwd_weighted(_lib.ptr(pre), _lib.ptr(dact), _lib.ptr(row_w), _lib.ptr(dpre),
-                                              _lib.ptr(act_w), _lib.ptr(dwrow), _lib.ptr(state.total_rows),
-                                              _lib.c_int(F), _lib.c_int(cap), s), "halo_swiglu_bwd_weighted")
+        d_gate_up_bias = d_down_bias = None
+        if ctx.glu is None:
+            _lib.check(L.halo_swiglu_bwd_weighted(_lib.ptr(pre), _lib.ptr(dact), _lib.ptr(row_w), _lib.ptr(dpre),
+                                                  _lib.ptr(act_w), _lib.ptr(dwrow), _lib.ptr(state.total_rows),
+                                                  _lib.c_int(F), _lib.c_int(cap), s), "halo_swiglu_bwd_weighted")
+        else:
+            limit, alpha = ctx.glu
+            _lib.check(L.halo_expert_glu_bwd(_lib.ptr(pre), _lib.ptr(dact), _lib.ptr(row_w), _lib.ptr(dpre), _lib.ptr(act_w),
+                                             _lib.ptr(dwrow), _lib.ptr(state.total_rows), _lib.c_int(F), _lib.c_int(cap),
+                                             _lib.c_float(limit), _lib.c_float(alpha), s), "halo_expert_glu_bwd")
+            # the expert's output includes its down bias: <dout, b_down[e]> joins the routing-weight gradient
+            _lib.check(L.halo_expert_bias_rowdot(_lib.ptr(dy), _lib.ptr(down_bias), _lib.ptr(dwrow), _lib.ptr(state.seg_start),
+                                                 _lib.c_int(state.n_local), _lib.ptr(state.total_rows), _lib.c_int(H),
+                                                 _lib.c_int(cap), s), "halo_expert_bias_rowdot")
+            # bias gradients: column sums over each expert's rows (dy is still the incoming gradient here; its storage
+            # may take the input-gradient rows below)
+            if ctx.needs_input_grad[10]:
+                d_down_bias = _expert_colsum(state, dy, row_w, H).to(down_bias.dtype)
+            if ctx.needs_input_grad[9]:
+                d_gate_up_bias = _expert_colsum(state, dpre, None, F2).to(down_bias.dtype)
         need_weight_grads = ctx.needs_input_grad[3] or ctx.needs_input_grad[4]
 
         def weight_grads():
@@ -768,10 +826,10 @@ class _MoEExperts(torch.autograd.Function):
                 joined.record(side)
             dw_gate_up, dw_down = weight_grads()
             main.wait_event(joined)
-        return dx, None, dw, dw_gate_up, dw_down, None, None, None, None
+        return dx, None, dw, dw_gate_up, dw_down, None, None, None, None, d_gate_up_bias, d_down_bias, None, None
 
 
-def _moe_experts_lanes(x, topk_idx, topk_w, w_gate_up, w_down, lanes, state_out, skip_output):
+def _moe_experts_lanes(x, topk_idx, topk_w, w_gate_up, w_down, lanes, state_out, skip_output, glu=(None, None, 0.0, 0.0)):
     """Cut the tokens into one part per lane and run each part's whole expert op (push, products, pull) on the
     lane's own stream and buffers: while one part moves rows over NVLink, another part's products keep the
     tensor cores busy. Every rank cuts at the same places, so the lanes' barriers pair up across ranks."""
@@ -793,7 +851,7 @@ def _moe_experts_lanes(x, topk_idx, topk_w, w_gate_up, w_down, lanes, state_out,
         xs, ids, ws = x[lo:hi], topk_idx[lo:hi], topk_w[lo:hi]
         lane.stream.wait_event(fork)
         with torch.cuda.stream(lane.stream):
-            o = _MoEExperts.apply(xs, ids, ws, w_gate_up, w_down, lane, state_out, grad_mode, skip_output)
+            o = _MoEExperts.apply(xs, ids, ws, w_gate_up, w_down, lane, state_out, grad_mode, skip_output, *glu)
             ev = torch.cuda.Event()
             ev.record(lane.stream)
         outs.append(o)
@@ -806,23 +864,31 @@ def _moe_experts_lanes(x, topk_idx, topk_w, w_gate_up, w_down, lanes, state_out,
 
 
 def moe_experts(x, topk_idx, topk_w, w_gate_up, w_down, transport=None, state_out: list | None = None,
-                skip_output: bool = False):
+                skip_output: bool = False, glu: tuple | None = None):
     """Apply the routed experts.
 
     x: [T, H] bf16; topk_idx: int32 [T, k] global expert ids; topk_w: [T, k] routing weights;
     w_gate_up: [E_local, 2F, H] (gate rows then up rows per expert); w_down: [E_local, H, F].
     ``skip_output``: the caller will not read the result (a recomputation that only rebuilds what the
     backward needs); the returned tensor is then uninitialised.
+    ``glu = (gate_up_bias [E_local, 2F], down_bias [E_local, H], limit, alpha)``: experts with bias vectors around a
+    clamped GLU, ``(up + 1) * gate * sigmoid(alpha * gate)`` with ``gate <= limit`` and ``|up| <= limit`` (GPU only: the
+    tensor-op form is :func:`halo_b200.ops.biased_glu_experts.biased_glu_experts`).
     """
     if transport is None:
         transport = LocalTransport()
+    if glu is not None:
+        if not x.is_cuda or not hasattr(transport, "peer_table"):
+            raise NotImplementedError("experts with bias vectors / a clamped GLU run through the grouped kernels on a GPU only")
+        glu = (glu[0].contiguous(), glu[1].contiguous(), float(glu[2]), float(glu[3]))
     if not x.is_cuda or hasattr(transport, "reference_ffn") and not hasattr(transport, "peer_table"):
         offset = transport.rank * w_gate_up.shape[0]
         if transport.n_ranks > 1:
             return transport.reference_ffn(x, topk_idx, topk_w, w_gate_up, w_down)
         return moe_ffn_reference(x, topk_idx, topk_w, w_gate_up, w_down, offset)
     lanes = getattr(transport, "lanes", None)
+    extra = glu if glu is not None else (None, None, 0.0, 0.0)
     if lanes:
-        return _moe_experts_lanes(x.contiguous(), topk_idx, topk_w, w_gate_up, w_down, lanes, state_out, skip_output)
+        return _moe_experts_lanes(x.contiguous(), topk_idx, topk_w, w_gate_up, w_down, lanes, state_out, skip_output, extra)
     return _MoEExperts.apply(x.contiguous(), topk_idx, topk_w, w_gate_up, w_down, transport, state_out,
-                             torch.is_grad_enabled(), skip_output)
+                             torch.is_grad_enabled(), skip_output, *extra)

@@ -211,11 +211,13 @@ def reject_model_layout(pc, model_cfg, packed: bool = True) -> None:
                 f"tensor_parallel_size ({pc.tp_size}) must divide num_attention_heads "
                 f"({model_cfg.num_attention_heads}) and num_key_value_heads ({model_cfg.num_key_value_heads})")
     if getattr(model_cfg, "attention_sinks", False) or getattr(model_cfg, "expert_bias", False):
-        cut = [name for name, size in (("expert_parallel_size", pc.ep_size), ("expert_tensor_parallel_size", pc.expert_tp_size),
+        # whole experts move between ranks (their bias rows with them), so expert parallelism is fine; nothing cuts
+        # inside an expert, a head group or a row
+        cut = [name for name, size in (("expert_tensor_parallel_size", pc.expert_tp_size),
                                        ("tensor_parallel_size", pc.tp_size), ("context_parallel_size", pc.cp_size)) if size > 1]
         if cut:
-            raise ConfigError(f"{model_cfg.family}: attention sinks and experts with bias vectors run whole on every rank "
-                              f"(data parallelism and pipeline stages only); drop {', '.join(cut)}")
+            raise ConfigError(f"{model_cfg.family}: attention sinks and experts with bias vectors are not cut inside an expert, "
+                              f"a head group or a row (data, expert and pipeline parallelism only); drop {', '.join(cut)}")
     masked_only = [what for what, on in (("a sliding window", getattr(model_cfg, "sliding_window", 0)),
                                          ("a configured softmax scale", (getattr(model_cfg, "query_pre_attn_scalar", 0) or model_cfg.head_dim) != model_cfg.head_dim),
                                          ("a tanh-GELU gate", getattr(model_cfg, "hidden_activation", "silu") != "silu")) if on]

@@ -225,10 +225,16 @@ def test_gpt_oss_trains_and_sinks_follow_the_policy(tmp_path):
         policy_from_flags(True, True)
     with pytest.raises(ValueError, match="no attention sinks"):
         apply_sinks_policy(build_model(family_config("llama"), device="cpu"), "trainable")
-    for axis in ("ep_size", "tp_size", "cp_size"):
-        with pytest.raises(ConfigError, match="run whole on every rank"):
+    for axis in ("tp_size", "cp_size"):
+        with pytest.raises(ConfigError, match="not cut inside an expert, a head group or a row"):
             reject_model_layout(ParallelismConfig(world_size=2, **{axis: 2}), cfg)
     reject_model_layout(ParallelismConfig(world_size=4, pp_size=2), cfg)
+    reject_model_layout(ParallelismConfig(world_size=2, ep_size=2), cfg)       # whole experts move, their bias rows with them
+    # an expert-parallel rank holds its slice of the banks and of the two bias banks
+    from halo_b200.models.qwen3 import SparseMoE
+
+    sliced = SparseMoE(cfg, torch.float32, "meta", cfg.num_experts // 2)
+    assert sliced.experts_gate_up_bias.shape[0] == sliced.experts_down_bias.shape[0] == cfg.num_experts // 2
 
 
 def test_keys_visited_follow_each_layers_window():

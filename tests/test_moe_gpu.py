@@ -71,6 +71,51 @@ def test_moe_experts_fwd_bwd(T, H, F, E, k, fused):
     _close(wda.grad, wdb.grad, 4e-2, "dw_down")
 
 
+@pytest.mark.parametrize("T,H,F,E,k", [(64, 256, 128, 8, 2), (777, 512, 256, 16, 4), (3000, 1024, 512, 32, 4)])
+def test_biased_clamped_glu_experts_fwd_bwd(T, H, F, E, k):
+    """Experts with bias vectors around a clamped GLU on the grouped kernels (bias / activation row kernels between the
+    products) against the dense fp32 form: output and every gradient, the two bias banks' included."""
+    from halo_b200.ops import _lib
+    from halo_b200.ops.biased_glu_experts import GLU_ALPHA, biased_glu_experts_reference
+    from halo_b200.ops.moe import LocalTransport, moe_experts
+
+    torch.manual_seed(2)
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    wgu = (torch.randn(E, 2 * F, H, device="cuda") * 0.08).bfloat16()      # pre-activations of a few units: both clamps bite
+    wd = (torch.randn(E, H, F, device="cuda") * 0.05).bfloat16()
+    bgu = (torch.randn(E, 2 * F, device="cuda") * 0.5).bfloat16()
+    bd = (torch.randn(E, H, device="cuda") * 0.5).bfloat16()
+    limit = 2.0
+    scores = torch.rand(T, E, device="cuda")
+    w, idx = torch.topk(scores, k, dim=-1)
+    w = (w / w.sum(-1, keepdim=True)).float()
+    idx = idx.to(torch.int32)
+
+    leaves = [t.clone().requires_grad_() for t in (x, w, wgu, wd, bgu, bd)]
+    xa, wa, wgua, wda, bgua, bda = leaves
+    out = moe_experts(xa, idx, wa, wgua, wda, LocalTransport(), glu=(bgua, bda, limit, GLU_ALPHA))
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+    refs = [t.float().requires_grad_() for t in (x, w, wgu, wd, bgu, bd)]
+    xb, wb, wgub, wdb, bgub, bdb = refs
+    ref = biased_glu_experts_reference(xb, idx, wb, wgub, bgub, wdb, bdb, limit)
+    _close(out, ref, 3e-2, "out")
+    g = torch.randn_like(out)
+    out.backward(g)
+    ref.backward(g.float())
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+    for got, want, name in zip(leaves, refs, ("dx", "dw_route", "dw_gate_up", "dw_down", "db_gate_up", "db_down")):
+        _close(got.grad, want.grad, 4e-2, name)
+    # a recomputation that skips its output still gives the same gradients
+    again = [t.clone().requires_grad_() for t in (x, w, wgu, wd, bgu, bd)]
+    out2 = moe_experts(again[0], idx, again[1], again[2], again[3], LocalTransport(), skip_output=True,
+                       glu=(again[4], again[5], limit, GLU_ALPHA))
+    out2.backward(g)
+    for a, b2 in zip(again, leaves):
+        assert torch.equal(a.grad, b2.grad)
+
+
 def test_fused_moe_calls_in_a_row_share_one_control_block():
     """Several layers' worth of calls through one transport (forward, a recomputation that skips its output, backward):
     the control block's call numbers, buffer parities and arrival counters must carry over from call to call."""
