@@ -18,22 +18,28 @@ from halo_b200.entrypoints.script import (build_runtime, init_training_script, l
                                           run_trainer, with_distributed_teardown)
 
 
-def rollouts_from_jsonl(path: str, group: int):
-    """Each line: {"prompt_ids": [...], "completion_ids": [...], "reward": x, "sampler_logps": [...]?}; lines of
-    one prompt are consecutive. Yields one round per ``group``-aligned block of 64 prompts."""
+def rollouts_from_jsonl(path: str, group: int, dp_rank: int = 0, dp_size: int = 1, seed: int = 0, epochs: float = 1.0,
+                        prompts_per_round: int = 64, shuffle: bool = True):
+    """Each line: {"prompt_ids": [...], "completion_ids": [...], "reward": x, "sampler_logps": [...]?, "group_id": g?}.
+    Without ``group_id`` every ``group`` consecutive lines are one prompt's generations. A data-parallel rank trains on
+    its own contiguous cut of the groups, ``prompts_per_round`` groups per round, reshuffled every epoch with a seed all
+    ranks share (:class:`halo_b200.trainers.grpo.group_sampler.GroupSampler`)."""
+    from halo_b200.trainers.grpo.group_sampler import GroupSampler
     from halo_b200.trainers.grpo.trainer import Rollout
 
     rows = [json.loads(l) for l in open(path) if l.strip()]
-    per_round = 64 * group
+    ids = [r["group_id"] if "group_id" in r else i // group for i, r in enumerate(rows)]
+    sampler = GroupSampler(ids, dp_rank, dp_size, prompts_per_round, shuffle, seed)
 
     def source(round_index: int):
-        block = rows[round_index * per_round:(round_index + 1) * per_round]
-        if not block:
+        picked = sampler.round_rows(round_index, epochs)
+        if picked is None:
             return None
         return [Rollout(np.asarray(r["prompt_ids"]), np.asarray(r["completion_ids"]),
                         None if r.get("sampler_logps") is None else np.asarray(r["sampler_logps"], dtype=np.float32),
-                        float(r["reward"])) for r in block]
+                        float(r["reward"])) for r in (rows[i] for i in picked)]
 
+    source.sampler = sampler
     return source
 
 
@@ -223,7 +229,8 @@ def main(argv=None):
     elif grpo_args.rollout_backend == "in_process":
         source = in_process_source(model, model_args, data_args, train_args, grpo_args, pc)
     elif data_args.dataset_path:
-        source = rollouts_from_jsonl(data_args.dataset_path, grpo_args.num_generations)
+        source = rollouts_from_jsonl(data_args.dataset_path, grpo_args.num_generations, pc.data_parallel_rank,
+                                     pc.data_parallel_size, seed=train_args.seed, epochs=train_args.num_train_epochs)
     else:
         vocab = data_args.synthetic_vocab or model.cfg.vocab_size
 
