@@ -56,6 +56,12 @@ def init_training_script(device, model_args, train_args, par_args, world_size: i
     reject_across_ranks(reason, what="parallelism configuration")
     from halo_b200.runtime import filesystem
 
+    if dist.is_initialized() and torch.device(device).type == "cuda":
+        # the declared NVLink domain against what the GPUs report (placement, fabric cliques, multi-node prerequisites)
+        from halo_b200.parallel import nvlink_fabric
+
+        nvlink_fabric.validate_domain(pc.nvlink_domain_size, pc.world_size, pc.gpus_per_node)
+        nvlink_fabric.verify_mnnvl_prerequisites(pc.nvlink_domain_size, pc.gpus_per_node)
     if dist.is_initialized():
         # the writer of each scope (rank 0 on shared storage, local rank 0 per node otherwise) creates the directory;
         # a multi-node job then checks the declaration against what the mounts do
