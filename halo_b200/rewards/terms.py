@@ -62,8 +62,45 @@ class RewardModelTerm(RewardTerm):
     endpoint: str = ""
 
 
+@dataclass(frozen=True)
+class PolicyCheckTerm(RewardTerm):
+    """The White Circle API's policy check of the completion in its conversation against the policies of
+    ``environment_id``. With nothing listed the score is 1 unless the completion was flagged, else 0; with ``policies``
+    (policy ids) it is the fraction of them the completion did not violate; a ``checklist`` (the policy ids of its
+    items) is one judgment: its confidence is the fraction of items hit, its score 1 minus that. A term lists
+    ``policies`` or a ``checklist``, not both. ``view``: "full" reads every assistant turn of the completion, "final"
+    the last one. ``max_retries`` bounds the retries of a rate-limited or failed request, ``retry_wait`` is the first
+    backoff in seconds."""
+    environment_id: str = ""
+    policies: tuple = ()
+    checklist: tuple = ()
+    region: str = "us"
+    view: str = "full"
+    max_retries: int = 4
+    retry_wait: float = 1.0
+    request_timeout: float = 30.0
+    max_concurrency: int = 8
+
+    def __post_init__(self):
+        super().__post_init__()
+        if not str(self.environment_id).strip():
+            raise ValueError(f"term {self.name!r}: environment_id is required")
+        for f in ("policies", "checklist"):
+            ids = getattr(self, f)
+            if isinstance(ids, str) or not hasattr(ids, "__iter__"):
+                raise ValueError(f"term {self.name!r}: {f} must be a list of policy ids, got {ids!r}")
+            object.__setattr__(self, f, tuple(ids))
+        if self.policies and self.checklist:
+            raise ValueError(f"term {self.name!r}: list policies or a checklist, not both")
+        if self.view not in ("full", "final"):
+            raise ValueError(f"term {self.name!r}: view must be 'full' or 'final'")
+        if self.max_retries < 0 or self.retry_wait < 0 or self.request_timeout <= 0 or self.max_concurrency < 1:
+            raise ValueError(f"term {self.name!r}: max_retries / retry_wait must not be negative, request_timeout and "
+                             "max_concurrency must be positive")
+
+
 TERM_TYPES = {"environment": EnvironmentTerm, "grader": GraderTerm, "format": FormatTerm, "judge": JudgeTerm,
-              "reward_model": RewardModelTerm}
+              "reward_model": RewardModelTerm, "whitecircle": PolicyCheckTerm}
 
 
 def parse_terms(spec: list[dict]) -> list[RewardTerm]:
@@ -92,6 +129,7 @@ class RewardComposer:
     terms: list[RewardTerm]
     judge: Callable[[JudgeTerm, dict], Awaitable[float]] | None = None
     reward_model: Callable[[RewardModelTerm, dict], Awaitable[float]] | None = None
+    policy_check: Callable[[PolicyCheckTerm, dict], Awaitable[float]] | None = None
     timeout_s: float = 120.0
     failures: int = field(default=0, init=False)
 
@@ -120,6 +158,10 @@ class RewardComposer:
                 if self.reward_model is None:
                     raise RuntimeError(f"term {t.name!r} needs a reward-model scorer")
                 pending[t.name] = asyncio.ensure_future(self.reward_model(t, episode))
+            elif isinstance(t, PolicyCheckTerm):
+                if self.policy_check is None:
+                    raise RuntimeError(f"term {t.name!r} needs a policy-check scorer")
+                pending[t.name] = asyncio.ensure_future(self.policy_check(t, episode))
         if pending:
             done, late = await asyncio.wait(pending.values(), timeout=self.timeout_s)
             for name, fut in pending.items():
