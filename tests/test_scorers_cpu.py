@@ -1,4 +1,4 @@
-"""External reward scorers against a local HTTP server that plays the judge, the reward model and the policy-check API:
+"""External reward scorers against a local HTTP server that plays a judge model, a reward model and the policy-check API:
 verdict arithmetic, retries on 429 / 5xx with Retry-After, per-sample failure isolation, the launch probe, chunking of
 long conversations, and the composer wiring."""
 
