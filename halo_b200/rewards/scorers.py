@@ -156,11 +156,11 @@ class JudgeScorer(Scorer):
         text = content_text(reply["choices"][0]["message"].get("content"))
         found = _JSON_OBJECT.search(text)
         if not found:
-            raise ValueError(f"the judge model's reply holds no JSON object: {text[:120]!r}")
+            raise ValueError(f"the grading model's reply holds no JSON object: {text[:120]!r}")
         verdict = json.loads(found.group(0))
         score = float(verdict["score"])
         if not 0.0 <= score <= 1.0:
-            raise ValueError(f"the judge model's score {score} is outside [0, 1]")
+            raise ValueError(f"the grading model's score {score} is outside [0, 1]")
         return ScoreResult(score, {f"{self.term.name}/score": score}, detail=verdict.get("reason"), veto=bool(verdict.get("veto", False)))
 
 
