@@ -90,6 +90,7 @@ class DataArguments:
     doc_length_min: int = 256
     doc_length_max: int = 16384
     num_proc: int = 4
+    cache_dir: str = ""                     # coordinated preprocessing cache (tokenise + pack once per filesystem scope); "" = every rank for itself
 
 
 @dataclass

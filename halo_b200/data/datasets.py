@@ -123,6 +123,19 @@ def build_sft_batches(data_args, tokenizer, dp_rank: int = 0, dp_world: int = 1,
         return [synthetic_packed_batch(data_args.packed_row_length, data_args.synthetic_vocab or vocab_size,
                                        seed=data_args.shuffle_seed * 100003 + i * dp_world + dp_rank,
                                        lo=data_args.doc_length_min, hi=data_args.doc_length_max) for i in range(n)]
+    if getattr(data_args, "cache_dir", ""):
+        # tokenise and pack once per filesystem scope, under a key of the files, the tokenizer and the packing settings;
+        # the other ranks wait for the artifact and read their rows from it
+        from .pipeline import Pipeline
+
+        fmt = data_args.dataset_format
+        pipe = Pipeline(data_args.dataset_path, data_args.cache_dir)
+        pipe.map(lambda rec: tokenize_record(rec, tokenizer, fmt), "tokenize", format=fmt,
+                 tokenizer=getattr(tokenizer, "name_or_path", type(tokenizer).__name__),
+                 vocab=getattr(tokenizer, "vocab_size", 0))
+        pipe.pack(data_args.packed_row_length, getattr(data_args, "packing_strategy", "sequential"),
+                  data_args.completion_only_loss, data_args.shuffle_seed)
+        return pipe.rows(dp_rank, dp_world)
     docs = [tokenize_record(r, tokenizer, data_args.dataset_format) for r in read_records(data_args.dataset_path)]
     order = np.random.default_rng(data_args.shuffle_seed).permutation(len(docs))
     docs = [docs[i] for i in order]
