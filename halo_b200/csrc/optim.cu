@@ -268,6 +268,15 @@ __device__ __forceinline__ float bf16_spacing_256th(float pf) {
     const uint32_t e = (__float_as_uint(pf) >> 23) & 0xFFu;
     return e > 15u ? __uint_as_float((e - 15u) << 23) : 0.f;
 }
+// 1 / bf16_spacing_256th(pf): the spacing is a power of two, so its reciprocal is exact and multiplying by it gives the
+// same bits as dividing by the spacing (0 where the spacing is 0)
+__device__ __forceinline__ float bf16_inv_spacing_256th(float pf) {
+    const uint32_t e = (__float_as_uint(pf) >> 23) & 0xFFu;
+    return e > 15u ? __uint_as_float((269u - e) << 23) : 0.f;
+}
+// groups whose largest moment is below this keep their scale and store zero codes: the reciprocal of a smaller scale
+// would overflow
+constexpr float kQ8MinScale = 1e-30f;
 
 template <bool GRAD_F32>
 __global__ void __launch_bounds__(kQ8Threads)
@@ -275,6 +284,17 @@ adamw_q8_kernel(const Q8Table tab, float beta1, float beta2, float omb1, float o
                 float eps, float wd_factor, unsigned long long key_step, const float* __restrict__ grad_scale,
                 const int* __restrict__ skip) {
     if (skip != nullptr && *skip != 0) return;
+    // decode tables: (q / 127)^2 and (q / 255)^2, the same fp32 operations the per-element form did, once per block
+    __shared__ float dec_m[128], dec_v[256];
+    {
+        const float rv = (float)threadIdx.x / 255.f;
+        dec_v[threadIdx.x] = rv * rv;
+        if (threadIdx.x < 128) {
+            const float rm = (float)threadIdx.x / 127.f;
+            dec_m[threadIdx.x] = rm * rm;
+        }
+    }
+    __syncthreads();
     int lo = 0, hi = tab.n_tensors;
     while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
@@ -302,6 +322,7 @@ adamw_q8_kernel(const Q8Table tab, float beta1, float beta2, float omb1, float o
         if (!GRAD_F32) scale = __bfloat162float(__float2bfloat16_rn(scale));
     }
     const float ms = m_scale[group], vs = v_scale[group];
+    const float inv_bc2 = 1.f / bc2_sqrt;
     float w[8], m[8], s[8];
     float m_max = 0.f, s_max = 0.f;
     // eight consecutive elements per lane: one 16-byte load of the parameters (and of bf16 gradients), 8-byte loads of
@@ -359,15 +380,13 @@ adamw_q8_kernel(const Q8Table tab, float beta1, float beta2, float omb1, float o
             if (!GRAD_F32) g = __bfloat162float(__float2bfloat16_rn(g));
         }
         const float wf = pf + (float)c * bf16_spacing_256th(pf);
-        const float rm = (float)(qm < 0 ? -qm : qm) / 127.f;
-        float mf = (rm * rm) * ms;
+        float mf = dec_m[qm < 0 ? -qm : qm] * ms;
         if (qm < 0) mf = -mf;
-        const float rv = (float)qv / 255.f;
-        const float sf = (rv * rv) * vs;
+        const float sf = dec_v[qv] * vs;
         const float mn = mf * beta1 + g * omb1;
         const float vn = (sf * sf) * beta2 + (g * g) * omb2;
         const float sn = sqrtf(vn);
-        const float denom = sn / bc2_sqrt + eps;
+        const float denom = sn * inv_bc2 + eps;
         w[j] = wf * wd_factor - (step_size * mn) / denom;
         m[j] = ok ? mn : 0.f;
         s[j] = ok ? sn : 0.f;
@@ -383,6 +402,9 @@ adamw_q8_kernel(const Q8Table tab, float beta1, float beta2, float omb1, float o
         m_scale[group] = m_max;
         v_scale[group] = s_max;
     }
+    // one reciprocal per group instead of a division per element
+    const float inv_m = m_max > kQ8MinScale ? 1.f / m_max : 0.f;
+    const float inv_s = s_max > kQ8MinScale ? 1.f / s_max : 0.f;
     const long long quad = e0 >> 2;
     const Philox r0 = philox4x32_10(k0, k1, (uint32_t)quad, (uint32_t)((unsigned long long)quad >> 32));
     const Philox r1 = philox4x32_10(k0, k1, (uint32_t)(quad + 1), (uint32_t)((unsigned long long)(quad + 1) >> 32));
@@ -398,25 +420,25 @@ adamw_q8_kernel(const Q8Table tab, float beta1, float beta2, float omb1, float o
         const float uv = (float)((word >> 11) & 0x7FFu) / 2048.f;
         const float uc = (float)(word >> 22) / 1024.f;
         int qm = 0;
-        if (m_max > 0.f) {
-            const float r = sqrtf(fabsf(m[j]) / m_max) * 127.f;
+        if (inv_m > 0.f) {
+            const float r = sqrtf(fabsf(m[j]) * inv_m) * 127.f;
             qm = (int)floorf(r + um);
             qm = qm > 127 ? 127 : qm;
             if (m[j] < 0.f) qm = -qm;
         }
         int qv = 0;
-        if (s_max > 0.f && s[j] > 0.f) {
-            const float r = sqrtf(s[j] / s_max) * 255.f;
+        if (inv_s > 0.f && s[j] > 0.f) {
+            const float r = sqrtf(s[j] * inv_s) * 255.f;
             qv = (int)floorf(r + uv);
             qv = qv > 255 ? 255 : (qv < 1 ? 1 : qv);
         }
         const __nv_bfloat16 pn = __float2bfloat16_rn(w[j]);
         const float pnf = __bfloat162float(pn);
-        const float st = bf16_spacing_256th(pnf);
+        const float inv_st = bf16_inv_spacing_256th(pnf);
         int c = 0;
-        if (st > 0.f) {
+        if (inv_st > 0.f) {
             // stochastic: an update below 1/256 of the spacing still moves the weight in expectation
-            c = (int)floorf((w[j] - pnf) / st + uc);
+            c = (int)floorf((w[j] - pnf) * inv_st + uc);
             c = c > 127 ? 127 : (c < -128 ? -128 : c);
         }
         pout[j] = pn;

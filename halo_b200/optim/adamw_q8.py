@@ -64,6 +64,9 @@ def dequantize_moments(mq, vq, m_scale, v_scale):
     return m, s * s
 
 
+MIN_SCALE = 1e-30     # kQ8MinScale of the kernel
+
+
 def _sqrt32(x: torch.Tensor) -> torch.Tensor:
     """Correctly rounded fp32 square root (what ``sqrtf`` gives on the device): the CPU's vectorised fp32 ``sqrt`` is off
     by an ulp on a fraction of a percent of inputs; rounding the fp64 root to fp32 is exact."""
@@ -93,7 +96,7 @@ def adamw_q8_step_reference(p, g, corr, mq, vq, m_scale, v_scale, *, beta1, beta
     mn = m * f32(beta1) + gf * omb1
     vn = v_from_codes * f32(beta2) + (gf * gf) * omb2
     sn = _sqrt32(vn)
-    denom = sn / f32(bc2_sqrt) + f32(eps)
+    denom = sn * (f32(1.0) / f32(bc2_sqrt)) + f32(eps)
     wn = w * f32(wd_factor) - (f32(step_size) * mn) / denom
     # group maxima
     G = n_groups(n)
@@ -109,13 +112,14 @@ def adamw_q8_step_reference(p, g, corr, mq, vq, m_scale, v_scale, *, beta1, beta
     um = (rnd_t & 0x7FF).float() / 2048.0
     uv = ((rnd_t >> 11) & 0x7FF).float() / 2048.0
     uc = (rnd_t >> 22).float() / 1024.0
-    safe_mm = torch.where(mm > 0, mm, torch.ones_like(mm))
-    qm = torch.floor(_sqrt32(mn.abs() / safe_mm) * 127.0 + um).clamp(max=127.0)
-    qm = torch.where(mm > 0, qm, torch.zeros_like(qm))
+    # one reciprocal per group; groups whose largest moment is below MIN_SCALE keep their scale and store zero codes
+    inv_mm = torch.where(mm > f32(MIN_SCALE), f32(1.0) / torch.where(mm > 0, mm, torch.ones_like(mm)), torch.zeros_like(mm))
+    qm = torch.floor(_sqrt32(mn.abs() * inv_mm) * 127.0 + um).clamp(max=127.0)
+    qm = torch.where(inv_mm > 0, qm, torch.zeros_like(qm))
     qm = torch.where(mn < 0, -qm, qm)
-    safe_sm = torch.where(sm > 0, sm, torch.ones_like(sm))
-    qv = torch.floor(_sqrt32(sn / safe_sm) * 255.0 + uv).clamp(min=1.0, max=255.0)
-    qv = torch.where((sm > 0) & (sn > 0), qv, torch.zeros_like(qv))
+    inv_sm = torch.where(sm > f32(MIN_SCALE), f32(1.0) / torch.where(sm > 0, sm, torch.ones_like(sm)), torch.zeros_like(sm))
+    qv = torch.floor(_sqrt32(sn * inv_sm) * 255.0 + uv).clamp(min=1.0, max=255.0)
+    qv = torch.where((inv_sm > 0) & (sn > 0), qv, torch.zeros_like(qv))
     pn = wn.bfloat16()
     pnf = pn.float()
     st = spacing_256th(pnf)
