@@ -4,7 +4,12 @@
     python -m halo_b200.checkpoint.tools.lowp_convert export-block-fp8 <src> <dst> [--keep REGEX ...]
     python -m halo_b200.checkpoint.tools.lowp_convert export <src> <dst> --format mxfp8|mxfp4|nvfp4 [--keep REGEX ...]
     python -m halo_b200.checkpoint.tools.lowp_convert dequant <src> <dst>
+    python -m halo_b200.checkpoint.tools.lowp_convert dequant-static-fp8 <src> <dst>
+    python -m halo_b200.checkpoint.tools.lowp_convert dequant-mxfp4-experts <src> <dst>
 
+``dequant-static-fp8`` reads releases with one static scale per matrix (or per expert of a bank);
+``dequant-mxfp4-experts`` unpacks expert banks stored as ``<bank>_blocks`` / ``<bank>_scales`` (packed e2m1 codes with
+one power-of-two scale per 32 values, the gpt-oss hub layout) into the bf16 banks the family's loader reads.
 ``dequant-block-fp8`` turns a served-weights release in 128 x 128 block FP8 (every ``<name>.weight`` in
 ``float8_e4m3fn`` beside a ``<name>.weight_scale_inv`` of one fp32 factor per block) into bf16 - the form training
 starts from. ``export`` writes the matrices of a bf16 checkpoint in a block-scaled format: ``<name>.weight`` holds the
@@ -60,6 +65,107 @@ def dequant_block_fp8(src: str, dst: str) -> int:
         cfg["torch_dtype"] = "bfloat16"
         json.dump(cfg, open(cfg_path, "w"), indent=2)
     return n
+
+
+def _as_plain_bf16_config(dst: str) -> None:
+    cfg_path = os.path.join(dst, "config.json")
+    if os.path.isfile(cfg_path):
+        cfg = json.load(open(cfg_path))
+        cfg.pop("quantization_config", None)
+        cfg["torch_dtype"] = "bfloat16"
+        json.dump(cfg, open(cfg_path, "w"), indent=2)
+
+
+def _reject_in_place(src: str, dst: str) -> None:
+    if os.path.realpath(src) == os.path.realpath(dst):
+        raise ValueError("the output directory is the input: the writer would delete the shards it is reading")
+
+
+def dequant_static_fp8(src: str, dst: str) -> int:
+    """Releases with STATIC scales: every ``<name>.weight`` in ``float8_e4m3fn`` beside a ``<name>.weight_scale`` that is
+    one factor for the matrix, or one per expert for a 3-D bank ``[E, ...]``. ``weight = fp8 * scale`` in fp32, rounded
+    once to bf16. Activation scales (``input_scale`` / ``activation_scale``), which only a quantised forward reads, are
+    dropped; floats that were never quantised land as bf16. A source without a single fp8 tensor is refused (the result
+    would be a plain copy reported as a conversion)."""
+    _reject_in_place(src, dst)
+    idx = CheckpointIndex(src)
+    names = sorted(idx.weight_map)
+    fp8 = [n for n in names if n.endswith("weight") and n + "_scale" in idx]
+    if not fp8:
+        raise ValueError(f"{src!r} holds no tensor with a static weight_scale beside it: nothing to dequantise")
+    writer = StreamingShardWriter(dst)
+    n_done = 0
+    for name in names:
+        if name.endswith(("weight_scale", "input_scale", "activation_scale")):
+            continue
+        t = idx.get(name)
+        if name + "_scale" in idx:
+            if t.dtype != torch.float8_e4m3fn:
+                raise ValueError(f"{name} has a weight_scale but is {t.dtype}, not float8_e4m3fn")
+            s = idx.get(name + "_scale").float().reshape(-1)
+            if s.numel() == 1:
+                full = s.reshape(())
+            elif t.dim() == 3 and s.numel() == t.shape[0]:
+                full = s.reshape(-1, 1, 1)
+            else:
+                raise ValueError(f"{name}_scale has {s.numel()} entries: expected one for the matrix"
+                                 + (f" or one per expert ({t.shape[0]})" if t.dim() == 3 else ""))
+            t = (t.float() * full).to(torch.bfloat16)
+            n_done += 1
+        elif t.is_floating_point() and t.dtype != torch.bfloat16:
+            t = t.to(torch.bfloat16)
+        writer.add(name, t)
+    writer.finish()
+    copy_side_files(src, dst)
+    _as_plain_bf16_config(dst)
+    return n_done
+
+
+# the sixteen values of a 4-bit e2m1 code (sign, two exponent bits, one mantissa bit)
+_E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0)
+
+
+def unpack_mxfp4_blocks(blocks: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """``blocks`` uint8 ``[..., G, B/2]`` (two e2m1 codes per byte, the low nibble first) and ``scales`` uint8
+    ``[..., G]`` (a power-of-two exponent with bias 127 per block of B values) -> fp32 ``[..., G * B]``."""
+    if blocks.dtype != torch.uint8 or scales.dtype != torch.uint8 or blocks.shape[:-1] != scales.shape:
+        raise ValueError(f"packed blocks {tuple(blocks.shape)} {blocks.dtype} do not match scales {tuple(scales.shape)} {scales.dtype}")
+    lut = torch.tensor(_E2M1, dtype=torch.float32)
+    lo, hi = lut[(blocks & 0x0F).long()], lut[(blocks >> 4).long()]
+    vals = torch.stack([lo, hi], dim=-1).reshape(*blocks.shape[:-1], blocks.shape[-1] * 2)
+    vals = torch.ldexp(vals, (scales.to(torch.int32) - 127)[..., None])
+    return vals.reshape(*scales.shape[:-1], scales.shape[-1] * blocks.shape[-1] * 2)
+
+
+def dequant_mxfp4_experts(src: str, dst: str) -> int:
+    """Releases whose expert banks are packed MXFP4 (the gpt-oss hub layout): ``<bank>_blocks`` and ``<bank>_scales``
+    become ``<bank>`` in bf16. The packed form stores a bank as ``[E, out, G, 16]`` (the reduction axis blocked last);
+    the bf16 form the family's loaders read is ``[E, in, out]``, so the unpacked bank is transposed. Everything else is
+    copied as it is."""
+    _reject_in_place(src, dst)
+    idx = CheckpointIndex(src)
+    names = sorted(idx.weight_map)
+    packed = [n[:-len("_blocks")] for n in names if n.endswith("_blocks")]
+    if not packed:
+        raise ValueError(f"{src!r} holds no '<name>_blocks' tensor: nothing to dequantise")
+    writer = StreamingShardWriter(dst)
+    for name in names:
+        if name.endswith("_scales") and name[:-len("_scales")] in packed:
+            continue
+        if name.endswith("_blocks"):
+            base = name[:-len("_blocks")]
+            if base + "_scales" not in idx:
+                raise KeyError(f"{name} has no {base}_scales beside it")
+            full = unpack_mxfp4_blocks(idx.get(name), idx.get(base + "_scales"))
+            if full.dim() == 3:
+                full = full.transpose(1, 2)
+            writer.add(base, full.to(torch.bfloat16).contiguous())
+            continue
+        writer.add(name, idx.get(name))
+    writer.finish()
+    copy_side_files(src, dst)
+    _as_plain_bf16_config(dst)
+    return len(packed)
 
 
 def export_block_fp8(src: str, dst: str, keep: list[str] | None = None) -> int:
@@ -166,7 +272,7 @@ def dequant(src: str, dst: str) -> int:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.splitlines()[0])
     sub = ap.add_subparsers(dest="cmd", required=True)
-    for cmd in ("dequant-block-fp8", "dequant"):
+    for cmd in ("dequant-block-fp8", "dequant", "dequant-static-fp8", "dequant-mxfp4-experts"):
         p = sub.add_parser(cmd)
         p.add_argument("src")
         p.add_argument("dst")
@@ -185,6 +291,10 @@ def main(argv=None) -> int:
         n = dequant_block_fp8(args.src, args.dst)
     elif args.cmd == "dequant":
         n = dequant(args.src, args.dst)
+    elif args.cmd == "dequant-static-fp8":
+        n = dequant_static_fp8(args.src, args.dst)
+    elif args.cmd == "dequant-mxfp4-experts":
+        n = dequant_mxfp4_experts(args.src, args.dst)
     elif args.cmd == "export-block-fp8":
         n = export_block_fp8(args.src, args.dst, args.keep)
     else:

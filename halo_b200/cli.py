@@ -43,6 +43,7 @@ TOOLS = {
     "merge-adapter": "halo_b200.checkpoint.tools.merge_adapter",
     "lowp-convert": "halo_b200.checkpoint.tools.lowp_convert",
     "merge-pp-stages": "halo_b200.checkpoint.tools.merge_pp_stages",
+    "reattach-vision": "halo_b200.checkpoint.tools.reattach_vision",
     "weight-push-bench": "benchmarks.weight_push",
     "bench": "bench",
 }

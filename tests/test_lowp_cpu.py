@@ -191,3 +191,90 @@ def test_quantisation_aware_training_rounds_every_product():
     assert abs(coarse(b.input_ids, b.position_ids, b.cu_seqlens, b.labels).item() - want) > abs(loss.item() - want)
     with pytest.raises(ValueError, match="no multiples"):
         apply_lowp_compute(build_model(dataclasses.replace(cfg, moe_intermediate_size=80), device="cpu", seed=0), "mxfp8")
+
+
+def test_static_fp8_and_packed_mxfp4_releases(tmp_path):
+    """Releases with static per-matrix / per-expert FP8 scales, and with expert banks packed as MXFP4 blocks (the gpt-oss
+    hub layout): both come back as plain bf16 checkpoints, the second one loadable by the family's loader."""
+    import json
+
+    import pytest
+    from safetensors.torch import load_file, save_file
+
+    from halo_b200.checkpoint.load import CheckpointIndex, from_pretrained
+    from halo_b200.checkpoint.save import save_model
+    from halo_b200.checkpoint.tools import lowp_convert
+    from halo_b200.models.qwen3 import build_model
+    from tests.test_families_cpu import family_config
+
+    torch.manual_seed(0)
+    # --- static scales
+    w = torch.randn(64, 48)
+    bank = torch.randn(3, 16, 24)
+    s_w, s_bank = torch.tensor(0.02), torch.tensor([0.01, 0.03, 0.05])
+    src = tmp_path / "static"
+    src.mkdir()
+    save_file({"model.layers.0.self_attn.q_proj.weight": (w / s_w).to(torch.float8_e4m3fn),
+               "model.layers.0.self_attn.q_proj.weight_scale": s_w.reshape(1),
+               "model.layers.0.self_attn.q_proj.input_scale": torch.tensor([0.5]),
+               "model.layers.0.mlp.experts.weight": (bank / s_bank[:, None, None]).to(torch.float8_e4m3fn),
+               "model.layers.0.mlp.experts.weight_scale": s_bank,
+               "model.norm.weight": torch.ones(48, dtype=torch.float32)}, str(src / "model.safetensors"))
+    (src / "config.json").write_text(json.dumps({"model_type": "mistral", "quantization_config": {"quant_method": "fp8"}}))
+    assert lowp_convert.main(["dequant-static-fp8", str(src), str(tmp_path / "static_bf16")]) == 0
+    out = CheckpointIndex(str(tmp_path / "static_bf16"))
+    assert sorted(out.weight_map) == ["model.layers.0.mlp.experts.weight", "model.layers.0.self_attn.q_proj.weight", "model.norm.weight"]
+    got = out.get("model.layers.0.self_attn.q_proj.weight")
+    assert got.dtype == torch.bfloat16 and (got.float() - w).abs().max() < 0.08 * w.abs().max()
+    got_bank = out.get("model.layers.0.mlp.experts.weight")
+    assert torch.equal(got_bank, ((bank / s_bank[:, None, None]).to(torch.float8_e4m3fn).float() * s_bank[:, None, None]).bfloat16())
+    assert out.get("model.norm.weight").dtype == torch.bfloat16
+    assert "quantization_config" not in json.load(open(tmp_path / "static_bf16" / "config.json"))
+    with pytest.raises(ValueError, match="output directory is the input"):
+        lowp_convert.dequant_static_fp8(str(src), str(src))
+    with pytest.raises(ValueError, match="nothing to dequantise"):
+        lowp_convert.dequant_static_fp8(str(tmp_path / "static_bf16"), str(tmp_path / "again"))
+
+    # --- packed MXFP4: codes and exponents chosen at random, so the expected values are exact
+    codes = torch.randint(0, 16, (2, 5, 3, 32))
+    exps = torch.randint(120, 131, (2, 5, 3), dtype=torch.int32)
+    lut = torch.tensor(lowp_convert._E2M1)
+    want = (lut[codes] * torch.pow(2.0, (exps - 127).float())[..., None]).reshape(2, 5, 96)
+    blocks = (codes[..., 0::2] | (codes[..., 1::2] << 4)).to(torch.uint8)             # low nibble first
+    assert torch.equal(lowp_convert.unpack_mxfp4_blocks(blocks, exps.to(torch.uint8)), want)
+
+    # a gpt-oss checkpoint whose banks are packed that way loads as the bf16 model it encodes
+    cfg = family_config("gpt_oss")
+    model = build_model(cfg, device="cpu", seed=2)
+    ckpt = tmp_path / "gpt_oss_bf16"
+    save_model(model, str(ckpt), save_dtype=torch.bfloat16)
+    shard = [f for f in os.listdir(ckpt) if f.endswith(".safetensors")]
+    assert len(shard) == 1
+    tensors = load_file(str(ckpt / shard[0]))
+    packed, exact = {}, {}
+    for name, t in tensors.items():
+        if name.endswith(("experts.gate_up_proj", "experts.down_proj")):
+            E, n_in, n_out = t.shape                                                      # the hub's bf16 banks are [E, in, out]
+            c = torch.randint(0, 16, (E, n_out, n_in // 32, 32))
+            e = torch.randint(118, 126, (E, n_out, n_in // 32), dtype=torch.int32)
+            vals = (lut[c] * torch.pow(2.0, (e - 127).float())[..., None]).reshape(E, n_out, n_in)
+            packed[name + "_blocks"] = (c[..., 0::2] | (c[..., 1::2] << 4)).to(torch.uint8)
+            packed[name + "_scales"] = e.to(torch.uint8)
+            exact[name] = vals.transpose(1, 2).contiguous().bfloat16()
+        else:
+            packed[name] = t
+            exact[name] = t
+    src4 = tmp_path / "gpt_oss_mxfp4"
+    src4.mkdir()
+    save_file(packed, str(src4 / "model.safetensors"))
+    cfg_json = json.load(open(ckpt / "config.json"))
+    cfg_json["quantization_config"] = {"quant_method": "mxfp4"}
+    (src4 / "config.json").write_text(json.dumps(cfg_json))
+    assert lowp_convert.main(["dequant-mxfp4-experts", str(src4), str(tmp_path / "gpt_oss_back")]) == 0
+    back = CheckpointIndex(str(tmp_path / "gpt_oss_back"))
+    assert sorted(back.weight_map) == sorted(exact)
+    for name, t in exact.items():
+        assert torch.equal(back.get(name), t), name
+    loaded = from_pretrained(str(tmp_path / "gpt_oss_back"), device="cpu")
+    bank0 = loaded.layers[0].mlp.experts_down
+    assert torch.isfinite(bank0).all() and bank0.shape == model.layers[0].mlp.experts_down.shape

@@ -187,3 +187,59 @@ def test_compressed_tensors_block_names_the_quantised_modules(tmp_path):
             module = name[:-len(".weight_scale")]
             assert any(p.match(module) for p in pats) and module not in qc["ignore"], module
     assert all("layers.0." in m for m in qc["ignore"]) and qc["ignore"]
+
+
+def test_reattach_vision(tmp_path):
+    """A trained text tower goes back into its multimodal wrapper: trained tensors under the wrapper's names, the vision
+    tower streamed back, the composite config regrafted; mismatches are refused by name."""
+    import json
+
+    import pytest
+    import torch
+    from safetensors.torch import save_file
+
+    from halo_b200.checkpoint.load import CheckpointIndex
+    from halo_b200.checkpoint.tools import reattach_vision as R
+
+    torch.manual_seed(0)
+    base = {"model.language_model.embed_tokens.weight": torch.randn(10, 4), "model.language_model.layers.0.mlp.down_proj.weight": torch.randn(4, 8),
+            "model.language_model.norm.weight": torch.ones(4), "lm_head.weight": torch.randn(10, 4),
+            "model.visual.patch_embed.weight": torch.randn(6, 3), "model.multi_modal_projector.linear.weight": torch.randn(4, 6)}
+    trained = {"model.embed_tokens.weight": torch.randn(10, 4), "model.layers.0.mlp.down_proj.weight": torch.randn(4, 8),
+               "model.norm.weight": torch.full((4,), 2.0), "lm_head.weight": torch.randn(10, 4),
+               "model.mtp.proj.weight": torch.randn(4, 8)}
+    for name, tensors, cfg in (("base", base, {"model_type": "wrapper_vl", "vision_config": {"depth": 2}, "text_config": {"model_type": "wrapper_text", "hidden_size": 4}}),
+                               ("export", trained, {"model_type": "qwen3", "hidden_size": 4, "architectures": ["Qwen3ForCausalLM"], "rope_theta": 5.0})):
+        (tmp_path / name).mkdir()
+        save_file(tensors, str(tmp_path / name / "model.safetensors"))
+        (tmp_path / name / "config.json").write_text(json.dumps(cfg))
+    (tmp_path / "base" / "preprocessor_config.json").write_text("{}")
+    assert R.main([str(tmp_path / "export"), str(tmp_path / "base"), str(tmp_path / "out")]) == 0
+    out = CheckpointIndex(str(tmp_path / "out"))
+    assert sorted(out.weight_map) == sorted(list(base) + ["model.language_model.mtp.proj.weight"])
+    assert torch.equal(out.get("model.language_model.norm.weight"), trained["model.norm.weight"])
+    assert torch.equal(out.get("lm_head.weight"), trained["lm_head.weight"])
+    assert torch.equal(out.get("model.visual.patch_embed.weight"), base["model.visual.patch_embed.weight"])
+    assert torch.equal(out.get("model.language_model.mtp.proj.weight"), trained["model.mtp.proj.weight"])
+    cfg = json.load(open(tmp_path / "out" / "config.json"))
+    assert cfg["model_type"] == "wrapper_vl" and cfg["vision_config"] == {"depth": 2}
+    assert cfg["text_config"] == {"model_type": "wrapper_text", "hidden_size": 4, "rope_theta": 5.0}
+    assert (tmp_path / "out" / "preprocessor_config.json").is_file()
+    # refusals
+    with pytest.raises(ValueError, match="not text-only"):
+        R.plan(list(trained) + ["model.visual.x"], list(base))
+    with pytest.raises(ValueError, match="not a multimodal checkpoint"):
+        R.plan(list(trained), [n for n in base if "visual" not in n and "projector" not in n])
+    with pytest.raises(ValueError, match="names no tensor of the base's text tower"):
+        R.plan(list(trained) + ["model.layers.1.mlp.down_proj.weight"], list(base))
+    with pytest.raises(ValueError, match="lacks 1 tensors"):
+        R.plan([n for n in trained if "norm" not in n], list(base))
+    wrong = dict(trained)
+    wrong["model.layers.0.mlp.down_proj.weight"] = torch.randn(4, 16)
+    (tmp_path / "wrong").mkdir()
+    save_file(wrong, str(tmp_path / "wrong" / "model.safetensors"))
+    (tmp_path / "wrong" / "config.json").write_text("{}")
+    with pytest.raises(ValueError, match="a base of another size"):
+        R.reattach(str(tmp_path / "wrong"), str(tmp_path / "base"), str(tmp_path / "out2"))
+    with pytest.raises(ValueError, match="one of the inputs"):
+        R.reattach(str(tmp_path / "export"), str(tmp_path / "base"), str(tmp_path / "base"))
