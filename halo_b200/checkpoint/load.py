@@ -81,10 +81,20 @@ def load_model_weights(model, directory: str, strict: bool = True) -> dict:
         if whole is not None:
             # stored as one transformed tensor (transposed, gate / up interleaved): undone on the host
             hub, to_runtime = whole
-            if hub not in index:
+            if hub in index:
+                stored = index.get(hub)
+            elif hub + "_blocks" in index and hub + "_scales" in index:
+                # a release with packed MXFP4 banks ([E, out, G, 16] codes, one power-of-two scale per 32 values): unpacked
+                # to the bf16 form [E, in, out] the release's own bf16 twin stores
+                from halo_b200.ops.lowp import unpack_mxfp4_blocks
+
+                stored = unpack_mxfp4_blocks(index.get(hub + "_blocks"), index.get(hub + "_scales")).transpose(1, 2)
+            else:
                 missing.append(hub)
                 continue
-            t = to_runtime(index.get(hub))
+            t = to_runtime(stored)
+            if is_expert and t.shape[0] != p.shape[0]:
+                t = t[offset:offset + p.shape[0]]          # an expert-parallel rank keeps its experts of the whole bank
             if tuple(t.shape) != tuple(p.shape):
                 raise ValueError(f"{hub}: checkpoint shape {tuple(t.shape)} does not fit {tuple(p.shape)}")
             p.copy_(t.to(p.dtype))

@@ -19,7 +19,7 @@ import torch.distributed as dist
 from halo_b200.runtime.consensus import DeferredRankFailure
 
 from .atomic import atomic_write_json, remove_stale_staged
-from .hub_layout import runtime_to_hub
+from .hub_layout import runtime_to_hub, whole_bank_source
 from .writing import StreamingShardWriter
 
 COMPLETE_MARKER = "trainer_state.json"
@@ -126,6 +126,9 @@ def save_model(model, directory: str, is_writer: bool | None = None, save_dtype:
         if not getattr(p, "is_expert", False):
             continue
         if sharded_experts and n_ep > 1:
+            if whole_bank_source(name, cfg, first_layer) is not None:
+                raise NotImplementedError(f"{name}: this family stores an expert bank as ONE tensor, which per-rank shards "
+                                          "cannot hold under one name; save unsharded (save_sharded_ep: false)")
             with guard.catch():
                 for hub, t in runtime_to_hub(name, saved_tensor(name, p), cfg, first_layer, ep_rank * p.shape[0]).items():
                     writer.add(hub, t)

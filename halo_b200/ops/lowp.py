@@ -188,3 +188,19 @@ class WeightRoundTripCache:
 
     def clear(self) -> None:
         self._entries.clear()
+
+
+# the sixteen values of a 4-bit e2m1 code (sign, two exponent bits, one mantissa bit)
+E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0)
+
+
+def unpack_mxfp4_blocks(blocks: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """``blocks`` uint8 ``[..., G, B/2]`` (two e2m1 codes per byte, the low nibble first) and ``scales`` uint8
+    ``[..., G]`` (a power-of-two exponent with bias 127 per block of B values) -> fp32 ``[..., G * B]``."""
+    if blocks.dtype != torch.uint8 or scales.dtype != torch.uint8 or blocks.shape[:-1] != scales.shape:
+        raise ValueError(f"packed blocks {tuple(blocks.shape)} {blocks.dtype} do not match scales {tuple(scales.shape)} {scales.dtype}")
+    lut = torch.tensor(E2M1_VALUES, dtype=torch.float32)
+    lo, hi = lut[(blocks & 0x0F).long()], lut[(blocks >> 4).long()]
+    vals = torch.stack([lo, hi], dim=-1).reshape(*blocks.shape[:-1], blocks.shape[-1] * 2)
+    vals = torch.ldexp(vals, (scales.to(torch.int32) - 127)[..., None])
+    return vals.reshape(*scales.shape[:-1], scales.shape[-1] * blocks.shape[-1] * 2)

@@ -278,3 +278,20 @@ def test_static_fp8_and_packed_mxfp4_releases(tmp_path):
     loaded = from_pretrained(str(tmp_path / "gpt_oss_back"), device="cpu")
     bank0 = loaded.layers[0].mlp.experts_down
     assert torch.isfinite(bank0).all() and bank0.shape == model.layers[0].mlp.experts_down.shape
+    # the packed release also loads as it is (the loader unpacks the banks), to the same weights
+    direct = from_pretrained(str(src4), device="cpu")
+    for (n, a_), (_, b_) in zip(loaded.named_parameters(), direct.named_parameters()):
+        assert torch.equal(a_, b_), n
+    # an expert-parallel rank keeps its experts of a bank stored whole
+    from halo_b200.checkpoint.load import load_model_weights
+    from halo_b200.models.qwen3 import Qwen3Model
+
+    class _SecondOfTwo:
+        n_ranks, rank = 2, 1
+
+    half = Qwen3Model(cfg, dtype=torch.float32, device="cpu", transport=_SecondOfTwo())
+    load_model_weights(half, str(tmp_path / "gpt_oss_back"))
+    n_local = cfg.num_experts // 2
+    assert half.layers[0].mlp.experts_gate_up_bias.shape[0] == n_local
+    assert torch.equal(half.layers[1].mlp.experts_down, loaded.layers[1].mlp.experts_down[n_local:])
+    assert torch.equal(half.layers[0].mlp.experts_gate_up_bias, loaded.layers[0].mlp.experts_gate_up_bias[n_local:])
