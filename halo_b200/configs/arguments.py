@@ -211,6 +211,8 @@ class RewardArguments:
 class EmbeddingArguments:
     temperature: float = 0.05
     pairs_per_row: int = 16
+    pooling: Literal["last_token", "mean"] = "last_token"
+    sentence_transformers_layout: bool = True      # write modules.json / 1_Pooling beside the final checkpoint
 
 
 @dataclass

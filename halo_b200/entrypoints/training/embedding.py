@@ -18,9 +18,17 @@ def main(argv=None):
     runtime = getattr(model, "parallel_runtime", runtime)
     batches = build_embedding_batches(data_args, load_tokenizer(model_args), pc.data_parallel_rank, pc.data_parallel_size,
                                       model.cfg.vocab_size, emb_args.pairs_per_row)
-    trainer = EmbeddingTrainer(model, train_args, batches, temperature=emb_args.temperature, device=device, parallel=runtime,
-                               parallelism_fingerprint=pc.fingerprint())
-    return run_trainer(trainer, train_args)
+    trainer = EmbeddingTrainer(model, train_args, batches, temperature=emb_args.temperature, pooling=emb_args.pooling,
+                               device=device, parallel=runtime, parallelism_fingerprint=pc.fingerprint())
+    result = run_trainer(trainer, train_args)
+    if emb_args.sentence_transformers_layout and trainer.is_main:
+        import os
+
+        from halo_b200.trainers.reward import write_sentence_transformers_layout
+
+        write_sentence_transformers_layout(os.path.join(train_args.output_dir, "final"), model.cfg.hidden_size, emb_args.pooling,
+                                           data_args.packed_row_length)
+    return result
 
 
 if __name__ == "__main__":

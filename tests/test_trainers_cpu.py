@@ -309,6 +309,38 @@ def test_classification_and_embedding_entry_points(tmp_path, method, extra, arch
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert "step 3 " in r.stdout + r.stderr
     assert json.load(open(tmp_path / "run" / "final" / "config.json"))["architectures"] == [arch]
+    if method == "embedding":
+        # the pipeline description a sentence-transformers loader reads, and the embedding metrics in the log
+        final = tmp_path / "run" / "final"
+        modules = json.load(open(final / "modules.json"))
+        assert [m["type"].rsplit(".", 1)[1] for m in modules] == ["Transformer", "Pooling", "Normalize"] and modules[0]["path"] == ""
+        pool = json.load(open(final / "1_Pooling" / "config.json"))
+        assert pool["pooling_mode_lasttoken"] and not pool["pooling_mode_mean_tokens"] and pool["word_embedding_dimension"] > 0
+        assert json.load(open(final / "sentence_bert_config.json"))["max_seq_length"] == 256
+        assert "embed/mrr" in r.stdout + r.stderr and "embed/cos_sim" in r.stdout + r.stderr
+
+
+def test_embedding_pooling_and_metrics():
+    from halo_b200.data.packing import synthetic_packed_batch
+    from halo_b200.models.config import tiny_moe_config
+    from halo_b200.models.qwen3 import build_model
+    from halo_b200.trainers.reward import embedding_metrics, last_token_states, pooled_states
+
+    model = build_model(tiny_moe_config(), device="cpu", seed=0, gradient_checkpointing=False)
+    batch = synthetic_packed_batch(96, model.cfg.vocab_size, seed=1, lo=10, hi=30)
+    h = model.hidden_states(batch.input_ids, batch.position_ids, batch.cu_seqlens)
+    mean = pooled_states(model, batch, "mean")
+    cu = [int(x) for x in batch.cu_seqlens]
+    for i, (a, b) in enumerate(zip(cu[:-1], cu[1:])):
+        assert torch.allclose(mean[i], h[a:b].float().mean(0), atol=1e-5)
+    assert torch.equal(pooled_states(model, batch, "last_token"), last_token_states(model, batch))
+    with pytest.raises(ValueError):
+        pooled_states(model, batch, "cls")
+    q = torch.nn.functional.normalize(torch.eye(4) + 0.01, dim=-1)
+    perfect = embedding_metrics(q, q.clone(), torch.full((8,), 3.0))
+    assert perfect["embed/mrr"] == 1.0 and perfect["embed/cos_sim"] > 0.999 and perfect["embed/norm"] == 3.0
+    shuffled = embedding_metrics(q, q[[1, 0, 3, 2]], torch.ones(8))
+    assert 0.25 <= shuffled["embed/mrr"] <= 0.5 and shuffled["embed/std"] > 0            # every positive is outranked by the query's twin
 
 
 # ---- SDPG: GRPO + on-policy self-distillation from a privileged (hinted) pass of the same policy ----------------------
