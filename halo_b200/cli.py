@@ -33,6 +33,7 @@ TOOLS = {
     "kernel-bench": "benchmarks.kernels",
     "nvlink-health": "halo_b200.diagnostics.nvlink_health",
     "trace-report": "halo_b200.diagnostics.trace_report",
+    "stack-dump": "halo_b200.diagnostics.stack_dump",
     "convert-recipe": "halo_b200.configs.convert_recipe",
     "prepare-dataset": "halo_b200.data.preprocessed",
     "deduplicate": "halo_b200.data.deduplication",

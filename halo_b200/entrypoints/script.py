@@ -69,6 +69,13 @@ def init_training_script(device, model_args, train_args, par_args, world_size: i
         filesystem.verify_job_directories(train_args.output_dir)
     elif hlog.is_main_process():
         os.makedirs(train_args.output_dir, exist_ok=True)
+    try:
+        # `cli run stack-dump <output_dir>` then shows where every rank of a running (or hung) job stands
+        from halo_b200.diagnostics import stack_dump
+
+        stack_dump.install(train_args.output_dir)
+    except (OSError, ValueError, RuntimeError) as exc:     # a read-only directory, a non-main thread: diagnostics only
+        log.warning("stack-dump handler not installed: %s", exc)
     return pc
 
 
