@@ -115,6 +115,21 @@ def cases(small: bool):
 
     out["moe_experts_fwd_bwd"] = (moe_fb, 3 * expert_flops, 0.0)
 
+    # experts with bias vectors around a clamped GLU (the gpt-oss form): the same grouped products with the bias /
+    # activation row kernels between them (separate-kernel pipeline)
+    from halo_b200.ops.biased_glu_experts import GLU_ALPHA
+
+    b_gu, b_dn = bf16(E, 2 * F).requires_grad_(True), bf16(E, H).requires_grad_(True)
+    out["moe_glu_experts_fwd"] = (lambda: moe_ops.moe_experts(x, idx, w, w_gu, w_dn, glu=(b_gu.detach(), b_dn.detach(), 7.0, GLU_ALPHA)),
+                                  expert_flops, 0.0)
+
+    def moe_glu_fb():
+        y = moe_ops.moe_experts(xg, idx, w, wg, wd, glu=(b_gu, b_dn, 7.0, GLU_ALPHA))
+        y.backward(dy)
+        xg.grad = wg.grad = wd.grad = b_gu.grad = b_dn.grad = None
+
+    out["moe_glu_experts_fwd_bwd"] = (moe_glu_fb, 3 * expert_flops, 0.0)
+
     # ---- attention ----------------------------------------------------------------------------
     for dist_name in ("chat", "loguniform"):
         lens = sample_doc_lengths(T, np.random.default_rng(0), dist_name)
