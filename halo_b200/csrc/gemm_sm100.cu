@@ -270,7 +270,7 @@ __device__ __forceinline__ bool fetch_work_pair(const GemmParams& p, int idx, in
     w.c_row = tm * 256;
     w.m_valid = min(256, p.M - tm * 256);
     w.pad0 = w.pad1 = 0;
-    if (p.epi == kEpiSwiglu) {
+    if (epi_is_glu(p.epi)) {
         w.b_mn = tn * 128;
         w.b_mn2 = p.swiglu_f + tn * 128;
         w.c_col = tn * 128;
@@ -691,7 +691,7 @@ int halo_gemm_bf16(const void* A, const void* B, void* C, void* aux, int M, int 
     p.C = C; p.aux = aux; p.ldc = ldc; p.ld_aux = ld_aux; p.epi = epi; p.alpha = alpha;
     p.M = M; p.N = N; p.K = K;
     p.tiles_m = (M + kBlockM - 1) / kBlockM;
-    if (epi == kEpiSwiglu) {
+    if (epi_is_glu(epi)) {
         if (N % 2) return -20;
         p.swiglu_f = N / 2;
         p.tiles_n = (p.swiglu_f + 127) / 128;
@@ -702,7 +702,7 @@ int halo_gemm_bf16(const void* A, const void* B, void* C, void* aux, int M, int 
     p.list = nullptr; p.list_count = nullptr; p.status = status;
     // measured: the pair kernel wins on mainloop-bound products with narrow outputs; wide outputs (the vocabulary
     // head, large square products), short reductions and the SwiGLU epilogue run faster on the single-CTA kernel
-    if (use_pair() && (g_use_pair == 2 || (p.tiles_n <= 24 && K >= 1536 && epi != kEpiSwiglu))) {
+    if (use_pair() && (g_use_pair == 2 || (p.tiles_n <= 24 && K >= 1536 && !epi_is_glu(epi)))) {
         const long long pair_tiles = (long long)((M + 255) / 256) * p.tiles_n;
         const int max_pairs = num_sms() / 2;
         return dispatch_gemm_pair(a_mn_major, b_mn_major, ta, tb, p, (int)(pair_tiles < max_pairs ? pair_tiles : max_pairs),
@@ -764,6 +764,29 @@ int halo_gemm_bf16_list(const void* A, long long a_rows, long long a_cols, long 
     // `pair`: the list holds 256-row tiles planned for the CTA-pair kernel (see halo_plan_grouped_*)
     if (pair) return dispatch_gemm_pair(a_mn_major, b_mn_major, ta, tb, p, num_sms() / 2, (cudaStream_t)stream);
     return dispatch_gemm(a_mn_major, b_mn_major, ta, tb, p, num_sms(), (cudaStream_t)stream);
+}
+
+// As halo_gemm_bf16_list with the clamped-GLU epilogue: `bias` is the expert bias bank [E, 2F] in bf16, read through
+// the tile's B coordinates (the list must have been planned with swiglu_f = F and b_mn_stride = 2F, so that a tile's
+// gate / up column origins are also its origins in the bias bank).
+int halo_gemm_bf16_list_glu(const void* A, long long a_rows, long long a_cols, long long lda,
+                            const void* B, long long b_rows, long long b_cols, long long ldb, void* C,
+                            void* aux, long long ldc, long long ld_aux, int swiglu_f, const void* bias, float limit,
+                            float glu_alpha, const void* list, const int* list_count, int* status, void* stream) {
+    if (!bias || swiglu_f <= 0 || swiglu_f % 8) return -1;
+    CUtensorMap ta, tb;
+    int rc = make_tmap_bf16(&ta, A, a_rows, a_cols, lda, 128);
+    if (rc) return rc;
+    rc = make_tmap_bf16(&tb, B, b_rows, b_cols, ldb, 128);
+    if (rc) return rc * 10;
+    GemmParams p{};
+    p.C = C; p.aux = aux; p.ldc = ldc; p.ld_aux = ld_aux; p.epi = kEpiClampedGlu; p.alpha = 1.f;
+    p.swiglu_f = swiglu_f;
+    p.list = reinterpret_cast<const GemmWork*>(list);
+    p.list_count = list_count;
+    p.status = status;
+    p.glu_bias = bias; p.glu_limit = limit; p.glu_alpha = glu_alpha;
+    return dispatch_gemm(0, 0, ta, tb, p, num_sms(), (cudaStream_t)stream);
 }
 
 int halo_plan_grouped_m(const int* seg_start, const int* seg_rows, int num_experts, int n_cols,

@@ -23,7 +23,13 @@ enum : int {
     kEpiAccumBf16 = 2,
     kEpiAccumF32 = 3,
     kEpiSwiglu = 4,  // columns [0,128) are gate, [128,256) are up: C = silu(gate) * up
+    // as kEpiSwiglu, for experts with bias vectors around a clamped GLU: the tile's B coordinates index the bias bank
+    // (one bias per row of B), pre = acc + bias, gate = min(pre_gate, limit), up = clamp(pre_up, -limit, limit),
+    // C = (up + 1) * gate * sigmoid(glu_alpha * gate); aux receives the biased pre-activations
+    kEpiClampedGlu = 5,
 };
+
+__host__ __device__ __forceinline__ bool epi_is_glu(int epi) { return epi == kEpiSwiglu || epi == kEpiClampedGlu; }
 
 struct GemmWork {
     int a_mn;     // A coordinate along M of the tile's first row
@@ -59,6 +65,9 @@ struct GemmParams {
     // NVLink stores of the early tiles drain while the later tiles are still being multiplied.
     void* c_peers[8];
     int rs_ranks, rs_rank, rs_rows;
+    // kEpiClampedGlu: bias bank as one bf16 vector indexed like the rows of B, the clamp and the gate's slope
+    const void* glu_bias;
+    float glu_limit, glu_alpha;
 };
 
 __device__ __forceinline__ bool fetch_work(const GemmParams& p, int idx, int total, GemmWork& w) {
@@ -97,7 +106,7 @@ __device__ __forceinline__ bool fetch_work(const GemmParams& p, int idx, int tot
     w.c_row = tm * kBlockM;
     if (p.rs_ranks > 1) w.c_row = p.rs_rank * p.rs_rows + (tm * kBlockM - w.pad0 * p.rs_rows);
     w.m_valid = min(kBlockM, p.M - tm * kBlockM);
-    if (p.epi == kEpiSwiglu) {
+    if (epi_is_glu(p.epi)) {
         w.b_mn = tn * 128;
         w.b_mn2 = p.swiglu_f + tn * 128;
         w.c_col = tn * 128;
@@ -170,7 +179,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const GemmWor
         }
         return;
     }
-    if (p.epi == kEpiSwiglu) {
+    if (epi_is_glu(p.epi)) {
+        const bool clamped = (p.epi == kEpiClampedGlu);
 #pragma unroll 1
         for (int c = 0; c < 128; c += 32) {
             uint32_t g[32], u[32];
@@ -188,6 +198,15 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const GemmWor
                 for (int j = 0; j < 32; j += 8) {
                     if (c + j + 8 <= w.n_valid) {
                         uint32_t o[4], pg[4], pu[4];
+                        // the expert's bias for these eight gate and eight up columns: indexed like the rows of B
+                        uint4 bias_g4 = make_uint4(0, 0, 0, 0), bias_u4 = make_uint4(0, 0, 0, 0);
+                        if (clamped) {
+                            const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(p.glu_bias);
+                            bias_g4 = *reinterpret_cast<const uint4*>(bias + w.b_mn + c + j);
+                            bias_u4 = *reinterpret_cast<const uint4*>(bias + w.b_mn2 + c + j);
+                        }
+                        const __nv_bfloat162* bias_g = reinterpret_cast<const __nv_bfloat162*>(&bias_g4);
+                        const __nv_bfloat162* bias_u = reinterpret_cast<const __nv_bfloat162*>(&bias_u4);
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             // round the pre-activations to bf16 first so a later
@@ -196,13 +215,26 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const GemmWor
                             float g1 = zero ? 0.f : __uint_as_float(g[j + 2 * q + 1]) * p.alpha;
                             float u0 = zero ? 0.f : __uint_as_float(u[j + 2 * q]) * p.alpha;
                             float u1 = zero ? 0.f : __uint_as_float(u[j + 2 * q + 1]) * p.alpha;
+                            if (clamped) {
+                                const float2 bgf = __bfloat1622float2(bias_g[q]), buf = __bfloat1622float2(bias_u[q]);
+                                g0 += bgf.x; g1 += bgf.y; u0 += buf.x; u1 += buf.y;
+                            }
                             pg[q] = pack_bf16(g0, g1);
                             pu[q] = pack_bf16(u0, u1);
                             __nv_bfloat162 gb = *reinterpret_cast<__nv_bfloat162*>(&pg[q]);
                             __nv_bfloat162 ub = *reinterpret_cast<__nv_bfloat162*>(&pu[q]);
                             float2 gf = __bfloat1622float2(gb), uf = __bfloat1622float2(ub);
-                            float a0 = gf.x * sigmoid_fast(gf.x) * uf.x;
-                            float a1 = gf.y * sigmoid_fast(gf.y) * uf.y;
+                            float a0, a1;
+                            if (clamped) {
+                                const float gx = fminf(gf.x, p.glu_limit), gy = fminf(gf.y, p.glu_limit);
+                                const float ux = fminf(fmaxf(uf.x, -p.glu_limit), p.glu_limit);
+                                const float uy = fminf(fmaxf(uf.y, -p.glu_limit), p.glu_limit);
+                                a0 = (ux + 1.f) * gx * sigmoid_fast(p.glu_alpha * gx);
+                                a1 = (uy + 1.f) * gy * sigmoid_fast(p.glu_alpha * gy);
+                            } else {
+                                a0 = gf.x * sigmoid_fast(gf.x) * uf.x;
+                                a1 = gf.y * sigmoid_fast(gf.y) * uf.y;
+                            }
                             o[q] = pack_bf16(a0, a1);
                         }
                         *reinterpret_cast<uint4*>(out + j) = make_uint4(o[0], o[1], o[2], o[3]);

@@ -1,12 +1,11 @@
 // Element-wise half of routed experts with per-expert bias vectors and a clamped GLU (the gpt-oss expert form), on rows
 // grouped by expert:
 //
-//   pre  = x W_gate_up^T + b_gate_up[e]                    (the product comes from the grouped GEMM, bias added here)
+//   pre  = x W_gate_up^T + b_gate_up[e]                    (bias, clamp and activation run in the grouped GEMM's epilogue)
 //   gate = min(pre[:F], limit);  up = clamp(pre[F:], -limit, limit)
 //   act  = (up + 1) * gate * sigmoid(alpha * gate)
 //   y    = act W_down^T + b_down[e]                        (bias added to the rows of the second grouped GEMM)
 //
-//   expert_glu_fwd        pre += bias (in place, so the backward reads the biased values), act written
 //   expert_glu_bwd        dpre (over pre) and w * act (over the incoming dact), per-row <dact, act> for the routing weights
 //   expert_add_bias_rows  y_rows += b_down[e], or per-row <dy, b_down[e]> added to the routing-weight gradient
 //   expert_colsum         per-expert column sums of a row buffer (optionally weighted per row): the bias gradients,
@@ -15,7 +14,8 @@
 // Rows of expert e are seg_start[e] .. seg_start[e] + seg_rows[e] - 1; segments start on multiples of 128 rows and the
 // rows between a segment's end and the next start are pads. A row's expert is found by bisection over seg_start.
 // Pad rows get their expert's bias like any other row: nothing reads them back (the combine addresses real rows only,
-// and the backward scales them by a routing weight of zero).
+// and the backward scales them by a routing weight of zero). The forward's bias + clamp + activation is the
+// kEpiClampedGlu epilogue of the grouped GEMM (gemm_sm100.cuh); this file holds what has no product to ride on.
 //
 // Native form of the gpt-oss branch of halo/models/moe/experts.py and the bias / clamp epilogues of
 // halo/kernels/fused_glu.py:118-205.
@@ -39,52 +39,7 @@ __device__ __forceinline__ int expert_of_row(const int* __restrict__ seg_start, 
     return lo;
 }
 
-// one warp per row; 8 bf16 per lane per step
-__global__ void __launch_bounds__(256)
-expert_glu_fwd_kernel(__nv_bfloat16* pre, const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ act,
-                      const int* __restrict__ seg_start, int n_local, const int* __restrict__ total_rows, int F,
-                      int cap_rows, float limit, float alpha) {
-    const int lane = threadIdx.x & 31;
-    const int rows = min(*total_rows, cap_rows);
-    const int nvec = F / 8;
-    for (long long r = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); r < rows; r += (long long)gridDim.x * 8) {
-        const int e = expert_of_row(seg_start, n_local, r);
-        __nv_bfloat16* pg = pre + r * 2 * F;
-        const __nv_bfloat16* bg = bias + (long long)e * 2 * F;
-        for (int v = lane; v < nvec; v += 32) {
-            const uint4 gu = *reinterpret_cast<const uint4*>(pg + v * 8);
-            const uint4 uu = *reinterpret_cast<const uint4*>(pg + F + v * 8);
-            const uint4 bgu = *reinterpret_cast<const uint4*>(bg + v * 8);
-            const uint4 buu = *reinterpret_cast<const uint4*>(bg + F + v * 8);
-            const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gu);
-            const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uu);
-            const __nv_bfloat162* bgh = reinterpret_cast<const __nv_bfloat162*>(&bgu);
-            const __nv_bfloat162* buh = reinterpret_cast<const __nv_bfloat162*>(&buu);
-            uint4 og, ou, oa;
-            __nv_bfloat162* ogh = reinterpret_cast<__nv_bfloat162*>(&og);
-            __nv_bfloat162* ouh = reinterpret_cast<__nv_bfloat162*>(&ou);
-            __nv_bfloat162* oah = reinterpret_cast<__nv_bfloat162*>(&oa);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const float2 g0 = __bfloat1622float2(gh[q]), u0 = __bfloat1622float2(uh[q]);
-                const float2 bgf = __bfloat1622float2(bgh[q]), buf = __bfloat1622float2(buh[q]);
-                // the biased pre-activation is kept in bf16 (the backward starts from the stored value)
-                ogh[q] = __floats2bfloat162_rn(g0.x + bgf.x, g0.y + bgf.y);
-                ouh[q] = __floats2bfloat162_rn(u0.x + buf.x, u0.y + buf.y);
-                const float2 g = __bfloat1622float2(ogh[q]), u = __bfloat1622float2(ouh[q]);
-                const float gx = fminf(g.x, limit), gy = fminf(g.y, limit);
-                const float ux = fminf(fmaxf(u.x, -limit), limit), uy = fminf(fmaxf(u.y, -limit), limit);
-                oah[q] = __floats2bfloat162_rn((ux + 1.f) * gx * sigmoid_fast(alpha * gx),
-                                               (uy + 1.f) * gy * sigmoid_fast(alpha * gy));
-            }
-            *reinterpret_cast<uint4*>(pg + v * 8) = og;
-            *reinterpret_cast<uint4*>(pg + F + v * 8) = ou;
-            *reinterpret_cast<uint4*>(act + r * F + v * 8) = oa;
-        }
-    }
-}
-
-// dpre may be pre and act_w may be dact (in place): a thread reads the vectors it overwrites before it writes them
+// one warp per row; 8 bf16 per lane per step. dpre may be pre and act_w may be dact (in place): a thread reads the vectors it overwrites before it writes them
 __global__ void __launch_bounds__(256)
 expert_glu_bwd_kernel(const __nv_bfloat16* pre, const __nv_bfloat16* dact, const float* __restrict__ w,
                       __nv_bfloat16* dpre, __nv_bfloat16* act_w, float* __restrict__ dwrow,
@@ -204,15 +159,6 @@ expert_colsum_kernel(const __nv_bfloat16* __restrict__ src, const float* __restr
 
 extern "C" {
 using namespace halo;
-
-int halo_expert_glu_fwd(void* pre, const void* bias, void* act, const int* seg_start, int n_local, const int* total_rows,
-                        int F, int cap_rows, float limit, float alpha, void* stream) {
-    if (F % 8 || n_local <= 0) return -1;
-    expert_glu_fwd_kernel<<<2368, 256, 0, (cudaStream_t)stream>>>(
-        (__nv_bfloat16*)pre, (const __nv_bfloat16*)bias, (__nv_bfloat16*)act, seg_start, n_local, total_rows, F, cap_rows,
-        limit, alpha);
-    return HALO_LAUNCH_CHECK();
-}
 
 int halo_expert_glu_bwd(const void* pre, const void* dact, const float* w, void* dpre, void* act_w, float* dwrow,
                         const int* total_rows, int F, int cap_rows, float limit, float alpha, void* stream) {

@@ -55,16 +55,15 @@ def biased_glu_experts(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, gate
 def biased_glu_experts_reference(x, idx, w, gate_up, gate_up_bias, down, down_bias, limit: float = 7.0, alpha: float = GLU_ALPHA,
                                  stored_dtype=None):
     """Every expert on every token, masked by the routing weights (dense form, fp32). ``stored_dtype``: the
-    pre-activations are rounded to this dtype where the grouped kernels store them (the product, then product + bias),
+    pre-activations are rounded to this dtype where the grouped kernels store them (product + bias, once),
     so that the clamps cut - and pass gradients - at the same elements as in the kernels: a value within one rounding
     step of ``limit`` is clamped in one form and not in the other otherwise."""
     E = gate_up.shape[0]
     xf = x.float()
     dense_w = torch.zeros(x.shape[0], E, dtype=torch.float32, device=x.device).scatter_add(1, idx.long(), w.float())
     pre = torch.einsum("th,efh->tef", xf, gate_up.float())
+    pre = pre + gate_up_bias.float()[None]
     if stored_dtype is not None:
-        pre = (pre.to(stored_dtype).float() + gate_up_bias.float()[None]).to(stored_dtype).float()
-    else:
-        pre = pre + gate_up_bias.float()[None]
+        pre = pre.to(stored_dtype).float()            # the grouped product's epilogue rounds accumulator + bias once
     y = torch.einsum("tef,ehf->teh", clamped_glu(pre, limit, alpha), down.float()) + down_bias.float()[None]
     return (y * dense_w[..., None]).sum(1).to(x.dtype)

@@ -332,22 +332,24 @@ def grouped_swiglu_ffn_fwd(state: RoutingState, x_rows, w_gate_up, w_down, save_
 
 
 def grouped_biased_glu_fwd(state: RoutingState, x_rows, w_gate_up, gate_up_bias, limit: float, alpha: float, transport=None):
-    """Experts with bias vectors and a clamped GLU: the first product stores the raw pre-activations, one row kernel adds
-    the expert's bias (in place: the backward reads the biased values) and writes ``(up + 1) * gate * sigmoid(alpha gate)``
-    of the clamped halves. Returns (act [cap, F], pre [cap, 2F])."""
+    """Experts with bias vectors and a clamped GLU: the first product's epilogue adds the expert's bias to the
+    accumulators (the bias bank is indexed like the rows of the weight bank), stores the biased pre-activations (the
+    backward reads them) and writes ``(up + 1) * gate * sigmoid(alpha gate)`` of the clamped halves.
+    Returns (act [cap, F], pre [cap, 2F])."""
     E, F2, H = w_gate_up.shape
     F = F2 // 2
     cap = x_rows.shape[0]
     dev = x_rows.device
     act = _alloc(transport, (cap, F), torch.bfloat16, dev)
     pre = _alloc(transport, (cap, F2), torch.bfloat16, dev)
-    pair = _pair_ok(H, False)
-    lst1 = _tile_list(state, "m", pair, n_cols=F2, k_dim=H, b_mn_stride=F2, b_k_stride=0, swiglu_f=0)
-    _gemm_list(x_rows, w_gate_up.reshape(E * F2, H), pre, lst1, 0, 0, EPI_STORE_BF16, pair=pair)
-    _lib.check(_lib.lib().halo_expert_glu_fwd(
-        _lib.ptr(pre), _lib.ptr(gate_up_bias), _lib.ptr(act), _lib.ptr(state.seg_start), _lib.c_int(state.n_local),
-        _lib.ptr(state.total_rows), _lib.c_int(F), _lib.c_int(cap), _lib.c_float(limit), _lib.c_float(alpha),
-        _lib.stream_ptr(dev)), "halo_expert_glu_fwd")
+    lst, cnt = _tile_list(state, "m", n_cols=F2, k_dim=H, b_mn_stride=F2, b_k_stride=0, swiglu_f=F)
+    b2d = w_gate_up.reshape(E * F2, H)
+    _lib.check(_lib.lib().halo_gemm_bf16_list_glu(
+        _lib.ptr(x_rows), _lib.c_ll(x_rows.shape[0]), _lib.c_ll(x_rows.shape[1]), _lib.c_ll(x_rows.stride(0)),
+        _lib.ptr(b2d), _lib.c_ll(b2d.shape[0]), _lib.c_ll(b2d.shape[1]), _lib.c_ll(b2d.stride(0)),
+        _lib.ptr(act), _lib.ptr(pre), _lib.c_ll(act.stride(0)), _lib.c_ll(pre.stride(0)), _lib.c_int(F),
+        _lib.ptr(gate_up_bias), _lib.c_float(limit), _lib.c_float(alpha), _lib.ptr(lst), _lib.ptr(cnt),
+        _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev)), "halo_gemm_bf16_list_glu")
     return act, pre
 
 

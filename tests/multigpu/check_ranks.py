@@ -61,6 +61,44 @@ def _check_expert_call(tr, dev, rank, world, what, T, call):
     close(wd.grad, gd[e0:e1], 5e-2, f"ep dw_down ({what})")
 
 
+def check_biased_glu_experts(tr, dev, rank, world):
+    """Experts with bias vectors around a clamped GLU, sharded over the ranks (whole experts with their bias rows): output
+    and gradients of this rank's tokens against the dense fp32 form over ALL experts. Gradients are compared by norm: a
+    pre-activation within a rounding step of the clamp can fall on either side in two correct summation orders."""
+    from halo_b200.ops.biased_glu_experts import GLU_ALPHA, biased_glu_experts_reference
+    from halo_b200.ops.moe import moe_experts
+
+    H, F, E, k, T, limit = 512, 256, 16, 4, 1536 - 128 * (rank % 3), 2.0
+    g = torch.Generator(device=dev).manual_seed(11)
+    wgu_full = (torch.randn(E, 2 * F, H, device=dev, generator=g) * 0.08).bfloat16()
+    wd_full = (torch.randn(E, H, F, device=dev, generator=g) * 0.05).bfloat16()
+    bgu_full = (torch.randn(E, 2 * F, device=dev, generator=g) * 0.5).bfloat16()
+    bd_full = (torch.randn(E, H, device=dev, generator=g) * 0.5).bfloat16()
+    g2 = torch.Generator(device=dev).manual_seed(300 + rank)
+    x = torch.randn(T, H, device=dev, generator=g2).bfloat16()
+    w, idx = torch.topk(torch.rand(T, E, device=dev, generator=g2), k, dim=-1)
+    w = (w / w.sum(-1, keepdim=True)).float()
+    idx = idx.to(torch.int32)
+    e0, e1 = rank * (E // world), (rank + 1) * (E // world)
+    mine = [t.detach().clone().requires_grad_() for t in (x, w, wgu_full[e0:e1], wd_full[e0:e1], bgu_full[e0:e1], bd_full[e0:e1])]
+    out = moe_experts(mine[0], idx, mine[1], mine[2], mine[3], tr, glu=(mine[4], mine[5], limit, GLU_ALPHA))
+    gout = torch.randn(T, H, device=dev, generator=g2).bfloat16()
+    out.backward(gout)
+    torch.cuda.synchronize()
+    full = [t.detach().float().requires_grad_() for t in (x, w.clone(), wgu_full, wd_full, bgu_full, bd_full)]
+    ref = biased_glu_experts_reference(full[0], idx, full[1], full[2], full[4], full[3], full[5], limit, stored_dtype=torch.bfloat16)
+    ref.backward(gout.float())
+    close(out, ref, 3e-2, "biased glu ep out")
+    wants = [full[0].grad, full[1].grad]
+    for t in full[2:]:
+        gsum = t.grad.clone()
+        dist.all_reduce(gsum)                       # a bank's gradient collects every rank's tokens
+        wants.append(gsum[e0:e1])
+    for got, want, name in zip(mine, wants, ("dx", "dw_route", "dw_gate_up", "dw_down", "db_gate_up", "db_down")):
+        diff = got.grad.float() - want
+        assert diff.norm().item() <= 2e-2 * want.norm().item() + 1e-6, f"biased glu ep {name}: {diff.norm().item()} of {want.norm().item()}"
+
+
 def check_fused_optimizer(dev, rank, world):
     from halo_b200.optim.adamw_bf16 import adamw_bf16_step_reference, param_name_hash, SR_KEY
     from halo_b200.parallel.zero import FusedShardedAdamW
@@ -400,6 +438,9 @@ def main():
         tr.configure(max_tokens=1536, top_k=4, hidden=512, n_local_experts=16 // world)
         check_expert_transport(tr, dev, rank, world, "movement inside the GEMM kernels" if fused else "separate push / pull kernels")
         _lib.raise_on_status(dev)
+        if not fused:
+            check_biased_glu_experts(tr, dev, rank, world)
+            _lib.raise_on_status(dev)
     check_fused_optimizer(dev, rank, world)
     check_broadcast_and_allreduce(dev, rank, world)
     check_sharded_weight_push(dev, rank, world)
