@@ -52,11 +52,17 @@ class EfficiencyCallback(Callback):
             self._last = time.perf_counter()
 
     def on_batch(self, trainer, batch):
-        self.note_batch(batch)
+        # the ranks of a tensor-parallel group work on ONE row together: each accounts for its share of the tokens and
+        # of the model FLOPs, so the per-GPU figures stay per GPU
+        tp = getattr(getattr(trainer, "model", None), "tensor_parallel", None)
+        # likewise the stages of a pipeline: a micro-batch passes through all of them
+        stage = getattr(getattr(trainer, "engine", None), "stage", None)
+        ways = max(1, int(getattr(tp, "size", 1) or 1)) * max(1, int(getattr(stage, "n_stages", 1) or 1))
+        self.note_batch(batch, share=1.0 / ways)
 
-    def note_batch(self, batch):
-        self._tokens += batch.n_tokens
-        self._flops += model_flops_per_step(self.cfg, batch.cu_seqlens, batch.n_tokens)
+    def note_batch(self, batch, share: float = 1.0):
+        self._tokens += batch.n_tokens * share
+        self._flops += model_flops_per_step(self.cfg, batch.cu_seqlens, batch.n_tokens) * share
 
     def on_log(self, trainer, logs):
         if self._last is None or "step_seconds" not in logs:

@@ -116,11 +116,14 @@ def _pipeline_runtime(pc, device, group):
         raise ValueError(f"with pipeline stages of {width} ranks, expert_parallel_size must be 1 or {width}, got {pc.ep_size}")
     ranks = [dist.get_global_rank(group, r) for r in range(world)] if group is not dist.group.WORLD else list(range(world))
     stage, pos = rank // width, rank % width
-    chain = stage_group = None
+    chain = chain_up = stage_group = None
     for j in range(width):                                # chains: one rank of every stage
         g = dist.new_group(ranks[j::width])
+        # a second communicator over the same ranks for the gradients that travel up the pipeline: activations and
+        # gradients cross in the steady state, and on one NCCL communicator their sends would wait behind each other
+        g_up = dist.new_group(ranks[j::width]) if device.type == "cuda" else g
         if j == pos:
-            chain = g
+            chain, chain_up = g, g_up
     for s in range(pc.pp_size):                           # stages: their replicas
         g = dist.new_group(ranks[s * width:(s + 1) * width]) if width > 1 else None
         if s == stage:
@@ -135,7 +138,7 @@ def _pipeline_runtime(pc, device, group):
             parallel = ParallelRuntime(device, dp_group=stage_group, ep_group=stage_group, transport=CollectiveTransport(stage_group))
         else:
             parallel = ParallelRuntime(device, dp_group=stage_group)
-    return {"kind": "pp", "chain": chain, "stage": stage, "n_stages": pc.pp_size, "position": pos, "width": width,
+    return {"kind": "pp", "chain": chain, "chain_up": chain_up, "stage": stage, "n_stages": pc.pp_size, "position": pos, "width": width,
             "parallel": parallel, "device": device, "schedule": pc.pp_schedule, "split": pc.pp_split, "pc": pc}
 
 
@@ -144,7 +147,7 @@ def finish_pipeline_runtime(spec: dict, model, optimizer, row_len: int, max_grad
     from halo_b200.parallel.pipeline import PipelineStage
     from halo_b200.trainers.pipeline_engine import PipelineEngine
 
-    stage = PipelineStage(model, spec["chain"], row_len)
+    stage = PipelineStage(model, spec["chain"], row_len, up_group=spec.get("chain_up"))
     return PipelineEngine(stage, optimizer, max_grad_norm, spec["schedule"], lr_scheduler, parallel=spec["parallel"],
                           min_microbatches=spec["n_stages"] if spec["schedule"] == "1f1b" else 1)
 

@@ -59,8 +59,16 @@ class _InFlight:
 class PipelineStage:
     """One stage's slice of the model plus its neighbours in the pipeline group."""
 
-    def __init__(self, model, group, row_len: int, dtype=None):
+    def __init__(self, model, group, row_len: int, dtype=None, up_group=None):
+        """``group`` carries the activations down the pipeline; ``up_group`` (same ranks, its own communicator) the
+        gradients back up. On NCCL the point-to-point operations of one communicator run in the order they were
+        issued, and a send only finishes once its receive has started: in the steady state of 1F1B stage s issues
+        send(activation k+1), recv(gradient k) while stage s+1 issues send(gradient k), recv(activation k+1) - with one
+        communicator each stage's send waits behind the other's, for ever. Two communicators let the two directions
+        progress independently. ``up_group=None`` uses ``group`` for both (gloo, whose sends are buffered, and
+        forward-only use)."""
         self.model, self.group = model, group
+        self.up_group = up_group if up_group is not None else group
         self.n_stages = dist.get_world_size(group)
         self.stage = dist.get_rank(group)
         self.is_first, self.is_last = self.stage == 0, self.stage == self.n_stages - 1
@@ -72,16 +80,16 @@ class PipelineStage:
         self.next = None if self.is_last else dist.get_global_rank(group, self.stage + 1) if group is not None else self.stage + 1
 
     # ---- messages ------------------------------------------------------------------------------
-    def _recv(self, src: int) -> torch.Tensor:
+    def _recv(self, src: int, up: bool = False) -> torch.Tensor:
         t = torch.empty(self.shape, dtype=self.dtype, device=self.device)
-        dist.recv(t, src=src, group=self.group)
+        dist.recv(t, src=src, group=self.up_group if up else self.group)
         return t
 
-    def _send(self, t: torch.Tensor, dst: int) -> None:
+    def _send(self, t: torch.Tensor, dst: int, up: bool = False) -> None:
         # never a blocking send: in the steady state a stage sends an activation down while its neighbour sends
         # a gradient up, and two blocking sends facing each other would wait for ever
         t = t.contiguous()
-        self._pending.append((dist.isend(t, dst=dst, group=self.group), t))
+        self._pending.append((dist.isend(t, dst=dst, group=self.up_group if up else self.group), t))
 
     def drain(self) -> None:
         for work, _ in self._pending:
@@ -114,10 +122,10 @@ class PipelineStage:
         if self.is_last:
             fl.out.backward()
         else:
-            g = self._recv(self.next)
+            g = self._recv(self.next, up=True)
             torch.autograd.backward(fl.out, g)
         if not self.is_first:
-            self._send(fl.x_in.grad, self.prev)
+            self._send(fl.x_in.grad, self.prev, up=True)
 
 
 def run_schedule(stage: PipelineStage, micro_batches: list, normalizer, schedule: str = "1f1b") -> torch.Tensor:

@@ -290,6 +290,12 @@ def test_efficiency_metrics_reach_the_logs(tmp_path):
     assert rec["tokens_per_s_per_gpu"] > 0 and rec["mfu"] > 0
     flops = model_flops_per_step(cfg, batches[1].cu_seqlens, batches[1].n_tokens)
     assert abs(rec["mfu"] * eff.peak * (128 / rec["tokens_per_s_per_gpu"]) / flops - 1.0) < 1e-6
+    # the ranks of a tensor-parallel pair work on one row together: each accounts for half of it
+    import types
+
+    pair = EfficiencyCallback(cfg, 2)
+    pair.on_batch(types.SimpleNamespace(model=types.SimpleNamespace(tensor_parallel=types.SimpleNamespace(size=2))), batches[0])
+    assert pair._tokens == batches[0].n_tokens / 2 and abs(pair._flops - model_flops_per_step(cfg, batches[0].cu_seqlens, 128) / 2) < 1.0
 
 
 @pytest.mark.parametrize("method,extra,arch", [("classification", "num_labels: 4\n", "Qwen3MoeForSequenceClassification"),
