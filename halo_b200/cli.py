@@ -41,6 +41,7 @@ TOOLS = {
     "evaluate": "halo_b200.entrypoints.evaluation",
     "reward-scoring": "halo_b200.entrypoints.reward_scoring",
     "env-eval": "halo_b200.entrypoints.env_eval",
+    "code-tasks": "halo_b200.entrypoints.code_tasks",
     "merge-adapter": "halo_b200.checkpoint.tools.merge_adapter",
     "lowp-convert": "halo_b200.checkpoint.tools.lowp_convert",
     "merge-pp-stages": "halo_b200.checkpoint.tools.merge_pp_stages",

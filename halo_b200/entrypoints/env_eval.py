@@ -4,7 +4,8 @@
 
 Every task is played ``--n`` times through the same episode loop training uses (multi-turn, tools, sandboxed code);
 the report gives the mean score, pass@1 and pass@n (a task passes when an episode scores 1), the share of episodes
-cut for malformed turns or the turn budget, and tool calls per episode. Episodes are written to ``--out`` as JSONL.
+cut for malformed turns or the turn budget, and tool calls per episode. Episodes are written to ``--out`` as JSONL
+(line 1 is the run's meta record; ``code_tasks regrade`` grades the recorded programs again offline).
 The role of the reference's environment eval runners (halo/entrypoints/{generic_env_eval,code_contests_eval}.py)."""
 
 from __future__ import annotations
@@ -34,8 +35,10 @@ def evaluate_tasks(model, tokenizer, tasks: list[dict], env_type: str, n: int, s
                 env = make_environment(env_type, task, **(env_options or {}))
                 rec = await play_episode(env, policy.for_episode(ti * n + k), composer)
                 episodes.append({"task": ti, "sample": k, "score": rec.score, "reward": rec.info.get("reward", rec.score),
-                                 "done_reason": rec.done_reason, "tool_calls": rec.tool_calls_used, "turns": len(rec.turns),
-                                 "completion": rec.completion})
+                                 "done_reason": rec.done_reason, "tool_calls": rec.tool_calls_used, "n_turns": len(rec.turns),
+                                 "completion": rec.completion, "task_id": task.get("id"),
+                                 # the policy's turns as the offline re-grader reads them (code_tasks regrade)
+                                 "turns": [{"role": "assistant", "content": t.content} for t in rec.turns]})
 
     with torch.no_grad():
         asyncio.run(run())
@@ -74,6 +77,9 @@ def main(argv=None) -> int:
                                       SamplingParams(args.max_new_tokens, args.temperature, 0, args.top_p), options)
     if args.out:
         with open(args.out, "w") as f:
+            # line 1: what the offline re-grader needs to rebuild the run (environment, its options, the task file)
+            f.write(json.dumps({"meta": {"env": args.env, "options": options, "tasks": args.tasks, "n": args.n,
+                                         "checkpoint": args.checkpoint, "report": report}}) + "\n")
             for e in episodes:
                 f.write(json.dumps(e) + "\n")
     print(json.dumps(report))

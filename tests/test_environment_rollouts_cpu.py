@@ -136,4 +136,4 @@ def test_environment_evaluation_report():
                                       {"protocol": "native"})
     # under the tagged-call protocol free text is a final answer: a random policy answers at once, wrongly
     assert report["episodes"] == 4 and report["tasks"] == 2 and report["mean_score"] == 0.0 and report["pass@2"] == 0.0
-    assert report["cut_short"] == 0.0 and all(e["done_reason"] == "answered" and e["turns"] == 1 for e in episodes)
+    assert report["cut_short"] == 0.0 and all(e["done_reason"] == "answered" and e["n_turns"] == 1 and len(e["turns"]) == 1 for e in episodes)
