@@ -53,6 +53,19 @@ def broadcast_object(obj: Any, src: int = 0, group=None) -> Any:
     return box[0]
 
 
+def share_from_leader(produce, group=None) -> Any:
+    """COLLECTIVE over ``group``. The group's first rank calls ``produce()``; every rank returns its result (None is a
+    result like any other). For ranks that must process identical inputs - the slices of one tensor-parallel replica -
+    when each would otherwise draw its own (sampled rollouts, a shuffled batch)."""
+    if not _live(group) or dist.get_world_size(group) == 1:
+        return produce()
+    leader = dist.get_rank(group) == 0
+    src = dist.get_global_rank(group, 0) if group is not None else 0
+    box = [produce() if leader else None]
+    dist.broadcast_object_list(box, src=src, group=group)
+    return box[0]
+
+
 def gather_on_rank0(obj: Any, group=None) -> list | None:
     """Every rank's object on group rank 0 (None elsewhere). Large pickles move in 64 MiB windows as
     a SUM-reduce of byte buffers, which needs no per-peer point-to-point buffers."""

@@ -219,12 +219,31 @@ class GRPOTrainer(Trainer):
         """One list of micro-batches per round: the trainer loop runs a list as exactly one optimizer step, so the
         next round's rollouts are requested only after this round's update (and weight push) has happened."""
         while True:
-            rollouts = self.rollout_source(self.rounds_done)
+            rollouts = self._shared_round(self.rounds_done)
             if rollouts is None:
                 return
             batches = self.plan_round(rollouts)
             yield [b.pin() if torch.cuda.is_available() else b for b in batches]
             self.rounds_done += 1
+
+    def _sibling_group(self):
+        """The group whose ranks hold slices of ONE model replica (tensor parallel, or expert tensor parallel): they run
+        collectives inside the forward, so they must train on identical rows."""
+        tp = getattr(self.model, "tensor_parallel", None)
+        etp = getattr(self.model, "expert_tensor_parallel", None)
+        sliced = tp if tp is not None else etp
+        return getattr(sliced, "group", None)
+
+    def _shared_round(self, index: int):
+        """This round's rollouts. Under tensor / expert tensor parallelism only the group's first rank asks the source;
+        its rollouts (or its end-of-data) are broadcast to the siblings: independently sampled rounds would differ in
+        row count and length, and the siblings' collectives would wait for each other for ever."""
+        group = self._sibling_group()
+        if group is None:
+            return self.rollout_source(index)
+        from halo_b200.runtime.collectives import share_from_leader
+
+        return share_from_leader(lambda: self.rollout_source(index), group)
 
     def skip_consumed(self, it):
         """A resumed run continues with round ``global_step``: one round is one optimizer step, and rounds the

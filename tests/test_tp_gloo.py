@@ -143,3 +143,42 @@ def test_checkpoint_loads_into_tensor_parallel_slices(tmp_path):
     d = str(tmp_path / "ckpt")
     save_model(model, d, save_dtype=None)
     run_gloo_ranks(_sliced_load_worker, 2, args=(d,), timeout=120.0)
+
+
+def _leader_worker(rank, world):
+    import types
+
+    import numpy as np
+    import torch.distributed as dist
+
+    from halo_b200.runtime.collectives import share_from_leader
+    from halo_b200.trainers.grpo.trainer import GRPOTrainer, Rollout
+
+    # two tensor-parallel pairs: (0, 1) and (2, 3); every rank would sample something else
+    pairs = [dist.new_group([0, 1]), dist.new_group([2, 3])]
+    mine = pairs[rank // 2]
+    calls = []
+
+    def source(i):
+        calls.append(i)
+        if i == 2:
+            return None
+        return [Rollout(np.arange(3 + rank), np.arange(2 + i), None, float(rank))]
+
+    got = share_from_leader(lambda: source(0), mine)
+    assert got[0].reward == float(2 * (rank // 2)) and len(got[0].prompt_ids) == 3 + 2 * (rank // 2)     # the pair's first rank's
+    assert calls == ([0] if rank % 2 == 0 else [])                                                      # only leaders sampled
+    # through the trainer's seam: a model that carries a tensor-parallel descriptor
+    fake = types.SimpleNamespace(model=types.SimpleNamespace(tensor_parallel=types.SimpleNamespace(group=mine), expert_tensor_parallel=None),
+                                 rollout_source=source)
+    fake._sibling_group = lambda: GRPOTrainer._sibling_group(fake)
+    r1 = GRPOTrainer._shared_round(fake, 1)
+    assert r1[0].reward == float(2 * (rank // 2)) and len(r1[0].completion_ids) == 3
+    assert GRPOTrainer._shared_round(fake, 2) is None                                                   # end of data reaches the follower too
+    plain = types.SimpleNamespace(model=types.SimpleNamespace(tensor_parallel=None, expert_tensor_parallel=None), rollout_source=source)
+    plain._sibling_group = lambda: GRPOTrainer._sibling_group(plain)
+    assert GRPOTrainer._shared_round(plain, 0)[0].reward == float(rank)                                  # no slicing: every rank its own
+
+
+def test_rollouts_come_from_the_leader_of_a_sliced_replica():
+    run_gloo_ranks(_leader_worker, 4, timeout=240)
