@@ -161,9 +161,9 @@ def _token_cutting_runtime(pc, device, group):
     width = pc.tp_size if pc.tp_size > 1 else pc.cp_size
     if pc.tp_size > 1 and pc.cp_size > 1:
         raise ValueError("tensor and context parallelism together are not wired into the entry points")
-    if pc.ep_size > 1 and (pc.tp_size > 1 or pc.ep_size != world):
-        raise ValueError("with context parallelism the experts are sharded over every rank of the job (expert_parallel_size "
-                         f"= {world}); expert parallelism together with tensor parallelism is not wired into the entry points")
+    if pc.ep_size > 1 and pc.ep_size != world:
+        raise ValueError("with tensor or context parallelism the experts are sharded over every rank of the job "
+                         f"(expert_parallel_size = {world}), got {pc.ep_size}")
     ranks = [dist.get_global_rank(group, r) for r in range(world)] if group is not dist.group.WORLD else list(range(world))
     mine = replica = None
     for b in range(world // width):                       # blocks of consecutive ranks share a row
@@ -201,7 +201,8 @@ def finish_token_cutting_runtime(spec: dict, cfg, max_tokens: int):
 
             transport = CollectiveTransport(spec["group"])
         return spec["runtime_cls"](spec["device"], dp_group=spec["group"], ep_group=spec["group"], transport=transport,
-                                   context_parallel=cp)
+                                   context_parallel=cp, tensor_parallel=tp,
+                                   tp_replica_group=spec["replica_group"] if tp is not None else None)
     return spec["runtime_cls"](spec["device"], dp_group=spec["group"], tensor_parallel=tp, context_parallel=cp,
                                tp_replica_group=spec["replica_group"] if tp is not None else None)
 
@@ -244,7 +245,7 @@ def load_policy_model(model_args, pc, device, runtime, gradient_checkpointing=Tr
         transport = runtime.transport
         if transport is not None and hasattr(transport, "configure") and cfg.is_moe:
             # a rank holds its share of a row (plus what the tile-aligned cuts add)
-            share = max_tokens // max(pc.cp_size, 1) + 512
+            share = max_tokens // max(pc.cp_size, pc.tp_size, 1) + 512
             transport.configure(max_tokens=share, top_k=cfg.num_experts_per_tok, hidden=cfg.hidden_size,
                                 n_local_experts=cfg.num_experts // transport.n_ranks)
         model = build_model(cfg, device=device, dtype=dtype, gradient_checkpointing=gradient_checkpointing,
