@@ -89,6 +89,10 @@ class SymmetricTransport:
             if name == "ctrl":
                 t.zero_()
             hdl = symm.rendezvous(t, self.group)
+            if int(getattr(hdl, "world_size", self.n_ranks)) != self.n_ranks or int(getattr(hdl, "rank", self.rank)) != self.rank:
+                # the peer table must be this group's: kernels index it by the group rank
+                raise RuntimeError(f"symmetric-memory handle of {name!r} describes rank {hdl.rank} of {hdl.world_size}, the "
+                                   f"expert-parallel group has rank {self.rank} of {self.n_ranks}")
             self._bufs[name] = (t, hdl)
         self._barrier_handle = self._bufs["recv_x"][1]
         if self.fused:
