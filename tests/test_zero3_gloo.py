@@ -8,7 +8,7 @@ import torch
 from tests.common.gloo import run_gloo_ranks
 
 
-def _train(rank, world, sharded, moe, out_dir=None):
+def _train(rank, world, sharded, moe, out_dir=None, light_layers=0):
     import dataclasses
 
     import torch.distributed as dist
@@ -29,6 +29,8 @@ def _train(rank, world, sharded, moe, out_dir=None):
 
         transport, ep_group = CollectiveTransport(dist.group.WORLD), dist.group.WORLD
     model = build_model(cfg, device="cpu", dtype=torch.float32, seed=11, transport=transport, gradient_checkpointing=True)
+    for layer in model.layers[len(model.layers) - light_layers:]:
+        layer.recompute_policy = "mlp"           # the lighter policy: attention keeps its graph, the feed-forward half is re-run
     parallel = ParallelRuntime("cpu", dp_group=dist.group.WORLD, ep_group=ep_group, transport=transport)
     zero3 = None
     if sharded:
@@ -74,9 +76,9 @@ def _train(rank, world, sharded, moe, out_dir=None):
     return losses, weights
 
 
-def _worker(rank, world, moe, out_dir):
-    want_l, want_w = _train(rank, world, False, moe)
-    got_l, got_w = _train(rank, world, True, moe, out_dir)
+def _worker(rank, world, moe, out_dir, light_layers=0):
+    want_l, want_w = _train(rank, world, False, moe, light_layers=light_layers)
+    got_l, got_w = _train(rank, world, True, moe, out_dir, light_layers=light_layers)
     assert len(want_l) == len(got_l)
     for a, b in zip(want_l, got_l):
         assert abs(a - b) <= 1e-5 * max(1.0, abs(a)), (want_l, got_l)
@@ -102,3 +104,11 @@ def test_sharded_layers_train_like_the_replicated_model(moe, tmp_path):
 
 def test_three_ranks_pad_the_layer_to_a_multiple_of_the_world():
     run_gloo_ranks(_worker, 3, args=(False, None), timeout=240.0)
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_sharded_layers_under_the_lighter_recomputation_policy(moe):
+    """Two of three layers keep the graph of their attention half and re-run only the feed-forward half: the layer's
+    parameters are gathered for the first pass, and again from the re-run of the second half until the backward of the
+    first; what the attention half saved is read through the parameters bound in that second window."""
+    run_gloo_ranks(_worker, 2, args=(moe, None, 2), timeout=240.0)
