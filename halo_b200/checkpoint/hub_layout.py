@@ -23,10 +23,12 @@ MOE_HUB_NAMES = {
     "mixtral": ("block_sparse_moe", "w1", "w3", "w2"),
     "glm4_moe": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "deepseek_v3": ("mlp", "gate_proj", "up_proj", "down_proj"),
+    "mistral4": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "olmoe": ("mlp", "gate_proj", "up_proj", "down_proj"),
 }
-# gpt-oss stores each bank as ONE tensor, transposed, with gate and up columns interleaved (``INTERLEAVED_GLU``)
-WHOLE_BANK_FAMILIES = ("gpt_oss",)
+# gpt-oss stores each bank as ONE tensor, transposed, with gate and up columns interleaved (``INTERLEAVED_GLU``);
+# Mistral 4 stores each bank as one tensor in the runtime's own layout (``FUSED``: gate rows, then up rows)
+WHOLE_BANK_FAMILIES = ("gpt_oss", "mistral4")
 
 
 def _interleave(gate_then_up: torch.Tensor, dim: int) -> torch.Tensor:
@@ -49,6 +51,9 @@ def whole_bank_source(name: str, cfg, first_layer: int = 0):
     if not m or getattr(cfg, "family", "") not in WHOLE_BANK_FAMILIES:
         return None
     pre = f"model.layers.{int(m.group(1)) + first_layer}.mlp.experts."
+    if cfg.family == "mistral4":
+        return {"mlp.experts_gate_up": (pre + "gate_up_proj", lambda t: t),
+                "mlp.experts_down": (pre + "down_proj", lambda t: t)}.get(m.group(2))
     return {
         "mlp.experts_gate_up": (pre + "gate_up_proj", lambda t: _deinterleave(t.transpose(1, 2), 1).contiguous()),
         "mlp.experts_gate_up_bias": (pre + "gate_up_proj_bias", lambda t: _deinterleave(t, 1).contiguous()),
@@ -56,7 +61,7 @@ def whole_bank_source(name: str, cfg, first_layer: int = 0):
         "mlp.experts_down_bias": (pre + "down_proj_bias", lambda t: t),
     }.get(m.group(2))
 # how a family names its always-on shared feed-forward block
-SHARED_EXPERT_NAMES = {"glm4_moe": "shared_experts", "deepseek_v3": "shared_experts"}
+SHARED_EXPERT_NAMES = {"glm4_moe": "shared_experts", "deepseek_v3": "shared_experts", "mistral4": "shared_experts"}
 
 
 LAYER_NORMS = ("input_layernorm", "post_attention_layernorm", "pre_feedforward_layernorm", "post_feedforward_layernorm")
@@ -130,9 +135,10 @@ def runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, e
     if rest == "mlp.down_proj":
         return {pre + "mlp.down_proj.weight": tensor}
     if getattr(cfg, "family", "") in WHOLE_BANK_FAMILIES and rest.startswith("mlp."):
-        if expert_offset or (rest.startswith("mlp.experts_") and tensor.shape[0] != cfg.num_experts):
+        if rest.startswith("mlp.experts_") and (expert_offset or tensor.shape[0] != cfg.num_experts):
             raise ValueError("this family's banks are stored whole: a shard of the experts has no hub form")
-        whole = {"mlp.gate": ("router.weight", lambda t: t), "mlp.gate_bias": ("router.bias", lambda t: t),
+        whole = {"mlp.experts_gate_up": ("experts.gate_up_proj", lambda t: t),
+                 "mlp.experts_down": ("experts.down_proj", lambda t: t)} if cfg.family == "mistral4" else {"mlp.gate": ("router.weight", lambda t: t), "mlp.gate_bias": ("router.bias", lambda t: t),
                  "mlp.experts_gate_up": ("experts.gate_up_proj", lambda t: _interleave(t, 1).transpose(1, 2)),
                  "mlp.experts_gate_up_bias": ("experts.gate_up_proj_bias", lambda t: _interleave(t, 1)),
                  "mlp.experts_down": ("experts.down_proj", lambda t: t.transpose(1, 2)),

@@ -245,6 +245,7 @@ class Generator:
             cache.begin_decode()
             dctx = ForwardContext(None, m.rope(cache.lengths), m.transport)
             dctx.rope_local = m.rope_local(cache.lengths)
+            dctx.query_scale = m.query_scale(cache.lengths)
             dctx.kv_cache = cache
             dctx.routing_trace = trace
             trunk = m.trunk_states(tok, dctx)

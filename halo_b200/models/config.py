@@ -42,6 +42,9 @@ FAMILIES = {
     "gemma2": dict(architecture="Gemma2ForCausalLM", moe=False, qk_norm=False, bias_key=True, bias_default=False, has_window=True),
     "gemma3_text": dict(architecture="Gemma3ForCausalLM", moe=False, qk_norm=True, bias_key=True, bias_default=False, has_window=True),
     "deepseek_v3": dict(architecture="DeepseekV3ForCausalLM", moe=True, qk_norm=False, bias_key=True, bias_default=False, has_window=False),
+    # Mistral 4: the DeepSeek-V3 block (latent attention, shared experts, group-limited routing) with softmax router
+    # scores, expert banks stored whole, and queries scaled by 1 + beta * log(1 + floor(position / period))
+    "mistral4": dict(architecture="Mistral4ForCausalLM", moe=True, qk_norm=False, bias_key=True, bias_default=False, has_window=False),
     "gpt_oss": dict(architecture="GptOssForCausalLM", moe=True, qk_norm=False, bias_key=True, bias_default=True, has_window=True),
 }
 
@@ -74,6 +77,8 @@ class ModelConfig:
     n_group: int = 1                       # group-limited routing: experts in ``n_group`` groups, ``topk_group`` of them eligible
     topk_group: int = 1
     routed_scaling_factor: float = 1.0
+    query_scale_beta: float = 0.0          # > 0: queries times 1 + beta * log(1 + floor(position / query_scale_period)) (Mistral 4)
+    query_scale_period: int = 0
     sliding_window: int = 0                # > 0: every query sees only its last ``sliding_window`` keys (Mistral-style)
     hidden_activation: str = "silu"        # gate activation of the dense feed-forward block: "silu" | "gelu_tanh"
     sandwich_norms: bool = False           # an RMSNorm on the output of each block too (Gemma): four norms per layer
@@ -114,6 +119,11 @@ class ModelConfig:
     @property
     def is_moe(self) -> bool:
         return self.num_experts > 0
+
+    @property
+    def grouped_routing(self) -> bool:
+        """The router ranks through the group-limited path (tensor ops) instead of the plain softmax top-k kernel."""
+        return self.score_function == "sigmoid" or self.n_group > 1 or self.routed_scaling_factor != 1.0
 
     def layer_is_moe(self, i: int) -> bool:
         return self.is_moe and i not in self.mlp_only_layers and (i + 1) % self.decoder_sparse_step == 0
@@ -236,7 +246,7 @@ class ModelConfig:
                       "output_router_logits": False, "swiglu_limit": self.glu_limit,
                       "layer_types": list(self.layer_types or ["sliding_attention" if self.sliding_window else "full_attention"]
                                           * self.num_hidden_layers)})
-        elif self.family in ("glm4_moe", "deepseek_v3"):
+        elif self.family in ("glm4_moe", "deepseek_v3", "mistral4"):
             first_dense = 0
             while first_dense in self.mlp_only_layers:
                 first_dense += 1
@@ -257,6 +267,21 @@ class ModelConfig:
                           "qk_nope_head_dim": self.qk_nope_head_dim, "qk_rope_head_dim": self.qk_rope_head_dim,
                           "v_head_dim": self.v_head_dim, "rope_interleave": self.rope_interleave,
                           "head_dim": self.qk_rope_head_dim})
+                if self.family == "mistral4":
+                    # a head is the un-rotated and the rotated slice together; the rotary table covers the rotated share
+                    whole = self.qk_nope_head_dim + self.qk_rope_head_dim
+                    d["head_dim"] = whole
+                    d.pop("rope_scaling", None)
+                    d.pop("rope_theta", None)
+                    d["rope_parameters"] = dict(d["rope_parameters"], partial_rotary_factor=self.qk_rope_head_dim / whole)
+                    stored = d["rope_parameters"].get("original_max_position_embeddings")
+                    if self.query_scale_beta and stored and int(stored) != self.query_scale_period:
+                        raise ValueError("mistral4 stores ONE original_max_position_embeddings: the period of the query stretch "
+                                         f"({self.query_scale_period}) must equal the rotary scaling's ({stored})")
+                    # the release's code reads both keys unconditionally: a zero beta is written, not left out
+                    d["rope_parameters"]["llama_4_scaling_beta"] = self.query_scale_beta
+                    d["rope_parameters"].setdefault("original_max_position_embeddings",
+                                                    self.query_scale_period or self.max_position_embeddings)
         elif self.family == "olmoe":
             d.update({"num_experts": self.num_experts, "num_experts_per_tok": self.num_experts_per_tok,
                       "norm_topk_prob": self.norm_topk_prob, "intermediate_size": self.moe_intermediate_size, "clip_qkv": None,
@@ -318,11 +343,20 @@ class ModelConfig:
                 scaling = None
         hd = d.get("head_dim") or d["hidden_size"] // d["num_attention_heads"]
         extra = {}
-        if mt == "deepseek_v3":
+        if mt in ("deepseek_v3", "mistral4"):
             n_exp, width, dense_width = d["n_routed_experts"], d["moe_intermediate_size"], d["intermediate_size"]
-            topk, renorm = d.get("num_experts_per_tok", 8), d.get("norm_topk_prob", True)
+            topk, renorm = d.get("num_experts_per_tok", 8 if mt == "deepseek_v3" else 4), d.get("norm_topk_prob", True)
             hd = int(d.get("qk_rope_head_dim", 64))            # the rotary table is built for the rotary slice
-            extra = dict(score_function="sigmoid", router_bias=True, n_group=int(d.get("n_group", 1)),
+            routing = dict(score_function="sigmoid", router_bias=True)
+            if mt == "mistral4":
+                routing = dict(score_function="softmax", router_bias=False)
+                beta = float(rp.get("llama_4_scaling_beta") or 0.0)
+                if beta:
+                    routing.update(query_scale_beta=beta, query_scale_period=int(rp["original_max_position_embeddings"]))
+                if scaling:
+                    for key in ("llama_4_scaling_beta", "max_position_embeddings"):
+                        scaling.pop(key, None)
+            extra = dict(**routing, n_group=int(d.get("n_group", 1)),
                          topk_group=int(d.get("topk_group", 1)), routed_scaling_factor=float(d.get("routed_scaling_factor", 1.0)),
                          shared_expert_intermediate_size=int(d.get("n_shared_experts", 0) or 0) * width,
                          mlp_only_layers=list(range(int(d.get("first_k_dense_replace", 0)))), use_qk_norm=False,

@@ -1,4 +1,4 @@
-"""Multi-head latent attention (DeepSeek-V2 / V3): queries pass through a low-rank bottleneck with its own RMSNorm,
+"""Multi-head latent attention (DeepSeek-V2 / V3, Mistral 4): queries pass through a low-rank bottleneck with its own RMSNorm,
 keys and values are expanded from one shared latent vector per token, and the rotary embedding acts on a separate
 slice of every query head and on ONE key slice shared by all heads.
 
@@ -60,10 +60,11 @@ class LatentAttention(nn.Module):
         self.kv_b_proj = matrix(Hq * (self.nope + self.v_dim), cfg.kv_lora_rank)
         self.o_proj = matrix(H, Hq * self.v_dim)
         self.window, self.sinks, self.lora, self.lowp = 0, None, None, ""
-        # yarn: the softmax temperature grows with the context extension (squared: it scales q and k)
+        # yarn: the softmax temperature grows with the context extension (squared: it scales q and k); Mistral 4 keeps
+        # the plain scale and stretches its queries by position instead (``ctx.query_scale``)
         self.scale = self.qk_dim ** -0.5
         rs = cfg.rope_scaling or {}
-        if rs.get("rope_type", rs.get("type", "default")) != "default" and rs.get("mscale_all_dim"):
+        if cfg.family != "mistral4" and rs.get("rope_type", rs.get("type", "default")) != "default" and rs.get("mscale_all_dim"):
             factor = float(rs["factor"])
             m = 1.0 if factor <= 1.0 else 0.1 * float(rs["mscale_all_dim"]) * math.log(factor) + 1.0
             self.scale *= m * m
@@ -88,6 +89,8 @@ class LatentAttention(nn.Module):
         k_rope = rotate(k_rope.reshape(T, 1, self.rope_dim), ctx.rope, cfg.rope_interleave).expand(-1, Hq, -1)
         q = torch.cat([q[..., :self.nope], q_rope], dim=-1)
         k = torch.cat([k_nope, k_rope], dim=-1)
+        if getattr(ctx, "query_scale", None) is not None:
+            q = q * ctx.query_scale[:, None, None].to(q.dtype)
         if self.v_dim < self.qk_dim:
             v = torch.nn.functional.pad(v, (0, self.qk_dim - self.v_dim))       # the op takes one width; the pad is sliced off below
         cache = ctx.kv_cache

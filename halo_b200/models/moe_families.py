@@ -75,7 +75,7 @@ for _s in (
     MoEFamilySpec("inkling", SEPARATE_GLU, missing="family decoder"),
     MoEFamilySpec("laguna", SEPARATE_GLU, missing="family decoder"),
     MoEFamilySpec("lfm2_moe", SEPARATE_MLP, score_function="sigmoid", selection_bias=True, missing="short-convolution mixer layers"),
-    MoEFamilySpec("mistral4", SEPARATE_MLP, missing="family decoder"),
+    MoEFamilySpec("mistral4", FUSED, grouped_topk=True, shared_experts=True, runnable=True),
     MoEFamilySpec("olmoe", SEPARATE_GLU, norm_topk_prob=False, runnable=True),
     MoEFamilySpec("mixtral", SEPARATE_MLP, router_name="block_sparse_moe.gate", experts_prefix="block_sparse_moe.experts",
                   runnable=True),

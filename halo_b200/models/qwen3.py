@@ -364,9 +364,9 @@ class SparseMoE(nn.Module):
             idx = forced.to(logits.device)
             if partial:                   # merged on the device: no host read of "is anything missing"
                 with torch.no_grad():
-                    own, _ = (moe_ops.router_sigmoid_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob, bias, cfg.n_group,
-                                                          cfg.topk_group, cfg.routed_scaling_factor)
-                              if cfg.score_function == "sigmoid" else
+                    own, _ = (moe_ops.router_grouped_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob, bias, cfg.n_group,
+                                                          cfg.topk_group, cfg.routed_scaling_factor, cfg.score_function)
+                              if cfg.grouped_routing else
                               moe_ops.router_topk(logits.detach(), cfg.num_experts_per_tok, cfg.norm_topk_prob, bias))
                 idx = torch.where(idx < 0, own.to(idx.dtype), idx)
             idx = idx.to(torch.int32)
@@ -375,9 +375,9 @@ class SparseMoE(nn.Module):
             if cfg.norm_topk_prob:
                 w = w / (w.sum(-1, keepdim=True) + (1e-20 if cfg.score_function == "sigmoid" else 0.0))
             w = w * cfg.routed_scaling_factor
-        elif cfg.score_function == "sigmoid":
-            idx, w = moe_ops.router_sigmoid_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob, bias, cfg.n_group,
-                                                 cfg.topk_group, cfg.routed_scaling_factor)
+        elif cfg.grouped_routing:
+            idx, w = moe_ops.router_grouped_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob, bias, cfg.n_group,
+                                                 cfg.topk_group, cfg.routed_scaling_factor, cfg.score_function)
         else:
             idx, w = moe_ops.router_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob, self.selection_bias)
         if self.load_counter is not None and not getattr(ctx, "output_unused", False):
@@ -538,6 +538,7 @@ class ForwardContext:
         self.kv_cache = None         # halo_b200.inference.generate.KVCache while sampling
         self.attention_mask = None   # bool [T, T]: an explicit mask (tree packing) served by the masked-attention op
         self.rope_local = None       # rotary table of the windowed layers when their base differs (Gemma 3)
+        self.query_scale = None      # [T] fp32: per-position stretch of the queries (Mistral 4), else None
         self._window_plans = {}      # window size -> attention plan cut to that window (built on first use)
 
     def window_plan(self, window: int):
@@ -674,7 +675,15 @@ class Qwen3Model(nn.Module):
         plan = attn_ops.build_plan(cu_seqlens, device=dev)
         ctx = ForwardContext(plan, rope, self.transport, record_routing, replay_topk, tp=self.tensor_parallel)
         ctx.rope_local = self.rope_local(position_ids)
+        ctx.query_scale = self.query_scale(position_ids)
         return ctx
+
+    def query_scale(self, position_ids):
+        """``1 + beta * log(1 + floor(position / period))`` per token, or None for families without it."""
+        beta, period = self.cfg.query_scale_beta, self.cfg.query_scale_period
+        if not beta or not period:
+            return None
+        return 1.0 + beta * torch.log1p(torch.floor(position_ids.reshape(-1).float() / period))
 
     def rope_local(self, position_ids):
         """The windowed layers' own table (their rotary base, no scaling), or None when they share the full layers'."""

@@ -47,13 +47,13 @@ def router_topk_reference(logits: torch.Tensor, k: int, renorm: bool, sel_bias: 
     return idx.to(torch.int32), w
 
 
-def router_sigmoid_topk(logits: torch.Tensor, k: int, renorm: bool, sel_bias: torch.Tensor | None = None, n_group: int = 1,
-                        topk_group: int = 1, scaling: float = 1.0):
-    """Routing of the sigmoid-score families (DeepSeek-V3 / GLM-4 style): scores = sigmoid(logits); the ranking adds the
-    selection bias and, with ``n_group > 1``, keeps only the ``topk_group`` groups of experts whose two best biased
+def router_grouped_topk(logits: torch.Tensor, k: int, renorm: bool, sel_bias: torch.Tensor | None = None, n_group: int = 1,
+                        topk_group: int = 1, scaling: float = 1.0, score: str = "sigmoid"):
+    """Group-limited routing (DeepSeek-V3 / GLM-4 with sigmoid scores, Mistral 4 with softmax scores): the ranking adds
+    the selection bias and, with ``n_group > 1``, keeps only the ``topk_group`` groups of experts whose two best biased
     scores sum highest; the weights are the unbiased scores of the chosen experts, renormalised and scaled. Tensor
     ops with autograd (the score matrix is ``[T, E]``: small beside the expert products)."""
-    scores = torch.sigmoid(logits.float())
+    scores = torch.sigmoid(logits.float()) if score == "sigmoid" else torch.softmax(logits.float(), dim=-1)
     choice = scores if sel_bias is None else scores + sel_bias.float()
     if n_group > 1:
         T, E = choice.shape
@@ -66,6 +66,10 @@ def router_sigmoid_topk(logits: torch.Tensor, k: int, renorm: bool, sel_bias: to
     if renorm:
         w = w / (w.sum(-1, keepdim=True) + 1e-20)
     return idx.to(torch.int32), w * scaling
+
+
+def router_sigmoid_topk(logits, k, renorm, sel_bias=None, n_group=1, topk_group=1, scaling=1.0):
+    return router_grouped_topk(logits, k, renorm, sel_bias, n_group, topk_group, scaling, "sigmoid")
 
 
 class _RouterTopK(torch.autograd.Function):

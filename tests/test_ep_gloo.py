@@ -3,6 +3,7 @@ one process that sees the whole batch (the plumbing configuration: 4 layers, hid
 width 128, top-2, vocab 4096, fp32, packed 512-token rows, micro-batch 2 per rank, AdamW 1e-4, 20 steps)."""
 
 import numpy as np
+import pytest
 import torch
 
 from halo_b200.data.packing import pack_documents
@@ -164,11 +165,12 @@ def _latent_family_worker(rank, world, directory):
     assert torch.allclose(a, b, atol=1e-5)
 
 
-def test_latent_attention_family_under_expert_parallelism(tmp_path):
+@pytest.mark.parametrize("family", ["deepseek_v3", "mistral4"])       # the second stores each expert bank as ONE tensor
+def test_latent_attention_family_under_expert_parallelism(tmp_path, family):
     from halo_b200.checkpoint.save import save_model
     from halo_b200.models.qwen3 import build_model
     from tests.test_families_cpu import family_config
 
-    model = build_model(family_config("deepseek_v3"), device="cpu", seed=9, gradient_checkpointing=False)
+    model = build_model(family_config(family), device="cpu", seed=9, gradient_checkpointing=False)
     save_model(model, str(tmp_path / "ckpt"), save_dtype=None)
     run_gloo_ranks(_latent_family_worker, 2, args=(str(tmp_path / "ckpt"),), timeout=240.0)

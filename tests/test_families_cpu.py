@@ -46,6 +46,13 @@ def family_config(family: str, **kw) -> ModelConfig:
         base.update(num_experts=8, score_function="sigmoid", router_bias=True, n_group=2, topk_group=1, routed_scaling_factor=2.5,
                     shared_expert_intermediate_size=96, mlp_only_layers=[0], use_qk_norm=False, num_key_value_heads=4, head_dim=16,
                     kv_lora_rank=32, q_lora_rank=48, qk_nope_head_dim=24, qk_rope_head_dim=16, v_head_dim=20)
+    if family == "mistral4":
+        # positions reach past the period (so the query stretch is visible), two of four groups eligible
+        base.update(num_experts=8, n_group=4, topk_group=2, routed_scaling_factor=1.5, shared_expert_intermediate_size=96,
+                    mlp_only_layers=[0], use_qk_norm=False, num_key_value_heads=4, head_dim=16, kv_lora_rank=32, q_lora_rank=48,
+                    qk_nope_head_dim=24, qk_rope_head_dim=16, v_head_dim=20, query_scale_beta=0.3, query_scale_period=16,
+                    rope_scaling={"rope_type": "yarn", "factor": 4.0, "beta_fast": 32.0, "beta_slow": 1.0, "mscale": 1.0,
+                                  "mscale_all_dim": 1.0, "original_max_position_embeddings": 16})
     if family == "gpt_oss":
         base.update(intermediate_size=96, sliding_window=16, layer_types=["sliding_attention", "full_attention"], attention_sinks=True,
                     output_bias=True, router_logit_bias=True, expert_bias=True, expert_activation="clamped_glu", rms_norm_eps=1e-5,
@@ -69,7 +76,9 @@ CASES = [("mistral", {"sliding_window": 16}), ("qwen2", {"sliding_window": 24}),
          ("gpt_oss", {}), ("gemma2", {}), ("gemma3_text", {}), ("gemma3_text", {"rope_scaling": {"rope_type": "linear", "factor": 8.0}, "tie_word_embeddings": False}),
          ("deepseek_v3", {}), ("deepseek_v3", {"q_lora_rank": 0, "rope_interleave": False}),
          ("deepseek_v3", {"rope_scaling": {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 64, "mscale": 1.0,
-                                           "mscale_all_dim": 1.0, "beta_fast": 32.0, "beta_slow": 1.0}})]
+                                           "mscale_all_dim": 1.0, "beta_fast": 32.0, "beta_slow": 1.0}}),
+         ("mistral4", {}), ("mistral4", {"q_lora_rank": 0, "rope_interleave": False, "n_group": 1, "topk_group": 1,
+                                         "routed_scaling_factor": 1.0, "query_scale_beta": 0.0, "query_scale_period": 0})]
 
 
 @pytest.mark.parametrize("family,extra", CASES, ids=[f"{f}-{'-'.join(e) or 'plain'}" for f, e in CASES])
@@ -116,7 +125,8 @@ def test_family_round_trip_through_transformers(tmp_path, family, extra):
     d = str(tmp_path / "hf")
     save_model(model, d, save_dtype=None)
     assert ModelConfig.load(d) == cfg
-    hf = transformers.AutoModelForCausalLM.from_pretrained(d, torch_dtype=torch.float32, attn_implementation="eager")
+    # by the architecture's own class: not every text model is registered with the causal-LM auto class
+    hf = getattr(transformers, FAMILIES[family]["architecture"]).from_pretrained(d, dtype=torch.float32, attn_implementation="eager")
     hf.eval()
     assert type(hf).__name__ == FAMILIES[family]["architecture"]
     ids = np.random.default_rng(2).integers(0, cfg.vocab_size, size=96)
@@ -253,18 +263,19 @@ def test_keys_visited_follow_each_layers_window():
     assert keys_visited_per_layer(plain, cu) == [full] * 2
 
 
-@pytest.mark.parametrize("streams", [1, 2])
-def test_latent_attention_model_trains(streams):
+@pytest.mark.parametrize("family,streams", [("deepseek_v3", 1), ("deepseek_v3", 2), ("mistral4", 1)])
+def test_latent_attention_model_trains(family, streams):
     """DeepSeek-V3 shape (latent attention, sigmoid group-limited routing, shared experts, a leading dense layer) takes
-    optimizer steps under per-layer recomputation - also on two hyper-connected residual streams; layouts that would cut
-    the attention block are refused by name."""
+    optimizer steps under per-layer recomputation - also on two hyper-connected residual streams - and so does the
+    Mistral 4 shape (softmax scores, position-stretched queries); layouts that would cut the attention block are refused
+    by name."""
     from halo_b200.config_validation import ConfigError
     from halo_b200.data.packing import synthetic_packed_batch
     from halo_b200.parallel.config import ParallelismConfig
     from halo_b200.parallel.rules import reject_model_layout
     from halo_b200.trainers.engine import TrainEngine
 
-    cfg = family_config("deepseek_v3", hc_mult=streams)
+    cfg = family_config(family, hc_mult=streams)
     model = build_model(cfg, device="cpu", seed=2, gradient_checkpointing=True)
     assert sum(p.numel() for p in model.parameters()) == cfg.param_counts()["total"]
     engine = TrainEngine(model, torch.optim.AdamW(model.parameters(), lr=3e-3), "cpu", max_grad_norm=1.0)

@@ -49,6 +49,13 @@ def latent_cfg():
                        max_position_embeddings=64)
 
 
+def stretched_cfg():
+    """Mistral 4 style: latent attention with softmax group-limited routing and queries stretched by position; the period
+    (4) is shorter than the prompts, so prefill and decode steps both cross it."""
+    return dataclasses.replace(latent_cfg(), model_type="mistral4", score_function="softmax", router_bias=False, n_group=2, topk_group=1,
+                               routed_scaling_factor=1.5, query_scale_beta=0.4, query_scale_period=4)
+
+
 def gemma_cfg():
     """Gemma 3 style: windowed layers with their own rotary base, a full layer, output norms, tanh-GELU gate, scaled embeddings."""
     return dataclasses.replace(dense_cfg(), model_type="gemma3_text", num_hidden_layers=3, sliding_window=6, max_position_embeddings=64,
@@ -63,9 +70,9 @@ def capped_cfg():
                                use_qk_norm=False, rope_local_theta=0.0, attn_logit_softcapping=1.0, final_logit_softcapping=0.5)
 
 
-@pytest.mark.parametrize("kind", ["dense", "moe", "windowed", "sinks", "latent", "gemma", "capped"])
+@pytest.mark.parametrize("kind", ["dense", "moe", "windowed", "sinks", "latent", "stretched", "gemma", "capped"])
 def test_cached_decoding_equals_the_full_forward(kind):
-    cfg = {"dense": dense_cfg, "windowed": windowed_cfg, "sinks": sink_cfg, "latent": latent_cfg, "gemma": gemma_cfg, "capped": capped_cfg,
+    cfg = {"dense": dense_cfg, "windowed": windowed_cfg, "sinks": sink_cfg, "latent": latent_cfg, "stretched": stretched_cfg, "gemma": gemma_cfg, "capped": capped_cfg,
            "moe": lambda: dataclasses.replace(tiny_moe_config(), num_hidden_layers=2, vocab_size=128)}[kind]()
     model = build_model(cfg, device="cpu", seed=7, gradient_checkpointing=False)
     if kind == "sinks":
