@@ -24,6 +24,7 @@ MOE_HUB_NAMES = {
     "glm4_moe": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "deepseek_v3": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "mistral4": ("mlp", "gate_proj", "up_proj", "down_proj"),
+    "lfm2_moe": ("feed_forward", "w1", "w3", "w2"),
     "olmoe": ("mlp", "gate_proj", "up_proj", "down_proj"),
 }
 # gpt-oss stores each bank as ONE tensor, transposed, with gate and up columns interleaved (``INTERLEAVED_GLU``);
@@ -76,11 +77,35 @@ def stored_with_unit_offset(name: str, cfg) -> bool:
     return name == "norm" or bool(m and m.group(2) in LAYER_NORMS + ("self_attn.q_norm", "self_attn.k_norm"))
 
 
+# families whose hub names differ from the common ones only by substitution: (common fragment, family's fragment), applied
+# in order to every hub name the common rules produce
+_FAMILY_RENAMES = {
+    "lfm2_moe": (("model.norm.weight", "model.embedding_norm.weight"), (".input_layernorm.", ".operator_norm."),
+                 (".post_attention_layernorm.", ".ffn_norm."), (".self_attn.o_proj.", ".self_attn.out_proj."),
+                 (".self_attn.q_norm.", ".self_attn.q_layernorm."), (".self_attn.k_norm.", ".self_attn.k_layernorm."),
+                 (".mlp.gate_proj.", ".feed_forward.w1."), (".mlp.up_proj.", ".feed_forward.w3."),
+                 (".mlp.down_proj.", ".feed_forward.w2."), (".feed_forward.gate.e_score_correction_bias", ".feed_forward.expert_bias")),
+}
+
+
 def runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, expert_offset: int = 0) -> dict:
-    if stored_with_unit_offset(name, cfg):
-        tensor = tensor - 1
     """One runtime tensor -> {hub name: tensor}. ``first_layer``: global index of ``layers.0`` (pipeline
     stages); ``expert_offset``: global index of local expert 0 (expert-parallel shards)."""
+    out = _common_runtime_to_hub(name, tensor, cfg, first_layer, expert_offset)
+    renames = _FAMILY_RENAMES.get(getattr(cfg, "family", ""))
+    if not renames:
+        return out
+    renamed = {}
+    for hub, t in out.items():
+        for old, new in renames:
+            hub = hub.replace(old, new)
+        renamed[hub] = t
+    return renamed
+
+
+def _common_runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, expert_offset: int = 0) -> dict:
+    if stored_with_unit_offset(name, cfg):
+        tensor = tensor - 1
     if name == "embed_tokens":
         return {"model.embed_tokens.weight": tensor}
     if name == "norm":
@@ -97,8 +122,8 @@ def runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, e
                "mtp.output_norm": "shared_head.norm.weight"}
         if name in own:
             return {f"model.layers.{cfg.num_hidden_layers}.{own[name]}": tensor}
-        return runtime_to_hub(f"layers.{cfg.num_hidden_layers - first_layer}." + name[len("mtp.layer."):], tensor, cfg, first_layer,
-                              expert_offset)
+        return _common_runtime_to_hub(f"layers.{cfg.num_hidden_layers - first_layer}." + name[len("mtp.layer."):], tensor, cfg,
+                                      first_layer, expert_offset)
     m = _LAYER.match(name)
     if not m:
         raise KeyError(f"no hub name for runtime parameter {name!r}")
@@ -123,6 +148,10 @@ def runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: int = 0, e
               "self_attn.kv_a_norm": "kv_a_layernorm.weight", "self_attn.kv_b_proj": "kv_b_proj.weight"}
     if rest in latent:          # multi-head latent attention (DeepSeek)
         return {pre + "self_attn." + latent[rest]: tensor}
+    conv = {"self_attn.conv_in_proj": "conv.in_proj.weight", "self_attn.conv_taps": "conv.conv.weight",
+            "self_attn.conv_out_proj": "conv.out_proj.weight"}
+    if rest in conv:            # gated short-convolution mixer (LFM2)
+        return {pre + conv[rest]: tensor}
     if rest == "self_attn.o_bias":
         return {pre + "self_attn.o_proj.bias": tensor}
     if rest == "self_attn.sinks":

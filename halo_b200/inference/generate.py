@@ -55,6 +55,7 @@ class KVCache:
         self.mode = "prefill"
         self._layer = 0
         self._rows = self._cols = None
+        self._conv: dict[int, torch.Tensor] = {}      # layer index -> [batch, taps - 1, hidden]: a conv mixer's recent inputs
 
     def begin_prefill(self, seq_of_token: torch.Tensor, pos_of_token: torch.Tensor, lengths: torch.Tensor) -> None:
         self.mode, self._layer = "prefill", 0
@@ -71,6 +72,21 @@ class KVCache:
 
     def end_decode(self) -> None:
         self.lengths += 1
+
+    def conv_state(self, layer: int, depth: int, like: torch.Tensor) -> torch.Tensor:
+        """The last ``depth`` inputs of a short-convolution layer per sequence, oldest first (zeros before a sequence's start)."""
+        st = self._conv.get(layer)
+        if st is None:
+            st = self._conv[layer] = torch.zeros(self.k.shape[1], depth, like.shape[-1], dtype=like.dtype, device=like.device)
+        return st
+
+    def store_conv_tail(self, layer: int, depth: int, x: torch.Tensor) -> None:
+        """Prefill: keep every prompt's last ``depth`` rows of ``x [T, hidden]`` (packed prompts) for the decode steps."""
+        st = self.conv_state(layer, depth, x)
+        st.zero_()
+        slot = self._cols - (self._prefill_lengths[self._rows] - depth)
+        keep = slot >= 0
+        st[self._rows[keep], slot[keep]] = x[keep]
 
     def write(self, k: torch.Tensor, v: torch.Tensor) -> int:
         """Store this layer's keys / values ``[T, kv_heads * head_dim]``; returns the layer's index."""
@@ -246,6 +262,7 @@ class Generator:
             dctx = ForwardContext(None, m.rope(cache.lengths), m.transport)
             dctx.rope_local = m.rope_local(cache.lengths)
             dctx.query_scale = m.query_scale(cache.lengths)
+            dctx.positions = cache.lengths
             dctx.kv_cache = cache
             dctx.routing_trace = trace
             trunk = m.trunk_states(tok, dctx)

@@ -45,6 +45,9 @@ FAMILIES = {
     # Mistral 4: the DeepSeek-V3 block (latent attention, shared experts, group-limited routing) with softmax router
     # scores, expert banks stored whole, and queries scaled by 1 + beta * log(1 + floor(position / period))
     "mistral4": dict(architecture="Mistral4ForCausalLM", moe=True, qk_norm=False, bias_key=True, bias_default=False, has_window=False),
+    # LFM2-MoE: gated short-convolution mixers in the layers ``layer_types`` names ``conv``, attention with per-head q / k
+    # norms in the others; sigmoid router scores ranked with a stored per-expert bias; leading dense layers
+    "lfm2_moe": dict(architecture="Lfm2MoeForCausalLM", moe=True, qk_norm=True, bias_key=False, bias_default=False, has_window=False),
     "gpt_oss": dict(architecture="GptOssForCausalLM", moe=True, qk_norm=False, bias_key=True, bias_default=True, has_window=True),
 }
 
@@ -77,6 +80,8 @@ class ModelConfig:
     n_group: int = 1                       # group-limited routing: experts in ``n_group`` groups, ``topk_group`` of them eligible
     topk_group: int = 1
     routed_scaling_factor: float = 1.0
+    norm_topk_eps: float = 1e-20           # added to the sum the chosen weights are divided by (group-limited path)
+    conv_kernel: int = 0                   # taps of the short-convolution mixer in the layers ``layer_types`` names "conv" (LFM2)
     query_scale_beta: float = 0.0          # > 0: queries times 1 + beta * log(1 + floor(position / query_scale_period)) (Mistral 4)
     query_scale_period: int = 0
     sliding_window: int = 0                # > 0: every query sees only its last ``sliding_window`` keys (Mistral-style)
@@ -125,6 +130,10 @@ class ModelConfig:
         """The router ranks through the group-limited path (tensor ops) instead of the plain softmax top-k kernel."""
         return self.score_function == "sigmoid" or self.n_group > 1 or self.routed_scaling_factor != 1.0
 
+    def layer_is_conv(self, i: int) -> bool:
+        """The layer's mixer is a gated short convolution instead of attention."""
+        return bool(self.layer_types) and i < len(self.layer_types) and self.layer_types[i] == "conv"
+
     def layer_is_moe(self, i: int) -> bool:
         return self.is_moe and i not in self.mlp_only_layers and (i + 1) % self.decoder_sparse_step == 0
 
@@ -151,13 +160,15 @@ class ModelConfig:
         shared += self.num_experts if self.router_bias else 0
         shared += self.num_experts if self.router_logit_bias else 0
         total = active = 0
+        conv_mixer = 4 * H * H + H * self.conv_kernel + 2 * H        # in / out projections, taps, the layer's two norms
         for i in range(self.num_hidden_layers):
+            mixer = conv_mixer if self.layer_is_conv(i) else attn
             if self.layer_is_moe(i):
-                total += attn + self.num_experts * expert + self.num_experts * H + shared
-                active += attn + self.num_experts_per_tok * expert + self.num_experts * H + shared
+                total += mixer + self.num_experts * expert + self.num_experts * H + shared
+                active += mixer + self.num_experts_per_tok * expert + self.num_experts * H + shared
             else:
-                total += attn + dense_mlp
-                active += attn + dense_mlp
+                total += mixer + dense_mlp
+                active += mixer + dense_mlp
         if self.num_nextn_predict_layers:
             L = self.num_hidden_layers
             moe = self.layer_is_moe(L)
@@ -282,6 +293,21 @@ class ModelConfig:
                     d["rope_parameters"]["llama_4_scaling_beta"] = self.query_scale_beta
                     d["rope_parameters"].setdefault("original_max_position_embeddings",
                                                     self.query_scale_period or self.max_position_embeddings)
+        elif self.family == "lfm2_moe":
+            first_dense = 0
+            while first_dense in self.mlp_only_layers:
+                first_dense += 1
+            if sorted(self.mlp_only_layers) != list(range(first_dense)):
+                raise ValueError("lfm2_moe stores its dense layers as a leading run (num_dense_layers)")
+            for key in ("rms_norm_eps", "rope_theta", "rope_scaling", "hidden_act", "attention_dropout"):
+                d.pop(key, None)
+            if self.head_dim * self.num_attention_heads == self.hidden_size:
+                d.pop("head_dim")
+            d.update({"norm_eps": self.rms_norm_eps, "num_dense_layers": first_dense, "num_experts": self.num_experts,
+                      "num_experts_per_tok": self.num_experts_per_tok, "moe_intermediate_size": self.moe_intermediate_size,
+                      "use_expert_bias": self.router_bias, "routed_scaling_factor": self.routed_scaling_factor,
+                      "norm_topk_prob": self.norm_topk_prob, "conv_bias": False, "conv_L_cache": self.conv_kernel,
+                      "layer_types": list(self.layer_types or ["full_attention"] * self.num_hidden_layers)})
         elif self.family == "olmoe":
             d.update({"num_experts": self.num_experts, "num_experts_per_tok": self.num_experts_per_tok,
                       "norm_topk_prob": self.norm_topk_prob, "intermediate_size": self.moe_intermediate_size, "clip_qkv": None,
@@ -363,6 +389,16 @@ class ModelConfig:
                          kv_lora_rank=int(d["kv_lora_rank"]), q_lora_rank=int(d.get("q_lora_rank") or 0),
                          qk_nope_head_dim=int(d["qk_nope_head_dim"]), qk_rope_head_dim=hd, v_head_dim=int(d["v_head_dim"]),
                          rope_interleave=bool(d.get("rope_interleave", True)))
+        elif mt == "lfm2_moe":
+            if d.get("conv_bias"):
+                raise ValueError("lfm2_moe with conv_bias: the biased convolution and projections are not built")
+            n_exp, width, dense_width = d["num_experts"], d["moe_intermediate_size"], d["intermediate_size"]
+            topk, renorm = d.get("num_experts_per_tok", 4), d.get("norm_topk_prob", True)
+            extra = dict(score_function="sigmoid", router_bias=bool(d.get("use_expert_bias", True)), norm_topk_eps=1e-6,
+                         routed_scaling_factor=float(d.get("routed_scaling_factor", 1.0)),
+                         mlp_only_layers=list(range(int(d.get("num_dense_layers", 2)))), rms_norm_eps=float(d.get("norm_eps", 1e-5)),
+                         conv_kernel=int(d.get("conv_L_cache", 3)), layer_types=list(d["layer_types"]),
+                         tie_word_embeddings=bool(d.get("tie_word_embeddings", d.get("tie_embedding", True))))
         elif mt == "glm4_moe":
             n_exp, width, dense_width = d["n_routed_experts"], d["moe_intermediate_size"], d["intermediate_size"]
             topk, renorm = d.get("num_experts_per_tok", 8), d.get("norm_topk_prob", True)

@@ -74,7 +74,8 @@ for _s in (
     MoEFamilySpec("cohere2_moe", SEPARATE_GLU, missing="parallel attention/FFN block, layer norm"),
     MoEFamilySpec("inkling", SEPARATE_GLU, missing="family decoder"),
     MoEFamilySpec("laguna", SEPARATE_GLU, missing="family decoder"),
-    MoEFamilySpec("lfm2_moe", SEPARATE_MLP, score_function="sigmoid", selection_bias=True, missing="short-convolution mixer layers"),
+    MoEFamilySpec("lfm2_moe", SEPARATE_MLP, score_function="sigmoid", selection_bias=True, router_name="feed_forward.gate",
+                  experts_prefix="feed_forward.experts", runnable=True),
     MoEFamilySpec("mistral4", FUSED, grouped_topk=True, shared_experts=True, runnable=True),
     MoEFamilySpec("olmoe", SEPARATE_GLU, norm_topk_prob=False, runnable=True),
     MoEFamilySpec("mixtral", SEPARATE_MLP, router_name="block_sparse_moe.gate", experts_prefix="block_sparse_moe.experts",

@@ -365,7 +365,7 @@ class SparseMoE(nn.Module):
             if partial:                   # merged on the device: no host read of "is anything missing"
                 with torch.no_grad():
                     own, _ = (moe_ops.router_grouped_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob, bias, cfg.n_group,
-                                                          cfg.topk_group, cfg.routed_scaling_factor, cfg.score_function)
+                                                          cfg.topk_group, cfg.routed_scaling_factor, cfg.score_function, cfg.norm_topk_eps)
                               if cfg.grouped_routing else
                               moe_ops.router_topk(logits.detach(), cfg.num_experts_per_tok, cfg.norm_topk_prob, bias))
                 idx = torch.where(idx < 0, own.to(idx.dtype), idx)
@@ -373,11 +373,11 @@ class SparseMoE(nn.Module):
             probs = torch.sigmoid(logits.float()) if cfg.score_function == "sigmoid" else torch.softmax(logits.float(), dim=-1)
             w = probs.gather(-1, idx.long())
             if cfg.norm_topk_prob:
-                w = w / (w.sum(-1, keepdim=True) + (1e-20 if cfg.score_function == "sigmoid" else 0.0))
+                w = w / (w.sum(-1, keepdim=True) + (cfg.norm_topk_eps if cfg.grouped_routing else 0.0))
             w = w * cfg.routed_scaling_factor
         elif cfg.grouped_routing:
             idx, w = moe_ops.router_grouped_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob, bias, cfg.n_group,
-                                                 cfg.topk_group, cfg.routed_scaling_factor, cfg.score_function)
+                                                 cfg.topk_group, cfg.routed_scaling_factor, cfg.score_function, cfg.norm_topk_eps)
         else:
             idx, w = moe_ops.router_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob, self.selection_bias)
         if self.load_counter is not None and not getattr(ctx, "output_unused", False):
@@ -434,7 +434,11 @@ class DecoderLayer(nn.Module):
         H = cfg.hidden_size
         self.input_layernorm = nn.Parameter(torch.ones(H, dtype=dtype, device=device))
         self.post_attention_layernorm = nn.Parameter(torch.ones(H, dtype=dtype, device=device))
-        if cfg.kv_lora_rank:
+        if cfg.layer_is_conv(idx):
+            from .short_conv import ShortConv
+
+            self.self_attn = ShortConv(cfg, dtype, device, tp_size, idx)
+        elif cfg.kv_lora_rank:
             from .latent_attention import LatentAttention
 
             self.self_attn = LatentAttention(cfg, dtype, device, tp_size, idx)
@@ -539,6 +543,7 @@ class ForwardContext:
         self.attention_mask = None   # bool [T, T]: an explicit mask (tree packing) served by the masked-attention op
         self.rope_local = None       # rotary table of the windowed layers when their base differs (Gemma 3)
         self.query_scale = None      # [T] fp32: per-position stretch of the queries (Mistral 4), else None
+        self.positions = None        # [T]: each token's index inside its document (the segment marks of convolution mixers)
         self._window_plans = {}      # window size -> attention plan cut to that window (built on first use)
 
     def window_plan(self, window: int):
@@ -676,6 +681,7 @@ class Qwen3Model(nn.Module):
         ctx = ForwardContext(plan, rope, self.transport, record_routing, replay_topk, tp=self.tensor_parallel)
         ctx.rope_local = self.rope_local(position_ids)
         ctx.query_scale = self.query_scale(position_ids)
+        ctx.positions = position_ids.reshape(-1)
         return ctx
 
     def query_scale(self, position_ids):

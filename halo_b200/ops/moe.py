@@ -48,7 +48,7 @@ def router_topk_reference(logits: torch.Tensor, k: int, renorm: bool, sel_bias: 
 
 
 def router_grouped_topk(logits: torch.Tensor, k: int, renorm: bool, sel_bias: torch.Tensor | None = None, n_group: int = 1,
-                        topk_group: int = 1, scaling: float = 1.0, score: str = "sigmoid"):
+                        topk_group: int = 1, scaling: float = 1.0, score: str = "sigmoid", eps: float = 1e-20):
     """Group-limited routing (DeepSeek-V3 / GLM-4 with sigmoid scores, Mistral 4 with softmax scores): the ranking adds
     the selection bias and, with ``n_group > 1``, keeps only the ``topk_group`` groups of experts whose two best biased
     scores sum highest; the weights are the unbiased scores of the chosen experts, renormalised and scaled. Tensor
@@ -64,7 +64,7 @@ def router_grouped_topk(logits: torch.Tensor, k: int, renorm: bool, sel_bias: to
     idx = choice.detach().topk(k, dim=-1).indices
     w = scores.gather(-1, idx)
     if renorm:
-        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+        w = w / (w.sum(-1, keepdim=True) + eps)
     return idx.to(torch.int32), w * scaling
 
 

@@ -227,5 +227,8 @@ def reject_model_layout(pc, model_cfg, packed: bool = True) -> None:
     if getattr(model_cfg, "kv_lora_rank", 0) and (pc.tp_size > 1 or pc.cp_size > 1):
         raise ConfigError(f"{model_cfg.family}: latent attention runs on whole rows with all heads on every rank; drop "
                           f"tensor_parallel_size / context_parallel_size (expert and pipeline parallelism are fine)")
+    if getattr(model_cfg, "conv_kernel", 0) and (pc.tp_size > 1 or pc.cp_size > 1):
+        raise ConfigError(f"{model_cfg.family}: the short-convolution mixer reads a token's predecessors in its row, so rows are not "
+                          f"cut; drop tensor_parallel_size / context_parallel_size (expert and pipeline parallelism are fine)")
     if pc.pp_size > 1 and model_cfg.num_hidden_layers < pc.pp_size:
         raise ConfigError(f"{model_cfg.num_hidden_layers} layers cannot fill {pc.pp_size} pipeline stages")

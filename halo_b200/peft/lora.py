@@ -184,6 +184,8 @@ def apply_lora(model, spec: LoraSpec, seed: int = 0) -> dict:
         gi = li + first_layer
         shapes = {t: s for t, s in (("q_proj", (q_rows, H)), ("k_proj", (kv_rows, H)), ("v_proj", (kv_rows, H)),
                                     ("o_proj", (H, q_rows))) if t in dense}
+        if hasattr(layer.self_attn, "conv_taps"):
+            shapes = {}            # a short-convolution mixer has no q / k / v / o projections: attention targets skip the layer
         layer.self_attn.lora = LoraSet(spec, shapes, dtype, device, seed * 7919 + gi * 4 + 0) if shapes else None
         mlps = []
         if hasattr(layer.mlp, "experts_gate_up"):

@@ -53,6 +53,10 @@ def family_config(family: str, **kw) -> ModelConfig:
                     qk_nope_head_dim=24, qk_rope_head_dim=16, v_head_dim=20, query_scale_beta=0.3, query_scale_period=16,
                     rope_scaling={"rope_type": "yarn", "factor": 4.0, "beta_fast": 32.0, "beta_slow": 1.0, "mscale": 1.0,
                                   "mscale_all_dim": 1.0, "original_max_position_embeddings": 16})
+    if family == "lfm2_moe":
+        base.update(num_hidden_layers=4, layer_types=["conv", "conv", "full_attention", "conv"], conv_kernel=3, num_experts=8,
+                    score_function="sigmoid", router_bias=True, norm_topk_eps=1e-6, routed_scaling_factor=1.5, mlp_only_layers=[0],
+                    rms_norm_eps=1e-5, tie_word_embeddings=True)
     if family == "gpt_oss":
         base.update(intermediate_size=96, sliding_window=16, layer_types=["sliding_attention", "full_attention"], attention_sinks=True,
                     output_bias=True, router_logit_bias=True, expert_bias=True, expert_activation="clamped_glu", rms_norm_eps=1e-5,
@@ -77,6 +81,8 @@ CASES = [("mistral", {"sliding_window": 16}), ("qwen2", {"sliding_window": 24}),
          ("deepseek_v3", {}), ("deepseek_v3", {"q_lora_rank": 0, "rope_interleave": False}),
          ("deepseek_v3", {"rope_scaling": {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 64, "mscale": 1.0,
                                            "mscale_all_dim": 1.0, "beta_fast": 32.0, "beta_slow": 1.0}}),
+         ("lfm2_moe", {}), ("lfm2_moe", {"conv_kernel": 4, "router_bias": False, "tie_word_embeddings": False,
+                                         "layer_types": ["full_attention", "conv", "conv", "conv"]}),
          ("mistral4", {}), ("mistral4", {"q_lora_rank": 0, "rope_interleave": False, "n_group": 1, "topk_group": 1,
                                          "routed_scaling_factor": 1.0, "query_scale_beta": 0.0, "query_scale_period": 0})]
 
@@ -99,9 +105,18 @@ def test_family_round_trip_through_transformers(tmp_path, family, extra):
                 layer.self_attn.kv_a_norm.normal_(1.0, 0.2, generator=torch.Generator().manual_seed(29))
                 if cfg.q_lora_rank:
                     layer.self_attn.q_a_norm.normal_(1.0, 0.2, generator=torch.Generator().manual_seed(31))
+    if cfg.conv_kernel:
+        with torch.no_grad():
+            g = torch.Generator().manual_seed(41)
+            for layer in model.layers:       # taps near zero would hide a reversed or shifted kernel
+                if hasattr(layer.self_attn, "conv_taps"):
+                    layer.self_attn.conv_taps.normal_(0.0, 0.6, generator=g)
+                    layer.self_attn.conv_in_proj.normal_(0.0, 0.15, generator=g)
     if cfg.use_qk_norm:
         with torch.no_grad():
             for layer in model.layers:       # all-ones norm weights would hide a wrong norm scope
+                if not hasattr(layer.self_attn, "q_norm"):
+                    continue
                 layer.self_attn.q_norm.normal_(1.0, 0.2, generator=torch.Generator().manual_seed(17))
                 layer.self_attn.k_norm.normal_(1.0, 0.2, generator=torch.Generator().manual_seed(19))
     if cfg.router_bias:
@@ -288,6 +303,51 @@ def test_latent_attention_model_trains(family, streams):
         assert f"layers.1.self_attn.{name}" in moved, name
     for axis in ("tp_size", "cp_size"):
         with pytest.raises(ConfigError, match="latent attention"):
+            reject_model_layout(ParallelismConfig(world_size=2, **{axis: 2}), cfg)
+    reject_model_layout(ParallelismConfig(world_size=2, ep_size=2), cfg)
+
+
+def test_short_convolution_family_trains_and_keeps_documents_apart():
+    """LFM2-MoE shape: the taps of a conv layer never reach across a document's first token in a packed row (each
+    document's logits equal the ones it gets alone), the model takes optimizer steps under per-layer recomputation, and
+    layouts that would cut a row are refused by name."""
+    from halo_b200.config_validation import ConfigError
+    from halo_b200.data.packing import synthetic_packed_batch
+    from halo_b200.models.attention_cost import keys_visited_per_layer
+    from halo_b200.parallel.config import ParallelismConfig
+    from halo_b200.parallel.rules import reject_model_layout
+    from halo_b200.trainers.engine import TrainEngine
+
+    cfg = family_config("lfm2_moe")
+    model = build_model(cfg, device="cpu", seed=2, gradient_checkpointing=True)
+    assert sum(p.numel() for p in model.parameters()) == cfg.param_counts()["total"]
+    with torch.no_grad():
+        for layer in model.layers:
+            if hasattr(layer.self_attn, "conv_taps"):
+                layer.self_attn.conv_taps.normal_(0.0, 0.6, generator=torch.Generator().manual_seed(3))
+    rng = np.random.default_rng(4)
+    docs = [rng.integers(0, cfg.vocab_size, size=n) for n in (1, 2, 17, 5)]       # shorter than the kernel, too
+    b = pack_documents(docs)
+    with torch.no_grad():
+        packed = model.hidden_states(b.input_ids, b.position_ids, b.cu_seqlens)
+        start = 0
+        for d in docs:
+            alone, _ = logits_of(model, d)
+            together = packed[start:start + len(d)] @ model.head_weight().t()
+            assert torch.allclose(alone, together, atol=2e-5), float((alone - together).abs().max())
+            start += len(d)
+    visited = keys_visited_per_layer(cfg, [0, 40, 96])
+    assert [v == 0.0 for v in visited] == [True, True, False, True]
+    engine = TrainEngine(model, torch.optim.AdamW(model.parameters(), lr=3e-3), "cpu", max_grad_norm=1.0)
+    batch = synthetic_packed_batch(96, cfg.vocab_size, seed=0, lo=20, hi=50)
+    before = {n: p.detach().clone() for n, p in model.named_parameters()}
+    losses = [float(engine.train_step(batch).loss.reshape(-1)[0]) for _ in range(6)]
+    assert losses[-1] < losses[0] - 0.3, losses
+    moved = {n for n, p in model.named_parameters() if not torch.equal(p, before[n])}
+    for name in ("conv_in_proj", "conv_taps", "conv_out_proj"):
+        assert f"layers.1.self_attn.{name}" in moved, name
+    for axis in ("tp_size", "cp_size"):
+        with pytest.raises(ConfigError, match="short-convolution"):
             reject_model_layout(ParallelismConfig(world_size=2, **{axis: 2}), cfg)
     reject_model_layout(ParallelismConfig(world_size=2, ep_size=2), cfg)
 

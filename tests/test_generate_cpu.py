@@ -56,6 +56,14 @@ def stretched_cfg():
                                routed_scaling_factor=1.5, query_scale_beta=0.4, query_scale_period=4)
 
 
+def conv_cfg():
+    """LFM2-MoE style: short-convolution mixers (4 taps: longer than the shortest prompt) around one attention layer."""
+    return ModelConfig(vocab_size=128, hidden_size=64, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                       intermediate_size=96, moe_intermediate_size=48, num_experts=4, num_experts_per_tok=2, model_type="lfm2_moe",
+                       use_qk_norm=True, score_function="sigmoid", router_bias=True, norm_topk_eps=1e-6, mlp_only_layers=[0],
+                       layer_types=["conv", "full_attention", "conv"], conv_kernel=4, max_position_embeddings=64)
+
+
 def gemma_cfg():
     """Gemma 3 style: windowed layers with their own rotary base, a full layer, output norms, tanh-GELU gate, scaled embeddings."""
     return dataclasses.replace(dense_cfg(), model_type="gemma3_text", num_hidden_layers=3, sliding_window=6, max_position_embeddings=64,
@@ -70,11 +78,16 @@ def capped_cfg():
                                use_qk_norm=False, rope_local_theta=0.0, attn_logit_softcapping=1.0, final_logit_softcapping=0.5)
 
 
-@pytest.mark.parametrize("kind", ["dense", "moe", "windowed", "sinks", "latent", "stretched", "gemma", "capped"])
+@pytest.mark.parametrize("kind", ["dense", "moe", "windowed", "sinks", "latent", "stretched", "conv", "gemma", "capped"])
 def test_cached_decoding_equals_the_full_forward(kind):
-    cfg = {"dense": dense_cfg, "windowed": windowed_cfg, "sinks": sink_cfg, "latent": latent_cfg, "stretched": stretched_cfg, "gemma": gemma_cfg, "capped": capped_cfg,
+    cfg = {"dense": dense_cfg, "windowed": windowed_cfg, "sinks": sink_cfg, "latent": latent_cfg, "stretched": stretched_cfg, "conv": conv_cfg, "gemma": gemma_cfg, "capped": capped_cfg,
            "moe": lambda: dataclasses.replace(tiny_moe_config(), num_hidden_layers=2, vocab_size=128)}[kind]()
     model = build_model(cfg, device="cpu", seed=7, gradient_checkpointing=False)
+    if kind == "conv":
+        with torch.no_grad():
+            for layer in model.layers:       # taps near zero would hide a stale or shifted cache
+                if hasattr(layer.self_attn, "conv_taps"):
+                    layer.self_attn.conv_taps.normal_(0.0, 0.6, generator=torch.Generator().manual_seed(5))
     if kind == "sinks":
         with torch.no_grad():
             for layer in model.layers:
