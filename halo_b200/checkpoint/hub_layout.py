@@ -135,7 +135,8 @@ def _common_runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: in
     if rest.startswith(("attn_hc.", "ffn_hc.")):       # hyper-connection parameters keep their names
         return {pre + rest: tensor}
     if rest == "self_attn.qkv_proj":
-        q, k, v = tensor.split([Hq * D, Hkv * D, Hkv * D], dim=0)
+        # an output gate rides in the query projection (per head: query rows, then gate rows), so that block is twice as tall
+        q, k, v = tensor.split([Hq * D * (2 if getattr(cfg, "attn_output_gate", False) else 1), Hkv * D, Hkv * D], dim=0)
         return {pre + "self_attn.q_proj.weight": q, pre + "self_attn.k_proj.weight": k,
                 pre + "self_attn.v_proj.weight": v}
     if rest == "self_attn.qkv_bias":
@@ -152,6 +153,11 @@ def _common_runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: in
             "self_attn.conv_out_proj": "conv.out_proj.weight"}
     if rest in conv:            # gated short-convolution mixer (LFM2)
         return {pre + conv[rest]: tensor}
+    delta = {"self_attn.gdn_in_proj_qkvz": "in_proj_qkvz.weight", "self_attn.gdn_in_proj_ba": "in_proj_ba.weight",
+             "self_attn.gdn_conv": "conv1d.weight", "self_attn.gdn_time_step": "dt_bias", "self_attn.gdn_A_log": "A_log",
+             "self_attn.gdn_norm": "norm.weight", "self_attn.gdn_out_proj": "out_proj.weight"}
+    if rest in delta:           # gated delta-rule linear attention (Qwen3-Next)
+        return {pre + "linear_attn." + delta[rest]: tensor}
     if rest == "self_attn.o_bias":
         return {pre + "self_attn.o_proj.bias": tensor}
     if rest == "self_attn.sinks":

@@ -56,6 +56,7 @@ class KVCache:
         self._layer = 0
         self._rows = self._cols = None
         self._conv: dict[int, torch.Tensor] = {}      # layer index -> [batch, taps - 1, hidden]: a conv mixer's recent inputs
+        self.recurrent: dict[int, torch.Tensor] = {}  # layer index -> [batch, heads, dk, dv]: a linear-attention layer's state
 
     def begin_prefill(self, seq_of_token: torch.Tensor, pos_of_token: torch.Tensor, lengths: torch.Tensor) -> None:
         self.mode, self._layer = "prefill", 0
@@ -78,6 +79,12 @@ class KVCache:
         st = self._conv.get(layer)
         if st is None:
             st = self._conv[layer] = torch.zeros(self.k.shape[1], depth, like.shape[-1], dtype=like.dtype, device=like.device)
+        return st
+
+    def recurrent_state(self, layer: int, heads: int, dk: int, dv: int) -> torch.Tensor:
+        st = self.recurrent.get(layer)
+        if st is None:
+            st = self.recurrent[layer] = torch.zeros(self.k.shape[1], heads, dk, dv, dtype=torch.float32, device=self.k.device)
         return st
 
     def store_conv_tail(self, layer: int, depth: int, x: torch.Tensor) -> None:

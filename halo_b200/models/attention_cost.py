@@ -34,8 +34,8 @@ def keys_visited_per_layer(cfg, cu_seqlens) -> list[float]:
     lengths = np.diff(np.asarray(cu_seqlens, dtype=np.float64))
     by_window = {}
     kinds = getattr(cfg, "layer_types", None) or []
-    # a short-convolution layer visits a fixed handful of tokens per token: no pair count
-    return [0.0 if i < len(kinds) and kinds[i] == "conv" else by_window.setdefault(w, causal_pairs(lengths, w))
+    # a short-convolution or linear-attention layer does a fixed amount of work per token: no pair count
+    return [0.0 if i < len(kinds) and kinds[i] in ("conv", "linear_attention") else by_window.setdefault(w, causal_pairs(lengths, w))
             for i, w in enumerate(layer_windows(cfg))]
 
 

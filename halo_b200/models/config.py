@@ -45,6 +45,9 @@ FAMILIES = {
     # Mistral 4: the DeepSeek-V3 block (latent attention, shared experts, group-limited routing) with softmax router
     # scores, expert banks stored whole, and queries scaled by 1 + beta * log(1 + floor(position / period))
     "mistral4": dict(architecture="Mistral4ForCausalLM", moe=True, qk_norm=False, bias_key=True, bias_default=False, has_window=False),
+    # Qwen3-Next: gated delta-rule linear attention in the layers ``layer_types`` names ``linear_attention``, attention with
+    # an output gate, a quarter of each head rotated and norms stored around zero in the others; Qwen2-MoE's gated shared expert
+    "qwen3_next": dict(architecture="Qwen3NextForCausalLM", moe=True, qk_norm=True, bias_key=True, bias_default=False, has_window=False),
     # LFM2-MoE: gated short-convolution mixers in the layers ``layer_types`` names ``conv``, attention with per-head q / k
     # norms in the others; sigmoid router scores ranked with a stored per-expert bias; leading dense layers
     "lfm2_moe": dict(architecture="Lfm2MoeForCausalLM", moe=True, qk_norm=True, bias_key=False, bias_default=False, has_window=False),
@@ -81,6 +84,12 @@ class ModelConfig:
     topk_group: int = 1
     routed_scaling_factor: float = 1.0
     norm_topk_eps: float = 1e-20           # added to the sum the chosen weights are divided by (group-limited path)
+    attn_output_gate: bool = False         # attention output times sigmoid(gate); the gate rides in the query projection (Qwen3-Next)
+    linear_num_key_heads: int = 0          # gated delta-rule layers (``layer_types`` entry "linear_attention"): heads and widths
+    linear_num_value_heads: int = 0
+    linear_key_head_dim: int = 0
+    linear_value_head_dim: int = 0
+    linear_conv_kernel_dim: int = 4
     conv_kernel: int = 0                   # taps of the short-convolution mixer in the layers ``layer_types`` names "conv" (LFM2)
     query_scale_beta: float = 0.0          # > 0: queries times 1 + beta * log(1 + floor(position / query_scale_period)) (Mistral 4)
     query_scale_period: int = 0
@@ -134,6 +143,10 @@ class ModelConfig:
         """The layer's mixer is a gated short convolution instead of attention."""
         return bool(self.layer_types) and i < len(self.layer_types) and self.layer_types[i] == "conv"
 
+    def layer_is_linear_attention(self, i: int) -> bool:
+        """The layer's mixer is the gated delta-rule recurrence instead of attention."""
+        return bool(self.layer_types) and i < len(self.layer_types) and self.layer_types[i] == "linear_attention"
+
     def layer_is_moe(self, i: int) -> bool:
         return self.is_moe and i not in self.mlp_only_layers and (i + 1) % self.decoder_sparse_step == 0
 
@@ -161,8 +174,14 @@ class ModelConfig:
         shared += self.num_experts if self.router_logit_bias else 0
         total = active = 0
         conv_mixer = 4 * H * H + H * self.conv_kernel + 2 * H        # in / out projections, taps, the layer's two norms
+        key_dim, value_dim = self.linear_num_key_heads * self.linear_key_head_dim, self.linear_num_value_heads * self.linear_value_head_dim
+        linear_mixer = (H * (2 * key_dim + 2 * value_dim) + H * 2 * self.linear_num_value_heads
+                        + (2 * key_dim + value_dim) * self.linear_conv_kernel_dim + 2 * self.linear_num_value_heads
+                        + self.linear_value_head_dim + value_dim * H + 2 * H)
+        if self.attn_output_gate:
+            attn += H * self.num_attention_heads * D
         for i in range(self.num_hidden_layers):
-            mixer = conv_mixer if self.layer_is_conv(i) else attn
+            mixer = conv_mixer if self.layer_is_conv(i) else linear_mixer if self.layer_is_linear_attention(i) else attn
             if self.layer_is_moe(i):
                 total += mixer + self.num_experts * expert + self.num_experts * H + shared
                 active += mixer + self.num_experts_per_tok * expert + self.num_experts * H + shared
@@ -329,6 +348,12 @@ class ModelConfig:
             })
             if self.shared_expert_intermediate_size:
                 d["shared_expert_intermediate_size"] = self.shared_expert_intermediate_size
+            if self.family == "qwen3_next":
+                d.update({"layer_types": list(self.layer_types or ["full_attention"] * self.num_hidden_layers),
+                          "linear_num_key_heads": self.linear_num_key_heads, "linear_num_value_heads": self.linear_num_value_heads,
+                          "linear_key_head_dim": self.linear_key_head_dim, "linear_value_head_dim": self.linear_value_head_dim,
+                          "linear_conv_kernel_dim": self.linear_conv_kernel_dim, "partial_rotary_factor": self.partial_rotary_factor})
+                d["rope_parameters"] = dict(d["rope_parameters"], partial_rotary_factor=self.partial_rotary_factor)
         return d
 
     @property
@@ -389,6 +414,17 @@ class ModelConfig:
                          kv_lora_rank=int(d["kv_lora_rank"]), q_lora_rank=int(d.get("q_lora_rank") or 0),
                          qk_nope_head_dim=int(d["qk_nope_head_dim"]), qk_rope_head_dim=hd, v_head_dim=int(d["v_head_dim"]),
                          rope_interleave=bool(d.get("rope_interleave", True)))
+        elif mt == "qwen3_next":
+            n_exp, width, dense_width = d.get("num_experts", 0), d.get("moe_intermediate_size", 0), d.get("intermediate_size", 0)
+            topk, renorm = d.get("num_experts_per_tok", 10), d.get("norm_topk_prob", True)
+            every = int(d.get("full_attention_interval", 4))
+            extra = dict(layer_types=list(d.get("layer_types") or ["full_attention" if (i + 1) % every == 0 else "linear_attention"
+                                                                    for i in range(d["num_hidden_layers"])]),
+                         partial_rotary_factor=float(d.get("partial_rotary_factor", rp.get("partial_rotary_factor", 0.25))),
+                         attn_output_gate=True, norm_unit_offset=True, shared_expert_gate=bool(d.get("shared_expert_intermediate_size", 0)),
+                         linear_num_key_heads=int(d.get("linear_num_key_heads", 16)), linear_num_value_heads=int(d.get("linear_num_value_heads", 32)),
+                         linear_key_head_dim=int(d.get("linear_key_head_dim", 128)), linear_value_head_dim=int(d.get("linear_value_head_dim", 128)),
+                         linear_conv_kernel_dim=int(d.get("linear_conv_kernel_dim", 4)))
         elif mt == "lfm2_moe":
             if d.get("conv_bias"):
                 raise ValueError("lfm2_moe with conv_bias: the biased convolution and projections are not built")

@@ -246,6 +246,37 @@ class Attention(nn.Module):
         return self._out(o)
 
 
+class GatedAttention(Attention):
+    """Attention whose output is multiplied by ``sigmoid(gate)`` before the output projection (Qwen3-Next). The gate comes
+    out of the query projection: its rows are, per head, the head's query rows then its gate rows - the hub's own order,
+    kept at run time so that the checkpoint's ``q_proj`` loads as one block in front of ``k_proj`` and ``v_proj``.
+    Unsliced rows and heads only; low-rank adapters on ``q_proj`` are refused by the adapter code."""
+
+    def __init__(self, cfg: ModelConfig, dtype, device, tp_size: int = 1, layer_idx: int = 0):
+        if tp_size > 1 or cfg.attention_bias:
+            raise ValueError("gated attention is built without a q / k / v bias and is not cut over tensor-parallel ranks")
+        super().__init__(cfg, dtype, device, tp_size, layer_idx)
+        H, D = cfg.hidden_size, cfg.head_dim
+        self.qkv_proj = nn.Parameter(torch.empty((2 * self.n_heads + 2 * self.n_kv_heads) * D, H, dtype=dtype, device=device))
+        self._gate = None
+
+    def _qkv(self, h):
+        D, Hq = self.cfg.head_dim, self.n_heads
+        wide = self._biased(_linear(h, self.qkv_proj, self.lowp))
+        qg = wide[:, :2 * Hq * D].reshape(-1, Hq, 2 * D)
+        self._gate = qg[..., D:].reshape(-1, Hq * D)
+        qkv = torch.cat([qg[..., :D].reshape(-1, Hq * D), wide[:, 2 * Hq * D:]], dim=-1)
+        if self.lora is not None:
+            q, kv = Hq * D, self.n_kv_heads * D
+            # the query block carries no adapter here (its projection also makes the gate): its range passes through
+            qkv = self.lora.add_fused(h, qkv, [("q_proj", 0, q), ("k_proj", q, q + kv), ("v_proj", q + kv, q + 2 * kv)])
+        return qkv
+
+    def _out(self, o):
+        gate, self._gate = self._gate, None
+        return super()._out(o * torch.sigmoid(gate.float()).to(o.dtype))
+
+
 class DenseMLP(nn.Module):
     def __init__(self, hidden: int, width: int, dtype, device, tp_size: int = 1):
         super().__init__()
@@ -438,6 +469,12 @@ class DecoderLayer(nn.Module):
             from .short_conv import ShortConv
 
             self.self_attn = ShortConv(cfg, dtype, device, tp_size, idx)
+        elif cfg.layer_is_linear_attention(idx):
+            from .gated_delta_net import GatedDeltaNet
+
+            self.self_attn = GatedDeltaNet(cfg, dtype, device, tp_size, idx)
+        elif cfg.attn_output_gate:
+            self.self_attn = GatedAttention(cfg, dtype, device, tp_size, idx)
         elif cfg.kv_lora_rank:
             from .latent_attention import LatentAttention
 

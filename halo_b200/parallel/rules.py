@@ -230,5 +230,9 @@ def reject_model_layout(pc, model_cfg, packed: bool = True) -> None:
     if getattr(model_cfg, "conv_kernel", 0) and (pc.tp_size > 1 or pc.cp_size > 1):
         raise ConfigError(f"{model_cfg.family}: the short-convolution mixer reads a token's predecessors in its row, so rows are not "
                           f"cut; drop tensor_parallel_size / context_parallel_size (expert and pipeline parallelism are fine)")
+    if (getattr(model_cfg, "linear_num_value_heads", 0) or getattr(model_cfg, "attn_output_gate", False)) and (pc.tp_size > 1 or pc.cp_size > 1):
+        raise ConfigError(f"{model_cfg.family}: the gated delta-rule layers carry a state along the row and the gated attention keeps "
+                          f"all heads on every rank, so rows and heads are not cut; drop tensor_parallel_size / context_parallel_size "
+                          f"(expert and pipeline parallelism are fine)")
     if pc.pp_size > 1 and model_cfg.num_hidden_layers < pc.pp_size:
         raise ConfigError(f"{model_cfg.num_hidden_layers} layers cannot fill {pc.pp_size} pipeline stages")

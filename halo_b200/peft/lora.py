@@ -170,6 +170,9 @@ def apply_lora(model, spec: LoraSpec, seed: int = 0) -> dict:
     if getattr(cfg, "kv_lora_rank", 0) and attention_targets:
         raise ValueError(f"targets {attention_targets}: latent attention has no such projections (its low-rank bottlenecks are "
                          f"already adapters of a kind); target the feed-forward blocks or the routed experts")
+    if getattr(cfg, "attn_output_gate", False) and "q_proj" in attention_targets:
+        raise ValueError("target q_proj: this family's query projection also produces the output gate (rows interleaved per head); "
+                         "target k_proj / v_proj / o_proj, the feed-forward blocks or the routed experts")
     for p in model.parameters():
         p.requires_grad_(False)
     ref = next(model.parameters())
@@ -184,8 +187,8 @@ def apply_lora(model, spec: LoraSpec, seed: int = 0) -> dict:
         gi = li + first_layer
         shapes = {t: s for t, s in (("q_proj", (q_rows, H)), ("k_proj", (kv_rows, H)), ("v_proj", (kv_rows, H)),
                                     ("o_proj", (H, q_rows))) if t in dense}
-        if hasattr(layer.self_attn, "conv_taps"):
-            shapes = {}            # a short-convolution mixer has no q / k / v / o projections: attention targets skip the layer
+        if hasattr(layer.self_attn, "conv_taps") or hasattr(layer.self_attn, "gdn_conv"):
+            shapes = {}            # a convolution / linear-attention mixer has no q / k / v / o projections: attention targets skip the layer
         layer.self_attn.lora = LoraSet(spec, shapes, dtype, device, seed * 7919 + gi * 4 + 0) if shapes else None
         mlps = []
         if hasattr(layer.mlp, "experts_gate_up"):

@@ -53,6 +53,11 @@ def family_config(family: str, **kw) -> ModelConfig:
                     qk_nope_head_dim=24, qk_rope_head_dim=16, v_head_dim=20, query_scale_beta=0.3, query_scale_period=16,
                     rope_scaling={"rope_type": "yarn", "factor": 4.0, "beta_fast": 32.0, "beta_slow": 1.0, "mscale": 1.0,
                                   "mscale_all_dim": 1.0, "original_max_position_embeddings": 16})
+    if family == "qwen3_next":
+        base.update(num_hidden_layers=4, layer_types=["linear_attention", "linear_attention", "full_attention", "linear_attention"],
+                    partial_rotary_factor=0.25, attn_output_gate=True, norm_unit_offset=True, shared_expert_intermediate_size=64,
+                    shared_expert_gate=True, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=8,
+                    linear_value_head_dim=12, linear_conv_kernel_dim=4)
     if family == "lfm2_moe":
         base.update(num_hidden_layers=4, layer_types=["conv", "conv", "full_attention", "conv"], conv_kernel=3, num_experts=8,
                     score_function="sigmoid", router_bias=True, norm_topk_eps=1e-6, routed_scaling_factor=1.5, mlp_only_layers=[0],
@@ -81,6 +86,8 @@ CASES = [("mistral", {"sliding_window": 16}), ("qwen2", {"sliding_window": 24}),
          ("deepseek_v3", {}), ("deepseek_v3", {"q_lora_rank": 0, "rope_interleave": False}),
          ("deepseek_v3", {"rope_scaling": {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 64, "mscale": 1.0,
                                            "mscale_all_dim": 1.0, "beta_fast": 32.0, "beta_slow": 1.0}}),
+         ("qwen3_next", {}), ("qwen3_next", {"linear_num_key_heads": 4, "linear_conv_kernel_dim": 3, "shared_expert_intermediate_size": 48,
+                                             "mlp_only_layers": [1]}),
          ("lfm2_moe", {}), ("lfm2_moe", {"conv_kernel": 4, "router_bias": False, "tie_word_embeddings": False,
                                          "layer_types": ["full_attention", "conv", "conv", "conv"]}),
          ("mistral4", {}), ("mistral4", {"q_lora_rank": 0, "rope_interleave": False, "n_group": 1, "topk_group": 1,
@@ -105,6 +112,18 @@ def test_family_round_trip_through_transformers(tmp_path, family, extra):
                 layer.self_attn.kv_a_norm.normal_(1.0, 0.2, generator=torch.Generator().manual_seed(29))
                 if cfg.q_lora_rank:
                     layer.self_attn.q_a_norm.normal_(1.0, 0.2, generator=torch.Generator().manual_seed(31))
+    if cfg.linear_num_value_heads:
+        with torch.no_grad():
+            g = torch.Generator().manual_seed(43)
+            for layer in model.layers:       # small taps, unit decay rates and a unit norm would hide a wrong order or a dropped term
+                if hasattr(layer.self_attn, "gdn_conv"):
+                    a = layer.self_attn
+                    a.gdn_conv.normal_(0.0, 0.5, generator=g)
+                    a.gdn_in_proj_qkvz.normal_(0.0, 0.3, generator=g)
+                    a.gdn_in_proj_ba.normal_(0.0, 0.5, generator=g)
+                    a.gdn_A_log.uniform_(-1.0, 1.5, generator=g)
+                    a.gdn_time_step.normal_(0.5, 0.5, generator=g)
+                    a.gdn_norm.normal_(1.0, 0.2, generator=g)
     if cfg.conv_kernel:
         with torch.no_grad():
             g = torch.Generator().manual_seed(41)
@@ -350,6 +369,100 @@ def test_short_convolution_family_trains_and_keeps_documents_apart():
         with pytest.raises(ConfigError, match="short-convolution"):
             reject_model_layout(ParallelismConfig(world_size=2, **{axis: 2}), cfg)
     reject_model_layout(ParallelismConfig(world_size=2, ep_size=2), cfg)
+
+
+def test_chunked_delta_rule_equals_the_recurrence():
+    """The chunked form (triangular solve per chunk, documents side by side) against the token-by-token recurrence: outputs,
+    each document's final state and the gradients of every input, for chunk sizes that do and do not divide the documents."""
+    from halo_b200.models.gated_delta_net import chunked_gated_delta_rule, recurrent_gated_delta_step
+
+    g = torch.Generator().manual_seed(1)
+    lengths, H, dk, dv = [5, 1, 23, 8], 3, 6, 4
+    T = sum(lengths)
+    leaves = [torch.randn(T, H, dk, generator=g), torch.randn(T, H, dk, generator=g), torch.randn(T, H, dv, generator=g),
+              -torch.rand(T, H, generator=g) * 2.0, torch.rand(T, H, generator=g)]
+    leaves = [t.double().requires_grad_() for t in leaves]
+
+    def prepared():
+        q, k, v, lg, beta = leaves
+        return q / q.norm(dim=-1, keepdim=True), k / k.norm(dim=-1, keepdim=True), v, lg, beta
+
+    def recurrent():
+        q, k, v, lg, beta = prepared()
+        outs, finals, start = [], [], 0
+        for n in lengths:
+            s = torch.zeros(1, H, dk, dv)
+            for t in range(start, start + n):
+                o, s = recurrent_gated_delta_step(s, q[t][None].float(), k[t][None].float(), v[t][None].float(), lg[t][None].float(),
+                                                  beta[t][None].float())
+                outs.append(o[0])
+            finals.append(s[0])
+            start += n
+        return torch.stack(outs), torch.stack(finals)
+
+    probe_o, probe_s = torch.randn(T, H, dv, generator=g), torch.randn(len(lengths), H, dk, dv, generator=g)
+    want_o, want_s = recurrent()
+    want = torch.autograd.grad((want_o * probe_o).sum() + (want_s * probe_s).sum(), leaves)
+    for chunk in (4, 8, 64):
+        got_o, got_s = chunked_gated_delta_rule(*prepared(), lengths, chunk=chunk)
+        assert torch.allclose(got_o, want_o.float(), atol=2e-5), (chunk, float((got_o - want_o).abs().max()))
+        assert torch.allclose(got_s, want_s.float(), atol=2e-5), chunk
+        got = torch.autograd.grad((got_o * probe_o).sum() + (got_s * probe_s).sum(), leaves)
+        for a, b, name in zip(got, want, "q k v log_g beta".split()):
+            assert torch.allclose(a, b, atol=5e-5), (chunk, name, float((a - b).abs().max()))
+
+
+def test_linear_attention_family_trains_and_keeps_documents_apart():
+    """Qwen3-Next shape: neither the convolution nor the matrix state of a linear-attention layer crosses a document's first
+    token in a packed row; the model takes optimizer steps under per-layer recomputation; row- and head-cutting layouts and an
+    adapter on the gate-carrying query projection are refused by name."""
+    from halo_b200.config_validation import ConfigError
+    from halo_b200.data.packing import synthetic_packed_batch
+    from halo_b200.parallel.config import ParallelismConfig
+    from halo_b200.parallel.rules import reject_model_layout
+    from halo_b200.peft.lora import LoraSpec, apply_lora
+    from halo_b200.trainers.engine import TrainEngine
+
+    cfg = family_config("qwen3_next")
+    model = build_model(cfg, device="cpu", seed=2, gradient_checkpointing=True)
+    assert sum(p.numel() for p in model.parameters()) == cfg.param_counts()["total"]
+    with torch.no_grad():
+        for layer in model.layers:
+            if hasattr(layer.self_attn, "gdn_conv"):
+                layer.self_attn.gdn_conv.normal_(0.0, 0.5, generator=torch.Generator().manual_seed(3))
+                layer.self_attn.gdn_in_proj_qkvz.normal_(0.0, 0.3, generator=torch.Generator().manual_seed(4))
+    rng = np.random.default_rng(4)
+    docs = [rng.integers(0, cfg.vocab_size, size=n) for n in (2, 70, 1, 9)]       # one longer than a chunk
+    b = pack_documents(docs)
+    with torch.no_grad():
+        packed = model.hidden_states(b.input_ids, b.position_ids, b.cu_seqlens)
+        start = 0
+        for d in docs:
+            alone, _ = logits_of(model, d)
+            together = packed[start:start + len(d)] @ model.head_weight().t()
+            assert torch.allclose(alone, together, atol=5e-5), float((alone - together).abs().max())
+            start += len(d)
+    engine = TrainEngine(model, torch.optim.AdamW(model.parameters(), lr=3e-3), "cpu", max_grad_norm=1.0)
+    batch = synthetic_packed_batch(96, cfg.vocab_size, seed=0, lo=20, hi=50)
+    before = {n: p.detach().clone() for n, p in model.named_parameters()}
+    losses = [float(engine.train_step(batch).loss.reshape(-1)[0]) for _ in range(6)]
+    assert losses[-1] < losses[0] - 0.3, losses
+    moved = {n for n, p in model.named_parameters() if not torch.equal(p, before[n])}
+    for name in ("gdn_in_proj_qkvz", "gdn_in_proj_ba", "gdn_conv", "gdn_time_step", "gdn_A_log", "gdn_norm", "gdn_out_proj"):
+        assert f"layers.1.self_attn.{name}" in moved, name
+    assert "layers.2.self_attn.qkv_proj" in moved
+    for axis in ("tp_size", "cp_size"):
+        with pytest.raises(ConfigError, match="delta-rule"):
+            reject_model_layout(ParallelismConfig(world_size=2, **{axis: 2}), cfg)
+    reject_model_layout(ParallelismConfig(world_size=2, ep_size=2), cfg)
+    with pytest.raises(ValueError, match="output gate"):
+        apply_lora(build_model(cfg, device="cpu", seed=2), LoraSpec(r=4, target_modules=["q_proj", "v_proj"]))
+    counts = apply_lora(model, LoraSpec(r=4, target_modules=["k_proj", "v_proj", "o_proj", "down_proj"]))
+    assert counts["trainable"] > 0
+    assert model.layers[0].self_attn.lora is None and model.layers[2].self_attn.lora is not None
+    out = model(batch.input_ids, batch.position_ids, batch.cu_seqlens, batch.labels)
+    (out.loss if hasattr(out, "loss") else out).sum().backward()
+    assert model.layers[2].self_attn.lora.B["v_proj"].grad is not None
 
 
 def test_gemma3_trains_under_every_recomputation_policy():

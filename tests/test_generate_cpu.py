@@ -64,6 +64,17 @@ def conv_cfg():
                        layer_types=["conv", "full_attention", "conv"], conv_kernel=4, max_position_embeddings=64)
 
 
+def linear_cfg():
+    """Qwen3-Next style: gated delta-rule layers (conv of 4 taps in front) around one gated-attention layer with a quarter of
+    each head rotated."""
+    return ModelConfig(vocab_size=128, hidden_size=64, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                       intermediate_size=96, moe_intermediate_size=48, num_experts=4, num_experts_per_tok=2, model_type="qwen3_next",
+                       use_qk_norm=True, shared_expert_intermediate_size=48, shared_expert_gate=True, attn_output_gate=True,
+                       norm_unit_offset=True, partial_rotary_factor=0.25, layer_types=["linear_attention", "full_attention", "linear_attention"],
+                       linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=8, linear_value_head_dim=12,
+                       linear_conv_kernel_dim=4, max_position_embeddings=64)
+
+
 def gemma_cfg():
     """Gemma 3 style: windowed layers with their own rotary base, a full layer, output norms, tanh-GELU gate, scaled embeddings."""
     return dataclasses.replace(dense_cfg(), model_type="gemma3_text", num_hidden_layers=3, sliding_window=6, max_position_embeddings=64,
@@ -78,9 +89,9 @@ def capped_cfg():
                                use_qk_norm=False, rope_local_theta=0.0, attn_logit_softcapping=1.0, final_logit_softcapping=0.5)
 
 
-@pytest.mark.parametrize("kind", ["dense", "moe", "windowed", "sinks", "latent", "stretched", "conv", "gemma", "capped"])
+@pytest.mark.parametrize("kind", ["dense", "moe", "windowed", "sinks", "latent", "stretched", "conv", "linear", "gemma", "capped"])
 def test_cached_decoding_equals_the_full_forward(kind):
-    cfg = {"dense": dense_cfg, "windowed": windowed_cfg, "sinks": sink_cfg, "latent": latent_cfg, "stretched": stretched_cfg, "conv": conv_cfg, "gemma": gemma_cfg, "capped": capped_cfg,
+    cfg = {"dense": dense_cfg, "windowed": windowed_cfg, "sinks": sink_cfg, "latent": latent_cfg, "stretched": stretched_cfg, "conv": conv_cfg, "linear": linear_cfg, "gemma": gemma_cfg, "capped": capped_cfg,
            "moe": lambda: dataclasses.replace(tiny_moe_config(), num_hidden_layers=2, vocab_size=128)}[kind]()
     model = build_model(cfg, device="cpu", seed=7, gradient_checkpointing=False)
     if kind == "conv":
@@ -88,6 +99,12 @@ def test_cached_decoding_equals_the_full_forward(kind):
             for layer in model.layers:       # taps near zero would hide a stale or shifted cache
                 if hasattr(layer.self_attn, "conv_taps"):
                     layer.self_attn.conv_taps.normal_(0.0, 0.6, generator=torch.Generator().manual_seed(5))
+    if kind == "linear":
+        with torch.no_grad():
+            for layer in model.layers:       # taps and projections near zero would hide a stale convolution or matrix state
+                if hasattr(layer.self_attn, "gdn_conv"):
+                    layer.self_attn.gdn_conv.normal_(0.0, 0.5, generator=torch.Generator().manual_seed(5))
+                    layer.self_attn.gdn_in_proj_qkvz.normal_(0.0, 0.3, generator=torch.Generator().manual_seed(6))
     if kind == "sinks":
         with torch.no_grad():
             for layer in model.layers:
