@@ -25,6 +25,7 @@ MOE_HUB_NAMES = {
     "deepseek_v3": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "mistral4": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "lfm2_moe": ("feed_forward", "w1", "w3", "w2"),
+    "qwen3_5_moe_text": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "olmoe": ("mlp", "gate_proj", "up_proj", "down_proj"),
 }
 # gpt-oss stores each bank as ONE tensor, transposed, with gate and up columns interleaved (``INTERLEAVED_GLU``);
@@ -80,6 +81,7 @@ def stored_with_unit_offset(name: str, cfg) -> bool:
 # families whose hub names differ from the common ones only by substitution: (common fragment, family's fragment), applied
 # in order to every hub name the common rules produce
 _FAMILY_RENAMES = {
+    "qwen3_5_moe_text": (("model.", "model.language_model."),),
     "lfm2_moe": (("model.norm.weight", "model.embedding_norm.weight"), (".input_layernorm.", ".operator_norm."),
                  (".post_attention_layernorm.", ".ffn_norm."), (".self_attn.o_proj.", ".self_attn.out_proj."),
                  (".self_attn.q_norm.", ".self_attn.q_layernorm."), (".self_attn.k_norm.", ".self_attn.k_layernorm."),
@@ -155,7 +157,10 @@ def _common_runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: in
         return {pre + conv[rest]: tensor}
     delta = {"self_attn.gdn_in_proj_qkvz": "in_proj_qkvz.weight", "self_attn.gdn_in_proj_ba": "in_proj_ba.weight",
              "self_attn.gdn_conv": "conv1d.weight", "self_attn.gdn_time_step": "dt_bias", "self_attn.gdn_A_log": "A_log",
-             "self_attn.gdn_norm": "norm.weight", "self_attn.gdn_out_proj": "out_proj.weight"}
+             "self_attn.gdn_norm": "norm.weight", "self_attn.gdn_out_proj": "out_proj.weight",
+             # Qwen3.5 stores one projection per role, each in flat head order
+             "self_attn.gdn_in_proj_qkv": "in_proj_qkv.weight", "self_attn.gdn_in_proj_z": "in_proj_z.weight",
+             "self_attn.gdn_in_proj_b": "in_proj_b.weight", "self_attn.gdn_in_proj_a": "in_proj_a.weight"}
     if rest in delta:           # gated delta-rule linear attention (Qwen3-Next)
         return {pre + "linear_attn." + delta[rest]: tensor}
     if rest == "self_attn.o_bias":

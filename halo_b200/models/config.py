@@ -48,6 +48,9 @@ FAMILIES = {
     # Qwen3-Next: gated delta-rule linear attention in the layers ``layer_types`` names ``linear_attention``, attention with
     # an output gate, a quarter of each head rotated and norms stored around zero in the others; Qwen2-MoE's gated shared expert
     "qwen3_next": dict(architecture="Qwen3NextForCausalLM", moe=True, qk_norm=True, bias_key=True, bias_default=False, has_window=False),
+    # Qwen3.5-MoE (text tower): Qwen3-Next's layers with the linear-attention projections stored one per role, every layer
+    # sparse, router weights always renormalised, and tensors named under ``model.language_model``
+    "qwen3_5_moe_text": dict(architecture="Qwen3_5MoeForCausalLM", moe=True, qk_norm=True, bias_key=True, bias_default=False, has_window=False),
     # LFM2-MoE: gated short-convolution mixers in the layers ``layer_types`` names ``conv``, attention with per-head q / k
     # norms in the others; sigmoid router scores ranked with a stored per-expert bias; leading dense layers
     "lfm2_moe": dict(architecture="Lfm2MoeForCausalLM", moe=True, qk_norm=True, bias_key=False, bias_default=False, has_window=False),
@@ -348,7 +351,12 @@ class ModelConfig:
             })
             if self.shared_expert_intermediate_size:
                 d["shared_expert_intermediate_size"] = self.shared_expert_intermediate_size
-            if self.family == "qwen3_next":
+            if self.family == "qwen3_5_moe_text":
+                if self.mlp_only_layers or self.decoder_sparse_step != 1 or not self.norm_topk_prob:
+                    raise ValueError("qwen3_5_moe_text: every layer is sparse and the router always renormalises")
+                for key in ("decoder_sparse_step", "mlp_only_layers", "norm_topk_prob"):
+                    d.pop(key, None)
+            if self.family in ("qwen3_next", "qwen3_5_moe_text"):
                 d.update({"layer_types": list(self.layer_types or ["full_attention"] * self.num_hidden_layers),
                           "linear_num_key_heads": self.linear_num_key_heads, "linear_num_value_heads": self.linear_num_value_heads,
                           "linear_key_head_dim": self.linear_key_head_dim, "linear_value_head_dim": self.linear_value_head_dim,
@@ -366,6 +374,10 @@ class ModelConfig:
     @classmethod
     def from_hf_dict(cls, d: dict) -> "ModelConfig":
         mt = d.get("model_type", "qwen3")
+        if mt == "qwen3_5_moe" and "text_config" in d:
+            # the multimodal release: its text tower is the model here (the tensors carry the same names either way)
+            d = dict(d["text_config"], tie_word_embeddings=d.get("tie_word_embeddings", d["text_config"].get("tie_word_embeddings", False)))
+            mt = d["model_type"] = "qwen3_5_moe_text"
         if mt not in FAMILIES:
             raise ValueError(f"model_type {mt!r} has no family registered here (known: {sorted(FAMILIES)})")
         fam = FAMILIES[mt]
@@ -414,7 +426,7 @@ class ModelConfig:
                          kv_lora_rank=int(d["kv_lora_rank"]), q_lora_rank=int(d.get("q_lora_rank") or 0),
                          qk_nope_head_dim=int(d["qk_nope_head_dim"]), qk_rope_head_dim=hd, v_head_dim=int(d["v_head_dim"]),
                          rope_interleave=bool(d.get("rope_interleave", True)))
-        elif mt == "qwen3_next":
+        elif mt in ("qwen3_next", "qwen3_5_moe_text"):
             n_exp, width, dense_width = d.get("num_experts", 0), d.get("moe_intermediate_size", 0), d.get("intermediate_size", 0)
             topk, renorm = d.get("num_experts_per_tok", 10), d.get("norm_topk_prob", True)
             every = int(d.get("full_attention_interval", 4))

@@ -128,9 +128,17 @@ class GatedDeltaNet(nn.Module):
         def param(*shape):
             return nn.Parameter(torch.empty(*shape, dtype=dtype, device=device))
 
-        # the hub's own row order: per key head, its q, k, and its value heads' v and z (b and a likewise)
-        self.gdn_in_proj_qkvz = param(2 * key_dim + 2 * value_dim, H)
-        self.gdn_in_proj_ba = param(2 * self.Hv, H)
+        # the hub's own row order. Qwen3-Next: two projections grouped per key head (its q, k, and its value heads' v and
+        # z; b and a likewise). Qwen3.5: one projection per role, heads in flat order
+        self.per_role = cfg.family == "qwen3_5_moe_text"
+        if self.per_role:
+            self.gdn_in_proj_qkv = param(2 * key_dim + value_dim, H)
+            self.gdn_in_proj_z = param(value_dim, H)
+            self.gdn_in_proj_b = param(self.Hv, H)
+            self.gdn_in_proj_a = param(self.Hv, H)
+        else:
+            self.gdn_in_proj_qkvz = param(2 * key_dim + 2 * value_dim, H)
+            self.gdn_in_proj_ba = param(2 * self.Hv, H)
         self.gdn_conv = param(2 * key_dim + value_dim, 1, cfg.linear_conv_kernel_dim)
         self.gdn_time_step = param(self.Hv)
         self.gdn_A_log = param(self.Hv)
@@ -144,11 +152,16 @@ class GatedDeltaNet(nn.Module):
         cfg, T = self.cfg, h.shape[0]
         Hk, Hv, dk, dv = self.Hk, self.Hv, self.dk, self.dv
         r = Hv // Hk
-        qkvz = gemm.linear(h, self.gdn_in_proj_qkvz).reshape(T, Hk, 2 * dk + 2 * r * dv)
-        q, k, v, z = qkvz.split([dk, dk, r * dv, r * dv], dim=-1)
-        ba = gemm.linear(h, self.gdn_in_proj_ba).reshape(T, Hk, 2 * r)
-        b, a = ba[..., :r].reshape(T, Hv), ba[..., r:].reshape(T, Hv)
-        mixed = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=-1)
+        if self.per_role:
+            mixed = gemm.linear(h, self.gdn_in_proj_qkv)
+            z = gemm.linear(h, self.gdn_in_proj_z)
+            b, a = gemm.linear(h, self.gdn_in_proj_b), gemm.linear(h, self.gdn_in_proj_a)
+        else:
+            qkvz = gemm.linear(h, self.gdn_in_proj_qkvz).reshape(T, Hk, 2 * dk + 2 * r * dv)
+            q, k, v, z = qkvz.split([dk, dk, r * dv, r * dv], dim=-1)
+            ba = gemm.linear(h, self.gdn_in_proj_ba).reshape(T, Hk, 2 * r)
+            b, a = ba[..., :r].reshape(T, Hv), ba[..., r:].reshape(T, Hv)
+            mixed = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=-1)
         K = cfg.linear_conv_kernel_dim
         taps = self.gdn_conv[:, 0, :]
         cache = ctx.kv_cache

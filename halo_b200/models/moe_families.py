@@ -56,8 +56,7 @@ def register(spec: MoEFamilySpec) -> MoEFamilySpec:
 for _s in (
     MoEFamilySpec("qwen3_moe", SEPARATE_GLU, runnable=True),
     MoEFamilySpec("qwen2_moe", SEPARATE_GLU, norm_topk_prob=False, shared_experts=True, runnable=True),
-    MoEFamilySpec("qwen3_5_moe", FUSED, shared_experts=True,
-                  missing="its checkpoint names and multimodal wrapper (the gated delta-rule layers and gated attention are built: see qwen3_next)"),
+    MoEFamilySpec("qwen3_5_moe", SEPARATE_GLU, shared_experts=True, runnable=True),      # its text tower: model_type qwen3_5_moe_text
     MoEFamilySpec("qwen3_next", SEPARATE_GLU, shared_experts=True, runnable=True),
     MoEFamilySpec("qwen4_exp", FUSED, shared_experts=True, missing="block-sparse attention"),
     MoEFamilySpec("gpt_oss", INTERLEAVED_GLU, activation="gptoss", expert_bias=True, router_name="mlp.router", runnable=True),

@@ -53,7 +53,7 @@ def family_config(family: str, **kw) -> ModelConfig:
                     qk_nope_head_dim=24, qk_rope_head_dim=16, v_head_dim=20, query_scale_beta=0.3, query_scale_period=16,
                     rope_scaling={"rope_type": "yarn", "factor": 4.0, "beta_fast": 32.0, "beta_slow": 1.0, "mscale": 1.0,
                                   "mscale_all_dim": 1.0, "original_max_position_embeddings": 16})
-    if family == "qwen3_next":
+    if family in ("qwen3_next", "qwen3_5_moe_text"):
         base.update(num_hidden_layers=4, layer_types=["linear_attention", "linear_attention", "full_attention", "linear_attention"],
                     partial_rotary_factor=0.25, attn_output_gate=True, norm_unit_offset=True, shared_expert_intermediate_size=64,
                     shared_expert_gate=True, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=8,
@@ -88,6 +88,7 @@ CASES = [("mistral", {"sliding_window": 16}), ("qwen2", {"sliding_window": 24}),
                                            "mscale_all_dim": 1.0, "beta_fast": 32.0, "beta_slow": 1.0}}),
          ("qwen3_next", {}), ("qwen3_next", {"linear_num_key_heads": 4, "linear_conv_kernel_dim": 3, "shared_expert_intermediate_size": 48,
                                              "mlp_only_layers": [1]}),
+         ("qwen3_5_moe_text", {}),
          ("lfm2_moe", {}), ("lfm2_moe", {"conv_kernel": 4, "router_bias": False, "tie_word_embeddings": False,
                                          "layer_types": ["full_attention", "conv", "conv", "conv"]}),
          ("mistral4", {}), ("mistral4", {"q_lora_rank": 0, "rope_interleave": False, "n_group": 1, "topk_group": 1,
@@ -119,8 +120,10 @@ def test_family_round_trip_through_transformers(tmp_path, family, extra):
                 if hasattr(layer.self_attn, "gdn_conv"):
                     a = layer.self_attn
                     a.gdn_conv.normal_(0.0, 0.5, generator=g)
-                    a.gdn_in_proj_qkvz.normal_(0.0, 0.3, generator=g)
-                    a.gdn_in_proj_ba.normal_(0.0, 0.5, generator=g)
+                    for name, std in (("gdn_in_proj_qkvz", 0.3), ("gdn_in_proj_ba", 0.5), ("gdn_in_proj_qkv", 0.3), ("gdn_in_proj_z", 0.3),
+                                      ("gdn_in_proj_b", 0.5), ("gdn_in_proj_a", 0.5)):
+                        if hasattr(a, name):
+                            getattr(a, name).normal_(0.0, std, generator=g)
                     a.gdn_A_log.uniform_(-1.0, 1.5, generator=g)
                     a.gdn_time_step.normal_(0.5, 0.5, generator=g)
                     a.gdn_norm.normal_(1.0, 0.2, generator=g)
@@ -202,6 +205,9 @@ def test_window_and_family_gates():
     assert ModelConfig.from_hf_dict(q).layer_types == ["full_attention", "sliding_attention"]
     q["max_window_layers"] = 2
     assert ModelConfig.from_hf_dict(q).sliding_window == 0
+    text = family_config("qwen3_5_moe_text").to_hf_dict()
+    wrapped = {"model_type": "qwen3_5_moe", "text_config": text, "vision_config": {"depth": 2}, "tie_word_embeddings": False}
+    assert ModelConfig.from_hf_dict(wrapped) == family_config("qwen3_5_moe_text")     # a multimodal config reads as its text tower
     with pytest.raises(ValueError, match="no family registered"):
         ModelConfig.from_hf_dict({**d, "model_type": "mamba"})
 
