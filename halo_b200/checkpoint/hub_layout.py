@@ -24,6 +24,7 @@ MOE_HUB_NAMES = {
     "glm4_moe": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "deepseek_v3": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "mistral4": ("mlp", "gate_proj", "up_proj", "down_proj"),
+    "glm4_moe_lite": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "lfm2_moe": ("feed_forward", "w1", "w3", "w2"),
     "qwen3_5_moe_text": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "olmoe": ("mlp", "gate_proj", "up_proj", "down_proj"),
@@ -63,7 +64,8 @@ def whole_bank_source(name: str, cfg, first_layer: int = 0):
         "mlp.experts_down_bias": (pre + "down_proj_bias", lambda t: t),
     }.get(m.group(2))
 # how a family names its always-on shared feed-forward block
-SHARED_EXPERT_NAMES = {"glm4_moe": "shared_experts", "deepseek_v3": "shared_experts", "mistral4": "shared_experts"}
+SHARED_EXPERT_NAMES = {"glm4_moe": "shared_experts", "deepseek_v3": "shared_experts", "mistral4": "shared_experts",
+                       "glm4_moe_lite": "shared_experts"}
 
 
 LAYER_NORMS = ("input_layernorm", "post_attention_layernorm", "pre_feedforward_layernorm", "post_feedforward_layernorm")

@@ -42,6 +42,8 @@ FAMILIES = {
     "gemma2": dict(architecture="Gemma2ForCausalLM", moe=False, qk_norm=False, bias_key=True, bias_default=False, has_window=True),
     "gemma3_text": dict(architecture="Gemma3ForCausalLM", moe=False, qk_norm=True, bias_key=True, bias_default=False, has_window=True),
     "deepseek_v3": dict(architecture="DeepseekV3ForCausalLM", moe=True, qk_norm=False, bias_key=True, bias_default=False, has_window=False),
+    # GLM-4.7-Flash: the DeepSeek-V3 block with its dense layers named one by one (``mlp_layer_types``)
+    "glm4_moe_lite": dict(architecture="Glm4MoeLiteForCausalLM", moe=True, qk_norm=False, bias_key=True, bias_default=False, has_window=False),
     # Mistral 4: the DeepSeek-V3 block (latent attention, shared experts, group-limited routing) with softmax router
     # scores, expert banks stored whole, and queries scaled by 1 + beta * log(1 + floor(position / period))
     "mistral4": dict(architecture="Mistral4ForCausalLM", moe=True, qk_norm=False, bias_key=True, bias_default=False, has_window=False),
@@ -279,11 +281,11 @@ class ModelConfig:
                       "output_router_logits": False, "swiglu_limit": self.glu_limit,
                       "layer_types": list(self.layer_types or ["sliding_attention" if self.sliding_window else "full_attention"]
                                           * self.num_hidden_layers)})
-        elif self.family in ("glm4_moe", "deepseek_v3", "mistral4"):
+        elif self.family in ("glm4_moe", "deepseek_v3", "mistral4", "glm4_moe_lite"):
             first_dense = 0
             while first_dense in self.mlp_only_layers:
                 first_dense += 1
-            if sorted(self.mlp_only_layers) != list(range(first_dense)):
+            if self.family != "glm4_moe_lite" and sorted(self.mlp_only_layers) != list(range(first_dense)):
                 raise ValueError("glm4_moe stores its dense layers as a leading run (first_k_dense_replace)")
             d.update({"moe_intermediate_size": self.moe_intermediate_size, "n_routed_experts": self.num_experts,
                       "num_experts_per_tok": self.num_experts_per_tok, "norm_topk_prob": self.norm_topk_prob,
@@ -300,6 +302,9 @@ class ModelConfig:
                           "qk_nope_head_dim": self.qk_nope_head_dim, "qk_rope_head_dim": self.qk_rope_head_dim,
                           "v_head_dim": self.v_head_dim, "rope_interleave": self.rope_interleave,
                           "head_dim": self.qk_rope_head_dim})
+                if self.family == "glm4_moe_lite":
+                    d.pop("first_k_dense_replace")
+                    d["mlp_layer_types"] = ["dense" if i in self.mlp_only_layers else "sparse" for i in range(self.num_hidden_layers)]
                 if self.family == "mistral4":
                     # a head is the un-rotated and the rotated slice together; the rotary table covers the rotated share
                     whole = self.qk_nope_head_dim + self.qk_rope_head_dim
@@ -406,7 +411,7 @@ class ModelConfig:
                 scaling = None
         hd = d.get("head_dim") or d["hidden_size"] // d["num_attention_heads"]
         extra = {}
-        if mt in ("deepseek_v3", "mistral4"):
+        if mt in ("deepseek_v3", "mistral4", "glm4_moe_lite"):
             n_exp, width, dense_width = d["n_routed_experts"], d["moe_intermediate_size"], d["intermediate_size"]
             topk, renorm = d.get("num_experts_per_tok", 8 if mt == "deepseek_v3" else 4), d.get("norm_topk_prob", True)
             hd = int(d.get("qk_rope_head_dim", 64))            # the rotary table is built for the rotary slice
@@ -422,8 +427,9 @@ class ModelConfig:
             extra = dict(**routing, n_group=int(d.get("n_group", 1)),
                          topk_group=int(d.get("topk_group", 1)), routed_scaling_factor=float(d.get("routed_scaling_factor", 1.0)),
                          shared_expert_intermediate_size=int(d.get("n_shared_experts", 0) or 0) * width,
-                         mlp_only_layers=list(range(int(d.get("first_k_dense_replace", 0)))), use_qk_norm=False,
-                         kv_lora_rank=int(d["kv_lora_rank"]), q_lora_rank=int(d.get("q_lora_rank") or 0),
+                         mlp_only_layers=([i for i, kind in enumerate(d.get("mlp_layer_types") or ["dense"] + ["sparse"] * (d["num_hidden_layers"] - 1))
+                                           if kind == "dense"] if mt == "glm4_moe_lite" else list(range(int(d.get("first_k_dense_replace", 0))))),
+                         use_qk_norm=False, kv_lora_rank=int(d["kv_lora_rank"]), q_lora_rank=int(d.get("q_lora_rank") or 0),
                          qk_nope_head_dim=int(d["qk_nope_head_dim"]), qk_rope_head_dim=hd, v_head_dim=int(d["v_head_dim"]),
                          rope_interleave=bool(d.get("rope_interleave", True)))
         elif mt in ("qwen3_next", "qwen3_5_moe_text"):

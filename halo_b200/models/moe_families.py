@@ -66,6 +66,8 @@ for _s in (
                   grouped_topk=True, shared_experts=True, missing="its compressed sparse attention (latent attention and hyper-connections are built: see deepseek_v3)"),
     MoEFamilySpec("glm4_moe", SEPARATE_GLU, score_function="sigmoid", selection_bias=True, grouped_topk=True,
                   shared_experts=True, runnable=True),
+    MoEFamilySpec("glm4_moe_lite", SEPARATE_GLU, score_function="sigmoid", selection_bias=True, grouped_topk=True, routed_scaling_factor=1.8,
+                  shared_experts=True, runnable=True),
     MoEFamilySpec("glm5_next", SEPARATE_GLU, score_function="sigmoid", selection_bias=True, shared_experts=True,
                   missing="sparse (DSA) attention, hyper-connections"),
     MoEFamilySpec("gemma4", FUSED, activation="gelu_tanh", missing="sliding/global attention mix, logit soft-capping"),

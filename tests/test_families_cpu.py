@@ -42,7 +42,7 @@ def family_config(family: str, **kw) -> ModelConfig:
         base.update(num_hidden_layers=3, sliding_window=16, layer_types=["sliding_attention", "sliding_attention", "full_attention"],
                     hidden_activation="gelu_tanh", sandwich_norms=True, norm_unit_offset=True, embedding_multiplier=128 ** 0.5,
                     query_pre_attn_scalar=24, rope_local_theta=500.0, tie_word_embeddings=True)
-    if family == "deepseek_v3":
+    if family in ("deepseek_v3", "glm4_moe_lite"):
         base.update(num_experts=8, score_function="sigmoid", router_bias=True, n_group=2, topk_group=1, routed_scaling_factor=2.5,
                     shared_expert_intermediate_size=96, mlp_only_layers=[0], use_qk_norm=False, num_key_value_heads=4, head_dim=16,
                     kv_lora_rank=32, q_lora_rank=48, qk_nope_head_dim=24, qk_rope_head_dim=16, v_head_dim=20)
@@ -86,6 +86,7 @@ CASES = [("mistral", {"sliding_window": 16}), ("qwen2", {"sliding_window": 24}),
          ("deepseek_v3", {}), ("deepseek_v3", {"q_lora_rank": 0, "rope_interleave": False}),
          ("deepseek_v3", {"rope_scaling": {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 64, "mscale": 1.0,
                                            "mscale_all_dim": 1.0, "beta_fast": 32.0, "beta_slow": 1.0}}),
+         ("glm4_moe_lite", {}), ("glm4_moe_lite", {"num_hidden_layers": 3, "mlp_only_layers": [0, 2], "n_group": 1, "topk_group": 1}),
          ("qwen3_next", {}), ("qwen3_next", {"linear_num_key_heads": 4, "linear_conv_kernel_dim": 3, "shared_expert_intermediate_size": 48,
                                              "mlp_only_layers": [1]}),
          ("qwen3_5_moe_text", {}),
