@@ -25,6 +25,7 @@ MOE_HUB_NAMES = {
     "deepseek_v3": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "mistral4": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "glm4_moe_lite": ("mlp", "gate_proj", "up_proj", "down_proj"),
+    "glm_moe_dsa": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "lfm2_moe": ("feed_forward", "w1", "w3", "w2"),
     "qwen3_5_moe_text": ("mlp", "gate_proj", "up_proj", "down_proj"),
     "olmoe": ("mlp", "gate_proj", "up_proj", "down_proj"),
@@ -65,7 +66,7 @@ def whole_bank_source(name: str, cfg, first_layer: int = 0):
     }.get(m.group(2))
 # how a family names its always-on shared feed-forward block
 SHARED_EXPERT_NAMES = {"glm4_moe": "shared_experts", "deepseek_v3": "shared_experts", "mistral4": "shared_experts",
-                       "glm4_moe_lite": "shared_experts"}
+                       "glm4_moe_lite": "shared_experts", "glm_moe_dsa": "shared_experts"}
 
 
 LAYER_NORMS = ("input_layernorm", "post_attention_layernorm", "pre_feedforward_layernorm", "post_feedforward_layernorm")
@@ -150,7 +151,11 @@ def _common_runtime_to_hub(name: str, tensor: torch.Tensor, cfg, first_layer: in
         return {pre + "self_attn.o_proj.weight": tensor}
     latent = {"self_attn.q_a_proj": "q_a_proj.weight", "self_attn.q_a_norm": "q_a_layernorm.weight", "self_attn.q_b_proj": "q_b_proj.weight",
               "self_attn.q_proj": "q_proj.weight", "self_attn.kv_a_proj": "kv_a_proj_with_mqa.weight",
-              "self_attn.kv_a_norm": "kv_a_layernorm.weight", "self_attn.kv_b_proj": "kv_b_proj.weight"}
+              "self_attn.kv_a_norm": "kv_a_layernorm.weight", "self_attn.kv_b_proj": "kv_b_proj.weight",
+              # the key-selecting indexer of sparse latent attention
+              "self_attn.indexer_wq_b": "indexer.wq_b.weight", "self_attn.indexer_wk": "indexer.wk.weight",
+              "self_attn.indexer_k_norm": "indexer.k_norm.weight", "self_attn.indexer_k_norm_bias": "indexer.k_norm.bias",
+              "self_attn.indexer_weights_proj": "indexer.weights_proj.weight"}
     if rest in latent:          # multi-head latent attention (DeepSeek)
         return {pre + "self_attn." + latent[rest]: tensor}
     conv = {"self_attn.conv_in_proj": "conv.in_proj.weight", "self_attn.conv_taps": "conv.conv.weight",

@@ -44,6 +44,9 @@ FAMILIES = {
     "deepseek_v3": dict(architecture="DeepseekV3ForCausalLM", moe=True, qk_norm=False, bias_key=True, bias_default=False, has_window=False),
     # GLM-4.7-Flash: the DeepSeek-V3 block with its dense layers named one by one (``mlp_layer_types``)
     "glm4_moe_lite": dict(architecture="Glm4MoeLiteForCausalLM", moe=True, qk_norm=False, bias_key=True, bias_default=False, has_window=False),
+    # GLM-5 (DSA): the GLM-4.7-Flash block whose attention sees, per query, only the ``index_topk`` keys a small indexer
+    # ranks highest; rotary pairs stored in halves, plain softmax scale
+    "glm_moe_dsa": dict(architecture="GlmMoeDsaForCausalLM", moe=True, qk_norm=False, bias_key=True, bias_default=False, has_window=False),
     # Mistral 4: the DeepSeek-V3 block (latent attention, shared experts, group-limited routing) with softmax router
     # scores, expert banks stored whole, and queries scaled by 1 + beta * log(1 + floor(position / period))
     "mistral4": dict(architecture="Mistral4ForCausalLM", moe=True, qk_norm=False, bias_key=True, bias_default=False, has_window=False),
@@ -89,6 +92,9 @@ class ModelConfig:
     topk_group: int = 1
     routed_scaling_factor: float = 1.0
     norm_topk_eps: float = 1e-20           # added to the sum the chosen weights are divided by (group-limited path)
+    index_topk: int = 0                    # > 0: sparse attention - an indexer picks this many keys per query (GLM-5 / DeepSeek-V3.2 style)
+    index_n_heads: int = 0
+    index_head_dim: int = 0
     attn_output_gate: bool = False         # attention output times sigmoid(gate); the gate rides in the query projection (Qwen3-Next)
     linear_num_key_heads: int = 0          # gated delta-rule layers (``layer_types`` entry "linear_attention"): heads and widths
     linear_num_value_heads: int = 0
@@ -168,6 +174,9 @@ class ModelConfig:
             q_side = (H * self.q_lora_rank + self.q_lora_rank + self.q_lora_rank * Hq * dqk) if self.q_lora_rank else H * Hq * dqk
             attn = (q_side + H * (self.kv_lora_rank + self.qk_rope_head_dim) + self.kv_lora_rank
                     + self.kv_lora_rank * Hq * (self.qk_nope_head_dim + self.v_head_dim) + Hq * self.v_head_dim * H + 2 * H)
+            if self.index_topk:
+                attn += (self.q_lora_rank * self.index_n_heads * self.index_head_dim + H * self.index_head_dim + 2 * self.index_head_dim
+                         + H * self.index_n_heads)
         else:
             attn = (H * self.qkv_dim + self.num_attention_heads * D * H + (norm_width if self.use_qk_norm else 0) + 2 * H
                     + (2 * H if self.sandwich_norms else 0) + (self.qkv_dim if self.attention_bias else 0) + (H if self.output_bias else 0)
@@ -281,11 +290,11 @@ class ModelConfig:
                       "output_router_logits": False, "swiglu_limit": self.glu_limit,
                       "layer_types": list(self.layer_types or ["sliding_attention" if self.sliding_window else "full_attention"]
                                           * self.num_hidden_layers)})
-        elif self.family in ("glm4_moe", "deepseek_v3", "mistral4", "glm4_moe_lite"):
+        elif self.family in ("glm4_moe", "deepseek_v3", "mistral4", "glm4_moe_lite", "glm_moe_dsa"):
             first_dense = 0
             while first_dense in self.mlp_only_layers:
                 first_dense += 1
-            if self.family != "glm4_moe_lite" and sorted(self.mlp_only_layers) != list(range(first_dense)):
+            if self.family not in ("glm4_moe_lite", "glm_moe_dsa") and sorted(self.mlp_only_layers) != list(range(first_dense)):
                 raise ValueError("glm4_moe stores its dense layers as a leading run (first_k_dense_replace)")
             d.update({"moe_intermediate_size": self.moe_intermediate_size, "n_routed_experts": self.num_experts,
                       "num_experts_per_tok": self.num_experts_per_tok, "norm_topk_prob": self.norm_topk_prob,
@@ -302,7 +311,12 @@ class ModelConfig:
                           "qk_nope_head_dim": self.qk_nope_head_dim, "qk_rope_head_dim": self.qk_rope_head_dim,
                           "v_head_dim": self.v_head_dim, "rope_interleave": self.rope_interleave,
                           "head_dim": self.qk_rope_head_dim})
-                if self.family == "glm4_moe_lite":
+                if self.family == "glm_moe_dsa":
+                    if self.rope_interleave:
+                        raise ValueError("glm_moe_dsa stores its rotary pairs in halves (rope_interleave False)")
+                    d.pop("rope_interleave")
+                    d.update({"index_topk": self.index_topk, "index_n_heads": self.index_n_heads, "index_head_dim": self.index_head_dim})
+                if self.family in ("glm4_moe_lite", "glm_moe_dsa"):
                     d.pop("first_k_dense_replace")
                     d["mlp_layer_types"] = ["dense" if i in self.mlp_only_layers else "sparse" for i in range(self.num_hidden_layers)]
                 if self.family == "mistral4":
@@ -411,7 +425,7 @@ class ModelConfig:
                 scaling = None
         hd = d.get("head_dim") or d["hidden_size"] // d["num_attention_heads"]
         extra = {}
-        if mt in ("deepseek_v3", "mistral4", "glm4_moe_lite"):
+        if mt in ("deepseek_v3", "mistral4", "glm4_moe_lite", "glm_moe_dsa"):
             n_exp, width, dense_width = d["n_routed_experts"], d["moe_intermediate_size"], d["intermediate_size"]
             topk, renorm = d.get("num_experts_per_tok", 8 if mt == "deepseek_v3" else 4), d.get("norm_topk_prob", True)
             hd = int(d.get("qk_rope_head_dim", 64))            # the rotary table is built for the rotary slice
@@ -427,11 +441,15 @@ class ModelConfig:
             extra = dict(**routing, n_group=int(d.get("n_group", 1)),
                          topk_group=int(d.get("topk_group", 1)), routed_scaling_factor=float(d.get("routed_scaling_factor", 1.0)),
                          shared_expert_intermediate_size=int(d.get("n_shared_experts", 0) or 0) * width,
-                         mlp_only_layers=([i for i, kind in enumerate(d.get("mlp_layer_types") or ["dense"] + ["sparse"] * (d["num_hidden_layers"] - 1))
-                                           if kind == "dense"] if mt == "glm4_moe_lite" else list(range(int(d.get("first_k_dense_replace", 0))))),
+                         mlp_only_layers=([i for i, kind in enumerate(d.get("mlp_layer_types") or (["dense"] + ["sparse"] * (d["num_hidden_layers"] - 1) if mt == "glm4_moe_lite" else
+                                                                                                   ["dense"] * min(3, d["num_hidden_layers"]) + ["sparse"] * max(d["num_hidden_layers"] - 3, 0)))
+                                           if kind == "dense"] if mt in ("glm4_moe_lite", "glm_moe_dsa") else list(range(int(d.get("first_k_dense_replace", 0))))),
                          use_qk_norm=False, kv_lora_rank=int(d["kv_lora_rank"]), q_lora_rank=int(d.get("q_lora_rank") or 0),
                          qk_nope_head_dim=int(d["qk_nope_head_dim"]), qk_rope_head_dim=hd, v_head_dim=int(d["v_head_dim"]),
-                         rope_interleave=bool(d.get("rope_interleave", True)))
+                         rope_interleave=bool(d.get("rope_interleave", mt != "glm_moe_dsa")))
+            if mt == "glm_moe_dsa":
+                extra.update(index_topk=int(d.get("index_topk", 2048)), index_n_heads=int(d.get("index_n_heads", 32)),
+                             index_head_dim=int(d.get("index_head_dim", 128)))
         elif mt in ("qwen3_next", "qwen3_5_moe_text"):
             n_exp, width, dense_width = d.get("num_experts", 0), d.get("moe_intermediate_size", 0), d.get("intermediate_size", 0)
             topk, renorm = d.get("num_experts_per_tok", 10), d.get("norm_topk_prob", True)

@@ -59,15 +59,49 @@ class LatentAttention(nn.Module):
         self.kv_a_norm = nn.Parameter(torch.ones(cfg.kv_lora_rank, dtype=dtype, device=device))
         self.kv_b_proj = matrix(Hq * (self.nope + self.v_dim), cfg.kv_lora_rank)
         self.o_proj = matrix(H, Hq * self.v_dim)
+        if cfg.index_topk:
+            # sparse attention: a small indexer ranks the keys of every query and attention sees the best ``index_topk``.
+            # The ranking is a hard choice (no gradient reaches these tensors through the loss), so they are held fixed
+            if not cfg.q_lora_rank:
+                raise ValueError("the indexer reads the low-rank query state: it needs q_lora_rank > 0")
+            Hi, Di = cfg.index_n_heads, cfg.index_head_dim
+            self.indexer_wq_b = matrix(Hi * Di, cfg.q_lora_rank)
+            self.indexer_wk = matrix(Di, H)
+            self.indexer_k_norm = nn.Parameter(torch.ones(Di, dtype=dtype, device=device))
+            self.indexer_k_norm_bias = nn.Parameter(torch.zeros(Di, dtype=dtype, device=device))
+            self.indexer_weights_proj = matrix(Hi, H)
+            for p in (self.indexer_wq_b, self.indexer_wk, self.indexer_k_norm, self.indexer_k_norm_bias, self.indexer_weights_proj):
+                p.requires_grad_(False)
         self.window, self.sinks, self.lora, self.lowp = 0, None, None, ""
         # yarn: the softmax temperature grows with the context extension (squared: it scales q and k); Mistral 4 keeps
         # the plain scale and stretches its queries by position instead (``ctx.query_scale``)
         self.scale = self.qk_dim ** -0.5
         rs = cfg.rope_scaling or {}
-        if cfg.family != "mistral4" and rs.get("rope_type", rs.get("type", "default")) != "default" and rs.get("mscale_all_dim"):
+        if cfg.family not in ("mistral4", "glm_moe_dsa") and rs.get("rope_type", rs.get("type", "default")) != "default" and rs.get("mscale_all_dim"):
             factor = float(rs["factor"])
             m = 1.0 if factor <= 1.0 else 0.1 * float(rs["mscale_all_dim"]) * math.log(factor) + 1.0
             self.scale *= m * m
+
+    @torch.no_grad()
+    def selected_keys(self, h, q_low, rope, mask):
+        """``[T, T]`` bool: for every query, the ``index_topk`` visible keys with the highest indexer score
+
+            score[s, t] = sum over indexer heads of  weight[s, head] * relu(q[s, head] . k[t]) / sqrt(width)
+
+        (all visible keys when there are fewer). The indexer turns the LEADING ``rope`` dims of its queries and of its one
+        key per token, pairs stored in halves."""
+        cfg = self.cfg
+        T, Hi, Di, R = h.shape[0], cfg.index_n_heads, cfg.index_head_dim, self.rope_dim
+        q = gemm.linear(q_low, self.indexer_wq_b).reshape(T, Hi, Di)
+        k = torch.nn.functional.layer_norm(gemm.linear(h, self.indexer_wk).float(), (Di,), self.indexer_k_norm.float(),
+                                           self.indexer_k_norm_bias.float(), 1e-6).to(h.dtype)
+        q = torch.cat([rotate(q[..., :R], rope, False), q[..., R:]], dim=-1)
+        k = torch.cat([rotate(k[:, None, :R], rope, False)[:, 0], k[:, R:]], dim=-1)
+        weights = gemm.linear(h, self.indexer_weights_proj).float() * Hi ** -0.5
+        scores = torch.relu(torch.einsum("shd,td->sht", q.float(), k.float()) * Di ** -0.5)
+        ranked = torch.einsum("sht,sh->st", scores, weights).masked_fill(~mask, float("-inf"))
+        top = ranked.topk(min(cfg.index_topk, T), dim=-1).indices
+        return torch.zeros_like(mask).scatter_(1, top, True) & mask
 
     def forward(self, h, ctx):
         from halo_b200.ops.masked_attention import masked_attention, window_mask
@@ -76,8 +110,10 @@ class LatentAttention(nn.Module):
         if ctx.cp is not None or ctx.tp is not None:
             raise NotImplementedError("latent attention runs on unsliced rows")
         T, Hq = h.shape[0], cfg.num_attention_heads
+        q_low = None
         if cfg.q_lora_rank:
-            q = gemm.linear(rms_norm(gemm.linear(h, self.q_a_proj), self.q_a_norm, cfg.rms_norm_eps), self.q_b_proj)
+            q_low = rms_norm(gemm.linear(h, self.q_a_proj), self.q_a_norm, cfg.rms_norm_eps)
+            q = gemm.linear(q_low, self.q_b_proj)
         else:
             q = gemm.linear(h, self.q_proj)
         q = q.reshape(T, Hq, self.qk_dim)
@@ -98,6 +134,9 @@ class LatentAttention(nn.Module):
             # generation: the expanded keys and padded values of this layer go to the cache; a decode step reads it
             li = cache.write(k.reshape(T, Hq * self.qk_dim), v.reshape(T, Hq * self.qk_dim))
             if cache.mode != "prefill":
+                if cfg.index_topk and cache.k.shape[2] > cfg.index_topk:
+                    raise NotImplementedError(f"cached decoding past index_topk ({cfg.index_topk}) keys: the indexer's key cache is "
+                                              "not built; up to that length every key is selected and decoding is exact")
                 o = cache.attend(li, q.reshape(T, Hq * self.qk_dim), Hq, scale=self.scale).reshape(T, Hq, self.qk_dim)
                 return gemm.linear(o[..., :self.v_dim].reshape(T, Hq * self.v_dim), self.o_proj)
         mask = getattr(ctx, "attention_mask", None)
@@ -107,5 +146,7 @@ class LatentAttention(nn.Module):
             mask = ctx.causal
         elif mask.device != h.device:
             mask = ctx.attention_mask = mask.to(h.device)
+        if cfg.index_topk:
+            mask = self.selected_keys(h, q_low, ctx.rope, mask)
         o = masked_attention(q, k, v.contiguous(), mask, scale=self.scale)[..., :self.v_dim]
         return gemm.linear(o.reshape(T, Hq * self.v_dim), self.o_proj)

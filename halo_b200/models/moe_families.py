@@ -68,11 +68,13 @@ for _s in (
                   shared_experts=True, runnable=True),
     MoEFamilySpec("glm4_moe_lite", SEPARATE_GLU, score_function="sigmoid", selection_bias=True, grouped_topk=True, routed_scaling_factor=1.8,
                   shared_experts=True, runnable=True),
+    MoEFamilySpec("glm_moe_dsa", SEPARATE_GLU, score_function="sigmoid", selection_bias=True, grouped_topk=True, routed_scaling_factor=2.5,
+                  shared_experts=True, runnable=True),
     MoEFamilySpec("glm5_next", SEPARATE_GLU, score_function="sigmoid", selection_bias=True, shared_experts=True,
-                  missing="sparse (DSA) attention, hyper-connections"),
-    MoEFamilySpec("gemma4", FUSED, activation="gelu_tanh", missing="sliding/global attention mix, logit soft-capping"),
+                  missing="its checkpoint names (sparse attention behind an indexer and hyper-connections are built: see glm_moe_dsa and hc_mult)"),
+    MoEFamilySpec("gemma4", FUSED, activation="gelu_tanh", missing="per-layer head widths, keys / values shared between layers, per-layer input embeddings and the dense block beside the experts (the sliding / full mix and soft-capping are built: see gemma3_text)"),
     MoEFamilySpec("bailing_moe", SEPARATE_GLU, score_function="sigmoid", selection_bias=True, grouped_topk=True,
-                  shared_experts=True, missing="grouped top-k routing"),
+                  shared_experts=True, missing="its checkpoint names (group-limited sigmoid routing with a stored bias and shared experts are built: see glm4_moe)"),
     MoEFamilySpec("cohere2_moe", SEPARATE_GLU, missing="parallel attention/FFN block, layer norm"),
     MoEFamilySpec("inkling", SEPARATE_GLU, missing="family decoder"),
     MoEFamilySpec("laguna", SEPARATE_GLU, missing="family decoder"),
@@ -83,7 +85,7 @@ for _s in (
     MoEFamilySpec("mixtral", SEPARATE_MLP, router_name="block_sparse_moe.gate", experts_prefix="block_sparse_moe.experts",
                   runnable=True),
     MoEFamilySpec("nemotron_h", SEPARATE_MLP, score_function="sigmoid", shared_experts=True, activation="relu2",
-                  missing="Mamba-2 mixer layers, non-gated experts"),
+                  missing="Mamba-2 mixer layers, one block per layer, non-gated experts (document-bounded convolutions and a chunked state recurrence are built: see qwen3_next)"),
     MoEFamilySpec("step3p7", SEPARATE_GLU, shared_experts=True, missing="family decoder"),
     MoEFamilySpec("zaya", SEPARATE_GLU, missing="compressed-convolution attention"),
 ):

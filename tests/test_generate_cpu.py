@@ -75,6 +75,13 @@ def linear_cfg():
                        linear_conv_kernel_dim=4, max_position_embeddings=64)
 
 
+def sparse_cfg():
+    """GLM-5 (DSA) style: latent attention behind a key-selecting indexer; up to ``index_topk`` keys every key is selected,
+    so cached decoding is exact."""
+    return dataclasses.replace(latent_cfg(), model_type="glm_moe_dsa", rope_interleave=False, index_topk=32, index_n_heads=2,
+                               index_head_dim=20)
+
+
 def gemma_cfg():
     """Gemma 3 style: windowed layers with their own rotary base, a full layer, output norms, tanh-GELU gate, scaled embeddings."""
     return dataclasses.replace(dense_cfg(), model_type="gemma3_text", num_hidden_layers=3, sliding_window=6, max_position_embeddings=64,
@@ -89,9 +96,9 @@ def capped_cfg():
                                use_qk_norm=False, rope_local_theta=0.0, attn_logit_softcapping=1.0, final_logit_softcapping=0.5)
 
 
-@pytest.mark.parametrize("kind", ["dense", "moe", "windowed", "sinks", "latent", "stretched", "conv", "linear", "gemma", "capped"])
+@pytest.mark.parametrize("kind", ["dense", "moe", "windowed", "sinks", "latent", "stretched", "sparse", "conv", "linear", "gemma", "capped"])
 def test_cached_decoding_equals_the_full_forward(kind):
-    cfg = {"dense": dense_cfg, "windowed": windowed_cfg, "sinks": sink_cfg, "latent": latent_cfg, "stretched": stretched_cfg, "conv": conv_cfg, "linear": linear_cfg, "gemma": gemma_cfg, "capped": capped_cfg,
+    cfg = {"dense": dense_cfg, "windowed": windowed_cfg, "sinks": sink_cfg, "latent": latent_cfg, "stretched": stretched_cfg, "sparse": sparse_cfg, "conv": conv_cfg, "linear": linear_cfg, "gemma": gemma_cfg, "capped": capped_cfg,
            "moe": lambda: dataclasses.replace(tiny_moe_config(), num_hidden_layers=2, vocab_size=128)}[kind]()
     model = build_model(cfg, device="cpu", seed=7, gradient_checkpointing=False)
     if kind == "conv":
