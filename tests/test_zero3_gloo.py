@@ -112,3 +112,27 @@ def test_sharded_layers_under_the_lighter_recomputation_policy(moe):
     parameters are gathered for the first pass, and again from the re-run of the second half until the backward of the
     first; what the attention half saved is read through the parameters bound in that second window."""
     run_gloo_ranks(_worker, 2, args=(moe, None, 2), timeout=240.0)
+
+
+def _family_worker(rank, world, family, out_dir):
+    import dataclasses
+
+    import halo_b200.models.config as config_module
+    from tests.test_families_cpu import family_config
+
+    # the training helper builds the "tiny-moe" preset: stand the family's small configuration in its place
+    config_module.PRESETS["tiny-moe"] = lambda: dataclasses.replace(family_config(family), vocab_size=256)
+    want_l, want_w = _train(rank, world, False, True)
+    got_l, got_w = _train(rank, world, True, True, out_dir)
+    for a, b in zip(want_l, got_l):
+        assert abs(a - b) <= 1e-4 * max(1.0, abs(a)), (want_l, got_l)
+    assert set(got_w) == set(want_w), set(got_w) ^ set(want_w)
+    for n in want_w:
+        assert float((got_w[n] - want_w[n]).abs().max()) < 2e-3, n
+
+
+@pytest.mark.parametrize("family", ["qwen3_next", "lfm2_moe"])
+def test_sharded_layers_of_mixer_families(family, tmp_path):
+    """Layers whose mixer is a convolution or a linear-attention block (three-dimensional tap tensors, per-head vectors)
+    shard, train, save and reload like attention layers, with the experts cut over the same two ranks."""
+    run_gloo_ranks(_family_worker, 2, args=(family, str(tmp_path / "ckpt")), timeout=400.0)
